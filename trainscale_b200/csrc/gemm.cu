@@ -1,0 +1,322 @@
+// bf16 GEMM for sm_100a: C[M,N] = alpha * sum_k A[m,k] * B[n,k] (+ C), fp32 accumulation in TMEM.
+//
+// Design (one CTA per SM, persistent over output tiles):
+//   warp 0      TMA producer   - streams 128x64 A tiles and BNx64 B tiles into a STAGES-deep shared-memory ring
+//                                (128-byte swizzle, plain non-multicast tiled loads)
+//   warp 1      MMA issuer     - one elected thread issues tcgen05.mma (128 x BN x 16) into one of two TMEM
+//                                accumulators, tcgen05.commit releases ring slots / publishes the accumulator
+//   warps 2..5  epilogue       - tcgen05.ld the finished accumulator (each warp owns its 32 TMEM lanes),
+//                                scale / add / convert and store with 16-byte vector stores, while the MMA
+//                                warp already works on the next tile in the other accumulator
+// Operands may be K-major or MN-major in memory, so forward (X W^T), dgrad (dY W) and wgrad (dY^T X)
+// all run without a transpose pass.
+//
+// Replaces the library GEMMs behind F.linear in the reference
+// (data_pipeline/trainer/distributed/tensor_parallel.py:1061,1214) and the zero-bubble split-backward
+// GEMMs (data_pipeline/trainer/distributed/zbpp.py:202,232).
+#include "common.cuh"
+#include "host_common.h"
+
+namespace ts {
+
+constexpr int GEMM_BM = 128;
+constexpr int GEMM_BK = 64;
+constexpr int GEMM_THREADS = 192;
+constexpr int GEMM_GROUP_M = 8;
+
+struct GemmParams {
+  int M, N, K;
+  int ldc;
+  int a_mn, b_mn;       // 0 = K-major operand, 1 = MN-major operand
+  int out_fp32;         // C dtype: 0 = bf16, 1 = fp32
+  int accumulate;       // 1: C = alpha*acc + C
+  float alpha;
+  void* C;
+  int num_m_tiles, num_n_tiles, k_blocks;
+};
+
+template <int BN>
+struct GemmSmem {
+  static constexpr int STAGES = (BN == 256) ? 4 : (BN == 128 ? 6 : 8);
+  static constexpr int A_BYTES = GEMM_BM * GEMM_BK * 2;   // 16 KiB
+  static constexpr int B_BYTES = BN * GEMM_BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int BAR_BYTES = 256;
+  static constexpr int TOTAL = STAGES * STAGE_BYTES + BAR_BYTES + 1024;   // + alignment slack
+};
+
+template <int BN>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmParams p) {
+  using S = GemmSmem<BN>;
+  constexpr int STAGES = S::STAGES;
+  constexpr uint32_t TMEM_COLS = (2 * BN <= 32) ? 32 : 2 * BN;   // two accumulators
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* smem_a = smem;
+  uint8_t* smem_b = smem + STAGES * S::A_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * S::STAGE_BYTES);
+  uint64_t* full_bar = bars;                    // [STAGES]
+  uint64_t* empty_bar = bars + STAGES;          // [STAGES]
+  uint64_t* tfull_bar = bars + 2 * STAGES;      // [2]
+  uint64_t* tempty_bar = bars + 2 * STAGES + 2; // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    mbar_init(&tfull_bar[0], 1);
+    mbar_init(&tfull_bar[1], 1);
+    mbar_init(&tempty_bar[0], 4);
+    mbar_init(&tempty_bar[1], 4);
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+    tc_fence_before_sync();
+  }
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int num_tiles = p.num_m_tiles * p.num_n_tiles;
+  const int tiles_per_group = GEMM_GROUP_M * p.num_n_tiles;
+  bool alive = true;
+
+  auto tile_coords = [&](int t, int& m0, int& n0) {
+    const int g = t / tiles_per_group;
+    const int first_m = g * GEMM_GROUP_M;
+    const int gsz = min(p.num_m_tiles - first_m, GEMM_GROUP_M);
+    const int r = t - g * tiles_per_group;
+    m0 = (first_m + (r % gsz)) * GEMM_BM;
+    n0 = (r / gsz) * BN;
+  };
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (elect_one_sync()) {
+      uint32_t it = 0;
+      for (int t = blockIdx.x; t < num_tiles && alive; t += gridDim.x) {
+        int m0, n0;
+        tile_coords(t, m0, n0);
+        for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1u;
+          if (!mbar_wait(&empty_bar[s], ph ^ 1u, alive, 100)) break;
+          mbar_expect_tx(&full_bar[s], S::STAGE_BYTES);
+          uint8_t* a_dst = smem_a + s * S::A_BYTES;
+          uint8_t* b_dst = smem_b + s * S::B_BYTES;
+          const int k0 = kb * GEMM_BK;
+          if (!p.a_mn) {
+            tma_load_2d(a_dst, &tmA, &full_bar[s], k0, m0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < GEMM_BM / 64; ++j) tma_load_2d(a_dst + j * 8192, &tmA, &full_bar[s], m0 + j * 64, k0);
+          }
+          if (!p.b_mn) {
+            tma_load_2d(b_dst, &tmB, &full_bar[s], k0, n0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j) tma_load_2d(b_dst + j * 8192, &tmB, &full_bar[s], n0 + j * 64, k0);
+          }
+        }
+      }
+      if (!alive) {
+        // tear-down after a failed wait: give the loads that are still in flight a bounded time to land
+        const uint32_t first = it > (uint32_t)STAGES ? it - STAGES : 0u;
+        for (uint32_t i = first; i < it; ++i) {
+          const long long t0 = clock64();
+          while (!mbar_try_wait(&full_bar[i % STAGES], (i / STAGES) & 1u) && clock64() - t0 < 2000000ll) {
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer ------------------------------
+    if (elect_one_sync()) {
+      const uint32_t idesc = make_idesc(GEMM_BM, BN, 1, 1, (uint32_t)p.a_mn, (uint32_t)p.b_mn);
+      const uint32_t a_kstep = p.a_mn ? 2048u : 32u;
+      const uint32_t b_kstep = p.b_mn ? 2048u : 32u;
+      const uint32_t a_lbo = p.a_mn ? 8192u : 16u;
+      const uint32_t b_lbo = p.b_mn ? 8192u : 16u;
+      uint32_t it = 0, tile_it = 0;
+      for (int t = blockIdx.x; t < num_tiles && alive; t += gridDim.x, ++tile_it) {
+        const uint32_t acc = tile_it & 1u;
+        const uint32_t acc_ph = (tile_it >> 1) & 1u;
+        if (!mbar_wait(&tempty_bar[acc], acc_ph ^ 1u, alive, 200)) break;
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1u;
+          if (!mbar_wait(&full_bar[s], ph, alive, 201)) break;
+          tc_fence_after_sync();
+          const uint32_t a_addr = smem_u32(smem_a + s * S::A_BYTES);
+          const uint32_t b_addr = smem_u32(smem_b + s * S::B_BYTES);
+#pragma unroll
+          for (int k = 0; k < GEMM_BK / 16; ++k) {
+            const uint64_t ad = make_smem_desc_sw128(a_addr + k * a_kstep, a_lbo, 1024);
+            const uint64_t bd = make_smem_desc_sw128(b_addr + k * b_kstep, b_lbo, 1024);
+            umma_f16_ss(d_tmem, ad, bd, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[s]);   // slot is free once these MMAs have read it
+        }
+        if (!alive) break;
+        umma_commit(&tfull_bar[acc]);   // accumulator complete
+      }
+    }
+  } else {
+    // ------------------------------ epilogue (warps 2..5) ------------------------------
+    const int q = warp & 3;   // TMEM lane quarter this warp may access
+    uint32_t tile_it = 0;
+    for (int t = blockIdx.x; t < num_tiles && alive; t += gridDim.x, ++tile_it) {
+      int m0, n0;
+      tile_coords(t, m0, n0);
+      const uint32_t acc = tile_it & 1u;
+      const uint32_t acc_ph = (tile_it >> 1) & 1u;
+      if (!mbar_wait(&tfull_bar[acc], acc_ph, alive, 300)) break;
+      tc_fence_after_sync();
+      const int row = m0 + q * 32 + lane;
+      const uint32_t t_row = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(t_row + c * 32, r);
+        tc_wait_ld();
+        const int col0 = n0 + c * 32;
+        if (row < p.M && col0 < p.N) {
+          const bool full = (col0 + 32 <= p.N);
+          if (p.out_fp32) {
+            float* dst = reinterpret_cast<float*>(p.C) + static_cast<size_t>(row) * p.ldc + col0;
+            if (full && ((reinterpret_cast<uintptr_t>(dst) & 15u) == 0)) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                float4 v = make_float4(__uint_as_float(r[4 * j]) * p.alpha, __uint_as_float(r[4 * j + 1]) * p.alpha,
+                                       __uint_as_float(r[4 * j + 2]) * p.alpha, __uint_as_float(r[4 * j + 3]) * p.alpha);
+                if (p.accumulate) {
+                  const float4 o = *reinterpret_cast<const float4*>(dst + 4 * j);
+                  v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
+                }
+                *reinterpret_cast<float4*>(dst + 4 * j) = v;
+              }
+            } else {
+              for (int j = 0; j < 32 && col0 + j < p.N; ++j) {
+                float v = __uint_as_float(r[j]) * p.alpha;
+                if (p.accumulate) v += dst[j];
+                dst[j] = v;
+              }
+            }
+          } else {
+            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<size_t>(row) * p.ldc + col0;
+            if (full && ((reinterpret_cast<uintptr_t>(dst) & 15u) == 0)) {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                float f[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(r[8 * j + e]) * p.alpha;
+                if (p.accumulate) {
+                  const uint4 o = *reinterpret_cast<const uint4*>(dst + 8 * j);
+                  const float2 o0 = unpack_bf16x2(o.x), o1 = unpack_bf16x2(o.y), o2 = unpack_bf16x2(o.z),
+                               o3 = unpack_bf16x2(o.w);
+                  f[0] += o0.x; f[1] += o0.y; f[2] += o1.x; f[3] += o1.y;
+                  f[4] += o2.x; f[5] += o2.y; f[6] += o3.x; f[7] += o3.y;
+                }
+                uint4 v;
+                v.x = pack_bf16x2(f[0], f[1]);
+                v.y = pack_bf16x2(f[2], f[3]);
+                v.z = pack_bf16x2(f[4], f[5]);
+                v.w = pack_bf16x2(f[6], f[7]);
+                *reinterpret_cast<uint4*>(dst + 8 * j) = v;
+              }
+            } else {
+              for (int j = 0; j < 32 && col0 + j < p.N; ++j) {
+                float v = __uint_as_float(r[j]) * p.alpha;
+                if (p.accumulate) v += __bfloat162float(dst[j]);
+                dst[j] = __float2bfloat16(v);
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+template <int BN>
+static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, cudaStream_t stream) {
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         GemmSmem<BN>::TOTAL);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  const int tiles = p.num_m_tiles * p.num_n_tiles;
+  const int grid = tiles < sm_count() ? tiles : sm_count();
+  gemm_bf16_kernel<BN><<<grid, GEMM_THREADS, GemmSmem<BN>::TOTAL, stream>>>(tmA, tmB, p);
+  return (int)cudaGetLastError();
+}
+
+}  // namespace ts
+
+TS_DEFINE_ERROR_API(ts_gemm)
+
+// C[M,N] = alpha * A . B^T (+ C).
+//   a_mn == 0: A is stored [M][lda] (K contiguous);   a_mn == 1: A is stored [K][lda] (M contiguous)
+//   b_mn == 0: B is stored [N][ldb] (K contiguous);   b_mn == 1: B is stored [K][ldb] (N contiguous)
+//   out_fp32: C is fp32 (else bf16); accumulate: add into the existing C.
+//   bn: N tile (256, 128 or 64; 0 = choose).
+// Leading dimensions are in elements and must keep rows 16-byte aligned. Returns 0 on success.
+extern "C" int ts_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc,
+                            int a_mn, int b_mn, int out_fp32, int accumulate, float alpha, int bn, void* stream) {
+  using namespace ts;
+  if (M <= 0 || N <= 0 || K <= 0) return -10;
+  if (bn == 0) {
+    // prefer the widest tile that still gives every SM work
+    const int tiles256 = ((M + 127) / 128) * ((N + 255) / 256);
+    bn = (N >= 256 && tiles256 >= sm_count()) ? 256 : (N >= 128 ? 128 : 64);
+    if (N >= 256 && tiles256 < sm_count() && ((M + 127) / 128) * ((N + 127) / 128) < tiles256 * 2) bn = 128;
+  }
+  if (bn != 256 && bn != 128 && bn != 64) return -11;
+  CUtensorMap tmA, tmB;
+  int rc;
+  if (!a_mn)
+    rc = make_tmap_2d(&tmA, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)M, (uint64_t)K, (uint64_t)lda, GEMM_BM, 64);
+  else
+    rc = make_tmap_2d(&tmA, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)K, (uint64_t)M, (uint64_t)lda, 64, 64);
+  if (rc) return rc * 100 - 1;
+  if (!b_mn)
+    rc = make_tmap_2d(&tmB, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, (uint32_t)bn, 64);
+  else
+    rc = make_tmap_2d(&tmB, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, 64, 64);
+  if (rc) return rc * 100 - 2;
+  GemmParams p;
+  p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.a_mn = a_mn; p.b_mn = b_mn; p.out_fp32 = out_fp32;
+  p.accumulate = accumulate; p.alpha = alpha; p.C = C;
+  p.num_m_tiles = (M + GEMM_BM - 1) / GEMM_BM;
+  p.num_n_tiles = (N + bn - 1) / bn;
+  p.k_blocks = (K + GEMM_BK - 1) / GEMM_BK;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (bn == 256) return launch_gemm<256>(tmA, tmB, p, st);
+  if (bn == 128) return launch_gemm<128>(tmA, tmB, p, st);
+  return launch_gemm<64>(tmA, tmB, p, st);
+}

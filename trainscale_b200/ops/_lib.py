@@ -1,0 +1,66 @@
+"""ctypes loader for the in-tree CUDA libraries.
+
+A library is loaded on first use.  On a machine with a GPU a missing library is an error (the CUDA
+path must be the one that runs); on a CPU-only machine the callers use their PyTorch reference math.
+"""
+from __future__ import annotations
+
+import ctypes
+import functools
+
+import torch
+
+from .build import build_all, lib_path
+
+_ERR_NAMES = {0: "none", 1: "mbarrier wait timed out", 2: "flag wait timed out", 3: "bad argument", 4: "tmem"}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def cuda_available() -> bool:
+    return torch.cuda.is_available()
+
+
+@functools.lru_cache(maxsize=None)
+def load(name: str) -> ctypes.CDLL:
+    path = lib_path(name)
+    if not path.exists():
+        build_all()
+    if not path.exists():
+        raise KernelError(f"CUDA library {path} is missing; run `python -m trainscale_b200.ops.build`")
+    return ctypes.CDLL(str(path))
+
+
+def stream_ptr() -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def ptr(t: torch.Tensor | None) -> ctypes.c_void_p:
+    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+def check(rc: int, what: str) -> None:
+    if rc != 0:
+        raise KernelError(f"{what} failed with code {rc}")
+
+
+def device_error(name: str) -> tuple[int, int, int, int]:
+    """Read (and leave untouched) the error word of library `name`: (code, site, block, extra)."""
+    lib = load(name)
+    buf = (ctypes.c_uint * 4)()
+    getattr(lib, f"ts_{name}_get_error")(buf)
+    return tuple(int(x) for x in buf)
+
+
+def clear_device_error(name: str) -> None:
+    getattr(load(name), f"ts_{name}_clear_error")()
+
+
+def raise_on_device_error(name: str) -> None:
+    code, site, block, extra = device_error(name)
+    if code:
+        clear_device_error(name)
+        raise KernelError(f"{name} kernel reported '{_ERR_NAMES.get(code, code)}' at site {site} "
+                          f"(block {block}, extra {extra})")

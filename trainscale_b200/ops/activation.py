@@ -1,0 +1,63 @@
+"""Gated activations (SwiGLU / GeGLU) over a fused gate|up projection output.
+
+Reference: data_pipeline/trainer/kernels/triton_kernels.py:1042-1295.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+import torch.nn.functional as F
+
+from . import _lib
+
+_ACT = {"silu": 0, "swiglu": 0, "gelu": 1, "geglu": 1, "gelu_tanh": 2}
+
+
+def glu_reference(gate_up: torch.Tensor, act: str = "silu") -> torch.Tensor:
+    g, u = gate_up.float().chunk(2, dim=-1)
+    a = F.silu(g) if _ACT[act] == 0 else F.gelu(g, approximate="tanh" if _ACT[act] == 2 else "none")
+    return (a * u).to(gate_up.dtype)
+
+
+class _GluFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, gate_up, act):
+        lib = _lib.load("elementwise")
+        I = gate_up.shape[-1] // 2
+        gu = gate_up.reshape(-1, 2 * I)
+        gu = gu if gu.is_contiguous() else gu.contiguous()
+        out = torch.empty(gu.shape[0], I, dtype=gu.dtype, device=gu.device)
+        rc = lib.ts_glu_fwd(_lib.ptr(gu), _lib.ptr(out), ctypes.c_longlong(gu.shape[0]), I, 2 * I, act,
+                            _lib.stream_ptr())
+        _lib.check(rc, "ts_glu_fwd")
+        ctx.save_for_backward(gu)
+        ctx.act = act
+        ctx.in_shape = gate_up.shape
+        return out.view(*gate_up.shape[:-1], I)
+
+    @staticmethod
+    def backward(ctx, dout):
+        lib = _lib.load("elementwise")
+        (gu,) = ctx.saved_tensors
+        I = gu.shape[1] // 2
+        d = dout.reshape(-1, I)
+        d = d if d.is_contiguous() else d.contiguous()
+        dgu = torch.empty_like(gu)
+        rc = lib.ts_glu_bwd(_lib.ptr(d), _lib.ptr(gu), _lib.ptr(dgu), ctypes.c_longlong(gu.shape[0]), I, 2 * I,
+                            ctx.act, _lib.stream_ptr())
+        _lib.check(rc, "ts_glu_bwd")
+        return dgu.view(ctx.in_shape), None
+
+
+def glu(gate_up: torch.Tensor, act: str = "silu") -> torch.Tensor:
+    """act(gate) * up for gate_up = [..., gate | up]."""
+    I = gate_up.shape[-1] // 2
+    if gate_up.is_cuda and gate_up.dtype == torch.bfloat16 and I % 8 == 0:
+        return _GluFn.apply(gate_up, _ACT[act])
+    return glu_reference(gate_up, act)
+
+
+def swiglu(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """silu(gate) * up for separate tensors (API parity with the reference's swiglu_forward)."""
+    return glu(torch.cat((gate, up), dim=-1), "silu")

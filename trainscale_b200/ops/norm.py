@@ -1,0 +1,100 @@
+"""RMSNorm (optionally fused with the residual add) on the sm_100a kernels, with autograd.
+
+Reference behaviour: data_pipeline/trainer/kernels/triton_kernels.py:477-682 (forward stores rstd in fp32,
+backward dx = rstd*(dy*w - xhat*mean(dy*w*xhat)), dw = sum_rows dy*xhat) and the fused add+norm of
+data_pipeline/trainer/kernels/layernorm_kernels.py:496.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import _lib
+
+
+def rmsnorm_reference(x, w, eps=1e-5, residual=None, w_offset=0.0):
+    """fp32 PyTorch math; returns (y, new_residual)."""
+    h = x if residual is None else (x.float() + residual.float()).to(x.dtype)
+    hf = h.float()
+    y = hf * torch.rsqrt(hf.pow(2).mean(-1, keepdim=True) + eps) * (w.float() + w_offset)
+    return y.to(x.dtype), h
+
+
+class _RMSNormFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, residual, eps, w_offset):
+        lib = _lib.load("elementwise")
+        H = x.shape[-1]
+        x2 = x.reshape(-1, H)
+        x2 = x2 if x2.is_contiguous() else x2.contiguous()
+        rows = x2.shape[0]
+        y = torch.empty_like(x2)
+        rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
+        res_out = None
+        r2 = None
+        if residual is not None:
+            r2 = residual.reshape(-1, H)
+            r2 = r2 if r2.is_contiguous() else r2.contiguous()
+            res_out = torch.empty_like(x2)
+        rc = lib.ts_rmsnorm_fwd(_lib.ptr(x2), _lib.ptr(r2), _lib.ptr(w), _lib.ptr(y), _lib.ptr(res_out),
+                                _lib.ptr(rstd), ctypes.c_longlong(rows), H, ctypes.c_float(eps),
+                                ctypes.c_float(w_offset), _lib.stream_ptr())
+        _lib.check(rc, "ts_rmsnorm_fwd")
+        h = x2 if residual is None else res_out
+        ctx.save_for_backward(h, w, rstd)
+        ctx.w_offset = w_offset
+        ctx.has_res = residual is not None
+        ctx.shape = x.shape
+        if residual is None:
+            return y.view(x.shape), x
+        ctx.mark_non_differentiable()
+        return y.view(x.shape), res_out.view(x.shape)
+
+    @staticmethod
+    def backward(ctx, dy, dres):
+        lib = _lib.load("elementwise")
+        h, w, rstd = ctx.saved_tensors
+        rows, H = h.shape
+        dy2 = dy.reshape(rows, H)
+        dy2 = dy2 if dy2.is_contiguous() else dy2.contiguous()
+        dres2 = None
+        if dres is not None:
+            dres2 = dres.reshape(rows, H)
+            dres2 = dres2 if dres2.is_contiguous() else dres2.contiguous()
+        dx = torch.empty_like(h)
+        parts = lib.ts_rmsnorm_bwd_parts(ctypes.c_longlong(rows))
+        partial = torch.empty(parts, H, dtype=torch.float32, device=h.device)
+        main_grad = getattr(w, "main_grad", None)
+        if main_grad is not None:
+            acc = bool(getattr(w, "grad_added", False))
+            f32 = main_grad if main_grad.dtype == torch.float32 else None
+            b16 = main_grad if main_grad.dtype == torch.bfloat16 else None
+            dw_out = None
+            w.grad_added = True
+        else:
+            acc = False
+            dw_out = torch.empty(H, dtype=torch.float32, device=h.device)
+            f32, b16 = dw_out, None
+        rc = lib.ts_rmsnorm_bwd(_lib.ptr(dy2), _lib.ptr(h), _lib.ptr(w), _lib.ptr(rstd), _lib.ptr(dres2), _lib.ptr(dx),
+                                _lib.ptr(partial), _lib.ptr(f32), _lib.ptr(b16), int(acc), ctypes.c_longlong(rows), H,
+                                ctypes.c_float(ctx.w_offset), _lib.stream_ptr())
+        _lib.check(rc, "ts_rmsnorm_bwd")
+        dxv = dx.view(ctx.shape)
+        dw = None if dw_out is None else dw_out.to(w.dtype)
+        # with a residual input, d(residual) == d(x): both feed h = x + residual
+        return dxv, dw, (dxv if ctx.has_res else None), None, None
+
+
+def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float = 1e-5, residual: torch.Tensor | None = None,
+            w_offset: float = 0.0):
+    """Returns (normed, new_residual). `new_residual` is x (+ residual) and is what the next block adds to."""
+    H = x.shape[-1]
+    if x.is_cuda and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and H % 8 == 0 and H <= 8192:
+        return _RMSNormFn.apply(x, w, residual, eps, w_offset)
+    return rmsnorm_reference(x, w, eps, residual, w_offset)
+
+
+def layernorm(x, w, b=None, eps=1e-5):
+    """LayerNorm (PyTorch op; kept for model families that need it)."""
+    return torch.nn.functional.layer_norm(x, (x.shape[-1],), w, b, eps)
