@@ -1,0 +1,219 @@
+"""Training callbacks: the 11-hook protocol, a handler that actually fires them from SOTATrainer, and the stock
+callbacks (early stopping, checkpointing, logging with console / TensorBoard / W&B backends, progress bar).
+
+Hook names and stock callbacks follow data_pipeline/trainer/callbacks/__init__.py:61-634.  (The reference's
+SOTATrainer registers callbacks but never triggers them, data_pipeline/trainer/trainers/sota_trainer.py:839-881;
+here every hook is fired by the loop.)
+"""
+from __future__ import annotations
+
+import json
+import logging
+import math
+import os
+import shutil
+import time
+from dataclasses import dataclass, field
+from pathlib import Path
+from typing import Any
+
+logger = logging.getLogger("trainscale_b200")
+
+HOOKS = ("on_init_end", "on_train_begin", "on_train_end", "on_epoch_begin", "on_epoch_end", "on_step_begin",
+         "on_step_end", "on_evaluate", "on_save", "on_log", "on_prediction_step")
+
+
+@dataclass
+class CallbackContext:
+    trainer: Any = None
+    state: Any = None
+    config: Any = None
+    model: Any = None
+    optimizer: Any = None
+    scheduler: Any = None
+    metrics: dict = field(default_factory=dict)
+    logs: dict = field(default_factory=dict)
+    should_stop: bool = False
+    should_save: bool = False
+    should_evaluate: bool = False
+    should_log: bool = False
+
+
+class Callback:
+    """Override any of the hooks; each receives the shared CallbackContext."""
+    order = 0
+
+    def on_init_end(self, ctx): ...
+    def on_train_begin(self, ctx): ...
+    def on_train_end(self, ctx): ...
+    def on_epoch_begin(self, ctx): ...
+    def on_epoch_end(self, ctx): ...
+    def on_step_begin(self, ctx): ...
+    def on_step_end(self, ctx): ...
+    def on_evaluate(self, ctx): ...
+    def on_save(self, ctx): ...
+    def on_log(self, ctx): ...
+    def on_prediction_step(self, ctx): ...
+
+
+class CallbackHandler:
+    def __init__(self, callbacks: list[Callback] | None = None):
+        self.callbacks: list[Callback] = []
+        for c in callbacks or []:
+            self.add(c)
+
+    def add(self, cb: Callback | type) -> None:
+        cb = cb() if isinstance(cb, type) else cb
+        self.callbacks.append(cb)
+        self.callbacks.sort(key=lambda c: c.order)
+
+    def remove(self, cb_type: type) -> None:
+        self.callbacks = [c for c in self.callbacks if not isinstance(c, cb_type)]
+
+    def fire(self, hook: str, ctx: CallbackContext) -> CallbackContext:
+        if hook not in HOOKS:
+            raise ValueError(f"unknown hook {hook}")
+        for c in self.callbacks:
+            getattr(c, hook)(ctx)
+        return ctx
+
+    def __getattr__(self, name):
+        if name in HOOKS:
+            return lambda ctx: self.fire(name, ctx)
+        raise AttributeError(name)
+
+
+class EarlyStoppingCallback(Callback):
+    def __init__(self, patience: int = 3, threshold: float = 0.0, metric: str = "eval_loss", greater_is_better=False):
+        self.patience, self.threshold, self.metric, self.greater = patience, threshold, metric, greater_is_better
+        self.best: float | None = None
+        self.counter = 0
+
+    def on_evaluate(self, ctx):
+        v = ctx.metrics.get(self.metric)
+        if v is None:
+            return
+        improved = self.best is None or ((v > self.best + self.threshold) if self.greater
+                                         else (v < self.best - self.threshold))
+        if improved:
+            self.best, self.counter = v, 0
+        else:
+            self.counter += 1
+            if self.counter >= self.patience:
+                ctx.should_stop = True
+
+
+class CheckpointCallback(Callback):
+    """save_strategy steps | epoch | best, rotation by save_total_limit (checkpoint-best is never pruned)."""
+
+    def __init__(self, output_dir: str, save_strategy: str = "steps", save_steps: int = 100, save_total_limit: int = 3,
+                 metric: str = "eval_loss", greater_is_better: bool = False):
+        self.output_dir, self.strategy, self.save_steps = Path(output_dir), save_strategy, save_steps
+        self.limit, self.metric, self.greater = save_total_limit, metric, greater_is_better
+        self.best = None
+
+    def on_step_end(self, ctx):
+        if self.strategy == "steps" and self.save_steps > 0 and ctx.state.global_step % self.save_steps == 0:
+            ctx.should_save = True
+
+    def on_epoch_end(self, ctx):
+        if self.strategy in ("epoch", "epochs"):
+            ctx.should_save = True
+
+    def on_evaluate(self, ctx):
+        if self.strategy != "best":
+            return
+        v = ctx.metrics.get(self.metric)
+        if v is not None and (self.best is None or (v > self.best if self.greater else v < self.best)):
+            self.best = v
+            ctx.should_save = True
+
+    def on_save(self, ctx):
+        self.cleanup_old_checkpoints()
+
+    def cleanup_old_checkpoints(self):
+        if self.limit is None or self.limit <= 0 or not self.output_dir.exists():
+            return
+        ckpts = []
+        for p in self.output_dir.glob("checkpoint-*"):
+            tail = p.name.split("-", 1)[1]
+            if tail.isdigit():
+                ckpts.append((int(tail), p))
+        ckpts.sort()
+        for _, p in ckpts[:-self.limit]:
+            shutil.rmtree(p, ignore_errors=True)
+
+
+class LoggingCallback(Callback):
+    def __init__(self, logging_steps: int = 10, backends: tuple[str, ...] = ("console",), log_dir: str | None = None,
+                 rank: int = 0):
+        self.logging_steps, self.backends, self.log_dir, self.rank = logging_steps, backends, log_dir, rank
+        self._tb = None
+        self._wandb = None
+        self._jsonl = None
+
+    def on_train_begin(self, ctx):
+        if self.rank != 0:
+            return
+        if "tensorboard" in self.backends:
+            try:
+                from torch.utils.tensorboard import SummaryWriter
+                self._tb = SummaryWriter(self.log_dir)
+            except Exception:   # tensorboard not installed
+                self._tb = None
+        if "wandb" in self.backends:
+            try:
+                import wandb
+                self._wandb = wandb
+            except Exception:
+                self._wandb = None
+        if "jsonl" in self.backends and self.log_dir:
+            Path(self.log_dir).mkdir(parents=True, exist_ok=True)
+            self._jsonl = open(Path(self.log_dir) / "train_log.jsonl", "a")
+
+    def on_step_end(self, ctx):
+        if self.logging_steps > 0 and ctx.state.global_step % self.logging_steps == 0:
+            ctx.should_log = True
+
+    def on_log(self, ctx):
+        if self.rank != 0:
+            return
+        step = ctx.state.global_step
+        if "console" in self.backends and ctx.logs.get("line"):
+            logger.info(ctx.logs["line"])
+        scalars = {k: v for k, v in ctx.logs.items() if isinstance(v, (int, float))}
+        if self._tb is not None:
+            for k, v in scalars.items():
+                self._tb.add_scalar(k, v, step)
+        if self._wandb is not None and getattr(self._wandb, "run", None) is not None:
+            self._wandb.log(scalars, step=step)
+        if self._jsonl is not None:
+            self._jsonl.write(json.dumps({"step": step, **scalars}) + "\n")
+            self._jsonl.flush()
+
+    def on_train_end(self, ctx):
+        if self._tb is not None:
+            self._tb.close()
+        if self._jsonl is not None:
+            self._jsonl.close()
+
+
+class ProgressCallback(Callback):
+    def __init__(self, rank: int = 0):
+        self.rank, self.bar = rank, None
+
+    def on_train_begin(self, ctx):
+        if self.rank == 0:
+            try:
+                from tqdm import tqdm
+                self.bar = tqdm(total=getattr(ctx.state, "max_steps", None), desc="train", leave=False)
+            except Exception:
+                self.bar = None
+
+    def on_step_end(self, ctx):
+        if self.bar is not None:
+            self.bar.update(1)
+
+    def on_train_end(self, ctx):
+        if self.bar is not None:
+            self.bar.close()

@@ -1,0 +1,165 @@
+"""Checkpoint save / resume.
+
+Directory layout follows data_pipeline/trainer/trainers/sota_trainer.py:2920-3314 and
+data_pipeline/trainer/distributed/fsdp2.py:2317-2363:
+
+  checkpoint-{step}/
+    model.safetensors (+ config.json)   full weights in HuggingFace Llama naming, written by rank 0
+    optim/shard-{rank:05d}-of-{world:05d}.pt   this rank's fp32 master / moment slices (flat engine)
+    meta.pt            {epoch, step, api_version, config{sharding_strategy, mixed_precision, world_size}, extra{...}}
+    trainer_state.pt   {optimizer|None, scheduler, state{...}, config, rng_state{python,numpy,torch,cuda}, meta{...}}
+
+Every file is written to `<name>.tmp` and renamed, tensors are moved to CPU first, and a world-size mismatch on
+resume re-slices the flat optimizer shards instead of failing (`reshard_optimizer_state`).
+"""
+from __future__ import annotations
+
+import json
+import os
+import time
+from dataclasses import asdict
+from pathlib import Path
+
+import torch
+import torch.distributed as dist
+
+from ..core.errors import CheckpointLoadError, CheckpointSaveError
+
+API_VERSION = "ts_flat_v1"
+
+
+def atomic_torch_save(obj, path: Path) -> None:
+    path.parent.mkdir(parents=True, exist_ok=True)
+    tmp = path.with_name(path.name + ".tmp")
+    torch.save(obj, tmp)
+    os.replace(tmp, path)
+
+
+def _to_cpu(o):
+    if torch.is_tensor(o):
+        return o.detach().cpu()
+    if isinstance(o, dict):
+        return {k: _to_cpu(v) for k, v in o.items()}
+    if isinstance(o, (list, tuple)):
+        return type(o)(_to_cpu(v) for v in o)
+    return o
+
+
+def save_model_weights(model, path: Path, max_shard_bytes: int = 5 * 2 ** 30) -> None:
+    """HF-format weights: safetensors shards + index (or model.pt when safetensors is unavailable)."""
+    from ..hub import ModelSerializer
+    sd = model.to_hf_state_dict() if hasattr(model, "to_hf_state_dict") else model.state_dict()
+    ModelSerializer(max_shard_bytes).save(sd, path)
+    if hasattr(model, "hf_config_dict"):
+        (path / "config.json").write_text(json.dumps(model.hf_config_dict(), indent=2))
+
+
+def load_model_weights(model, path: Path, strict: bool = True) -> None:
+    from ..hub import ModelDeserializer
+    sd = ModelDeserializer().load(path)
+    if hasattr(model, "load_hf_state_dict"):
+        model.load_hf_state_dict(sd, strict=strict)
+    else:
+        model.load_state_dict(sd, strict=strict)
+
+
+def save_training_checkpoint(trainer, path: Path) -> None:
+    path = Path(path)
+    rank, world = trainer.rank, trainer.world_size
+    try:
+        if trainer.is_distributed:
+            dist.barrier()
+        if rank == 0:
+            path.mkdir(parents=True, exist_ok=True)
+            save_model_weights(trainer.model, path)
+        if trainer.is_distributed:
+            dist.barrier()
+        eng = trainer.engine
+        sharded = eng is not None and hasattr(eng, "state_dict")
+        if sharded:
+            write_shard = eng.cfg.sharding_strategy != "NO_SHARD" or rank == 0 if hasattr(eng, "cfg") else True
+            if write_shard:
+                atomic_torch_save(_to_cpu(eng.state_dict()), path / "optim" / f"shard-{rank:05d}-of-{world:05d}.pt")
+        if rank == 0:
+            st = trainer.state
+            meta = {"epoch": st.epoch, "step": st.global_step, "api_version": API_VERSION,
+                    "config": {"sharding_strategy": getattr(getattr(eng, "cfg", None), "sharding_strategy", "NONE"),
+                               "mixed_precision": str(trainer.dtype), "world_size": world},
+                    "extra": {"best_metric": st.best_metric, "patience_counter": st.patience_counter,
+                              "samples_seen": st.samples_seen}}
+            atomic_torch_save(meta, path / "meta.pt")
+            opt_sd = None
+            if not sharded and trainer.optimizer is not None and hasattr(trainer.optimizer, "state_dict"):
+                opt_sd = _to_cpu(trainer.optimizer.state_dict())
+            ts = {"optimizer": opt_sd,
+                  "scheduler": trainer.scheduler.state_dict() if trainer.scheduler is not None else None,
+                  "state": asdict(st), "config": trainer.config.to_dict(), "rng_state": trainer._collect_rng_states(),
+                  "scaler": None,
+                  "meta": {"torch_version": torch.__version__, "world_size": world, "rank": rank,
+                           "distributed_strategy": trainer.strategy, "timestamp": time.time()}}
+            atomic_torch_save(ts, path / "trainer_state.pt")
+        if trainer.is_distributed:
+            dist.barrier()
+    except OSError as e:
+        raise CheckpointSaveError(f"failed to write checkpoint {path}", cause=e)
+
+
+def reshard_optimizer_state(shards: list[dict], new_rank: int, new_world: int) -> dict:
+    """Re-slice flat optimizer shards saved at one world size for another."""
+    shards = sorted(shards, key=lambda s: s["rank"])
+    out = {k: v for k, v in shards[0].items() if k != "units"}
+    out.update(rank=new_rank, world=new_world, units={})
+    for name in shards[0]["units"]:
+        numel = shards[0]["units"][name]["numel"]
+        full = {}
+        for key in ("master", "exp_avg", "exp_avg_sq"):
+            if shards[0]["units"][name][key] is None:
+                full[key] = None
+                continue
+            full[key] = torch.cat([s["units"][name][key] for s in shards])[:numel]
+        n_new = numel // new_world
+        if numel % new_world:
+            raise CheckpointLoadError(f"unit {name}: {numel} elements do not divide over {new_world} ranks")
+        sl = slice(new_rank * n_new, (new_rank + 1) * n_new)
+        out["units"][name] = {k: (None if v is None else v[sl].clone()) for k, v in full.items()}
+        out["units"][name].update(shard_start=new_rank * n_new, numel=numel)
+    return out
+
+
+def load_training_checkpoint(trainer, path: Path) -> None:
+    path = Path(path)
+    if not path.exists():
+        raise CheckpointLoadError(f"checkpoint {path} does not exist")
+    try:
+        load_model_weights(trainer.model, path, strict=False)
+        eng = trainer.engine
+        if eng is not None and hasattr(eng, "units"):
+            # the flat buffers alias the parameters: refresh the fp32 masters from the loaded weights first
+            for u in eng.units:
+                u.master.copy_(u.flat_param[u.shard_start:u.shard_start + u.shard_numel])
+            files = sorted((path / "optim").glob("shard-*.pt")) if (path / "optim").exists() else []
+            if files:
+                saved_world = int(files[0].stem.split("-of-")[1])
+                mine = path / "optim" / f"shard-{trainer.rank:05d}-of-{trainer.world_size:05d}.pt"
+                if saved_world == trainer.world_size and mine.exists():
+                    eng.load_state_dict(torch.load(mine, map_location="cpu", weights_only=False))
+                elif eng.cfg.sharding_strategy == "NO_SHARD" and saved_world == trainer.world_size:
+                    eng.load_state_dict(torch.load(files[0], map_location="cpu", weights_only=False))
+                else:
+                    shards = [torch.load(f, map_location="cpu", weights_only=False) for f in files]
+                    eng.load_state_dict(reshard_optimizer_state(shards, trainer.rank if eng.cfg.sharding_strategy != "NO_SHARD" else 0,
+                                                                trainer.world_size if eng.cfg.sharding_strategy != "NO_SHARD" else 1))
+        tsf = path / "trainer_state.pt"
+        if tsf.exists():
+            ts = torch.load(tsf, map_location="cpu", weights_only=False)
+            for k, v in ts.get("state", {}).items():
+                if hasattr(trainer.state, k):
+                    setattr(trainer.state, k, v)
+            if ts.get("scheduler") is not None and trainer.scheduler is not None:
+                trainer.scheduler.load_state_dict(ts["scheduler"])
+            if ts.get("optimizer") is not None and trainer.optimizer is not None and eng is None:
+                trainer.optimizer.load_state_dict(ts["optimizer"])
+            if ts.get("rng_state") and ts.get("meta", {}).get("world_size") == trainer.world_size:
+                trainer._restore_rng_states(ts["rng_state"])
+    except (OSError, KeyError, RuntimeError) as e:
+        raise CheckpointLoadError(f"failed to load checkpoint {path}", cause=e)

@@ -307,7 +307,9 @@ __global__ void __launch_bounds__(CE_THREADS) cross_entropy_kernel(__nv_bfloat16
                                                                    int V, long long ld, int ignore_index,
                                                                    float label_smoothing, float logit_scale,
                                                                    float softcap, const float* __restrict__ gscale_ptr,
-                                                                   float gscale_mul, int write_grad) {
+                                                                   float gscale_mul,
+                                                                   const float* __restrict__ row_gscale,
+                                                                   int write_grad) {
   __shared__ float scratch[32];
   const size_t row = blockIdx.x;
   __nv_bfloat16* z = logits + row * ld;
@@ -359,7 +361,7 @@ __global__ void __launch_bounds__(CE_THREADS) cross_entropy_kernel(__nv_bfloat16
   }
   if (!write_grad) return;
   __syncthreads();   // z[label] was read above before any thread overwrites it
-  const float gs = ignored ? 0.f : (gscale_ptr ? gscale_ptr[0] : 1.f) * gscale_mul;
+  const float gs = ignored ? 0.f : (gscale_ptr ? gscale_ptr[0] : 1.f) * gscale_mul * (row_gscale ? row_gscale[row] : 1.f);
   const float sm_u = label_smoothing / V;
   for (int i = threadIdx.x; i < nvec; i += CE_THREADS) {
     float f[8];
@@ -681,13 +683,13 @@ extern "C" int ts_glu_bwd(const void* dout, const void* gate_up, void* dgate_up,
 
 extern "C" int ts_cross_entropy(void* logits, const long long* labels, float* loss, float* lse, long long rows, int V,
                                 long long ld, int ignore_index, float label_smoothing, float logit_scale,
-                                float softcap, const float* gscale_ptr, float gscale_mul, int write_grad,
-                                void* stream) {
+                                float softcap, const float* gscale_ptr, float gscale_mul,
+                                const float* row_gscale, int write_grad, void* stream) {
   if (rows <= 0) return 0;
   if (ld % 8 != 0 || (reinterpret_cast<uintptr_t>(logits) & 15u) != 0) return -10;
   cross_entropy_kernel<<<(unsigned)rows, CE_THREADS, 0, ST(stream)>>>((bf16*)logits, labels, loss, lse, V, ld,
                                                                       ignore_index, label_smoothing, logit_scale,
-                                                                      softcap, gscale_ptr, gscale_mul, write_grad);
+                                                                      softcap, gscale_ptr, gscale_mul, row_gscale, write_grad);
   return (int)cudaGetLastError();
 }
 

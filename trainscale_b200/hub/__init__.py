@@ -1,0 +1,295 @@
+"""Model serialisation (sharded safetensors + index with sha256), local "hub" loading, retry / circuit-breaker
+helpers and the checkpoint manager.
+
+Surface after data_pipeline/trainer/hub/__init__.py:284-1652 (CircuitBreaker, RetryPolicy, execute_with_retry,
+compute_sha256, ModelSerializer, ModelDeserializer, HubManager, generate_model_card, CheckpointManager).
+Network pushes are delegated to `huggingface_hub` when it is importable and a token is configured.
+"""
+from __future__ import annotations
+
+import hashlib
+import json
+import os
+import random
+import shutil
+import time
+from concurrent.futures import ThreadPoolExecutor
+from dataclasses import dataclass, field
+from pathlib import Path
+from typing import Any, Callable
+
+import torch
+
+from ..core.errors import CheckpointLoadError, HubError
+
+try:
+    from safetensors.torch import load_file as _st_load, save_file as _st_save
+    HAVE_SAFETENSORS = True
+except Exception:   # pragma: no cover
+    HAVE_SAFETENSORS = False
+
+
+class CircuitBreaker:
+    """closed -> open after `failure_threshold` consecutive failures -> half-open after `reset_timeout` s."""
+
+    def __init__(self, failure_threshold: int = 5, reset_timeout: float = 60.0, clock: Callable[[], float] = time.monotonic):
+        self.failure_threshold, self.reset_timeout, self.clock = failure_threshold, reset_timeout, clock
+        self.failures, self.opened_at, self.state = 0, None, "closed"
+
+    def allow(self) -> bool:
+        if self.state == "open" and self.clock() - self.opened_at >= self.reset_timeout:
+            self.state = "half_open"
+        return self.state != "open"
+
+    def record_success(self):
+        self.failures, self.state, self.opened_at = 0, "closed", None
+
+    def record_failure(self):
+        self.failures += 1
+        if self.state == "half_open" or self.failures >= self.failure_threshold:
+            self.state, self.opened_at = "open", self.clock()
+
+
+@dataclass
+class RetryPolicy:
+    max_attempts: int = 3
+    base_delay: float = 0.5
+    max_delay: float = 30.0
+    backoff: float = 2.0
+    jitter: float = 0.1
+    retry_on: tuple = (OSError, TimeoutError, ConnectionError)
+
+    def delay(self, attempt: int) -> float:
+        d = min(self.max_delay, self.base_delay * self.backoff ** attempt)
+        return d * (1.0 + random.uniform(-self.jitter, self.jitter))
+
+
+def execute_with_retry(fn: Callable, policy: RetryPolicy | None = None, breaker: CircuitBreaker | None = None,
+                       sleep: Callable[[float], None] = time.sleep):
+    policy = policy or RetryPolicy()
+    last = None
+    for attempt in range(policy.max_attempts):
+        if breaker is not None and not breaker.allow():
+            raise HubError("circuit breaker is open", failures=breaker.failures)
+        try:
+            out = fn()
+            if breaker is not None:
+                breaker.record_success()
+            return out
+        except policy.retry_on as e:
+            last = e
+            if breaker is not None:
+                breaker.record_failure()
+            if attempt + 1 < policy.max_attempts:
+                sleep(policy.delay(attempt))
+    raise HubError(f"operation failed after {policy.max_attempts} attempts", cause=last)
+
+
+def compute_sha256(path: str | os.PathLike, chunk: int = 1 << 22) -> str:
+    h = hashlib.sha256()
+    with open(path, "rb") as f:
+        while True:
+            b = f.read(chunk)
+            if not b:
+                break
+            h.update(b)
+    return h.hexdigest()
+
+
+class ModelSerializer:
+    """state dict -> `model.safetensors` or `model-0000i-of-0000n.safetensors` + `model.safetensors.index.json`."""
+
+    def __init__(self, max_shard_bytes: int = 5 * 2 ** 30):
+        self.max_shard_bytes = max_shard_bytes
+
+    def plan(self, sd: dict[str, torch.Tensor]) -> list[list[str]]:
+        shards, cur, size = [], [], 0
+        for k, v in sd.items():
+            b = v.numel() * v.element_size()
+            if cur and size + b > self.max_shard_bytes:
+                shards.append(cur)
+                cur, size = [], 0
+            cur.append(k)
+            size += b
+        if cur:
+            shards.append(cur)
+        return shards
+
+    def save(self, sd: dict[str, torch.Tensor], out_dir: str | os.PathLike) -> dict:
+        out = Path(out_dir)
+        out.mkdir(parents=True, exist_ok=True)
+        sd = {k: v.detach().cpu().contiguous() for k, v in sd.items()}
+        if not HAVE_SAFETENSORS:
+            tmp = out / "model.pt.tmp"
+            torch.save(sd, tmp)
+            os.replace(tmp, out / "model.pt")
+            return {"format": "pt", "files": ["model.pt"]}
+        # tied tensors share storage: safetensors refuses aliases, so clone duplicates
+        seen: dict[int, str] = {}
+        for k, v in list(sd.items()):
+            p = v.data_ptr()
+            if p in seen and v.numel() > 0:
+                sd[k] = v.clone()
+            seen[p] = k
+        shards = self.plan(sd)
+        n = len(shards)
+        weight_map, files, hashes = {}, [], {}
+        for i, keys in enumerate(shards):
+            name = "model.safetensors" if n == 1 else f"model-{i + 1:05d}-of-{n:05d}.safetensors"
+            tmp = out / (name + ".tmp")
+            _st_save({k: sd[k] for k in keys}, str(tmp), metadata={"format": "pt"})
+            os.replace(tmp, out / name)
+            files.append(name)
+            hashes[name] = compute_sha256(out / name)
+            weight_map.update({k: name for k in keys})
+        index = {"metadata": {"total_size": sum(v.numel() * v.element_size() for v in sd.values()), "sha256": hashes},
+                 "weight_map": weight_map}
+        (out / "model.safetensors.index.json").write_text(json.dumps(index, indent=2))
+        return {"format": "safetensors", "files": files}
+
+
+class ModelDeserializer:
+    def __init__(self, verify_integrity: bool = True, num_threads: int = 4):
+        self.verify, self.num_threads = verify_integrity, num_threads
+
+    def load(self, in_dir: str | os.PathLike) -> dict[str, torch.Tensor]:
+        d = Path(in_dir)
+        idx = d / "model.safetensors.index.json"
+        if idx.exists() and HAVE_SAFETENSORS:
+            index = json.loads(idx.read_text())
+            files = sorted(set(index["weight_map"].values()))
+            hashes = index.get("metadata", {}).get("sha256", {})
+
+            def one(name):
+                p = d / name
+                if not p.exists():
+                    raise CheckpointLoadError(f"missing shard {name}", directory=str(d))
+                if self.verify and name in hashes and compute_sha256(p) != hashes[name]:
+                    raise CheckpointLoadError(f"sha256 mismatch for {name}", directory=str(d))
+                return _st_load(str(p))
+
+            out: dict[str, torch.Tensor] = {}
+            with ThreadPoolExecutor(max_workers=self.num_threads) as ex:
+                for part in ex.map(one, files):
+                    out.update(part)
+            return out
+        if (d / "model.safetensors").exists() and HAVE_SAFETENSORS:
+            return _st_load(str(d / "model.safetensors"))
+        for name in ("model.pt", "pytorch_model.bin"):
+            if (d / name).exists():
+                return torch.load(d / name, map_location="cpu", weights_only=True)
+        raise CheckpointLoadError(f"no model weights found in {d}")
+
+
+def load_pretrained(path: str | os.PathLike, dtype=torch.bfloat16, device=None):
+    """Build the framework decoder from a local HF-format directory (config.json + safetensors)."""
+    from ..models.llama import LlamaConfig, build_model
+    p = Path(path)
+    cfg = LlamaConfig.from_dict(json.loads((p / "config.json").read_text()))
+    model = build_model(cfg, dtype=dtype, device=device)
+    model.load_hf_state_dict(ModelDeserializer().load(p), strict=True)
+    return model
+
+
+def generate_model_card(model_name: str, base_model: str = "", config: dict | None = None, metrics: dict | None = None,
+                        tags: list[str] | None = None) -> str:
+    tags = tags or ["trainscale-b200"]
+    lines = ["---", "library_name: trainscale-b200", f"base_model: {base_model}" if base_model else "base_model: none",
+             "tags:"] + [f"- {t}" for t in tags] + ["---", "", f"# {model_name}", ""]
+    if metrics:
+        lines += ["## Metrics", ""] + [f"- **{k}**: {v}" for k, v in metrics.items()] + [""]
+    if config:
+        lines += ["## Training configuration", "", "```json", json.dumps(config, indent=2, default=str), "```", ""]
+    return "\n".join(lines)
+
+
+class HubManager:
+    """Thin wrapper over `huggingface_hub` with retry + circuit breaker; a no-op target directory when offline."""
+
+    def __init__(self, repo_id: str | None = None, token: str | None = None, private: bool = False,
+                 policy: RetryPolicy | None = None):
+        self.repo_id, self.token, self.private = repo_id, token or os.environ.get("HF_TOKEN"), private
+        self.policy, self.breaker = policy or RetryPolicy(), CircuitBreaker()
+
+    def available(self) -> bool:
+        try:
+            import huggingface_hub  # noqa: F401
+            return bool(self.repo_id and self.token)
+        except Exception:
+            return False
+
+    def push(self, folder: str | os.PathLike, commit_message: str = "upload") -> str | None:
+        if not self.available():
+            return None
+        from huggingface_hub import HfApi
+        api = HfApi(token=self.token)
+
+        def go():
+            api.create_repo(self.repo_id, private=self.private, exist_ok=True)
+            return api.upload_folder(repo_id=self.repo_id, folder_path=str(folder), commit_message=commit_message)
+
+        return str(execute_with_retry(go, self.policy, self.breaker))
+
+    def pull(self, local_dir: str | os.PathLike) -> str | None:
+        if not self.available():
+            return None
+        from huggingface_hub import snapshot_download
+        return execute_with_retry(lambda: snapshot_download(self.repo_id, local_dir=str(local_dir), token=self.token),
+                                  self.policy, self.breaker)
+
+
+class CheckpointManager:
+    """Atomic directory checkpoints with metadata, pruning and best / latest tracking."""
+
+    def __init__(self, root: str | os.PathLike, save_total_limit: int = 3, metric: str = "eval_loss",
+                 greater_is_better: bool = False, hub: HubManager | None = None):
+        self.root, self.limit, self.metric, self.greater, self.hub = Path(root), save_total_limit, metric, greater_is_better, hub
+        self.root.mkdir(parents=True, exist_ok=True)
+        self.best_value: float | None = None
+
+    def save(self, step: int, writer: Callable[[Path], None], metrics: dict | None = None) -> Path:
+        final = self.root / f"checkpoint-{step}"
+        tmp = self.root / f".tmp-checkpoint-{step}"
+        if tmp.exists():
+            shutil.rmtree(tmp)
+        tmp.mkdir(parents=True)
+        writer(tmp)
+        (tmp / "checkpoint_meta.json").write_text(json.dumps({"step": step, "metrics": metrics or {}, "time": time.time()}))
+        if final.exists():
+            shutil.rmtree(final)
+        os.replace(tmp, final)
+        (self.root / "latest").write_text(final.name)
+        v = (metrics or {}).get(self.metric)
+        if v is not None and (self.best_value is None or (v > self.best_value if self.greater else v < self.best_value)):
+            self.best_value = v
+            (self.root / "best").write_text(final.name)
+        self._prune_old_checkpoints()
+        if self.hub is not None:
+            self.hub.push(final, f"checkpoint {step}")
+        return final
+
+    def list(self) -> list[Path]:
+        out = [(int(p.name.split("-")[1]), p) for p in self.root.glob("checkpoint-*") if p.name.split("-")[1].isdigit()]
+        return [p for _, p in sorted(out)]
+
+    def latest(self) -> Path | None:
+        f = self.root / "latest"
+        if f.exists() and (self.root / f.read_text().strip()).exists():
+            return self.root / f.read_text().strip()
+        all_ = self.list()
+        return all_[-1] if all_ else None
+
+    def best(self) -> Path | None:
+        f = self.root / "best"
+        return self.root / f.read_text().strip() if f.exists() else None
+
+    def _prune_old_checkpoints(self):
+        if not self.limit or self.limit <= 0:
+            return
+        keep = {p.name for p in self.list()[-self.limit:]}
+        b = self.best()
+        if b is not None:
+            keep.add(b.name)
+        for p in self.list():
+            if p.name not in keep:
+                shutil.rmtree(p, ignore_errors=True)

@@ -1,0 +1,375 @@
+"""Llama-style decoder owned by the framework (GQA, RoPE, SwiGLU, RMSNorm, tied or untied head).
+
+The reference has no model code: it loads a HuggingFace `AutoModelForCausalLM` and monkey-patches layers
+(data_pipeline/trainer/trainers/sota_trainer.py:1161-1212, data_pipeline/trainer/registry/__init__.py:1033-1324).
+Here the decoder is built for the sm_100a kernels from the start:
+  * q/k/v are ONE projection ([Hq+2Hkv]*D rows) and gate/up are ONE projection, so each block is four GEMMs;
+  * RoPE rotates the q|k heads of the fused buffer in place, attention reads that buffer directly;
+  * the residual add is fused into the following RMSNorm;
+  * the loss head is the chunked fused lm_head + cross-entropy (logits are never materialised).
+State dicts convert to and from the HuggingFace Llama naming (`to_hf_state_dict` / `load_hf_state_dict`).
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import asdict, dataclass, field
+from typing import Any
+
+import torch
+import torch.nn as nn
+from torch.utils.checkpoint import checkpoint
+
+from ..ops import activation, attention, cross_entropy, gemm, norm, rope
+
+
+@dataclass
+class LlamaConfig:
+    vocab_size: int = 32000
+    hidden_size: int = 256
+    intermediate_size: int = 688
+    num_hidden_layers: int = 4
+    num_attention_heads: int = 4
+    num_key_value_heads: int | None = None
+    head_dim: int | None = None
+    rms_norm_eps: float = 1e-5
+    rope_theta: float = 10000.0
+    rope_scaling: dict | None = None
+    rope_interleaved: bool = False
+    max_position_embeddings: int = 8192
+    tie_word_embeddings: bool = False
+    hidden_act: str = "silu"
+    sliding_window: int | None = None
+    attn_logit_softcap: float = 0.0
+    final_logit_softcap: float = 0.0
+    initializer_range: float = 0.02
+    model_type: str = "llama"
+
+    def __post_init__(self):
+        if self.num_key_value_heads is None:
+            self.num_key_value_heads = self.num_attention_heads
+        if self.head_dim is None:
+            self.head_dim = self.hidden_size // self.num_attention_heads
+
+    def to_dict(self) -> dict:
+        return asdict(self)
+
+    @classmethod
+    def from_dict(cls, d: dict) -> "LlamaConfig":
+        keys = {f for f in cls.__dataclass_fields__}
+        return cls(**{k: v for k, v in d.items() if k in keys})
+
+    def num_parameters(self, include_embeddings: bool = True) -> int:
+        H, I, L, V = self.hidden_size, self.intermediate_size, self.num_hidden_layers, self.vocab_size
+        D, Hq, Hkv = self.head_dim, self.num_attention_heads, self.num_key_value_heads
+        per_layer = (Hq + 2 * Hkv) * D * H + Hq * D * H + 3 * H * I + 2 * H
+        n = L * per_layer + H
+        if include_embeddings:
+            n += V * H * (1 if self.tie_word_embeddings else 2)
+        return n
+
+    def flops_per_token(self, seq_len: int, causal: bool = True) -> float:
+        """Training FLOPs per token: 6 * matmul params + attention (12 * L * d_attn * S, halved if causal)."""
+        H, I, L, V = self.hidden_size, self.intermediate_size, self.num_hidden_layers, self.vocab_size
+        D, Hq, Hkv = self.head_dim, self.num_attention_heads, self.num_key_value_heads
+        mm = L * ((Hq + 2 * Hkv) * D * H + Hq * D * H + 3 * H * I) + V * H
+        attn = 12 * L * Hq * D * seq_len * (0.5 if causal else 1.0)
+        return 6.0 * mm + attn
+
+
+PRESETS: dict[str, dict[str, Any]] = {
+    "tiny": dict(vocab_size=32000, hidden_size=256, intermediate_size=688, num_hidden_layers=4,
+                 num_attention_heads=4, num_key_value_heads=4, rms_norm_eps=1e-5, rope_theta=10000.0),
+    "llama3-8b": dict(vocab_size=128256, hidden_size=4096, intermediate_size=14336, num_hidden_layers=32,
+                      num_attention_heads=32, num_key_value_heads=8, rms_norm_eps=1e-5, rope_theta=500000.0,
+                      max_position_embeddings=131072),
+    "llama3-70b": dict(vocab_size=128256, hidden_size=8192, intermediate_size=28672, num_hidden_layers=80,
+                       num_attention_heads=64, num_key_value_heads=8, rms_norm_eps=1e-5, rope_theta=500000.0,
+                       max_position_embeddings=131072),
+    "llama3-1b": dict(vocab_size=128256, hidden_size=2048, intermediate_size=8192, num_hidden_layers=16,
+                      num_attention_heads=32, num_key_value_heads=8, head_dim=64, rope_theta=500000.0,
+                      tie_word_embeddings=True, max_position_embeddings=131072),
+    "mistral-7b": dict(vocab_size=32000, hidden_size=4096, intermediate_size=14336, num_hidden_layers=32,
+                       num_attention_heads=32, num_key_value_heads=8, rope_theta=10000.0, sliding_window=4096,
+                       model_type="mistral"),
+    "qwen2-7b": dict(vocab_size=152064, hidden_size=3584, intermediate_size=18944, num_hidden_layers=28,
+                     num_attention_heads=28, num_key_value_heads=4, rope_theta=1000000.0, rms_norm_eps=1e-6,
+                     model_type="qwen2"),
+}
+
+
+def preset_config(name: str, **overrides) -> LlamaConfig:
+    d = dict(PRESETS[name])
+    d.update(overrides)
+    return LlamaConfig(**d)
+
+
+class RMSNorm(nn.Module):
+    def __init__(self, dim: int, eps: float = 1e-5):
+        super().__init__()
+        self.weight = nn.Parameter(torch.ones(dim))
+        self.eps = eps
+
+    def forward(self, x, residual=None):
+        return norm.rmsnorm(x, self.weight, self.eps, residual)
+
+
+class LlamaAttention(nn.Module):
+    def __init__(self, cfg: LlamaConfig):
+        super().__init__()
+        self.cfg = cfg
+        self.n_heads, self.n_kv, self.hd = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+        self.wqkv = nn.Parameter(torch.empty((self.n_heads + 2 * self.n_kv) * self.hd, cfg.hidden_size))
+        self.wo = nn.Parameter(torch.empty(cfg.hidden_size, self.n_heads * self.hd))
+
+    def forward(self, x, cos, sin, position_ids=None, cu_seqlens=None, doc_ids=None, kv_cache=None):
+        qkv = gemm.linear(x, self.wqkv)
+        offset = 0 if kv_cache is None else kv_cache.seq_len
+        qkv = rope.apply_rope_qkv(qkv, self.n_heads + self.n_kv, self.hd, cos, sin, position_ids, x.shape[-2], offset,
+                                  self.cfg.rope_interleaved)
+        if kv_cache is not None:
+            o = kv_cache.attend(qkv, self)
+        else:
+            o = attention.attention_qkv(qkv, self.n_heads, self.n_kv, self.hd, True, None, self.cfg.sliding_window,
+                                        self.cfg.attn_logit_softcap, cu_seqlens, doc_ids)
+        return gemm.linear(o, self.wo)
+
+
+class LlamaMLP(nn.Module):
+    def __init__(self, cfg: LlamaConfig):
+        super().__init__()
+        self.act = cfg.hidden_act
+        self.w_gate_up = nn.Parameter(torch.empty(2 * cfg.intermediate_size, cfg.hidden_size))
+        self.w_down = nn.Parameter(torch.empty(cfg.hidden_size, cfg.intermediate_size))
+
+    def forward(self, x):
+        return gemm.linear(activation.glu(gemm.linear(x, self.w_gate_up), self.act), self.w_down)
+
+
+class LlamaDecoderLayer(nn.Module):
+    def __init__(self, cfg: LlamaConfig):
+        super().__init__()
+        self.input_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps)
+        self.self_attn = LlamaAttention(cfg)
+        self.post_attention_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps)
+        self.mlp = LlamaMLP(cfg)
+
+    def forward(self, x, residual, cos, sin, position_ids=None, cu_seqlens=None, doc_ids=None, kv_cache=None):
+        h, residual = self.input_layernorm(x, residual)
+        a = self.self_attn(h, cos, sin, position_ids, cu_seqlens, doc_ids, kv_cache)
+        h, residual = self.post_attention_layernorm(a, residual)
+        return self.mlp(h), residual
+
+
+@dataclass
+class CausalLMOutput:
+    loss: torch.Tensor | None = None
+    logits: torch.Tensor | None = None
+    hidden_states: torch.Tensor | None = None
+    num_tokens: torch.Tensor | None = None
+
+
+class LlamaModel(nn.Module):
+    def __init__(self, cfg: LlamaConfig):
+        super().__init__()
+        self.cfg = cfg
+        self.embed_tokens = nn.Embedding(cfg.vocab_size, cfg.hidden_size)
+        self.layers = nn.ModuleList(LlamaDecoderLayer(cfg) for _ in range(cfg.num_hidden_layers))
+        self.norm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps)
+        self.gradient_checkpointing = False
+        self.checkpoint_every = 1
+        self._rope_cache: dict = {}
+
+    def rope_tables(self, device, needed: int):
+        key = (str(device),)
+        cached = self._rope_cache.get(key)
+        if cached is None or cached[0].shape[0] < needed:
+            n = max(needed, min(self.cfg.max_position_embeddings, 8192))
+            sc = dict(self.cfg.rope_scaling or {})
+            kind = sc.pop("rope_type", sc.pop("type", "none"))
+            kw = {}
+            if kind != "none":
+                kw = dict(scaling=kind, factor=sc.get("factor", 1.0),
+                          original_max_pos=sc.get("original_max_position_embeddings", 8192),
+                          low_freq_factor=sc.get("low_freq_factor", 1.0),
+                          high_freq_factor=sc.get("high_freq_factor", 4.0))
+            cached = rope.rope_tables(n, self.cfg.head_dim, self.cfg.rope_theta, device, **kw)
+            self._rope_cache[key] = cached
+        return cached
+
+    def forward(self, input_ids, position_ids=None, cu_seqlens=None, doc_ids=None, kv_caches=None,
+                inputs_embeds=None):
+        x = self.embed_tokens(input_ids) if inputs_embeds is None else inputs_embeds
+        S = x.shape[1]
+        past = 0 if not kv_caches else kv_caches[0].seq_len
+        need = S + past
+        if position_ids is not None:
+            need = max(need, self.cfg.max_position_embeddings if self.cfg.max_position_embeddings <= 1 << 17 else need)
+        cos, sin = self.rope_tables(x.device, need)
+        residual = None
+        for i, layer in enumerate(self.layers):
+            cache = None if kv_caches is None else kv_caches[i]
+            if self.gradient_checkpointing and self.training and (i % self.checkpoint_every == 0):
+                x, residual = checkpoint(layer, x, residual, cos, sin, position_ids, cu_seqlens, doc_ids, None,
+                                         use_reentrant=False)
+            else:
+                x, residual = layer(x, residual, cos, sin, position_ids, cu_seqlens, doc_ids, cache)
+        x, _ = self.norm(x, residual)
+        return x
+
+
+class LlamaForCausalLM(nn.Module):
+    """Decoder + loss head. `forward(input_ids, labels=...)` shifts labels by one (labels are NOT pre-shifted,
+    as in data_pipeline/trainer/trainers/sota_trainer.py:2044-2055) and returns the mean loss over
+    non-ignored tokens."""
+
+    def __init__(self, cfg: LlamaConfig):
+        super().__init__()
+        self.config = cfg
+        self.model = LlamaModel(cfg)
+        self.lm_head = None if cfg.tie_word_embeddings else nn.Parameter(torch.empty(cfg.vocab_size, cfg.hidden_size))
+        self.loss_chunk_tokens = cross_entropy.DEFAULT_CHUNK_TOKENS
+        self.reset_parameters()
+
+    # ---------------------------------------------------------------- init / introspection
+    @torch.no_grad()
+    def reset_parameters(self, seed: int | None = None):
+        gen = None
+        if seed is not None:
+            gen = torch.Generator(device="cpu").manual_seed(seed)
+        std = self.config.initializer_range
+        for name, p in self.named_parameters():
+            if p.dim() == 1:
+                p.fill_(1.0)
+            else:
+                s = std
+                if name.endswith("wo") or name.endswith("w_down"):
+                    s = std / math.sqrt(2 * self.config.num_hidden_layers)
+                if gen is not None:
+                    p.copy_(torch.randn(p.shape, generator=gen) * s)
+                else:
+                    p.normal_(0.0, s)
+
+    @property
+    def head_weight(self) -> torch.Tensor:
+        return self.model.embed_tokens.weight if self.lm_head is None else self.lm_head
+
+    def num_parameters(self) -> int:
+        return sum(p.numel() for p in self.parameters())
+
+    def gradient_checkpointing_enable(self, every: int = 1):
+        self.model.gradient_checkpointing = True
+        self.model.checkpoint_every = max(1, every)
+
+    def gradient_checkpointing_disable(self):
+        self.model.gradient_checkpointing = False
+
+    # ---------------------------------------------------------------- forward
+    def forward(self, input_ids=None, attention_mask=None, labels=None, position_ids=None, cu_seqlens=None,
+                doc_ids=None, kv_caches=None, return_logits: bool | None = None, loss_scale: float = 1.0,
+                label_smoothing: float = 0.0, ignore_index: int = -100, shift_labels: bool = True,
+                inputs_embeds=None, **_unused) -> CausalLMOutput:
+        h = self.model(input_ids, position_ids, cu_seqlens, doc_ids, kv_caches, inputs_embeds)
+        out = CausalLMOutput(hidden_states=h)
+        if labels is not None:
+            if attention_mask is not None:
+                labels = labels.masked_fill(attention_mask == 0, ignore_index)
+            if shift_labels:
+                tgt = torch.full_like(labels, ignore_index)
+                tgt[..., :-1] = labels[..., 1:]
+                if doc_ids is not None:   # never predict across a packed-document boundary
+                    tgt[..., :-1] = tgt[..., :-1].masked_fill(doc_ids[..., 1:] != doc_ids[..., :-1], ignore_index)
+            else:
+                tgt = labels
+            loss, count = cross_entropy.fused_linear_cross_entropy(
+                h, self.head_weight, tgt, ignore_index, label_smoothing, 1.0, self.config.final_logit_softcap,
+                self.loss_chunk_tokens, "mean", loss_scale)
+            out.loss, out.num_tokens = loss, count
+        if return_logits or (return_logits is None and labels is None):
+            out.logits = self.logits(h)
+        return out
+
+    def logits(self, hidden: torch.Tensor) -> torch.Tensor:
+        z = gemm.linear(hidden, self.head_weight)
+        cap = self.config.final_logit_softcap
+        return cap * torch.tanh(z / cap) if cap and cap > 0 else z
+
+    # ---------------------------------------------------------------- HF interop
+    def to_hf_state_dict(self) -> dict[str, torch.Tensor]:
+        cfg = self.config
+        D, Hq, Hkv, I = cfg.head_dim, cfg.num_attention_heads, cfg.num_key_value_heads, cfg.intermediate_size
+        sd = {"model.embed_tokens.weight": self.model.embed_tokens.weight.detach(),
+              "model.norm.weight": self.model.norm.weight.detach()}
+        for i, l in enumerate(self.model.layers):
+            p = f"model.layers.{i}."
+            q, k, v = l.self_attn.wqkv.detach().split((Hq * D, Hkv * D, Hkv * D), dim=0)
+            g, u = l.mlp.w_gate_up.detach().split((I, I), dim=0)
+            sd.update({p + "self_attn.q_proj.weight": q, p + "self_attn.k_proj.weight": k,
+                       p + "self_attn.v_proj.weight": v, p + "self_attn.o_proj.weight": l.self_attn.wo.detach(),
+                       p + "mlp.gate_proj.weight": g, p + "mlp.up_proj.weight": u,
+                       p + "mlp.down_proj.weight": l.mlp.w_down.detach(),
+                       p + "input_layernorm.weight": l.input_layernorm.weight.detach(),
+                       p + "post_attention_layernorm.weight": l.post_attention_layernorm.weight.detach()})
+        if self.lm_head is not None:
+            sd["lm_head.weight"] = self.lm_head.detach()
+        return sd
+
+    @torch.no_grad()
+    def load_hf_state_dict(self, sd: dict[str, torch.Tensor], strict: bool = True) -> list[str]:
+        missing = []
+
+        def get(name):
+            if name not in sd:
+                missing.append(name)
+                return None
+            return sd[name]
+
+        def put(dst, parts):
+            if any(p is None for p in parts):
+                return
+            dst.copy_(torch.cat([p.to(dst.dtype) for p in parts], dim=0) if len(parts) > 1 else parts[0])
+
+        put(self.model.embed_tokens.weight, [get("model.embed_tokens.weight")])
+        put(self.model.norm.weight, [get("model.norm.weight")])
+        for i, l in enumerate(self.model.layers):
+            p = f"model.layers.{i}."
+            put(l.self_attn.wqkv, [get(p + f"self_attn.{n}_proj.weight") for n in "qkv"])
+            put(l.self_attn.wo, [get(p + "self_attn.o_proj.weight")])
+            put(l.mlp.w_gate_up, [get(p + "mlp.gate_proj.weight"), get(p + "mlp.up_proj.weight")])
+            put(l.mlp.w_down, [get(p + "mlp.down_proj.weight")])
+            put(l.input_layernorm.weight, [get(p + "input_layernorm.weight")])
+            put(l.post_attention_layernorm.weight, [get(p + "post_attention_layernorm.weight")])
+        if self.lm_head is not None:
+            put(self.lm_head, [get("lm_head.weight")])
+        if strict and missing:
+            raise KeyError(f"missing keys in state dict: {missing[:8]}{'...' if len(missing) > 8 else ''}")
+        return missing
+
+    def hf_config_dict(self) -> dict:
+        c = self.config
+        return {"architectures": ["LlamaForCausalLM"], "model_type": "llama", "vocab_size": c.vocab_size,
+                "hidden_size": c.hidden_size, "intermediate_size": c.intermediate_size,
+                "num_hidden_layers": c.num_hidden_layers, "num_attention_heads": c.num_attention_heads,
+                "num_key_value_heads": c.num_key_value_heads, "head_dim": c.head_dim, "rms_norm_eps": c.rms_norm_eps,
+                "rope_theta": c.rope_theta, "rope_scaling": c.rope_scaling,
+                "max_position_embeddings": c.max_position_embeddings, "tie_word_embeddings": c.tie_word_embeddings,
+                "hidden_act": c.hidden_act, "torch_dtype": "bfloat16"}
+
+
+def build_model(cfg: LlamaConfig | str | dict, dtype=torch.bfloat16, device=None, seed: int | None = None) -> LlamaForCausalLM:
+    if isinstance(cfg, str):
+        cfg = preset_config(cfg)
+    elif isinstance(cfg, dict):
+        cfg = LlamaConfig.from_dict(cfg)
+    prev = torch.get_default_dtype()
+    torch.set_default_dtype(dtype)
+    try:
+        if device is not None:
+            with torch.device(device):
+                m = LlamaForCausalLM(cfg)
+        else:
+            m = LlamaForCausalLM(cfg)
+    finally:
+        torch.set_default_dtype(prev)
+    if seed is not None:
+        m.reset_parameters(seed)
+    return m

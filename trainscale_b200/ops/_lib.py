@@ -64,3 +64,14 @@ def raise_on_device_error(name: str) -> None:
         clear_device_error(name)
         raise KernelError(f"{name} kernel reported '{_ERR_NAMES.get(code, code)}' at site {site} "
                           f"(block {block}, extra {extra})")
+
+
+# number of launcher calls made through `check` (each is at least one kernel of this library)
+LAUNCHES = 0
+_orig_check = check
+
+
+def check(rc: int, what: str) -> None:  # noqa: F811
+    global LAUNCHES
+    LAUNCHES += 1
+    _orig_check(rc, what)

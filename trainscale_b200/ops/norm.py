@@ -47,12 +47,11 @@ class _RMSNormFn(torch.autograd.Function):
         ctx.has_res = residual is not None
         ctx.shape = x.shape
         if residual is None:
-            return y.view(x.shape), x
-        ctx.mark_non_differentiable()
+            return y.view(x.shape)
         return y.view(x.shape), res_out.view(x.shape)
 
     @staticmethod
-    def backward(ctx, dy, dres):
+    def backward(ctx, dy, dres=None):
         lib = _lib.load("elementwise")
         h, w, rstd = ctx.saved_tensors
         rows, H = h.shape
@@ -91,6 +90,8 @@ def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float = 1e-5, residual: torch
     """Returns (normed, new_residual). `new_residual` is x (+ residual) and is what the next block adds to."""
     H = x.shape[-1]
     if x.is_cuda and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and H % 8 == 0 and H <= 8192:
+        if residual is None:
+            return _RMSNormFn.apply(x, w, None, eps, w_offset), x
         return _RMSNormFn.apply(x, w, residual, eps, w_offset)
     return rmsnorm_reference(x, w, eps, residual, w_offset)
 
