@@ -75,3 +75,11 @@ def check(rc: int, what: str) -> None:  # noqa: F811
     global LAUNCHES
     LAUNCHES += 1
     _orig_check(rc, what)
+
+
+def raise_on_any_device_error() -> None:
+    """Check the error word of every library that has been built."""
+    from .build import sources
+    for src in sources():
+        if lib_path(src.stem).exists():
+            raise_on_device_error(src.stem)
