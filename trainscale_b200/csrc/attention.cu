@@ -1,0 +1,399 @@
+// Flash attention for sm_100a on tcgen05 / TMEM / TMA: causal or full, GQA, packed documents (cu_seqlens).
+//
+// Forward, per CTA (one 256-row query block of one head = two 128-row tiles that ping-pong):
+//   warp 0        TMA loader: Q tiles once, then a 2-deep ring of 128-row K and V tiles (128-byte swizzle)
+//   warp 1        MMA issuer (one thread): S_t = Q_t K^T into TMEM, later O_t += P_t V with P_t read from TMEM
+//   warps 2..5    softmax for tile 0, warps 6..9 for tile 1: one thread per query row (its own TMEM lane), so row
+//                 max / sum need no shuffles; P is written back over S as packed bf16, O is rescaled in TMEM
+//                 only when the running max moved by more than 2^8 (exact: O and the row sum share the stale max)
+// While one tile's rows are in softmax the tensor core works on the other tile.
+// Backward is two kernels that recompute S and dP: one owns a K/V tile and accumulates dK, dV over the query
+// tiles of its head group; one owns a Q tile and accumulates dQ over the K/V tiles.  No atomics, deterministic.
+//
+// Replaces data_pipeline/trainer/kernels/flash_attention.py:147-560 (Triton forward, dq and dk/dv kernels).
+#include "common.cuh"
+#include "host_common.h"
+
+namespace ts {
+
+struct AttnParams {
+  // strides are in elements; q/k/v/o/do/dq/dk/dv rows are tokens, heads are laid out along the row
+  int q_col0, k_col0, v_col0;   // column of head 0 inside the q / k / v tensor maps
+  int Hq, Hkv, group;           // group = Hq / Hkv
+  int B, S;                     // uniform batch (ignored when cu_seqlens != nullptr)
+  const int* cu_seqlens;        // [B + 1] or nullptr
+  int causal;
+  float scale_log2;             // softmax scale * log2(e)
+  __nv_bfloat16* o;             // [rows][o_stride], head h at column h*D
+  int o_stride;
+  float* lse;                   // [Hq][total_rows]
+  long long total_rows;
+  // backward
+  const __nv_bfloat16* dout;    // [rows][o_stride]
+  const float* delta;           // [Hq][total_rows] rowsum(dO * O)
+  __nv_bfloat16* dq;            // written at column q_col0 + h*D of rows with stride dqkv_stride
+  __nv_bfloat16* dk;
+  __nv_bfloat16* dv;
+  int dqkv_stride;
+  float scale;                  // softmax scale (natural units)
+};
+
+__device__ __forceinline__ void seq_bounds(const AttnParams& p, int b, int& start, int& len) {
+  if (p.cu_seqlens) {
+    start = p.cu_seqlens[b];
+    len = p.cu_seqlens[b + 1] - start;
+  } else {
+    start = b * p.S;
+    len = p.S;
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// forward
+// ------------------------------------------------------------------------------------------------
+template <int D>
+struct FwdSmem {
+  static constexpr int TILE = 128 * D * 2;
+  static constexpr int KV_STAGES = 2;
+  static constexpr int Q_OFF = 0;
+  static constexpr int K_OFF = 2 * TILE;
+  static constexpr int V_OFF = K_OFF + KV_STAGES * TILE;
+  static constexpr int BAR_OFF = V_OFF + KV_STAGES * TILE;
+  static constexpr int TOTAL = BAR_OFF + 256 + 1024;
+};
+
+constexpr int FWD_THREADS = 320;
+
+template <int D>
+__global__ void __launch_bounds__(FWD_THREADS, 1)
+flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                 const __grid_constant__ CUtensorMap tmV, AttnParams p) {
+  using SM = FwdSmem<D>;
+  constexpr int DCH = D / 64;
+  constexpr uint32_t TMEM_COLS = 512;
+  constexpr uint32_t O_COL0 = 256;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SM::BAR_OFF);
+  uint64_t* q_full = bars;          // [2]
+  uint64_t* k_full = bars + 2;      // [2]
+  uint64_t* k_empty = bars + 4;     // [2]
+  uint64_t* v_full = bars + 6;      // [2]
+  uint64_t* v_empty = bars + 8;     // [2]
+  uint64_t* s_full = bars + 10;     // [2]
+  uint64_t* p_full = bars + 12;     // [2]
+  uint64_t* o_full = bars + 14;     // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int hk = h / p.group;
+  int q_start, Lq, k_start, Lk;
+  seq_bounds(p, b, q_start, Lq);
+  k_start = q_start;
+  Lk = Lq;
+  const int n_qblocks = (Lq + 255) / 256;
+  if ((int)blockIdx.x >= n_qblocks) return;
+  const int qb = n_qblocks - 1 - blockIdx.x;   // heaviest (latest) causal blocks first
+  const int off = Lk - Lq;
+  int r0[2], nkv[2];
+#pragma unroll
+  for (int t = 0; t < 2; ++t) {
+    r0[t] = qb * 256 + t * 128;
+    if (r0[t] >= Lq) {
+      nkv[t] = 0;
+    } else {
+      const int kv_end = p.causal ? min(Lk, r0[t] + 128 + off) : Lk;
+      nkv[t] = (kv_end + 127) / 128;
+    }
+  }
+  const int n = max(nkv[0], nkv[1]);
+
+  if (threadIdx.x == 0) {
+    tma_prefetch_desc(&tmQ);
+    tma_prefetch_desc(&tmK);
+    tma_prefetch_desc(&tmV);
+    for (int i = 0; i < 16; ++i) mbar_init(&bars[i], (i == 12 || i == 13) ? 4 : 1);
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+    tc_fence_before_sync();
+  }
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  bool alive = true;
+
+  if (warp == 0) {
+    if (elect_one_sync()) {
+#pragma unroll
+      for (int t = 0; t < 2; ++t) {
+        if (nkv[t] == 0) continue;
+        mbar_expect_tx(&q_full[t], SM::TILE);
+#pragma unroll
+        for (int j = 0; j < DCH; ++j)
+          tma_load_2d(smem + SM::Q_OFF + t * SM::TILE + j * 16384, &tmQ, &q_full[t], p.q_col0 + h * D + j * 64,
+                      q_start + r0[t]);
+      }
+      for (int i = 0; i < n && alive; ++i) {
+        const int s = i & 1;
+        const uint32_t ph = (i >> 1) & 1u;
+        if (!mbar_wait(&k_empty[s], ph ^ 1u, alive, 400)) break;
+        mbar_expect_tx(&k_full[s], SM::TILE);
+#pragma unroll
+        for (int j = 0; j < DCH; ++j)
+          tma_load_2d(smem + SM::K_OFF + s * SM::TILE + j * 16384, &tmK, &k_full[s], p.k_col0 + hk * D + j * 64,
+                      k_start + i * 128);
+        if (!mbar_wait(&v_empty[s], ph ^ 1u, alive, 401)) break;
+        mbar_expect_tx(&v_full[s], SM::TILE);
+#pragma unroll
+        for (int j = 0; j < DCH; ++j)
+          tma_load_2d(smem + SM::V_OFF + s * SM::TILE + j * 16384, &tmV, &v_full[s], p.v_col0 + hk * D + j * 64,
+                      k_start + i * 128);
+      }
+    }
+  } else if (warp == 1) {
+    if (elect_one_sync()) {
+      const uint32_t idesc_s = make_idesc(128, 128, 1, 1, 0, 0);
+      const uint32_t idesc_o = make_idesc(128, D, 1, 1, 0, 1);
+      auto issue_s = [&](int t, int stage) {
+        const uint32_t qa = smem_u32(smem + SM::Q_OFF + t * SM::TILE);
+        const uint32_t ka = smem_u32(smem + SM::K_OFF + stage * SM::TILE);
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+          const uint32_t o = (k >> 2) * 16384 + (k & 3) * 32;
+          umma_f16_ss(tmem_base + t * 128, make_smem_desc_sw128(qa + o, 16, 1024),
+                      make_smem_desc_sw128(ka + o, 16, 1024), idesc_s, k != 0);
+        }
+        umma_commit(&s_full[t]);
+      };
+      for (int t = 0; t < 2; ++t)
+        if (nkv[t] > 0) mbar_wait(&q_full[t], 0, alive, 500);
+      if (n > 0 && mbar_wait(&k_full[0], 0, alive, 501)) {
+        tc_fence_after_sync();
+        for (int t = 0; t < 2; ++t)
+          if (nkv[t] > 0) issue_s(t, 0);
+        umma_commit(&k_empty[0]);
+      }
+      for (int i = 0; i < n && alive; ++i) {
+        const int s = i & 1;
+        if (!mbar_wait(&v_full[s], (i >> 1) & 1u, alive, 502)) break;
+        bool k_waited = false;
+        for (int t = 0; t < 2 && alive; ++t) {
+          if (i < nkv[t]) {
+            if (!mbar_wait(&p_full[t], i & 1u, alive, 503)) break;
+            tc_fence_after_sync();
+            const uint32_t va = smem_u32(smem + SM::V_OFF + s * SM::TILE);
+#pragma unroll
+            for (int kk = 0; kk < 8; ++kk)
+              umma_f16_ts(tmem_base + O_COL0 + t * D, tmem_base + t * 128 + kk * 8,
+                          make_smem_desc_sw128(va + kk * 2048, 16384, 1024), idesc_o, (i | kk) != 0);
+            if (i == nkv[t] - 1) umma_commit(&o_full[t]);
+          }
+          if (i + 1 < nkv[t]) {
+            if (!k_waited) {
+              if (!mbar_wait(&k_full[(i + 1) & 1], ((i + 1) >> 1) & 1u, alive, 504)) break;
+              tc_fence_after_sync();
+              k_waited = true;
+            }
+            issue_s(t, (i + 1) & 1);
+          }
+        }
+        if (!alive) break;
+        if (i + 1 < n) umma_commit(&k_empty[(i + 1) & 1]);
+        umma_commit(&v_empty[s]);
+      }
+    }
+  } else {
+    // ------------------------------ softmax / correction / epilogue ------------------------------
+    const int t = (warp - 2) >> 2;
+    const int q4 = warp & 3;
+    const int r = q4 * 32 + lane;
+    const int row = r0[t] + r;                  // row inside the sequence
+    const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(q4 * 32) << 16);
+    const uint32_t t_s = t_lane + t * 128;
+    const uint32_t t_o = t_lane + O_COL0 + t * D;
+    float m_used = -INFINITY, l = 0.f;
+    const int nt = nkv[t];
+    for (int i = 0; i < nt && alive; ++i) {
+      if (!mbar_wait(&s_full[t], i & 1u, alive, 600)) break;
+      tc_fence_after_sync();
+      const int c0 = i * 128;
+      const bool need_mask = (p.causal && (c0 + 127 > r0[t] + off)) || (c0 + 128 > Lk);
+      const int limit = p.causal ? min(Lk - 1, row + off) : Lk - 1;   // last visible column
+      // pass 1: row max
+      float mx = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32b_x32(t_s + c * 32, v);
+        tc_wait_ld();
+        if (need_mask) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (c0 + c * 32 + j <= limit) mx = fmaxf(mx, __uint_as_float(v[j]));
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) mx = fmaxf(mx, __uint_as_float(v[j]));
+        }
+      }
+      const float m_new = fmaxf(m_used, mx * p.scale_log2);
+      const bool grow = (m_new - m_used > 8.0f);   // also true on the first block (m_used = -inf)
+      if (__any_sync(0xffffffffu, grow)) {
+        const float alpha = (m_used == -INFINITY) ? 0.f : exp2f(m_used - m_new);
+        m_used = m_new;
+        l *= alpha;
+        if (i > 0) {
+#pragma unroll 1
+          for (int c = 0; c < D / 32; ++c) {
+            uint32_t v[32];
+            tmem_ld_32x32b_x32(t_o + c * 32, v);
+            tc_wait_ld();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * alpha);
+            tmem_st_32x32b_x32(t_o + c * 32, v);
+          }
+        }
+      }
+      const float m_sub = (m_used == -INFINITY) ? 0.f : m_used;
+      // pass 2: P = exp2(S*scale - m), packed bf16 written over the first 64 columns of S
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32], pk[16];
+        tmem_ld_32x32b_x32(t_s + c * 32, v);
+        tc_wait_ld();
+#pragma unroll
+        for (int j = 0; j < 32; j += 2) {
+          float p0 = exp2f(fmaf(__uint_as_float(v[j]), p.scale_log2, -m_sub));
+          float p1 = exp2f(fmaf(__uint_as_float(v[j + 1]), p.scale_log2, -m_sub));
+          if (need_mask) {
+            if (c0 + c * 32 + j > limit) p0 = 0.f;
+            if (c0 + c * 32 + j + 1 > limit) p1 = 0.f;
+          }
+          l += p0 + p1;
+          pk[j >> 1] = pack_bf16x2(p0, p1);
+        }
+        tmem_st_32x32b_x16(t_s + c * 16, pk);
+      }
+      tc_wait_st();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&p_full[t]);
+    }
+    if (nt > 0 && alive && mbar_wait(&o_full[t], 0, alive, 601)) {
+      tc_fence_after_sync();
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      const bool valid = row < Lq;
+      __nv_bfloat16* dst = p.o + static_cast<size_t>(q_start + row) * p.o_stride + h * D;
+#pragma unroll 1
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32b_x32(t_o + c * 32, v);
+        tc_wait_ld();
+        if (valid) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            uint4 o4;
+            o4.x = pack_bf16x2(__uint_as_float(v[8 * j]) * inv, __uint_as_float(v[8 * j + 1]) * inv);
+            o4.y = pack_bf16x2(__uint_as_float(v[8 * j + 2]) * inv, __uint_as_float(v[8 * j + 3]) * inv);
+            o4.z = pack_bf16x2(__uint_as_float(v[8 * j + 4]) * inv, __uint_as_float(v[8 * j + 5]) * inv);
+            o4.w = pack_bf16x2(__uint_as_float(v[8 * j + 6]) * inv, __uint_as_float(v[8 * j + 7]) * inv);
+            *reinterpret_cast<uint4*>(dst + c * 32 + j * 8) = o4;
+          }
+        }
+      }
+      if (valid && p.lse)
+        p.lse[static_cast<size_t>(h) * p.total_rows + q_start + row] =
+            l > 0.f ? (m_used + log2f(l)) * 0.6931471805599453f : -INFINITY;
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// delta[h][row] = sum_d dO[row][h*D + d] * O[row][h*D + d]
+__global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ dout,
+                                  float* __restrict__ delta, long long total_rows, int Hq, int D, int o_stride) {
+  const long long gw = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (gw >= total_rows * Hq) return;
+  const long long row = gw / Hq;
+  const int h = static_cast<int>(gw - row * Hq);
+  const __nv_bfloat16* a = o + row * o_stride + h * D;
+  const __nv_bfloat16* g = dout + row * o_stride + h * D;
+  float s = 0.f;
+  for (int d = lane * 2; d < D; d += 64) {
+    const float2 x = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(a + d));
+    const float2 y = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(g + d));
+    s += x.x * y.x + x.y * y.y;
+  }
+  s = warp_sum(s);
+  if (lane == 0) delta[static_cast<size_t>(h) * total_rows + row] = s;
+}
+
+template <int D>
+static int launch_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const AttnParams& p,
+                      int max_len, cudaStream_t st) {
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(flash_fwd_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         FwdSmem<D>::TOTAL);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  dim3 grid((max_len + 255) / 256, p.Hq, p.B);
+  flash_fwd_kernel<D><<<grid, FWD_THREADS, FwdSmem<D>::TOTAL, st>>>(tq, tk, tv, p);
+  return (int)cudaGetLastError();
+}
+
+}  // namespace ts
+
+TS_DEFINE_ERROR_API(ts_attention)
+
+using namespace ts;
+
+// q, k, v: bf16 row-major token matrices [total_rows][*_stride]; head h of q starts at column h*D (+ col0).
+// They may alias one fused qkv buffer (pass the same base with different col0).
+// cu_seqlens: device int32 [B+1] for packed documents or nullptr for B sequences of S tokens.
+// max_len: longest sequence (host knowledge; S for the uniform case).
+extern "C" int ts_flash_fwd(const void* q, const void* k, const void* v, void* o, float* lse, long long total_rows,
+                            int q_stride, int k_stride, int v_stride, int o_stride, int q_col0, int k_col0,
+                            int v_col0, int Hq, int Hkv, int D, int B, int S, const int* cu_seqlens, int max_len,
+                            int causal, float scale, void* stream) {
+  if ((D != 64 && D != 128) || Hq % Hkv != 0 || total_rows <= 0) return -10;
+  CUtensorMap tq, tk, tv;
+  int rc = make_tmap_2d(&tq, q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)total_rows, (uint64_t)q_stride,
+                        (uint64_t)q_stride, 128, 64);
+  if (rc) return rc * 100 - 1;
+  rc = make_tmap_2d(&tk, k, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)total_rows, (uint64_t)k_stride,
+                    (uint64_t)k_stride, 128, 64);
+  if (rc) return rc * 100 - 2;
+  rc = make_tmap_2d(&tv, v, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)total_rows, (uint64_t)v_stride,
+                    (uint64_t)v_stride, 128, 64);
+  if (rc) return rc * 100 - 3;
+  AttnParams p{};
+  p.q_col0 = q_col0; p.k_col0 = k_col0; p.v_col0 = v_col0;
+  p.Hq = Hq; p.Hkv = Hkv; p.group = Hq / Hkv; p.B = B; p.S = S; p.cu_seqlens = cu_seqlens; p.causal = causal;
+  p.scale = scale; p.scale_log2 = scale * 1.4426950408889634f;
+  p.o = (__nv_bfloat16*)o; p.o_stride = o_stride; p.lse = lse; p.total_rows = total_rows;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (D == 128) return launch_fwd<128>(tq, tk, tv, p, max_len, st);
+  return launch_fwd<64>(tq, tk, tv, p, max_len, st);
+}
+
+extern "C" int ts_attn_delta(const void* o, const void* dout, float* delta, long long total_rows, int Hq, int D,
+                             int o_stride, void* stream) {
+  const long long warps = total_rows * Hq;
+  const int threads = 256;
+  const long long blocks = (warps * 32 + threads - 1) / threads;
+  attn_delta_kernel<<<(unsigned)blocks, threads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      (const __nv_bfloat16*)o, (const __nv_bfloat16*)dout, delta, total_rows, Hq, D, o_stride);
+  return (int)cudaGetLastError();
+}

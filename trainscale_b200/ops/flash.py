@@ -1,24 +1,99 @@
-"""CUDA flash attention binding (csrc/attention.cu) with autograd."""
+"""Binding of the tcgen05 flash-attention kernels (csrc/attention.cu) with autograd.
+
+Inputs are token-major: a fused qkv buffer [B, S, (Hq + 2 Hkv) * D] (or separate q / k / v views of it); the
+kernels address heads through TMA coordinates, so nothing is split, transposed or made contiguous first.
+"""
 from __future__ import annotations
 
+import ctypes
 import math
 
 import torch
-import torch.nn.functional as F
+
+from . import _lib
+
+_ll = ctypes.c_longlong
+_f = ctypes.c_float
 
 
 def supported(head_dim: int, window, softcap) -> bool:
     return head_dim in (64, 128) and not window and not softcap
 
 
-def flash_attention_qkv(qkv, n_heads, n_kv_heads, head_dim, causal=True, scale=None, cu_seqlens=None):
-    # interim library path until the tcgen05 kernels land
-    B, S, _ = qkv.shape
-    q, k, v = qkv.split((n_heads * head_dim, n_kv_heads * head_dim, n_kv_heads * head_dim), dim=-1)
-    q = q.view(B, S, n_heads, head_dim).transpose(1, 2)
-    k = k.view(B, S, n_kv_heads, head_dim).transpose(1, 2)
-    v = v.view(B, S, n_kv_heads, head_dim).transpose(1, 2)
+def _fwd(qkv2d, Hq, Hkv, D, B, S, cu_seqlens, max_len, causal, scale):
+    lib = _lib.load("attention")
+    rows, width = qkv2d.shape
+    o = torch.empty(rows, Hq * D, dtype=qkv2d.dtype, device=qkv2d.device)
+    lse = torch.empty(Hq, rows, dtype=torch.float32, device=qkv2d.device)
+    rc = lib.ts_flash_fwd(_lib.ptr(qkv2d), _lib.ptr(qkv2d), _lib.ptr(qkv2d), _lib.ptr(o), _lib.ptr(lse), _ll(rows),
+                          width, width, width, Hq * D, 0, Hq * D, (Hq + Hkv) * D, Hq, Hkv, D, B, S,
+                          _lib.ptr(cu_seqlens), max_len, int(causal), _f(scale), _lib.stream_ptr())
+    _lib.check(rc, "ts_flash_fwd")
+    return o, lse
+
+
+def _bwd(qkv2d, o, lse, dout, Hq, Hkv, D, B, S, cu_seqlens, max_len, causal, scale):
+    lib = _lib.load("attention")
+    rows, width = qkv2d.shape
+    dqkv = torch.empty_like(qkv2d)
+    delta = torch.empty(Hq, rows, dtype=torch.float32, device=qkv2d.device)
+    rc = lib.ts_attn_delta(_lib.ptr(o), _lib.ptr(dout), _lib.ptr(delta), _ll(rows), Hq, D, Hq * D, _lib.stream_ptr())
+    _lib.check(rc, "ts_attn_delta")
+    rc = lib.ts_flash_bwd(_lib.ptr(qkv2d), _lib.ptr(qkv2d), _lib.ptr(qkv2d), _lib.ptr(dout), _lib.ptr(lse),
+                          _lib.ptr(delta), _lib.ptr(dqkv), _ll(rows), width, Hq * D, 0, Hq * D, (Hq + Hkv) * D, Hq, Hkv,
+                          D, B, S, _lib.ptr(cu_seqlens), max_len, int(causal), _f(scale), _lib.stream_ptr())
+    _lib.check(rc, "ts_flash_bwd")
+    return dqkv
+
+
+class _FlashQKV(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, qkv, Hq, Hkv, D, causal, scale, cu_seqlens, max_len):
+        B, S, W = qkv.shape
+        q2 = qkv.reshape(B * S, W)
+        if not q2.is_contiguous():
+            q2 = q2.contiguous()
+        if cu_seqlens is not None:
+            nb, ml = cu_seqlens.numel() - 1, int(max_len or S * B)
+            o, lse = _fwd(q2, Hq, Hkv, D, nb, 0, cu_seqlens, ml, causal, scale)
+        else:
+            o, lse = _fwd(q2, Hq, Hkv, D, B, S, None, S, causal, scale)
+        ctx.save_for_backward(q2, o, lse, cu_seqlens)
+        ctx.args = (Hq, Hkv, D, B, S, causal, scale, max_len)
+        return o.view(B, S, Hq * D)
+
+    @staticmethod
+    def backward(ctx, dout):
+        q2, o, lse, cu = ctx.saved_tensors
+        Hq, Hkv, D, B, S, causal, scale, max_len = ctx.args
+        d2 = dout.reshape(B * S, Hq * D)
+        if not d2.is_contiguous():
+            d2 = d2.contiguous()
+        if cu is not None:
+            dqkv = _bwd(q2, o, lse, d2, Hq, Hkv, D, cu.numel() - 1, 0, cu, int(max_len or S * B), causal, scale)
+        else:
+            dqkv = _bwd(q2, o, lse, d2, Hq, Hkv, D, B, S, None, S, causal, scale)
+        return dqkv.view(B, S, -1), None, None, None, None, None, None, None
+
+
+def flash_attention_qkv(qkv: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int, causal: bool = True,
+                        scale: float | None = None, cu_seqlens: torch.Tensor | None = None,
+                        max_seqlen: int | None = None) -> torch.Tensor:
+    scale = scale if scale is not None else 1.0 / math.sqrt(head_dim)
     if cu_seqlens is not None:
-        raise NotImplementedError
-    o = F.scaled_dot_product_attention(q, k, v, is_causal=causal, scale=scale, enable_gqa=n_heads != n_kv_heads)
-    return o.transpose(1, 2).reshape(B, S, n_heads * head_dim)
+        cu_seqlens = cu_seqlens.to(torch.int32)
+    return _FlashQKV.apply(qkv, n_heads, n_kv_heads, head_dim, causal, scale, cu_seqlens, max_seqlen)
+
+
+def flash_forward_only(qkv: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int, causal: bool = True,
+                       scale: float | None = None, cu_seqlens: torch.Tensor | None = None, max_seqlen: int | None = None):
+    """(out [B,S,Hq*D], lse [Hq, B*S]) without autograd."""
+    B, S, W = qkv.shape
+    scale = scale if scale is not None else 1.0 / math.sqrt(head_dim)
+    q2 = qkv.reshape(B * S, W)
+    if cu_seqlens is not None:
+        cu = cu_seqlens.to(torch.int32)
+        o, lse = _fwd(q2, n_heads, n_kv_heads, head_dim, cu.numel() - 1, 0, cu, int(max_seqlen or B * S), causal, scale)
+    else:
+        o, lse = _fwd(q2, n_heads, n_kv_heads, head_dim, B, S, None, S, causal, scale)
+    return o.view(B, S, -1), lse
