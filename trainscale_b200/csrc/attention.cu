@@ -338,6 +338,475 @@ __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __n
   if (lane == 0) delta[static_cast<size_t>(h) * total_rows + row] = s;
 }
 
+
+// ------------------------------------------------------------------------------------------------
+// backward, kernel 1: dK / dV.  One CTA owns a 128-row K/V tile of one kv head and walks the 64-row query
+// sub-tiles of every query head in its group.  TMEM: two (S^T | dP^T) buffers of 64+64 columns, dV and dK
+// accumulators.  P^T and dS^T are written back over S^T / dP^T as packed bf16 and fed to the MMA from TMEM.
+// ------------------------------------------------------------------------------------------------
+template <int D>
+struct BwdSmem {
+  static constexpr int BIG = 128 * D * 2;     // resident 128-row tile
+  static constexpr int SMALL = 64 * D * 2;    // streamed 64-row tile
+  static constexpr int STAGES = 3;
+  static constexpr int A_OFF = 0;             // resident tile 0 (K or Q)
+  static constexpr int B_OFF = BIG;           // resident tile 1 (V or dO)
+  static constexpr int S0_OFF = 2 * BIG;      // streamed tile 0 ring (Q or K)
+  static constexpr int S1_OFF = S0_OFF + STAGES * SMALL;   // streamed tile 1 ring (dO or V)
+  static constexpr int VEC_OFF = S1_OFF + STAGES * SMALL;  // 2 x (64 lse + 64 delta) floats
+  static constexpr int BAR_OFF = VEC_OFF + 1024;
+  static constexpr int TOTAL = BAR_OFF + 256 + 1024;
+};
+
+constexpr int BWD_THREADS = 192;
+
+__device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+
+template <int D>
+__global__ void __launch_bounds__(BWD_THREADS, 1)
+flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_constant__ CUtensorMap tmK128,
+                      const __grid_constant__ CUtensorMap tmV128, const __grid_constant__ CUtensorMap tmdO64,
+                      AttnParams p) {
+  using SM = BwdSmem<D>;
+  constexpr int DCH = D / 64;
+  constexpr int STAGES = SM::STAGES;
+  constexpr uint32_t TMEM_COLS = 512;
+  constexpr uint32_t DV_COL = 256, DK_COL = 384;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  float* vec = reinterpret_cast<float*>(smem + SM::VEC_OFF);   // [2][128]: lse2[64], delta[64]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SM::BAR_OFF);
+  uint64_t* kv_full = bars;            // [1]
+  uint64_t* qd_full = bars + 1;        // [3]
+  uint64_t* qd_empty = bars + 4;       // [3]
+  uint64_t* s_full = bars + 7;         // [2]
+  uint64_t* p_full = bars + 9;         // [2]
+  uint64_t* acc_full = bars + 11;      // [1]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int j = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+  int q_start, Lq;
+  seq_bounds(p, b, q_start, Lq);
+  const int k_start = q_start, Lk = Lq;
+  if (j * 128 >= Lk) return;
+  const int off = Lk - Lq;
+  const int n_u = (Lq + 63) / 64;
+  const int u_start = p.causal ? max(0, (j * 128 - off) / 64) : 0;
+  const int per_head = n_u - u_start;
+  const int total = per_head * p.group;
+
+  if (threadIdx.x == 0) {
+    tma_prefetch_desc(&tmQ64);
+    tma_prefetch_desc(&tmK128);
+    tma_prefetch_desc(&tmV128);
+    tma_prefetch_desc(&tmdO64);
+    for (int i = 0; i < 12; ++i) mbar_init(&bars[i], (i == 9 || i == 10) ? 4 : 1);
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+    tc_fence_before_sync();
+  }
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  bool alive = true;
+
+  if (warp == 0) {
+    if (elect_one_sync()) {
+      mbar_expect_tx(kv_full, 2 * SM::BIG);
+#pragma unroll
+      for (int c = 0; c < DCH; ++c) {
+        tma_load_2d(smem + SM::A_OFF + c * 16384, &tmK128, kv_full, p.k_col0 + hk * D + c * 64, k_start + j * 128);
+        tma_load_2d(smem + SM::B_OFF + c * 16384, &tmV128, kv_full, p.v_col0 + hk * D + c * 64, k_start + j * 128);
+      }
+      for (int it = 0; it < total && alive; ++it) {
+        const int s = it % STAGES;
+        const uint32_t ph = (it / STAGES) & 1u;
+        const int g = it / per_head, u = u_start + it % per_head;
+        const int h = hk * p.group + g;
+        if (!mbar_wait(&qd_empty[s], ph ^ 1u, alive, 700)) break;
+        mbar_expect_tx(&qd_full[s], 2 * SM::SMALL);
+#pragma unroll
+        for (int c = 0; c < DCH; ++c) {
+          tma_load_2d(smem + SM::S0_OFF + s * SM::SMALL + c * 8192, &tmQ64, &qd_full[s], p.q_col0 + h * D + c * 64,
+                      q_start + u * 64);
+          tma_load_2d(smem + SM::S1_OFF + s * SM::SMALL + c * 8192, &tmdO64, &qd_full[s], h * D + c * 64,
+                      q_start + u * 64);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (elect_one_sync()) {
+      const uint32_t idesc_s = make_idesc(128, 64, 1, 1, 0, 0);
+      const uint32_t idesc_acc = make_idesc(128, D, 1, 1, 0, 1);
+      const uint32_t ka = smem_u32(smem + SM::A_OFF), va = smem_u32(smem + SM::B_OFF);
+      auto issue12 = [&](int it) {
+        const int s = it % STAGES;
+        if (!mbar_wait(&qd_full[s], (it / STAGES) & 1u, alive, 710)) return;
+        tc_fence_after_sync();
+        const uint32_t qa = smem_u32(smem + SM::S0_OFF + s * SM::SMALL);
+        const uint32_t da = smem_u32(smem + SM::S1_OFF + s * SM::SMALL);
+        const uint32_t st = tmem_base + (it & 1) * 128;
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+          const uint32_t oa = (k >> 2) * 16384 + (k & 3) * 32, ob = (k >> 2) * 8192 + (k & 3) * 32;
+          umma_f16_ss(st, make_smem_desc_sw128(ka + oa, 16, 1024), make_smem_desc_sw128(qa + ob, 16, 1024), idesc_s,
+                      k != 0);
+        }
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+          const uint32_t oa = (k >> 2) * 16384 + (k & 3) * 32, ob = (k >> 2) * 8192 + (k & 3) * 32;
+          umma_f16_ss(st + 64, make_smem_desc_sw128(va + oa, 16, 1024), make_smem_desc_sw128(da + ob, 16, 1024),
+                      idesc_s, k != 0);
+        }
+        umma_commit(&s_full[it & 1]);
+      };
+      if (mbar_wait(kv_full, 0, alive, 711)) {
+        issue12(0);
+        if (total > 1 && alive) issue12(1);
+        for (int it = 0; it < total && alive; ++it) {
+          const int bsel = it & 1, s = it % STAGES;
+          if (!mbar_wait(&p_full[bsel], (it >> 1) & 1u, alive, 712)) break;
+          tc_fence_after_sync();
+          const uint32_t qa = smem_u32(smem + SM::S0_OFF + s * SM::SMALL);
+          const uint32_t da = smem_u32(smem + SM::S1_OFF + s * SM::SMALL);
+          const uint32_t st = tmem_base + bsel * 128;
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk)
+            umma_f16_ts(tmem_base + DV_COL, st + kk * 8, make_smem_desc_sw128(da + kk * 2048, 8192, 1024), idesc_acc,
+                        (it | kk) != 0);
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk)
+            umma_f16_ts(tmem_base + DK_COL, st + 64 + kk * 8, make_smem_desc_sw128(qa + kk * 2048, 8192, 1024),
+                        idesc_acc, (it | kk) != 0);
+          umma_commit(&qd_empty[s]);
+          if (it + 2 < total) issue12(it + 2);
+        }
+        if (alive) umma_commit(acc_full);
+      }
+    }
+  } else {
+    const int q4 = warp & 3;
+    const int r = q4 * 32 + lane;            // kv row inside the tile
+    const int ct = threadIdx.x - 64;         // 0..127 among the compute threads
+    const int kv_row = j * 128 + r;
+    const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(q4 * 32) << 16);
+    for (int it = 0; it < total && alive; ++it) {
+      const int g = it / per_head, u = u_start + it % per_head;
+      const int h = hk * p.group + g;
+      float* vb = vec + (it & 1) * 128;
+      {
+        const int c = ct & 63;
+        const int qrow = u * 64 + c;
+        float val = 0.f;
+        if (qrow < Lq) {
+          const size_t idx = static_cast<size_t>(h) * p.total_rows + q_start + qrow;
+          val = (ct < 64) ? p.lse[idx] * 1.4426950408889634f : p.delta[idx];
+        }
+        vb[ct] = val;
+      }
+      named_bar_sync(1, 128);
+      if (!mbar_wait(&s_full[it & 1], (it >> 1) & 1u, alive, 720)) break;
+      tc_fence_after_sync();
+      const uint32_t t_s = t_lane + (it & 1) * 128;
+      const bool need_mask = (p.causal && (j * 128 + 127 > u * 64 + off)) || (u * 64 + 64 > Lq) || (j * 128 + 128 > Lk);
+#pragma unroll 1
+      for (int cc = 0; cc < 2; ++cc) {
+        uint32_t sv[32], dv[32], pp[16], ds[16];
+        tmem_ld_32x32b_x32(t_s + cc * 32, sv);
+        tmem_ld_32x32b_x32(t_s + 64 + cc * 32, dv);
+        tc_wait_ld();
+#pragma unroll
+        for (int e = 0; e < 32; e += 2) {
+          float pv[2], dsv[2];
+#pragma unroll
+          for (int x = 0; x < 2; ++x) {
+            const int c = cc * 32 + e + x;
+            float pe = exp2f(fmaf(__uint_as_float(sv[e + x]), p.scale_log2, -vb[c]));
+            if (need_mask) {
+              const int qrow = u * 64 + c;
+              const bool ok = (kv_row < Lk) && (qrow < Lq) && (!p.causal || kv_row <= qrow + off);
+              if (!ok) pe = 0.f;
+            }
+            pv[x] = pe;
+            dsv[x] = pe * (__uint_as_float(dv[e + x]) - vb[64 + c]);
+          }
+          pp[e >> 1] = pack_bf16x2(pv[0], pv[1]);
+          ds[e >> 1] = pack_bf16x2(dsv[0], dsv[1]);
+        }
+        tmem_st_32x32b_x16(t_s + cc * 16, pp);
+        tmem_st_32x32b_x16(t_s + 64 + cc * 16, ds);
+      }
+      tc_wait_st();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&p_full[it & 1]);
+    }
+    if (alive && mbar_wait(acc_full, 0, alive, 721)) {
+      tc_fence_after_sync();
+      const bool valid = kv_row < Lk;
+      __nv_bfloat16* dvp = p.dv + static_cast<size_t>(k_start + kv_row) * p.dqkv_stride + p.v_col0 + hk * D;
+      __nv_bfloat16* dkp = p.dk + static_cast<size_t>(k_start + kv_row) * p.dqkv_stride + p.k_col0 + hk * D;
+#pragma unroll 1
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32b_x32(t_lane + DV_COL + c * 32, v);
+        tc_wait_ld();
+        if (valid) {
+#pragma unroll
+          for (int x = 0; x < 4; ++x) {
+            uint4 o4;
+            o4.x = pack_bf16x2(__uint_as_float(v[8 * x]), __uint_as_float(v[8 * x + 1]));
+            o4.y = pack_bf16x2(__uint_as_float(v[8 * x + 2]), __uint_as_float(v[8 * x + 3]));
+            o4.z = pack_bf16x2(__uint_as_float(v[8 * x + 4]), __uint_as_float(v[8 * x + 5]));
+            o4.w = pack_bf16x2(__uint_as_float(v[8 * x + 6]), __uint_as_float(v[8 * x + 7]));
+            *reinterpret_cast<uint4*>(dvp + c * 32 + x * 8) = o4;
+          }
+        }
+        tmem_ld_32x32b_x32(t_lane + DK_COL + c * 32, v);
+        tc_wait_ld();
+        if (valid) {
+#pragma unroll
+          for (int x = 0; x < 4; ++x) {
+            uint4 o4;
+            o4.x = pack_bf16x2(__uint_as_float(v[8 * x]) * p.scale, __uint_as_float(v[8 * x + 1]) * p.scale);
+            o4.y = pack_bf16x2(__uint_as_float(v[8 * x + 2]) * p.scale, __uint_as_float(v[8 * x + 3]) * p.scale);
+            o4.z = pack_bf16x2(__uint_as_float(v[8 * x + 4]) * p.scale, __uint_as_float(v[8 * x + 5]) * p.scale);
+            o4.w = pack_bf16x2(__uint_as_float(v[8 * x + 6]) * p.scale, __uint_as_float(v[8 * x + 7]) * p.scale);
+            *reinterpret_cast<uint4*>(dkp + c * 32 + x * 8) = o4;
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// backward, kernel 2: dQ.  One CTA owns a 128-row query tile of one head (Q and dO resident) and walks the
+// 64-row K/V sub-tiles it can see.  TMEM: two (S | dP) buffers of 64+64 columns and the dQ accumulator.
+// ------------------------------------------------------------------------------------------------
+template <int D>
+__global__ void __launch_bounds__(BWD_THREADS, 1)
+flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ128, const __grid_constant__ CUtensorMap tmK64,
+                    const __grid_constant__ CUtensorMap tmV64, const __grid_constant__ CUtensorMap tmdO128,
+                    AttnParams p) {
+  using SM = BwdSmem<D>;
+  constexpr int DCH = D / 64;
+  constexpr int STAGES = SM::STAGES;
+  constexpr uint32_t TMEM_COLS = 512;
+  constexpr uint32_t DQ_COL = 256;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SM::BAR_OFF);
+  uint64_t* q_full = bars;             // [1]
+  uint64_t* kv_full = bars + 1;        // [3]
+  uint64_t* kv_empty = bars + 4;       // [3]
+  uint64_t* s_full = bars + 7;         // [2]
+  uint64_t* p_full = bars + 9;         // [2]
+  uint64_t* acc_full = bars + 11;      // [1]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int hk = h / p.group;
+  int q_start, Lq;
+  seq_bounds(p, b, q_start, Lq);
+  const int k_start = q_start, Lk = Lq;
+  const int n_qt = (Lq + 127) / 128;
+  if ((int)blockIdx.x >= n_qt) return;
+  const int i = n_qt - 1 - blockIdx.x;
+  const int off = Lk - Lq;
+  const int kv_end = p.causal ? min(Lk, i * 128 + 128 + off) : Lk;
+  const int total = (kv_end + 63) / 64;
+
+  if (threadIdx.x == 0) {
+    tma_prefetch_desc(&tmQ128);
+    tma_prefetch_desc(&tmK64);
+    tma_prefetch_desc(&tmV64);
+    tma_prefetch_desc(&tmdO128);
+    for (int x = 0; x < 12; ++x) mbar_init(&bars[x], (x == 9 || x == 10) ? 4 : 1);
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+    tc_fence_before_sync();
+  }
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  bool alive = true;
+
+  if (warp == 0) {
+    if (elect_one_sync()) {
+      mbar_expect_tx(q_full, 2 * SM::BIG);
+#pragma unroll
+      for (int c = 0; c < DCH; ++c) {
+        tma_load_2d(smem + SM::A_OFF + c * 16384, &tmQ128, q_full, p.q_col0 + h * D + c * 64, q_start + i * 128);
+        tma_load_2d(smem + SM::B_OFF + c * 16384, &tmdO128, q_full, h * D + c * 64, q_start + i * 128);
+      }
+      for (int it = 0; it < total && alive; ++it) {
+        const int s = it % STAGES;
+        if (!mbar_wait(&kv_empty[s], ((it / STAGES) & 1u) ^ 1u, alive, 800)) break;
+        mbar_expect_tx(&kv_full[s], 2 * SM::SMALL);
+#pragma unroll
+        for (int c = 0; c < DCH; ++c) {
+          tma_load_2d(smem + SM::S0_OFF + s * SM::SMALL + c * 8192, &tmK64, &kv_full[s], p.k_col0 + hk * D + c * 64,
+                      k_start + it * 64);
+          tma_load_2d(smem + SM::S1_OFF + s * SM::SMALL + c * 8192, &tmV64, &kv_full[s], p.v_col0 + hk * D + c * 64,
+                      k_start + it * 64);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (elect_one_sync()) {
+      const uint32_t idesc_s = make_idesc(128, 64, 1, 1, 0, 0);
+      const uint32_t idesc_acc = make_idesc(128, D, 1, 1, 0, 1);
+      const uint32_t qa = smem_u32(smem + SM::A_OFF), da = smem_u32(smem + SM::B_OFF);
+      auto issue12 = [&](int it) {
+        const int s = it % STAGES;
+        if (!mbar_wait(&kv_full[s], (it / STAGES) & 1u, alive, 810)) return;
+        tc_fence_after_sync();
+        const uint32_t ka = smem_u32(smem + SM::S0_OFF + s * SM::SMALL);
+        const uint32_t va = smem_u32(smem + SM::S1_OFF + s * SM::SMALL);
+        const uint32_t st = tmem_base + (it & 1) * 128;
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+          const uint32_t oa = (k >> 2) * 16384 + (k & 3) * 32, ob = (k >> 2) * 8192 + (k & 3) * 32;
+          umma_f16_ss(st, make_smem_desc_sw128(qa + oa, 16, 1024), make_smem_desc_sw128(ka + ob, 16, 1024), idesc_s,
+                      k != 0);
+        }
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+          const uint32_t oa = (k >> 2) * 16384 + (k & 3) * 32, ob = (k >> 2) * 8192 + (k & 3) * 32;
+          umma_f16_ss(st + 64, make_smem_desc_sw128(da + oa, 16, 1024), make_smem_desc_sw128(va + ob, 16, 1024),
+                      idesc_s, k != 0);
+        }
+        umma_commit(&s_full[it & 1]);
+      };
+      if (mbar_wait(q_full, 0, alive, 811)) {
+        issue12(0);
+        if (total > 1 && alive) issue12(1);
+        for (int it = 0; it < total && alive; ++it) {
+          const int bsel = it & 1, s = it % STAGES;
+          if (!mbar_wait(&p_full[bsel], (it >> 1) & 1u, alive, 812)) break;
+          tc_fence_after_sync();
+          const uint32_t ka = smem_u32(smem + SM::S0_OFF + s * SM::SMALL);
+          const uint32_t st = tmem_base + bsel * 128;
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk)
+            umma_f16_ts(tmem_base + DQ_COL, st + 64 + kk * 8, make_smem_desc_sw128(ka + kk * 2048, 8192, 1024),
+                        idesc_acc, (it | kk) != 0);
+          umma_commit(&kv_empty[s]);
+          if (it + 2 < total) issue12(it + 2);
+        }
+        if (alive) umma_commit(acc_full);
+      }
+    }
+  } else {
+    const int q4 = warp & 3;
+    const int r = q4 * 32 + lane;
+    const int qrow = i * 128 + r;
+    const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(q4 * 32) << 16);
+    float lse2 = 0.f, delta = 0.f;
+    if (qrow < Lq) {
+      const size_t idx = static_cast<size_t>(h) * p.total_rows + q_start + qrow;
+      lse2 = p.lse[idx] * 1.4426950408889634f;
+      delta = p.delta[idx];
+    }
+    const int limit = (qrow < Lq) ? (p.causal ? min(Lk - 1, qrow + off) : Lk - 1) : -1;
+    for (int it = 0; it < total && alive; ++it) {
+      if (!mbar_wait(&s_full[it & 1], (it >> 1) & 1u, alive, 820)) break;
+      tc_fence_after_sync();
+      const uint32_t t_s = t_lane + (it & 1) * 128;
+      const bool need_mask = (it * 64 + 63 > i * 128 + off && p.causal) || (it * 64 + 64 > Lk) || (i * 128 + 128 > Lq);
+#pragma unroll 1
+      for (int cc = 0; cc < 2; ++cc) {
+        uint32_t sv[32], dv[32], ds[16];
+        tmem_ld_32x32b_x32(t_s + cc * 32, sv);
+        tmem_ld_32x32b_x32(t_s + 64 + cc * 32, dv);
+        tc_wait_ld();
+#pragma unroll
+        for (int e = 0; e < 32; e += 2) {
+          float dsv[2];
+#pragma unroll
+          for (int x = 0; x < 2; ++x) {
+            float pe = exp2f(fmaf(__uint_as_float(sv[e + x]), p.scale_log2, -lse2));
+            if (need_mask && (it * 64 + cc * 32 + e + x > limit)) pe = 0.f;
+            dsv[x] = pe * (__uint_as_float(dv[e + x]) - delta);
+          }
+          ds[e >> 1] = pack_bf16x2(dsv[0], dsv[1]);
+        }
+        tmem_st_32x32b_x16(t_s + 64 + cc * 16, ds);
+      }
+      tc_wait_st();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&p_full[it & 1]);
+    }
+    if (alive && mbar_wait(acc_full, 0, alive, 821)) {
+      tc_fence_after_sync();
+      const bool valid = qrow < Lq;
+      __nv_bfloat16* dqp = p.dq + static_cast<size_t>(q_start + qrow) * p.dqkv_stride + p.q_col0 + h * D;
+#pragma unroll 1
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32b_x32(t_lane + DQ_COL + c * 32, v);
+        tc_wait_ld();
+        if (valid) {
+#pragma unroll
+          for (int x = 0; x < 4; ++x) {
+            uint4 o4;
+            o4.x = pack_bf16x2(__uint_as_float(v[8 * x]) * p.scale, __uint_as_float(v[8 * x + 1]) * p.scale);
+            o4.y = pack_bf16x2(__uint_as_float(v[8 * x + 2]) * p.scale, __uint_as_float(v[8 * x + 3]) * p.scale);
+            o4.z = pack_bf16x2(__uint_as_float(v[8 * x + 4]) * p.scale, __uint_as_float(v[8 * x + 5]) * p.scale);
+            o4.w = pack_bf16x2(__uint_as_float(v[8 * x + 6]) * p.scale, __uint_as_float(v[8 * x + 7]) * p.scale);
+            *reinterpret_cast<uint4*>(dqp + c * 32 + x * 8) = o4;
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+template <int D>
+static int launch_bwd(const CUtensorMap* m, const AttnParams& p, int max_len, cudaStream_t st) {
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(flash_bwd_dkdv_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         BwdSmem<D>::TOTAL);
+    if (e != cudaSuccess) return (int)e;
+    e = cudaFuncSetAttribute(flash_bwd_dq_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdSmem<D>::TOTAL);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  // m: [0]=q64 [1]=k128 [2]=v128 [3]=do64 [4]=q128 [5]=k64 [6]=v64 [7]=do128
+  dim3 g1((max_len + 127) / 128, p.Hkv, p.B);
+  flash_bwd_dkdv_kernel<D><<<g1, BWD_THREADS, BwdSmem<D>::TOTAL, st>>>(m[0], m[1], m[2], m[3], p);
+  dim3 g2((max_len + 127) / 128, p.Hq, p.B);
+  flash_bwd_dq_kernel<D><<<g2, BWD_THREADS, BwdSmem<D>::TOTAL, st>>>(m[4], m[5], m[6], m[7], p);
+  return (int)cudaGetLastError();
+}
+
 template <int D>
 static int launch_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const AttnParams& p,
                       int max_len, cudaStream_t st) {
@@ -396,4 +865,36 @@ extern "C" int ts_attn_delta(const void* o, const void* dout, float* delta, long
   attn_delta_kernel<<<(unsigned)blocks, threads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       (const __nv_bfloat16*)o, (const __nv_bfloat16*)dout, delta, total_rows, Hq, D, o_stride);
   return (int)cudaGetLastError();
+}
+
+// Gradient of ts_flash_fwd. dq/dk/dv are written into `dqkv` (same row layout and column offsets as q/k/v inside
+// a fused buffer of row stride `qkv_stride`); every element of the q|k|v column range is written.
+extern "C" int ts_flash_bwd(const void* q, const void* k, const void* v, const void* dout, const float* lse,
+                            const float* delta, void* dqkv, long long total_rows, int qkv_stride, int o_stride,
+                            int q_col0, int k_col0, int v_col0, int Hq, int Hkv, int D, int B, int S,
+                            const int* cu_seqlens, int max_len, int causal, float scale, void* stream) {
+  if ((D != 64 && D != 128) || Hq % Hkv != 0 || total_rows <= 0) return -10;
+  CUtensorMap m[8];
+  const void* bases[4] = {q, k, v, dout};
+  const int strides[4] = {qkv_stride, qkv_stride, qkv_stride, o_stride};
+  const int small_first[4] = {1, 0, 0, 1};   // q, dO are streamed (64 rows) in the dK/dV kernel; k, v in the dQ kernel
+  for (int t = 0; t < 4; ++t) {
+    int rc = make_tmap_2d(&m[t], bases[t], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)total_rows,
+                          (uint64_t)strides[t], (uint64_t)strides[t], small_first[t] ? 64 : 128, 64);
+    if (rc) return rc * 100 - 10 - t;
+    rc = make_tmap_2d(&m[4 + t], bases[t], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)total_rows,
+                      (uint64_t)strides[t], (uint64_t)strides[t], small_first[t] ? 128 : 64, 64);
+    if (rc) return rc * 100 - 20 - t;
+  }
+  AttnParams p{};
+  p.q_col0 = q_col0; p.k_col0 = k_col0; p.v_col0 = v_col0;
+  p.Hq = Hq; p.Hkv = Hkv; p.group = Hq / Hkv; p.B = B; p.S = S; p.cu_seqlens = cu_seqlens; p.causal = causal;
+  p.scale = scale; p.scale_log2 = scale * 1.4426950408889634f;
+  p.o_stride = o_stride; p.lse = const_cast<float*>(lse); p.delta = delta; p.total_rows = total_rows;
+  p.dout = (const __nv_bfloat16*)dout;
+  p.dq = p.dk = p.dv = (__nv_bfloat16*)dqkv;
+  p.dqkv_stride = qkv_stride;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (D == 128) return launch_bwd<128>(m, p, max_len, st);
+  return launch_bwd<64>(m, p, max_len, st);
 }
