@@ -77,7 +77,7 @@ def test_rmsnorm_fwd_bwd(rows, H, with_res):
     (y.float() * gy.float()).sum().add((r.float() * gr.float()).sum()).backward()
     xr, wr = x.detach().float().requires_grad_(), w.detach().float().requires_grad_()
     rr = res.detach().float().requires_grad_() if with_res else None
-    h = xr if rr is None else (xr + rr).to(torch.bfloat16).float() + ((xr + rr) - (xr + rr).detach())
+    h = xr if rr is None else (xr + rr).detach().to(torch.bfloat16).float() + ((xr + rr) - (xr + rr).detach())
     yr = h * torch.rsqrt(h.pow(2).mean(-1, keepdim=True) + 1e-5) * wr
     ((yr * gy.float()).sum() + (h * gr.float()).sum()).backward()
     assert rel_err(y, yr) < 1e-2

@@ -25,7 +25,18 @@ typedef CUresult (*PFN_encodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_
                                     const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                     CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
+// The driver entry point needs a current context in the calling thread; a thread that has not made a
+// runtime call yet (e.g. an autograd worker) has none, so bind the primary context once per thread.
+inline void ensure_thread_context() {
+  static thread_local bool ready = false;
+  if (!ready) {
+    cudaFree(0);
+    ready = true;
+  }
+}
+
 inline PFN_encodeTiled get_encode_fn() {
+  ensure_thread_context();
   static PFN_encodeTiled fn = nullptr;
   static std::once_flag once;
   std::call_once(once, [] {
@@ -53,6 +64,9 @@ inline int make_tmap_2d(CUtensorMap* out, const void* base, CUtensorMapDataType 
   cuuint32_t estr[2] = {1, 1};
   CUresult r = fn(out, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    fprintf(stderr, "[trainscale_b200] cuTensorMapEncodeTiled failed (%d): base=%p rows=%llu cols=%llu ld=%llu box=%ux%u\n",
+            (int)r, base, (unsigned long long)rows, (unsigned long long)cols, (unsigned long long)ld, box_rows, box_cols);
   return r == CUDA_SUCCESS ? 0 : -3;
 }
 
