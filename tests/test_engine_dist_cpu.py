@@ -1,0 +1,21 @@
+"""gloo / CPU multi-process tests of the flat engine's sharding, reduction and re-gather logic."""
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+
+CASE = Path(__file__).parent / "dist_cases" / "engine_equivalence.py"
+
+
+def launch(nproc, *args, port=29611, timeout=300):
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
+           "--master-addr", "127.0.0.1", "--master-port", str(port), str(CASE), *args]
+    return subprocess.run(cmd, capture_output=True, text=True, timeout=timeout)
+
+
+@pytest.mark.parametrize("strategy,port", [("SHARD_GRAD_OP", 29611), ("NO_SHARD", 29612)])
+def test_two_rank_engine_matches_single_process(strategy, port):
+    r = launch(2, "--device", "cpu", "--strategy", strategy, port=port)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    assert "ok=True" in r.stdout

@@ -378,6 +378,14 @@ class FlatShardedEngine:
             for seg in u.segments():
                 sl = slice(seg.start, seg.end)
                 out = u.flat_param[s0 + seg.start:s0 + seg.end]
+                if fused_norm and cfg.optimizer == "adamw":
+                    from . import fused_comm
+                    fused_comm.adamw_bcast(self._symm, u.flat_param, s0 + seg.start, u.master[sl], u.exp_avg[sl],
+                                           u.exp_avg_sq[sl], g[sl], lr=lr, beta1=b1, beta2=b2,
+                                           eps=self.param_groups[0]["eps"], weight_decay=seg.weight_decay,
+                                           step=self.step_count, sumsq=self.norm_sq, max_norm=cfg.max_grad_norm,
+                                           skip_flag=skip)
+                    continue
                 if cfg.optimizer == "lion":
                     optim_ops.lion_flat_(u.master[sl], u.exp_avg[sl], g[sl], out, lr=lr, beta1=b1, beta2=b2,
                                          weight_decay=seg.weight_decay)
@@ -387,7 +395,12 @@ class FlatShardedEngine:
                                           step=self.step_count, sumsq=self.norm_sq, max_norm=cfg.max_grad_norm,
                                           skip_flag=skip)
         if self.world > 1 and cfg.sharding_strategy != "NO_SHARD":
-            self._all_gather_params()
+            if fused_norm and cfg.optimizer == "adamw":
+                # the update kernels already stored into every rank's buffer: one barrier makes them visible
+                from . import fused_comm
+                fused_comm.barrier(self._symm, self.units[0].flat_param)
+            else:
+                self._all_gather_params()
         self.zero_grad()
         return self.last_grad_norm
 

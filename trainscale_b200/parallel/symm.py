@@ -1,0 +1,96 @@
+"""Symmetric (peer-mapped) device memory for the fused compute+collective kernels.
+
+Every rank allocates the same sizes in the same order; each allocation is rendezvoused once and yields the peer
+addresses of the buffer on all ranks, the addresses of its signal pad and, when the fabric supports it, an
+NVSwitch multicast address.  Allocation and handle exchange go through `torch.distributed._symmetric_memory`
+(CUDA VMM + fabric/posix handles over the process group's store); the kernels in csrc/comm.cu only ever see raw
+addresses.  The reference has no counterpart (it issues every collective through torch.distributed -> NCCL,
+data_pipeline/trainer/kernels/distributed_kernels.py:480-1072).
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from dataclasses import dataclass
+
+import torch
+import torch.distributed as dist
+
+
+@dataclass
+class SymmBuffer:
+    tensor: torch.Tensor
+    handle: object
+    peer_ptrs: ctypes.Array        # c_ulonglong[world]
+    pad_ptrs: ctypes.Array
+    multicast_ptr: int
+    epochs: dict
+
+    def next_epoch(self, key: str) -> int:
+        e = self.epochs.get(key, 0) + 1
+        self.epochs[key] = e
+        return e
+
+
+class SymmetricHeap:
+    """Allocator + registry of symmetric buffers of one process group."""
+
+    def __init__(self, group, device):
+        self.group = group if group is not None else dist.group.WORLD
+        self.device = torch.device(device)
+        self.rank = dist.get_rank(self.group)
+        self.world = dist.get_world_size(self.group)
+        self._by_ptr: dict[int, SymmBuffer] = {}
+        self.use_multicast = os.environ.get("TS_SYMM_MULTICAST", "1") != "0"
+        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        # generous by default (ranks can be seconds apart on the first step); tests shorten it
+        self.wait_cycles = int(float(os.environ.get("TS_SYMM_WAIT_SECONDS", "60")) * 1.9e9)
+
+    @classmethod
+    def try_create(cls, group, device):
+        if os.environ.get("TS_DISABLE_SYMM", "0") == "1":
+            return None
+        try:
+            import torch.distributed._symmetric_memory as symm_mem  # noqa: F401
+            heap = cls(group, device)
+            probe = heap.alloc(1024, torch.float32)   # fails here if peer access / VMM sharing is unavailable
+            del probe
+            return heap
+        except Exception as e:   # noqa: BLE001 - any failure means "use the NCCL path"
+            if os.environ.get("TS_SYMM_DEBUG"):
+                import traceback
+                traceback.print_exc()
+            if dist.get_rank() == 0:
+                print(f"[trainscale_b200] symmetric memory unavailable ({type(e).__name__}: {e}); using NCCL path")
+            return None
+
+    def alloc(self, numel: int, dtype: torch.dtype) -> torch.Tensor:
+        import torch.distributed._symmetric_memory as symm_mem
+        t = symm_mem.empty(numel, dtype=dtype, device=self.device)
+        h = symm_mem.rendezvous(t, self.group)
+        t.zero_()
+        arr = ctypes.c_ulonglong * self.world
+        mc = int(h.multicast_ptr) if (self.use_multicast and h.has_multicast_support(self.device.type, self.device.index)
+                                      ) else 0
+        buf = SymmBuffer(t, h, arr(*[int(p) for p in h.buffer_ptrs]), arr(*[int(p) for p in h.signal_pad_ptrs]), mc, {})
+        self._by_ptr[t.data_ptr()] = buf
+        return t
+
+    def lookup(self, t: torch.Tensor) -> tuple[SymmBuffer, int]:
+        """(buffer, byte offset) of a tensor that is a view into a symmetric allocation."""
+        p = t.data_ptr()
+        b = self._by_ptr.get(p)
+        if b is not None:
+            return b, 0
+        for base, buf in self._by_ptr.items():
+            size = buf.tensor.numel() * buf.tensor.element_size()
+            if base <= p < base + size:
+                return buf, p - base
+        raise KeyError("tensor is not backed by symmetric memory")
+
+    def check_status(self) -> None:
+        if int(self.status.item()) != 0:
+            self.status.zero_()
+            from ..core.errors import CommunicationError
+            raise CommunicationError("a peer did not arrive within the wait limit of a fused collective",
+                                     rank=self.rank, world=self.world)
