@@ -1,0 +1,89 @@
+"""DataLoader construction (fluent builder + one-call helpers).
+
+After data_pipeline/data/dataloader_factory.py:45-372: `DataLoaderBuilder` with `_create_sampler`
+(DistributedSampler(seed, drop_last) | seeded RandomSampler | SequentialSampler), `build_dataloader`, and
+`build_distributed_dataloaders` (every rank's loader in one process, for tests).
+"""
+from __future__ import annotations
+
+from typing import Callable
+
+import torch
+from torch.utils.data import DataLoader, DistributedSampler, IterableDataset, RandomSampler, SequentialSampler
+
+from ..core.errors import DataLoadingError
+
+
+class DataLoaderBuilder:
+    def __init__(self, dataset):
+        self.dataset = dataset
+        self._batch_size, self._shuffle, self._seed = 8, False, 42
+        self._num_workers, self._pin, self._drop_last = 0, False, False
+        self._prefetch, self._persistent = None, False
+        self._collate: Callable | None = None
+        self._dist, self._rank, self._world = False, 0, 1
+
+    def batch_size(self, n: int):
+        if n <= 0:
+            raise DataLoadingError("batch_size must be positive", batch_size=n)
+        self._batch_size = n
+        return self
+
+    def shuffle(self, on: bool = True, seed: int = 42):
+        self._shuffle, self._seed = on, seed
+        return self
+
+    def workers(self, n: int, prefetch_factor: int | None = None, persistent: bool = False):
+        self._num_workers, self._prefetch, self._persistent = n, prefetch_factor, persistent
+        return self
+
+    def pin_memory(self, on: bool = True):
+        self._pin = on
+        return self
+
+    def drop_last(self, on: bool = True):
+        self._drop_last = on
+        return self
+
+    def collate(self, fn: Callable):
+        self._collate = fn
+        return self
+
+    def distributed(self, rank: int, world_size: int):
+        self._dist, self._rank, self._world = world_size > 1, rank, world_size
+        return self
+
+    def _create_sampler(self):
+        if isinstance(self.dataset, IterableDataset):
+            return None
+        if self._dist:
+            return DistributedSampler(self.dataset, num_replicas=self._world, rank=self._rank, shuffle=self._shuffle,
+                                      seed=self._seed, drop_last=self._drop_last)
+        if self._shuffle:
+            return RandomSampler(self.dataset, generator=torch.Generator().manual_seed(self._seed))
+        return SequentialSampler(self.dataset)
+
+    def build(self) -> DataLoader:
+        kw = dict(batch_size=self._batch_size, sampler=self._create_sampler(), num_workers=self._num_workers,
+                  pin_memory=self._pin and torch.cuda.is_available(), drop_last=self._drop_last, collate_fn=self._collate)
+        if self._num_workers > 0:
+            if self._prefetch:
+                kw["prefetch_factor"] = self._prefetch
+            kw["persistent_workers"] = self._persistent
+        return DataLoader(self.dataset, **kw)
+
+
+def build_dataloader(dataset, batch_size: int = 8, shuffle: bool = False, seed: int = 42, num_workers: int = 0,
+                     pin_memory: bool = False, drop_last: bool = False, collate_fn=None, distributed: bool = False,
+                     rank: int = 0, world_size: int = 1, prefetch_factor=None, persistent_workers=False) -> DataLoader:
+    b = (DataLoaderBuilder(dataset).batch_size(batch_size).shuffle(shuffle, seed)
+         .workers(num_workers, prefetch_factor, persistent_workers).pin_memory(pin_memory).drop_last(drop_last))
+    if collate_fn is not None:
+        b.collate(collate_fn)
+    if distributed:
+        b.distributed(rank, world_size)
+    return b.build()
+
+
+def build_distributed_dataloaders(dataset, world_size: int, **kw) -> list[DataLoader]:
+    return [build_dataloader(dataset, distributed=True, rank=r, world_size=world_size, **kw) for r in range(world_size)]

@@ -1,0 +1,111 @@
+"""Trainer-side sequence packing over already tokenised examples.
+
+After data_pipeline/trainer/packing.py:39-375: first-fit-decreasing over lengths, `pack_sequences` emitting
+input_ids / attention_mask / labels / position_ids + `cu_seqlens` (int32), block-diagonal additive mask,
+`unpack_sequences`, `PackedDataset`, `get_packing_stats`.  Here `cu_seqlens` feeds the variable-length flash
+attention kernel directly (the reference emits it but has no kernel that consumes it).
+"""
+from __future__ import annotations
+
+from typing import Sequence
+
+import torch
+from torch.utils.data import Dataset
+
+
+def first_fit_decreasing(lengths: Sequence[int], max_length: int) -> list[list[int]]:
+    order = sorted(range(len(lengths)), key=lambda i: -lengths[i])
+    bins, free = [], []
+    for i in order:
+        n = min(lengths[i], max_length)
+        for b in range(len(bins)):
+            if free[b] >= n:
+                bins[b].append(i)
+                free[b] -= n
+                break
+        else:
+            bins.append([i])
+            free.append(max_length - n)
+    return bins
+
+
+def pack_sequences(sequences: Sequence[dict], max_length: int, pad_token_id: int = 0, label_pad: int = -100) -> list[dict]:
+    """Each input dict holds 1-D `input_ids` (and optionally `labels`); returns packed dicts of tensors."""
+    lengths = [min(len(s["input_ids"]), max_length) for s in sequences]
+    out = []
+    for b in first_fit_decreasing(lengths, max_length):
+        ids, labels, pos, cu = [], [], [], [0]
+        for i in b:
+            x = torch.as_tensor(sequences[i]["input_ids"])[:max_length]
+            y = torch.as_tensor(sequences[i].get("labels", sequences[i]["input_ids"]))[:max_length]
+            ids.append(x)
+            labels.append(y)
+            pos.append(torch.arange(len(x)))
+            cu.append(cu[-1] + len(x))
+        ids, labels, pos = torch.cat(ids), torch.cat(labels), torch.cat(pos)
+        n = len(ids)
+        pad = max_length - n
+        mask = torch.cat((torch.ones(n, dtype=torch.long), torch.zeros(pad, dtype=torch.long)))
+        if pad:
+            ids = torch.cat((ids, torch.full((pad,), pad_token_id, dtype=ids.dtype)))
+            labels = torch.cat((labels, torch.full((pad,), label_pad, dtype=labels.dtype)))
+            pos = torch.cat((pos, torch.zeros(pad, dtype=pos.dtype)))
+        doc = torch.full((max_length,), -1, dtype=torch.long)
+        for k in range(len(b)):
+            doc[cu[k]:cu[k + 1]] = k
+        out.append({"input_ids": ids, "attention_mask": mask, "labels": labels, "position_ids": pos,
+                    "document_ids": doc, "cu_seqlens": torch.tensor(cu, dtype=torch.int32), "source_indices": list(b)})
+    return out
+
+
+def create_packed_attention_mask(cu_seqlens: torch.Tensor, total_length: int, dtype=torch.float32) -> torch.Tensor:
+    """Block-diagonal causal additive mask [L, L]: 0 where attention is allowed, -inf elsewhere."""
+    m = torch.full((total_length, total_length), float("-inf"), dtype=dtype)
+    cu = cu_seqlens.tolist()
+    for a, b in zip(cu[:-1], cu[1:]):
+        n = b - a
+        m[a:b, a:b] = torch.triu(torch.full((n, n), float("-inf"), dtype=dtype), diagonal=1)
+    return m
+
+
+def unpack_sequences(packed: torch.Tensor, cu_seqlens: torch.Tensor) -> list[torch.Tensor]:
+    cu = cu_seqlens.tolist()
+    return [packed[..., a:b, :] if packed.dim() > 1 else packed[a:b] for a, b in zip(cu[:-1], cu[1:])]
+
+
+class PackedDataset(Dataset):
+    def __init__(self, dataset, max_length: int, pad_token_id: int = 0, window: int = 1024):
+        seqs = [dataset[i] for i in range(len(dataset))]
+        self.items = []
+        for s in range(0, len(seqs), window):   # pack inside windows so that memory stays bounded
+            self.items += pack_sequences(seqs[s:s + window], max_length, pad_token_id)
+
+    def __len__(self):
+        return len(self.items)
+
+    def __getitem__(self, i):
+        d = dict(self.items[i])
+        d.pop("source_indices", None)
+        d.pop("cu_seqlens", None)   # ragged across items; rebuilt from document_ids by the collate function
+        return d
+
+
+def cu_seqlens_from_document_ids(document_ids: torch.Tensor) -> tuple[torch.Tensor, int]:
+    """[B, S] document ids (pad = -1) -> int32 cu_seqlens over the flattened B*S axis and the longest segment.
+    Padding tails become their own segments so that every row belongs to exactly one segment."""
+    flat = document_ids.reshape(-1)
+    S = document_ids.shape[-1]
+    pos = torch.arange(flat.numel(), device=flat.device)
+    change = torch.ones_like(flat, dtype=torch.bool)
+    change[1:] = (flat[1:] != flat[:-1]) | (pos[1:] % S == 0)
+    starts = pos[change]
+    cu = torch.cat((starts, torch.tensor([flat.numel()], device=flat.device))).to(torch.int32)
+    return cu, int((cu[1:] - cu[:-1]).max())
+
+
+def get_packing_stats(lengths: Sequence[int], max_length: int) -> dict:
+    bins = first_fit_decreasing(lengths, max_length)
+    used = sum(min(n, max_length) for n in lengths)
+    return {"num_sequences": len(lengths), "num_packed": len(bins), "efficiency": used / max(1, len(bins) * max_length),
+            "padding_efficiency": used / max(1, len(lengths) * max_length),
+            "compression_ratio": len(lengths) / max(1, len(bins))}
