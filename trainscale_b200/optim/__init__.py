@@ -1,0 +1,582 @@
+"""Optimizer zoo behind `create_optimizer` (torch.optim.Optimizer subclasses).
+
+Covers the reference's list (data_pipeline/trainer/optimizers/{base,adamw,lamb,adafactor,sota_optimizers}.py):
+AdamW / FusedAdamW (the sm_100a flat kernel per tensor), Adam8bit (block-wise 8-bit moment storage), Lion, LAMB,
+AdaFactor (factored second moment), CAME, SophiaG (Hutchinson / GNB Hessian EMA), Prodigy, ScheduleFreeAdamW, Muon
+(Newton-Schulz orthogonalised momentum), ADOPT, plus `clip_grad_norm_` with the reference's coefficient
+`max_norm / (norm + 1e-6)` clamped to 1 (data_pipeline/trainer/distributed/sota_utils.py:1294-1299).
+The sharded hot path does not go through these classes: the flat engine owns its AdamW / Lion state
+(parallel/flat_engine.py); these serve non-sharded models, LoRA adapters and the remaining optimizer types.
+"""
+from __future__ import annotations
+
+import math
+from typing import Iterable
+
+import torch
+from torch.optim import Optimizer
+
+from ..ops import optim as K
+
+
+@torch.no_grad()
+def clip_grad_norm_(parameters: Iterable[torch.Tensor], max_norm: float, norm_type: float = 2.0) -> torch.Tensor:
+    grads = [p.grad for p in parameters if p.grad is not None]
+    if not grads:
+        return torch.zeros(())
+    if norm_type == float("inf"):
+        total = torch.stack([g.abs().max() for g in grads]).max()
+    else:
+        total = torch.stack([torch.linalg.vector_norm(g.float(), norm_type) for g in grads]).norm(norm_type)
+    coef = (max_norm / (total + 1e-6)).clamp(max=1.0)
+    for g in grads:
+        g.mul_(coef.to(g.dtype))
+    return total
+
+
+class AdamW(Optimizer):
+    """Decoupled AdamW. CUDA fp32 tensors with bf16/fp32 grads use the fused flat kernel (one launch per tensor)."""
+
+    def __init__(self, params, lr=2e-5, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01, amsgrad=False, fused=True):
+        super().__init__(params, dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay, amsgrad=amsgrad, fused=fused))
+
+    @torch.no_grad()
+    def step(self, closure=None):
+        loss = closure() if closure is not None else None
+        for g in self.param_groups:
+            b1, b2 = g["betas"]
+            for p in g["params"]:
+                if p.grad is None:
+                    continue
+                st = self.state[p]
+                if not st:
+                    st["step"] = 0
+                    st["exp_avg"] = torch.zeros_like(p, dtype=torch.float32)
+                    st["exp_avg_sq"] = torch.zeros_like(p, dtype=torch.float32)
+                    if g["amsgrad"]:
+                        st["max_exp_avg_sq"] = torch.zeros_like(p, dtype=torch.float32)
+                    if p.dtype != torch.float32:
+                        st["master"] = p.detach().float().clone()
+                st["step"] += 1
+                master = st.get("master", p)
+                grad = p.grad
+                if g["fused"] and p.is_cuda and not g["amsgrad"] and grad.dtype in (torch.float32, torch.bfloat16) \
+                        and master.is_contiguous() and grad.is_contiguous():
+                    low = p.view(-1) if p.dtype == torch.bfloat16 else None
+                    K.adamw_flat_(master.view(-1), st["exp_avg"].view(-1), st["exp_avg_sq"].view(-1), grad.view(-1), low,
+                                  lr=g["lr"], beta1=b1, beta2=b2, eps=g["eps"], weight_decay=g["weight_decay"],
+                                  step=st["step"])
+                    if "master" in st and low is None:
+                        p.copy_(master)
+                    continue
+                gf = grad.float()
+                st["exp_avg"].mul_(b1).add_(gf, alpha=1 - b1)
+                st["exp_avg_sq"].mul_(b2).addcmul_(gf, gf, value=1 - b2)
+                bc1, bc2 = 1 - b1 ** st["step"], 1 - b2 ** st["step"]
+                v = st["exp_avg_sq"]
+                if g["amsgrad"]:
+                    torch.maximum(st["max_exp_avg_sq"], v, out=st["max_exp_avg_sq"])
+                    v = st["max_exp_avg_sq"]
+                master.mul_(1 - g["lr"] * g["weight_decay"])
+                master.addcdiv_(st["exp_avg"] / bc1, (v / bc2).sqrt().add_(g["eps"]), value=-g["lr"])
+                if master is not p:
+                    p.copy_(master)
+        return loss
+
+
+FusedAdamW = AdamW
+
+
+def _quantize_blockwise(x: torch.Tensor, block: int = 256):
+    flat = x.reshape(-1)
+    pad = (-flat.numel()) % block
+    if pad:
+        flat = torch.cat((flat, flat.new_zeros(pad)))
+    b = flat.view(-1, block)
+    scale = b.abs().amax(dim=1, keepdim=True).clamp(min=1e-12)
+    q = torch.round(b / scale * 127).to(torch.int8)
+    return q, scale.squeeze(1)
+
+
+def _dequantize_blockwise(q: torch.Tensor, scale: torch.Tensor, shape, numel: int):
+    return (q.float() * (scale.unsqueeze(1) / 127)).reshape(-1)[:numel].view(shape)
+
+
+class Adam8bit(Optimizer):
+    """AdamW whose moments are stored as block-wise int8 (+ one fp32 scale per 256 values); the second moment is
+    stored as sqrt(v) to keep its dynamic range inside 8 bits."""
+
+    def __init__(self, params, lr=2e-5, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01, block_size=256,
+                 min_8bit_size=4096):
+        super().__init__(params, dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay, block_size=block_size,
+                                      min_8bit_size=min_8bit_size))
+
+    @torch.no_grad()
+    def step(self, closure=None):
+        loss = closure() if closure is not None else None
+        for g in self.param_groups:
+            b1, b2 = g["betas"]
+            for p in g["params"]:
+                if p.grad is None:
+                    continue
+                st = self.state[p]
+                small = p.numel() < g["min_8bit_size"]
+                if not st:
+                    st["step"] = 0
+                    z = torch.zeros_like(p, dtype=torch.float32)
+                    if small:
+                        st["m"], st["v"] = z, z.clone()
+                    else:
+                        st["m_q"], st["m_s"] = _quantize_blockwise(z, g["block_size"])
+                        st["v_q"], st["v_s"] = _quantize_blockwise(z, g["block_size"])
+                st["step"] += 1
+                gf = p.grad.float()
+                if small:
+                    m, v = st["m"], st["v"]
+                else:
+                    m = _dequantize_blockwise(st["m_q"], st["m_s"], p.shape, p.numel())
+                    v = _dequantize_blockwise(st["v_q"], st["v_s"], p.shape, p.numel()).pow(2)
+                m = m.mul(b1).add(gf, alpha=1 - b1)
+                v = v.mul(b2).addcmul(gf, gf, value=1 - b2)
+                bc1, bc2 = 1 - b1 ** st["step"], 1 - b2 ** st["step"]
+                pf = p.float().mul_(1 - g["lr"] * g["weight_decay"])
+                pf.addcdiv_(m / bc1, (v / bc2).sqrt().add_(g["eps"]), value=-g["lr"])
+                p.copy_(pf)
+                if small:
+                    st["m"], st["v"] = m, v
+                else:
+                    st["m_q"], st["m_s"] = _quantize_blockwise(m, g["block_size"])
+                    st["v_q"], st["v_s"] = _quantize_blockwise(v.sqrt(), g["block_size"])
+        return loss
+
+    def state_bytes(self) -> int:
+        n = 0
+        for st in self.state.values():
+            for v in st.values():
+                if torch.is_tensor(v):
+                    n += v.numel() * v.element_size()
+        return n
+
+
+class Lion(Optimizer):
+    def __init__(self, params, lr=1e-4, betas=(0.9, 0.99), weight_decay=0.0):
+        super().__init__(params, dict(lr=lr, betas=betas, weight_decay=weight_decay))
+
+    @torch.no_grad()
+    def step(self, closure=None):
+        loss = closure() if closure is not None else None
+        for g in self.param_groups:
+            b1, b2 = g["betas"]
+            for p in g["params"]:
+                if p.grad is None:
+                    continue
+                st = self.state[p]
+                if not st:
+                    st["exp_avg"] = torch.zeros_like(p, dtype=torch.float32)
+                gf = p.grad.float()
+                u = (st["exp_avg"] * b1 + gf * (1 - b1)).sign_()
+                pf = p.float().mul_(1 - g["lr"] * g["weight_decay"]).add_(u, alpha=-g["lr"])
+                p.copy_(pf)
+                st["exp_avg"].mul_(b2).add_(gf, alpha=1 - b2)
+        return loss
+
+
+class LAMB(Optimizer):
+    def __init__(self, params, lr=1e-3, betas=(0.9, 0.999), eps=1e-6, weight_decay=0.01, clamp_trust=(0.0, 10.0)):
+        super().__init__(params, dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay, clamp_trust=clamp_trust))
+
+    @torch.no_grad()
+    def step(self, closure=None):
+        loss = closure() if closure is not None else None
+        for g in self.param_groups:
+            b1, b2 = g["betas"]
+            for p in g["params"]:
+                if p.grad is None:
+                    continue
+                st = self.state[p]
+                if not st:
+                    st["step"], st["m"], st["v"] = 0, torch.zeros_like(p, dtype=torch.float32), torch.zeros_like(p, dtype=torch.float32)
+                st["step"] += 1
+                gf = p.grad.float()
+                st["m"].mul_(b1).add_(gf, alpha=1 - b1)
+                st["v"].mul_(b2).addcmul_(gf, gf, value=1 - b2)
+                mh, vh = st["m"] / (1 - b1 ** st["step"]), st["v"] / (1 - b2 ** st["step"])
+                pf = p.float()
+                upd = mh / (vh.sqrt() + g["eps"]) + g["weight_decay"] * pf
+                wn, un = pf.norm(), upd.norm()
+                trust = torch.where((wn > 0) & (un > 0), wn / un, torch.ones_like(wn)).clamp(*g["clamp_trust"])
+                p.copy_(pf - g["lr"] * trust * upd)
+        return loss
+
+
+class AdaFactor(Optimizer):
+    """Factored second moments for matrices (row / column EMA), update clipping by RMS, optional relative step."""
+
+    def __init__(self, params, lr=None, eps=(1e-30, 1e-3), clip_threshold=1.0, decay_rate=-0.8, beta1=None,
+                 weight_decay=0.0, scale_parameter=True, relative_step=True, warmup_init=False):
+        super().__init__(params, dict(lr=lr, eps=eps, clip_threshold=clip_threshold, decay_rate=decay_rate, beta1=beta1,
+                                      weight_decay=weight_decay, scale_parameter=scale_parameter,
+                                      relative_step=relative_step and lr is None, warmup_init=warmup_init))
+
+    @staticmethod
+    def _rms(x):
+        return x.norm() / math.sqrt(max(1, x.numel()))
+
+    @torch.no_grad()
+    def step(self, closure=None):
+        loss = closure() if closure is not None else None
+        for g in self.param_groups:
+            for p in g["params"]:
+                if p.grad is None:
+                    continue
+                gf = p.grad.float()
+                st = self.state[p]
+                factored = gf.dim() >= 2
+                if not st:
+                    st["step"] = 0
+                    if factored:
+                        st["row"] = torch.zeros(gf.shape[:-1], device=gf.device)
+                        st["col"] = torch.zeros(gf.shape[:-2] + gf.shape[-1:], device=gf.device)
+                    else:
+                        st["v"] = torch.zeros_like(gf)
+                    if g["beta1"] is not None:
+                        st["m"] = torch.zeros_like(gf)
+                    st["rms"] = 0.0
+                st["step"] += 1
+                pf = p.float()
+                st["rms"] = float(self._rms(pf))
+                if g["relative_step"]:
+                    min_step = 1e-6 * st["step"] if g["warmup_init"] else 1e-2
+                    lr = min(min_step, 1.0 / math.sqrt(st["step"]))
+                else:
+                    lr = g["lr"]
+                if g["scale_parameter"]:
+                    lr = lr * max(g["eps"][1], st["rms"])
+                beta2 = 1.0 - st["step"] ** g["decay_rate"]
+                upd = gf * gf + g["eps"][0]
+                if factored:
+                    st["row"].mul_(beta2).add_(upd.mean(-1), alpha=1 - beta2)
+                    st["col"].mul_(beta2).add_(upd.mean(-2), alpha=1 - beta2)
+                    r = (st["row"] / st["row"].mean(-1, keepdim=True)).rsqrt().unsqueeze(-1)
+                    c = st["col"].unsqueeze(-2).rsqrt()
+                    u = gf * r * c
+                else:
+                    st["v"].mul_(beta2).add_(upd, alpha=1 - beta2)
+                    u = gf * st["v"].rsqrt()
+                u.div_(max(1.0, float(self._rms(u)) / g["clip_threshold"]))
+                u.mul_(lr)
+                if g["beta1"] is not None:
+                    st["m"].mul_(g["beta1"]).add_(u, alpha=1 - g["beta1"])
+                    u = st["m"]
+                if g["weight_decay"]:
+                    pf.mul_(1 - g["weight_decay"] * lr)
+                p.copy_(pf - u)
+        return loss
+
+
+class CAME(Optimizer):
+    """Confidence-guided AdaFactor: a second factored EMA of the update's instability rescales the step."""
+
+    def __init__(self, params, lr=2e-4, eps=(1e-30, 1e-16), clip_threshold=1.0, betas=(0.9, 0.999, 0.9999), weight_decay=0.0):
+        super().__init__(params, dict(lr=lr, eps=eps, clip_threshold=clip_threshold, betas=betas, weight_decay=weight_decay))
+
+    @torch.no_grad()
+    def step(self, closure=None):
+        loss = closure() if closure is not None else None
+        for g in self.param_groups:
+            b1, b2, b3 = g["betas"]
+            for p in g["params"]:
+                if p.grad is None:
+                    continue
+                gf = p.grad.float()
+                st = self.state[p]
+                fac = gf.dim() >= 2
+                if not st:
+                    st["m"] = torch.zeros_like(gf)
+                    if fac:
+                        st["row"], st["col"] = torch.zeros(gf.shape[:-1], device=gf.device), torch.zeros(gf.shape[:-2] + gf.shape[-1:], device=gf.device)
+                        st["rrow"], st["rcol"] = st["row"].clone(), st["col"].clone()
+                    else:
+                        st["v"] = torch.zeros_like(gf)
+                upd = gf * gf + g["eps"][0]
+                if fac:
+                    st["row"].mul_(b2).add_(upd.mean(-1), alpha=1 - b2)
+                    st["col"].mul_(b2).add_(upd.mean(-2), alpha=1 - b2)
+                    u = gf * (st["row"] / st["row"].mean(-1, keepdim=True)).rsqrt().unsqueeze(-1) * st["col"].unsqueeze(-2).rsqrt()
+                else:
+                    st["v"].mul_(b2).add_(upd, alpha=1 - b2)
+                    u = gf * st["v"].rsqrt()
+                u.div_(max(1.0, float(u.norm() / math.sqrt(u.numel())) / g["clip_threshold"]))
+                st["m"].mul_(b1).add_(u, alpha=1 - b1)
+                if fac:
+                    res = (u - st["m"]) ** 2 + g["eps"][1]
+                    st["rrow"].mul_(b3).add_(res.mean(-1), alpha=1 - b3)
+                    st["rcol"].mul_(b3).add_(res.mean(-2), alpha=1 - b3)
+                    step_ = st["m"] * (st["rrow"] / st["rrow"].mean(-1, keepdim=True)).rsqrt().unsqueeze(-1) * st["rcol"].unsqueeze(-2).rsqrt()
+                else:
+                    step_ = st["m"]
+                pf = p.float()
+                if g["weight_decay"]:
+                    pf.mul_(1 - g["lr"] * g["weight_decay"])
+                p.copy_(pf - g["lr"] * step_)
+        return loss
+
+
+class SophiaG(Optimizer):
+    """Clipped second-order step: p -= lr * clip(m / max(rho * h, eps), 1). Call `update_hessian()` every k steps
+    after a backward on sampled labels (Gauss-Newton-Bartlett) or with `hutchinson=True` grads."""
+
+    def __init__(self, params, lr=1e-4, betas=(0.965, 0.99), rho=0.04, weight_decay=0.1, eps=1e-15):
+        super().__init__(params, dict(lr=lr, betas=betas, rho=rho, weight_decay=weight_decay, eps=eps))
+
+    @torch.no_grad()
+    def update_hessian(self, batch_size: int = 1):
+        for g in self.param_groups:
+            b2 = g["betas"][1]
+            for p in g["params"]:
+                if p.grad is None:
+                    continue
+                st = self.state[p]
+                if "h" not in st:
+                    st["h"] = torch.zeros_like(p, dtype=torch.float32)
+                st["h"].mul_(b2).addcmul_(p.grad.float(), p.grad.float(), value=(1 - b2) * batch_size)
+
+    @torch.no_grad()
+    def step(self, closure=None):
+        loss = closure() if closure is not None else None
+        for g in self.param_groups:
+            b1 = g["betas"][0]
+            for p in g["params"]:
+                if p.grad is None:
+                    continue
+                st = self.state[p]
+                if "m" not in st:
+                    st["m"] = torch.zeros_like(p, dtype=torch.float32)
+                if "h" not in st:
+                    st["h"] = torch.zeros_like(p, dtype=torch.float32)
+                st["m"].mul_(b1).add_(p.grad.float(), alpha=1 - b1)
+                pf = p.float().mul_(1 - g["lr"] * g["weight_decay"])
+                ratio = (st["m"].abs() / (g["rho"] * st["h"] + g["eps"])).clamp(max=1.0)
+                p.copy_(pf - g["lr"] * st["m"].sign() * ratio)
+        return loss
+
+
+class Prodigy(Optimizer):
+    """Parameter-free AdamW: the step size scale d is estimated from <g, x0 - x> / ||s||_1."""
+
+    def __init__(self, params, lr=1.0, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0, d0=1e-6, d_coef=1.0, growth_rate=float("inf")):
+        super().__init__(params, dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay, d=d0, d0=d0, d_coef=d_coef,
+                                      growth_rate=growth_rate, k=0, d_numerator=0.0))
+
+    @torch.no_grad()
+    def step(self, closure=None):
+        loss = closure() if closure is not None else None
+        g0 = self.param_groups[0]
+        b1, b2 = g0["betas"]
+        b3 = math.sqrt(b2)
+        d, lr = g0["d"], g0["lr"]
+        dlr = d * lr
+        num = g0["d_numerator"] * b3
+        denom = 0.0
+        for g in self.param_groups:
+            for p in g["params"]:
+                if p.grad is None:
+                    continue
+                gf = p.grad.float()
+                st = self.state[p]
+                if not st:
+                    st["s"] = torch.zeros_like(gf)
+                    st["p0"] = p.detach().float().clone()
+                    st["m"], st["v"] = torch.zeros_like(gf), torch.zeros_like(gf)
+                num += (d / g0["d0"]) * dlr * float((gf * (st["p0"] - p.float())).sum())
+                st["m"].mul_(b1).add_(gf, alpha=d * (1 - b1))
+                st["v"].mul_(b2).addcmul_(gf, gf, value=d * d * (1 - b2))
+                st["s"].mul_(b3).add_(gf, alpha=(d / g0["d0"]) * dlr)
+                denom += float(st["s"].abs().sum())
+        if denom > 0:
+            d_hat = g0["d_coef"] * num / denom
+            d = max(d, min(d_hat, d * g0["growth_rate"]))
+        for g in self.param_groups:
+            g["d"], g["d_numerator"], g["k"] = d, num, g["k"] + 1
+            for p in g["params"]:
+                if p.grad is None:
+                    continue
+                st = self.state[p]
+                pf = p.float()
+                if g["weight_decay"]:
+                    pf.mul_(1 - g["weight_decay"] * dlr)
+                p.copy_(pf - dlr * st["m"] / (st["v"].sqrt() + d * g["eps"]))
+        return loss
+
+
+class ScheduleFreeAdamW(Optimizer):
+    """Schedule-free AdamW (interpolated iterate y for gradients, averaged iterate x for evaluation).
+    Call `.train()` before training steps and `.eval()` before evaluation / checkpointing."""
+
+    def __init__(self, params, lr=2.5e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0, warmup_steps=0, r=0.0):
+        super().__init__(params, dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay, warmup_steps=warmup_steps,
+                                      r=r, k=0, train_mode=True, weight_sum=0.0))
+
+    @torch.no_grad()
+    def _swap(self, to_train: bool):
+        for g in self.param_groups:
+            if g["train_mode"] == to_train:
+                continue
+            b1 = g["betas"][0]
+            for p in g["params"]:
+                st = self.state.get(p)
+                if st and "z" in st:
+                    w = (1 - b1) if to_train else (1 - 1 / b1)
+                    p.copy_(torch.lerp(p.float(), st["z"], w))
+            g["train_mode"] = to_train
+
+    def train(self):
+        self._swap(True)
+
+    def eval(self):
+        self._swap(False)
+
+    @torch.no_grad()
+    def step(self, closure=None):
+        loss = closure() if closure is not None else None
+        for g in self.param_groups:
+            b1, b2 = g["betas"]
+            k = g["k"] + 1
+            sched = min(1.0, k / g["warmup_steps"]) if g["warmup_steps"] > 0 else 1.0
+            lr = g["lr"] * sched * math.sqrt(1 - b2 ** k)
+            w = (lr ** 2) * (k ** g["r"])
+            g["weight_sum"] += w
+            c = w / g["weight_sum"] if g["weight_sum"] > 0 else 0.0
+            for p in g["params"]:
+                if p.grad is None:
+                    continue
+                st = self.state[p]
+                if not st:
+                    st["z"] = p.detach().float().clone()
+                    st["v"] = torch.zeros_like(p, dtype=torch.float32)
+                gf = p.grad.float()
+                st["v"].mul_(b2).addcmul_(gf, gf, value=1 - b2)
+                gn = gf / (st["v"].sqrt() + g["eps"])
+                y = p.float()
+                if g["weight_decay"]:
+                    gn = gn + g["weight_decay"] * y
+                y = torch.lerp(y, st["z"], c)
+                y.add_(gn, alpha=lr * (b1 * (1 - c) - 1))
+                st["z"].sub_(gn, alpha=lr)
+                p.copy_(y)
+            g["k"] = k
+        return loss
+
+
+def newton_schulz_orthogonalize(G: torch.Tensor, steps: int = 5) -> torch.Tensor:
+    a, b, c = 3.4445, -4.7750, 2.0315
+    X = G.float()
+    t = X.shape[-2] > X.shape[-1]
+    if t:
+        X = X.transpose(-1, -2)
+    X = X / (X.norm(dim=(-2, -1), keepdim=True) + 1e-7)
+    for _ in range(steps):
+        A = X @ X.transpose(-1, -2)
+        X = a * X + (b * A + c * A @ A) @ X
+    return X.transpose(-1, -2) if t else X
+
+
+class Muon(Optimizer):
+    """Momentum + Newton-Schulz orthogonalisation for 2-D weights; AdamW for everything else."""
+
+    def __init__(self, params, lr=0.02, momentum=0.95, nesterov=True, ns_steps=5, weight_decay=0.0,
+                 adamw_lr=3e-4, adamw_betas=(0.9, 0.95), adamw_eps=1e-8):
+        super().__init__(params, dict(lr=lr, momentum=momentum, nesterov=nesterov, ns_steps=ns_steps,
+                                      weight_decay=weight_decay, adamw_lr=adamw_lr, adamw_betas=adamw_betas, adamw_eps=adamw_eps))
+
+    @torch.no_grad()
+    def step(self, closure=None):
+        loss = closure() if closure is not None else None
+        for g in self.param_groups:
+            for p in g["params"]:
+                if p.grad is None:
+                    continue
+                gf = p.grad.float()
+                st = self.state[p]
+                pf = p.float()
+                if gf.dim() == 2 and min(gf.shape) > 1:
+                    if not st:
+                        st["buf"] = torch.zeros_like(gf)
+                    st["buf"].mul_(g["momentum"]).add_(gf)
+                    u = gf.add(st["buf"], alpha=g["momentum"]) if g["nesterov"] else st["buf"]
+                    u = newton_schulz_orthogonalize(u, g["ns_steps"]) * max(1.0, gf.shape[0] / gf.shape[1]) ** 0.5
+                    pf.mul_(1 - g["lr"] * g["weight_decay"]).add_(u, alpha=-g["lr"])
+                else:
+                    if not st:
+                        st["step"], st["m"], st["v"] = 0, torch.zeros_like(gf), torch.zeros_like(gf)
+                    st["step"] += 1
+                    b1, b2 = g["adamw_betas"]
+                    st["m"].mul_(b1).add_(gf, alpha=1 - b1)
+                    st["v"].mul_(b2).addcmul_(gf, gf, value=1 - b2)
+                    pf.addcdiv_(st["m"] / (1 - b1 ** st["step"]), (st["v"] / (1 - b2 ** st["step"])).sqrt() + g["adamw_eps"],
+                                value=-g["adamw_lr"])
+                p.copy_(pf)
+        return loss
+
+
+class ADOPT(Optimizer):
+    """Adam with the second moment of the PREVIOUS step in the normaliser (converges for any beta2)."""
+
+    def __init__(self, params, lr=1e-3, betas=(0.9, 0.9999), eps=1e-6, weight_decay=0.0, clip_lambda=lambda k: k ** 0.25):
+        super().__init__(params, dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay, clip_lambda=clip_lambda))
+
+    @torch.no_grad()
+    def step(self, closure=None):
+        loss = closure() if closure is not None else None
+        for g in self.param_groups:
+            b1, b2 = g["betas"]
+            for p in g["params"]:
+                if p.grad is None:
+                    continue
+                gf = p.grad.float()
+                st = self.state[p]
+                if not st:
+                    st["step"], st["m"], st["v"] = 0, torch.zeros_like(gf), gf * gf
+                    st["step"] = 1
+                    continue
+                st["step"] += 1
+                n = gf / torch.clamp(st["v"].sqrt(), min=g["eps"])
+                if g["clip_lambda"] is not None:
+                    c = g["clip_lambda"](st["step"])
+                    n.clamp_(-c, c)
+                st["m"].mul_(b1).add_(n, alpha=1 - b1)
+                pf = p.float().mul_(1 - g["lr"] * g["weight_decay"])
+                p.copy_(pf - g["lr"] * st["m"])
+                st["v"].mul_(b2).addcmul_(gf, gf, value=1 - b2)
+        return loss
+
+
+_OPTIMIZERS = {"adamw": AdamW, "fused_adamw": AdamW, "adam8bit": Adam8bit, "adamw_8bit": Adam8bit, "lion": Lion,
+               "lamb": LAMB, "adafactor": AdaFactor, "came": CAME, "sophia": SophiaG, "sophiag": SophiaG,
+               "prodigy": Prodigy, "schedule_free": ScheduleFreeAdamW, "schedulefree": ScheduleFreeAdamW, "muon": Muon,
+               "adopt": ADOPT}
+
+
+def create_optimizer(params, config=None, name: str | None = None, **kw) -> Optimizer:
+    """From a SOTAConfig `optimizer` section (or a name + keyword arguments)."""
+    params = [p for p in params if p.requires_grad] if not isinstance(params, list) or (params and torch.is_tensor(params[0])) else params
+    if config is not None:
+        name = name or getattr(config.type, "value", config.type)
+        base = dict(lr=config.learning_rate, weight_decay=config.weight_decay)
+        if name in ("adamw", "fused_adamw", "adam8bit", "lamb", "adopt", "schedule_free", "prodigy"):
+            base["betas"] = tuple(config.betas)
+            base["eps"] = config.eps
+        if name == "lion":
+            base["betas"] = tuple(config.lion_betas)
+        if name == "adafactor":
+            base = dict(lr=config.learning_rate, weight_decay=config.weight_decay, relative_step=False)
+        if name in ("came",):
+            base = dict(lr=config.learning_rate, weight_decay=config.weight_decay)
+        if name in ("sophia", "sophiag", "muon"):
+            base = dict(lr=config.learning_rate, weight_decay=config.weight_decay)
+        base.update(kw)
+        kw = base
+    name = (name or "adamw").lower()
+    if name not in _OPTIMIZERS:
+        raise ValueError(f"unknown optimizer {name!r}; choose from {sorted(_OPTIMIZERS)}")
+    return _OPTIMIZERS[name](params, **kw)
