@@ -19,3 +19,12 @@ def test_two_rank_engine_matches_single_process(strategy, port):
     r = launch(2, "--device", "cpu", "--strategy", strategy, port=port)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
     assert "ok=True" in r.stdout
+
+
+def test_tensor_and_sequence_parallel_match_unsharded():
+    case = Path(__file__).parent / "dist_cases" / "tp_equivalence.py"
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+           "127.0.0.1", "--master-port", "29631", str(case)]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    assert r.stdout.count("ok=True") == 2

@@ -1,0 +1,199 @@
+"""N-D process mesh: pp x dp_replicate x dp_shard x cp x tp (tp innermost), plus ep / etp views for MoE.
+
+Dimension names and derived meshes follow data_pipeline/trainer/distributed/parallel_dims.py:1039-1317
+(dp_shard = -1 means "whatever is left"; fsdp = dp_shard * cp, batch = dp_replicate * dp_shard,
+loss = batch * cp) and the rank layout of data_pipeline/trainer/distributed/tensor_parallel.py:260-306
+(rank = dp * (pp * tp) + pp_idx * tp + tp_idx is the 3-D special case).  Groups are created lazily with
+`dist.new_group` so that the same code runs on NCCL and on gloo (CPU tests).  Topology facts used for defaults
+on B200 / NVSwitch: every GPU of a node reaches every peer at full NVLink bandwidth, so dimension placement inside
+a node is not bandwidth-sensitive; tp and cp are still innermost to keep them inside one node on multi-node jobs.
+"""
+from __future__ import annotations
+
+import itertools
+import os
+from dataclasses import dataclass, field
+from typing import Sequence
+
+import torch
+import torch.distributed as dist
+
+NVLINK5_GBPS_PER_DIRECTION = 900.0
+DIM_ORDER = ("pp", "dp_replicate", "dp_shard", "cp", "tp")
+
+
+@dataclass
+class ParallelDimsConfig:
+    dp_replicate: int = 1
+    dp_shard: int = -1
+    cp: int = 1
+    tp: int = 1
+    pp: int = 1
+    ep: int = 1
+    etp: int = 1
+    sp: bool = False
+    world_size: int = 1
+
+    def resolve(self) -> "ParallelDimsConfig":
+        fixed = self.dp_replicate * self.cp * self.tp * self.pp
+        if self.world_size % fixed != 0:
+            raise ValueError(f"world size {self.world_size} is not divisible by dp_replicate*cp*tp*pp = {fixed}")
+        shard = self.world_size // fixed if self.dp_shard in (-1, 0) else self.dp_shard
+        if shard * fixed != self.world_size:
+            raise ValueError(f"dp_replicate({self.dp_replicate}) * dp_shard({shard}) * cp({self.cp}) * tp({self.tp}) * "
+                             f"pp({self.pp}) != world size {self.world_size}")
+        if self.ep > 1 and (shard * self.cp * self.dp_replicate) % self.ep != 0 and (shard * self.cp) % self.ep != 0:
+            raise ValueError(f"ep({self.ep}) must divide the data-parallel ranks")
+        return ParallelDimsConfig(self.dp_replicate, shard, self.cp, self.tp, self.pp, self.ep, self.etp, self.sp,
+                                  self.world_size)
+
+
+class ParallelDims:
+    """Coordinates of this rank and the process groups along every (possibly flattened) dimension."""
+
+    def __init__(self, cfg: ParallelDimsConfig, rank: int | None = None, create_groups: bool = True):
+        self.cfg = cfg.resolve()
+        self.rank = rank if rank is not None else (dist.get_rank() if dist.is_initialized() else 0)
+        self.sizes = {d: getattr(self.cfg, d) for d in DIM_ORDER}
+        self.coords = self._coords_of(self.rank)
+        self._groups: dict[str, dist.ProcessGroup | None] = {}
+        self._group_ranks: dict[str, list[int]] = {}
+        self._create = create_groups and dist.is_initialized() and dist.get_world_size() > 1
+
+    # ---------------------------------------------------------------- layout arithmetic
+    def _coords_of(self, rank: int) -> dict[str, int]:
+        out, r = {}, rank
+        for d in reversed(DIM_ORDER):
+            out[d] = r % self.sizes[d]
+            r //= self.sizes[d]
+        return out
+
+    def rank_of(self, **coords) -> int:
+        c = dict(self.coords)
+        c.update(coords)
+        r = 0
+        for d in DIM_ORDER:
+            r = r * self.sizes[d] + c[d]
+        return r
+
+    def ranks_along(self, dims: Sequence[str], rank: int | None = None) -> list[int]:
+        """Ranks that share every coordinate with `rank` except along `dims` (ordered, outer dim first)."""
+        base = self._coords_of(self.rank if rank is None else rank)
+        out = []
+        for combo in itertools.product(*[range(self.sizes[d]) for d in dims]):
+            c = dict(base)
+            c.update(dict(zip(dims, combo)))
+            r = 0
+            for d in DIM_ORDER:
+                r = r * self.sizes[d] + c[d]
+            out.append(r)
+        return out
+
+    _FLAT = {"fsdp": ("dp_shard", "cp"), "batch": ("dp_replicate", "dp_shard"), "loss": ("dp_replicate", "dp_shard", "cp"),
+             "dp": ("dp_replicate", "dp_shard"), "dp_cp": ("dp_replicate", "dp_shard", "cp")}
+
+    def dims_of(self, name: str) -> tuple[str, ...]:
+        return self._FLAT.get(name, (name,))
+
+    def size(self, name: str) -> int:
+        n = 1
+        for d in self.dims_of(name):
+            n *= self.sizes[d]
+        return n
+
+    def local_rank(self, name: str) -> int:
+        r = 0
+        for d in self.dims_of(name):
+            r = r * self.sizes[d] + self.coords[d]
+        return r
+
+    def enabled(self, name: str) -> bool:
+        return self.size(name) > 1
+
+    # ---------------------------------------------------------------- groups
+    def group(self, name: str):
+        """Process group along `name` (None when its size is 1 or torch.distributed is not running)."""
+        if name in self._groups:
+            return self._groups[name]
+        dims = self.dims_of(name)
+        if self.size(name) == 1 or not self._create:
+            self._groups[name] = None
+            self._group_ranks[name] = self.ranks_along(dims)
+            return None
+        mine = None
+        seen = set()
+        for r in range(self.cfg.world_size):   # every rank creates every group, in the same order
+            ranks = tuple(self.ranks_along(dims, r))
+            if ranks in seen:
+                continue
+            seen.add(ranks)
+            g = dist.new_group(list(ranks))
+            if self.rank in ranks:
+                mine = g
+                self._group_ranks[name] = list(ranks)
+        self._groups[name] = mine
+        return mine
+
+    def group_ranks(self, name: str) -> list[int]:
+        if name not in self._group_ranks:
+            self.group(name)
+        return self._group_ranks[name]
+
+    # pipeline helpers
+    @property
+    def pp_stage(self) -> int:
+        return self.coords["pp"]
+
+    @property
+    def is_first_stage(self) -> bool:
+        return self.coords["pp"] == 0
+
+    @property
+    def is_last_stage(self) -> bool:
+        return self.coords["pp"] == self.sizes["pp"] - 1
+
+    def pp_neighbor(self, delta: int) -> int:
+        return self.rank_of(pp=(self.coords["pp"] + delta) % self.sizes["pp"])
+
+    def describe(self) -> str:
+        return " x ".join(f"{d}={self.sizes[d]}" for d in DIM_ORDER) + f" | rank {self.rank} at {self.coords}"
+
+
+def create_parallel_dims_from_config(dist_cfg, world_size: int | None = None, rank: int | None = None) -> ParallelDims:
+    """From a SOTAConfig `distributed` section (its `parallel` sub-section and the legacy degree keys)."""
+    p = dist_cfg.parallel
+    ws = world_size if world_size is not None else (dist.get_world_size() if dist.is_initialized() else 1)
+    strat = str(dist_cfg.strategy).lower()
+    pp = p.pp if p.pp > 1 else (dist_cfg.num_pipeline_stages if strat in ("zbpp", "pipeline_zbpp", "pipeline", "pp") else 1)
+    cp = p.cp if p.cp > 1 else (dist_cfg.context_parallel_size if strat in ("context_parallel", "cp") else 1)
+    pp, cp = min(pp, ws), min(cp, ws)
+    return ParallelDims(ParallelDimsConfig(p.dp_replicate, p.dp_shard, cp, p.tp, pp, p.ep, p.etp, p.sp, ws), rank)
+
+
+@dataclass
+class MemoryEstimate:
+    params_gb: float
+    grads_gb: float
+    optimizer_gb: float
+    activations_gb: float
+
+    @property
+    def total_gb(self) -> float:
+        return self.params_gb + self.grads_gb + self.optimizer_gb + self.activations_gb
+
+
+def estimate_memory(n_params: float, dims: ParallelDimsConfig, seq_len: int, micro_batch: int, hidden: int, layers: int,
+                    checkpointing: bool = True, keep_params_gathered: bool = True) -> MemoryEstimate:
+    """Per-GPU memory model for the flat engine (bf16 params + grads, fp32 master + 2 moments sharded over fsdp)."""
+    d = dims.resolve()
+    model_split = d.tp * d.pp
+    shard = d.dp_shard * d.cp
+    p = n_params / model_split
+    params = p * 2 / (1 if keep_params_gathered else shard)
+    grads = p * 2
+    optim = p * 12 / shard
+    tokens = seq_len * micro_batch / (d.cp * (d.tp if d.sp else 1))
+    per_layer = tokens * hidden * 2 * (2 if checkpointing else 34)
+    act = per_layer * layers / d.pp
+    gb = 1 / 2 ** 30
+    return MemoryEstimate(params * gb, grads * gb, optim * gb, act * gb)

@@ -1,0 +1,370 @@
+"""Tensor parallelism (Megatron column / row split) with optional sequence parallelism, for the framework decoder.
+
+Covers data_pipeline/trainer/distributed/tensor_parallel.py:487-2282: the conjugate communication ops as
+autograd functions (copy / reduce / scatter / gather over the hidden dim, all-gather / reduce-scatter over the
+sequence dim), `ColumnParallelLinear`, `RowParallelLinear`, `VocabParallelEmbedding`,
+`vocab_parallel_cross_entropy` (max / sum-exp / target-logit all-reduces), sequence-parallel norm gradient
+all-reduce (data_pipeline/trainer/distributed/finalize_grads.py:148) and `shard_model_for_tensor_parallel`, which
+here slices the trained weights (q/k/v by head, gate/up by column block) instead of re-initialising them.
+
+Two communication back-ends: `nccl` (torch.distributed collectives: the measured baseline path) and `fused`
+(csrc/tp_gemm.cu: all-gather fused into the consuming GEMM, reduce-scatter / all-reduce fused into the producing
+GEMM's epilogue over peer memory).
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+import torch.nn.functional as F
+
+from ..ops import gemm
+
+
+@dataclass
+class TPContext:
+    group: object | None
+    size: int = 1
+    rank: int = 0
+    sequence_parallel: bool = False
+    comm: str = "nccl"          # nccl | fused
+    heap: object | None = None  # SymmetricHeap for the fused path
+
+    @classmethod
+    def from_group(cls, group, sequence_parallel=False, comm="nccl", heap=None) -> "TPContext":
+        if group is None or not dist.is_initialized():
+            return cls(None)
+        return cls(group, dist.get_world_size(group), dist.get_rank(group), sequence_parallel, comm, heap)
+
+    @property
+    def active(self) -> bool:
+        return self.size > 1
+
+
+# ------------------------------------------------------------------------------------------------ raw collectives
+def _all_reduce(x, ctx, op=dist.ReduceOp.SUM):
+    if ctx.active:
+        x = x.contiguous()
+        dist.all_reduce(x, op=op, group=ctx.group)
+    return x
+
+
+def _all_gather_dim(x, ctx, dim):
+    if not ctx.active:
+        return x
+    x = x.contiguous()
+    if dim == 0 or x.dim() == 1:
+        out = torch.empty((x.shape[0] * ctx.size, *x.shape[1:]), dtype=x.dtype, device=x.device)
+        if x.is_cuda:
+            dist.all_gather_into_tensor(out, x, group=ctx.group)
+        else:
+            parts = list(out.chunk(ctx.size, 0))
+            dist.all_gather(parts, x, group=ctx.group)
+        return out
+    parts = [torch.empty_like(x) for _ in range(ctx.size)]
+    dist.all_gather(parts, x, group=ctx.group)
+    return torch.cat(parts, dim=dim)
+
+
+def _reduce_scatter_dim0(x, ctx):
+    if not ctx.active:
+        return x
+    x = x.contiguous()
+    out = torch.empty((x.shape[0] // ctx.size, *x.shape[1:]), dtype=x.dtype, device=x.device)
+    if x.is_cuda:
+        dist.reduce_scatter_tensor(out, x, group=ctx.group)
+    else:   # gloo: all-reduce then slice
+        dist.all_reduce(x, group=ctx.group)
+        out.copy_(x.chunk(ctx.size, 0)[ctx.rank])
+    return out
+
+
+def _split_dim(x, ctx, dim):
+    return x.chunk(ctx.size, dim=dim)[ctx.rank].contiguous() if ctx.active else x
+
+
+# ------------------------------------------------------------------------------------------------ autograd comm ops
+class _CopyToTP(torch.autograd.Function):           # f: identity fwd, all-reduce bwd
+    @staticmethod
+    def forward(ctx, x, tp):
+        ctx.tp = tp
+        return x
+
+    @staticmethod
+    def backward(ctx, g):
+        return _all_reduce(g, ctx.tp), None
+
+
+class _ReduceFromTP(torch.autograd.Function):       # g: all-reduce fwd, identity bwd
+    @staticmethod
+    def forward(ctx, x, tp):
+        return _all_reduce(x, tp)
+
+    @staticmethod
+    def backward(ctx, g):
+        return g, None
+
+
+class _ScatterToTP(torch.autograd.Function):        # split last dim fwd, all-gather bwd
+    @staticmethod
+    def forward(ctx, x, tp):
+        ctx.tp = tp
+        return _split_dim(x, tp, -1)
+
+    @staticmethod
+    def backward(ctx, g):
+        return _all_gather_dim(g, ctx.tp, -1), None
+
+
+class _GatherFromTP(torch.autograd.Function):       # all-gather last dim fwd, split bwd
+    @staticmethod
+    def forward(ctx, x, tp):
+        ctx.tp = tp
+        return _all_gather_dim(x, tp, -1)
+
+    @staticmethod
+    def backward(ctx, g):
+        return _split_dim(g, ctx.tp, -1), None
+
+
+class _GatherSeq(torch.autograd.Function):          # SP: all-gather tokens fwd, reduce-scatter bwd
+    @staticmethod
+    def forward(ctx, x, tp):
+        ctx.tp = tp
+        return _all_gather_dim(x, tp, 0)
+
+    @staticmethod
+    def backward(ctx, g):
+        return _reduce_scatter_dim0(g, ctx.tp), None
+
+
+class _ReduceScatterSeq(torch.autograd.Function):   # SP: reduce-scatter tokens fwd, all-gather bwd
+    @staticmethod
+    def forward(ctx, x, tp):
+        ctx.tp = tp
+        return _reduce_scatter_dim0(x, tp)
+
+    @staticmethod
+    def backward(ctx, g):
+        return _all_gather_dim(g, ctx.tp, 0), None
+
+
+class _ScatterSeq(torch.autograd.Function):         # SP entry: split tokens fwd, all-gather bwd
+    @staticmethod
+    def forward(ctx, x, tp):
+        ctx.tp = tp
+        return _split_dim(x, tp, 0)
+
+    @staticmethod
+    def backward(ctx, g):
+        return _all_gather_dim(g, ctx.tp, 0), None
+
+
+def copy_to_tensor_parallel_region(x, tp): return _CopyToTP.apply(x, tp) if tp.active else x
+def reduce_from_tensor_parallel_region(x, tp): return _ReduceFromTP.apply(x, tp) if tp.active else x
+def scatter_to_tensor_parallel_region(x, tp): return _ScatterToTP.apply(x, tp) if tp.active else x
+def gather_from_tensor_parallel_region(x, tp): return _GatherFromTP.apply(x, tp) if tp.active else x
+def all_gather_from_sequence_parallel_region(x, tp): return _GatherSeq.apply(x, tp) if tp.active else x
+def reduce_scatter_to_sequence_parallel_region(x, tp): return _ReduceScatterSeq.apply(x, tp) if tp.active else x
+def scatter_to_sequence_parallel_region(x, tp): return _ScatterSeq.apply(x, tp) if tp.active else x
+
+
+# ------------------------------------------------------------------------------------------------ layers
+class ColumnParallelLinear(nn.Module):
+    """y_local = x W_local^T with W split along the output dim. With SP the input tokens are all-gathered first
+    (fused into the GEMM on the `fused` back-end)."""
+
+    def __init__(self, in_features: int, out_features: int, tp: TPContext, bias: bool = False, gather_output=False,
+                 dtype=None, device=None):
+        super().__init__()
+        assert out_features % tp.size == 0, "out_features must divide by the TP size"
+        self.tp, self.gather_output = tp, gather_output
+        self.in_features, self.out_features = in_features, out_features
+        self.weight = nn.Parameter(torch.empty(out_features // tp.size, in_features, dtype=dtype, device=device))
+        self.bias = nn.Parameter(torch.zeros(out_features // tp.size, dtype=dtype, device=device)) if bias else None
+        nn.init.normal_(self.weight, std=0.02)
+
+    def forward(self, x):
+        tp = self.tp
+        if tp.active and tp.sequence_parallel:
+            if tp.comm == "fused" and x.is_cuda:
+                from . import tp_fused
+                y = tp_fused.all_gather_linear(x, self.weight, tp)
+            else:
+                y = gemm.linear(all_gather_from_sequence_parallel_region(x, tp), self.weight)
+        else:
+            y = gemm.linear(copy_to_tensor_parallel_region(x, tp), self.weight)
+        if self.bias is not None:
+            y = y + self.bias
+        return gather_from_tensor_parallel_region(y, tp) if self.gather_output else y
+
+
+class RowParallelLinear(nn.Module):
+    """y = sum_r x_r W_r^T with W split along the input dim; the partial sums are all-reduced, or reduce-scattered
+    over tokens with SP (fused into the GEMM epilogue on the `fused` back-end)."""
+
+    def __init__(self, in_features: int, out_features: int, tp: TPContext, bias: bool = False, input_is_parallel=True,
+                 dtype=None, device=None):
+        super().__init__()
+        assert in_features % tp.size == 0, "in_features must divide by the TP size"
+        self.tp, self.input_is_parallel = tp, input_is_parallel
+        self.weight = nn.Parameter(torch.empty(out_features, in_features // tp.size, dtype=dtype, device=device))
+        self.bias = nn.Parameter(torch.zeros(out_features, dtype=dtype, device=device)) if bias else None
+        nn.init.normal_(self.weight, std=0.02)
+
+    def forward(self, x):
+        tp = self.tp
+        if not self.input_is_parallel:
+            x = scatter_to_tensor_parallel_region(x, tp)
+        if tp.active and tp.comm == "fused" and x.is_cuda:
+            from . import tp_fused
+            y = tp_fused.linear_reduce(x, self.weight, tp, scatter=tp.sequence_parallel)
+        else:
+            y = gemm.linear(x, self.weight)
+            y = reduce_scatter_to_sequence_parallel_region(y, tp) if tp.sequence_parallel else \
+                reduce_from_tensor_parallel_region(y, tp)
+        return y if self.bias is None else y + self.bias
+
+
+class VocabParallelEmbedding(nn.Module):
+    def __init__(self, num_embeddings: int, embedding_dim: int, tp: TPContext, dtype=None, device=None):
+        super().__init__()
+        self.tp = tp
+        self.num_embeddings = num_embeddings
+        per = math.ceil(num_embeddings / tp.size)
+        self.start, self.end = tp.rank * per, min(num_embeddings, (tp.rank + 1) * per)
+        self.weight = nn.Parameter(torch.empty(per, embedding_dim, dtype=dtype, device=device))
+        nn.init.normal_(self.weight, std=0.02)
+
+    def forward(self, ids):
+        if not self.tp.active:
+            return F.embedding(ids, self.weight)
+        mask = (ids < self.start) | (ids >= self.end)
+        local = (ids - self.start).masked_fill(mask, 0)
+        out = F.embedding(local, self.weight).masked_fill(mask.unsqueeze(-1), 0.0)
+        return reduce_from_tensor_parallel_region(out, self.tp)
+
+
+class _VocabParallelCE(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, logits_local, labels, tp, vocab_start, ignore_index):
+        z = logits_local.float()
+        m = z.max(dim=-1).values
+        m = _all_reduce(m, tp, dist.ReduceOp.MAX)
+        z = z - m.unsqueeze(-1)
+        ez = z.exp()
+        s = _all_reduce(ez.sum(-1), tp)
+        vend = vocab_start + z.shape[-1]
+        mine = (labels >= vocab_start) & (labels < vend)
+        idx = (labels - vocab_start).masked_fill(~mine, 0)
+        tgt = z.gather(-1, idx.unsqueeze(-1)).squeeze(-1).masked_fill(~mine, 0.0)
+        tgt = _all_reduce(tgt, tp)
+        valid = labels != ignore_index
+        loss = (s.log() - tgt).masked_fill(~valid, 0.0)
+        ctx.save_for_backward(ez / s.unsqueeze(-1), idx, mine & valid, valid)
+        return loss
+
+    @staticmethod
+    def backward(ctx, g):
+        p, idx, mine, valid = ctx.saved_tensors
+        grad = p.clone()
+        grad.scatter_add_(-1, idx.unsqueeze(-1), -mine.unsqueeze(-1).to(grad.dtype))
+        grad = grad * (g * valid).unsqueeze(-1)
+        return grad, None, None, None, None
+
+
+def vocab_parallel_cross_entropy(logits_local: torch.Tensor, labels: torch.Tensor, tp: TPContext, vocab_start: int,
+                                 ignore_index: int = -100) -> torch.Tensor:
+    """Per-token loss for logits split along the vocabulary; three small all-reduces (max, sum-exp, target logit)."""
+    return _VocabParallelCE.apply(logits_local, labels, tp, vocab_start, ignore_index)
+
+
+class VocabParallelCrossEntropyLoss(nn.Module):
+    def __init__(self, tp: TPContext, vocab_start: int, ignore_index: int = -100, reduction: str = "mean"):
+        super().__init__()
+        self.tp, self.vocab_start, self.ignore_index, self.reduction = tp, vocab_start, ignore_index, reduction
+
+    def forward(self, logits_local, labels):
+        loss = vocab_parallel_cross_entropy(logits_local, labels, self.tp, self.vocab_start, self.ignore_index)
+        if self.reduction == "mean":
+            return loss.sum() / (labels != self.ignore_index).sum().clamp(min=1)
+        return loss.sum() if self.reduction == "sum" else loss
+
+
+# ------------------------------------------------------------------------------------------------ model sharding
+def shard_llama_state_for_tp(model, tp_size: int, tp_rank: int) -> None:
+    """In place: keep this rank's slice of every projection of a framework decoder. q/k/v rows are taken per head
+    group, gate/up per column block, o / down per input block; norms and embeddings stay replicated."""
+    cfg = model.config
+    D, Hq, Hkv, I = cfg.head_dim, cfg.num_attention_heads, cfg.num_key_value_heads, cfg.intermediate_size
+    assert Hq % tp_size == 0 and Hkv % tp_size == 0 and I % tp_size == 0, "heads / ffn must divide by the TP size"
+    hq, hkv, i_loc = Hq // tp_size, Hkv // tp_size, I // tp_size
+    with torch.no_grad():
+        for layer in model.model.layers:
+            a, m = layer.self_attn, layer.mlp
+            q, k, v = a.wqkv.data.split((Hq * D, Hkv * D, Hkv * D), dim=0)
+            a.wqkv = nn.Parameter(torch.cat((q[tp_rank * hq * D:(tp_rank + 1) * hq * D],
+                                             k[tp_rank * hkv * D:(tp_rank + 1) * hkv * D],
+                                             v[tp_rank * hkv * D:(tp_rank + 1) * hkv * D])).contiguous())
+            a.wo = nn.Parameter(a.wo.data[:, tp_rank * hq * D:(tp_rank + 1) * hq * D].contiguous())
+            a.n_heads, a.n_kv = hq, hkv
+            g, u = m.w_gate_up.data.split((I, I), dim=0)
+            m.w_gate_up = nn.Parameter(torch.cat((g[tp_rank * i_loc:(tp_rank + 1) * i_loc],
+                                                  u[tp_rank * i_loc:(tp_rank + 1) * i_loc])).contiguous())
+            m.w_down = nn.Parameter(m.w_down.data[:, tp_rank * i_loc:(tp_rank + 1) * i_loc].contiguous())
+
+
+class _TPBlockIO(nn.Module):
+    """Wraps a sub-module whose first GEMM is column-parallel and last GEMM is row-parallel."""
+
+    def __init__(self, inner: nn.Module, tp: TPContext):
+        super().__init__()
+        self.inner, self.tp = inner, tp
+
+    def forward(self, x, *args, **kw):
+        tp = self.tp
+        if tp.sequence_parallel:
+            B, S, H = x.shape   # tokens are sharded along S; gather them (B must be 1 per shard row-block)
+            xg = all_gather_from_sequence_parallel_region(x.reshape(B * S, H), tp).view(B, S * tp.size, H) if B == 1 else \
+                all_gather_from_sequence_parallel_region(x.transpose(0, 1).contiguous(), tp).transpose(0, 1)
+            y = self.inner(xg, *args, **kw)
+            if B == 1:
+                return reduce_scatter_to_sequence_parallel_region(y.reshape(-1, H), tp).view(B, S, H)
+            return reduce_scatter_to_sequence_parallel_region(y.transpose(0, 1).contiguous(), tp).transpose(0, 1)
+        return reduce_from_tensor_parallel_region(self.inner(copy_to_tensor_parallel_region(x, tp), *args, **kw), tp)
+
+
+def shard_model_for_tensor_parallel(model, tp: TPContext):
+    """Slice the weights for this TP rank and wrap attention / MLP with the conjugate communication ops.
+    With sequence parallelism the caller feeds / receives token-sharded hidden states between blocks and must
+    all-reduce the norm-weight gradients over the TP group (`allreduce_sequence_parallel_grads`)."""
+    if not tp.active:
+        return model
+    shard_llama_state_for_tp(model, tp.size, tp.rank)
+    for layer in model.model.layers:
+        layer.self_attn = _TPBlockIO(layer.self_attn, tp)
+        layer.mlp = _TPBlockIO(layer.mlp, tp)
+    model.tp = tp
+    return model
+
+
+def allreduce_sequence_parallel_grads(model, tp: TPContext) -> None:
+    """Norm weights see only this rank's tokens under SP: sum their gradients over the TP group."""
+    if not (tp.active and tp.sequence_parallel):
+        return
+    grads = []
+    for n, p in model.named_parameters():
+        if p.dim() == 1:
+            g = getattr(p, "main_grad", None) if p.grad is None else p.grad
+            if g is not None:
+                grads.append(g)
+    if grads:
+        flat = torch.cat([g.reshape(-1).float() for g in grads])
+        dist.all_reduce(flat, group=tp.group)
+        off = 0
+        for g in grads:
+            g.copy_(flat[off:off + g.numel()].view_as(g))
+            off += g.numel()
