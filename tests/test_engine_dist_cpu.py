@@ -28,3 +28,21 @@ def test_tensor_and_sequence_parallel_match_unsharded():
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=300)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
     assert r.stdout.count("ok=True") == 2
+
+
+def test_pipeline_stages_match_single_process():
+    case = Path(__file__).parent / "dist_cases" / "pp_equivalence.py"
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+           "127.0.0.1", "--master-port", "29651", str(case)]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    assert r.stdout.count("ok=True") == 6
+
+
+def test_schedule_simulator_bubbles():
+    from trainscale_b200.parallel.pp import create_schedule, simulate
+    P, M = 4, 8
+    res = {n: simulate([create_schedule(n, s, P, M) for s in range(P)]) for n in ("gpipe", "1f1b", "zero_bubble")}
+    assert abs(res["1f1b"]["bubble_fraction"] - (P - 1) / (M + P - 1)) < 1e-9
+    assert res["zero_bubble"]["bubble_fraction"] < 0.5 * res["1f1b"]["bubble_fraction"]
+    assert res["gpipe"]["makespan"] == res["1f1b"]["makespan"]

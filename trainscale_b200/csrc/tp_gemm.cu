@@ -1,0 +1,410 @@
+// Tensor-parallel GEMMs fused with their collective over NVLink peer memory (sm_100a, tcgen05 + TMEM + TMA).
+//
+//   mode GATHER  (all-gather -> GEMM):  A's rows are sharded over the W ranks (sequence parallelism).  Copier warps
+//       of the same persistent kernel pull the remote row blocks into a local buffer with plain peer loads, in the
+//       order the MMA tiles will need them (own rows first, then rank+1, rank+2, ...), and publish per-row-block
+//       counters; the TMA producer waits on the counter of a row block (bounded) before it loads tiles from it.
+//       The transfer overlaps the math tile by tile and every remote byte crosses NVLink once.
+//   mode REDUCE  (GEMM -> reduce-scatter): the epilogue adds each 128-row tile of partial sums straight into the
+//       owning rank's fp32 buffer with vector `red.global.add.v4.f32` over peer pointers; no partial-sum tensor is
+//       ever written locally and nothing waits for the whole GEMM to finish before data moves.
+// Both modes run the cross-rank hand-shakes inside the kernel: an entry barrier (peer operands are ready / the
+// reduction buffers are cleared) performed by CTA 0 and published through a local flag, and an exit barrier
+// performed by the last CTA to finish (so a rank's kernel completes only after every peer has finished touching
+// its memory).  All waits are bounded and report through the error word / status word.
+//
+// TMA loads here are plain tiled loads (never cluster multicast), and they only ever read THIS GPU's memory: the
+// remote rows are brought in by ordinary ld.global from peer pointers.
+//
+// Replaces the serial all_gather -> F.linear and F.linear -> reduce_scatter pairs of
+// data_pipeline/trainer/distributed/tensor_parallel.py:1053-1061,1214-1219.
+#include "common.cuh"
+#include "host_common.h"
+
+namespace ts {
+
+constexpr int TP_BM = 128, TP_BK = 64, TP_GROUP_M = 8, TP_MAX_WORLD = 16;
+constexpr int TP_THREADS = 320;          // warp 0 TMA, warp 1 MMA, warps 2..5 epilogue, warps 6..9 copiers
+constexpr int TP_SUB = 4;                // a remote row block is fetched as TP_SUB column slices
+
+struct TpPeers {
+  const void* src[TP_MAX_WORLD];         // GATHER: every rank's A shard ([rows_per_rank][K] bf16)
+  float* dst[TP_MAX_WORLD];              // REDUCE: every rank's fp32 accumulation buffer ([rows_per_rank][N])
+  unsigned int* pad[TP_MAX_WORLD];       // signal pads
+};
+
+struct TpParams {
+  int M, N, K, ldc;
+  int b_mn;
+  int mode;                              // 1 = GATHER, 2 = REDUCE
+  int rank, world, rows_per_rank;
+  void* C;                               // GATHER: bf16 output [M][ldc]
+  __nv_bfloat16* a_full;                 // GATHER: local [M][K] buffer the remote rows are staged into
+  int num_m_tiles, num_n_tiles, k_blocks;
+  unsigned int* flags;                   // [0] entry flag, [1] done counter, [2 + m_block] staging counters
+  unsigned int epoch, slot0;
+  long long wait_cycles;
+  unsigned int* status;
+};
+
+template <int BN>
+struct TpSmem {
+  static constexpr int STAGES = (BN == 256) ? 4 : 6;
+  static constexpr int A_BYTES = TP_BM * TP_BK * 2;
+  static constexpr int B_BYTES = BN * TP_BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int TOTAL = STAGES * STAGE_BYTES + 256 + 1024;
+};
+
+__device__ __forceinline__ void red_add_v4_f32(float* p, float a, float b, float c, float d) {
+  asm volatile("red.relaxed.sys.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(a), "f"(b), "f"(c), "f"(d)
+               : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async_global() { asm volatile("fence.proxy.async.global;" ::: "memory"); }
+
+template <int BN>
+__global__ void __launch_bounds__(TP_THREADS, 1)
+tp_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, TpParams p,
+               TpPeers peers) {
+  using S = TpSmem<BN>;
+  constexpr int STAGES = S::STAGES;
+  constexpr uint32_t TMEM_COLS = 2 * BN;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* smem_a = smem;
+  uint8_t* smem_b = smem + STAGES * S::A_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * S::STAGE_BYTES);
+  uint64_t* full_bar = bars;
+  uint64_t* empty_bar = bars + STAGES;
+  uint64_t* tfull_bar = bars + 2 * STAGES;
+  uint64_t* tempty_bar = bars + 2 * STAGES + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    mbar_init(&tfull_bar[0], 1);
+    mbar_init(&tfull_bar[1], 1);
+    mbar_init(&tempty_bar[0], 4);
+    mbar_init(&tempty_bar[1], 4);
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+    tc_fence_before_sync();
+  }
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int num_tiles = p.num_m_tiles * p.num_n_tiles;
+  const int tiles_per_group = TP_GROUP_M * p.num_n_tiles;
+  const int m_tiles_per_rank = p.rows_per_rank / TP_BM;
+  bool alive = true;
+
+  // logical m index j -> physical row block: own rows first, then the next ranks' rows in ring order
+  auto phys_m = [&](int j) {
+    if (p.mode != 1) return j;
+    return (j + p.rank * m_tiles_per_rank) % p.num_m_tiles;
+  };
+  auto tile_coords = [&](int t, int& mt, int& n0) {
+    const int g = t / tiles_per_group;
+    const int first_m = g * TP_GROUP_M;
+    const int gsz = min(p.num_m_tiles - first_m, TP_GROUP_M);
+    const int r = t - g * tiles_per_group;
+    mt = phys_m(first_m + (r % gsz));
+    n0 = (r / gsz) * BN;
+  };
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (elect_one_sync()) {
+      uint32_t it = 0;
+      int last_ready = -1;
+      for (int t = blockIdx.x; t < num_tiles && alive; t += gridDim.x) {
+        int mt, n0;
+        tile_coords(t, mt, n0);
+        if (p.mode == 1 && mt / m_tiles_per_rank != p.rank && mt != last_ready) {
+          // the rows of this block come from a peer: wait until the copiers have staged all of it
+          if (!flag_wait_geq_gpu(p.flags + 2 + mt, p.epoch * TP_SUB, p.wait_cycles, 1000)) {
+            alive = false;
+            if (p.status) atomicExch(p.status, 1u);
+            break;
+          }
+          fence_proxy_async_global();
+          last_ready = mt;
+        }
+        for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
+          const int s = it % STAGES;
+          if (!mbar_wait(&empty_bar[s], ((it / STAGES) & 1u) ^ 1u, alive, 1001)) break;
+          mbar_expect_tx(&full_bar[s], S::STAGE_BYTES);
+          tma_load_2d(smem_a + s * S::A_BYTES, &tmA, &full_bar[s], kb * TP_BK, mt * TP_BM);
+          uint8_t* b_dst = smem_b + s * S::B_BYTES;
+          if (!p.b_mn) {
+            tma_load_2d(b_dst, &tmB, &full_bar[s], kb * TP_BK, n0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j) tma_load_2d(b_dst + j * 8192, &tmB, &full_bar[s], n0 + j * 64, kb * TP_BK);
+          }
+        }
+      }
+      if (!alive) {
+        const uint32_t first = it > (uint32_t)STAGES ? it - STAGES : 0u;
+        for (uint32_t i = first; i < it; ++i) {
+          const long long t0 = clock64();
+          while (!mbar_try_wait(&full_bar[i % STAGES], (i / STAGES) & 1u) && clock64() - t0 < 2000000ll) {
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer ------------------------------
+    if (elect_one_sync()) {
+      const uint32_t idesc = make_idesc(TP_BM, BN, 1, 1, 0u, (uint32_t)p.b_mn);
+      const uint32_t b_kstep = p.b_mn ? 2048u : 32u;
+      const uint32_t b_lbo = p.b_mn ? 8192u : 16u;
+      uint32_t it = 0, tile_it = 0;
+      for (int t = blockIdx.x; t < num_tiles && alive; t += gridDim.x, ++tile_it) {
+        const uint32_t acc = tile_it & 1u;
+        if (!mbar_wait(&tempty_bar[acc], ((tile_it >> 1) & 1u) ^ 1u, alive, 1010)) break;
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
+          const int s = it % STAGES;
+          if (!mbar_wait(&full_bar[s], (it / STAGES) & 1u, alive, 1011)) break;
+          tc_fence_after_sync();
+          const uint32_t a_addr = smem_u32(smem_a + s * S::A_BYTES);
+          const uint32_t b_addr = smem_u32(smem_b + s * S::B_BYTES);
+#pragma unroll
+          for (int k = 0; k < TP_BK / 16; ++k)
+            umma_f16_ss(d_tmem, make_smem_desc_sw128(a_addr + k * 32, 16, 1024),
+                        make_smem_desc_sw128(b_addr + k * b_kstep, b_lbo, 1024), idesc, (kb | k) != 0 ? 1u : 0u);
+          umma_commit(&empty_bar[s]);
+        }
+        if (!alive) break;
+        umma_commit(&tfull_bar[acc]);
+      }
+    }
+  } else if (warp < 6) {
+    // ------------------------------ epilogue ------------------------------
+    const int q = warp & 3;
+    uint32_t tile_it = 0;
+    bool entry_ok = (p.mode != 2);
+    for (int t = blockIdx.x; t < num_tiles && alive; t += gridDim.x, ++tile_it) {
+      int mt, n0;
+      tile_coords(t, mt, n0);
+      const uint32_t acc = tile_it & 1u;
+      if (!mbar_wait(&tfull_bar[acc], (tile_it >> 1) & 1u, alive, 1020)) break;
+      tc_fence_after_sync();
+      if (!entry_ok) {
+        // nobody may add into a peer's buffer before every rank has cleared it (entry barrier by CTA 0)
+        if (!flag_wait_geq_gpu(p.flags, p.epoch, p.wait_cycles, 1021)) {
+          alive = false;
+          if (p.status) atomicExch(p.status, 1u);
+          break;
+        }
+        entry_ok = true;
+      }
+      const int row = mt * TP_BM + q * 32 + lane;
+      const uint32_t t_row = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(t_row + c * 32, r);
+        tc_wait_ld();
+        const int col0 = n0 + c * 32;
+        if (row >= p.M || col0 >= p.N) continue;
+        if (p.mode == 2) {
+          const int owner = row / p.rows_per_rank;
+          float* dst = peers.dst[owner] + static_cast<size_t>(row - owner * p.rows_per_rank) * p.N + col0;
+          if (col0 + 32 <= p.N) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              red_add_v4_f32(dst + 4 * j, __uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                             __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+          } else {
+            for (int j = 0; j < 32 && col0 + j < p.N; ++j) atomicAdd_system(dst + j, __uint_as_float(r[j]));
+          }
+        } else {
+          __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<size_t>(row) * p.ldc + col0;
+          if (col0 + 32 <= p.N && ((reinterpret_cast<uintptr_t>(dst) & 15u) == 0)) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              uint4 v;
+              v.x = pack_bf16x2(__uint_as_float(r[8 * j]), __uint_as_float(r[8 * j + 1]));
+              v.y = pack_bf16x2(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]));
+              v.z = pack_bf16x2(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]));
+              v.w = pack_bf16x2(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]));
+              *reinterpret_cast<uint4*>(dst + 8 * j) = v;
+            }
+          } else {
+            for (int j = 0; j < 32 && col0 + j < p.N; ++j) dst[j] = __float2bfloat16(__uint_as_float(r[j]));
+          }
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+    }
+    __threadfence_system();   // peer adds of this thread are ordered before the CTA's "done" count
+  } else {
+    // ------------------------------ copiers (warps 6..9) ------------------------------
+    const int ct = threadIdx.x - 192;   // 0..127
+    if (blockIdx.x == 0) {
+      // entry barrier with the peers, then publish it to the other CTAs of this GPU through flags[0]
+      if (ct < p.world) {
+        __threadfence_system();
+        st_release_sys(peers.pad[ct] + p.slot0 + p.rank, p.epoch);
+        if (!flag_wait_geq_sys(peers.pad[p.rank] + p.slot0 + ct, p.epoch, p.wait_cycles, 1030) && p.status)
+          atomicExch(p.status, 1u);
+      }
+      asm volatile("bar.sync 2, 128;" ::: "memory");
+      if (ct == 0) {
+        const unsigned int bad = p.status ? atomicAdd(p.status, 0u) : 0u;
+        if (!bad) st_release_gpu(p.flags, p.epoch);
+      }
+    }
+    if (p.mode == 1) {
+      if (!flag_wait_geq_gpu(p.flags, p.epoch, p.wait_cycles, 1031)) {
+        if (ct == 0 && p.status) atomicExch(p.status, 1u);
+      } else {
+        // remote row blocks in the order the tiles need them; work item = (row block, column slice)
+        const int remote_blocks = p.num_m_tiles - m_tiles_per_rank;
+        const int items = remote_blocks * TP_SUB;
+        const int vec_per_row = (p.K / TP_SUB) >> 3;   // 16-byte vectors per row slice
+        for (int item = blockIdx.x; item < items; item += gridDim.x) {
+          const int jb = item / TP_SUB, sub = item - jb * TP_SUB;
+          const int mt = (jb + (p.rank + 1) * m_tiles_per_rank) % p.num_m_tiles;
+          const int owner = mt / m_tiles_per_rank;
+          const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(peers.src[owner]) +
+                                     static_cast<size_t>(mt - owner * m_tiles_per_rank) * TP_BM * p.K + sub * (p.K / TP_SUB);
+          __nv_bfloat16* dst = p.a_full + static_cast<size_t>(mt) * TP_BM * p.K + sub * (p.K / TP_SUB);
+          for (int v = ct; v < TP_BM * vec_per_row; v += 128) {
+            const int rr = v / vec_per_row, cc = v - rr * vec_per_row;
+            const uint4 val = *reinterpret_cast<const uint4*>(src + static_cast<size_t>(rr) * p.K + cc * 8);
+            *reinterpret_cast<uint4*>(dst + static_cast<size_t>(rr) * p.K + cc * 8) = val;
+          }
+          __threadfence();
+          asm volatile("bar.sync 2, 128;" ::: "memory");
+          if (ct == 0) atom_add_release_gpu(p.flags + 2 + mt, 1u);
+        }
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+  // ------------------------------ exit barrier: the last CTA to finish talks to the peers ------------------------------
+  if (warp == 6) {
+    unsigned int last = 0;
+    if (lane == 0) {
+      __threadfence_system();
+      last = (atomicAdd(p.flags + 1, 1u) == gridDim.x - 1) ? 1u : 0u;
+    }
+    last = __shfl_sync(0xffffffffu, last, 0);
+    if (last) {
+      bool ok = true;
+      if (lane < p.world) {
+        __threadfence_system();
+        st_release_sys(peers.pad[lane] + p.slot0 + TP_MAX_WORLD + p.rank, p.epoch);
+        ok = flag_wait_geq_sys(peers.pad[p.rank] + p.slot0 + TP_MAX_WORLD + lane, p.epoch, p.wait_cycles, 1040);
+      }
+      if (!ok && p.status) atomicExch(p.status, 1u);
+      __syncwarp();
+      if (lane == 0) p.flags[1] = 0u;
+    }
+  }
+}
+
+// dst[i] = bf16(src[i]); src[i] = 0  (turns a finished fp32 reduction buffer into the layer output and re-arms it)
+__global__ void cast_and_clear_kernel(float* __restrict__ src, __nv_bfloat16* __restrict__ dst, long long n) {
+  for (long long i = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) * 4; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x * 4) {
+    const float4 v = *reinterpret_cast<const float4*>(src + i);
+    uint2 o;
+    o.x = pack_bf16x2(v.x, v.y);
+    o.y = pack_bf16x2(v.z, v.w);
+    *reinterpret_cast<uint2*>(dst + i) = o;
+    *reinterpret_cast<float4*>(src + i) = make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+}
+
+template <int BN>
+static int launch_tp(const CUtensorMap& tmA, const CUtensorMap& tmB, const TpParams& p, const TpPeers& peers,
+                     cudaStream_t st) {
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(tp_gemm_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, TpSmem<BN>::TOTAL);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  const int tiles = p.num_m_tiles * p.num_n_tiles;
+  // every CTA must be resident at once (CTA 0 publishes the entry barrier, the last CTA runs the exit barrier,
+  // copiers feed other CTAs' tiles): never launch more CTAs than SMs
+  const int grid = tiles < sm_count() ? tiles : sm_count();
+  tp_gemm_kernel<BN><<<grid, TP_THREADS, TpSmem<BN>::TOTAL, st>>>(tmA, tmB, p, peers);
+  return (int)cudaGetLastError();
+}
+
+}  // namespace ts
+
+TS_DEFINE_ERROR_API(ts_tp_gemm)
+
+using namespace ts;
+
+// mode 1 (all-gather -> GEMM):  C[M,N] = gather_rows(A_shards)[M,K] . B^T.  `a_full` is a local [M][K] bf16 buffer
+//   whose own block (rows rank*rows_per_rank ...) already holds this rank's shard; src_ptrs[r] = rank r's shard.
+// mode 2 (GEMM -> reduce-scatter): dst_ptrs[owner][row - owner*rows_per_rank][:] += A[M,K] . B^T rows, fp32.
+// B: b_mn == 0 -> [N][ldb] K-major, b_mn == 1 -> [K][ldb] N-major.  flags: device u32[2 + M/128], zero-initialised once
+// and reused across calls with a growing `epoch`.  pad_ptrs / slot0: signal pads (2*16 slots from slot0 are used).
+extern "C" int ts_tp_gemm(int mode, const void* A, const void* B, void* C, void* a_full, int M, int N, int K, int lda,
+                          int ldb, int ldc, int b_mn, const unsigned long long* src_ptrs,
+                          const unsigned long long* dst_ptrs, const unsigned long long* pad_ptrs, int rank, int world,
+                          unsigned int* flags, unsigned int epoch, unsigned int slot0, long long wait_cycles,
+                          unsigned int* status, void* stream) {
+  if (world > TP_MAX_WORLD || M % (TP_BM * world) != 0 || K % (8 * TP_SUB) != 0) return -10;
+  if (mode != 1 && mode != 2) return -11;
+  const int bn = (N >= 256) ? 256 : 128;
+  const void* a_base = (mode == 1) ? a_full : A;
+  const int a_ld = (mode == 1) ? K : lda;
+  CUtensorMap tmA, tmB;
+  int rc = make_tmap_2d(&tmA, a_base, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)M, (uint64_t)K, (uint64_t)a_ld, TP_BM, 64);
+  if (rc) return rc * 100 - 1;
+  if (!b_mn)
+    rc = make_tmap_2d(&tmB, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, (uint32_t)bn, 64);
+  else
+    rc = make_tmap_2d(&tmB, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, 64, 64);
+  if (rc) return rc * 100 - 2;
+  TpParams p{};
+  p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.b_mn = b_mn; p.mode = mode; p.rank = rank; p.world = world;
+  p.rows_per_rank = M / world; p.C = C; p.a_full = (__nv_bfloat16*)a_full;
+  p.num_m_tiles = M / TP_BM; p.num_n_tiles = (N + bn - 1) / bn; p.k_blocks = (K + TP_BK - 1) / TP_BK;
+  p.flags = flags; p.epoch = epoch; p.slot0 = slot0; p.wait_cycles = wait_cycles; p.status = status;
+  TpPeers peers{};
+  for (int r = 0; r < world; ++r) {
+    peers.src[r] = src_ptrs ? reinterpret_cast<const void*>(src_ptrs[r]) : nullptr;
+    peers.dst[r] = dst_ptrs ? reinterpret_cast<float*>(dst_ptrs[r]) : nullptr;
+    peers.pad[r] = reinterpret_cast<unsigned int*>(pad_ptrs[r]);
+  }
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  return bn == 256 ? launch_tp<256>(tmA, tmB, p, peers, st) : launch_tp<128>(tmA, tmB, p, peers, st);
+}
+
+extern "C" int ts_cast_and_clear(float* src, void* dst, long long n, void* stream) {
+  if (n <= 0 || n % 4 != 0) return n == 0 ? 0 : -10;
+  long long blocks = (n / 4 + 255) / 256;
+  if (blocks > (long long)sm_count() * 8) blocks = (long long)sm_count() * 8;
+  cast_and_clear_kernel<<<(unsigned)blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(src, (__nv_bfloat16*)dst, n);
+  return (int)cudaGetLastError();
+}

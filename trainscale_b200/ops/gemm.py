@@ -83,6 +83,62 @@ def matmul_tn(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None,
     return out
 
 
+class WgradQueue:
+    """Deferred weight-gradient GEMMs (zero-bubble pipeline schedules): inside `with queue.defer():` a linear's
+    backward only runs the input-gradient GEMM and parks (dy, x, w); `queue.run()` executes the parked
+    weight-gradient GEMMs later, when the schedule has a bubble to fill."""
+
+    _active: "WgradQueue | None" = None
+
+    def __init__(self):
+        self.items: list = []
+
+    class _Ctx:
+        def __init__(self, q):
+            self.q = q
+
+        def __enter__(self):
+            self.prev = WgradQueue._active
+            WgradQueue._active = self.q
+            return self.q
+
+        def __exit__(self, *a):
+            WgradQueue._active = self.prev
+
+    def defer(self):
+        return WgradQueue._Ctx(self)
+
+    def push(self, dy2, x, w):
+        self.items.append((dy2, x, w))
+
+    def run(self, max_items: int | None = None) -> int:
+        n = 0
+        while self.items and (max_items is None or n < max_items):
+            dy2, x, w = self.items.pop(0)
+            _accumulate_wgrad(dy2, x, w)
+            n += 1
+        return n
+
+    def __len__(self):
+        return len(self.items)
+
+
+def _accumulate_wgrad(dy2, x, w):
+    """dW += dy^T x into w.main_grad when the engine owns one, else into w.grad."""
+    x2 = _rows2d(x)
+    main_grad = getattr(w, "main_grad", None)
+    if main_grad is not None:
+        if dy2.is_cuda and dy2.dtype == torch.bfloat16:
+            matmul_tn(dy2, x2, out=main_grad.view(w.shape), accumulate=getattr(w, "grad_added", False))
+        else:
+            g = dy2.float().t() @ x2.float()
+            main_grad.view(w.shape).copy_(main_grad.view(w.shape).float() + g if getattr(w, "grad_added", False) else g)
+        w.grad_added = True
+        return
+    g = matmul_tn(dy2, x2) if (dy2.is_cuda and dy2.dtype == torch.bfloat16) else (dy2.float().t() @ x2.float()).to(w.dtype)
+    w.grad = g if w.grad is None else w.grad + g
+
+
 class _LinearFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w):
@@ -97,7 +153,9 @@ class _LinearFn(torch.autograd.Function):
         dx = dw = None
         if ctx.needs_input_grad[0]:
             dx = matmul_nn(dy2, w).view_as(x)
-        if ctx.needs_input_grad[1]:
+        if ctx.needs_input_grad[1] and WgradQueue._active is not None:
+            WgradQueue._active.push(dy2, x, w)
+        elif ctx.needs_input_grad[1]:
             main_grad = getattr(w, "main_grad", None)
             if main_grad is not None:
                 # gradient accumulated straight into the owner's buffer (fp32 or bf16) by the epilogue
@@ -114,4 +172,26 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None) -
     if x.is_cuda and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
         y = _LinearFn.apply(x, w)
         return y if bias is None else y + bias
+    if WgradQueue._active is not None and w.requires_grad:
+        y = _SplitLinearCPU.apply(x, w)
+        return y if bias is None else y + bias
     return torch.nn.functional.linear(x, w, bias)
+
+
+class _SplitLinearCPU(torch.autograd.Function):
+    """PyTorch-op linear whose weight gradient can be deferred (CPU / fp32 path of the zero-bubble split)."""
+
+    @staticmethod
+    def forward(ctx, x, w):
+        ctx.save_for_backward(x, w)
+        return torch.nn.functional.linear(x, w)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        dx = (dy2 @ w).view_as(x) if ctx.needs_input_grad[0] else None
+        if WgradQueue._active is not None:
+            WgradQueue._active.push(dy2, x, w)
+            return dx, None
+        return dx, (dy2.t() @ x.reshape(-1, x.shape[-1])).to(w.dtype)

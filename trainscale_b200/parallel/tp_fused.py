@@ -1,0 +1,142 @@
+"""Autograd wrappers of the fused tensor-parallel GEMMs (csrc/tp_gemm.cu).
+
+`all_gather_linear`  y[M, N_local] = all_gather_rows(x_shard) @ W_local^T   - the gather runs inside the GEMM
+`linear_reduce`      y_shard[M/W, N] = reduce_scatter_rows(x @ W_local^T)    - the reduction runs in the epilogue
+Their backward passes are each other's fused form (dgrad of a gathered input is a GEMM -> reduce-scatter, dgrad of
+a reduce-scattered output is an all-gather -> GEMM), and the weight gradients reuse the gathered operand.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from ..ops import _lib
+from ..ops.gemm import matmul_tn
+
+_ll, _u = ctypes.c_longlong, ctypes.c_uint
+
+
+class _Buffers:
+    """Symmetric staging / accumulation buffers and flag words, cached per shape on the heap object."""
+
+    def __init__(self, heap):
+        self.heap = heap
+        self.cache: dict = {}
+
+    def get(self, kind: str, rows: int, cols: int, n_mblocks: int):
+        key = (kind, rows, cols)
+        b = self.cache.get(key)
+        if b is None:
+            dt = torch.bfloat16 if kind == "src" else torch.float32
+            t = self.heap.alloc(rows * cols, dt).view(rows, cols)
+            buf, _ = self.heap.lookup(t)
+            flags = torch.zeros(2 + n_mblocks, dtype=torch.int32, device=t.device)
+            b = {"t": t, "buf": buf, "flags": flags, "epoch": 0}
+            self.cache[key] = b
+        b["epoch"] += 1
+        return b
+
+
+def _buffers(tp) -> _Buffers:
+    if not hasattr(tp.heap, "_tp_buffers"):
+        tp.heap._tp_buffers = _Buffers(tp.heap)
+    return tp.heap._tp_buffers
+
+
+def _launch(mode, tp, b, A, B, C, a_full, M, N, K, lda, ldb, ldc, b_mn):
+    lib = _lib.load("tp_gemm")
+    buf = b["buf"]
+    src = buf.peer_ptrs if mode == 1 else None
+    dst = buf.peer_ptrs if mode == 2 else None
+    rc = lib.ts_tp_gemm(mode, _lib.ptr(A), _lib.ptr(B), _lib.ptr(C), _lib.ptr(a_full), M, N, K, lda, ldb, ldc, int(b_mn),
+                        src, dst, buf.pad_ptrs, tp.rank, tp.size, _lib.ptr(b["flags"]), _u(b["epoch"]), _u(0),
+                        _ll(tp.heap.wait_cycles), _lib.ptr(tp.heap.status), _lib.stream_ptr())
+    _lib.check(rc, "ts_tp_gemm")
+
+
+def _gather_gemm(x_shard, w, tp, b_mn):
+    """(y [M, N], a_full [M, K]); w is [N, K] (b_mn False) or [K, N] (b_mn True)."""
+    Ms, K = x_shard.shape
+    M = Ms * tp.size
+    N = w.shape[1] if b_mn else w.shape[0]
+    b = _buffers(tp).get("src", Ms, K, M // 128)
+    b["t"].copy_(x_shard)
+    a_full = torch.empty(M, K, dtype=x_shard.dtype, device=x_shard.device)
+    a_full[tp.rank * Ms:(tp.rank + 1) * Ms].copy_(x_shard)
+    y = torch.empty(M, N, dtype=x_shard.dtype, device=x_shard.device)
+    _launch(1, tp, b, None, w, y, a_full, M, N, K, K, w.stride(0), N, b_mn)
+    return y, a_full
+
+
+def _gemm_reduce(x, w, tp, b_mn):
+    """y_shard [M/W, N] (bf16) = reduce_scatter(x @ w^T)."""
+    M, K = x.shape
+    N = w.shape[1] if b_mn else w.shape[0]
+    Ms = M // tp.size
+    b = _buffers(tp).get("acc", Ms, N, M // 128)
+    _launch(2, tp, b, x, w, None, None, M, N, K, x.stride(0), w.stride(0), N, b_mn)
+    out = torch.empty(Ms, N, dtype=x.dtype, device=x.device)
+    lib = _lib.load("tp_gemm")
+    rc = lib.ts_cast_and_clear(_lib.ptr(b["t"]), _lib.ptr(out), _ll(Ms * N), _lib.stream_ptr())
+    _lib.check(rc, "ts_cast_and_clear")
+    return out
+
+
+class _AllGatherLinear(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x_shard, w, tp):
+        y, a_full = _gather_gemm(x_shard.contiguous(), w, tp, False)
+        ctx.save_for_backward(a_full, w)
+        ctx.tp = tp
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        a_full, w = ctx.saved_tensors
+        dy = dy.contiguous()
+        dx = _gemm_reduce(dy, w, ctx.tp, True)           # [M, N] . [N, K] -> reduce-scatter rows
+        main_grad = getattr(w, "main_grad", None)
+        if main_grad is not None:
+            matmul_tn(dy, a_full, out=main_grad.view(w.shape), accumulate=getattr(w, "grad_added", False))
+            w.grad_added = True
+            dw = None
+        else:
+            dw = matmul_tn(dy, a_full)
+        return dx, dw, None
+
+
+class _LinearReduce(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, tp):
+        x = x.contiguous()
+        ctx.save_for_backward(x, w)
+        ctx.tp = tp
+        return _gemm_reduce(x, w, tp, False)
+
+    @staticmethod
+    def backward(ctx, dy_shard):
+        x, w = ctx.saved_tensors
+        dx, dy_full = _gather_gemm(dy_shard.contiguous(), w, ctx.tp, True)   # gather(dy)[M, N] . W[N, K]
+        main_grad = getattr(w, "main_grad", None)
+        if main_grad is not None:
+            matmul_tn(dy_full, x, out=main_grad.view(w.shape), accumulate=getattr(w, "grad_added", False))
+            w.grad_added = True
+            dw = None
+        else:
+            dw = matmul_tn(dy_full, x)
+        return dx, dw, None
+
+
+def all_gather_linear(x_shard: torch.Tensor, w: torch.Tensor, tp) -> torch.Tensor:
+    shp = x_shard.shape
+    y = _AllGatherLinear.apply(x_shard.reshape(-1, shp[-1]), w, tp)
+    return y
+
+
+def linear_reduce(x: torch.Tensor, w: torch.Tensor, tp, scatter: bool = True) -> torch.Tensor:
+    y = _LinearReduce.apply(x.reshape(-1, x.shape[-1]), w, tp)
+    if not scatter:
+        from .tp import _all_gather_dim
+        y = _all_gather_dim(y, tp, 0)
+    return y
