@@ -46,3 +46,25 @@ def test_schedule_simulator_bubbles():
     assert abs(res["1f1b"]["bubble_fraction"] - (P - 1) / (M + P - 1)) < 1e-9
     assert res["zero_bubble"]["bubble_fraction"] < 0.5 * res["1f1b"]["bubble_fraction"]
     assert res["gpipe"]["makespan"] == res["1f1b"]["makespan"]
+
+
+@pytest.mark.parametrize("n,port", [(2, 29671), (4, 29672)])
+def test_ring_attention_matches_full_attention(n, port):
+    case = Path(__file__).parent / "dist_cases" / "cp_equivalence.py"
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr",
+           "127.0.0.1", "--master-port", str(port), str(case)]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=400)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    assert r.stdout.count("ok=True") == n
+
+
+def test_head_tail_and_zigzag_layouts_roundtrip():
+    import torch
+    from trainscale_b200.parallel.cp import HeadTailBalancer, ZigZagBalancer, shard_inputs
+    x = torch.arange(2 * 32).view(2, 32)
+    for cls in (HeadTailBalancer, ZigZagBalancer):
+        parts = [cls(4, r).shard(x) for r in range(4)]
+        assert torch.equal(cls(4, 0).unshard(parts), x)
+    b = shard_inputs({"input_ids": x}, 4, 1)
+    assert b["position_ids"][0].tolist() == list(range(4, 8)) + list(range(24, 28))
+    assert b["labels"][0, 3].item() == x[0, 8].item() and b["labels"][0, -1].item() == x[0, 28].item()
