@@ -1,0 +1,779 @@
+"""Inference engine: paged KV cache, continuous batching with chunked prefill, sampling, streaming, an
+OpenAI-compatible HTTP server and a CLI.
+
+API surface after data_pipeline/trainer/inference.py:229-2421 (`EngineConfig` with scheduler / cache / parallel /
+speculative / LoRA / observability sub-configs, `GenerationParams`, `RequestMetrics` with TTFT / TPOT, percentile
+`MetricsAggregator`, `EngineBuilder`, `SOTAInferenceEngine.generate`, `SOTAAsyncStreamEngine.generate_stream /
+abort_request`, `EnginePresets`, `create_openai_server` with /v1/completions, /v1/chat/completions, /health,
+/metrics, CLI sub-commands probe | batch | stream | serve | bench).  The reference wraps vLLM; this engine runs
+the framework's own decoder on its own kernels: flash attention with packed prompts (cu_seqlens) for prefill,
+paged split-KV decode attention, tcgen05 GEMMs, fused norms.
+"""
+from __future__ import annotations
+
+import argparse
+import asyncio
+import ctypes
+import json
+import math
+import sys
+import time
+from collections import deque
+from dataclasses import asdict, dataclass, field
+from typing import Any, AsyncIterator, Iterable
+
+import torch
+
+from ..core.types import Err, Ok, Result
+from ..ops import _lib, activation, attention, gemm, norm, rope
+from .kv_cache import PagedKVCache
+from .sampling import apply_penalties, sample
+
+
+# ------------------------------------------------------------------------------------------------ configuration
+@dataclass
+class QuantizationConfig:
+    method: str | None = None          # None | fp8 (weights kept bf16 when None)
+    kv_cache_dtype: str = "auto"
+
+
+@dataclass
+class ParallelConfig:
+    tensor_parallel_size: int = 1
+    pipeline_parallel_size: int = 1
+
+
+@dataclass
+class SchedulerConfig:
+    max_num_seqs: int = 64
+    max_num_batched_tokens: int = 8192
+    enable_chunked_prefill: bool = True
+    policy: str = "fcfs"
+
+
+@dataclass
+class CacheConfig:
+    block_size: int = 16
+    gpu_memory_utilization: float = 0.9
+    num_gpu_blocks: int | None = None
+    enable_prefix_caching: bool = True
+    max_model_len: int = 8192
+
+
+@dataclass
+class SpeculativeConfig:
+    enabled: bool = False
+    draft_model: str | None = None
+    num_speculative_tokens: int = 4
+
+
+@dataclass
+class LoRAServingConfig:
+    enabled: bool = False
+    max_loras: int = 1
+    max_lora_rank: int = 64
+
+
+@dataclass
+class ObservabilityConfig:
+    collect_metrics: bool = True
+    log_requests: bool = False
+
+
+@dataclass
+class EngineConfig:
+    model: str = "tiny"                       # preset name or local HF-format directory
+    tokenizer: str | None = None              # None -> built-in byte tokenizer unless `model` is a directory
+    dtype: str = "bfloat16"
+    device: str = "auto"
+    seed: int = 0
+    quantization: QuantizationConfig = field(default_factory=QuantizationConfig)
+    parallel: ParallelConfig = field(default_factory=ParallelConfig)
+    scheduler: SchedulerConfig = field(default_factory=SchedulerConfig)
+    cache: CacheConfig = field(default_factory=CacheConfig)
+    speculative: SpeculativeConfig = field(default_factory=SpeculativeConfig)
+    lora: LoRAServingConfig = field(default_factory=LoRAServingConfig)
+    observability: ObservabilityConfig = field(default_factory=ObservabilityConfig)
+    enforce_eager: bool = True
+
+
+@dataclass
+class GenerationParams:
+    max_tokens: int = 128
+    temperature: float = 0.7
+    top_p: float = 1.0
+    top_k: int = 0
+    min_p: float = 0.0
+    repetition_penalty: float = 1.0
+    presence_penalty: float = 0.0
+    frequency_penalty: float = 0.0
+    stop: list[str] = field(default_factory=list)
+    stop_token_ids: list[int] = field(default_factory=list)
+    ignore_eos: bool = False
+    seed: int | None = None
+    logprobs: bool = False
+    n: int = 1
+
+    def validate(self) -> None:
+        if self.max_tokens < 1:
+            raise ValueError("max_tokens must be >= 1")
+        if self.temperature < 0:
+            raise ValueError("temperature must be >= 0")
+        if not 0 < self.top_p <= 1:
+            raise ValueError("top_p must be in (0, 1]")
+
+
+@dataclass
+class RequestMetrics:
+    request_id: str = ""
+    prompt_tokens: int = 0
+    completion_tokens: int = 0
+    arrival: float = 0.0
+    first_token: float | None = None
+    finished: float | None = None
+    cached_prompt_tokens: int = 0
+
+    @property
+    def ttft(self) -> float | None:
+        return None if self.first_token is None else self.first_token - self.arrival
+
+    @property
+    def tpot(self) -> float | None:
+        if self.finished is None or self.first_token is None or self.completion_tokens < 2:
+            return None
+        return (self.finished - self.first_token) / (self.completion_tokens - 1)
+
+    @property
+    def e2e(self) -> float | None:
+        return None if self.finished is None else self.finished - self.arrival
+
+
+class MetricsAggregator:
+    def __init__(self):
+        self.records: list[RequestMetrics] = []
+
+    def add(self, m: RequestMetrics) -> None:
+        self.records.append(m)
+
+    @staticmethod
+    def _pct(vals: list[float], p: float) -> float | None:
+        if not vals:
+            return None
+        vals = sorted(vals)
+        k = (len(vals) - 1) * p
+        lo, hi = math.floor(k), math.ceil(k)
+        return vals[lo] + (vals[hi] - vals[lo]) * (k - lo)
+
+    def summary(self) -> dict:
+        out = {"requests": len(self.records), "prompt_tokens": sum(r.prompt_tokens for r in self.records),
+               "completion_tokens": sum(r.completion_tokens for r in self.records)}
+        for name in ("ttft", "tpot", "e2e"):
+            vals = [getattr(r, name) for r in self.records if getattr(r, name) is not None]
+            for p in (0.5, 0.95, 0.99):
+                out[f"{name}_p{int(p * 100)}"] = self._pct(vals, p)
+        return out
+
+    def prometheus(self) -> str:
+        s = self.summary()
+        lines = []
+        for k, v in s.items():
+            if v is not None:
+                lines.append(f"trainscale_inference_{k} {v}")
+        return "\n".join(lines) + "\n"
+
+
+@dataclass
+class InferenceResponse:
+    request_id: str
+    prompt: str
+    text: str
+    token_ids: list[int]
+    finish_reason: str
+    metrics: RequestMetrics
+    logprobs: list[float] | None = None
+
+
+@dataclass
+class StreamChunk:
+    request_id: str
+    text: str
+    token_id: int
+    finished: bool
+    finish_reason: str | None = None
+
+
+# ------------------------------------------------------------------------------------------------ model runner
+class ModelRunner:
+    """Runs the framework decoder over a flattened token batch with a paged KV cache."""
+
+    def __init__(self, model, cache: PagedKVCache, device):
+        self.model, self.cache, self.device = model.eval(), cache, torch.device(device)
+        self.cfg = model.config
+        self.cuda = self.device.type == "cuda" and next(model.parameters()).dtype == torch.bfloat16
+        self.cos, self.sin = model.model.rope_tables(self.device, min(self.cfg.max_position_embeddings, 1 << 16))
+
+    def _write_cache(self, layer: int, qkv2d: torch.Tensor, slots: torch.Tensor) -> None:
+        c = self.cfg
+        Hq, Hkv, D = c.num_attention_heads, c.num_key_value_heads, c.head_dim
+        kw = Hkv * D
+        if self.cuda:
+            lib = _lib.load("decode")
+            rc = lib.ts_kv_cache_write(_lib.ptr(qkv2d), qkv2d.stride(0), Hq * D, Hq * D + kw, _lib.ptr(self.cache.k[layer]),
+                                       _lib.ptr(self.cache.v[layer]), _lib.ptr(slots), ctypes.c_longlong(qkv2d.shape[0]),
+                                       kw, _lib.stream_ptr())
+            _lib.check(rc, "ts_kv_cache_write")
+        else:
+            k = qkv2d[:, Hq * D:Hq * D + kw].view(-1, Hkv, D)
+            v = qkv2d[:, Hq * D + kw:].view(-1, Hkv, D)
+            self.cache.k[layer].view(-1, Hkv, D)[slots] = k
+            self.cache.v[layer].view(-1, Hkv, D)[slots] = v
+
+    def _gathered_kv(self, layer: int, seq_id: int):
+        s = self.cache.seqs[seq_id]
+        idx = torch.tensor(s.blocks, device=self.device)
+        c = self.cfg
+        k = self.cache.k[layer][idx].reshape(-1, c.num_key_value_heads, c.head_dim)[:s.num_tokens]
+        v = self.cache.v[layer][idx].reshape(-1, c.num_key_value_heads, c.head_dim)[:s.num_tokens]
+        return k, v
+
+    def _attend(self, layer: int, qkv2d: torch.Tensor, seq_ids: list[int], q_lens: list[int], fresh: bool,
+                block_table, seq_lens) -> torch.Tensor:
+        c = self.cfg
+        Hq, Hkv, D = c.num_attention_heads, c.num_key_value_heads, c.head_dim
+        scale = 1.0 / math.sqrt(D)
+        T = qkv2d.shape[0]
+        if self.cuda and fresh and D in (64, 128):
+            # every sequence starts at position 0: packed-prompt flash attention
+            from ..ops import flash
+            cu = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0).tolist()), dtype=torch.int32, device=self.device)
+            o, _ = flash.flash_forward_only(qkv2d.unsqueeze(0), Hq, Hkv, D, True, scale, cu, max(q_lens))
+            return o.view(T, Hq * D)
+        if self.cuda and all(n == 1 for n in q_lens) and D in (64, 128):
+            lib = _lib.load("decode")
+            n = len(seq_ids)
+            chunk = 512
+            splits = max(1, -(-int(seq_lens.max().item()) // chunk))
+            out = torch.empty(n, Hq * D, dtype=qkv2d.dtype, device=self.device)
+            po = torch.empty(n, Hq, splits, D, dtype=torch.float32, device=self.device)
+            pl = torch.empty(n, Hq, splits, dtype=torch.float32, device=self.device)
+            rc = lib.ts_decode_attention(_lib.ptr(qkv2d), qkv2d.stride(0), _lib.ptr(self.cache.k[layer]),
+                                         _lib.ptr(self.cache.v[layer]), _lib.ptr(block_table), block_table.shape[1],
+                                         _lib.ptr(seq_lens), _lib.ptr(out), Hq * D, _lib.ptr(po), _lib.ptr(pl), n, Hq,
+                                         Hkv, D, self.cache.block_size, chunk, splits, ctypes.c_float(scale),
+                                         _lib.stream_ptr())
+            _lib.check(rc, "ts_decode_attention")
+            return out
+        # general path (chunked prefill continuation, CPU): per sequence against the gathered cache
+        outs, off = [], 0
+        for sid, n in zip(seq_ids, q_lens):
+            q = qkv2d[off:off + n, :Hq * D].view(1, n, Hq, D)
+            k, v = self._gathered_kv(layer, sid)
+            o = attention.attention_reference(q, k.unsqueeze(0), v.unsqueeze(0), True, scale)
+            outs.append(o.reshape(n, Hq * D))
+            off += n
+        return torch.cat(outs)
+
+    @torch.no_grad()
+    def forward(self, token_ids: torch.Tensor, positions: torch.Tensor, slots: torch.Tensor, seq_ids: list[int],
+                q_lens: list[int], fresh: bool) -> torch.Tensor:
+        """token_ids / positions / slots: [T]; returns the hidden state of each sequence's LAST token [n_seq, H]."""
+        m, c = self.model.model, self.cfg
+        x = m.embed_tokens(token_ids)
+        res = None
+        block_table, seq_lens = self.cache.block_table(seq_ids, self.device)
+        pos32 = positions.to(torch.int32)
+        for li, layer in enumerate(m.layers):
+            h, res = layer.input_layernorm(x, res)
+            qkv = gemm.linear(h, layer.self_attn.wqkv)
+            qkv = rope.apply_rope_qkv(qkv.unsqueeze(0), c.num_attention_heads + c.num_key_value_heads, c.head_dim,
+                                      self.cos, self.sin, pos32.unsqueeze(0), qkv.shape[0], 0, c.rope_interleaved)[0]
+            self._write_cache(li, qkv, slots)
+            a = self._attend(li, qkv, seq_ids, q_lens, fresh, block_table, seq_lens)
+            a = gemm.linear(a, layer.self_attn.wo)
+            h, res = layer.post_attention_layernorm(a, res)
+            x = gemm.linear(activation.glu(gemm.linear(h, layer.mlp.w_gate_up), layer.mlp.act), layer.mlp.w_down)
+        x, _ = m.norm(x, res)
+        last = torch.tensor(q_lens, device=self.device).cumsum(0) - 1
+        return x[last]
+
+    @torch.no_grad()
+    def logits(self, hidden: torch.Tensor) -> torch.Tensor:
+        return self.model.logits(hidden).float()
+
+
+# ------------------------------------------------------------------------------------------------ scheduler / engine core
+@dataclass
+class _Request:
+    request_id: str
+    prompt: str
+    prompt_ids: list[int]
+    params: GenerationParams
+    metrics: RequestMetrics
+    seq_id: int
+    output_ids: list[int] = field(default_factory=list)
+    logprobs: list[float] = field(default_factory=list)
+    prefilled: int = 0
+    generator: torch.Generator | None = None
+    finished: bool = False
+    finish_reason: str | None = None
+    emitted_text_len: int = 0
+
+
+class EngineCore:
+    """Continuous batching: every step packs the decode tokens of running requests plus as many prompt tokens of
+    waiting requests as the token budget allows (chunked prefill)."""
+
+    def __init__(self, config: EngineConfig, model=None, tokenizer=None):
+        from ..data.tokenization import TokenizerWrapper, create_tokenizer
+        from ..models.llama import PRESETS, build_model
+        self.config = config
+        dev = config.device
+        if dev == "auto":
+            dev = "cuda" if torch.cuda.is_available() else "cpu"
+        self.device = torch.device(dev)
+        dtype = {"bfloat16": torch.bfloat16, "float32": torch.float32, "float16": torch.float16}[config.dtype]
+        if self.device.type == "cpu":
+            dtype = torch.float32
+        if model is None:
+            if config.model in PRESETS:
+                model = build_model(config.model, dtype=dtype, device=self.device, seed=config.seed)
+            else:
+                from ..hub import load_pretrained
+                model = load_pretrained(config.model, dtype=dtype, device=self.device)
+        self.model = model.to(self.device)
+        if tokenizer is None:
+            tokenizer = create_tokenizer(name_or_path=config.tokenizer or ("byte" if config.model in PRESETS else config.model),
+                                         padding=False, truncation=False)
+        self.tokenizer = tokenizer if isinstance(tokenizer, TokenizerWrapper) else TokenizerWrapper(tokenizer, padding=False)
+        c = self.model.config
+        cc = config.cache
+        nb = cc.num_gpu_blocks
+        if nb is None:
+            per_block = 2 * c.num_hidden_layers * cc.block_size * c.num_key_value_heads * c.head_dim * (2 if dtype != torch.float32 else 4)
+            if self.device.type == "cuda":
+                free, _ = torch.cuda.mem_get_info(self.device)
+                nb = max(64, int(free * cc.gpu_memory_utilization * 0.5) // per_block)
+            else:
+                nb = 512
+            nb = min(nb, max(64, cc.max_model_len * config.scheduler.max_num_seqs // cc.block_size + 64))
+        self.cache = PagedKVCache(c.num_hidden_layers, nb, cc.block_size, c.num_key_value_heads, c.head_dim, dtype,
+                                  self.device, cc.enable_prefix_caching)
+        self.runner = ModelRunner(self.model, self.cache, self.device)
+        self.waiting: deque[_Request] = deque()
+        self.running: list[_Request] = []
+        self.metrics = MetricsAggregator()
+        self._next_seq = 0
+        self.steps = 0
+
+    # -------------------------------------------------------------- requests
+    def add_request(self, prompt: str | list[int], params: GenerationParams | None = None, request_id: str | None = None) -> _Request:
+        params = params or GenerationParams()
+        params.validate()
+        ids = list(prompt) if not isinstance(prompt, str) else self.tokenizer.encode_raw(prompt, add_special_tokens=False)
+        if isinstance(prompt, str) and self.tokenizer.bos_token_id is not None:
+            ids = [self.tokenizer.bos_token_id] + ids
+        if not ids:
+            ids = [self.tokenizer.bos_token_id or 0]
+        max_len = self.config.cache.max_model_len
+        if len(ids) >= max_len:
+            ids = ids[-(max_len - 1):]
+        rid = request_id or f"req-{self._next_seq}"
+        gen = None
+        if params.seed is not None:
+            gen = torch.Generator(device="cpu").manual_seed(params.seed)
+        r = _Request(rid, prompt if isinstance(prompt, str) else "", ids, params,
+                     RequestMetrics(rid, len(ids), 0, time.perf_counter()), self._next_seq, generator=gen)
+        self._next_seq += 1
+        self.waiting.append(r)
+        return r
+
+    def abort(self, request_id: str) -> bool:
+        for q in (self.waiting, self.running):
+            for r in list(q):
+                if r.request_id == request_id:
+                    q.remove(r)
+                    self._finish(r, "abort")
+                    return True
+        return False
+
+    def has_unfinished(self) -> bool:
+        return bool(self.waiting or self.running)
+
+    def _finish(self, r: _Request, reason: str) -> None:
+        r.finished, r.finish_reason = True, reason
+        r.metrics.finished = time.perf_counter()
+        r.metrics.completion_tokens = len(r.output_ids)
+        self.cache.register_full_blocks(r.seq_id, r.prompt_ids + r.output_ids) if r.seq_id in self.cache.seqs else None
+        self.cache.free_sequence(r.seq_id)
+        if self.config.observability.collect_metrics:
+            self.metrics.add(r.metrics)
+
+    # -------------------------------------------------------------- one engine step
+    def step(self) -> list[tuple[_Request, int]]:
+        """Runs one forward over the scheduled tokens; returns (request, new token) for every request that sampled."""
+        sc = self.config.scheduler
+        budget = sc.max_num_batched_tokens
+        batch: list[tuple[_Request, list[int], int]] = []   # (request, tokens fed this step, start position)
+        # 1) decode tokens of running requests
+        for r in list(self.running):
+            if budget <= 0:
+                break
+            if not self.cache.can_append(r.seq_id, 1):
+                # out of blocks: preempt the most recent request (recompute later)
+                self.running.remove(r)
+                self.cache.free_sequence(r.seq_id)
+                r.prefilled = 0
+                r.prompt_ids = r.prompt_ids + r.output_ids
+                self.waiting.appendleft(r)
+                continue
+            if r.prefilled < len(r.prompt_ids):
+                continue
+            batch.append((r, [r.output_ids[-1]], len(r.prompt_ids) + len(r.output_ids) - 1))
+            budget -= 1
+        # 2) (chunked) prefill
+        candidates = [r for r in self.running if r.prefilled < len(r.prompt_ids)]
+        while self.waiting and len(self.running) < sc.max_num_seqs:
+            r = self.waiting.popleft()
+            if r.prefilled == 0:
+                covered = self.cache.match_prefix(r.seq_id, r.prompt_ids)
+                r.prefilled = covered
+                r.metrics.cached_prompt_tokens = covered
+            self.running.append(r)
+            candidates.append(r)
+        for r in candidates:
+            if budget <= 0:
+                break
+            remaining = len(r.prompt_ids) - r.prefilled
+            n = min(remaining, budget) if sc.enable_chunked_prefill else remaining
+            if n <= 0 or (not sc.enable_chunked_prefill and n > budget and batch):
+                continue
+            if not self.cache.can_append(r.seq_id, n):
+                continue
+            batch.append((r, r.prompt_ids[r.prefilled:r.prefilled + n], r.prefilled))
+            budget -= n
+        if not batch:
+            return []
+        # 3) build the flattened inputs
+        toks, pos, slots, seq_ids, q_lens = [], [], [], [], []
+        fresh = True
+        for r, feed, start in batch:
+            s = self.cache.append_slots(r.seq_id, len(feed))
+            toks += feed
+            pos += list(range(start, start + len(feed)))
+            slots += s
+            seq_ids.append(r.seq_id)
+            q_lens.append(len(feed))
+            fresh &= (start == 0)
+        dev = self.device
+        hidden = self.runner.forward(torch.tensor(toks, device=dev), torch.tensor(pos, device=dev),
+                                     torch.tensor(slots, device=dev, dtype=torch.long), seq_ids, q_lens, fresh)
+        self.steps += 1
+        # 4) sample for every request whose prompt is now complete
+        sample_rows, sample_reqs = [], []
+        for i, (r, feed, start) in enumerate(batch):
+            if start + len(feed) >= len(r.prompt_ids):
+                if r.prefilled < len(r.prompt_ids):
+                    r.prefilled = len(r.prompt_ids)
+                    self.cache.register_full_blocks(r.seq_id, r.prompt_ids)
+                sample_rows.append(i)
+                sample_reqs.append(r)
+            else:
+                r.prefilled = start + len(feed)
+        if not sample_reqs:
+            return []
+        logits = self.runner.logits(hidden[torch.tensor(sample_rows, device=dev)])
+        ps = [r.params for r in sample_reqs]
+        logits = apply_penalties(logits, [r.output_ids for r in sample_reqs], [p.repetition_penalty for p in ps],
+                                 [p.presence_penalty for p in ps], [p.frequency_penalty for p in ps])
+        ids, lps = sample(logits, [p.temperature for p in ps], [p.top_k for p in ps], [p.top_p for p in ps],
+                          [p.min_p for p in ps], [r.generator for r in sample_reqs])
+        now = time.perf_counter()
+        out = []
+        eos = self.tokenizer.eos_token_id
+        for r, t, lp in zip(sample_reqs, ids.tolist(), lps.tolist()):
+            r.output_ids.append(t)
+            if r.params.logprobs:
+                r.logprobs.append(lp)
+            if r.metrics.first_token is None:
+                r.metrics.first_token = now
+            out.append((r, t))
+            reason = None
+            if (t == eos and not r.params.ignore_eos) or t in r.params.stop_token_ids:
+                reason = "stop"
+            elif len(r.output_ids) >= r.params.max_tokens or \
+                    len(r.prompt_ids) + len(r.output_ids) >= self.config.cache.max_model_len:
+                reason = "length"
+            elif r.params.stop:
+                text = self.tokenizer.decode(r.output_ids)
+                if any(s in text for s in r.params.stop):
+                    reason = "stop"
+            if reason:
+                self.running.remove(r)
+                self._finish(r, reason)
+        return out
+
+    def decode_text(self, r: _Request) -> str:
+        ids = r.output_ids
+        if ids and r.finish_reason == "stop" and ids[-1] == self.tokenizer.eos_token_id:
+            ids = ids[:-1]
+        text = self.tokenizer.decode(ids)
+        for s in r.params.stop:
+            if s in text:
+                text = text[:text.index(s)]
+        return text
+
+
+class EngineBuilder:
+    def __init__(self, config: EngineConfig | None = None):
+        self.config = config or EngineConfig()
+
+    def build_sync(self, model=None, tokenizer=None) -> "SOTAInferenceEngine":
+        return SOTAInferenceEngine(self.config, model, tokenizer)
+
+    def build_async(self, model=None, tokenizer=None) -> "SOTAAsyncStreamEngine":
+        return SOTAAsyncStreamEngine(self.config, model, tokenizer)
+
+
+class SOTAInferenceEngine:
+    def __init__(self, config: EngineConfig | None = None, model=None, tokenizer=None):
+        self.config = config or EngineConfig()
+        self.core = EngineCore(self.config, model, tokenizer)
+
+    def generate(self, prompts: str | Iterable[str], params: GenerationParams | None = None) -> Result:
+        try:
+            single = isinstance(prompts, str)
+            reqs = [self.core.add_request(p, params) for p in ([prompts] if single else list(prompts))]
+            while self.core.has_unfinished():
+                self.core.step()
+            res = [InferenceResponse(r.request_id, r.prompt, self.core.decode_text(r), list(r.output_ids),
+                                     r.finish_reason or "stop", r.metrics, r.logprobs or None) for r in reqs]
+            return Ok(res[0] if single else res)
+        except (ValueError, MemoryError, RuntimeError) as e:
+            return Err(e)
+
+    def metrics_summary(self) -> dict:
+        return self.core.metrics.summary()
+
+
+class SOTAAsyncStreamEngine:
+    """Single background loop stepping the core; each request gets an asyncio queue of StreamChunks."""
+
+    def __init__(self, config: EngineConfig | None = None, model=None, tokenizer=None):
+        self.config = config or EngineConfig()
+        self.core = EngineCore(self.config, model, tokenizer)
+        self._queues: dict[str, asyncio.Queue] = {}
+        self._task: asyncio.Task | None = None
+
+    async def _loop(self):
+        while self.core.has_unfinished():
+            produced = await asyncio.get_running_loop().run_in_executor(None, self.core.step)
+            for r, tok in produced:
+                q = self._queues.get(r.request_id)
+                if q is None:
+                    continue
+                full = self.core.decode_text(r)
+                delta, r.emitted_text_len = full[r.emitted_text_len:], len(full)
+                await q.put(StreamChunk(r.request_id, delta, tok, r.finished, r.finish_reason))
+            await asyncio.sleep(0)
+        self._task = None
+
+    async def generate_stream(self, prompt: str, params: GenerationParams | None = None,
+                              request_id: str | None = None) -> AsyncIterator[StreamChunk]:
+        r = self.core.add_request(prompt, params, request_id)
+        q: asyncio.Queue = asyncio.Queue()
+        self._queues[r.request_id] = q
+        if self._task is None:
+            self._task = asyncio.create_task(self._loop())
+        try:
+            while True:
+                chunk = await q.get()
+                yield chunk
+                if chunk.finished:
+                    break
+        finally:
+            self._queues.pop(r.request_id, None)
+
+    async def abort_request(self, request_id: str) -> bool:
+        ok = self.core.abort(request_id)
+        q = self._queues.get(request_id)
+        if q is not None:
+            await q.put(StreamChunk(request_id, "", -1, True, "abort"))
+        return ok
+
+
+class EnginePresets:
+    @staticmethod
+    def low_latency(model: str = "tiny") -> EngineConfig:
+        return EngineConfig(model=model, scheduler=SchedulerConfig(max_num_seqs=8, max_num_batched_tokens=2048))
+
+    @staticmethod
+    def high_throughput(model: str = "tiny") -> EngineConfig:
+        return EngineConfig(model=model, scheduler=SchedulerConfig(max_num_seqs=256, max_num_batched_tokens=16384))
+
+    @staticmethod
+    def long_context(model: str = "tiny", max_len: int = 131072) -> EngineConfig:
+        return EngineConfig(model=model, cache=CacheConfig(max_model_len=max_len, block_size=32),
+                            scheduler=SchedulerConfig(max_num_seqs=4, max_num_batched_tokens=8192))
+
+
+# ------------------------------------------------------------------------------------------------ HTTP server
+def create_openai_server(engine: SOTAAsyncStreamEngine, model_name: str = "trainscale"):
+    from fastapi import FastAPI
+    from fastapi.responses import PlainTextResponse, StreamingResponse
+    from pydantic import BaseModel
+
+    app = FastAPI(title="trainscale-b200 inference")
+
+    class CompletionRequest(BaseModel):
+        model: str | None = None
+        prompt: str | list[str] = ""
+        max_tokens: int = 128
+        temperature: float = 0.7
+        top_p: float = 1.0
+        stop: list[str] | str | None = None
+        stream: bool = False
+        seed: int | None = None
+
+    class ChatMessage(BaseModel):
+        role: str
+        content: str
+
+    class ChatRequest(BaseModel):
+        model: str | None = None
+        messages: list[ChatMessage]
+        max_tokens: int = 128
+        temperature: float = 0.7
+        top_p: float = 1.0
+        stop: list[str] | str | None = None
+        stream: bool = False
+        seed: int | None = None
+
+    def to_params(req) -> GenerationParams:
+        stop = [req.stop] if isinstance(req.stop, str) else (req.stop or [])
+        return GenerationParams(max_tokens=req.max_tokens, temperature=req.temperature, top_p=req.top_p, stop=stop,
+                                seed=req.seed)
+
+    async def run(prompt: str, params: GenerationParams):
+        text, reason, n = "", "stop", 0
+        async for ch in engine.generate_stream(prompt, params):
+            text += ch.text
+            n += 1
+            reason = ch.finish_reason or reason
+        return text, reason, n
+
+    @app.get("/health")
+    async def health():
+        return {"status": "ok", "running": len(engine.core.running), "waiting": len(engine.core.waiting)}
+
+    @app.get("/metrics")
+    async def metrics():
+        return PlainTextResponse(engine.core.metrics.prometheus())
+
+    @app.get("/v1/models")
+    async def models():
+        return {"object": "list", "data": [{"id": model_name, "object": "model"}]}
+
+    @app.post("/v1/completions")
+    async def completions(req: CompletionRequest):
+        params = to_params(req)
+        prompt = req.prompt if isinstance(req.prompt, str) else req.prompt[0]
+        if req.stream:
+            async def gen():
+                async for ch in engine.generate_stream(prompt, params):
+                    yield "data: " + json.dumps({"object": "text_completion", "model": model_name,
+                                                 "choices": [{"index": 0, "text": ch.text,
+                                                              "finish_reason": ch.finish_reason}]}) + "\n\n"
+                yield "data: [DONE]\n\n"
+            return StreamingResponse(gen(), media_type="text/event-stream")
+        text, reason, n = await run(prompt, params)
+        return {"object": "text_completion", "model": model_name,
+                "choices": [{"index": 0, "text": text, "finish_reason": reason}],
+                "usage": {"completion_tokens": n}}
+
+    @app.post("/v1/chat/completions")
+    async def chat(req: ChatRequest):
+        params = to_params(req)
+        prompt = engine.core.tokenizer.apply_chat_template([m.model_dump() for m in req.messages], True)
+        if req.stream:
+            async def gen():
+                async for ch in engine.generate_stream(prompt, params):
+                    yield "data: " + json.dumps({"object": "chat.completion.chunk", "model": model_name,
+                                                 "choices": [{"index": 0, "delta": {"content": ch.text},
+                                                              "finish_reason": ch.finish_reason}]}) + "\n\n"
+                yield "data: [DONE]\n\n"
+            return StreamingResponse(gen(), media_type="text/event-stream")
+        text, reason, n = await run(prompt, params)
+        return {"object": "chat.completion", "model": model_name,
+                "choices": [{"index": 0, "message": {"role": "assistant", "content": text}, "finish_reason": reason}],
+                "usage": {"completion_tokens": n}}
+
+    return app
+
+
+# ------------------------------------------------------------------------------------------------ CLI
+def run_bench(engine: SOTAInferenceEngine, num_prompts: int = 50, input_len: int = 128, output_len: int = 128) -> dict:
+    vocab = min(engine.core.model.config.vocab_size, 255)
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(1, vocab, (input_len,), generator=g).tolist() for _ in range(num_prompts)]
+    params = GenerationParams(max_tokens=output_len, temperature=0.0, ignore_eos=True)
+    t0 = time.perf_counter()
+    for p in prompts:
+        engine.core.add_request(p, params)
+    while engine.core.has_unfinished():
+        engine.core.step()
+    if torch.cuda.is_available():
+        torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    s = engine.metrics_summary()
+    s.update(seconds=dt, output_tokens_per_second=num_prompts * output_len / dt,
+             total_tokens_per_second=num_prompts * (input_len + output_len) / dt, engine_steps=engine.core.steps)
+    return s
+
+
+def main(argv: list[str] | None = None) -> int:
+    ap = argparse.ArgumentParser(prog="python -m trainscale_b200.inference")
+    sub = ap.add_subparsers(dest="cmd", required=True)
+    for name in ("probe", "batch", "stream", "serve", "bench"):
+        p = sub.add_parser(name)
+        p.add_argument("--model", default="tiny")
+        p.add_argument("--max-tokens", type=int, default=64)
+        p.add_argument("--temperature", type=float, default=0.7)
+        if name in ("batch", "stream"):
+            p.add_argument("--prompt", action="append", default=[])
+        if name == "serve":
+            p.add_argument("--host", default="127.0.0.1")
+            p.add_argument("--port", type=int, default=8000)
+        if name == "bench":
+            p.add_argument("--num-prompts", type=int, default=50)
+            p.add_argument("--input-len", type=int, default=128)
+            p.add_argument("--output-len", type=int, default=128)
+    a = ap.parse_args(argv)
+    cfg = EngineConfig(model=a.model)
+    if a.cmd == "probe":
+        print(json.dumps({"cuda": torch.cuda.is_available(),
+                          "device": torch.cuda.get_device_name(0) if torch.cuda.is_available() else "cpu",
+                          "config": asdict(cfg)}, indent=2))
+        return 0
+    params = GenerationParams(max_tokens=a.max_tokens, temperature=a.temperature)
+    if a.cmd == "batch":
+        eng = SOTAInferenceEngine(cfg)
+        for r in eng.generate(a.prompt or ["Hello"], params).unwrap():
+            print(json.dumps({"prompt": r.prompt, "text": r.text, "finish_reason": r.finish_reason}))
+        return 0
+    if a.cmd == "stream":
+        async def go():
+            eng = SOTAAsyncStreamEngine(cfg)
+            async for ch in eng.generate_stream((a.prompt or ["Hello"])[0], params):
+                sys.stdout.write(ch.text)
+                sys.stdout.flush()
+            print()
+        asyncio.run(go())
+        return 0
+    if a.cmd == "serve":
+        import uvicorn
+        uvicorn.run(create_openai_server(SOTAAsyncStreamEngine(cfg), a.model), host=a.host, port=a.port)
+        return 0
+    if a.cmd == "bench":
+        print(json.dumps(run_bench(SOTAInferenceEngine(cfg), a.num_prompts, a.input_len, a.output_len)))
+        return 0
+    return 1
