@@ -1,0 +1,178 @@
+"""Kernel micro-benchmarks: `python -m trainscale_b200.benchmark_suite [--only NAME] [--small] [--json out.json]`.
+
+Same cases as data_pipeline/trainer/kernels/benchmark_suite.py:97-340 (RMSNorm, GELU/SwiGLU, RoPE, cross-entropy,
+flash attention) plus the GEMM and optimizer kernels, each timed with CUDA events after warm-up (L2 flushed between
+iterations) against a PyTorch baseline, and reported as achieved bandwidth / FLOP rate and as a fraction of the
+measured peaks (MEASURED_PEAKS.json next to the repository root when present).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+from pathlib import Path
+
+import torch
+import torch.nn.functional as F
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def peaks() -> dict:
+    try:
+        return json.loads((ROOT / "MEASURED_PEAKS.json").read_text())
+    except Exception:
+        return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "fallback": True}
+
+
+class Timer:
+    def __init__(self, flush_mb: int = 256):
+        self.flush = torch.empty(flush_mb * 2 ** 20, dtype=torch.int8, device="cuda")
+
+    def __call__(self, fn, iters: int = 10, warmup: int = 3) -> float:
+        for _ in range(warmup):
+            fn()
+        torch.cuda.synchronize()
+        total = 0.0
+        for _ in range(iters):
+            self.flush.zero_()           # evict L2 (126 MB)
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            total += a.elapsed_time(b)
+        return total / iters
+
+
+def bench_rmsnorm(t, small):
+    from .ops import norm
+    out = []
+    shapes = [(4, 2048, 4096)] if small else [(4, 2048, 4096), (4, 4096, 8192), (32, 2048, 4096), (32, 4096, 8192)]
+    for B, S, D in shapes:
+        x = torch.randn(B * S, D, device="cuda", dtype=torch.bfloat16)
+        w = torch.ones(D, device="cuda", dtype=torch.bfloat16)
+        ms = t(lambda: norm.rmsnorm(x, w))
+        base = t(lambda: F.rms_norm(x, (D,), w, 1e-5))
+        out.append(dict(name=f"rmsnorm B={B},S={S},D={D}", ms=ms, baseline_ms=base, gbs=2 * x.numel() * 2 / ms / 1e6))
+    return out
+
+
+def bench_swiglu(t, small):
+    from .ops import activation
+    out = []
+    for rows, I in ([(2048, 11008)] if small else [(2048, 11008), (8192, 14336)]):
+        gu = torch.randn(rows, 2 * I, device="cuda", dtype=torch.bfloat16)
+        ms = t(lambda: activation.glu(gu))
+        base = t(lambda: F.silu(gu[:, :I]) * gu[:, I:])
+        out.append(dict(name=f"swiglu rows={rows},I={I}", ms=ms, baseline_ms=base, gbs=3 * rows * I * 2 / ms / 1e6))
+    return out
+
+
+def bench_rope(t, small):
+    from .ops import rope
+    out = []
+    for S in ([4096] if small else [4096, 8192, 16384]):
+        Hq, Hkv, D = 32, 8, 128
+        cos, sin = rope.rope_tables(S, D, 500000.0, "cuda")
+        qkv = torch.randn(1, S, (Hq + 2 * Hkv) * D, device="cuda", dtype=torch.bfloat16)
+        ms = t(lambda: rope.apply_rope_qkv(qkv, Hq + Hkv, D, cos, sin))
+        base = t(lambda: qkv.clone())
+        out.append(dict(name=f"rope S={S}", ms=ms, baseline_ms=base, gbs=2 * qkv.numel() * 2 / ms / 1e6))
+    return out
+
+
+def bench_cross_entropy(t, small):
+    from .ops import cross_entropy as ce
+    out = []
+    V = 128256
+    for T in ([4096] if small else [4096, 16384]):
+        logits = torch.randn(T, V, device="cuda", dtype=torch.bfloat16)
+        labels = torch.randint(0, V, (T,), device="cuda")
+        ms = t(lambda: ce.cross_entropy_logits(logits, labels), iters=5)
+        base = t(lambda: F.cross_entropy(logits.float(), labels), iters=5)
+        out.append(dict(name=f"cross_entropy T={T},V={V}", ms=ms, baseline_ms=base, gbs=logits.numel() * 2 / ms / 1e6))
+    return out
+
+
+def bench_gemm(t, small):
+    from .ops import gemm
+    out = []
+    shapes = [(4096, 4096, 4096)] if small else [(8192, 4096, 4096), (8192, 6144, 4096), (8192, 28672, 4096),
+                                                 (8192, 4096, 14336), (8192, 128256, 4096)]
+    for M, N, K in shapes:
+        a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+        b = torch.randn(N, K, device="cuda", dtype=torch.bfloat16)
+        c = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        ms = t(lambda: gemm.matmul_nt(a, b, out=c))
+        base = t(lambda: torch.matmul(a, b.t(), out=c))
+        out.append(dict(name=f"gemm {M}x{N}x{K}", ms=ms, baseline_ms=base, tflops=2 * M * N * K / ms / 1e9))
+    return out
+
+
+def bench_attention(t, small):
+    from .ops import flash
+    out = []
+    for S in ([2048] if small else [4096, 8192, 16384]):
+        Hq, Hkv, D = 32, 8, 128
+        qkv = torch.randn(1, S, (Hq + 2 * Hkv) * D, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+        ms = t(lambda: flash.flash_forward_only(qkv.detach(), Hq, Hkv, D, True))
+        q, k, v = [x.transpose(1, 2) for x in qkv.detach().view(1, S, Hq + 2 * Hkv, D).split((Hq, Hkv, Hkv), 2)]
+        base = t(lambda: F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True))
+        fl = 4 * S * S * D * Hq / 2
+        out.append(dict(name=f"flash_fwd S={S}", ms=ms, baseline_ms=base, tflops=fl / ms / 1e9))
+        o = flash.flash_attention_qkv(qkv, Hq, Hkv, D, True)
+        g = torch.randn_like(o)
+        ms = t(lambda: o.backward(g, retain_graph=True), iters=5)
+        out.append(dict(name=f"flash_bwd S={S}", ms=ms, baseline_ms=None, tflops=2.5 * fl / ms / 1e9))
+    return out
+
+
+def bench_adamw(t, small):
+    from .ops import optim
+    n = (1 << 26) if small else (1 << 28)
+    p, m, v = (torch.zeros(n, device="cuda") for _ in range(3))
+    g = torch.randn(n, device="cuda").to(torch.bfloat16)
+    low = torch.empty(n, device="cuda", dtype=torch.bfloat16)
+    ms = t(lambda: optim.adamw_flat_(p, m, v, g, low, lr=1e-3, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1, step=3),
+           iters=5)
+    return [dict(name=f"adamw_flat n={n}", ms=ms, baseline_ms=None, gbs=n * 28 / ms / 1e6)]
+
+
+CASES = {"rmsnorm": bench_rmsnorm, "swiglu": bench_swiglu, "rope": bench_rope, "cross_entropy": bench_cross_entropy,
+         "gemm": bench_gemm, "attention": bench_attention, "adamw": bench_adamw}
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--only", default=None, choices=sorted(CASES))
+    ap.add_argument("--small", action="store_true", help="one small shape per case (for profiler captures)")
+    ap.add_argument("--json", default=None)
+    ap.add_argument("--device", default="cuda")
+    a = ap.parse_args(argv)
+    if not torch.cuda.is_available():
+        print("no CUDA device")
+        return 0
+    pk = peaks()
+    t = Timer(64 if a.small else 256)
+    rows = []
+    for name, fn in CASES.items():
+        if a.only and name != a.only:
+            continue
+        rows += fn(t, a.small)
+    tag = "of fallback" if pk.get("fallback") else "of measured"
+    for r in rows:
+        frac = r["gbs"] / pk["hbm_gbs"] if "gbs" in r else r["tflops"] / pk["bf16_tflops"]
+        r["fraction_of_peak"] = frac
+        sp = f"{r['baseline_ms'] / r['ms']:.2f}x" if r.get("baseline_ms") else "  -  "
+        rate = f"{r['gbs']:.0f} GB/s" if "gbs" in r else f"{r['tflops']:.0f} TFLOPS"
+        print(f"{r['name']:<40s} {r['ms']:8.3f} ms  baseline {r.get('baseline_ms') or float('nan'):8.3f} ms  {sp:>7s}  "
+              f"{rate:>12s}  {frac:5.2f} {tag}")
+    if a.json:
+        Path(a.json).write_text(json.dumps(rows, indent=1))
+    from .ops import _lib
+    _lib.raise_on_any_device_error()
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())
