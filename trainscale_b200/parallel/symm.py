@@ -70,8 +70,7 @@ class SymmetricHeap:
         h = symm_mem.rendezvous(t, self.group)
         t.zero_()
         arr = ctypes.c_ulonglong * self.world
-        mc = int(h.multicast_ptr) if (self.use_multicast and h.has_multicast_support(self.device.type, self.device.index)
-                                      ) else 0
+        mc = int(getattr(h, "multicast_ptr", 0) or 0) if self.use_multicast else 0
         buf = SymmBuffer(t, h, arr(*[int(p) for p in h.buffer_ptrs]), arr(*[int(p) for p in h.signal_pad_ptrs]), mc, {})
         self._by_ptr[t.data_ptr()] = buf
         return t
