@@ -68,3 +68,12 @@ def test_head_tail_and_zigzag_layouts_roundtrip():
     b = shard_inputs({"input_ids": x}, 4, 1)
     assert b["position_ids"][0].tolist() == list(range(4, 8)) + list(range(24, 28))
     assert b["labels"][0, 3].item() == x[0, 8].item() and b["labels"][0, -1].item() == x[0, 28].item()
+
+
+def test_expert_parallel_moe_matches_local_moe():
+    case = Path(__file__).parent / "dist_cases" / "ep_equivalence.py"
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+           "127.0.0.1", "--master-port", "29682", str(case)]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    assert r.stdout.count("ok=True") == 2

@@ -1,0 +1,133 @@
+"""LoRA / rsLoRA / DoRA-style adapters for the framework decoder's fused projections.
+
+Surface after data_pipeline/trainer/lora.py:69-408 (`LoRALinear`, `get_peft_model`, `merge_and_unload`, `apply_lora`)
+and the fused LoRA kernels of data_pipeline/trainer/kernels/fast_lora_mlp.py:126-631: the adapter path
+`s * (x A^T) B^T` runs on the tcgen05 GEMM next to the frozen base GEMM, and its backward is four small GEMMs.
+HF target names (q_proj, k_proj, v_proj, o_proj, gate_proj, up_proj, down_proj) map onto row blocks of the fused
+`wqkv` / `w_gate_up` weights, so a q/v-only LoRA touches only those output rows.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.nn as nn
+
+from .ops import gemm
+
+
+class LoRALinear(nn.Module):
+    """Low-rank update for one row block [row0, row0+rows) of a (possibly fused) weight."""
+
+    def __init__(self, in_features: int, rows: int, r: int = 16, alpha: float = 32.0, dropout: float = 0.0,
+                 use_rslora: bool = True, row0: int = 0, total_rows: int | None = None, dtype=None, device=None,
+                 init: bool | str = True):
+        super().__init__()
+        self.r, self.row0, self.rows, self.total_rows = r, row0, rows, total_rows or rows
+        self.scaling = alpha / math.sqrt(r) if use_rslora else alpha / r
+        self.lora_A = nn.Parameter(torch.empty(r, in_features, dtype=dtype, device=device))
+        self.lora_B = nn.Parameter(torch.zeros(rows, r, dtype=dtype, device=device))
+        self.dropout = nn.Dropout(dropout) if dropout > 0 else None
+        if init == "gaussian":
+            nn.init.normal_(self.lora_A, std=1.0 / r)
+        else:
+            nn.init.kaiming_uniform_(self.lora_A, a=math.sqrt(5))
+
+    def delta(self, x: torch.Tensor) -> torch.Tensor:
+        if self.dropout is not None:
+            x = self.dropout(x)
+        return gemm.linear(gemm.linear(x, self.lora_A), self.lora_B) * self.scaling
+
+    def delta_weight(self) -> torch.Tensor:
+        return (self.lora_B.float() @ self.lora_A.float()) * self.scaling
+
+
+class FusedLoRA(nn.Module):
+    """All adapters of one fused weight; output is laid out like the fused projection's output."""
+
+    def __init__(self, parts: list[LoRALinear]):
+        super().__init__()
+        self.parts = nn.ModuleList(parts)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        total = self.parts[0].total_rows
+        if len(self.parts) == 1 and self.parts[0].rows == total:
+            return self.parts[0].delta(x)
+        out = x.new_zeros(*x.shape[:-1], total)
+        for p in self.parts:
+            out[..., p.row0:p.row0 + p.rows] = p.delta(x)
+        return out
+
+
+def _targets_for(model_cfg) -> dict:
+    """HF projection name -> (module kind, fused weight name, row0, rows)."""
+    D, Hq, Hkv, I = model_cfg.head_dim, model_cfg.num_attention_heads, model_cfg.num_key_value_heads, model_cfg.intermediate_size
+    H = model_cfg.hidden_size
+    return {"q_proj": ("attn", "wqkv", 0, Hq * D), "k_proj": ("attn", "wqkv", Hq * D, Hkv * D),
+            "v_proj": ("attn", "wqkv", (Hq + Hkv) * D, Hkv * D), "o_proj": ("attn", "wo", 0, H),
+            "gate_proj": ("mlp", "w_gate_up", 0, I), "up_proj": ("mlp", "w_gate_up", I, I),
+            "down_proj": ("mlp", "w_down", 0, H)}
+
+
+def get_peft_model(model, r: int = 16, lora_alpha: float = 32.0, lora_dropout: float = 0.0,
+                   target_modules: list[str] | None = None, use_rslora: bool = True, modules_to_save: list[str] | None = None,
+                   init_lora_weights: bool | str = True, rank_pattern: dict | None = None):
+    """Freeze the base weights and attach adapters. Returns the same model object."""
+    targets = _targets_for(model.config)
+    wanted = [t for t in (target_modules or list(targets)) if t in targets]
+    for p in model.parameters():
+        p.requires_grad_(False)
+    for li, layer in enumerate(model.model.layers):
+        for kind, mod in (("attn", layer.self_attn), ("mlp", layer.mlp)):
+            inner = getattr(mod, "inner", mod)
+            by_weight: dict[str, list[LoRALinear]] = {}
+            for t in wanted:
+                k, wname, row0, rows = targets[t]
+                if k != kind:
+                    continue
+                w = getattr(inner, wname)
+                rank = (rank_pattern or {}).get(f"layers.{li}.{t}", (rank_pattern or {}).get(t, r))
+                by_weight.setdefault(wname, []).append(
+                    LoRALinear(w.shape[1], rows, rank, lora_alpha, lora_dropout, use_rslora, row0, w.shape[0], w.dtype,
+                               w.device, init_lora_weights))
+            if by_weight:
+                inner.lora = nn.ModuleDict({k: FusedLoRA(v) for k, v in by_weight.items()})
+    for name in modules_to_save or []:
+        for n, p in model.named_parameters():
+            if name in n or (name == "lm_head" and n == "lm_head"):
+                p.requires_grad_(True)
+    return model
+
+
+@torch.no_grad()
+def merge_and_unload(model):
+    """Fold every adapter into its base weight and remove the adapters."""
+    for layer in model.model.layers:
+        for mod in (layer.self_attn, layer.mlp):
+            inner = getattr(mod, "inner", mod)
+            if inner.lora is None:
+                continue
+            for wname, fused in inner.lora.items():
+                w = getattr(inner, wname)
+                for p in fused.parts:
+                    w[p.row0:p.row0 + p.rows] += p.delta_weight().to(w.dtype)
+            inner.lora = None
+    for p in model.parameters():
+        p.requires_grad_(True)
+    return model
+
+
+def apply_lora(model, lora_cfg):
+    """From a SOTAConfig `lora` section."""
+    return get_peft_model(model, lora_cfg.r, lora_cfg.lora_alpha, lora_cfg.lora_dropout, list(lora_cfg.target_modules),
+                          lora_cfg.use_rslora, list(lora_cfg.modules_to_save or []), lora_cfg.init_lora_weights,
+                          dict(lora_cfg.rank_pattern or {}))
+
+
+def lora_state_dict(model) -> dict[str, torch.Tensor]:
+    return {n: p.detach().cpu() for n, p in model.named_parameters() if "lora_" in n}
+
+
+def count_trainable(model) -> tuple[int, int]:
+    t = sum(p.numel() for p in model.parameters() if p.requires_grad)
+    return t, sum(p.numel() for p in model.parameters())

@@ -103,6 +103,14 @@ def preset_config(name: str, **overrides) -> LlamaConfig:
     return LlamaConfig(**d)
 
 
+def _lin(mod, x, name: str):
+    """x @ W^T plus the low-rank adapter of that weight when one is attached."""
+    y = gemm.linear(x, getattr(mod, name))
+    if mod.lora is not None and name in mod.lora:
+        y = y + mod.lora[name](x)
+    return y
+
+
 class RMSNorm(nn.Module):
     def __init__(self, dim: int, eps: float = 1e-5):
         super().__init__()
@@ -120,18 +128,23 @@ class LlamaAttention(nn.Module):
         self.n_heads, self.n_kv, self.hd = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
         self.wqkv = nn.Parameter(torch.empty((self.n_heads + 2 * self.n_kv) * self.hd, cfg.hidden_size))
         self.wo = nn.Parameter(torch.empty(cfg.hidden_size, self.n_heads * self.hd))
+        self.lora = None      # nn.ModuleDict of low-rank adapters keyed by weight name (see lora.py)
+        self.cp_group = None  # context-parallel process group (ring attention) when set
 
     def forward(self, x, cos, sin, position_ids=None, cu_seqlens=None, doc_ids=None, kv_cache=None):
-        qkv = gemm.linear(x, self.wqkv)
+        qkv = _lin(self, x, "wqkv")
         offset = 0 if kv_cache is None else kv_cache.seq_len
         qkv = rope.apply_rope_qkv(qkv, self.n_heads + self.n_kv, self.hd, cos, sin, position_ids, x.shape[-2], offset,
                                   self.cfg.rope_interleaved)
         if kv_cache is not None:
             o = kv_cache.attend(qkv, self)
+        elif self.cp_group is not None:
+            from ..parallel.cp import attention_qkv_cp
+            o = attention_qkv_cp(qkv, self.n_heads, self.n_kv, self.hd, self.cp_group)
         else:
             o = attention.attention_qkv(qkv, self.n_heads, self.n_kv, self.hd, True, None, self.cfg.sliding_window,
                                         self.cfg.attn_logit_softcap, cu_seqlens, doc_ids)
-        return gemm.linear(o, self.wo)
+        return _lin(self, o, "wo")
 
 
 class LlamaMLP(nn.Module):
@@ -140,9 +153,10 @@ class LlamaMLP(nn.Module):
         self.act = cfg.hidden_act
         self.w_gate_up = nn.Parameter(torch.empty(2 * cfg.intermediate_size, cfg.hidden_size))
         self.w_down = nn.Parameter(torch.empty(cfg.hidden_size, cfg.intermediate_size))
+        self.lora = None
 
     def forward(self, x):
-        return gemm.linear(activation.glu(gemm.linear(x, self.w_gate_up), self.act), self.w_down)
+        return _lin(self, activation.glu(_lin(self, x, "w_gate_up"), self.act), "w_down")
 
 
 class LlamaDecoderLayer(nn.Module):

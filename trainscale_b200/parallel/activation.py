@@ -1,0 +1,182 @@
+"""Activation checkpointing policies and activation offload to pinned host memory.
+
+After data_pipeline/trainer/distributed/activation_checkpoint.py:85-2356 (modes NONE / SELECTIVE (every n-th layer) /
+MEMORY_BUDGET / FULL / OFFLOAD / HIERARCHICAL, `MemoryProfiler`, `ActivationCheckpoint.apply`) and
+activation_offload.py:92-910 (pinned `TensorPool`, saved-tensor hooks, d2h / h2d streams, byte summary).
+"""
+from __future__ import annotations
+
+import contextlib
+from dataclasses import dataclass, field
+from enum import Enum
+
+import torch
+import torch.nn as nn
+
+
+class CheckpointMode(str, Enum):
+    NONE = "none"
+    SELECTIVE = "selective"
+    OP_SELECTIVE = "op_selective"
+    MEMORY_BUDGET = "memory_budget"
+    FULL = "full"
+    OFFLOAD = "offload"
+    HIERARCHICAL = "hierarchical"
+
+
+@dataclass
+class ActivationCheckpointConfig:
+    mode: CheckpointMode = CheckpointMode.SELECTIVE
+    frequency: int = 2                 # SELECTIVE: recompute every n-th layer
+    memory_budget_gb: float | None = None
+    bytes_per_layer: float | None = None
+    offload_min_bytes: int = 1 << 20
+    hierarchical_group: int = 4
+
+
+class MemoryProfiler:
+    _inst = None
+
+    def __new__(cls):
+        if cls._inst is None:
+            cls._inst = super().__new__(cls)
+            cls._inst.snapshots = []
+        return cls._inst
+
+    def snapshot(self, tag: str = "") -> dict:
+        if torch.cuda.is_available():
+            s = {"tag": tag, "allocated": torch.cuda.memory_allocated(), "reserved": torch.cuda.memory_reserved(),
+                 "peak": torch.cuda.max_memory_allocated()}
+        else:
+            s = {"tag": tag, "allocated": 0, "reserved": 0, "peak": 0}
+        self.snapshots.append(s)
+        return s
+
+    def pressure(self) -> float:
+        if not torch.cuda.is_available():
+            return 0.0
+        free, total = torch.cuda.mem_get_info()
+        return 1.0 - free / total
+
+
+class SelectiveCheckpointPolicy:
+    def __init__(self, cfg: ActivationCheckpointConfig, num_layers: int):
+        self.cfg, self.L = cfg, num_layers
+
+    def layers_to_checkpoint(self) -> list[int]:
+        m = CheckpointMode(self.cfg.mode)
+        if m == CheckpointMode.NONE:
+            return []
+        if m in (CheckpointMode.FULL, CheckpointMode.OFFLOAD):
+            return list(range(self.L))
+        if m == CheckpointMode.MEMORY_BUDGET and self.cfg.memory_budget_gb and self.cfg.bytes_per_layer:
+            keep = int(self.cfg.memory_budget_gb * 2 ** 30 // self.cfg.bytes_per_layer)
+            return list(range(max(0, self.L - keep)))     # recompute the earliest layers, keep the latest
+        if m == CheckpointMode.HIERARCHICAL:
+            g = max(1, self.cfg.hierarchical_group)
+            return [i for i in range(self.L) if i % g != g - 1]
+        f = max(1, self.cfg.frequency)
+        return [i for i in range(self.L) if i % f == 0]
+
+
+class ActivationCheckpoint:
+    def __init__(self, cfg: ActivationCheckpointConfig | None = None):
+        self.cfg = cfg or ActivationCheckpointConfig()
+
+    def apply(self, model) -> list[int]:
+        """Configure the framework decoder (it recomputes layer i when i % checkpoint_every == 0) or wrap generic
+        `nn.ModuleList` layers with torch's checkpoint wrapper. Returns the checkpointed layer indices."""
+        inner = getattr(model, "model", model)
+        layers = getattr(inner, "layers", None)
+        if layers is None:
+            return []
+        chosen = SelectiveCheckpointPolicy(self.cfg, len(layers)).layers_to_checkpoint()
+        if hasattr(inner, "gradient_checkpointing"):
+            inner.gradient_checkpointing = bool(chosen)
+            inner.checkpoint_layers = set(chosen)
+            if chosen:
+                steps = sorted(set(b - a for a, b in zip(chosen, chosen[1:]))) or [1]
+                inner.checkpoint_every = steps[0] if len(steps) == 1 and chosen[0] == 0 else 1
+            return chosen
+        from torch.distributed.algorithms._checkpoint.checkpoint_wrapper import checkpoint_wrapper
+        for i in chosen:
+            layers[i] = checkpoint_wrapper(layers[i])
+        return chosen
+
+
+def create_activation_checkpoint_from_config(d: dict | None) -> ActivationCheckpoint:
+    d = dict(d or {})
+    mode = d.get("ac_mode", d.get("mode", "selective"))
+    return ActivationCheckpoint(ActivationCheckpointConfig(CheckpointMode(mode), int(d.get("ac_frequency", d.get("frequency", 2)))))
+
+
+class PinnedTensorPool:
+    """Reusable pinned host buffers keyed by (shape, dtype)."""
+
+    def __init__(self):
+        self.free: dict[tuple, list[torch.Tensor]] = {}
+        self.bytes_allocated = 0
+
+    def get(self, shape, dtype) -> torch.Tensor:
+        key = (tuple(shape), dtype)
+        lst = self.free.get(key)
+        if lst:
+            return lst.pop()
+        t = torch.empty(shape, dtype=dtype, pin_memory=torch.cuda.is_available())
+        self.bytes_allocated += t.numel() * t.element_size()
+        return t
+
+    def put(self, t: torch.Tensor) -> None:
+        self.free.setdefault((tuple(t.shape), t.dtype), []).append(t)
+
+
+class ActivationOffloader:
+    """`with offloader.scope():` moves saved activations >= min_bytes to pinned host memory on a copy stream and
+    brings them back on demand in backward (saved-tensor hooks)."""
+
+    def __init__(self, min_bytes: int = 1 << 20):
+        self.min_bytes = min_bytes
+        self.pool = PinnedTensorPool()
+        self.cuda = torch.cuda.is_available()
+        self.d2h = torch.cuda.Stream() if self.cuda else None
+        self.h2d = torch.cuda.Stream() if self.cuda else None
+        self.offloaded_bytes = 0
+        self.restored_bytes = 0
+
+    def _pack(self, t: torch.Tensor):
+        if not t.is_cuda or t.numel() * t.element_size() < self.min_bytes or isinstance(t, nn.Parameter) \
+                or getattr(t, "_ts_unit", None) is not None or not t.is_contiguous():
+            return t
+        host = self.pool.get(t.shape, t.dtype)
+        self.d2h.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(self.d2h):
+            host.copy_(t, non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record(self.d2h)
+        t.record_stream(self.d2h)
+        self.offloaded_bytes += t.numel() * t.element_size()
+        return ("offloaded", host, ev, t.device)
+
+    def _unpack(self, obj):
+        if not (isinstance(obj, tuple) and len(obj) == 4 and obj[0] == "offloaded"):
+            return obj
+        _, host, ev, dev = obj
+        ev.synchronize()
+        with torch.cuda.stream(self.h2d):
+            out = host.to(dev, non_blocking=True)
+        torch.cuda.current_stream().wait_stream(self.h2d)
+        self.pool.put(host)
+        self.restored_bytes += out.numel() * out.element_size()
+        return out
+
+    @contextlib.contextmanager
+    def scope(self):
+        if not self.cuda:
+            yield self
+            return
+        with torch.autograd.graph.saved_tensors_hooks(self._pack, self._unpack):
+            yield self
+
+    def summary(self) -> str:
+        return (f"offloaded {self.offloaded_bytes / 2 ** 30:.2f} GiB, restored {self.restored_bytes / 2 ** 30:.2f} GiB, "
+                f"pinned pool {self.pool.bytes_allocated / 2 ** 30:.2f} GiB")

@@ -1,0 +1,257 @@
+"""Replicated data parallelism: the DDP engine surface, gradient-compression hooks and hierarchical all-reduce.
+
+After data_pipeline/trainer/distributed/ddp.py:115-1953 (bucket-size table by interconnect, GradientCompression
+NONE / FP16 / BF16 / POWERSGD / TOPK, comm hooks, `HierarchicalAllReduceManager`, `SOTADDPEngine.wrap_model /
+no_sync / check_health`, `DDPInitializer.init_process_group`, `create_ddp_engine`).  The engine itself is the flat
+engine in NO_SHARD mode (one contiguous gradient buffer per decoder layer = one bucket, all-reduced on a side stream
+as soon as the layer's backward has been queued); hooks transform a bucket before / after its all-reduce.
+"""
+from __future__ import annotations
+
+import contextlib
+import datetime
+import os
+from dataclasses import dataclass, field
+from enum import Enum
+from typing import Callable
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+from ..core.types import Err, Ok, Result
+
+BUCKET_MB = {"b200_nvlink": (80, 40), "h100_nvlink": (50, 25), "a100_nvlink": (40, 25), "pcie": (25, 25), "cpu": (25, 25)}
+
+
+def detect_gpu_topology() -> str:
+    if not torch.cuda.is_available():
+        return "cpu"
+    name = torch.cuda.get_device_name(0)
+    for k in ("B200", "H100", "A100"):
+        if k in name:
+            return f"{k.lower()}_nvlink"
+    return "pcie"
+
+
+class GradientCompression(str, Enum):
+    NONE = "none"
+    FP16 = "fp16"
+    BF16 = "bf16"
+    POWERSGD = "powersgd"
+    TOPK = "topk"
+
+
+@dataclass
+class DDPConfig:
+    bucket_cap_mb: int | None = None
+    gradient_compression: GradientCompression = GradientCompression.NONE
+    gradient_as_bucket_view: bool = True
+    static_graph: bool = True
+    find_unused_parameters: bool = False
+    broadcast_buffers: bool = True
+    powersgd_rank: int = 4
+    powersgd_start_iter: int = 10
+    topk_ratio: float = 0.01
+    timeout_seconds: int = 1800
+    hierarchical: bool = False
+    use_triton_kernels: bool = False   # accepted for file compatibility; unused
+
+    def resolved_bucket_mb(self) -> int:
+        return self.bucket_cap_mb or BUCKET_MB[detect_gpu_topology()][0]
+
+
+# ------------------------------------------------------------------------------------------------ hooks: bucket -> averaged bucket
+def allreduce_hook(group, bucket: torch.Tensor) -> torch.Tensor:
+    dist.all_reduce(bucket, group=group)
+    return bucket.div_(dist.get_world_size(group))
+
+
+class CastCompressionHook:
+    """All-reduce in fp16 / bf16 (with a pre-scale by 1/world so the sum cannot overflow), then cast back."""
+
+    def __init__(self, dtype: torch.dtype):
+        self.dtype = dtype
+
+    def __call__(self, group, bucket: torch.Tensor) -> torch.Tensor:
+        w = dist.get_world_size(group)
+        low = (bucket / w).to(self.dtype)
+        dist.all_reduce(low, group=group)
+        bucket.copy_(low)
+        return bucket
+
+
+class PowerSGDHook:
+    """Rank-r PowerSGD with error feedback on 2-D views of each bucket; plain all-reduce for the first iterations."""
+
+    def __init__(self, rank: int = 4, start_iter: int = 10, seed: int = 0):
+        self.rank, self.start_iter, self.iter = rank, start_iter, 0
+        self.state: dict[int, dict] = {}
+        self.gen = torch.Generator().manual_seed(seed)
+
+    def reset(self):
+        self.state.clear()
+        self.iter = 0
+
+    def __call__(self, group, bucket: torch.Tensor, key: int = 0) -> torch.Tensor:
+        self.iter += 1
+        w = dist.get_world_size(group)
+        if self.iter <= self.start_iter or bucket.numel() < 4 * self.rank * self.rank:
+            dist.all_reduce(bucket, group=group)
+            return bucket.div_(w)
+        n = bucket.numel()
+        rows = int(n ** 0.5)
+        cols = (n + rows - 1) // rows
+        st = self.state.setdefault(key, {})
+        if "err" not in st or st["err"].numel() != rows * cols:
+            st["err"] = torch.zeros(rows * cols, dtype=torch.float32, device=bucket.device)
+            st["q"] = torch.randn(cols, self.rank, generator=self.gen).to(bucket.device)
+        m = torch.zeros(rows * cols, dtype=torch.float32, device=bucket.device)
+        m[:n] = bucket.float()
+        m = (m + st["err"]).view(rows, cols)
+        p = m @ st["q"]
+        dist.all_reduce(p, group=group)
+        p, _ = torch.linalg.qr(p / w)
+        q = m.t() @ p
+        dist.all_reduce(q, group=group)
+        q = q / w
+        approx = p @ q.t()
+        st["err"] = (m - approx).reshape(-1)
+        st["q"] = q
+        bucket.copy_(approx.reshape(-1)[:n])
+        return bucket
+
+
+class TopKSparsificationHook:
+    """Keep the largest-|g| fraction per rank (error feedback for the rest), exchange (index, value) pairs."""
+
+    def __init__(self, ratio: float = 0.01):
+        self.ratio = ratio
+        self.err: dict[int, torch.Tensor] = {}
+
+    def __call__(self, group, bucket: torch.Tensor, key: int = 0) -> torch.Tensor:
+        w = dist.get_world_size(group)
+        g = bucket.float() + self.err.get(key, 0)
+        k = max(1, int(g.numel() * self.ratio))
+        vals, idx = g.abs().topk(k)
+        sel = g[idx]
+        rest = g.clone()
+        rest[idx] = 0
+        self.err[key] = rest
+        all_idx = [torch.empty_like(idx) for _ in range(w)]
+        all_val = [torch.empty_like(sel) for _ in range(w)]
+        dist.all_gather(all_idx, idx, group=group)
+        dist.all_gather(all_val, sel, group=group)
+        out = torch.zeros_like(g)
+        for i, v in zip(all_idx, all_val):
+            out.index_add_(0, i, v)
+        bucket.copy_(out / w)
+        return bucket
+
+
+def make_hook(cfg: DDPConfig) -> Callable | None:
+    c = GradientCompression(cfg.gradient_compression)
+    if c == GradientCompression.FP16:
+        return CastCompressionHook(torch.float16)
+    if c == GradientCompression.BF16:
+        return CastCompressionHook(torch.bfloat16)
+    if c == GradientCompression.POWERSGD:
+        return PowerSGDHook(cfg.powersgd_rank, cfg.powersgd_start_iter)
+    if c == GradientCompression.TOPK:
+        return TopKSparsificationHook(cfg.topk_ratio)
+    return None
+
+
+class HierarchicalAllReduceManager:
+    """intra-node reduce -> inter-node all-reduce among node leaders -> intra-node broadcast."""
+
+    def __init__(self, local_world: int | None = None):
+        self.world, self.rank = dist.get_world_size(), dist.get_rank()
+        self.local_world = local_world or int(os.environ.get("LOCAL_WORLD_SIZE", self.world))
+        self.node = self.rank // self.local_world
+        n_nodes = self.world // self.local_world
+        self.intra = self.inter = None
+        for n in range(n_nodes):
+            g = dist.new_group(list(range(n * self.local_world, (n + 1) * self.local_world)))
+            if n == self.node:
+                self.intra = g
+        leaders = [n * self.local_world for n in range(n_nodes)]
+        g = dist.new_group(leaders)
+        self.inter = g if self.rank in leaders else None
+        self.is_leader = self.rank in leaders
+        self.leader = self.node * self.local_world
+
+    def all_reduce(self, t: torch.Tensor) -> torch.Tensor:
+        dist.reduce(t, self.leader, group=self.intra)
+        if self.is_leader and self.inter is not None:
+            dist.all_reduce(t, group=self.inter)
+        dist.broadcast(t, self.leader, group=self.intra)
+        return t.div_(self.world)
+
+
+class SOTADDPEngine:
+    def __init__(self, config: DDPConfig | None = None, **kw):
+        self.config = config or DDPConfig(**{k: v for k, v in kw.items() if k in DDPConfig.__dataclass_fields__})
+        self.hook = make_hook(self.config)
+        self.engine = None
+
+    def wrap_model(self, model: nn.Module, lr: float = 2e-5, **engine_kw):
+        """Builds the flat NO_SHARD engine around `model`; the compression hook (if any) replaces the bucket
+        all-reduce. Returns the model (parameters now alias the engine's buffers)."""
+        from .flat_engine import EngineConfig, FlatShardedEngine
+        ec = EngineConfig(sharding_strategy="NO_SHARD", lr=lr, **engine_kw)
+        self.engine = FlatShardedEngine(model, ec)
+        if self.hook is not None and self.engine.world > 1:
+            eng, hook = self.engine, self.hook
+
+            def reduce_with_hook(u, cur):
+                hook(eng.pg if eng.pg is not None else dist.group.WORLD, u.flat_grad)
+                u.reduce_event = True
+            eng._reduce_ddp = reduce_with_hook
+        return model
+
+    @contextlib.contextmanager
+    def no_sync(self):
+        with (self.engine.no_sync() if self.engine is not None else contextlib.nullcontext()):
+            yield
+
+    def check_health(self, timeout_s: float = 30.0) -> bool:
+        if not dist.is_initialized():
+            return True
+        t = torch.ones(1, device=self.engine.device if self.engine else "cpu")
+        try:
+            dist.all_reduce(t)
+            return bool(t.item() == dist.get_world_size())
+        except RuntimeError:
+            return False
+
+
+class DDPInitializer:
+    @staticmethod
+    def init_process_group(backend: str = "nccl", timeout_seconds: int = 1800) -> Result:
+        """env:// rendezvous from torchrun variables. NCCL debug output is enabled by DDP_DEBUG=1."""
+        if dist.is_initialized():
+            return Ok(dist.get_world_size())
+        try:
+            if backend == "nccl" and not torch.cuda.is_available():
+                backend = "gloo"
+            if os.environ.get("DDP_DEBUG"):
+                os.environ.setdefault("NCCL_DEBUG", "INFO")
+            os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+            os.environ.setdefault("MASTER_PORT", "29500")
+            kw = {}
+            if backend == "nccl":
+                lr = int(os.environ.get("LOCAL_RANK", "0"))
+                torch.cuda.set_device(lr)
+                kw["device_id"] = torch.device("cuda", lr)
+            dist.init_process_group(backend, timeout=datetime.timedelta(seconds=timeout_seconds), **kw)
+            return Ok(dist.get_world_size())
+        except Exception as e:   # noqa: BLE001
+            return Err(e)
+
+
+def create_ddp_engine(**kw) -> Result:
+    try:
+        return Ok(SOTADDPEngine(**kw))
+    except (TypeError, ValueError) as e:
+        return Err(e)

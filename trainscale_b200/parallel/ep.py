@@ -1,0 +1,343 @@
+"""Mixture-of-experts layers and expert parallelism.
+
+Feature set after data_pipeline/trainer/distributed/expert_parallel.py:83-1976 (TopK / ExpertChoice / SoftMoE
+routers, ExpertFFN, GroupedExperts, SharedExpert, MoELayer, all-to-all dispatcher, ExpertParallelMoE, HierarchicalMoE;
+capacity = max(min_cap, cf * T * k / E), aux losses E * sum f_i P_i, z-loss, importance CV^2) and the MoE kernels of
+data_pipeline/trainer/kernels/moe_kernels.py:219-785 (token permute / un-permute, grouped GEMM, router top-k softmax).
+The distributed combine here returns the expert outputs to their source ranks (the reference's returns zeros).
+
+Token movement: tokens are sorted by expert once (permute), each expert's contiguous slice runs the tcgen05 GEMMs
+(one launch per expert per projection), and the un-permute applies the routing weights.  Across ranks the sorted
+slices are exchanged with `all_to_all_single` using exact (not capacity-padded) split sizes.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+import torch.nn.functional as F
+
+from ..ops import activation, gemm
+
+
+@dataclass
+class ExpertParallelConfig:
+    num_experts: int = 8
+    top_k: int = 2
+    hidden_size: int = 256
+    intermediate_size: int = 512
+    capacity_factor: float = 1.25
+    min_capacity: int = 4
+    drop_tokens: bool = False
+    router: str = "top_k"              # top_k | expert_choice | soft
+    aux_loss_weight: float = 1e-2
+    z_loss_weight: float = 1e-3
+    num_shared_experts: int = 0
+    normalize_topk: bool = True
+    jitter: float = 0.0
+
+
+def moe_capacity(tokens: int, num_experts: int, top_k: int, capacity_factor: float, min_capacity: int = 4) -> int:
+    return max(min_capacity, int(math.ceil(capacity_factor * tokens * top_k / num_experts)))
+
+
+# ------------------------------------------------------------------------------------------------ routers
+class TopKRouter(nn.Module):
+    def __init__(self, cfg: ExpertParallelConfig, dtype=None, device=None):
+        super().__init__()
+        self.cfg = cfg
+        self.weight = nn.Parameter(torch.empty(cfg.num_experts, cfg.hidden_size, dtype=dtype, device=device))
+        nn.init.normal_(self.weight, std=0.02)
+
+    def forward(self, x: torch.Tensor):
+        """x [T, H] -> (weights [T, k], experts [T, k], aux dict)."""
+        cfg = self.cfg
+        logits = F.linear(x.float(), self.weight.float())
+        if self.training and cfg.jitter > 0:
+            logits = logits * torch.empty_like(logits).uniform_(1 - cfg.jitter, 1 + cfg.jitter)
+        probs = torch.softmax(logits, dim=-1)
+        w, idx = probs.topk(cfg.top_k, dim=-1)
+        if cfg.normalize_topk:
+            w = w / w.sum(-1, keepdim=True).clamp(min=1e-9)
+        f = F.one_hot(idx, cfg.num_experts).float().sum(1).mean(0) / cfg.top_k
+        P = probs.mean(0)
+        aux = {"load_balance": cfg.num_experts * (f * P).sum(), "z_loss": (torch.logsumexp(logits, -1) ** 2).mean(),
+               "importance_cv2": probs.sum(0).var() / probs.sum(0).mean().clamp(min=1e-9) ** 2,
+               "tokens_per_expert": F.one_hot(idx, cfg.num_experts).sum((0, 1))}
+        return w.to(x.dtype), idx, aux
+
+
+class ExpertChoiceRouter(nn.Module):
+    """Each expert picks its top-`capacity` tokens (perfect balance, tokens may get 0..E experts)."""
+
+    def __init__(self, cfg: ExpertParallelConfig, dtype=None, device=None):
+        super().__init__()
+        self.cfg = cfg
+        self.weight = nn.Parameter(torch.empty(cfg.num_experts, cfg.hidden_size, dtype=dtype, device=device))
+        nn.init.normal_(self.weight, std=0.02)
+
+    def forward(self, x):
+        cfg = self.cfg
+        T = x.shape[0]
+        probs = torch.softmax(F.linear(x.float(), self.weight.float()), dim=-1)     # [T, E]
+        cap = min(T, moe_capacity(T, cfg.num_experts, cfg.top_k, cfg.capacity_factor, cfg.min_capacity))
+        w, tok = probs.t().topk(cap, dim=-1)                                          # [E, cap]
+        return w.to(x.dtype), tok, {"capacity": cap}
+
+
+class SoftMoERouter(nn.Module):
+    """Soft MoE: every slot is a convex combination of all tokens (fully differentiable, no dropping)."""
+
+    def __init__(self, cfg: ExpertParallelConfig, slots_per_expert: int = 1, dtype=None, device=None):
+        super().__init__()
+        self.cfg, self.slots = cfg, slots_per_expert
+        self.phi = nn.Parameter(torch.empty(cfg.hidden_size, cfg.num_experts * slots_per_expert, dtype=dtype, device=device))
+        nn.init.normal_(self.phi, std=0.02)
+
+    def forward(self, x):
+        logits = x.float() @ self.phi.float()                  # [T, E*slots]
+        dispatch = torch.softmax(logits, dim=0)                # over tokens
+        combine = torch.softmax(logits, dim=1)                 # over slots
+        return dispatch.to(x.dtype), combine.to(x.dtype), {}
+
+
+# ------------------------------------------------------------------------------------------------ experts
+class ExpertFFN(nn.Module):
+    def __init__(self, hidden: int, inter: int, dtype=None, device=None):
+        super().__init__()
+        self.w_gate_up = nn.Parameter(torch.empty(2 * inter, hidden, dtype=dtype, device=device))
+        self.w_down = nn.Parameter(torch.empty(hidden, inter, dtype=dtype, device=device))
+        nn.init.normal_(self.w_gate_up, std=0.02)
+        nn.init.normal_(self.w_down, std=0.02)
+
+    def forward(self, x):
+        return gemm.linear(activation.glu(gemm.linear(x, self.w_gate_up)), self.w_down)
+
+
+class GroupedExperts(nn.Module):
+    """E experts stored as stacked weights; `forward(x_sorted, counts)` runs each expert on its contiguous slice."""
+
+    def __init__(self, num_experts: int, hidden: int, inter: int, dtype=None, device=None):
+        super().__init__()
+        self.num_experts = num_experts
+        self.w_gate_up = nn.Parameter(torch.empty(num_experts, 2 * inter, hidden, dtype=dtype, device=device))
+        self.w_down = nn.Parameter(torch.empty(num_experts, hidden, inter, dtype=dtype, device=device))
+        nn.init.normal_(self.w_gate_up, std=0.02)
+        nn.init.normal_(self.w_down, std=0.02)
+
+    def forward(self, x_sorted: torch.Tensor, counts: list[int]) -> torch.Tensor:
+        outs, off = [], 0
+        for e, n in enumerate(counts):
+            if n == 0:
+                continue
+            xe = x_sorted[off:off + n]
+            outs.append(gemm.linear(activation.glu(gemm.linear(xe, self.w_gate_up[e])), self.w_down[e]))
+            off += n
+        if not outs:
+            return x_sorted.new_zeros(0, x_sorted.shape[-1])
+        return torch.cat(outs)
+
+
+class SharedExpert(ExpertFFN):
+    pass
+
+
+def permute_tokens(x: torch.Tensor, experts: torch.Tensor, num_experts: int):
+    """x [T, H], experts [T, k] -> (x_sorted [T*k, H], order [T*k], counts [E]); row i of x_sorted is token order[i] // k."""
+    flat = experts.reshape(-1)
+    order = torch.argsort(flat, stable=True)
+    counts = torch.bincount(flat, minlength=num_experts)
+    return x[order // experts.shape[1]], order, counts
+
+
+def unpermute_tokens(y_sorted: torch.Tensor, order: torch.Tensor, weights: torch.Tensor, T: int) -> torch.Tensor:
+    """Weighted scatter-add of expert outputs back to token order."""
+    k = weights.shape[1]
+    w = weights.reshape(-1)[order].unsqueeze(-1)
+    out = y_sorted.new_zeros(T, y_sorted.shape[-1], dtype=torch.float32)
+    out.index_add_(0, order // k, (y_sorted * w).float())
+    return out.to(y_sorted.dtype)
+
+
+class MoELayer(nn.Module):
+    """Single-process MoE block (all experts local)."""
+
+    def __init__(self, cfg: ExpertParallelConfig, dtype=None, device=None):
+        super().__init__()
+        self.cfg = cfg
+        self.router = {"top_k": TopKRouter, "expert_choice": ExpertChoiceRouter}.get(cfg.router, TopKRouter)(cfg, dtype, device) \
+            if cfg.router != "soft" else SoftMoERouter(cfg, 1, dtype, device)
+        self.experts = GroupedExperts(cfg.num_experts, cfg.hidden_size, cfg.intermediate_size, dtype, device)
+        self.shared = nn.ModuleList(SharedExpert(cfg.hidden_size, cfg.intermediate_size, dtype, device)
+                                    for _ in range(cfg.num_shared_experts))
+        self.aux_loss = torch.zeros(())
+
+    def _aux(self, aux: dict) -> torch.Tensor:
+        cfg = self.cfg
+        loss = 0.0
+        if "load_balance" in aux:
+            loss = loss + cfg.aux_loss_weight * aux["load_balance"]
+        if "z_loss" in aux:
+            loss = loss + cfg.z_loss_weight * aux["z_loss"]
+        return loss
+
+    def route_and_run(self, x2: torch.Tensor, run_experts) -> torch.Tensor:
+        cfg = self.cfg
+        T = x2.shape[0]
+        if cfg.router == "soft":
+            dispatch, combine, aux = self.router(x2)
+            slots = dispatch.t() @ x2                                        # [E, H] (one slot per expert)
+            y = run_experts(slots, torch.arange(cfg.num_experts, device=x2.device).unsqueeze(1),
+                            torch.ones(cfg.num_experts, 1, device=x2.device, dtype=x2.dtype))
+            self.aux_loss = x2.new_zeros(())
+            return combine @ y
+        if cfg.router == "expert_choice":
+            w, tok, aux = self.router(x2)                                    # [E, cap]
+            E, cap = tok.shape
+            xs = x2[tok.reshape(-1)]
+            ys = self.experts(xs, [cap] * E)
+            out = x2.new_zeros(T, x2.shape[-1], dtype=torch.float32)
+            out.index_add_(0, tok.reshape(-1), (ys * w.reshape(-1, 1)).float())
+            self.aux_loss = x2.new_zeros(())
+            return out.to(x2.dtype)
+        w, idx, aux = self.router(x2)
+        if cfg.drop_tokens:
+            cap = moe_capacity(T, cfg.num_experts, cfg.top_k, cfg.capacity_factor, cfg.min_capacity)
+            pos = torch.zeros_like(idx)
+            flat = idx.reshape(-1)
+            onehot = F.one_hot(flat, cfg.num_experts)
+            rank_in_expert = (onehot.cumsum(0) - 1).gather(1, flat.unsqueeze(1)).squeeze(1)
+            keep = (rank_in_expert < cap).view_as(idx)
+            w = w * keep
+        self.aux_loss = self._aux(aux)
+        return run_experts(x2, idx, w)
+
+    def _local(self, x2, idx, w):
+        xs, order, counts = permute_tokens(x2, idx, self.cfg.num_experts)
+        ys = self.experts(xs, counts.tolist())
+        return unpermute_tokens(ys, order, w, x2.shape[0])
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        shp = x.shape
+        x2 = x.reshape(-1, shp[-1])
+        y = self.route_and_run(x2, self._local)
+        for s in self.shared:
+            y = y + s(x2)
+        return y.view(shp)
+
+
+# ------------------------------------------------------------------------------------------------ expert parallelism
+class _AllToAll(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, in_splits, out_splits, group):
+        ctx.in_splits, ctx.out_splits, ctx.group = in_splits, out_splits, group
+        out = x.new_empty(sum(out_splits), *x.shape[1:])
+        dist.all_to_all_single(out, x.contiguous(), out_splits, in_splits, group=group)
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        out = g.new_empty(sum(ctx.in_splits), *g.shape[1:])
+        dist.all_to_all_single(out, g.contiguous(), ctx.in_splits, ctx.out_splits, group=ctx.group)
+        return out, None, None, None
+
+
+class AllToAllDispatcher:
+    """Moves expert-sorted token rows to the ranks that own the experts, and back."""
+
+    def __init__(self, group, num_experts: int):
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        assert num_experts % self.world == 0, "num_experts must divide by the expert-parallel size"
+        self.num_experts, self.local_experts = num_experts, num_experts // self.world
+
+    def dispatch(self, x_sorted: torch.Tensor, counts: torch.Tensor):
+        """counts [E] (tokens this rank routes to each global expert). Returns (rows for my experts ordered by
+        (source rank, local expert), recv_counts [W, E_local], bookkeeping)."""
+        W, El = self.world, self.local_experts
+        send_counts = counts.view(W, El)
+        recv_counts = torch.empty_like(send_counts)
+        dist.all_to_all_single(recv_counts, send_counts.contiguous(), group=self.group)
+        in_splits = send_counts.sum(1).tolist()
+        out_splits = recv_counts.sum(1).tolist()
+        recv = _AllToAll.apply(x_sorted, in_splits, out_splits, self.group)
+        return recv, recv_counts, (in_splits, out_splits)
+
+    def combine(self, y: torch.Tensor, book) -> torch.Tensor:
+        in_splits, out_splits = book
+        return _AllToAll.apply(y, out_splits, in_splits, self.group)
+
+
+class ExpertParallelMoE(MoELayer):
+    """MoE block whose experts are sharded over an expert-parallel group (E / W local experts per rank)."""
+
+    def __init__(self, cfg: ExpertParallelConfig, group, dtype=None, device=None):
+        nn.Module.__init__(self)
+        self.cfg = cfg
+        self.router = TopKRouter(cfg, dtype, device)
+        self.dispatcher = AllToAllDispatcher(group, cfg.num_experts)
+        self.experts = GroupedExperts(self.dispatcher.local_experts, cfg.hidden_size, cfg.intermediate_size, dtype, device)
+        self.shared = nn.ModuleList(SharedExpert(cfg.hidden_size, cfg.intermediate_size, dtype, device)
+                                    for _ in range(cfg.num_shared_experts))
+        self.aux_loss = torch.zeros(())
+
+    def _distributed(self, x2, idx, w):
+        d = self.dispatcher
+        xs, order, counts = permute_tokens(x2, idx, self.cfg.num_experts)
+        recv, recv_counts, book = d.dispatch(xs, counts)
+        # received rows are ordered (source rank, local expert): regroup them by local expert
+        W, El = d.world, d.local_experts
+        rc = recv_counts.tolist()
+        offs, o = [[0] * El for _ in range(W)], 0
+        for r in range(W):
+            for e in range(El):
+                offs[r][e] = o
+                o += rc[r][e]
+        gather_idx = torch.cat([torch.arange(offs[r][e], offs[r][e] + rc[r][e], device=x2.device)
+                                for e in range(El) for r in range(W)]) if o > 0 else torch.zeros(0, dtype=torch.long, device=x2.device)
+        per_expert = [sum(rc[r][e] for r in range(W)) for e in range(El)]
+        ye = self.experts(recv[gather_idx], per_expert)
+        back = torch.empty_like(ye)
+        back[gather_idx] = ye
+        ys = d.combine(back, book)
+        return unpermute_tokens(ys, order, w, x2.shape[0])
+
+    def forward(self, x):
+        shp = x.shape
+        x2 = x.reshape(-1, shp[-1])
+        y = self.route_and_run(x2, self._distributed)
+        for s in self.shared:
+            y = y + s(x2)
+        return y.view(shp)
+
+
+class HierarchicalMoE(nn.Module):
+    """Two-level routing: a coarse router picks a group, the group's MoE picks experts."""
+
+    def __init__(self, cfg: ExpertParallelConfig, num_groups: int = 2, dtype=None, device=None):
+        super().__init__()
+        assert cfg.num_experts % num_groups == 0
+        import dataclasses
+        sub = dataclasses.replace(cfg, num_experts=cfg.num_experts // num_groups)
+        self.groups = nn.ModuleList(MoELayer(sub, dtype, device) for _ in range(num_groups))
+        self.coarse = nn.Linear(cfg.hidden_size, num_groups, bias=False, dtype=dtype, device=device)
+
+    def forward(self, x):
+        shp = x.shape
+        x2 = x.reshape(-1, shp[-1])
+        g = torch.softmax(self.coarse(x2).float(), -1)
+        top = g.argmax(-1)
+        out = torch.zeros_like(x2)
+        for gi, layer in enumerate(self.groups):
+            m = top == gi
+            if m.any():
+                out[m] = layer(x2[m]) * g[m, gi].unsqueeze(-1).to(x2.dtype)
+        return out.view(shp)
+
+    @property
+    def aux_loss(self):
+        return sum(l.aux_loss for l in self.groups)
