@@ -1,0 +1,358 @@
+"""Evaluation metrics, training trackers and their distributed reduction.
+
+After data_pipeline/trainer/metrics/*.py: `Metric` ABC with Accuracy / Precision / Recall / F1 / AUROC / Perplexity /
+BLEU / ROUGE / MSE / MAE / R2 (`__init__.py:16-433`), `sync_metric(s)` and `DistributedMetricBuffer`
+(`distributed.py:53-173`), `GradientTracker` (`gradient.py:30`), `LossTracker` / `AccuracyTracker` (`loss.py:32,309`),
+`ThroughputTracker` (`throughput.py:96`), `TrainingMetrics` (`training.py:35`).
+"""
+from __future__ import annotations
+
+import math
+from collections import Counter, deque
+from typing import Sequence
+
+import torch
+import torch.distributed as dist
+
+from .throughput import PEAK_TFLOPS, ThroughputTracker, device_peak_tflops  # noqa: F401
+
+
+def sync_metric(value: float | torch.Tensor, op: str = "mean", group=None) -> float:
+    if not (dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1):
+        return float(value)
+    t = torch.as_tensor(float(value), dtype=torch.float64)
+    if dist.get_backend(group) == "nccl":
+        t = t.float().cuda()
+    dist.all_reduce(t, op=dist.ReduceOp.MAX if op == "max" else dist.ReduceOp.SUM, group=group)
+    return float(t / dist.get_world_size(group)) if op == "mean" else float(t)
+
+
+def sync_metrics(values: dict[str, float], op: str = "mean", group=None) -> dict[str, float]:
+    if not (dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1):
+        return dict(values)
+    keys = sorted(values)
+    t = torch.tensor([float(values[k]) for k in keys], dtype=torch.float32)
+    if dist.get_backend(group) == "nccl":
+        t = t.cuda()
+    dist.all_reduce(t, group=group)
+    if op == "mean":
+        t /= dist.get_world_size(group)
+    return dict(zip(keys, t.tolist()))
+
+
+class DistributedMetricBuffer:
+    """Accumulate named sums locally; one all-reduce when read."""
+
+    def __init__(self):
+        self.sums: dict[str, float] = {}
+
+    def add(self, name: str, value: float, weight: float = 1.0):
+        self.sums[name] = self.sums.get(name, 0.0) + float(value) * weight
+        self.sums[name + "/weight"] = self.sums.get(name + "/weight", 0.0) + weight
+
+    def compute(self, group=None) -> dict[str, float]:
+        tot = sync_metrics(self.sums, "sum", group)
+        return {k: v / max(tot.get(k + "/weight", 1.0), 1e-12) for k, v in tot.items() if not k.endswith("/weight")}
+
+    def reset(self):
+        self.sums.clear()
+
+
+class Metric:
+    def update(self, preds, targets): raise NotImplementedError
+    def compute(self) -> float: raise NotImplementedError
+    def reset(self): raise NotImplementedError
+
+
+class _Counts(Metric):
+    def __init__(self, num_classes: int | None = None, average: str = "macro", ignore_index: int = -100):
+        self.num_classes, self.average, self.ignore_index = num_classes, average, ignore_index
+        self.reset()
+
+    def reset(self):
+        self.tp, self.fp, self.fn, self.correct, self.total = Counter(), Counter(), Counter(), 0, 0
+
+    def update(self, preds, targets):
+        p = torch.as_tensor(preds)
+        t = torch.as_tensor(targets)
+        if p.dim() > t.dim():
+            p = p.argmax(-1)
+        p, t = p.reshape(-1), t.reshape(-1)
+        keep = t != self.ignore_index
+        p, t = p[keep], t[keep]
+        self.correct += int((p == t).sum())
+        self.total += int(t.numel())
+        for c in torch.unique(torch.cat((p, t))).tolist():
+            self.tp[c] += int(((p == c) & (t == c)).sum())
+            self.fp[c] += int(((p == c) & (t != c)).sum())
+            self.fn[c] += int(((p != c) & (t == c)).sum())
+
+    def _prf(self):
+        classes = sorted(set(self.tp) | set(self.fp) | set(self.fn))
+        if self.average == "micro":
+            tp, fp, fn = sum(self.tp.values()), sum(self.fp.values()), sum(self.fn.values())
+            p = tp / max(tp + fp, 1)
+            r = tp / max(tp + fn, 1)
+            return p, r, 2 * p * r / max(p + r, 1e-12)
+        ps, rs, fs = [], [], []
+        for c in classes:
+            p = self.tp[c] / max(self.tp[c] + self.fp[c], 1)
+            r = self.tp[c] / max(self.tp[c] + self.fn[c], 1)
+            ps.append(p)
+            rs.append(r)
+            fs.append(2 * p * r / max(p + r, 1e-12))
+        n = max(len(classes), 1)
+        return sum(ps) / n, sum(rs) / n, sum(fs) / n
+
+
+class Accuracy(_Counts):
+    def compute(self): return self.correct / max(self.total, 1)
+
+
+class Precision(_Counts):
+    def compute(self): return self._prf()[0]
+
+
+class Recall(_Counts):
+    def compute(self): return self._prf()[1]
+
+
+class F1Score(_Counts):
+    def compute(self): return self._prf()[2]
+
+
+class AUROC(Metric):
+    def __init__(self): self.reset()
+    def reset(self): self.scores, self.labels = [], []
+
+    def update(self, preds, targets):
+        self.scores += torch.as_tensor(preds).reshape(-1).tolist()
+        self.labels += torch.as_tensor(targets).reshape(-1).tolist()
+
+    def compute(self):
+        pairs = sorted(zip(self.scores, self.labels))
+        pos = sum(1 for _, l in pairs if l == 1)
+        neg = len(pairs) - pos
+        if pos == 0 or neg == 0:
+            return float("nan")
+        rank_sum, i = 0.0, 0
+        while i < len(pairs):
+            j = i
+            while j < len(pairs) and pairs[j][0] == pairs[i][0]:
+                j += 1
+            avg_rank = (i + j + 1) / 2
+            rank_sum += avg_rank * sum(1 for k in range(i, j) if pairs[k][1] == 1)
+            i = j
+        return (rank_sum - pos * (pos + 1) / 2) / (pos * neg)
+
+
+class Perplexity(Metric):
+    def __init__(self, ignore_index: int = -100):
+        self.ignore_index = ignore_index
+        self.reset()
+
+    def reset(self): self.nll, self.n = 0.0, 0
+
+    def update(self, logits, targets):
+        lp = torch.log_softmax(torch.as_tensor(logits).float(), -1)
+        t = torch.as_tensor(targets)
+        m = t != self.ignore_index
+        self.nll += float(-(lp.gather(-1, t.clamp(min=0).unsqueeze(-1)).squeeze(-1) * m).sum())
+        self.n += int(m.sum())
+
+    def update_from_loss(self, mean_loss: float, num_tokens: int):
+        self.nll += mean_loss * num_tokens
+        self.n += num_tokens
+
+    def compute(self): return math.exp(min(self.nll / max(self.n, 1), 50.0))
+
+
+def _ngrams(tokens: Sequence, n: int) -> Counter:
+    return Counter(tuple(tokens[i:i + n]) for i in range(len(tokens) - n + 1))
+
+
+class BLEU(Metric):
+    def __init__(self, max_n: int = 4, smooth: bool = True):
+        self.max_n, self.smooth = max_n, smooth
+        self.reset()
+
+    def reset(self):
+        self.match, self.total = [0] * self.max_n, [0] * self.max_n
+        self.hyp_len = self.ref_len = 0
+
+    def update(self, hypotheses: Sequence[str | Sequence], references: Sequence[str | Sequence]):
+        for h, r in zip(hypotheses, references):
+            h = h.split() if isinstance(h, str) else list(h)
+            r = r.split() if isinstance(r, str) else list(r)
+            self.hyp_len += len(h)
+            self.ref_len += len(r)
+            for n in range(1, self.max_n + 1):
+                hn, rn = _ngrams(h, n), _ngrams(r, n)
+                self.match[n - 1] += sum(min(c, rn[g]) for g, c in hn.items())
+                self.total[n - 1] += max(len(h) - n + 1, 0)
+
+    def compute(self):
+        if self.hyp_len == 0:
+            return 0.0
+        logs = []
+        for m, t in zip(self.match, self.total):
+            if self.smooth:
+                m, t = m + 1, t + 1
+            if m == 0 or t == 0:
+                return 0.0
+            logs.append(math.log(m / t))
+        bp = 1.0 if self.hyp_len > self.ref_len else math.exp(1 - self.ref_len / max(self.hyp_len, 1))
+        return bp * math.exp(sum(logs) / self.max_n)
+
+
+class ROUGE(Metric):
+    """ROUGE-1 / ROUGE-2 / ROUGE-L F-measures."""
+
+    def __init__(self): self.reset()
+    def reset(self): self.scores = {"rouge1": [], "rouge2": [], "rougeL": []}
+
+    @staticmethod
+    def _lcs(a, b):
+        dp = [0] * (len(b) + 1)
+        for x in a:
+            prev = 0
+            for j, y in enumerate(b, 1):
+                cur = dp[j]
+                dp[j] = prev + 1 if x == y else max(dp[j], dp[j - 1])
+                prev = cur
+        return dp[-1]
+
+    @staticmethod
+    def _f(m, h, r):
+        if m == 0:
+            return 0.0
+        p, rc = m / max(h, 1), m / max(r, 1)
+        return 2 * p * rc / (p + rc)
+
+    def update(self, hypotheses, references):
+        for h, r in zip(hypotheses, references):
+            h = h.split() if isinstance(h, str) else list(h)
+            r = r.split() if isinstance(r, str) else list(r)
+            for n, key in ((1, "rouge1"), (2, "rouge2")):
+                hn, rn = _ngrams(h, n), _ngrams(r, n)
+                self.scores[key].append(self._f(sum(min(c, rn[g]) for g, c in hn.items()), sum(hn.values()), sum(rn.values())))
+            self.scores["rougeL"].append(self._f(self._lcs(h, r), len(h), len(r)))
+
+    def compute(self):
+        return {k: sum(v) / max(len(v), 1) for k, v in self.scores.items()}
+
+
+class _Regression(Metric):
+    def __init__(self): self.reset()
+    def reset(self): self.p, self.t = [], []
+
+    def update(self, preds, targets):
+        self.p.append(torch.as_tensor(preds).float().reshape(-1))
+        self.t.append(torch.as_tensor(targets).float().reshape(-1))
+
+    def _cat(self): return torch.cat(self.p), torch.cat(self.t)
+
+
+class MSE(_Regression):
+    def compute(self):
+        p, t = self._cat()
+        return float(((p - t) ** 2).mean())
+
+
+class MAE(_Regression):
+    def compute(self):
+        p, t = self._cat()
+        return float((p - t).abs().mean())
+
+
+class R2Score(_Regression):
+    def compute(self):
+        p, t = self._cat()
+        return float(1 - ((p - t) ** 2).sum() / ((t - t.mean()) ** 2).sum().clamp(min=1e-12))
+
+
+class LossTracker:
+    """EMA loss (decay 0.99), token-weighted mean, perplexity; `sync()` reduces over ranks."""
+
+    def __init__(self, ema_decay: float = 0.99, window: int = 100):
+        self.decay, self.ema = ema_decay, None
+        self.sum, self.tokens = 0.0, 0
+        self.window = deque(maxlen=window)
+
+    def update(self, loss, num_tokens: int = 1):
+        l = float(loss)
+        if not math.isfinite(l):
+            return
+        self.ema = l if self.ema is None else self.decay * self.ema + (1 - self.decay) * l
+        self.sum += l * num_tokens
+        self.tokens += num_tokens
+        self.window.append(l)
+
+    @property
+    def mean(self): return self.sum / max(self.tokens, 1)
+    @property
+    def perplexity(self): return math.exp(min(self.mean, 50.0))
+    @property
+    def windowed(self): return sum(self.window) / max(len(self.window), 1)
+
+    def sync(self, group=None):
+        tot = sync_metrics({"sum": self.sum, "tokens": float(self.tokens)}, "sum", group)
+        return tot["sum"] / max(tot["tokens"], 1.0)
+
+    def state_dict(self): return {"ema": self.ema, "sum": self.sum, "tokens": self.tokens}
+
+    def load_state_dict(self, sd):
+        self.ema, self.sum, self.tokens = sd["ema"], sd["sum"], sd["tokens"]
+
+
+class AccuracyTracker:
+    """Next-token accuracy with the causal shift (logits[..., :-1] vs labels[..., 1:])."""
+
+    def __init__(self, ignore_index: int = -100):
+        self.ignore_index, self.correct, self.total = ignore_index, 0, 0
+
+    def update_from_logits(self, logits, labels):
+        p = logits[..., :-1, :].argmax(-1)
+        t = labels[..., 1:]
+        m = t != self.ignore_index
+        self.correct += int(((p == t) & m).sum())
+        self.total += int(m.sum())
+
+    @property
+    def accuracy(self): return self.correct / max(self.total, 1)
+
+
+class GradientTracker:
+    def __init__(self, window: int = 100, explode_threshold: float = 1e6):
+        self.norms = deque(maxlen=window)
+        self.nan_count, self.threshold, self.clipped = 0, explode_threshold, 0
+
+    def update(self, grad_norm, max_norm: float | None = None):
+        g = float(grad_norm)
+        if not math.isfinite(g):
+            self.nan_count += 1
+            return
+        self.norms.append(g)
+        if max_norm and g > max_norm:
+            self.clipped += 1
+
+    @property
+    def mean(self): return sum(self.norms) / max(len(self.norms), 1)
+    def exploding(self) -> bool: return bool(self.norms) and self.norms[-1] > self.threshold
+    def state_dict(self): return {"norms": list(self.norms), "nan_count": self.nan_count, "clipped": self.clipped}
+
+
+class TrainingMetrics:
+    """Bundle of the trackers a training loop updates."""
+
+    def __init__(self, flops_per_token: float = 0.0, world_size: int = 1):
+        self.loss, self.acc, self.grad = LossTracker(), AccuracyTracker(), GradientTracker()
+        self.throughput = ThroughputTracker(flops_per_token, world_size=world_size)
+
+    def summary(self) -> dict:
+        return {"loss": self.loss.mean, "loss_ema": self.loss.ema, "ppl": self.loss.perplexity, "acc": self.acc.accuracy,
+                "grad_norm": self.grad.mean, "tokens_per_second": self.throughput.tokens_per_second(),
+                "mfu": self.throughput.compute_mfu()}
+
+    def state_dict(self):
+        return {"loss": self.loss.state_dict(), "grad": self.grad.state_dict(), "throughput": self.throughput.state_dict()}

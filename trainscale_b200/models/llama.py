@@ -222,7 +222,9 @@ class LlamaModel(nn.Module):
         residual = None
         for i, layer in enumerate(self.layers):
             cache = None if kv_caches is None else kv_caches[i]
-            if self.gradient_checkpointing and self.training and (i % self.checkpoint_every == 0):
+            ck = getattr(self, "checkpoint_layers", None)
+            recompute = (i in ck) if ck is not None else (i % self.checkpoint_every == 0)
+            if self.gradient_checkpointing and self.training and recompute:
                 x, residual = checkpoint(layer, x, residual, cos, sin, position_ids, cu_seqlens, doc_ids, None,
                                          use_reentrant=False)
             else:

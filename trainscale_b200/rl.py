@@ -1,0 +1,190 @@
+"""RL / preference-training utilities and the preference trainer (DPO / SimPO / ORPO / KTO / CPO).
+
+Utilities after data_pipeline/trainer/rl_training.py:95-671 (`selective_log_softmax`, `chunked_log_softmax`,
+`compute_advantages` (group-normalised), `grpo_loss`, `drgrpo_loss`, `dapo_loss`, `left_pack_padding`, `GRPOCompute`,
+`RewardModel`).  The reference ships the data stage and the losses but no preference training loop
+(data_pipeline/trainer/loss/sota_losses.py:1151, preprocessing/prompt_engine.py:1929); `PreferenceTrainer` is that
+loop: policy (and a frozen reference copy) under the flat engine, chosen and rejected sequences concatenated into
+one forward, per-token log-probs from the fused lm_head + log-prob kernel (logits never materialised).
+"""
+from __future__ import annotations
+
+import copy
+from typing import Any, Dict
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from .losses import CPOLoss, DPOLoss, KTOLoss, ORPOLoss, SimPOLoss
+from .ops import cross_entropy as ce_ops
+
+
+def selective_log_softmax(logits: torch.Tensor, index: torch.Tensor) -> torch.Tensor:
+    """log_softmax(logits)[..., index] without keeping the full log-softmax."""
+    sel = logits.gather(-1, index.unsqueeze(-1)).squeeze(-1).float()
+    return sel - torch.logsumexp(logits.float(), dim=-1)
+
+
+def chunked_log_softmax(hidden: torch.Tensor, lm_head: torch.Tensor, labels: torch.Tensor, chunk_tokens: int = 4096,
+                        ignore_index: int = -100) -> torch.Tensor:
+    """Per-token log p(label) from hidden states, chunked over tokens: only [B, L] values are kept."""
+    return ce_ops.fused_linear_token_logprobs(hidden, lm_head, labels, ignore_index, chunk_tokens)
+
+
+def compute_advantages(rewards: torch.Tensor, group_size: int, eps: float = 1e-4, scale: bool = True) -> torch.Tensor:
+    """Group-normalised advantages: rewards [N] with consecutive groups of `group_size` samples per prompt."""
+    r = rewards.float().view(-1, group_size)
+    a = r - r.mean(1, keepdim=True)
+    if scale:
+        a = a / (r.std(1, keepdim=True) + eps)
+    return a.reshape(-1)
+
+
+def _masked_mean(x, mask, dim=None):
+    return (x * mask).sum(dim) / mask.sum(dim).clamp(min=1)
+
+
+def grpo_loss(logp: torch.Tensor, old_logp: torch.Tensor, ref_logp: torch.Tensor | None, advantages: torch.Tensor,
+              mask: torch.Tensor, clip: float = 0.2, beta: float = 0.01) -> torch.Tensor:
+    """Clipped surrogate per token, averaged per sequence then over the batch, plus the k3 KL estimator."""
+    ratio = torch.exp(logp - old_logp)
+    a = advantages.unsqueeze(-1)
+    obj = torch.minimum(ratio * a, ratio.clamp(1 - clip, 1 + clip) * a)
+    per_tok = -obj
+    if ref_logp is not None and beta > 0:
+        d = ref_logp - logp
+        per_tok = per_tok + beta * (torch.exp(d) - d - 1)
+    return _masked_mean(per_tok, mask, dim=-1).mean()
+
+
+def drgrpo_loss(logp, old_logp, advantages, mask, clip: float = 0.2, max_len: int | None = None) -> torch.Tensor:
+    """Dr. GRPO: no std scaling in the advantage and a constant length normaliser (removes the length bias)."""
+    ratio = torch.exp(logp - old_logp)
+    a = advantages.unsqueeze(-1)
+    obj = torch.minimum(ratio * a, ratio.clamp(1 - clip, 1 + clip) * a)
+    L = max_len or mask.shape[-1]
+    return -((obj * mask).sum(-1) / L).mean()
+
+
+def dapo_loss(logp, old_logp, advantages, mask, clip_low: float = 0.2, clip_high: float = 0.28) -> torch.Tensor:
+    """DAPO: decoupled clip range and token-level normalisation over the whole batch."""
+    ratio = torch.exp(logp - old_logp)
+    a = advantages.unsqueeze(-1)
+    obj = torch.minimum(ratio * a, ratio.clamp(1 - clip_low, 1 + clip_high) * a)
+    return -(obj * mask).sum() / mask.sum().clamp(min=1)
+
+
+def left_pack_padding(ids: torch.Tensor, mask: torch.Tensor, pad_id: int = 0):
+    """Move real tokens to the left of every row (stable), padding to the right."""
+    order = torch.argsort((mask == 0).int(), dim=1, stable=True)
+    return ids.gather(1, order).masked_fill(mask.gather(1, order) == 0, pad_id), mask.gather(1, order)
+
+
+class GRPOCompute:
+    def __init__(self, group_size: int = 8, clip: float = 0.2, beta: float = 0.01, variant: str = "grpo"):
+        self.group_size, self.clip, self.beta, self.variant = group_size, clip, beta, variant
+
+    def __call__(self, logp, old_logp, ref_logp, rewards, mask):
+        adv = compute_advantages(rewards, self.group_size, scale=self.variant != "drgrpo")
+        if self.variant == "drgrpo":
+            return drgrpo_loss(logp, old_logp, adv, mask, self.clip)
+        if self.variant == "dapo":
+            return dapo_loss(logp, old_logp, adv, mask, self.clip)
+        return grpo_loss(logp, old_logp, ref_logp, adv, mask, self.clip, self.beta)
+
+
+class RewardModel(nn.Module):
+    """Decoder backbone + scalar head read at the last real token."""
+
+    def __init__(self, backbone):
+        super().__init__()
+        self.backbone = backbone
+        h = backbone.config.hidden_size
+        p = next(backbone.parameters())
+        self.value_head = nn.Linear(h, 1, bias=False, dtype=p.dtype, device=p.device)
+
+    def forward(self, input_ids, attention_mask=None):
+        h = self.backbone.model(input_ids)
+        if attention_mask is None:
+            last = torch.full((h.shape[0],), h.shape[1] - 1, device=h.device)
+        else:
+            last = attention_mask.long().sum(1).clamp(min=1) - 1
+        return self.value_head(h[torch.arange(h.shape[0], device=h.device), last]).squeeze(-1).float()
+
+
+class PreferenceTrainer:
+    """Preference optimisation on batches with chosen_/rejected_ input_ids, attention_mask and labels."""
+
+    def __init__(self, policy, engine=None, ref_model=None, loss: str = "dpo", beta: float = 0.1, **loss_kw):
+        self.policy, self.engine, self.kind = policy, engine, loss
+        self.ref = ref_model
+        if self.ref is not None:
+            self.ref.eval()
+            for p in self.ref.parameters():
+                p.requires_grad_(False)
+        self.loss_fn = {"dpo": lambda: DPOLoss(beta, **loss_kw), "simpo": lambda: SimPOLoss(beta, **loss_kw),
+                        "orpo": lambda: ORPOLoss(**loss_kw), "kto": lambda: KTOLoss(beta, **loss_kw),
+                        "cpo": lambda: CPOLoss(beta, **loss_kw)}[loss]()
+
+    @staticmethod
+    def make_reference(policy):
+        """Frozen copy of the policy taken before the engine re-points its parameters at flat buffers."""
+        ref = copy.deepcopy(policy)
+        for p in ref.parameters():
+            p.requires_grad_(False)
+        return ref.eval()
+
+    def _seq_logps(self, model, ids, mask, labels, grad: bool):
+        ctx = torch.enable_grad() if grad else torch.no_grad()
+        with ctx:
+            h = model.model(ids)
+            w = model.head_weight
+            lab = labels.masked_fill(mask == 0, -100)
+            tgt = torch.full_like(lab, -100)
+            tgt[:, :-1] = lab[:, 1:]
+            lp = ce_ops.fused_linear_token_logprobs(h, w if grad else w.detach(), tgt)
+            return lp.sum(-1), (tgt != -100).sum(-1)
+
+    def compute_loss(self, batch: Dict[str, torch.Tensor]):
+        B = batch["chosen_input_ids"].shape[0]
+        ids = torch.cat((batch["chosen_input_ids"], batch["rejected_input_ids"]))
+        mask = torch.cat((batch["chosen_attention_mask"], batch["rejected_attention_mask"]))
+        labels = torch.cat((batch["chosen_labels"], batch["rejected_labels"]))
+        lp, n = self._seq_logps(self.policy, ids, mask, labels, True)
+        pc, pr, nc, nr = lp[:B], lp[B:], n[:B], n[B:]
+        metrics = {}
+        if self.kind == "dpo":
+            rc = rr = None
+            if self.ref is not None and not self.loss_fn.reference_free:
+                rl, _ = self._seq_logps(self.ref, ids, mask, labels, False)
+                rc, rr = rl[:B], rl[B:]
+            loss, cr, rjr = self.loss_fn(pc, pr, rc, rr)
+            metrics = {"reward_accuracy": (cr > rjr).float().mean(), "reward_margin": (cr - rjr).mean()}
+        elif self.kind == "simpo":
+            loss, cr, rjr = self.loss_fn(pc, pr, nc.float(), nr.float())
+            metrics = {"reward_accuracy": (cr > rjr).float().mean()}
+        elif self.kind == "orpo":
+            nll = -(pc / nc.clamp(min=1)).mean()
+            loss, ratio = self.loss_fn(pc / nc.clamp(min=1), pr / nr.clamp(min=1), nll)
+            metrics = {"log_odds_ratio": ratio.mean()}
+        elif self.kind == "cpo":
+            loss = self.loss_fn(pc, pr, -(pc / nc.clamp(min=1)).mean())
+        else:   # kto on paired data: chosen = desirable, rejected = undesirable
+            rl = torch.zeros_like(lp)
+            if self.ref is not None:
+                rl, _ = self._seq_logps(self.ref, ids, mask, labels, False)
+            tag = torch.cat((torch.ones(B), torch.zeros(B))).to(lp.device)
+            loss, _ = self.loss_fn(lp, rl, tag)
+        return loss, metrics
+
+    def train_step(self, batch: Dict[str, torch.Tensor], lr: float | None = None):
+        loss, metrics = self.compute_loss(batch)
+        if self.engine is not None:
+            self.engine.micro_step = max(1, self.engine.cfg.gradient_accumulation_steps) - 1
+            self.engine.backward(loss)
+            gn = self.engine.step(lr)
+        else:
+            loss.backward()
+            gn = None
+        return loss.detach(), metrics, gn
