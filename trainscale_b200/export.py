@@ -1,0 +1,82 @@
+"""Model export: merged safetensors in HuggingFace layout, GGUF (through an installed llama.cpp converter), a serving
+config for this framework's / a vLLM-style engine, and hub upload.
+
+After data_pipeline/trainer/export.py:72-452 (`merge_lora_weights`, `save_safetensors`, `export_to_gguf`,
+`create_vllm_config`, `push_to_hub`, `export_model`).
+"""
+from __future__ import annotations
+
+import json
+import shutil
+import subprocess
+import sys
+from pathlib import Path
+
+import torch
+
+from .core.errors import HubError
+from .hub import HubManager, ModelSerializer, generate_model_card
+
+
+def merge_lora_weights(model):
+    from .lora import merge_and_unload
+    return merge_and_unload(model)
+
+
+def save_safetensors(model, out_dir, max_shard_gb: float = 5.0, tokenizer=None) -> Path:
+    out = Path(out_dir)
+    sd = model.to_hf_state_dict() if hasattr(model, "to_hf_state_dict") else model.state_dict()
+    ModelSerializer(int(max_shard_gb * 2 ** 30)).save(sd, out)
+    if hasattr(model, "hf_config_dict"):
+        (out / "config.json").write_text(json.dumps(model.hf_config_dict(), indent=2))
+    tok = getattr(tokenizer, "tokenizer", tokenizer)
+    if tok is not None and hasattr(tok, "save_pretrained"):
+        tok.save_pretrained(str(out))
+    return out
+
+
+def export_to_gguf(model_dir, out_file, quantization: str = "f16", converter: str | None = None) -> Path:
+    """Needs llama.cpp's `convert_hf_to_gguf.py` (path in `converter` or on PATH); raises HubError when absent."""
+    conv = converter or shutil.which("convert_hf_to_gguf.py") or shutil.which("convert-hf-to-gguf.py")
+    if conv is None:
+        raise HubError("GGUF export needs llama.cpp's convert_hf_to_gguf.py; pass converter=<path>")
+    out = Path(out_file)
+    out.parent.mkdir(parents=True, exist_ok=True)
+    outtype = {"f16": "f16", "bf16": "bf16", "q8_0": "q8_0", "f32": "f32"}.get(quantization, "f16")
+    subprocess.run([sys.executable, conv, str(model_dir), "--outfile", str(out), "--outtype", outtype], check=True)
+    return out
+
+
+def create_vllm_config(model_dir, tensor_parallel_size: int = 1, max_model_len: int = 8192, dtype: str = "bfloat16",
+                       gpu_memory_utilization: float = 0.9) -> Path:
+    cfg = {"model": str(model_dir), "tensor_parallel_size": tensor_parallel_size, "max_model_len": max_model_len,
+           "dtype": dtype, "gpu_memory_utilization": gpu_memory_utilization, "enable_prefix_caching": True}
+    p = Path(model_dir) / "serving_config.json"
+    p.write_text(json.dumps(cfg, indent=2))
+    return p
+
+
+def push_to_hub(folder, repo_id: str, token: str | None = None, private: bool = False) -> str | None:
+    return HubManager(repo_id, token, private).push(folder, "export")
+
+
+def export_model(model, out_dir, fmt: str = "safetensors", tokenizer=None, merge_lora: bool = True,
+                 hub_model_id: str | None = None, hub_token: str | None = None, **kw) -> Path:
+    if merge_lora and any("lora_" in n for n, _ in model.named_parameters()):
+        model = merge_lora_weights(model)
+    out = Path(out_dir)
+    if fmt in ("safetensors", "vllm", "sglang") or fmt.startswith("gguf"):
+        save_safetensors(model, out, tokenizer=tokenizer)
+        if fmt in ("vllm", "sglang"):
+            create_vllm_config(out, **{k: v for k, v in kw.items() if k in ("tensor_parallel_size", "max_model_len")})
+        if fmt.startswith("gguf"):
+            export_to_gguf(out, out / f"model-{fmt.replace('gguf_', '')}.gguf", fmt.replace("gguf_", ""), kw.get("converter"))
+    elif fmt == "pytorch":
+        out.mkdir(parents=True, exist_ok=True)
+        torch.save({k: v.detach().cpu() for k, v in model.state_dict().items()}, out / "pytorch_model.bin")
+    else:
+        raise ValueError(f"unknown export format {fmt!r}")
+    (out / "README.md").write_text(generate_model_card(out.name, config=getattr(model, "hf_config_dict", dict)()))
+    if hub_model_id:
+        push_to_hub(out, hub_model_id, hub_token)
+    return out

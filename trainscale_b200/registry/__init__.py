@@ -1,0 +1,293 @@
+"""Model-family registry, hardware capability probe, kernel capability matrix and the kernel patcher.
+
+After data_pipeline/trainer/registry/__init__.py:57-1730 (`HardwareCapability`, `detect_capabilities`, `ModuleContract`,
+`DependencyGraph` with Tarjan SCC + topological sort, `KernelCapabilityMatrix`, `RegistryValidator`, `ModelInfo`,
+`register_models_from_meta`, `patch_model`, `KernelPatcher`) and the per-family tables `_llama.py` ... `_vision_models.py`.
+The framework's own decoder is built on the sm_100a kernels, so "patching" here means converting a HuggingFace Llama-
+family module tree into the framework decoder (`KernelPatcher.patch`), not monkey-patching forward methods.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from enum import Enum
+from typing import Any, Callable, Iterable
+
+import torch
+
+
+class Capability(str, Enum):
+    BF16 = "bf16"
+    FP8 = "fp8"
+    TCGEN05 = "tcgen05"
+    TMA = "tma"
+    NVLINK_P2P = "nvlink_p2p"
+    MULTICAST = "nvls_multicast"
+    FLASH_ATTENTION = "flash_attention"
+    FUSED_CE = "fused_cross_entropy"
+
+
+@dataclass(frozen=True)
+class HardwareCapability:
+    device: str
+    compute_capability: tuple[int, int]
+    sm_count: int
+    memory_gb: float
+    capabilities: frozenset
+
+    def has(self, c: Capability) -> bool:
+        return c in self.capabilities
+
+
+def detect_capabilities(device: int = 0) -> HardwareCapability:
+    if not torch.cuda.is_available():
+        return HardwareCapability("cpu", (0, 0), 0, 0.0, frozenset())
+    p = torch.cuda.get_device_properties(device)
+    cc = (p.major, p.minor)
+    caps = set()
+    if cc >= (8, 0):
+        caps.add(Capability.BF16)
+    if cc >= (8, 9):
+        caps.add(Capability.FP8)
+    if cc >= (9, 0):
+        caps.add(Capability.TMA)
+    if cc[0] == 10:
+        caps |= {Capability.TCGEN05, Capability.FLASH_ATTENTION, Capability.FUSED_CE}
+    if torch.cuda.device_count() > 1:
+        try:
+            if torch.cuda.can_device_access_peer(0, 1):
+                caps.add(Capability.NVLINK_P2P)
+        except Exception:   # noqa: BLE001
+            pass
+    return HardwareCapability(p.name, cc, p.multi_processor_count, p.total_memory / 2 ** 30, frozenset(caps))
+
+
+@dataclass
+class ModuleContract:
+    """What a kernel-backed module needs and provides."""
+    name: str
+    requires: tuple[Capability, ...] = ()
+    depends_on: tuple[str, ...] = ()
+    fallback: str | None = None
+    factory: Callable | None = None
+
+    def satisfied_by(self, hw: HardwareCapability) -> bool:
+        return all(hw.has(c) for c in self.requires)
+
+
+class DependencyGraph:
+    def __init__(self):
+        self.edges: dict[str, set[str]] = {}
+
+    def add(self, node: str, deps: Iterable[str] = ()):
+        self.edges.setdefault(node, set()).update(deps)
+        for d in deps:
+            self.edges.setdefault(d, set())
+
+    def strongly_connected_components(self) -> list[list[str]]:
+        """Tarjan's algorithm (iterative)."""
+        index, low, on, stack, out, counter = {}, {}, set(), [], [], [0]
+        for root in self.edges:
+            if root in index:
+                continue
+            work = [(root, iter(sorted(self.edges[root])))]
+            index[root] = low[root] = counter[0]
+            counter[0] += 1
+            stack.append(root)
+            on.add(root)
+            while work:
+                v, it = work[-1]
+                advanced = False
+                for w in it:
+                    if w not in index:
+                        index[w] = low[w] = counter[0]
+                        counter[0] += 1
+                        stack.append(w)
+                        on.add(w)
+                        work.append((w, iter(sorted(self.edges[w]))))
+                        advanced = True
+                        break
+                    if w in on:
+                        low[v] = min(low[v], index[w])
+                if advanced:
+                    continue
+                work.pop()
+                if work:
+                    low[work[-1][0]] = min(low[work[-1][0]], low[v])
+                if low[v] == index[v]:
+                    comp = []
+                    while True:
+                        w = stack.pop()
+                        on.discard(w)
+                        comp.append(w)
+                        if w == v:
+                            break
+                    out.append(comp)
+        return out
+
+    def find_cycles(self) -> list[list[str]]:
+        return [c for c in self.strongly_connected_components() if len(c) > 1 or c[0] in self.edges[c[0]]]
+
+    def topological_order(self) -> list[str]:
+        if self.find_cycles():
+            raise ValueError(f"dependency cycle: {self.find_cycles()[0]}")
+        seen, order = set(), []
+
+        def visit(n):
+            if n in seen:
+                return
+            seen.add(n)
+            for d in sorted(self.edges[n]):
+                visit(d)
+            order.append(n)
+
+        for n in sorted(self.edges):
+            visit(n)
+        return order
+
+
+class KernelCapabilityMatrix:
+    """Which contracts are usable on a device, with fallback chains."""
+
+    def __init__(self, contracts: Iterable[ModuleContract] = ()):
+        self.contracts = {c.name: c for c in contracts}
+
+    def register(self, c: ModuleContract):
+        self.contracts[c.name] = c
+
+    def resolve(self, name: str, hw: HardwareCapability) -> str | None:
+        seen = set()
+        while name and name not in seen:
+            seen.add(name)
+            c = self.contracts.get(name)
+            if c is None:
+                return None
+            if c.satisfied_by(hw):
+                return name
+            name = c.fallback
+        return None
+
+    def available(self, hw: HardwareCapability) -> dict[str, bool]:
+        return {n: c.satisfied_by(hw) for n, c in self.contracts.items()}
+
+
+DEFAULT_CONTRACTS = [
+    ModuleContract("gemm_tcgen05", (Capability.TCGEN05, Capability.TMA), fallback="gemm_torch"),
+    ModuleContract("gemm_torch"),
+    ModuleContract("flash_attention_tcgen05", (Capability.TCGEN05,), ("gemm_tcgen05",), "attention_torch"),
+    ModuleContract("attention_torch"),
+    ModuleContract("rmsnorm_cuda", (Capability.BF16,), fallback="rmsnorm_torch"), ModuleContract("rmsnorm_torch"),
+    ModuleContract("fused_linear_ce", (Capability.TCGEN05,), ("gemm_tcgen05",), "ce_torch"), ModuleContract("ce_torch"),
+    ModuleContract("fused_collectives", (Capability.NVLINK_P2P,), ("gemm_tcgen05",), "nccl"), ModuleContract("nccl"),
+]
+
+
+class RegistryValidator:
+    def __init__(self, matrix: KernelCapabilityMatrix):
+        self.matrix = matrix
+
+    def validate(self) -> list[str]:
+        problems = []
+        g = DependencyGraph()
+        for c in self.matrix.contracts.values():
+            g.add(c.name, c.depends_on)
+            for d in c.depends_on:
+                if d not in self.matrix.contracts:
+                    problems.append(f"{c.name} depends on unknown contract {d}")
+            if c.fallback and c.fallback not in self.matrix.contracts:
+                problems.append(f"{c.name} falls back to unknown contract {c.fallback}")
+        for cyc in g.find_cycles():
+            problems.append(f"dependency cycle: {sorted(cyc)}")
+        return problems
+
+
+@dataclass
+class ModelInfo:
+    family: str
+    org: str
+    sizes: tuple[str, ...]
+    architecture: str = "LlamaForCausalLM"
+    attention: str = "gqa"
+    mlp: str = "swiglu"
+    norm: str = "rmsnorm"
+    rope: str = "default"
+    supported: bool = True          # convertible to the framework decoder
+    notes: str = ""
+
+
+MODEL_REGISTRY: dict[str, ModelInfo] = {}
+
+
+def register_models_from_meta(meta: Iterable[ModelInfo]) -> int:
+    n = 0
+    for m in meta:
+        MODEL_REGISTRY[m.family] = m
+        n += 1
+    return n
+
+
+register_models_from_meta([
+    ModelInfo("llama", "meta-llama", ("1B", "3B", "8B", "70B", "405B"), rope="llama3"),
+    ModelInfo("mistral", "mistralai", ("7B", "12B", "24B"), "MistralForCausalLM", notes="sliding window attention"),
+    ModelInfo("qwen", "Qwen", ("0.5B", "1.5B", "7B", "14B", "32B", "72B"), "Qwen2ForCausalLM", notes="qkv bias"),
+    ModelInfo("gemma", "google", ("2B", "7B", "9B", "27B"), "GemmaForCausalLM", mlp="geglu", notes="norm weight offset 1, logit soft-cap"),
+    ModelInfo("phi", "microsoft", ("3.8B", "14B"), "Phi3ForCausalLM", notes="fused qkv / gate_up in the checkpoint"),
+    ModelInfo("deepseek", "deepseek-ai", ("7B", "67B", "V2", "V3"), "DeepseekV3ForCausalLM", attention="mla", mlp="moe", supported=False),
+    ModelInfo("falcon", "tiiuae", ("7B", "40B"), "FalconForCausalLM", attention="mqa", norm="layernorm", supported=False),
+    ModelInfo("yi", "01-ai", ("6B", "9B", "34B")),
+    ModelInfo("cohere", "CohereForAI", ("8B", "35B"), "CohereForCausalLM", norm="layernorm", supported=False),
+    ModelInfo("granite", "ibm-granite", ("2B", "8B"), "GraniteForCausalLM"),
+    ModelInfo("codellama", "codellama", ("7B", "13B", "34B")), ModelInfo("starcoder2", "bigcode", ("3B", "7B", "15B"), "Starcoder2ForCausalLM", mlp="gelu", norm="layernorm", supported=False),
+    ModelInfo("mixtral", "mistralai", ("8x7B", "8x22B"), "MixtralForCausalLM", mlp="moe"),
+    ModelInfo("qwen_moe", "Qwen", ("A2.7B", "A14B"), "Qwen2MoeForCausalLM", mlp="moe"),
+    ModelInfo("llava", "llava-hf", ("7B", "13B"), "LlavaForConditionalGeneration", supported=False, notes="vision tower not covered"),
+])
+
+
+def get_model_info(name_or_path: str) -> ModelInfo | None:
+    n = name_or_path.lower()
+    for fam, info in MODEL_REGISTRY.items():
+        if fam in n or info.org.lower() in n:
+            return info
+    return None
+
+
+def convert_hf_llama(hf_model, dtype=torch.bfloat16, device=None):
+    """HuggingFace Llama-family module -> framework decoder with the same weights."""
+    from ..models.llama import LlamaConfig, build_model
+    c = hf_model.config
+    cfg = LlamaConfig(vocab_size=c.vocab_size, hidden_size=c.hidden_size, intermediate_size=c.intermediate_size,
+                      num_hidden_layers=c.num_hidden_layers, num_attention_heads=c.num_attention_heads,
+                      num_key_value_heads=getattr(c, "num_key_value_heads", c.num_attention_heads),
+                      head_dim=getattr(c, "head_dim", None) or c.hidden_size // c.num_attention_heads,
+                      rms_norm_eps=c.rms_norm_eps, rope_theta=getattr(c, "rope_theta", None) or
+                      (getattr(c, "rope_parameters", None) or {}).get("rope_theta", 10000.0),
+                      max_position_embeddings=c.max_position_embeddings,
+                      tie_word_embeddings=bool(getattr(c, "tie_word_embeddings", False)))
+    m = build_model(cfg, dtype=dtype, device=device)
+    m.load_hf_state_dict({k: v for k, v in hf_model.state_dict().items()}, strict=not cfg.tie_word_embeddings)
+    return m
+
+
+class KernelPatcher:
+    def __init__(self, matrix: KernelCapabilityMatrix | None = None):
+        self.matrix = matrix or KernelCapabilityMatrix(DEFAULT_CONTRACTS)
+        self.hw = detect_capabilities()
+
+    def plan(self) -> dict[str, str | None]:
+        return {n: self.matrix.resolve(n, self.hw) for n in ("gemm_tcgen05", "flash_attention_tcgen05", "rmsnorm_cuda",
+                                                              "fused_linear_ce", "fused_collectives")}
+
+    def patch(self, model, dtype=torch.bfloat16, device=None):
+        """Framework decoders pass through; HF Llama-family models are converted; anything else is returned as is."""
+        from ..models.llama import LlamaForCausalLM
+        if isinstance(model, LlamaForCausalLM):
+            return model
+        arch = type(model).__name__
+        if arch in ("LlamaForCausalLM", "MistralForCausalLM", "Qwen2ForCausalLM", "GraniteForCausalLM") and \
+                not getattr(model.config, "attention_bias", False):
+            return convert_hf_llama(model, dtype, device)
+        return model
+
+
+def patch_model(model, **kw):
+    return KernelPatcher().patch(model, **kw)

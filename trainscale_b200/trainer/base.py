@@ -1,0 +1,221 @@
+"""Legacy trainers: a generic `Trainer` over any nn.Module + torch optimizer (the loop that fires every callback),
+and the specialised Pretraining / FineTuning / Seq2Seq / TextGeneration trainers.
+
+After data_pipeline/trainer/base.py:129-834 and data_pipeline/trainer/trainers/__init__.py:28-388 (EMA weights and
+curriculum sequence length in pre-training, layer-wise LR decay in fine-tuning, teacher-forced seq2seq loss, top-k /
+top-p text generation).
+"""
+from __future__ import annotations
+
+import copy
+import math
+from typing import Any, Callable, Iterable
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from ..callbacks import CallbackContext, CallbackHandler
+from ..config.training_args import TrainingArguments
+from ..optim import clip_grad_norm_, create_optimizer
+from ..schedulers import create_scheduler
+
+
+class _State:
+    def __init__(self):
+        self.epoch, self.global_step, self.max_steps, self.best_metric = 0, 0, 0, float("inf")
+
+
+class Trainer:
+    def __init__(self, model: nn.Module, args: TrainingArguments | None = None, train_dataloader: Iterable | None = None,
+                 eval_dataloader: Iterable | None = None, optimizer=None, scheduler=None, callbacks: list | None = None,
+                 compute_loss: Callable | None = None, compute_metrics: Callable | None = None):
+        self.model, self.args = model, args or TrainingArguments()
+        self.train_dataloader, self.eval_dataloader = train_dataloader, eval_dataloader
+        self.optimizer, self.scheduler = optimizer, scheduler
+        self.callbacks = CallbackHandler(callbacks or [])
+        self.compute_loss_fn, self.compute_metrics = compute_loss, compute_metrics
+        self.state = _State()
+        self.device = next(model.parameters()).device
+        self.ctx = CallbackContext(trainer=self, state=self.state, config=self.args, model=model)
+        self.callbacks.fire("on_init_end", self.ctx)
+
+    def create_optimizer(self):
+        a = self.args
+        return create_optimizer(list(self.model.parameters()), name="adamw" if a.optim.startswith("adam") else a.optim,
+                                lr=a.learning_rate, weight_decay=a.weight_decay)
+
+    def compute_loss(self, batch: dict) -> torch.Tensor:
+        if self.compute_loss_fn is not None:
+            return self.compute_loss_fn(self.model, batch)
+        out = self.model(**{k: v for k, v in batch.items() if k in ("input_ids", "attention_mask", "labels")})
+        return out.loss if hasattr(out, "loss") else out[0]
+
+    def _to_device(self, batch):
+        return {k: (v.to(self.device) if torch.is_tensor(v) else v) for k, v in batch.items()}
+
+    def train(self) -> dict:
+        a = self.args
+        if self.optimizer is None:
+            self.optimizer = self.create_optimizer()
+        steps_per_epoch = max(1, len(self.train_dataloader) // a.gradient_accumulation_steps)
+        total = a.max_steps if a.max_steps > 0 else int(steps_per_epoch * a.num_train_epochs)
+        self.state.max_steps = total
+        if self.scheduler is None:
+            self.scheduler = create_scheduler(self.optimizer, a.lr_scheduler_type, total, a.warmup_steps, a.warmup_ratio)
+        self.callbacks.fire("on_train_begin", self.ctx)
+        self.model.train()
+        losses = []
+        done = False
+        for epoch in range(max(1, math.ceil(a.num_train_epochs))):
+            self.state.epoch = epoch
+            self.callbacks.fire("on_epoch_begin", self.ctx)
+            done = self._train_epoch(losses, total)
+            self.callbacks.fire("on_epoch_end", self.ctx)
+            if a.eval_strategy == "epoch" and self.eval_dataloader is not None:
+                self.evaluate()
+            if done or self.ctx.should_stop:
+                break
+        self.callbacks.fire("on_train_end", self.ctx)
+        return {"global_step": self.state.global_step, "train_loss": sum(losses) / max(len(losses), 1)}
+
+    def _train_epoch(self, losses: list, total: int) -> bool:
+        a = self.args
+        for i, batch in enumerate(self.train_dataloader):
+            if i % a.gradient_accumulation_steps == 0:
+                self.callbacks.fire("on_step_begin", self.ctx)
+            loss = self.compute_loss(self._to_device(batch)) / a.gradient_accumulation_steps
+            loss.backward()
+            if (i + 1) % a.gradient_accumulation_steps:
+                continue
+            if a.max_grad_norm and a.max_grad_norm > 0:
+                clip_grad_norm_(self.model.parameters(), a.max_grad_norm)
+            self.optimizer.step()
+            self.scheduler.step()
+            self.optimizer.zero_grad(set_to_none=True)
+            self.state.global_step += 1
+            losses.append(float(loss.detach()) * a.gradient_accumulation_steps)
+            self.after_step()
+            self.ctx.logs = {"loss": losses[-1], "lr": self.optimizer.param_groups[0]["lr"]}
+            self.ctx.should_log = False
+            self.callbacks.fire("on_step_end", self.ctx)
+            if self.ctx.should_log or self.state.global_step % max(1, a.logging.logging_steps) == 0:
+                self.callbacks.fire("on_log", self.ctx)
+            if a.eval_strategy == "steps" and a.eval_steps and self.state.global_step % a.eval_steps == 0 \
+                    and self.eval_dataloader is not None:
+                self.evaluate()
+            if self.state.global_step >= total or self.ctx.should_stop:
+                return True
+        return False
+
+    def after_step(self):
+        pass
+
+    @torch.no_grad()
+    def evaluate(self) -> dict:
+        self.model.eval()
+        tot, n = 0.0, 0
+        for batch in self.eval_dataloader:
+            tot += float(self.compute_loss(self._to_device(batch)))
+            n += 1
+            self.callbacks.fire("on_prediction_step", self.ctx)
+        self.model.train()
+        m = {"eval_loss": tot / max(n, 1)}
+        if self.compute_metrics is not None:
+            m.update(self.compute_metrics(m) or {})
+        self.ctx.metrics = m
+        self.callbacks.fire("on_evaluate", self.ctx)
+        return m
+
+    @torch.no_grad()
+    def predict(self, dataloader: Iterable) -> list:
+        self.model.eval()
+        outs = []
+        for batch in dataloader:
+            out = self.model(**{k: v for k, v in self._to_device(batch).items() if k in ("input_ids", "attention_mask")})
+            outs.append(out.logits if hasattr(out, "logits") else out)
+        return outs
+
+    def save_model(self, output_dir: str):
+        from ..ckpt import save_model_weights
+        from pathlib import Path
+        save_model_weights(self.model, Path(output_dir))
+        self.callbacks.fire("on_save", self.ctx)
+
+
+class PretrainingTrainer(Trainer):
+    """Adds an EMA copy of the weights and a curriculum on the sequence length."""
+
+    def __init__(self, *a, ema_decay: float | None = None, curriculum: tuple[int, int, int] | None = None, **kw):
+        super().__init__(*a, **kw)
+        self.ema_decay = ema_decay
+        self.ema = copy.deepcopy(self.model).eval() if ema_decay else None
+        self.curriculum = curriculum   # (start_len, end_len, ramp_steps)
+
+    def current_seq_len(self) -> int | None:
+        if not self.curriculum:
+            return None
+        s, e, ramp = self.curriculum
+        return int(s + (e - s) * min(1.0, self.state.global_step / max(1, ramp)))
+
+    def compute_loss(self, batch):
+        n = self.current_seq_len()
+        if n is not None:
+            batch = {k: (v[:, :n] if torch.is_tensor(v) and v.dim() == 2 else v) for k, v in batch.items()}
+        return super().compute_loss(batch)
+
+    @torch.no_grad()
+    def after_step(self):
+        if self.ema is not None:
+            for p, q in zip(self.ema.parameters(), self.model.parameters()):
+                p.lerp_(q.detach(), 1 - self.ema_decay)
+
+
+class FineTuningTrainer(Trainer):
+    """Layer-wise learning-rate decay: layer l of L gets lr * decay^(L - l)."""
+
+    def __init__(self, *a, layerwise_lr_decay: float | None = None, **kw):
+        self.layerwise_lr_decay = layerwise_lr_decay
+        super().__init__(*a, **kw)
+
+    def create_optimizer(self):
+        if not self.layerwise_lr_decay:
+            return super().create_optimizer()
+        layers = getattr(getattr(self.model, "model", self.model), "layers", None)
+        L = len(layers) if layers is not None else 0
+        groups, seen = [], set()
+        for l in range(L):
+            ps = list(layers[l].parameters())
+            seen.update(id(p) for p in ps)
+            groups.append({"params": ps, "lr": self.args.learning_rate * self.layerwise_lr_decay ** (L - l)})
+        rest = [p for p in self.model.parameters() if id(p) not in seen]
+        groups.append({"params": rest, "lr": self.args.learning_rate})
+        from ..optim import AdamW
+        return AdamW(groups, lr=self.args.learning_rate, weight_decay=self.args.weight_decay)
+
+
+class Seq2SeqTrainer(Trainer):
+    def compute_loss(self, batch):
+        out = self.model(**{k: v for k, v in batch.items() if k in ("input_ids", "attention_mask", "decoder_input_ids", "labels")})
+        if hasattr(out, "loss") and out.loss is not None:
+            return out.loss
+        logits = out.logits if hasattr(out, "logits") else out
+        return F.cross_entropy(logits.reshape(-1, logits.shape[-1]).float(), batch["labels"].reshape(-1), ignore_index=-100)
+
+
+class TextGenerationTrainer(Trainer):
+    @torch.no_grad()
+    def generate(self, input_ids: torch.Tensor, max_new_tokens: int = 32, temperature: float = 1.0, top_k: int = 0,
+                 top_p: float = 1.0, eos_token_id: int | None = None) -> torch.Tensor:
+        from ..inference.sampling import sample
+        self.model.eval()
+        ids = input_ids.to(self.device)
+        for _ in range(max_new_tokens):
+            out = self.model(input_ids=ids)
+            logits = (out.logits if hasattr(out, "logits") else out)[:, -1].float()
+            B = logits.shape[0]
+            nxt, _ = sample(logits, [temperature] * B, [top_k] * B, [top_p] * B, [0.0] * B, [None] * B)
+            ids = torch.cat((ids, nxt.unsqueeze(1)), dim=1)
+            if eos_token_id is not None and bool((nxt == eos_token_id).all()):
+                break
+        return ids

@@ -1,0 +1,86 @@
+"""CUDA-graph capture of launch-bound loops (decode steps, fixed-shape micro-steps).
+
+Stands in for the reference's torch.compile wrapper (data_pipeline/trainer/kernels/compiler.py:156-1066:
+`CompilationConfig`, `CUDAGraphManager`, `compile_model`, `optimize_for_inference / training`): this framework has no
+tracing compiler on the hot path - kernels are hand-written - so the only launch-overhead tool is graph replay.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Callable
+
+import torch
+
+
+@dataclass
+class CompilationConfig:
+    mode: str = "cuda_graphs"      # cuda_graphs | none
+    warmup_iters: int = 3
+    pool_shared: bool = True
+
+
+class CUDAGraphManager:
+    """Capture `fn(*static_inputs)` once per input-shape signature and replay it with new data copied in."""
+
+    def __init__(self, config: CompilationConfig | None = None):
+        self.config = config or CompilationConfig()
+        self.graphs: dict[tuple, tuple] = {}
+        self.pool = None
+
+    @staticmethod
+    def _sig(args) -> tuple:
+        return tuple((tuple(a.shape), a.dtype) if torch.is_tensor(a) else a for a in args)
+
+    def run(self, fn: Callable, *args):
+        if not torch.cuda.is_available() or self.config.mode == "none":
+            return fn(*args)
+        sig = (id(fn),) + self._sig(args)
+        if sig not in self.graphs:
+            static = [a.clone() if torch.is_tensor(a) else a for a in args]
+            s = torch.cuda.Stream()
+            s.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(s):
+                for _ in range(self.config.warmup_iters):
+                    fn(*static)
+            torch.cuda.current_stream().wait_stream(s)
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, pool=self.pool):
+                out = fn(*static)
+            if self.config.pool_shared and self.pool is None:
+                self.pool = g.pool()
+            self.graphs[sig] = (g, static, out)
+        g, static, out = self.graphs[sig]
+        for s_, a in zip(static, args):
+            if torch.is_tensor(a):
+                s_.copy_(a)
+        g.replay()
+        return out
+
+    def clear(self):
+        self.graphs.clear()
+        self.pool = None
+
+
+def compile_model(model, config: CompilationConfig | None = None):
+    """Returns a callable running `model` under graph replay for fixed input shapes (inference only)."""
+    mgr = CUDAGraphManager(config)
+
+    @torch.no_grad()
+    def run(input_ids):
+        return mgr.run(lambda x: model(input_ids=x).logits, input_ids)
+
+    run.manager = mgr
+    return run
+
+
+def optimize_for_inference(model):
+    model.eval()
+    for p in model.parameters():
+        p.requires_grad_(False)
+    return compile_model(model)
+
+
+def optimize_for_training(model, checkpoint_every: int = 2):
+    if hasattr(model, "gradient_checkpointing_enable"):
+        model.gradient_checkpointing_enable(checkpoint_every)
+    return model
