@@ -1,0 +1,199 @@
+"""Losses, schedulers, optimizers, callbacks, hub/checkpoint manager, registry, metrics, LoRA, quantisation, RL utils."""
+import math
+
+import pytest
+import torch
+import torch.nn.functional as F
+
+from trainscale_b200 import losses as L
+from trainscale_b200.callbacks import CallbackContext, CallbackHandler, Callback, CheckpointCallback, EarlyStoppingCallback
+from trainscale_b200.hub import CheckpointManager, CircuitBreaker, ModelDeserializer, ModelSerializer, RetryPolicy, execute_with_retry
+from trainscale_b200.core.errors import CheckpointLoadError, HubError
+from trainscale_b200.schedulers import create_scheduler
+
+
+def test_dpo_family_formulas():
+    pc, pr, rc, rr = torch.tensor([-5.0, -3.0]), torch.tensor([-6.0, -2.5]), torch.tensor([-5.5, -3.0]), torch.tensor([-5.8, -2.9])
+    x = (pc - pr) - (rc - rr)
+    loss, cr, rjr = L.DPOLoss(0.1)(pc, pr, rc, rr)
+    assert torch.allclose(loss, -F.logsigmoid(0.1 * x).mean()) and torch.allclose(cr, 0.1 * (pc - rc))
+    assert torch.allclose(L.DPOLoss(0.1, "hinge")(pc, pr, rc, rr)[0], torch.relu(1 - 0.1 * x).mean())
+    assert torch.allclose(L.DPOLoss(0.1, "ipo")(pc, pr, rc, rr)[0], ((x - 5.0) ** 2).mean())
+    sm = L.DPOLoss(0.1, label_smoothing=0.2)(pc, pr, rc, rr)[0]
+    assert torch.allclose(sm, (-0.8 * F.logsigmoid(0.1 * x) - 0.2 * F.logsigmoid(-0.1 * x)).mean())
+    s, _, _ = L.SimPOLoss(2.0, 0.5)(pc, pr, torch.tensor([5.0, 3.0]), torch.tensor([6.0, 2.0]))
+    assert torch.allclose(s, -F.logsigmoid(2.0 * (pc / torch.tensor([5.0, 3.0]) - pr / torch.tensor([6.0, 2.0])) - 0.5).mean())
+    lp = torch.tensor([-0.5, -0.2])
+    assert torch.allclose(L.ORPOLoss.log_odds(lp), lp - torch.log1p(-lp.exp()))
+
+
+def test_lm_losses_match_torch():
+    torch.manual_seed(0)
+    lg, lb = torch.randn(2, 5, 11), torch.randint(0, 11, (2, 5))
+    lb[0, 0] = -100
+    ref = F.cross_entropy(lg.view(-1, 11), lb.view(-1), ignore_index=-100)
+    assert torch.allclose(L.CrossEntropyLoss()(lg, lb), ref)
+    h, w = torch.randn(10, 16), torch.randn(11, 16)
+    assert torch.allclose(L.ChunkedCrossEntropyLoss()(h, w, lb.view(-1)), F.cross_entropy(h @ w.t(), lb.view(-1), ignore_index=-100), atol=1e-5)
+    t = torch.randn(2, 5, 11)
+    d = L.DistillationLoss(2.0, 0.5)(lg, t, lb)
+    valid = lb.view(-1) != -100
+    kd = F.kl_div(torch.log_softmax(lg.view(-1, 11)[valid] / 2, -1), torch.softmax(t.view(-1, 11)[valid] / 2, -1), reduction="batchmean") * 4
+    assert torch.allclose(d, 0.5 * kd + 0.5 * ref, atol=1e-5)
+    assert len(L.LossRegistry.available()) >= 30 and isinstance(L.create_loss("focal"), L.FocalLoss)
+    lbl = L.LoadBalancingLoss(4, 1, 1.0)(torch.zeros(8, 4), torch.arange(8) % 4)
+    assert abs(float(lbl) - 1.0) < 1e-6        # perfectly balanced routing gives E * sum (1/E * 1/E) = 1
+
+
+def test_schedulers_shapes():
+    opt = torch.optim.SGD([torch.nn.Parameter(torch.zeros(1))], lr=1.0)
+    s = create_scheduler(opt, "wsd", 100, warmup_steps=10, min_lr_ratio=0.1, stable_ratio=0.5)
+    lrs = []
+    for _ in range(100):
+        lrs.append(opt.param_groups[0]["lr"])
+        s.step()
+    assert lrs[0] == pytest.approx(0.1) and lrs[9] == pytest.approx(1.0) and lrs[40] == 1.0 and lrs[-1] < 0.2
+    assert all(a >= b - 1e-12 for a, b in zip(lrs[55:], lrs[56:]))
+    opt2 = torch.optim.SGD([torch.nn.Parameter(torch.zeros(1))], lr=2.0)
+    c = create_scheduler(opt2, "cosine", 50, warmup_ratio=0.1, min_lr_ratio=0.0)
+    assert c.warmup_steps == 5
+    for _ in range(50):
+        c.step()
+    assert opt2.param_groups[0]["lr"] == pytest.approx(0.0, abs=1e-6)
+    st = c.state_dict()
+    c2 = create_scheduler(torch.optim.SGD([torch.nn.Parameter(torch.zeros(1))], lr=2.0), "cosine", 50, warmup_steps=5)
+    c2.load_state_dict(st)
+    assert c2.last_step == c.last_step
+    for name in ("linear", "polynomial", "inverse_sqrt", "rex", "cosine_restart", "onecycle", "constant"):
+        o = torch.optim.SGD([torch.nn.Parameter(torch.zeros(1))], lr=1.0)
+        sch = create_scheduler(o, name, 20, warmup_steps=2)
+        for _ in range(20):
+            sch.step()
+            assert math.isfinite(o.param_groups[0]["lr"]) and o.param_groups[0]["lr"] >= 0
+
+
+def test_callbacks_fire_in_order_and_checkpoint_rotation(tmp_path):
+    seen = []
+
+    class Rec(Callback):
+        def on_step_end(self, ctx):
+            seen.append(ctx.state.global_step)
+
+    class S:
+        global_step = 0
+    h = CallbackHandler([Rec()])
+    ctx = CallbackContext(state=S())
+    for i in range(3):
+        S.global_step = i + 1
+        h.fire("on_step_end", ctx)
+    assert seen == [1, 2, 3]
+    with pytest.raises(ValueError):
+        h.fire("on_nothing", ctx)
+    es = EarlyStoppingCallback(patience=2)
+    for v in (1.0, 0.9, 0.95, 0.96):
+        ctx.metrics = {"eval_loss": v}
+        es.on_evaluate(ctx)
+    assert ctx.should_stop
+    for s in (10, 20, 30, 40):
+        (tmp_path / f"checkpoint-{s}").mkdir()
+    (tmp_path / "checkpoint-best").mkdir()
+    CheckpointCallback(str(tmp_path), save_total_limit=2).cleanup_old_checkpoints()
+    assert sorted(p.name for p in tmp_path.iterdir()) == ["checkpoint-30", "checkpoint-40", "checkpoint-best"]
+
+
+def test_serializer_integrity_retry_and_manager(tmp_path):
+    sd = {f"w{i}": torch.randn(64, 64) for i in range(6)}
+    info = ModelSerializer(max_shard_bytes=40000).save(sd, tmp_path / "m")
+    assert len(info["files"]) > 1
+    back = ModelDeserializer().load(tmp_path / "m")
+    assert all(torch.equal(back[k], sd[k]) for k in sd)
+    shard = tmp_path / "m" / info["files"][0]
+    data = bytearray(shard.read_bytes())
+    data[-1] ^= 0xFF
+    shard.write_bytes(bytes(data))
+    with pytest.raises(CheckpointLoadError):
+        ModelDeserializer().load(tmp_path / "m")
+    calls = {"n": 0}
+
+    def flaky():
+        calls["n"] += 1
+        if calls["n"] < 3:
+            raise OSError("transient")
+        return "ok"
+    assert execute_with_retry(flaky, RetryPolicy(max_attempts=4, base_delay=0), sleep=lambda s: None) == "ok"
+    br = CircuitBreaker(failure_threshold=2, reset_timeout=10, clock=lambda: 0.0)
+    with pytest.raises(HubError):
+        execute_with_retry(lambda: (_ for _ in ()).throw(OSError("down")), RetryPolicy(max_attempts=5, base_delay=0), br, sleep=lambda s: None)
+    assert br.state == "open"
+    cm = CheckpointManager(tmp_path / "ck", save_total_limit=2)
+    for step, loss in ((1, 3.0), (2, 1.0), (3, 2.0), (4, 2.5)):
+        cm.save(step, lambda d: (d / "x.txt").write_text("x"), {"eval_loss": loss})
+    names = [p.name for p in cm.list()]
+    assert "checkpoint-2" in names and "checkpoint-4" in names and "checkpoint-1" not in names   # best is kept
+    assert cm.latest().name == "checkpoint-4" and cm.best().name == "checkpoint-2"
+
+
+def test_registry_graph_and_hf_conversion():
+    from transformers import LlamaConfig as HC, LlamaForCausalLM as HM
+    from trainscale_b200.registry import DependencyGraph, KernelCapabilityMatrix, DEFAULT_CONTRACTS, RegistryValidator, detect_capabilities, patch_model
+    g = DependencyGraph()
+    g.add("a", ["b"])
+    g.add("b", ["c"])
+    assert g.topological_order() == ["c", "b", "a"]
+    g.add("c", ["a"])
+    assert g.find_cycles() and pytest.raises(ValueError, g.topological_order)
+    m = KernelCapabilityMatrix(DEFAULT_CONTRACTS)
+    assert RegistryValidator(m).validate() == []
+    assert m.resolve("flash_attention_tcgen05", detect_capabilities()) in ("flash_attention_tcgen05", "attention_torch")
+    hf = HM(HC(vocab_size=256, hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+               num_key_value_heads=2, max_position_embeddings=64)).eval()
+    mine = patch_model(hf, dtype=torch.float32).eval()
+    ids = torch.randint(0, 256, (2, 12))
+    assert (mine(ids).logits - hf(ids).logits).abs().max() < 1e-4
+    assert abs(mine(ids, labels=ids).loss.item() - hf(ids, labels=ids).loss.item()) < 1e-5
+
+
+def test_lora_quant_rl_metrics():
+    from trainscale_b200.lora import count_trainable, get_peft_model, merge_and_unload
+    from trainscale_b200.models.llama import build_model
+    from trainscale_b200.quantization import block_dequantize_fp8, block_quantize_fp8, fast_dequantize, quantize_nf4
+    from trainscale_b200.rl import compute_advantages, grpo_loss, left_pack_padding, selective_log_softmax
+    from trainscale_b200.metrics import BLEU, F1Score, LossTracker, Perplexity
+    m = build_model("tiny", dtype=torch.float32, seed=0)
+    ids = torch.randint(0, 32000, (1, 8))
+    base = m(ids).logits
+    get_peft_model(m, r=4, target_modules=["q_proj", "v_proj"])
+    t, tot = count_trainable(m)
+    assert 0 < t < 0.01 * tot and torch.allclose(m(ids).logits, base, atol=1e-5)
+    for n, p in m.named_parameters():
+        if "lora_B" in n:
+            torch.nn.init.normal_(p, std=0.05)
+    tuned = m(ids).logits
+    merge_and_unload(m)
+    assert (m(ids).logits - tuned).abs().max() < 1e-4 and not any("lora_" in n for n, _ in m.named_parameters())
+    w = torch.randn(200, 130)
+    q, s = block_quantize_fp8(w)
+    assert (block_dequantize_fp8(q, s, dtype=torch.float32) - w).abs().max() < 0.3 and s.shape == (2, 2)
+    pk, am, sh = quantize_nf4(w)
+    assert (fast_dequantize(pk, am, sh, torch.float32) - w).abs().mean() < 0.15
+    lg, idx = torch.randn(3, 7), torch.tensor([1, 2, 3])
+    assert torch.allclose(selective_log_softmax(lg, idx), torch.log_softmax(lg, -1).gather(1, idx[:, None]).squeeze(1), atol=1e-6)
+    adv = compute_advantages(torch.tensor([1.0, 2, 3, 4]), 4)
+    assert abs(float(adv.mean())) < 1e-6
+    lp = torch.zeros(4, 3)
+    assert float(grpo_loss(lp, lp, lp, adv, torch.ones(4, 3))) == pytest.approx(0.0, abs=1e-6)
+    ids2, mk = left_pack_padding(torch.tensor([[0, 5, 0, 6]]), torch.tensor([[0, 1, 0, 1]]))
+    assert ids2.tolist() == [[5, 6, 0, 0]]
+    f = F1Score()
+    f.update(torch.tensor([0, 1, 1]), torch.tensor([0, 1, 0]))
+    assert 0 < f.compute() < 1
+    b = BLEU()
+    b.update(["a b c d e"], ["a b c d e"])
+    assert b.compute() == pytest.approx(1.0)
+    p = Perplexity()
+    p.update(torch.zeros(4, 10), torch.zeros(4, dtype=torch.long))
+    assert p.compute() == pytest.approx(10.0, rel=1e-4)
+    lt = LossTracker()
+    lt.update(2.0, 10)
+    lt.update(4.0, 30)
+    assert lt.mean == pytest.approx(3.5)

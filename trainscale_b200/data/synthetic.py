@@ -13,7 +13,8 @@ from torch.utils.data import DataLoader, Dataset
 
 class SyntheticTokenDataset(Dataset):
     def __init__(self, vocab_size: int, seq_len: int, num_samples: int = 1 << 16, seed: int = 0,
-                 packed: bool = False, min_doc: int = 64, max_doc: int = 512):
+                 packed: bool = False, min_doc: int = 64, max_doc: int = 512, mode: str = "uniform"):
+        self.mode = mode    # "uniform": i.i.d. tokens (benchmarks); "arith": t[i+1] = t[i] + 7 mod V (a learnable toy task)
         self.vocab_size, self.seq_len, self.num_samples, self.seed = vocab_size, seq_len, num_samples, seed
         self.packed, self.min_doc, self.max_doc = packed, min_doc, max_doc
 
@@ -23,6 +24,8 @@ class SyntheticTokenDataset(Dataset):
     def __getitem__(self, idx):
         g = torch.Generator().manual_seed(self.seed * 1000003 + idx)
         ids = torch.randint(0, self.vocab_size, (self.seq_len,), generator=g, dtype=torch.int64)
+        if self.mode == "arith":
+            ids = (ids[0] + 7 * torch.arange(self.seq_len)) % self.vocab_size
         item = {"input_ids": ids, "attention_mask": torch.ones(self.seq_len, dtype=torch.int64), "labels": ids.clone()}
         if self.packed:
             doc = torch.empty(self.seq_len, dtype=torch.int64)
