@@ -781,3 +781,62 @@ extern "C" int ts_softmax_rows(const void* x, void* y, long long rows, int V, vo
   softmax_rows_kernel<<<(unsigned)rows, 256, 0, ST(stream)>>>((const bf16*)x, (bf16*)y, V);
   return (int)cudaGetLastError();
 }
+
+// ---------------------------------------------------------------------------------------------------
+// Allocation-free RMSNorm backward (declared and documented in no_alloc.h).
+// ---------------------------------------------------------------------------------------------------
+#include "no_alloc.h"
+
+// Built-in workspace for the per-CTA partial sums of dw.  In host code this name is only a handle for
+// cudaGetSymbolAddress; it is not a device address and must never be passed to a kernel as one.
+static __device__ __align__(256) float g_noalloc_dw_partial[TS_NOALLOC_MAX_PARTS * TS_NOALLOC_MAX_H];
+
+namespace {
+constexpr int kMaxDevices = 64;
+float* g_noalloc_ptr[kMaxDevices] = {nullptr};
+std::mutex g_noalloc_mutex;
+
+// Device address of the workspace on the current device (looked up once per device, with that device current).
+int noalloc_workspace(float** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= kMaxDevices) return -21;
+  std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+  if (g_noalloc_ptr[dev] == nullptr) {
+    float* p = nullptr;
+    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_noalloc_dw_partial);
+    if (e != cudaSuccess) return (int)e;
+    if (p == nullptr) return -22;
+    g_noalloc_ptr[dev] = p;
+  }
+  *out = g_noalloc_ptr[dev];
+  return 0;
+}
+}  // namespace
+
+extern "C" int ts_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void* w, const float* rstd, const void* dres,
+                                      void* dx, float* dw_f32, void* dw_bf16, int accumulate_dw, long long rows, int H,
+                                      float w_offset, void* stream) {
+  if (rows <= 0 || H <= 0 || H % 8 != 0 || H > TS_NOALLOC_MAX_H) {
+    fprintf(stderr,
+            "[trainscale_b200] ts_rmsnorm_bwd_noalloc: rows=%lld H=%d rejected (need rows > 0, H %% 8 == 0, H <= %d: "
+            "the built-in workspace holds %d x %d floats)\n",
+            rows, H, TS_NOALLOC_MAX_H, TS_NOALLOC_MAX_PARTS, TS_NOALLOC_MAX_H);
+    return -20;
+  }
+  float* workspace = nullptr;
+  const int rc = noalloc_workspace(&workspace);
+  if (rc != 0) return rc;
+  // one partial row per CTA, never more rows than the workspace holds
+  const int parts = rows < TS_NOALLOC_MAX_PARTS ? (int)rows : TS_NOALLOC_MAX_PARTS;
+  rmsnorm_bwd_kernel<<<parts, NORM_THREADS, 0, ST(stream)>>>((const bf16*)dy, (const bf16*)x, (const bf16*)w, rstd,
+                                                             (const bf16*)dres, (bf16*)dx, workspace, (int)rows, H,
+                                                             w_offset);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return (int)e;
+  // every CTA wrote its whole partial row above, so the reduction reads only values of this call
+  rmsnorm_dw_reduce_kernel<<<(H + 255) / 256, 256, 0, ST(stream)>>>(workspace, dw_f32, (bf16*)dw_bf16, parts, H,
+                                                                    accumulate_dw);
+  return (int)cudaGetLastError();
+}
