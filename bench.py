@@ -102,7 +102,7 @@ def run_ours(args) -> dict:
     torch.cuda.set_device(local)
     mcfg = preset_config(args.model)
     seq, mb = args.seq, args.micro_batch
-    ac = args.ac if args.ac != "auto" else ("full" if world == 1 else ("half" if world == 2 else "none"))
+    ac = args.ac if args.ac != "auto" else ("half" if world == 1 else "none")
     cfg = SOTAConfig.from_dict({
         "training_mode": "full",
         "model": {"architecture": args.model},

@@ -358,7 +358,7 @@ struct BwdSmem {
   static constexpr int TOTAL = BAR_OFF + 256 + 1024;
 };
 
-constexpr int BWD_THREADS = 192;
+constexpr int BWD_THREADS = 320;   // warp 0 TMA, warp 1 MMA, warps 2..5 and 6..9: two compute warpgroups (32 columns each)
 
 __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
@@ -404,7 +404,7 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_co
     tma_prefetch_desc(&tmK128);
     tma_prefetch_desc(&tmV128);
     tma_prefetch_desc(&tmdO64);
-    for (int i = 0; i < 12; ++i) mbar_init(&bars[i], (i == 9 || i == 10) ? 4 : 1);
+    for (int i = 0; i < 12; ++i) mbar_init(&bars[i], (i == 9 || i == 10) ? 8 : 1);
     fence_barrier_init();
   }
   if (warp == 1) {
@@ -479,12 +479,12 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_co
           const uint32_t st = tmem_base + bsel * 128;
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk)
-            umma_f16_ts(tmem_base + DV_COL, st + kk * 8, make_smem_desc_sw128(da + kk * 2048, 8192, 1024), idesc_acc,
-                        (it | kk) != 0);
+            umma_f16_ts(tmem_base + DV_COL, st + (kk >> 1) * 32 + (kk & 1) * 8,
+                        make_smem_desc_sw128(da + kk * 2048, 8192, 1024), idesc_acc, (it | kk) != 0);
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk)
-            umma_f16_ts(tmem_base + DK_COL, st + 64 + kk * 8, make_smem_desc_sw128(qa + kk * 2048, 8192, 1024),
-                        idesc_acc, (it | kk) != 0);
+            umma_f16_ts(tmem_base + DK_COL, st + 64 + (kk >> 1) * 32 + (kk & 1) * 8,
+                        make_smem_desc_sw128(qa + kk * 2048, 8192, 1024), idesc_acc, (it | kk) != 0);
           umma_commit(&qd_empty[s]);
           if (it + 2 < total) issue12(it + 2);
         }
@@ -493,31 +493,34 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_co
     }
   } else {
     const int q4 = warp & 3;
+    const int wg = (warp - 2) >> 2;          // compute warpgroup: owns query columns [wg*32, wg*32+32) of the sub-tile
     const int r = q4 * 32 + lane;            // kv row inside the tile
-    const int ct = threadIdx.x - 64;         // 0..127 among the compute threads
+    const int ct = threadIdx.x - 64;         // 0..255 among the compute threads
     const int kv_row = j * 128 + r;
     const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(q4 * 32) << 16);
-    for (int it = 0; it < total && alive; ++it) {
+    // per-column (lse * log2e, delta) pairs of the next sub-tile are fetched one iteration ahead
+    auto fetch_vec = [&](int it) -> float {
       const int g = it / per_head, u = u_start + it % per_head;
       const int h = hk * p.group + g;
+      const int c = ct & 63;
+      const int qrow = u * 64 + c;
+      if (ct >= 128 || qrow >= Lq) return 0.f;
+      const size_t idx = static_cast<size_t>(h) * p.total_rows + q_start + qrow;
+      return (ct < 64) ? p.lse[idx] * 1.4426950408889634f : p.delta[idx];
+    };
+    float nxt = total > 0 ? fetch_vec(0) : 0.f;
+    for (int it = 0; it < total && alive; ++it) {
+      const int u = u_start + it % per_head;
       float* vb = vec + (it & 1) * 128;
-      {
-        const int c = ct & 63;
-        const int qrow = u * 64 + c;
-        float val = 0.f;
-        if (qrow < Lq) {
-          const size_t idx = static_cast<size_t>(h) * p.total_rows + q_start + qrow;
-          val = (ct < 64) ? p.lse[idx] * 1.4426950408889634f : p.delta[idx];
-        }
-        vb[ct] = val;
-      }
-      named_bar_sync(1, 128);
+      if (ct < 128) vb[ct] = nxt;
+      if (it + 1 < total) nxt = fetch_vec(it + 1);
+      named_bar_sync(1, 256);
       if (!mbar_wait(&s_full[it & 1], (it >> 1) & 1u, alive, 720)) break;
       tc_fence_after_sync();
       const uint32_t t_s = t_lane + (it & 1) * 128;
       const bool need_mask = (p.causal && (j * 128 + 127 > u * 64 + off)) || (u * 64 + 64 > Lq) || (j * 128 + 128 > Lk);
-#pragma unroll 1
-      for (int cc = 0; cc < 2; ++cc) {
+      {
+        const int cc = wg;
         uint32_t sv[32], dv[32], pp[16], ds[16];
         tmem_ld_32x32b_x32(t_s + cc * 32, sv);
         tmem_ld_32x32b_x32(t_s + 64 + cc * 32, dv);
@@ -540,8 +543,9 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_co
           pp[e >> 1] = pack_bf16x2(pv[0], pv[1]);
           ds[e >> 1] = pack_bf16x2(dsv[0], dsv[1]);
         }
-        tmem_st_32x32b_x16(t_s + cc * 16, pp);
-        tmem_st_32x32b_x16(t_s + 64 + cc * 16, ds);
+        // each warpgroup overwrites only columns of its own (already consumed) chunk
+        tmem_st_32x32b_x16(t_s + cc * 32, pp);
+        tmem_st_32x32b_x16(t_s + 64 + cc * 32, ds);
       }
       tc_wait_st();
       tc_fence_before_sync();
@@ -554,7 +558,7 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_co
       __nv_bfloat16* dvp = p.dv + static_cast<size_t>(k_start + kv_row) * p.dqkv_stride + p.v_col0 + hk * D;
       __nv_bfloat16* dkp = p.dk + static_cast<size_t>(k_start + kv_row) * p.dqkv_stride + p.k_col0 + hk * D;
 #pragma unroll 1
-      for (int c = 0; c < D / 32; ++c) {
+      for (int c = wg; c < D / 32; c += 2) {
         uint32_t v[32];
         tmem_ld_32x32b_x32(t_lane + DV_COL + c * 32, v);
         tc_wait_ld();
@@ -637,7 +641,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ128, const __grid_con
     tma_prefetch_desc(&tmK64);
     tma_prefetch_desc(&tmV64);
     tma_prefetch_desc(&tmdO128);
-    for (int x = 0; x < 12; ++x) mbar_init(&bars[x], (x == 9 || x == 10) ? 4 : 1);
+    for (int x = 0; x < 12; ++x) mbar_init(&bars[x], (x == 9 || x == 10) ? 8 : 1);
     fence_barrier_init();
   }
   if (warp == 1) {
@@ -708,8 +712,8 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ128, const __grid_con
           const uint32_t st = tmem_base + bsel * 128;
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk)
-            umma_f16_ts(tmem_base + DQ_COL, st + 64 + kk * 8, make_smem_desc_sw128(ka + kk * 2048, 8192, 1024),
-                        idesc_acc, (it | kk) != 0);
+            umma_f16_ts(tmem_base + DQ_COL, st + 64 + (kk >> 1) * 32 + (kk & 1) * 8,
+                        make_smem_desc_sw128(ka + kk * 2048, 8192, 1024), idesc_acc, (it | kk) != 0);
           umma_commit(&kv_empty[s]);
           if (it + 2 < total) issue12(it + 2);
         }
@@ -718,6 +722,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ128, const __grid_con
     }
   } else {
     const int q4 = warp & 3;
+    const int wg = (warp - 2) >> 2;
     const int r = q4 * 32 + lane;
     const int qrow = i * 128 + r;
     const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(q4 * 32) << 16);
@@ -733,8 +738,8 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ128, const __grid_con
       tc_fence_after_sync();
       const uint32_t t_s = t_lane + (it & 1) * 128;
       const bool need_mask = (it * 64 + 63 > i * 128 + off && p.causal) || (it * 64 + 64 > Lk) || (i * 128 + 128 > Lq);
-#pragma unroll 1
-      for (int cc = 0; cc < 2; ++cc) {
+      {
+        const int cc = wg;
         uint32_t sv[32], dv[32], ds[16];
         tmem_ld_32x32b_x32(t_s + cc * 32, sv);
         tmem_ld_32x32b_x32(t_s + 64 + cc * 32, dv);
@@ -750,7 +755,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ128, const __grid_con
           }
           ds[e >> 1] = pack_bf16x2(dsv[0], dsv[1]);
         }
-        tmem_st_32x32b_x16(t_s + 64 + cc * 16, ds);
+        tmem_st_32x32b_x16(t_s + 64 + cc * 32, ds);
       }
       tc_wait_st();
       tc_fence_before_sync();
@@ -762,7 +767,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ128, const __grid_con
       const bool valid = qrow < Lq;
       __nv_bfloat16* dqp = p.dq + static_cast<size_t>(q_start + qrow) * p.dqkv_stride + p.q_col0 + h * D;
 #pragma unroll 1
-      for (int c = 0; c < D / 32; ++c) {
+      for (int c = wg; c < D / 32; c += 2) {
         uint32_t v[32];
         tmem_ld_32x32b_x32(t_lane + DQ_COL + c * 32, v);
         tc_wait_ld();

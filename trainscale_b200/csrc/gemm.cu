@@ -261,6 +261,223 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   }
 }
 
+
+// ---------------------------------------------------------------------------------------------------------
+// cta_group::2 variant: a cluster of two CTAs computes one 256 x 256 tile.  Each CTA streams its own 128 rows of A
+// and its own half (128 rows of N) of B, so the shared-memory fill per MMA is 2/3 of the single-CTA kernel's and the
+// ring is 6 stages deep.  The leader (even cluster rank) issues the MMAs for both CTAs; every CTA drains its own
+// 128 accumulator lanes.  Loads are plain tiled loads whose completion is signalled on the leader's barrier.
+// ---------------------------------------------------------------------------------------------------------
+constexpr int G2_STAGES = 6;
+constexpr int G2_STAGE_BYTES = 32768;      // A 128x64 + B-half 128x64, bf16
+constexpr int G2_SMEM = G2_STAGES * G2_STAGE_BYTES + 256 + 1024;
+
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmParams p) {
+  constexpr int STAGES = G2_STAGES;
+  constexpr int BN = 256;
+  constexpr uint32_t TMEM_COLS = 512;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* smem_a = smem;
+  uint8_t* smem_b = smem + STAGES * 16384;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * G2_STAGE_BYTES);
+  uint64_t* full_bar = bars;
+  uint64_t* empty_bar = bars + STAGES;
+  uint64_t* tfull_bar = bars + 2 * STAGES;
+  uint64_t* tempty_bar = bars + 2 * STAGES + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t crank = cluster_ctarank();
+  const bool leader = (crank == 0);
+
+  if (threadIdx.x == 0) {
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);     // leader's copy is the one in use: one arrive.expect_tx, bytes from both CTAs
+      mbar_init(&empty_bar[s], 1);    // one multicast commit per phase
+    }
+    mbar_init(&tfull_bar[0], 1);
+    mbar_init(&tfull_bar[1], 1);
+    mbar_init(&tempty_bar[0], 8);     // 4 epilogue warps of each CTA arrive on the leader's copy
+    mbar_init(&tempty_bar[1], 8);
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc_2cta(tmem_slot, TMEM_COLS);
+    tmem_relinquish_2cta();
+    tc_fence_before_sync();
+  }
+  __syncthreads();
+  cluster_sync_all();                 // the peer's barriers exist before anything signals them
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int m_tiles = (p.M + 255) / 256;
+  const int n_tiles = (p.N + BN - 1) / BN;
+  const int num_tiles = m_tiles * n_tiles;
+  const int tiles_per_group = GEMM_GROUP_M * n_tiles;
+  const int cluster_id = blockIdx.x >> 1, num_clusters = gridDim.x >> 1;
+  bool alive = true;
+
+  auto tile_coords = [&](int t, int& m0, int& n0) {
+    const int g = t / tiles_per_group;
+    const int first_m = g * GEMM_GROUP_M;
+    const int gsz = min(m_tiles - first_m, GEMM_GROUP_M);
+    const int r = t - g * tiles_per_group;
+    m0 = (first_m + (r % gsz)) * 256 + (int)crank * 128;   // this CTA's 128 rows
+    n0 = (r / gsz) * BN;
+  };
+
+  if (warp == 0) {
+    if (elect_one_sync()) {
+      uint32_t it = 0;
+      for (int t = cluster_id; t < num_tiles && alive; t += num_clusters) {
+        int m0, n0;
+        tile_coords(t, m0, n0);
+        const int nb0 = n0 + (int)crank * 128;             // this CTA's half of the B tile
+        for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
+          const int s = it % STAGES;
+          if (!mbar_wait(&empty_bar[s], ((it / STAGES) & 1u) ^ 1u, alive, 110)) break;
+          if (leader) mbar_expect_tx(&full_bar[s], 2 * G2_STAGE_BYTES);
+          uint8_t* a_dst = smem_a + s * 16384;
+          uint8_t* b_dst = smem_b + s * 16384;
+          const int k0 = kb * GEMM_BK;
+          if (!p.a_mn) {
+            tma_load_2d_2cta(a_dst, &tmA, &full_bar[s], k0, m0);
+          } else {
+            tma_load_2d_2cta(a_dst, &tmA, &full_bar[s], m0, k0);
+            tma_load_2d_2cta(a_dst + 8192, &tmA, &full_bar[s], m0 + 64, k0);
+          }
+          if (!p.b_mn) {
+            tma_load_2d_2cta(b_dst, &tmB, &full_bar[s], k0, nb0);
+          } else {
+            tma_load_2d_2cta(b_dst, &tmB, &full_bar[s], nb0, k0);
+            tma_load_2d_2cta(b_dst + 8192, &tmB, &full_bar[s], nb0 + 64, k0);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (leader && elect_one_sync()) {
+      const uint32_t idesc = make_idesc(256, BN, 1, 1, (uint32_t)p.a_mn, (uint32_t)p.b_mn);
+      const uint32_t a_kstep = p.a_mn ? 2048u : 32u;
+      const uint32_t b_kstep = p.b_mn ? 2048u : 32u;
+      const uint32_t a_lbo = p.a_mn ? 8192u : 16u;
+      const uint32_t b_lbo = p.b_mn ? 8192u : 16u;
+      uint32_t it = 0, tile_it = 0;
+      for (int t = cluster_id; t < num_tiles && alive; t += num_clusters, ++tile_it) {
+        const uint32_t acc = tile_it & 1u;
+        if (!mbar_wait(&tempty_bar[acc], ((tile_it >> 1) & 1u) ^ 1u, alive, 210)) break;
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
+          const int s = it % STAGES;
+          if (!mbar_wait(&full_bar[s], (it / STAGES) & 1u, alive, 211)) break;
+          tc_fence_after_sync();
+          const uint32_t a_addr = smem_u32(smem_a + s * 16384);
+          const uint32_t b_addr = smem_u32(smem_b + s * 16384);
+#pragma unroll
+          for (int k = 0; k < GEMM_BK / 16; ++k)
+            umma_f16_ss_2cta(d_tmem, make_smem_desc_sw128(a_addr + k * a_kstep, a_lbo, 1024),
+                             make_smem_desc_sw128(b_addr + k * b_kstep, b_lbo, 1024), idesc, (kb | k) != 0 ? 1u : 0u);
+          umma_commit_2cta_mc(&empty_bar[s], 3);
+        }
+        if (!alive) break;
+        umma_commit_2cta_mc(&tfull_bar[acc], 3);
+      }
+    }
+  } else {
+    const int q = warp & 3;
+    uint32_t tile_it = 0;
+    for (int t = cluster_id; t < num_tiles && alive; t += num_clusters, ++tile_it) {
+      int m0, n0;
+      tile_coords(t, m0, n0);
+      const uint32_t acc = tile_it & 1u;
+      if (!mbar_wait(&tfull_bar[acc], (tile_it >> 1) & 1u, alive, 310)) break;
+      tc_fence_after_sync();
+      const int row = m0 + q * 32 + lane;
+      const uint32_t t_row = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(t_row + c * 32, r);
+        tc_wait_ld();
+        const int col0 = n0 + c * 32;
+        if (row < p.M && col0 < p.N) {
+          const bool full = (col0 + 32 <= p.N);
+          if (p.out_fp32) {
+            float* dst = reinterpret_cast<float*>(p.C) + static_cast<size_t>(row) * p.ldc + col0;
+            for (int j = 0; j < 32 && (full || col0 + j < p.N); ++j) {
+              float v = __uint_as_float(r[j]) * p.alpha;
+              if (p.accumulate) v += dst[j];
+              dst[j] = v;
+            }
+          } else {
+            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<size_t>(row) * p.ldc + col0;
+            if (full && !p.accumulate && ((reinterpret_cast<uintptr_t>(dst) & 15u) == 0)) {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                uint4 v;
+                v.x = pack_bf16x2(__uint_as_float(r[8 * j]) * p.alpha, __uint_as_float(r[8 * j + 1]) * p.alpha);
+                v.y = pack_bf16x2(__uint_as_float(r[8 * j + 2]) * p.alpha, __uint_as_float(r[8 * j + 3]) * p.alpha);
+                v.z = pack_bf16x2(__uint_as_float(r[8 * j + 4]) * p.alpha, __uint_as_float(r[8 * j + 5]) * p.alpha);
+                v.w = pack_bf16x2(__uint_as_float(r[8 * j + 6]) * p.alpha, __uint_as_float(r[8 * j + 7]) * p.alpha);
+                *reinterpret_cast<uint4*>(dst + 8 * j) = v;
+              }
+            } else {
+              for (int j = 0; j < 32 && col0 + j < p.N; ++j) {
+                float v = __uint_as_float(r[j]) * p.alpha;
+                if (p.accumulate) v += __bfloat162float(dst[j]);
+                dst[j] = __float2bfloat16(v);
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(&tempty_bar[acc], 0);   // the leader's MMA thread owns the accumulators
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();   // nobody leaves (or frees TMEM) while the peer may still signal or read
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc_2cta(tmem_base, TMEM_COLS);
+  }
+}
+
+static int launch_gemm_2cta(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, cudaStream_t stream) {
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_2cta_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, G2_SMEM);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  const int tiles = ((p.M + 255) / 256) * ((p.N + 255) / 256);
+  int clusters = sm_count() / 2;
+  if (tiles < clusters) clusters = tiles;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(clusters * 2);
+  cfg.blockDim = dim3(GEMM_THREADS);
+  cfg.dynamicSmemBytes = G2_SMEM;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return (int)cudaLaunchKernelEx(&cfg, gemm_bf16_2cta_kernel, tmA, tmB, p);
+}
+
 template <int BN>
 static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, cudaStream_t stream) {
   static bool configured = false;
@@ -295,7 +512,11 @@ extern "C" int ts_gemm_bf16(const void* A, const void* B, void* C, int M, int N,
     const int tiles256 = ((M + 127) / 128) * ((N + 255) / 256);
     bn = (N >= 256 && tiles256 >= sm_count()) ? 256 : (N >= 128 ? 128 : 64);
     if (N >= 256 && tiles256 < sm_count() && ((M + 127) / 128) * ((N + 127) / 128) < tiles256 * 2) bn = 128;
+    // the paired-CTA kernel wins whenever every CTA pair gets at least one 256 x 256 tile
+    if (N >= 256 && M >= 256 && ((M + 255) / 256) * ((N + 255) / 256) >= sm_count() / 2) bn = 512;
   }
+  const bool two_cta = (bn == 512);
+  if (two_cta) bn = 128;   // per-CTA B box: 128 rows of N
   if (bn != 256 && bn != 128 && bn != 64) return -11;
   CUtensorMap tmA, tmB;
   int rc;
@@ -316,6 +537,7 @@ extern "C" int ts_gemm_bf16(const void* A, const void* B, void* C, int M, int N,
   p.num_n_tiles = (N + bn - 1) / bn;
   p.k_blocks = (K + GEMM_BK - 1) / GEMM_BK;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (two_cta) return launch_gemm_2cta(tmA, tmB, p, st);
   if (bn == 256) return launch_gemm<256>(tmA, tmB, p, st);
   if (bn == 128) return launch_gemm<128>(tmA, tmB, p, st);
   return launch_gemm<64>(tmA, tmB, p, st);
