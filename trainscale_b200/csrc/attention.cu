@@ -87,15 +87,16 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int h = blockIdx.y, b = blockIdx.z;
+  // grid: x = head + heads * batch (fastest), y = tile: the whole grid is dispatched longest-tile-first
+  const int h = blockIdx.x % p.Hq, b = blockIdx.x / p.Hq;
   const int hk = h / p.group;
   int q_start, Lq, k_start, Lk;
   seq_bounds(p, b, q_start, Lq);
   k_start = q_start;
   Lk = Lq;
   const int n_qblocks = (Lq + 255) / 256;
-  if ((int)blockIdx.x >= n_qblocks) return;
-  const int qb = n_qblocks - 1 - blockIdx.x;   // heaviest (latest) causal blocks first
+  if ((int)blockIdx.y >= n_qblocks) return;
+  const int qb = n_qblocks - 1 - blockIdx.y;   // heaviest (latest) causal blocks first
   const int off = Lk - Lq;
   int r0[2], nkv[2];
 #pragma unroll
@@ -224,60 +225,60 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       const int c0 = i * 128;
       const bool need_mask = (p.causal && (c0 + 127 > r0[t] + off)) || (c0 + 128 > Lk);
       const int limit = p.causal ? min(Lk - 1, row + off) : Lk - 1;   // last visible column
-      // pass 1: row max
-      float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32b_x32(t_s + c * 32, v);
-        tc_wait_ld();
-        if (need_mask) {
+      // the thread's whole row of S (128 columns) comes into registers once
+      uint32_t v[128];
 #pragma unroll
-          for (int j = 0; j < 32; ++j)
-            if (c0 + c * 32 + j <= limit) mx = fmaxf(mx, __uint_as_float(v[j]));
-        } else {
+      for (int c = 0; c < 4; ++c) tmem_ld_32x32b_x32(t_s + c * 32, v + c * 32);
+      tc_wait_ld();
+      float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+      if (need_mask) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) mx = fmaxf(mx, __uint_as_float(v[j]));
-        }
+        for (int j = 0; j < 128; ++j)
+          if (c0 + j > limit) v[j] = 0xff800000u;   // -inf: drops out of the max and gives exp2 = 0
       }
+#pragma unroll
+      for (int j = 0; j < 128; j += 4) {
+        mx0 = fmaxf(mx0, __uint_as_float(v[j]));
+        mx1 = fmaxf(mx1, __uint_as_float(v[j + 1]));
+        mx2 = fmaxf(mx2, __uint_as_float(v[j + 2]));
+        mx3 = fmaxf(mx3, __uint_as_float(v[j + 3]));
+      }
+      const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
       const float m_new = fmaxf(m_used, mx * p.scale_log2);
       const bool grow = (m_new - m_used > 8.0f);   // also true on the first block (m_used = -inf)
       if (__any_sync(0xffffffffu, grow)) {
-        const float alpha = (m_used == -INFINITY) ? 0.f : exp2f(m_used - m_new);
+        const float alpha = (m_used == -INFINITY) ? 0.f : fast_ex2(m_used - m_new);
         m_used = m_new;
         l *= alpha;
         if (i > 0) {
 #pragma unroll 1
-          for (int c = 0; c < D / 32; ++c) {
-            uint32_t v[32];
-            tmem_ld_32x32b_x32(t_o + c * 32, v);
+          for (int c = 0; c < D / 16; ++c) {
+            uint32_t o[16];
+            tmem_ld_32x32b_x16(t_o + c * 16, o);
             tc_wait_ld();
 #pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * alpha);
-            tmem_st_32x32b_x32(t_o + c * 32, v);
+            for (int j = 0; j < 16; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * alpha);
+            tmem_st_32x32b_x16(t_o + c * 16, o);
           }
         }
       }
       const float m_sub = (m_used == -INFINITY) ? 0.f : m_used;
-      // pass 2: P = exp2(S*scale - m), packed bf16 written over the first 64 columns of S
-#pragma unroll 1
+      // P = exp2(S*scale - m), packed bf16 written over the first 64 columns of S
+      float l0 = 0.f, l1 = 0.f;
+#pragma unroll
       for (int c = 0; c < 4; ++c) {
-        uint32_t v[32], pk[16];
-        tmem_ld_32x32b_x32(t_s + c * 32, v);
-        tc_wait_ld();
+        uint32_t pk[16];
 #pragma unroll
         for (int j = 0; j < 32; j += 2) {
-          float p0 = exp2f(fmaf(__uint_as_float(v[j]), p.scale_log2, -m_sub));
-          float p1 = exp2f(fmaf(__uint_as_float(v[j + 1]), p.scale_log2, -m_sub));
-          if (need_mask) {
-            if (c0 + c * 32 + j > limit) p0 = 0.f;
-            if (c0 + c * 32 + j + 1 > limit) p1 = 0.f;
-          }
-          l += p0 + p1;
+          const float p0 = fast_ex2(fmaf(__uint_as_float(v[c * 32 + j]), p.scale_log2, -m_sub));
+          const float p1 = fast_ex2(fmaf(__uint_as_float(v[c * 32 + j + 1]), p.scale_log2, -m_sub));
+          l0 += p0;
+          l1 += p1;
           pk[j >> 1] = pack_bf16x2(p0, p1);
         }
         tmem_st_32x32b_x16(t_s + c * 16, pk);
       }
+      l += l0 + l1;
       tc_wait_st();
       tc_fence_before_sync();
       __syncwarp();
@@ -348,7 +349,7 @@ template <int D>
 struct BwdSmem {
   static constexpr int BIG = 128 * D * 2;     // resident 128-row tile
   static constexpr int SMALL = 64 * D * 2;    // streamed 64-row tile
-  static constexpr int STAGES = 3;
+  static constexpr int STAGES = (D == 128) ? 5 : 6;   // deep ring: the streamed tiles' L2 latency must hide behind 2+ iterations
   static constexpr int A_OFF = 0;             // resident tile 0 (K or Q)
   static constexpr int B_OFF = BIG;           // resident tile 1 (V or dO)
   static constexpr int S0_OFF = 2 * BIG;      // streamed tile 0 ring (Q or K)
@@ -380,15 +381,16 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_co
   float* vec = reinterpret_cast<float*>(smem + SM::VEC_OFF);   // [2][128]: lse2[64], delta[64]
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SM::BAR_OFF);
   uint64_t* kv_full = bars;            // [1]
-  uint64_t* qd_full = bars + 1;        // [3]
-  uint64_t* qd_empty = bars + 4;       // [3]
-  uint64_t* s_full = bars + 7;         // [2]
-  uint64_t* p_full = bars + 9;         // [2]
-  uint64_t* acc_full = bars + 11;      // [1]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
+  uint64_t* s_full = bars + 1;         // [2]
+  uint64_t* p_full = bars + 3;         // [2]
+  uint64_t* acc_full = bars + 5;       // [1]
+  uint64_t* qd_full = bars + 6;        // [STAGES]
+  uint64_t* qd_empty = bars + 6 + SM::STAGES;   // [STAGES]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 6 + 2 * SM::STAGES);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int j = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+  // grid: x = kv head + kv heads * batch (fastest), y = kv tile; low tiles see the most queries and go first
+  const int j = blockIdx.y, hk = blockIdx.x % p.Hkv, b = blockIdx.x / p.Hkv;
   int q_start, Lq;
   seq_bounds(p, b, q_start, Lq);
   const int k_start = q_start, Lk = Lq;
@@ -404,7 +406,7 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_co
     tma_prefetch_desc(&tmK128);
     tma_prefetch_desc(&tmV128);
     tma_prefetch_desc(&tmdO64);
-    for (int i = 0; i < 12; ++i) mbar_init(&bars[i], (i == 9 || i == 10) ? 8 : 1);
+    for (int i = 0; i < 6 + 2 * SM::STAGES; ++i) mbar_init(&bars[i], (i == 3 || i == 4) ? 8 : 1);
     fence_barrier_init();
   }
   if (warp == 1) {
@@ -512,7 +514,7 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_co
     for (int it = 0; it < total && alive; ++it) {
       const int u = u_start + it % per_head;
       float* vb = vec + (it & 1) * 128;
-      if (ct < 128) vb[ct] = nxt;
+      if (ct < 128) vb[(ct & 63) * 2 + (ct >> 6)] = nxt;   // (lse2, delta) pairs per column
       if (it + 1 < total) nxt = fetch_vec(it + 1);
       named_bar_sync(1, 256);
       if (!mbar_wait(&s_full[it & 1], (it >> 1) & 1u, alive, 720)) break;
@@ -528,17 +530,19 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_co
 #pragma unroll
         for (int e = 0; e < 32; e += 2) {
           float pv[2], dsv[2];
+          const float4 ld4 = *reinterpret_cast<const float4*>(vb + 2 * (cc * 32 + e));   // warp-wide broadcast
+          const float lsev[2] = {ld4.x, ld4.z}, delv[2] = {ld4.y, ld4.w};
 #pragma unroll
           for (int x = 0; x < 2; ++x) {
             const int c = cc * 32 + e + x;
-            float pe = exp2f(fmaf(__uint_as_float(sv[e + x]), p.scale_log2, -vb[c]));
+            float pe = fast_ex2(fmaf(__uint_as_float(sv[e + x]), p.scale_log2, -lsev[x]));
             if (need_mask) {
               const int qrow = u * 64 + c;
               const bool ok = (kv_row < Lk) && (qrow < Lq) && (!p.causal || kv_row <= qrow + off);
               if (!ok) pe = 0.f;
             }
             pv[x] = pe;
-            dsv[x] = pe * (__uint_as_float(dv[e + x]) - vb[64 + c]);
+            dsv[x] = pe * (__uint_as_float(dv[e + x]) - delv[x]);
           }
           pp[e >> 1] = pack_bf16x2(pv[0], pv[1]);
           ds[e >> 1] = pack_bf16x2(dsv[0], dsv[1]);
@@ -616,22 +620,23 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ128, const __grid_con
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SM::BAR_OFF);
   uint64_t* q_full = bars;             // [1]
-  uint64_t* kv_full = bars + 1;        // [3]
-  uint64_t* kv_empty = bars + 4;       // [3]
-  uint64_t* s_full = bars + 7;         // [2]
-  uint64_t* p_full = bars + 9;         // [2]
-  uint64_t* acc_full = bars + 11;      // [1]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
+  uint64_t* s_full = bars + 1;         // [2]
+  uint64_t* p_full = bars + 3;         // [2]
+  uint64_t* acc_full = bars + 5;       // [1]
+  uint64_t* kv_full = bars + 6;        // [STAGES]
+  uint64_t* kv_empty = bars + 6 + SM::STAGES;   // [STAGES]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 6 + 2 * SM::STAGES);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int h = blockIdx.y, b = blockIdx.z;
+  // grid: x = head + heads * batch (fastest), y = tile: the whole grid is dispatched longest-tile-first
+  const int h = blockIdx.x % p.Hq, b = blockIdx.x / p.Hq;
   const int hk = h / p.group;
   int q_start, Lq;
   seq_bounds(p, b, q_start, Lq);
   const int k_start = q_start, Lk = Lq;
   const int n_qt = (Lq + 127) / 128;
-  if ((int)blockIdx.x >= n_qt) return;
-  const int i = n_qt - 1 - blockIdx.x;
+  if ((int)blockIdx.y >= n_qt) return;
+  const int i = n_qt - 1 - blockIdx.y;
   const int off = Lk - Lq;
   const int kv_end = p.causal ? min(Lk, i * 128 + 128 + off) : Lk;
   const int total = (kv_end + 63) / 64;
@@ -641,7 +646,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ128, const __grid_con
     tma_prefetch_desc(&tmK64);
     tma_prefetch_desc(&tmV64);
     tma_prefetch_desc(&tmdO128);
-    for (int x = 0; x < 12; ++x) mbar_init(&bars[x], (x == 9 || x == 10) ? 8 : 1);
+    for (int x = 0; x < 6 + 2 * SM::STAGES; ++x) mbar_init(&bars[x], (x == 3 || x == 4) ? 8 : 1);
     fence_barrier_init();
   }
   if (warp == 1) {
@@ -749,7 +754,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ128, const __grid_con
           float dsv[2];
 #pragma unroll
           for (int x = 0; x < 2; ++x) {
-            float pe = exp2f(fmaf(__uint_as_float(sv[e + x]), p.scale_log2, -lse2));
+            float pe = fast_ex2(fmaf(__uint_as_float(sv[e + x]), p.scale_log2, -lse2));
             if (need_mask && (it * 64 + cc * 32 + e + x > limit)) pe = 0.f;
             dsv[x] = pe * (__uint_as_float(dv[e + x]) - delta);
           }
@@ -805,9 +810,9 @@ static int launch_bwd(const CUtensorMap* m, const AttnParams& p, int max_len, cu
     configured = true;
   }
   // m: [0]=q64 [1]=k128 [2]=v128 [3]=do64 [4]=q128 [5]=k64 [6]=v64 [7]=do128
-  dim3 g1((max_len + 127) / 128, p.Hkv, p.B);
+  dim3 g1(p.Hkv * p.B, (max_len + 127) / 128, 1);
   flash_bwd_dkdv_kernel<D><<<g1, BWD_THREADS, BwdSmem<D>::TOTAL, st>>>(m[0], m[1], m[2], m[3], p);
-  dim3 g2((max_len + 127) / 128, p.Hq, p.B);
+  dim3 g2(p.Hq * p.B, (max_len + 127) / 128, 1);
   flash_bwd_dq_kernel<D><<<g2, BWD_THREADS, BwdSmem<D>::TOTAL, st>>>(m[4], m[5], m[6], m[7], p);
   return (int)cudaGetLastError();
 }
@@ -822,7 +827,7 @@ static int launch_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtens
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  dim3 grid((max_len + 255) / 256, p.Hq, p.B);
+  dim3 grid(p.Hq * p.B, (max_len + 255) / 256, 1);
   flash_fwd_kernel<D><<<grid, FWD_THREADS, FwdSmem<D>::TOTAL, st>>>(tq, tk, tv, p);
   return (int)cudaGetLastError();
 }
