@@ -11,6 +11,7 @@
 // tiles of its head group; one owns a Q tile and accumulates dQ over the K/V tiles.  No atomics, deterministic.
 //
 // Replaces data_pipeline/trainer/kernels/flash_attention.py:147-560 (Triton forward, dq and dk/dv kernels).
+#include <type_traits>
 #include "common.cuh"
 #include "host_common.h"
 
@@ -349,13 +350,13 @@ template <int D>
 struct BwdSmem {
   static constexpr int BIG = 128 * D * 2;     // resident 128-row tile
   static constexpr int SMALL = 64 * D * 2;    // streamed 64-row tile
-  static constexpr int STAGES = (D == 128) ? 5 : 6;   // deep ring: the streamed tiles' L2 latency must hide behind 2+ iterations
+  static constexpr int STAGES = 4;
   static constexpr int A_OFF = 0;             // resident tile 0 (K or Q)
   static constexpr int B_OFF = BIG;           // resident tile 1 (V or dO)
   static constexpr int S0_OFF = 2 * BIG;      // streamed tile 0 ring (Q or K)
   static constexpr int S1_OFF = S0_OFF + STAGES * SMALL;   // streamed tile 1 ring (dO or V)
-  static constexpr int VEC_OFF = S1_OFF + STAGES * SMALL;  // 2 x (64 lse + 64 delta) floats
-  static constexpr int BAR_OFF = VEC_OFF + 1024;
+  static constexpr int VEC_OFF = S1_OFF + STAGES * SMALL;  // per stage: 64 x (lse * log2e, delta) float pairs
+  static constexpr int BAR_OFF = VEC_OFF + STAGES * 512;
   static constexpr int TOTAL = BAR_OFF + 256 + 1024;
 };
 
@@ -378,7 +379,7 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_co
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  float* vec = reinterpret_cast<float*>(smem + SM::VEC_OFF);   // [2][128]: lse2[64], delta[64]
+  float* vec = reinterpret_cast<float*>(smem + SM::VEC_OFF);   // [STAGES][64] (lse * log2e, delta) pairs
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SM::BAR_OFF);
   uint64_t* kv_full = bars;            // [1]
   uint64_t* s_full = bars + 1;         // [2]
@@ -406,7 +407,8 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_co
     tma_prefetch_desc(&tmK128);
     tma_prefetch_desc(&tmV128);
     tma_prefetch_desc(&tmdO64);
-    for (int i = 0; i < 6 + 2 * SM::STAGES; ++i) mbar_init(&bars[i], (i == 3 || i == 4) ? 8 : 1);
+    for (int i = 0; i < 6 + 2 * SM::STAGES; ++i)
+      mbar_init(&bars[i], (i == 3 || i == 4) ? 8 : ((i >= 6 && i < 6 + SM::STAGES) ? 2 : 1));
     fence_barrier_init();
   }
   if (warp == 1) {
@@ -420,19 +422,32 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_co
   bool alive = true;
 
   if (warp == 0) {
-    if (elect_one_sync()) {
+    // the whole warp runs the producer loop: lane 0 issues the tiled loads, every lane brings two columns'
+    // (lse * log2e, delta) pairs of the sub-tile into the stage's vector buffer (fetched one stage ahead)
+    if (lane == 0) {
       mbar_expect_tx(kv_full, 2 * SM::BIG);
 #pragma unroll
       for (int c = 0; c < DCH; ++c) {
         tma_load_2d(smem + SM::A_OFF + c * 16384, &tmK128, kv_full, p.k_col0 + hk * D + c * 64, k_start + j * 128);
         tma_load_2d(smem + SM::B_OFF + c * 16384, &tmV128, kv_full, p.v_col0 + hk * D + c * 64, k_start + j * 128);
       }
-      for (int it = 0; it < total && alive; ++it) {
-        const int s = it % STAGES;
-        const uint32_t ph = (it / STAGES) & 1u;
-        const int g = it / per_head, u = u_start + it % per_head;
-        const int h = hk * p.group + g;
-        if (!mbar_wait(&qd_empty[s], ph ^ 1u, alive, 700)) break;
+    }
+    auto fetch_vec = [&](int it, int col) -> float2 {
+      const int g = it / per_head, u = u_start + it % per_head;
+      const int h = hk * p.group + g;
+      const int qrow = u * 64 + col;
+      if (it >= total || qrow >= Lq) return make_float2(0.f, 0.f);
+      const size_t idx = static_cast<size_t>(h) * p.total_rows + q_start + qrow;
+      return make_float2(p.lse[idx] * 1.4426950408889634f, p.delta[idx]);
+    };
+    float2 n0 = fetch_vec(0, lane), n1 = fetch_vec(0, lane + 32);
+    for (int it = 0; it < total && alive; ++it) {
+      const int s = it % STAGES;
+      const uint32_t ph = (it / STAGES) & 1u;
+      const int g = it / per_head, u = u_start + it % per_head;
+      const int h = hk * p.group + g;
+      if (!mbar_wait(&qd_empty[s], ph ^ 1u, alive, 700)) break;
+      if (lane == 0) {
         mbar_expect_tx(&qd_full[s], 2 * SM::SMALL);
 #pragma unroll
         for (int c = 0; c < DCH; ++c) {
@@ -442,6 +457,13 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_co
                       q_start + u * 64);
         }
       }
+      float2* vb2 = reinterpret_cast<float2*>(vec + s * 128);
+      vb2[lane] = n0;
+      vb2[lane + 32] = n1;
+      n0 = fetch_vec(it + 1, lane);
+      n1 = fetch_vec(it + 1, lane + 32);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&qd_full[s]);   // second arrival of the phase: the vectors are in place
     }
   } else if (warp == 1) {
     if (elect_one_sync()) {
@@ -497,26 +519,12 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_co
     const int q4 = warp & 3;
     const int wg = (warp - 2) >> 2;          // compute warpgroup: owns query columns [wg*32, wg*32+32) of the sub-tile
     const int r = q4 * 32 + lane;            // kv row inside the tile
-    const int ct = threadIdx.x - 64;         // 0..255 among the compute threads
     const int kv_row = j * 128 + r;
     const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(q4 * 32) << 16);
-    // per-column (lse * log2e, delta) pairs of the next sub-tile are fetched one iteration ahead
-    auto fetch_vec = [&](int it) -> float {
-      const int g = it / per_head, u = u_start + it % per_head;
-      const int h = hk * p.group + g;
-      const int c = ct & 63;
-      const int qrow = u * 64 + c;
-      if (ct >= 128 || qrow >= Lq) return 0.f;
-      const size_t idx = static_cast<size_t>(h) * p.total_rows + q_start + qrow;
-      return (ct < 64) ? p.lse[idx] * 1.4426950408889634f : p.delta[idx];
-    };
-    float nxt = total > 0 ? fetch_vec(0) : 0.f;
     for (int it = 0; it < total && alive; ++it) {
       const int u = u_start + it % per_head;
-      float* vb = vec + (it & 1) * 128;
-      if (ct < 128) vb[(ct & 63) * 2 + (ct >> 6)] = nxt;   // (lse2, delta) pairs per column
-      if (it + 1 < total) nxt = fetch_vec(it + 1);
-      named_bar_sync(1, 256);
+      // written by the producer warp before its arrival on qd_full, which the MMA thread observed before s_full
+      const float* vb = vec + (it % STAGES) * 128;
       if (!mbar_wait(&s_full[it & 1], (it >> 1) & 1u, alive, 720)) break;
       tc_fence_after_sync();
       const uint32_t t_s = t_lane + (it & 1) * 128;
@@ -527,26 +535,25 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_co
         tmem_ld_32x32b_x32(t_s + cc * 32, sv);
         tmem_ld_32x32b_x32(t_s + 64 + cc * 32, dv);
         tc_wait_ld();
+        // the masked and the unmasked tile bodies are separate straight-line code: a per-element branch would
+        // serialise the 32 independent exp chains
+        auto body = [&](auto masked) {
 #pragma unroll
-        for (int e = 0; e < 32; e += 2) {
-          float pv[2], dsv[2];
-          const float4 ld4 = *reinterpret_cast<const float4*>(vb + 2 * (cc * 32 + e));   // warp-wide broadcast
-          const float lsev[2] = {ld4.x, ld4.z}, delv[2] = {ld4.y, ld4.w};
-#pragma unroll
-          for (int x = 0; x < 2; ++x) {
-            const int c = cc * 32 + e + x;
-            float pe = fast_ex2(fmaf(__uint_as_float(sv[e + x]), p.scale_log2, -lsev[x]));
-            if (need_mask) {
-              const int qrow = u * 64 + c;
-              const bool ok = (kv_row < Lk) && (qrow < Lq) && (!p.causal || kv_row <= qrow + off);
-              if (!ok) pe = 0.f;
+          for (int e = 0; e < 32; e += 2) {
+            const float4 ld4 = *reinterpret_cast<const float4*>(vb + 2 * (cc * 32 + e));   // warp-wide broadcast
+            float p0 = fast_ex2(fmaf(__uint_as_float(sv[e]), p.scale_log2, -ld4.x));
+            float p1 = fast_ex2(fmaf(__uint_as_float(sv[e + 1]), p.scale_log2, -ld4.z));
+            if constexpr (decltype(masked)::value) {
+              const int qrow = u * 64 + cc * 32 + e;
+              const bool rok = kv_row < Lk;
+              p0 = (rok && qrow < Lq && (!p.causal || kv_row <= qrow + off)) ? p0 : 0.f;
+              p1 = (rok && qrow + 1 < Lq && (!p.causal || kv_row <= qrow + 1 + off)) ? p1 : 0.f;
             }
-            pv[x] = pe;
-            dsv[x] = pe * (__uint_as_float(dv[e + x]) - delv[x]);
+            pp[e >> 1] = pack_bf16x2(p0, p1);
+            ds[e >> 1] = pack_bf16x2(p0 * (__uint_as_float(dv[e]) - ld4.y), p1 * (__uint_as_float(dv[e + 1]) - ld4.w));
           }
-          pp[e >> 1] = pack_bf16x2(pv[0], pv[1]);
-          ds[e >> 1] = pack_bf16x2(dsv[0], dsv[1]);
-        }
+        };
+        if (need_mask) body(std::true_type{}); else body(std::false_type{});
         // each warpgroup overwrites only columns of its own (already consumed) chunk
         tmem_st_32x32b_x16(t_s + cc * 32, pp);
         tmem_st_32x32b_x16(t_s + 64 + cc * 32, ds);
@@ -749,17 +756,20 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ128, const __grid_con
         tmem_ld_32x32b_x32(t_s + cc * 32, sv);
         tmem_ld_32x32b_x32(t_s + 64 + cc * 32, dv);
         tc_wait_ld();
+        auto body = [&](auto masked) {
 #pragma unroll
-        for (int e = 0; e < 32; e += 2) {
-          float dsv[2];
-#pragma unroll
-          for (int x = 0; x < 2; ++x) {
-            float pe = fast_ex2(fmaf(__uint_as_float(sv[e + x]), p.scale_log2, -lse2));
-            if (need_mask && (it * 64 + cc * 32 + e + x > limit)) pe = 0.f;
-            dsv[x] = pe * (__uint_as_float(dv[e + x]) - delta);
+          for (int e = 0; e < 32; e += 2) {
+            float p0 = fast_ex2(fmaf(__uint_as_float(sv[e]), p.scale_log2, -lse2));
+            float p1 = fast_ex2(fmaf(__uint_as_float(sv[e + 1]), p.scale_log2, -lse2));
+            if constexpr (decltype(masked)::value) {
+              const int col = it * 64 + cc * 32 + e;
+              p0 = (col <= limit) ? p0 : 0.f;
+              p1 = (col + 1 <= limit) ? p1 : 0.f;
+            }
+            ds[e >> 1] = pack_bf16x2(p0 * (__uint_as_float(dv[e]) - delta), p1 * (__uint_as_float(dv[e + 1]) - delta));
           }
-          ds[e >> 1] = pack_bf16x2(dsv[0], dsv[1]);
-        }
+        };
+        if (need_mask) body(std::true_type{}); else body(std::false_type{});
         tmem_st_32x32b_x16(t_s + 64 + cc * 32, ds);
       }
       tc_wait_st();
