@@ -19,7 +19,7 @@ import torch
 import torch.nn as nn
 from torch.utils.checkpoint import checkpoint
 
-from ..ops import activation, attention, cross_entropy, gemm, norm, rope
+from ..ops import activation, attention, cross_entropy, fused_blocks, gemm, norm, rope
 
 
 @dataclass
@@ -132,9 +132,12 @@ class LlamaAttention(nn.Module):
         self.cp_group = None  # context-parallel process group (ring attention) when set
 
     def forward(self, x, cos, sin, position_ids=None, cu_seqlens=None, doc_ids=None, kv_cache=None):
-        qkv = _lin(self, x, "wqkv")
+        return self.attend(_lin(self, x, "wqkv"), cos, sin, position_ids, cu_seqlens, doc_ids, kv_cache)
+
+    def attend(self, qkv, cos, sin, position_ids=None, cu_seqlens=None, doc_ids=None, kv_cache=None):
+        """Everything after the fused q|k|v projection: rotary embedding, attention, output projection."""
         offset = 0 if kv_cache is None else kv_cache.seq_len
-        qkv = rope.apply_rope_qkv(qkv, self.n_heads + self.n_kv, self.hd, cos, sin, position_ids, x.shape[-2], offset,
+        qkv = rope.apply_rope_qkv(qkv, self.n_heads + self.n_kv, self.hd, cos, sin, position_ids, qkv.shape[-2], offset,
                                   self.cfg.rope_interleaved)
         if kv_cache is not None:
             o = kv_cache.attend(qkv, self)
@@ -166,8 +169,16 @@ class LlamaDecoderLayer(nn.Module):
         self.self_attn = LlamaAttention(cfg)
         self.post_attention_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps)
         self.mlp = LlamaMLP(cfg)
+        self.op_selective = False   # keep only GEMM-side tensors; norm / GLU outputs are rebuilt in backward
 
     def forward(self, x, residual, cos, sin, position_ids=None, cu_seqlens=None, doc_ids=None, kv_cache=None):
+        if self.op_selective and self.training and kv_cache is None and self.self_attn.lora is None \
+                and self.mlp.lora is None:
+            n1, n2 = self.input_layernorm, self.post_attention_layernorm
+            qkv, residual = fused_blocks.norm_linear(x, residual, n1.weight, self.self_attn.wqkv, n1.eps)
+            a = self.self_attn.attend(qkv, cos, sin, position_ids, cu_seqlens, doc_ids, None)
+            gu, residual = fused_blocks.norm_linear(a, residual, n2.weight, self.mlp.w_gate_up, n2.eps)
+            return fused_blocks.glu_linear(gu, self.mlp.w_down, self.mlp.act), residual
         h, residual = self.input_layernorm(x, residual)
         a = self.self_attn(h, cos, sin, position_ids, cu_seqlens, doc_ids, kv_cache)
         h, residual = self.post_attention_layernorm(a, residual)
@@ -275,6 +286,12 @@ class LlamaForCausalLM(nn.Module):
     def gradient_checkpointing_enable(self, every: int = 1):
         self.model.gradient_checkpointing = True
         self.model.checkpoint_every = max(1, every)
+
+    def op_selective_recompute(self, enabled: bool = True):
+        """Operator-level selective recomputation: no layer is re-run, but norm and GLU outputs are rebuilt in
+        backward instead of stored (see ops/fused_blocks.py)."""
+        for layer in self.model.layers:
+            layer.op_selective = enabled
 
     def gradient_checkpointing_disable(self):
         self.model.gradient_checkpointing = False

@@ -20,17 +20,33 @@ def glu_reference(gate_up: torch.Tensor, act: str = "silu") -> torch.Tensor:
     return (a * u).to(gate_up.dtype)
 
 
+def glu_fwd_raw(gu, act_id: int):
+    """gu: contiguous [rows, 2I] bf16 -> [rows, I]."""
+    lib = _lib.load("elementwise")
+    I = gu.shape[1] // 2
+    out = torch.empty(gu.shape[0], I, dtype=gu.dtype, device=gu.device)
+    rc = lib.ts_glu_fwd(_lib.ptr(gu), _lib.ptr(out), ctypes.c_longlong(gu.shape[0]), I, 2 * I, act_id, _lib.stream_ptr())
+    _lib.check(rc, "ts_glu_fwd")
+    return out
+
+
+def glu_bwd_raw(d, gu, act_id: int):
+    lib = _lib.load("elementwise")
+    I = gu.shape[1] // 2
+    dgu = torch.empty_like(gu)
+    rc = lib.ts_glu_bwd(_lib.ptr(d), _lib.ptr(gu), _lib.ptr(dgu), ctypes.c_longlong(gu.shape[0]), I, 2 * I, act_id,
+                        _lib.stream_ptr())
+    _lib.check(rc, "ts_glu_bwd")
+    return dgu
+
+
 class _GluFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, gate_up, act):
-        lib = _lib.load("elementwise")
         I = gate_up.shape[-1] // 2
         gu = gate_up.reshape(-1, 2 * I)
         gu = gu if gu.is_contiguous() else gu.contiguous()
-        out = torch.empty(gu.shape[0], I, dtype=gu.dtype, device=gu.device)
-        rc = lib.ts_glu_fwd(_lib.ptr(gu), _lib.ptr(out), ctypes.c_longlong(gu.shape[0]), I, 2 * I, act,
-                            _lib.stream_ptr())
-        _lib.check(rc, "ts_glu_fwd")
+        out = glu_fwd_raw(gu, act)
         ctx.save_for_backward(gu)
         ctx.act = act
         ctx.in_shape = gate_up.shape
@@ -38,16 +54,11 @@ class _GluFn(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dout):
-        lib = _lib.load("elementwise")
         (gu,) = ctx.saved_tensors
         I = gu.shape[1] // 2
         d = dout.reshape(-1, I)
         d = d if d.is_contiguous() else d.contiguous()
-        dgu = torch.empty_like(gu)
-        rc = lib.ts_glu_bwd(_lib.ptr(d), _lib.ptr(gu), _lib.ptr(dgu), ctypes.c_longlong(gu.shape[0]), I, 2 * I,
-                            ctx.act, _lib.stream_ptr())
-        _lib.check(rc, "ts_glu_bwd")
-        return dgu.view(ctx.in_shape), None
+        return glu_bwd_raw(d, gu, ctx.act).view(ctx.in_shape), None
 
 
 def glu(gate_up: torch.Tensor, act: str = "silu") -> torch.Tensor:

@@ -139,6 +139,26 @@ def _accumulate_wgrad(dy2, x, w):
     w.grad = g if w.grad is None else w.grad + g
 
 
+def linear_bwd(dy, x, w, need_dx: bool = True, need_dw: bool = True):
+    """Backward of y = x @ w^T on the tcgen05 kernels. Returns (dx, dw); dw is None when the weight gradient was
+    accumulated into `w.main_grad` by the GEMM epilogue or parked on the active `WgradQueue`."""
+    dy2 = _rows2d(dy)
+    dx = dw = None
+    if need_dx:
+        dx = matmul_nn(dy2, w).view_as(x)
+    if need_dw and WgradQueue._active is not None:
+        WgradQueue._active.push(dy2, x, w)
+    elif need_dw:
+        main_grad = getattr(w, "main_grad", None)
+        if main_grad is not None:
+            # gradient accumulated straight into the owner's buffer (fp32 or bf16) by the epilogue
+            matmul_tn(dy2, x, out=main_grad.view(w.shape), accumulate=getattr(w, "grad_added", False))
+            w.grad_added = True
+        else:
+            dw = matmul_tn(dy2, x)
+    return dx, dw
+
+
 class _LinearFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w):
@@ -149,22 +169,7 @@ class _LinearFn(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dy):
         x, w = ctx.saved_tensors
-        dy2 = _rows2d(dy)
-        dx = dw = None
-        if ctx.needs_input_grad[0]:
-            dx = matmul_nn(dy2, w).view_as(x)
-        if ctx.needs_input_grad[1] and WgradQueue._active is not None:
-            WgradQueue._active.push(dy2, x, w)
-        elif ctx.needs_input_grad[1]:
-            main_grad = getattr(w, "main_grad", None)
-            if main_grad is not None:
-                # gradient accumulated straight into the owner's buffer (fp32 or bf16) by the epilogue
-                matmul_tn(dy2, x, out=main_grad.view(w.shape), accumulate=getattr(w, "grad_added", False))
-                w.grad_added = True
-                dw = None
-            else:
-                dw = matmul_tn(dy2, x)
-        return dx, dw
+        return linear_bwd(dy, x, w, ctx.needs_input_grad[0], ctx.needs_input_grad[1])
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:

@@ -21,66 +21,70 @@ def rmsnorm_reference(x, w, eps=1e-5, residual=None, w_offset=0.0):
     return y.to(x.dtype), h
 
 
+def rmsnorm_fwd_raw(x2, r2, w, eps, w_offset=0.0):
+    """Kernel call on 2-D contiguous bf16 rows. Returns (y, h, rstd) with h = x (+ residual), the tensor the
+    backward needs."""
+    lib = _lib.load("elementwise")
+    rows, H = x2.shape
+    y = torch.empty_like(x2)
+    rstd = torch.empty(rows, dtype=torch.float32, device=x2.device)
+    res_out = torch.empty_like(x2) if r2 is not None else None
+    rc = lib.ts_rmsnorm_fwd(_lib.ptr(x2), _lib.ptr(r2), _lib.ptr(w), _lib.ptr(y), _lib.ptr(res_out),
+                            _lib.ptr(rstd), ctypes.c_longlong(rows), H, ctypes.c_float(eps),
+                            ctypes.c_float(w_offset), _lib.stream_ptr())
+    _lib.check(rc, "ts_rmsnorm_fwd")
+    return y, (x2 if r2 is None else res_out), rstd
+
+
+def rmsnorm_bwd_raw(dy2, h, w, rstd, dres2, w_offset=0.0):
+    """Returns (dx, dw). dw is None when the weight gradient went straight into `w.main_grad`."""
+    lib = _lib.load("elementwise")
+    rows, H = h.shape
+    dx = torch.empty_like(h)
+    parts = lib.ts_rmsnorm_bwd_parts(ctypes.c_longlong(rows))
+    partial = torch.empty(parts, H, dtype=torch.float32, device=h.device)
+    main_grad = getattr(w, "main_grad", None)
+    if main_grad is not None:
+        acc = bool(getattr(w, "grad_added", False))
+        f32 = main_grad if main_grad.dtype == torch.float32 else None
+        b16 = main_grad if main_grad.dtype == torch.bfloat16 else None
+        dw_out = None
+        w.grad_added = True
+    else:
+        acc = False
+        dw_out = torch.empty(H, dtype=torch.float32, device=h.device)
+        f32, b16 = dw_out, None
+    rc = lib.ts_rmsnorm_bwd(_lib.ptr(dy2), _lib.ptr(h), _lib.ptr(w), _lib.ptr(rstd), _lib.ptr(dres2), _lib.ptr(dx),
+                            _lib.ptr(partial), _lib.ptr(f32), _lib.ptr(b16), int(acc), ctypes.c_longlong(rows), H,
+                            ctypes.c_float(w_offset), _lib.stream_ptr())
+    _lib.check(rc, "ts_rmsnorm_bwd")
+    return dx, (None if dw_out is None else dw_out.to(w.dtype))
+
+
+def _rows(t, H):
+    t2 = t.reshape(-1, H)
+    return t2 if t2.is_contiguous() else t2.contiguous()
+
+
 class _RMSNormFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w, residual, eps, w_offset):
-        lib = _lib.load("elementwise")
         H = x.shape[-1]
-        x2 = x.reshape(-1, H)
-        x2 = x2 if x2.is_contiguous() else x2.contiguous()
-        rows = x2.shape[0]
-        y = torch.empty_like(x2)
-        rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
-        res_out = None
-        r2 = None
-        if residual is not None:
-            r2 = residual.reshape(-1, H)
-            r2 = r2 if r2.is_contiguous() else r2.contiguous()
-            res_out = torch.empty_like(x2)
-        rc = lib.ts_rmsnorm_fwd(_lib.ptr(x2), _lib.ptr(r2), _lib.ptr(w), _lib.ptr(y), _lib.ptr(res_out),
-                                _lib.ptr(rstd), ctypes.c_longlong(rows), H, ctypes.c_float(eps),
-                                ctypes.c_float(w_offset), _lib.stream_ptr())
-        _lib.check(rc, "ts_rmsnorm_fwd")
-        h = x2 if residual is None else res_out
+        y, h, rstd = rmsnorm_fwd_raw(_rows(x, H), None if residual is None else _rows(residual, H), w, eps, w_offset)
         ctx.save_for_backward(h, w, rstd)
         ctx.w_offset = w_offset
         ctx.has_res = residual is not None
         ctx.shape = x.shape
         if residual is None:
             return y.view(x.shape)
-        return y.view(x.shape), res_out.view(x.shape)
+        return y.view(x.shape), h.view(x.shape)
 
     @staticmethod
     def backward(ctx, dy, dres=None):
-        lib = _lib.load("elementwise")
         h, w, rstd = ctx.saved_tensors
-        rows, H = h.shape
-        dy2 = dy.reshape(rows, H)
-        dy2 = dy2 if dy2.is_contiguous() else dy2.contiguous()
-        dres2 = None
-        if dres is not None:
-            dres2 = dres.reshape(rows, H)
-            dres2 = dres2 if dres2.is_contiguous() else dres2.contiguous()
-        dx = torch.empty_like(h)
-        parts = lib.ts_rmsnorm_bwd_parts(ctypes.c_longlong(rows))
-        partial = torch.empty(parts, H, dtype=torch.float32, device=h.device)
-        main_grad = getattr(w, "main_grad", None)
-        if main_grad is not None:
-            acc = bool(getattr(w, "grad_added", False))
-            f32 = main_grad if main_grad.dtype == torch.float32 else None
-            b16 = main_grad if main_grad.dtype == torch.bfloat16 else None
-            dw_out = None
-            w.grad_added = True
-        else:
-            acc = False
-            dw_out = torch.empty(H, dtype=torch.float32, device=h.device)
-            f32, b16 = dw_out, None
-        rc = lib.ts_rmsnorm_bwd(_lib.ptr(dy2), _lib.ptr(h), _lib.ptr(w), _lib.ptr(rstd), _lib.ptr(dres2), _lib.ptr(dx),
-                                _lib.ptr(partial), _lib.ptr(f32), _lib.ptr(b16), int(acc), ctypes.c_longlong(rows), H,
-                                ctypes.c_float(ctx.w_offset), _lib.stream_ptr())
-        _lib.check(rc, "ts_rmsnorm_bwd")
+        H = h.shape[1]
+        dx, dw = rmsnorm_bwd_raw(_rows(dy, H), h, w, rstd, None if dres is None else _rows(dres, H), ctx.w_offset)
         dxv = dx.view(ctx.shape)
-        dw = None if dw_out is None else dw_out.to(w.dtype)
         # with a residual input, d(residual) == d(x): both feed h = x + residual
         return dxv, dw, (dxv if ctx.has_res else None), None, None
 

@@ -90,6 +90,11 @@ class ActivationCheckpoint:
         layers = getattr(inner, "layers", None)
         if layers is None:
             return []
+        if self.cfg.mode == CheckpointMode.OP_SELECTIVE and hasattr(model, "op_selective_recompute"):
+            model.op_selective_recompute(True)      # no layer is re-run; norm / GLU outputs are rebuilt in backward
+            if hasattr(inner, "gradient_checkpointing"):
+                inner.gradient_checkpointing = False
+            return []
         chosen = SelectiveCheckpointPolicy(self.cfg, len(layers)).layers_to_checkpoint()
         if hasattr(inner, "gradient_checkpointing"):
             inner.gradient_checkpointing = bool(chosen)

@@ -189,6 +189,9 @@ class SOTATrainer:
         d = self.config.distributed
         fc = dict(d.fsdp_config or {})
         use_ckpt = bool(fc.get("activation_checkpointing", d.gradient_checkpointing))
+        if str(fc.get("ac_mode", "")).lower() == "op_selective" and hasattr(self.model, "op_selective_recompute"):
+            self.model.op_selective_recompute(True)   # operator-level: nothing is re-run but norm / GLU outputs
+            use_ckpt = False
         if use_ckpt and hasattr(self.model, "gradient_checkpointing_enable"):
             every = int(fc.get("ac_frequency", 1)) or 1
             self.model.gradient_checkpointing_enable(every)
