@@ -256,3 +256,50 @@ def test_model_matches_reference_math_and_trains():
     g1 = m.model.layers[0].mlp.w_down.grad.float().cpu()
     g2 = ref.model.layers[0].mlp.w_down.grad
     assert rel_err(g1, g2) < 6e-2
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("rows,H,bias", [(64, 1024, True), (777, 4096, True), (33, 2048, False)])
+def test_layernorm_fwd_bwd(rows, H, bias):
+    from trainscale_b200.ops import norm
+    torch.manual_seed(0)
+    x = (torch.randn(rows, H, device="cuda") * 2 + 0.5).to(torch.bfloat16).requires_grad_(True)
+    w = (1 + 0.1 * torch.randn(H, device="cuda")).to(torch.bfloat16).requires_grad_(True)
+    b = (0.1 * torch.randn(H, device="cuda")).to(torch.bfloat16).requires_grad_(True) if bias else None
+    y = norm.layernorm(x, w, b, 1e-5)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    xr, wr = x.detach().float().requires_grad_(True), w.detach().float().requires_grad_(True)
+    br = b.detach().float().requires_grad_(True) if bias else None
+    yr = torch.nn.functional.layer_norm(xr, (H,), wr, br, 1e-5)
+    yr.backward(dy.float())
+    assert (y.float() - yr).abs().max().item() < 3e-2
+    assert (x.grad.float() - xr.grad).abs().max().item() < 3e-2 * max(1.0, xr.grad.abs().max().item())
+    assert (w.grad.float() - wr.grad).abs().max().item() < 2e-2 * max(1.0, wr.grad.abs().max().item())
+    if bias:
+        assert (b.grad.float() - br.grad).abs().max().item() < 2e-2 * max(1.0, br.grad.abs().max().item())
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("S,Hq,Hkv,D,window,softcap", [
+    (1024, 4, 2, 128, 256, 0.0), (1000, 2, 2, 64, 100, 0.0), (768, 4, 1, 128, 0, 30.0), (896, 2, 1, 128, 300, 50.0),
+    (512, 2, 2, 128, 1, 0.0)])
+def test_flash_window_softcap_fwd_bwd(S, Hq, Hkv, D, window, softcap):
+    from trainscale_b200.ops import flash, _lib
+    from trainscale_b200.ops.attention import attention_reference, _split_qkv
+    torch.manual_seed(0)
+    B = 2
+    qkv = torch.randn(B, S, (Hq + 2 * Hkv) * D, device="cuda", dtype=torch.bfloat16).requires_grad_(True)
+    o = flash.flash_attention_qkv(qkv, Hq, Hkv, D, True, None, None, None, window, softcap)
+    do = torch.randn_like(o)
+    o.backward(do)
+    torch.cuda.synchronize()
+    assert _lib.device_error("attention")[0] == 0
+    q2 = qkv.detach().float().requires_grad_(True)
+    q, k, v = _split_qkv(q2, Hq, Hkv, D)
+    ref = attention_reference(q, k, v, True, None, window or None, softcap).reshape(B, S, Hq * D)
+    ref.backward(do.float())
+    assert (o.float() - ref).abs().max().item() < 3e-2
+    sizes = [Hq * D, Hkv * D, Hkv * D]
+    for a, b_ in zip(qkv.grad.split(sizes, -1), q2.grad.split(sizes, -1)):
+        assert (a.float() - b_).abs().max().item() < 3e-2 * max(b_.abs().max().item(), 1.0)

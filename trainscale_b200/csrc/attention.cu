@@ -37,7 +37,15 @@ struct AttnParams {
   __nv_bfloat16* dv;
   int dqkv_stride;
   float scale;                  // softmax scale (natural units)
+  int window;                   // > 0: key j is visible to query i only if j > i - window (sliding window)
+  float cap_inv, cap_log2;      // logit soft-cap c: s' = c * tanh(s * scale / c); cap_inv = scale / c, cap_log2 = c * log2(e)
 };
+
+__device__ __forceinline__ float fast_tanh(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 
 __device__ __forceinline__ void seq_bounds(const AttnParams& p, int b, int& start, int& len) {
   if (p.cu_seqlens) {
@@ -65,7 +73,7 @@ struct FwdSmem {
 
 constexpr int FWD_THREADS = 320;
 
-template <int D>
+template <int D, bool EXT>   // EXT: sliding window / logit soft-cap code paths compiled in
 __global__ void __launch_bounds__(FWD_THREADS, 1)
 flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, AttnParams p) {
@@ -110,6 +118,10 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       nkv[t] = (kv_end + 127) / 128;
     }
   }
+  // sliding window: key blocks entirely left of the first row's window are never loaded
+  const int kb_lo = (EXT && p.window > 0) ? max(0, qb * 256 + off - p.window + 1) / 128 : 0;
+#pragma unroll
+  for (int t = 0; t < 2; ++t) nkv[t] = max(0, nkv[t] - kb_lo);
   const int n = max(nkv[0], nkv[1]);
 
   if (threadIdx.x == 0) {
@@ -148,13 +160,13 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 #pragma unroll
         for (int j = 0; j < DCH; ++j)
           tma_load_2d(smem + SM::K_OFF + s * SM::TILE + j * 16384, &tmK, &k_full[s], p.k_col0 + hk * D + j * 64,
-                      k_start + i * 128);
+                      k_start + (kb_lo + i) * 128);
         if (!mbar_wait(&v_empty[s], ph ^ 1u, alive, 401)) break;
         mbar_expect_tx(&v_full[s], SM::TILE);
 #pragma unroll
         for (int j = 0; j < DCH; ++j)
           tma_load_2d(smem + SM::V_OFF + s * SM::TILE + j * 16384, &tmV, &v_full[s], p.v_col0 + hk * D + j * 64,
-                      k_start + i * 128);
+                      k_start + (kb_lo + i) * 128);
       }
     }
   } else if (warp == 1) {
@@ -223,19 +235,27 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     for (int i = 0; i < nt && alive; ++i) {
       if (!mbar_wait(&s_full[t], i & 1u, alive, 600)) break;
       tc_fence_after_sync();
-      const int c0 = i * 128;
-      const bool need_mask = (p.causal && (c0 + 127 > r0[t] + off)) || (c0 + 128 > Lk);
+      const int c0 = (kb_lo + i) * 128;
+      const bool need_mask = (p.causal && (c0 + 127 > r0[t] + off)) || (c0 + 128 > Lk) ||
+                             (EXT && p.window > 0 && c0 <= r0[t] + 127 + off - p.window);
       const int limit = p.causal ? min(Lk - 1, row + off) : Lk - 1;   // last visible column
+      const int lo = (EXT && p.window > 0) ? row + off - p.window + 1 : 0;  // first visible column
       // the thread's whole row of S (128 columns) comes into registers once
       uint32_t v[128];
 #pragma unroll
       for (int c = 0; c < 4; ++c) tmem_ld_32x32b_x32(t_s + c * 32, v + c * 32);
       tc_wait_ld();
       float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+      float sc = p.scale_log2;
+      if (EXT && p.cap_log2 > 0.f) {   // soft-capped logits, already in log2 units
+#pragma unroll
+        for (int j = 0; j < 128; ++j) v[j] = __float_as_uint(p.cap_log2 * fast_tanh(__uint_as_float(v[j]) * p.cap_inv));
+        sc = 1.f;
+      }
       if (need_mask) {
 #pragma unroll
         for (int j = 0; j < 128; ++j)
-          if (c0 + j > limit) v[j] = 0xff800000u;   // -inf: drops out of the max and gives exp2 = 0
+          if (c0 + j > limit || c0 + j < lo) v[j] = 0xff800000u;   // -inf: drops out of the max, exp2 gives 0
       }
 #pragma unroll
       for (int j = 0; j < 128; j += 4) {
@@ -245,7 +265,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         mx3 = fmaxf(mx3, __uint_as_float(v[j + 3]));
       }
       const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
-      const float m_new = fmaxf(m_used, mx * p.scale_log2);
+      const float m_new = fmaxf(m_used, mx * sc);
       const bool grow = (m_new - m_used > 8.0f);   // also true on the first block (m_used = -inf)
       if (__any_sync(0xffffffffu, grow)) {
         const float alpha = (m_used == -INFINITY) ? 0.f : fast_ex2(m_used - m_new);
@@ -271,8 +291,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         uint32_t pk[16];
 #pragma unroll
         for (int j = 0; j < 32; j += 2) {
-          const float p0 = fast_ex2(fmaf(__uint_as_float(v[c * 32 + j]), p.scale_log2, -m_sub));
-          const float p1 = fast_ex2(fmaf(__uint_as_float(v[c * 32 + j + 1]), p.scale_log2, -m_sub));
+          const float p0 = fast_ex2(fmaf(__uint_as_float(v[c * 32 + j]), sc, -m_sub));
+          const float p1 = fast_ex2(fmaf(__uint_as_float(v[c * 32 + j + 1]), sc, -m_sub));
           l0 += p0;
           l1 += p1;
           pk[j >> 1] = pack_bf16x2(p0, p1);
@@ -366,7 +386,7 @@ __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
 
-template <int D>
+template <int D, bool EXT>   // EXT: sliding window / logit soft-cap code paths compiled in
 __global__ void __launch_bounds__(BWD_THREADS, 1)
 flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_constant__ CUtensorMap tmK128,
                       const __grid_constant__ CUtensorMap tmV128, const __grid_constant__ CUtensorMap tmdO64,
@@ -399,7 +419,9 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_co
   const int off = Lk - Lq;
   const int n_u = (Lq + 63) / 64;
   const int u_start = p.causal ? max(0, (j * 128 - off) / 64) : 0;
-  const int per_head = n_u - u_start;
+  // sliding window: the last query row that sees any key of this tile is (j*128 + 127) - off + window - 1
+  const int u_end = (EXT && p.window > 0) ? min(n_u, (j * 128 + 127 - off + p.window - 1) / 64 + 1) : n_u;
+  const int per_head = u_end - u_start;
   const int total = per_head * p.group;
 
   if (threadIdx.x == 0) {
@@ -528,7 +550,8 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_co
       if (!mbar_wait(&s_full[it & 1], (it >> 1) & 1u, alive, 720)) break;
       tc_fence_after_sync();
       const uint32_t t_s = t_lane + (it & 1) * 128;
-      const bool need_mask = (p.causal && (j * 128 + 127 > u * 64 + off)) || (u * 64 + 64 > Lq) || (j * 128 + 128 > Lk);
+      const bool need_mask = (p.causal && (j * 128 + 127 > u * 64 + off)) || (u * 64 + 64 > Lq) ||
+                             (j * 128 + 128 > Lk) || (EXT && p.window > 0 && j * 128 <= u * 64 + 63 + off - p.window);
       {
         const int cc = wg;
         uint32_t sv[32], dv[32], pp[16], ds[16];
@@ -537,23 +560,38 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_co
         tc_wait_ld();
         // the masked and the unmasked tile bodies are separate straight-line code: a per-element branch would
         // serialise the 32 independent exp chains
-        auto body = [&](auto masked) {
+        auto body = [&](auto masked, auto capped) {
 #pragma unroll
           for (int e = 0; e < 32; e += 2) {
             const float4 ld4 = *reinterpret_cast<const float4*>(vb + 2 * (cc * 32 + e));   // warp-wide broadcast
-            float p0 = fast_ex2(fmaf(__uint_as_float(sv[e]), p.scale_log2, -ld4.x));
-            float p1 = fast_ex2(fmaf(__uint_as_float(sv[e + 1]), p.scale_log2, -ld4.z));
+            float p0, p1, g0 = 1.f, g1 = 1.f;   // g = d(capped logit) / d(scaled logit)
+            if constexpr (decltype(capped)::value) {
+              const float t0 = fast_tanh(__uint_as_float(sv[e]) * p.cap_inv);
+              const float t1 = fast_tanh(__uint_as_float(sv[e + 1]) * p.cap_inv);
+              p0 = fast_ex2(fmaf(t0, p.cap_log2, -ld4.x));
+              p1 = fast_ex2(fmaf(t1, p.cap_log2, -ld4.z));
+              g0 = 1.f - t0 * t0;
+              g1 = 1.f - t1 * t1;
+            } else {
+              p0 = fast_ex2(fmaf(__uint_as_float(sv[e]), p.scale_log2, -ld4.x));
+              p1 = fast_ex2(fmaf(__uint_as_float(sv[e + 1]), p.scale_log2, -ld4.z));
+            }
             if constexpr (decltype(masked)::value) {
               const int qrow = u * 64 + cc * 32 + e;
               const bool rok = kv_row < Lk;
-              p0 = (rok && qrow < Lq && (!p.causal || kv_row <= qrow + off)) ? p0 : 0.f;
-              p1 = (rok && qrow + 1 < Lq && (!p.causal || kv_row <= qrow + 1 + off)) ? p1 : 0.f;
+              const int wlo = (EXT && p.window > 0) ? p.window : 0x3fffffff;   // visible iff kv_row > qrow + off - window
+              p0 = (rok && qrow < Lq && (!p.causal || kv_row <= qrow + off) && kv_row > qrow + off - wlo) ? p0 : 0.f;
+              p1 = (rok && qrow + 1 < Lq && (!p.causal || kv_row <= qrow + 1 + off) && kv_row > qrow + 1 + off - wlo)
+                       ? p1 : 0.f;
             }
             pp[e >> 1] = pack_bf16x2(p0, p1);
-            ds[e >> 1] = pack_bf16x2(p0 * (__uint_as_float(dv[e]) - ld4.y), p1 * (__uint_as_float(dv[e + 1]) - ld4.w));
+            ds[e >> 1] = pack_bf16x2(p0 * g0 * (__uint_as_float(dv[e]) - ld4.y),
+                                     p1 * g1 * (__uint_as_float(dv[e + 1]) - ld4.w));
           }
         };
-        if (need_mask) body(std::true_type{}); else body(std::false_type{});
+        if (EXT && p.cap_log2 > 0.f) body(std::true_type{}, std::true_type{});   // soft-cap: one (masked) variant only
+        else if (need_mask) body(std::true_type{}, std::false_type{});
+        else body(std::false_type{}, std::false_type{});
         // each warpgroup overwrites only columns of its own (already consumed) chunk
         tmem_st_32x32b_x16(t_s + cc * 32, pp);
         tmem_st_32x32b_x16(t_s + 64 + cc * 32, ds);
@@ -612,7 +650,7 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_co
 // backward, kernel 2: dQ.  One CTA owns a 128-row query tile of one head (Q and dO resident) and walks the
 // 64-row K/V sub-tiles it can see.  TMEM: two (S | dP) buffers of 64+64 columns and the dQ accumulator.
 // ------------------------------------------------------------------------------------------------
-template <int D>
+template <int D, bool EXT>   // EXT: sliding window / logit soft-cap code paths compiled in
 __global__ void __launch_bounds__(BWD_THREADS, 1)
 flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ128, const __grid_constant__ CUtensorMap tmK64,
                     const __grid_constant__ CUtensorMap tmV64, const __grid_constant__ CUtensorMap tmdO128,
@@ -646,7 +684,9 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ128, const __grid_con
   const int i = n_qt - 1 - blockIdx.y;
   const int off = Lk - Lq;
   const int kv_end = p.causal ? min(Lk, i * 128 + 128 + off) : Lk;
-  const int total = (kv_end + 63) / 64;
+  // sliding window: 64-key sub-tiles entirely left of the first row's window are skipped
+  const int sub0 = (EXT && p.window > 0) ? max(0, i * 128 + off - p.window + 1) / 64 : 0;
+  const int total = (kv_end + 63) / 64 - sub0;
 
   if (threadIdx.x == 0) {
     tma_prefetch_desc(&tmQ128);
@@ -681,9 +721,9 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ128, const __grid_con
 #pragma unroll
         for (int c = 0; c < DCH; ++c) {
           tma_load_2d(smem + SM::S0_OFF + s * SM::SMALL + c * 8192, &tmK64, &kv_full[s], p.k_col0 + hk * D + c * 64,
-                      k_start + it * 64);
+                      k_start + (sub0 + it) * 64);
           tma_load_2d(smem + SM::S1_OFF + s * SM::SMALL + c * 8192, &tmV64, &kv_full[s], p.v_col0 + hk * D + c * 64,
-                      k_start + it * 64);
+                      k_start + (sub0 + it) * 64);
         }
       }
     }
@@ -745,31 +785,47 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ128, const __grid_con
       delta = p.delta[idx];
     }
     const int limit = (qrow < Lq) ? (p.causal ? min(Lk - 1, qrow + off) : Lk - 1) : -1;
+    const int lo = (EXT && p.window > 0) ? qrow + off - p.window + 1 : 0;
     for (int it = 0; it < total && alive; ++it) {
       if (!mbar_wait(&s_full[it & 1], (it >> 1) & 1u, alive, 820)) break;
       tc_fence_after_sync();
       const uint32_t t_s = t_lane + (it & 1) * 128;
-      const bool need_mask = (it * 64 + 63 > i * 128 + off && p.causal) || (it * 64 + 64 > Lk) || (i * 128 + 128 > Lq);
+      const int col0 = (sub0 + it) * 64;
+      const bool need_mask = (col0 + 63 > i * 128 + off && p.causal) || (col0 + 64 > Lk) || (i * 128 + 128 > Lq) ||
+                             (EXT && p.window > 0 && col0 <= i * 128 + 127 + off - p.window);
       {
         const int cc = wg;
         uint32_t sv[32], dv[32], ds[16];
         tmem_ld_32x32b_x32(t_s + cc * 32, sv);
         tmem_ld_32x32b_x32(t_s + 64 + cc * 32, dv);
         tc_wait_ld();
-        auto body = [&](auto masked) {
+        auto body = [&](auto masked, auto capped) {
 #pragma unroll
           for (int e = 0; e < 32; e += 2) {
-            float p0 = fast_ex2(fmaf(__uint_as_float(sv[e]), p.scale_log2, -lse2));
-            float p1 = fast_ex2(fmaf(__uint_as_float(sv[e + 1]), p.scale_log2, -lse2));
-            if constexpr (decltype(masked)::value) {
-              const int col = it * 64 + cc * 32 + e;
-              p0 = (col <= limit) ? p0 : 0.f;
-              p1 = (col + 1 <= limit) ? p1 : 0.f;
+            float p0, p1, g0 = 1.f, g1 = 1.f;
+            if constexpr (decltype(capped)::value) {
+              const float t0 = fast_tanh(__uint_as_float(sv[e]) * p.cap_inv);
+              const float t1 = fast_tanh(__uint_as_float(sv[e + 1]) * p.cap_inv);
+              p0 = fast_ex2(fmaf(t0, p.cap_log2, -lse2));
+              p1 = fast_ex2(fmaf(t1, p.cap_log2, -lse2));
+              g0 = 1.f - t0 * t0;
+              g1 = 1.f - t1 * t1;
+            } else {
+              p0 = fast_ex2(fmaf(__uint_as_float(sv[e]), p.scale_log2, -lse2));
+              p1 = fast_ex2(fmaf(__uint_as_float(sv[e + 1]), p.scale_log2, -lse2));
             }
-            ds[e >> 1] = pack_bf16x2(p0 * (__uint_as_float(dv[e]) - delta), p1 * (__uint_as_float(dv[e + 1]) - delta));
+            if constexpr (decltype(masked)::value) {
+              const int col = col0 + cc * 32 + e;
+              p0 = (col <= limit && col >= lo) ? p0 : 0.f;
+              p1 = (col + 1 <= limit && col + 1 >= lo) ? p1 : 0.f;
+            }
+            ds[e >> 1] = pack_bf16x2(p0 * g0 * (__uint_as_float(dv[e]) - delta),
+                                     p1 * g1 * (__uint_as_float(dv[e + 1]) - delta));
           }
         };
-        if (need_mask) body(std::true_type{}); else body(std::false_type{});
+        if (EXT && p.cap_log2 > 0.f) body(std::true_type{}, std::true_type{});
+        else if (need_mask) body(std::true_type{}, std::false_type{});
+        else body(std::false_type{}, std::false_type{});
         tmem_st_32x32b_x16(t_s + 64 + cc * 32, ds);
       }
       tc_wait_st();
@@ -808,37 +864,37 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ128, const __grid_con
   }
 }
 
-template <int D>
+template <int D, bool EXT>
 static int launch_bwd(const CUtensorMap* m, const AttnParams& p, int max_len, cudaStream_t st) {
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(flash_bwd_dkdv_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(flash_bwd_dkdv_kernel<D, EXT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          BwdSmem<D>::TOTAL);
     if (e != cudaSuccess) return (int)e;
-    e = cudaFuncSetAttribute(flash_bwd_dq_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdSmem<D>::TOTAL);
+    e = cudaFuncSetAttribute(flash_bwd_dq_kernel<D, EXT>, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdSmem<D>::TOTAL);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
   // m: [0]=q64 [1]=k128 [2]=v128 [3]=do64 [4]=q128 [5]=k64 [6]=v64 [7]=do128
   dim3 g1(p.Hkv * p.B, (max_len + 127) / 128, 1);
-  flash_bwd_dkdv_kernel<D><<<g1, BWD_THREADS, BwdSmem<D>::TOTAL, st>>>(m[0], m[1], m[2], m[3], p);
+  flash_bwd_dkdv_kernel<D, EXT><<<g1, BWD_THREADS, BwdSmem<D>::TOTAL, st>>>(m[0], m[1], m[2], m[3], p);
   dim3 g2(p.Hq * p.B, (max_len + 127) / 128, 1);
-  flash_bwd_dq_kernel<D><<<g2, BWD_THREADS, BwdSmem<D>::TOTAL, st>>>(m[4], m[5], m[6], m[7], p);
+  flash_bwd_dq_kernel<D, EXT><<<g2, BWD_THREADS, BwdSmem<D>::TOTAL, st>>>(m[4], m[5], m[6], m[7], p);
   return (int)cudaGetLastError();
 }
 
-template <int D>
+template <int D, bool EXT>
 static int launch_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const AttnParams& p,
                       int max_len, cudaStream_t st) {
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(flash_fwd_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(flash_fwd_kernel<D, EXT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          FwdSmem<D>::TOTAL);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
   dim3 grid(p.Hq * p.B, (max_len + 255) / 256, 1);
-  flash_fwd_kernel<D><<<grid, FWD_THREADS, FwdSmem<D>::TOTAL, st>>>(tq, tk, tv, p);
+  flash_fwd_kernel<D, EXT><<<grid, FWD_THREADS, FwdSmem<D>::TOTAL, st>>>(tq, tk, tv, p);
   return (int)cudaGetLastError();
 }
 
@@ -852,10 +908,11 @@ using namespace ts;
 // They may alias one fused qkv buffer (pass the same base with different col0).
 // cu_seqlens: device int32 [B+1] for packed documents or nullptr for B sequences of S tokens.
 // max_len: longest sequence (host knowledge; S for the uniform case).
-extern "C" int ts_flash_fwd(const void* q, const void* k, const void* v, void* o, float* lse, long long total_rows,
-                            int q_stride, int k_stride, int v_stride, int o_stride, int q_col0, int k_col0,
-                            int v_col0, int Hq, int Hkv, int D, int B, int S, const int* cu_seqlens, int max_len,
-                            int causal, float scale, void* stream) {
+// window > 0 restricts every query to the last `window` keys; softcap > 0 applies c * tanh(s / c) to the scaled logits.
+extern "C" int ts_flash_fwd_ex(const void* q, const void* k, const void* v, void* o, float* lse, long long total_rows,
+                               int q_stride, int k_stride, int v_stride, int o_stride, int q_col0, int k_col0,
+                               int v_col0, int Hq, int Hkv, int D, int B, int S, const int* cu_seqlens, int max_len,
+                               int causal, float scale, int window, float softcap, void* stream) {
   if ((D != 64 && D != 128) || Hq % Hkv != 0 || total_rows <= 0) return -10;
   CUtensorMap tq, tk, tv;
   int rc = make_tmap_2d(&tq, q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)total_rows, (uint64_t)q_stride,
@@ -871,10 +928,22 @@ extern "C" int ts_flash_fwd(const void* q, const void* k, const void* v, void* o
   p.q_col0 = q_col0; p.k_col0 = k_col0; p.v_col0 = v_col0;
   p.Hq = Hq; p.Hkv = Hkv; p.group = Hq / Hkv; p.B = B; p.S = S; p.cu_seqlens = cu_seqlens; p.causal = causal;
   p.scale = scale; p.scale_log2 = scale * 1.4426950408889634f;
+  p.window = window > 0 ? window : 0;
+  p.cap_inv = softcap > 0.f ? scale / softcap : 0.f;
+  p.cap_log2 = softcap > 0.f ? softcap * 1.4426950408889634f : 0.f;
   p.o = (__nv_bfloat16*)o; p.o_stride = o_stride; p.lse = lse; p.total_rows = total_rows;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  if (D == 128) return launch_fwd<128>(tq, tk, tv, p, max_len, st);
-  return launch_fwd<64>(tq, tk, tv, p, max_len, st);
+  const bool ext = p.window > 0 || p.cap_log2 > 0.f;
+  if (D == 128) return ext ? launch_fwd<128, true>(tq, tk, tv, p, max_len, st) : launch_fwd<128, false>(tq, tk, tv, p, max_len, st);
+  return ext ? launch_fwd<64, true>(tq, tk, tv, p, max_len, st) : launch_fwd<64, false>(tq, tk, tv, p, max_len, st);
+}
+
+extern "C" int ts_flash_fwd(const void* q, const void* k, const void* v, void* o, float* lse, long long total_rows,
+                            int q_stride, int k_stride, int v_stride, int o_stride, int q_col0, int k_col0,
+                            int v_col0, int Hq, int Hkv, int D, int B, int S, const int* cu_seqlens, int max_len,
+                            int causal, float scale, void* stream) {
+  return ts_flash_fwd_ex(q, k, v, o, lse, total_rows, q_stride, k_stride, v_stride, o_stride, q_col0, k_col0, v_col0, Hq,
+                         Hkv, D, B, S, cu_seqlens, max_len, causal, scale, 0, 0.f, stream);
 }
 
 extern "C" int ts_attn_delta(const void* o, const void* dout, float* delta, long long total_rows, int Hq, int D,
@@ -889,10 +958,11 @@ extern "C" int ts_attn_delta(const void* o, const void* dout, float* delta, long
 
 // Gradient of ts_flash_fwd. dq/dk/dv are written into `dqkv` (same row layout and column offsets as q/k/v inside
 // a fused buffer of row stride `qkv_stride`); every element of the q|k|v column range is written.
-extern "C" int ts_flash_bwd(const void* q, const void* k, const void* v, const void* dout, const float* lse,
-                            const float* delta, void* dqkv, long long total_rows, int qkv_stride, int o_stride,
-                            int q_col0, int k_col0, int v_col0, int Hq, int Hkv, int D, int B, int S,
-                            const int* cu_seqlens, int max_len, int causal, float scale, void* stream) {
+extern "C" int ts_flash_bwd_ex(const void* q, const void* k, const void* v, const void* dout, const float* lse,
+                               const float* delta, void* dqkv, long long total_rows, int qkv_stride, int o_stride,
+                               int q_col0, int k_col0, int v_col0, int Hq, int Hkv, int D, int B, int S,
+                               const int* cu_seqlens, int max_len, int causal, float scale, int window, float softcap,
+                               void* stream) {
   if ((D != 64 && D != 128) || Hq % Hkv != 0 || total_rows <= 0) return -10;
   CUtensorMap m[8];
   const void* bases[4] = {q, k, v, dout};
@@ -910,11 +980,23 @@ extern "C" int ts_flash_bwd(const void* q, const void* k, const void* v, const v
   p.q_col0 = q_col0; p.k_col0 = k_col0; p.v_col0 = v_col0;
   p.Hq = Hq; p.Hkv = Hkv; p.group = Hq / Hkv; p.B = B; p.S = S; p.cu_seqlens = cu_seqlens; p.causal = causal;
   p.scale = scale; p.scale_log2 = scale * 1.4426950408889634f;
+  p.window = window > 0 ? window : 0;
+  p.cap_inv = softcap > 0.f ? scale / softcap : 0.f;
+  p.cap_log2 = softcap > 0.f ? softcap * 1.4426950408889634f : 0.f;
   p.o_stride = o_stride; p.lse = const_cast<float*>(lse); p.delta = delta; p.total_rows = total_rows;
   p.dout = (const __nv_bfloat16*)dout;
   p.dq = p.dk = p.dv = (__nv_bfloat16*)dqkv;
   p.dqkv_stride = qkv_stride;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  if (D == 128) return launch_bwd<128>(m, p, max_len, st);
-  return launch_bwd<64>(m, p, max_len, st);
+  const bool ext = p.window > 0 || p.cap_log2 > 0.f;
+  if (D == 128) return ext ? launch_bwd<128, true>(m, p, max_len, st) : launch_bwd<128, false>(m, p, max_len, st);
+  return ext ? launch_bwd<64, true>(m, p, max_len, st) : launch_bwd<64, false>(m, p, max_len, st);
+}
+
+extern "C" int ts_flash_bwd(const void* q, const void* k, const void* v, const void* dout, const float* lse,
+                            const float* delta, void* dqkv, long long total_rows, int qkv_stride, int o_stride,
+                            int q_col0, int k_col0, int v_col0, int Hq, int Hkv, int D, int B, int S,
+                            const int* cu_seqlens, int max_len, int causal, float scale, void* stream) {
+  return ts_flash_bwd_ex(q, k, v, dout, lse, delta, dqkv, total_rows, qkv_stride, o_stride, q_col0, k_col0, v_col0, Hq,
+                         Hkv, D, B, S, cu_seqlens, max_len, causal, scale, 0, 0.f, stream);
 }

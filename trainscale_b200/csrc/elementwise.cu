@@ -166,6 +166,127 @@ __global__ void rmsnorm_dw_reduce_kernel(const float* __restrict__ partial, floa
 }
 
 // ---------------------------------------------------------------------------------------------------
+// LayerNorm: y = (x - mean) * rstd * w + b.  Same row-per-CTA layout as RMSNorm; mean and rstd are kept in fp32
+// for the backward, which also produces per-CTA partial rows of dw and db ([parts][2][H]).
+// ---------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(NORM_THREADS) layernorm_fwd_kernel(const __nv_bfloat16* __restrict__ x,
+                                                                     const __nv_bfloat16* __restrict__ w,
+                                                                     const __nv_bfloat16* __restrict__ b,
+                                                                     __nv_bfloat16* __restrict__ y,
+                                                                     float* __restrict__ mean_out,
+                                                                     float* __restrict__ rstd_out, int H, float eps) {
+  __shared__ float scratch[32];
+  const size_t row = blockIdx.x;
+  const __nv_bfloat16* xr = x + row * H;
+  const int nvec = H >> 3;
+  float cache[NORM_MAXV][8];
+  float s = 0.f;
+  int c = 0;
+  for (int i = threadIdx.x; i < nvec && c < NORM_MAXV; i += NORM_THREADS, ++c) {
+    load8(xr + i * 8, cache[c]);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) s += cache[c][e];
+  }
+  const float mean = block_sum(s, scratch) / H;
+  __syncthreads();   // scratch is reused by the second reduction
+  float v = 0.f;
+  c = 0;
+  for (int i = threadIdx.x; i < nvec && c < NORM_MAXV; i += NORM_THREADS, ++c) {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      cache[c][e] -= mean;
+      v += cache[c][e] * cache[c][e];
+    }
+  }
+  const float rstd = rsqrtf(block_sum(v, scratch) / H + eps);
+  if (threadIdx.x == 0) {
+    if (mean_out) mean_out[row] = mean;
+    if (rstd_out) rstd_out[row] = rstd;
+  }
+  c = 0;
+  for (int i = threadIdx.x; i < nvec && c < NORM_MAXV; i += NORM_THREADS, ++c) {
+    float wv[8], bv[8], o[8];
+    load8(w + i * 8, wv);
+    if (b) load8(b + i * 8, bv);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) o[e] = cache[c][e] * rstd * wv[e] + (b ? bv[e] : 0.f);
+    store8(y + row * H + i * 8, o);
+  }
+}
+
+__global__ void __launch_bounds__(NORM_THREADS) layernorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy,
+                                                                     const __nv_bfloat16* __restrict__ x,
+                                                                     const __nv_bfloat16* __restrict__ w,
+                                                                     const float* __restrict__ mean,
+                                                                     const float* __restrict__ rstd,
+                                                                     __nv_bfloat16* __restrict__ dx,
+                                                                     float* __restrict__ partial, int rows, int H) {
+  __shared__ float scratch[32];
+  const int nvec = H >> 3;
+  float dwacc[NORM_MAXV][8], dbacc[NORM_MAXV][8];
+#pragma unroll
+  for (int c = 0; c < NORM_MAXV; ++c)
+#pragma unroll
+    for (int e = 0; e < 8; ++e) dwacc[c][e] = dbacc[c][e] = 0.f;
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    const size_t off = static_cast<size_t>(row) * H;
+    const float mu = mean[row], rs = rstd[row];
+    float xh[NORM_MAXV][8], g[NORM_MAXV][8];
+    float s1 = 0.f, s2 = 0.f;
+    int c = 0;
+    for (int i = threadIdx.x; i < nvec && c < NORM_MAXV; i += NORM_THREADS, ++c) {
+      float xv[8], dv[8], wv[8];
+      load8(x + off + i * 8, xv);
+      load8(dy + off + i * 8, dv);
+      load8(w + i * 8, wv);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        xh[c][e] = (xv[e] - mu) * rs;
+        g[c][e] = dv[e] * wv[e];
+        s1 += g[c][e];
+        s2 += g[c][e] * xh[c][e];
+        dwacc[c][e] += dv[e] * xh[c][e];
+        dbacc[c][e] += dv[e];
+      }
+    }
+    s1 = block_sum(s1, scratch) / H;
+    __syncthreads();
+    s2 = block_sum(s2, scratch) / H;
+    __syncthreads();
+    c = 0;
+    for (int i = threadIdx.x; i < nvec && c < NORM_MAXV; i += NORM_THREADS, ++c) {
+      float o[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) o[e] = rs * (g[c][e] - s1 - xh[c][e] * s2);
+      store8(dx + off + i * 8, o);
+    }
+  }
+  int c = 0;
+  for (int i = threadIdx.x; i < nvec && c < NORM_MAXV; i += NORM_THREADS, ++c) {
+    float* dst = partial + (static_cast<size_t>(blockIdx.x) * 2) * H + i * 8;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      dst[e] = dwacc[c][e];
+      dst[H + e] = dbacc[c][e];
+    }
+  }
+}
+
+// partial: [parts][2][H] -> dw[H], db[H] (fp32)
+__global__ void layernorm_dwdb_reduce_kernel(const float* __restrict__ partial, float* __restrict__ dw,
+                                             float* __restrict__ db, int parts, int H) {
+  const int col = blockIdx.x * blockDim.x + threadIdx.x;
+  if (col >= H) return;
+  float sw = 0.f, sb = 0.f;
+  for (int p = 0; p < parts; ++p) {
+    sw += partial[(static_cast<size_t>(p) * 2) * H + col];
+    sb += partial[(static_cast<size_t>(p) * 2 + 1) * H + col];
+  }
+  dw[col] = sw;
+  if (db) db[col] = sb;
+}
+
+// ---------------------------------------------------------------------------------------------------
 // RoPE applied in place to `n_heads` consecutive heads of width D at the start of every row.
 // Row t of `x` starts at x + t*row_stride; position of row t is pos[t] (if given) else (t % seq) + offset.
 // cos/sin tables are fp32 [max_pos][D/2]. `sign` = -1 gives the backward pass (inverse rotation).
@@ -645,6 +766,25 @@ extern "C" int ts_rmsnorm_bwd(const void* dy, const void* x, const void* w, cons
                                                              w_offset);
   rmsnorm_dw_reduce_kernel<<<(H + 255) / 256, 256, 0, ST(stream)>>>(dw_partial, dw_f32, (bf16*)dw_bf16, parts, H,
                                                                     accumulate_dw);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int ts_layernorm_fwd(const void* x, const void* w, const void* b, void* y, float* mean, float* rstd,
+                                long long rows, int H, float eps, void* stream) {
+  if (H % 8 != 0 || H > NORM_THREADS * NORM_MAXV * 8 || rows <= 0) return -10;
+  layernorm_fwd_kernel<<<(unsigned)rows, NORM_THREADS, 0, ST(stream)>>>((const bf16*)x, (const bf16*)w, (const bf16*)b,
+                                                                         (bf16*)y, mean, rstd, H, eps);
+  return (int)cudaGetLastError();
+}
+
+// partial: fp32 workspace of ts_rmsnorm_bwd_parts(rows) * 2 * H floats; dw / db: fp32 [H]
+extern "C" int ts_layernorm_bwd(const void* dy, const void* x, const void* w, const float* mean, const float* rstd,
+                                void* dx, float* partial, float* dw, float* db, long long rows, int H, void* stream) {
+  if (H % 8 != 0 || H > NORM_THREADS * NORM_MAXV * 8 || rows <= 0) return -10;
+  const int parts = ts_rmsnorm_bwd_parts(rows);
+  layernorm_bwd_kernel<<<parts, NORM_THREADS, 0, ST(stream)>>>((const bf16*)dy, (const bf16*)x, (const bf16*)w, mean,
+                                                               rstd, (bf16*)dx, partial, (int)rows, H);
+  layernorm_dwdb_reduce_kernel<<<(H + 255) / 256, 256, 0, ST(stream)>>>(partial, dw, db, parts, H);
   return (int)cudaGetLastError();
 }
 

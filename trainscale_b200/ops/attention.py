@@ -64,7 +64,8 @@ def attention_qkv(qkv: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: in
     if qkv.is_cuda and qkv.dtype == torch.bfloat16:
         from . import flash
         if flash.supported(head_dim, window, softcap):
-            return flash.flash_attention_qkv(qkv, n_heads, n_kv_heads, head_dim, causal, scale, cu_seqlens)
+            return flash.flash_attention_qkv(qkv, n_heads, n_kv_heads, head_dim, causal, scale, cu_seqlens,
+                                             None, window, softcap)
     q, k, v = _split_qkv(qkv, n_heads, n_kv_heads, head_dim)
     if doc_ids is None and cu_seqlens is not None:
         idx = torch.arange(B * S, device=qkv.device)

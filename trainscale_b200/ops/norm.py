@@ -100,6 +100,46 @@ def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float = 1e-5, residual: torch
     return rmsnorm_reference(x, w, eps, residual, w_offset)
 
 
+class _LayerNormFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, b, eps):
+        lib = _lib.load("elementwise")
+        H = x.shape[-1]
+        x2 = _rows(x, H)
+        rows = x2.shape[0]
+        y = torch.empty_like(x2)
+        mean = torch.empty(rows, dtype=torch.float32, device=x.device)
+        rstd = torch.empty_like(mean)
+        rc = lib.ts_layernorm_fwd(_lib.ptr(x2), _lib.ptr(w), _lib.ptr(b), _lib.ptr(y), _lib.ptr(mean), _lib.ptr(rstd),
+                                  ctypes.c_longlong(rows), H, ctypes.c_float(eps), _lib.stream_ptr())
+        _lib.check(rc, "ts_layernorm_fwd")
+        ctx.save_for_backward(x2, w, mean, rstd)
+        ctx.has_bias, ctx.shape = b is not None, x.shape
+        return y.view(x.shape)
+
+    @staticmethod
+    def backward(ctx, dy):
+        lib = _lib.load("elementwise")
+        x2, w, mean, rstd = ctx.saved_tensors
+        rows, H = x2.shape
+        dy2 = _rows(dy, H)
+        dx = torch.empty_like(x2)
+        parts = lib.ts_rmsnorm_bwd_parts(ctypes.c_longlong(rows))
+        partial = torch.empty(parts, 2, H, dtype=torch.float32, device=x2.device)
+        dw = torch.empty(H, dtype=torch.float32, device=x2.device)
+        db = torch.empty(H, dtype=torch.float32, device=x2.device) if ctx.has_bias else None
+        rc = lib.ts_layernorm_bwd(_lib.ptr(dy2), _lib.ptr(x2), _lib.ptr(w), _lib.ptr(mean), _lib.ptr(rstd), _lib.ptr(dx),
+                                  _lib.ptr(partial), _lib.ptr(dw), _lib.ptr(db), ctypes.c_longlong(rows), H,
+                                  _lib.stream_ptr())
+        _lib.check(rc, "ts_layernorm_bwd")
+        return dx.view(ctx.shape), dw.to(w.dtype), (db.to(w.dtype) if db is not None else None), None
+
+
 def layernorm(x, w, b=None, eps=1e-5):
-    """LayerNorm (PyTorch op; kept for model families that need it)."""
-    return torch.nn.functional.layer_norm(x, (x.shape[-1],), w, b, eps)
+    """LayerNorm over the last dimension (sm_100a kernel for bf16 CUDA rows up to 8192 wide, PyTorch otherwise).
+    Reference kernels: data_pipeline/trainer/kernels/layernorm_kernels.py:143-621."""
+    H = x.shape[-1]
+    if x.is_cuda and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and H % 8 == 0 and H <= 8192 \
+            and (b is None or b.dtype == torch.bfloat16):
+        return _LayerNormFn.apply(x, w, b, eps)
+    return torch.nn.functional.layer_norm(x, (H,), w, b, eps)
