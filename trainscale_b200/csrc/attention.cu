@@ -579,14 +579,21 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_co
             if constexpr (decltype(masked)::value) {
               const int qrow = u * 64 + cc * 32 + e;
               const bool rok = kv_row < Lk;
-              const int wlo = (EXT && p.window > 0) ? p.window : 0x3fffffff;   // visible iff kv_row > qrow + off - window
-              p0 = (rok && qrow < Lq && (!p.causal || kv_row <= qrow + off) && kv_row > qrow + off - wlo) ? p0 : 0.f;
-              p1 = (rok && qrow + 1 < Lq && (!p.causal || kv_row <= qrow + 1 + off) && kv_row > qrow + 1 + off - wlo)
-                       ? p1 : 0.f;
+              p0 = (rok && qrow < Lq && (!p.causal || kv_row <= qrow + off)) ? p0 : 0.f;
+              p1 = (rok && qrow + 1 < Lq && (!p.causal || kv_row <= qrow + 1 + off)) ? p1 : 0.f;
+              if constexpr (EXT) {   // sliding window: visible iff kv_row > qrow + off - window
+                if (p.window > 0) {
+                  p0 = (kv_row > qrow + off - p.window) ? p0 : 0.f;
+                  p1 = (kv_row > qrow + 1 + off - p.window) ? p1 : 0.f;
+                }
+              }
             }
             pp[e >> 1] = pack_bf16x2(p0, p1);
-            ds[e >> 1] = pack_bf16x2(p0 * g0 * (__uint_as_float(dv[e]) - ld4.y),
-                                     p1 * g1 * (__uint_as_float(dv[e + 1]) - ld4.w));
+            if constexpr (decltype(capped)::value)
+              ds[e >> 1] = pack_bf16x2(p0 * g0 * (__uint_as_float(dv[e]) - ld4.y),
+                                       p1 * g1 * (__uint_as_float(dv[e + 1]) - ld4.w));
+            else
+              ds[e >> 1] = pack_bf16x2(p0 * (__uint_as_float(dv[e]) - ld4.y), p1 * (__uint_as_float(dv[e + 1]) - ld4.w));
           }
         };
         if (EXT && p.cap_log2 > 0.f) body(std::true_type{}, std::true_type{});   // soft-cap: one (masked) variant only
@@ -816,11 +823,18 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ128, const __grid_con
             }
             if constexpr (decltype(masked)::value) {
               const int col = col0 + cc * 32 + e;
-              p0 = (col <= limit && col >= lo) ? p0 : 0.f;
-              p1 = (col + 1 <= limit && col + 1 >= lo) ? p1 : 0.f;
+              p0 = (col <= limit) ? p0 : 0.f;
+              p1 = (col + 1 <= limit) ? p1 : 0.f;
+              if constexpr (EXT) {
+                p0 = (col >= lo) ? p0 : 0.f;
+                p1 = (col + 1 >= lo) ? p1 : 0.f;
+              }
             }
-            ds[e >> 1] = pack_bf16x2(p0 * g0 * (__uint_as_float(dv[e]) - delta),
-                                     p1 * g1 * (__uint_as_float(dv[e + 1]) - delta));
+            if constexpr (decltype(capped)::value)
+              ds[e >> 1] = pack_bf16x2(p0 * g0 * (__uint_as_float(dv[e]) - delta),
+                                       p1 * g1 * (__uint_as_float(dv[e + 1]) - delta));
+            else
+              ds[e >> 1] = pack_bf16x2(p0 * (__uint_as_float(dv[e]) - delta), p1 * (__uint_as_float(dv[e + 1]) - delta));
           }
         };
         if (EXT && p.cap_log2 > 0.f) body(std::true_type{}, std::true_type{});

@@ -33,6 +33,79 @@ struct GemmParams {
   float alpha;
   void* C;
   int num_m_tiles, num_n_tiles, k_blocks;
+  // grouped (mixture-of-experts) modes
+  const int* tile_expert;   // MODE 1: expert of every 128-row tile of A / C (-1: tile unused)
+  const int* seg_start;     // MODE 2: [E + 1] first row of every expert's (128-aligned) segment along the K axis
+  int group_rows;           // MODE 1: rows (K-major B) or K extent (MN-major B) of one expert inside the stacked B
+  int num_groups;           // MODE 2: E; C is [E][M][ldc]
+};
+
+// 32 consecutive fp32 accumulator columns of one output row: scale, optionally add to C, convert, store.
+__device__ __forceinline__ void gemm_store_chunk(const GemmParams& p, const uint32_t* r, size_t row, int col0) {
+  const bool full = (col0 + 32 <= p.N);
+  if (p.out_fp32) {
+    float* dst = reinterpret_cast<float*>(p.C) + row * p.ldc + col0;
+    if (full && ((reinterpret_cast<uintptr_t>(dst) & 15u) == 0)) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float4 v = make_float4(__uint_as_float(r[4 * j]) * p.alpha, __uint_as_float(r[4 * j + 1]) * p.alpha,
+                               __uint_as_float(r[4 * j + 2]) * p.alpha, __uint_as_float(r[4 * j + 3]) * p.alpha);
+        if (p.accumulate) {
+          const float4 o = *reinterpret_cast<const float4*>(dst + 4 * j);
+          v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
+        }
+        *reinterpret_cast<float4*>(dst + 4 * j) = v;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {   // static indices keep the accumulator chunk in registers
+        if (col0 + j < p.N) {
+          float v = __uint_as_float(r[j]) * p.alpha;
+          if (p.accumulate) v += dst[j];
+          dst[j] = v;
+        }
+      }
+    }
+  } else {
+    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + row * p.ldc + col0;
+    if (full && ((reinterpret_cast<uintptr_t>(dst) & 15u) == 0)) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float f[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(r[8 * j + e]) * p.alpha;
+        if (p.accumulate) {
+          const uint4 o = *reinterpret_cast<const uint4*>(dst + 8 * j);
+          const float2 o0 = unpack_bf16x2(o.x), o1 = unpack_bf16x2(o.y), o2 = unpack_bf16x2(o.z),
+                       o3 = unpack_bf16x2(o.w);
+          f[0] += o0.x; f[1] += o0.y; f[2] += o1.x; f[3] += o1.y;
+          f[4] += o2.x; f[5] += o2.y; f[6] += o3.x; f[7] += o3.y;
+        }
+        uint4 v;
+        v.x = pack_bf16x2(f[0], f[1]);
+        v.y = pack_bf16x2(f[2], f[3]);
+        v.z = pack_bf16x2(f[4], f[5]);
+        v.w = pack_bf16x2(f[6], f[7]);
+        *reinterpret_cast<uint4*>(dst + 8 * j) = v;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        if (col0 + j < p.N) {
+          float v = __uint_as_float(r[j]) * p.alpha;
+          if (p.accumulate) v += __bfloat162float(dst[j]);
+          dst[j] = __float2bfloat16(v);
+        }
+      }
+    }
+  }
+}
+
+struct GemmTile {
+  int m0, n0;        // tile origin in the A-row / B-row (output) index spaces
+  int b_off;         // MODE 1: offset of this tile's expert along B's row (K-major) or K (MN-major) coordinate
+  int k0, k_blocks;  // MODE 2: first reduction row and number of 64-wide reduction blocks
+  size_t c_row0;     // MODE 2: first output row of this expert's C slab
 };
 
 template <int BN>
@@ -45,7 +118,10 @@ struct GemmSmem {
   static constexpr int TOTAL = STAGES * STAGE_BYTES + BAR_BYTES + 1024;   // + alignment slack
 };
 
-template <int BN>
+// MODE 0: dense.  MODE 1: grouped rows - every 128-row tile of A/C belongs to one expert whose weight is a slab of
+// the stacked B operand (forward and dgrad of a mixture-of-experts layer on an expert-sorted, 128-aligned token
+// buffer).  MODE 2: grouped reduction - one output slab per expert, reduced over that expert's row segment (wgrad).
+template <int BN, int MODE>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmParams p) {
   using S = GemmSmem<BN>;
@@ -88,17 +164,39 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
-  const int num_tiles = p.num_m_tiles * p.num_n_tiles;
+  const int tiles_per_slab = p.num_m_tiles * p.num_n_tiles;
+  const int num_tiles = tiles_per_slab * (MODE == 2 ? p.num_groups : 1);
   const int tiles_per_group = GEMM_GROUP_M * p.num_n_tiles;
   bool alive = true;
 
-  auto tile_coords = [&](int t, int& m0, int& n0) {
+  // every role walks the same tile sequence and skips the same tiles (returns false), so their phase counters agree
+  auto tile_info = [&](int t, GemmTile& ti) -> bool {
+    int e = 0;
+    if (MODE == 2) {
+      e = t / tiles_per_slab;
+      t -= e * tiles_per_slab;
+    }
     const int g = t / tiles_per_group;
     const int first_m = g * GEMM_GROUP_M;
     const int gsz = min(p.num_m_tiles - first_m, GEMM_GROUP_M);
     const int r = t - g * tiles_per_group;
-    m0 = (first_m + (r % gsz)) * GEMM_BM;
-    n0 = (r / gsz) * BN;
+    ti.m0 = (first_m + (r % gsz)) * GEMM_BM;
+    ti.n0 = (r / gsz) * BN;
+    ti.b_off = 0;
+    ti.k0 = 0;
+    ti.k_blocks = p.k_blocks;
+    ti.c_row0 = 0;
+    if (MODE == 1) {
+      const int ex = p.tile_expert[ti.m0 / GEMM_BM];
+      if (ex < 0) return false;
+      ti.b_off = ex * p.group_rows;
+    } else if (MODE == 2) {
+      const int s0 = p.seg_start[e], s1 = p.seg_start[e + 1];
+      ti.k0 = s0;
+      ti.k_blocks = (s1 - s0) / GEMM_BK;
+      ti.c_row0 = static_cast<size_t>(e) * p.M;
+    }
+    return true;
   };
 
   if (warp == 0) {
@@ -106,16 +204,17 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     if (elect_one_sync()) {
       uint32_t it = 0;
       for (int t = blockIdx.x; t < num_tiles && alive; t += gridDim.x) {
-        int m0, n0;
-        tile_coords(t, m0, n0);
-        for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
+        GemmTile ti;
+        if (!tile_info(t, ti)) continue;
+        const int m0 = ti.m0, n0 = ti.n0;
+        for (int kb = 0; kb < ti.k_blocks; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1u;
           if (!mbar_wait(&empty_bar[s], ph ^ 1u, alive, 100)) break;
           mbar_expect_tx(&full_bar[s], S::STAGE_BYTES);
           uint8_t* a_dst = smem_a + s * S::A_BYTES;
           uint8_t* b_dst = smem_b + s * S::B_BYTES;
-          const int k0 = kb * GEMM_BK;
+          const int k0 = ti.k0 + kb * GEMM_BK;
           if (!p.a_mn) {
             tma_load_2d(a_dst, &tmA, &full_bar[s], k0, m0);
           } else {
@@ -123,10 +222,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             for (int j = 0; j < GEMM_BM / 64; ++j) tma_load_2d(a_dst + j * 8192, &tmA, &full_bar[s], m0 + j * 64, k0);
           }
           if (!p.b_mn) {
-            tma_load_2d(b_dst, &tmB, &full_bar[s], k0, n0);
+            tma_load_2d(b_dst, &tmB, &full_bar[s], k0, n0 + ti.b_off);
           } else {
 #pragma unroll
-            for (int j = 0; j < BN / 64; ++j) tma_load_2d(b_dst + j * 8192, &tmB, &full_bar[s], n0 + j * 64, k0);
+            for (int j = 0; j < BN / 64; ++j)
+              tma_load_2d(b_dst + j * 8192, &tmB, &full_bar[s], n0 + j * 64, k0 + ti.b_off);
           }
         }
       }
@@ -149,13 +249,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const uint32_t a_lbo = p.a_mn ? 8192u : 16u;
       const uint32_t b_lbo = p.b_mn ? 8192u : 16u;
       uint32_t it = 0, tile_it = 0;
-      for (int t = blockIdx.x; t < num_tiles && alive; t += gridDim.x, ++tile_it) {
+      for (int t = blockIdx.x; t < num_tiles && alive; t += gridDim.x) {
+        GemmTile ti;
+        if (!tile_info(t, ti) || ti.k_blocks == 0) continue;   // an empty reduction is zero-filled by the epilogue
         const uint32_t acc = tile_it & 1u;
         const uint32_t acc_ph = (tile_it >> 1) & 1u;
+        ++tile_it;
         if (!mbar_wait(&tempty_bar[acc], acc_ph ^ 1u, alive, 200)) break;
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
+        for (int kb = 0; kb < ti.k_blocks; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1u;
           if (!mbar_wait(&full_bar[s], ph, alive, 201)) break;
@@ -178,14 +281,27 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     // ------------------------------ epilogue (warps 2..5) ------------------------------
     const int q = warp & 3;   // TMEM lane quarter this warp may access
     uint32_t tile_it = 0;
-    for (int t = blockIdx.x; t < num_tiles && alive; t += gridDim.x, ++tile_it) {
-      int m0, n0;
-      tile_coords(t, m0, n0);
+    for (int t = blockIdx.x; t < num_tiles && alive; t += gridDim.x) {
+      GemmTile ti;
+      if (!tile_info(t, ti)) continue;
+      const int m0 = ti.m0, n0 = ti.n0;
+      const int row = m0 + q * 32 + lane;
+      if (ti.k_blocks == 0) {
+        // nothing to reduce (an expert without tokens): the slab is zero unless it accumulates
+        if (!p.accumulate && row < p.M) {
+          uint32_t z[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) z[j] = 0u;
+          for (int c = 0; c < BN / 32; ++c)
+            if (n0 + c * 32 < p.N) gemm_store_chunk(p, z, ti.c_row0 + row, n0 + c * 32);
+        }
+        continue;
+      }
       const uint32_t acc = tile_it & 1u;
       const uint32_t acc_ph = (tile_it >> 1) & 1u;
+      ++tile_it;
       if (!mbar_wait(&tfull_bar[acc], acc_ph, alive, 300)) break;
       tc_fence_after_sync();
-      const int row = m0 + q * 32 + lane;
       const uint32_t t_row = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
@@ -193,59 +309,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         tmem_ld_32x32b_x32(t_row + c * 32, r);
         tc_wait_ld();
         const int col0 = n0 + c * 32;
-        if (row < p.M && col0 < p.N) {
-          const bool full = (col0 + 32 <= p.N);
-          if (p.out_fp32) {
-            float* dst = reinterpret_cast<float*>(p.C) + static_cast<size_t>(row) * p.ldc + col0;
-            if (full && ((reinterpret_cast<uintptr_t>(dst) & 15u) == 0)) {
-#pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                float4 v = make_float4(__uint_as_float(r[4 * j]) * p.alpha, __uint_as_float(r[4 * j + 1]) * p.alpha,
-                                       __uint_as_float(r[4 * j + 2]) * p.alpha, __uint_as_float(r[4 * j + 3]) * p.alpha);
-                if (p.accumulate) {
-                  const float4 o = *reinterpret_cast<const float4*>(dst + 4 * j);
-                  v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
-                }
-                *reinterpret_cast<float4*>(dst + 4 * j) = v;
-              }
-            } else {
-              for (int j = 0; j < 32 && col0 + j < p.N; ++j) {
-                float v = __uint_as_float(r[j]) * p.alpha;
-                if (p.accumulate) v += dst[j];
-                dst[j] = v;
-              }
-            }
-          } else {
-            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<size_t>(row) * p.ldc + col0;
-            if (full && ((reinterpret_cast<uintptr_t>(dst) & 15u) == 0)) {
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                float f[8];
-#pragma unroll
-                for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(r[8 * j + e]) * p.alpha;
-                if (p.accumulate) {
-                  const uint4 o = *reinterpret_cast<const uint4*>(dst + 8 * j);
-                  const float2 o0 = unpack_bf16x2(o.x), o1 = unpack_bf16x2(o.y), o2 = unpack_bf16x2(o.z),
-                               o3 = unpack_bf16x2(o.w);
-                  f[0] += o0.x; f[1] += o0.y; f[2] += o1.x; f[3] += o1.y;
-                  f[4] += o2.x; f[5] += o2.y; f[6] += o3.x; f[7] += o3.y;
-                }
-                uint4 v;
-                v.x = pack_bf16x2(f[0], f[1]);
-                v.y = pack_bf16x2(f[2], f[3]);
-                v.z = pack_bf16x2(f[4], f[5]);
-                v.w = pack_bf16x2(f[6], f[7]);
-                *reinterpret_cast<uint4*>(dst + 8 * j) = v;
-              }
-            } else {
-              for (int j = 0; j < 32 && col0 + j < p.N; ++j) {
-                float v = __uint_as_float(r[j]) * p.alpha;
-                if (p.accumulate) v += __bfloat162float(dst[j]);
-                dst[j] = __float2bfloat16(v);
-              }
-            }
-          }
-        }
+        if (row < p.M && col0 < p.N) gemm_store_chunk(p, r, ti.c_row0 + row, col0);
       }
       tc_fence_before_sync();
       __syncwarp();
@@ -407,36 +471,7 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         tmem_ld_32x32b_x32(t_row + c * 32, r);
         tc_wait_ld();
         const int col0 = n0 + c * 32;
-        if (row < p.M && col0 < p.N) {
-          const bool full = (col0 + 32 <= p.N);
-          if (p.out_fp32) {
-            float* dst = reinterpret_cast<float*>(p.C) + static_cast<size_t>(row) * p.ldc + col0;
-            for (int j = 0; j < 32 && (full || col0 + j < p.N); ++j) {
-              float v = __uint_as_float(r[j]) * p.alpha;
-              if (p.accumulate) v += dst[j];
-              dst[j] = v;
-            }
-          } else {
-            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<size_t>(row) * p.ldc + col0;
-            if (full && !p.accumulate && ((reinterpret_cast<uintptr_t>(dst) & 15u) == 0)) {
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                uint4 v;
-                v.x = pack_bf16x2(__uint_as_float(r[8 * j]) * p.alpha, __uint_as_float(r[8 * j + 1]) * p.alpha);
-                v.y = pack_bf16x2(__uint_as_float(r[8 * j + 2]) * p.alpha, __uint_as_float(r[8 * j + 3]) * p.alpha);
-                v.z = pack_bf16x2(__uint_as_float(r[8 * j + 4]) * p.alpha, __uint_as_float(r[8 * j + 5]) * p.alpha);
-                v.w = pack_bf16x2(__uint_as_float(r[8 * j + 6]) * p.alpha, __uint_as_float(r[8 * j + 7]) * p.alpha);
-                *reinterpret_cast<uint4*>(dst + 8 * j) = v;
-              }
-            } else {
-              for (int j = 0; j < 32 && col0 + j < p.N; ++j) {
-                float v = __uint_as_float(r[j]) * p.alpha;
-                if (p.accumulate) v += __bfloat162float(dst[j]);
-                dst[j] = __float2bfloat16(v);
-              }
-            }
-          }
-        }
+        if (row < p.M && col0 < p.N) gemm_store_chunk(p, r, static_cast<size_t>(row), col0);
       }
       tc_fence_before_sync();
       __syncwarp();
@@ -478,18 +513,18 @@ static int launch_gemm_2cta(const CUtensorMap& tmA, const CUtensorMap& tmB, cons
   return (int)cudaLaunchKernelEx(&cfg, gemm_bf16_2cta_kernel, tmA, tmB, p);
 }
 
-template <int BN>
+template <int BN, int MODE = 0>
 static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, cudaStream_t stream) {
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel<BN, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          GemmSmem<BN>::TOTAL);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  const int tiles = p.num_m_tiles * p.num_n_tiles;
+  const int tiles = p.num_m_tiles * p.num_n_tiles * (MODE == 2 ? p.num_groups : 1);
   const int grid = tiles < sm_count() ? tiles : sm_count();
-  gemm_bf16_kernel<BN><<<grid, GEMM_THREADS, GemmSmem<BN>::TOTAL, stream>>>(tmA, tmB, p);
+  gemm_bf16_kernel<BN, MODE><<<grid, GEMM_THREADS, GemmSmem<BN>::TOTAL, stream>>>(tmA, tmB, p);
   return (int)cudaGetLastError();
 }
 
@@ -536,9 +571,60 @@ extern "C" int ts_gemm_bf16(const void* A, const void* B, void* C, int M, int N,
   p.num_m_tiles = (M + GEMM_BM - 1) / GEMM_BM;
   p.num_n_tiles = (N + bn - 1) / bn;
   p.k_blocks = (K + GEMM_BK - 1) / GEMM_BK;
+  p.tile_expert = nullptr; p.seg_start = nullptr; p.group_rows = 0; p.num_groups = 1;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   if (two_cta) return launch_gemm_2cta(tmA, tmB, p, st);
   if (bn == 256) return launch_gemm<256>(tmA, tmB, p, st);
   if (bn == 128) return launch_gemm<128>(tmA, tmB, p, st);
   return launch_gemm<64>(tmA, tmB, p, st);
+}
+
+// Grouped GEMM over an expert-sorted token buffer whose per-expert segments start on 128-row boundaries.
+//   mode 1 (forward / dgrad): C[P][N] = A[P][K] * B_e, where e = tile_expert[row / 128] (-1 skips the tile) and B is
+//     the stack of E expert matrices: K-major [E*N][ldb] (b_mn = 0) or MN-major [E*K][ldb] (b_mn = 1).  a_mn = 0.
+//   mode 2 (wgrad): C[e][M][N] = sum over rows r in [seg_start[e], seg_start[e+1]) of A[r][m] * B[r][n]; both operands
+//     MN-major (a_mn = b_mn = 1), K = P.  An empty segment gives a zero slab (or leaves C alone when accumulating).
+// `groups` is the device int32 array tile_expert (mode 1, ceil(P/128) entries) or seg_start (mode 2, E + 1 entries).
+// Serves the grouped expert GEMMs of data_pipeline/trainer/kernels/moe_kernels.py:219-785.
+extern "C" int ts_gemm_grouped_bf16(const void* A, const void* B, void* C, int mode, int M, int N, int K, int lda,
+                                    int ldb, int ldc, int a_mn, int b_mn, int out_fp32, int accumulate, float alpha,
+                                    const int* groups, int num_groups, void* stream) {
+  using namespace ts;
+  if (M <= 0 || N <= 0 || K <= 0 || num_groups <= 0 || groups == nullptr) return -10;
+  if (mode == 1 && (a_mn != 0 || K % GEMM_BK != 0)) return -12;
+  if (mode == 2 && (a_mn != 1 || b_mn != 1)) return -12;
+  if (mode != 1 && mode != 2) return -11;
+  const int bn = (N >= 256) ? 256 : (N >= 128 ? 128 : 64);
+  CUtensorMap tmA, tmB;
+  int rc;
+  if (!a_mn)
+    rc = make_tmap_2d(&tmA, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)M, (uint64_t)K, (uint64_t)lda, GEMM_BM, 64);
+  else
+    rc = make_tmap_2d(&tmA, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)K, (uint64_t)M, (uint64_t)lda, 64, 64);
+  if (rc) return rc * 100 - 1;
+  const uint64_t eb = (mode == 1) ? (uint64_t)num_groups : 1u;   // mode 1: B stacks the experts along its row axis
+  if (!b_mn)
+    rc = make_tmap_2d(&tmB, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, eb * N, (uint64_t)K, (uint64_t)ldb, (uint32_t)bn, 64);
+  else
+    rc = make_tmap_2d(&tmB, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, eb * K, (uint64_t)N, (uint64_t)ldb, 64, 64);
+  if (rc) return rc * 100 - 2;
+  GemmParams p;
+  p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.a_mn = a_mn; p.b_mn = b_mn; p.out_fp32 = out_fp32;
+  p.accumulate = accumulate; p.alpha = alpha; p.C = C;
+  p.num_m_tiles = (M + GEMM_BM - 1) / GEMM_BM;
+  p.num_n_tiles = (N + bn - 1) / bn;
+  p.k_blocks = (K + GEMM_BK - 1) / GEMM_BK;
+  p.tile_expert = (mode == 1) ? groups : nullptr;
+  p.seg_start = (mode == 2) ? groups : nullptr;
+  p.group_rows = b_mn ? K : N;
+  p.num_groups = num_groups;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (mode == 1) {
+    if (bn == 256) return launch_gemm<256, 1>(tmA, tmB, p, st);
+    if (bn == 128) return launch_gemm<128, 1>(tmA, tmB, p, st);
+    return launch_gemm<64, 1>(tmA, tmB, p, st);
+  }
+  if (bn == 256) return launch_gemm<256, 2>(tmA, tmB, p, st);
+  if (bn == 128) return launch_gemm<128, 2>(tmA, tmB, p, st);
+  return launch_gemm<64, 2>(tmA, tmB, p, st);
 }

@@ -216,6 +216,12 @@ class MoELayer(nn.Module):
         return run_experts(x2, idx, w)
 
     def _local(self, x2, idx, w):
+        from ..ops import moe as moe_ops
+        if moe_ops.available(x2) and isinstance(self.experts, GroupedExperts) \
+                and self.experts.w_gate_up.dtype == torch.bfloat16 and self.experts.w_down.shape[-1] % 64 == 0 \
+                and x2.shape[-1] % 64 == 0:
+            # device-side plan + one grouped tcgen05 GEMM per projection: no host sync on the expert counts
+            return moe_ops.moe_ffn(x2, idx, w, self.experts.w_gate_up, self.experts.w_down)
         xs, order, counts = permute_tokens(x2, idx, self.cfg.num_experts)
         ys = self.experts(xs, counts.tolist())
         return unpermute_tokens(ys, order, w, x2.shape[0])
