@@ -3,9 +3,9 @@ amax history, an `FP8Linear` that stores block-scaled fp8 weights, NF4-style 4-b
 
 After data_pipeline/trainer/kernels/fp8_kernels.py:144-1055 (block amax -> scale = amax / 448, saturating cast,
 row-wise activation quantisation, `FP8Linear`) and data_pipeline/trainer/quantization.py:47-322 (`QuantizationConfig`,
-`fast_dequantize`, `estimate_memory_usage`).  The GEMM of `FP8Linear` dequantises the weight block-wise to bf16 and
-runs the bf16 tcgen05 kernel with fp32 accumulation: numerically the block-scaled product the reference's fp8 kernel
-computes; a native kind::f8f6f4 mainloop is the planned replacement.
+`fast_dequantize`, `estimate_memory_usage`).  On CUDA bf16 inputs `FP8Linear` runs the native block-scaled
+kind::f8f6f4 tcgen05 GEMM of ops/fp8.py (forward and dgrad); elsewhere it dequantises block-wise and uses the plain
+matmul, which is also the oracle.
 """
 from __future__ import annotations
 
@@ -107,6 +107,10 @@ class FP8Linear(nn.Module):
         self.out_features, self.in_features = weight.shape
 
     def forward(self, x):
+        from .ops import fp8 as fp8_ops
+        if self.block == 128 and self.quantize_activations and fp8_ops.available(x) \
+                and self.weight_q.dtype == torch.float8_e4m3fn:
+            return fp8_ops.fp8_linear(x, None, self.weight_q, self.weight_scale)
         return _FP8LinearFn.apply(x, self.weight_q, self.weight_scale, self.block, self.quantize_activations)
 
     def dequantized_weight(self, dtype=torch.bfloat16):
