@@ -21,6 +21,8 @@ def main():
     ap.add_argument("--comm", default="auto")
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--tol", type=float, default=2e-4)
+    ap.add_argument("--recompute", action="store_true", help="layer-wise activation recomputation in both runs")
+    ap.add_argument("--accum", type=int, default=1, help="micro-batches per optimizer step")
     a = ap.parse_args()
     cuda = a.device == "cuda"
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
@@ -36,7 +38,10 @@ def main():
     S, B = (256, 2) if cuda else (32, 2)
     model = build_model(cfg, dtype=dtype, device=dev, seed=3)
     ref = build_model(cfg, dtype=dtype, device=dev, seed=3)
-    ec = dict(param_dtype=dtype, lr=1e-2, weight_decay=0.01, max_grad_norm=1.0, eps=1e-3)  # large eps: no sign(g) blow-up of rounding noise
+    if a.recompute:
+        model.gradient_checkpointing_enable(1)
+        ref.gradient_checkpointing_enable(1)
+    ec = dict(gradient_accumulation_steps=a.accum, param_dtype=dtype, lr=1e-2, weight_decay=0.01, max_grad_norm=1.0, eps=1e-3)  # large eps: no sign(g) blow-up of rounding noise
     eng = FlatShardedEngine(model, EngineConfig(sharding_strategy=a.strategy, comm=a.comm, **ec), device=dev)
     # the oracle: one process, global batch, no sharding (a private 1-rank view of the engine)
     ref_eng = FlatShardedEngine.__new__(FlatShardedEngine)
@@ -49,20 +54,26 @@ def main():
     g = torch.Generator().manual_seed(11)
     fused = eng._symm is not None
     for step in range(a.steps):
-        ids = torch.randint(0, cfg.vocab_size, (world * B, S), generator=g).to(dev)
-        mine = ids[rank * B:(rank + 1) * B]
-        loss = model(mine, labels=mine).loss
-        eng.backward(loss)
+        for micro in range(a.accum):
+            ids = torch.randint(0, cfg.vocab_size, (world * B, S), generator=g).to(dev)
+            mine = ids[rank * B:(rank + 1) * B]
+            loss = model(mine, labels=mine, loss_scale=1.0 / a.accum).loss
+            eng.backward(loss)
+            rl = ref(ids, labels=ids, loss_scale=1.0 / a.accum).loss
+            ref_eng.backward(rl)
         gn = eng.step()
-        rl = ref(ids, labels=ids).loss
-        ref_eng.backward(rl)
         rgn = ref_eng.step()
         if cuda:
             torch.cuda.synchronize()
         assert abs(float(gn) - float(rgn)) < (5e-2 if cuda else 1e-3) * max(1.0, float(rgn)), (float(gn), float(rgn))
     err = 0.0
-    for (n, p), (_, q) in zip(model.named_parameters(), ref.named_parameters()):
-        err = max(err, (p.float() - q.float()).abs().max().item())
+    with eng.summon_full_params():
+        for (n, p), (_, q) in zip(model.named_parameters(), ref.named_parameters()):
+            err = max(err, (p.float() - q.float()).abs().max().item())
+    if a.strategy == "FULL_SHARD" and world > 1:
+        assert all(u.flat_param.untyped_storage().nbytes() == 0 for u in eng.units if u.resharded), \
+            "parameters must be re-sharded after use"
+        assert any(u.resharded for u in eng.units)
     tol = 3e-2 if cuda else a.tol
     ok = err < tol
     flag = torch.tensor([0.0 if ok else 1.0], device=dev)

@@ -14,9 +14,16 @@ def launch(nproc, *args, port=29611, timeout=300):
     return subprocess.run(cmd, capture_output=True, text=True, timeout=timeout)
 
 
-@pytest.mark.parametrize("strategy,port", [("SHARD_GRAD_OP", 29611), ("NO_SHARD", 29612)])
+@pytest.mark.parametrize("strategy,port", [("SHARD_GRAD_OP", 29611), ("NO_SHARD", 29612), ("FULL_SHARD", 29613)])
 def test_two_rank_engine_matches_single_process(strategy, port):
     r = launch(2, "--device", "cpu", "--strategy", strategy, port=port)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+
+
+@pytest.mark.parametrize("extra,port", [(["--recompute"], 29614), (["--accum", "2"], 29615)])
+def test_full_shard_with_recompute_and_accumulation(extra, port):
+    """FULL_SHARD re-gathers inside the recomputation of a layer and reduces every micro-batch into its shard."""
+    r = launch(2, "--device", "cpu", "--strategy", "FULL_SHARD", *extra, port=port)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
     assert "ok=True" in r.stdout
 

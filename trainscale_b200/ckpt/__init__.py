@@ -14,6 +14,8 @@ resume re-slices the flat optimizer shards instead of failing (`reshard_optimize
 """
 from __future__ import annotations
 
+import contextlib
+
 import json
 import os
 import time
@@ -69,12 +71,16 @@ def save_training_checkpoint(trainer, path: Path) -> None:
     try:
         if trainer.is_distributed:
             dist.barrier()
-        if rank == 0:
-            path.mkdir(parents=True, exist_ok=True)
-            save_model_weights(trainer.model, path)
+        eng = trainer.engine
+        # FULL_SHARD keeps only shards between steps: every rank takes part in materialising the weights
+        summon = eng.summon_full_params() if eng is not None and hasattr(eng, "summon_full_params") \
+            else contextlib.nullcontext()
+        with summon:
+            if rank == 0:
+                path.mkdir(parents=True, exist_ok=True)
+                save_model_weights(trainer.model, path)
         if trainer.is_distributed:
             dist.barrier()
-        eng = trainer.engine
         sharded = eng is not None and hasattr(eng, "state_dict")
         if sharded:
             write_shard = eng.cfg.sharding_strategy != "NO_SHARD" or rank == 0 if hasattr(eng, "cfg") else True
@@ -131,12 +137,19 @@ def load_training_checkpoint(trainer, path: Path) -> None:
     if not path.exists():
         raise CheckpointLoadError(f"checkpoint {path} does not exist")
     try:
-        load_model_weights(trainer.model, path, strict=False)
         eng = trainer.engine
+        summon = eng.summon_full_params() if eng is not None and hasattr(eng, "summon_full_params") \
+            else contextlib.nullcontext()
+        with summon:
+            load_model_weights(trainer.model, path, strict=False)
+            if eng is not None and hasattr(eng, "units"):
+                # the flat buffers alias the parameters: refresh the shards and fp32 masters from the loaded weights
+                for u in eng.units:
+                    src = u.flat_param[u.shard_start:u.shard_start + u.shard_numel]
+                    if getattr(u, "resharded", False):
+                        u.param_shard.copy_(src)
+                    u.master.copy_(src)
         if eng is not None and hasattr(eng, "units"):
-            # the flat buffers alias the parameters: refresh the fp32 masters from the loaded weights first
-            for u in eng.units:
-                u.master.copy_(u.flat_param[u.shard_start:u.shard_start + u.shard_numel])
             files = sorted((path / "optim").glob("shard-*.pt")) if (path / "optim").exists() else []
             if files:
                 saved_world = int(files[0].stem.split("-of-")[1])

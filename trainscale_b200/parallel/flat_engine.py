@@ -15,7 +15,9 @@ buffers laid out for the B200 kernels:
     weights back, and an all-gather of the updated shards (peer stores from the update kernel, or NCCL).
 
 Sharding strategies (names as in data_pipeline/trainer/distributed/fsdp2.py:384-406):
-  FULL_SHARD     parameters are re-gathered per unit before forward and before backward
+  FULL_SHARD     every decoder-layer unit keeps only its 1/W bf16 shard; the full buffer is all-gathered into a
+                 recycled pool slot before the unit's forward and again before its backward (next unit prefetched on
+                 the communication stream), gradients are reduce-scattered and their buffer recycled per unit
   SHARD_GRAD_OP  parameters stay gathered between steps (default on 180 GB parts: a full bf16 copy of an
                  8B model is 16 GB), gradients + optimizer state sharded
   NO_SHARD       DDP: gradients all-reduced, every rank holds the full optimizer state
@@ -65,8 +67,15 @@ class FlatUnit:
     """One contiguous parameter/gradient buffer with its optimizer shard."""
 
     def __init__(self, name: str, named_params: list[tuple[str, nn.Parameter]], cfg: EngineConfig, rank: int,
-                 world: int, device, grad_dtype: torch.dtype, alloc: Callable | None = None):
+                 world: int, device, grad_dtype: torch.dtype, alloc: Callable | None = None,
+                 resharded: bool = False):
         self.name, self.cfg, self.rank, self.world = name, cfg, rank, world
+        # FULL_SHARD: between uses only `param_shard` exists; the full buffers come from the engine's pools
+        self.resharded = resharded
+        self.grad_dtype = grad_dtype
+        self.grad_slot = None
+        self.gather_event = None
+        self.gathered = True
         decay = [(n, p) for n, p in named_params if p.dim() > 1 or cfg.decay_norm_and_bias]
         nodecay = [(n, p) for n, p in named_params if not (p.dim() > 1 or cfg.decay_norm_and_bias)]
         self.entries: list[tuple[str, nn.Parameter, int, int]] = []
@@ -82,7 +91,7 @@ class FlatUnit:
         self.shard_start = self.shard_numel * rank if cfg.sharding_strategy != "NO_SHARD" else 0
         alloc = alloc or (lambda n, dt: torch.zeros(n, dtype=dt, device=device))
         self.flat_param = alloc(self.numel, cfg.param_dtype)
-        self.flat_grad = alloc(self.numel, grad_dtype)
+        self.flat_grad = None if resharded else alloc(self.numel, grad_dtype)
         # optimizer shard
         self.master = torch.zeros(self.shard_numel, dtype=torch.float32, device=device)
         self.exp_avg = torch.zeros(self.shard_numel, dtype=torch.float32, device=device)
@@ -95,11 +104,38 @@ class FlatUnit:
             for n, p, o, k in self.entries:
                 self.flat_param[o:o + k].copy_(p.detach().reshape(-1))
                 p.data = self.flat_param[o:o + k].view(p.shape)
-                p.main_grad = self.flat_grad[o:o + k].view(p.shape)
+                if self.flat_grad is not None:
+                    p.main_grad = self.flat_grad[o:o + k].view(p.shape)
                 p.grad_added = False
                 p._ts_unit = self
             s, e = self.shard_start, self.shard_start + self.shard_numel
             self.master.copy_(self.flat_param[s:e])
+        self.shapes = [tuple(p.shape) for _, p, _, _ in self.entries]
+        # alignment gaps between tensors and the tail padding: no kernel writes them, a recycled buffer must zero them
+        self.gaps = [(o + k, nxt) for (_, _, o, k), nxt in
+                     zip(self.entries, [e[2] for e in self.entries[1:]] + [self.numel]) if nxt > o + k]
+        self.param_shard: torch.Tensor | None = None
+
+    # --- FULL_SHARD residency -------------------------------------------------------------------------------
+    # The full parameter buffer of a re-sharded unit keeps ONE storage object for its whole life; releasing it
+    # shrinks that storage to zero bytes and gathering grows it again.  Module parameters and every view autograd
+    # saved during forward (a transposed weight, say) reference the storage, not an address, so they see the
+    # re-gathered values in backward.
+    def free_full_params(self):
+        self.flat_param.untyped_storage().resize_(0)
+        self.gathered = False
+
+    def alloc_full_params(self):
+        self.flat_param.untyped_storage().resize_(self.numel * self.flat_param.element_size())
+
+    @torch.no_grad()
+    def bind_grads(self, buf: torch.Tensor | None):
+        self.flat_grad = buf
+        if buf is not None:
+            for a, b in self.gaps:
+                buf[a:b].zero_()
+        for (n, p, o, k), shp in zip(self.entries, self.shapes):
+            p.main_grad = None if buf is None else buf[o:o + k].view(shp)
 
     # --- segments of this rank's shard with a uniform weight decay
     def segments(self) -> list[_Segment]:
@@ -136,6 +172,50 @@ class _Boundary(torch.autograd.Function):
         return (None, None, *grads)
 
 
+class _PreBackward(torch.autograd.Function):
+    """Identity on a unit's outputs: its backward runs before anything inside the unit is differentiated
+    (FULL_SHARD re-gathers the unit's parameters and binds a gradient buffer there)."""
+
+    @staticmethod
+    def forward(ctx, engine, unit_idx, *tensors):
+        ctx.engine, ctx.unit_idx = engine, unit_idx
+        return tensors if len(tensors) > 1 else tensors[0]
+
+    @staticmethod
+    def backward(ctx, *grads):
+        ctx.engine._unit_pre_backward(ctx.unit_idx)
+        return (None, None, *grads)
+
+
+class _BufferPool:
+    """Recycled full-size buffers (gathered parameters / unit gradients).  A released slot carries the event after
+    which its last user is done; the next user's stream waits on it, so reuse never races across streams."""
+
+    def __init__(self, device):
+        self.device = device
+        self.slots: list[dict] = []
+
+    def acquire(self, numel: int, dtype: torch.dtype, stream):
+        for i, s in enumerate(self.slots):
+            if not s["busy"] and s["buf"].numel() >= numel and s["buf"].dtype == dtype:
+                s["busy"] = True
+                if s["event"] is not None and stream is not None:
+                    stream.wait_event(s["event"])
+                return i, s["buf"][:numel]
+        self.slots.append({"buf": torch.empty(numel, dtype=dtype, device=self.device), "busy": True, "event": None})
+        return len(self.slots) - 1, self.slots[-1]["buf"]
+
+    def release(self, idx: int, stream):
+        s = self.slots[idx]
+        s["busy"] = False
+        if stream is not None:
+            s["event"] = torch.cuda.Event()
+            s["event"].record(stream)
+
+    def bytes(self) -> int:
+        return sum(s["buf"].numel() * s["buf"].element_size() for s in self.slots)
+
+
 class FlatShardedEngine:
     """Owns the flat buffers, the gradient reduction schedule and the sharded optimizer step."""
 
@@ -155,10 +235,15 @@ class FlatShardedEngine:
         self.grad_dtype = grad_dtype
         self.step_count = 0
         self.micro_step = 0
+        self._in_backward = False
+        self._deferred_reduce: list = []
         self.param_groups = [{"lr": cfg.lr, "weight_decay": cfg.weight_decay, "betas": cfg.betas, "eps": cfg.eps,
                               "initial_lr": cfg.lr}]
         self._symm = None
-        if self.distributed and self.is_cuda and cfg.comm in ("auto", "fused"):
+        # FULL_SHARD recycles its gather / gradient buffers between units, which the peer-memory kernels (they read
+        # a peer's buffer without a hand-shake on its reuse) do not allow: it runs on the library collectives
+        self.full_shard = cfg.sharding_strategy == "FULL_SHARD" and self.distributed
+        if self.distributed and self.is_cuda and cfg.comm in ("auto", "fused") and not self.full_shard:
             from . import symm
             self._symm = symm.SymmetricHeap.try_create(self.pg, self.device)
             if self._symm is None and cfg.comm == "fused":
@@ -176,7 +261,7 @@ class FlatShardedEngine:
             seen.update(id(p) for _, p in named)
             gd = torch.float32 if name in ("", "root") else grad_dtype
             self.units.append(FlatUnit(name or "root", named, cfg, self.rank, self.world, self.device, gd,
-                                       self._alloc_fn()))
+                                       self._alloc_fn(), resharded=self.full_shard and name not in ("", "root")))
         rest = [(n, p) for n, p in model.named_parameters() if id(p) not in seen]
         if rest:
             self.units.append(FlatUnit("root", rest, cfg, self.rank, self.world, self.device, torch.float32,
@@ -188,9 +273,15 @@ class FlatShardedEngine:
         self.comm_stream = torch.cuda.Stream(device=self.device, priority=-1) if self.is_cuda else None
         # GEMM / norm epilogues write main_grad directly only on the CUDA bf16 path
         self.direct_grads = self.is_cuda and cfg.param_dtype == torch.bfloat16
+        self._grad_pool = _BufferPool(self.device)
         self._install_boundaries(unit_modules)
         if self.distributed:
             self._sync_initial_params()
+        for u in self.units:
+            if u.resharded:
+                s0 = u.shard_start
+                u.param_shard = u.flat_param[s0:s0 + u.shard_numel].clone()
+                u.free_full_params()      # the construction-time full copy is dropped here
 
     # ------------------------------------------------------------------ construction helpers
     def _alloc_fn(self):
@@ -227,7 +318,11 @@ class FlatShardedEngine:
                     args = list(args)
                     for (i, _), o in zip(tens, outs):
                         args[i] = o
-                return _orig(*args, **kw)
+                res = _orig(*args, **kw)
+                if engine.units[_idx].resharded:
+                    res = engine._wrap_outputs(_idx, res)
+                    engine._unit_post_forward(_idx)
+                return res
 
             mod.forward = wrapped
 
@@ -239,11 +334,118 @@ class FlatShardedEngine:
 
     # ------------------------------------------------------------------ forward / backward scheduling
     def _unit_pre_forward(self, idx: int):
-        pass   # FULL_SHARD re-gather hooks attach here (see parallel/fsdp.py)
+        u = self.units[idx]
+        if not u.resharded:
+            return
+        self._ensure_gathered(idx)
+        nxt = idx + 1                       # prefetch the next unit's parameters behind this unit's compute
+        if torch.is_grad_enabled() and self._in_backward:
+            nxt = idx - 1                   # a recomputation inside backward walks the units downwards
+        if 0 <= nxt < len(self.units) and self.units[nxt].resharded:
+            self._start_gather(nxt)
+
+    def _unit_post_forward(self, idx: int):
+        if self._in_backward:
+            return                          # recomputation: the backward of this unit follows immediately
+        self._release_params(idx)
+
+    def _unit_pre_backward(self, idx: int):
+        u = self.units[idx]
+        self._in_backward = True
+        self._ensure_gathered(idx)
+        if idx - 1 >= 0 and self.units[idx - 1].resharded:
+            self._start_gather(idx - 1)
+        if u.flat_grad is None:
+            u.grad_slot, buf = self._grad_pool.acquire(u.numel, u.grad_dtype, self._cur_stream())
+            u.bind_grads(buf)
+
+    def _wrap_outputs(self, idx: int, res):
+        """Unit outputs pass through a node whose backward runs before anything inside the unit."""
+        if not torch.is_grad_enabled():
+            return res
+        if torch.is_tensor(res):
+            return _PreBackward.apply(self, idx, res) if res.requires_grad else res
+        if isinstance(res, (tuple, list)):
+            pos = [i for i, t in enumerate(res) if torch.is_tensor(t) and t.requires_grad]
+            if not pos:
+                return res
+            outs = _PreBackward.apply(self, idx, *[res[i] for i in pos])
+            outs = outs if isinstance(outs, tuple) else (outs,)
+            lst = list(res)
+            for i, o in zip(pos, outs):
+                lst[i] = o
+            return type(res)(lst) if isinstance(res, tuple) else lst
+        return res
+
+    def _cur_stream(self):
+        return torch.cuda.current_stream() if self.is_cuda else None
+
+    def _start_gather(self, idx: int):
+        """All-gather unit `idx`'s shards into a pool buffer on the communication stream."""
+        u = self.units[idx]
+        if u.gathered or u.gather_event is not None:
+            return
+        stream = self.comm_stream
+        u.alloc_full_params()      # on the compute stream's allocator: its earlier users are ordered before us
+        buf = u.flat_param
+        if stream is not None:
+            # the memory's previous user and the optimizer's update of the shard are both on the compute stream
+            stream.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(stream) if stream is not None else contextlib.nullcontext():
+            if self.is_cuda:
+                dist.all_gather_into_tensor(buf, u.param_shard, group=self.pg)
+                u.gather_event = torch.cuda.Event()
+                u.gather_event.record(stream)
+            else:
+                parts = [torch.empty_like(u.param_shard) for _ in range(self.world)]
+                dist.all_gather(parts, u.param_shard, group=self.pg)
+                buf.copy_(torch.cat(parts))
+                u.gather_event = True
+
+    def _ensure_gathered(self, idx: int):
+        u = self.units[idx]
+        if u.gathered:
+            return
+        if u.gather_event is None:
+            self._start_gather(idx)
+        if self.is_cuda:
+            torch.cuda.current_stream().wait_event(u.gather_event)
+        u.gather_event = None
+        u.gathered = True
+
+    def _release_params(self, idx: int):
+        u = self.units[idx]
+        if not u.gathered or not u.resharded:
+            return
+        u.free_full_params()       # freed on the compute stream, after everything queued there that reads it
+
+    @contextlib.contextmanager
+    def summon_full_params(self):
+        """All parameters materialised (checkpoint export, evaluation hooks); re-sharded on exit."""
+        touched = []
+        for i, u in enumerate(self.units):
+            if u.resharded and not u.gathered:
+                self._ensure_gathered(i)
+                touched.append(i)
+        try:
+            yield
+        finally:
+            for i in touched:
+                self._release_params(i)
 
     def _unit_backward_done(self, idx: int):
         u = self.units[idx]
         u.grad_ready = True
+        if u.resharded:
+            # FULL_SHARD reduces every micro-batch into the fp32 shard.  With the direct-gradient kernels every
+            # weight gradient of the unit is complete here; plain autograd may still hold some back, so that path
+            # reduces when the whole backward has returned.
+            if self.direct_grads:
+                self._launch_reduce(u)
+            else:
+                self._deferred_reduce.append(u)
+            self._release_params(idx)
+            return
         if self._is_sync_step() and self.cfg.overlap_grad_reduce and self.world > 1 and self.direct_grads:
             self._launch_reduce(u)
 
@@ -262,7 +464,13 @@ class FlatShardedEngine:
     def backward(self, loss: torch.Tensor) -> bool:
         """Backward of one micro-batch (the loss is expected to be pre-scaled by 1/accumulation steps,
         which the model's fused loss head does through `loss_scale`). Returns True on a sync boundary."""
-        loss.backward()
+        try:
+            loss.backward()
+        finally:
+            self._in_backward = False
+        for u in self._deferred_reduce:
+            self._launch_reduce(u)
+        self._deferred_reduce.clear()
         sync = self._is_sync_step()
         self.micro_step += 1
         return sync
@@ -289,6 +497,14 @@ class FlatShardedEngine:
     def _launch_reduce(self, u: FlatUnit):
         if u.reduce_event is not None:
             return
+        if u.resharded and u.flat_grad is None:
+            # no backward reached this unit in the current micro-batch: nothing to add to its shard
+            if u.shard_grad is None:
+                u.shard_grad = torch.zeros(u.shard_numel, dtype=torch.float32, device=self.device)
+            elif not getattr(u, "shard_accum", False):
+                u.shard_grad.zero_()
+            u.reduce_event = True
+            return
         self._collect_autograd_grads(u)
         cur = torch.cuda.current_stream() if self.is_cuda else None
         if self.cfg.sharding_strategy == "NO_SHARD":
@@ -312,6 +528,7 @@ class FlatShardedEngine:
 
     def _reduce_scatter(self, u, cur):
         stream = self.comm_stream
+        first = u.shard_grad is None or not getattr(u, "shard_accum", False)
         if u.shard_grad is None:
             u.shard_grad = torch.empty(u.shard_numel, dtype=torch.float32, device=self.device)
         if stream is not None:
@@ -325,16 +542,30 @@ class FlatShardedEngine:
                 if self.is_cuda:
                     tmp = torch.empty(u.shard_numel, dtype=u.flat_grad.dtype, device=self.device)
                     dist.reduce_scatter_tensor(tmp, u.flat_grad, op=dist.ReduceOp.AVG, group=self.pg)
-                    u.shard_grad.copy_(tmp)
+                    red = tmp
                 else:   # gloo has no reduce_scatter_tensor: all-reduce then slice
                     full = u.flat_grad.float()
                     dist.all_reduce(full, group=self.pg)
-                    u.shard_grad.copy_(full[u.shard_start:u.shard_start + u.shard_numel] / self.world)
+                    red = full[u.shard_start:u.shard_start + u.shard_numel] / self.world
+                if u.resharded and not first:
+                    u.shard_grad.add_(red)          # later micro-batches of an accumulation window
+                else:
+                    u.shard_grad.copy_(red)
             if stream is not None:
                 u.reduce_event = torch.cuda.Event()
                 u.reduce_event.record(stream)
             else:
                 u.reduce_event = True
+        if u.resharded:
+            # the full gradient buffer goes back to the pool (its next user waits for this reduction)
+            u.shard_accum = True
+            self._grad_pool.release(u.grad_slot, stream)
+            u.grad_slot = None
+            u.bind_grads(None)
+            for _, p, _, _ in u.entries:
+                p.grad_added = False
+            if not self._is_sync_step():
+                u.reduce_event = None           # the next micro-batch reduces again
 
     # ------------------------------------------------------------------ optimizer step
     def _shard_grad_view(self, u: FlatUnit) -> torch.Tensor:
@@ -377,7 +608,7 @@ class FlatShardedEngine:
             s0 = u.shard_start
             for seg in u.segments():
                 sl = slice(seg.start, seg.end)
-                out = u.flat_param[s0 + seg.start:s0 + seg.end]
+                out = u.param_shard[sl] if u.resharded else u.flat_param[s0 + seg.start:s0 + seg.end]
                 if fused_norm and cfg.optimizer == "adamw":
                     from . import fused_comm
                     fused_comm.adamw_bcast(self._symm, u.flat_param, s0 + seg.start, u.master[sl], u.exp_avg[sl],
@@ -406,6 +637,8 @@ class FlatShardedEngine:
 
     def _all_gather_params(self):
         for u in self.units:
+            if u.resharded:
+                continue                    # stays sharded: re-gathered unit by unit in the next forward
             if self._symm is not None:
                 from . import fused_comm
                 fused_comm.all_gather_inplace(self._symm, u.flat_param, u.shard_start, u.shard_numel)
@@ -424,6 +657,7 @@ class FlatShardedEngine:
         for u in self.units:
             u.mark_grads_fresh()
             u.reduce_event = None
+            u.shard_accum = False
         if self._symm is not None and self.world > 1:
             self.norm_sq.zero_()
             self.nonfinite.zero_()
@@ -452,11 +686,17 @@ class FlatShardedEngine:
             g.update(s)
 
     def full_model_state_dict(self) -> dict[str, torch.Tensor]:
+        if any(u.resharded for u in self.units):
+            with self.summon_full_params():
+                return {n: p.detach().clone() for n, p in self.model.named_parameters()}
         return {n: p.detach() for n, p in self.model.named_parameters()}
 
     def memory_summary(self) -> str:
-        pb = sum(u.flat_param.numel() * u.flat_param.element_size() for u in self.units)
-        gb = sum(u.flat_grad.numel() * u.flat_grad.element_size() for u in self.units)
+        pb = sum(u.flat_param.numel() * u.flat_param.element_size() for u in self.units if not u.resharded) + \
+            sum(u.param_shard.numel() * u.param_shard.element_size() +
+                u.flat_param.untyped_storage().nbytes() for u in self.units if u.resharded)
+        gb = sum(u.flat_grad.numel() * u.flat_grad.element_size() for u in self.units if not u.resharded) + \
+            self._grad_pool.bytes()
         ob = sum(u.master.numel() * 4 * (3 if u.exp_avg_sq is not None else 2) for u in self.units)
         s = f"params {pb / 2**30:.2f} GiB | grads {gb / 2**30:.2f} GiB | optim shard {ob / 2**30:.2f} GiB"
         if self.is_cuda:
