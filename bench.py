@@ -235,7 +235,7 @@ def main():
     ap.add_argument("--seq", type=int, default=SEQ)
     ap.add_argument("--micro-batch", type=int, default=MICRO_BATCH)
     ap.add_argument("--ac", default="auto", choices=["auto", "full", "half", "op_selective", "none"])
-    ap.add_argument("--sharding", default="shard_grad_op", choices=["full", "shard_grad_op", "no_shard"])
+    ap.add_argument("--sharding", default="shard_grad_op", choices=["full", "full_shard", "shard_grad_op", "no_shard"])
     ap.add_argument("--comm", default="auto", choices=["auto", "fused", "nccl"])
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
