@@ -138,7 +138,50 @@ def bench_adamw(t, small):
     return [dict(name=f"adamw_flat n={n}", ms=ms, baseline_ms=None, gbs=n * 28 / ms / 1e6)]
 
 
-CASES = {"rmsnorm": bench_rmsnorm, "swiglu": bench_swiglu, "rope": bench_rope, "cross_entropy": bench_cross_entropy,
+def bench_fp8(t, small):
+    from .ops import fp8
+    out = []
+    for M, N, K in ([(4096, 4096, 4096)] if small else [(8192, 4096, 4096), (8192, 28672, 4096), (8192, 4096, 14336)]):
+        x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+        w = (torch.randn(N, K, device="cuda") / K ** 0.5).to(torch.bfloat16)
+        xq, xs = fp8.quant_act(x)
+        wq, ws = fp8.quant_block(w)
+        ms = t(lambda: fp8.gemm_fp8(xq, xs, wq, ws, N))
+        out.append(dict(name=f"fp8_gemm {M}x{N}x{K}", ms=ms, baseline_ms=None, tflops=2 * M * N * K / ms / 1e9))
+        ms = t(lambda: fp8.quant_act(x))
+        out.append(dict(name=f"fp8_quant_act {M}x{K}", ms=ms, baseline_ms=None, gbs=M * K * 3 / ms / 1e6))
+    return out
+
+
+def bench_moe(t, small):
+    from .ops import moe
+    out = []
+    for T, H, I, E, k in ([(4096, 2048, 1024, 8, 2)] if small else [(8192, 4096, 1792, 8, 2), (8192, 2048, 1024, 64, 6)]):
+        x = torch.randn(T, H, device="cuda", dtype=torch.bfloat16)
+        wgu = (torch.randn(E, 2 * I, H, device="cuda") * 0.02).to(torch.bfloat16)
+        wd = (torch.randn(E, H, I, device="cuda") * 0.02).to(torch.bfloat16)
+        w, ids = torch.softmax(torch.randn(T, E, device="cuda"), -1).topk(k, -1)
+        w = w.to(torch.bfloat16)
+        ms = t(lambda: moe.moe_ffn(x, ids, w, wgu, wd))
+        out.append(dict(name=f"moe_ffn fwd T={T} H={H} I={I} E={E} k={k}", ms=ms, baseline_ms=None,
+                        tflops=2 * T * k * H * I * 3 / ms / 1e9))
+    return out
+
+
+def bench_layernorm(t, small):
+    from .ops import norm
+    out = []
+    for rows, H in ([(8192, 4096)] if small else [(8192, 4096), (32768, 4096), (16384, 8192)]):
+        x = torch.randn(rows, H, device="cuda", dtype=torch.bfloat16)
+        w = torch.ones(H, device="cuda", dtype=torch.bfloat16)
+        b = torch.zeros(H, device="cuda", dtype=torch.bfloat16)
+        ms = t(lambda: norm.layernorm(x, w, b))
+        base = t(lambda: F.layer_norm(x, (H,), w, b))
+        out.append(dict(name=f"layernorm_fwd {rows}x{H}", ms=ms, baseline_ms=base, gbs=rows * H * 4 / ms / 1e6))
+    return out
+
+
+CASES = {"fp8": bench_fp8, "moe": bench_moe, "layernorm": bench_layernorm, "rmsnorm": bench_rmsnorm, "swiglu": bench_swiglu, "rope": bench_rope, "cross_entropy": bench_cross_entropy,
          "gemm": bench_gemm, "attention": bench_attention, "adamw": bench_adamw}
 
 
