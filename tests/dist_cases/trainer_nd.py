@@ -1,0 +1,91 @@
+"""torchrun case: SOTATrainer driven by a config dict with pipeline or tensor+sequence parallelism.  Every step's loss
+must match a single-process trainer fed the same global batches."""
+import argparse
+import os
+import sys
+from pathlib import Path
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, str(Path(__file__).resolve().parents[2]))
+
+from trainscale_b200.config.sota_config import SOTAConfig  # noqa: E402
+from trainscale_b200.models.llama import LlamaConfig, build_model  # noqa: E402
+from trainscale_b200.trainer.sota_trainer import SOTATrainer  # noqa: E402
+
+
+def make_cfg(strategy, parallel, world, enabled):
+    return SOTAConfig.from_dict({
+        "training_mode": "full",
+        "model": {"architecture": "llama-tiny"},
+        "optimizer": {"type": "adamw", "learning_rate": 1e-2, "weight_decay": 0.0, "max_grad_norm": 1.0, "eps": 1e-3},
+        "scheduler": {"type": "constant", "warmup_steps": 0},
+        "loss": {"type": "chunked_ce"},
+        "distributed": {"enabled": enabled, "backend": "gloo", "strategy": strategy, "world_size": world,
+                        "gradient_checkpointing": False, "parallel": parallel, "comm": "nccl"},
+        "hardware": {"precision": "fp32", "device": "cpu"},
+        "data": {"max_seq_length": 32},
+        "training": {"per_device_train_batch_size": 4, "gradient_accumulation_steps": 1, "max_steps": 100,
+                     "logging_steps": 10 ** 9, "save_strategy": "no", "eval_strategy": "no",
+                     "output_dir": "/tmp/ts_nd_case"},
+    })
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--mode", default="pp", choices=["pp", "sp"])
+    a = ap.parse_args()
+    dist.init_process_group("gloo")
+    rank, world = dist.get_rank(), dist.get_world_size()
+    mcfg = LlamaConfig(vocab_size=256, hidden_size=64, intermediate_size=128, num_hidden_layers=4,
+                       num_attention_heads=4, num_key_value_heads=2, head_dim=16)
+    if a.mode == "pp":
+        par = {"pp": world, "dp_shard": 1, "pp_schedule": "1f1b", "pp_microbatches": 2}
+        strategy, B = "pipeline", 4
+    else:
+        par = {"tp": world, "dp_shard": 1, "sp": True}
+        strategy, B = "tensor_parallel", 1
+    tr = SOTATrainer(make_cfg(strategy, par, world, True))
+    tr.setup_model(model=build_model(mcfg, dtype=torch.float32, device="cpu", seed=7))
+    tr.setup_optimizer()
+    tr.setup_scheduler(100)
+    # oracle: same model alone
+    saved_init, saved_ws = dist.is_initialized, dist.get_world_size
+    ref = SOTATrainer.__new__(SOTATrainer)
+    env_ws = os.environ["WORLD_SIZE"]
+    try:
+        dist.is_initialized = lambda: False
+        os.environ["WORLD_SIZE"] = "1"
+        ref.__init__(make_cfg("single", {}, 1, False))
+        ref.setup_model(model=build_model(mcfg, dtype=torch.float32, device="cpu", seed=7))
+        ref.setup_optimizer()
+        ref.setup_scheduler(100)
+    finally:
+        dist.is_initialized = saved_init
+        os.environ["WORLD_SIZE"] = env_ws
+    g = torch.Generator().manual_seed(5)
+    ok = True
+    for step in range(3):
+        ids = torch.randint(0, 256, (B, 32), generator=g)
+        l1 = tr.train_step({"input_ids": ids, "labels": ids})
+        try:
+            dist.is_initialized = lambda: False
+            l0 = ref.train_step({"input_ids": ids, "labels": ids})
+        finally:
+            dist.is_initialized = saved_init
+        good = abs(l1 - l0) < 2e-3 * max(1.0, abs(l0))
+        ok &= good
+        if rank == 0:
+            print(f"step {step} mode={a.mode} loss={l1:.5f} oracle={l0:.5f} ok={good}", flush=True)
+    flag = torch.tensor([0.0 if ok else 1.0])
+    dist.all_reduce(flag)
+    if rank == 0:
+        print(f"RESULT mode={a.mode} ok={flag.item() == 0}")
+    dist.barrier()
+    dist.destroy_process_group()
+    sys.exit(0 if flag.item() == 0 else 1)
+
+
+if __name__ == "__main__":
+    main()

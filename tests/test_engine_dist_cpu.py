@@ -84,3 +84,16 @@ def test_expert_parallel_moe_matches_local_moe():
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=300)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
     assert r.stdout.count("ok=True") == 2
+
+
+ND_CASE = Path(__file__).parent / "dist_cases" / "trainer_nd.py"
+
+
+@pytest.mark.parametrize("mode,port", [("pp", 29621), ("sp", 29622)])
+def test_trainer_config_drives_pipeline_and_sequence_parallel(mode, port):
+    """SOTATrainer with `distributed.strategy: pipeline` (1F1B, 2 micro-batches) and with tensor + sequence
+    parallelism reproduces the single-process losses step by step (global grad-norm clip included)."""
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+           "127.0.0.1", "--master-port", str(port), str(ND_CASE), "--mode", mode]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]

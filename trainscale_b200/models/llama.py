@@ -231,6 +231,13 @@ class LlamaModel(nn.Module):
             need = max(need, self.cfg.max_position_embeddings if self.cfg.max_position_embeddings <= 1 << 17 else need)
         cos, sin = self.rope_tables(x.device, need)
         residual = None
+        sp = getattr(self, "sp_ctx", None)
+        if sp is not None:
+            # sequence parallelism: the residual stream between blocks holds S / tp tokens per rank
+            from ..parallel import tp as TP
+            if x.shape[0] != 1:
+                raise ValueError("sequence-parallel training expects one sequence per micro-batch")
+            x = TP.scatter_to_sequence_parallel_region(x.view(S, -1), sp).view(1, S // sp.size, -1)
         for i, layer in enumerate(self.layers):
             cache = None if kv_caches is None else kv_caches[i]
             ck = getattr(self, "checkpoint_layers", None)
@@ -241,7 +248,26 @@ class LlamaModel(nn.Module):
             else:
                 x, residual = layer(x, residual, cos, sin, position_ids, cu_seqlens, doc_ids, cache)
         x, _ = self.norm(x, residual)
+        if sp is not None:
+            from ..parallel import tp as TP
+            # every rank then computes the full loss on the gathered tokens: the backward of the gather sums the
+            # tp copies of the gradient, so it is divided by tp here
+            x = TP.all_gather_from_sequence_parallel_region(x.view(S // sp.size, -1), sp).view(1, S, -1)
+            x = _ScaleGrad.apply(x, 1.0 / sp.size)
         return x
+
+
+class _ScaleGrad(torch.autograd.Function):
+    """Identity whose backward multiplies the gradient by a constant."""
+
+    @staticmethod
+    def forward(ctx, x, scale):
+        ctx.scale = scale
+        return x.view_as(x)
+
+    @staticmethod
+    def backward(ctx, g):
+        return g * ctx.scale, None
 
 
 class LlamaForCausalLM(nn.Module):

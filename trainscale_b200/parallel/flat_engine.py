@@ -220,10 +220,12 @@ class FlatShardedEngine:
     """Owns the flat buffers, the gradient reduction schedule and the sharded optimizer step."""
 
     def __init__(self, model: nn.Module, cfg: EngineConfig, process_group=None, device=None,
-                 unit_modules: list[tuple[str, nn.Module]] | None = None):
+                 unit_modules: list[tuple[str, nn.Module]] | None = None, solo: bool = False):
+        """`solo`: this rank shares its parameters with nobody (a data-parallel group of one inside a larger job,
+        e.g. pure pipeline or tensor parallelism): no collective is ever issued."""
         self.model, self.cfg = model, cfg
         self.pg = process_group
-        self.distributed = dist.is_available() and dist.is_initialized() and \
+        self.distributed = (not solo) and dist.is_available() and dist.is_initialized() and \
             dist.get_world_size(process_group) > 1
         self.world = dist.get_world_size(process_group) if self.distributed else 1
         self.rank = dist.get_rank(process_group) if self.distributed else 0
@@ -237,6 +239,9 @@ class FlatShardedEngine:
         self.micro_step = 0
         self._in_backward = False
         self._deferred_reduce: list = []
+        self.norm_groups: list = []
+        self.replicated_params: list = []
+        self.replica_factor = 1
         self.param_groups = [{"lr": cfg.lr, "weight_decay": cfg.weight_decay, "betas": cfg.betas, "eps": cfg.eps,
                               "initial_lr": cfg.lr}]
         self._symm = None
@@ -599,6 +604,20 @@ class FlatShardedEngine:
         if self.world > 1 and cfg.sharding_strategy != "NO_SHARD":
             dist.all_reduce(self.norm_sq, group=self.pg)
             dist.all_reduce(self.nonfinite, op=dist.ReduceOp.MAX, group=self.pg)
+        if self.replicated_params and self.world == 1:
+            # parameters replicated over a tensor-parallel group would be counted once per rank by the all-reduce
+            # below: keep 1/tp of their share here (their gradients are identical on every rank of that group)
+            rep = torch.zeros_like(self.norm_sq)
+            for p in self.replicated_params:
+                g = getattr(p, "main_grad", None)
+                if g is not None:
+                    rep += g.float().pow(2).sum()
+            self.norm_sq -= rep * (1.0 - 1.0 / self.replica_factor)
+        for g in self.norm_groups:
+            # model-parallel groups whose ranks hold disjoint parameters (pipeline stages): the clip uses the norm
+            # of the whole model
+            dist.all_reduce(self.norm_sq, group=g)
+            dist.all_reduce(self.nonfinite, op=dist.ReduceOp.MAX, group=g)
         self.last_grad_norm = self.norm_sq.sqrt()
         self.step_count += 1
         b1, b2 = self.param_groups[0]["betas"]

@@ -16,33 +16,95 @@ class NDEngine:
         cfg = trainer.config
         self.dims = create_parallel_dims_from_config(cfg.distributed)
         self.strategy = strategy
+        self.trainer = trainer
         model = trainer.model
         p = cfg.distributed.parallel
+        self.tp = None
+        self.pipelined = False
+        gas = max(1, cfg.training.gradient_accumulation_steps)
+        overlap = True
         if self.dims.enabled("tp"):
             from . import tp as TP
-            heap = None
-            ctx = TP.TPContext.from_group(self.dims.group("tp"), p.sp, "nccl", heap)
-            if p.sp:
-                raise NotImplementedError("sequence-parallel training through SOTATrainer: use parallel/tp.py directly")
+            ctx = TP.TPContext.from_group(self.dims.group("tp"), p.sp, "nccl", None)
             TP.shard_model_for_tensor_parallel(model, ctx)
             self.tp = ctx
+            if p.sp:
+                # token-sharded residual stream between blocks (see LlamaModel.forward); the norm-weight gradients
+                # are summed over the tp group after backward, before the data-parallel reduction
+                model.model.sp_ctx = ctx
+                overlap = False
         if self.dims.enabled("cp"):
             g = self.dims.group("cp")
             for layer in model.model.layers:
                 attn = getattr(layer.self_attn, "inner", layer.self_attn)
                 attn.cp_group = g
             self.cp_group = g
+        opt_model = model
         if self.dims.enabled("pp"):
-            raise NotImplementedError("pipeline training through SOTATrainer: use parallel/pp.PipelineRuntime directly")
+            from . import pp as PP
+            P, stage = self.dims.size("pp"), self.dims.local_rank("pp")
+            self.pp_ranks = self.dims.group_ranks("pp")
+            self.stage_module = PP.split_model_into_stages(model, P, stage)
+            mine = {id(l) for l in self.stage_module.layers}
+            for i, layer in enumerate(model.model.layers):     # other stages' layers are dropped on this rank
+                if id(layer) not in mine:
+                    model.model.layers[i] = torch.nn.Identity()
+            self.runtime = PP.PipelineRuntime(self.stage_module, stage, P, group=None, schedule=p.pp_schedule,
+                                              prev_rank=self.pp_ranks[stage - 1] if stage > 0 else None,
+                                              next_rank=self.pp_ranks[stage + 1] if stage < P - 1 else None)
+            self.pp_microbatches = int(p.pp_microbatches or 0)
+            self.pipelined = True
+            opt_model = self.stage_module
+            overlap = False            # the schedule interleaves micro-batches: reduce once, in step()
+            gas = gas * max(1, self.pp_microbatches or 1)
         ec = EngineConfig(sharding_strategy="SHARD_GRAD_OP", param_dtype=trainer.dtype,
-                          gradient_accumulation_steps=cfg.training.gradient_accumulation_steps,
+                          gradient_accumulation_steps=gas, overlap_grad_reduce=overlap,
                           max_grad_norm=cfg.optimizer.max_grad_norm, lr=cfg.optimizer.learning_rate,
                           betas=tuple(cfg.optimizer.betas), eps=cfg.optimizer.eps, weight_decay=cfg.optimizer.weight_decay,
                           comm="nccl")
+        if self.pipelined and ec.grad_dtype is None:
+            ec.grad_dtype = torch.float32     # gradients of several micro-batches accumulate in the buffers
         # gradients are averaged over every rank that saw different tokens of the same weights: dp x cp
-        self.flat = FlatShardedEngine(model, ec, process_group=self.dims.group("dp_cp"), device=trainer.device)
+        self.flat = FlatShardedEngine(opt_model, ec, process_group=self.dims.group("dp_cp"), device=trainer.device,
+                                      solo=self.dims.size("dp_cp") == 1)
+        if self.pipelined:
+            self.flat.norm_groups.append(self.dims.group("pp"))
+        if self.tp is not None:
+            # sharded weights contribute once per shard, replicated ones (norms, embeddings, head) once in total
+            self.flat.norm_groups.append(self.dims.group("tp"))
+            self.flat.replicated_params = [q for n, q in opt_model.named_parameters()
+                                           if q.dim() == 1 or "embed_tokens" in n or "lm_head" in n]
+            self.flat.replica_factor = self.dims.size("tp")
         self.param_groups = self.flat.param_groups
         self.cfg = ec
+
+    # ------------------------------------------------------------------ pipeline step
+    def forward_backward(self, batch: dict, loss_scale: float):
+        """Runs the pipeline schedule over the micro-batches of `batch`; returns (loss, token count) on every stage
+        (the last stage's values are broadcast over the pipeline group for logging)."""
+        from . import pp as PP
+        B, S = batch["input_ids"].shape
+        M = self.pp_microbatches or B
+        if B % M != 0:
+            raise ValueError(f"batch of {B} sequences does not split into {M} pipeline micro-batches")
+        mbs = PP.split_into_microbatches({k: v for k, v in batch.items() if torch.is_tensor(v)}, M)
+        H = self.stage_module.config.hidden_size
+        act_shape = (B // M, S, 2 * H)
+        dev = batch["input_ids"].device
+        loss = self.runtime.train_step(mbs, act_shape, self.trainer.dtype, dev, extra_scale=loss_scale)
+        lc = self.trainer.config.loss
+        labels = batch.get("labels", batch["input_ids"])
+        ntok = (labels[..., 1:] != lc.ignore_index).sum()
+        out = torch.zeros(1, dtype=torch.float32, device=dev)
+        if loss is not None:
+            out[0] = loss.float()
+        dist.broadcast(out, src=self.pp_ranks[-1], group=self.dims.group("pp"))
+        if getattr(self.stage_module, "_tied", False) or (self.stage_module.first and
+                                                          self.stage_module.config.tie_word_embeddings):
+            PP.allreduce_tied_embedding_grads(self.stage_module, self.dims.group("pp"), self.pp_ranks[0],
+                                              self.pp_ranks[-1])
+        self.flat.micro_step += 1
+        return out[0], ntok
 
     def shard_batch(self, batch: dict) -> dict:
         if self.dims.enabled("cp"):
@@ -51,7 +113,11 @@ class NDEngine:
         return batch
 
     def backward(self, loss):
-        return self.flat.backward(loss)
+        sync = self.flat.backward(loss)
+        if self.tp is not None and self.tp.sequence_parallel:
+            from . import tp as TP
+            TP.allreduce_sequence_parallel_grads(self.trainer.model, self.tp)
+        return sync
 
     def step(self, lr=None):
         return self.flat.step(lr)

@@ -286,9 +286,11 @@ class PipelineRuntime:
         self.stats["recv_bytes"] += buf.numel() * buf.element_size()
         return buf, dist.irecv(buf, src, group=self.group)
 
-    def train_step(self, microbatches: Sequence[dict], act_shape: tuple, act_dtype, device) -> torch.Tensor | None:
+    def train_step(self, microbatches: Sequence[dict], act_shape: tuple, act_dtype, device,
+                   extra_scale: float = 1.0) -> torch.Tensor | None:
         """Runs all micro-batches through this stage; returns the mean loss on the last stage (None elsewhere).
-        `act_shape` is the packed activation shape [mb, S, 2H] exchanged between stages."""
+        `act_shape` is the packed activation shape [mb, S, 2H] exchanged between stages; `extra_scale` multiplies
+        every micro-batch loss (gradient accumulation over several pipeline steps)."""
         M = len(microbatches)
         acts = create_schedule(self.schedule_name, self.stage, self.P, M)
         split = any(a.op == W_OP for a in acts)
@@ -308,7 +310,7 @@ class PipelineRuntime:
                     x.requires_grad_(True)
                 inputs[a.mb] = x
                 if self.last:
-                    out = self.mod(x, labels=mb.get("labels", mb["input_ids"]), loss_scale=1.0 / M)
+                    out = self.mod(x, labels=mb.get("labels", mb["input_ids"]), loss_scale=extra_scale / M)
                     losses.append(out.detach())
                 else:
                     out = self.mod(x)

@@ -267,7 +267,19 @@ class SOTATrainer:
 
     # ------------------------------------------------------------------ one micro-step
     def _to_device(self, batch: Dict[str, Any]) -> Dict[str, Any]:
-        return {k: (v.to(self.device, non_blocking=True) if torch.is_tensor(v) else v) for k, v in batch.items()}
+        batch = {k: (v.to(self.device, non_blocking=True) if torch.is_tensor(v) else v) for k, v in batch.items()}
+        if self.engine is not None and hasattr(self.engine, "shard_batch"):
+            batch = self.engine.shard_batch(batch)     # context parallelism: this rank's sequence chunks
+        return batch
+
+    def _loss_and_backward(self, batch: Dict[str, Any], loss_scale: float):
+        """Forward + backward of one micro-batch.  A pipeline engine runs its own schedule over the batch."""
+        if self.engine is not None and hasattr(self.engine, "forward_backward") and self.engine.pipelined:
+            return self.engine.forward_backward(batch, loss_scale)
+        loss, ntok = self._forward_loss(batch, loss_scale)
+        if self.engine is not None:
+            self.engine.backward(loss)
+        return loss, ntok
 
     def _forward_loss(self, batch: Dict[str, Any], loss_scale: float):
         """Returns (scaled loss, valid-token count tensor)."""
@@ -277,7 +289,8 @@ class SOTATrainer:
             out = m(input_ids=batch["input_ids"], attention_mask=batch.get("attention_mask"),
                     labels=batch.get("labels", batch["input_ids"]), position_ids=batch.get("position_ids"),
                     doc_ids=batch.get("document_ids"), cu_seqlens=batch.get("cu_seqlens"), loss_scale=loss_scale,
-                    label_smoothing=lc.label_smoothing, ignore_index=lc.ignore_index)
+                    label_smoothing=lc.label_smoothing, ignore_index=lc.ignore_index,
+                    shift_labels=not batch.get("labels_shifted", False))
             return out.loss, out.num_tokens
         out = m(**{k: v for k, v in batch.items() if k in ("input_ids", "attention_mask", "labels")})
         loss = out.loss if hasattr(out, "loss") and out.loss is not None else None
@@ -315,12 +328,12 @@ class SOTATrainer:
             self.setup_scheduler(max(1, self.config.training.max_steps))
         self.model.train()
         batch = self._to_device(batch)
-        loss, _ = self._forward_loss(batch, 1.0)
         if self.engine is not None:
             self.engine.micro_step = max(1, self.config.training.gradient_accumulation_steps) - 1
-            self.engine.backward(loss)
+            loss, _ = self._loss_and_backward(batch, 1.0)
             self.engine.step(self.optimizer.param_groups[0]["lr"])
         else:
+            loss, _ = self._forward_loss(batch, 1.0)
             self._generic_backward_step(loss, True)
         self.scheduler.step()
         self.state.global_step += 1
@@ -374,13 +387,13 @@ class SOTATrainer:
                     step_tokens = 0
                 batch = self._to_device(batch)
                 step_tokens += int(batch["input_ids"].numel())
-                loss, ntok = self._forward_loss(batch, 1.0 / gas)
                 sync = (step + 1) % gas == 0
                 if self.engine is not None:
-                    self.engine.backward(loss)
+                    loss, ntok = self._loss_and_backward(batch, 1.0 / gas)
                     if sync:
                         last_gn = self.engine.step(self.optimizer.param_groups[0]["lr"])
                 else:
+                    loss, ntok = self._forward_loss(batch, 1.0 / gas)
                     gn = self._generic_backward_step(loss, sync)
                     if gn is not None:
                         last_gn = gn.detach()
