@@ -89,3 +89,75 @@ def test_async_stream_and_server_app():
     app = create_openai_server(eng)
     paths = {r.path for r in app.routes}
     assert {"/v1/completions", "/v1/chat/completions", "/health", "/metrics"} <= paths
+
+
+def _tiny_lm(seed, layers=2, vocab=97):
+    from trainscale_b200.models.llama import LlamaConfig, build_model
+    cfg = LlamaConfig(vocab_size=vocab, hidden_size=64, intermediate_size=128, num_hidden_layers=layers,
+                      num_attention_heads=4, num_key_value_heads=2, head_dim=16, max_position_embeddings=256)
+    return build_model(cfg, dtype=torch.float32, device="cpu", seed=seed).eval()
+
+
+def test_speculative_greedy_equals_target_greedy():
+    from trainscale_b200.inference.speculative import greedy_generate, speculative_generate
+    target, draft = _tiny_lm(1), _tiny_lm(2, layers=1)
+    prompt = [5, 17, 3, 42, 8]
+    want = greedy_generate(target, prompt, 24)
+    got, stats = speculative_generate(target, draft, prompt, 24, k=4)
+    assert got == want
+    assert stats.proposed > 0 and 0.0 <= stats.acceptance_rate <= 1.0
+    # a draft identical to the target is always accepted: k + 1 tokens per target forward
+    got2, stats2 = speculative_generate(target, target, prompt, 24, k=3)
+    assert got2 == want and stats2.acceptance_rate == 1.0
+    assert stats2.target_forwards <= 1 + (24 + 3) // 4 + 1
+
+
+def test_speculative_sampling_runs_and_respects_eos():
+    from trainscale_b200.inference.speculative import speculative_generate
+    target, draft = _tiny_lm(1), _tiny_lm(3, layers=1)
+    g = torch.Generator().manual_seed(0)
+    out, stats = speculative_generate(target, draft, [1, 2, 3], 16, k=3, temperature=0.8, generator=g)
+    assert 1 <= len(out) <= 16 and all(0 <= t < 97 for t in out)
+    out2, _ = speculative_generate(target, draft, [1, 2, 3], 16, k=3, temperature=0.0, eos_token_id=out[0])
+    assert len(out2) >= 1
+
+
+def test_lora_adapter_registry_switches_weights():
+    from trainscale_b200.inference.speculative import LoRAAdapterRegistry
+    from trainscale_b200.lora import get_peft_model
+    m = get_peft_model(_tiny_lm(4), r=4, lora_alpha=8.0)
+    ids = torch.tensor([[3, 9, 27, 81]])
+    reg = LoRAAdapterRegistry(m, max_loras=2)
+    base = m(input_ids=ids).logits.clone()
+    for name, seed in (("a", 10), ("b", 11), ("c", 12)):
+        torch.manual_seed(seed)
+        for n, p in m.named_parameters():
+            if n.endswith("lora_B"):
+                p.data.normal_(std=0.05)
+        reg.register(name)
+    outs = {}
+    for name in ("a", "b", "c", "a"):
+        reg.activate(name)
+        outs.setdefault(name, []).append(m(input_ids=ids).logits.clone())
+    assert not torch.allclose(outs["a"][0], outs["b"][0]) and not torch.allclose(outs["b"][0], outs["c"][0])
+    assert torch.allclose(outs["a"][0], outs["a"][1])         # came back from the offloaded copy unchanged
+    reg.activate(None)
+    assert torch.allclose(m(input_ids=ids).logits, base, atol=1e-6)
+    groups = reg.group_requests(["a", None, "b", "a", None])
+    assert groups[0][0] is None and sorted(i for _, g in groups for i in g) == [0, 1, 2, 3, 4]
+
+
+def test_engine_generate_with_speculative_config_matches_plain_engine():
+    from trainscale_b200.inference.engine import EngineConfig, GenerationParams, SOTAInferenceEngine
+    target, draft = _tiny_lm(1, vocab=300), _tiny_lm(2, layers=1, vocab=300)   # the byte tokenizer's id range
+    cfg = EngineConfig()
+    plain = SOTAInferenceEngine(cfg, model=target)
+    params = GenerationParams(max_tokens=12, temperature=0.0)
+    want = plain.generate("hello world", params).unwrap()
+    cfg2 = EngineConfig()
+    cfg2.speculative.enabled = True
+    cfg2.speculative.num_speculative_tokens = 3
+    spec = SOTAInferenceEngine(cfg2, model=target, draft_model=draft)
+    got = spec.generate("hello world", params).unwrap()
+    assert got.token_ids == want.token_ids
+    assert 0.0 <= got.speculative_acceptance <= 1.0

@@ -535,13 +535,42 @@ class EngineBuilder:
 
 
 class SOTAInferenceEngine:
-    def __init__(self, config: EngineConfig | None = None, model=None, tokenizer=None):
+    def __init__(self, config: EngineConfig | None = None, model=None, tokenizer=None, draft_model=None):
         self.config = config or EngineConfig()
         self.core = EngineCore(self.config, model, tokenizer)
+        self.draft_model = draft_model      # small model of the same vocabulary for `speculative.enabled`
+
+    def _generate_speculative(self, prompts: list[str], params: GenerationParams) -> list["InferenceResponse"]:
+        """One request at a time through draft-and-verify decoding (inference/speculative.py)."""
+        from .speculative import speculative_generate
+        out = []
+        for p in prompts:
+            r = self.core.add_request(p, params)
+            self.core.waiting.remove(r)
+            gen = r.generator
+            t0 = time.perf_counter()
+            ids, stats = speculative_generate(self.core.model, self.draft_model, r.prompt_ids, params.max_tokens,
+                                              k=self.config.speculative.num_speculative_tokens,
+                                              temperature=params.temperature, eos_token_id=self.core.tokenizer.eos_token_id,
+                                              generator=gen)
+            r.output_ids = ids
+            r.finish_reason = "stop" if ids and ids[-1] == self.core.tokenizer.eos_token_id else "length"
+            r.metrics.completion_tokens = len(ids)
+            r.metrics.first_token = t0
+            r.metrics.finished = time.perf_counter()
+            self.core.metrics.add(r.metrics)
+            resp = InferenceResponse(r.request_id, r.prompt, self.core.decode_text(r), list(ids), r.finish_reason, r.metrics,
+                                     None)
+            resp.speculative_acceptance = stats.acceptance_rate
+            out.append(resp)
+        return out
 
     def generate(self, prompts: str | Iterable[str], params: GenerationParams | None = None) -> Result:
         try:
             single = isinstance(prompts, str)
+            if self.config.speculative.enabled and self.draft_model is not None:
+                res = self._generate_speculative([prompts] if single else list(prompts), params or GenerationParams())
+                return Ok(res[0] if single else res)
             reqs = [self.core.add_request(p, params) for p in ([prompts] if single else list(prompts))]
             while self.core.has_unfinished():
                 self.core.step()
