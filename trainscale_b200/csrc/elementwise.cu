@@ -25,6 +25,14 @@ __device__ __forceinline__ void load8(const __nv_bfloat16* p, float* f) {
     f[2 * i + 1] = t.y;
   }
 }
+__device__ __forceinline__ void unpack8(const bf16x8& r, float* f) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 t = unpack_bf16x2(r.v[i]);
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
 __device__ __forceinline__ void store8(__nv_bfloat16* p, const float* f) {
   bf16x8 r;
 #pragma unroll
@@ -93,10 +101,75 @@ __global__ void __launch_bounds__(NORM_THREADS) rmsnorm_fwd_kernel(const __nv_bf
   }
 }
 
+// Warp-per-row forward for rows of up to 32 * VPL vectors (H <= 4096 with VPL = 16): the whole row sits in the
+// warp's registers, the reduction is shuffle-only, and a warp keeps VPL independent 16-byte loads in flight.  Warps
+// walk rows with a grid stride, so there is no per-row CTA launch.
+template <int VPL>
+__global__ void __launch_bounds__(128) rmsnorm_fwd_warp_kernel(const __nv_bfloat16* __restrict__ x,
+                                                               const __nv_bfloat16* __restrict__ residual,
+                                                               const __nv_bfloat16* __restrict__ w,
+                                                               __nv_bfloat16* __restrict__ y,
+                                                               __nv_bfloat16* __restrict__ res_out,
+                                                               float* __restrict__ rstd_out, long long rows, int H,
+                                                               float eps, float w_offset) {
+  const int lane = threadIdx.x & 31;
+  const int nvec = H >> 3;
+  const long long warps = static_cast<long long>(gridDim.x) * (blockDim.x >> 5);
+  for (long long row = blockIdx.x * static_cast<long long>(blockDim.x >> 5) + (threadIdx.x >> 5); row < rows;
+       row += warps) {
+    const __nv_bfloat16* xr = x + row * H;
+    float f[VPL][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int c = 0; c < VPL; ++c) {
+      const int i = lane + c * 32;
+      if (i < nvec) load8(xr + i * 8, f[c]);
+    }
+    if (residual) {
+#pragma unroll
+      for (int c = 0; c < VPL; ++c) {
+        const int i = lane + c * 32;
+        if (i < nvec) {
+          float r[8];
+          load8(residual + row * H + i * 8, r);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) f[c][e] += r[e];
+          store8(res_out + row * H + i * 8, f[c]);
+          // the sum is rounded to bf16 exactly as the stored residual stream is
+#pragma unroll
+          for (int e = 0; e < 8; ++e) f[c][e] = __bfloat162float(__float2bfloat16(f[c][e]));
+        }
+      }
+    }
+#pragma unroll
+    for (int c = 0; c < VPL; ++c) {
+      if (lane + c * 32 < nvec) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) ss += f[c][e] * f[c][e];
+      }
+    }
+    ss = warp_sum(ss);
+    const float rstd = rsqrtf(ss / H + eps);
+    if (lane == 0 && rstd_out) rstd_out[row] = rstd;
+#pragma unroll
+    for (int c = 0; c < VPL; ++c) {
+      const int i = lane + c * 32;
+      if (i < nvec) {
+        float wv[8];
+        load8(w + i * 8, wv);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) f[c][e] = f[c][e] * rstd * (wv[e] + w_offset);
+        store8(y + row * H + i * 8, f[c]);
+      }
+    }
+  }
+}
+
 // RMSNorm backward. Each CTA walks rows blockIdx.x, +gridDim.x, ... ; dx is written per row and the
 // weight gradient is accumulated in registers and written as one fp32 partial row per CTA
 // (dw_partial[gridDim.x][H]); rmsnorm_dw_reduce_kernel sums the partials. `dres` (optional) is an extra
 // gradient flowing into the same tensor (the residual branch) and is added into dx.
+template <int MAXV>   // vectors per thread kept in registers: rows of up to 256 * MAXV * 8 elements
 __global__ void __launch_bounds__(NORM_THREADS) rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy,
                                                                    const __nv_bfloat16* __restrict__ x,
                                                                    const __nv_bfloat16* __restrict__ w,
@@ -107,22 +180,34 @@ __global__ void __launch_bounds__(NORM_THREADS) rmsnorm_bwd_kernel(const __nv_bf
                                                                    float w_offset) {
   __shared__ float scratch[32];
   const int nvec = H >> 3;
-  float dwacc[NORM_MAXV][8];
+  float dwacc[MAXV][8];
 #pragma unroll
-  for (int c = 0; c < NORM_MAXV; ++c)
+  for (int c = 0; c < MAXV; ++c)
 #pragma unroll
     for (int e = 0; e < 8; ++e) dwacc[c][e] = 0.f;
 
+  // the next row's x / dy are requested before the block reduction of the current row, so the loads are in
+  // flight while the CTA waits at the barrier
+  bf16x8 nx[MAXV], nd[MAXV];
+  auto fetch = [&](int row) {
+    const size_t off = static_cast<size_t>(row) * H;
+    int c = 0;
+    for (int i = threadIdx.x; i < nvec && c < MAXV; i += NORM_THREADS, ++c) {
+      nx[c] = *reinterpret_cast<const bf16x8*>(x + off + i * 8);
+      nd[c] = *reinterpret_cast<const bf16x8*>(dy + off + i * 8);
+    }
+  };
+  if (static_cast<int>(blockIdx.x) < rows) fetch(blockIdx.x);
   for (int row = blockIdx.x; row < rows; row += gridDim.x) {
     const size_t off = static_cast<size_t>(row) * H;
     const float rs = rstd[row];
-    float xh[NORM_MAXV][8], g[NORM_MAXV][8];
+    float xh[MAXV][8], g[MAXV][8];
     float dot = 0.f;
     int c = 0;
-    for (int i = threadIdx.x; i < nvec && c < NORM_MAXV; i += NORM_THREADS, ++c) {
+    for (int i = threadIdx.x; i < nvec && c < MAXV; i += NORM_THREADS, ++c) {
       float xv[8], dv[8], wv[8];
-      load8(x + off + i * 8, xv);
-      load8(dy + off + i * 8, dv);
+      unpack8(nx[c], xv);
+      unpack8(nd[c], dv);
       load8(w + i * 8, wv);
 #pragma unroll
       for (int e = 0; e < 8; ++e) {
@@ -132,9 +217,10 @@ __global__ void __launch_bounds__(NORM_THREADS) rmsnorm_bwd_kernel(const __nv_bf
         dwacc[c][e] += dv[e] * xh[c][e];
       }
     }
+    if (row + static_cast<int>(gridDim.x) < rows) fetch(row + gridDim.x);
     dot = block_sum(dot, scratch) / H;
     c = 0;
-    for (int i = threadIdx.x; i < nvec && c < NORM_MAXV; i += NORM_THREADS, ++c) {
+    for (int i = threadIdx.x; i < nvec && c < MAXV; i += NORM_THREADS, ++c) {
       float o[8];
 #pragma unroll
       for (int e = 0; e < 8; ++e) o[e] = rs * (g[c][e] - xh[c][e] * dot);
@@ -148,7 +234,7 @@ __global__ void __launch_bounds__(NORM_THREADS) rmsnorm_bwd_kernel(const __nv_bf
     }
   }
   int c = 0;
-  for (int i = threadIdx.x; i < nvec && c < NORM_MAXV; i += NORM_THREADS, ++c) {
+  for (int i = threadIdx.x; i < nvec && c < MAXV; i += NORM_THREADS, ++c) {
     float* dst = dw_partial + static_cast<size_t>(blockIdx.x) * H + i * 8;
     *reinterpret_cast<float4*>(dst) = make_float4(dwacc[c][0], dwacc[c][1], dwacc[c][2], dwacc[c][3]);
     *reinterpret_cast<float4*>(dst + 4) = make_float4(dwacc[c][4], dwacc[c][5], dwacc[c][6], dwacc[c][7]);
@@ -314,38 +400,56 @@ __global__ void rope_kernel(__nv_bfloat16* __restrict__ x, const float* __restri
   }
 }
 
-// Vectorised rotate-half variant: each thread rotates 8 pairs (two 16-byte loads, two stores).
+// Vectorised rotate-half variant: a thread owns 8 rotation pairs of one row (one 16-byte column slice of the first
+// half of a head and its partner in the second half), loads their cos / sin once and walks ROPE_HPT heads with them.
+constexpr int ROPE_HPT = 4;
 __global__ void rope_half_vec_kernel(__nv_bfloat16* __restrict__ x, const float* __restrict__ cos_t,
                                      const float* __restrict__ sin_t, const int* __restrict__ pos, long long rows,
                                      int row_stride, int n_heads, int D, int seq, int offset, float sign) {
   const int half = D >> 1;
   const int vec_per_head = half >> 3;
-  const int vec_per_row = n_heads * vec_per_head;
-  const long long total = rows * vec_per_row;
+  const int groups = (n_heads + ROPE_HPT - 1) / ROPE_HPT;
+  const int items_per_row = groups * vec_per_head;
+  const long long total = rows * items_per_row;
   for (long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; idx < total;
        idx += static_cast<long long>(gridDim.x) * blockDim.x) {
-    const long long row = idx / vec_per_row;
-    const int rem = static_cast<int>(idx - row * vec_per_row);
-    const int head = rem / vec_per_head, v = rem - head * vec_per_head;
+    const long long row = idx / items_per_row;
+    const int rem = static_cast<int>(idx - row * items_per_row);
+    const int grp = rem / vec_per_head, v = rem - grp * vec_per_head;
     const int p = pos ? pos[row] : static_cast<int>(row % seq) + offset;
     const float* cp = cos_t + static_cast<size_t>(p) * half + v * 8;
     const float* sp = sin_t + static_cast<size_t>(p) * half + v * 8;
-    __nv_bfloat16* base = x + row * row_stride + head * D + v * 8;
-    float a[8], b[8], oa[8], ob[8];
-    load8(base, a);
-    load8(base + half, b);
     const float4 c0 = *reinterpret_cast<const float4*>(cp), c1 = *reinterpret_cast<const float4*>(cp + 4);
     const float4 s0 = *reinterpret_cast<const float4*>(sp), s1 = *reinterpret_cast<const float4*>(sp + 4);
     const float cc[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
-    const float sn[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+    const float sn[8] = {s0.x * sign, s0.y * sign, s0.z * sign, s0.w * sign,
+                         s1.x * sign, s1.y * sign, s1.z * sign, s1.w * sign};
+    const int h0 = grp * ROPE_HPT;
+    bf16x8 ra[ROPE_HPT], rb[ROPE_HPT];
 #pragma unroll
-    for (int e = 0; e < 8; ++e) {
-      const float s = sn[e] * sign;
-      oa[e] = a[e] * cc[e] - b[e] * s;
-      ob[e] = b[e] * cc[e] + a[e] * s;
+    for (int j = 0; j < ROPE_HPT; ++j) {
+      if (h0 + j < n_heads) {
+        const __nv_bfloat16* base = x + row * row_stride + (h0 + j) * D + v * 8;
+        ra[j] = *reinterpret_cast<const bf16x8*>(base);
+        rb[j] = *reinterpret_cast<const bf16x8*>(base + half);
+      }
     }
-    store8(base, oa);
-    store8(base + half, ob);
+#pragma unroll
+    for (int j = 0; j < ROPE_HPT; ++j) {
+      if (h0 + j < n_heads) {
+        __nv_bfloat16* base = x + row * row_stride + (h0 + j) * D + v * 8;
+        float a[8], b[8], oa[8], ob[8];
+        unpack8(ra[j], a);
+        unpack8(rb[j], b);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          oa[e] = a[e] * cc[e] - b[e] * sn[e];
+          ob[e] = b[e] * cc[e] + a[e] * sn[e];
+        }
+        store8(base, oa);
+        store8(base + half, ob);
+      }
+    }
   }
 }
 
@@ -744,6 +848,18 @@ typedef __nv_bfloat16 bf16;
 extern "C" int ts_rmsnorm_fwd(const void* x, const void* residual, const void* w, void* y, void* res_out,
                               float* rstd, long long rows, int H, float eps, float w_offset, void* stream) {
   if (H % 8 != 0 || rows <= 0) return -10;
+  if (H <= 4096) {
+    long long blocks = (rows + 3) / 4;
+    const long long cap = static_cast<long long>(sm_count()) * 8;
+    if (blocks > cap) blocks = cap;
+    if (H <= 2048)
+      rmsnorm_fwd_warp_kernel<8><<<(unsigned)blocks, 128, 0, ST(stream)>>>(
+          (const bf16*)x, (const bf16*)residual, (const bf16*)w, (bf16*)y, (bf16*)res_out, rstd, rows, H, eps, w_offset);
+    else
+      rmsnorm_fwd_warp_kernel<16><<<(unsigned)blocks, 128, 0, ST(stream)>>>(
+          (const bf16*)x, (const bf16*)residual, (const bf16*)w, (bf16*)y, (bf16*)res_out, rstd, rows, H, eps, w_offset);
+    return (int)cudaGetLastError();
+  }
   rmsnorm_fwd_kernel<<<(unsigned)rows, NORM_THREADS, 0, ST(stream)>>>(
       (const bf16*)x, (const bf16*)residual, (const bf16*)w, (bf16*)y, (bf16*)res_out, rstd, H, eps, w_offset);
   return (int)cudaGetLastError();
@@ -761,9 +877,14 @@ extern "C" int ts_rmsnorm_bwd(const void* dy, const void* x, const void* w, cons
                               long long rows, int H, float w_offset, void* stream) {
   if (H % 8 != 0 || H > NORM_THREADS * NORM_MAXV * 8 || rows <= 0) return -10;
   const int parts = ts_rmsnorm_bwd_parts(rows);
-  rmsnorm_bwd_kernel<<<parts, NORM_THREADS, 0, ST(stream)>>>((const bf16*)dy, (const bf16*)x, (const bf16*)w, rstd,
-                                                             (const bf16*)dres, (bf16*)dx, dw_partial, (int)rows, H,
-                                                             w_offset);
+  if (H <= NORM_THREADS * 2 * 8)
+    rmsnorm_bwd_kernel<2><<<parts, NORM_THREADS, 0, ST(stream)>>>((const bf16*)dy, (const bf16*)x, (const bf16*)w, rstd,
+                                                                  (const bf16*)dres, (bf16*)dx, dw_partial, (int)rows,
+                                                                  H, w_offset);
+  else
+    rmsnorm_bwd_kernel<NORM_MAXV><<<parts, NORM_THREADS, 0, ST(stream)>>>((const bf16*)dy, (const bf16*)x,
+                                                                          (const bf16*)w, rstd, (const bf16*)dres,
+                                                                          (bf16*)dx, dw_partial, (int)rows, H, w_offset);
   rmsnorm_dw_reduce_kernel<<<(H + 255) / 256, 256, 0, ST(stream)>>>(dw_partial, dw_f32, (bf16*)dw_bf16, parts, H,
                                                                     accumulate_dw);
   return (int)cudaGetLastError();
@@ -796,7 +917,7 @@ extern "C" int ts_rope(void* x, const float* cos_t, const float* sin_t, const in
   const bool vec_ok = !interleaved && (D % 16 == 0) && (row_stride % 8 == 0) &&
                       ((reinterpret_cast<uintptr_t>(x) & 15u) == 0) && ((reinterpret_cast<uintptr_t>(cos_t) & 15u) == 0);
   if (vec_ok) {
-    const long long total = rows * n_heads * (D / 16);
+    const long long total = rows * ((n_heads + ROPE_HPT - 1) / ROPE_HPT) * (D / 16);
     rope_half_vec_kernel<<<grid_for(total, 256, 16), 256, 0, ST(stream)>>>((bf16*)x, cos_t, sin_t, pos, rows,
                                                                            row_stride, n_heads, D, seq, offset, sign);
   } else {
@@ -970,7 +1091,7 @@ extern "C" int ts_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void*
   if (rc != 0) return rc;
   // one partial row per CTA, never more rows than the workspace holds
   const int parts = rows < TS_NOALLOC_MAX_PARTS ? (int)rows : TS_NOALLOC_MAX_PARTS;
-  rmsnorm_bwd_kernel<<<parts, NORM_THREADS, 0, ST(stream)>>>((const bf16*)dy, (const bf16*)x, (const bf16*)w, rstd,
+  rmsnorm_bwd_kernel<NORM_MAXV><<<parts, NORM_THREADS, 0, ST(stream)>>>((const bf16*)dy, (const bf16*)x, (const bf16*)w, rstd,
                                                              (const bf16*)dres, (bf16*)dx, workspace, (int)rows, H,
                                                              w_offset);
   cudaError_t e = cudaGetLastError();
