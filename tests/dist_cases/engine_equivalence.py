@@ -23,6 +23,7 @@ def main():
     ap.add_argument("--tol", type=float, default=2e-4)
     ap.add_argument("--recompute", action="store_true", help="layer-wise activation recomputation in both runs")
     ap.add_argument("--accum", type=int, default=1, help="micro-batches per optimizer step")
+    ap.add_argument("--replicate", type=int, default=1, help="hybrid sharding: number of replicas of every shard")
     a = ap.parse_args()
     cuda = a.device == "cuda"
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
@@ -42,7 +43,20 @@ def main():
         model.gradient_checkpointing_enable(1)
         ref.gradient_checkpointing_enable(1)
     ec = dict(gradient_accumulation_steps=a.accum, param_dtype=dtype, lr=1e-2, weight_decay=0.01, max_grad_norm=1.0, eps=1e-3)  # large eps: no sign(g) blow-up of rounding noise
-    eng = FlatShardedEngine(model, EngineConfig(sharding_strategy=a.strategy, comm=a.comm, **ec), device=dev)
+    shard_pg = rep_pg = None
+    if a.replicate > 1:
+        # ranks [0..S) [S..2S) ... are the shard groups; ranks with equal position in their group replicate each other
+        S_ = world // a.replicate
+        for g0 in range(a.replicate):
+            grp = dist.new_group(list(range(g0 * S_, (g0 + 1) * S_)))
+            if rank // S_ == g0:
+                shard_pg = grp
+        for j in range(S_):
+            grp = dist.new_group(list(range(j, world, S_)))
+            if rank % S_ == j:
+                rep_pg = grp
+    eng = FlatShardedEngine(model, EngineConfig(sharding_strategy=a.strategy, comm=a.comm, **ec), device=dev,
+                            process_group=shard_pg, replicate_group=rep_pg)
     # the oracle: one process, global batch, no sharding (a private 1-rank view of the engine)
     ref_eng = FlatShardedEngine.__new__(FlatShardedEngine)
     saved = dist.get_world_size

@@ -86,6 +86,12 @@ def test_expert_parallel_moe_matches_local_moe():
     assert r.stdout.count("ok=True") == 2
 
 
+def test_hybrid_sharding_four_ranks():
+    """2 shard groups x 2 replicas: reduce-scatter inside a group, average of the shards across groups."""
+    r = launch(4, "--device", "cpu", "--strategy", "SHARD_GRAD_OP", "--replicate", "2", port=29616)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+
+
 ND_CASE = Path(__file__).parent / "dist_cases" / "trainer_nd.py"
 
 

@@ -220,11 +220,15 @@ class FlatShardedEngine:
     """Owns the flat buffers, the gradient reduction schedule and the sharded optimizer step."""
 
     def __init__(self, model: nn.Module, cfg: EngineConfig, process_group=None, device=None,
-                 unit_modules: list[tuple[str, nn.Module]] | None = None, solo: bool = False):
+                 unit_modules: list[tuple[str, nn.Module]] | None = None, solo: bool = False,
+                 replicate_group=None):
         """`solo`: this rank shares its parameters with nobody (a data-parallel group of one inside a larger job,
-        e.g. pure pipeline or tensor parallelism): no collective is ever issued."""
+        e.g. pure pipeline or tensor parallelism): no collective is ever issued.
+        `replicate_group`: hybrid sharding - `process_group` is the shard group (inside a node, say) and the ranks of
+        `replicate_group` hold the same shard; reduced gradient shards are additionally averaged over it."""
         self.model, self.cfg = model, cfg
         self.pg = process_group
+        self.replicate_group = replicate_group
         self.distributed = (not solo) and dist.is_available() and dist.is_initialized() and \
             dist.get_world_size(process_group) > 1
         self.world = dist.get_world_size(process_group) if self.distributed else 1
@@ -248,7 +252,10 @@ class FlatShardedEngine:
         # FULL_SHARD recycles its gather / gradient buffers between units, which the peer-memory kernels (they read
         # a peer's buffer without a hand-shake on its reuse) do not allow: it runs on the library collectives
         self.full_shard = cfg.sharding_strategy == "FULL_SHARD" and self.distributed
-        if self.distributed and self.is_cuda and cfg.comm in ("auto", "fused") and not self.full_shard:
+        # (the fused reduce-scatter also sums the squared gradients inside the kernel, which would come before the
+        # replica average of hybrid sharding: that mode uses the library collectives too)
+        if self.distributed and self.is_cuda and cfg.comm in ("auto", "fused") and not self.full_shard \
+                and replicate_group is None:
             from . import symm
             self._symm = symm.SymmetricHeap.try_create(self.pg, self.device)
             if self._symm is None and cfg.comm == "fused":
@@ -333,6 +340,9 @@ class FlatShardedEngine:
 
     def _sync_initial_params(self):
         for u in self.units:
+            if self.replicate_group is not None:
+                dist.broadcast(u.flat_param, src=dist.get_global_rank(self.replicate_group, 0),
+                               group=self.replicate_group)
             dist.broadcast(u.flat_param, src=dist.get_global_rank(self.pg, 0) if self.pg else 0, group=self.pg)
             s = u.shard_start
             u.master.copy_(u.flat_param[s:s + u.shard_numel])
@@ -525,6 +535,7 @@ class FlatShardedEngine:
             dist.all_reduce(u.flat_grad, op=dist.ReduceOp.AVG if self.is_cuda else dist.ReduceOp.SUM, group=self.pg)
             if not self.is_cuda:
                 u.flat_grad.div_(self.world)
+            self._replica_average(u.flat_grad)
             if stream is not None:
                 u.reduce_event = torch.cuda.Event()
                 u.reduce_event.record(stream)
@@ -552,6 +563,9 @@ class FlatShardedEngine:
                     full = u.flat_grad.float()
                     dist.all_reduce(full, group=self.pg)
                     red = full[u.shard_start:u.shard_start + u.shard_numel] / self.world
+                if self.replicate_group is not None:
+                    red = red.float() if red.dtype != torch.float32 else red
+                    self._replica_average(red)
                 if u.resharded and not first:
                     u.shard_grad.add_(red)          # later micro-batches of an accumulation window
                 else:
@@ -571,6 +585,16 @@ class FlatShardedEngine:
                 p.grad_added = False
             if not self._is_sync_step():
                 u.reduce_event = None           # the next micro-batch reduces again
+
+    def _replica_average(self, t: torch.Tensor) -> None:
+        if self.replicate_group is None:
+            return
+        n = dist.get_world_size(self.replicate_group)
+        if self.is_cuda:
+            dist.all_reduce(t, op=dist.ReduceOp.AVG, group=self.replicate_group)
+        else:
+            dist.all_reduce(t, group=self.replicate_group)
+            t.div_(n)
 
     # ------------------------------------------------------------------ optimizer step
     def _shard_grad_view(self, u: FlatUnit) -> torch.Tensor:

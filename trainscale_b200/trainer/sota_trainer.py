@@ -231,6 +231,14 @@ class SOTATrainer:
             lr=c.optimizer.learning_rate, betas=betas, eps=c.optimizer.eps, weight_decay=c.optimizer.weight_decay,
             optimizer="lion" if opt_type == "lion" else "adamw", comm=d.comm)
         c.training.gradient_accumulation_steps = ec.gradient_accumulation_steps
+        par = d.parallel
+        if self.is_distributed and strat == "fsdp" and int(getattr(par, "dp_replicate", 1) or 1) > 1:
+            # hybrid sharding: shard inside groups of world / dp_replicate ranks, replicate across them
+            from ..parallel.mesh import create_parallel_dims_from_config
+            dims = create_parallel_dims_from_config(d)
+            self._hsdp_dims = dims
+            return FlatShardedEngine(self.model, ec, process_group=dims.group("fsdp"), device=self.device,
+                                     replicate_group=dims.group("dp_replicate"))
         return FlatShardedEngine(self.model, ec, device=self.device)
 
     def _flops_per_token(self) -> float:
