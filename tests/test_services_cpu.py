@@ -197,3 +197,40 @@ def test_lora_quant_rl_metrics():
     lt.update(2.0, 10)
     lt.update(4.0, 30)
     assert lt.mean == pytest.approx(3.5)
+
+
+def test_ptrr_balancer_and_planning_helpers():
+    import torch
+    from trainscale_b200.parallel import cp, mesh
+    bal = [cp.create_balancer("ptrr", 4, r) for r in range(4)]
+    idx = torch.cat([b.indices(64) for b in bal]).sort().values
+    assert torch.equal(idx, torch.arange(64))
+    assert bal[1].indices(64)[:4].tolist() == [4, 5, 6, 7] and bal[1].indices(64)[4:8].tolist() == [24, 25, 26, 27]
+    x = torch.arange(64).view(1, 64)
+    assert torch.equal(bal[0].unshard([b.shard(x) for b in bal]), x)
+    est = mesh.MemoryEstimator.estimate_per_gpu_memory
+    one = est(8_030_000_000, 1, 8192, 4096, 32, intermediate_dim=14336)
+    eight = est(8_030_000_000, 1, 8192, 4096, 32, dp_shard_degree=8, intermediate_dim=14336)
+    assert one > eight and mesh.MemoryEstimator.fits(eight) and not mesh.MemoryEstimator.fits(one, capacity_gb=80)
+    sel = mesh.CommAlgorithmSelector(8)
+    assert sel.all_reduce(4096) == "one_shot_p2p" and sel.all_reduce(1 << 28) == "multimem"
+    assert mesh.CommAlgorithmSelector(8, nvswitch=False).all_reduce(1 << 28) == "ring"
+    assert mesh.HardwareDetector.detect()["num_gpus"] >= 0
+
+
+def test_gradient_plumbing_helpers_single_process():
+    import torch
+    from trainscale_b200.parallel import dist_utils
+    out = torch.zeros(4)
+    dist_utils.reduce_scatter_with_fp32_accumulation(out, torch.arange(4.0))
+    assert out.tolist() == [0.0, 1.0, 2.0, 3.0]
+    lin = torch.nn.Linear(4, 4)
+    lin(torch.ones(2, 4)).sum().backward()
+    g0 = lin.weight.grad.clone()
+    dist_utils.finalize_model_grads(lin, num_tokens=torch.tensor(4.0), dp_group=False)
+    assert torch.allclose(lin.weight.grad, g0 / 4)
+    mgr = dist_utils.DistributedManager()
+    assert mgr is dist_utils.DistributedManager() and mgr.world_size == 1
+    assert mgr.reduce_dict({"loss": 2.0}) == {"loss": 2.0}
+    sync = dist_utils.GradientSynchronizer(engine=object(), accumulation_steps=4)
+    assert [sync.should_sync(i) for i in range(4)] == [False, False, False, True]

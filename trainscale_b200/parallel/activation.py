@@ -185,3 +185,36 @@ class ActivationOffloader:
     def summary(self) -> str:
         return (f"offloaded {self.offloaded_bytes / 2 ** 30:.2f} GiB, restored {self.restored_bytes / 2 ** 30:.2f} GiB, "
                 f"pinned pool {self.pool.bytes_allocated / 2 ** 30:.2f} GiB")
+
+
+class ChunkOffloadHandler(ActivationOffloader):
+    """Offloads the saved activations of one model chunk (a pipeline stage's micro-batch, a group of layers) and
+    keeps per-chunk accounting, so that a pipeline schedule can offload chunk k while chunk k+1 computes and bring it
+    back just before its backward (data_pipeline/trainer/distributed/activation_offload.py:358)."""
+
+    def __init__(self, chunk_id: int = 0, min_bytes: int = 1 << 20):
+        super().__init__(min_bytes)
+        self.chunk_id = chunk_id
+
+
+class PipelineOffloadManager:
+    """One `ChunkOffloadHandler` per in-flight micro-batch of a pipeline stage
+    (data_pipeline/trainer/distributed/activation_offload.py:531)."""
+
+    def __init__(self, min_bytes: int = 1 << 20):
+        self.min_bytes = min_bytes
+        self.handlers: dict[int, ChunkOffloadHandler] = {}
+
+    def scope(self, micro_batch: int):
+        h = self.handlers.setdefault(micro_batch, ChunkOffloadHandler(micro_batch, self.min_bytes))
+        return h.scope()
+
+    def release(self, micro_batch: int) -> None:
+        self.handlers.pop(micro_batch, None)
+
+    def summary(self) -> str:
+        return "; ".join(f"mb{k}: {h.summary()}" for k, h in sorted(self.handlers.items()))
+
+
+def print_offload_summary(manager: "PipelineOffloadManager | ActivationOffloader") -> None:
+    print(manager.summary())

@@ -66,12 +66,30 @@ class ZigZagBalancer(HeadTailBalancer):
         return pos[owner == r]
 
 
+class PTRRBalancer(HeadTailBalancer):
+    """4*cp chunks walked forward, reverse, reverse, forward: rank r owns chunks r, 2cp-1-r, 3cp-1-r, 3cp+r
+    (data_pipeline/trainer/distributed/context_parallel.py:1224).  Falls back to plain contiguous chunks when the
+    sequence is shorter than 4*cp tokens."""
+
+    def indices(self, seq_len: int, rank: int | None = None) -> torch.Tensor:
+        r = self.rank if rank is None else rank
+        n = 4 * self.cp
+        c = seq_len // n
+        if c < 1 or seq_len % n != 0:
+            per = seq_len // self.cp
+            return torch.arange(r * per, (r + 1) * per if r < self.cp - 1 else seq_len)
+        ids = [r, 2 * self.cp - 1 - r, 3 * self.cp - 1 - r, 3 * self.cp + r]
+        return torch.cat([torch.arange(i * c, (i + 1) * c) for i in ids])
+
+
 def create_balancer(name: str, cp: int, rank: int):
     name = (name or "head_tail").lower()
     if name in ("head_tail", "headtail"):
         return HeadTailBalancer(cp, rank)
     if name in ("zigzag", "zig_zag"):
         return ZigZagBalancer(cp, rank)
+    if name == "ptrr":
+        return PTRRBalancer(cp, rank)
     raise ValueError(f"unknown context-parallel balancer {name!r}")
 
 

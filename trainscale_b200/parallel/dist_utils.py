@@ -263,3 +263,136 @@ class HeartbeatMonitor:
             elif now - prev[1] > timeout_s:
                 stale.append(r)
         return stale
+
+
+# ------------------------------------------------------------------------------------------------ gradient plumbing
+def reduce_scatter_with_fp32_accumulation(output: torch.Tensor, input: torch.Tensor, group=None) -> torch.Tensor:
+    """Reduce-scatter of a low-precision tensor whose sum is taken in fp32: every rank receives the W slices meant
+    for it (all-to-all) and adds them in fp32 (data_pipeline/trainer/distributed/reduce_scatter_fp32.py:90).
+    `input` is [W * n], `output` [n] in any float dtype.  On the flat engine's CUDA path the same arithmetic runs
+    inside `ts_symm_reduce_scatter`; this is the library-collective form."""
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    if world == 1:
+        output.copy_(input.view(-1)[:output.numel()])
+        return output
+    n = output.numel()
+    recv = torch.empty_like(input.view(-1))
+    if input.is_cuda:
+        dist.all_to_all_single(recv, input.contiguous().view(-1), group=group)
+    else:   # gloo has no all_to_all_single on every build: gather slices with all_gather
+        parts = [torch.empty_like(input.view(-1)) for _ in range(world)]
+        dist.all_gather(parts, input.contiguous().view(-1), group=group)
+        r = dist.get_rank(group)
+        recv = torch.cat([p[r * n:(r + 1) * n] for p in parts])
+    output.copy_(recv.view(world, n).float().sum(0))
+    return output
+
+
+def allreduce_layernorm_grads(model, group) -> None:
+    """Sequence parallelism: norm weights saw only this rank's tokens; sum their gradients over the TP group."""
+    from .tp import TPContext, allreduce_sequence_parallel_grads
+    ctx = TPContext(group, dist.get_world_size(group), dist.get_rank(group), True)
+    allreduce_sequence_parallel_grads(model, ctx)
+
+
+def allreduce_word_embedding_grads(stage_module, group, first_rank: int, last_rank: int) -> None:
+    """Tied embeddings on the first and last pipeline stage: sum their gradients."""
+    from .pp import allreduce_tied_embedding_grads
+    allreduce_tied_embedding_grads(stage_module, group, first_rank, last_rank)
+
+
+def finalize_model_grads(model, *, tp_group=None, sequence_parallel: bool = False, pp_group=None, stage_module=None,
+                         first_rank: int = 0, last_rank: int = 0, num_tokens: torch.Tensor | None = None,
+                         dp_group=None) -> None:
+    """Everything that must happen to gradients between backward and the optimizer step besides the data-parallel
+    reduction (data_pipeline/trainer/distributed/finalize_grads.py:314): SP norm-weight all-reduce, tied-embedding
+    all-reduce across pipeline ends, optional scaling by the global number of tokens."""
+    if sequence_parallel and tp_group is not None:
+        allreduce_layernorm_grads(model, tp_group)
+    if pp_group is not None and stage_module is not None:
+        allreduce_word_embedding_grads(stage_module, pp_group, first_rank, last_rank)
+    if num_tokens is not None:
+        total = num_tokens.detach().float().clone()
+        if dist.is_initialized() and dp_group is not False:
+            dist.all_reduce(total, group=dp_group)
+        scale = 1.0 / total.clamp(min=1.0)
+        for p in model.parameters():
+            g = getattr(p, "main_grad", None) if p.grad is None else p.grad
+            if g is not None:
+                g.mul_(scale.to(g.dtype))
+
+
+class GradientSynchronizer:
+    """`with sync.accumulate(step):` suppresses the engine's gradient reduction except on the last micro-batch of an
+    accumulation window (data_pipeline/trainer/distributed/__init__.py GradientSynchronizer)."""
+
+    def __init__(self, engine, accumulation_steps: int = 1):
+        self.engine, self.steps = engine, max(1, accumulation_steps)
+
+    def should_sync(self, micro_step: int) -> bool:
+        return (micro_step + 1) % self.steps == 0
+
+    def accumulate(self, micro_step: int):
+        import contextlib
+        if self.should_sync(micro_step) or not hasattr(self.engine, "no_sync"):
+            return contextlib.nullcontext()
+        return self.engine.no_sync()
+
+
+class DistributedManager:
+    """Process-wide entry point: process-group initialisation, model wrapping into the flat engine, thin collective
+    helpers (data_pipeline/trainer/distributed/__init__.py:265)."""
+
+    _instance: "DistributedManager | None" = None
+
+    def __new__(cls):
+        if cls._instance is None:
+            cls._instance = super().__new__(cls)
+            cls._instance.state = None
+        return cls._instance
+
+    def init_process_group(self, backend: str | None = None) -> "DistributedState":
+        self.state = DistributedState.from_environment()
+        self.state.initialize(backend)
+        return self.state
+
+    @property
+    def world_size(self) -> int:
+        return dist.get_world_size() if dist.is_initialized() else 1
+
+    @property
+    def rank(self) -> int:
+        return dist.get_rank() if dist.is_initialized() else 0
+
+    def wrap_model(self, model, strategy: str = "fsdp", **engine_kwargs):
+        """strategy: ddp | fsdp / zero2 | full_shard / zero3. Returns the FlatShardedEngine that owns the model's
+        parameters, gradients and sharded optimizer state."""
+        from .flat_engine import EngineConfig, FlatShardedEngine
+        sharding = {"ddp": "NO_SHARD", "fsdp": "SHARD_GRAD_OP", "zero2": "SHARD_GRAD_OP", "full_shard": "FULL_SHARD",
+                    "zero3": "FULL_SHARD"}[strategy.lower()]
+        p = next(model.parameters())
+        return FlatShardedEngine(model, EngineConfig(sharding_strategy=sharding, param_dtype=p.dtype, **engine_kwargs),
+                                 device=p.device)
+
+    def all_reduce(self, t: torch.Tensor, op: str = "sum", group=None) -> torch.Tensor:
+        return dist_reduce(t, op, group)
+
+    def all_gather(self, t: torch.Tensor, group=None) -> list[torch.Tensor]:
+        return dist_all_gather(t, group)
+
+    def broadcast(self, t: torch.Tensor, src: int = 0, group=None) -> torch.Tensor:
+        if dist.is_initialized() and dist.get_world_size(group) > 1:
+            dist.broadcast(t, src, group=group)
+        return t
+
+    def reduce_dict(self, d: dict, average: bool = True, group=None) -> dict:
+        if not dist.is_initialized() or dist.get_world_size(group) == 1:
+            return dict(d)
+        keys = sorted(d)
+        flat = torch.stack([torch.as_tensor(d[k], dtype=torch.float32).reshape(()) for k in keys])
+        if torch.cuda.is_available() and dist.get_backend(group) == "nccl":
+            flat = flat.cuda()
+        dist.all_reduce(flat, group=group)
+        if average:
+            flat /= dist.get_world_size(group)
+        return {k: flat[i].item() for i, k in enumerate(keys)}

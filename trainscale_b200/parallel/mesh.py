@@ -197,3 +197,88 @@ def estimate_memory(n_params: float, dims: ParallelDimsConfig, seq_len: int, mic
     act = per_layer * layers / d.pp
     gb = 1 / 2 ** 30
     return MemoryEstimate(params * gb, grads * gb, optim * gb, act * gb)
+
+
+# ------------------------------------------------------------------------------------------------ planning helpers
+class HardwareDetector:
+    """What the job runs on: GPU count / name / memory, NVLink-connected peers, NUMA node of every GPU.
+    After data_pipeline/trainer/distributed/parallel_dims.py:294-760 (read-only: nothing is configured here)."""
+
+    @staticmethod
+    def detect() -> dict:
+        import os
+        info = {"num_gpus": 0, "name": None, "memory_gb": 0.0, "sm_count": 0, "peer_access": [], "numa": {},
+                "nvswitch": False}
+        if not torch.cuda.is_available():
+            return info
+        n = torch.cuda.device_count()
+        prop = torch.cuda.get_device_properties(0)
+        info.update(num_gpus=n, name=prop.name, memory_gb=prop.total_memory / 2 ** 30, sm_count=prop.multi_processor_count)
+        peers = [[i == j or torch.cuda.can_device_access_peer(i, j) for j in range(n)] for i in range(n)]
+        info["peer_access"] = peers
+        # every GPU reaching every other one directly is what an NVSwitch box looks like from here
+        info["nvswitch"] = n > 2 and all(all(row) for row in peers)
+        for i in range(n):
+            try:
+                bus = torch.cuda.get_device_properties(i).pci_bus_id
+                path = f"/sys/bus/pci/devices/0000:{bus:02x}:00.0/numa_node"
+                if os.path.exists(path):
+                    info["numa"][i] = int(open(path).read().strip())
+            except Exception:
+                pass
+        return info
+
+
+class MemoryEstimator:
+    """Per-GPU bytes of a parallel configuration before anything is allocated
+    (data_pipeline/trainer/distributed/parallel_dims.py:771)."""
+
+    @staticmethod
+    def estimate_per_gpu_memory(model_params: int, batch_size: int, seq_len: int, hidden_dim: int, num_layers: int,
+                                tp_degree: int = 1, pp_degree: int = 1, cp_degree: int = 1, dp_shard_degree: int = 1,
+                                use_activation_checkpointing: bool = False, precision_bytes: int = 2,
+                                shard_params: bool = False, intermediate_dim: int | None = None) -> int:
+        local = model_params / (tp_degree * pp_degree)
+        params = local * precision_bytes / (dp_shard_degree if shard_params else 1)
+        grads = local * precision_bytes
+        optim = local * 12 / dp_shard_degree                      # fp32 master + two Adam moments, sharded
+        tokens = batch_size * seq_len / cp_degree
+        inter = intermediate_dim or 4 * hidden_dim
+        per_layer = tokens * precision_bytes * ((5 * hidden_dim + 2 * inter + inter) / tp_degree + 2 * hidden_dim)
+        layers = num_layers / pp_degree
+        acts = per_layer * layers
+        if use_activation_checkpointing:
+            acts = tokens * hidden_dim * precision_bytes * layers + per_layer      # layer inputs + one live layer
+        return int(params + grads + optim + acts)
+
+    @staticmethod
+    def fits(bytes_needed: int, capacity_gb: float = 180.0, headroom: float = 0.92) -> bool:
+        return bytes_needed <= capacity_gb * 2 ** 30 * headroom
+
+
+class CommAlgorithmSelector:
+    """Which implementation a collective of a given size should use on an NVSwitch box: small messages are launch-bound
+    (one-shot peer-memory kernels), large ones bandwidth-bound (in-switch reduction when available, else the library
+    ring).  After data_pipeline/trainer/distributed/parallel_dims.py:957."""
+
+    def __init__(self, world: int, nvswitch: bool = True, multicast: bool = True):
+        self.world, self.nvswitch, self.multicast = world, nvswitch, multicast
+
+    def all_reduce(self, nbytes: int) -> str:
+        if self.world == 1:
+            return "none"
+        if self.nvswitch and nbytes <= 256 << 10:
+            return "one_shot_p2p"
+        if self.nvswitch and self.multicast:
+            return "multimem"
+        return "ring"
+
+    def reduce_scatter(self, nbytes: int) -> str:
+        if self.world == 1:
+            return "none"
+        return ("multimem" if self.multicast else "p2p_pull") if self.nvswitch else "ring"
+
+    def bucket_bytes(self) -> int:
+        """Gradient bucket size: collective cost on NVSwitch is latency- not link-bound, so buckets only need to
+        amortise a launch (tens of MB)."""
+        return (80 << 20) if self.nvswitch else (25 << 20)

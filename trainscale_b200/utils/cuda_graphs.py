@@ -84,3 +84,22 @@ def optimize_for_training(model, checkpoint_every: int = 2):
     if hasattr(model, "gradient_checkpointing_enable"):
         model.gradient_checkpointing_enable(checkpoint_every)
     return model
+
+
+class ModelCompiler:
+    """Facade with the reference's compiler surface (data_pipeline/trainer/kernels/compiler.py:513) on this
+    framework's mechanism: kernels are hand-written, so "compiling" a model means capturing its launch-bound step in a
+    CUDA graph and choosing the recompute policy, not tracing it."""
+
+    def __init__(self, config: CompilationConfig | None = None):
+        self.config = config or CompilationConfig()
+        self.graphs = CUDAGraphManager()
+
+    def compile(self, model):
+        return compile_model(model, self.config)
+
+    def for_inference(self, model):
+        return optimize_for_inference(model)
+
+    def for_training(self, model, checkpoint_every: int = 2):
+        return optimize_for_training(model, checkpoint_every)
