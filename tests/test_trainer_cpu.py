@@ -75,3 +75,23 @@ def test_synthetic_packed_batch_schema():
     d, p = b["document_ids"][0], b["position_ids"][0]
     starts = torch.nonzero(p == 0).flatten()
     assert starts[0] == 0 and torch.all(d[starts[1:]] == d[starts[1:] - 1] + 1)
+
+
+def test_op_selective_recompute_matches_plain_path_on_cpu():
+    """The operator-level recompute blocks fall back to the separate ops off the CUDA bf16 path: same loss and grads."""
+    import torch
+    from trainscale_b200.models.llama import LlamaConfig, build_model
+    cfg = LlamaConfig(vocab_size=128, hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+                      num_key_value_heads=2, head_dim=16)
+    m = build_model(cfg, dtype=torch.float32, device="cpu", seed=0).train()
+    ids = torch.randint(0, 128, (2, 24), generator=torch.Generator().manual_seed(0))
+    l0 = m(input_ids=ids, labels=ids).loss
+    l0.backward()
+    g0 = {n: p.grad.clone() for n, p in m.named_parameters()}
+    m.zero_grad(set_to_none=True)
+    m.op_selective_recompute(True)
+    l1 = m(input_ids=ids, labels=ids).loss
+    l1.backward()
+    assert abs(l0.item() - l1.item()) < 1e-6
+    for n, p in m.named_parameters():
+        assert torch.allclose(p.grad, g0[n], atol=1e-6), n
