@@ -18,6 +18,8 @@
 //
 // Replaces the serial all_gather -> F.linear and F.linear -> reduce_scatter pairs of
 // data_pipeline/trainer/distributed/tensor_parallel.py:1053-1061,1214-1219.
+#include <cstdlib>
+
 #include "common.cuh"
 #include "host_common.h"
 
@@ -29,7 +31,7 @@ constexpr int TP_SUB = 4;                // a remote row block is fetched as TP_
 
 struct TpPeers {
   const void* src[TP_MAX_WORLD];         // GATHER: every rank's A shard ([rows_per_rank][K] bf16)
-  float* dst[TP_MAX_WORLD];              // REDUCE: every rank's fp32 accumulation buffer ([rows_per_rank][N])
+  void* dst[TP_MAX_WORLD];               // REDUCE: every rank's accumulation buffer ([rows_per_rank][N], fp32 or bf16)
   unsigned int* pad[TP_MAX_WORLD];       // signal pads
 };
 
@@ -37,6 +39,7 @@ struct TpParams {
   int M, N, K, ldc;
   int b_mn;
   int mode;                              // 1 = GATHER, 2 = REDUCE
+  int acc_bf16;                          // REDUCE: accumulate packed bf16 pairs (8 elements per 16-byte red) instead of fp32
   int rank, world, rows_per_rank;
   void* C;                               // GATHER: bf16 output [M][ldc]
   __nv_bfloat16* a_full;                 // GATHER: local [M][K] buffer the remote rows are staged into
@@ -60,7 +63,48 @@ __device__ __forceinline__ void red_add_v4_f32(float* p, float a, float b, float
   asm volatile("red.relaxed.sys.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(a), "f"(b), "f"(c), "f"(d)
                : "memory");
 }
+__device__ __forceinline__ void red_add_v4_bf16x2(void* p, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("red.relaxed.sys.global.add.noftz.v4.bf16x2 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(a), "r"(b), "r"(c),
+               "r"(d)
+               : "memory");
+}
+// one 32-column chunk of partial sums of `row` added into the owner's buffer
+__device__ __forceinline__ void tp_reduce_chunk(const TpParams& p, const TpPeers& peers, const uint32_t* r, int row,
+                                                int col0);
 __device__ __forceinline__ void fence_proxy_async_global() { asm volatile("fence.proxy.async.global;" ::: "memory"); }
+
+__device__ __forceinline__ void tp_reduce_chunk(const TpParams& p, const TpPeers& peers, const uint32_t* r, int row,
+                                                int col0) {
+  const int owner = row / p.rows_per_rank;
+  const size_t off = static_cast<size_t>(row - owner * p.rows_per_rank) * p.N + col0;
+  if (p.acc_bf16) {
+    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(peers.dst[owner]) + off;
+    if (col0 + 32 <= p.N && ((reinterpret_cast<uintptr_t>(dst) & 15u) == 0)) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        red_add_v4_bf16x2(dst + 8 * j, pack_bf16x2(__uint_as_float(r[8 * j]), __uint_as_float(r[8 * j + 1])),
+                          pack_bf16x2(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3])),
+                          pack_bf16x2(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5])),
+                          pack_bf16x2(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7])));
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (col0 + j < p.N) atomicAdd(dst + j, __float2bfloat16(__uint_as_float(r[j])));
+    }
+    return;
+  }
+  float* dst = reinterpret_cast<float*>(peers.dst[owner]) + off;
+  if (col0 + 32 <= p.N) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      red_add_v4_f32(dst + 4 * j, __uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]), __uint_as_float(r[4 * j + 2]),
+                     __uint_as_float(r[4 * j + 3]));
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (col0 + j < p.N) atomicAdd_system(dst + j, __uint_as_float(r[j]));
+  }
+}
 
 template <int BN>
 __global__ void __launch_bounds__(TP_THREADS, 1)
@@ -110,8 +154,10 @@ tp_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   bool alive = true;
 
   // logical m index j -> physical row block: own rows first, then the next ranks' rows in ring order
+  // REDUCE: the next ranks' rows first and the own rows last, so that remote additions start at once and the tail of
+  // the kernel only touches local memory
   auto phys_m = [&](int j) {
-    if (p.mode != 1) return j;
+    if (p.mode != 1) return (j + (p.rank + 1) * m_tiles_per_rank) % p.num_m_tiles;
     return (j + p.rank * m_tiles_per_rank) % p.num_m_tiles;
   };
   auto tile_coords = [&](int t, int& mt, int& n0) {
@@ -222,16 +268,7 @@ tp_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         const int col0 = n0 + c * 32;
         if (row >= p.M || col0 >= p.N) continue;
         if (p.mode == 2) {
-          const int owner = row / p.rows_per_rank;
-          float* dst = peers.dst[owner] + static_cast<size_t>(row - owner * p.rows_per_rank) * p.N + col0;
-          if (col0 + 32 <= p.N) {
-#pragma unroll
-            for (int j = 0; j < 8; ++j)
-              red_add_v4_f32(dst + 4 * j, __uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
-                             __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
-          } else {
-            for (int j = 0; j < 32 && col0 + j < p.N; ++j) atomicAdd_system(dst + j, __uint_as_float(r[j]));
-          }
+          tp_reduce_chunk(p, peers, r, row, col0);
         } else {
           __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<size_t>(row) * p.ldc + col0;
           if (col0 + 32 <= p.N && ((reinterpret_cast<uintptr_t>(dst) & 15u) == 0)) {
@@ -245,7 +282,9 @@ tp_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
               *reinterpret_cast<uint4*>(dst + 8 * j) = v;
             }
           } else {
-            for (int j = 0; j < 32 && col0 + j < p.N; ++j) dst[j] = __float2bfloat16(__uint_as_float(r[j]));
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (col0 + j < p.N) dst[j] = __float2bfloat16(__uint_as_float(r[j]));
           }
         }
       }
@@ -286,10 +325,27 @@ tp_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(peers.src[owner]) +
                                      static_cast<size_t>(mt - owner * m_tiles_per_rank) * TP_BM * p.K + sub * (p.K / TP_SUB);
           __nv_bfloat16* dst = p.a_full + static_cast<size_t>(mt) * TP_BM * p.K + sub * (p.K / TP_SUB);
-          for (int v = ct; v < TP_BM * vec_per_row; v += 128) {
-            const int rr = v / vec_per_row, cc = v - rr * vec_per_row;
-            const uint4 val = *reinterpret_cast<const uint4*>(src + static_cast<size_t>(rr) * p.K + cc * 8);
-            *reinterpret_cast<uint4*>(dst + static_cast<size_t>(rr) * p.K + cc * 8) = val;
+          // eight independent 16-byte peer loads per thread are in flight before the first store: a remote load
+          // takes microseconds, and one-at-a-time copies would leave the link idle
+          const int nvec = TP_BM * vec_per_row;
+          for (int v0 = ct; v0 < nvec; v0 += 128 * 8) {
+            uint4 val[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+              const int v = v0 + u * 128;
+              if (v < nvec) {
+                const int rr = v / vec_per_row, cc = v - rr * vec_per_row;
+                val[u] = *reinterpret_cast<const uint4*>(src + static_cast<size_t>(rr) * p.K + cc * 8);
+              }
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+              const int v = v0 + u * 128;
+              if (v < nvec) {
+                const int rr = v / vec_per_row, cc = v - rr * vec_per_row;
+                *reinterpret_cast<uint4*>(dst + static_cast<size_t>(rr) * p.K + cc * 8) = val[u];
+              }
+            }
           }
           __threadfence();
           asm volatile("bar.sync 2, 128;" ::: "memory");
@@ -325,6 +381,307 @@ tp_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       if (lane == 0) p.flags[1] = 0u;
     }
   }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// Paired-CTA variant (cta_group::2): a cluster of two CTAs owns a 256 x 256 tile, each CTA its own 128 rows of A and
+// half of B; the leader issues the MMAs for both (same mainloop as the plain paired-CTA GEMM).  The cross-rank
+// protocol is unchanged: copier warps of every CTA stage remote row blocks, the producer of a CTA waits for the
+// staging counter of the 128-row block it loads, epilogues add into the owner's buffer, CTA 0 runs the entry barrier
+// and the last CTA the exit barrier.  Requires rows_per_rank % 256 == 0.
+// ---------------------------------------------------------------------------------------------------------------
+constexpr int TP2_STAGES = 6;
+constexpr int TP2_STAGE_BYTES = 32768;
+constexpr int TP2_SMEM = TP2_STAGES * TP2_STAGE_BYTES + 256 + 1024;
+
+__global__ void __launch_bounds__(TP_THREADS, 1)
+tp_gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, TpParams p,
+                    TpPeers peers) {
+  constexpr int STAGES = TP2_STAGES;
+  constexpr int BN = 256;
+  constexpr uint32_t TMEM_COLS = 512;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* smem_a = smem;
+  uint8_t* smem_b = smem + STAGES * 16384;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * TP2_STAGE_BYTES);
+  uint64_t* full_bar = bars;
+  uint64_t* empty_bar = bars + STAGES;
+  uint64_t* tfull_bar = bars + 2 * STAGES;
+  uint64_t* tempty_bar = bars + 2 * STAGES + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t crank = cluster_ctarank();
+  const bool leader = (crank == 0);
+  if (threadIdx.x == 0) {
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    mbar_init(&tfull_bar[0], 1);
+    mbar_init(&tfull_bar[1], 1);
+    mbar_init(&tempty_bar[0], 8);
+    mbar_init(&tempty_bar[1], 8);
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc_2cta(tmem_slot, TMEM_COLS);
+    tmem_relinquish_2cta();
+    tc_fence_before_sync();
+  }
+  __syncthreads();
+  cluster_sync_all();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int m_tiles = p.M / 256;                       // 256-row super-blocks
+  const int n_tiles = (p.N + BN - 1) / BN;
+  const int num_tiles = m_tiles * n_tiles;
+  const int tiles_per_group = TP_GROUP_M * n_tiles;
+  const int sb_per_rank = p.rows_per_rank / 256;
+  const int m_blocks_per_rank = p.rows_per_rank / TP_BM;
+  const int cluster_id = blockIdx.x >> 1, num_clusters = gridDim.x >> 1;
+  bool alive = true;
+
+  // logical super-block j -> physical: GATHER walks the own rows first, then the next ranks' rows in ring order
+  auto tile_coords = [&](int t, int& mt, int& n0) {
+    const int g = t / tiles_per_group;
+    const int first_m = g * TP_GROUP_M;
+    const int gsz = min(m_tiles - first_m, TP_GROUP_M);
+    const int r = t - g * tiles_per_group;
+    int sb = first_m + (r % gsz);
+    sb = (sb + (p.mode == 1 ? p.rank : p.rank + 1) * sb_per_rank) % m_tiles;   // REDUCE: remote rows first, own last
+    mt = sb * 2 + (int)crank;                          // this CTA's 128-row block
+    n0 = (r / gsz) * BN;
+  };
+
+  if (warp == 0) {
+    if (elect_one_sync()) {
+      uint32_t it = 0;
+      int last_ready = -1;
+      for (int t = cluster_id; t < num_tiles && alive; t += num_clusters) {
+        int mt, n0;
+        tile_coords(t, mt, n0);
+        if (p.mode == 1 && mt / m_blocks_per_rank != p.rank && mt != last_ready) {
+          if (!flag_wait_geq_gpu(p.flags + 2 + mt, p.epoch * TP_SUB, p.wait_cycles, 1100)) {
+            alive = false;
+            if (p.status) atomicExch(p.status, 1u);
+            break;
+          }
+          fence_proxy_async_global();
+          last_ready = mt;
+        }
+        const int nb0 = n0 + (int)crank * 128;
+        for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
+          const int s = it % STAGES;
+          if (!mbar_wait(&empty_bar[s], ((it / STAGES) & 1u) ^ 1u, alive, 1101)) break;
+          if (leader) mbar_expect_tx(&full_bar[s], 2 * TP2_STAGE_BYTES);
+          tma_load_2d_2cta(smem_a + s * 16384, &tmA, &full_bar[s], kb * TP_BK, mt * TP_BM);
+          uint8_t* b_dst = smem_b + s * 16384;
+          if (!p.b_mn) {
+            tma_load_2d_2cta(b_dst, &tmB, &full_bar[s], kb * TP_BK, nb0);
+          } else {
+            tma_load_2d_2cta(b_dst, &tmB, &full_bar[s], nb0, kb * TP_BK);
+            tma_load_2d_2cta(b_dst + 8192, &tmB, &full_bar[s], nb0 + 64, kb * TP_BK);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (leader && elect_one_sync()) {
+      const uint32_t idesc = make_idesc(256, BN, 1, 1, 0u, (uint32_t)p.b_mn);
+      const uint32_t b_kstep = p.b_mn ? 2048u : 32u;
+      const uint32_t b_lbo = p.b_mn ? 8192u : 16u;
+      uint32_t it = 0, tile_it = 0;
+      for (int t = cluster_id; t < num_tiles && alive; t += num_clusters, ++tile_it) {
+        const uint32_t acc = tile_it & 1u;
+        if (!mbar_wait(&tempty_bar[acc], ((tile_it >> 1) & 1u) ^ 1u, alive, 1110)) break;
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
+          const int s = it % STAGES;
+          if (!mbar_wait(&full_bar[s], (it / STAGES) & 1u, alive, 1111)) break;
+          tc_fence_after_sync();
+          const uint32_t a_addr = smem_u32(smem_a + s * 16384), b_addr = smem_u32(smem_b + s * 16384);
+#pragma unroll
+          for (int k = 0; k < TP_BK / 16; ++k)
+            umma_f16_ss_2cta(d_tmem, make_smem_desc_sw128(a_addr + k * 32, 16, 1024),
+                             make_smem_desc_sw128(b_addr + k * b_kstep, b_lbo, 1024), idesc, (kb | k) != 0 ? 1u : 0u);
+          umma_commit_2cta_mc(&empty_bar[s], 3);
+        }
+        if (!alive) break;
+        umma_commit_2cta_mc(&tfull_bar[acc], 3);
+      }
+    }
+  } else if (warp < 6) {
+    const int q = warp & 3;
+    uint32_t tile_it = 0;
+    bool entry_ok = (p.mode != 2);
+    for (int t = cluster_id; t < num_tiles && alive; t += num_clusters, ++tile_it) {
+      int mt, n0;
+      tile_coords(t, mt, n0);
+      const uint32_t acc = tile_it & 1u;
+      if (!mbar_wait(&tfull_bar[acc], (tile_it >> 1) & 1u, alive, 1120)) break;
+      tc_fence_after_sync();
+      if (!entry_ok) {
+        if (!flag_wait_geq_gpu(p.flags, p.epoch, p.wait_cycles, 1121)) {
+          alive = false;
+          if (p.status) atomicExch(p.status, 1u);
+          break;
+        }
+        entry_ok = true;
+      }
+      const int row = mt * TP_BM + q * 32 + lane;
+      const uint32_t t_row = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(t_row + c * 32, r);
+        tc_wait_ld();
+        const int col0 = n0 + c * 32;
+        if (row >= p.M || col0 >= p.N) continue;
+        if (p.mode == 2) {
+          tp_reduce_chunk(p, peers, r, row, col0);
+        } else {
+          __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<size_t>(row) * p.ldc + col0;
+          if (col0 + 32 <= p.N && ((reinterpret_cast<uintptr_t>(dst) & 15u) == 0)) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              uint4 v;
+              v.x = pack_bf16x2(__uint_as_float(r[8 * j]), __uint_as_float(r[8 * j + 1]));
+              v.y = pack_bf16x2(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]));
+              v.z = pack_bf16x2(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]));
+              v.w = pack_bf16x2(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]));
+              *reinterpret_cast<uint4*>(dst + 8 * j) = v;
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (col0 + j < p.N) dst[j] = __float2bfloat16(__uint_as_float(r[j]));
+          }
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(&tempty_bar[acc], 0);
+    }
+    __threadfence_system();
+  } else {
+    // ------------------------------ copiers (warps 6..9): identical protocol to the single-CTA kernel ------------------------------
+    const int ct = threadIdx.x - 192;
+    if (blockIdx.x == 0) {
+      if (ct < p.world) {
+        __threadfence_system();
+        st_release_sys(peers.pad[ct] + p.slot0 + p.rank, p.epoch);
+        if (!flag_wait_geq_sys(peers.pad[p.rank] + p.slot0 + ct, p.epoch, p.wait_cycles, 1130) && p.status)
+          atomicExch(p.status, 1u);
+      }
+      asm volatile("bar.sync 2, 128;" ::: "memory");
+      if (ct == 0) {
+        const unsigned int bad = p.status ? atomicAdd(p.status, 0u) : 0u;
+        if (!bad) st_release_gpu(p.flags, p.epoch);
+      }
+    }
+    if (p.mode == 1) {
+      if (!flag_wait_geq_gpu(p.flags, p.epoch, p.wait_cycles, 1131)) {
+        if (ct == 0 && p.status) atomicExch(p.status, 1u);
+      } else {
+        const int total_blocks = p.M / TP_BM;
+        const int remote_blocks = total_blocks - m_blocks_per_rank;
+        const int items = remote_blocks * TP_SUB;
+        const int vec_per_row = (p.K / TP_SUB) >> 3;
+        for (int item = blockIdx.x; item < items; item += gridDim.x) {
+          const int jb = item / TP_SUB, sub = item - jb * TP_SUB;
+          const int mt = (jb + (p.rank + 1) * m_blocks_per_rank) % total_blocks;
+          const int owner = mt / m_blocks_per_rank;
+          const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(peers.src[owner]) +
+                                     static_cast<size_t>(mt - owner * m_blocks_per_rank) * TP_BM * p.K + sub * (p.K / TP_SUB);
+          __nv_bfloat16* dst = p.a_full + static_cast<size_t>(mt) * TP_BM * p.K + sub * (p.K / TP_SUB);
+          // eight independent 16-byte peer loads per thread are in flight before the first store: a remote load
+          // takes microseconds, and one-at-a-time copies would leave the link idle
+          const int nvec = TP_BM * vec_per_row;
+          for (int v0 = ct; v0 < nvec; v0 += 128 * 8) {
+            uint4 val[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+              const int v = v0 + u * 128;
+              if (v < nvec) {
+                const int rr = v / vec_per_row, cc = v - rr * vec_per_row;
+                val[u] = *reinterpret_cast<const uint4*>(src + static_cast<size_t>(rr) * p.K + cc * 8);
+              }
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+              const int v = v0 + u * 128;
+              if (v < nvec) {
+                const int rr = v / vec_per_row, cc = v - rr * vec_per_row;
+                *reinterpret_cast<uint4*>(dst + static_cast<size_t>(rr) * p.K + cc * 8) = val[u];
+              }
+            }
+          }
+          __threadfence();
+          asm volatile("bar.sync 2, 128;" ::: "memory");
+          if (ct == 0) atom_add_release_gpu(p.flags + 2 + mt, 1u);
+        }
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc_2cta(tmem_base, TMEM_COLS);
+  }
+  if (warp == 6) {
+    unsigned int last = 0;
+    if (lane == 0) {
+      __threadfence_system();
+      last = (atomicAdd(p.flags + 1, 1u) == gridDim.x - 1) ? 1u : 0u;
+    }
+    last = __shfl_sync(0xffffffffu, last, 0);
+    if (last) {
+      bool ok = true;
+      if (lane < p.world) {
+        __threadfence_system();
+        st_release_sys(peers.pad[lane] + p.slot0 + TP_MAX_WORLD + p.rank, p.epoch);
+        ok = flag_wait_geq_sys(peers.pad[p.rank] + p.slot0 + TP_MAX_WORLD + lane, p.epoch, p.wait_cycles, 1140);
+      }
+      if (!ok && p.status) atomicExch(p.status, 1u);
+      __syncwarp();
+      if (lane == 0) p.flags[1] = 0u;
+    }
+  }
+}
+
+static int launch_tp_2cta(const CUtensorMap& tmA, const CUtensorMap& tmB, const TpParams& p, const TpPeers& peers,
+                          cudaStream_t st) {
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(tp_gemm_2cta_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TP2_SMEM);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  const int tiles = (p.M / 256) * ((p.N + 255) / 256);
+  int clusters = sm_count() / 2;
+  if (tiles < clusters) clusters = tiles;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(clusters * 2);      // all CTAs resident at once: at most one per SM
+  cfg.blockDim = dim3(TP_THREADS);
+  cfg.dynamicSmemBytes = TP2_SMEM;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return (int)cudaLaunchKernelEx(&cfg, tp_gemm_2cta_kernel, tmA, tmB, p, peers);
 }
 
 // dst[i] = bf16(src[i]); src[i] = 0  (turns a finished fp32 reduction buffer into the layer output and re-arms it)
@@ -366,6 +723,8 @@ using namespace ts;
 // mode 1 (all-gather -> GEMM):  C[M,N] = gather_rows(A_shards)[M,K] . B^T.  `a_full` is a local [M][K] bf16 buffer
 //   whose own block (rows rank*rows_per_rank ...) already holds this rank's shard; src_ptrs[r] = rank r's shard.
 // mode 2 (GEMM -> reduce-scatter): dst_ptrs[owner][row - owner*rows_per_rank][:] += A[M,K] . B^T rows, fp32.
+// mode 3: as mode 2 with bf16 accumulation buffers (8 elements per 16-byte red; the sum of W partials is rounded to
+//   bf16 after every addition, like a bf16 ring reduce-scatter).
 // B: b_mn == 0 -> [N][ldb] K-major, b_mn == 1 -> [K][ldb] N-major.  flags: device u32[2 + M/128], zero-initialised once
 // and reused across calls with a growing `epoch`.  pad_ptrs / slot0: signal pads (2*16 slots from slot0 are used).
 extern "C" int ts_tp_gemm(int mode, const void* A, const void* B, void* C, void* a_full, int M, int N, int K, int lda,
@@ -374,8 +733,13 @@ extern "C" int ts_tp_gemm(int mode, const void* A, const void* B, void* C, void*
                           unsigned int* flags, unsigned int epoch, unsigned int slot0, long long wait_cycles,
                           unsigned int* status, void* stream) {
   if (world > TP_MAX_WORLD || M % (TP_BM * world) != 0 || K % (8 * TP_SUB) != 0) return -10;
+  const int acc_bf16 = (mode == 3);     // mode 3: GEMM -> reduce-scatter with packed-bf16 accumulation buffers
+  if (mode == 3) mode = 2;
   if (mode != 1 && mode != 2) return -11;
-  const int bn = (N >= 256) ? 256 : 128;
+  // paired-CTA kernel: every rank's rows split into 256-row super-blocks and enough 256 x 256 tiles for every CTA pair
+  const bool two_cta = (M / world) % 256 == 0 && N >= 256 && (M / 256) * ((N + 255) / 256) >= sm_count() / 2 &&
+                       getenv("TS_TP_GEMM_1CTA") == nullptr;
+  const int bn = two_cta ? 128 : ((N >= 256) ? 256 : 128);     // B box rows (the paired kernel loads half tiles)
   const void* a_base = (mode == 1) ? a_full : A;
   const int a_ld = (mode == 1) ? K : lda;
   CUtensorMap tmA, tmB;
@@ -388,16 +752,18 @@ extern "C" int ts_tp_gemm(int mode, const void* A, const void* B, void* C, void*
   if (rc) return rc * 100 - 2;
   TpParams p{};
   p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.b_mn = b_mn; p.mode = mode; p.rank = rank; p.world = world;
+  p.acc_bf16 = acc_bf16;
   p.rows_per_rank = M / world; p.C = C; p.a_full = (__nv_bfloat16*)a_full;
   p.num_m_tiles = M / TP_BM; p.num_n_tiles = (N + bn - 1) / bn; p.k_blocks = (K + TP_BK - 1) / TP_BK;
   p.flags = flags; p.epoch = epoch; p.slot0 = slot0; p.wait_cycles = wait_cycles; p.status = status;
   TpPeers peers{};
   for (int r = 0; r < world; ++r) {
     peers.src[r] = src_ptrs ? reinterpret_cast<const void*>(src_ptrs[r]) : nullptr;
-    peers.dst[r] = dst_ptrs ? reinterpret_cast<float*>(dst_ptrs[r]) : nullptr;
+    peers.dst[r] = dst_ptrs ? reinterpret_cast<void*>(dst_ptrs[r]) : nullptr;
     peers.pad[r] = reinterpret_cast<unsigned int*>(pad_ptrs[r]);
   }
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (two_cta) return launch_tp_2cta(tmA, tmB, p, peers, st);
   return bn == 256 ? launch_tp<256>(tmA, tmB, p, peers, st) : launch_tp<128>(tmA, tmB, p, peers, st);
 }
 

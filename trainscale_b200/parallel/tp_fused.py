@@ -7,6 +7,8 @@ a reduce-scattered output is an all-gather -> GEMM), and the weight gradients re
 """
 from __future__ import annotations
 
+import os
+
 import ctypes
 
 import torch
@@ -28,7 +30,7 @@ class _Buffers:
         key = (kind, rows, cols)
         b = self.cache.get(key)
         if b is None:
-            dt = torch.bfloat16 if kind == "src" else torch.float32
+            dt = torch.float32 if kind == "acc" else torch.bfloat16     # "src", "acc16": bf16
             t = self.heap.alloc(rows * cols, dt).view(rows, cols)
             buf, _ = self.heap.lookup(t)
             flags = torch.zeros(2 + n_mblocks, dtype=torch.int32, device=t.device)
@@ -48,7 +50,7 @@ def _launch(mode, tp, b, A, B, C, a_full, M, N, K, lda, ldb, ldc, b_mn):
     lib = _lib.load("tp_gemm")
     buf = b["buf"]
     src = buf.peer_ptrs if mode == 1 else None
-    dst = buf.peer_ptrs if mode == 2 else None
+    dst = buf.peer_ptrs if mode in (2, 3) else None
     rc = lib.ts_tp_gemm(mode, _lib.ptr(A), _lib.ptr(B), _lib.ptr(C), _lib.ptr(a_full), M, N, K, lda, ldb, ldc, int(b_mn),
                         src, dst, buf.pad_ptrs, tp.rank, tp.size, _lib.ptr(b["flags"]), _u(b["epoch"]), _u(0),
                         _ll(tp.heap.wait_cycles), _lib.ptr(tp.heap.status), _lib.stream_ptr())
@@ -69,11 +71,23 @@ def _gather_gemm(x_shard, w, tp, b_mn):
     return y, a_full
 
 
+# GEMM -> reduce-scatter accumulates the ranks' partial sums either in fp32 buffers (16-byte reds of 4 values, then a
+# cast pass) or directly in the bf16 output format (16-byte reds of 8 values, no cast pass; every addition rounds to
+# bf16, as a bf16 ring reduce-scatter does).  The packed form moves half the bytes and is the default.
+ACC_BF16 = os.environ.get("TS_TP_ACC_FP32", "0") != "1"
+
+
 def _gemm_reduce(x, w, tp, b_mn):
     """y_shard [M/W, N] (bf16) = reduce_scatter(x @ w^T)."""
     M, K = x.shape
     N = w.shape[1] if b_mn else w.shape[0]
     Ms = M // tp.size
+    if ACC_BF16 and x.dtype == torch.bfloat16:
+        b = _buffers(tp).get("acc16", Ms, N, M // 128)
+        _launch(3, tp, b, x, w, None, None, M, N, K, x.stride(0), w.stride(0), N, b_mn)
+        out = b["t"].clone()
+        b["t"].zero_()        # re-armed before the next call's entry barrier tells the peers so
+        return out
     b = _buffers(tp).get("acc", Ms, N, M // 128)
     _launch(2, tp, b, x, w, None, None, M, N, K, x.stride(0), w.stride(0), N, b_mn)
     out = torch.empty(Ms, N, dtype=x.dtype, device=x.device)
