@@ -219,7 +219,10 @@ def run_ours(args) -> dict:
                 "h2d_bytes_per_step": int(host[0].numel() * host[0].element_size()) * world,
                 "d2h_bytes_per_step": 4 * world},
         "gpu_launches": launches, "final_loss": final_loss,
-        "peak_mem_gb": torch.cuda.max_memory_allocated() / 2 ** 30,
+        # torch's allocator peak plus the symmetric-memory buffers (flat parameters / gradients of the fused path),
+        # which are allocated outside it
+        "peak_mem_gb": (torch.cuda.max_memory_allocated() +
+                        getattr(getattr(trainer.engine, "_symm", None), "bytes_allocated", 0)) / 2 ** 30,
     }
     trainer.cleanup()
     return out if rank == 0 else {}

@@ -73,6 +73,7 @@ class SymmetricHeap:
         mc = int(getattr(h, "multicast_ptr", 0) or 0) if self.use_multicast else 0
         buf = SymmBuffer(t, h, arr(*[int(p) for p in h.buffer_ptrs]), arr(*[int(p) for p in h.signal_pad_ptrs]), mc, {})
         self._by_ptr[t.data_ptr()] = buf
+        self.bytes_allocated = getattr(self, "bytes_allocated", 0) + numel * t.element_size()
         return t
 
     def lookup(self, t: torch.Tensor) -> tuple[SymmBuffer, int]:
