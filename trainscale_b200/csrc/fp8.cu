@@ -3,9 +3,9 @@
 //   C[m][n] = sum_kb ( sum_{k in block kb} Aq[m][k] * Bq[n][k] ) * sa[kb][m] * sb[n / 128][kb]
 //
 // Activations carry one fp32 scale per 1 x 128 block, weights one per 128 x 128 block.  The tensor core reduces one
-// 128-deep block at a time (tcgen05.mma kind::f8f6f4, four K=32 instructions) into one of two TMEM accumulators; eight
+// 128-deep block at a time (tcgen05.mma kind::f8f6f4, four K=32 instructions) into one of four TMEM accumulators; eight
 // epilogue warps drain the finished block, apply the two scales and add into fp32 registers ("promotion") while the MMA
-// warp already fills the other accumulator.  B may be K-major ([N][K], forward) or MN-major ([K][N], dgrad: the same
+// warp already fills the next accumulators.  B may be K-major ([N][K], forward) or MN-major ([K][N], dgrad: the same
 // stored weight without a transpose pass).
 //
 // Replaces _fp8_matmul_block_scaled_kernel / _fp8_matmul_row_scaled_kernel and the quantisation kernels of
@@ -156,7 +156,8 @@ struct Fp8GemmParams {
 __global__ void __launch_bounds__(F8_THREADS, 1)
 fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, Fp8GemmParams p) {
   constexpr int STAGES = F8_STAGES;
-  constexpr uint32_t TMEM_COLS = 2 * F8_BN;
+  constexpr int NACC = 4;                     // 128-column accumulators in flight between MMA and promotion
+  constexpr uint32_t TMEM_COLS = NACC * F8_BN;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* smem_a = smem;
@@ -164,9 +165,9 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * F8_STAGE_BYTES);
   uint64_t* full_bar = bars;
   uint64_t* empty_bar = bars + STAGES;
-  uint64_t* tfull_bar = bars + 2 * STAGES;
-  uint64_t* tempty_bar = bars + 2 * STAGES + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  uint64_t* tfull_bar = bars + 2 * STAGES;            // [NACC]
+  uint64_t* tempty_bar = bars + 2 * STAGES + NACC;     // [NACC]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 2 * NACC);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
@@ -176,10 +177,10 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
     }
-    mbar_init(&tfull_bar[0], 1);
-    mbar_init(&tfull_bar[1], 1);
-    mbar_init(&tempty_bar[0], 8);
-    mbar_init(&tempty_bar[1], 8);
+    for (int a = 0; a < NACC; ++a) {
+      mbar_init(&tfull_bar[a], 1);
+      mbar_init(&tempty_bar[a], 8);
+    }
     fence_barrier_init();
   }
   if (warp == 1) {
@@ -224,8 +225,8 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       for (int t = blockIdx.x; t < num_tiles && alive; t += gridDim.x) {
         for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
           const int s = it % STAGES;
-          const uint32_t acc = it & 1u;
-          if (!mbar_wait(&tempty_bar[acc], ((it >> 1) & 1u) ^ 1u, alive, 910)) break;
+          const uint32_t acc = it % NACC;
+          if (!mbar_wait(&tempty_bar[acc], ((it / NACC) & 1u) ^ 1u, alive, 910)) break;
           if (!mbar_wait(&full_bar[s], (it / STAGES) & 1u, alive, 911)) break;
           tc_fence_after_sync();
           const uint32_t a_addr = smem_u32(smem_a + s * 16384), b_addr = smem_u32(smem_b + s * 16384);
@@ -253,9 +254,9 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       for (int j = 0; j < 64; ++j) accum[j] = 0.f;
       const float* sbp = p.sb + static_cast<long long>(n0 / 128) * p.sb_n;
       for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
-        const uint32_t acc = it & 1u;
+        const uint32_t acc = it % NACC;
         const float sc = p.sa[static_cast<size_t>(kb) * p.M + rowc] * sbp[kb * p.sb_k];
-        if (!mbar_wait(&tfull_bar[acc], (it >> 1) & 1u, alive, 920)) break;
+        if (!mbar_wait(&tfull_bar[acc], (it / NACC) & 1u, alive, 920)) break;
         tc_fence_after_sync();
         uint32_t v[64];
         tmem_ld_32x32b_x32(t_lane + acc * F8_BN, v);

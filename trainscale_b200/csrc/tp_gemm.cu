@@ -77,6 +77,27 @@ __device__ __forceinline__ void tp_reduce_chunk(const TpParams& p, const TpPeers
                                                 int col0) {
   const int owner = row / p.rows_per_rank;
   const size_t off = static_cast<size_t>(row - owner * p.rows_per_rank) * p.N + col0;
+  if (p.acc_bf16 && owner == p.rank && p.C != nullptr) {
+    // this rank's own rows need no reduction traffic: the partial sum is stored into a private buffer and added to
+    // what the peers reduced into the shared one after the kernel
+    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + off;
+    if (col0 + 32 <= p.N && ((reinterpret_cast<uintptr_t>(dst) & 15u) == 0)) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        uint4 v;
+        v.x = pack_bf16x2(__uint_as_float(r[8 * j]), __uint_as_float(r[8 * j + 1]));
+        v.y = pack_bf16x2(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]));
+        v.z = pack_bf16x2(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]));
+        v.w = pack_bf16x2(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]));
+        *reinterpret_cast<uint4*>(dst + 8 * j) = v;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (col0 + j < p.N) dst[j] = __float2bfloat16(__uint_as_float(r[j]));
+    }
+    return;
+  }
   if (p.acc_bf16) {
     __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(peers.dst[owner]) + off;
     if (col0 + 32 <= p.N && ((reinterpret_cast<uintptr_t>(dst) & 15u) == 0)) {
@@ -684,6 +705,26 @@ static int launch_tp_2cta(const CUtensorMap& tmA, const CUtensorMap& tmB, const 
   return (int)cudaLaunchKernelEx(&cfg, tp_gemm_2cta_kernel, tmA, tmB, p, peers);
 }
 
+// out[i] = own[i] + acc[i]; acc[i] = 0  (bf16: the rank's own partial sums plus what the peers reduced into the shared
+// buffer, which is re-armed for the next call)
+__global__ void add_and_clear_kernel(const __nv_bfloat16* __restrict__ own, __nv_bfloat16* __restrict__ acc,
+                                     __nv_bfloat16* __restrict__ out, long long n) {
+  for (long long i = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) * 8; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x * 8) {
+    const uint4 a = *reinterpret_cast<const uint4*>(own + i);
+    const uint4 b = *reinterpret_cast<const uint4*>(acc + i);
+    const float2 a0 = unpack_bf16x2(a.x), a1 = unpack_bf16x2(a.y), a2 = unpack_bf16x2(a.z), a3 = unpack_bf16x2(a.w);
+    const float2 b0 = unpack_bf16x2(b.x), b1 = unpack_bf16x2(b.y), b2 = unpack_bf16x2(b.z), b3 = unpack_bf16x2(b.w);
+    uint4 o;
+    o.x = pack_bf16x2(a0.x + b0.x, a0.y + b0.y);
+    o.y = pack_bf16x2(a1.x + b1.x, a1.y + b1.y);
+    o.z = pack_bf16x2(a2.x + b2.x, a2.y + b2.y);
+    o.w = pack_bf16x2(a3.x + b3.x, a3.y + b3.y);
+    *reinterpret_cast<uint4*>(out + i) = o;
+    *reinterpret_cast<uint4*>(acc + i) = make_uint4(0u, 0u, 0u, 0u);
+  }
+}
+
 // dst[i] = bf16(src[i]); src[i] = 0  (turns a finished fp32 reduction buffer into the layer output and re-arms it)
 __global__ void cast_and_clear_kernel(float* __restrict__ src, __nv_bfloat16* __restrict__ dst, long long n) {
   for (long long i = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) * 4; i < n;
@@ -772,5 +813,15 @@ extern "C" int ts_cast_and_clear(float* src, void* dst, long long n, void* strea
   long long blocks = (n / 4 + 255) / 256;
   if (blocks > (long long)sm_count() * 8) blocks = (long long)sm_count() * 8;
   cast_and_clear_kernel<<<(unsigned)blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(src, (__nv_bfloat16*)dst, n);
+  return (int)cudaGetLastError();
+}
+
+// out = own + acc (bf16), acc = 0.  In place when out == own.
+extern "C" int ts_add_and_clear(const void* own, void* acc, void* out, long long n, void* stream) {
+  if (n <= 0 || n % 8 != 0) return n == 0 ? 0 : -10;
+  long long blocks = (n / 8 + 255) / 256;
+  if (blocks > (long long)sm_count() * 8) blocks = (long long)sm_count() * 8;
+  add_and_clear_kernel<<<(unsigned)blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      (const __nv_bfloat16*)own, (__nv_bfloat16*)acc, (__nv_bfloat16*)out, n);
   return (int)cudaGetLastError();
 }

@@ -84,9 +84,13 @@ def _gemm_reduce(x, w, tp, b_mn):
     Ms = M // tp.size
     if ACC_BF16 and x.dtype == torch.bfloat16:
         b = _buffers(tp).get("acc16", Ms, N, M // 128)
-        _launch(3, tp, b, x, w, None, None, M, N, K, x.stride(0), w.stride(0), N, b_mn)
-        out = b["t"].clone()
-        b["t"].zero_()        # re-armed before the next call's entry barrier tells the peers so
+        out = torch.empty(Ms, N, dtype=x.dtype, device=x.device)     # receives this rank's own partial sums
+        _launch(3, tp, b, x, w, out, None, M, N, K, x.stride(0), w.stride(0), N, b_mn)
+        lib = _lib.load("tp_gemm")
+        # out += what the peers reduced into the shared buffer; the buffer is re-armed (zeroed) in the same pass,
+        # before the next call's entry barrier tells the peers so
+        rc = lib.ts_add_and_clear(_lib.ptr(out), _lib.ptr(b["t"]), _lib.ptr(out), _ll(Ms * N), _lib.stream_ptr())
+        _lib.check(rc, "ts_add_and_clear")
         return out
     b = _buffers(tp).get("acc", Ms, N, M // 128)
     _launch(2, tp, b, x, w, None, None, M, N, K, x.stride(0), w.stride(0), N, b_mn)
