@@ -35,11 +35,17 @@ struct TpPeers {
   unsigned int* pad[TP_MAX_WORLD];       // signal pads
 };
 
+struct TpMaps {
+  CUtensorMap m[TP_MAX_WORLD];           // REDUCE by bulk tensor reduction: rank r's [rows_per_rank][N] bf16 accumulation buffer
+};
+
 struct TpParams {
   int M, N, K, ldc;
   int b_mn;
   int mode;                              // 1 = GATHER, 2 = REDUCE
   int acc_bf16;                          // REDUCE: accumulate packed bf16 pairs (8 elements per 16-byte red) instead of fp32
+  int tma_red;                           // REDUCE: epilogue tiles are added into the owner's bf16 buffer by bulk tensor reductions
+  int push;                              // REDUCE: no atomics - partial sums are stored into slot `rank` of the owner's staging buffer
   int rank, world, rows_per_rank;
   void* C;                               // GATHER: bf16 output [M][ldc]
   __nv_bfloat16* a_full;                 // GATHER: local [M][K] buffer the remote rows are staged into
@@ -77,7 +83,29 @@ __device__ __forceinline__ void tp_reduce_chunk(const TpParams& p, const TpPeers
                                                 int col0) {
   const int owner = row / p.rows_per_rank;
   const size_t off = static_cast<size_t>(row - owner * p.rows_per_rank) * p.N + col0;
-  if (p.acc_bf16 && owner == p.rank && p.C != nullptr) {
+  if (p.push && owner != p.rank) {
+    // plain 16-byte stores of this rank's partial sums into its own slot of the owner's staging buffer
+    // ([W][rows_per_rank][N] bf16): nothing is read-modify-written across NVLink, the owner adds the slots afterwards
+    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(peers.dst[owner]) +
+                         static_cast<size_t>(p.rank) * p.rows_per_rank * p.N + off;
+    if (col0 + 32 <= p.N && ((reinterpret_cast<uintptr_t>(dst) & 15u) == 0)) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        uint4 v;
+        v.x = pack_bf16x2(__uint_as_float(r[8 * j]), __uint_as_float(r[8 * j + 1]));
+        v.y = pack_bf16x2(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]));
+        v.z = pack_bf16x2(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]));
+        v.w = pack_bf16x2(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]));
+        *reinterpret_cast<uint4*>(dst + 8 * j) = v;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (col0 + j < p.N) dst[j] = __float2bfloat16(__uint_as_float(r[j]));
+    }
+    return;
+  }
+  if ((p.acc_bf16 || p.push) && owner == p.rank && p.C != nullptr) {
     // this rank's own rows need no reduction traffic: the partial sum is stored into a private buffer and added to
     // what the peers reduced into the shared one after the kernel
     __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + off;
@@ -413,11 +441,12 @@ tp_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 // ---------------------------------------------------------------------------------------------------------------
 constexpr int TP2_STAGES = 6;
 constexpr int TP2_STAGE_BYTES = 32768;
-constexpr int TP2_SMEM = TP2_STAGES * TP2_STAGE_BYTES + 256 + 1024;
+constexpr int TP2_STG_BYTES = 128 * 64 * 2;        // one 128 x 64 bf16 epilogue tile (128-byte swizzled rows)
+constexpr int TP2_SMEM = TP2_STAGES * TP2_STAGE_BYTES + 2 * TP2_STG_BYTES + 256 + 1024;
 
 __global__ void __launch_bounds__(TP_THREADS, 1)
 tp_gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, TpParams p,
-                    TpPeers peers) {
+                    TpPeers peers, const __grid_constant__ TpMaps maps) {
   constexpr int STAGES = TP2_STAGES;
   constexpr int BN = 256;
   constexpr uint32_t TMEM_COLS = 512;
@@ -425,7 +454,8 @@ tp_gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* smem_a = smem;
   uint8_t* smem_b = smem + STAGES * 16384;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * TP2_STAGE_BYTES);
+  uint8_t* stg = smem + STAGES * TP2_STAGE_BYTES;      // two epilogue staging tiles (1024-byte aligned)
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * TP2_STAGE_BYTES + 2 * TP2_STG_BYTES);
   uint64_t* full_bar = bars;
   uint64_t* empty_bar = bars + STAGES;
   uint64_t* tfull_bar = bars + 2 * STAGES;
@@ -541,6 +571,7 @@ tp_gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     const int q = warp & 3;
     uint32_t tile_it = 0;
     bool entry_ok = (p.mode != 2);
+    uint32_t stg_it = 0;
     for (int t = cluster_id; t < num_tiles && alive; t += num_clusters, ++tile_it) {
       int mt, n0;
       tile_coords(t, mt, n0);
@@ -557,6 +588,44 @@ tp_gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       }
       const int row = mt * TP_BM + q * 32 + lane;
       const uint32_t t_row = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
+      if (p.mode == 2 && p.tma_red) {
+        // 64-column slices of the tile go through a swizzled shared-memory staging tile and are added into the owner's
+        // bf16 buffer by the copy engine: full-width packets on NVLink instead of 16-byte reductions per thread
+        const int et = threadIdx.x - 64;                    // 0..127 among the epilogue threads
+        const int owner = (mt * TP_BM) / p.rows_per_rank;
+        const int y0 = mt * TP_BM - owner * p.rows_per_rank;
+        const uint32_t rr = static_cast<uint32_t>(q * 32 + lane);
+#pragma unroll 1
+        for (int c2 = 0; c2 < BN / 64; ++c2) {
+          uint8_t* buf = stg + (stg_it & 1u) * TP2_STG_BYTES;
+          if (et == 0) tma_store_wait_read<1>();            // the reduction that last read this buffer has drained it
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          uint32_t r[64];
+          tmem_ld_32x32b_x32(t_row + c2 * 64, r);
+          tmem_ld_32x32b_x32(t_row + c2 * 64 + 32, r + 32);
+          tc_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            uint4 v;
+            v.x = pack_bf16x2(__uint_as_float(r[8 * j]), __uint_as_float(r[8 * j + 1]));
+            v.y = pack_bf16x2(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]));
+            v.z = pack_bf16x2(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]));
+            v.w = pack_bf16x2(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]));
+            *reinterpret_cast<uint4*>(buf + sw128_offset(rr, static_cast<uint32_t>(j))) = v;
+          }
+          fence_proxy_async_smem();
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          if (et == 0 && n0 + c2 * 64 < p.N) {
+            tma_reduce_add_2d(&maps.m[owner], buf, n0 + c2 * 64, y0);
+            tma_store_commit();
+          }
+          ++stg_it;
+        }
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(&tempty_bar[acc], 0);
+        continue;
+      }
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
@@ -589,6 +658,7 @@ tp_gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(&tempty_bar[acc], 0);
     }
+    if (p.mode == 2 && p.tma_red && threadIdx.x == 64) tma_store_wait<0>();   // every bulk reduction of this CTA is done
     __threadfence_system();
   } else {
     // ------------------------------ copiers (warps 6..9): identical protocol to the single-CTA kernel ------------------------------
@@ -680,7 +750,7 @@ tp_gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 }
 
 static int launch_tp_2cta(const CUtensorMap& tmA, const CUtensorMap& tmB, const TpParams& p, const TpPeers& peers,
-                          cudaStream_t st) {
+                          const TpMaps& maps, cudaStream_t st) {
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(tp_gemm_2cta_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TP2_SMEM);
@@ -702,7 +772,7 @@ static int launch_tp_2cta(const CUtensorMap& tmA, const CUtensorMap& tmB, const 
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  return (int)cudaLaunchKernelEx(&cfg, tp_gemm_2cta_kernel, tmA, tmB, p, peers);
+  return (int)cudaLaunchKernelEx(&cfg, tp_gemm_2cta_kernel, tmA, tmB, p, peers, maps);
 }
 
 // out[i] = own[i] + acc[i]; acc[i] = 0  (bf16: the rank's own partial sums plus what the peers reduced into the shared
@@ -764,6 +834,12 @@ using namespace ts;
 // mode 1 (all-gather -> GEMM):  C[M,N] = gather_rows(A_shards)[M,K] . B^T.  `a_full` is a local [M][K] bf16 buffer
 //   whose own block (rows rank*rows_per_rank ...) already holds this rank's shard; src_ptrs[r] = rank r's shard.
 // mode 2 (GEMM -> reduce-scatter): dst_ptrs[owner][row - owner*rows_per_rank][:] += A[M,K] . B^T rows, fp32.
+// mode 5: as mode 3 (shared bf16 accumulation buffers), but every 128 x 64 slice of an output tile is staged in shared
+//   memory and added by one bulk tensor reduction (`cp.reduce.async.bulk.tensor ... add`) into the owner's buffer;
+//   needs the paired-CTA kernel (rows_per_rank % 256 == 0, N >= 256, N % 8 == 0), else returns -13.
+// mode 4: no atomics.  dst_ptrs[owner] is a [W][rows_per_rank][N] bf16 staging buffer; this rank stores its partial sums
+//   of the owner's rows into slot `rank` with plain 16-byte stores and its own rows into C ([rows_per_rank][N]); the
+//   caller then adds the W - 1 foreign slots to C (ts_sum_slots).
 // mode 3: as mode 2 with bf16 accumulation buffers (8 elements per 16-byte red; the sum of W partials is rounded to
 //   bf16 after every addition, like a bf16 ring reduce-scatter).
 // B: b_mn == 0 -> [N][ldb] K-major, b_mn == 1 -> [K][ldb] N-major.  flags: device u32[2 + M/128], zero-initialised once
@@ -775,7 +851,9 @@ extern "C" int ts_tp_gemm(int mode, const void* A, const void* B, void* C, void*
                           unsigned int* status, void* stream) {
   if (world > TP_MAX_WORLD || M % (TP_BM * world) != 0 || K % (8 * TP_SUB) != 0) return -10;
   const int acc_bf16 = (mode == 3);     // mode 3: GEMM -> reduce-scatter with packed-bf16 accumulation buffers
-  if (mode == 3) mode = 2;
+  const int push = (mode == 4);         // mode 4: GEMM -> reduce-scatter by plain stores into per-source staging slots
+  const int tma_red = (mode == 5);      // mode 5: as mode 3, tiles added by bulk tensor reductions (paired-CTA kernel only)
+  if (mode == 3 || mode == 4 || mode == 5) mode = 2;
   if (mode != 1 && mode != 2) return -11;
   // paired-CTA kernel: every rank's rows split into 256-row super-blocks and enough 256 x 256 tiles for every CTA pair
   const bool two_cta = (M / world) % 256 == 0 && N >= 256 && (M / 256) * ((N + 255) / 256) >= sm_count() / 2 &&
@@ -794,6 +872,9 @@ extern "C" int ts_tp_gemm(int mode, const void* A, const void* B, void* C, void*
   TpParams p{};
   p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.b_mn = b_mn; p.mode = mode; p.rank = rank; p.world = world;
   p.acc_bf16 = acc_bf16;
+  p.push = push;
+  p.tma_red = tma_red;
+  p.acc_bf16 = acc_bf16 || tma_red;
   p.rows_per_rank = M / world; p.C = C; p.a_full = (__nv_bfloat16*)a_full;
   p.num_m_tiles = M / TP_BM; p.num_n_tiles = (N + bn - 1) / bn; p.k_blocks = (K + TP_BK - 1) / TP_BK;
   p.flags = flags; p.epoch = epoch; p.slot0 = slot0; p.wait_cycles = wait_cycles; p.status = status;
@@ -804,7 +885,18 @@ extern "C" int ts_tp_gemm(int mode, const void* A, const void* B, void* C, void*
     peers.pad[r] = reinterpret_cast<unsigned int*>(pad_ptrs[r]);
   }
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  if (two_cta) return launch_tp_2cta(tmA, tmB, p, peers, st);
+  if (tma_red && (!two_cta || N % 8 != 0)) return -13;   // the caller falls back to mode 3 for such shapes
+  if (two_cta) {
+    TpMaps maps{};
+    if (tma_red) {
+      for (int r = 0; r < world; ++r) {
+        rc = make_tmap_2d(&maps.m[r], peers.dst[r], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)(M / world),
+                          (uint64_t)N, (uint64_t)N, 128, 64);
+        if (rc) return rc * 100 - 3;
+      }
+    }
+    return launch_tp_2cta(tmA, tmB, p, peers, maps, st);
+  }
   return bn == 256 ? launch_tp<256>(tmA, tmB, p, peers, st) : launch_tp<128>(tmA, tmB, p, peers, st);
 }
 
@@ -823,5 +915,43 @@ extern "C" int ts_add_and_clear(const void* own, void* acc, void* out, long long
   if (blocks > (long long)sm_count() * 8) blocks = (long long)sm_count() * 8;
   add_and_clear_kernel<<<(unsigned)blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       (const __nv_bfloat16*)own, (__nv_bfloat16*)acc, (__nv_bfloat16*)out, n);
+  return (int)cudaGetLastError();
+}
+
+// out[i] = own[i] + sum over s != rank of staging[s][i]  (bf16, fp32 accumulation).  In place when out == own.
+__global__ void sum_slots_kernel(const __nv_bfloat16* __restrict__ own, const __nv_bfloat16* __restrict__ staging,
+                                 __nv_bfloat16* __restrict__ out, long long n, int world, int rank) {
+  for (long long i = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) * 8; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x * 8) {
+    float acc[8];
+    {
+      const uint4 a = *reinterpret_cast<const uint4*>(own + i);
+      const float2 a0 = ts::unpack_bf16x2(a.x), a1 = ts::unpack_bf16x2(a.y), a2 = ts::unpack_bf16x2(a.z),
+                   a3 = ts::unpack_bf16x2(a.w);
+      acc[0] = a0.x; acc[1] = a0.y; acc[2] = a1.x; acc[3] = a1.y; acc[4] = a2.x; acc[5] = a2.y; acc[6] = a3.x; acc[7] = a3.y;
+    }
+    for (int s = 0; s < world; ++s) {
+      if (s == rank) continue;
+      const uint4 b = *reinterpret_cast<const uint4*>(staging + static_cast<size_t>(s) * n + i);
+      const float2 b0 = ts::unpack_bf16x2(b.x), b1 = ts::unpack_bf16x2(b.y), b2 = ts::unpack_bf16x2(b.z),
+                   b3 = ts::unpack_bf16x2(b.w);
+      acc[0] += b0.x; acc[1] += b0.y; acc[2] += b1.x; acc[3] += b1.y; acc[4] += b2.x; acc[5] += b2.y; acc[6] += b3.x; acc[7] += b3.y;
+    }
+    uint4 o;
+    o.x = ts::pack_bf16x2(acc[0], acc[1]);
+    o.y = ts::pack_bf16x2(acc[2], acc[3]);
+    o.z = ts::pack_bf16x2(acc[4], acc[5]);
+    o.w = ts::pack_bf16x2(acc[6], acc[7]);
+    *reinterpret_cast<uint4*>(out + i) = o;
+  }
+}
+
+extern "C" int ts_sum_slots(const void* own, const void* staging, void* out, long long n, int world, int rank,
+                            void* stream) {
+  if (n <= 0 || n % 8 != 0) return n == 0 ? 0 : -10;
+  long long blocks = (n / 8 + 255) / 256;
+  if (blocks > (long long)sm_count() * 8) blocks = (long long)sm_count() * 8;
+  sum_slots_kernel<<<(unsigned)blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      (const __nv_bfloat16*)own, (const __nv_bfloat16*)staging, (__nv_bfloat16*)out, n, world, rank);
   return (int)cudaGetLastError();
 }

@@ -50,7 +50,7 @@ def _launch(mode, tp, b, A, B, C, a_full, M, N, K, lda, ldb, ldc, b_mn):
     lib = _lib.load("tp_gemm")
     buf = b["buf"]
     src = buf.peer_ptrs if mode == 1 else None
-    dst = buf.peer_ptrs if mode in (2, 3) else None
+    dst = buf.peer_ptrs if mode in (2, 3, 4) else None
     rc = lib.ts_tp_gemm(mode, _lib.ptr(A), _lib.ptr(B), _lib.ptr(C), _lib.ptr(a_full), M, N, K, lda, ldb, ldc, int(b_mn),
                         src, dst, buf.pad_ptrs, tp.rank, tp.size, _lib.ptr(b["flags"]), _u(b["epoch"]), _u(0),
                         _ll(tp.heap.wait_cycles), _lib.ptr(tp.heap.status), _lib.stream_ptr())
@@ -75,6 +75,11 @@ def _gather_gemm(x_shard, w, tp, b_mn):
 # cast pass) or directly in the bf16 output format (16-byte reds of 8 values, no cast pass; every addition rounds to
 # bf16, as a bf16 ring reduce-scatter does).  The packed form moves half the bytes and is the default.
 ACC_BF16 = os.environ.get("TS_TP_ACC_FP32", "0") != "1"
+# "push": no atomics at all - every rank stores its partial sums of a peer's rows into its own slot of that peer's
+# staging buffer with plain 16-byte stores (NVLink carries them far better than 16-byte reductions) and the owner adds
+# the W slots in fp32 after the kernel.  "red": reductions into one shared buffer (ACC_BF16 picks the format).
+# "tma": shared bf16 buffer, output slices added by bulk tensor reductions (`cp.reduce.async.bulk.tensor`).
+REDUCE_MODE = os.environ.get("TS_TP_REDUCE", "red")
 
 
 def _gemm_reduce(x, w, tp, b_mn):
@@ -82,6 +87,29 @@ def _gemm_reduce(x, w, tp, b_mn):
     M, K = x.shape
     N = w.shape[1] if b_mn else w.shape[0]
     Ms = M // tp.size
+    if REDUCE_MODE == "tma" and x.dtype == torch.bfloat16 and Ms % 256 == 0 and N >= 256 and N % 8 == 0:
+        # 128 x 64 output slices are added into the owner's bf16 buffer by bulk tensor reductions of the copy engine
+        b = _buffers(tp).get("acc16", Ms, N, M // 128)
+        lib = _lib.load("tp_gemm")
+        buf = b["buf"]
+        rc = lib.ts_tp_gemm(5, _lib.ptr(x), _lib.ptr(w), None, None, M, N, K, x.stride(0), w.stride(0), N, int(b_mn),
+                            None, buf.peer_ptrs, buf.pad_ptrs, tp.rank, tp.size, _lib.ptr(b["flags"]), _u(b["epoch"]),
+                            _u(0), _ll(tp.heap.wait_cycles), _lib.ptr(tp.heap.status), _lib.stream_ptr())
+        if rc != -13:
+            _lib.check(rc, "ts_tp_gemm")
+            out = b["t"].clone()
+            b["t"].zero_()        # re-armed before the next call's entry barrier tells the peers so
+            return out
+    if REDUCE_MODE == "push" and x.dtype == torch.bfloat16:
+        # per-source staging slots on the owner, plain stores only; the slots are summed after the kernel
+        b = _buffers(tp).get("push", tp.size * Ms, N, M // 128)
+        out = torch.empty(Ms, N, dtype=x.dtype, device=x.device)     # receives this rank's own partial sums
+        _launch(4, tp, b, x, w, out, None, M, N, K, x.stride(0), w.stride(0), N, b_mn)
+        lib = _lib.load("tp_gemm")
+        rc = lib.ts_sum_slots(_lib.ptr(out), _lib.ptr(b["t"]), _lib.ptr(out), _ll(Ms * N), tp.size, tp.rank,
+                              _lib.stream_ptr())
+        _lib.check(rc, "ts_sum_slots")
+        return out
     if ACC_BF16 and x.dtype == torch.bfloat16:
         b = _buffers(tp).get("acc16", Ms, N, M // 128)
         out = torch.empty(Ms, N, dtype=x.dtype, device=x.device)     # receives this rank's own partial sums
