@@ -71,3 +71,22 @@ def test_moe_layer_uses_grouped_path_and_matches_loop():
     for s in layer.shared:
         ref = ref + s(x2)
     assert (y.reshape(-1, 256).float() - ref.float()).abs().max().item() < 3e-2 * max(ref.float().abs().max().item(), 1.0)
+
+
+@pytest.mark.parametrize("T,E,k,norm", [(300, 8, 2, True), (1000, 64, 6, True), (77, 160, 8, False), (512, 5, 1, True)])
+def test_router_topk_softmax_kernel(T, E, k, norm):
+    from trainscale_b200.ops import moe
+    torch.manual_seed(0)
+    logits = torch.randn(T, E, device="cuda", requires_grad=True)
+    w, idx, probs = moe.topk_softmax(logits, k, norm)
+    ref_l = logits.detach().clone().requires_grad_(True)
+    rp = torch.softmax(ref_l, -1)
+    rw, ridx = rp.topk(k, -1)
+    if norm:
+        rw = rw / rw.sum(-1, keepdim=True)
+    assert torch.equal(idx, ridx)
+    assert torch.allclose(w, rw, atol=1e-6) and torch.allclose(probs, rp, atol=1e-6)
+    gw, gp = torch.randn_like(w), torch.randn_like(probs)
+    ((w * gw).sum() + (probs * gp).sum()).backward()
+    ((rw * gw).sum() + (rp * gp).sum()).backward()
+    assert torch.allclose(logits.grad, ref_l.grad, atol=1e-5)

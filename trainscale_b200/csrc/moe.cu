@@ -152,6 +152,72 @@ __global__ void moe_combine_dw_kernel(const __nv_bfloat16* __restrict__ dout, co
   }
 }
 
+// Router: softmax over E experts and top-k selection, one warp per token (E <= 1024).  probs [T][E] fp32 is written for
+// the auxiliary losses and the backward; weights are the selected probabilities, optionally renormalised to sum to 1.
+// Ties resolve to the lower expert index, as torch.topk does on equal values in practice for distinct logits.
+constexpr int ROUTER_MAX_PER_LANE = 32;
+__global__ void __launch_bounds__(128) moe_topk_softmax_kernel(const float* __restrict__ logits, float* __restrict__ probs,
+                                                              float* __restrict__ weights, int* __restrict__ idx, int T,
+                                                              int E, int k, int normalize) {
+  const int lane = threadIdx.x & 31;
+  const int per = (E + 31) / 32;
+  for (int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); t < T; t += gridDim.x * (blockDim.x >> 5)) {
+    float v[ROUTER_MAX_PER_LANE];
+    float mx = -INFINITY;
+#pragma unroll 4
+    for (int j = 0; j < per; ++j) {
+      const int e = lane + j * 32;
+      v[j] = e < E ? logits[static_cast<size_t>(t) * E + e] : -INFINITY;
+      mx = fmaxf(mx, v[j]);
+    }
+    mx = warp_max(mx);
+    float sum = 0.f;
+#pragma unroll 4
+    for (int j = 0; j < per; ++j) {
+      v[j] = (lane + j * 32 < E) ? __expf(v[j] - mx) : 0.f;
+      sum += v[j];
+    }
+    sum = warp_sum(sum);
+    const float inv = 1.f / sum;
+#pragma unroll 4
+    for (int j = 0; j < per; ++j) {
+      v[j] *= inv;
+      const int e = lane + j * 32;
+      if (e < E) probs[static_cast<size_t>(t) * E + e] = v[j];
+    }
+    float wsum = 0.f;
+    for (int s = 0; s < k; ++s) {
+      // arg-max over what is left: (value, lowest index) reduced across the warp
+      float best = -1.f;
+      int best_e = 0x7fffffff;
+#pragma unroll 4
+      for (int j = 0; j < per; ++j) {
+        const int e = lane + j * 32;
+        if (e < E && v[j] > best) {
+          best = v[j];
+          best_e = e;
+        }
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+        if (ob > best || (ob == best && oe < best_e)) {
+          best = ob;
+          best_e = oe;
+        }
+      }
+      if (lane == 0) {
+        weights[static_cast<size_t>(t) * k + s] = best;
+        idx[static_cast<size_t>(t) * k + s] = best_e;
+      }
+      wsum += best;
+      if ((best_e & 31) == lane) v[best_e >> 5] = -1.f;   // taken
+    }
+    if (normalize && lane < k) weights[static_cast<size_t>(t) * k + lane] /= fmaxf(wsum, 1e-9f);
+  }
+}
+
 }  // namespace ts
 
 TS_DEFINE_ERROR_API(ts_moe)
@@ -201,5 +267,16 @@ extern "C" int ts_moe_combine_dw(const void* dout, const void* y, const int* des
   if (n <= 0 || H % 8 != 0 || k <= 0) return -10;
   moe_combine_dw_kernel<<<row_grid(n), 256, 0, ST(stream)>>>((const __nv_bfloat16*)dout, (const __nv_bfloat16*)y, dest,
                                                              dw, n, H, k);
+  return (int)cudaGetLastError();
+}
+
+// logits fp32 [T][E] -> probs fp32 [T][E], weights fp32 [T][k], idx int32 [T][k]
+extern "C" int ts_moe_topk_softmax(const float* logits, float* probs, float* weights, int* idx, int T, int E, int k,
+                                   int normalize, void* stream) {
+  if (T <= 0 || E <= 0 || E > 32 * ROUTER_MAX_PER_LANE || k <= 0 || k > 32 || k > E) return -10;
+  long long blocks = (T + 3) / 4;
+  const long long cap = static_cast<long long>(sm_count()) * 16;
+  if (blocks > cap) blocks = cap;
+  moe_topk_softmax_kernel<<<(unsigned)blocks, 128, 0, ST(stream)>>>(logits, probs, weights, idx, T, E, k, normalize);
   return (int)cudaGetLastError();
 }

@@ -166,3 +166,51 @@ def moe_ffn(x2: torch.Tensor, expert_ids: torch.Tensor, weights: torch.Tensor, w
     h = activation.glu(h, act)
     y = grouped_linear(h, w_down, plan)
     return _CombineFn.apply(y, weights, plan)
+
+
+class _TopKSoftmaxFn(torch.autograd.Function):
+    """Router softmax + top-k on the device kernel; the (small, [T, E]) backward is written with torch ops."""
+
+    @staticmethod
+    def forward(ctx, logits, k, normalize):
+        lib = _lib.load("moe")
+        T, E = logits.shape
+        lg = logits.float().contiguous()
+        probs = torch.empty_like(lg)
+        w = torch.empty(T, k, dtype=torch.float32, device=lg.device)
+        idx = torch.empty(T, k, dtype=torch.int32, device=lg.device)
+        rc = lib.ts_moe_topk_softmax(_lib.ptr(lg), _lib.ptr(probs), _lib.ptr(w), _lib.ptr(idx), T, E, int(k),
+                                     int(bool(normalize)), _lib.stream_ptr())
+        _lib.check(rc, "ts_moe_topk_softmax")
+        idx64 = idx.long()
+        ctx.save_for_backward(probs, w, idx64)
+        ctx.normalize, ctx.in_dtype = bool(normalize), logits.dtype
+        ctx.mark_non_differentiable(idx64)
+        return w, idx64, probs
+
+    @staticmethod
+    def backward(ctx, dw, _didx, dprobs):
+        probs, w, idx = ctx.saved_tensors
+        dp = torch.zeros_like(probs) if dprobs is None else dprobs.float().clone()
+        if dw is not None:
+            dw = dw.float()
+            if ctx.normalize:
+                raw = probs.gather(1, idx)
+                s = raw.sum(-1, keepdim=True).clamp(min=1e-9)
+                dsel = (dw - (dw * w).sum(-1, keepdim=True)) / s
+            else:
+                dsel = dw
+            dp.scatter_add_(1, idx, dsel)
+        dlogits = probs * (dp - (dp * probs).sum(-1, keepdim=True))
+        return dlogits.to(ctx.in_dtype), None, None
+
+
+def topk_softmax(logits: torch.Tensor, k: int, normalize: bool = True):
+    """(weights [T, k] fp32, experts [T, k] int64, probs [T, E] fp32) of the router logits."""
+    if logits.is_cuda and logits.shape[1] <= 1024 and k <= 32:
+        return _TopKSoftmaxFn.apply(logits, k, normalize)
+    probs = torch.softmax(logits.float(), dim=-1)
+    w, idx = probs.topk(k, dim=-1)
+    if normalize:
+        w = w / w.sum(-1, keepdim=True).clamp(min=1e-9)
+    return w, idx, probs

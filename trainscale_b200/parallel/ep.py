@@ -58,10 +58,8 @@ class TopKRouter(nn.Module):
         logits = F.linear(x.float(), self.weight.float())
         if self.training and cfg.jitter > 0:
             logits = logits * torch.empty_like(logits).uniform_(1 - cfg.jitter, 1 + cfg.jitter)
-        probs = torch.softmax(logits, dim=-1)
-        w, idx = probs.topk(cfg.top_k, dim=-1)
-        if cfg.normalize_topk:
-            w = w / w.sum(-1, keepdim=True).clamp(min=1e-9)
+        from ..ops import moe as moe_ops
+        w, idx, probs = moe_ops.topk_softmax(logits, cfg.top_k, cfg.normalize_topk)   # device kernel on CUDA
         f = F.one_hot(idx, cfg.num_experts).float().sum(1).mean(0) / cfg.top_k
         P = probs.mean(0)
         aux = {"load_balance": cfg.num_experts * (f * P).sum(), "z_loss": (torch.logsumexp(logits, -1) ** 2).mean(),
