@@ -303,3 +303,24 @@ def test_flash_window_softcap_fwd_bwd(S, Hq, Hkv, D, window, softcap):
     sizes = [Hq * D, Hkv * D, Hkv * D]
     for a, b_ in zip(qkv.grad.split(sizes, -1), q2.grad.split(sizes, -1)):
         assert (a.float() - b_).abs().max().item() < 3e-2 * max(b_.abs().max().item(), 1.0)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("rows,V,gamma", [(64, 1024, 2.0), (333, 32000, 1.5), (128, 128256, 2.0)])
+def test_focal_loss_on_ce_kernel(rows, V, gamma):
+    from trainscale_b200.losses import FocalLoss
+    torch.manual_seed(0)
+    logits = (torch.randn(rows, V, device="cuda") * 2).to(torch.bfloat16).requires_grad_(True)
+    labels = torch.randint(0, V, (rows,), device="cuda")
+    labels[::7] = -100
+    fl = FocalLoss(gamma=gamma, alpha=0.25)
+    loss = fl(logits, labels)
+    loss.backward()
+    ref_l = logits.detach().float().requires_grad_(True)
+    valid = labels != -100
+    logp = torch.log_softmax(ref_l[valid], -1).gather(1, labels[valid].unsqueeze(1)).squeeze(1)
+    ref = (0.25 * -((1 - logp.exp()) ** gamma) * logp).mean()
+    ref.backward()
+    assert abs(loss.item() - ref.item()) < 2e-3 * max(1.0, abs(ref.item()))
+    err = (logits.grad.float() - ref_l.grad).abs().max().item()
+    assert err < 3e-2 * max(ref_l.grad.abs().max().item(), 1e-6)

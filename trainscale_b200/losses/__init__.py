@@ -111,6 +111,15 @@ class FocalLoss(nn.Module):
         self.gamma, self.alpha, self.ignore_index, self.reduction = gamma, alpha, ignore_index, reduction
 
     def forward(self, logits, labels):
+        if logits.is_cuda and logits.dtype == torch.bfloat16 and logits.shape[-1] % 8 == 0:
+            # row kernel: online log-sum-exp forward, (softmax - onehot) * row scale backward, nothing V-wide in fp32
+            from ..ops.cross_entropy import focal_loss_rows
+            lab = labels.reshape(-1)
+            loss = focal_loss_rows(logits.reshape(-1, logits.shape[-1]), lab, self.gamma, self.ignore_index)
+            loss = loss[lab != self.ignore_index]
+            if self.alpha is not None:
+                loss = self.alpha * loss
+            return _reduce(loss, self.reduction) if loss.numel() else logits.sum() * 0
         logits = logits.reshape(-1, logits.shape[-1]).float()
         labels = labels.reshape(-1)
         valid = labels != self.ignore_index
@@ -130,6 +139,15 @@ class PolyLoss(nn.Module):
         self.epsilon, self.ignore_index = epsilon, ignore_index
 
     def forward(self, logits, labels):
+        if logits.is_cuda and logits.dtype == torch.bfloat16 and logits.shape[-1] % 8 == 0:
+            # row kernel: online log-sum-exp forward, (softmax - onehot) * row scale backward, nothing V-wide in fp32
+            from ..ops.cross_entropy import focal_loss_rows
+            lab = labels.reshape(-1)
+            loss = focal_loss_rows(logits.reshape(-1, logits.shape[-1]), lab, self.gamma, self.ignore_index)
+            loss = loss[lab != self.ignore_index]
+            if self.alpha is not None:
+                loss = self.alpha * loss
+            return _reduce(loss, self.reduction) if loss.numel() else logits.sum() * 0
         logits = logits.reshape(-1, logits.shape[-1]).float()
         labels = labels.reshape(-1)
         valid = labels != self.ignore_index

@@ -44,6 +44,48 @@ def cross_entropy_logits(logits: torch.Tensor, labels: torch.Tensor, ignore_inde
     return loss, lse
 
 
+class _FocalLossFn(torch.autograd.Function):
+    """Focal loss -(1 - p)^gamma log p on materialised bf16 logits.  Forward: one pass of the cross-entropy kernel gives
+    the per-row ce = -log p.  Backward: d loss / d ce = (1 - p)^gamma + gamma p (1 - p)^(gamma - 1) ce goes in as the
+    kernel's per-row gradient scale, and the kernel writes (softmax - onehot) * scale over a copy of the logits."""
+
+    @staticmethod
+    def forward(ctx, logits, labels, gamma, ignore_index):
+        rows = logits.shape[0]
+        loss = torch.empty(rows, dtype=torch.float32, device=logits.device)
+        lse = torch.empty(rows, dtype=torch.float32, device=logits.device)
+        lg = logits if logits.stride(-1) == 1 and logits.stride(0) % 8 == 0 else logits.contiguous()
+        if lg.stride(0) % 8 != 0 or lg.data_ptr() % 16 != 0:
+            pad = torch.zeros(rows, _pad_ld(lg.shape[1]), dtype=lg.dtype, device=lg.device)
+            pad[:, :lg.shape[1]] = lg
+            lg = pad[:, :logits.shape[1]]
+        _ce_rows(lg, labels, loss, lse, ignore_index, 0.0, 1.0, 0.0, None, 1.0, None, False)
+        p = torch.exp(-loss)
+        valid = labels != ignore_index
+        focal = torch.where(valid, (1 - p).clamp(min=0) ** gamma * loss, torch.zeros_like(loss))
+        ctx.save_for_backward(lg, labels, loss, p, valid)
+        ctx.gamma, ctx.ignore_index = gamma, ignore_index
+        return focal
+
+    @staticmethod
+    def backward(ctx, dfocal):
+        lg, labels, ce, p, valid = ctx.saved_tensors
+        g = ctx.gamma
+        one_m = (1 - p).clamp(min=0)
+        dce = one_m ** g + (g * p * one_m ** (g - 1) * ce if g != 0 else 0.0)
+        scale = torch.where(valid, dce * dfocal.float(), torch.zeros_like(ce)).contiguous()
+        grad = lg.clone()
+        loss = torch.empty_like(ce)
+        lse = torch.empty_like(ce)
+        _ce_rows(grad, labels, loss, lse, ctx.ignore_index, 0.0, 1.0, 0.0, None, 1.0, scale, True)
+        return grad, None, None, None
+
+
+def focal_loss_rows(logits: torch.Tensor, labels: torch.Tensor, gamma: float = 2.0, ignore_index: int = -100):
+    """Per-row focal loss of bf16 CUDA logits [rows, V] on the cross-entropy kernel (rows with ignore_index give 0)."""
+    return _FocalLossFn.apply(logits, labels, float(gamma), int(ignore_index))
+
+
 def _pad_ld(V: int) -> int:
     return (V + 7) // 8 * 8
 
