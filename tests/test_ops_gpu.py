@@ -324,3 +324,19 @@ def test_focal_loss_on_ce_kernel(rows, V, gamma):
     assert abs(loss.item() - ref.item()) < 2e-3 * max(1.0, abs(ref.item()))
     err = (logits.grad.float() - ref_l.grad).abs().max().item()
     assert err < 3e-2 * max(ref_l.grad.abs().max().item(), 1e-6)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name", ["silu", "gelu", "gelu_tanh"])
+def test_plain_activation_kernel(name):
+    from trainscale_b200.ops import activation
+    torch.manual_seed(0)
+    x = (torch.randn(513, 1024, device="cuda") * 2).to(torch.bfloat16).requires_grad_(True)
+    y = activation.act(x, name)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    xr = x.detach().float().requires_grad_(True)
+    yr = F.silu(xr) if name == "silu" else F.gelu(xr, approximate="tanh" if name == "gelu_tanh" else "none")
+    yr.backward(dy.float())
+    assert (y.float() - yr).abs().max().item() < 3e-2
+    assert (x.grad.float() - xr.grad).abs().max().item() < 5e-2

@@ -512,6 +512,30 @@ __global__ void glu_bwd_kernel(const __nv_bfloat16* __restrict__ dout, const __n
   }
 }
 
+// Plain (un-gated) activation: y = act(x); backward dx = dy * act'(x).  n is a multiple of 8.
+__global__ void act_fwd_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y, long long n, int act) {
+  for (long long i = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) * 8; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x * 8) {
+    float a[8], o[8];
+    load8(x + i, a);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) o[e] = act_fwd(a[e], act);
+    store8(y + i, o);
+  }
+}
+__global__ void act_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                               __nv_bfloat16* __restrict__ dx, long long n, int act) {
+  for (long long i = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) * 8; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x * 8) {
+    float a[8], d[8], o[8];
+    load8(x + i, a);
+    load8(dy + i, d);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) o[e] = d[e] * act_bwd(a[e], act);
+    store8(dx + i, o);
+  }
+}
+
 // ---------------------------------------------------------------------------------------------------
 // Row cross-entropy over materialised logits [rows][V] (a vocabulary chunk loop lives in the caller).
 // Pass 1: online max / sum-exp. Pass 2 (optional): logits <- (softmax - onehot) * gscale in place.
@@ -939,6 +963,18 @@ extern "C" int ts_glu_bwd(const void* dout, const void* gate_up, void* dgate_up,
   if (I % 8 != 0 || ld % 8 != 0) return -10;
   glu_bwd_kernel<<<grid_for(rows * (I / 8), 256, 16), 256, 0, ST(stream)>>>((const bf16*)dout, (const bf16*)gate_up,
                                                                             (bf16*)dgate_up, rows, I, ld, act);
+  return (int)cudaGetLastError();
+}
+
+// act: 0 = SiLU, 1 = GELU (erf), 2 = GELU (tanh)
+extern "C" int ts_act_fwd(const void* x, void* y, long long n, int act, void* stream) {
+  if (n <= 0 || n % 8 != 0) return n == 0 ? 0 : -10;
+  act_fwd_kernel<<<grid_for(n / 8, 256, 16), 256, 0, ST(stream)>>>((const bf16*)x, (bf16*)y, n, act);
+  return (int)cudaGetLastError();
+}
+extern "C" int ts_act_bwd(const void* dy, const void* x, void* dx, long long n, int act, void* stream) {
+  if (n <= 0 || n % 8 != 0) return n == 0 ? 0 : -10;
+  act_bwd_kernel<<<grid_for(n / 8, 256, 16), 256, 0, ST(stream)>>>((const bf16*)dy, (const bf16*)x, (bf16*)dx, n, act);
   return (int)cudaGetLastError();
 }
 

@@ -72,3 +72,41 @@ def glu(gate_up: torch.Tensor, act: str = "silu") -> torch.Tensor:
 def swiglu(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
     """silu(gate) * up for separate tensors (API parity with the reference's swiglu_forward)."""
     return glu(torch.cat((gate, up), dim=-1), "silu")
+
+
+class _ActFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, act_id):
+        lib = _lib.load("elementwise")
+        xc = x if x.is_contiguous() else x.contiguous()
+        y = torch.empty_like(xc)
+        _lib.check(lib.ts_act_fwd(_lib.ptr(xc), _lib.ptr(y), ctypes.c_longlong(xc.numel()), act_id, _lib.stream_ptr()),
+                   "ts_act_fwd")
+        ctx.save_for_backward(xc)
+        ctx.act_id = act_id
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        lib = _lib.load("elementwise")
+        (xc,) = ctx.saved_tensors
+        d = dy if dy.is_contiguous() else dy.contiguous()
+        dx = torch.empty_like(xc)
+        _lib.check(lib.ts_act_bwd(_lib.ptr(d), _lib.ptr(xc), _lib.ptr(dx), ctypes.c_longlong(xc.numel()), ctx.act_id,
+                                  _lib.stream_ptr()), "ts_act_bwd")
+        return dx, None
+
+
+def act(x: torch.Tensor, name: str = "gelu") -> torch.Tensor:
+    """Un-gated SiLU / GELU (erf or tanh form) on the vectorised kernel for bf16 CUDA tensors, PyTorch otherwise
+    (data_pipeline/trainer/kernels/triton_kernels.py:1295)."""
+    kind = _ACT[name]
+    if x.is_cuda and x.dtype == torch.bfloat16 and x.numel() % 8 == 0:
+        return _ActFn.apply(x, kind)
+    if kind == 0:
+        return F.silu(x)
+    return F.gelu(x, approximate="tanh" if kind == 2 else "none")
+
+
+def gelu(x: torch.Tensor, approximate: str = "none") -> torch.Tensor:
+    return act(x, "gelu_tanh" if approximate == "tanh" else "gelu")
