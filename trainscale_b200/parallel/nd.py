@@ -25,7 +25,12 @@ class NDEngine:
         overlap = True
         if self.dims.enabled("tp"):
             from . import tp as TP
-            ctx = TP.TPContext.from_group(self.dims.group("tp"), p.sp, "nccl", None)
+            heap = None
+            if cfg.distributed.comm in ("auto", "fused") and torch.device(trainer.device).type == "cuda":
+                # all-gather->GEMM and GEMM->reduce-scatter inside one kernel over the tp group's peer memory
+                from .symm import SymmetricHeap
+                heap = SymmetricHeap.try_create(self.dims.group("tp"), trainer.device)
+            ctx = TP.TPContext.from_group(self.dims.group("tp"), p.sp, "fused" if heap is not None else "nccl", heap)
             TP.shard_model_for_tensor_parallel(model, ctx)
             self.tp = ctx
             if p.sp:
