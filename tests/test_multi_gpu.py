@@ -38,3 +38,13 @@ def test_engine_matches_single_process_on_two_gpus(args, port):
 def test_tensor_parallel_decoder_on_two_gpus(args, port):
     out = _launch("tp_equivalence.py", "--cuda", *args, port=port)
     assert "ok=False" not in out
+
+
+@pytest.mark.parametrize("mode,port", [("sp", 29738), ("pp", 29739)])
+def test_trainer_config_tensor_sequence_and_pipeline_parallel_on_two_gpus(mode, port):
+    """YAML-style config -> SOTATrainer -> tensor + sequence parallel decoder on the fused all-gather->GEMM /
+    GEMM->reduce-scatter kernels (and a 2-stage pipeline), losses against a single-process trainer."""
+    out = _launch("trainer_nd.py", "--mode", mode, "--cuda", port=port)
+    assert "RESULT" in out and "ok=True" in out
+    if mode == "sp":
+        assert "tp comm: fused" in out

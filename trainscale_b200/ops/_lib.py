@@ -38,7 +38,14 @@ def stream_ptr() -> ctypes.c_void_p:
 
 
 def ptr(t: torch.Tensor | None) -> ctypes.c_void_p:
-    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+    """Device address of `t` for a kernel argument.  The kernels launch on the CURRENT device's stream, so a tensor
+    that lives on another GPU is refused here, on the host, instead of faulting on the device."""
+    if t is None:
+        return ctypes.c_void_p(0)
+    if t.is_cuda and t.device.index != torch.cuda.current_device():
+        raise KernelError(f"tensor on {t.device} passed to a kernel while the current device is "
+                          f"cuda:{torch.cuda.current_device()}; call torch.cuda.set_device (or use torch.cuda.device) first")
+    return ctypes.c_void_p(t.data_ptr())
 
 
 def check(rc: int, what: str) -> None:
