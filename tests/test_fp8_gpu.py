@@ -71,3 +71,25 @@ def test_fp8linear_module_uses_native_path():
     ref = x.detach().float() @ w.float().t()
     assert (y.float() - ref).abs().mean().item() <= 0.05 * ref.abs().mean().item() + 1e-3
     assert x.grad is not None and torch.isfinite(x.grad.float()).all()
+
+
+def test_decoder_trains_with_fp8_projections():
+    """enable_fp8(): layer projections on the fp8 kernel; loss tracks the bf16 model and goes down under training."""
+    from trainscale_b200.models.llama import LlamaConfig, build_model
+    from trainscale_b200.parallel.flat_engine import EngineConfig, FlatShardedEngine
+    cfg = LlamaConfig(vocab_size=512, hidden_size=256, intermediate_size=512, num_hidden_layers=2,
+                      num_attention_heads=4, num_key_value_heads=2, head_dim=64)
+    ref = build_model(cfg, dtype=torch.bfloat16, device="cuda", seed=0)
+    m = build_model(cfg, dtype=torch.bfloat16, device="cuda", seed=0)
+    m.enable_fp8(True)
+    ids = torch.randint(0, 512, (4, 256), device="cuda", generator=torch.Generator(device="cuda").manual_seed(0))
+    l_ref, l_fp8 = ref(ids, labels=ids).loss.item(), m(ids, labels=ids).loss.item()
+    assert abs(l_ref - l_fp8) < 0.05 * l_ref
+    eng = FlatShardedEngine(m, EngineConfig(lr=3e-3), device=torch.device("cuda"))
+    losses = []
+    for _ in range(8):
+        loss = m(ids, labels=ids).loss
+        eng.backward(loss)
+        eng.step()
+        losses.append(loss.item())
+    assert all(l == l for l in losses) and losses[-1] < losses[0] - 0.3, losses

@@ -104,8 +104,15 @@ def preset_config(name: str, **overrides) -> LlamaConfig:
 
 
 def _lin(mod, x, name: str):
-    """x @ W^T plus the low-rank adapter of that weight when one is attached."""
-    y = gemm.linear(x, getattr(mod, name))
+    """x @ W^T plus the low-rank adapter of that weight when one is attached.  With `mod.fp8` the product runs on the
+    block-scaled fp8 tensor-core kernel (forward and dgrad; wgrad and the master weights stay bf16 / fp32)."""
+    w = getattr(mod, name)
+    if getattr(mod, "fp8", False) and x.is_cuda and x.dtype == torch.bfloat16 and x.shape[-1] % 128 == 0 \
+            and w.shape[0] % 8 == 0:
+        from ..ops import fp8 as fp8_ops
+        y = fp8_ops.fp8_linear(x, w)
+    else:
+        y = gemm.linear(x, w)
     if mod.lora is not None and name in mod.lora:
         y = y + mod.lora[name](x)
     return y
@@ -173,7 +180,7 @@ class LlamaDecoderLayer(nn.Module):
 
     def forward(self, x, residual, cos, sin, position_ids=None, cu_seqlens=None, doc_ids=None, kv_cache=None):
         if self.op_selective and self.training and kv_cache is None and self.self_attn.lora is None \
-                and self.mlp.lora is None:
+                and self.mlp.lora is None and not getattr(self.mlp, "fp8", False):
             n1, n2 = self.input_layernorm, self.post_attention_layernorm
             qkv, residual = fused_blocks.norm_linear(x, residual, n1.weight, self.self_attn.wqkv, n1.eps)
             a = self.self_attn.attend(qkv, cos, sin, position_ids, cu_seqlens, doc_ids, None)
@@ -312,6 +319,12 @@ class LlamaForCausalLM(nn.Module):
     def gradient_checkpointing_enable(self, every: int = 1):
         self.model.gradient_checkpointing = True
         self.model.checkpoint_every = max(1, every)
+
+    def enable_fp8(self, enabled: bool = True):
+        """Block-scaled fp8 (E4M3) GEMMs for the attention and MLP projections (the head and the embedding stay bf16)."""
+        for layer in self.model.layers:
+            layer.self_attn.fp8 = enabled
+            layer.mlp.fp8 = enabled
 
     def op_selective_recompute(self, enabled: bool = True):
         """Operator-level selective recomputation: no layer is re-run, but norm and GLU outputs are rebuilt in

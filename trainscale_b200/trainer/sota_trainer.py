@@ -186,6 +186,9 @@ class SOTATrainer:
         if self.config.lora.enabled:
             from ..lora import apply_lora
             self.model = apply_lora(self.model, self.config.lora)
+        if getattr(self.config.hardware.precision, "value", self.config.hardware.precision) in ("fp8_e4m3", "fp8") \
+                and hasattr(self.model, "enable_fp8") and self.device.type == "cuda":
+            self.model.enable_fp8(True)      # bf16 parameters, fp8 tensor-core GEMMs for the layer projections
         d = self.config.distributed
         fc = dict(d.fsdp_config or {})
         use_ckpt = bool(fc.get("activation_checkpointing", d.gradient_checkpointing))
