@@ -48,3 +48,9 @@ def test_trainer_config_tensor_sequence_and_pipeline_parallel_on_two_gpus(mode, 
     assert "RESULT" in out and "ok=True" in out
     if mode == "sp":
         assert "tp comm: fused" in out
+
+
+def test_weight_gather_gemm_on_two_gpus():
+    """The parameter all-gather of a ZeRO-3 forward inside the GEMM kernel equals the product with the full weight."""
+    out = _launch("weight_gather_gemm.py", port=29742)
+    assert "RESULT weight_gather ok=True" in out

@@ -42,7 +42,7 @@ struct TpMaps {
 struct TpParams {
   int M, N, K, ldc;
   int b_mn;
-  int mode;                              // 1 = GATHER, 2 = REDUCE
+  int mode;                              // 1 = GATHER (rows of A), 2 = REDUCE, 3 = GATHER_B (rows of the weight operand)
   int acc_bf16;                          // REDUCE: accumulate packed bf16 pairs (8 elements per 16-byte red) instead of fp32
   int tma_red;                           // REDUCE: epilogue tiles are added into the owner's bf16 buffer by bulk tensor reductions
   int push;                              // REDUCE: no atomics - partial sums are stored into slot `rank` of the owner's staging buffer
@@ -504,9 +504,14 @@ tp_gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     const int gsz = min(m_tiles - first_m, TP_GROUP_M);
     const int r = t - g * tiles_per_group;
     int sb = first_m + (r % gsz);
-    sb = (sb + (p.mode == 1 ? p.rank : p.rank + 1) * sb_per_rank) % m_tiles;   // REDUCE: remote rows first, own last
+    int nt = r / gsz;
+    if (p.mode == 3) {
+      nt = (nt + p.rank * (n_tiles / p.world)) % n_tiles;       // GATHER_B: this rank's own weight rows first
+    } else {
+      sb = (sb + (p.mode == 1 ? p.rank : p.rank + 1) * sb_per_rank) % m_tiles;   // REDUCE: remote rows first, own last
+    }
     mt = sb * 2 + (int)crank;                          // this CTA's 128-row block
-    n0 = (r / gsz) * BN;
+    n0 = nt * BN;
   };
 
   if (warp == 0) {
@@ -526,6 +531,19 @@ tp_gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           last_ready = mt;
         }
         const int nb0 = n0 + (int)crank * 128;
+        if (p.mode == 3) {
+          // the 128 weight rows this CTA loads come from a peer: wait until the copiers have staged the block
+          const int nblk = nb0 / TP_BM, n_blocks_per_rank = p.N / (TP_BM * p.world);
+          if (nblk / n_blocks_per_rank != p.rank && nblk != last_ready) {
+            if (!flag_wait_geq_gpu(p.flags + 2 + nblk, p.epoch * TP_SUB, p.wait_cycles, 1102)) {
+              alive = false;
+              if (p.status) atomicExch(p.status, 1u);
+              break;
+            }
+            fence_proxy_async_global();
+            last_ready = nblk;
+          }
+        }
         for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
           const int s = it % STAGES;
           if (!mbar_wait(&empty_bar[s], ((it / STAGES) & 1u) ^ 1u, alive, 1101)) break;
@@ -676,11 +694,13 @@ tp_gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         if (!bad) st_release_gpu(p.flags, p.epoch);
       }
     }
-    if (p.mode == 1) {
+    if (p.mode == 1 || p.mode == 3) {
       if (!flag_wait_geq_gpu(p.flags, p.epoch, p.wait_cycles, 1131)) {
         if (ct == 0 && p.status) atomicExch(p.status, 1u);
       } else {
-        const int total_blocks = p.M / TP_BM;
+        // GATHER stages rows of A ([M][K]), GATHER_B rows of the weight ([N][K]); same walk, other extents
+        const int total_blocks = (p.mode == 1 ? p.M : p.N) / TP_BM;
+        const int m_blocks_per_rank = total_blocks / p.world;
         const int remote_blocks = total_blocks - m_blocks_per_rank;
         const int items = remote_blocks * TP_SUB;
         const int vec_per_row = (p.K / TP_SUB) >> 3;
@@ -954,4 +974,36 @@ extern "C" int ts_sum_slots(const void* own, const void* staging, void* out, lon
   sum_slots_kernel<<<(unsigned)blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       (const __nv_bfloat16*)own, (const __nv_bfloat16*)staging, (__nv_bfloat16*)out, n, world, rank);
   return (int)cudaGetLastError();
+}
+
+// Weight-gather GEMM (the ZeRO-3 / FSDP forward in one kernel): C[M][N] = A[M][K] . gather_rows(W_shards)[N][K]^T.
+// Every rank owns N / world consecutive rows of the weight; `w_full` is a local [N][K] bf16 buffer whose own block
+// already holds this rank's shard, src_ptrs[r] = rank r's shard.  Copier warps of the persistent paired-CTA GEMM pull
+// the remote row blocks in the order the tiles need them (the own N tiles are computed first) and the TMA producer of
+// a CTA waits on the counter of the 128-row block it loads.  Requires (N / world) % 256 == 0, M % 256 == 0.
+// flags: device u32[2 + N/128].
+extern "C" int ts_weight_gather_gemm(const void* A, void* C, void* w_full, int M, int N, int K, int lda, int ldc,
+                                     const unsigned long long* src_ptrs, const unsigned long long* pad_ptrs, int rank,
+                                     int world, unsigned int* flags, unsigned int epoch, unsigned int slot0,
+                                     long long wait_cycles, unsigned int* status, void* stream) {
+  if (world > TP_MAX_WORLD || world <= 0 || N % (256 * world) != 0 || M % 256 != 0 || K % (8 * TP_SUB) != 0) return -10;
+  if ((M / 256) * (N / 256) < sm_count() / 2) return -13;       // too small for the paired-CTA kernel
+  CUtensorMap tmA, tmB;
+  int rc = make_tmap_2d(&tmA, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)M, (uint64_t)K, (uint64_t)lda, TP_BM, 64);
+  if (rc) return rc * 100 - 1;
+  rc = make_tmap_2d(&tmB, w_full, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)N, (uint64_t)K, (uint64_t)K, 128, 64);
+  if (rc) return rc * 100 - 2;
+  TpParams p{};
+  p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.b_mn = 0; p.mode = 3; p.rank = rank; p.world = world;
+  p.rows_per_rank = M;        // A is not sharded
+  p.C = C; p.a_full = (__nv_bfloat16*)w_full;                  // staging target of the copiers
+  p.num_m_tiles = M / TP_BM; p.num_n_tiles = N / 128; p.k_blocks = (K + TP_BK - 1) / TP_BK;
+  p.flags = flags; p.epoch = epoch; p.slot0 = slot0; p.wait_cycles = wait_cycles; p.status = status;
+  TpPeers peers{};
+  for (int r = 0; r < world; ++r) {
+    peers.src[r] = reinterpret_cast<const void*>(src_ptrs[r]);
+    peers.pad[r] = reinterpret_cast<unsigned int*>(pad_ptrs[r]);
+  }
+  TpMaps maps{};
+  return launch_tp_2cta(tmA, tmB, p, peers, maps, reinterpret_cast<cudaStream_t>(stream));
 }

@@ -187,3 +187,34 @@ def linear_reduce(x: torch.Tensor, w: torch.Tensor, tp, scatter: bool = True) ->
         from .tp import _all_gather_dim
         y = _all_gather_dim(y, tp, 0)
     return y
+
+
+def gather_weight_linear(x: torch.Tensor, w_shard: torch.Tensor, tp) -> torch.Tensor:
+    """y[M, N] = x[M, K] @ gather_rows(w_shard over the group)[N, K]^T with the weight all-gather running inside the
+    GEMM kernel (the parameter gather of a ZeRO-3 / FSDP forward): peers' row blocks are pulled over NVLink by copier
+    warps while the tensor cores already work on the tiles of this rank's own rows.  Forward only.
+    Falls back to all_gather + GEMM for shapes the paired-CTA kernel does not take."""
+    import torch.distributed as dist
+    from ..ops.gemm import matmul_nt
+    M, K = x.shape
+    Ns = w_shard.shape[0]
+    N = Ns * tp.size
+    lib = _lib.load("tp_gemm")
+    if x.is_cuda and x.dtype == torch.bfloat16 and Ns % 256 == 0 and M % 256 == 0 and K % 32 == 0:
+        b = _buffers(tp).get("wsrc", Ns, K, N // 128)
+        b["t"].copy_(w_shard)
+        w_full = torch.empty(N, K, dtype=x.dtype, device=x.device)
+        w_full[tp.rank * Ns:(tp.rank + 1) * Ns].copy_(w_shard)
+        y = torch.empty(M, N, dtype=x.dtype, device=x.device)
+        buf = b["buf"]
+        xc = x if x.is_contiguous() else x.contiguous()
+        rc = lib.ts_weight_gather_gemm(_lib.ptr(xc), _lib.ptr(y), _lib.ptr(w_full), M, N, K, xc.stride(0), N,
+                                       buf.peer_ptrs, buf.pad_ptrs, tp.rank, tp.size, _lib.ptr(b["flags"]),
+                                       _u(b["epoch"]), _u(0), _ll(tp.heap.wait_cycles), _lib.ptr(tp.heap.status),
+                                       _lib.stream_ptr())
+        if rc != -13:
+            _lib.check(rc, "ts_weight_gather_gemm")
+            return y
+    full = torch.empty(N, K, dtype=w_shard.dtype, device=w_shard.device)
+    dist.all_gather_into_tensor(full, w_shard.contiguous(), group=tp.group)
+    return matmul_nt(x, full)
