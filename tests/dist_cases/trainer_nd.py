@@ -94,6 +94,38 @@ def main():
         ok &= good
         if rank == 0:
             print(f"step {step} mode={a.mode} loss={l1:.5f} oracle={l0:.5f} ok={good}", flush=True)
+    # one HuggingFace-layout checkpoint out of the model-parallel ranks: equal to the oracle's weights, and a resume
+    # from it leaves every rank's shard / stage as it was
+    import tempfile
+    box = [tempfile.mkdtemp(prefix="ts_nd_ckpt_") if rank == 0 else None]
+    dist.broadcast_object_list(box, src=0)
+    ck = Path(box[0]) / "checkpoint-3"
+    tr.save_checkpoint(ck)
+    exp = tr.export(output_dir=str(Path(box[0]) / "export"), fmt="safetensors")
+    if rank == 0:
+        from trainscale_b200.hub import ModelDeserializer
+        want = ref.model.to_hf_state_dict()
+        for d in (ck, exp):
+            got = ModelDeserializer().load(d)
+            same_keys = set(got) == set(want)
+            worst = max(float((got[k].float().cpu() - want[k].float().cpu()).abs().max()) for k in want if k in got)
+            shapes = all(got[k].shape == want[k].shape for k in want if k in got)
+            good = same_keys and shapes and worst < (6e-2 if CUDA else 2e-3)
+            ok &= good
+            print(f"checkpoint {d.name}: keys={same_keys} shapes={shapes} max|diff|={worst:.2e} ok={good}", flush=True)
+    own = tr.engine.stage_module if tr.engine.pipelined else tr.model     # a stage trains only its own layers
+    before = {n: q.detach().clone() for n, q in own.named_parameters()}
+    with torch.no_grad():
+        for q in own.parameters():
+            q.zero_()
+    tr.load_checkpoint(ck)
+    back = all(torch.equal(q.detach(), before[n]) for n, q in own.named_parameters())
+    ok &= back
+    if not back:
+        bad = [n for n, q in own.named_parameters() if not torch.equal(q.detach(), before[n])]
+        print(f"rank {rank}: not restored: {bad[:6]}", flush=True)
+    if rank == 0:
+        print(f"resume restores this rank's weights: {back}", flush=True)
     flag = torch.tensor([0.0 if ok else 1.0], device=dev)
     dist.all_reduce(flag)
     if CUDA:

@@ -56,10 +56,45 @@ def save_model_weights(model, path: Path, max_shard_bytes: int = 5 * 2 ** 30) ->
         (path / "config.json").write_text(json.dumps(model.hf_config_dict(), indent=2))
 
 
-def load_model_weights(model, path: Path, strict: bool = True) -> None:
+def save_model_parallel_weights(trainer, path: Path) -> None:
+    """Weights of a tensor- / pipeline-parallel run as ONE HuggingFace-layout checkpoint.  Every tensor-parallel
+    group gathers its projections to full width; the ranks whose tp / dp / cp coordinates are 0 (one per pipeline
+    stage) write their stage's layers as shard files of a common numbering, and global rank 0 writes the index over
+    all stages.  Collective: every rank calls it."""
+    from ..hub import HAVE_SAFETENSORS, ModelSerializer
+    eng, model = trainer.engine, trainer.model
+    dims = eng.dims
+    first = last = True
+    if eng.pipelined:
+        first, last = eng.stage_module.first, eng.stage_module.last
+    writer = dims.local_rank("tp") == 0 and dims.local_rank("dp_cp") == 0
+    sd = model.to_hf_state_dict(tp=eng.tp, first=first, last=last, keep=writer)
+    if not writer:
+        return
+    P, stage = dims.size("pp"), dims.pp_stage
+    if P > 1 and not HAVE_SAFETENSORS:
+        raise CheckpointSaveError("a pipelined checkpoint needs the safetensors package (one shard file per stage)")
+    ser = ModelSerializer()
+    if P == 1:
+        ser.save(sd, path)
+    else:
+        counts = [None] * P
+        dist.all_gather_object(counts, len(ser.plan(sd)), group=dims.group("pp"))
+        part = ser.save_part(sd, path, sum(counts[:stage]), sum(counts))
+        parts = [None] * P
+        dist.all_gather_object(parts, part, group=dims.group("pp"))
+        if stage == 0:
+            ser.write_index(path, parts)
+    if trainer.rank == 0 and hasattr(model, "hf_config_dict"):
+        (path / "config.json").write_text(json.dumps(model.hf_config_dict(), indent=2))
+
+
+def load_model_weights(model, path: Path, strict: bool = True, tp=None) -> None:
     from ..hub import ModelDeserializer
     sd = ModelDeserializer().load(path)
-    if hasattr(model, "load_hf_state_dict"):
+    if tp is not None:
+        model.load_hf_state_dict(sd, strict=strict, tp=tp)
+    elif hasattr(model, "load_hf_state_dict"):
         model.load_hf_state_dict(sd, strict=strict)
     else:
         model.load_state_dict(sd, strict=strict)
@@ -78,6 +113,11 @@ def save_training_checkpoint(trainer, path: Path) -> None:
         with summon:
             if rank == 0:
                 path.mkdir(parents=True, exist_ok=True)
+            if eng is not None and hasattr(eng, "dims") and (eng.tp is not None or eng.pipelined):
+                if trainer.is_distributed:
+                    dist.barrier()
+                save_model_parallel_weights(trainer, path)
+            elif rank == 0:
                 save_model_weights(trainer.model, path)
         if trainer.is_distributed:
             dist.barrier()
@@ -141,7 +181,7 @@ def load_training_checkpoint(trainer, path: Path) -> None:
         summon = eng.summon_full_params() if eng is not None and hasattr(eng, "summon_full_params") \
             else contextlib.nullcontext()
         with summon:
-            load_model_weights(trainer.model, path, strict=False)
+            load_model_weights(trainer.model, path, strict=False, tp=getattr(eng, "tp", None))
             if eng is not None and hasattr(eng, "units"):
                 # the flat buffers alias the parameters: refresh the shards and fp32 masters from the loaded weights
                 for u in eng.units:

@@ -118,12 +118,22 @@ class ModelSerializer:
     def save(self, sd: dict[str, torch.Tensor], out_dir: str | os.PathLike) -> dict:
         out = Path(out_dir)
         out.mkdir(parents=True, exist_ok=True)
-        sd = {k: v.detach().cpu().contiguous() for k, v in sd.items()}
         if not HAVE_SAFETENSORS:
+            sd = {k: v.detach().cpu().contiguous() for k, v in sd.items()}
             tmp = out / "model.pt.tmp"
             torch.save(sd, tmp)
             os.replace(tmp, out / "model.pt")
             return {"format": "pt", "files": ["model.pt"]}
+        part = self.save_part(sd, out, 0, len(self.plan(sd)))
+        self.write_index(out, [part])
+        return {"format": "safetensors", "files": part["files"]}
+
+    def save_part(self, sd: dict[str, torch.Tensor], out_dir: str | os.PathLike, first_index: int, total: int) -> dict:
+        """Write this writer's tensors as shard files number first_index+1 ... of `total` (several writers, e.g. one
+        per pipeline stage, fill one directory); returns {files, weight_map, sha256, total_size} for `write_index`."""
+        out = Path(out_dir)
+        out.mkdir(parents=True, exist_ok=True)
+        sd = {k: v.detach().cpu().contiguous() for k, v in sd.items()}
         # tied tensors share storage: safetensors refuses aliases, so clone duplicates
         seen: dict[int, str] = {}
         for k, v in list(sd.items()):
@@ -131,21 +141,27 @@ class ModelSerializer:
             if p in seen and v.numel() > 0:
                 sd[k] = v.clone()
             seen[p] = k
-        shards = self.plan(sd)
-        n = len(shards)
         weight_map, files, hashes = {}, [], {}
-        for i, keys in enumerate(shards):
-            name = "model.safetensors" if n == 1 else f"model-{i + 1:05d}-of-{n:05d}.safetensors"
+        for i, keys in enumerate(self.plan(sd)):
+            name = "model.safetensors" if total == 1 else f"model-{first_index + i + 1:05d}-of-{total:05d}.safetensors"
             tmp = out / (name + ".tmp")
             _st_save({k: sd[k] for k in keys}, str(tmp), metadata={"format": "pt"})
             os.replace(tmp, out / name)
             files.append(name)
             hashes[name] = compute_sha256(out / name)
             weight_map.update({k: name for k in keys})
-        index = {"metadata": {"total_size": sum(v.numel() * v.element_size() for v in sd.values()), "sha256": hashes},
-                 "weight_map": weight_map}
-        (out / "model.safetensors.index.json").write_text(json.dumps(index, indent=2))
-        return {"format": "safetensors", "files": files}
+        return {"files": files, "weight_map": weight_map, "sha256": hashes,
+                "total_size": sum(v.numel() * v.element_size() for v in sd.values())}
+
+    @staticmethod
+    def write_index(out_dir: str | os.PathLike, parts: list[dict]) -> None:
+        weight_map, hashes, size = {}, {}, 0
+        for p in parts:
+            weight_map.update(p["weight_map"])
+            hashes.update(p["sha256"])
+            size += p["total_size"]
+        index = {"metadata": {"total_size": size, "sha256": hashes}, "weight_map": weight_map}
+        (Path(out_dir) / "model.safetensors.index.json").write_text(json.dumps(index, indent=2))
 
 
 class ModelDeserializer:

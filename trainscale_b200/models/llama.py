@@ -366,34 +366,73 @@ class LlamaForCausalLM(nn.Module):
         return cap * torch.tanh(z / cap) if cap and cap > 0 else z
 
     # ---------------------------------------------------------------- HF interop
-    def to_hf_state_dict(self) -> dict[str, torch.Tensor]:
+    @torch.no_grad()
+    def to_hf_state_dict(self, tp=None, first: bool = True, last: bool = True,
+                         keep: bool = True) -> dict[str, torch.Tensor]:
+        """Weights in HuggingFace Llama naming (layout of transformers' LlamaForCausalLM checkpoints).
+
+        `tp`: a tensor-parallel context; every projection is then gathered over its group to full width (a
+        collective: all ranks of the group call this), one tensor at a time, landing on the host.  `keep=False`
+        takes part in the gathers and returns an empty dict (ranks that do not write).
+        Layers replaced by `nn.Identity` (other pipeline stages) are skipped; `first` / `last` say whether this
+        stage owns the embedding and the final norm + head."""
+        import torch.distributed as dist
         cfg = self.config
         D, Hq, Hkv, I = cfg.head_dim, cfg.num_attention_heads, cfg.num_key_value_heads, cfg.intermediate_size
-        sd = {"model.embed_tokens.weight": self.model.embed_tokens.weight.detach(),
-              "model.norm.weight": self.model.norm.weight.detach()}
+        ws = tp.size if tp is not None and tp.active else 1
+        sd: dict[str, torch.Tensor] = {}
+
+        def full(t, dim):
+            t = t.detach()
+            if ws == 1:
+                return t
+            parts = [torch.empty_like(t) for _ in range(ws)]
+            dist.all_gather(parts, t.contiguous(), group=tp.group)
+            return torch.cat(parts, dim).cpu() if keep else None
+
+        def put(name, t):
+            if keep:
+                sd[name] = t
+
+        if first:
+            put("model.embed_tokens.weight", self.model.embed_tokens.weight.detach())
+        if last:
+            put("model.norm.weight", self.model.norm.weight.detach())
         for i, l in enumerate(self.model.layers):
+            if isinstance(l, nn.Identity):
+                continue
             p = f"model.layers.{i}."
-            q, k, v = l.self_attn.wqkv.detach().split((Hq * D, Hkv * D, Hkv * D), dim=0)
-            g, u = l.mlp.w_gate_up.detach().split((I, I), dim=0)
-            sd.update({p + "self_attn.q_proj.weight": q, p + "self_attn.k_proj.weight": k,
-                       p + "self_attn.v_proj.weight": v, p + "self_attn.o_proj.weight": l.self_attn.wo.detach(),
-                       p + "mlp.gate_proj.weight": g, p + "mlp.up_proj.weight": u,
-                       p + "mlp.down_proj.weight": l.mlp.w_down.detach(),
-                       p + "input_layernorm.weight": l.input_layernorm.weight.detach(),
-                       p + "post_attention_layernorm.weight": l.post_attention_layernorm.weight.detach()})
-        if self.lm_head is not None:
-            sd["lm_head.weight"] = self.lm_head.detach()
+            attn, mlp = getattr(l.self_attn, "inner", l.self_attn), getattr(l.mlp, "inner", l.mlp)
+            q, k, v = attn.wqkv.detach().split((Hq // ws * D, Hkv // ws * D, Hkv // ws * D), dim=0)
+            g, u = mlp.w_gate_up.detach().split((I // ws, I // ws), dim=0)
+            for name, t, dim in (("self_attn.q_proj", q, 0), ("self_attn.k_proj", k, 0), ("self_attn.v_proj", v, 0),
+                                 ("self_attn.o_proj", attn.wo, 1), ("mlp.gate_proj", g, 0), ("mlp.up_proj", u, 0),
+                                 ("mlp.down_proj", mlp.w_down, 1)):
+                put(p + name + ".weight", full(t, dim))
+            put(p + "input_layernorm.weight", l.input_layernorm.weight.detach())
+            put(p + "post_attention_layernorm.weight", l.post_attention_layernorm.weight.detach())
+        if self.lm_head is not None and last:
+            put("lm_head.weight", self.lm_head.detach())
         return sd
 
     @torch.no_grad()
-    def load_hf_state_dict(self, sd: dict[str, torch.Tensor], strict: bool = True) -> list[str]:
+    def load_hf_state_dict(self, sd: dict[str, torch.Tensor], strict: bool = True, tp=None) -> list[str]:
+        """Inverse of `to_hf_state_dict`.  With a tensor-parallel context each rank copies its slice of every
+        projection (head groups of q/k/v, column blocks of gate/up, input blocks of o/down); `nn.Identity` layers
+        (other pipeline stages) are skipped."""
         missing = []
+        ws = tp.size if tp is not None and tp.active else 1
+        r = tp.rank if ws > 1 else 0
 
-        def get(name):
+        def get(name, dim=None):
             if name not in sd:
                 missing.append(name)
                 return None
-            return sd[name]
+            t = sd[name]
+            if dim is not None and ws > 1:
+                n = t.shape[dim] // ws
+                t = t.narrow(dim, r * n, n)
+            return t
 
         def put(dst, parts):
             if any(p is None for p in parts):
@@ -403,11 +442,14 @@ class LlamaForCausalLM(nn.Module):
         put(self.model.embed_tokens.weight, [get("model.embed_tokens.weight")])
         put(self.model.norm.weight, [get("model.norm.weight")])
         for i, l in enumerate(self.model.layers):
+            if isinstance(l, nn.Identity):
+                continue
             p = f"model.layers.{i}."
-            put(l.self_attn.wqkv, [get(p + f"self_attn.{n}_proj.weight") for n in "qkv"])
-            put(l.self_attn.wo, [get(p + "self_attn.o_proj.weight")])
-            put(l.mlp.w_gate_up, [get(p + "mlp.gate_proj.weight"), get(p + "mlp.up_proj.weight")])
-            put(l.mlp.w_down, [get(p + "mlp.down_proj.weight")])
+            attn, mlp = getattr(l.self_attn, "inner", l.self_attn), getattr(l.mlp, "inner", l.mlp)
+            put(attn.wqkv, [get(p + f"self_attn.{n}_proj.weight", 0) for n in "qkv"])
+            put(attn.wo, [get(p + "self_attn.o_proj.weight", 1)])
+            put(mlp.w_gate_up, [get(p + "mlp.gate_proj.weight", 0), get(p + "mlp.up_proj.weight", 0)])
+            put(mlp.w_down, [get(p + "mlp.down_proj.weight", 1)])
             put(l.input_layernorm.weight, [get(p + "input_layernorm.weight")])
             put(l.post_attention_layernorm.weight, [get(p + "post_attention_layernorm.weight")])
         if self.lm_head is not None:

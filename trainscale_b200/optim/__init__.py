@@ -130,6 +130,10 @@ class Adam8bit(Optimizer):
                         st["m_q"], st["m_s"] = _quantize_blockwise(z, g["block_size"])
                         st["v_q"], st["v_s"] = _quantize_blockwise(z, g["block_size"])
                 st["step"] += 1
+                if not small and g["block_size"] in K.QUANT_BLOCKS and K.native_ok(p, p.grad):
+                    K.adam8bit_(p, p.grad, st["m_q"], st["m_s"], st["v_q"], st["v_s"], lr=g["lr"], beta1=b1, beta2=b2,
+                                eps=g["eps"], weight_decay=g["weight_decay"], step=st["step"])
+                    continue
                 gf = p.grad.float()
                 if small:
                     m, v = st["m"], st["v"]
@@ -197,6 +201,13 @@ class LAMB(Optimizer):
                 if not st:
                     st["step"], st["m"], st["v"] = 0, torch.zeros_like(p, dtype=torch.float32), torch.zeros_like(p, dtype=torch.float32)
                 st["step"] += 1
+                if K.native_ok(p, p.grad):
+                    if "upd" not in st:
+                        st["upd"], st["norms"] = torch.empty_like(st["m"]), torch.zeros(2, device=p.device)
+                    K.lamb_(p, p.grad, st["m"], st["v"], st["upd"], st["norms"], lr=g["lr"], beta1=b1, beta2=b2,
+                            eps=g["eps"], weight_decay=g["weight_decay"], step=st["step"],
+                            trust_lo=g["clamp_trust"][0], trust_hi=g["clamp_trust"][1])
+                    continue
                 gf = p.grad.float()
                 st["m"].mul_(b1).add_(gf, alpha=1 - b1)
                 st["v"].mul_(b2).addcmul_(gf, gf, value=1 - b2)
@@ -229,30 +240,41 @@ class AdaFactor(Optimizer):
             for p in g["params"]:
                 if p.grad is None:
                     continue
-                gf = p.grad.float()
                 st = self.state[p]
-                factored = gf.dim() >= 2
+                factored = p.dim() >= 2
                 if not st:
                     st["step"] = 0
                     if factored:
-                        st["row"] = torch.zeros(gf.shape[:-1], device=gf.device)
-                        st["col"] = torch.zeros(gf.shape[:-2] + gf.shape[-1:], device=gf.device)
+                        st["row"] = torch.zeros(p.shape[:-1], device=p.device)
+                        st["col"] = torch.zeros(p.shape[:-2] + p.shape[-1:], device=p.device)
                     else:
-                        st["v"] = torch.zeros_like(gf)
+                        st["v"] = torch.zeros_like(p, dtype=torch.float32)
                     if g["beta1"] is not None:
-                        st["m"] = torch.zeros_like(gf)
+                        st["m"] = torch.zeros_like(p, dtype=torch.float32)
                     st["rms"] = 0.0
                 st["step"] += 1
-                pf = p.float()
-                st["rms"] = float(self._rms(pf))
                 if g["relative_step"]:
                     min_step = 1e-6 * st["step"] if g["warmup_init"] else 1e-2
                     lr = min(min_step, 1.0 / math.sqrt(st["step"]))
                 else:
                     lr = g["lr"]
+                beta2 = 1.0 - st["step"] ** g["decay_rate"]
+                if K.native_ok(p, p.grad) and p.dim() <= 2 and p.numel() < 2 ** 31:
+                    # device path: parameter RMS, update RMS and the clip stay on the device
+                    if "u" not in st:
+                        st["u"] = torch.empty_like(p, dtype=torch.float32)
+                        st["sums"] = torch.zeros(2, device=p.device)
+                        if factored:
+                            st["col_tmp"] = torch.zeros_like(st["col"])
+                    K.adafactor_(p, p.grad, st, lr=lr, beta2=beta2, eps0=g["eps"][0], eps1=g["eps"][1],
+                                 clip=g["clip_threshold"], scale_parameter=g["scale_parameter"], beta1=g["beta1"],
+                                 weight_decay=g["weight_decay"])
+                    continue
+                gf = p.grad.float()
+                pf = p.float()
+                st["rms"] = float(self._rms(pf))
                 if g["scale_parameter"]:
                     lr = lr * max(g["eps"][1], st["rms"])
-                beta2 = 1.0 - st["step"] ** g["decay_rate"]
                 upd = gf * gf + g["eps"][0]
                 if factored:
                     st["row"].mul_(beta2).add_(upd.mean(-1), alpha=1 - beta2)
@@ -339,6 +361,9 @@ class SophiaG(Optimizer):
                 st = self.state[p]
                 if "h" not in st:
                     st["h"] = torch.zeros_like(p, dtype=torch.float32)
+                if K.native_ok(st["h"], p.grad):
+                    K.sophia_hessian_(p.grad, st["h"], beta2=b2, scale=(1 - b2) * batch_size)
+                    continue
                 st["h"].mul_(b2).addcmul_(p.grad.float(), p.grad.float(), value=(1 - b2) * batch_size)
 
     @torch.no_grad()
@@ -354,6 +379,10 @@ class SophiaG(Optimizer):
                     st["m"] = torch.zeros_like(p, dtype=torch.float32)
                 if "h" not in st:
                     st["h"] = torch.zeros_like(p, dtype=torch.float32)
+                if K.native_ok(p, p.grad):
+                    K.sophia_step_(p, p.grad, st["m"], st["h"], lr=g["lr"], beta1=b1, rho=g["rho"],
+                                   weight_decay=g["weight_decay"], eps=g["eps"])
+                    continue
                 st["m"].mul_(b1).add_(p.grad.float(), alpha=1 - b1)
                 pf = p.float().mul_(1 - g["lr"] * g["weight_decay"])
                 ratio = (st["m"].abs() / (g["rho"] * st["h"] + g["eps"])).clamp(max=1.0)
@@ -454,6 +483,10 @@ class ScheduleFreeAdamW(Optimizer):
                 if not st:
                     st["z"] = p.detach().float().clone()
                     st["v"] = torch.zeros_like(p, dtype=torch.float32)
+                if K.native_ok(p, p.grad):
+                    K.schedule_free_(p, p.grad, st["z"], st["v"], lr=lr, beta1=b1, beta2=b2, eps=g["eps"],
+                                     weight_decay=g["weight_decay"], c=c)
+                    continue
                 gf = p.grad.float()
                 st["v"].mul_(b2).addcmul_(gf, gf, value=1 - b2)
                 gn = gf / (st["v"].sqrt() + g["eps"])
@@ -468,8 +501,28 @@ class ScheduleFreeAdamW(Optimizer):
         return loss
 
 
+def _newton_schulz_bf16(G: torch.Tensor, steps: int) -> torch.Tensor:
+    """The quintic iteration in bf16 on the tcgen05 GEMM (three GEMMs per step, the polynomial's additions folded
+    into the GEMMs' alpha / accumulate epilogues).  Returns bf16."""
+    from ..ops import gemm
+    a, b, c = 3.4445, -4.7750, 2.0315
+    t = G.shape[0] > G.shape[1]
+    X = G.float().t() if t else G.float()
+    X = (X / (X.norm() + 1e-7)).to(torch.bfloat16).contiguous()
+    for _ in range(steps):
+        A = gemm.matmul_nt(X, X)                                # A = X X^T (symmetric)
+        B = A * b
+        gemm.matmul_nt(A, A, out=B, accumulate=True, alpha=c)   # B = b A + c A A   (A^T = A)
+        Xn = X * a
+        gemm.matmul_nn(B, X, out=Xn, accumulate=True)           # X <- a X + B X
+        X = Xn
+    return X.t() if t else X
+
+
 def newton_schulz_orthogonalize(G: torch.Tensor, steps: int = 5) -> torch.Tensor:
     a, b, c = 3.4445, -4.7750, 2.0315
+    if G.is_cuda and G.dim() == 2 and G.shape[0] % 8 == 0 and G.shape[1] % 8 == 0:
+        return _newton_schulz_bf16(G, steps)
     X = G.float()
     t = X.shape[-2] > X.shape[-1]
     if t:
@@ -533,13 +586,18 @@ class ADOPT(Optimizer):
             for p in g["params"]:
                 if p.grad is None:
                     continue
-                gf = p.grad.float()
                 st = self.state[p]
                 if not st:
-                    st["step"], st["m"], st["v"] = 0, torch.zeros_like(gf), gf * gf
-                    st["step"] = 1
+                    gf = p.grad.float()
+                    st["step"], st["m"], st["v"] = 1, torch.zeros_like(gf), gf * gf
                     continue
                 st["step"] += 1
+                if K.native_ok(p, p.grad):
+                    clip = g["clip_lambda"](st["step"]) if g["clip_lambda"] is not None else None
+                    K.adopt_(p, p.grad, st["m"], st["v"], lr=g["lr"], beta1=b1, beta2=b2, eps=g["eps"],
+                             weight_decay=g["weight_decay"], clip=clip)
+                    continue
+                gf = p.grad.float()
                 n = gf / torch.clamp(st["v"].sqrt(), min=g["eps"])
                 if g["clip_lambda"] is not None:
                     c = g["clip_lambda"](st["step"])

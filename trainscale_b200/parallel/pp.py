@@ -222,7 +222,9 @@ class LlamaStage(nn.Module):
         self._tied = last and model.lm_head is None
         if self._tied:
             self.tied_embedding = model.model.embed_tokens   # last stage keeps its own copy; grads are all-reduced
-        self._rope = model.model
+        # rotary tables come from the whole decoder; kept out of the module tree so that a stage's parameters are
+        # exactly what it trains (the optimizer of stage k must not hold another stage's embedding or norm)
+        object.__setattr__(self, "_rope", model.model)
 
     def forward(self, x, labels=None, loss_scale: float = 1.0):
         """First stage: x = token ids [B, S]. Other stages: x = packed (hidden | residual) [B, S, 2H].

@@ -15,6 +15,8 @@ causal shift + loss run in the fused lm_head/cross-entropy head, and DDP/FSDP ar
 """
 from __future__ import annotations
 
+import contextlib
+
 import logging
 import math
 import os
@@ -545,12 +547,30 @@ class SOTATrainer:
         from ..export import export_model
         e = self.config.export
         out = Path(output_dir or e.output_dir)
+        fmt = fmt or getattr(e.format, "value", e.format)
+        eng = self.engine
         if self.is_distributed:
             dist.barrier()
-        if not self.is_main:
-            return None
-        return export_model(self.model, out, fmt or getattr(e.format, "value", e.format), tokenizer=tokenizer,
-                            merge_lora=e.merge_lora)
+        if eng is not None and hasattr(eng, "dims") and (eng.tp is not None or eng.pipelined):
+            # tensor / pipeline parallel: the weights live on several ranks; all of them take part
+            if str(fmt).lower() not in ("safetensors", "hf", "huggingface"):
+                raise ValueError(f"export format {fmt!r} of a model-parallel run: export safetensors, then convert "
+                                 "the checkpoint on one process")
+            from ..ckpt import save_model_parallel_weights
+            if self.is_main:
+                out.mkdir(parents=True, exist_ok=True)
+            dist.barrier()
+            save_model_parallel_weights(self, out)
+            dist.barrier()
+            if self.is_main and tokenizer is not None and hasattr(tokenizer, "save_pretrained"):
+                tokenizer.save_pretrained(str(out))
+            return out if self.is_main else None
+        summon = eng.summon_full_params() if eng is not None and hasattr(eng, "summon_full_params") \
+            else contextlib.nullcontext()
+        with summon:       # FULL_SHARD keeps only shards between steps; every rank materialises, rank 0 writes
+            if not self.is_main:
+                return None
+            return export_model(self.model, out, fmt, tokenizer=tokenizer, merge_lora=e.merge_lora)
 
     def cleanup(self) -> None:
         self.engine = None
