@@ -1,0 +1,114 @@
+"""The reference's class-level API of the distributed layer (FSDP2 facade, general pipeline API) on CPU."""
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+import torch.nn as nn
+
+CASES = Path(__file__).parent / "dist_cases"
+
+
+def launch(case, nproc, port, *args, timeout=300):
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
+           "--master-addr", "127.0.0.1", "--master-port", str(port), str(CASES / case), *args]
+    return subprocess.run(cmd, capture_output=True, text=True, timeout=timeout)
+
+
+def test_fsdp2_facade_two_ranks():
+    r = launch("fsdp2_facade.py", 2, 29681)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    assert "RESULT ok=True" in r.stdout
+
+
+def test_fsdp2_config_and_helpers():
+    from trainscale_b200.parallel import fsdp2 as F
+    c = F.FSDP2Config(sharding_strategy="hybrid_shard", mixed_precision="bf16", bucket_size_mb=40)
+    assert c.sharding_strategy is F.ShardingStrategy.HYBRID_SHARD and c.bucket_size_bytes == 40 * 2 ** 20
+    assert c.to_engine_config().sharding_strategy == "FULL_SHARD"
+    assert F.ShardingStrategy.NO_SHARD.requires_all_gather is False
+    assert F.MixedPrecisionPolicy.FULL_BF16.get_param_dtype() is torch.bfloat16
+    with pytest.raises(ValueError):
+        F.FSDP2Config(gradient_accumulation_steps=0)
+    with pytest.raises(ValueError):
+        F.FSDP2Config(mixed_precision="fp16")
+    pool = F.MemoryPool("cpu")
+    a = pool.allocate(1000, torch.float32)
+    ptr = a.data_ptr()
+    pool.release(a)
+    b = pool.allocate(900, torch.float32)
+    assert b.data_ptr() == ptr and pool.get_stats()["hits"] == 1
+    acc = F.GradientAccumulator(2)
+    lin = nn.Linear(4, 4)
+    for _ in range(2):
+        lin(torch.ones(1, 4)).sum().backward()
+        acc.accumulate(lin)
+    assert acc.should_sync
+    acc.apply_to_model(lin)
+    assert torch.allclose(lin.weight.grad, torch.ones(4, 4))
+    mc = F.MetricsCollector("cpu")
+    with mc.measure_forward():
+        pass
+    mc.record_step()
+    assert "forward_ms" in mc.get_average()
+    f = F.create_fsdp2_from_dict({"fsdp_sharding_strategy": "shard_grad_op", "fsdp_mixed_precision": "fp32",
+                                  "gradient_checkpointing": False, "max_grad_norm": 0.5, "unknown_key": 1})
+    assert f.config.gradient_clipping_norm == 0.5 and not f.config.activation_checkpointing
+    assert F.detect_hardware().is_err() or F.detect_hardware().unwrap().sm_count > 0
+
+
+def _chain(n=8):
+    torch.manual_seed(0)
+    return nn.Sequential(*[nn.Sequential(nn.Linear(16, 16), nn.Tanh()) for _ in range(n)])
+
+
+@pytest.mark.parametrize("sched,P,V,M,ckpt", [("gpipe", 4, 1, 4, False), ("1f1b", 4, 1, 8, True),
+                                              ("interleaved", 2, 2, 4, False), ("zero_bubble", 4, 1, 8, False),
+                                              ("chimera", 4, 1, 8, False)])
+def test_pipeline_schedules_in_one_process(sched, P, V, M, ckpt):
+    from trainscale_b200.parallel import pipeline as PL
+    x, y = torch.randn(16, 16), torch.randn(16, 16)
+    ref = _chain()
+    loss_ref = nn.functional.mse_loss(ref(x), y)
+    loss_ref.backward()
+    m = _chain()
+    cfg = PL.PipelineConfig(num_stages=P, num_virtual_stages=V, num_microbatches=M, schedule=sched,
+                            memory=PL.MemoryConfig(enable_activation_checkpointing=ckpt))
+    stages = PL.split_model_into_stages(m, P if sched == "chimera" else P * V, checkpoint_activations=ckpt)
+    pipe = PL.PipelineParallel(stages, cfg, nn.functional.mse_loss)
+    with PL.pipeline_profiler(pipe, sched) as rep:
+        loss = pipe(PL.split_into_microbatches(x, M), PL.split_into_microbatches(y, M))
+    assert abs(float(loss) - float(loss_ref)) < 1e-6
+    for a, b in zip(m.parameters(), ref.parameters()):
+        torch.testing.assert_close(a.grad, b.grad, rtol=1e-5, atol=1e-7)
+    assert rep["forwards"] == rep["backwards"] == M * len(stages) * (1 if sched != "chimera" else 1)
+    assert (rep["weight_grads"] > 0) == (sched == "zero_bubble")
+
+
+def test_chimera_order_and_balancing():
+    from trainscale_b200.parallel import pipeline as PL
+    acts = PL.chimera_schedule(4, 8)
+    for w, lst in enumerate(acts):
+        assert sum(a.op == "F" for a in lst) == 8 and sum(a.op == "B" for a in lst) == 8
+        assert {a.mb for a in lst if a.chunk == 0} == {0, 1, 2, 3} and {a.mb for a in lst if a.chunk == 1} == {4, 5, 6, 7}
+    # both ends start a forward at once: the fill bubble of a one-directional pipeline is halved
+    assert acts[0][0] == PL.Action("F", 0, 0) and acts[3][0] == PL.Action("F", 4, 1)
+    with pytest.raises(ValueError):
+        PL.chimera_schedule(3, 8)
+    layers = [nn.Linear(64, 64) for _ in range(6)] + [nn.Linear(64, 4096), nn.Linear(4096, 64)]
+    r = PL.balance_stages_by_memory(layers, 4)
+    assert sum(len(x) for x in r) == 8 and len(r) == 4
+    heavy = max(range(4), key=lambda s: sum(PL.estimate_stage_memory(layers[i])["total"] for i in r[s]))
+    assert len(r[heavy]) <= 2                      # the two large layers do not share a stage with many others
+    assert float(PL.merge_microbatches([torch.tensor(1.0), torch.tensor(3.0)])) == 2.0
+    pool = PL.TensorPool()
+    t = pool.allocate((4, 4))
+    pool.deallocate(t)
+    assert pool.allocate((4, 4)).data_ptr() == t.data_ptr() and pool.stats()["reuses"] == 1
+
+
+def test_pipeline_api_across_ranks():
+    r = launch("pipeline_api.py", 2, 29682)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    assert "RESULT ok=True" in r.stdout

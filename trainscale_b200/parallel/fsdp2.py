@@ -1,0 +1,801 @@
+"""The sharded data-parallel engine under the reference's FSDP2 names.
+
+`SOTAFSDP2` keeps the call protocol of data_pipeline/trainer/distributed/fsdp2.py:1182-2050 (`wrap_model`,
+`forward_context`, `backward` -> "is this a sync step", `step`, `clip_grad_norm_`, `get_state_dict`,
+`summon_full_params`, `memory_summary`) and `FSDPCheckpointManager` the one of fsdp2.py:2052-2950, but what runs
+underneath is the flat-buffer engine (`flat_engine.FlatShardedEngine`): per-layer contiguous bf16 parameter / gradient
+buffers, fp32 master + moment shards, reduce-scatter fused with the gradient norm and AdamW fused with the parameter
+broadcast over NVLink peer memory.  There is no wrapper module: `wrap_model` returns the model it was given, with its
+parameters re-pointed into the flat buffers.
+"""
+from __future__ import annotations
+
+import contextlib
+import time
+from collections import deque
+from dataclasses import dataclass, field
+from enum import Enum
+from pathlib import Path
+from typing import Any, NamedTuple
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+from ..core.types import Err, Ok, Result
+from .flat_engine import EngineConfig, FlatShardedEngine
+
+
+# ------------------------------------------------------------------------------------------------ hardware
+class ComputeCapability(NamedTuple):
+    major: int
+    minor: int
+
+    @property
+    def sm_version(self) -> int:
+        return self.major * 10 + self.minor
+
+    @property
+    def supports_bf16(self) -> bool:
+        return self.major >= 8
+
+    @property
+    def supports_fp8(self) -> bool:
+        return self.sm_version >= 89
+
+    @property
+    def supports_tma(self) -> bool:
+        return self.major >= 9
+
+    @property
+    def supports_tcgen05(self) -> bool:
+        return self.major == 10
+
+
+@dataclass(frozen=True)
+class HardwareInfo:
+    name: str
+    capability: ComputeCapability
+    total_memory: int
+    sm_count: int
+    device_id: int = 0
+
+    @property
+    def memory_gb(self) -> float:
+        return self.total_memory / 2 ** 30
+
+    @property
+    def is_datacenter_gpu(self) -> bool:
+        return any(t in self.name.upper() for t in ("B200", "B100", "GB200", "H100", "H200", "A100"))
+
+    @property
+    def is_blackwell(self) -> bool:
+        return self.capability.major == 10
+
+
+def detect_hardware(device_id: int = 0) -> Result:
+    """Properties of one GPU (read only). Err when there is no CUDA device."""
+    if not torch.cuda.is_available():
+        return Err(RuntimeError("no CUDA device"))
+    try:
+        p = torch.cuda.get_device_properties(device_id)
+        return Ok(HardwareInfo(p.name, ComputeCapability(p.major, p.minor), p.total_memory, p.multi_processor_count,
+                               device_id))
+    except (RuntimeError, AssertionError) as e:
+        return Err(e)
+
+
+# ------------------------------------------------------------------------------------------------ policy enums
+class ShardingStrategy(Enum):
+    FULL_SHARD = "full_shard"            # ZeRO-3: parameters, gradients and optimizer state sharded
+    SHARD_GRAD_OP = "shard_grad_op"      # ZeRO-2: parameters stay whole between steps
+    NO_SHARD = "no_shard"                # DDP on the flat buffers
+    HYBRID_SHARD = "hybrid_shard"        # shard inside a group, replicate across groups
+
+    @property
+    def requires_all_gather(self) -> bool:
+        return self is not ShardingStrategy.NO_SHARD
+
+    @property
+    def requires_reduce_scatter(self) -> bool:
+        return self is not ShardingStrategy.NO_SHARD
+
+    @property
+    def engine_name(self) -> str:
+        return "FULL_SHARD" if self is ShardingStrategy.HYBRID_SHARD else self.name
+
+
+class MixedPrecisionPolicy(Enum):
+    FULL_BF16 = "bf16"          # bf16 parameters, gradients reduced in bf16 (fp32 when accumulating), fp32 masters
+    FULL_FP16 = "fp16"
+    PARAM_FP32 = "fp32"
+    PURE_BF16 = "pure_bf16"
+
+    def get_param_dtype(self) -> torch.dtype:
+        return {"bf16": torch.bfloat16, "pure_bf16": torch.bfloat16, "fp16": torch.float16,
+                "fp32": torch.float32}[self.value]
+
+    def get_reduce_dtype(self) -> torch.dtype:
+        return torch.float32 if self is MixedPrecisionPolicy.PARAM_FP32 else self.get_param_dtype()
+
+    @property
+    def requires_loss_scaling(self) -> bool:
+        return self is MixedPrecisionPolicy.FULL_FP16
+
+
+class OffloadStrategy(Enum):
+    NONE = "none"
+    CPU_OPTIMIZER = "cpu_optimizer"
+    CPU_FULL = "cpu_full"
+
+    @property
+    def requires_pinned_memory(self) -> bool:
+        return self is not OffloadStrategy.NONE
+
+
+class BackwardPrefetchMode(Enum):
+    BACKWARD_PRE = "backward_pre"
+    BACKWARD_POST = "backward_post"
+    NONE = "none"
+
+
+# ------------------------------------------------------------------------------------------------ pools / streams
+class MemoryPool:
+    """Recycles device buffers by power-of-two size class so that the per-layer gather / reduce buffers of a step
+    never go back to the caching allocator (fsdp2.py:463-586 keeps the same interface)."""
+
+    def __init__(self, device: torch.device | str = "cpu", max_cached_bytes: int = 8 * 2 ** 30):
+        self.device = torch.device(device)
+        self.max_cached_bytes = max_cached_bytes
+        self._free: dict[tuple[int, torch.dtype], list[torch.Tensor]] = {}
+        self._out: dict[int, tuple[int, torch.dtype]] = {}
+        self.hits = self.misses = 0
+        self.cached_bytes = 0
+
+    @staticmethod
+    def _bucket_size(numel: int) -> int:
+        return 1 << max(9, (max(1, numel) - 1).bit_length())
+
+    def allocate(self, numel: int, dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+        key = (self._bucket_size(numel), dtype)
+        lst = self._free.get(key)
+        if lst:
+            buf = lst.pop()
+            self.cached_bytes -= buf.numel() * buf.element_size()
+            self.hits += 1
+        else:
+            buf = torch.empty(key[0], dtype=dtype, device=self.device)
+            self.misses += 1
+        view = buf[:numel]
+        self._out[view.data_ptr()] = key
+        return view
+
+    def release(self, tensor: torch.Tensor) -> None:
+        key = self._out.pop(tensor.data_ptr(), None)
+        if key is None:
+            return
+        nbytes = key[0] * tensor.element_size()
+        if self.cached_bytes + nbytes > self.max_cached_bytes:
+            return                                   # over budget: let the allocator have it back
+        base = tensor.new_empty(0).set_(tensor.untyped_storage(), tensor.storage_offset(), (key[0],))
+        self._free.setdefault(key, []).append(base)
+        self.cached_bytes += nbytes
+
+    def clear(self) -> None:
+        self._free.clear()
+        self.cached_bytes = 0
+
+    def get_stats(self) -> dict[str, Any]:
+        tot = self.hits + self.misses
+        return {"hits": self.hits, "misses": self.misses, "hit_rate": self.hits / tot if tot else 0.0,
+                "cached_bytes": self.cached_bytes, "outstanding": len(self._out)}
+
+
+class StreamManager:
+    """Named side streams (all-gather, reduce-scatter, host transfer) next to the compute stream, with the event
+    hand-offs between them.  On a CPU device every accessor returns None and the syncs are no-ops."""
+
+    def __init__(self, device: torch.device | str):
+        self.device = torch.device(device)
+        self._cuda = self.device.type == "cuda"
+        mk = (lambda: torch.cuda.Stream(self.device)) if self._cuda else (lambda: None)
+        self._allgather, self._reduce_scatter, self._transfer = mk(), mk(), mk()
+
+    @property
+    def compute(self):
+        return torch.cuda.current_stream(self.device) if self._cuda else None
+
+    @property
+    def allgather(self):
+        return self._allgather
+
+    @property
+    def reduce_scatter(self):
+        return self._reduce_scatter
+
+    @property
+    def transfer(self):
+        return self._transfer
+
+    def sync_stream_to(self, waiter, producer) -> None:
+        if self._cuda and waiter is not None and producer is not None:
+            ev = torch.cuda.Event()
+            ev.record(producer)
+            waiter.wait_event(ev)
+
+    def sync_allgather_to_compute(self) -> None:
+        self.sync_stream_to(self.compute, self._allgather)
+
+    def sync_compute_to_reduce_scatter(self) -> None:
+        self.sync_stream_to(self._reduce_scatter, self.compute)
+
+    def synchronize_all(self) -> None:
+        if self._cuda:
+            for s in (self._allgather, self._reduce_scatter, self._transfer):
+                s.synchronize()
+            torch.cuda.current_stream(self.device).synchronize()
+
+
+# ------------------------------------------------------------------------------------------------ config
+@dataclass
+class FSDP2Config:
+    """Field names of fsdp2.py:746-843.  Fields that steer torch FSDP internals there (`use_orig_params`,
+    `limit_all_gathers`, `sync_module_states`, wrap policy lists) are accepted and recorded; the flat engine has one
+    unit per decoder layer and always keeps original parameter objects."""
+    sharding_strategy: ShardingStrategy = ShardingStrategy.FULL_SHARD
+    mixed_precision: MixedPrecisionPolicy = MixedPrecisionPolicy.FULL_BF16
+    offload_strategy: OffloadStrategy = OffloadStrategy.NONE
+    use_orig_params: bool = True
+    forward_prefetch: bool = True
+    backward_prefetch: BackwardPrefetchMode = BackwardPrefetchMode.BACKWARD_PRE
+    reshard_after_forward: bool = True
+    limit_all_gathers: bool = True
+    use_triton_kernels: bool = False         # no Triton here: the CUDA kernels are always on
+    use_memory_pool: bool = True
+    bucket_size_mb: int = 25
+    sync_module_states: bool = True
+    auto_wrap_policy: list[str] | None = None
+    ignored_modules: list[str] | None = None
+    min_num_params: int = 100_000_000
+    activation_checkpointing: bool = True
+    ac_mode: str = "selective"               # full | selective | op_selective | offload
+    ac_frequency: int = 2
+    ac_offload_to_cpu: bool = False
+    gradient_accumulation_steps: int = 1
+    gradient_clipping_norm: float | None = 1.0
+    use_cuda_graphs: bool = False
+    cuda_graph_warmup_iters: int = 3
+    deterministic: bool = False
+    debug_mode: bool = False
+    # optimizer owned by the engine (fused with the parameter broadcast)
+    learning_rate: float = 2e-5
+    betas: tuple[float, float] = (0.9, 0.999)
+    eps: float = 1e-8
+    weight_decay: float = 0.01
+    comm: str = "auto"                       # auto | fused | nccl
+
+    def __post_init__(self) -> None:
+        if isinstance(self.sharding_strategy, str):
+            self.sharding_strategy = ShardingStrategy(self.sharding_strategy.lower())
+        if isinstance(self.mixed_precision, str):
+            self.mixed_precision = MixedPrecisionPolicy(self.mixed_precision.lower())
+        if isinstance(self.offload_strategy, str):
+            self.offload_strategy = OffloadStrategy(self.offload_strategy.lower())
+        if isinstance(self.backward_prefetch, str):
+            self.backward_prefetch = BackwardPrefetchMode(self.backward_prefetch.lower())
+        if self.auto_wrap_policy is None:
+            self.auto_wrap_policy = ["LlamaDecoderLayer"]
+        if self.ignored_modules is None:
+            self.ignored_modules = []
+        self._validate()
+
+    def _validate(self) -> None:
+        if self.gradient_accumulation_steps < 1:
+            raise ValueError("gradient_accumulation_steps must be >= 1")
+        if self.bucket_size_mb < 1:
+            raise ValueError("bucket_size_mb must be >= 1")
+        if self.gradient_clipping_norm is not None and self.gradient_clipping_norm <= 0:
+            raise ValueError("gradient_clipping_norm must be positive (or None)")
+        if self.ac_mode not in ("full", "selective", "op_selective", "offload", "none"):
+            raise ValueError(f"unknown ac_mode {self.ac_mode!r}")
+        if self.mixed_precision is MixedPrecisionPolicy.FULL_FP16:
+            raise ValueError("fp16 parameters are not supported by the sm_100a kernels; use bf16")
+
+    @property
+    def bucket_size_bytes(self) -> int:
+        return self.bucket_size_mb * 2 ** 20
+
+    def to_engine_config(self) -> EngineConfig:
+        return EngineConfig(sharding_strategy=self.sharding_strategy.engine_name,
+                            param_dtype=self.mixed_precision.get_param_dtype(),
+                            gradient_accumulation_steps=self.gradient_accumulation_steps,
+                            max_grad_norm=self.gradient_clipping_norm or 0.0, lr=self.learning_rate,
+                            betas=tuple(self.betas), eps=self.eps, weight_decay=self.weight_decay, comm=self.comm)
+
+
+# ------------------------------------------------------------------------------------------------ metrics
+@dataclass
+class FSDPMetrics:
+    forward_ms: float = 0.0
+    backward_ms: float = 0.0
+    optimizer_ms: float = 0.0
+    allgather_ms: float = 0.0
+    reduce_scatter_ms: float = 0.0
+    peak_memory_gb: float = 0.0
+    allocated_memory_gb: float = 0.0
+    gradient_norm: float = 0.0
+    step: int = 0
+
+    def reset(self) -> None:
+        for k in ("forward_ms", "backward_ms", "optimizer_ms", "allgather_ms", "reduce_scatter_ms"):
+            setattr(self, k, 0.0)
+
+    def to_dict(self) -> dict[str, float]:
+        return dict(self.__dict__)
+
+
+class MetricsCollector:
+    """Phase timers that never block the host: on CUDA a phase records an event pair and the elapsed time is read
+    at the NEXT `record_step` (after the events have certainly completed); on CPU a wall clock is used."""
+
+    def __init__(self, device: torch.device | str = "cpu", history: int = 1000, enabled: bool = True):
+        self.device = torch.device(device)
+        self.enabled = enabled
+        self._cur = FSDPMetrics()
+        self._hist: deque[dict] = deque(maxlen=history)
+        self._pending: list[tuple[str, Any, Any]] = []
+        self._last_norm = 0.0
+
+    @property
+    def current(self) -> FSDPMetrics:
+        return self._cur
+
+    def _flush_pending_events(self) -> None:
+        keep = []
+        for name, a, b in self._pending:
+            if b.query():
+                setattr(self._cur, name, getattr(self._cur, name) + a.elapsed_time(b))
+            else:
+                keep.append((name, a, b))
+        self._pending = keep
+
+    @contextlib.contextmanager
+    def _measure(self, name: str):
+        if not self.enabled:
+            yield
+            return
+        if self.device.type == "cuda":
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            try:
+                yield
+            finally:
+                b.record()
+                self._pending.append((name, a, b))
+        else:
+            t0 = time.perf_counter()
+            try:
+                yield
+            finally:
+                setattr(self._cur, name, getattr(self._cur, name) + (time.perf_counter() - t0) * 1e3)
+
+    def measure_allgather(self):
+        return self._measure("allgather_ms")
+
+    def measure_reduce_scatter(self):
+        return self._measure("reduce_scatter_ms")
+
+    def measure_forward(self):
+        return self._measure("forward_ms")
+
+    def measure_backward(self):
+        return self._measure("backward_ms")
+
+    def measure_optimizer(self):
+        return self._measure("optimizer_ms")
+
+    def update_memory_stats(self) -> None:
+        if self.device.type == "cuda":
+            self._cur.peak_memory_gb = torch.cuda.max_memory_allocated(self.device) / 2 ** 30
+            self._cur.allocated_memory_gb = torch.cuda.memory_allocated(self.device) / 2 ** 30
+
+    def set_gradient_norm(self, norm: float) -> None:
+        self._last_norm = self._cur.gradient_norm = float(norm)
+
+    def record_step(self) -> None:
+        self._flush_pending_events()
+        self._cur.step += 1
+        self._hist.append(self._cur.to_dict())
+        self._cur.reset()
+
+    def get_average(self, last_n: int = 100) -> dict[str, float]:
+        rows = list(self._hist)[-last_n:]
+        if not rows:
+            return {}
+        return {k: sum(r[k] for r in rows) / len(rows) for k in rows[0] if k != "step"}
+
+    def get_last_gradient_norm(self) -> float:
+        return self._last_norm
+
+
+class GradientAccumulator:
+    """fp32 side buffers that sum micro-batch gradients of a plain model (the engine accumulates in its own flat
+    buffers; this class serves models trained without it)."""
+
+    def __init__(self, accumulation_steps: int = 1, dtype: torch.dtype = torch.float32):
+        self.accumulation_steps = max(1, accumulation_steps)
+        self.dtype = dtype
+        self._step = 0
+        self._bufs: dict[nn.Parameter, torch.Tensor] = {}
+
+    @property
+    def should_sync(self) -> bool:
+        return self._step >= self.accumulation_steps
+
+    @property
+    def current_step(self) -> int:
+        return self._step
+
+    @torch.no_grad()
+    def accumulate(self, model: nn.Module) -> None:
+        for p in model.parameters():
+            if p.grad is None:
+                continue
+            b = self._bufs.get(p)
+            if b is None:
+                self._bufs[p] = p.grad.detach().to(self.dtype).clone()
+            else:
+                b.add_(p.grad.to(self.dtype))
+            p.grad = None
+        self._step += 1
+
+    @torch.no_grad()
+    def apply_to_model(self, model: nn.Module) -> None:
+        inv = 1.0 / max(1, self._step)
+        for p in model.parameters():
+            b = self._bufs.get(p)
+            if b is not None:
+                p.grad = (b * inv).to(p.dtype)
+
+    def reset(self) -> None:
+        self._step = 0
+        for b in self._bufs.values():
+            b.zero_()
+
+
+class MixedPrecisionContext:
+    """Autocast + (fp16 only) loss scaling around a step.  The framework models compute in their parameter dtype,
+    so for bf16 / fp32 policies this is a transparent context."""
+
+    def __init__(self, policy: MixedPrecisionPolicy, device_type: str = "cuda"):
+        self.policy, self.device_type = policy, device_type
+        self._scaler = torch.amp.GradScaler(device_type) if policy.requires_loss_scaling else None
+
+    @property
+    def enabled(self) -> bool:
+        return self.policy is not MixedPrecisionPolicy.PARAM_FP32
+
+    @property
+    def scaler(self):
+        return self._scaler
+
+    def autocast(self):
+        if not self.enabled or self.policy is MixedPrecisionPolicy.PURE_BF16:
+            return contextlib.nullcontext()
+        return torch.autocast(self.device_type, dtype=self.policy.get_param_dtype())
+
+    def scale_loss(self, loss: torch.Tensor) -> torch.Tensor:
+        return self._scaler.scale(loss) if self._scaler is not None else loss
+
+    def unscale_grads(self, optimizer) -> None:
+        if self._scaler is not None:
+            self._scaler.unscale_(optimizer)
+
+    def step_optimizer(self, optimizer) -> None:
+        if self._scaler is not None:
+            self._scaler.step(optimizer)
+            self._scaler.update()
+        else:
+            optimizer.step()
+
+
+# ------------------------------------------------------------------------------------------------ engine facade
+class SOTAFSDP2:
+    """Sharded data parallelism with the reference's call protocol:
+
+        fsdp = SOTAFSDP2(FSDP2Config(...));  model = fsdp.wrap_model(model)
+        with fsdp.forward_context():  loss = model(ids, labels=ids).loss / accumulation_steps
+        if fsdp.backward(loss):  fsdp.step()
+
+    The optimizer lives inside the engine (AdamW on fp32 shards, fused with the parameter broadcast); `step` accepts
+    the reference's `(optimizer, scheduler)` arguments and uses only the scheduler / the learning rate they carry."""
+
+    def __init__(self, config: FSDP2Config | None = None, device_mesh: Any = None, process_group=None,
+                 device: torch.device | str | None = None):
+        self._config = config or FSDP2Config()
+        self._device_mesh = device_mesh
+        self._pg = process_group
+        self._wrapped_model: nn.Module | None = None
+        self.engine: FlatShardedEngine | None = None
+        self._init_distributed_info()
+        if device is None:
+            device = torch.device("cuda", self._local_rank) if torch.cuda.is_available() else torch.device("cpu")
+        self._device = torch.device(device)
+        if self._device.type == "cuda":
+            torch.cuda.set_device(self._device)
+        hw = detect_hardware(self._device.index or 0) if self._device.type == "cuda" else Err(RuntimeError("cpu"))
+        self._hardware_info = hw.unwrap() if hw.is_ok() else None
+        self._metrics = MetricsCollector(self._device)
+        self._mp_context = MixedPrecisionContext(self._config.mixed_precision, self._device.type)
+        self._memory_pool = MemoryPool(self._device) if self._config.use_memory_pool else None
+        self._streams = StreamManager(self._device)
+        self._last_norm: torch.Tensor | None = None
+
+    def _init_distributed_info(self) -> None:
+        import os
+        on = dist.is_available() and dist.is_initialized()
+        self._rank = dist.get_rank() if on else 0
+        self._world_size = dist.get_world_size(self._pg) if on else 1
+        self._local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    config = property(lambda self: self._config)
+    metrics = property(lambda self: self._metrics)
+    rank = property(lambda self: self._rank)
+    world_size = property(lambda self: self._world_size)
+    is_rank_zero = property(lambda self: self._rank == 0)
+    model = property(lambda self: self._wrapped_model)
+    device = property(lambda self: self._device)
+    hardware_info = property(lambda self: self._hardware_info)
+    param_groups = property(lambda self: self.engine.param_groups if self.engine is not None else [])
+
+    # ---------------------------------------------------------------- wrap
+    def _apply_activation_checkpointing(self, model: nn.Module) -> None:
+        c = self._config
+        if not c.activation_checkpointing or c.ac_mode == "none":
+            return
+        if c.ac_mode == "op_selective" and hasattr(model, "op_selective_recompute"):
+            model.op_selective_recompute()
+            return
+        from .activation import ActivationCheckpoint, ActivationCheckpointConfig, CheckpointMode
+        mode = {"full": CheckpointMode.FULL, "selective": CheckpointMode.SELECTIVE,
+                "offload": CheckpointMode.OFFLOAD}[c.ac_mode]
+        ActivationCheckpoint(ActivationCheckpointConfig(mode=mode, selective_frequency=c.ac_frequency)).apply(model)
+
+    def wrap_model(self, model: nn.Module, device_mesh: Any = None) -> nn.Module:
+        """Move the model to this rank's device, apply activation recomputation, then build the flat buffers and the
+        optimizer shards.  Returns the same module object."""
+        c = self._config
+        if next(model.parameters()).device != self._device:
+            model.to(self._device)
+        want = c.mixed_precision.get_param_dtype()
+        if next(model.parameters()).dtype != want:
+            model.to(want)
+        self._apply_activation_checkpointing(model)
+        shard_pg, replicate_pg = self._pg, None
+        mesh = device_mesh or self._device_mesh
+        if c.sharding_strategy is ShardingStrategy.HYBRID_SHARD and mesh is not None:
+            # a 2-D mesh (replicate, shard), torch DeviceMesh or anything with get_group(name)
+            shard_pg, replicate_pg = mesh.get_group("shard"), mesh.get_group("replicate")
+        self.engine = FlatShardedEngine(model, c.to_engine_config(), process_group=shard_pg, device=self._device,
+                                        replicate_group=replicate_pg)
+        self._wrapped_model = model
+        return model
+
+    # ---------------------------------------------------------------- step protocol
+    @contextlib.contextmanager
+    def forward_context(self):
+        with self._metrics.measure_forward(), self._mp_context.autocast():
+            yield
+
+    def no_sync(self):
+        return self.engine.no_sync()
+
+    def backward(self, loss: torch.Tensor, retain_graph: bool = False) -> bool:
+        """Backward of one micro-batch; True when the accumulation boundary is reached (call `step()` then)."""
+        if retain_graph:
+            raise ValueError("retain_graph is not supported: the engine reduces gradients during this backward")
+        with self._metrics.measure_backward():
+            return self.engine.backward(self._mp_context.scale_loss(loss))
+
+    def step(self, optimizer: Any = None, scheduler: Any = None) -> torch.Tensor:
+        """Clip by the global norm, AdamW on the shards, re-gather.  Returns the gradient norm (device tensor)."""
+        lr = None
+        if optimizer is not None and getattr(optimizer, "param_groups", None):
+            lr = optimizer.param_groups[0].get("lr")
+        with self._metrics.measure_optimizer():
+            norm = self.engine.step(lr)
+        self._last_norm = norm
+        if scheduler is not None:
+            scheduler.step()
+        self._metrics.update_memory_stats()
+        self._metrics.record_step()
+        return norm
+
+    def clip_grad_norm_(self, max_norm: float | None = None, norm_type: float = 2.0) -> torch.Tensor | None:
+        """The clip happens inside `step` (the norm falls out of the fused reduce-scatter); this sets the threshold for
+        the following steps and returns the last measured norm."""
+        if norm_type != 2.0:
+            raise ValueError("only the 2-norm is supported")
+        if max_norm is not None:
+            self.engine.cfg.max_grad_norm = float(max_norm)
+        return self._last_norm
+
+    def zero_grad(self) -> None:
+        self.engine.zero_grad()
+
+    # ---------------------------------------------------------------- state
+    def get_state_dict(self, optimizer: Any = None, full_state_dict: bool = True, cpu_offload: bool = True,
+                       hf_names: bool = False) -> dict[str, Any]:
+        """{"model": full weights (every rank takes part; tensors on the host when cpu_offload),
+            "optimizer": this rank's fp32 master / moment shards}."""
+        with self.summon_full_params(writeback=False):
+            m = self._wrapped_model
+            sd = m.to_hf_state_dict() if hf_names and hasattr(m, "to_hf_state_dict") else \
+                {n: p.detach() for n, p in m.named_parameters()}
+            # always a copy: under FULL_SHARD the full buffers are released again when this block ends
+            sd = {k: (v.cpu() if cpu_offload and v.is_cuda else v.clone()) for k, v in sd.items()}
+        return {"model": sd if (full_state_dict or self._world_size == 1) else {}, "optimizer": self.engine.state_dict()}
+
+    def load_state_dict(self, state: dict[str, Any], strict: bool = True) -> None:
+        m = self._wrapped_model
+        if state.get("model"):
+            with self.summon_full_params(writeback=True):
+                own = dict(m.named_parameters())
+                missing = [k for k in own if k not in state["model"]]
+                if strict and missing:
+                    raise KeyError(f"missing parameters: {missing[:6]}")
+                with torch.no_grad():
+                    for k, v in state["model"].items():
+                        if k in own:
+                            own[k].copy_(v)
+        if state.get("optimizer"):
+            self.engine.load_state_dict(state["optimizer"])
+
+    @contextlib.contextmanager
+    def summon_full_params(self, writeback: bool = True):
+        """Full parameters on every rank inside the block.  With `writeback`, edits made inside are carried into the
+        shards and the fp32 masters on exit."""
+        with self.engine.summon_full_params():
+            yield
+            if writeback:
+                with torch.no_grad():
+                    for u in self.engine.units:
+                        src = u.flat_param[u.shard_start:u.shard_start + u.shard_numel]
+                        if getattr(u, "resharded", False):
+                            u.param_shard.copy_(src)
+                        u.master.copy_(src)
+
+    # ---------------------------------------------------------------- memory
+    def reset_peak_memory_stats(self) -> None:
+        if self._device.type == "cuda":
+            torch.cuda.reset_peak_memory_stats(self._device)
+
+    def empty_cache(self) -> None:
+        if self._memory_pool is not None:
+            self._memory_pool.clear()
+        if self._device.type == "cuda":
+            torch.cuda.empty_cache()
+
+    def memory_summary(self) -> str:
+        s = self.engine.memory_summary() if self.engine is not None else "not wrapped"
+        if self._memory_pool is not None:
+            st = self._memory_pool.get_stats()
+            s += f" | pool hit rate {st['hit_rate']:.2f}"
+        return f"[{self._config.sharding_strategy.value} x{self._world_size}] {s}"
+
+
+# ------------------------------------------------------------------------------------------------ checkpoints
+class FSDPCheckpointManager:
+    """`save_checkpoint(fsdp, optimizer, path, epoch, step, extra_state, sharded)` / `load_checkpoint(...)`.
+
+    sharded=True : `model.safetensors` written by rank 0 from the gathered weights + one optimizer shard file per rank
+                   (`optim/shard-XXXXX-of-YYYYY.pt`, re-sliceable across world sizes) + `meta.pt`.
+    sharded=False: one `checkpoint.pt` on rank 0 with the full weights and rank 0's optimizer shard.
+    Both return Result; every rank must call them (the weight gather and the barriers are collectives)."""
+
+    API_VERSION = "ts_flat_v1"
+
+    @staticmethod
+    def _barrier(fsdp: SOTAFSDP2) -> None:
+        if fsdp.world_size > 1:
+            dist.barrier(group=fsdp._pg)
+
+    @staticmethod
+    def save_checkpoint(fsdp: SOTAFSDP2, optimizer: Any, path: str | Path, epoch: int = 0, step: int = 0,
+                        extra_state: dict[str, Any] | None = None, sharded: bool = True) -> Result:
+        from ..ckpt import atomic_torch_save, _to_cpu
+        from ..hub import ModelSerializer
+        path = Path(path)
+        try:
+            FSDPCheckpointManager._barrier(fsdp)
+            state = fsdp.get_state_dict(optimizer, full_state_dict=True, cpu_offload=True, hf_names=sharded)
+            meta = {"epoch": epoch, "step": step, "api_version": FSDPCheckpointManager.API_VERSION,
+                    "config": {"sharding_strategy": fsdp.config.sharding_strategy.value,
+                               "mixed_precision": fsdp.config.mixed_precision.value, "world_size": fsdp.world_size},
+                    "extra": extra_state or {}}
+            if sharded:
+                if fsdp.is_rank_zero:
+                    path.mkdir(parents=True, exist_ok=True)
+                    ModelSerializer().save(state["model"], path)
+                    atomic_torch_save(meta, path / "meta.pt")
+                FSDPCheckpointManager._barrier(fsdp)
+                atomic_torch_save(_to_cpu(state["optimizer"]),
+                                  path / "optim" / f"shard-{fsdp.engine.rank:05d}-of-{fsdp.engine.world:05d}.pt")
+            elif fsdp.is_rank_zero:
+                path.parent.mkdir(parents=True, exist_ok=True)
+                atomic_torch_save({"model": state["model"], "optimizer": _to_cpu(state["optimizer"]), "meta": meta},
+                                  path if path.suffix else path / "checkpoint.pt")
+            FSDPCheckpointManager._barrier(fsdp)
+            return Ok(None)
+        except (OSError, RuntimeError, ValueError, KeyError) as e:
+            return Err(e)
+
+    @staticmethod
+    def load_checkpoint(fsdp: SOTAFSDP2, optimizer: Any, path: str | Path, sharded: bool = True,
+                        strict: bool = True) -> Result:
+        from ..ckpt import reshard_optimizer_state
+        from ..hub import ModelDeserializer
+        path = Path(path)
+        try:
+            if sharded:
+                sd = ModelDeserializer().load(path)
+                m = fsdp.model
+                with fsdp.summon_full_params(writeback=True):
+                    if hasattr(m, "load_hf_state_dict"):
+                        m.load_hf_state_dict(sd, strict=strict)
+                    else:
+                        m.load_state_dict(sd, strict=strict)
+                files = sorted((path / "optim").glob("shard-*.pt"))
+                eng = fsdp.engine
+                mine = path / "optim" / f"shard-{eng.rank:05d}-of-{eng.world:05d}.pt"
+                if mine.exists():
+                    eng.load_state_dict(torch.load(mine, map_location="cpu", weights_only=False))
+                elif files:
+                    shards = [torch.load(f, map_location="cpu", weights_only=False) for f in files]
+                    eng.load_state_dict(reshard_optimizer_state(shards, eng.rank, eng.world))
+                meta = torch.load(path / "meta.pt", map_location="cpu", weights_only=False) \
+                    if (path / "meta.pt").exists() else {}
+            else:
+                f = path if path.suffix else path / "checkpoint.pt"
+                blob = torch.load(f, map_location="cpu", weights_only=False)
+                fsdp.load_state_dict({"model": blob["model"], "optimizer": blob["optimizer"]
+                                      if fsdp.world_size == 1 else None}, strict=strict)
+                meta = blob.get("meta", {})
+            FSDPCheckpointManager._barrier(fsdp)
+            return Ok(meta)
+        except (OSError, RuntimeError, ValueError, KeyError) as e:
+            return Err(e)
+
+
+# ------------------------------------------------------------------------------------------------ factories
+def create_fsdp2(sharding_strategy: str = "full_shard", mixed_precision: str = "bf16",
+                 activation_checkpointing: bool = True, gradient_accumulation_steps: int = 1,
+                 gradient_clipping_norm: float | None = 1.0, **kwargs) -> SOTAFSDP2:
+    """String-configured constructor; extra keyword arguments are FSDP2Config fields or SOTAFSDP2 arguments
+    (`process_group`, `device`, `device_mesh`)."""
+    ctor = {k: kwargs.pop(k) for k in ("process_group", "device", "device_mesh") if k in kwargs}
+    cfg = FSDP2Config(sharding_strategy=sharding_strategy, mixed_precision=mixed_precision,
+                      activation_checkpointing=activation_checkpointing,
+                      gradient_accumulation_steps=gradient_accumulation_steps,
+                      gradient_clipping_norm=gradient_clipping_norm, **kwargs)
+    return SOTAFSDP2(cfg, **ctor)
+
+
+def create_fsdp2_from_dict(config_dict: dict[str, Any]) -> SOTAFSDP2:
+    """From the `distributed:` section of the training YAML (keys `fsdp_*` as in
+    data_pipeline/trainer/core/sota_config.py:299-338) or from plain FSDP2Config field names."""
+    d = dict(config_dict)
+    known = set(FSDP2Config.__dataclass_fields__)
+    out: dict[str, Any] = {}
+    alias = {"fsdp_sharding_strategy": "sharding_strategy", "fsdp_mixed_precision": "mixed_precision",
+             "fsdp_forward_prefetch": "forward_prefetch", "fsdp_backward_prefetch": "backward_prefetch",
+             "fsdp_limit_all_gathers": "limit_all_gathers", "fsdp_use_orig_params": "use_orig_params",
+             "gradient_checkpointing": "activation_checkpointing", "max_grad_norm": "gradient_clipping_norm",
+             "fsdp_bucket_size_mb": "bucket_size_mb", "fsdp_ac_mode": "ac_mode", "fsdp_ac_frequency": "ac_frequency"}
+    for k, v in d.items():
+        k = alias.get(k, k)
+        if k in known:
+            out[k] = v
+    if isinstance(out.get("backward_prefetch"), bool):
+        out["backward_prefetch"] = "backward_pre" if out["backward_prefetch"] else "none"
+    return SOTAFSDP2(FSDP2Config(**out))
