@@ -112,3 +112,62 @@ def test_pipeline_api_across_ranks():
     r = launch("pipeline_api.py", 2, 29682)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
     assert "RESULT ok=True" in r.stdout
+
+
+def test_zbpp_schedule_optimizer_and_partitioner():
+    import itertools
+    from trainscale_b200.parallel import pp as PP
+    from trainscale_b200.parallel import zbpp as Z
+    prof = [Z.StageProfile(100, 100, 100, 1 << 20, 1 << 22, 0, 0) for _ in range(4)]
+    base = PP.simulate([PP.one_f_one_b_schedule(s, 4, 8) for s in range(4)])["bubble_fraction"]
+    h1 = Z.ZBPPScheduleOptimizer(Z.ScheduleConfig(4, 8, 1 << 30, prof)).optimize()
+    h2 = Z.ZBPPScheduleOptimizer(Z.ScheduleConfig(4, 8, 1 << 30, prof, enable_interleaving=False)).optimize()
+    assert h2.bubble_fraction < h1.bubble_fraction < base
+    assert max(h1.peak_memory_bytes.values()) <= (1 << 22) + 4 * (1 << 20)         # ZB-H1: no more than 1F1B's stage 0
+    tight = Z.ZBPPScheduleOptimizer(Z.ScheduleConfig(4, 8, (1 << 22) + 2 * (1 << 20), prof)).optimize()
+    assert max(tight.peak_memory_bytes.values()) <= (1 << 22) + 2 * (1 << 20)
+    with pytest.raises(ValueError):
+        Z.ZBPPScheduleOptimizer(Z.ScheduleConfig(4, 8, 1 << 22, prof)).optimize()
+    for st, lst in h1.schedule.items():                                            # every op once, W after its B
+        for op in (Z.OpType.FORWARD, Z.OpType.BACKWARD_INPUT, Z.OpType.BACKWARD_PARAMS):
+            assert sorted(s.microbatch_id for s in lst if s.op_type == op) == list(range(8))
+        pos = {(s.op_type, s.microbatch_id): i for i, s in enumerate(lst)}
+        assert all(pos[(Z.OpType.BACKWARD_PARAMS, m)] > pos[(Z.OpType.BACKWARD_INPUT, m)] for m in range(8))
+    costs = [3, 1, 4, 1, 5, 9, 2, 6]
+    b = Z.ModelPartitioner._dp_partition(costs, 3)
+    got = max(sum(costs[b[j]:b[j + 1]]) for j in range(3))
+    brute = min(max(sum(costs[:i]), sum(costs[i:j]), sum(costs[j:])) for i, j in itertools.combinations(range(1, 8), 2))
+    assert got == brute
+
+
+def test_zbpp_pipeline_with_sync_bypass_matches_global_clip():
+    import copy
+    from trainscale_b200.optim import AdamW
+    from trainscale_b200.parallel import zbpp as Z
+    torch.manual_seed(0)
+    model = nn.Sequential(*[nn.Sequential(nn.Linear(16, 16), nn.Tanh()) for _ in range(8)])
+    ref = copy.deepcopy(model)
+    x, y = torch.randn(16, 16), torch.randn(16, 16)
+    # a threshold far below the gradient norm: every optimistic local step must be rolled back and redone
+    pipe = Z.create_zbpp_pipeline(model, 4, 8, lr=1e-2, weight_decay=0.0, max_grad_norm=0.05)
+    opt = AdamW(ref.parameters(), lr=1e-2, weight_decay=0.0)
+    for _ in range(3):
+        loss = pipe.train_step(x, y)
+        lr_ = nn.functional.mse_loss(ref(x), y)
+        lr_.backward()
+        torch.nn.utils.clip_grad_norm_(ref.parameters(), 0.05)
+        opt.step()
+        opt.zero_grad()
+        assert abs(float(loss) - float(lr_)) < 1e-5
+    assert pipe.finalize() == 4
+    assert all(o.rollbacks >= 1 for o in pipe.engine.optimizers)
+    for a, b in zip(pipe.parameters(), ref.parameters()):
+        torch.testing.assert_close(a, b, rtol=1e-4, atol=1e-5)
+    rep = Z.ZBPPBenchmark(pipe, x, y).run_all()
+    assert rep["passed"] and rep["schedule"]["bubble_fraction"] < rep["schedule"]["one_f_one_b_bubble"]
+    st = Z.PipelineStageModule(nn.Linear(4, 4))
+    inp = torch.randn(2, 4)                       # no input gradient needed: the weight work must still be parked
+    st(inp).sum().backward()
+    assert st.module.weight.grad is None and st.num_deferred == 1
+    st.execute_deferred_b_params()
+    torch.testing.assert_close(st.module.weight.grad, inp.sum(0).expand(4, 4))
