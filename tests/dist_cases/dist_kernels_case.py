@@ -1,0 +1,69 @@
+"""torchrun case (gloo, 4 ranks): the collective facade, the two-level all-reduce, the bucketed gradient hook and
+the [data, pipeline, tensor] group factory."""
+import copy
+import sys
+from pathlib import Path
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+sys.path.insert(0, str(Path(__file__).resolve().parents[2]))
+
+from trainscale_b200.parallel import dist_kernels as DK  # noqa: E402
+
+
+def main():
+    dist.init_process_group("gloo")
+    rank, world = dist.get_rank(), dist.get_world_size()
+    k = DK.get_distributed_kernels(DK.DistributedConfig(bucket_size_mb=0.001))
+    ok = True
+    t = torch.full((5,), float(rank + 1))
+    ok &= float(k.all_reduce(t.clone())[0]) == sum(range(1, world + 1))
+    a, b = torch.full((300,), float(rank)), torch.full((7,), float(rank), dtype=torch.float64)
+    k.all_reduce_fused([a, b], average=True)
+    ok &= abs(float(a[0]) - (world - 1) / 2) < 1e-6 and abs(float(b[0]) - (world - 1) / 2) < 1e-9
+    g = k.all_gather(torch.full((2, 3), float(rank)), dim=1)
+    ok &= g.shape == (2, 3 * world) and float(g[0, 3 * (world - 1)]) == world - 1
+    full = torch.arange(world * 4, dtype=torch.float32).view(world * 2, 2)
+    rs = k.reduce_scatter_tensor(None, full.clone())
+    ok &= torch.equal(rs, full[2 * rank:2 * rank + 2] * world)
+    sp = k.sequence_parallel_all_gather(torch.full((1, 2, 4), float(rank)), seq_dim=1)
+    ok &= sp.shape == (1, 2 * world, 4)
+    back = k.sequence_parallel_reduce_scatter(sp.clone(), seq_dim=1)
+    ok &= torch.equal(back, torch.full((1, 2, 4), float(rank) * world))
+    nxt, prv = (rank + 1) % world, (rank - 1) % world
+    got = k.pipeline_send_recv(torch.full((3,), float(rank)), torch.empty(3), nxt, prv)
+    ok &= float(got[0]) == prv
+    # groups: tp=2, pp=1 -> dp = world/2
+    groups = DK.create_process_groups(tensor_parallel_size=2)
+    ok &= dist.get_world_size(groups["tensor"]) == 2 and groups["pipeline"] is None
+    ok &= (world == 2 and groups["data"] is None) or dist.get_world_size(groups["data"]) == world // 2
+    # two-level all-reduce: local = tensor group, global = data group
+    h = DK.HierarchicalCommunicator(groups["tensor"], groups["data"])
+    x = torch.arange(11, dtype=torch.float32) + rank
+    want = sum(torch.arange(11, dtype=torch.float32) + r for r in range(world))
+    ok &= torch.allclose(h.hierarchical_all_reduce(x.clone()), want)
+    # gradient hook vs plain averaging
+    torch.manual_seed(0)
+    m = nn.Sequential(nn.Linear(8, 16), nn.Tanh(), nn.Linear(16, 4))
+    ref = copy.deepcopy(m)
+    hook = DK.GradientSyncHook(m.parameters(), DK.DistributedConfig(bucket_size_mb=0.0005))
+    gen = torch.Generator().manual_seed(7)
+    X = torch.randn(world * 2, 8, generator=gen)
+    m(X[2 * rank:2 * rank + 2]).pow(2).mean().backward()
+    hook.synchronize()
+    ref(X).pow(2).mean().backward()
+    ok &= all(torch.allclose(p.grad, q.grad, atol=1e-6) for p, q in zip(m.parameters(), ref.parameters()))
+    ok &= len(hook._buckets) > 1
+    hook.remove_hooks()
+    flag = torch.tensor([0.0 if ok else 1.0])
+    dist.all_reduce(flag)
+    if rank == 0:
+        print(f"RESULT ok={flag.item() == 0}")
+    dist.destroy_process_group()
+    sys.exit(0 if flag.item() == 0 else 1)
+
+
+if __name__ == "__main__":
+    main()

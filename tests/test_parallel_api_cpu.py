@@ -171,3 +171,46 @@ def test_zbpp_pipeline_with_sync_bypass_matches_global_clip():
     assert st.module.weight.grad is None and st.num_deferred == 1
     st.execute_deferred_b_params()
     torch.testing.assert_close(st.module.weight.grad, inp.sum(0).expand(4, 4))
+
+
+def test_grad_buffer_zero1_two_ranks():
+    r = launch("grad_buffer_zero1.py", 2, 29684)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    assert "RESULT ok=True" in r.stdout
+
+
+def test_dist_kernels_four_ranks():
+    r = launch("dist_kernels_case.py", 4, 29686)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    assert "RESULT ok=True" in r.stdout
+
+
+def test_gradient_compressor_and_buckets():
+    from trainscale_b200.parallel import dist_kernels as DK
+    torch.manual_seed(0)
+    g = torch.randn(64, 32)
+    c = DK.GradientCompressor(topk_ratio=0.1)
+    payload, ctx = c.compress(g, key="w")
+    out = c.decompress(payload, ctx)
+    assert int((out != 0).sum()) == int(64 * 32 * 0.1)
+    torch.testing.assert_close(out + c._error_buffers["w"], g)              # nothing is lost, only delayed
+    payload2, ctx2 = c.compress(torch.zeros_like(g), key="w")               # the residual comes back next step
+    assert float(c.decompress(payload2, ctx2).abs().sum()) > 0
+    low = torch.randn(64, 4) @ torch.randn(4, 32)
+    p = DK.GradientCompressor(use_powersgd=True, powersgd_rank=4)
+    for _ in range(3):                                                       # power iteration converges on rank 4
+        payload, ctx = p.compress(low, key="m")
+        p._error_buffers.pop("m")
+    torch.testing.assert_close(p.decompress(payload, ctx), low, rtol=1e-3, atol=1e-3)
+    assert sum(t.numel() for t in payload) < low.numel() / 4
+    cast, ctx = DK.GradientCompressor(use_bf16=True).compress(g)
+    assert cast[0].dtype is torch.bfloat16 and DK.GradientCompressor().decompress(cast, ctx).dtype is torch.float32
+    ts = [torch.zeros(100), torch.zeros(100), torch.zeros(10, dtype=torch.float64), torch.zeros(300)]
+    buckets = DK.BucketManager(bucket_size_mb=1000 / 2 ** 20).create_buckets(ts)
+    assert [len(b.tensors) for b in buckets] == [2, 1, 1]
+    k = DK.DistributedKernels()                                              # no process group: identities
+    x = torch.ones(3)
+    assert k.all_reduce(x) is x and k.all_gather(x) is x and k.reduce_scatter(x) is x
+    assert DK.get_world_info()[1] == 1 and DK.get_distributed_backend() is DK.DistributedBackend.NONE
+    z = DK.ZeroCopyTransfer("cpu")
+    assert z.host_to_device(x) is x and z.device_to_host(x) is x
