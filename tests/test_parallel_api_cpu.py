@@ -214,3 +214,9 @@ def test_gradient_compressor_and_buckets():
     assert DK.get_world_info()[1] == 1 and DK.get_distributed_backend() is DK.DistributedBackend.NONE
     z = DK.ZeroCopyTransfer("cpu")
     assert z.host_to_device(x) is x and z.device_to_host(x) is x
+
+
+def test_tensor_parallel_blocks_two_ranks():
+    r = launch("tp_blocks.py", 2, 29688)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    assert "RESULT ok=True" in r.stdout and r.stdout.count("ok=True") >= 3

@@ -368,3 +368,164 @@ def allreduce_sequence_parallel_grads(model, tp: TPContext) -> None:
         for g in grads:
             g.copy_(flat[off:off + g.numel()].view_as(g))
             off += g.numel()
+
+
+# ------------------------------------------------------------------------------------------------ generic building blocks
+class ProcessGroupManager:
+    """Process groups of a [data, pipeline, tensor] layout (tensor ranks adjacent, so that they share a node's
+    NVLink); sequence parallelism uses the tensor group.  One instance per process
+    (data_pipeline/trainer/distributed/tensor_parallel.py:133-480 keeps the same registry)."""
+
+    _instance: "ProcessGroupManager | None" = None
+
+    def __init__(self):
+        self.tp_size = self.pp_size = self.dp_size = 1
+        self.tp_group = self.pp_group = self.dp_group = None
+        self.tp_rank = self.pp_rank = self.dp_rank = 0
+        self.initialized = False
+
+    @classmethod
+    def get(cls) -> "ProcessGroupManager":
+        if cls._instance is None:
+            cls._instance = cls()
+        return cls._instance
+
+    def initialize(self, tensor_parallel_size: int = 1, pipeline_parallel_size: int = 1) -> "ProcessGroupManager":
+        """Collective over the whole job."""
+        from .dist_kernels import create_process_groups
+        self.tp_size, self.pp_size = tensor_parallel_size, pipeline_parallel_size
+        if dist.is_available() and dist.is_initialized():
+            world, rank = dist.get_world_size(), dist.get_rank()
+            g = create_process_groups(tensor_parallel_size, pipeline_parallel_size)
+            self.tp_group, self.pp_group, self.dp_group = g["tensor"], g["pipeline"], g["data"]
+            self.dp_size = world // (tensor_parallel_size * pipeline_parallel_size)
+            self.tp_rank = rank % tensor_parallel_size
+            self.pp_rank = (rank // tensor_parallel_size) % pipeline_parallel_size
+            self.dp_rank = rank // (tensor_parallel_size * pipeline_parallel_size)
+        elif tensor_parallel_size * pipeline_parallel_size != 1:
+            raise RuntimeError("model parallelism needs an initialised process group")
+        self.initialized = True
+        return self
+
+    @property
+    def sp_group(self):
+        return self.tp_group
+
+    def tp_context(self, sequence_parallel: bool = False, comm: str = "nccl", heap=None) -> TPContext:
+        if self.tp_group is None:
+            return TPContext(None, 1, 0, sequence_parallel, comm, heap)
+        return TPContext.from_group(self.tp_group, sequence_parallel, comm, heap)
+
+    def destroy(self) -> None:
+        type(self)._instance = None
+
+
+class ParallelEmbedding(nn.Module):
+    """Embedding table split along the HIDDEN dimension: every rank looks up all tokens in its slice of columns and the
+    slices are all-gathered (no masking needed, unlike the vocabulary split)."""
+
+    def __init__(self, num_embeddings: int, embedding_dim: int, tp: TPContext, gather_output: bool = True,
+                 dtype=None, device=None):
+        super().__init__()
+        assert embedding_dim % tp.size == 0, "embedding_dim must divide by the TP size"
+        self.tp, self.gather_output = tp, gather_output
+        self.num_embeddings, self.embedding_dim = num_embeddings, embedding_dim
+        self.weight = nn.Parameter(torch.empty(num_embeddings, embedding_dim // tp.size, dtype=dtype, device=device))
+        nn.init.normal_(self.weight, std=0.02)
+
+    def forward(self, ids):
+        out = F.embedding(ids, self.weight)
+        return gather_from_tensor_parallel_region(out, self.tp) if self.gather_output else out
+
+
+class SequenceParallelLayerNorm(nn.Module):
+    """RMSNorm / LayerNorm applied to this rank's tokens under sequence parallelism.  The weights are replicated but
+    each rank sees only 1/tp of the tokens, so their gradients must be summed over the group: the parameters carry
+    `sequence_parallel = True` and `allreduce_sequence_parallel_grads` picks them up."""
+
+    def __init__(self, hidden_size: int, eps: float = 1e-5, rms: bool = True, bias: bool = False, dtype=None,
+                 device=None):
+        super().__init__()
+        self.eps, self.rms = eps, rms
+        self.weight = nn.Parameter(torch.ones(hidden_size, dtype=dtype, device=device))
+        self.bias = nn.Parameter(torch.zeros(hidden_size, dtype=dtype, device=device)) if (bias and not rms) else None
+        for p in self.parameters():
+            p.sequence_parallel = True
+
+    def forward(self, x):
+        from ..ops import norm as N
+        if self.rms:
+            return N.rmsnorm(x, self.weight, self.eps)[0]
+        return N.layernorm(x, self.weight, self.bias, self.eps)
+
+
+class ParallelMLP(nn.Module):
+    """Column-parallel up (gate|up for gated activations) -> activation -> row-parallel down: one collective per
+    direction (all-reduce, or all-gather + reduce-scatter of tokens with sequence parallelism)."""
+
+    def __init__(self, hidden_size: int, intermediate_size: int, tp: TPContext, gated: bool = True,
+                 activation: str = "silu", bias: bool = False, dtype=None, device=None):
+        super().__init__()
+        self.tp, self.gated, self.activation = tp, gated, activation
+        self.up = ColumnParallelLinear(hidden_size, intermediate_size, tp, bias, dtype=dtype, device=device)
+        self.gate = ColumnParallelLinear(hidden_size, intermediate_size, tp, bias, dtype=dtype, device=device) \
+            if gated else None
+        self.down = RowParallelLinear(intermediate_size, hidden_size, tp, bias, dtype=dtype, device=device)
+
+    def _act(self, x):
+        return {"silu": F.silu, "gelu": F.gelu, "relu": F.relu}[self.activation](x)
+
+    def forward(self, x):
+        h = self._act(self.gate(x)) * self.up(x) if self.gated else self._act(self.up(x))
+        return self.down(h)
+
+
+class ParallelSelfAttention(nn.Module):
+    """Heads split over the tensor group: column-parallel q / k / v (grouped-query: kv heads split too), local causal
+    attention over this rank's heads, row-parallel output projection."""
+
+    def __init__(self, hidden_size: int, num_heads: int, tp: TPContext, num_kv_heads: int | None = None,
+                 head_dim: int | None = None, causal: bool = True, rope_theta: float | None = 10000.0, bias: bool = False,
+                 dtype=None, device=None):
+        super().__init__()
+        kv = num_kv_heads or num_heads
+        assert num_heads % tp.size == 0 and kv % tp.size == 0, "heads must divide by the TP size"
+        self.tp, self.causal = tp, causal
+        self.head_dim = head_dim or hidden_size // num_heads
+        self.h_loc, self.kv_loc = num_heads // tp.size, kv // tp.size
+        self.rope_theta = rope_theta
+        D = self.head_dim
+        self.q_proj = ColumnParallelLinear(hidden_size, num_heads * D, tp, bias, dtype=dtype, device=device)
+        self.k_proj = ColumnParallelLinear(hidden_size, kv * D, tp, bias, dtype=dtype, device=device)
+        self.v_proj = ColumnParallelLinear(hidden_size, kv * D, tp, bias, dtype=dtype, device=device)
+        self.o_proj = RowParallelLinear(num_heads * D, hidden_size, tp, bias, dtype=dtype, device=device)
+
+    def _rope(self, x, S):
+        D = self.head_dim
+        inv = 1.0 / (self.rope_theta ** (torch.arange(0, D, 2, device=x.device, dtype=torch.float32) / D))
+        ang = torch.arange(S, device=x.device, dtype=torch.float32)[:, None] * inv[None]
+        cos, sin = ang.cos()[None, :, None, :], ang.sin()[None, :, None, :]
+        x1, x2 = x.float()[..., : D // 2], x.float()[..., D // 2:]
+        return torch.cat((x1 * cos - x2 * sin, x2 * cos + x1 * sin), -1).to(x.dtype)
+
+    def forward(self, x):
+        """x: [B, S, H] (with sequence parallelism [B, S/tp, H]; B must be 1 there, tokens are the sharded axis)."""
+        tp = self.tp
+        sp = tp.active and tp.sequence_parallel
+        B = x.shape[0]
+        if sp:
+            assert B == 1, "sequence parallelism shards the tokens of one sequence"
+            x = x.reshape(-1, x.shape[-1])
+        q, k, v = self.q_proj(x), self.k_proj(x), self.v_proj(x)
+        S = q.shape[0] if sp else q.shape[1]
+        q = q.view(B, S, self.h_loc, self.head_dim)
+        k = k.view(B, S, self.kv_loc, self.head_dim)
+        v = v.view(B, S, self.kv_loc, self.head_dim)
+        if self.rope_theta:
+            q, k = self._rope(q, S), self._rope(k, S)
+        from ..ops import attention as A
+        qkv = torch.cat((q.reshape(B, S, -1), k.reshape(B, S, -1), v.reshape(B, S, -1)), dim=-1)
+        o = A.attention_qkv(qkv, self.h_loc, self.kv_loc, self.head_dim, causal=self.causal)
+        o = o.reshape(B, S, self.h_loc * self.head_dim)
+        y = self.o_proj(o.reshape(-1, o.shape[-1]) if sp else o)
+        return y.view(B, -1, y.shape[-1]) if sp else y
