@@ -220,3 +220,39 @@ def test_tensor_parallel_blocks_two_ranks():
     r = launch("tp_blocks.py", 2, 29688)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
     assert "RESULT ok=True" in r.stdout and r.stdout.count("ok=True") >= 3
+
+
+def test_context_parallel_engine_two_ranks():
+    r = launch("cp_engine.py", 2, 29690)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    assert "RESULT ok=True" in r.stdout
+
+
+def test_context_parallel_helpers():
+    from trainscale_b200.parallel import cp as CP
+    a = CP.TensorArena(4096)
+    t = a.allocate((10, 10), torch.float32)
+    assert t.is_ok() and t.unwrap().shape == (10, 10) and a.allocate((1000,), torch.float32).is_err()
+    a.reset()
+    assert a.available_bytes == 4096
+    pool = CP.RingBufferPool(2, (4,), torch.float32)
+    _, i = pool.get_compute_buffer()
+    _, j = pool.get_recv_buffer()
+    with pytest.raises(RuntimeError):
+        pool.get_compute_buffer()
+    pool.mark_free(i)
+    assert pool.get_compute_buffer()[1] == i and j != i
+    s = CP.BalancedCPScheduler(CP.HybridCPConfig(8192, 8))
+    L = [30000, 9000, 4000, 4000, 2000, 1000, 500, 500, 400]
+    plan = s.balanced_schedule(L)
+    assert all(plan[g] for g in range(8))                                     # nobody idles
+    assert sorted({i for g in plan for i, _ in g}) == list(range(len(L)))
+    assert [cp for i, cp in plan[0] if i == 0] == [4] and s.get_total_workload(30000) == 30000 ** 2 / 4
+    grp, nxt = s.next_hdp_group(L)
+    assert sum(cp for _, cp in grp) <= 8 and nxt == len(grp)
+    assert CP.create_context_parallel_engine(2).is_err() and CP.create_context_parallel_engine(1, "bogus").is_err()
+    assert CP.ContextParallelConfig.from_dict({"cp_degree": 1, "load_balancer": "zigzag", "junk": 1}).is_ok()
+    seen = []
+    CP.hybrid_context_parallel_forward_backward(lambda b, cp, slot: seen.append((b["input_ids"].shape[1], cp, slot)),
+                                                [{"input_ids": torch.zeros(1, n)} for n in L], s, rank=1)
+    assert seen[0] == (30000, 4, 1)

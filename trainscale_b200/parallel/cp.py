@@ -20,8 +20,11 @@ from __future__ import annotations
 import math
 from dataclasses import dataclass
 
+from enum import IntEnum
+
 import torch
 import torch.distributed as dist
+import torch.nn as nn
 
 from ..ops.attention import attention_reference
 
@@ -353,3 +356,387 @@ class BalancedCPScheduler:
                 load[g] = best_load + w
                 plan[g].append((i, cp))
         return plan
+
+    # -- the reference scheduler's finer-grained steps (hybrid_cp_scheduler.py:149-621), on the same cost model
+    def get_total_workload(self, length: int, cp: int | None = None) -> float:
+        """Attention work one GPU does for a sequence of `length` split over `cp` GPUs: L^2 / cp."""
+        return self.workload(length, cp or self.gpus_needed(length))
+
+    def make_buckets_equal(self, lengths: list[int], num_buckets: int) -> list[list[int]]:
+        """Longest-processing-time split of sequence indices into `num_buckets` buckets of near-equal total work."""
+        buckets: list[list[int]] = [[] for _ in range(num_buckets)]
+        load = [0.0] * num_buckets
+        for i in sorted(range(len(lengths)), key=lambda k: -self.get_total_workload(lengths[k])):
+            b = min(range(num_buckets), key=load.__getitem__)
+            buckets[b].append(i)
+            load[b] += self.get_total_workload(lengths[i])
+        return buckets
+
+    def next_hdp_group(self, lengths: list[int], start: int = 0) -> tuple[list[tuple[int, int]], int]:
+        """Takes sequences from `start` on until their GPU demand fills the world: returns [(index, cp)], next start."""
+        used, out, i = 0, [], start
+        while i < len(lengths):
+            cp = self.gpus_needed(lengths[i])
+            if used + cp > self.cfg.world_size:
+                break
+            out.append((i, cp))
+            used += cp
+            i += 1
+        if not out and i < len(lengths):          # a single sequence that wants the whole world
+            out.append((i, self.cfg.world_size))
+            i += 1
+        return out, i
+
+    def _trim_overloaded(self, plan: list[list[tuple[int, int]]], lengths: list[int], tolerance: float = 1.25):
+        """Moves single-GPU sequences off GPUs whose load exceeds tolerance x mean onto the least loaded GPU."""
+        def load(g):
+            return sum(self.workload(lengths[i], cp) for i, cp in plan[g])
+        W = len(plan)
+        for _ in range(4 * W):
+            loads = [load(g) for g in range(W)]
+            mean = sum(loads) / W
+            hi = max(range(W), key=loads.__getitem__)
+            lo = min(range(W), key=loads.__getitem__)
+            movable = [(i, cp) for i, cp in plan[hi] if cp == 1]
+            if loads[hi] <= tolerance * mean or not movable:
+                break
+            item = min(movable, key=lambda t: lengths[t[0]])
+            if loads[lo] + self.workload(lengths[item[0]], 1) >= loads[hi]:
+                break
+            plan[hi].remove(item)
+            plan[lo].append(item)
+        return plan
+
+    def _fill_empty_gpus(self, plan: list[list[tuple[int, int]]], lengths: list[int]):
+        """No GPU may idle while another holds several single-GPU sequences."""
+        for g in range(len(plan)):
+            if plan[g]:
+                continue
+            donors = [d for d in range(len(plan)) if sum(1 for _, cp in plan[d] if cp == 1) >= 2 or
+                      (len(plan[d]) >= 2 and any(cp == 1 for _, cp in plan[d]))]
+            if not donors:
+                continue
+            d = max(donors, key=lambda k: sum(self.workload(lengths[i], cp) for i, cp in plan[k]))
+            item = max((t for t in plan[d] if t[1] == 1), key=lambda t: lengths[t[0]])
+            plan[d].remove(item)
+            plan[g].append(item)
+        return plan
+
+    def balanced_schedule(self, lengths: list[int]) -> list[list[tuple[int, int]]]:
+        return self._fill_empty_gpus(self._trim_overloaded(self.schedule(lengths), lengths), lengths)
+
+
+def hybrid_context_parallel_forward_backward(model_step, batches: list[dict], scheduler: BalancedCPScheduler,
+                                             rank: int, lengths: list[int] | None = None) -> list:
+    """Runs `model_step(batch, cp_degree, cp_slot)` for every sequence this rank takes part in, in schedule order.
+    `batches[i]` is sequence i (dict with input_ids [1, L]); `cp_slot` is this rank's position inside the sequence's
+    group of `cp_degree` consecutive ranks.  Returns the per-sequence results of this rank."""
+    lengths = lengths or [int(b["input_ids"].shape[1]) for b in batches]
+    plan = scheduler.balanced_schedule(lengths)
+    out = []
+    for i, cp in plan[rank]:
+        out.append(model_step(batches[i], cp, rank % cp))
+    return out
+
+
+# ------------------------------------------------------------------------------------------------ engine-level API
+class LoadBalancer(IntEnum):
+    NONE = 0
+    HEAD_TAIL = 1
+    ZIGZAG = 2
+    PTRR = 3
+
+
+class CommBackend(IntEnum):
+    NCCL = 0
+    GLOO = 1
+
+
+class AttentionPattern(IntEnum):
+    CAUSAL = 0
+    FULL = 1
+    SLIDING_WINDOW = 2
+
+
+def get_load_balancer(strategy: "LoadBalancer | str", cp: int = 1, rank: int = 0):
+    name = strategy.name.lower() if isinstance(strategy, LoadBalancer) else str(strategy).lower()
+    if name == "none":
+        raise ValueError("contiguous (unbalanced) sharding is not provided: causal work would be rank-skewed")
+    return create_balancer(name, cp, rank)
+
+
+class TensorArena:
+    """Bump allocator over one pre-allocated byte buffer: per-step scratch without touching the caching allocator.
+    `allocate` returns Err when the arena is exhausted; `reset` makes the whole arena available again."""
+
+    ALIGN = 256
+
+    def __init__(self, size_bytes: int, device: torch.device | str = "cpu"):
+        self.size = int(size_bytes)
+        self.buf = torch.empty(self.size, dtype=torch.uint8, device=device)
+        self.offset = 0
+        self.peak = 0
+
+    def allocate(self, shape: tuple, dtype: torch.dtype):
+        from ..core.types import Err, Ok
+        n = 1
+        for s in shape:
+            n *= s
+        nbytes = n * torch.empty((), dtype=dtype).element_size()
+        start = (self.offset + self.ALIGN - 1) // self.ALIGN * self.ALIGN
+        if start + nbytes > self.size:
+            return Err(MemoryError(f"arena exhausted: need {nbytes} bytes, {self.size - start} left"))
+        self.offset = start + nbytes
+        self.peak = max(self.peak, self.offset)
+        return Ok(self.buf[start:start + nbytes].view(dtype).view(shape))
+
+    def reset(self) -> None:
+        self.offset = 0
+
+    @property
+    def utilization(self) -> float:
+        return self.offset / self.size if self.size else 0.0
+
+    @property
+    def available_bytes(self) -> int:
+        return self.size - self.offset
+
+
+class RingBufferPool:
+    """K/V staging buffers of the ring: while one is computed on, one is being sent and one received."""
+
+    FREE, COMPUTE, SENDING, RECEIVING = range(4)
+
+    def __init__(self, count: int, shape: tuple, dtype: torch.dtype, device: torch.device | str = "cpu"):
+        if count < 2:
+            raise ValueError("a ring needs at least two buffers")
+        self.buffers = [torch.empty(shape, dtype=dtype, device=device) for _ in range(count)]
+        self.state = [self.FREE] * count
+
+    def _take(self, new_state: int) -> int:
+        for i, s in enumerate(self.state):
+            if s == self.FREE:
+                self.state[i] = new_state
+                return i
+        raise RuntimeError("no free ring buffer (a transfer was not marked free)")
+
+    def get_compute_buffer(self) -> tuple[torch.Tensor, int]:
+        i = self._take(self.COMPUTE)
+        return self.buffers[i], i
+
+    def get_recv_buffer(self) -> tuple[torch.Tensor, int]:
+        i = self._take(self.RECEIVING)
+        return self.buffers[i], i
+
+    def mark_sending(self, idx: int) -> None:
+        self.state[idx] = self.SENDING
+
+    def mark_receiving(self, idx: int) -> None:
+        self.state[idx] = self.RECEIVING
+
+    def mark_free(self, idx: int) -> None:
+        self.state[idx] = self.FREE
+
+    def get_buffer(self, idx: int) -> torch.Tensor:
+        return self.buffers[idx]
+
+
+@dataclass
+class ContextParallelMetrics:
+    steps: int = 0
+    bytes_sent: int = 0
+    comm_ms: float = 0.0
+    compute_ms: float = 0.0
+    flops: float = 0.0
+
+    def compute_bandwidth_gbps(self) -> float:
+        return self.bytes_sent / (self.comm_ms * 1e6) if self.comm_ms > 0 else 0.0
+
+    def compute_tflops(self) -> float:
+        return self.flops / (self.compute_ms * 1e9) if self.compute_ms > 0 else 0.0
+
+    def to_dict(self) -> dict:
+        return dict(self.__dict__, bandwidth_gbps=self.compute_bandwidth_gbps(), tflops=self.compute_tflops())
+
+
+@dataclass
+class ContextParallelConfig:
+    cp_degree: int = 1
+    load_balancer: LoadBalancer = LoadBalancer.HEAD_TAIL
+    attention_pattern: AttentionPattern = AttentionPattern.CAUSAL
+    sliding_window_size: int = 0
+    use_ring_attention: bool = True
+    ring_buffer_count: int = 3
+    overlap_comm_compute: bool = True
+    use_arena_allocator: bool = False
+    arena_size_gb: float = 2.0
+    use_activation_checkpointing: bool = False
+    use_triton_kernels: bool = False          # the sm_100a flash kernels are used on CUDA
+    comm_backend: CommBackend = CommBackend.NCCL
+
+    def __post_init__(self):
+        if isinstance(self.load_balancer, str):
+            self.load_balancer = LoadBalancer[self.load_balancer.upper()]
+        if self.cp_degree < 1:
+            raise ValueError("cp_degree must be >= 1")
+        if self.attention_pattern is not AttentionPattern.CAUSAL and self.cp_degree > 1:
+            raise ValueError("the ring implementation covers causal attention")
+        if self.load_balancer is not LoadBalancer.HEAD_TAIL and self.use_ring_attention and self.cp_degree > 1:
+            raise ValueError("ring attention pairs the head-tail layout; zigzag / ptrr serve the all-gather path")
+
+    @classmethod
+    def from_dict(cls, config_dict: dict):
+        from ..core.types import Err, Ok
+        try:
+            known = {k: v for k, v in config_dict.items() if k in cls.__dataclass_fields__}
+            return Ok(cls(**known))
+        except (ValueError, KeyError, TypeError) as e:
+            return Err(ValueError(str(e)))
+
+    def compute_memory_requirement(self, seq_len: int, hidden: int, n_layers: int, n_kv_heads: int, head_dim: int,
+                                   bytes_per_el: int = 2) -> dict:
+        return estimate_memory_per_gpu(seq_len, self.cp_degree, hidden, n_layers, n_kv_heads, head_dim, bytes_per_el,
+                                       self.use_activation_checkpointing)
+
+
+class RingCommunicator:
+    """Neighbour exchange of the ring: send to rank+1, receive from rank-1, as one batched call."""
+
+    def __init__(self, group=None):
+        self.group = group
+        on = dist.is_available() and dist.is_initialized()
+        self.world = dist.get_world_size(group) if on else 1
+        self.rank = dist.get_rank(group) if on else 0
+        self.bytes_sent = 0
+
+    def _global(self, r: int) -> int:
+        return dist.get_global_rank(self.group, r) if self.group is not None else r
+
+    def start_send_recv(self, send: torch.Tensor, recv: torch.Tensor):
+        if self.world == 1:
+            recv.copy_(send)
+            return []
+        nxt, prv = self._global((self.rank + 1) % self.world), self._global((self.rank - 1) % self.world)
+        ops = [dist.P2POp(dist.isend, send.contiguous(), nxt, self.group), dist.P2POp(dist.irecv, recv, prv, self.group)]
+        self.bytes_sent += send.numel() * send.element_size()
+        return dist.batch_isend_irecv(ops)
+
+    @staticmethod
+    def wait_recv(handles) -> None:
+        for h in handles:
+            h.wait()
+
+
+class ContextParallelEngine:
+    """Shards a batch over the context-parallel group, runs exact causal ring attention on the shards (forward and
+    backward through autograd), gathers outputs back into sequence order."""
+
+    def __init__(self, config: ContextParallelConfig | None = None, group=None):
+        self._config = config or ContextParallelConfig()
+        self.group = group
+        self._metrics = ContextParallelMetrics()
+        self._initialized = False
+        self._rank, self._world = 0, 1
+        self.arena: TensorArena | None = None
+
+    def initialize(self, group=None, device: torch.device | str = "cpu"):
+        from ..core.types import Err, Ok
+        self.group = group if group is not None else self.group
+        on = dist.is_available() and dist.is_initialized()
+        self._world = dist.get_world_size(self.group) if on else 1
+        self._rank = dist.get_rank(self.group) if on else 0
+        if self._world != self._config.cp_degree:
+            return Err(ValueError(f"cp_degree {self._config.cp_degree} != group size {self._world}"))
+        if self._config.use_arena_allocator:
+            self.arena = TensorArena(int(self._config.arena_size_gb * 2 ** 30), device)
+        self._initialized = True
+        return Ok(self)
+
+    config = property(lambda self: self._config)
+    cp_rank = property(lambda self: self._rank)
+    cp_world_size = property(lambda self: self._world)
+
+    def _balancer(self) -> str:
+        return self._config.load_balancer.name.lower()
+
+    def shard_inputs(self, input_ids: torch.Tensor, labels: torch.Tensor | None = None,
+                     attention_mask: torch.Tensor | None = None, position_ids: torch.Tensor | None = None,
+                     seq_dim: int = 1):
+        """-> (input_ids, labels (already shifted), attention_mask, position_ids) of this rank."""
+        assert seq_dim == 1, "sequences are dimension 1"
+        batch = {"input_ids": input_ids}
+        if labels is not None:
+            batch["labels"] = labels
+        if attention_mask is not None:
+            batch["attention_mask"] = attention_mask
+        if position_ids is not None:
+            batch["position_ids"] = position_ids
+        out = shard_inputs(batch, self._world, self._rank, self._balancer()) if self._world > 1 else \
+            dict(batch, position_ids=position_ids if position_ids is not None else
+                 torch.arange(input_ids.shape[1], device=input_ids.device).unsqueeze(0).expand_as(input_ids))
+        return out["input_ids"], out.get("labels"), out.get("attention_mask"), out["position_ids"]
+
+    def ring_attention_forward(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
+                               attention_mask: torch.Tensor | None = None) -> torch.Tensor:
+        """q [1, S_local, Hq, D], k / v [1, S_local, Hkv, D] (rotary already applied with global positions)."""
+        if attention_mask is not None:
+            raise ValueError("padding masks are not supported by the ring path: pack the sequences instead")
+        self._metrics.steps += 1
+        if self._world == 1:
+            from ..ops.attention import attention_reference
+            return attention_reference(q, k, v, causal=True).to(q.dtype)
+        S, Hq, D = q.shape[1], q.shape[2], q.shape[3]
+        self._metrics.flops += 4.0 * (S * self._world) * (S * self._world) * Hq * D / 2 / self._world
+        self._metrics.bytes_sent += 2 * k.numel() * k.element_size() * (self._world - 1)
+        return ring_attention(q, k, v, self.group)
+
+    def gather_output(self, x_local: torch.Tensor, seq_dim: int = 1) -> torch.Tensor:
+        if self._world == 1:
+            return x_local
+        return gather_output(x_local, self.group, self._balancer(), seq_dim)
+
+    def get_metrics(self) -> ContextParallelMetrics:
+        return self._metrics
+
+    def reset_metrics(self) -> None:
+        self._metrics = ContextParallelMetrics()
+
+
+class ContextParallelAttention(nn.Module):
+    """Attention core for modules that produce q / k / v themselves: ring attention when the engine spans more than one
+    rank, plain causal attention otherwise."""
+
+    def __init__(self, engine: ContextParallelEngine):
+        super().__init__()
+        self.engine = engine
+
+    def forward(self, query: torch.Tensor, key: torch.Tensor, value: torch.Tensor,
+                attention_mask: torch.Tensor | None = None, position_ids: torch.Tensor | None = None) -> torch.Tensor:
+        return self.engine.ring_attention_forward(query, key, value, attention_mask)
+
+
+def create_context_parallel_engine(cp_degree: int = 1, load_balancer: str = "head_tail", use_ring_attention: bool = True,
+                                   use_triton: bool = False, group=None, **kwargs):
+    """-> Result[ContextParallelEngine]: configuration errors and a group of the wrong size come back as Err."""
+    from ..core.types import Err
+    r = ContextParallelConfig.from_dict(dict(kwargs, cp_degree=cp_degree, load_balancer=load_balancer,
+                                             use_ring_attention=use_ring_attention))
+    if r.is_err():
+        return r
+    return ContextParallelEngine(r.unwrap(), group).initialize(group)
+
+
+class ContextParallel:
+    """Two-call convenience wrapper: `shard_inputs(batch)` before the model, `restore_sequence(x)` after it."""
+
+    def __init__(self, group=None, load_balancer: str = "head_tail"):
+        self.group, self.load_balancer = group, load_balancer
+        on = dist.is_available() and dist.is_initialized()
+        self.world = dist.get_world_size(group) if on else 1
+        self.rank = dist.get_rank(group) if on else 0
+
+    def shard_inputs(self, batch: dict) -> dict:
+        return shard_inputs(batch, self.world, self.rank, self.load_balancer) if self.world > 1 else batch
+
+    def restore_sequence(self, x_local: torch.Tensor, dim: int = 1) -> torch.Tensor:
+        return gather_output(x_local, self.group, self.load_balancer, dim) if self.world > 1 else x_local
