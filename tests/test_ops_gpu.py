@@ -340,3 +340,22 @@ def test_plain_activation_kernel(name):
     yr.backward(dy.float())
     assert (y.float() - yr).abs().max().item() < 3e-2
     assert (x.grad.float() - xr.grad).abs().max().item() < 5e-2
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("rows,V,smoothing", [(257, 1000, 0.0), (512, 32000, 0.1), (64, 4099, 0.0)])
+def test_fused_cross_entropy_loss_module_forward_backward(rows, V, smoothing):
+    """FusedCrossEntropyLoss on materialised bf16 logits: loss and d(logits) from the row kernel against fp32 PyTorch."""
+    from trainscale_b200.losses import FusedCrossEntropyLoss
+    torch.manual_seed(0)
+    logits = (torch.randn(rows, V, device="cuda") * 2).to(torch.bfloat16).requires_grad_(True)
+    labels = torch.randint(0, V, (rows,), device="cuda")
+    labels[::7] = -100
+    loss = FusedCrossEntropyLoss(label_smoothing=smoothing)(logits, labels)
+    loss.backward()
+    ref_in = logits.detach().float().requires_grad_(True)
+    ref = torch.nn.functional.cross_entropy(ref_in, labels, ignore_index=-100, label_smoothing=smoothing)
+    ref.backward()
+    assert abs(float(loss) - float(ref)) < 2e-3 * max(1.0, abs(float(ref)))
+    torch.testing.assert_close(logits.grad.float(), ref_in.grad, rtol=2e-2, atol=2e-5)
+    assert float(logits.grad[::7].abs().max()) == 0.0

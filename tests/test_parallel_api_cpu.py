@@ -256,3 +256,103 @@ def test_context_parallel_helpers():
     CP.hybrid_context_parallel_forward_backward(lambda b, cp, slot: seen.append((b["input_ids"].shape[1], cp, slot)),
                                                 [{"input_ids": torch.zeros(1, n)} for n in L], s, rank=1)
     assert seen[0] == (30000, 4, 1)
+
+
+def test_utility_surface_single_process():
+    import copy
+    import tempfile
+    from trainscale_b200.parallel import activation as A
+    from trainscale_b200.parallel import ddp as DDP
+    from trainscale_b200.parallel import dist_utils as U
+    from trainscale_b200.parallel import mesh as M
+    from trainscale_b200.utils.cuda_graphs import InductorConfigManager
+    # memory pressure monitor on a fake probe
+    used = [10]
+    mon = DDP.MemoryPressureMonitor(probe=lambda: (used[0], 100))
+    assert mon.check() == "normal" and mon.suggested_bucket_mb(80) == 80
+    used[0] = 90
+    assert mon.check() == "high" and mon.suggested_bucket_mb(80) == 40
+    used[0] = 97
+    assert mon.check() == "critical" and mon.suggested_bucket_mb(80) == 20 and len(mon.events) == 2
+    t = DDP.CUDATimer("cpu")
+    with t:
+        pass
+    assert t.elapsed_ms() >= 0 and DDP.SyncMode("local_sgd") is DDP.SyncMode.LOCAL_SGD
+    assert DDP.DDPMetrics(allreduce_ms=1.0, bytes_reduced=10 ** 9).bus_bandwidth_gbs(8) == pytest.approx(1750.0)
+    # hierarchical recomputation == plain backward
+    torch.manual_seed(0)
+    layers = nn.ModuleList([nn.Sequential(nn.Linear(8, 8), nn.Tanh()) for _ in range(9)])
+    ref = copy.deepcopy(layers)
+    x = torch.randn(4, 8, requires_grad=True)
+    x2 = x.detach().clone().requires_grad_(True)
+    h = A.HierarchicalCheckpointManager(layers)
+    h(x).sum().backward()
+    z = x2
+    for l in ref:
+        z = l(z)
+    z.sum().backward()
+    assert h.group_size == 3 and h.kept_tensors() == 6
+    torch.testing.assert_close(x.grad, x2.grad)
+    for a, b in zip(layers.parameters(), ref.parameters()):
+        torch.testing.assert_close(a.grad, b.grad)
+    assert A.CheckpointFunction.__name__ == "CheckpointFunction"
+    pool = A.ActivationPool()
+    buf = pool.get((4, 4), torch.float32, "cpu")
+    pool.put(buf)
+    assert pool.get((4, 4), torch.float32, "cpu").data_ptr() == buf.data_ptr() and pool.hits == 1
+    # mesh views
+    cfg = M.ParallelDimsConfig(dp_replicate=2, dp_shard=-1, cp=2, tp=2, pp=2, world_size=32)
+    v = M.MeshCache.views(cfg, rank=13)
+    assert v["dense"].size("fsdp") == 4 and v["loss"].size() == 8 and v["dataloading"].shape == (2, 4, 2, 2)
+    assert M.MeshCache.get(cfg, rank=13) is M.MeshCache.get(cfg, rank=13)
+    with pytest.raises(KeyError):
+        v["loss"].get_group("tp")
+    # engine factory + checkpoint helpers
+    from trainscale_b200.models.llama import LlamaConfig, build_model
+    m = build_model(LlamaConfig(vocab_size=64, hidden_size=32, intermediate_size=64, num_hidden_layers=2,
+                                num_attention_heads=2, num_key_value_heads=2, head_dim=16), dtype=torch.float32,
+                    device="cpu", seed=0)
+    m, eng = U.prepare_model_for_distributed(m, "zero2", device="cpu", param_dtype=torch.float32, lr=1e-2)
+    ids = torch.randint(0, 64, (2, 8))
+    eng.backward(m(ids, labels=ids).loss)
+    eng.step()
+    d = tempfile.mkdtemp()
+    U.save_checkpoint_distributed(d, m, eng, {"step": 1})
+    w = {k: t.clone() for k, t in m.state_dict().items()}
+    with torch.no_grad():
+        for p in m.parameters():
+            p.zero_()
+    assert U.load_checkpoint_distributed(d, m, eng) == {"step": 1}
+    assert all(torch.equal(w[k], t) for k, t in m.state_dict().items())
+    with pytest.raises(ValueError):
+        U.prepare_model_for_distributed(m, "bogus", device="cpu")
+    assert U.DeviceManager().device.type in ("cpu", "cuda") and U.HardwareTopology.detect().num_gpus >= 0
+    assert U.get_process_group("world") is None
+    # inductor options only touch torch when asked to, and are restored
+    import torch._inductor.config as ic
+    before = ic.max_autotune
+    with InductorConfigManager(apply_to_torch=True).for_mode("max-autotune") as mgr:
+        assert ic.max_autotune is True and mgr.compilation_config().mode == "cuda_graphs"
+    assert ic.max_autotune == before and InductorConfigManager(max_autotune=True).apply() == {}
+
+
+def test_registry_module_patchers_keep_the_maths():
+    transformers = pytest.importorskip("transformers")
+    from trainscale_b200.registry import auto_patch, auto_patch_layernorm
+    cfg = transformers.LlamaConfig(vocab_size=128, hidden_size=64, intermediate_size=128, num_hidden_layers=2,
+                                   num_attention_heads=4, num_key_value_heads=2)
+    torch.manual_seed(0)
+    m = transformers.LlamaForCausalLM(cfg).eval()
+    ids = torch.randint(0, 128, (1, 16))
+    with torch.no_grad():
+        ref = m(ids).logits
+    counts = auto_patch(m)
+    assert counts["layernorm"] == 5 and counts["mlp"] == 2 and counts["fp8_linear"] == 0
+    with torch.no_grad():
+        torch.testing.assert_close(m(ids).logits, ref)
+    assert auto_patch(m)["layernorm"] == 0                       # idempotent
+    ln = nn.Sequential(nn.LayerNorm(16))
+    x = torch.randn(2, 16)
+    want = ln(x)
+    assert auto_patch_layernorm(ln) == 1
+    torch.testing.assert_close(ln(x), want)

@@ -185,6 +185,90 @@ CASES = {"fp8": bench_fp8, "moe": bench_moe, "layernorm": bench_layernorm, "rmsn
          "gemm": bench_gemm, "attention": bench_attention, "adamw": bench_adamw}
 
 
+class BenchmarkSuite:
+    """Object form of the kernel benchmarks (data_pipeline/trainer/kernels/benchmark_suite.py:97-338 has the same
+    `run_*` / `report` surface): each `run_*` times one kernel family with CUDA events (L2 flushed between
+    iterations) against the PyTorch op of the same maths and appends rows to `self.results`."""
+
+    def __init__(self, small: bool = False, device: str = "cuda"):
+        self.small, self.device = small, device
+        self.results: list[dict] = []
+        self._timer: Timer | None = None
+
+    def _run(self, fn) -> list[dict]:
+        if not torch.cuda.is_available():
+            return []
+        if self._timer is None:
+            self._timer = Timer(64 if self.small else 256)
+        rows = fn(self._timer, self.small)
+        self.results += rows
+        return rows
+
+    def run_rms_norm(self):
+        return self._run(bench_rmsnorm)
+
+    def run_layer_norm(self):
+        return self._run(bench_layernorm)
+
+    def run_fused_gelu(self):
+        return self._run(bench_gelu)
+
+    def run_swiglu(self):
+        return self._run(bench_swiglu)
+
+    def run_fp8_quantization(self):
+        return self._run(bench_fp8)
+
+    def run_rope(self):
+        return self._run(bench_rope)
+
+    def run_flash_attention(self):
+        return self._run(bench_attention)
+
+    def run_cross_entropy(self):
+        return self._run(bench_cross_entropy)
+
+    def run_gemm(self):
+        return self._run(bench_gemm)
+
+    def run_optimizer(self):
+        return self._run(bench_adamw)
+
+    def run_moe(self):
+        return self._run(bench_moe)
+
+    def run_all(self):
+        for name in ("run_rms_norm", "run_layer_norm", "run_fused_gelu", "run_swiglu", "run_fp8_quantization",
+                     "run_rope", "run_flash_attention", "run_cross_entropy", "run_gemm", "run_optimizer", "run_moe"):
+            getattr(self, name)()
+        return self.results
+
+    def report(self) -> str:
+        pk = peaks()
+        tag = "of fallback" if pk.get("fallback") else "of measured"
+        lines = []
+        for r in self.results:
+            frac = r["gbs"] / pk["hbm_gbs"] if "gbs" in r else r["tflops"] / pk["bf16_tflops"]
+            rate = f"{r['gbs']:.0f} GB/s" if "gbs" in r else f"{r['tflops']:.0f} TFLOPS"
+            sp = f"{r['baseline_ms'] / r['ms']:.2f}x" if r.get("baseline_ms") else "-"
+            lines.append(f"{r['name']:<40s} {r['ms']:8.3f} ms  {sp:>7s}  {rate:>12s}  {frac:5.2f} {tag}")
+        return "\n".join(lines)
+
+
+def bench_gelu(t, small):
+    from .ops import activation
+    out = []
+    for n in ([1 << 24] if small else [1 << 24, 1 << 27]):
+        x = torch.randn(n, device="cuda", dtype=torch.bfloat16)
+        ms = t(lambda: activation.gelu(x, "tanh"))
+        base = t(lambda: F.gelu(x, approximate="tanh"))
+        out.append(dict(name=f"gelu n={n}", ms=ms, baseline_ms=base, gbs=2 * n * 2 / ms / 1e6))
+    return out
+
+
+CASES["gelu"] = bench_gelu
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--only", default=None, choices=sorted(CASES))

@@ -78,15 +78,17 @@ class FusedCrossEntropyLoss(CrossEntropyLoss):
     """Same contract; CUDA bf16 logits go through the row kernel (loss + lse in one pass)."""
 
     def forward(self, logits, labels):
-        if logits.is_cuda and logits.dtype == torch.bfloat16 and self.z == 0 and self.reduction in ("mean", "sum") \
-                and not logits.requires_grad:
+        if logits.is_cuda and logits.dtype == torch.bfloat16 and self.z == 0 and self.reduction in ("mean", "sum"):
             z = logits.reshape(-1, logits.shape[-1])
-            if z.stride(0) % 8 == 0 and z.data_ptr() % 16 == 0:
-                rows, _ = ce_ops.cross_entropy_logits(z.contiguous(), labels.reshape(-1).long(), self.ignore_index,
-                                                      self.label_smoothing)
-                s = rows.sum()
-                return s / (labels != self.ignore_index).sum().clamp(min=1) if self.reduction == "mean" else s
+            # forward and backward both run on the row kernel (FusedCrossEntropyFunction)
+            rows = ce_ops.cross_entropy_rows(z, labels.reshape(-1), self.ignore_index, self.label_smoothing)
+            s = rows.sum()
+            return s / (labels != self.ignore_index).sum().clamp(min=1) if self.reduction == "mean" else s
         return super().forward(logits, labels)
+
+
+FusedCrossEntropyFunction = ce_ops.FusedCrossEntropyFunction
+Fast_CrossEntropyLoss = FusedCrossEntropyLoss      # name used by data_pipeline/trainer/kernels/triton_kernels.py:330
 
 
 class ChunkedCrossEntropyLoss(nn.Module):

@@ -81,6 +81,44 @@ class _FocalLossFn(torch.autograd.Function):
         return grad, None, None, None
 
 
+class FusedCrossEntropyFunction(torch.autograd.Function):
+    """Cross-entropy on materialised bf16 CUDA logits [rows, V] with the row kernel on both sides: forward = one pass
+    (per-row loss + lse), backward = one pass writing (softmax - target) * per-row scale over a copy of the logits.
+    Returns the per-row losses (0 for ignored rows); reduce them outside."""
+
+    @staticmethod
+    def forward(ctx, logits, labels, ignore_index=-100, label_smoothing=0.0):
+        rows = logits.shape[0]
+        lg = logits if logits.stride(-1) == 1 else logits.contiguous()
+        if lg.stride(0) % 8 != 0 or lg.data_ptr() % 16 != 0:
+            pad = torch.zeros(rows, _pad_ld(lg.shape[1]), dtype=lg.dtype, device=lg.device)
+            pad[:, :lg.shape[1]] = lg
+            lg = pad[:, :logits.shape[1]]
+        labels = labels.reshape(-1).to(torch.int64)
+        loss = torch.empty(rows, dtype=torch.float32, device=lg.device)
+        lse = torch.empty(rows, dtype=torch.float32, device=lg.device)
+        _ce_rows(lg, labels, loss, lse, ignore_index, label_smoothing, 1.0, 0.0, None, 1.0, None, False)
+        ctx.save_for_backward(lg, labels)
+        ctx.ignore_index, ctx.label_smoothing = ignore_index, label_smoothing
+        return loss
+
+    @staticmethod
+    def backward(ctx, dloss):
+        lg, labels = ctx.saved_tensors
+        grad = lg.clone()
+        tmp_loss = torch.empty(lg.shape[0], dtype=torch.float32, device=lg.device)
+        tmp_lse = torch.empty_like(tmp_loss)
+        _ce_rows(grad, labels, tmp_loss, tmp_lse, ctx.ignore_index, ctx.label_smoothing, 1.0, 0.0, None, 1.0,
+                 dloss.float().contiguous(), True)
+        return grad, None, None, None
+
+
+def cross_entropy_rows(logits: torch.Tensor, labels: torch.Tensor, ignore_index: int = -100,
+                       label_smoothing: float = 0.0) -> torch.Tensor:
+    """Differentiable per-row cross-entropy of bf16 CUDA logits on the row kernel."""
+    return FusedCrossEntropyFunction.apply(logits, labels, int(ignore_index), float(label_smoothing))
+
+
 def focal_loss_rows(logits: torch.Tensor, labels: torch.Tensor, gamma: float = 2.0, ignore_index: int = -100):
     """Per-row focal loss of bf16 CUDA logits [rows, V] on the cross-entropy kernel (rows with ignore_index give 0)."""
     return _FocalLossFn.apply(logits, labels, float(gamma), int(ignore_index))

@@ -296,6 +296,79 @@ class AdaFactor(Optimizer):
         return loss
 
 
+class DistributedAdaFactor(AdaFactor):
+    """AdaFactor for matrices that are row-sharded over a process group (tensor-parallel column-parallel weights,
+    ZeRO shards that keep whole rows): the row statistics are local, the column statistics and the row-mean / RMS
+    scalars are all-reduced so that every shard applies exactly the update of the unsharded matrix
+    (data_pipeline/trainer/optimizers/adafactor.py:1561 has the same role)."""
+
+    def __init__(self, params, group=None, **kw):
+        super().__init__(params, **kw)
+        self.group = group
+
+    def _world(self) -> int:
+        import torch.distributed as dist
+        return dist.get_world_size(self.group) if dist.is_available() and dist.is_initialized() else 1
+
+    def _sum(self, t: torch.Tensor) -> torch.Tensor:
+        import torch.distributed as dist
+        if self._world() > 1:
+            dist.all_reduce(t, group=self.group)
+        return t
+
+    @torch.no_grad()
+    def step(self, closure=None):
+        loss = closure() if closure is not None else None
+        W = self._world()
+        for g in self.param_groups:
+            for p in g["params"]:
+                if p.grad is None:
+                    continue
+                gf, pf = p.grad.float(), p.float()
+                st = self.state[p]
+                factored = gf.dim() >= 2
+                if not st:
+                    st["step"] = 0
+                    if factored:
+                        st["row"] = torch.zeros(gf.shape[:-1], device=gf.device)
+                        st["col"] = torch.zeros(gf.shape[:-2] + gf.shape[-1:], device=gf.device)
+                    else:
+                        st["v"] = torch.zeros_like(gf)
+                    if g["beta1"] is not None:
+                        st["m"] = torch.zeros_like(gf)
+                st["step"] += 1
+                n_global = self._sum(torch.tensor(float(pf.numel()), device=pf.device))
+                rms_p = float((self._sum(pf.pow(2).sum()) / n_global).sqrt())
+                if g["relative_step"]:
+                    min_step = 1e-6 * st["step"] if g["warmup_init"] else 1e-2
+                    lr = min(min_step, 1.0 / math.sqrt(st["step"]))
+                else:
+                    lr = g["lr"]
+                if g["scale_parameter"]:
+                    lr = lr * max(g["eps"][1], rms_p)
+                beta2 = 1.0 - st["step"] ** g["decay_rate"]
+                upd = gf * gf + g["eps"][0]
+                if factored:
+                    st["row"].mul_(beta2).add_(upd.mean(-1), alpha=1 - beta2)
+                    col_mean = self._sum(upd.sum(-2)) / (gf.shape[-2] * W)       # mean over ALL rows of the matrix
+                    st["col"].mul_(beta2).add_(col_mean, alpha=1 - beta2)
+                    row_mean = self._sum(st["row"].sum(-1, keepdim=True)) / (gf.shape[-2] * W)
+                    u = gf * (st["row"] / row_mean).rsqrt().unsqueeze(-1) * st["col"].unsqueeze(-2).rsqrt()
+                else:
+                    st["v"].mul_(beta2).add_(upd, alpha=1 - beta2)
+                    u = gf * st["v"].rsqrt()
+                rms_u = float((self._sum(u.pow(2).sum()) / n_global).sqrt())
+                u.div_(max(1.0, rms_u / g["clip_threshold"]))
+                u.mul_(lr)
+                if g["beta1"] is not None:
+                    st["m"].mul_(g["beta1"]).add_(u, alpha=1 - g["beta1"])
+                    u = st["m"]
+                if g["weight_decay"]:
+                    pf.mul_(1 - g["weight_decay"] * lr)
+                p.copy_(pf - u)
+        return loss
+
+
 class CAME(Optimizer):
     """Confidence-guided AdaFactor: a second factored EMA of the update's instability rescales the step."""
 
@@ -610,7 +683,7 @@ class ADOPT(Optimizer):
 
 
 _OPTIMIZERS = {"adamw": AdamW, "fused_adamw": AdamW, "adam8bit": Adam8bit, "adamw_8bit": Adam8bit, "lion": Lion,
-               "lamb": LAMB, "adafactor": AdaFactor, "came": CAME, "sophia": SophiaG, "sophiag": SophiaG,
+               "lamb": LAMB, "adafactor": AdaFactor, "distributed_adafactor": DistributedAdaFactor, "came": CAME, "sophia": SophiaG, "sophiag": SophiaG,
                "prodigy": Prodigy, "schedule_free": ScheduleFreeAdamW, "schedulefree": ScheduleFreeAdamW, "muon": Muon,
                "adopt": ADOPT}
 

@@ -218,3 +218,83 @@ class PipelineOffloadManager:
 
 def print_offload_summary(manager: "PipelineOffloadManager | ActivationOffloader") -> None:
     print(manager.summary())
+
+
+# ------------------------------------------------------------------------------------------------ more of the policy surface
+class ActivationPool:
+    """Device buffers for recomputed activations, recycled by (shape, dtype): a layer's recomputation in step n reuses
+    the storage its recomputation used in step n-1 instead of going through the allocator."""
+
+    def __init__(self, max_bytes: int = 8 * 2 ** 30):
+        self.max_bytes = max_bytes
+        self._free: dict[tuple, list[torch.Tensor]] = {}
+        self.bytes_cached = 0
+        self.hits = self.misses = 0
+
+    def get(self, shape, dtype: torch.dtype, device) -> torch.Tensor:
+        key = (tuple(shape), dtype, str(device))
+        lst = self._free.get(key)
+        if lst:
+            t = lst.pop()
+            self.bytes_cached -= t.numel() * t.element_size()
+            self.hits += 1
+            return t
+        self.misses += 1
+        return torch.empty(shape, dtype=dtype, device=device)
+
+    def put(self, t: torch.Tensor) -> None:
+        nb = t.numel() * t.element_size()
+        if self.bytes_cached + nb > self.max_bytes:
+            return
+        self._free.setdefault((tuple(t.shape), t.dtype, str(t.device)), []).append(t.detach())
+        self.bytes_cached += nb
+
+    def clear(self) -> None:
+        self._free.clear()
+        self.bytes_cached = 0
+
+
+def _checkpoint_function():
+    from .pipeline import CheckpointFunction as F
+    return F
+
+
+def __getattr__(name):          # `CheckpointFunction` lives in pipeline.py; exposed here without an import cycle
+    if name == "CheckpointFunction":
+        return _checkpoint_function()
+    raise AttributeError(name)
+
+
+class HierarchicalCheckpointManager:
+    """Two-level recomputation for a chain of L layers: the chain is cut into groups of `group_size`; the forward keeps
+    only each group's input (L / g tensors).  In backward a group is re-run once, and during that re-run each layer
+    keeps only ITS input (g tensors), re-running itself when its turn comes.  Peak kept activations are about
+    L / g + g layer inputs (minimal at g = sqrt(L)) for two extra forwards."""
+
+    def __init__(self, layers, group_size: int | None = None, use_reentrant: bool = False):
+        self.layers = list(layers)
+        L = len(self.layers)
+        self.group_size = group_size or max(1, int(round(L ** 0.5)))
+        self.use_reentrant = use_reentrant
+        self.groups = [self.layers[i:i + self.group_size] for i in range(0, L, self.group_size)]
+
+    def kept_tensors(self) -> int:
+        return len(self.groups) + self.group_size
+
+    def _run_group(self, group, x, *args):
+        from torch.utils.checkpoint import checkpoint
+        for layer in group:
+            x = checkpoint(layer, x, *args, use_reentrant=self.use_reentrant) if torch.is_grad_enabled() \
+                else layer(x, *args)
+        return x
+
+    def forward(self, x, *args):
+        from torch.utils.checkpoint import checkpoint
+        for g in self.groups:
+            if torch.is_grad_enabled():
+                x = checkpoint(self._run_group, g, x, *args, use_reentrant=self.use_reentrant)
+            else:
+                x = self._run_group(g, x, *args)
+        return x
+
+    __call__ = forward

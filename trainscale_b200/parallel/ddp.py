@@ -38,8 +38,16 @@ class GradientCompression(str, Enum):
     NONE = "none"
     FP16 = "fp16"
     BF16 = "bf16"
+    FP8 = "fp8"
     POWERSGD = "powersgd"
     TOPK = "topk"
+    ONEBIT = "onebit"
+
+
+class SyncMode(str, Enum):
+    SYNC = "sync"                    # reduce at the end of backward
+    ASYNC = "async"                  # reduce every bucket on a side stream while backward continues
+    LOCAL_SGD = "local_sgd"          # no gradient exchange; parameters are averaged every `local_sgd_period` steps
 
 
 @dataclass
@@ -149,17 +157,181 @@ class TopKSparsificationHook:
         return bucket
 
 
+class FP16CompressionHook(CastCompressionHook):
+    def __init__(self):
+        super().__init__(torch.float16)
+
+
+class BF16CompressionHook(CastCompressionHook):
+    def __init__(self):
+        super().__init__(torch.bfloat16)
+
+
+class FP8CompressionHook:
+    """Per-bucket absmax-scaled E4M3 payload (a quarter of fp32 traffic).  Every rank's scaled bytes are all-gathered
+    and summed in fp32 locally: 8-bit floats cannot be summed by the collective without losing the small addends."""
+
+    def __call__(self, group, bucket: torch.Tensor, key: int = 0) -> torch.Tensor:
+        w = dist.get_world_size(group)
+        g = bucket.float()
+        scale = g.abs().max().clamp(min=1e-12) / 448.0
+        q = (g / scale).to(torch.float8_e4m3fn).view(torch.uint8)
+        qs = [torch.empty_like(q) for _ in range(w)]
+        ss = [torch.empty_like(scale) for _ in range(w)]
+        dist.all_gather(qs, q, group=group)
+        dist.all_gather(ss, scale, group=group)
+        out = torch.zeros_like(g)
+        for qi, si in zip(qs, ss):
+            out += qi.view(torch.float8_e4m3fn).float() * si
+        bucket.copy_(out / w)
+        return bucket
+
+
+class OneBitCompressionHook:
+    """1-bit gradients with error feedback: sign(g + e) scaled by mean |g + e|; what the sign loses stays in e.
+    Signs travel packed 8 per byte (all-gather), scales as one float per rank."""
+
+    def __init__(self):
+        self.err: dict[int, torch.Tensor] = {}
+
+    def __call__(self, group, bucket: torch.Tensor, key: int = 0) -> torch.Tensor:
+        w = dist.get_world_size(group)
+        g = bucket.float() + self.err.get(key, 0)
+        scale = g.abs().mean()
+        sign = g >= 0
+        self.err[key] = g - torch.where(sign, scale, -scale)
+        n = g.numel()
+        pad = (-n) % 8
+        bits = torch.cat((sign, sign.new_zeros(pad))) if pad else sign
+        packed = (bits.view(-1, 8).to(torch.uint8) << torch.arange(8, device=g.device, dtype=torch.uint8)).sum(1) \
+            .to(torch.uint8)
+        ps = [torch.empty_like(packed) for _ in range(w)]
+        ss = [torch.empty_like(scale) for _ in range(w)]
+        dist.all_gather(ps, packed, group=group)
+        dist.all_gather(ss, scale, group=group)
+        out = torch.zeros(n + pad, dtype=torch.float32, device=g.device)
+        shifts = torch.arange(8, device=g.device, dtype=torch.uint8)
+        for pi, si in zip(ps, ss):
+            b = ((pi.unsqueeze(1) >> shifts) & 1).reshape(-1).float()
+            out += (2 * b - 1) * si
+        bucket.copy_(out[:n] / w)
+        return bucket
+
+
 def make_hook(cfg: DDPConfig) -> Callable | None:
     c = GradientCompression(cfg.gradient_compression)
     if c == GradientCompression.FP16:
-        return CastCompressionHook(torch.float16)
+        return FP16CompressionHook()
     if c == GradientCompression.BF16:
-        return CastCompressionHook(torch.bfloat16)
+        return BF16CompressionHook()
+    if c == GradientCompression.FP8:
+        return FP8CompressionHook()
+    if c == GradientCompression.ONEBIT:
+        return OneBitCompressionHook()
     if c == GradientCompression.POWERSGD:
         return PowerSGDHook(cfg.powersgd_rank, cfg.powersgd_start_iter)
     if c == GradientCompression.TOPK:
         return TopKSparsificationHook(cfg.topk_ratio)
     return None
+
+
+class CUDATimer:
+    """Event-pair timer that never blocks the host: `stop()` records, `elapsed_ms()` reads once the events are done
+    (None until then).  On CPU it is a wall clock."""
+
+    def __init__(self, device: torch.device | str | None = None):
+        self.cuda = torch.cuda.is_available() and (device is None or torch.device(device).type == "cuda")
+        self._a = self._b = None
+        self._t0 = self._dt = None
+
+    def start(self) -> "CUDATimer":
+        if self.cuda:
+            self._a, self._b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            self._a.record()
+        else:
+            import time
+            self._t0 = time.perf_counter()
+        return self
+
+    def stop(self) -> "CUDATimer":
+        if self.cuda:
+            self._b.record()
+        else:
+            import time
+            self._dt = (time.perf_counter() - self._t0) * 1e3
+        return self
+
+    def elapsed_ms(self) -> float | None:
+        if self.cuda:
+            return self._a.elapsed_time(self._b) if self._b is not None and self._b.query() else None
+        return self._dt
+
+    __enter__ = start
+
+    def __exit__(self, *exc):
+        self.stop()
+
+
+@dataclass
+class DDPMetrics:
+    steps: int = 0
+    allreduce_ms: float = 0.0
+    backward_ms: float = 0.0
+    bytes_reduced: int = 0
+    compression_ratio: float = 1.0
+    skipped_syncs: int = 0
+
+    def record_allreduce(self, nbytes: int, ms: float | None) -> None:
+        self.bytes_reduced += nbytes
+        if ms is not None:
+            self.allreduce_ms += ms
+
+    def bus_bandwidth_gbs(self, world: int) -> float:
+        """Ring all-reduce moves 2 (w-1)/w of the payload per rank."""
+        if self.allreduce_ms <= 0 or world < 2:
+            return 0.0
+        return self.bytes_reduced * 2 * (world - 1) / world / (self.allreduce_ms * 1e6)
+
+    def to_dict(self) -> dict:
+        return dict(self.__dict__)
+
+
+class MemoryPressureMonitor:
+    """Watches allocated / total device memory; above `high` it asks for relief (smaller buckets, cache release),
+    above `critical` it releases the allocator cache itself.  Readings come from torch's allocator (or from the
+    injected `probe`, for tests): nothing on the device is configured."""
+
+    def __init__(self, device: torch.device | str | None = None, high: float = 0.85, critical: float = 0.95,
+                 probe: Callable[[], tuple[int, int]] | None = None):
+        self.device = torch.device(device) if device is not None else None
+        self.high, self.critical = high, critical
+        self._probe = probe
+        self.events: list[tuple[str, float]] = []
+
+    def usage(self) -> float:
+        if self._probe is not None:
+            used, total = self._probe()
+        elif torch.cuda.is_available():
+            free, total = torch.cuda.mem_get_info(self.device)
+            used = total - free
+        else:
+            return 0.0
+        return used / total if total else 0.0
+
+    def level(self) -> str:
+        u = self.usage()
+        return "critical" if u >= self.critical else "high" if u >= self.high else "normal"
+
+    def check(self) -> str:
+        lvl = self.level()
+        if lvl != "normal":
+            self.events.append((lvl, self.usage()))
+        if lvl == "critical" and torch.cuda.is_available() and self._probe is None:
+            torch.cuda.empty_cache()
+        return lvl
+
+    def suggested_bucket_mb(self, base_mb: int) -> int:
+        return {"normal": base_mb, "high": max(1, base_mb // 2), "critical": max(1, base_mb // 4)}[self.level()]
 
 
 class HierarchicalAllReduceManager:

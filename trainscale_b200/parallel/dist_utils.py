@@ -396,3 +396,228 @@ class DistributedManager:
         if average:
             flat /= dist.get_world_size(group)
         return {k: flat[i].item() for i, k in enumerate(keys)}
+
+
+# ------------------------------------------------------------------------------------------------ more of the utility surface
+def allreduce_position_embedding_grads(model, group, attr: str = "position_embeddings") -> None:
+    """Learned position embeddings replicated over a group (e.g. on several pipeline stages): sum their gradients."""
+    if group is None or not dist.is_initialized():
+        return
+    for name, p in model.named_parameters():
+        if attr in name:
+            g = getattr(p, "main_grad", None) if p.grad is None else p.grad
+            if g is not None:
+                dist.all_reduce(g, group=group)
+
+
+def scale_grads_by_token_count(model, num_tokens: torch.Tensor, group=None) -> torch.Tensor:
+    """Divide every gradient by the number of (non-ignored) tokens of the global batch; returns that number."""
+    total = num_tokens.detach().float().clone()
+    if dist.is_available() and dist.is_initialized():
+        dist.all_reduce(total, group=group)
+    scale = 1.0 / total.clamp(min=1.0)
+    for p in model.parameters():
+        g = getattr(p, "main_grad", None) if p.grad is None else p.grad
+        if g is not None:
+            g.mul_(scale.to(g.dtype))
+    return total
+
+
+_scale_grads_by_token_count = scale_grads_by_token_count
+
+
+class DeviceManager:
+    """Which device this process uses and what it can do (read-only queries)."""
+
+    def __init__(self, local_rank: int | None = None):
+        self.local_rank = int(os.environ.get("LOCAL_RANK", "0")) if local_rank is None else local_rank
+        self.cuda = torch.cuda.is_available()
+
+    @property
+    def device(self) -> torch.device:
+        return torch.device("cuda", self.local_rank % max(1, torch.cuda.device_count())) if self.cuda \
+            else torch.device("cpu")
+
+    def set_device(self) -> torch.device:
+        if self.cuda:
+            torch.cuda.set_device(self.device)
+        return self.device
+
+    def device_count(self) -> int:
+        return torch.cuda.device_count() if self.cuda else 0
+
+    def supports_bf16(self) -> bool:
+        return (not self.cuda) or torch.cuda.get_device_capability(self.device)[0] >= 8
+
+    def memory_stats(self) -> dict[str, float]:
+        if not self.cuda:
+            return {"allocated_gb": 0.0, "reserved_gb": 0.0, "total_gb": 0.0}
+        d = self.device
+        return {"allocated_gb": torch.cuda.memory_allocated(d) / 2 ** 30,
+                "reserved_gb": torch.cuda.memory_reserved(d) / 2 ** 30,
+                "total_gb": torch.cuda.get_device_properties(d).total_memory / 2 ** 30}
+
+    def synchronize(self) -> None:
+        if self.cuda:
+            torch.cuda.synchronize(self.device)
+
+    def empty_cache(self) -> None:
+        if self.cuda:
+            torch.cuda.empty_cache()
+
+
+@dataclass
+class HardwareTopology:
+    """GPUs of this node as seen by the runtime: count, name, memory, who can read whose memory directly."""
+    num_gpus: int = 0
+    gpu_name: str | None = None
+    memory_gb: float = 0.0
+    sm_count: int = 0
+    peer_access: tuple = ()
+    nvswitch: bool = False
+    numa: dict | None = None
+
+    @classmethod
+    def detect(cls) -> "HardwareTopology":
+        from .mesh import HardwareDetector
+        i = HardwareDetector.detect()
+        return cls(i["num_gpus"], i["name"], i["memory_gb"], i["sm_count"],
+                   tuple(tuple(r) for r in i["peer_access"]), i["nvswitch"], i["numa"])
+
+    @property
+    def fully_connected(self) -> bool:
+        return self.num_gpus > 1 and all(all(r) for r in self.peer_access)
+
+    def recommended_bucket_mb(self) -> int:
+        from .ddp import BUCKET_MB, detect_gpu_topology
+        return BUCKET_MB[detect_gpu_topology()][0]
+
+
+class DistributedLogger:
+    """Rank-aware logging: by default only rank 0 emits; `all_ranks=True` prefixes every line with the rank."""
+
+    def __init__(self, name: str = "trainscale_b200", all_ranks: bool = False, level: int = logging.INFO):
+        self._log = logging.getLogger(name)
+        self._log.setLevel(level)
+        self.all_ranks = all_ranks
+
+    @staticmethod
+    def _rank() -> int:
+        return dist.get_rank() if dist.is_available() and dist.is_initialized() else int(os.environ.get("RANK", "0"))
+
+    def _emit(self, level: int, msg: str, *a) -> None:
+        r = self._rank()
+        if self.all_ranks:
+            self._log.log(level, f"[rank {r}] {msg}", *a)
+        elif r == 0:
+            self._log.log(level, msg, *a)
+
+    def info(self, msg: str, *a) -> None:
+        self._emit(logging.INFO, msg, *a)
+
+    def warning(self, msg: str, *a) -> None:
+        self._emit(logging.WARNING, msg, *a)
+
+    def error(self, msg: str, *a) -> None:          # errors are never silenced
+        self._log.error(f"[rank {self._rank()}] {msg}", *a)
+
+    def debug(self, msg: str, *a) -> None:
+        self._emit(logging.DEBUG, msg, *a)
+
+
+_GROUPS: dict[str, object] = {}
+
+
+def setup_distributed(backend: str | None = None, timeout_s: int = 1800) -> DistributedState:
+    """Rendezvous from the launcher's environment (no-op for a single process); selects this rank's GPU."""
+    return DistributedState.initialize(backend, timeout_s)
+
+
+def register_process_group(name: str, group) -> None:
+    _GROUPS[name] = group
+
+
+def get_process_group(name: str = "world"):
+    """Named groups registered by the mesh / parallel engines ("world" is the default group)."""
+    if name == "world":
+        return dist.group.WORLD if dist.is_available() and dist.is_initialized() else None
+    return _GROUPS.get(name)
+
+
+def sync_gradients(model, group=None, average: bool = True, bucket_mb: float = 25.0) -> None:
+    """One-shot bucketed all-reduce of a plain model's `.grad`s (for code that does not use an engine)."""
+    if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size(group) == 1:
+        return
+    from .dist_kernels import DistributedConfig, DistributedKernels
+    grads = [p.grad for p in model.parameters() if p.grad is not None]
+    DistributedKernels(DistributedConfig(bucket_size_mb=bucket_mb)).all_reduce_fused(grads, group=group, average=average)
+
+
+def prepare_model_for_distributed(model, strategy: str = "ddp", device=None, **engine_kwargs):
+    """Moves the model to this rank's device and builds the engine for `strategy` (ddp | fsdp | zero2 | zero3 |
+    single).  Returns (model, engine); the engine is None for `single`."""
+    dev = torch.device(device) if device is not None else DeviceManager().set_device()
+    model.to(dev)
+    s = strategy.lower()
+    if s in ("single", "none"):
+        return model, None
+    from .flat_engine import EngineConfig, FlatShardedEngine
+    shard = {"ddp": "NO_SHARD", "fsdp": "FULL_SHARD", "fsdp2": "FULL_SHARD", "zero3": "FULL_SHARD",
+             "zero2": "SHARD_GRAD_OP", "shard_grad_op": "SHARD_GRAD_OP"}.get(s)
+    if shard is None:
+        raise ValueError(f"unknown strategy {strategy!r}")
+    group = engine_kwargs.pop("process_group", None)
+    eng = FlatShardedEngine(model, EngineConfig(sharding_strategy=shard, **engine_kwargs), process_group=group,
+                            device=dev)
+    return model, eng
+
+
+def save_checkpoint_distributed(path, model, engine=None, extra: dict | None = None) -> None:
+    """Collective: rank 0 writes the full weights (+ `extra`), every rank writes its optimizer shard."""
+    from ..ckpt import _to_cpu, atomic_torch_save
+    from pathlib import Path
+    path = Path(path)
+    on = dist.is_available() and dist.is_initialized()
+    rank, world = (dist.get_rank(), dist.get_world_size()) if on else (0, 1)
+    sd = engine.full_model_state_dict() if engine is not None and hasattr(engine, "full_model_state_dict") \
+        else model.state_dict()
+    if rank == 0:
+        atomic_torch_save({"model": _to_cpu(sd), "extra": extra or {}}, path / "model.pt")
+    if engine is not None and hasattr(engine, "state_dict"):
+        atomic_torch_save(_to_cpu(engine.state_dict()), path / "optim" / f"shard-{rank:05d}-of-{world:05d}.pt")
+    if on:
+        dist.barrier()
+
+
+def load_checkpoint_distributed(path, model, engine=None, strict: bool = True) -> dict:
+    """Inverse of `save_checkpoint_distributed`; optimizer shards saved at another world size are re-sliced."""
+    from ..ckpt import reshard_optimizer_state
+    from pathlib import Path
+    path = Path(path)
+    blob = torch.load(path / "model.pt", map_location="cpu", weights_only=False)
+    summon = engine.summon_full_params() if engine is not None and hasattr(engine, "summon_full_params") \
+        else contextlib.nullcontext()
+    with summon:
+        own = dict(model.named_parameters())
+        missing = [k for k in own if k not in blob["model"]]
+        if strict and missing:
+            raise KeyError(f"missing parameters in checkpoint: {missing[:6]}")
+        with torch.no_grad():
+            for k, v in blob["model"].items():
+                if k in own:
+                    own[k].copy_(v)
+        if engine is not None and hasattr(engine, "units"):
+            for u in engine.units:
+                src = u.flat_param[u.shard_start:u.shard_start + u.shard_numel]
+                if getattr(u, "resharded", False):
+                    u.param_shard.copy_(src)
+                u.master.copy_(src)
+    if engine is not None and (path / "optim").exists():
+        files = sorted((path / "optim").glob("shard-*.pt"))
+        mine = path / "optim" / f"shard-{engine.rank:05d}-of-{engine.world:05d}.pt"
+        if mine.exists():
+            engine.load_state_dict(torch.load(mine, map_location="cpu", weights_only=False))
+        elif files:
+            shards = [torch.load(f, map_location="cpu", weights_only=False) for f in files]
+            engine.load_state_dict(reshard_optimizer_state(shards, engine.rank, engine.world))
+    return blob.get("extra", {})

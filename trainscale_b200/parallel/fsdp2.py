@@ -559,7 +559,7 @@ class SOTAFSDP2:
         from .activation import ActivationCheckpoint, ActivationCheckpointConfig, CheckpointMode
         mode = {"full": CheckpointMode.FULL, "selective": CheckpointMode.SELECTIVE,
                 "offload": CheckpointMode.OFFLOAD}[c.ac_mode]
-        ActivationCheckpoint(ActivationCheckpointConfig(mode=mode, selective_frequency=c.ac_frequency)).apply(model)
+        ActivationCheckpoint(ActivationCheckpointConfig(mode=mode, frequency=c.ac_frequency)).apply(model)
 
     def wrap_model(self, model: nn.Module, device_mesh: Any = None) -> nn.Module:
         """Move the model to this rank's device, apply activation recomputation, then build the flat buffers and the

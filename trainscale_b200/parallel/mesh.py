@@ -159,6 +159,78 @@ class ParallelDims:
         return " x ".join(f"{d}={self.sizes[d]}" for d in DIM_ORDER) + f" | rank {self.rank} at {self.coords}"
 
 
+class MeshView:
+    """One named view of the mesh: ordered dimension names (outer first), their sizes, this rank's coordinates and
+    the process group along every dimension of the view."""
+
+    def __init__(self, name: str, dims: "ParallelDims", axes: Sequence[str]):
+        self.name, self.axes = name, tuple(axes)
+        self.shape = tuple(dims.size(a) for a in axes)
+        self.coords = tuple(dims.local_rank(a) for a in axes)
+        self._dims = dims
+
+    def get_group(self, axis: str):
+        if axis not in self.axes:
+            raise KeyError(f"mesh {self.name!r} has no dimension {axis!r} (has {self.axes})")
+        return self._dims.group(axis)
+
+    def size(self, axis: str | None = None) -> int:
+        if axis is None:
+            n = 1
+            for s in self.shape:
+                n *= s
+            return n
+        return self.shape[self.axes.index(axis)]
+
+    def __repr__(self) -> str:
+        return f"MeshView({self.name}: " + " x ".join(f"{a}={s}" for a, s in zip(self.axes, self.shape)) + ")"
+
+
+def build_mesh(dims: "ParallelDims") -> dict[str, MeshView]:
+    """The four views that the layers of a training job index (parallel_dims.py:1225-1317 builds the same set):
+      dataloading [pp, batch, cp, tp]              which ranks read the same samples
+      loss        [loss]                           ranks whose losses are averaged (dp_replicate * dp_shard * cp)
+      dense       [pp, dp_replicate, fsdp, tp]     sharding of dense weights (fsdp = dp_shard * cp)
+      sparse      [pp, dp_replicate, fsdp, tp]     expert weights; ep / etp are sub-divisions of fsdp x tp and get their
+                                                   groups from `ParallelDims.group("ep")` when ep > 1"""
+    return {"dataloading": MeshView("dataloading", dims, ("pp", "batch", "cp", "tp")),
+            "loss": MeshView("loss", dims, ("loss",)),
+            "dense": MeshView("dense", dims, ("pp", "dp_replicate", "fsdp", "tp")),
+            "sparse": MeshView("sparse", dims, ("pp", "dp_replicate", "fsdp", "tp"))}
+
+
+class MeshCache:
+    """Process groups are expensive to create and must be created by all ranks in the same order: one ParallelDims
+    (with its lazily created groups and views) per distinct configuration, shared by every engine of the process."""
+
+    _cache: dict[tuple, "ParallelDims"] = {}
+    _views: dict[tuple, dict[str, MeshView]] = {}
+
+    @staticmethod
+    def _key(cfg: ParallelDimsConfig) -> tuple:
+        c = cfg.resolve()
+        return (c.pp, c.dp_replicate, c.dp_shard, c.cp, c.tp, c.ep, c.etp, c.world_size)
+
+    @classmethod
+    def get(cls, cfg: ParallelDimsConfig, rank: int | None = None) -> "ParallelDims":
+        k = cls._key(cfg) + (rank,)
+        if k not in cls._cache:
+            cls._cache[k] = ParallelDims(cfg, rank)
+        return cls._cache[k]
+
+    @classmethod
+    def views(cls, cfg: ParallelDimsConfig, rank: int | None = None) -> dict[str, MeshView]:
+        k = cls._key(cfg) + (rank,)
+        if k not in cls._views:
+            cls._views[k] = build_mesh(cls.get(cfg, rank))
+        return cls._views[k]
+
+    @classmethod
+    def clear(cls) -> None:
+        cls._cache.clear()
+        cls._views.clear()
+
+
 def create_parallel_dims_from_config(dist_cfg, world_size: int | None = None, rank: int | None = None) -> ParallelDims:
     """From a SOTAConfig `distributed` section (its `parallel` sub-section and the legacy degree keys)."""
     p = dist_cfg.parallel

@@ -13,6 +13,7 @@ from enum import Enum
 from typing import Any, Callable, Iterable
 
 import torch
+import torch.nn as nn
 
 
 class Capability(str, Enum):
@@ -291,3 +292,123 @@ class KernelPatcher:
 
 def patch_model(model, **kw):
     return KernelPatcher().patch(model, **kw)
+
+
+# ------------------------------------------------------------------------------------------------ module-level patchers
+# For models that are NOT converted to the framework decoder (other architectures, custom heads): swap the forward of
+# recognisable sub-modules for the framework ops.  Weights and state-dict keys stay as they are.  Each patcher returns
+# the number of modules it changed (data_pipeline/trainer/registry/__init__.py:1033-1300 has the same entry points).
+def _is_rmsnorm(m: nn.Module) -> bool:
+    return type(m).__name__.endswith("RMSNorm") and hasattr(m, "weight") and m.weight is not None and m.weight.dim() == 1
+
+
+def auto_patch_layernorm(model: nn.Module) -> int:
+    """`nn.LayerNorm` and `*RMSNorm` modules -> `ops.norm.layernorm` / `ops.norm.rmsnorm` (sm_100a kernels for bf16 CUDA
+    rows, PyTorch maths otherwise)."""
+    import types
+    from ..ops import norm as N
+    n = 0
+    for m in model.modules():
+        if getattr(m, "_ts_patched", False):
+            continue
+        if isinstance(m, nn.LayerNorm) and len(m.normalized_shape) == 1 and m.weight is not None:
+            m.forward = types.MethodType(lambda self, x: N.layernorm(x, self.weight, self.bias, self.eps), m)
+        elif _is_rmsnorm(m):
+            eps = float(getattr(m, "variance_epsilon", getattr(m, "eps", 1e-6)) or 1e-6)
+            off = 1.0 if "Gemma" in type(m).__name__ else 0.0       # Gemma stores w - 1
+            m.forward = types.MethodType(
+                lambda self, x, _e=eps, _o=off: N.rmsnorm(x, self.weight, _e, None, _o)[0], m)
+        else:
+            continue
+        m._ts_patched = True
+        n += 1
+    return n
+
+
+def auto_patch_mlp(model: nn.Module) -> int:
+    """Gated MLPs (`gate_proj` / `up_proj` / `down_proj` without biases, SiLU or GELU gate) -> framework GEMMs and the
+    fused gate * up kernel."""
+    import types
+    from ..ops import activation as A
+    from ..ops import gemm as G
+    n = 0
+    for m in model.modules():
+        if getattr(m, "_ts_patched", False):
+            continue
+        g, u, d = (getattr(m, k, None) for k in ("gate_proj", "up_proj", "down_proj"))
+        if not all(isinstance(t, nn.Linear) and t.bias is None for t in (g, u, d)):
+            continue
+        act_name = type(getattr(m, "act_fn", nn.SiLU())).__name__.lower()
+        kind = "silu" if "silu" in act_name or "swish" in act_name else "gelu_tanh" if "gelu" in act_name else None
+        if kind is None:
+            continue
+
+        def fwd(self, x, _k=kind):
+            gu = torch.cat((G.linear(x, self.gate_proj.weight), G.linear(x, self.up_proj.weight)), dim=-1)
+            return G.linear(A.glu(gu, _k), self.down_proj.weight)
+        m.forward = types.MethodType(fwd, m)
+        m._ts_patched = True
+        n += 1
+    return n
+
+
+def auto_patch_rope(model: nn.Module) -> int:
+    """Replaces `apply_rotary_pos_emb` in the Python module that defines the model's attention class with a version on
+    the framework rotary kernel (rotate-half layout, cos / sin of shape [B, S, D] as transformers passes them).
+    Returns the number of patched modules (0 when the model's source has no such function)."""
+    import sys
+    from ..ops import rope as R
+    seen, n = set(), 0
+    for m in model.modules():
+        mod = sys.modules.get(type(m).__module__)
+        if mod is None or mod.__name__ in seen or not hasattr(mod, "apply_rotary_pos_emb"):
+            continue
+        seen.add(mod.__name__)
+        if getattr(mod.apply_rotary_pos_emb, "_ts_patched", False):
+            continue
+        orig = mod.apply_rotary_pos_emb
+
+        def patched(q, k, cos, sin, position_ids=None, unsqueeze_dim=1, _orig=orig):
+            # q, k: [B, H, S, D]; tables [B, S, D] with the two halves equal
+            ok = q.dim() == 4 and cos.dim() == 3 and unsqueeze_dim == 1 and cos.shape[0] == 1 and q.is_cuda \
+                and q.dtype == torch.bfloat16
+            if not ok:
+                return _orig(q, k, cos, sin, position_ids, unsqueeze_dim) if position_ids is not None \
+                    else _orig(q, k, cos, sin, unsqueeze_dim=unsqueeze_dim)
+            D = q.shape[-1]
+            c, s = cos[0, :, : D // 2].float().contiguous(), sin[0, :, : D // 2].float().contiguous()
+            qo = R.apply_rope(q.transpose(1, 2).contiguous(), c, s).transpose(1, 2)
+            ko = R.apply_rope(k.transpose(1, 2).contiguous(), c, s).transpose(1, 2)
+            return qo, ko
+        patched._ts_patched = True
+        mod.apply_rotary_pos_emb = patched
+        n += 1
+    return n
+
+
+def auto_patch_fp8_linear(model: nn.Module, min_features: int = 1024, skip: tuple[str, ...] = ("lm_head",)) -> int:
+    """Bias-free `nn.Linear` layers with both dimensions >= `min_features` and divisible by 128 -> block-scaled fp8
+    GEMM (bf16 CUDA inputs; other inputs take the original path)."""
+    import types
+    from ..ops import fp8 as F8
+    n = 0
+    for name, m in model.named_modules():
+        if not isinstance(m, nn.Linear) or m.bias is not None or getattr(m, "_ts_patched", False):
+            continue
+        if any(s in name for s in skip) or min(m.in_features, m.out_features) < min_features or \
+                m.in_features % 128 or m.out_features % 128:
+            continue
+
+        def fwd(self, x):
+            if F8.available(x) and self.weight.dtype == torch.bfloat16:
+                return F8.fp8_linear(x, self.weight)
+            return nn.functional.linear(x, self.weight)
+        m.forward = types.MethodType(fwd, m)
+        m._ts_patched = True
+        n += 1
+    return n
+
+
+def auto_patch(model: nn.Module, layernorm: bool = True, mlp: bool = True, rope: bool = True, fp8: bool = False) -> dict:
+    return {"layernorm": auto_patch_layernorm(model) if layernorm else 0, "mlp": auto_patch_mlp(model) if mlp else 0,
+            "rope": auto_patch_rope(model) if rope else 0, "fp8_linear": auto_patch_fp8_linear(model) if fp8 else 0}

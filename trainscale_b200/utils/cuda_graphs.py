@@ -103,3 +103,82 @@ class ModelCompiler:
 
     def for_training(self, model, checkpoint_every: int = 2):
         return optimize_for_training(model, checkpoint_every)
+
+
+class InductorConfigManager:
+    """The reference tunes TorchInductor through this class (data_pipeline/trainer/kernels/compiler.py:190-288:
+    max-autotune, coordinate descent, epilogue fusion, CUDA-graph trees).  This framework has no tracing compiler on
+    its hot path, so the manager keeps the same interface but only (a) records the requested options, (b) maps the one
+    option that has a counterpart here - CUDA-graph capture - onto `CompilationConfig`, and (c) can apply the options
+    to `torch._inductor.config` for USER code that calls `torch.compile` on modules outside the framework
+    (`apply_to_torch=True`; restored by `restore()` / on leaving the `with` block)."""
+
+    KNOWN = ("max_autotune", "max_autotune_gemm", "coordinate_descent_tuning", "epilogue_fusion", "triton.cudagraphs",
+             "triton.cudagraph_trees", "shape_padding", "fx_graph_cache")
+
+    def __init__(self, apply_to_torch: bool = False, **options):
+        self.apply_to_torch = apply_to_torch
+        self.options: dict[str, object] = {}
+        self._saved: dict[str, object] = {}
+        self.configure(**options)
+
+    def configure(self, **options) -> "InductorConfigManager":
+        for k, v in options.items():
+            self.options[k.replace("__", ".")] = v
+        return self
+
+    def for_mode(self, mode: str) -> "InductorConfigManager":
+        """default | reduce-overhead | max-autotune, as in `torch.compile(mode=...)`."""
+        presets = {"default": {}, "reduce-overhead": {"triton.cudagraphs": True},
+                   "max-autotune": {"max_autotune": True, "coordinate_descent_tuning": True, "triton.cudagraphs": True}}
+        if mode not in presets:
+            raise ValueError(f"unknown mode {mode!r}")
+        self.options.update(presets[mode])
+        return self
+
+    def compilation_config(self) -> CompilationConfig:
+        graphs = bool(self.options.get("triton.cudagraphs") or self.options.get("triton.cudagraph_trees"))
+        return CompilationConfig(mode="cuda_graphs" if graphs else "none")
+
+    def _target(self):
+        try:
+            import torch._inductor.config as cfg
+            return cfg
+        except Exception:
+            return None
+
+    def apply(self) -> dict[str, object]:
+        """Returns the options that were actually set on torch's inductor config (empty unless apply_to_torch)."""
+        done: dict[str, object] = {}
+        cfg = self._target() if self.apply_to_torch else None
+        if cfg is None:
+            return done
+        for k, v in self.options.items():
+            obj, name = cfg, k
+            if "." in k:
+                head, name = k.split(".", 1)
+                obj = getattr(cfg, head, None)
+            if obj is not None and hasattr(obj, name):
+                self._saved.setdefault(k, getattr(obj, name))
+                setattr(obj, name, v)
+                done[k] = v
+        return done
+
+    def restore(self) -> None:
+        cfg = self._target()
+        if cfg is None:
+            return
+        for k, v in self._saved.items():
+            obj, name = cfg, k
+            if "." in k:
+                head, name = k.split(".", 1)
+                obj = getattr(cfg, head)
+            setattr(obj, name, v)
+        self._saved.clear()
+
+    def __enter__(self):
+        self.apply()
+        return self
+
+    def __exit__(self, *exc):
+        self.restore()
