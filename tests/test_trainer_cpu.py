@@ -95,3 +95,17 @@ def test_op_selective_recompute_matches_plain_path_on_cpu():
     assert abs(l0.item() - l1.item()) < 1e-6
     for n, p in m.named_parameters():
         assert torch.allclose(p.grad, g0[n], atol=1e-6), n
+
+
+def test_numerical_stability_check_counts_bad_windows():
+    from trainscale_b200.core.errors import GradientOverflowError
+    from trainscale_b200.trainer.sota_trainer import SOTATrainer
+    t = SOTATrainer.__new__(SOTATrainer)
+    assert t._check_numerical_stability(1.0, 2.0, 3) is True
+    assert t._check_numerical_stability(float("nan"), 2.0, 4) is False
+    assert t._check_numerical_stability(1.0, 1e7, 5) is True and t._bad_windows == 0      # exploding only warns
+    t.max_nonfinite_windows = 2
+    assert t._check_numerical_stability(1.0, float("inf")) is False
+    import pytest
+    with pytest.raises(GradientOverflowError):
+        t._check_numerical_stability(float("inf"))

@@ -456,6 +456,7 @@ class SOTATrainer:
             dist.all_reduce(vals)
             vals /= self.world_size
         loss, gn = (float(x) for x in vals.tolist())     # the only host sync of the loop
+        self._check_numerical_stability(loss, gn, self.state.global_step)
         self.ema_loss = loss if self.ema_loss is None else 0.99 * self.ema_loss + 0.01 * loss
         self.state.total_loss += loss * max(1, window_steps)
         lr = self.optimizer.param_groups[0]["lr"]
@@ -473,6 +474,32 @@ class SOTATrainer:
         self._ctx.logs = {**rec, "line": line}
         self.callbacks.fire("on_log", self._ctx)
         return rec
+
+    def _check_numerical_stability(self, loss: float | torch.Tensor, grad_norm: float | None = None,
+                                   step: int | None = None) -> bool:
+        """NaN / Inf loss or gradient norm -> False (and a warning); a finite norm above 1e6 only warns.  Called with
+        values that are on the host already (log time).  The update of a step whose gradients are non-finite has been
+        skipped on the device by the engine (`EngineConfig.skip_nonfinite`), with no host round trip; this check is
+        the visible trace of that, and after `max_nonfinite_windows` consecutive bad log windows training stops with
+        GradientOverflowError instead of burning the rest of the budget."""
+        from ..core.errors import GradientOverflowError
+        lv = float(loss) if not isinstance(loss, float) else loss
+        where = f" at step {step}" if step is not None else ""
+        ok = True
+        if not math.isfinite(lv):
+            logger.warning("non-finite loss%s: %s", where, lv)
+            ok = False
+        if grad_norm is not None:
+            if not math.isfinite(grad_norm):
+                logger.warning("non-finite gradient norm%s", where)
+                ok = False
+            elif grad_norm > 1e6:
+                logger.warning("exploding gradient norm%s: %.2e", where, grad_norm)
+        self._bad_windows = 0 if ok else getattr(self, "_bad_windows", 0) + 1
+        limit = getattr(self, "max_nonfinite_windows", 5)
+        if self._bad_windows >= limit:
+            raise GradientOverflowError(f"{self._bad_windows} consecutive log windows with non-finite loss or gradients")
+        return ok
 
     # ------------------------------------------------------------------ evaluation
     def _run_eval(self, dl, compute_metrics=None):
