@@ -31,8 +31,29 @@ def main():
     do = torch.randn(1, S, Hq, D, generator=g).to(dev, dtype)
     bal = CP.HeadTailBalancer(world, rank)
     ql, kl, vl, dol = [bal.shard(t).clone().requires_grad_(t is not do) for t in (q, k, v, do)]
-    out = CP.ring_attention(ql, kl, vl, dist.group.WORLD)
+    comm = sys.argv[sys.argv.index("--comm") + 1] if "--comm" in sys.argv else None
+    out = CP.ring_attention(ql, kl, vl, dist.group.WORLD, comm=comm)
     out.backward(dol)
+    if cuda:
+        used = type(out.grad_fn).__name__
+        # device time of forward+backward, max over ranks (second and third call: buffers and heap exist by then)
+        ms = 0.0
+        for _ in range(3):
+            q2, k2, v2 = (t.detach().clone().requires_grad_(True) for t in (ql, kl, vl))
+            dist.barrier()
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            CP.ring_attention(q2, k2, v2, dist.group.WORLD, comm=comm).backward(dol)
+            b.record()
+            torch.cuda.synchronize()
+            ms = a.elapsed_time(b)
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        if rank == 0:
+            print(f"TIMING comm={comm} path={used} fwd+bwd {t.item():.3f} ms (S={S}, cp={world})", flush=True)
+        from trainscale_b200.ops import _lib
+        _lib.raise_on_any_device_error()
     qr, kr, vr = [t.float().clone().requires_grad_(True) for t in (q, k, v)]
     ref = attention_reference(qr, kr, vr, True)
     ref.backward(do.float())

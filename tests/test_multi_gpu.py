@@ -54,3 +54,13 @@ def test_weight_gather_gemm_on_two_gpus():
     """The parameter all-gather of a ZeRO-3 forward inside the GEMM kernel equals the product with the full weight."""
     out = _launch("weight_gather_gemm.py", port=29742)
     assert "RESULT weight_gather ok=True" in out
+
+
+@pytest.mark.parametrize("comm,port", [("nccl", 29741), ("peer", 29742)])
+def test_context_parallel_attention_on_two_gpus(comm, port):
+    """Causal attention over a sequence sharded on two GPUs == full attention; K/V and dK/dV travel by NCCL send/recv
+    or through the framework's peer-memory kernels (pull all-gather, reduce-scatter)."""
+    out = _launch("cp_equivalence.py", "--cuda", "--comm", comm, port=port)
+    assert out.count("ok=True") == 2
+    assert ("path=_PeerAttention" in out) == (comm == "peer")
+    print(out[out.index("TIMING"):].splitlines()[0])

@@ -359,3 +359,41 @@ def test_fused_cross_entropy_loss_module_forward_backward(rows, V, smoothing):
     assert abs(float(loss) - float(ref)) < 2e-3 * max(1.0, abs(float(ref)))
     torch.testing.assert_close(logits.grad.float(), ref_in.grad, rtol=2e-2, atol=2e-5)
     assert float(logits.grad[::7].abs().max()) == 0.0
+
+
+@pytest.mark.gpu
+def test_lora_linear_with_epilogue_accumulation():
+    """Base projection + adapters accumulated by the GEMM epilogue into column blocks of the fused output, against the
+    two-step path (separate delta tensor) and an fp32 reference; gradients of x, A and B."""
+    from trainscale_b200.lora import FusedLoRA, LoRALinear
+    from trainscale_b200.ops import gemm
+    torch.manual_seed(0)
+    T, K, N1, N2, r = 512, 1024, 1024, 256, 16
+    dev, dt = "cuda", torch.bfloat16
+    x = torch.randn(T, K, device=dev, dtype=dt).requires_grad_(True)
+    w = (torch.randn(N1 + N2, K, device=dev) / K ** 0.5).to(dt)
+    parts = [LoRALinear(K, N1, r, row0=0, total_rows=N1 + N2, dtype=dt, device=dev),
+             LoRALinear(K, N2, r, row0=N1, total_rows=N1 + N2, dtype=dt, device=dev)]
+    for p in parts:
+        torch.nn.init.normal_(p.lora_B, std=0.05)
+    mod = FusedLoRA(parts)
+    dy = torch.randn(T, N1 + N2, device=dev, dtype=dt)
+    y = mod.linear(x, w)
+    y.backward(dy)
+    got = [x.grad.clone()] + [p.grad.clone() for p in mod.parameters()]
+    x.grad = None
+    mod.zero_grad()
+    # fp32 reference
+    xf = x.detach().float().requires_grad_(True)
+    ps = [(p.lora_A.detach().float().requires_grad_(True), p.lora_B.detach().float().requires_grad_(True), p) for p in parts]
+    yf = xf @ w.float().t()
+    yf = yf + torch.cat([(xf @ A.t()) @ B.t() * p.scaling for A, B, p in ps], dim=1)
+    yf.backward(dy.float())
+    torch.testing.assert_close(y.float(), yf, rtol=2e-2, atol=2e-2)
+    want = [xf.grad] + [t.grad for A, B, _ in ps for t in (A, B)]
+    for g, wv in zip(got, want):
+        err = float((g.float() - wv).abs().max()) / max(1e-6, float(wv.abs().max()))
+        assert err < 3e-2, err
+    # two-step path gives the same output up to bf16 rounding of the intermediate delta
+    y2 = gemm.linear(x, w) + mod(x)
+    torch.testing.assert_close(y.float(), y2.float(), rtol=2e-2, atol=3e-2)

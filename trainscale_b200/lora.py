@@ -49,6 +49,15 @@ class FusedLoRA(nn.Module):
         super().__init__()
         self.parts = nn.ModuleList(parts)
 
+    def linear(self, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+        """Base projection and all adapters in one autograd node (adapter products accumulated in the GEMM epilogue).
+        Adapter dropout needs its own input, so that case takes the two-step path."""
+        if any(p.dropout is not None and self.training for p in self.parts) or any(p.row0 % 8 for p in self.parts):
+            return gemm.linear(x, w) + self.forward(x)
+        meta = tuple((float(p.scaling), int(p.row0), int(p.rows)) for p in self.parts)
+        ab = [t for p in self.parts for t in (p.lora_A, p.lora_B)]
+        return _LoRALinearFn.apply(x, w, meta, *ab)
+
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         total = self.parts[0].total_rows
         if len(self.parts) == 1 and self.parts[0].rows == total:
@@ -57,6 +66,51 @@ class FusedLoRA(nn.Module):
         for p in self.parts:
             out[..., p.row0:p.row0 + p.rows] = p.delta(x)
         return out
+
+
+class _LoRALinearFn(torch.autograd.Function):
+    """y = x W^T + sum_i s_i (x A_i^T) B_i^T written into the column block of adapter i, with the adapter products
+    accumulated by the GEMM epilogue (alpha / accumulate) straight into y - no delta tensor, no separate add pass.
+    Backward mirrors it: dx = dy W + sum_i s_i (dy_i B_i) A_i (accumulating GEMMs), dA_i = s_i (dy_i B_i)^T x,
+    dB_i = s_i dy_i^T (x A_i^T).  Covers what the reference does with its fused LoRA kernels
+    (data_pipeline/trainer/kernels/lora_kernels.py: forward, dA / dB / dx backward)."""
+
+    @staticmethod
+    def forward(ctx, x, w, meta, *ab):
+        K = x.shape[-1]
+        x2 = x.reshape(-1, K)
+        y = gemm.matmul_nt(x2, w)
+        ts = []
+        for i, (s, row0, rows) in enumerate(meta):
+            A, B = ab[2 * i], ab[2 * i + 1]
+            t = gemm.matmul_nt(x2, A)
+            gemm.matmul_nt(t, B, out=y[:, row0:row0 + rows], accumulate=True, alpha=s)
+            ts.append(t)
+        ctx.save_for_backward(x2, w, *ab, *ts)
+        ctx.meta, ctx.shape = meta, x.shape
+        return y.view(*x.shape[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        n = len(ctx.meta)
+        saved = ctx.saved_tensors
+        x2, w, ab, ts = saved[0], saved[1], saved[2:2 + 2 * n], saved[2 + 2 * n:]
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        if dy2.stride(-1) != 1:
+            dy2 = dy2.contiguous()
+        need_x, need_w = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
+        dx = gemm.matmul_nn(dy2, w) if need_x else None
+        dw = gemm.matmul_tn(dy2, x2, out_dtype=torch.float32).to(w.dtype) if need_w else None
+        grads = []
+        for i, (s, row0, rows) in enumerate(ctx.meta):
+            A, B = ab[2 * i], ab[2 * i + 1]
+            dyi = dy2[:, row0:row0 + rows]
+            g = gemm.matmul_nn(dyi, B)                                   # [T, r]
+            if need_x:
+                gemm.matmul_nn(g, A, out=dx, accumulate=True, alpha=s)
+            grads.append(gemm.matmul_tn(g, x2, alpha=s).to(A.dtype) if ctx.needs_input_grad[3 + 2 * i] else None)
+            grads.append(gemm.matmul_tn(dyi, ts[i], alpha=s).to(B.dtype) if ctx.needs_input_grad[4 + 2 * i] else None)
+        return (dx.view(ctx.shape) if need_x else None, dw, None, *grads)
 
 
 def _targets_for(model_cfg) -> dict:

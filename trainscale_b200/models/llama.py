@@ -107,13 +107,16 @@ def _lin(mod, x, name: str):
     """x @ W^T plus the low-rank adapter of that weight when one is attached.  With `mod.fp8` the product runs on the
     block-scaled fp8 tensor-core kernel (forward and dgrad; wgrad and the master weights stay bf16 / fp32)."""
     w = getattr(mod, name)
+    has_lora = mod.lora is not None and name in mod.lora
+    if has_lora and not getattr(mod, "fp8", False) and hasattr(mod.lora[name], "linear"):
+        return mod.lora[name].linear(x, w)
     if getattr(mod, "fp8", False) and x.is_cuda and x.dtype == torch.bfloat16 and x.shape[-1] % 128 == 0 \
             and w.shape[0] % 8 == 0:
         from ..ops import fp8 as fp8_ops
         y = fp8_ops.fp8_linear(x, w)
     else:
         y = gemm.linear(x, w)
-    if mod.lora is not None and name in mod.lora:
+    if has_lora:
         y = y + mod.lora[name](x)
     return y
 

@@ -74,7 +74,7 @@ class _FocalLossFn(torch.autograd.Function):
         one_m = (1 - p).clamp(min=0)
         dce = one_m ** g + (g * p * one_m ** (g - 1) * ce if g != 0 else 0.0)
         scale = torch.where(valid, dce * dfocal.float(), torch.zeros_like(ce)).contiguous()
-        grad = lg.clone()
+        grad = _clone_keep_pitch(lg)
         loss = torch.empty_like(ce)
         lse = torch.empty_like(ce)
         _ce_rows(grad, labels, loss, lse, ctx.ignore_index, 0.0, 1.0, 0.0, None, 1.0, scale, True)
@@ -105,7 +105,7 @@ class FusedCrossEntropyFunction(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dloss):
         lg, labels = ctx.saved_tensors
-        grad = lg.clone()
+        grad = _clone_keep_pitch(lg)
         tmp_loss = torch.empty(lg.shape[0], dtype=torch.float32, device=lg.device)
         tmp_lse = torch.empty_like(tmp_loss)
         _ce_rows(grad, labels, tmp_loss, tmp_lse, ctx.ignore_index, ctx.label_smoothing, 1.0, 0.0, None, 1.0,
@@ -122,6 +122,14 @@ def cross_entropy_rows(logits: torch.Tensor, labels: torch.Tensor, ignore_index:
 def focal_loss_rows(logits: torch.Tensor, labels: torch.Tensor, gamma: float = 2.0, ignore_index: int = -100):
     """Per-row focal loss of bf16 CUDA logits [rows, V] on the cross-entropy kernel (rows with ignore_index give 0)."""
     return _FocalLossFn.apply(logits, labels, float(gamma), int(ignore_index))
+
+
+def _clone_keep_pitch(lg: torch.Tensor) -> torch.Tensor:
+    """Copy of a [rows, V] view with the SAME row pitch (a plain clone of a padded view packs the rows, and an odd V
+    then breaks the kernel's 16-byte row alignment)."""
+    out = torch.empty_strided(lg.shape, lg.stride(), dtype=lg.dtype, device=lg.device)
+    out.copy_(lg)
+    return out
 
 
 def _pad_ld(V: int) -> int:

@@ -223,6 +223,132 @@ class _RingExchange:
         return recv
 
 
+class _PeerKV:
+    """K/V exchange of context parallelism over NVLink peer memory instead of NCCL send/recv.
+
+    On an NVSwitch node every rank reaches every peer at full bandwidth, so there is no reason to pass K/V around a ring
+    hop by hop: each rank publishes its K/V chunk in a symmetric buffer and PULLS all other chunks with one kernel
+    (`csrc/comm.cu` pull all-gather, plain peer loads) on a side stream while the attention of its own chunk runs.
+    In backward every rank writes its partial dK/dV for all chunks into a symmetric fp32 buffer and the owners sum
+    their slot across ranks with the peer-memory reduce-scatter kernel.  Buffers are allocated once per
+    (group, size) - symmetric allocation is a collective - and reused by every layer; a device-side barrier before
+    each reuse keeps a fast rank from overwriting a slot that a slow rank is still reading."""
+
+    _heaps: dict = {}
+    _bufs: dict = {}
+
+    @classmethod
+    def get(cls, group, device, numel: int, dtype):
+        from .symm import SymmetricHeap
+        hk = (id(group), str(device))
+        if hk not in cls._heaps:
+            cls._heaps[hk] = SymmetricHeap.try_create(group, device)
+        heap = cls._heaps[hk]
+        if heap is None:
+            return None
+        bk = hk + (numel, dtype)
+        if bk not in cls._bufs:
+            cp = heap.world
+            cls._bufs[bk] = cls(heap, heap.alloc(cp * numel, dtype), heap.alloc(cp * numel, torch.float32), numel,
+                                torch.cuda.Stream(device=device))
+        return cls._bufs[bk]
+
+    def __init__(self, heap, kv_all, dkv_all, numel, stream):
+        self.heap, self.kv_all, self.dkv_all, self.numel, self.stream = heap, kv_all, dkv_all, numel, stream
+
+    def publish_and_gather(self, kv: torch.Tensor):
+        """Start pulling everybody's K/V; returns the [cp, ...] view that is complete after `wait()`."""
+        from . import fused_comm
+        heap, r, n = self.heap, self.heap.rank, self.numel
+        fused_comm.barrier(heap, self.kv_all)
+        self.kv_all[r * n:(r + 1) * n].copy_(kv.reshape(-1))
+        self.stream.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(self.stream):
+            fused_comm.all_gather_inplace(heap, self.kv_all, r * n, n)
+        return self.kv_all.view((heap.world,) + tuple(kv.shape))
+
+    def wait(self) -> None:
+        torch.cuda.current_stream().wait_stream(self.stream)
+
+    def grad_slots(self, shape) -> torch.Tensor:
+        """Zeroed [cp, *shape] fp32 partial-gradient slots (slot j = my contribution to rank j's dK/dV)."""
+        from . import fused_comm
+        fused_comm.barrier(self.heap, self.dkv_all)
+        self.dkv_all.zero_()
+        return self.dkv_all.view((self.heap.world,) + tuple(shape))
+
+    def reduce_grads(self, out: torch.Tensor) -> torch.Tensor:
+        """out (fp32, one slot) = sum over ranks of their slot for me."""
+        from . import fused_comm
+        fused_comm.reduce_scatter_fp32(self.heap, self.dkv_all, out.reshape(-1), self.heap.rank * self.numel, 1.0,
+                                       None, None)
+        return out
+
+
+def _use_peer(q: torch.Tensor, comm: str) -> bool:
+    return comm in ("auto", "peer", "fused") and q.is_cuda
+
+
+class _PeerAttention(torch.autograd.Function):
+    """Same maths as `_RingAttention`; K/V and dK/dV travel through `_PeerKV`."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, group, scale, pk):
+        cp, r = dist.get_world_size(group), dist.get_rank(group)
+        C = q.shape[0] // 2
+        kv = torch.stack((k, v)).contiguous()
+        kv_all = pk.publish_and_gather(kv)
+        o = [None, None]
+        lse = [None, None]
+        for step in range(cp):
+            j = (r - step) % cp
+            if step == 1:
+                pk.wait()                                   # the pull ran under the attention of the local chunk
+            cur = kv if step == 0 else kv_all[j]
+            for qs, ks, causal in _pairs_for_step(r, j, cp):
+                po, pl = _pair_forward(q[qs * C:(qs + 1) * C], cur[0, ks * C:(ks + 1) * C], cur[1, ks * C:(ks + 1) * C],
+                                       causal, scale)
+                if o[qs] is None:
+                    o[qs], lse[qs] = po.float(), pl
+                else:
+                    o[qs], lse[qs] = merge_partials(o[qs], lse[qs].transpose(0, 1), po, pl.transpose(0, 1))
+                    lse[qs] = lse[qs].transpose(0, 1)
+        if cp == 1:
+            pk.wait()
+        out = torch.cat((o[0], o[1])).to(q.dtype)
+        lse_all = torch.cat((lse[0], lse[1]), dim=1).contiguous()
+        ctx.save_for_backward(q, k, v, out, lse_all)
+        ctx.group, ctx.scale, ctx.pk = group, scale, pk
+        return out
+
+    @staticmethod
+    def backward(ctx, do):
+        q, k, v, out, lse_all = ctx.saved_tensors
+        group, scale, pk = ctx.group, ctx.scale, ctx.pk
+        cp, r = dist.get_world_size(group), dist.get_rank(group)
+        C = q.shape[0] // 2
+        kv = torch.stack((k, v)).contiguous()
+        kv_all = pk.publish_and_gather(kv)
+        slots = pk.grad_slots(kv.shape)                     # [cp, 2, 2C, Hkv, D] fp32
+        dq = torch.zeros(q.shape, dtype=torch.float32, device=q.device)
+        for step in range(cp):
+            j = (r - step) % cp
+            if step == 1:
+                pk.wait()
+            cur = kv if step == 0 else kv_all[j]
+            for qs, ks, causal in _pairs_for_step(r, j, cp):
+                sl_q, sl_k = slice(qs * C, (qs + 1) * C), slice(ks * C, (ks + 1) * C)
+                a, b, c = _pair_backward(q[sl_q], cur[0, sl_k], cur[1, sl_k], out[sl_q], lse_all[:, sl_q], do[sl_q],
+                                         causal, scale)
+                dq[sl_q] += a
+                slots[j, 0, sl_k] += b
+                slots[j, 1, sl_k] += c
+        if cp == 1:
+            pk.wait()
+        dkv = pk.reduce_grads(torch.empty(kv.shape, dtype=torch.float32, device=q.device))
+        return dq.to(q.dtype), dkv[0].to(k.dtype), dkv[1].to(v.dtype), None, None, None
+
+
 class _RingAttention(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, group, scale):
@@ -283,12 +409,25 @@ class _RingAttention(torch.autograd.Function):
         return dq.to(q.dtype), dkv[0].to(k.dtype), dkv[1].to(v.dtype), None, None
 
 
-def ring_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, group, scale: float | None = None) -> torch.Tensor:
+def ring_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, group, scale: float | None = None,
+                   comm: str | None = None) -> torch.Tensor:
     """Causal attention over a sequence sharded with the head-tail layout. q [B=1, S_local, Hq, D]; returns the same
-    shape. Local rows are (chunk rank | chunk 2cp-1-rank)."""
+    shape. Local rows are (chunk rank | chunk 2cp-1-rank).
+    `comm`: "nccl" = K/V passed around the ring with batched send/recv; "peer" = pulled over NVLink peer memory by the
+    framework's own kernels (`_PeerKV`); "auto" (default, or env TS_CP_COMM) = peer on CUDA when symmetric memory is
+    available, else nccl."""
+    import os
     B, S, Hq, D = q.shape
     assert B == 1, "ring attention handles one (packed) sequence per step"
     scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    comm = comm or os.environ.get("TS_CP_COMM", "auto")
+    if _use_peer(q, comm):
+        kv_numel = 2 * k[0].numel()
+        pk = _PeerKV.get(group, q.device, kv_numel, k.dtype) if (kv_numel * k.element_size()) % 16 == 0 else None
+        if pk is not None:
+            return _PeerAttention.apply(q[0], k[0], v[0], group, scale, pk).unsqueeze(0)
+        if comm == "peer":
+            raise RuntimeError("peer-memory context parallelism was requested but symmetric memory is unavailable")
     o = _RingAttention.apply(q[0], k[0], v[0], group, scale)
     return o.unsqueeze(0)
 
