@@ -62,5 +62,5 @@ def test_context_parallel_attention_on_two_gpus(comm, port):
     or through the framework's peer-memory kernels (pull all-gather, reduce-scatter)."""
     out = _launch("cp_equivalence.py", "--cuda", "--comm", comm, port=port)
     assert out.count("ok=True") == 2
-    assert ("path=_PeerAttention" in out) == (comm == "peer")
+    assert ("path=peer" in out) == (comm == "peer")
     print(out[out.index("TIMING"):].splitlines()[0])

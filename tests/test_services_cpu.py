@@ -234,3 +234,17 @@ def test_gradient_plumbing_helpers_single_process():
     assert mgr.reduce_dict({"loss": 2.0}) == {"loss": 2.0}
     sync = dist_utils.GradientSynchronizer(engine=object(), accumulation_steps=4)
     assert [sync.should_sync(i) for i in range(4)] == [False, False, False, True]
+
+
+def test_sophia_hutchinson_hessian_diagonal():
+    import torch
+    from trainscale_b200.optim import SophiaG
+    d = torch.tensor([1.0, 2.0, 3.0, 4.0])
+    x = torch.randn(4, requires_grad=True)
+    opt = SophiaG([x], betas=(0.9, 0.5))
+    opt.update_hessian_hutchinson(0.5 * (d * x * x).sum())          # diagonal Hessian: u * (H u) = d exactly
+    torch.testing.assert_close(opt.state[x]["h"], 0.5 * d)
+    x.grad = torch.ones(4)
+    before = x.detach().clone()
+    opt.step()
+    assert not torch.equal(before, x.detach())

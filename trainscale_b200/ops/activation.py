@@ -110,3 +110,31 @@ def act(x: torch.Tensor, name: str = "gelu") -> torch.Tensor:
 
 def gelu(x: torch.Tensor, approximate: str = "none") -> torch.Tensor:
     return act(x, "gelu_tanh" if approximate == "tanh" else "gelu")
+
+
+class _SoftmaxFn(torch.autograd.Function):
+    """Row softmax over the last dimension on the row kernel (bf16 CUDA rows whose pitch is a multiple of 8 elements);
+    backward dx = y * (dy - sum(dy * y))."""
+
+    @staticmethod
+    def forward(ctx, x):
+        V = x.shape[-1]
+        x2 = x.reshape(-1, V).contiguous()
+        y = torch.empty_like(x2)
+        lib = _lib.load("elementwise")
+        rc = lib.ts_softmax_rows(_lib.ptr(x2), _lib.ptr(y), ctypes.c_longlong(x2.shape[0]), V, _lib.stream_ptr())
+        _lib.check(rc, "ts_softmax_rows")
+        ctx.save_for_backward(y)
+        return y.view(x.shape)
+
+    @staticmethod
+    def backward(ctx, dy):
+        (y,) = ctx.saved_tensors
+        yf, df = y.float(), dy.reshape(y.shape).float()
+        return (yf * (df - (df * yf).sum(-1, keepdim=True))).to(dy.dtype).view(dy.shape)
+
+
+def softmax(x: torch.Tensor, dim: int = -1) -> torch.Tensor:
+    if x.is_cuda and x.dtype == torch.bfloat16 and dim in (-1, x.dim() - 1) and x.shape[-1] % 8 == 0:
+        return _SoftmaxFn.apply(x)
+    return torch.softmax(x.float(), dim).to(x.dtype)

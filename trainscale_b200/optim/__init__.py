@@ -439,6 +439,29 @@ class SophiaG(Optimizer):
                     continue
                 st["h"].mul_(b2).addcmul_(p.grad.float(), p.grad.float(), value=(1 - b2) * batch_size)
 
+    def update_hessian_hutchinson(self, loss: torch.Tensor, generator: torch.Generator | None = None) -> None:
+        """Hutchinson estimate of the Hessian diagonal: h <- b2 h + (1 - b2) u * (H u) with Rademacher u, from one
+        Hessian-vector product (a second backward through `loss`, which must have been built from operators that
+        support double differentiation - the framework's fused kernels do not; use the Gauss-Newton-Bartlett form
+        `update_hessian` with them)."""
+        params = [p for g in self.param_groups for p in g["params"] if p.requires_grad]
+        grads = torch.autograd.grad(loss, params, create_graph=True, allow_unused=True)
+        pairs = [(p, gr) for p, gr in zip(params, grads) if gr is not None]
+        us = [(torch.randint(0, 2, p.shape, generator=generator, device="cpu").to(p.device) * 2 - 1).to(gr.dtype)
+              for p, gr in pairs]
+        hvs = torch.autograd.grad([gr for _, gr in pairs], [p for p, _ in pairs], us, allow_unused=True)
+        with torch.no_grad():
+            for g in self.param_groups:
+                b2 = g["betas"][1]
+                ids = {id(p) for p in g["params"]}
+                for (p, _), u, hv in zip(pairs, us, hvs):
+                    if id(p) not in ids or hv is None:
+                        continue
+                    st = self.state[p]
+                    if "h" not in st:
+                        st["h"] = torch.zeros_like(p, dtype=torch.float32)
+                    st["h"].mul_(b2).add_((u * hv).float(), alpha=1 - b2)
+
     @torch.no_grad()
     def step(self, closure=None):
         loss = closure() if closure is not None else None
