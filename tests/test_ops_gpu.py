@@ -397,3 +397,50 @@ def test_lora_linear_with_epilogue_accumulation():
     # two-step path gives the same output up to bf16 rounding of the intermediate delta
     y2 = gemm.linear(x, w) + mod(x)
     torch.testing.assert_close(y.float(), y2.float(), rtol=2e-2, atol=3e-2)
+
+
+@pytest.mark.gpu
+def test_kernel_layer_entry_points_on_gpu():
+    """The public kernel-layer functions route bf16 CUDA tensors to the sm_100a kernels (launch counter moves) and
+    agree with fp32 PyTorch."""
+    import torch.nn.functional as F
+    import trainscale_b200.kernels as K
+    from trainscale_b200.ops import _lib
+    torch.manual_seed(0)
+    dev, dt = "cuda", torch.bfloat16
+    caps = K.get_kernel_capabilities()
+    assert caps["tcgen05"] and caps["flash_attention"] and caps["fp8"] and caps["optimizer_kernels"]
+    n0 = _lib.LAUNCHES
+    x, r = torch.randn(512, 1024, device=dev, dtype=dt), torch.randn(512, 1024, device=dev, dtype=dt)
+    w = (torch.rand(1024, device=dev) + 0.5).to(dt)
+    xf, rf, wf = x.float(), r.float(), w.float()
+    y, res = K.fused_add_rms_layernorm(x, r, w)
+    h = xf + rf
+    torch.testing.assert_close(y.float(), h * torch.rsqrt(h.pow(2).mean(-1, keepdim=True) + 1e-6) * wf, rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(K.fused_softmax(x).float(), torch.softmax(xf, -1), rtol=2e-2, atol=1e-4)
+    torch.testing.assert_close(K.swiglu_forward(x, r).float(), F.silu(xf) * rf, rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(K.fused_gelu(x).float(), F.gelu(xf, approximate="tanh"), rtol=2e-2, atol=2e-2)
+    logits = torch.randn(256, 4096, device=dev, dtype=dt)
+    labels = torch.randint(0, 4096, (256,), device=dev)
+    assert abs(float(K.fast_cross_entropy_loss(logits, labels)) - float(F.cross_entropy(logits.float(), labels))) < 5e-3
+    q = torch.randn(1, 512, 8, 128, device=dev, dtype=dt)
+    k, v = torch.randn(1, 512, 2, 128, device=dev, dtype=dt), torch.randn(1, 512, 2, 128, device=dev, dtype=dt)
+    torch.testing.assert_close(K.flash_attention(q, k, v).float(), K.naive_attention(q.float(), k.float(), v.float()),
+                               rtol=3e-2, atol=3e-2)
+    from trainscale_b200.ops.attention import attention_reference
+    torch.testing.assert_close(K.flash_attention(q, k, v, softcap=20.0, window_size=128).float(),
+                               attention_reference(q.float(), k.float(), v.float(), True, None, 128, 20.0),
+                               rtol=3e-2, atol=3e-2)
+    a, b = torch.randn(512, 1024, device=dev, dtype=dt), (torch.randn(768, 1024, device=dev) / 32).to(dt)
+    ref = a.float() @ b.float().t()
+    got = K.fp8_matmul_block_scaled(a, b).float()
+    assert float((got - ref).abs().max()) / float(ref.abs().max()) < 8e-2
+    rep = K.validate_lora_gradients(T=256, hidden=512, out=768, r=16)
+    assert rep["passed"], rep
+    sm = torch.randn(64, 1000, device=dev, dtype=dt).requires_grad_(True)
+    K.fused_softmax(sm)[:, 3].sum().backward()
+    sf = sm.detach().float().requires_grad_(True)
+    torch.softmax(sf, -1)[:, 3].sum().backward()
+    torch.testing.assert_close(sm.grad.float(), sf.grad, rtol=3e-2, atol=1e-4)
+    assert _lib.LAUNCHES - n0 >= 10
+    _lib.raise_on_any_device_error()

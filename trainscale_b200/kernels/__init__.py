@@ -189,3 +189,430 @@ class TritonGeGLU(TritonSwiGLU):
 
 
 RMSNorm, SwiGLU, GeGLU = TritonRMSNorm, TritonSwiGLU, TritonGeGLU
+
+
+# ------------------------------------------------------------------------------------------------ attention
+class AttentionMaskType(str, Enum):
+    CAUSAL = "causal"
+    FULL = "full"
+    SLIDING_WINDOW = "sliding_window"
+    DOCUMENT = "document"
+
+
+class AttentionBackend(str, Enum):
+    TCGEN05_FLASH = "tcgen05_flash"       # the framework kernel (bf16, head_dim 64 / 128)
+    REFERENCE = "reference"               # fp32 PyTorch maths
+
+
+class AttentionOutput(NamedTuple):
+    output: torch.Tensor
+    lse: torch.Tensor | None = None
+
+
+@dataclass
+class FlashAttentionConfig:
+    causal: bool = True
+    softmax_scale: float | None = None
+    window_size: int | None = None
+    softcap: float = 0.0
+    dropout: float = 0.0                  # not supported by the kernel; must stay 0
+
+
+@dataclass
+class FlexAttentionConfig(FlashAttentionConfig):
+    mask_type: AttentionMaskType = AttentionMaskType.CAUSAL
+    backend: AttentionBackend | None = None
+
+
+@dataclass
+class BackendCapabilities:
+    backend: AttentionBackend
+    head_dims: tuple = (64, 128)
+    sliding_window: bool = True
+    softcap: bool = True
+    varlen: bool = True
+    gqa: bool = True
+
+    @classmethod
+    def detect(cls) -> "BackendCapabilities":
+        return cls(AttentionBackend.TCGEN05_FLASH if supports_tcgen05() else AttentionBackend.REFERENCE)
+
+
+def is_flash_attn_available() -> bool:
+    """True when the framework's own flash kernels can run (an sm_100 GPU); no external flash-attn package is used."""
+    return supports_tcgen05()
+
+
+def flash_attention(q, k, v, causal: bool = True, softmax_scale: float | None = None, window_size: int | None = None,
+                    softcap: float = 0.0, cu_seqlens: torch.Tensor | None = None) -> torch.Tensor:
+    """q [B, S, Hq, D], k / v [B, S, Hkv, D] -> [B, S, Hq, D].  bf16 CUDA inputs run the tcgen05 flash kernels
+    (forward and backward); anything else the fp32 reference."""
+    B, S, Hq, D = q.shape
+    Hkv = k.shape[2]
+    if q.is_cuda and q.dtype == torch.bfloat16 and k.shape[1] == S:
+        qkv = torch.cat((q.reshape(B, S, -1), k.reshape(B, S, -1), v.reshape(B, S, -1)), dim=-1)
+        return _attn.attention_qkv(qkv, Hq, Hkv, D, causal, softmax_scale, window_size, softcap, cu_seqlens) \
+            .view(B, S, Hq, D)
+    doc = None
+    if cu_seqlens is not None:
+        idx = torch.arange(B * S, device=q.device)
+        doc = torch.bucketize(idx, cu_seqlens[1:].to(idx.dtype), right=True).view(B, S)
+    return _attn.attention_reference(q, k, v, causal, softmax_scale, window_size, softcap, doc).to(q.dtype)
+
+
+def naive_attention(q, k, v, causal: bool = True, softmax_scale: float | None = None):
+    return _attn.attention_reference(q, k, v, causal, softmax_scale).to(q.dtype)
+
+
+def scaled_dot_product_attention(q, k, v, attn_mask=None, is_causal: bool = False, scale: float | None = None):
+    """[B, H, S, D] layout of torch's function; an explicit mask takes torch's path, causal / full the flash kernels."""
+    if attn_mask is not None:
+        return F.scaled_dot_product_attention(q, k, v, attn_mask=attn_mask, is_causal=False, scale=scale)
+    return flash_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), is_causal, scale).transpose(1, 2)
+
+
+def slow_attention_softcapping(q, k, v, softcap: float, causal: bool = True, softmax_scale: float | None = None):
+    """fp32 reference of soft-capped attention: scores -> softcap * tanh(scores / softcap)."""
+    return _attn.attention_reference(q, k, v, causal, softmax_scale, None, softcap).to(q.dtype)
+
+
+def attention_softcapping_compiled(q, k, v, softcap: float, causal: bool = True, softmax_scale: float | None = None):
+    """Soft-capped attention on the flash kernel (the cap is applied to the scores inside the kernel)."""
+    return flash_attention(q, k, v, causal, softmax_scale, None, softcap)
+
+
+def create_causal_mask(seq_len: int, device=None, dtype=torch.float32) -> torch.Tensor:
+    return torch.full((seq_len, seq_len), float("-inf"), device=device, dtype=dtype).triu(1)
+
+
+def create_sliding_window_causal_mask(seq_len: int, window: int, device=None, dtype=torch.float32) -> torch.Tensor:
+    i = torch.arange(seq_len, device=device)
+    keep = (i[None, :] <= i[:, None]) & (i[:, None] - i[None, :] < window)
+    return torch.zeros(seq_len, seq_len, device=device, dtype=dtype).masked_fill(~keep, float("-inf"))
+
+
+def inference_attention_single_token(q, k_cache, v_cache, seq_lens: torch.Tensor | None = None,
+                                     softmax_scale: float | None = None) -> torch.Tensor:
+    """Decode step: q [B, Hq, D] against caches [B, S_max, Hkv, D] (valid prefix `seq_lens[b]`) -> [B, Hq, D]."""
+    B, Hq, D = q.shape
+    S, Hkv = k_cache.shape[1], k_cache.shape[2]
+    scale = softmax_scale if softmax_scale is not None else 1.0 / math.sqrt(D)
+    g = Hq // Hkv
+    qf = q.float().view(B, Hkv, g, D)
+    s = torch.einsum("bhgd,bshd->bhgs", qf, k_cache.float()) * scale
+    if seq_lens is not None:
+        pad = torch.arange(S, device=q.device)[None, :] >= seq_lens[:, None]
+        s = s.masked_fill(pad[:, None, None, :], float("-inf"))
+    o = torch.einsum("bhgs,bshd->bhgd", torch.softmax(s, -1), v_cache.float())
+    return o.reshape(B, Hq, D).to(q.dtype)
+
+
+class FlashAttention(nn.Module):
+    def __init__(self, config: FlashAttentionConfig | None = None):
+        super().__init__()
+        self.config = config or FlashAttentionConfig()
+        if self.config.dropout:
+            raise ValueError("attention dropout is not supported")
+
+    def forward(self, q, k, v, cu_seqlens=None):
+        c = self.config
+        return flash_attention(q, k, v, c.causal, c.softmax_scale, c.window_size, c.softcap, cu_seqlens)
+
+
+class FlexAttention(FlashAttention):
+    """Mask-type front end: causal / full / sliding window / packed documents map onto the kernel's own switches."""
+
+    def __init__(self, config: FlexAttentionConfig | None = None):
+        config = config or FlexAttentionConfig()
+        if config.mask_type is AttentionMaskType.FULL:
+            config.causal = False
+        if config.mask_type is AttentionMaskType.SLIDING_WINDOW and not config.window_size:
+            raise ValueError("sliding-window attention needs window_size")
+        super().__init__(config)
+
+
+class MultiHeadFlashAttention(nn.Module):
+    """Self-attention block: fused qkv projection, rotary embedding, flash attention, output projection."""
+
+    def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int | None = None, head_dim: int | None = None,
+                 causal: bool = True, rope_theta: float | None = 10000.0, max_position: int = 8192, dtype=None,
+                 device=None):
+        super().__init__()
+        self.h, self.kv = num_heads, num_kv_heads or num_heads
+        self.d = head_dim or hidden_size // num_heads
+        self.causal, self.rope_theta, self.max_position = causal, rope_theta, max_position
+        self.wqkv = nn.Parameter(torch.empty((self.h + 2 * self.kv) * self.d, hidden_size, dtype=dtype, device=device))
+        self.wo = nn.Parameter(torch.empty(hidden_size, self.h * self.d, dtype=dtype, device=device))
+        nn.init.normal_(self.wqkv, std=0.02)
+        nn.init.normal_(self.wo, std=0.02)
+        self._tables = None
+
+    def forward(self, x, cu_seqlens=None):
+        B, S, _ = x.shape
+        qkv = _gemm.linear(x, self.wqkv)
+        if self.rope_theta:
+            if self._tables is None or self._tables[0].device != x.device or self._tables[0].shape[0] < S:
+                self._tables = _rope.rope_tables(max(S, self.max_position), self.d, self.rope_theta, device=x.device)
+            qkv = _rope.apply_rope_qkv(qkv, self.h + self.kv, self.d, *self._tables)
+        o = _attn.attention_qkv(qkv, self.h, self.kv, self.d, self.causal, cu_seqlens=cu_seqlens)
+        return _gemm.linear(o, self.wo)
+
+
+# ------------------------------------------------------------------------------------------------ rotary embeddings
+class RoPEScalingType(str, Enum):
+    NONE = "none"
+    LINEAR = "linear"
+    NTK = "ntk"
+    DYNAMIC_NTK = "dynamic_ntk"
+    YARN = "yarn"
+    LLAMA3 = "llama3"
+    LONGROPE = "longrope"
+
+
+@dataclass
+class RoPEConfig:
+    dim: int = 128
+    max_position: int = 8192
+    theta: float = 10000.0
+    scaling_type: RoPEScalingType = RoPEScalingType.NONE
+    scaling_factor: float = 1.0
+    original_max_position: int = 8192
+    interleaved: bool = False
+
+
+def precompute_freqs_cis(dim: int, end: int, theta: float = 10000.0, scaling_factor: float = 1.0, device=None):
+    """(cos, sin) tables [end, dim/2] (linear position scaling when scaling_factor != 1)."""
+    return _rope.rope_tables(end, dim, theta, device=device,
+                             **({"scaling": "linear", "factor": scaling_factor} if scaling_factor != 1.0 else {}))
+
+
+class RoPEFrequencyCache:
+    """(cos, sin) tables per (config, device), grown on demand."""
+
+    def __init__(self):
+        self._cache: dict = {}
+
+    def get(self, cfg: RoPEConfig, seq_len: int, device=None):
+        key = (cfg.dim, cfg.theta, cfg.scaling_type, cfg.scaling_factor, cfg.original_max_position, str(device))
+        cur = self._cache.get(key)
+        if cur is None or cur[0].shape[0] < seq_len:
+            n = max(seq_len, cfg.max_position)
+            kind = cfg.scaling_type.value if cfg.scaling_type is not RoPEScalingType.LONGROPE else "yarn"
+            inv = _rope.rope_inv_freq(cfg.dim, cfg.theta, scaling=kind, factor=cfg.scaling_factor,
+                                      original_max_pos=cfg.original_max_position, max_pos=n)
+            ang = torch.outer(torch.arange(n, dtype=torch.float32), inv)
+            cur = (ang.cos().to(device).contiguous(), ang.sin().to(device).contiguous())
+            self._cache[key] = cur
+        return cur
+
+
+def fast_rope_embedding(q, k, cos, sin, positions=None, interleaved: bool = False):
+    """q [B, S, Hq, D], k [B, S, Hkv, D], tables [max_pos, D/2] -> rotated (q, k)."""
+    return _rope.apply_rope(q, cos, sin, positions, 0, interleaved), _rope.apply_rope(k, cos, sin, positions, 0, interleaved)
+
+
+def inplace_rope_embedding(qkv, n_heads: int, n_kv_heads: int, head_dim: int, cos, sin, positions=None):
+    """Rotates the q and k heads of a fused [B, S, (Hq + 2 Hkv) D] buffer (each k head once)."""
+    return _rope.apply_rope_qkv(qkv, n_heads + n_kv_heads, head_dim, cos, sin, positions)
+
+
+Fast_RoPE_Embedding = _rope._RopeFn
+
+
+# ------------------------------------------------------------------------------------------------ fused LoRA
+def torch_amp_custom_fwd(fn=None, **_kw):
+    """The framework's autograd functions compute in their input dtype and need no autocast bracketing; the decorators
+    exist so that code written against the reference's names imports and runs unchanged."""
+    return fn if fn is not None else (lambda f: f)
+
+
+torch_amp_custom_bwd = torch_amp_custom_fwd
+
+
+def matmul_lora(x, W, A=None, B=None, s: float = 1.0):
+    """x W^T + s (x A^T) B^T with the adapter product accumulated by the GEMM epilogue (A [r, in], B [out, r])."""
+    if A is None or B is None:
+        return _gemm.linear(x, W)
+    from ..lora import _LoRALinearFn
+    return _LoRALinearFn.apply(x, W, ((float(s), 0, int(W.shape[0])),), A, B)
+
+
+def get_lora_parameters(module):
+    """(W, A, B, scaling) of a module that carries one adapter (`LoRALinear`-style attributes), else (W, None, None, 1)."""
+    W = getattr(module, "weight", None)
+    A, B = getattr(module, "lora_A", None), getattr(module, "lora_B", None)
+    return W, A, B, float(getattr(module, "scaling", 1.0))
+
+
+def apply_lora_qkv(x, Wq, Wk, Wv, Aq=None, Bq=None, Ak=None, Bk=None, Av=None, Bv=None, s: float = 1.0):
+    return matmul_lora(x, Wq, Aq, Bq, s), matmul_lora(x, Wk, Ak, Bk, s), matmul_lora(x, Wv, Av, Bv, s)
+
+
+def apply_lora_mlp_swiglu(x, Wg, Wu, Wd, Ag=None, Bg=None, Au=None, Bu=None, Ad=None, Bd=None, s: float = 1.0):
+    h = _act.swiglu(matmul_lora(x, Wg, Ag, Bg, s), matmul_lora(x, Wu, Au, Bu, s))
+    return matmul_lora(h, Wd, Ad, Bd, s)
+
+
+class _LoRABlock(nn.Module):
+    def _adapter(self, name, out_f, in_f, r, dtype, device):
+        A = nn.Parameter(torch.empty(r, in_f, dtype=dtype, device=device))
+        B = nn.Parameter(torch.zeros(out_f, r, dtype=dtype, device=device))
+        nn.init.kaiming_uniform_(A, a=math.sqrt(5))
+        setattr(self, f"A_{name}", A)
+        setattr(self, f"B_{name}", B)
+
+    def _ab(self, name):
+        return getattr(self, f"A_{name}"), getattr(self, f"B_{name}")
+
+
+class LoRA_MLP(_LoRABlock):
+    """Frozen gated MLP with trainable low-rank adapters on gate / up / down."""
+
+    def __init__(self, hidden_size: int, intermediate_size: int, r: int = 16, alpha: float = 32.0, dtype=None,
+                 device=None):
+        super().__init__()
+        self.scaling = alpha / r
+        for n, (o, i) in {"gate": (intermediate_size, hidden_size), "up": (intermediate_size, hidden_size),
+                          "down": (hidden_size, intermediate_size)}.items():
+            w = nn.Parameter(torch.empty(o, i, dtype=dtype, device=device), requires_grad=False)
+            nn.init.normal_(w, std=0.02)
+            setattr(self, f"W_{n}", w)
+            self._adapter(n, o, i, r, dtype, device)
+
+    def forward(self, x):
+        return apply_lora_mlp_swiglu(x, self.W_gate, self.W_up, self.W_down, *self._ab("gate"), *self._ab("up"),
+                                     *self._ab("down"), s=self.scaling)
+
+
+class LoRA_QKV(_LoRABlock):
+    def __init__(self, hidden_size: int, q_out: int, kv_out: int, r: int = 16, alpha: float = 32.0, dtype=None,
+                 device=None):
+        super().__init__()
+        self.scaling = alpha / r
+        for n, o in {"q": q_out, "k": kv_out, "v": kv_out}.items():
+            w = nn.Parameter(torch.empty(o, hidden_size, dtype=dtype, device=device), requires_grad=False)
+            nn.init.normal_(w, std=0.02)
+            setattr(self, f"W_{n}", w)
+            self._adapter(n, o, hidden_size, r, dtype, device)
+
+    def forward(self, x):
+        return apply_lora_qkv(x, self.W_q, self.W_k, self.W_v, *self._ab("q"), *self._ab("k"), *self._ab("v"),
+                              s=self.scaling)
+
+
+def validate_lora_gradients(T: int = 64, hidden: int = 64, out: int = 96, r: int = 8, device=None, dtype=None,
+                            atol: float | None = None) -> dict:
+    """Gradients of `matmul_lora` (custom backward with accumulating GEMMs) against autograd on the plain formula."""
+    device = device or ("cuda" if torch.cuda.is_available() else "cpu")
+    dtype = dtype or (torch.bfloat16 if device == "cuda" else torch.float32)
+    g = torch.Generator().manual_seed(0)
+    mk = lambda *s: (torch.randn(*s, generator=g) * 0.1).to(device, dtype)   # noqa: E731
+    x, W, A, B = mk(T, hidden), mk(out, hidden), mk(r, hidden), mk(out, r)
+    leaves = [t.clone().requires_grad_(True) for t in (x, A, B)]
+    matmul_lora(leaves[0], W, leaves[1], leaves[2], 2.0).float().pow(2).sum().backward()
+    ref = [t.float().clone().requires_grad_(True) for t in (x, A, B)]
+    (ref[0] @ W.float().t() + 2.0 * (ref[0] @ ref[1].t()) @ ref[2].t()).pow(2).sum().backward()
+    errs = {n: float((a.grad.float() - b.grad).abs().max() / b.grad.abs().max().clamp(min=1e-9))
+            for n, a, b in zip(("dx", "dA", "dB"), leaves, ref)}
+    tol = atol if atol is not None else (3e-2 if dtype == torch.bfloat16 else 1e-4)
+    return dict(errs, passed=all(v < tol for v in errs.values()))
+
+
+# ------------------------------------------------------------------------------------------------ MoE
+@dataclass
+class MoEKernelConfig:
+    num_experts: int = 8
+    top_k: int = 2
+    segment_alignment: int = 128          # expert segments of the sorted layout start on tile boundaries
+    activation: str = "silu"
+
+
+def moe_grouped_gemm(x, expert_ids, weights, w_gate_up, w_down, activation: str = "silu"):
+    """Top-k expert FFN over tokens x [T, H]: device-side routing plan, permute into 128-aligned expert segments,
+    grouped tcgen05 GEMMs, weighted combine (w_gate_up [E, 2I, H], w_down [E, H, I])."""
+    if _moe.available(x):
+        return _moe.moe_ffn(x, expert_ids, weights, w_gate_up, w_down, activation)
+    out = torch.zeros(x.shape, dtype=torch.float32, device=x.device)       # per-expert loop (CPU / non-bf16 inputs)
+    for e in range(w_gate_up.shape[0]):
+        tok, slot = (expert_ids == e).nonzero(as_tuple=True)
+        if tok.numel():
+            h = _act.glu(x[tok].float() @ w_gate_up[e].float().t(), activation)
+            out.index_add_(0, tok, (h @ w_down[e].float().t()) * weights[tok, slot].float().unsqueeze(1))
+    return out.to(x.dtype)
+
+
+# ------------------------------------------------------------------------------------------------ fp8
+class FP8Format(str, Enum):
+    E4M3 = "e4m3"
+    E5M2 = "e5m2"
+
+
+@dataclass
+class FP8Config:
+    format: FP8Format = FP8Format.E4M3
+    block_size: int = 128
+    amax_history_len: int = 16
+    margin: int = 0
+
+
+def row_quantize_fp8(x2):
+    return _fp8.quant_row(x2)
+
+
+def block_quantize_fp8(w):
+    return _fp8.quant_block(w)
+
+
+def block_dequantize_fp8(q, scale):
+    return _fp8.dequant(q, scale, "block")
+
+
+def fp8_matmul_block_scaled(x2, w):
+    """x2 [M, K] bf16, w [N, K] bf16 -> x2 w^T through e4m3 operands (1x128 activation / 128x128 weight scales)."""
+    aq, sa = _fp8.quant_act(x2)
+    bq, sb = _fp8.quant_block(w)
+    return _fp8.gemm_fp8(aq, sa, bq, sb, w.shape[0])
+
+
+def fp8_matmul_row_scaled(x2, w):
+    """Per-row scaled operands; the product is formed on the dequantised bf16 values (tcgen05 bf16 GEMM)."""
+    xq, xs = _fp8.quant_row(x2)
+    wq, ws = _fp8.quant_row(w)
+    return _gemm.matmul_nt(_fp8.dequant(xq, xs, "row").to(x2.dtype), _fp8.dequant(wq, ws, "row").to(w.dtype))
+
+
+class FP8ScaleManager:
+    """Delayed scaling: keeps an amax history per tensor name and turns it into the scale of the next step."""
+
+    FMAX = {FP8Format.E4M3: 448.0, FP8Format.E5M2: 57344.0}
+
+    def __init__(self, config: FP8Config | None = None):
+        self.config = config or FP8Config()
+        self.history: dict[str, list[float]] = {}
+
+    def update(self, name: str, tensor: torch.Tensor) -> float:
+        h = self.history.setdefault(name, [])
+        h.append(float(tensor.detach().abs().max()))
+        del h[:-self.config.amax_history_len]
+        return self.scale(name)
+
+    def scale(self, name: str) -> float:
+        h = self.history.get(name)
+        amax = max(h) if h else 1.0
+        return (self.FMAX[self.config.format] / (2 ** self.config.margin)) / max(amax, 1e-12)
+
+
+class FP8Linear(nn.Module):
+    """Linear layer whose forward and input-gradient products run on the block-scaled fp8 kernel (bf16 CUDA inputs
+    with in_features a multiple of 128); weight gradient and parameters stay bf16."""
+
+    def __init__(self, in_features: int, out_features: int, bias: bool = False, dtype=torch.bfloat16, device=None):
+        super().__init__()
+        self.weight = nn.Parameter(torch.empty(out_features, in_features, dtype=dtype, device=device))
+        self.bias = nn.Parameter(torch.zeros(out_features, dtype=dtype, device=device)) if bias else None
+        nn.init.normal_(self.weight, std=0.02)
+
+    def forward(self, x):
+        y = _fp8.fp8_linear(x, self.weight) if _fp8.available(x) and self.weight.shape[0] % 8 == 0 \
+            else _gemm.linear(x, self.weight)
+        return y if self.bias is None else y + self.bias
