@@ -248,3 +248,45 @@ def test_sophia_hutchinson_hessian_diagonal():
     before = x.detach().clone()
     opt.step()
     assert not torch.equal(before, x.detach())
+
+
+def test_adapter_save_load_and_attention_interface(tmp_path):
+    import json
+    import pytest
+    import torch
+    from trainscale_b200.lora import get_peft_model, load_adapter, lora_state_dict, save_adapter
+    from trainscale_b200.models.llama import LlamaConfig, build_model
+    cfg = LlamaConfig(vocab_size=128, hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+                      num_key_value_heads=2, head_dim=16)
+    m = build_model(cfg, dtype=torch.float32, device="cpu", seed=0)
+    get_peft_model(m, r=4)
+    for n, p in m.named_parameters():
+        if "lora_B" in n:
+            torch.nn.init.normal_(p)
+    save_adapter(m, tmp_path)
+    keys = json.loads((tmp_path / "adapter_config.json").read_text())["target_modules"]
+    assert "q_proj" in keys and "down_proj" in keys
+    m2 = build_model(cfg, dtype=torch.float32, device="cpu", seed=0)
+    get_peft_model(m2, r=4)
+    assert load_adapter(m2, tmp_path) == []
+    a, b = lora_state_dict(m), lora_state_dict(m2)
+    assert len(a) == 28 and all(torch.equal(a[k], b[k]) for k in a)
+    ids = torch.randint(0, 128, (1, 12))
+    torch.testing.assert_close(m(ids).logits, m2(ids).logits)
+    # HF model routed through the registered attention function: unchanged results on CPU (falls back to SDPA)
+    transformers = pytest.importorskip("transformers")
+    from trainscale_b200.registry import ModelInfo, ModelMeta, auto_patch_attention
+    hf = transformers.LlamaForCausalLM(transformers.LlamaConfig(
+        vocab_size=128, hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+        num_key_value_heads=2)).eval()
+    with torch.no_grad():
+        ref = hf(ids).logits
+        assert auto_patch_attention(hf) == 2 and hf.config._attn_implementation == "trainscale_flash"
+        torch.testing.assert_close(hf(ids).logits, ref)
+    assert ModelMeta is ModelInfo
+    from trainscale_b200.utils.cuda_graphs import CUDAGraphManager, compilation_debug_mode, get_compilation_stats
+    mg = CUDAGraphManager()
+    before = get_compilation_stats()["eager_calls"]
+    with compilation_debug_mode(log=lambda s: None):
+        assert float(mg.run(lambda x: x + 1, torch.ones(2))[0]) == 2.0
+    assert get_compilation_stats()["eager_calls"] == before + 1 and get_compilation_stats(mg)["signatures"] == 0

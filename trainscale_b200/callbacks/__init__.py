@@ -7,6 +7,8 @@ here every hook is fired by the loop.)
 """
 from __future__ import annotations
 
+from enum import Enum
+
 import json
 import logging
 import math
@@ -142,6 +144,13 @@ class CheckpointCallback(Callback):
         ckpts.sort()
         for _, p in ckpts[:-self.limit]:
             shutil.rmtree(p, ignore_errors=True)
+
+
+class LoggingBackend(str, Enum):
+    CONSOLE = "console"
+    TENSORBOARD = "tensorboard"
+    WANDB = "wandb"
+    JSONL = "jsonl"
 
 
 class LoggingCallback(Callback):

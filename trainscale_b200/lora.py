@@ -185,3 +185,70 @@ def lora_state_dict(model) -> dict[str, torch.Tensor]:
 def count_trainable(model) -> tuple[int, int]:
     t = sum(p.numel() for p in model.parameters() if p.requires_grad)
     return t, sum(p.numel() for p in model.parameters())
+
+
+def _adapter_items(model):
+    """(PEFT-style key stem, LoRALinear) for every adapter of the model, e.g.
+    base_model.model.model.layers.3.self_attn.q_proj -> that layer's q adapter."""
+    targets = _targets_for(model.config)
+    by_slot = {(kind, w, row0): name for name, (kind, w, row0, _) in targets.items()}
+    for li, layer in enumerate(model.model.layers):
+        for kind, mod, hf in (("attn", layer.self_attn, "self_attn"), ("mlp", layer.mlp, "mlp")):
+            inner = getattr(mod, "inner", mod)
+            if getattr(inner, "lora", None) is None:
+                continue
+            for wname, fused in inner.lora.items():
+                for p in fused.parts:
+                    yield f"base_model.model.model.layers.{li}.{hf}.{by_slot[(kind, wname, p.row0)]}", p
+
+
+def save_adapter(model, path, adapter_config: dict | None = None) -> None:
+    """Writes `adapter_model.safetensors` (PEFT key layout: <module>.lora_A.weight / .lora_B.weight) and
+    `adapter_config.json`, so that the adapter also loads with the peft package on a HuggingFace Llama."""
+    import json
+    from pathlib import Path
+    path = Path(path)
+    path.mkdir(parents=True, exist_ok=True)
+    sd, ranks, targets, scale = {}, set(), set(), None
+    for stem, p in _adapter_items(model):
+        sd[f"{stem}.lora_A.weight"] = p.lora_A.detach().cpu().contiguous()
+        sd[f"{stem}.lora_B.weight"] = p.lora_B.detach().cpu().contiguous()
+        ranks.add(p.r)
+        targets.add(stem.rsplit(".", 1)[1])
+        scale = p.scaling
+    try:
+        from safetensors.torch import save_file
+        save_file(sd, str(path / "adapter_model.safetensors"))
+    except ImportError:
+        torch.save(sd, path / "adapter_model.bin")
+    r = max(ranks) if ranks else 0
+    cfg = {"peft_type": "LORA", "r": r, "target_modules": sorted(targets), "scaling": scale,
+           "lora_alpha": (scale or 0) * r, "use_rslora": False, "bias": "none", "task_type": "CAUSAL_LM"}
+    cfg.update(adapter_config or {})
+    (path / "adapter_config.json").write_text(json.dumps(cfg, indent=2))
+
+
+def load_adapter(model, path, strict: bool = True) -> list[str]:
+    """Loads adapter weights saved by `save_adapter` (or by peft, same key layout) into a model that already carries
+    adapters of the same shapes (`get_peft_model` first).  Returns the keys that found no adapter."""
+    from pathlib import Path
+    path = Path(path)
+    f = path / "adapter_model.safetensors"
+    if f.exists():
+        from safetensors.torch import load_file
+        sd = load_file(str(f))
+    else:
+        sd = torch.load(path / "adapter_model.bin", map_location="cpu", weights_only=True)
+    # peft inserts the adapter name ("default") before ".weight"
+    sd = {k.replace(".lora_A.default.", ".lora_A.").replace(".lora_B.default.", ".lora_B."): v for k, v in sd.items()}
+    used = set()
+    with torch.no_grad():
+        for stem, p in _adapter_items(model):
+            for part, dst in (("lora_A", p.lora_A), ("lora_B", p.lora_B)):
+                k = f"{stem}.{part}.weight"
+                if k in sd:
+                    dst.copy_(sd[k].to(dst.dtype))
+                    used.add(k)
+                elif strict:
+                    raise KeyError(f"adapter checkpoint has no {k}")
+    return sorted(set(sd) - used)

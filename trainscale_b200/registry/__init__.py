@@ -412,3 +412,40 @@ def auto_patch_fp8_linear(model: nn.Module, min_features: int = 1024, skip: tupl
 def auto_patch(model: nn.Module, layernorm: bool = True, mlp: bool = True, rope: bool = True, fp8: bool = False) -> dict:
     return {"layernorm": auto_patch_layernorm(model) if layernorm else 0, "mlp": auto_patch_mlp(model) if mlp else 0,
             "rope": auto_patch_rope(model) if rope else 0, "fp8_linear": auto_patch_fp8_linear(model) if fp8 else 0}
+
+
+ModelMeta = ModelInfo          # name used by the per-family registration files of the reference
+
+
+def auto_patch_attention(model: nn.Module, name: str = "trainscale_flash") -> int:
+    """Registers the framework's flash attention with transformers' attention interface and switches the model's
+    config to it, so that an unconverted HuggingFace model runs its attention on the tcgen05 kernels.  Calls that carry
+    an explicit mask (padding), dropout, or non-bf16 / CPU tensors are handed to transformers' SDPA path.
+    Returns the number of attention modules affected (0 when transformers has no such interface)."""
+    try:
+        from transformers import AttentionInterface
+        from transformers.integrations.sdpa_attention import sdpa_attention_forward
+    except Exception:
+        return 0
+    from ..kernels import flash_attention
+
+    def forward(module, query, key, value, attention_mask, dropout: float = 0.0, scaling=None, is_causal=None, **kw):
+        causal = is_causal if is_causal is not None else getattr(module, "is_causal", True)
+        usable = attention_mask is None and not dropout and query.is_cuda and query.dtype == torch.bfloat16 \
+            and query.shape[2] == key.shape[2] and query.shape[-1] in (64, 128) and not kw.get("sliding_window")
+        if not usable:
+            return sdpa_attention_forward(module, query, key, value, attention_mask, dropout=dropout, scaling=scaling,
+                                          is_causal=is_causal, **kw)
+        out = flash_attention(query.transpose(1, 2), key.transpose(1, 2), value.transpose(1, 2), bool(causal), scaling)
+        return out, None                                  # [B, S, H, D], as the interface expects
+
+    AttentionInterface.register(name, forward)
+    cfg = getattr(model, "config", None)
+    if cfg is not None:
+        cfg._attn_implementation = name
+    n = 0
+    for m in model.modules():
+        if type(m).__name__.endswith("Attention") and hasattr(m, "config"):
+            m.config._attn_implementation = name
+            n += 1
+    return n

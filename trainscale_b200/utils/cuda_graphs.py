@@ -182,3 +182,54 @@ class InductorConfigManager:
 
     def __exit__(self, *exc):
         self.restore()
+
+
+# ------------------------------------------------------------------------------------------------ diagnostics
+_STATS = {"captures": 0, "replays": 0, "eager_calls": 0, "signatures": 0}
+_DEBUG = {"on": False}
+
+
+def get_compilation_stats(manager: CUDAGraphManager | None = None) -> dict:
+    """Counters of graph capture / replay (of one manager, or process-wide when none is given)."""
+    if manager is not None:
+        return {"signatures": len(manager.graphs), "pool_shared": manager.pool is not None,
+                "captures": getattr(manager, "captures", len(manager.graphs)), "replays": getattr(manager, "replays", 0)}
+    return dict(_STATS)
+
+
+class compilation_debug_mode:
+    """`with compilation_debug_mode():` logs every capture (shape signature) and counts replays / eager calls."""
+
+    def __init__(self, log=print):
+        self.log = log
+
+    def __enter__(self):
+        self._prev = (_DEBUG["on"], _DEBUG.get("log"))
+        _DEBUG["on"], _DEBUG["log"] = True, self.log
+        return self
+
+    def __exit__(self, *exc):
+        _DEBUG["on"], _DEBUG["log"] = self._prev
+
+
+_orig_run = CUDAGraphManager.run
+
+
+def _counted_run(self, fn, *args):
+    if not torch.cuda.is_available() or self.config.mode == "none":
+        _STATS["eager_calls"] += 1
+        return _orig_run(self, fn, *args)
+    before = len(self.graphs)
+    out = _orig_run(self, fn, *args)
+    if len(self.graphs) > before:
+        _STATS["captures"] += 1
+        _STATS["signatures"] += 1
+        self.captures = getattr(self, "captures", 0) + 1
+        if _DEBUG["on"]:
+            _DEBUG["log"](f"[cuda-graph] captured {getattr(fn, '__name__', fn)} for {self._sig(args)}")
+    _STATS["replays"] += 1
+    self.replays = getattr(self, "replays", 0) + 1
+    return out
+
+
+CUDAGraphManager.run = _counted_run
