@@ -161,3 +161,52 @@ def test_engine_generate_with_speculative_config_matches_plain_engine():
     got = spec.generate("hello world", params).unwrap()
     assert got.token_ids == want.token_ids
     assert 0.0 <= got.speculative_acceptance <= 1.0
+
+
+def test_mixed_adapter_batch_matches_merged_models():
+    """Requests with adapter a, adapter b and no adapter share one continuous batch; each gets exactly the tokens that a
+    model with its adapter merged into the weights produces.  Two of the prompts are equal: the prefix cache must not
+    hand K/V computed under one adapter to a request that uses another."""
+    import copy
+    import torch
+    from trainscale_b200.inference.engine import EngineConfig, EngineCore, GenerationParams, LoRAServingConfig
+    from trainscale_b200.lora import get_peft_model, lora_state_dict, merge_and_unload
+    from trainscale_b200.models.llama import LlamaConfig, build_model
+    cfg = LlamaConfig(vocab_size=300, hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+                      num_key_value_heads=2, head_dim=16)
+    base = build_model(cfg, dtype=torch.float32, device="cpu", seed=0)
+    m = copy.deepcopy(base)
+    get_peft_model(m, r=4)
+    adapters = {}
+    for name, seed in (("a", 1), ("b", 2)):
+        g = torch.Generator().manual_seed(seed)
+        for n, p in m.named_parameters():
+            if "lora_" in n:
+                p.data = torch.randn(p.shape, generator=g) * 0.2
+        adapters[name] = lora_state_dict(m)
+    ec = EngineConfig(model="custom", tokenizer="byte", device="cpu", dtype="float32", lora=LoRAServingConfig(max_loras=4))
+
+    def run(model, reqs, ad=None):
+        eng = EngineCore(ec, model=model)
+        if ad:
+            eng.load_adapters(ad)
+        rs = [eng.add_request(p, GenerationParams(max_tokens=6, temperature=0.0, lora_name=a)) for p, a in reqs]
+        while eng.has_unfinished():
+            eng.step()
+        return [r.output_ids for r in rs]
+
+    prompts = [list(range(5, 45)), list(range(40, 52)), list(range(5, 45))]
+    mixed = run(m, list(zip(prompts, ("a", "b", None))), adapters)
+    for p, a, got in zip(prompts, ("a", "b", None), mixed):
+        mm = copy.deepcopy(base)
+        if a:
+            get_peft_model(mm, r=4)
+            for n, q in mm.named_parameters():
+                if n in adapters[a]:
+                    q.data = adapters[a][n].clone()
+            merge_and_unload(mm)
+        assert run(mm, [(p, None)])[0] == got
+    assert mixed[0] != mixed[2]
+    import pytest
+    with pytest.raises(ValueError):
+        EngineCore(EngineConfig(model="custom", tokenizer="byte", device="cpu", dtype="float32"), model=m).load_adapters(adapters)

@@ -90,3 +90,39 @@ def test_router_topk_softmax_kernel(T, E, k, norm):
     ((w * gw).sum() + (probs * gp).sum()).backward()
     ((rw * gw).sum() + (rp * gp).sum()).backward()
     assert torch.allclose(logits.grad, ref_l.grad, atol=1e-5)
+
+
+def test_batched_multi_adapter_lora_on_grouped_gemm():
+    """Per-token adapter ids -> low-rank updates through the MoE plan + grouped GEMMs, against the per-adapter loop."""
+    import copy
+    from trainscale_b200.inference.multi_lora import BatchedLoRA
+    from trainscale_b200.lora import get_peft_model, lora_state_dict
+    from trainscale_b200.models.llama import LlamaConfig, build_model
+    from trainscale_b200.ops import _lib
+    torch.manual_seed(0)
+    cfg = LlamaConfig(vocab_size=512, hidden_size=512, intermediate_size=1024, num_hidden_layers=1, num_attention_heads=4,
+                      num_key_value_heads=2, head_dim=128)
+    m = build_model(cfg, dtype=torch.bfloat16, device="cuda", seed=0)
+    get_peft_model(m, r=16)
+    adapters = {}
+    for name in ("a", "b", "c"):
+        for n, p in m.named_parameters():
+            if "lora_" in n:
+                p.data = (torch.randn(p.shape, device="cuda") * 0.1).to(p.dtype)
+        adapters[name] = copy.deepcopy(lora_state_dict(m))
+    bl = BatchedLoRA(m, adapters)
+    T = 777
+    x = torch.randn(T, 512, device="cuda", dtype=torch.bfloat16)
+    ids = torch.randint(0, 4, (T,), device="cuda")             # 3 = no adapter
+    n0 = _lib.LAUNCHES
+    got = bl.delta(0, "wqkv", x, ids)
+    assert _lib.LAUNCHES > n0
+    A, B = bl.weights[(0, "wqkv")]
+    want = torch.zeros(T, B.shape[1], device="cuda")
+    for a in range(3):
+        sel = ids == a
+        want[sel] = (x[sel].float() @ A[a].float().t()) @ B[a].float().t()
+    assert float(got[ids == 3].abs().max()) == 0.0
+    err = float((got.float() - want).abs().max()) / float(want.abs().max())
+    assert err < 3e-2, err
+    _lib.raise_on_any_device_error()

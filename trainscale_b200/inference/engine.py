@@ -113,6 +113,7 @@ class GenerationParams:
     seed: int | None = None
     logprobs: bool = False
     n: int = 1
+    lora_name: str | None = None        # adapter of this request (see EngineCore.load_adapters)
 
     def validate(self) -> None:
         if self.max_tokens < 1:
@@ -211,6 +212,15 @@ class ModelRunner:
         self.cfg = model.config
         self.cuda = self.device.type == "cuda" and next(model.parameters()).dtype == torch.bfloat16
         self.cos, self.sin = model.model.rope_tables(self.device, min(self.cfg.max_position_embeddings, 1 << 16))
+        self.lora = None                 # multi_lora.BatchedLoRA when adapters are loaded
+
+    def _lin(self, li: int, wname: str, w: torch.Tensor, x: torch.Tensor, adapter_ids) -> torch.Tensor:
+        y = gemm.linear(x, w)
+        if self.lora is not None and adapter_ids is not None:
+            d = self.lora.delta(li, wname, x, adapter_ids)
+            if d is not None:
+                y = y + d
+        return y
 
     def _write_cache(self, layer: int, qkv2d: torch.Tensor, slots: torch.Tensor) -> None:
         c = self.cfg
@@ -275,8 +285,9 @@ class ModelRunner:
 
     @torch.no_grad()
     def forward(self, token_ids: torch.Tensor, positions: torch.Tensor, slots: torch.Tensor, seq_ids: list[int],
-                q_lens: list[int], fresh: bool) -> torch.Tensor:
-        """token_ids / positions / slots: [T]; returns the hidden state of each sequence's LAST token [n_seq, H]."""
+                q_lens: list[int], fresh: bool, adapter_ids: torch.Tensor | None = None) -> torch.Tensor:
+        """token_ids / positions / slots: [T]; returns the hidden state of each sequence's LAST token [n_seq, H].
+        `adapter_ids` [T]: LoRA adapter index of every token (requests with different adapters share the batch)."""
         m, c = self.model.model, self.cfg
         x = m.embed_tokens(token_ids)
         res = None
@@ -284,14 +295,16 @@ class ModelRunner:
         pos32 = positions.to(torch.int32)
         for li, layer in enumerate(m.layers):
             h, res = layer.input_layernorm(x, res)
-            qkv = gemm.linear(h, layer.self_attn.wqkv)
+            qkv = self._lin(li, "wqkv", layer.self_attn.wqkv, h, adapter_ids)
             qkv = rope.apply_rope_qkv(qkv.unsqueeze(0), c.num_attention_heads + c.num_key_value_heads, c.head_dim,
                                       self.cos, self.sin, pos32.unsqueeze(0), qkv.shape[0], 0, c.rope_interleaved)[0]
             self._write_cache(li, qkv, slots)
             a = self._attend(li, qkv, seq_ids, q_lens, fresh, block_table, seq_lens)
-            a = gemm.linear(a, layer.self_attn.wo)
+            a = self._lin(li, "wo", layer.self_attn.wo, a, adapter_ids)
             h, res = layer.post_attention_layernorm(a, res)
-            x = gemm.linear(activation.glu(gemm.linear(h, layer.mlp.w_gate_up), layer.mlp.act), layer.mlp.w_down)
+            x = self._lin(li, "w_down", layer.mlp.w_down,
+                          activation.glu(self._lin(li, "w_gate_up", layer.mlp.w_gate_up, h, adapter_ids), layer.mlp.act),
+                          adapter_ids)
         x, _ = m.norm(x, res)
         last = torch.tensor(q_lens, device=self.device).cumsum(0) - 1
         return x[last]
@@ -387,6 +400,21 @@ class EngineCore:
         self.waiting.append(r)
         return r
 
+    def load_adapters(self, adapters: dict[str, dict[str, torch.Tensor]]) -> None:
+        """Make named LoRA adapters available to requests (`GenerationParams.lora_name`).  The model must carry LoRA
+        modules of matching shapes (`lora.get_peft_model`); requests that use different adapters, or none, are batched
+        together (`multi_lora.BatchedLoRA`)."""
+        from .multi_lora import BatchedLoRA
+        limit = getattr(getattr(self.config, "lora", None), "max_loras", None)
+        if limit and len(adapters) > limit:
+            raise ValueError(f"{len(adapters)} adapters exceed lora.max_loras = {limit}")
+        self.runner.lora = BatchedLoRA(self.model, adapters)
+
+    def _salt(self, r: "_Request") -> bytes:
+        """Prefix-cache namespace of a request: K/V computed under one adapter are not valid under another."""
+        name = r.params.lora_name if self.runner.lora is not None else None
+        return b"" if name is None else b"lora:" + name.encode()
+
     def abort(self, request_id: str) -> bool:
         for q in (self.waiting, self.running):
             for r in list(q):
@@ -403,7 +431,7 @@ class EngineCore:
         r.finished, r.finish_reason = True, reason
         r.metrics.finished = time.perf_counter()
         r.metrics.completion_tokens = len(r.output_ids)
-        self.cache.register_full_blocks(r.seq_id, r.prompt_ids + r.output_ids) if r.seq_id in self.cache.seqs else None
+        self.cache.register_full_blocks(r.seq_id, r.prompt_ids + r.output_ids, self._salt(r)) if r.seq_id in self.cache.seqs else None
         self.cache.free_sequence(r.seq_id)
         if self.config.observability.collect_metrics:
             self.metrics.add(r.metrics)
@@ -435,7 +463,7 @@ class EngineCore:
         while self.waiting and len(self.running) < sc.max_num_seqs:
             r = self.waiting.popleft()
             if r.prefilled == 0:
-                covered = self.cache.match_prefix(r.seq_id, r.prompt_ids)
+                covered = self.cache.match_prefix(r.seq_id, r.prompt_ids, self._salt(r))
                 r.prefilled = covered
                 r.metrics.cached_prompt_tokens = covered
             self.running.append(r)
@@ -454,11 +482,14 @@ class EngineCore:
         if not batch:
             return []
         # 3) build the flattened inputs
-        toks, pos, slots, seq_ids, q_lens = [], [], [], [], []
+        toks, pos, slots, seq_ids, q_lens, ad = [], [], [], [], [], []
         fresh = True
+        lora = self.runner.lora
         for r, feed, start in batch:
             s = self.cache.append_slots(r.seq_id, len(feed))
             toks += feed
+            if lora is not None:
+                ad += lora.ids_for([r.params.lora_name]) * len(feed)
             pos += list(range(start, start + len(feed)))
             slots += s
             seq_ids.append(r.seq_id)
@@ -466,7 +497,8 @@ class EngineCore:
             fresh &= (start == 0)
         dev = self.device
         hidden = self.runner.forward(torch.tensor(toks, device=dev), torch.tensor(pos, device=dev),
-                                     torch.tensor(slots, device=dev, dtype=torch.long), seq_ids, q_lens, fresh)
+                                     torch.tensor(slots, device=dev, dtype=torch.long), seq_ids, q_lens, fresh,
+                                     torch.tensor(ad, device=dev) if lora is not None else None)
         self.steps += 1
         # 4) sample for every request whose prompt is now complete
         sample_rows, sample_reqs = [], []
@@ -474,7 +506,7 @@ class EngineCore:
             if start + len(feed) >= len(r.prompt_ids):
                 if r.prefilled < len(r.prompt_ids):
                     r.prefilled = len(r.prompt_ids)
-                    self.cache.register_full_blocks(r.seq_id, r.prompt_ids)
+                    self.cache.register_full_blocks(r.seq_id, r.prompt_ids, self._salt(r))
                 sample_rows.append(i)
                 sample_reqs.append(r)
             else:

@@ -81,12 +81,13 @@ class PagedKVCache:
     def can_append(self, seq_id: int, new_tokens: int) -> bool:
         return self.blocks_needed(seq_id, new_tokens) <= self.alloc.num_free
 
-    def match_prefix(self, seq_id: int, tokens: list[int]) -> int:
-        """Reuse cached full blocks that hold the same token prefix; returns the number of tokens covered."""
+    def match_prefix(self, seq_id: int, tokens: list[int], salt: bytes = b"") -> int:
+        """Reuse cached full blocks that hold the same token prefix; returns the number of tokens covered.
+        `salt` separates caches whose keys / values differ for the same tokens (e.g. another LoRA adapter)."""
         s = self.seqs.setdefault(seq_id, SequenceBlocks())
         if not self.prefix_caching or s.blocks:
             return 0
-        parent = b""
+        parent = salt
         covered = 0
         # never cover the whole prompt: at least one token must run through the model to produce logits
         for i in range(0, max(0, len(tokens) - 1) // self.block_size * self.block_size, self.block_size):
@@ -114,11 +115,11 @@ class PagedKVCache:
             s.num_tokens += 1
         return slots
 
-    def register_full_blocks(self, seq_id: int, tokens: list[int]) -> None:
+    def register_full_blocks(self, seq_id: int, tokens: list[int], salt: bytes = b"") -> None:
         if not self.prefix_caching:
             return
         s = self.seqs[seq_id]
-        parent = b""
+        parent = salt
         for bi in range(min(len(s.blocks), len(tokens) // self.block_size)):
             h = hashlib.sha1(parent + str(tokens[bi * self.block_size:(bi + 1) * self.block_size]).encode()).digest()
             b = s.blocks[bi]
