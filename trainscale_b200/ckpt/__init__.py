@@ -150,8 +150,14 @@ def save_training_checkpoint(trainer, path: Path) -> None:
         raise CheckpointSaveError(f"failed to write checkpoint {path}", cause=e)
 
 
-def reshard_optimizer_state(shards: list[dict], new_rank: int, new_world: int) -> dict:
-    """Re-slice flat optimizer shards saved at one world size for another."""
+def reshard_optimizer_state(shards: list[dict], new_rank: int, new_world: int,
+                            layout: dict[str, tuple[int, int, int]] | None = None) -> dict:
+    """Re-slice flat optimizer shards saved at one world size for another.
+
+    A unit's flat buffer is padded to a multiple that depends on the world size, so the padded length at the new size
+    can differ from the saved one.  `layout` (unit name -> (padded numel, shard start, shard numel) of the engine that
+    will load the result; `engine_layout(engine)`) makes the slices exact; the padding holds zeros either way.
+    Without it the saved padded length must divide by the new world size."""
     shards = sorted(shards, key=lambda s: s["rank"])
     out = {k: v for k, v in shards[0].items() if k != "units"}
     out.update(rank=new_rank, world=new_world, units={})
@@ -163,13 +169,26 @@ def reshard_optimizer_state(shards: list[dict], new_rank: int, new_world: int) -
                 full[key] = None
                 continue
             full[key] = torch.cat([s["units"][name][key] for s in shards])[:numel]
-        n_new = numel // new_world
-        if numel % new_world:
-            raise CheckpointLoadError(f"unit {name}: {numel} elements do not divide over {new_world} ranks")
-        sl = slice(new_rank * n_new, (new_rank + 1) * n_new)
+        if layout is not None:
+            new_numel, start, n_new = layout[name]
+            for key, v in full.items():
+                if v is not None and v.numel() < new_numel:
+                    full[key] = torch.cat((v, v.new_zeros(new_numel - v.numel())))
+            sl = slice(start, start + n_new)
+            numel = new_numel
+        else:
+            n_new = numel // new_world
+            if numel % new_world:
+                raise CheckpointLoadError(f"unit {name}: {numel} elements do not divide over {new_world} ranks")
+            start = new_rank * n_new
+            sl = slice(start, start + n_new)
         out["units"][name] = {k: (None if v is None else v[sl].clone()) for k, v in full.items()}
-        out["units"][name].update(shard_start=new_rank * n_new, numel=numel)
+        out["units"][name].update(shard_start=start, numel=numel)
     return out
+
+
+def engine_layout(engine) -> dict[str, tuple[int, int, int]]:
+    return {u.name: (u.numel, u.shard_start, u.shard_numel) for u in engine.units}
 
 
 def load_training_checkpoint(trainer, path: Path) -> None:
@@ -201,7 +220,8 @@ def load_training_checkpoint(trainer, path: Path) -> None:
                 else:
                     shards = [torch.load(f, map_location="cpu", weights_only=False) for f in files]
                     eng.load_state_dict(reshard_optimizer_state(shards, trainer.rank if eng.cfg.sharding_strategy != "NO_SHARD" else 0,
-                                                                trainer.world_size if eng.cfg.sharding_strategy != "NO_SHARD" else 1))
+                                                                trainer.world_size if eng.cfg.sharding_strategy != "NO_SHARD" else 1,
+                                                                engine_layout(eng)))
         tsf = path / "trainer_state.pt"
         if tsf.exists():
             ts = torch.load(tsf, map_location="cpu", weights_only=False)
@@ -216,3 +236,77 @@ def load_training_checkpoint(trainer, path: Path) -> None:
                 trainer._restore_rng_states(ts["rng_state"])
     except (OSError, KeyError, RuntimeError) as e:
         raise CheckpointLoadError(f"failed to load checkpoint {path}", cause=e)
+
+
+# ------------------------------------------------------------------------------------------------ integrity / restart
+def verify_checkpoint(path: Path, world_size: int | None = None) -> list[str]:
+    """Problems of a checkpoint directory (empty list = usable): missing or unreadable metadata, weight shards whose
+    sha256 differs from the index, missing / truncated optimizer shards.  Reads files only; no process group needed."""
+    import zipfile
+    from ..hub import compute_sha256
+    path = Path(path)
+    problems: list[str] = []
+    if not path.is_dir():
+        return [f"{path} is not a directory"]
+    for name in ("meta.pt", "trainer_state.pt"):
+        f = path / name
+        if not f.exists():
+            problems.append(f"{name} is missing (the save did not finish)")
+            continue
+        try:
+            torch.load(f, map_location="cpu", weights_only=False)
+        except Exception as e:   # noqa: BLE001 - any unpickling / zip error means the file is damaged
+            problems.append(f"{name} is unreadable: {type(e).__name__}")
+    idx = path / "model.safetensors.index.json"
+    if idx.exists():
+        try:
+            index = json.loads(idx.read_text())
+            hashes = index.get("metadata", {}).get("sha256", {})
+            for name in sorted(set(index.get("weight_map", {}).values())):
+                f = path / name
+                if not f.exists():
+                    problems.append(f"weight shard {name} is missing")
+                elif name in hashes and compute_sha256(f) != hashes[name]:
+                    problems.append(f"weight shard {name} does not match its sha256")
+        except (OSError, ValueError) as e:
+            problems.append(f"weight index is unreadable: {e}")
+    elif not (path / "model.safetensors").exists() and not (path / "model.pt").exists():
+        problems.append("no model weights")
+    shards = sorted((path / "optim").glob("shard-*.pt")) if (path / "optim").exists() else []
+    if shards:
+        saved_world = int(shards[0].stem.split("-of-")[1])
+        have = {int(f.stem.split("-")[1]) for f in shards}
+        strategy = None
+        try:
+            strategy = torch.load(path / "meta.pt", map_location="cpu", weights_only=False)["config"]["sharding_strategy"]
+        except Exception:   # noqa: BLE001
+            pass
+        if strategy != "NO_SHARD" and have != set(range(saved_world)):
+            problems.append(f"optimizer shards {sorted(set(range(saved_world)) - have)} of {saved_world} are missing")
+        for f in shards:
+            if not zipfile.is_zipfile(f):
+                problems.append(f"optimizer shard {f.name} is truncated or corrupt")
+    return problems
+
+
+def list_checkpoints(output_dir: Path) -> list[Path]:
+    """`checkpoint-<step>` directories of a run, oldest first."""
+    out = []
+    for d in Path(output_dir).glob("checkpoint-*"):
+        try:
+            out.append((int(d.name.split("-", 1)[1]), d))
+        except ValueError:
+            continue
+    return [d for _, d in sorted(out)]
+
+
+def find_latest_valid_checkpoint(output_dir: Path, log=None) -> Path | None:
+    """Newest checkpoint that passes `verify_checkpoint`; damaged or half-written ones are skipped (and reported).
+    This is what a restarted job (torchrun --max-restarts, or a fresh launch with another world size) resumes from."""
+    for d in reversed(list_checkpoints(output_dir)):
+        problems = verify_checkpoint(d)
+        if not problems:
+            return d
+        if log is not None:
+            log(f"skipping {d.name}: " + "; ".join(problems))
+    return None

@@ -591,7 +591,7 @@ def save_checkpoint_distributed(path, model, engine=None, extra: dict | None = N
 
 def load_checkpoint_distributed(path, model, engine=None, strict: bool = True) -> dict:
     """Inverse of `save_checkpoint_distributed`; optimizer shards saved at another world size are re-sliced."""
-    from ..ckpt import reshard_optimizer_state
+    from ..ckpt import engine_layout, reshard_optimizer_state
     from pathlib import Path
     path = Path(path)
     blob = torch.load(path / "model.pt", map_location="cpu", weights_only=False)
@@ -619,5 +619,52 @@ def load_checkpoint_distributed(path, model, engine=None, strict: bool = True) -
             engine.load_state_dict(torch.load(mine, map_location="cpu", weights_only=False))
         elif files:
             shards = [torch.load(f, map_location="cpu", weights_only=False) for f in files]
-            engine.load_state_dict(reshard_optimizer_state(shards, engine.rank, engine.world))
+            engine.load_state_dict(reshard_optimizer_state(shards, engine.rank, engine.world, engine_layout(engine)))
     return blob.get("extra", {})
+
+
+# ------------------------------------------------------------------------------------------------ host-side fault injection
+class InjectedFault(RuntimeError):
+    """Raised by FaultInjector: stands for a rank that dies with a Python exception."""
+
+
+class FaultInjector:
+    """Failures made on the HOST, for tests of detection and recovery (nothing here touches a GPU):
+
+        raise@K[:rankR]   raise InjectedFault at step K (on rank R only, else on every rank)
+        exit@K[:rankR]    leave the process at step K without a word (os._exit), between steps
+        sleep@K=S[:rankR] sleep S seconds at step K (a slow rank)
+        mute@K[:rankR]    stop sending heartbeats from step K on (a rank whose messages are lost)
+
+    The spec comes from the constructor or the TS_FAULT environment variable; several faults are separated by ','.
+    Call `at_step(step)` between steps (never while a collective or kernel of this rank is in flight)."""
+
+    def __init__(self, spec: str | None = None, rank: int | None = None):
+        self.rank = int(os.environ.get("RANK", "0")) if rank is None else rank
+        self.faults: list[tuple[str, int, float, int | None]] = []
+        self.muted = False
+        for item in filter(None, (spec if spec is not None else os.environ.get("TS_FAULT", "")).split(",")):
+            head, _, who = item.partition(":rank")
+            kind, _, rest = head.partition("@")
+            step_s, _, arg = rest.partition("=")
+            self.faults.append((kind.strip(), int(step_s), float(arg) if arg else 0.0, int(who) if who else None))
+
+    def at_step(self, step: int) -> None:
+        for kind, k, arg, who in self.faults:
+            if who is not None and who != self.rank:
+                continue
+            if kind == "mute" and step >= k:
+                self.muted = True
+            if step != k:
+                continue
+            if kind == "raise":
+                raise InjectedFault(f"injected failure on rank {self.rank} at step {step}")
+            if kind == "exit":
+                os._exit(17)
+            if kind == "sleep":
+                time.sleep(arg)
+
+    def beat(self, monitor: HeartbeatMonitor) -> None:
+        """Heartbeat unless this rank has been muted."""
+        if not self.muted:
+            monitor.beat()

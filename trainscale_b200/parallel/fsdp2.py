@@ -733,7 +733,7 @@ class FSDPCheckpointManager:
     @staticmethod
     def load_checkpoint(fsdp: SOTAFSDP2, optimizer: Any, path: str | Path, sharded: bool = True,
                         strict: bool = True) -> Result:
-        from ..ckpt import reshard_optimizer_state
+        from ..ckpt import engine_layout, reshard_optimizer_state
         from ..hub import ModelDeserializer
         path = Path(path)
         try:
@@ -752,7 +752,7 @@ class FSDPCheckpointManager:
                     eng.load_state_dict(torch.load(mine, map_location="cpu", weights_only=False))
                 elif files:
                     shards = [torch.load(f, map_location="cpu", weights_only=False) for f in files]
-                    eng.load_state_dict(reshard_optimizer_state(shards, eng.rank, eng.world))
+                    eng.load_state_dict(reshard_optimizer_state(shards, eng.rank, eng.world, engine_layout(eng)))
                 meta = torch.load(path / "meta.pt", map_location="cpu", weights_only=False) \
                     if (path / "meta.pt").exists() else {}
             else:

@@ -372,7 +372,14 @@ class SOTATrainer:
         if self.scheduler is None:
             self.setup_scheduler(total_steps)
         if t.resume_from_checkpoint:
-            self.load_checkpoint(t.resume_from_checkpoint)
+            target = t.resume_from_checkpoint
+            if str(target).lower() in ("latest", "auto", "true"):
+                # elastic restart: newest checkpoint of this run that is complete and undamaged, whatever world size
+                # wrote it (optimizer shards are re-sliced on load); nothing to resume from on the first launch
+                from ..ckpt import find_latest_valid_checkpoint
+                target = find_latest_valid_checkpoint(Path(t.output_dir), log=logger.warning)
+            if target:
+                self.load_checkpoint(target)
         self.model.train()
         ctx = self._ctx
         self.callbacks.fire("on_train_begin", ctx)
