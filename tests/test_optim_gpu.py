@@ -5,7 +5,7 @@ import torch
 
 pytestmark = pytest.mark.gpu
 
-SHAPES = [(300, 257), (5000,), (64, 1024)]
+SHAPES = [(300, 257), (5000,), (64, 1024), (33, 127)]      # the last one: element count not a multiple of 4
 
 
 def _pair(dtype, seed=0):

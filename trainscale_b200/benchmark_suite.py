@@ -237,6 +237,9 @@ class BenchmarkSuite:
     def run_moe(self):
         return self._run(bench_moe)
 
+    def run_optimizer_kernels(self):
+        return self._run(bench_optimizers)
+
     def run_all(self):
         for name in ("run_rms_norm", "run_layer_norm", "run_fused_gelu", "run_swiglu", "run_fp8_quantization",
                      "run_rope", "run_flash_attention", "run_cross_entropy", "run_gemm", "run_optimizer", "run_moe"):
@@ -267,6 +270,47 @@ def bench_gelu(t, small):
 
 
 CASES["gelu"] = bench_gelu
+
+
+def bench_optimizers(t, small):
+    """Per-tensor optimizer kernels (csrc/optim.cu) against the same optimizer class on its PyTorch-op path.
+    GB/s counts the bytes the update must move once (parameter read + write, gradient, state read + write)."""
+    import trainscale_b200.optim as O
+    from .ops import optim as K
+    n_side = 4096 if small else 8192
+    out = []
+    # fp32 parameters and gradients (torch ties a .grad's dtype to its parameter's)
+    cases = [("adam8bit", O.Adam8bit, dict(lr=1e-4, block_size=2048), 8 + 4 + 4, False),
+             ("lamb", O.LAMB, dict(lr=1e-3), 28 + 12, False),
+             ("sophia", O.SophiaG, dict(lr=1e-4), 24, True),
+             ("schedule_free", O.ScheduleFreeAdamW, dict(lr=1e-3), 28, False),
+             ("adopt", O.ADOPT, dict(lr=1e-3), 28, False),
+             ("adafactor", O.AdaFactor, dict(lr=1e-3, relative_step=False), 4 + 12 + 12, False)]
+    for name, cls, kw, bytes_per_el, needs_h in cases:
+        res = {}
+        for path in ("kernel", "torch"):
+            p = torch.randn(n_side, n_side, device="cuda").requires_grad_(True)
+            p.grad = torch.randn(n_side, n_side, device="cuda")
+            opt = cls([p], **kw)
+            saved = K.native_ok
+            if path == "torch":
+                K.native_ok = lambda *a, **k: False
+            try:
+                if needs_h:
+                    opt.update_hessian(1)
+                opt.step()                      # state creation outside the timed region
+                res[path] = t(opt.step, iters=5, warmup=2)
+            finally:
+                K.native_ok = saved
+            del opt, p
+            torch.cuda.empty_cache()
+        n = n_side * n_side
+        out.append(dict(name=f"{name} step {n_side}x{n_side}", ms=res["kernel"], baseline_ms=res["torch"],
+                        gbs=n * bytes_per_el / res["kernel"] / 1e6))
+    return out
+
+
+CASES["optimizers"] = bench_optimizers
 
 
 def main(argv=None) -> int:

@@ -99,6 +99,107 @@ __global__ void __launch_bounds__(OPT_THREADS) adam8bit_kernel(PT* __restrict__ 
   }
 }
 
+// Vector form for quantisation blocks of 1024+ values: every thread owns groups of 4 CONSECUTIVE values, so parameters
+// and gradients move as 16-byte (fp32) / 8-byte (bf16) accesses and the int8 state as 4-byte words instead of single
+// bytes.  VEC4 = ITEMS / 4 groups per thread.
+template <typename T>
+__device__ __forceinline__ void ld4(const T* p, long long j, float (&o)[4]) {
+  if constexpr (sizeof(T) == 2) {
+    const uint2 u = *reinterpret_cast<const uint2*>(p + j);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.y));
+    o[0] = a.x; o[1] = a.y; o[2] = b.x; o[3] = b.y;
+  } else {
+    const float4 f = *reinterpret_cast<const float4*>(p + j);
+    o[0] = f.x; o[1] = f.y; o[2] = f.z; o[3] = f.w;
+  }
+}
+template <typename T>
+__device__ __forceinline__ void st4(T* p, long long j, const float (&v)[4]) {
+  if constexpr (sizeof(T) == 2) {
+    uint2 u;
+    *reinterpret_cast<__nv_bfloat162*>(&u.x) = __floats2bfloat162_rn(v[0], v[1]);
+    *reinterpret_cast<__nv_bfloat162*>(&u.y) = __floats2bfloat162_rn(v[2], v[3]);
+    *reinterpret_cast<uint2*>(p + j) = u;
+  } else {
+    *reinterpret_cast<float4*>(p + j) = make_float4(v[0], v[1], v[2], v[3]);
+  }
+}
+
+template <typename PT, typename GT, int ITEMS>
+__global__ void __launch_bounds__(OPT_THREADS) adam8bit_vec_kernel(PT* __restrict__ p, const GT* __restrict__ g,
+                                                                   int8_t* __restrict__ m_q, float* __restrict__ m_s,
+                                                                   int8_t* __restrict__ v_q, float* __restrict__ v_s,
+                                                                   long long n, long long nblocks, float lr, float b1,
+                                                                   float b2, float eps, float wd, float bc1, float bc2) {
+  static_assert(ITEMS % 4 == 0, "vector form needs groups of 4");
+  constexpr int BS = ITEMS * OPT_THREADS, VEC4 = ITEMS / 4;
+  __shared__ float scratch[32];
+  for (long long blk = blockIdx.x; blk < nblocks; blk += gridDim.x) {
+    const float ms = m_s[blk] * (1.f / 127.f), vs = v_s[blk] * (1.f / 127.f);
+    float mn[ITEMS], rn[ITEMS];
+    float m_abs = 0.f, r_abs = 0.f;
+#pragma unroll
+    for (int i = 0; i < VEC4; ++i) {
+      const long long j = blk * BS + (static_cast<long long>(i) * OPT_THREADS + threadIdx.x) * 4;
+      const char4 mq = *reinterpret_cast<const char4*>(m_q + j);     // state arrays cover whole blocks: always in range
+      const char4 vq = *reinterpret_cast<const char4*>(v_q + j);
+      const float mqf[4] = {(float)mq.x, (float)mq.y, (float)mq.z, (float)mq.w};
+      const float vqf[4] = {(float)vq.x, (float)vq.y, (float)vq.z, (float)vq.w};
+      float pv[4] = {0.f, 0.f, 0.f, 0.f}, gv[4] = {0.f, 0.f, 0.f, 0.f};
+      const bool full = j + 3 < n;
+      if (full) {
+        ld4(p, j, pv);
+        ld4(g, j, gv);
+      } else {
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          if (j + e < n) { pv[e] = ldf(p, j + e); gv[e] = ldf(g, j + e); }
+      }
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const bool live = j + e < n;
+        const float r = vqf[e] * vs;
+        const float m = b1 * (mqf[e] * ms) + (1.f - b1) * gv[e];
+        const float v = b2 * (r * r) + (1.f - b2) * gv[e] * gv[e];
+        pv[e] = pv[e] * (1.f - lr * wd) - lr * (m / bc1) / (sqrtf(v / bc2) + eps);
+        mn[i * 4 + e] = live ? m : 0.f;
+        rn[i * 4 + e] = live ? sqrtf(v) : 0.f;
+        m_abs = fmaxf(m_abs, fabsf(mn[i * 4 + e]));
+        r_abs = fmaxf(r_abs, rn[i * 4 + e]);
+      }
+      if (full) {
+        st4(p, j, pv);
+      } else {
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          if (j + e < n) stf(p, j + e, pv[e]);
+      }
+    }
+    m_abs = fmaxf(block_max(m_abs, scratch), 1e-12f);
+    r_abs = fmaxf(block_max(r_abs, scratch), 1e-12f);
+    if (threadIdx.x == 0) {
+      m_s[blk] = m_abs;
+      v_s[blk] = r_abs;
+    }
+#pragma unroll
+    for (int i = 0; i < VEC4; ++i) {
+      const long long j = blk * BS + (static_cast<long long>(i) * OPT_THREADS + threadIdx.x) * 4;
+      char4 mq, vq;
+      mq.x = static_cast<signed char>(rintf(mn[i * 4 + 0] / m_abs * 127.f));
+      mq.y = static_cast<signed char>(rintf(mn[i * 4 + 1] / m_abs * 127.f));
+      mq.z = static_cast<signed char>(rintf(mn[i * 4 + 2] / m_abs * 127.f));
+      mq.w = static_cast<signed char>(rintf(mn[i * 4 + 3] / m_abs * 127.f));
+      vq.x = static_cast<signed char>(rintf(rn[i * 4 + 0] / r_abs * 127.f));
+      vq.y = static_cast<signed char>(rintf(rn[i * 4 + 1] / r_abs * 127.f));
+      vq.z = static_cast<signed char>(rintf(rn[i * 4 + 2] / r_abs * 127.f));
+      vq.w = static_cast<signed char>(rintf(rn[i * 4 + 3] / r_abs * 127.f));
+      *reinterpret_cast<char4*>(m_q + j) = mq;
+      *reinterpret_cast<char4*>(v_q + j) = vq;
+    }
+  }
+}
+
 // Block-wise absmax int8 codec on its own (state init, checkpoint conversion).
 template <int ITEMS>
 __global__ void __launch_bounds__(OPT_THREADS) quant8_kernel(const float* __restrict__ x, int8_t* __restrict__ q,
@@ -394,9 +495,26 @@ extern "C" int ts_adam8bit(void* p, const void* g, int kind, void* m_q, float* m
   const float bc1 = 1.f - powf(b1, (float)step), bc2 = 1.f - powf(b2, (float)step);
   const long long cap = static_cast<long long>(sm_count()) * 8;
   const int grid = (int)(nblocks < cap ? nblocks : cap);
-  DISPATCH_PG(kind, DISPATCH_ITEMS(items, (adam8bit_kernel<PT, GT, IT><<<grid, OPT_THREADS, 0, ST(stream)>>>(
-                                              (PT*)p, (const GT*)g, (int8_t*)m_q, m_s, (int8_t*)v_q, v_s, n, nblocks, lr,
-                                              b1, b2, eps, wd, bc1, bc2))));
+  // the vector form needs 16-byte aligned parameter / gradient / state bases (torch allocations are)
+  const bool aligned = ((reinterpret_cast<uintptr_t>(p) | reinterpret_cast<uintptr_t>(g) |
+                         reinterpret_cast<uintptr_t>(m_q) | reinterpret_cast<uintptr_t>(v_q)) & 15u) == 0;
+  if (items == 1 || !aligned) {
+    DISPATCH_PG(kind, DISPATCH_ITEMS(items, (adam8bit_kernel<PT, GT, IT><<<grid, OPT_THREADS, 0, ST(stream)>>>(
+                                                (PT*)p, (const GT*)g, (int8_t*)m_q, m_s, (int8_t*)v_q, v_s, n, nblocks,
+                                                lr, b1, b2, eps, wd, bc1, bc2))));
+  } else {
+    switch (items) {
+      case 4: DISPATCH_PG(kind, (adam8bit_vec_kernel<PT, GT, 4><<<grid, OPT_THREADS, 0, ST(stream)>>>(
+                                    (PT*)p, (const GT*)g, (int8_t*)m_q, m_s, (int8_t*)v_q, v_s, n, nblocks, lr, b1, b2,
+                                    eps, wd, bc1, bc2))); break;
+      case 8: DISPATCH_PG(kind, (adam8bit_vec_kernel<PT, GT, 8><<<grid, OPT_THREADS, 0, ST(stream)>>>(
+                                    (PT*)p, (const GT*)g, (int8_t*)m_q, m_s, (int8_t*)v_q, v_s, n, nblocks, lr, b1, b2,
+                                    eps, wd, bc1, bc2))); break;
+      default: DISPATCH_PG(kind, (adam8bit_vec_kernel<PT, GT, 16><<<grid, OPT_THREADS, 0, ST(stream)>>>(
+                                     (PT*)p, (const GT*)g, (int8_t*)m_q, m_s, (int8_t*)v_q, v_s, n, nblocks, lr, b1, b2,
+                                     eps, wd, bc1, bc2))); break;
+    }
+  }
   return (int)cudaGetLastError();
 }
 
