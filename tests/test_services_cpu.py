@@ -290,3 +290,24 @@ def test_adapter_save_load_and_attention_interface(tmp_path):
     with compilation_debug_mode(log=lambda s: None):
         assert float(mg.run(lambda x: x + 1, torch.ones(2))[0]) == 2.0
     assert get_compilation_stats()["eager_calls"] == before + 1 and get_compilation_stats(mg)["signatures"] == 0
+
+
+def test_tracing_utilities(tmp_path):
+    import torch
+    from trainscale_b200.utils import tracing as T
+    timer = T.PhaseTimer("cpu")
+    for _ in range(2):
+        with timer("forward"):
+            torch.randn(8, 8) @ torch.randn(8, 8)
+    s = timer.summary()
+    assert s["forward"]["count"] == 2 and s["forward"]["total_ms"] >= 0
+    T.enable_nvtx(True)
+    with T.nvtx_range("phase"):          # without a GPU the range is a no-op, with one it pushes / pops
+        pass
+    T.nvtx_mark("tick")
+    T.enable_nvtx(False)
+    with T.profile_steps(tmp_path, wait=0, warmup=1, active=2) as prof:
+        for _ in range(4):
+            torch.randn(32, 32) @ torch.randn(32, 32)
+            prof.step()
+    assert (tmp_path / "trace_0.json").stat().st_size > 0

@@ -39,6 +39,8 @@ from ..models.llama import LlamaConfig, LlamaForCausalLM, build_model, preset_co
 from ..parallel.flat_engine import EngineConfig, FlatShardedEngine
 from ..schedulers import create_scheduler
 
+from ..utils.tracing import nvtx_range
+
 logger = logging.getLogger("trainscale_b200")
 
 STRATEGY_ALIASES = {
@@ -405,13 +407,16 @@ class SOTATrainer:
                     self.callbacks.fire("on_step_begin", ctx)
                     self.throughput.start_step()
                     step_tokens = 0
-                batch = self._to_device(batch)
+                with nvtx_range("h2d_batch"):
+                    batch = self._to_device(batch)
                 step_tokens += int(batch["input_ids"].numel())
                 sync = (step + 1) % gas == 0
                 if self.engine is not None:
-                    loss, ntok = self._loss_and_backward(batch, 1.0 / gas)
+                    with nvtx_range("forward_backward"):
+                        loss, ntok = self._loss_and_backward(batch, 1.0 / gas)
                     if sync:
-                        last_gn = self.engine.step(self.optimizer.param_groups[0]["lr"])
+                        with nvtx_range("reduce_clip_update"):
+                            last_gn = self.engine.step(self.optimizer.param_groups[0]["lr"])
                 else:
                     loss, ntok = self._forward_loss(batch, 1.0 / gas)
                     gn = self._generic_backward_step(loss, sync)
