@@ -493,7 +493,7 @@ class SOTATrainer:
         values that are on the host already (log time).  The update of a step whose gradients are non-finite has been
         skipped on the device by the engine (`EngineConfig.skip_nonfinite`), with no host round trip; this check is
         the visible trace of that, and after `max_nonfinite_windows` consecutive bad log windows training stops with
-        GradientOverflowError instead of burning the rest of the budget."""
+        GradientOverflowError instead of running on with a diverged model."""
         from ..core.errors import GradientOverflowError
         lv = float(loss) if not isinstance(loss, float) else loss
         where = f" at step {step}" if step is not None else ""
