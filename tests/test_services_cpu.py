@@ -311,3 +311,42 @@ def test_tracing_utilities(tmp_path):
             torch.randn(32, 32) @ torch.randn(32, 32)
             prof.step()
     assert (tmp_path / "trace_0.json").stat().st_size > 0
+
+
+def test_qwen2_bias_and_mixtral_moe_decoders_match_huggingface():
+    import pytest
+    import torch
+    transformers = pytest.importorskip("transformers")
+    from trainscale_b200.models.llama import build_model, preset_config
+    from trainscale_b200.registry import patch_model
+    torch.manual_seed(0)
+    ids = torch.randint(0, 64, (2, 12))
+    kw = dict(vocab_size=64, hidden_size=32, intermediate_size=48, num_hidden_layers=2, num_attention_heads=4,
+              num_key_value_heads=2)
+    cases = (transformers.MixtralForCausalLM(transformers.MixtralConfig(num_local_experts=4, num_experts_per_tok=2,
+                                                                         sliding_window=None, **kw)),
+             transformers.Qwen2ForCausalLM(transformers.Qwen2Config(**kw)))
+    for hf in cases:
+        hf = hf.eval()
+        with torch.no_grad():
+            for n, p in hf.named_parameters():
+                if n.endswith("bias"):
+                    p.normal_(0, 0.5)
+            ref = hf(ids).logits
+            m = patch_model(hf, dtype=torch.float32, device="cpu").eval()
+            torch.testing.assert_close(m(ids).logits, ref, rtol=1e-5, atol=1e-6)
+            back = type(hf)(hf.config).eval()
+            assert not back.load_state_dict(m.to_hf_state_dict(), strict=False).missing_keys
+            torch.testing.assert_close(back(ids).logits, ref)
+    # a mixture-of-experts model trains through the ordinary path (router and biases receive gradients, balance loss on)
+    cfg = preset_config("moe-tiny", vocab_size=128, router_aux_loss_coef=0.01, attention_bias=True)
+    m = build_model(cfg, dtype=torch.float32, device="cpu", seed=0)
+    assert m.num_parameters() == cfg.num_parameters()
+    ids = torch.randint(0, 128, (2, 16))
+    base = m(ids, labels=ids).loss
+    base.backward()
+    assert float(m.model.layers[0].mlp.router.grad.abs().sum()) > 0
+    assert float(m.model.layers[0].self_attn.bqkv.grad.abs().sum()) > 0
+    m.eval()
+    assert float(m(ids, labels=ids).loss) < float(base)            # no balance term outside training
+    assert m.hf_config_dict()["model_type"] == "mixtral"

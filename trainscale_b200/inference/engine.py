@@ -296,15 +296,20 @@ class ModelRunner:
         for li, layer in enumerate(m.layers):
             h, res = layer.input_layernorm(x, res)
             qkv = self._lin(li, "wqkv", layer.self_attn.wqkv, h, adapter_ids)
+            if layer.self_attn.bqkv is not None:
+                qkv = qkv + layer.self_attn.bqkv
             qkv = rope.apply_rope_qkv(qkv.unsqueeze(0), c.num_attention_heads + c.num_key_value_heads, c.head_dim,
                                       self.cos, self.sin, pos32.unsqueeze(0), qkv.shape[0], 0, c.rope_interleaved)[0]
             self._write_cache(li, qkv, slots)
             a = self._attend(li, qkv, seq_ids, q_lens, fresh, block_table, seq_lens)
             a = self._lin(li, "wo", layer.self_attn.wo, a, adapter_ids)
             h, res = layer.post_attention_layernorm(a, res)
-            x = self._lin(li, "w_down", layer.mlp.w_down,
-                          activation.glu(self._lin(li, "w_gate_up", layer.mlp.w_gate_up, h, adapter_ids), layer.mlp.act),
-                          adapter_ids)
+            if hasattr(layer.mlp, "router"):            # mixture of experts: the block routes by itself
+                x = layer.mlp(h)
+            else:
+                x = self._lin(li, "w_down", layer.mlp.w_down,
+                              activation.glu(self._lin(li, "w_gate_up", layer.mlp.w_gate_up, h, adapter_ids),
+                                             layer.mlp.act), adapter_ids)
         x, _ = m.norm(x, res)
         last = torch.tensor(q_lens, device=self.device).cumsum(0) - 1
         return x[last]

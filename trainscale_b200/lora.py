@@ -134,6 +134,8 @@ def get_peft_model(model, r: int = 16, lora_alpha: float = 32.0, lora_dropout: f
     for li, layer in enumerate(model.model.layers):
         for kind, mod in (("attn", layer.self_attn), ("mlp", layer.mlp)):
             inner = getattr(mod, "inner", mod)
+            if hasattr(inner, "router"):
+                continue                      # expert weights are 3-D; adapters attach to the attention projections only
             by_weight: dict[str, list[LoRALinear]] = {}
             for t in wanted:
                 k, wname, row0, rows = targets[t]

@@ -17,6 +17,7 @@ from typing import Any
 
 import torch
 import torch.nn as nn
+import torch.nn.functional as F
 from torch.utils.checkpoint import checkpoint
 
 from ..ops import activation, attention, cross_entropy, fused_blocks, gemm, norm, rope
@@ -43,6 +44,11 @@ class LlamaConfig:
     final_logit_softcap: float = 0.0
     initializer_range: float = 0.02
     model_type: str = "llama"
+    attention_bias: bool = False            # q / k / v projection biases (Qwen2 family)
+    num_local_experts: int = 0              # > 0: every MLP is a top-k mixture of experts (Mixtral / Qwen-MoE family)
+    num_experts_per_tok: int = 2
+    norm_topk_prob: bool = True
+    router_aux_loss_coef: float = 0.0       # load-balancing loss weight (0 = off)
 
     def __post_init__(self):
         if self.num_key_value_heads is None:
@@ -61,7 +67,11 @@ class LlamaConfig:
     def num_parameters(self, include_embeddings: bool = True) -> int:
         H, I, L, V = self.hidden_size, self.intermediate_size, self.num_hidden_layers, self.vocab_size
         D, Hq, Hkv = self.head_dim, self.num_attention_heads, self.num_key_value_heads
-        per_layer = (Hq + 2 * Hkv) * D * H + Hq * D * H + 3 * H * I + 2 * H
+        E = self.num_local_experts
+        mlp = 3 * H * I if E == 0 else E * (3 * H * I + H)
+        per_layer = (Hq + 2 * Hkv) * D * H + Hq * D * H + mlp + 2 * H
+        if self.attention_bias:
+            per_layer += (Hq + 2 * Hkv) * D
         n = L * per_layer + H
         if include_embeddings:
             n += V * H * (1 if self.tie_word_embeddings else 2)
@@ -71,7 +81,8 @@ class LlamaConfig:
         """Training FLOPs per token: 6 * matmul params + attention (12 * L * d_attn * S, halved if causal)."""
         H, I, L, V = self.hidden_size, self.intermediate_size, self.num_hidden_layers, self.vocab_size
         D, Hq, Hkv = self.head_dim, self.num_attention_heads, self.num_key_value_heads
-        mm = L * ((Hq + 2 * Hkv) * D * H + Hq * D * H + 3 * H * I) + V * H
+        active = 3 * H * I * (self.num_experts_per_tok if self.num_local_experts else 1)     # experts a token visits
+        mm = L * ((Hq + 2 * Hkv) * D * H + Hq * D * H + active) + V * H
         attn = 12 * L * Hq * D * seq_len * (0.5 if causal else 1.0)
         return 6.0 * mm + attn
 
@@ -93,7 +104,13 @@ PRESETS: dict[str, dict[str, Any]] = {
                        model_type="mistral"),
     "qwen2-7b": dict(vocab_size=152064, hidden_size=3584, intermediate_size=18944, num_hidden_layers=28,
                      num_attention_heads=28, num_key_value_heads=4, rope_theta=1000000.0, rms_norm_eps=1e-6,
-                     model_type="qwen2"),
+                     model_type="qwen2", attention_bias=True),
+    "mixtral-8x7b": dict(vocab_size=32000, hidden_size=4096, intermediate_size=14336, num_hidden_layers=32,
+                         num_attention_heads=32, num_key_value_heads=8, rope_theta=1000000.0, model_type="mixtral",
+                         num_local_experts=8, num_experts_per_tok=2, max_position_embeddings=32768),
+    "moe-tiny": dict(vocab_size=32000, hidden_size=256, intermediate_size=512, num_hidden_layers=2,
+                     num_attention_heads=4, num_key_value_heads=2, model_type="mixtral", num_local_experts=4,
+                     num_experts_per_tok=2),
 }
 
 
@@ -138,11 +155,15 @@ class LlamaAttention(nn.Module):
         self.n_heads, self.n_kv, self.hd = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
         self.wqkv = nn.Parameter(torch.empty((self.n_heads + 2 * self.n_kv) * self.hd, cfg.hidden_size))
         self.wo = nn.Parameter(torch.empty(cfg.hidden_size, self.n_heads * self.hd))
+        self.bqkv = nn.Parameter(torch.zeros((self.n_heads + 2 * self.n_kv) * self.hd)) if cfg.attention_bias else None
         self.lora = None      # nn.ModuleDict of low-rank adapters keyed by weight name (see lora.py)
         self.cp_group = None  # context-parallel process group (ring attention) when set
 
     def forward(self, x, cos, sin, position_ids=None, cu_seqlens=None, doc_ids=None, kv_cache=None):
-        return self.attend(_lin(self, x, "wqkv"), cos, sin, position_ids, cu_seqlens, doc_ids, kv_cache)
+        qkv = _lin(self, x, "wqkv")
+        if self.bqkv is not None:
+            qkv = qkv + self.bqkv
+        return self.attend(qkv, cos, sin, position_ids, cu_seqlens, doc_ids, kv_cache)
 
     def attend(self, qkv, cos, sin, position_ids=None, cu_seqlens=None, doc_ids=None, kv_cache=None):
         """Everything after the fused q|k|v projection: rotary embedding, attention, output projection."""
@@ -172,18 +193,55 @@ class LlamaMLP(nn.Module):
         return _lin(self, activation.glu(_lin(self, x, "w_gate_up"), self.act), "w_down")
 
 
+class LlamaMoEMLP(nn.Module):
+    """Top-k mixture of gated experts (Mixtral layout: router [E, H], experts' gate|up [E, 2I, H] and down [E, H, I]).
+    Routing = softmax over all experts, top-k, optional renormalisation.  On bf16 CUDA tensors the router top-k, the
+    device-side routing plan, the permute into 128-aligned expert segments, two grouped tcgen05 GEMMs and the weighted
+    combine are the kernels of ops/moe.py; elsewhere a loop over the experts gives the same result."""
+
+    def __init__(self, cfg: LlamaConfig):
+        super().__init__()
+        E, H, I = cfg.num_local_experts, cfg.hidden_size, cfg.intermediate_size
+        self.act, self.top_k, self.norm_topk = cfg.hidden_act, cfg.num_experts_per_tok, cfg.norm_topk_prob
+        self.aux_coef = cfg.router_aux_loss_coef
+        self.router = nn.Parameter(torch.empty(E, H))
+        self.w_gate_up = nn.Parameter(torch.empty(E, 2 * I, H))
+        self.w_down = nn.Parameter(torch.empty(E, H, I))
+        self.lora = None
+        self.aux_loss: torch.Tensor | None = None
+
+    def forward(self, x):
+        from ..ops import moe as moe_ops
+        shape = x.shape
+        x2 = x.reshape(-1, shape[-1])
+        logits = F.linear(x2, self.router)                       # [T, E]: a few experts wide, not worth a tiled GEMM
+        w, ids, probs = moe_ops.topk_softmax(logits, self.top_k, self.norm_topk)     # kernel on CUDA, torch ops on CPU
+        if moe_ops.available(x2):
+            y = moe_ops.moe_ffn(x2, ids, w.to(x2.dtype), self.w_gate_up, self.w_down, self.act)
+        else:
+            y = moe_ops.moe_ffn_reference(x2, ids, w, self.w_gate_up, self.w_down, self.act)
+        if self.aux_coef > 0 and self.training:
+            # Switch-style balance term: E * sum_e (fraction of routed slots on e) * (mean router probability of e)
+            E = self.router.shape[0]
+            frac = torch.zeros(E, device=x.device).index_add_(0, ids.reshape(-1).long(),
+                                                              torch.ones(ids.numel(), device=x.device)) / ids.numel()
+            self.aux_loss = E * (frac * probs.mean(0)).sum()
+        return y.view(shape)
+
+
 class LlamaDecoderLayer(nn.Module):
     def __init__(self, cfg: LlamaConfig):
         super().__init__()
         self.input_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps)
         self.self_attn = LlamaAttention(cfg)
         self.post_attention_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps)
-        self.mlp = LlamaMLP(cfg)
+        self.mlp = LlamaMoEMLP(cfg) if cfg.num_local_experts > 0 else LlamaMLP(cfg)
         self.op_selective = False   # keep only GEMM-side tensors; norm / GLU outputs are rebuilt in backward
 
     def forward(self, x, residual, cos, sin, position_ids=None, cu_seqlens=None, doc_ids=None, kv_cache=None):
         if self.op_selective and self.training and kv_cache is None and self.self_attn.lora is None \
-                and self.mlp.lora is None and not getattr(self.mlp, "fp8", False):
+                and self.mlp.lora is None and not getattr(self.mlp, "fp8", False) and self.self_attn.bqkv is None \
+                and isinstance(self.mlp, LlamaMLP):
             n1, n2 = self.input_layernorm, self.post_attention_layernorm
             qkv, residual = fused_blocks.norm_linear(x, residual, n1.weight, self.self_attn.wqkv, n1.eps)
             a = self.self_attn.attend(qkv, cos, sin, position_ids, cu_seqlens, doc_ids, None)
@@ -301,7 +359,9 @@ class LlamaForCausalLM(nn.Module):
             gen = torch.Generator(device="cpu").manual_seed(seed)
         std = self.config.initializer_range
         for name, p in self.named_parameters():
-            if p.dim() == 1:
+            if name.endswith("bqkv"):
+                p.zero_()
+            elif p.dim() == 1:
                 p.fill_(1.0)
             else:
                 s = std
@@ -358,6 +418,10 @@ class LlamaForCausalLM(nn.Module):
             loss, count = cross_entropy.fused_linear_cross_entropy(
                 h, self.head_weight, tgt, ignore_index, label_smoothing, 1.0, self.config.final_logit_softcap,
                 self.loss_chunk_tokens, "mean", loss_scale)
+            if self.config.num_local_experts > 0 and self.config.router_aux_loss_coef > 0 and self.training:
+                aux = [l.mlp.aux_loss for l in self.model.layers if getattr(l.mlp, "aux_loss", None) is not None]
+                if aux:
+                    loss = loss + self.config.router_aux_loss_coef * loss_scale * torch.stack(aux).mean()
             out.loss, out.num_tokens = loss, count
         if return_logits or (return_logits is None and labels is None):
             out.logits = self.logits(h)
@@ -407,11 +471,23 @@ class LlamaForCausalLM(nn.Module):
             p = f"model.layers.{i}."
             attn, mlp = getattr(l.self_attn, "inner", l.self_attn), getattr(l.mlp, "inner", l.mlp)
             q, k, v = attn.wqkv.detach().split((Hq // ws * D, Hkv // ws * D, Hkv // ws * D), dim=0)
-            g, u = mlp.w_gate_up.detach().split((I // ws, I // ws), dim=0)
-            for name, t, dim in (("self_attn.q_proj", q, 0), ("self_attn.k_proj", k, 0), ("self_attn.v_proj", v, 0),
-                                 ("self_attn.o_proj", attn.wo, 1), ("mlp.gate_proj", g, 0), ("mlp.up_proj", u, 0),
-                                 ("mlp.down_proj", mlp.w_down, 1)):
+            items = [("self_attn.q_proj", q, 0), ("self_attn.k_proj", k, 0), ("self_attn.v_proj", v, 0),
+                     ("self_attn.o_proj", attn.wo, 1)]
+            if isinstance(mlp, LlamaMoEMLP):
+                if ws > 1:
+                    raise NotImplementedError("mixture-of-experts layers are sharded by expert parallelism, not tp")
+                put(p + "mlp.gate.weight", mlp.router.detach())
+                put(p + "mlp.experts.gate_up_proj", mlp.w_gate_up.detach())
+                put(p + "mlp.experts.down_proj", mlp.w_down.detach())
+            else:
+                g, u = mlp.w_gate_up.detach().split((I // ws, I // ws), dim=0)
+                items += [("mlp.gate_proj", g, 0), ("mlp.up_proj", u, 0), ("mlp.down_proj", mlp.w_down, 1)]
+            for name, t, dim in items:
                 put(p + name + ".weight", full(t, dim))
+            if attn.bqkv is not None:
+                bq, bk, bv = attn.bqkv.detach().split((Hq // ws * D, Hkv // ws * D, Hkv // ws * D), dim=0)
+                for name, t in (("q_proj", bq), ("k_proj", bk), ("v_proj", bv)):
+                    put(p + f"self_attn.{name}.bias", full(t, 0))
             put(p + "input_layernorm.weight", l.input_layernorm.weight.detach())
             put(p + "post_attention_layernorm.weight", l.post_attention_layernorm.weight.detach())
         if self.lm_head is not None and last:
@@ -451,8 +527,20 @@ class LlamaForCausalLM(nn.Module):
             attn, mlp = getattr(l.self_attn, "inner", l.self_attn), getattr(l.mlp, "inner", l.mlp)
             put(attn.wqkv, [get(p + f"self_attn.{n}_proj.weight", 0) for n in "qkv"])
             put(attn.wo, [get(p + "self_attn.o_proj.weight", 1)])
-            put(mlp.w_gate_up, [get(p + "mlp.gate_proj.weight", 0), get(p + "mlp.up_proj.weight", 0)])
-            put(mlp.w_down, [get(p + "mlp.down_proj.weight", 1)])
+            if attn.bqkv is not None:
+                put(attn.bqkv, [get(p + f"self_attn.{n}_proj.bias", 0) for n in "qkv"])
+            if isinstance(mlp, LlamaMoEMLP):
+                put(mlp.router, [get(p + "mlp.gate.weight")])
+                if p + "mlp.experts.gate_up_proj" in sd or p + "mlp.experts.0.w1.weight" not in sd:
+                    put(mlp.w_gate_up, [get(p + "mlp.experts.gate_up_proj")])
+                    put(mlp.w_down, [get(p + "mlp.experts.down_proj")])
+                else:       # per-expert layout of older Mixtral checkpoints: w1 = gate, w3 = up, w2 = down
+                    for e in range(mlp.router.shape[0]):
+                        put(mlp.w_gate_up[e], [get(p + f"mlp.experts.{e}.w1.weight"), get(p + f"mlp.experts.{e}.w3.weight")])
+                        put(mlp.w_down[e], [get(p + f"mlp.experts.{e}.w2.weight")])
+            else:
+                put(mlp.w_gate_up, [get(p + "mlp.gate_proj.weight", 0), get(p + "mlp.up_proj.weight", 0)])
+                put(mlp.w_down, [get(p + "mlp.down_proj.weight", 1)])
             put(l.input_layernorm.weight, [get(p + "input_layernorm.weight")])
             put(l.post_attention_layernorm.weight, [get(p + "post_attention_layernorm.weight")])
         if self.lm_head is not None:
@@ -463,7 +551,11 @@ class LlamaForCausalLM(nn.Module):
 
     def hf_config_dict(self) -> dict:
         c = self.config
-        return {"architectures": ["LlamaForCausalLM"], "model_type": "llama", "vocab_size": c.vocab_size,
+        arch, mt = ("MixtralForCausalLM", "mixtral") if c.num_local_experts > 0 else \
+            ("Qwen2ForCausalLM", "qwen2") if c.attention_bias else ("LlamaForCausalLM", "llama")
+        extra = {"num_local_experts": c.num_local_experts, "num_experts_per_tok": c.num_experts_per_tok,
+                 "router_aux_loss_coef": c.router_aux_loss_coef} if c.num_local_experts > 0 else {}
+        return {**extra, "architectures": [arch], "model_type": mt, "vocab_size": c.vocab_size,
                 "hidden_size": c.hidden_size, "intermediate_size": c.intermediate_size,
                 "num_hidden_layers": c.num_hidden_layers, "num_attention_heads": c.num_attention_heads,
                 "num_key_value_heads": c.num_key_value_heads, "head_dim": c.head_dim, "rms_norm_eps": c.rms_norm_eps,

@@ -168,6 +168,18 @@ def moe_ffn(x2: torch.Tensor, expert_ids: torch.Tensor, weights: torch.Tensor, w
     return _CombineFn.apply(y, weights, plan)
 
 
+def moe_ffn_reference(x2: torch.Tensor, expert_ids: torch.Tensor, weights: torch.Tensor, w_gate_up: torch.Tensor,
+                      w_down: torch.Tensor, act: str = "silu") -> torch.Tensor:
+    """Same result as `moe_ffn` by a loop over the experts (fp32 accumulation); differentiable.  CPU / non-bf16 path."""
+    out = torch.zeros(x2.shape, dtype=torch.float32, device=x2.device)
+    for e in range(w_gate_up.shape[0]):
+        tok, slot = (expert_ids == e).nonzero(as_tuple=True)
+        if tok.numel():
+            h = activation.glu(x2[tok].float() @ w_gate_up[e].float().t(), act)
+            out = out.index_add(0, tok, (h @ w_down[e].float().t()) * weights[tok, slot].float().unsqueeze(1))
+    return out.to(x2.dtype)
+
+
 class _TopKSoftmaxFn(torch.autograd.Function):
     """Router softmax + top-k on the device kernel; the (small, [T, E]) backward is written with torch ops."""
 

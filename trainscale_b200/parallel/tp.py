@@ -302,9 +302,16 @@ def shard_llama_state_for_tp(model, tp_size: int, tp_rank: int) -> None:
     D, Hq, Hkv, I = cfg.head_dim, cfg.num_attention_heads, cfg.num_key_value_heads, cfg.intermediate_size
     assert Hq % tp_size == 0 and Hkv % tp_size == 0 and I % tp_size == 0, "heads / ffn must divide by the TP size"
     hq, hkv, i_loc = Hq // tp_size, Hkv // tp_size, I // tp_size
+    if getattr(cfg, "num_local_experts", 0) > 0:
+        raise NotImplementedError("mixture-of-experts layers are distributed by expert parallelism (parallel/ep.py)")
     with torch.no_grad():
         for layer in model.model.layers:
             a, m = layer.self_attn, layer.mlp
+            if getattr(a, "bqkv", None) is not None:
+                bq, bk, bv = a.bqkv.data.split((Hq * D, Hkv * D, Hkv * D), dim=0)
+                a.bqkv = nn.Parameter(torch.cat((bq[tp_rank * hq * D:(tp_rank + 1) * hq * D],
+                                                 bk[tp_rank * hkv * D:(tp_rank + 1) * hkv * D],
+                                                 bv[tp_rank * hkv * D:(tp_rank + 1) * hkv * D])).contiguous())
             q, k, v = a.wqkv.data.split((Hq * D, Hkv * D, Hkv * D), dim=0)
             a.wqkv = nn.Parameter(torch.cat((q[tp_rank * hq * D:(tp_rank + 1) * hq * D],
                                              k[tp_rank * hkv * D:(tp_rank + 1) * hkv * D],

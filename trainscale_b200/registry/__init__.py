@@ -239,7 +239,8 @@ register_models_from_meta([
     ModelInfo("granite", "ibm-granite", ("2B", "8B"), "GraniteForCausalLM"),
     ModelInfo("codellama", "codellama", ("7B", "13B", "34B")), ModelInfo("starcoder2", "bigcode", ("3B", "7B", "15B"), "Starcoder2ForCausalLM", mlp="gelu", norm="layernorm", supported=False),
     ModelInfo("mixtral", "mistralai", ("8x7B", "8x22B"), "MixtralForCausalLM", mlp="moe"),
-    ModelInfo("qwen_moe", "Qwen", ("A2.7B", "A14B"), "Qwen2MoeForCausalLM", mlp="moe"),
+    ModelInfo("qwen_moe", "Qwen", ("A2.7B", "A14B"), "Qwen2MoeForCausalLM", mlp="moe", supported=False,
+              notes="shared expert + per-layer dense/sparse mix not covered"),
     ModelInfo("llava", "llava-hf", ("7B", "13B"), "LlavaForConditionalGeneration", supported=False, notes="vision tower not covered"),
 ])
 
@@ -263,7 +264,17 @@ def convert_hf_llama(hf_model, dtype=torch.bfloat16, device=None):
                       rms_norm_eps=c.rms_norm_eps, rope_theta=getattr(c, "rope_theta", None) or
                       (getattr(c, "rope_parameters", None) or {}).get("rope_theta", 10000.0),
                       max_position_embeddings=c.max_position_embeddings,
-                      tie_word_embeddings=bool(getattr(c, "tie_word_embeddings", False)))
+                      tie_word_embeddings=bool(getattr(c, "tie_word_embeddings", False)),
+                      sliding_window=getattr(c, "sliding_window", None) if getattr(c, "use_sliding_window", True) else None,
+                      # Qwen2 has q / k / v biases without a config flag; Llama-style configs say so explicitly
+                      attention_bias=any(k.endswith("q_proj.bias") for k in hf_model.state_dict()),
+                      num_local_experts=int(getattr(c, "num_local_experts", 0) or 0),
+                      num_experts_per_tok=int(getattr(c, "num_experts_per_tok", 2) or 2),
+                      router_aux_loss_coef=float(getattr(c, "router_aux_loss_coef", 0.0) or 0.0)
+                      if getattr(c, "output_router_logits", False) else 0.0,
+                      model_type=getattr(c, "model_type", "llama"))
+    if any(k.endswith("o_proj.bias") for k in hf_model.state_dict()):
+        raise ValueError("output-projection biases are not supported by the framework decoder")
     m = build_model(cfg, dtype=dtype, device=device)
     m.load_hf_state_dict({k: v for k, v in hf_model.state_dict().items()}, strict=not cfg.tie_word_embeddings)
     return m
@@ -284,8 +295,8 @@ class KernelPatcher:
         if isinstance(model, LlamaForCausalLM):
             return model
         arch = type(model).__name__
-        if arch in ("LlamaForCausalLM", "MistralForCausalLM", "Qwen2ForCausalLM", "GraniteForCausalLM") and \
-                not getattr(model.config, "attention_bias", False):
+        if arch in ("LlamaForCausalLM", "MistralForCausalLM", "Qwen2ForCausalLM", "MixtralForCausalLM") and \
+                not any(k.endswith("o_proj.bias") for k in model.state_dict()):
             return convert_hf_llama(model, dtype, device)
         return model
 
