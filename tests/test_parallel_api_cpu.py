@@ -356,3 +356,9 @@ def test_registry_module_patchers_keep_the_maths():
     want = ln(x)
     assert auto_patch_layernorm(ln) == 1
     torch.testing.assert_close(ln(x), want)
+
+
+def test_expert_parallel_decoder_two_ranks():
+    r = launch("ep_decoder.py", 2, 29697)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    assert r.stdout.count("ok=True") == 2

@@ -345,3 +345,87 @@ class HierarchicalMoE(nn.Module):
     @property
     def aux_loss(self):
         return sum(l.aux_loss for l in self.groups)
+
+
+# ------------------------------------------------------------------------------------------------ decoder integration
+class ExpertParallelDecoderMoE(nn.Module):
+    """The decoder's mixture-of-experts MLP (`models.llama.LlamaMoEMLP`) with its experts sharded over an
+    expert-parallel group: rank r keeps experts [r E/W, (r+1) E/W); the router is replicated.  Tokens are sorted by
+    expert, sent to the owners with one all-to-all, run through the local experts, sent back and combined with the
+    routing weights.  Gradients of the local experts are complete on their owner (every token that chose them was
+    there); the router's gradient is a data-parallel gradient like any replicated parameter."""
+
+    def __init__(self, mlp, group):
+        super().__init__()
+        E = mlp.router.shape[0]
+        self.dispatcher = AllToAllDispatcher(group, E)
+        El, r = self.dispatcher.local_experts, self.dispatcher.rank
+        self.act, self.top_k, self.norm_topk, self.aux_coef = mlp.act, mlp.top_k, mlp.norm_topk, mlp.aux_coef
+        self.num_experts = E
+        self.router = nn.Parameter(mlp.router.detach().clone())
+        self.w_gate_up = nn.Parameter(mlp.w_gate_up.detach()[r * El:(r + 1) * El].clone())
+        self.w_down = nn.Parameter(mlp.w_down.detach()[r * El:(r + 1) * El].clone())
+        for p in (self.w_gate_up, self.w_down):
+            p.expert_parallel = True          # not replicated over the ep group: no gradient averaging across it
+        self.lora = None
+        self.aux_loss = None
+
+    def _local_experts(self, rows: torch.Tensor, per_expert: list[int]) -> torch.Tensor:
+        outs, off = [], 0
+        for e, n in enumerate(per_expert):
+            if n:
+                xe = rows[off:off + n]
+                outs.append(gemm.linear(activation.glu(gemm.linear(xe, self.w_gate_up[e]), self.act), self.w_down[e]))
+                off += n
+        return torch.cat(outs) if outs else rows.new_zeros(0, rows.shape[-1])
+
+    def forward(self, x):
+        from ..ops import moe as moe_ops
+        shape = x.shape
+        x2 = x.reshape(-1, shape[-1])
+        logits = F.linear(x2, self.router)
+        w, ids, probs = moe_ops.topk_softmax(logits, self.top_k, self.norm_topk)
+        d = self.dispatcher
+        xs, order, counts = permute_tokens(x2, ids, self.num_experts)
+        recv, recv_counts, book = d.dispatch(xs, counts)
+        W, El = d.world, d.local_experts
+        rc = recv_counts.tolist()
+        offs, o = [[0] * El for _ in range(W)], 0
+        for r in range(W):
+            for e in range(El):
+                offs[r][e] = o
+                o += rc[r][e]
+        gather_idx = torch.cat([torch.arange(offs[r][e], offs[r][e] + rc[r][e], device=x2.device)
+                                for e in range(El) for r in range(W)]) if o > 0 else \
+            torch.zeros(0, dtype=torch.long, device=x2.device)
+        ye = self._local_experts(recv[gather_idx], [sum(rc[r][e] for r in range(W)) for e in range(El)])
+        back = torch.zeros_like(recv)
+        back = back.index_copy(0, gather_idx, ye.to(back.dtype)) if o > 0 else back
+        ys = d.combine(back, book)
+        y = unpermute_tokens(ys, order, w.to(ys.dtype), x2.shape[0])
+        if self.aux_coef > 0 and self.training:
+            frac = torch.zeros(self.num_experts, device=x.device).index_add_(
+                0, ids.reshape(-1).long(), torch.ones(ids.numel(), device=x.device)) / ids.numel()
+            self.aux_loss = self.num_experts * (frac * probs.mean(0)).sum()
+        return y.view(shape)
+
+    def full_expert_weights(self):
+        """(w_gate_up [E, 2I, H], w_down [E, H, I]) gathered over the group (collective)."""
+        out = []
+        for t in (self.w_gate_up, self.w_down):
+            parts = [torch.empty_like(t) for _ in range(self.dispatcher.world)]
+            dist.all_gather(parts, t.detach().contiguous(), group=self.dispatcher.group)
+            out.append(torch.cat(parts))
+        return tuple(out)
+
+
+def shard_model_for_expert_parallel(model, group) -> int:
+    """Replace every mixture-of-experts MLP of a framework decoder by its expert-parallel form.  Returns the number of
+    layers converted.  Call before the data-parallel engine is built (parameters are re-created)."""
+    from ..models.llama import LlamaMoEMLP
+    n = 0
+    for layer in model.model.layers:
+        if isinstance(layer.mlp, LlamaMoEMLP):
+            layer.mlp = ExpertParallelDecoderMoE(layer.mlp, group)
+            n += 1
+    return n
