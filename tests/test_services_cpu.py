@@ -325,18 +325,20 @@ def test_qwen2_bias_and_mixtral_moe_decoders_match_huggingface():
               num_key_value_heads=2)
     cases = (transformers.MixtralForCausalLM(transformers.MixtralConfig(num_local_experts=4, num_experts_per_tok=2,
                                                                          sliding_window=None, **kw)),
-             transformers.Qwen2ForCausalLM(transformers.Qwen2Config(**kw)))
+             transformers.Qwen2ForCausalLM(transformers.Qwen2Config(**kw)),
+             transformers.GemmaForCausalLM(transformers.GemmaConfig(head_dim=16, **kw)))
     for hf in cases:
         hf = hf.eval()
         with torch.no_grad():
             for n, p in hf.named_parameters():
-                if n.endswith("bias"):
+                if n.endswith("bias") or (type(hf).__name__.startswith("Gemma") and "norm" in n):
                     p.normal_(0, 0.5)
             ref = hf(ids).logits
             m = patch_model(hf, dtype=torch.float32, device="cpu").eval()
             torch.testing.assert_close(m(ids).logits, ref, rtol=1e-5, atol=1e-6)
             back = type(hf)(hf.config).eval()
-            assert not back.load_state_dict(m.to_hf_state_dict(), strict=False).missing_keys
+            missing = back.load_state_dict(m.to_hf_state_dict(), strict=False).missing_keys
+            assert [k for k in missing if k != "lm_head.weight"] == []          # a tied head has no tensor of its own
             torch.testing.assert_close(back(ids).logits, ref)
     # a mixture-of-experts model trains through the ordinary path (router and biases receive gradients, balance loss on)
     cfg = preset_config("moe-tiny", vocab_size=128, router_aux_loss_coef=0.01, attention_bias=True)

@@ -290,6 +290,8 @@ class ModelRunner:
         `adapter_ids` [T]: LoRA adapter index of every token (requests with different adapters share the batch)."""
         m, c = self.model.model, self.cfg
         x = m.embed_tokens(token_ids)
+        if getattr(c, "scale_embeddings", False):
+            x = x * torch.tensor(c.hidden_size ** 0.5, dtype=x.dtype)
         res = None
         block_table, seq_lens = self.cache.block_table(seq_ids, self.device)
         pos32 = positions.to(torch.int32)

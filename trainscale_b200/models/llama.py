@@ -49,6 +49,8 @@ class LlamaConfig:
     num_experts_per_tok: int = 2
     norm_topk_prob: bool = True
     router_aux_loss_coef: float = 0.0       # load-balancing loss weight (0 = off)
+    norm_weight_offset: float = 0.0         # Gemma stores (norm weight - 1): y = x_hat * (offset + w)
+    scale_embeddings: bool = False          # Gemma multiplies the token embeddings by sqrt(hidden_size)
 
     def __post_init__(self):
         if self.num_key_value_heads is None:
@@ -139,13 +141,13 @@ def _lin(mod, x, name: str):
 
 
 class RMSNorm(nn.Module):
-    def __init__(self, dim: int, eps: float = 1e-5):
+    def __init__(self, dim: int, eps: float = 1e-5, offset: float = 0.0):
         super().__init__()
-        self.weight = nn.Parameter(torch.ones(dim))
-        self.eps = eps
+        self.weight = nn.Parameter(torch.full((dim,), 1.0 - offset))
+        self.eps, self.offset = eps, offset
 
     def forward(self, x, residual=None):
-        return norm.rmsnorm(x, self.weight, self.eps, residual)
+        return norm.rmsnorm(x, self.weight, self.eps, residual, self.offset)
 
 
 class LlamaAttention(nn.Module):
@@ -232,16 +234,16 @@ class LlamaMoEMLP(nn.Module):
 class LlamaDecoderLayer(nn.Module):
     def __init__(self, cfg: LlamaConfig):
         super().__init__()
-        self.input_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps)
+        self.input_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, cfg.norm_weight_offset)
         self.self_attn = LlamaAttention(cfg)
-        self.post_attention_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps)
+        self.post_attention_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, cfg.norm_weight_offset)
         self.mlp = LlamaMoEMLP(cfg) if cfg.num_local_experts > 0 else LlamaMLP(cfg)
         self.op_selective = False   # keep only GEMM-side tensors; norm / GLU outputs are rebuilt in backward
 
     def forward(self, x, residual, cos, sin, position_ids=None, cu_seqlens=None, doc_ids=None, kv_cache=None):
         if self.op_selective and self.training and kv_cache is None and self.self_attn.lora is None \
                 and self.mlp.lora is None and not getattr(self.mlp, "fp8", False) and self.self_attn.bqkv is None \
-                and isinstance(self.mlp, LlamaMLP):
+                and isinstance(self.mlp, LlamaMLP) and self.input_layernorm.offset == 0.0:
             n1, n2 = self.input_layernorm, self.post_attention_layernorm
             qkv, residual = fused_blocks.norm_linear(x, residual, n1.weight, self.self_attn.wqkv, n1.eps)
             a = self.self_attn.attend(qkv, cos, sin, position_ids, cu_seqlens, doc_ids, None)
@@ -267,7 +269,7 @@ class LlamaModel(nn.Module):
         self.cfg = cfg
         self.embed_tokens = nn.Embedding(cfg.vocab_size, cfg.hidden_size)
         self.layers = nn.ModuleList(LlamaDecoderLayer(cfg) for _ in range(cfg.num_hidden_layers))
-        self.norm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps)
+        self.norm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, cfg.norm_weight_offset)
         self.gradient_checkpointing = False
         self.checkpoint_every = 1
         self._rope_cache: dict = {}
@@ -292,6 +294,8 @@ class LlamaModel(nn.Module):
     def forward(self, input_ids, position_ids=None, cu_seqlens=None, doc_ids=None, kv_caches=None,
                 inputs_embeds=None):
         x = self.embed_tokens(input_ids) if inputs_embeds is None else inputs_embeds
+        if self.cfg.scale_embeddings and inputs_embeds is None:
+            x = x * torch.tensor(self.cfg.hidden_size ** 0.5, dtype=x.dtype)
         S = x.shape[1]
         past = 0 if not kv_caches else kv_caches[0].seq_len
         need = S + past
@@ -362,7 +366,7 @@ class LlamaForCausalLM(nn.Module):
             if name.endswith("bqkv"):
                 p.zero_()
             elif p.dim() == 1:
-                p.fill_(1.0)
+                p.fill_(1.0 - self.config.norm_weight_offset)
             else:
                 s = std
                 if name.endswith("wo") or name.endswith("w_down"):
@@ -552,7 +556,9 @@ class LlamaForCausalLM(nn.Module):
     def hf_config_dict(self) -> dict:
         c = self.config
         arch, mt = ("MixtralForCausalLM", "mixtral") if c.num_local_experts > 0 else \
-            ("Qwen2ForCausalLM", "qwen2") if c.attention_bias else ("LlamaForCausalLM", "llama")
+            ("Qwen2ForCausalLM", "qwen2") if c.attention_bias else \
+            ("GemmaForCausalLM", "gemma") if c.norm_weight_offset == 1.0 and c.scale_embeddings else \
+            ("LlamaForCausalLM", "llama")
         extra = {"num_local_experts": c.num_local_experts, "num_experts_per_tok": c.num_experts_per_tok,
                  "router_aux_loss_coef": c.router_aux_loss_coef} if c.num_local_experts > 0 else {}
         return {**extra, "architectures": [arch], "model_type": mt, "vocab_size": c.vocab_size,

@@ -232,6 +232,8 @@ class LlamaStage(nn.Module):
         from ..ops import cross_entropy
         if self.first:
             h, res = self.embed_tokens(x), None
+            if getattr(self.config, "scale_embeddings", False):
+                h = h * torch.tensor(self.config.hidden_size ** 0.5, dtype=h.dtype)
         else:
             H = x.shape[-1] // 2
             h, res = x[..., :H], x[..., H:]

@@ -272,7 +272,12 @@ def convert_hf_llama(hf_model, dtype=torch.bfloat16, device=None):
                       num_experts_per_tok=int(getattr(c, "num_experts_per_tok", 2) or 2),
                       router_aux_loss_coef=float(getattr(c, "router_aux_loss_coef", 0.0) or 0.0)
                       if getattr(c, "output_router_logits", False) else 0.0,
-                      model_type=getattr(c, "model_type", "llama"))
+                      model_type=getattr(c, "model_type", "llama"),
+                      hidden_act={"gelu_pytorch_tanh": "gelu_tanh", "gelu_new": "gelu_tanh"}.get(
+                          getattr(c, "hidden_activation", None) or getattr(c, "hidden_act", "silu"),
+                          getattr(c, "hidden_act", "silu")),
+                      norm_weight_offset=1.0 if getattr(c, "model_type", "") == "gemma" else 0.0,
+                      scale_embeddings=getattr(c, "model_type", "") == "gemma")
     if any(k.endswith("o_proj.bias") for k in hf_model.state_dict()):
         raise ValueError("output-projection biases are not supported by the framework decoder")
     m = build_model(cfg, dtype=dtype, device=device)
@@ -295,7 +300,8 @@ class KernelPatcher:
         if isinstance(model, LlamaForCausalLM):
             return model
         arch = type(model).__name__
-        if arch in ("LlamaForCausalLM", "MistralForCausalLM", "Qwen2ForCausalLM", "MixtralForCausalLM") and \
+        if arch in ("LlamaForCausalLM", "MistralForCausalLM", "Qwen2ForCausalLM", "MixtralForCausalLM",
+                    "GemmaForCausalLM") and \
                 not any(k.endswith("o_proj.bias") for k in model.state_dict()):
             return convert_hf_llama(model, dtype, device)
         return model
