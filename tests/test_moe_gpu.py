@@ -128,23 +128,36 @@ def test_batched_multi_adapter_lora_on_grouped_gemm():
     _lib.raise_on_any_device_error()
 
 
-def test_moe_decoder_on_gpu_matches_cpu_reference_path():
-    """The mixture-of-experts decoder (router top-k kernel, routing plan, grouped GEMMs) in bf16 on the GPU against the
-    same weights on the expert-loop path in fp32."""
+def test_moe_decoder_on_gpu_matches_expert_loop():
+    """The mixture-of-experts decoder in bf16 on the GPU: grouped-GEMM path (routing plan, permute, grouped tcgen05
+    GEMMs, combine) against the loop over experts on the SAME routing decisions (both use the router kernel's top-k, so
+    near-ties in the router cannot send tokens to different experts in the two runs)."""
     from trainscale_b200.models.llama import build_model, preset_config
     from trainscale_b200.ops import _lib
+    from trainscale_b200.ops import moe as moe_ops
     cfg = preset_config("moe-tiny", vocab_size=512, attention_bias=True, head_dim=64)
-    ref = build_model(cfg, dtype=torch.float32, device="cpu", seed=3)
-    m = build_model(cfg, dtype=torch.bfloat16, device="cuda", seed=3)
-    ids = torch.randint(0, 512, (2, 256), generator=torch.Generator().manual_seed(0))
+    ids = torch.randint(0, 512, (2, 256), generator=torch.Generator().manual_seed(0)).cuda()
+
+    def run(use_kernels: bool):
+        m = build_model(cfg, dtype=torch.bfloat16, device="cuda", seed=3)
+        saved = moe_ops.available
+        if not use_kernels:
+            moe_ops.available = lambda x: False
+        try:
+            out = m(ids, labels=ids)
+            out.loss.backward()
+        finally:
+            moe_ops.available = saved
+        mlp = m.model.layers[0].mlp
+        return float(out.loss), mlp.w_down.grad.float(), mlp.w_gate_up.grad.float(), m.model.layers[1].mlp.router.grad.float()
+
     n0 = _lib.LAUNCHES
-    out = m(ids.cuda(), labels=ids.cuda())
-    out.loss.backward()
-    assert _lib.LAUNCHES - n0 > 20
-    want = ref(ids, labels=ids)
-    want.loss.backward()
-    assert abs(float(out.loss) - float(want.loss)) < 3e-2 * float(want.loss)
-    g, gr = m.model.layers[0].mlp.w_down.grad.float().cpu(), ref.model.layers[0].mlp.w_down.grad
-    assert float((g - gr).abs().max()) < 0.1 * float(gr.abs().max()) + 1e-4
-    assert m.model.layers[1].mlp.router.grad is not None and torch.isfinite(m.model.layers[1].mlp.router.grad).all()
+    got = run(True)
+    fast_launches = _lib.LAUNCHES - n0
+    want = run(False)
+    assert fast_launches > 20
+    assert abs(got[0] - want[0]) < 2e-3 * want[0]
+    for g, w in zip(got[1:], want[1:]):
+        assert torch.isfinite(g).all()
+        assert float((g - w).abs().max()) < 5e-2 * float(w.abs().max()) + 1e-5
     _lib.raise_on_any_device_error()
