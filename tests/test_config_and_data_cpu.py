@@ -173,3 +173,22 @@ def test_data_pipeline_end_to_end_in_memory():
     assert b["input_ids"].shape == (2, 64) and (b["labels"] != -100).sum() > 0
     assert DataPipeline.from_config(dict(raw, type="x")).is_err()
     assert p.get_dataloader("nope").is_err()
+
+
+def test_every_shipped_yaml_parses_and_resolves_its_mesh():
+    import glob
+    from pathlib import Path
+    from trainscale_b200.config.sota_config import SOTAConfig
+    from trainscale_b200.parallel.mesh import create_parallel_dims_from_config
+    from trainscale_b200.trainer.sota_trainer import STRATEGY_ALIASES
+    files = sorted(glob.glob(str(Path(__file__).resolve().parents[1] / "configs" / "*.yaml")))
+    assert len(files) >= 7
+    seen = {}
+    for f in files:
+        c = SOTAConfig.from_yaml(f)
+        assert c.distributed.strategy in STRATEGY_ALIASES, f
+        if c.distributed.enabled:
+            d = create_parallel_dims_from_config(c.distributed, world_size=c.distributed.world_size, rank=0)
+            seen[Path(f).name] = d.sizes
+    assert seen["llama3_70b_tp4_pp2_fp8.yaml"]["tp"] == 4 and seen["llama3_70b_tp4_pp2_fp8.yaml"]["pp"] == 2
+    assert seen["llama3_8b_cp8_128k.yaml"]["cp"] == 8
