@@ -39,7 +39,9 @@ def main():
     e_exp = float((m.model.layers[0].mlp.w_down.grad - total).abs().max())
     full_gu, _ = m.model.layers[0].mlp.full_expert_weights()
     e_w = float((full_gu - ref.model.layers[0].mlp.w_gate_up.detach()).abs().max())
-    ok = max(e_loss, e_attn, e_router, e_exp) < 2e-5 and e_w == 0.0 and float(mine.abs().sum()) > 0
+    sd, sd_ref = m.to_hf_state_dict(), ref.to_hf_state_dict()          # export gathers the experts of every rank
+    e_sd = max(float((sd[k] - sd_ref[k]).abs().max()) for k in sd_ref) if set(sd) == set(sd_ref) else 1.0
+    ok = max(e_loss, e_attn, e_router, e_exp) < 2e-5 and e_w == 0.0 and e_sd == 0.0 and float(mine.abs().sum()) > 0
     print(f"RESULT rank={rank} loss={e_loss:.1e} attn={e_attn:.1e} router={e_router:.1e} experts={e_exp:.1e} ok={ok}",
           flush=True)
     flag = torch.tensor([0.0 if ok else 1.0])

@@ -477,7 +477,12 @@ class LlamaForCausalLM(nn.Module):
             q, k, v = attn.wqkv.detach().split((Hq // ws * D, Hkv // ws * D, Hkv // ws * D), dim=0)
             items = [("self_attn.q_proj", q, 0), ("self_attn.k_proj", k, 0), ("self_attn.v_proj", v, 0),
                      ("self_attn.o_proj", attn.wo, 1)]
-            if isinstance(mlp, LlamaMoEMLP):
+            if hasattr(mlp, "full_expert_weights"):        # expert-parallel block: gather the experts (collective)
+                gu, dn = mlp.full_expert_weights()
+                put(p + "mlp.gate.weight", mlp.router.detach())
+                put(p + "mlp.experts.gate_up_proj", gu)
+                put(p + "mlp.experts.down_proj", dn)
+            elif isinstance(mlp, LlamaMoEMLP):
                 if ws > 1:
                     raise NotImplementedError("mixture-of-experts layers are sharded by expert parallelism, not tp")
                 put(p + "mlp.gate.weight", mlp.router.detach())
