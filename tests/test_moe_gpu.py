@@ -159,5 +159,8 @@ def test_moe_decoder_on_gpu_matches_expert_loop():
     assert abs(got[0] - want[0]) < 2e-3 * want[0]
     for g, w in zip(got[1:], want[1:]):
         assert torch.isfinite(g).all()
-        assert float((g - w).abs().max()) < 5e-2 * float(w.abs().max()) + 1e-5
+        # bf16 GEMMs with bf16 intermediates against fp32 maths on the same bf16 weights: small in norm, and no
+        # single element far off
+        assert float((g - w).norm()) < 3e-2 * float(w.norm()) + 1e-6
+        assert float((g - w).abs().max()) < 0.2 * float(w.abs().max()) + 1e-5
     _lib.raise_on_any_device_error()
