@@ -197,9 +197,9 @@ class ZBPPScheduleOptimizer:
                     continue
                 start, pri, kind = min(cands)
                 if kind != "W" and w_pending[s] and start > t[s] + 1e-9:
-                    # the stage would idle until `start`: run a B_params if it fits in the gap (or anyway when the
-                    # gap is longer than the work)
-                    if t[s] + prof[s].b_params_us <= start + 1e-9 or start - t[s] >= prof[s].b_params_us * 0.5:
+                    # the stage would idle until `start`: run a B_params there if it ends before the critical-path
+                    # work could begin (a weight gradient that overran the gap would delay every later stage)
+                    if t[s] + prof[s].b_params_us <= start + 1e-9:
                         start, pri, kind = t[s], 2, "W"
                 key = (start, pri, s)
                 if best is None or key < best[0]:
