@@ -1,6 +1,7 @@
-"""Property tests of the pipeline schedules: for any stage / micro-batch count every generator emits each operation
-exactly once per (stage, micro-batch), the per-stage orders are executable without deadlock, memory limits are kept and
-the zero-bubble forms are never worse than 1F1B."""
+"""Property tests (hypothesis).  Pipeline schedules: for any stage / micro-batch count every generator emits each
+operation exactly once per (stage, micro-batch), the per-stage orders are executable without deadlock and memory limits
+are kept.  Context-parallel layouts partition the sequence and invert; mesh coordinates round-trip; optimizer shards
+re-slice exactly between any two world sizes."""
 import pytest
 
 hypothesis = pytest.importorskip("hypothesis")
@@ -81,3 +82,69 @@ def test_cost_driven_zero_bubble_scheduler(P, extra, f, b, w, slack, h2):
     if slack >= P:       # with 1F1B's memory the greedy order stays within 2 % of 1F1B's makespan (usually well below)
         base = PP.simulate([PP.one_f_one_b_schedule(s, P, M) for s in range(P)], {"F": f, "B": b + w, "W": 0.0})
         assert r.makespan_us <= base["makespan"] * 1.02
+
+
+@settings(max_examples=40, deadline=None)
+@given(cp=st.integers(1, 8), mult=st.integers(1, 4), name=st.sampled_from(["head_tail", "zigzag", "ptrr"]))
+def test_context_parallel_layouts_partition_the_sequence(cp, mult, name):
+    import torch
+    from trainscale_b200.parallel import cp as CP
+    S = 2 * cp * mult * 4
+    x = torch.arange(S).view(1, S, 1)
+    parts = [CP.create_balancer(name, cp, r).shard(x) for r in range(cp)]
+    assert sorted(torch.cat(parts, 1).flatten().tolist()) == list(range(S))          # every token exactly once
+    assert len({p.shape[1] for p in parts}) == 1                                      # equal shares
+    torch.testing.assert_close(CP.create_balancer(name, cp, 0).unshard(parts), x)    # and the inverse restores order
+    if name == "head_tail" and cp > 1:
+        # causal work (sum of positions + 1) is balanced to within one chunk pair
+        work = [int((p.flatten() + 1).sum()) for p in parts]
+        assert max(work) - min(work) <= S
+
+
+@settings(max_examples=40, deadline=None)
+@given(pp=st.integers(1, 3), rep=st.integers(1, 2), shard=st.integers(1, 3), cpd=st.integers(1, 2), tp=st.integers(1, 2))
+def test_mesh_coordinates_round_trip(pp, rep, shard, cpd, tp):
+    from trainscale_b200.parallel.mesh import ParallelDims, ParallelDimsConfig
+    world = pp * rep * shard * cpd * tp
+    cfg = ParallelDimsConfig(dp_replicate=rep, dp_shard=shard, cp=cpd, tp=tp, pp=pp, world_size=world)
+    seen = set()
+    for r in range(world):
+        d = ParallelDims(cfg, rank=r, create_groups=False)
+        assert d.rank_of(**d.coords) == r
+        seen.add(tuple(sorted(d.coords.items())))
+        tp_ranks = d.ranks_along(("tp",))
+        assert r in tp_ranks and len(tp_ranks) == tp and max(tp_ranks) - min(tp_ranks) == tp - 1   # tp innermost
+        assert d.size("fsdp") == shard * cpd and d.size("loss") == rep * shard * cpd
+    assert len(seen) == world
+
+
+@settings(max_examples=30, deadline=None)
+@given(old=st.integers(1, 6), new=st.integers(1, 6), used=st.integers(1, 5000))
+def test_optimizer_shards_reslice_exactly_between_world_sizes(old, new, used):
+    import torch
+    from trainscale_b200.ckpt import reshard_optimizer_state
+    align = 64
+
+    def padded(world):
+        q = align * world
+        return (used + q - 1) // q * q
+
+    full = torch.arange(used, dtype=torch.float32)
+    n_old = padded(old)
+    buf = torch.cat((full, torch.zeros(n_old - used)))
+    shards = [{"rank": r, "world": old, "step": 3,
+               "units": {"u": {"master": buf[r * n_old // old:(r + 1) * n_old // old].clone(),
+                               "exp_avg": buf[r * n_old // old:(r + 1) * n_old // old].clone() * 2, "exp_avg_sq": None,
+                               "shard_start": r * n_old // old, "numel": n_old}}} for r in range(old)]
+    n_new = padded(new)
+    got = []
+    for r in range(new):
+        layout = {"u": (n_new, r * n_new // new, n_new // new)}
+        out = reshard_optimizer_state(shards, r, new, layout)
+        assert out["units"]["u"]["exp_avg_sq"] is None and out["step"] == 3
+        got.append(out["units"]["u"]["master"])
+        torch.testing.assert_close(out["units"]["u"]["exp_avg"], out["units"]["u"]["master"] * 2)
+    whole = torch.cat(got)
+    assert whole.numel() == n_new
+    torch.testing.assert_close(whole[:used], full)
+    assert float(whole[used:].abs().sum()) == 0.0
