@@ -79,9 +79,9 @@ def test_cost_driven_zero_bubble_scheduler(P, extra, f, b, w, slack, h2):
         assert starts == sorted(starts)
     acts = r.actions()
     PP.simulate(acts, {"F": f, "B": b, "W": w})              # executable in the emitted order
-    if slack >= P:       # with 1F1B's memory the greedy order stays within 2 % of 1F1B's makespan (usually well below)
+    if slack >= P:       # with 1F1B's memory available the result is never slower than 1F1B
         base = PP.simulate([PP.one_f_one_b_schedule(s, P, M) for s in range(P)], {"F": f, "B": b + w, "W": 0.0})
-        assert r.makespan_us <= base["makespan"] * 1.02
+        assert r.makespan_us <= base["makespan"] * (1 + 1e-9) + 1e-6
 
 
 @settings(max_examples=40, deadline=None)

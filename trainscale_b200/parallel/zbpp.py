@@ -138,7 +138,82 @@ class ZBPPScheduleOptimizer:
             raise ValueError(f"stage {s}: the memory limit does not hold one micro-batch of activations")
         return cap
 
+    def _evaluate(self, orders: list[list[tuple[str, int]]]) -> ScheduleResult | None:
+        """Timeline of fixed per-stage orders [("F"|"B"|"W", micro-batch), ...]; None if an order cannot run."""
+        c = self.config
+        P, prof = c.num_stages, c.stage_profiles
+        t, idx, busy = [0.0] * P, [0] * P, [0.0] * P
+        f_done: dict[tuple, float] = {}
+        b_done: dict[tuple, float] = {}
+        mem = [prof[s].param_bytes for s in range(P)]
+        peak = list(mem)
+        slots: dict[int, list[ScheduleSlot]] = {s: [] for s in range(P)}
+        kinds = {"F": (OpType.FORWARD, Priority.HIGH), "B": (OpType.BACKWARD_INPUT, Priority.CRITICAL),
+                 "W": (OpType.BACKWARD_PARAMS, Priority.NORMAL)}
+        progressed = True
+        while progressed:
+            progressed = False
+            for s in range(P):
+                while idx[s] < len(orders[s]):
+                    kind, m = orders[s][idx[s]]
+                    if kind == "F":
+                        dep = 0.0 if s == 0 else (f_done.get((s - 1, m)))
+                        ready = dep if s == 0 else (None if dep is None else dep + prof[s - 1].comm_send_us)
+                        cost, dmem = prof[s].forward_us, prof[s].activation_bytes
+                    elif kind == "B":
+                        if (s, m) not in f_done:
+                            ready = None
+                        elif s == P - 1:
+                            ready = f_done[(s, m)]
+                        else:
+                            dep = b_done.get((s + 1, m))
+                            ready = None if dep is None else dep + prof[s + 1].comm_send_us
+                        cost, dmem = prof[s].b_input_us, 0
+                    else:
+                        ready = b_done.get((s, m))
+                        cost, dmem = prof[s].b_params_us, -prof[s].activation_bytes
+                    if ready is None:
+                        break
+                    start = max(t[s], ready)
+                    op, pr = kinds[kind]
+                    slots[s].append(ScheduleSlot(s, m, op, len(slots[s]), pr, cost, dmem, start))
+                    t[s] = start + cost
+                    busy[s] += cost
+                    mem[s] += dmem
+                    peak[s] = max(peak[s], mem[s])
+                    if kind == "F":
+                        f_done[(s, m)] = t[s]
+                    elif kind == "B":
+                        b_done[(s, m)] = t[s]
+                    idx[s] += 1
+                    progressed = True
+        if any(idx[s] < len(orders[s]) for s in range(P)):
+            return None
+        makespan = max(t)
+        bubble = (makespan * P - sum(busy)) / (makespan * P) if makespan > 0 else 0.0
+        return ScheduleResult(slots, bubble, {s: peak[s] for s in range(P)}, max(len(v) for v in slots.values()),
+                              makespan)
+
     def optimize(self) -> ScheduleResult:
+        """The greedy list schedule, unless plain 1F1B (every B_params right after its B_input) fits the memory limit
+        and finishes earlier - the greedy choice is a heuristic and can lose a few percent on small pipelines."""
+        best = self._greedy()
+        c = self.config
+        orders = []
+        for s in range(c.num_stages):
+            lst = []
+            for a in PP.one_f_one_b_schedule(s, c.num_stages, c.num_microbatches):
+                lst.append((a.op, a.mb))
+                if a.op == PP.B_OP:
+                    lst.append(("W", a.mb))
+            orders.append(lst)
+        plain = self._evaluate(orders)
+        if plain is not None and plain.makespan_us < best.makespan_us and \
+                all(v <= c.memory_limit_bytes for v in plain.peak_memory_bytes.values()):
+            return plain
+        return best
+
+    def _greedy(self) -> ScheduleResult:
         c = self.config
         P, M = c.num_stages, c.num_microbatches
         prof = c.stage_profiles
