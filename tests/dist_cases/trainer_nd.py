@@ -39,7 +39,7 @@ def make_cfg(strategy, parallel, world, enabled):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--mode", default="pp", choices=["pp", "sp"])
+    ap.add_argument("--mode", default="pp", choices=["pp", "sp", "cp", "ulysses"])
     ap.add_argument("--cuda", action="store_true", help="bf16 on GPUs through the CUDA kernels (fused TP path)")
     a = ap.parse_args()
     if CUDA:
@@ -57,6 +57,9 @@ def main():
     if a.mode == "pp":
         par = {"pp": world, "dp_shard": 1, "pp_schedule": "1f1b", "pp_microbatches": 2}
         strategy, B = "pipeline", 4
+    elif a.mode in ("cp", "ulysses"):
+        par = {"cp": world, "dp_shard": 1, "cp_balancer": "head_tail" if a.mode == "cp" else "ulysses"}
+        strategy, B = "context_parallel", 1
     else:
         par = {"tp": world, "dp_shard": 1, "sp": True}
         strategy, B = "tensor_parallel", 1
@@ -90,6 +93,11 @@ def main():
             l0 = ref.train_step({"input_ids": ids, "labels": ids})
         finally:
             dist.is_initialized = saved_init
+        if a.mode in ("cp", "ulysses"):
+            # every rank reports the mean over ITS tokens; the shards are equal up to the one ignored last label
+            t = torch.tensor([l1], device=dev)
+            dist.all_reduce(t)
+            l1 = float(t) / world
         good = abs(l1 - l0) < (3e-2 if CUDA else 2e-3) * max(1.0, abs(l0))
         ok &= good
         if rank == 0:

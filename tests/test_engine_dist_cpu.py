@@ -95,10 +95,12 @@ def test_hybrid_sharding_four_ranks():
 ND_CASE = Path(__file__).parent / "dist_cases" / "trainer_nd.py"
 
 
-@pytest.mark.parametrize("mode,port", [("pp", 29621), ("sp", 29622)])
+@pytest.mark.parametrize("mode,port", [("pp", 29621), ("sp", 29622), ("cp", 29623), ("ulysses", 29624)])
 def test_trainer_config_drives_pipeline_and_sequence_parallel(mode, port):
-    """SOTATrainer with `distributed.strategy: pipeline` (1F1B, 2 micro-batches) and with tensor + sequence
-    parallelism reproduces the single-process losses step by step (global grad-norm clip included)."""
+    """SOTATrainer with `distributed.strategy: pipeline` (1F1B, 2 micro-batches), with tensor + sequence parallelism and
+    with context parallelism (ring attention on head-tail shards, or all-to-all head / sequence exchange on contiguous
+    shards) reproduces the single-process losses step by step (global grad-norm clip included) and writes a checkpoint
+    equal to the single-process weights."""
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
            "127.0.0.1", "--master-port", str(port), str(ND_CASE), "--mode", mode]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=300)

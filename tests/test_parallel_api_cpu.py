@@ -362,3 +362,10 @@ def test_expert_parallel_decoder_two_ranks():
     r = launch("ep_decoder.py", 2, 29697)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
     assert r.stdout.count("ok=True") == 2
+
+
+@pytest.mark.parametrize("nproc,port", [(2, 29703), (4, 29704)])
+def test_ulysses_attention_matches_full_attention(nproc, port):
+    r = launch("ulysses.py", nproc, port)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    assert "RESULT ok=True" in r.stdout

@@ -175,8 +175,17 @@ class LlamaAttention(nn.Module):
         if kv_cache is not None:
             o = kv_cache.attend(qkv, self)
         elif self.cp_group is not None:
-            from ..parallel.cp import attention_qkv_cp
-            o = attention_qkv_cp(qkv, self.n_heads, self.n_kv, self.hd, self.cp_group)
+            if getattr(self, "cp_mode", "ring") == "ulysses":
+                # contiguous token shards; all-to-all to head shards, ordinary attention over the whole sequence
+                from ..parallel.cp import ulysses_attention
+                B, S = qkv.shape[0], qkv.shape[1]
+                q, k, v = qkv.split((self.n_heads * self.hd, self.n_kv * self.hd, self.n_kv * self.hd), dim=-1)
+                o = ulysses_attention(q.reshape(B, S, self.n_heads, self.hd), k.reshape(B, S, self.n_kv, self.hd),
+                                      v.reshape(B, S, self.n_kv, self.hd), self.cp_group, True, None,
+                                      self.cfg.sliding_window, self.cfg.attn_logit_softcap).reshape(B, S, -1)
+            else:
+                from ..parallel.cp import attention_qkv_cp
+                o = attention_qkv_cp(qkv, self.n_heads, self.n_kv, self.hd, self.cp_group)
         else:
             o = attention.attention_qkv(qkv, self.n_heads, self.n_kv, self.hd, True, None, self.cfg.sliding_window,
                                         self.cfg.attn_logit_softcap, cu_seqlens, doc_ids)

@@ -85,8 +85,21 @@ class PTRRBalancer(HeadTailBalancer):
         return torch.cat([torch.arange(i * c, (i + 1) * c) for i in ids])
 
 
+class ContiguousBalancer(HeadTailBalancer):
+    """Rank r owns tokens [r S/cp, (r+1) S/cp): the layout of all-to-all (Ulysses) sequence parallelism, where every
+    rank ends up attending over the whole sequence and causal balance is not a concern."""
+
+    def indices(self, seq_len: int, rank: int | None = None) -> torch.Tensor:
+        assert seq_len % self.cp == 0, "sequence length must divide by cp"
+        r = self.rank if rank is None else rank
+        c = seq_len // self.cp
+        return torch.arange(r * c, (r + 1) * c)
+
+
 def create_balancer(name: str, cp: int, rank: int):
     name = (name or "head_tail").lower()
+    if name in ("contiguous", "ulysses"):
+        return ContiguousBalancer(cp, rank)
     if name in ("head_tail", "headtail"):
         return HeadTailBalancer(cp, rank)
     if name in ("zigzag", "zig_zag"):
@@ -879,3 +892,46 @@ class ContextParallel:
 
     def restore_sequence(self, x_local: torch.Tensor, dim: int = 1) -> torch.Tensor:
         return gather_output(x_local, self.group, self.load_balancer, dim) if self.world > 1 else x_local
+
+
+# ------------------------------------------------------------------------------------------------ Ulysses (head <-> sequence all-to-all)
+def _seq_to_heads(x: torch.Tensor, group, P: int) -> torch.Tensor:
+    """[B, S/P, H, D] on every rank -> [B, S, H/P, D]: rank r ends with head group r of the whole sequence."""
+    from .ep import _AllToAll
+    B, Sl, H, D = x.shape
+    send = x.view(B, Sl, P, H // P, D).permute(2, 0, 1, 3, 4).contiguous().view(P * B * Sl, (H // P) * D)
+    recv = _AllToAll.apply(send, [B * Sl] * P, [B * Sl] * P, group)            # leading index = source rank = chunk
+    return recv.view(P, B, Sl, H // P, D).permute(1, 0, 2, 3, 4).reshape(B, P * Sl, H // P, D)
+
+
+def _heads_to_seq(x: torch.Tensor, group, P: int) -> torch.Tensor:
+    """Inverse of `_seq_to_heads`: [B, S, H/P, D] -> [B, S/P, H, D]."""
+    from .ep import _AllToAll
+    B, S, Hl, D = x.shape
+    Sl = S // P
+    send = x.view(B, P, Sl, Hl, D).permute(1, 0, 2, 3, 4).contiguous().view(P * B * Sl, Hl * D)
+    recv = _AllToAll.apply(send, [B * Sl] * P, [B * Sl] * P, group)            # leading index = source rank = head group
+    return recv.view(P, B, Sl, Hl, D).permute(1, 2, 0, 3, 4).reshape(B, Sl, P * Hl, D)
+
+
+def ulysses_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, group, causal: bool = True,
+                      scale: float | None = None, window: int | None = None, softcap: float = 0.0) -> torch.Tensor:
+    """Sequence parallelism by all-to-all (DeepSpeed-Ulysses): the sequence is sharded CONTIGUOUSLY over the group
+    (rank r holds tokens [r S/P, (r+1) S/P)), one all-to-all turns the token shards into head shards, every rank runs
+    ordinary (flash) attention over the whole sequence for Hq/P query and Hkv/P key/value heads, a second all-to-all
+    turns the result back.  Needs Hq and Hkv divisible by P; no causal load balancing is needed because every rank sees
+    all tokens.  q [B, S/P, Hq, D], k / v [B, S/P, Hkv, D] -> [B, S/P, Hq, D].  The reference has no such path."""
+    from ..ops import attention as A
+    P = dist.get_world_size(group) if dist.is_available() and dist.is_initialized() else 1
+    if P == 1:
+        B, S, Hq, D = q.shape
+        qkv = torch.cat((q.reshape(B, S, -1), k.reshape(B, S, -1), v.reshape(B, S, -1)), -1)
+        return A.attention_qkv(qkv, Hq, k.shape[2], D, causal, scale, window, softcap).view(B, S, Hq, D)
+    Hq, Hkv, D = q.shape[2], k.shape[2], q.shape[3]
+    if Hq % P or Hkv % P:
+        raise ValueError(f"Ulysses needs the head counts ({Hq}, {Hkv}) to divide by the group size {P}")
+    qh, kh, vh = _seq_to_heads(q, group, P), _seq_to_heads(k, group, P), _seq_to_heads(v, group, P)
+    B, S = qh.shape[0], qh.shape[1]
+    qkv = torch.cat((qh.reshape(B, S, -1), kh.reshape(B, S, -1), vh.reshape(B, S, -1)), -1)
+    o = A.attention_qkv(qkv, Hq // P, Hkv // P, D, causal, scale, window, softcap).view(B, S, Hq // P, D)
+    return _heads_to_seq(o, group, P)

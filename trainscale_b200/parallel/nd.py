@@ -38,11 +38,18 @@ class NDEngine:
                 # are summed over the tp group after backward, before the data-parallel reduction
                 model.model.sp_ctx = ctx
                 overlap = False
+        self.cp_balancer = "head_tail"
         if self.dims.enabled("cp"):
             g = self.dims.group("cp")
+            # cp_balancer: head_tail (default) = exact ring attention on causally balanced shards;
+            # ulysses / contiguous = all-to-all between token shards and head shards (heads must divide by cp)
+            self.cp_balancer = (getattr(p, "cp_balancer", None) or "head_tail").lower()
+            if self.cp_balancer not in ("head_tail", "ulysses", "contiguous"):
+                raise ValueError(f"cp_balancer {self.cp_balancer!r}: the trainer supports head_tail (ring) and ulysses")
+            mode = "ring" if self.cp_balancer == "head_tail" else "ulysses"
             for layer in model.model.layers:
                 attn = getattr(layer.self_attn, "inner", layer.self_attn)
-                attn.cp_group = g
+                attn.cp_group, attn.cp_mode = g, mode
             self.cp_group = g
         opt_model = model
         if self.dims.enabled("pp"):
@@ -114,7 +121,7 @@ class NDEngine:
     def shard_batch(self, batch: dict) -> dict:
         if self.dims.enabled("cp"):
             from .cp import shard_inputs
-            return shard_inputs(batch, self.dims.size("cp"), self.dims.local_rank("cp"))
+            return shard_inputs(batch, self.dims.size("cp"), self.dims.local_rank("cp"), self.cp_balancer)
         return batch
 
     def backward(self, loss):

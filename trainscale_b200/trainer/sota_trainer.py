@@ -291,6 +291,16 @@ class SOTATrainer:
         """Forward + backward of one micro-batch.  A pipeline engine runs its own schedule over the batch."""
         if self.engine is not None and hasattr(self.engine, "forward_backward") and self.engine.pipelined:
             return self.engine.forward_backward(batch, loss_scale)
+        cp_group = getattr(self.engine, "cp_group", None) if self.engine is not None else None
+        if cp_group is not None and batch.get("labels_shifted", False):
+            # context parallelism: every rank averages over ITS valid tokens and the engine averages the ranks, which
+            # equals the mean over the whole sequence only if the shards hold the same number of valid labels.  They do
+            # not in general (the last position has no label; packed documents mask more), so weight each rank by its
+            # share: local mean * (n_local * cp / n_global)
+            n_local = (batch["labels"] != self.config.loss.ignore_index).sum().float()
+            n_global = n_local.clone()
+            dist.all_reduce(n_global, group=cp_group)
+            loss_scale = loss_scale * float(n_local * dist.get_world_size(cp_group) / n_global.clamp(min=1.0))
         loss, ntok = self._forward_loss(batch, loss_scale)
         if self.engine is not None:
             self.engine.backward(loss)
