@@ -40,10 +40,11 @@ def test_tensor_parallel_decoder_on_two_gpus(args, port):
     assert "ok=False" not in out
 
 
-@pytest.mark.parametrize("mode,port", [("sp", 29738), ("pp", 29739)])
+@pytest.mark.parametrize("mode,port", [("sp", 29738), ("pp", 29739), ("cp", 29743), ("ulysses", 29744)])
 def test_trainer_config_tensor_sequence_and_pipeline_parallel_on_two_gpus(mode, port):
     """YAML-style config -> SOTATrainer -> tensor + sequence parallel decoder on the fused all-gather->GEMM /
-    GEMM->reduce-scatter kernels (and a 2-stage pipeline), losses against a single-process trainer."""
+    GEMM->reduce-scatter kernels, a 2-stage pipeline, and context parallelism (ring attention with K/V over peer memory,
+    Ulysses all-to-all): losses and the written checkpoint against a single-process trainer."""
     out = _launch("trainer_nd.py", "--mode", mode, "--cuda", port=port)
     assert "RESULT" in out and "ok=True" in out
     if mode == "sp":
