@@ -37,6 +37,15 @@ def main():
     full = eng.gather_output(out.detach())
     e_g = float((full - ref.detach()).abs().max())
     ok &= max(e_o, e_q, e_k, e_g) < 1e-4 and eng.get_metrics().steps == 1
+    # the same engine API without ring attention: contiguous shards + all-to-all (heads must divide by the group size)
+    eng2 = CP.create_context_parallel_engine(cp_degree=world, use_ring_attention=False, group=dist.group.WORLD).unwrap()
+    _, _, _, pos2 = eng2.shard_inputs(ids)
+    idx2 = pos2[0]
+    ok &= torch.equal(idx2, torch.arange(rank * S // world, (rank + 1) * S // world))
+    if Hq % world == 0 and Hkv % world == 0:
+        out2 = eng2.ring_attention_forward(q[:, idx2], k[:, idx2], v[:, idx2])
+        ok &= float((out2 - ref.detach()[:, idx2]).abs().max()) < 1e-4
+        ok &= float((eng2.gather_output(out2) - ref.detach()).abs().max()) < 1e-4
     cpw = CP.ContextParallel(dist.group.WORLD)
     sh = cpw.shard_inputs({"input_ids": ids})
     ok &= torch.equal(cpw.restore_sequence(sh["input_ids"]), ids)

@@ -809,7 +809,8 @@ class ContextParallelEngine:
     cp_world_size = property(lambda self: self._world)
 
     def _balancer(self) -> str:
-        return self._config.load_balancer.name.lower()
+        # without ring attention the engine exchanges token shards for head shards (Ulysses): contiguous token layout
+        return self._config.load_balancer.name.lower() if self._config.use_ring_attention else "contiguous"
 
     def shard_inputs(self, input_ids: torch.Tensor, labels: torch.Tensor | None = None,
                      attention_mask: torch.Tensor | None = None, position_ids: torch.Tensor | None = None,
@@ -839,6 +840,9 @@ class ContextParallelEngine:
             return attention_reference(q, k, v, causal=True).to(q.dtype)
         S, Hq, D = q.shape[1], q.shape[2], q.shape[3]
         self._metrics.flops += 4.0 * (S * self._world) * (S * self._world) * Hq * D / 2 / self._world
+        if not self._config.use_ring_attention:
+            self._metrics.bytes_sent += (2 * q.numel() + 2 * k.numel()) * q.element_size() * (self._world - 1) // self._world
+            return ulysses_attention(q, k, v, self.group)
         self._metrics.bytes_sent += 2 * k.numel() * k.element_size() * (self._world - 1)
         return ring_attention(q, k, v, self.group)
 
