@@ -444,3 +444,29 @@ def test_kernel_layer_entry_points_on_gpu():
     torch.testing.assert_close(sm.grad.float(), sf.grad, rtol=3e-2, atol=1e-4)
     assert _lib.LAUNCHES - n0 >= 10
     _lib.raise_on_any_device_error()
+
+
+@pytest.mark.gpu
+def test_registry_patchers_route_a_huggingface_model_onto_the_kernels():
+    """An unconverted transformers Llama in bf16 on the GPU: after `auto_patch` + `auto_patch_attention` its norms, gated
+    MLPs, rotary embedding and attention run on the framework kernels (launch counter moves) and the logits stay within
+    bf16 noise of the original modules."""
+    transformers = pytest.importorskip("transformers")
+    from trainscale_b200.ops import _lib
+    from trainscale_b200.registry import auto_patch, auto_patch_attention
+    torch.manual_seed(0)
+    cfg = transformers.LlamaConfig(vocab_size=1024, hidden_size=512, intermediate_size=1024, num_hidden_layers=2,
+                                   num_attention_heads=8, num_key_value_heads=2, head_dim=64)
+    m = transformers.LlamaForCausalLM(cfg).to("cuda", torch.bfloat16).eval()
+    ids = torch.randint(0, 1024, (1, 256), device="cuda")
+    with torch.no_grad():
+        ref = m(ids).logits.float()
+        counts = auto_patch(m)
+        n_attn = auto_patch_attention(m)
+        n0 = _lib.LAUNCHES
+        out = m(ids).logits.float()
+    assert counts["layernorm"] == 5 and counts["mlp"] == 2 and n_attn == 2
+    assert _lib.LAUNCHES - n0 >= 10
+    err = float((out - ref).abs().max()) / float(ref.abs().max())
+    assert err < 5e-2, err
+    _lib.raise_on_any_device_error()
