@@ -501,8 +501,7 @@ class Prodigy(Optimizer):
         b3 = math.sqrt(b2)
         d, lr = g0["d"], g0["lr"]
         dlr = d * lr
-        num = g0["d_numerator"] * b3
-        denom = 0.0
+        nums, dens = [], []            # 0-d device tensors: one host read per step, not two per tensor
         for g in self.param_groups:
             for p in g["params"]:
                 if p.grad is None:
@@ -513,11 +512,16 @@ class Prodigy(Optimizer):
                     st["s"] = torch.zeros_like(gf)
                     st["p0"] = p.detach().float().clone()
                     st["m"], st["v"] = torch.zeros_like(gf), torch.zeros_like(gf)
-                num += (d / g0["d0"]) * dlr * float((gf * (st["p0"] - p.float())).sum())
+                nums.append(torch.dot(gf.reshape(-1), (st["p0"] - p.float()).reshape(-1)))
                 st["m"].mul_(b1).add_(gf, alpha=d * (1 - b1))
                 st["v"].mul_(b2).addcmul_(gf, gf, value=d * d * (1 - b2))
                 st["s"].mul_(b3).add_(gf, alpha=(d / g0["d0"]) * dlr)
-                denom += float(st["s"].abs().sum())
+                dens.append(st["s"].abs().sum())
+        num, denom = g0["d_numerator"] * b3, 0.0
+        if nums:
+            dev = nums[0].device
+            both = torch.stack([torch.stack([t.to(dev) for t in nums]).sum(), torch.stack([t.to(dev) for t in dens]).sum()]).tolist()
+            num, denom = num + (d / g0["d0"]) * dlr * both[0], both[1]
         if denom > 0:
             d_hat = g0["d_coef"] * num / denom
             d = max(d, min(d_hat, d * g0["growth_rate"]))
