@@ -380,7 +380,7 @@ def test_every_optimizer_of_the_zoo_reduces_a_least_squares_loss(name):
         opt.step()
     if hasattr(opt, "eval"):
         opt.eval()
-    last = float(((x @ w + b - y) ** 2).mean())
+    last = ((x @ w + b - y) ** 2).mean().item()
     # AdaFactor's relative step (1e-2 x RMS of the weights) is slow by construction on weights this small
     bound = 0.8 if name == "adafactor" else 0.5
     assert bool(torch.isfinite(w).all()) and last < bound * first, (name, first, last)
