@@ -401,7 +401,7 @@ class CAME(Optimizer):
                 else:
                     st["v"].mul_(b2).add_(upd, alpha=1 - b2)
                     u = gf * st["v"].rsqrt()
-                u.div_(max(1.0, float(u.norm() / math.sqrt(u.numel())) / g["clip_threshold"]))
+                u.div_((u.norm() / (math.sqrt(u.numel()) * g["clip_threshold"])).clamp_(min=1.0))   # stays on the device
                 st["m"].mul_(b1).add_(u, alpha=1 - b1)
                 if fac:
                     res = (u - st["m"]) ** 2 + g["eps"][1]
