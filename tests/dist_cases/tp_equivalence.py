@@ -22,9 +22,10 @@ def main():
     else:
         dist.init_process_group("gloo")
         dev, dtype = torch.device("cpu"), torch.float32
-    cfg = LlamaConfig(vocab_size=512, hidden_size=256, intermediate_size=512, num_hidden_layers=2,
-                      num_attention_heads=4, num_key_value_heads=2, head_dim=64)
-    S = 256 if cuda else 32
+    # heads, FFN width and sequence grow with the group so that every rank keeps whole heads and 128-row blocks
+    cfg = LlamaConfig(vocab_size=512, hidden_size=256, intermediate_size=256 * max(2, world), num_hidden_layers=2,
+                      num_attention_heads=max(4, world), num_key_value_heads=max(2, world), head_dim=64)
+    S = 128 * max(2, world) if cuda else 32
     ok = True
     heap = None
     if fused:

@@ -39,7 +39,7 @@ def make_cfg(strategy, parallel, world, enabled):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--mode", default="pp", choices=["pp", "sp", "cp", "ulysses"])
+    ap.add_argument("--mode", default="pp", choices=["pp", "sp", "cp", "ulysses", "tp_dp"])
     ap.add_argument("--cuda", action="store_true", help="bf16 on GPUs through the CUDA kernels (fused TP path)")
     a = ap.parse_args()
     if CUDA:
@@ -60,6 +60,11 @@ def main():
     elif a.mode in ("cp", "ulysses"):
         par = {"cp": world, "dp_shard": 1, "cp_balancer": "head_tail" if a.mode == "cp" else "ulysses"}
         strategy, B = "context_parallel", 1
+    elif a.mode == "tp_dp":
+        # tensor parallel pairs x data parallel replicas: the clip must see the norm of the whole model, with the
+        # parameters replicated inside a pair (norms, embedding, head) counted once
+        par = {"tp": 2, "dp_shard": world // 2, "sp": True}
+        strategy, B = "tensor_parallel", world // 2
     else:
         par = {"tp": world, "dp_shard": 1, "sp": True}
         strategy, B = "tensor_parallel", 1
@@ -87,18 +92,24 @@ def main():
     ok = True
     for step in range(3):
         ids = torch.randint(0, 256, (B, S), generator=g)
-        l1 = tr.train_step({"input_ids": ids, "labels": ids})
+        mine = ids[rank // 2:rank // 2 + 1] if a.mode == "tp_dp" else ids
+        l1 = tr.train_step({"input_ids": mine, "labels": mine})
         try:
             dist.is_initialized = lambda: False
             l0 = ref.train_step({"input_ids": ids, "labels": ids})
         finally:
             dist.is_initialized = saved_init
-        if a.mode in ("cp", "ulysses"):
+        if a.mode in ("cp", "ulysses", "tp_dp"):
             # every rank reports the mean over ITS tokens; the shards are equal up to the one ignored last label
             t = torch.tensor([l1], device=dev)
             dist.all_reduce(t)
             l1 = float(t) / world
         good = abs(l1 - l0) < (3e-2 if CUDA else 2e-3) * max(1.0, abs(l0))
+        if a.mode == "tp_dp":
+            n1, n0 = float(tr.engine.flat.last_grad_norm), float(ref.engine.last_grad_norm)
+            good &= abs(n1 - n0) < (3e-2 if CUDA else 1e-3) * max(1.0, n0)
+            if rank == 0:
+                print(f"step {step} grad_norm={n1:.5f} oracle={n0:.5f}", flush=True)
         ok &= good
         if rank == 0:
             print(f"step {step} mode={a.mode} loss={l1:.5f} oracle={l0:.5f} ok={good}", flush=True)

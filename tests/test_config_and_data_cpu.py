@@ -192,3 +192,29 @@ def test_every_shipped_yaml_parses_and_resolves_its_mesh():
             seen[Path(f).name] = d.sizes
     assert seen["llama3_70b_tp4_pp2_fp8.yaml"]["tp"] == 4 and seen["llama3_70b_tp4_pp2_fp8.yaml"]["pp"] == 2
     assert seen["llama3_8b_cp8_128k.yaml"]["cp"] == 8
+
+
+def _reference_example_yamls():
+    from pathlib import Path
+    here = Path(__file__).resolve().parent.parent
+    for root in (here / "baseline" / "_ref" / "data_pipeline" / "examples", Path("/root/reference/data_pipeline/examples")):
+        found = sorted(root.glob("*.yaml")) if root.is_dir() else []
+        if found:
+            return found
+    return []
+
+
+@pytest.mark.parametrize("path", _reference_example_yamls() or [None], ids=lambda p: p.name if p else "absent")
+def test_reference_example_yamls_load_through_both_loaders(path):
+    """Every example YAML shipped with the reference (data_pipeline/examples/*.yaml) must load, unmodified, through
+    the trainer-side loader and the data-side loader, as the reference reads one file twice."""
+    if path is None:
+        pytest.skip("the reference's example YAMLs are not on this machine")
+    cfg = SOTAConfig.from_yaml(path)
+    raw = yaml.safe_load(path.read_text())
+    if "export" in raw and "save_merged_16bit" in raw["export"]:
+        assert cfg.export.save_merged_16bit == raw["export"]["save_merged_16bit"]
+    assert cfg.optimizer.learning_rate == float(raw.get("optimizer", {}).get("learning_rate", cfg.optimizer.learning_rate))
+    r = load_config(path)
+    assert r.is_ok(), r
+    assert r.unwrap().tokenizer.name_or_path

@@ -105,3 +105,13 @@ def test_trainer_config_drives_pipeline_and_sequence_parallel(mode, port):
            "127.0.0.1", "--master-port", str(port), str(ND_CASE), "--mode", mode]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=300)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+
+
+def test_tensor_parallel_pairs_times_data_parallel_clip_norm():
+    """tp=2 x dp=2 on four gloo ranks: the global gradient norm (replicated parameters counted once) and the losses
+    equal the single-process trainer's."""
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=4", "--master-addr",
+           "127.0.0.1", "--master-port", "29625", str(ND_CASE), "--mode", "tp_dp"]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    assert "RESULT mode=tp_dp ok=True" in r.stdout

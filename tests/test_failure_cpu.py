@@ -106,3 +106,40 @@ def test_restart_from_latest_undamaged_checkpoint_at_another_world_size(tmp_path
     assert outs[0][0] == 0, outs[0][1][-3000:]
     assert "ok=True" in outs[0][1] and "skipped=" in outs[0][1] and "skipped=0" not in outs[0][1]
     del older
+
+
+def test_expired_peer_wait_skips_the_update_and_raises(tmp_path):
+    """A fused collective that gave up waiting for a peer sets the heap's status word.  The engine folds that word into
+    its skip flag on the device (no update from an unwritten gradient shard) and the trainer raises where it reads the
+    loss.  The failing call is faked on the host: a status word that the test sets."""
+    import pytest
+    import torch
+    from trainscale_b200.core.errors import CommunicationError
+    from trainscale_b200.parallel.symm import SymmetricHeap
+    from trainscale_b200.config.sota_config import SOTAConfig
+    from trainscale_b200.trainer.sota_trainer import SOTATrainer
+
+    cfg = SOTAConfig.from_dict({
+        "model": {"architecture": {"vocab_size": 128, "hidden_size": 32, "intermediate_size": 64, "num_hidden_layers": 1,
+                                   "num_attention_heads": 2, "num_key_value_heads": 1}},
+        "optimizer": {"type": "adamw", "learning_rate": 1e-2}, "scheduler": {"type": "constant", "warmup_steps": 0},
+        "distributed": {"enabled": False, "strategy": "ddp"}, "hardware": {"device": "cpu", "precision": "fp32"},
+        "data": {"max_seq_length": 16},
+        "training": {"output_dir": str(tmp_path), "max_steps": 4, "save_strategy": "no", "eval_strategy": "no"}})
+    tr = SOTATrainer(cfg)
+    tr.setup_model()
+    heap = SymmetricHeap.__new__(SymmetricHeap)          # the status word and its readers, without any peer memory
+    heap.status = torch.zeros(1, dtype=torch.int32)
+    heap.rank, heap.world = 0, 1
+    tr.engine._symm = heap
+    ids = torch.randint(0, 128, (2, 16), generator=torch.Generator().manual_seed(0))
+    tr.train_step({"input_ids": ids, "labels": ids})       # healthy step: weights move
+    before = {n: p.detach().clone() for n, p in tr.model.named_parameters()}
+    heap.status.fill_(1)                                   # "a peer did not arrive"
+    with pytest.raises(CommunicationError):
+        tr.train_step({"input_ids": ids, "labels": ids})
+    for n, p in tr.model.named_parameters():
+        assert torch.equal(p.detach(), before[n]), f"{n} was updated from an unreduced gradient"
+    assert int(heap.status) == 0                           # reading the status clears it
+    tr.train_step({"input_ids": ids, "labels": ids})
+    assert any(not torch.equal(p.detach(), before[n]) for n, p in tr.model.named_parameters())

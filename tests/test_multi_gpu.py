@@ -22,21 +22,49 @@ def _launch(script, *args, port, nproc=2, timeout=600):
     return r.stdout
 
 
+def _need(nproc):
+    if torch.cuda.device_count() < nproc:
+        pytest.skip(f"needs {nproc} GPUs")
+
+
 @pytest.mark.parametrize("args,port", [
     (["--comm", "auto"], 29731),                          # fused reduce-scatter + AdamW/all-gather kernels
     (["--comm", "nccl"], 29732),                          # library collectives
-    (["--strategy", "FULL_SHARD"], 29733),
-    (["--strategy", "FULL_SHARD", "--recompute"], 29734),
+    (["--strategy", "FULL_SHARD", "--comm", "fused"], 29733),          # one-sided shard pulls + slot-ring reduce-scatter
+    (["--strategy", "FULL_SHARD", "--comm", "fused", "--recompute"], 29734),
+    (["--strategy", "FULL_SHARD", "--comm", "fused", "--accum", "2"], 29745),
+    (["--strategy", "FULL_SHARD", "--comm", "nccl"], 29746),
     (["--strategy", "NO_SHARD"], 29735),
 ])
 def test_engine_matches_single_process_on_two_gpus(args, port):
     out = _launch("engine_equivalence.py", "--device", "cuda", *args, port=port)
     assert "ok=True" in out
+    if "fused" in args:
+        assert "fused=True" in out
+
+
+@pytest.mark.parametrize("nproc", [4, 8])
+@pytest.mark.parametrize("args,port", [
+    (["--comm", "fused"], 29751),
+    (["--strategy", "FULL_SHARD", "--comm", "fused"], 29752),
+])
+def test_engine_matches_single_process_on_more_gpus(args, port, nproc):
+    """The peer-memory reduce-scatter / AdamW-broadcast / shard-pull kernels at 4 and 8 ranks."""
+    _need(nproc)
+    out = _launch("engine_equivalence.py", "--device", "cuda", *args, port=port + nproc, nproc=nproc)
+    assert "ok=True" in out and "fused=True" in out
 
 
 @pytest.mark.parametrize("args,port", [([], 29736), (["--fused"], 29737)])
 def test_tensor_parallel_decoder_on_two_gpus(args, port):
     out = _launch("tp_equivalence.py", "--cuda", *args, port=port)
+    assert "ok=False" not in out
+
+
+@pytest.mark.parametrize("nproc", [4, 8])
+def test_fused_tensor_parallel_decoder_on_more_gpus(nproc):
+    _need(nproc)
+    out = _launch("tp_equivalence.py", "--cuda", "--fused", port=29760 + nproc, nproc=nproc)
     assert "ok=False" not in out
 
 

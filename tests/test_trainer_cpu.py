@@ -109,3 +109,20 @@ def test_numerical_stability_check_counts_bad_windows():
     import pytest
     with pytest.raises(GradientOverflowError):
         t._check_numerical_stability(float("inf"))
+
+
+def test_partial_accumulation_window_at_epoch_end_is_dropped(tmp_path):
+    """A loader whose length is not a multiple of the accumulation steps: the left-over micro-batch of an epoch makes
+    no step and must not leak into the next epoch's first update (the run equals one over the loader without it)."""
+    def run(n_batches, sub):
+        cfg = make_cfg(tmp_path / sub, training={"num_train_epochs": 2, "max_steps": 0, "gradient_accumulation_steps": 2})
+        tr = SOTATrainer(cfg)
+        tr.setup_model()
+        out = tr.train(fixed_loader(8)[:n_batches])
+        return out, {n: p.detach().clone() for n, p in tr.model.named_parameters()}, tr
+    out5, p5, tr5 = run(5, "a")
+    out4, p4, _ = run(4, "b")
+    assert out5["global_step"] == out4["global_step"] == 4
+    for n in p4:
+        assert torch.equal(p5[n], p4[n]), n
+    assert tr5.engine.micro_step % 2 == 0

@@ -237,6 +237,7 @@ class ExportConfig:
     hub_token: Optional[str] = None
     hub_private: bool = False
     merge_lora: bool = True
+    save_merged_16bit: bool = True
     gguf_quantization: str = "q4_k_m"
 
 

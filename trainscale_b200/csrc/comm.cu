@@ -8,6 +8,11 @@
 //   ts_symm_adamw_bcast      sharded AdamW fused with the parameter all-gather: the update kernel writes each new
 //                            bf16 weight straight into every rank's parameter buffer (peer stores / multimem.st).
 //   ts_symm_all_gather       plain pull all-gather (used when another optimizer produced the shard).
+//   ts_symm_gather_pull      one-sided parameter gather of ZeRO-3: every rank keeps its 1/W bf16 shard of a unit in
+//                            symmetric memory and a consumer copies all W shards into a LOCAL full-size buffer with
+//                            plain peer loads.  No rendezvous: shards only change in the optimizer step, which is
+//                            fenced by the step's barriers, so a rank never waits for a peer to launch anything
+//                            (an NCCL all-gather makes every rank wait for the slowest one, once per layer).
 //   ts_symm_barrier          flag barrier over the signal pads (release/acquire at system scope, bounded waits).
 //
 // They replace the NCCL reduce_scatter_tensor / all_gather_into_tensor + separate cast / AdamW launches behind
@@ -230,6 +235,25 @@ symm_all_gather_kernel(PeerTable peers, PadTable pads, int rank, int world, long
   }
 }
 
+// one-sided gather: dst[pr * shard .. (pr+1) * shard) = peer pr's shard, for every pr (this rank's included).
+// Four 16-byte loads in flight per thread; the grid is kept small by the host so that the copy shares the SMs
+// with the GEMMs it runs under.
+__global__ void __launch_bounds__(512)
+symm_gather_pull_kernel(PeerTable peers, uint4* __restrict__ dst, int rank, int world, long long nvec) {
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (int pi = 0; pi < world; ++pi) {
+    const int pr = (rank + 1 + pi) % world;          // remote shards first, a different peer first on every rank
+    const uint4* __restrict__ src = reinterpret_cast<const uint4*>(peers.ptr[pr]);
+    uint4* d = dst + pr * nvec;
+    long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+    for (; i + 3 * stride < nvec; i += 4 * stride) {
+      const uint4 a = src[i], b = src[i + stride], c = src[i + 2 * stride], e = src[i + 3 * stride];
+      d[i] = a; d[i + stride] = b; d[i + 2 * stride] = c; d[i + 3 * stride] = e;
+    }
+    for (; i < nvec; i += stride) d[i] = src[i];
+  }
+}
+
 static inline void fill_tables(PeerTable& pt, PadTable& pd, const unsigned long long* ptrs,
                                const unsigned long long* pads, int world, long long byte_offset) {
   for (int i = 0; i < MAX_WORLD; ++i) {
@@ -312,6 +336,24 @@ extern "C" int ts_symm_all_gather(const unsigned long long* peer_ptrs, const uns
   fill_tables(pt, pd, peer_ptrs, pad_ptrs, world, byte_offset);
   symm_all_gather_kernel<<<sm_count(), 512, 0, ST(stream)>>>(pt, pd, rank, world, shard_bytes, slot0, epoch,
                                                              wait_cycles, status);
+  return (int)cudaGetLastError();
+}
+
+// peer_ptrs: the W addresses of the symmetric shard store; byte_offset: this unit's shard inside it; dst: local buffer
+// of world * shard_bytes.  Makes no flag traffic and waits for nobody.
+extern "C" int ts_symm_gather_pull(const unsigned long long* peer_ptrs, long long byte_offset, void* dst, int rank,
+                                   int world, long long shard_bytes, int max_blocks, void* stream) {
+  if (world > MAX_WORLD || shard_bytes % 16 != 0 || (reinterpret_cast<unsigned long long>(dst) & 15ull) ||
+      (byte_offset & 15ll))
+    return -10;
+  PeerTable pt; PadTable pd;
+  fill_tables(pt, pd, peer_ptrs, nullptr, world, byte_offset);
+  const long long nvec = shard_bytes >> 4;
+  long long blocks = (nvec + 2047) / 2048;
+  const long long cap = max_blocks > 0 ? max_blocks : 32;
+  if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;
+  symm_gather_pull_kernel<<<(unsigned)blocks, 512, 0, ST(stream)>>>(pt, reinterpret_cast<uint4*>(dst), rank, world, nvec);
   return (int)cudaGetLastError();
 }
 

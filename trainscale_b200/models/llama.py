@@ -415,7 +415,7 @@ class LlamaForCausalLM(nn.Module):
     def forward(self, input_ids=None, attention_mask=None, labels=None, position_ids=None, cu_seqlens=None,
                 doc_ids=None, kv_caches=None, return_logits: bool | None = None, loss_scale: float = 1.0,
                 label_smoothing: float = 0.0, ignore_index: int = -100, shift_labels: bool = True,
-                inputs_embeds=None, **_unused) -> CausalLMOutput:
+                inputs_embeds=None, loss_denominator=None, **_unused) -> CausalLMOutput:
         h = self.model(input_ids, position_ids, cu_seqlens, doc_ids, kv_caches, inputs_embeds)
         out = CausalLMOutput(hidden_states=h)
         if labels is not None:
@@ -430,7 +430,7 @@ class LlamaForCausalLM(nn.Module):
                 tgt = labels
             loss, count = cross_entropy.fused_linear_cross_entropy(
                 h, self.head_weight, tgt, ignore_index, label_smoothing, 1.0, self.config.final_logit_softcap,
-                self.loss_chunk_tokens, "mean", loss_scale)
+                self.loss_chunk_tokens, "mean", loss_scale, loss_denominator)
             if self.config.num_local_experts > 0 and self.config.router_aux_loss_coef > 0 and self.training:
                 aux = [l.mlp.aux_loss for l in self.model.layers if getattr(l.mlp, "aux_loss", None) is not None]
                 if aux:

@@ -139,7 +139,7 @@ def _pad_ld(V: int) -> int:
 class _FusedLinearCE(torch.autograd.Function):
     @staticmethod
     def forward(ctx, hidden, weight, labels, ignore_index, label_smoothing, logit_scale, softcap, chunk_tokens,
-                reduction, loss_scale):
+                reduction, loss_scale, denominator=None):
         T, H = hidden.shape
         V = weight.shape[0]
         dev = hidden.device
@@ -147,7 +147,8 @@ class _FusedLinearCE(torch.autograd.Function):
         valid = (labels != ignore_index)
         count = valid.sum().clamp(min=1).to(torch.float32)
         if reduction == "mean":
-            gscale = (1.0 / count).reshape(1)
+            den = count if denominator is None else denominator.to(torch.float32).clamp(min=1e-6)
+            gscale = (1.0 / den).reshape(1)
         else:
             gscale = torch.ones(1, dtype=torch.float32, device=dev)
         need_dh = hidden.requires_grad
@@ -194,17 +195,21 @@ class _FusedLinearCE(torch.autograd.Function):
         gw = None
         if dw is not None:
             gw = (dw * g).to(ctx.w_dtype)
-        return gh, gw, None, None, None, None, None, None, None, None
+        return gh, gw, None, None, None, None, None, None, None, None, None
 
 
 def fused_linear_cross_entropy(hidden: torch.Tensor, weight: torch.Tensor, labels: torch.Tensor,
                                ignore_index: int = -100, label_smoothing: float = 0.0, logit_scale: float = 1.0,
                                softcap: float = 0.0, chunk_tokens: int = DEFAULT_CHUNK_TOKENS,
-                               reduction: str = "mean", loss_scale: float = 1.0):
+                               reduction: str = "mean", loss_scale: float = 1.0,
+                               denominator: torch.Tensor | None = None):
     """loss (and valid-token count) of CE(hidden @ weight.T, labels) without materialising the logits.
 
     `labels` must already be aligned with `hidden` rows (the causal shift is the caller's job).
     `loss_scale` (e.g. 1/grad-accumulation) is folded into both the returned loss and the gradients.
+    `denominator` (a one-element device tensor): with reduction "mean", divide the summed loss by it instead of by
+    this call's own count of valid labels - a rank that holds a slice of a longer sequence passes its share of the
+    global count, and nothing is read back to the host.
     When `weight.main_grad` exists the weight gradient is accumulated straight into it.
     """
     h2 = hidden.reshape(-1, hidden.shape[-1])
@@ -212,13 +217,13 @@ def fused_linear_cross_entropy(hidden: torch.Tensor, weight: torch.Tensor, label
         if not h2.is_contiguous():
             h2 = h2.contiguous()
         return _FusedLinearCE.apply(h2, weight, labels, ignore_index, label_smoothing, logit_scale, softcap,
-                                    chunk_tokens, reduction, loss_scale)
+                                    chunk_tokens, reduction, loss_scale, denominator)
     return linear_cross_entropy_reference(h2, weight, labels, ignore_index, label_smoothing, logit_scale, softcap,
-                                          reduction, loss_scale)
+                                          reduction, loss_scale, denominator)
 
 
 def linear_cross_entropy_reference(hidden, weight, labels, ignore_index=-100, label_smoothing=0.0, logit_scale=1.0,
-                                   softcap=0.0, reduction="mean", loss_scale=1.0):
+                                   softcap=0.0, reduction="mean", loss_scale=1.0, denominator=None):
     """Plain PyTorch fp32 math with the same semantics (CPU path and test oracle)."""
     logits = (hidden.float() @ weight.float().t()) * logit_scale
     if softcap > 0:
@@ -228,7 +233,7 @@ def linear_cross_entropy_reference(hidden, weight, labels, ignore_index=-100, la
     loss = F.cross_entropy(logits, labels, ignore_index=ignore_index, label_smoothing=label_smoothing,
                            reduction="sum")
     if reduction == "mean":
-        loss = loss / count
+        loss = loss / (count if denominator is None else denominator.to(loss.dtype).clamp(min=1e-6).reshape(()))
     return loss * loss_scale, count
 
 

@@ -15,9 +15,12 @@ buffers laid out for the B200 kernels:
     weights back, and an all-gather of the updated shards (peer stores from the update kernel, or NCCL).
 
 Sharding strategies (names as in data_pipeline/trainer/distributed/fsdp2.py:384-406):
-  FULL_SHARD     every decoder-layer unit keeps only its 1/W bf16 shard; the full buffer is all-gathered into a
-                 recycled pool slot before the unit's forward and again before its backward (next unit prefetched on
-                 the communication stream), gradients are reduce-scattered and their buffer recycled per unit
+  FULL_SHARD     every decoder-layer unit keeps only its 1/W bf16 shard; the full buffer is gathered before the unit's
+                 forward and again before its backward (next unit prefetched on the communication stream), gradients
+                 are reduce-scattered and their buffer recycled per unit.  On the peer-memory path the shards live in
+                 symmetric memory and the gather is a one-sided pull (no rank waits for another to launch anything);
+                 gradients are written into a small ring of symmetric slots that the fused reduce-scatter reads, and
+                 a slot is handed back only after a device barrier says every peer has finished reading it
   SHARD_GRAD_OP  parameters stay gathered between steps (default on 180 GB parts: a full bf16 copy of an
                  8B model is 16 GB), gradients + optimizer state sharded
   NO_SHARD       DDP: gradients all-reduced, every rank holds the full optimizer state
@@ -52,6 +55,7 @@ class EngineConfig:
     decay_norm_and_bias: bool = True                # reference passes every parameter to AdamW with one wd
     optimizer: str = "adamw"                        # adamw | lion
     comm: str = "auto"                              # auto | fused | nccl
+    grad_slots: int = 3                             # FULL_SHARD on peer memory: gradient buffers in the slot ring
     overlap_grad_reduce: bool = True
     skip_nonfinite: bool = True
 
@@ -152,6 +156,7 @@ class FlatUnit:
     def mark_grads_fresh(self):
         for _, p, _, _ in self.entries:
             p.grad_added = False
+            p.grad = None        # a gradient ordinary autograd left behind (dropped accumulation window)
         self.grad_ready = False
 
     def any_grad(self) -> bool:
@@ -216,6 +221,34 @@ class _BufferPool:
         return sum(s["buf"].numel() * s["buf"].element_size() for s in self.slots)
 
 
+class _SymmetricSlotRing:
+    """Fixed ring of full-size gradient buffers in symmetric memory, used in the same order on every rank (the fused
+    reduce-scatter reads the SAME slot of every peer).  A slot is released on the communication stream behind a device
+    barrier of all ranks, so its next writer (any rank's backward) starts only when no peer still reads it."""
+
+    def __init__(self, heap, numel: int, dtype: torch.dtype, n_slots: int):
+        self.slots = [{"buf": heap.alloc(numel, dtype), "event": None} for _ in range(n_slots)]
+        self.next = 0
+
+    def acquire(self, numel: int, dtype: torch.dtype, stream):
+        i = self.next
+        self.next = (self.next + 1) % len(self.slots)
+        s = self.slots[i]
+        if s["buf"].numel() < numel or s["buf"].dtype != dtype:
+            raise RuntimeError("gradient slot ring was sized for another unit shape")
+        if s["event"] is not None and stream is not None:
+            stream.wait_event(s["event"])
+        return i, s["buf"][:numel]
+
+    def release(self, idx: int, stream):
+        ev = torch.cuda.Event()
+        ev.record(stream)
+        self.slots[idx]["event"] = ev
+
+    def bytes(self) -> int:
+        return sum(s["buf"].numel() * s["buf"].element_size() for s in self.slots)
+
+
 class FlatShardedEngine:
     """Owns the flat buffers, the gradient reduction schedule and the sharded optimizer step."""
 
@@ -249,17 +282,17 @@ class FlatShardedEngine:
         self.param_groups = [{"lr": cfg.lr, "weight_decay": cfg.weight_decay, "betas": cfg.betas, "eps": cfg.eps,
                               "initial_lr": cfg.lr}]
         self._symm = None
-        # FULL_SHARD recycles its gather / gradient buffers between units, which the peer-memory kernels (they read
-        # a peer's buffer without a hand-shake on its reuse) do not allow: it runs on the library collectives
+        self._symm_anchor = None
         self.full_shard = cfg.sharding_strategy == "FULL_SHARD" and self.distributed
-        # (the fused reduce-scatter also sums the squared gradients inside the kernel, which would come before the
-        # replica average of hybrid sharding: that mode uses the library collectives too)
-        if self.distributed and self.is_cuda and cfg.comm in ("auto", "fused") and not self.full_shard \
-                and replicate_group is None:
+        # (the fused reduce-scatter sums the squared gradients inside the kernel, which would come before the replica
+        # average of hybrid sharding: that mode uses the library collectives)
+        if self.distributed and self.is_cuda and cfg.comm in ("auto", "fused") and replicate_group is None:
             from . import symm
             self._symm = symm.SymmetricHeap.try_create(self.pg, self.device)
             if self._symm is None and cfg.comm == "fused":
                 raise RuntimeError("comm='fused' requested but symmetric memory is unavailable")
+            if self._symm is not None:
+                self._symm_anchor = self._symm.alloc(256, torch.float32)     # its signal pad carries the barriers
         # ---- partition parameters into units (a decoder layer each; everything else in unit 'root')
         if unit_modules is None:
             unit_modules = self._default_units(model)
@@ -272,8 +305,11 @@ class FlatShardedEngine:
                 continue
             seen.update(id(p) for _, p in named)
             gd = torch.float32 if name in ("", "root") else grad_dtype
+            resharded = self.full_shard and name not in ("", "root")
+            # a re-sharded unit's full buffers are ordinary memory (its storage is resized around each use); what its
+            # peers read are the shard store and the gradient slot ring below
             self.units.append(FlatUnit(name or "root", named, cfg, self.rank, self.world, self.device, gd,
-                                       self._alloc_fn(), resharded=self.full_shard and name not in ("", "root")))
+                                       None if resharded else self._alloc_fn(), resharded=resharded))
         rest = [(n, p) for n, p in model.named_parameters() if id(p) not in seen]
         if rest:
             self.units.append(FlatUnit("root", rest, cfg, self.rank, self.world, self.device, torch.float32,
@@ -289,11 +325,26 @@ class FlatShardedEngine:
         self._install_boundaries(unit_modules)
         if self.distributed:
             self._sync_initial_params()
-        for u in self.units:
-            if u.resharded:
-                s0 = u.shard_start
+        sharded = [u for u in self.units if u.resharded]
+        store = None
+        if sharded and self._symm is not None:
+            # every unit's bf16 shard in ONE symmetric allocation (peers pull from it), and the gradient slot ring
+            store = self._symm.alloc(sum(u.shard_numel for u in sharded), cfg.param_dtype)
+            self._grad_pool = _SymmetricSlotRing(self._symm, max(u.numel for u in sharded), grad_dtype,
+                                                 max(2, int(getattr(cfg, "grad_slots", 3))))
+        off = 0
+        for u in sharded:
+            s0 = u.shard_start
+            if store is not None:
+                u.param_shard = store[off:off + u.shard_numel]
+                u.param_shard.copy_(u.flat_param[s0:s0 + u.shard_numel])
+                off += u.shard_numel
+            else:
                 u.param_shard = u.flat_param[s0:s0 + u.shard_numel].clone()
-                u.free_full_params()      # the construction-time full copy is dropped here
+            u.free_full_params()      # the construction-time full copy is dropped here
+        if store is not None:
+            torch.cuda.synchronize(self.device)
+            dist.barrier(group=self.pg)   # every rank's shards are in place before anyone pulls them
 
     # ------------------------------------------------------------------ construction helpers
     def _alloc_fn(self):
@@ -408,7 +459,11 @@ class FlatShardedEngine:
             stream.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(stream) if stream is not None else contextlib.nullcontext():
             if self.is_cuda:
-                dist.all_gather_into_tensor(buf, u.param_shard, group=self.pg)
+                if self._symm is not None:
+                    from . import fused_comm
+                    fused_comm.gather_pull(self._symm, u.param_shard, buf)
+                else:
+                    dist.all_gather_into_tensor(buf, u.param_shard, group=self.pg)
                 u.gather_event = torch.cuda.Event()
                 u.gather_event.record(stream)
             else:
@@ -436,17 +491,28 @@ class FlatShardedEngine:
 
     @contextlib.contextmanager
     def summon_full_params(self):
-        """All parameters materialised (checkpoint export, evaluation hooks); re-sharded on exit."""
+        """All parameters materialised (checkpoint export, evaluation hooks); re-sharded on exit.  Collective: every
+        rank enters and leaves it.  On the peer-memory path the body may rewrite `param_shard` (a checkpoint load
+        does), so a device barrier separates the peers' pulls from the body, and the body from whatever pulls next."""
         touched = []
         for i, u in enumerate(self.units):
             if u.resharded and not u.gathered:
                 self._ensure_gathered(i)
                 touched.append(i)
+        fence = self._symm is not None and any(u.resharded for u in self.units)
+        if fence:
+            self._device_barrier()
         try:
             yield
         finally:
             for i in touched:
                 self._release_params(i)
+            if fence:
+                self._device_barrier()
+
+    def _device_barrier(self):
+        from . import fused_comm
+        fused_comm.barrier(self._symm, self._symm_anchor)
 
     def _unit_backward_done(self, idx: int):
         u = self.units[idx]
@@ -552,8 +618,19 @@ class FlatShardedEngine:
         with torch.cuda.stream(stream) if stream is not None else contextlib.nullcontext():
             if self._symm is not None:
                 from . import fused_comm
-                fused_comm.reduce_scatter_fp32(self._symm, u.flat_grad, u.shard_grad, u.shard_start, 1.0 / self.world,
-                                               self.norm_sq, self.nonfinite)
+                # the kernel also sums the squares of what it writes; with several micro-batches per step a re-sharded
+                # unit's shard is a sum of reductions, whose norm step() takes afterwards
+                once = not u.resharded or max(1, self.cfg.gradient_accumulation_steps) == 1
+                dst = u.shard_grad if first or not u.resharded else \
+                    torch.empty(u.shard_numel, dtype=torch.float32, device=self.device)
+                fused_comm.reduce_scatter_fp32(self._symm, u.flat_grad, dst, u.shard_start, 1.0 / self.world,
+                                               self.norm_sq if once else None, self.nonfinite if once else None)
+                u.norm_in_reduce = once
+                if dst is not u.shard_grad:
+                    u.shard_grad.add_(dst)
+                if u.resharded:
+                    # every peer has finished reading this slot before it goes back to the ring
+                    fused_comm.barrier(self._symm, u.flat_grad)
             else:
                 if self.is_cuda:
                     tmp = torch.empty(u.shard_numel, dtype=u.flat_grad.dtype, device=self.device)
@@ -623,20 +700,26 @@ class FlatShardedEngine:
         if not fused_norm:
             self.norm_sq.zero_()
             self.nonfinite.zero_()
-            for u in self.units:
+        for u in self.units:
+            if not (fused_norm and getattr(u, "norm_in_reduce", False)):
                 optim_ops.sumsq_(self.norm_sq, self._shard_grad_view(u), self.nonfinite)
+        if self._symm is not None:
+            # a fused collective that gave up waiting for a peer left its output unwritten: the update is skipped
+            # on every rank (the flag joins the non-finite word, reduced with MAX below); the host learns of it
+            # where it reads the loss (`check_comm_status`)
+            self.nonfinite.add_(self._symm.status_flag())
+        if self.replicated_params:
+            # parameters replicated over a tensor-parallel group would be counted once per rank by the all-reduce
+            # over that group below: keep 1/tp of their share (their gradients are identical on every rank of it).
+            # The share is taken from what this rank contributes to the sum: its reduced shard when the gradients are
+            # sharded, the whole buffer otherwise.
+            rep = torch.zeros_like(self.norm_sq)
+            for u, a, b in self._replicated_slices():
+                rep += self._shard_grad_view(u)[a:b].float().pow(2).sum()
+            self.norm_sq -= rep * (1.0 - 1.0 / self.replica_factor)
         if self.world > 1 and cfg.sharding_strategy != "NO_SHARD":
             dist.all_reduce(self.norm_sq, group=self.pg)
             dist.all_reduce(self.nonfinite, op=dist.ReduceOp.MAX, group=self.pg)
-        if self.replicated_params and self.world == 1:
-            # parameters replicated over a tensor-parallel group would be counted once per rank by the all-reduce
-            # below: keep 1/tp of their share here (their gradients are identical on every rank of that group)
-            rep = torch.zeros_like(self.norm_sq)
-            for p in self.replicated_params:
-                g = getattr(p, "main_grad", None)
-                if g is not None:
-                    rep += g.float().pow(2).sum()
-            self.norm_sq -= rep * (1.0 - 1.0 / self.replica_factor)
         for g in self.norm_groups:
             # model-parallel groups whose ranks hold disjoint parameters (pipeline stages): the clip uses the norm
             # of the whole model
@@ -652,7 +735,7 @@ class FlatShardedEngine:
             for seg in u.segments():
                 sl = slice(seg.start, seg.end)
                 out = u.param_shard[sl] if u.resharded else u.flat_param[s0 + seg.start:s0 + seg.end]
-                if fused_norm and cfg.optimizer == "adamw":
+                if fused_norm and cfg.optimizer == "adamw" and not u.resharded:
                     from . import fused_comm
                     fused_comm.adamw_bcast(self._symm, u.flat_param, s0 + seg.start, u.master[sl], u.exp_avg[sl],
                                            u.exp_avg_sq[sl], g[sl], lr=lr, beta1=b1, beta2=b2,
@@ -669,14 +752,42 @@ class FlatShardedEngine:
                                           step=self.step_count, sumsq=self.norm_sq, max_norm=cfg.max_grad_norm,
                                           skip_flag=skip)
         if self.world > 1 and cfg.sharding_strategy != "NO_SHARD":
-            if fused_norm and cfg.optimizer == "adamw":
-                # the update kernels already stored into every rank's buffer: one barrier makes them visible
-                from . import fused_comm
-                fused_comm.barrier(self._symm, self.units[0].flat_param)
-            else:
+            if not (fused_norm and cfg.optimizer == "adamw"):
                 self._all_gather_params()
+            if fused_norm:
+                # the update kernels stored into every rank's buffers / into the shards peers pull from: one device
+                # barrier makes them visible before anyone's next forward reads them
+                from . import fused_comm
+                fused_comm.barrier(self._symm, self._symm_anchor)
+                if self.step_count == 2:
+                    self._symm.mark_warm()
         self.zero_grad()
         return self.last_grad_norm
+
+    def check_comm_status(self) -> None:
+        """Host-side check (one device read) that no fused collective gave up on a peer and no kernel recorded an
+        error; raises CommunicationError / KernelError.  The trainer calls it where it reads the loss anyway."""
+        if self._symm is not None:
+            self._symm.check_status()
+        if self.is_cuda:
+            from ..ops import _lib
+            _lib.raise_on_any_device_error()
+
+    def _replicated_slices(self) -> list:
+        """(unit, start, end) ranges of this rank's gradient shard that belong to `replicated_params`."""
+        ids = {id(p) for p in self.replicated_params}
+        key = (len(ids), self.cfg.sharding_strategy)
+        if getattr(self, "_rep_slices_key", None) != key:
+            out = []
+            for u in self.units:
+                s0, s1 = u.shard_start, u.shard_start + u.shard_numel
+                for _, p, o, k in u.entries:
+                    if id(p) in ids:
+                        a, b = max(o, s0), min(o + k, s1)
+                        if b > a:
+                            out.append((u, a - s0, b - s0))
+            self._rep_slices, self._rep_slices_key = out, key
+        return self._rep_slices
 
     def _all_gather_params(self):
         for u in self.units:
@@ -701,6 +812,7 @@ class FlatShardedEngine:
             u.mark_grads_fresh()
             u.reduce_event = None
             u.shard_accum = False
+            u.norm_in_reduce = False
         if self._symm is not None and self.world > 1:
             self.norm_sq.zero_()
             self.nonfinite.zero_()

@@ -47,6 +47,20 @@ def all_gather_inplace(heap: SymmetricHeap, flat: torch.Tensor, shard_start: int
     _lib.check(rc, "ts_symm_all_gather")
 
 
+def gather_pull(heap: SymmetricHeap, shard: torch.Tensor, out_full: torch.Tensor, max_blocks: int = 0) -> None:
+    """out_full = concatenation over ranks of `shard` (a view into symmetric memory, same offset on every rank).
+    One-sided: reads the peers' shards with plain loads and waits for nobody; the caller guarantees that no rank is
+    writing its shard (shards change only inside the optimizer step, between the step's barriers)."""
+    buf, off = heap.lookup(shard)
+    nbytes = shard.numel() * shard.element_size()
+    if out_full.numel() * out_full.element_size() != nbytes * heap.world:
+        raise ValueError("gather_pull: output must hold world x shard")
+    lib = _lib.load("comm")
+    rc = lib.ts_symm_gather_pull(buf.peer_ptrs, _ll(off), _lib.ptr(out_full), heap.rank, heap.world, _ll(nbytes),
+                                 int(max_blocks), _lib.stream_ptr())
+    _lib.check(rc, "ts_symm_gather_pull")
+
+
 def barrier(heap: SymmetricHeap, anchor: torch.Tensor) -> None:
     """Device-side barrier of all ranks on the current stream (all earlier peer stores are visible after it)."""
     buf, _ = heap.lookup(anchor)

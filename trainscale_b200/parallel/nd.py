@@ -134,6 +134,22 @@ class NDEngine:
     def step(self, lr=None):
         return self.flat.step(lr)
 
+    def zero_grad(self):
+        self.flat.zero_grad()
+
+    def check_comm_status(self) -> None:
+        """Status words of every symmetric heap this engine's kernels wait on (tensor-parallel GEMMs, context-parallel
+        K/V exchange, data-parallel reduction); raises CommunicationError when a peer wait ran out."""
+        heaps = []
+        if self.tp is not None and getattr(self.tp, "heap", None) is not None:
+            heaps.append(self.tp.heap)
+        if self.dims.enabled("cp"):
+            from .cp import _PeerKV
+            heaps.extend(h for h in _PeerKV._heaps.values() if h is not None)
+        for h in heaps:
+            h.check_status()
+        self.flat.check_comm_status()
+
     @property
     def micro_step(self):
         return self.flat.micro_step

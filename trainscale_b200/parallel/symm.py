@@ -43,8 +43,17 @@ class SymmetricHeap:
         self._by_ptr: dict[int, SymmBuffer] = {}
         self.use_multicast = os.environ.get("TS_SYMM_MULTICAST", "1") != "0"
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
-        # generous by default (ranks can be seconds apart on the first step); tests shorten it
-        self.wait_cycles = int(float(os.environ.get("TS_SYMM_WAIT_SECONDS", "60")) * 1.9e9)
+        # A peer wait gives up after `wait_cycles` clock ticks and sets `status`.  Until `mark_warm()` the limit is
+        # generous (lazy library loading and first-use allocations put ranks tens of seconds apart on the first step);
+        # afterwards a rank that is this late is treated as lost.  TS_SYMM_WAIT_SECONDS overrides both (tests shorten it).
+        env = os.environ.get("TS_SYMM_WAIT_SECONDS")
+        self._cold_cycles = int(float(env if env else "60") * 1.9e9)
+        self._warm_cycles = int(float(env if env else "10") * 1.9e9)
+        self.wait_cycles = self._cold_cycles
+
+    def mark_warm(self) -> None:
+        """Call once every rank has completed a full step: later peer waits use the short limit."""
+        self.wait_cycles = self._warm_cycles
 
     @classmethod
     def try_create(cls, group, device):
@@ -88,7 +97,12 @@ class SymmetricHeap:
                 return buf, p - base
         raise KeyError("tensor is not backed by symmetric memory")
 
+    def status_flag(self) -> torch.Tensor:
+        """1.0 on the device when a fused collective of this heap gave up waiting for a peer (no host sync)."""
+        return self.status.ne(0).to(torch.float32)
+
     def check_status(self) -> None:
+        """Host read of the status word; raises CommunicationError when a peer wait ran out."""
         if int(self.status.item()) != 0:
             self.status.zero_()
             from ..core.errors import CommunicationError

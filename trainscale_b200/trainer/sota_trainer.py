@@ -248,6 +248,13 @@ class SOTATrainer:
                                      replicate_group=dims.group("dp_replicate"))
         return FlatShardedEngine(self.model, ec, device=self.device)
 
+    def _data_parallel_size(self) -> int:
+        """Ranks that consume different samples (tensor / pipeline / context ranks of one replica share theirs)."""
+        dims = getattr(self.engine, "dims", None)
+        if dims is not None:
+            return max(1, dims.size("dp"))
+        return self.world_size
+
     def _flops_per_token(self) -> float:
         cfg = getattr(self.model, "config", None)
         seq = self.config.data.max_seq_length
@@ -292,21 +299,21 @@ class SOTATrainer:
         if self.engine is not None and hasattr(self.engine, "forward_backward") and self.engine.pipelined:
             return self.engine.forward_backward(batch, loss_scale)
         cp_group = getattr(self.engine, "cp_group", None) if self.engine is not None else None
+        denom = None
         if cp_group is not None and batch.get("labels_shifted", False):
             # context parallelism: every rank averages over ITS valid tokens and the engine averages the ranks, which
             # equals the mean over the whole sequence only if the shards hold the same number of valid labels.  They do
-            # not in general (the last position has no label; packed documents mask more), so weight each rank by its
-            # share: local mean * (n_local * cp / n_global)
-            n_local = (batch["labels"] != self.config.loss.ignore_index).sum().float()
-            n_global = n_local.clone()
+            # not in general (the last position has no label; packed documents mask more), so each rank divides its
+            # summed loss by n_global / cp.  The count stays on the device: the loss head takes it as a tensor.
+            n_global = (batch["labels"] != self.config.loss.ignore_index).sum().float().reshape(1)
             dist.all_reduce(n_global, group=cp_group)
-            loss_scale = loss_scale * float(n_local * dist.get_world_size(cp_group) / n_global.clamp(min=1.0))
-        loss, ntok = self._forward_loss(batch, loss_scale)
+            denom = n_global.clamp(min=1.0) / dist.get_world_size(cp_group)
+        loss, ntok = self._forward_loss(batch, loss_scale, denom)
         if self.engine is not None:
             self.engine.backward(loss)
         return loss, ntok
 
-    def _forward_loss(self, batch: Dict[str, Any], loss_scale: float):
+    def _forward_loss(self, batch: Dict[str, Any], loss_scale: float, loss_denominator: torch.Tensor | None = None):
         """Returns (scaled loss, valid-token count tensor)."""
         lc = self.config.loss
         m = self.model
@@ -315,7 +322,7 @@ class SOTATrainer:
                     labels=batch.get("labels", batch["input_ids"]), position_ids=batch.get("position_ids"),
                     doc_ids=batch.get("document_ids"), cu_seqlens=batch.get("cu_seqlens"), loss_scale=loss_scale,
                     label_smoothing=lc.label_smoothing, ignore_index=lc.ignore_index,
-                    shift_labels=not batch.get("labels_shifted", False))
+                    shift_labels=not batch.get("labels_shifted", False), loss_denominator=loss_denominator)
             return out.loss, out.num_tokens
         out = m(**{k: v for k, v in batch.items() if k in ("input_ids", "attention_mask", "labels")})
         loss = out.loss if hasattr(out, "loss") and out.loss is not None else None
@@ -362,7 +369,16 @@ class SOTATrainer:
             self._generic_backward_step(loss, True)
         self.scheduler.step()
         self.state.global_step += 1
-        return float(loss.detach().float().item())
+        out = float(loss.detach().float().item())
+        self._check_comm()
+        return out
+
+    def _check_comm(self) -> None:
+        """After a host read of the loss (the stream has drained): did a fused collective give up on a peer, did any
+        kernel record an error?  Raises CommunicationError / KernelError instead of training on skipped updates."""
+        eng = self.engine
+        if eng is not None and hasattr(eng, "check_comm_status"):
+            eng.check_comm_status()
 
     # ------------------------------------------------------------------ train
     def train(self, train_dataloader: Iterable, eval_dataloader: Iterable | None = None,
@@ -422,6 +438,10 @@ class SOTATrainer:
                 step_tokens += int(batch["input_ids"].numel())
                 sync = (step + 1) % gas == 0
                 if self.engine is not None:
+                    if not getattr(self.engine, "pipelined", False):
+                        # this loop decides where an accumulation window ends; the engine's own counter (which picks
+                        # the micro-batch whose backward starts the overlapped reduction) follows it
+                        self.engine.micro_step = micro
                     with nvtx_range("forward_backward"):
                         loss, ntok = self._loss_and_backward(batch, 1.0 / gas)
                     if sync:
@@ -434,12 +454,12 @@ class SOTATrainer:
                         last_gn = gn.detach()
                 loss_acc += loss.detach().float()
                 tok_acc += ntok.float() if torch.is_tensor(ntok) else float(ntok)
-                self.state.samples_seen += int(batch["input_ids"].shape[0]) * self.world_size
+                self.state.samples_seen += int(batch["input_ids"].shape[0]) * self._data_parallel_size()
                 if not sync:
                     continue
                 self.scheduler.step()
                 self.state.global_step += 1
-                self.state.tokens_seen += step_tokens * self.world_size
+                self.state.tokens_seen += step_tokens * self._data_parallel_size()
                 self.throughput.end_step(step_tokens)
                 window_loss += loss_acc
                 window_steps += 1
@@ -459,6 +479,14 @@ class SOTATrainer:
                 if ctx.should_stop or self.state.global_step >= total_steps:
                     done = True
                     break
+            if not done and (step + 1) % gas != 0:
+                # the loader ended inside an accumulation window: those micro-batches make no step (the step count is
+                # len(loader) // gas per epoch) and must not leak into the first update of the next epoch
+                if self.engine is not None and hasattr(self.engine, "zero_grad"):
+                    self.engine.zero_grad()
+                elif self.optimizer is not None and self.engine is None:
+                    self.optimizer.zero_grad(set_to_none=True)
+                loss_acc.zero_()
             self.callbacks.fire("on_epoch_end", ctx)
             if eval_dataloader is not None and t.eval_strategy == "epoch" and not done:
                 self._run_eval(eval_dataloader, compute_metrics)
@@ -478,6 +506,7 @@ class SOTATrainer:
             dist.all_reduce(vals)
             vals /= self.world_size
         loss, gn = (float(x) for x in vals.tolist())     # the only host sync of the loop
+        self._check_comm()
         self._check_numerical_stability(loss, gn, self.state.global_step)
         self.ema_loss = loss if self.ema_loss is None else 0.99 * self.ema_loss + 0.01 * loss
         self.state.total_loss += loss * max(1, window_steps)
