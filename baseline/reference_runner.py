@@ -163,3 +163,10 @@ def run(args) -> dict:
             if world > 1:
                 break   # a failed multi-rank attempt leaves collectives in an unknown state: do not retry in-process
     return {"impl": "reference", "unavailable": "reference run failed: " + " | ".join(errors)[:600]} if rank == 0 else {}
+
+
+def run_reference(args) -> dict:
+    """Entry point of `bench.py --impl reference`."""
+    if not (REF_DIR / "data_pipeline").exists():
+        return {"impl": "reference", "unavailable": "reference is not installed under baseline/_ref"}
+    return run(args)

@@ -76,7 +76,10 @@ class ClockSampler:
                 "samples": len(sm)}
 
 
-def baseline_value() -> float | None:
+def baseline_value(n_gpus: int = 1) -> float | None:
+    """The number `vs_baseline` divides by: a published value from BASELINE.json when the reference publishes one (it
+    does not), else the reference's own throughput measured on this pool's B200s at the same GPU count
+    (baseline/measured_reference.json, also tabulated in BASELINE.md)."""
     try:
         pub = json.loads((ROOT / "BASELINE.json").read_text()).get("published", {})
         for v in pub.values():
@@ -84,10 +87,62 @@ def baseline_value() -> float | None:
                 return float(v)
     except Exception:
         pass
-    return None
+    try:
+        ref = json.loads((ROOT / "baseline" / "measured_reference.json").read_text())["tokens_per_s"]
+        v = ref.get(str(n_gpus))
+        return float(v) if v else None
+    except Exception:
+        return None
 
 
 def run_ours(args) -> dict:
+    """Headline measurement with `--sharding`, then (2+ GPUs) a shorter one with the other ZeRO mode whose value is
+    reported inside `config` (`other_sharding`).  The process group is created once here so that both trainers share
+    it.  A watchdog prints the headline line alone if the second measurement does not finish."""
+    import gc
+
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1 and not dist.is_initialized():
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", local))
+    out = measure(args, args.sharding, args.steps, args.warmup)
+    other = {"full_shard": "shard_grad_op", "full": "shard_grad_op"}.get(args.sharding, "full_shard")
+    if world > 1 and not args.no_secondary:
+        line = json.dumps(out)
+
+        def give_up():
+            if rank == 0:
+                print(line, flush=True)
+            os._exit(0)
+
+        dog = threading.Timer(args.secondary_timeout, give_up)
+        dog.daemon = True
+        dog.start()
+        try:
+            gc.collect()
+            torch.cuda.empty_cache()
+            torch.cuda.reset_peak_memory_stats()
+            sec = measure(args, other, min(args.steps, 6), 3, e2e=False)
+            if rank == 0:
+                out["config"]["other_sharding"] = {"sharding": other, "value": sec["value"], "unit": "tokens/s",
+                                                   "ms_per_step": sec["ms_per_step"], "steps": sec["steps"],
+                                                   "peak_mem_gb": sec["peak_mem_gb"]}
+        except Exception as e:   # noqa: BLE001 - the headline stands on its own
+            if rank == 0:
+                out["config"]["other_sharding"] = {"sharding": other, "error": f"{type(e).__name__}: {e}"[:200]}
+        dog.cancel()
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    return out
+
+
+def measure(args, sharding: str, steps: int, warmup: int, e2e: bool = True) -> dict:
     import torch
     import torch.distributed as dist
 
@@ -113,7 +168,7 @@ def run_ours(args) -> dict:
         "loss": {"type": "chunked_ce"},
         "distributed": {"enabled": world > 1, "backend": "nccl", "strategy": "fsdp2", "world_size": world,
                         "gradient_checkpointing": layer_ckpt, "comm": args.comm,
-                        "fsdp_config": {"sharding_strategy": args.sharding, "activation_checkpointing": layer_ckpt,
+                        "fsdp_config": {"sharding_strategy": sharding, "activation_checkpointing": layer_ckpt,
                                         "ac_mode": ac, "ac_frequency": 2 if ac == "half" else 1,
                                         "gradient_accumulation_steps": 1}},
         "hardware": {"precision": "bf16"},
@@ -127,7 +182,7 @@ def run_ours(args) -> dict:
     trainer.setup_optimizer()
     trainer.setup_scheduler(10 ** 6)
     dev = trainer.device
-    n_batches = args.warmup + args.steps
+    n_batches = warmup + steps
     g = torch.Generator().manual_seed(1234 + rank)
     host = [torch.randint(0, mcfg.vocab_size, (mb, seq), generator=g, dtype=torch.int64).pin_memory()
             for _ in range(n_batches)]
@@ -147,7 +202,7 @@ def run_ours(args) -> dict:
         return loss
 
     # ---- device-timed region
-    for i in range(args.warmup):
+    for i in range(warmup):
         try:
             device_step(devb[i])
         except torch.OutOfMemoryError:
@@ -168,25 +223,27 @@ def run_ours(args) -> dict:
     launches0 = _lib.LAUNCHES
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for i in range(args.steps):
-        loss = device_step(devb[args.warmup + i])
+    for i in range(steps):
+        loss = device_step(devb[warmup + i])
     e1.record()
     barrier()
     launches = _lib.LAUNCHES - launches0
     ms = e0.elapsed_time(e1)
     final_loss = float(loss.detach())
     # ---- end-to-end region through the public API (H2D from pinned memory + loss read each step)
-    for i in range(min(2, args.warmup)):
-        trainer.train_step({"input_ids": host[i], "labels": host[i]})
-    barrier()
-    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    f0.record()
-    for i in range(args.steps):
-        h = host[args.warmup + i]
-        trainer.train_step({"input_ids": h, "labels": h})
-    f1.record()
-    barrier()
-    ms_e2e = f0.elapsed_time(f1)
+    ms_e2e = ms
+    if e2e:
+        for i in range(min(2, warmup)):
+            trainer.train_step({"input_ids": host[i], "labels": host[i]})
+        barrier()
+        f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        f0.record()
+        for i in range(steps):
+            h = host[warmup + i]
+            trainer.train_step({"input_ids": h, "labels": h})
+        f1.record()
+        barrier()
+        ms_e2e = f0.elapsed_time(f1)
     clocks = sampler.stop() if rank == 0 else None
     t = torch.tensor([ms, ms_e2e], device=dev)
     if world > 1:
@@ -194,8 +251,8 @@ def run_ours(args) -> dict:
     ms, ms_e2e = (float(x) for x in t.tolist())
     _lib.raise_on_any_device_error()
     tokens_per_step = mb * seq * world
-    value = tokens_per_step * args.steps / (ms / 1e3)
-    e2e = tokens_per_step * args.steps / (ms_e2e / 1e3)
+    value = tokens_per_step * steps / (ms / 1e3)
+    e2e_value = tokens_per_step * steps / (ms_e2e / 1e3)
     peaks = {}
     try:
         peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text())
@@ -203,19 +260,19 @@ def run_ours(args) -> dict:
         pass
     flops_tok = mcfg.flops_per_token(seq)
     peak = float(peaks.get("bf16_tflops_sustained", 1385.7))
-    base = baseline_value()
+    base = baseline_value(world)
     out = {
         "metric": "train tokens/s/box (Llama-3-8B FSDP2 bf16)", "value": value, "unit": "tokens/s", "n_gpus": world,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
+        "steps": steps, "warmup": warmup, "ms_per_step": ms / steps, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": (value / base) if base else None, "dtype": "bf16",
         "data": "synthetic uniform-random tokens, random-init weights", "impl": "ours",
         "config": {"model": args.model, "global_batch": mb * world, "seq_len": seq,
-                   "parallelism": f"fsdp{world}" if world > 1 else "single", "sharding": args.sharding,
+                   "parallelism": f"fsdp{world}" if world > 1 else "single", "sharding": sharding,
                    "activation_checkpointing": ac, "comm": args.comm,
                    "l2": "inputs (16 GB of weights per step) are larger than L2; no explicit flush"},
         "mfu_of_measured_sustained_peak": value * flops_tok / 1e12 / (peak * world),
         "clocks": clocks,
-        "e2e": {"value": e2e, "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps,
+        "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": ms_e2e / steps,
                 "h2d_bytes_per_step": int(host[0].numel() * host[0].element_size()) * world,
                 "d2h_bytes_per_step": 4 * world},
         "gpu_launches": launches, "final_loss": final_loss,
@@ -225,7 +282,9 @@ def run_ours(args) -> dict:
                         getattr(getattr(trainer.engine, "_symm", None), "bytes_allocated", 0)) / 2 ** 30,
     }
     trainer.cleanup()
-    return out if rank == 0 else {}
+    del trainer, devb
+    return out if rank == 0 else {"value": value, "ms_per_step": ms / steps, "steps": steps, "peak_mem_gb": 0.0,
+                                  "config": {}}
 
 
 def main():
@@ -240,6 +299,8 @@ def main():
     ap.add_argument("--ac", default="auto", choices=["auto", "full", "half", "op_selective", "none"])
     ap.add_argument("--sharding", default="shard_grad_op", choices=["full", "full_shard", "shard_grad_op", "no_shard"])
     ap.add_argument("--comm", default="auto", choices=["auto", "fused", "nccl"])
+    ap.add_argument("--no-secondary", action="store_true", help="skip the measurement of the other sharding mode")
+    ap.add_argument("--secondary-timeout", type=float, default=300.0)
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -250,11 +311,11 @@ def main():
                str(Path(__file__).resolve())] + sys.argv[1:]
         raise SystemExit(subprocess.call(cmd))
     if args.impl == "reference":
-        from baseline.reference_bench import run_reference
+        from baseline.reference_runner import run_reference
         out = run_reference(args)
     else:
         out = run_ours(args)
-    if out:
+    if out and int(os.environ.get("RANK", "0")) == 0:
         print(json.dumps(out), flush=True)
 
 

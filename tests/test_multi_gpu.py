@@ -93,3 +93,12 @@ def test_context_parallel_attention_on_two_gpus(comm, port):
     assert out.count("ok=True") == 2
     assert ("path=peer" in out) == (comm == "peer")
     print(out[out.index("TIMING"):].splitlines()[0])
+
+
+@pytest.mark.parametrize("comm,port", [("fused", 29771), ("nccl", 29772)])
+def test_dpo_with_sharded_frozen_reference_on_two_gpus(comm, port):
+    """Policy under FULL_SHARD, frozen reference as parameter-only shards pulled layer by layer: losses, gradient norms
+    and weights against a single-process run."""
+    out = _launch("preference_equivalence.py", "--device", "cuda", "--comm", comm, port=port)
+    assert "RESULT preference" in out and "ok=True" in out
+    assert ("fused=True" in out) == (comm == "fused")

@@ -73,3 +73,14 @@ def synthetic_dataloader(vocab_size: int, seq_len: int, batch_size: int, num_bat
     ds = SyntheticTokenDataset(vocab_size, seq_len, num_batches * batch_size, seed * 977 + rank, packed, **kw)
     return DataLoader(ds, batch_size=batch_size, shuffle=False, drop_last=True, pin_memory=pin_memory,
                       num_workers=num_workers)
+
+
+def synthetic_preference_dataloader(vocab_size: int, prompt_len: int, response_len: int, batch_size: int,
+                                    num_batches: int = 64, seed: int = 0, pin_memory: bool = False, rank: int = 0,
+                                    num_workers: int = 0) -> DataLoader:
+    """Batches of prompt / chosen / rejected triples with the keys of the reference's preference stage
+    (data_pipeline/preprocessing/prompt_engine.py:1896-1979): chosen_/rejected_ input_ids, attention_mask, labels
+    (prompt positions masked with -100), prompt_input_ids, prompt_attention_mask."""
+    ds = SyntheticPreferenceDataset(vocab_size, prompt_len, response_len, num_batches * batch_size, seed * 977 + rank)
+    return DataLoader(ds, batch_size=batch_size, shuffle=False, drop_last=True, pin_memory=pin_memory,
+                      num_workers=num_workers)

@@ -72,8 +72,9 @@ class FlatUnit:
 
     def __init__(self, name: str, named_params: list[tuple[str, nn.Parameter]], cfg: EngineConfig, rank: int,
                  world: int, device, grad_dtype: torch.dtype, alloc: Callable | None = None,
-                 resharded: bool = False):
+                 resharded: bool = False, frozen: bool = False):
         self.name, self.cfg, self.rank, self.world = name, cfg, rank, world
+        self.frozen = frozen        # parameters only: no gradient buffer, no optimizer state (a frozen reference model)
         # FULL_SHARD: between uses only `param_shard` exists; the full buffers come from the engine's pools
         self.resharded = resharded
         self.grad_dtype = grad_dtype
@@ -95,11 +96,12 @@ class FlatUnit:
         self.shard_start = self.shard_numel * rank if cfg.sharding_strategy != "NO_SHARD" else 0
         alloc = alloc or (lambda n, dt: torch.zeros(n, dtype=dt, device=device))
         self.flat_param = alloc(self.numel, cfg.param_dtype)
-        self.flat_grad = None if resharded else alloc(self.numel, grad_dtype)
+        self.flat_grad = None if (resharded or frozen) else alloc(self.numel, grad_dtype)
         # optimizer shard
-        self.master = torch.zeros(self.shard_numel, dtype=torch.float32, device=device)
-        self.exp_avg = torch.zeros(self.shard_numel, dtype=torch.float32, device=device)
-        self.exp_avg_sq = torch.zeros(self.shard_numel, dtype=torch.float32, device=device) \
+        n_opt = 0 if frozen else self.shard_numel
+        self.master = torch.zeros(n_opt, dtype=torch.float32, device=device)
+        self.exp_avg = torch.zeros(n_opt, dtype=torch.float32, device=device)
+        self.exp_avg_sq = torch.zeros(n_opt, dtype=torch.float32, device=device) \
             if cfg.optimizer == "adamw" else None
         self.shard_grad: torch.Tensor | None = None   # fp32 reduced slice (world > 1)
         self.grad_ready = False
@@ -112,8 +114,11 @@ class FlatUnit:
                     p.main_grad = self.flat_grad[o:o + k].view(p.shape)
                 p.grad_added = False
                 p._ts_unit = self
+                if frozen:
+                    p.requires_grad_(False)
             s, e = self.shard_start, self.shard_start + self.shard_numel
-            self.master.copy_(self.flat_param[s:e])
+            if not frozen:
+                self.master.copy_(self.flat_param[s:e])
         self.shapes = [tuple(p.shape) for _, p, _, _ in self.entries]
         # alignment gaps between tensors and the tail padding: no kernel writes them, a recycled buffer must zero them
         self.gaps = [(o + k, nxt) for (_, _, o, k), nxt in
@@ -254,12 +259,15 @@ class FlatShardedEngine:
 
     def __init__(self, model: nn.Module, cfg: EngineConfig, process_group=None, device=None,
                  unit_modules: list[tuple[str, nn.Module]] | None = None, solo: bool = False,
-                 replicate_group=None):
-        """`solo`: this rank shares its parameters with nobody (a data-parallel group of one inside a larger job,
+                 replicate_group=None, frozen: bool = False):
+        """`frozen`: hold the model's parameters only (sharded and re-gathered unit by unit like a trained model's, but
+        with no gradient buffers and no optimizer state): the frozen reference model of preference training.
+        `solo`: this rank shares its parameters with nobody (a data-parallel group of one inside a larger job,
         e.g. pure pipeline or tensor parallelism): no collective is ever issued.
         `replicate_group`: hybrid sharding - `process_group` is the shard group (inside a node, say) and the ranks of
         `replicate_group` hold the same shard; reduced gradient shards are additionally averaged over it."""
         self.model, self.cfg = model, cfg
+        self.frozen = frozen
         self.pg = process_group
         self.replicate_group = replicate_group
         self.distributed = (not solo) and dist.is_available() and dist.is_initialized() and \
@@ -309,11 +317,12 @@ class FlatShardedEngine:
             # a re-sharded unit's full buffers are ordinary memory (its storage is resized around each use); what its
             # peers read are the shard store and the gradient slot ring below
             self.units.append(FlatUnit(name or "root", named, cfg, self.rank, self.world, self.device, gd,
-                                       None if resharded else self._alloc_fn(), resharded=resharded))
+                                       None if (resharded or frozen) else self._alloc_fn(), resharded=resharded,
+                                       frozen=frozen))
         rest = [(n, p) for n, p in model.named_parameters() if id(p) not in seen]
         if rest:
             self.units.append(FlatUnit("root", rest, cfg, self.rank, self.world, self.device, torch.float32,
-                                       self._alloc_fn()))
+                                       None if frozen else self._alloc_fn(), frozen=frozen))
         self._unit_index = {u.name: i for i, u in enumerate(self.units)}
         self.norm_sq = torch.zeros(1, dtype=torch.float32, device=self.device)
         self.nonfinite = torch.zeros(1, dtype=torch.float32, device=self.device)
@@ -330,6 +339,7 @@ class FlatShardedEngine:
         if sharded and self._symm is not None:
             # every unit's bf16 shard in ONE symmetric allocation (peers pull from it), and the gradient slot ring
             store = self._symm.alloc(sum(u.shard_numel for u in sharded), cfg.param_dtype)
+        if store is not None and not frozen:
             self._grad_pool = _SymmetricSlotRing(self._symm, max(u.numel for u in sharded), grad_dtype,
                                                  max(2, int(getattr(cfg, "grad_slots", 3))))
         off = 0
@@ -396,7 +406,8 @@ class FlatShardedEngine:
                                group=self.replicate_group)
             dist.broadcast(u.flat_param, src=dist.get_global_rank(self.pg, 0) if self.pg else 0, group=self.pg)
             s = u.shard_start
-            u.master.copy_(u.flat_param[s:s + u.shard_numel])
+            if not u.frozen:
+                u.master.copy_(u.flat_param[s:s + u.shard_numel])
 
     # ------------------------------------------------------------------ forward / backward scheduling
     def _unit_pre_forward(self, idx: int):

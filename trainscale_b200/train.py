@@ -26,7 +26,7 @@ def main(argv=None) -> int:
     a = ap.parse_args(argv)
     logging.basicConfig(level=logging.INFO, format="%(asctime)s %(message)s")
     from .config.sota_config import SOTAConfig
-    from .data.synthetic import synthetic_dataloader
+    from .data.synthetic import synthetic_dataloader, synthetic_preference_dataloader
     from .trainer.sota_trainer import SOTATrainer
 
     raw = yaml.safe_load(open(a.config)) or {}
@@ -39,7 +39,18 @@ def main(argv=None) -> int:
     trainer.setup_model()
     ds = raw.get("dataset") or {}
     steps = cfg.training.max_steps if cfg.training.max_steps > 0 else 100
-    if str(ds.get("name", "synthetic")).lower() == "synthetic":
+    if str(ds.get("name", "synthetic")).lower() == "synthetic" and trainer.preference_kind is not None:
+        # preference objectives train on prompt / chosen / rejected triples: half of max_seq_length each for the
+        # prompt and the response unless the dataset section says otherwise
+        vocab = trainer.model.config.vocab_size
+        p_len = int(ds.get("prompt_length", cfg.data.max_seq_length // 2))
+        r_len = int(ds.get("response_length", cfg.data.max_seq_length - p_len))
+        dl = synthetic_preference_dataloader(vocab, p_len, r_len, cfg.training.per_device_train_batch_size,
+                                             num_batches=steps * cfg.training.gradient_accumulation_steps,
+                                             seed=cfg.data.seed, rank=trainer.rank,
+                                             pin_memory=trainer.device.type == "cuda")
+        ev = None
+    elif str(ds.get("name", "synthetic")).lower() == "synthetic":
         vocab = trainer.model.config.vocab_size
         dl = synthetic_dataloader(vocab, cfg.data.max_seq_length, cfg.training.per_device_train_batch_size,
                                   num_batches=steps * cfg.training.gradient_accumulation_steps, seed=cfg.data.seed,

@@ -52,6 +52,8 @@ STRATEGY_ALIASES = {
     "tensor_parallel": "tensor_parallel", "nd": "nd", "3d": "nd",
 }
 
+PREFERENCE_LOSSES = ("dpo", "simpo", "orpo", "kto", "cpo")
+
 _SHARDING = {"full": "FULL_SHARD", "full_shard": "FULL_SHARD", "shard_grad_op": "SHARD_GRAD_OP",
              "zero2": "SHARD_GRAD_OP", "no_shard": "NO_SHARD", "hybrid_shard": "FULL_SHARD", "auto": "SHARD_GRAD_OP"}
 
@@ -156,6 +158,20 @@ class SOTATrainer:
             return "single"
         return s
 
+    @property
+    def preference_kind(self) -> str | None:
+        """The preference objective this run trains with, or None for language-model training: `loss.type` in
+        dpo / simpo / orpo / kto / cpo, or `training_mode: rl` with such an `rl.algorithm`
+        (data_pipeline/trainer/core/sota_config.py:53-60,261; losses data_pipeline/trainer/loss/sota_losses.py:1151,1448)."""
+        lt = str(getattr(self.config.loss.type, "value", self.config.loss.type)).lower()
+        if lt in PREFERENCE_LOSSES:
+            return lt
+        mode = str(getattr(self.config.training_mode, "value", self.config.training_mode)).lower()
+        alg = str(getattr(self.config.rl.algorithm, "value", self.config.rl.algorithm)).lower()
+        if mode == "rl" and alg in PREFERENCE_LOSSES:
+            return alg
+        return None
+
     # ------------------------------------------------------------------ model
     def _build_own_model(self) -> nn.Module:
         arch = self.config.model.architecture
@@ -204,14 +220,36 @@ class SOTATrainer:
             self.model.gradient_checkpointing_enable(every)
         self.throughput.flops_per_token = self._flops_per_token()
         strat = self.strategy
+        kind = self.preference_kind
+        ref_model = None
+        lc = self.config.loss
+        if kind in ("dpo", "kto") and not lc.reference_free and self.config.rl.use_ref_model:
+            # the frozen reference is the policy as it is now, copied before the engine re-points the policy's
+            # parameters at its flat buffers
+            import copy
+            ref_model = copy.deepcopy(self.model).eval()
         if strat in ("single", "ddp", "fsdp") and all(p.requires_grad for p in self.model.parameters()) \
                 and self._flat_engine_ok():
             self.engine = self._build_flat_engine(strat)
+            if ref_model is not None:
+                # parameter-only shards under the same sharding as the policy: no gradients, no optimizer state
+                self.ref_engine = self._build_flat_engine(strat, model=ref_model, frozen=True)
         elif strat in ("pipeline", "context_parallel", "tensor_parallel", "nd"):
             from ..parallel.nd import build_nd_engine
             self.engine = build_nd_engine(self, strat)
         else:
             self.engine = None   # generic nn.Module path: torch optimizer (+ DDP all-reduce of .grad)
+        if kind is not None:
+            from ..rl import PreferenceTrainer
+            kw = {"dpo": dict(loss_type=lc.dpo_variant, label_smoothing=lc.label_smoothing,
+                              reference_free=lc.reference_free or ref_model is None),
+                  "simpo": dict(gamma=lc.simpo_gamma, label_smoothing=lc.label_smoothing),
+                  "orpo": dict(alpha=lc.alpha), "cpo": dict(alpha=lc.alpha, label_smoothing=lc.label_smoothing),
+                  "kto": {}}[kind]
+            if kind == "orpo":
+                self.preference = PreferenceTrainer(self.model, None, None, "orpo", **kw)
+            else:
+                self.preference = PreferenceTrainer(self.model, None, ref_model, kind, lc.dpo_beta, **kw)
         self._ctx.model = self.model
         return self.model
 
@@ -219,8 +257,9 @@ class SOTATrainer:
         t = getattr(self.config.optimizer.type, "value", self.config.optimizer.type)
         return t in ("adamw", "fused_adamw", "lion")
 
-    def _build_flat_engine(self, strat: str) -> FlatShardedEngine:
+    def _build_flat_engine(self, strat: str, model: nn.Module | None = None, frozen: bool = False) -> FlatShardedEngine:
         c, d = self.config, self.config.distributed
+        model = self.model if model is None else model
         fc = dict(d.fsdp_config or {})
         if strat == "ddp":
             sharding = "NO_SHARD"
@@ -244,9 +283,15 @@ class SOTATrainer:
             from ..parallel.mesh import create_parallel_dims_from_config
             dims = create_parallel_dims_from_config(d)
             self._hsdp_dims = dims
-            return FlatShardedEngine(self.model, ec, process_group=dims.group("fsdp"), device=self.device,
-                                     replicate_group=dims.group("dp_replicate"))
-        return FlatShardedEngine(self.model, ec, device=self.device)
+            return FlatShardedEngine(model, ec, process_group=dims.group("fsdp"), device=self.device,
+                                     replicate_group=dims.group("dp_replicate"), frozen=frozen)
+        return FlatShardedEngine(model, ec, device=self.device, frozen=frozen)
+
+    @staticmethod
+    def _batch_tokens(batch: Dict[str, Any]) -> int:
+        if "input_ids" in batch:
+            return int(batch["input_ids"].numel())
+        return sum(int(v.numel()) for k, v in batch.items() if k in ("chosen_input_ids", "rejected_input_ids"))
 
     def _data_parallel_size(self) -> int:
         """Ranks that consume different samples (tensor / pipeline / context ranks of one replica share theirs)."""
@@ -317,6 +362,14 @@ class SOTATrainer:
         """Returns (scaled loss, valid-token count tensor)."""
         lc = self.config.loss
         m = self.model
+        if "chosen_input_ids" in batch:
+            if getattr(self, "preference", None) is None:
+                raise TrainingConfigurationError("a preference batch (chosen_/rejected_ keys) needs loss.type or "
+                                                 "rl.algorithm in " + "/".join(PREFERENCE_LOSSES))
+            loss, metrics = self.preference.compute_loss(batch)
+            self.last_preference_metrics = metrics
+            ntok = (batch["chosen_labels"] != lc.ignore_index).sum() + (batch["rejected_labels"] != lc.ignore_index).sum()
+            return loss * loss_scale, ntok
         if isinstance(m, LlamaForCausalLM) or hasattr(m, "loss_chunk_tokens"):
             out = m(input_ids=batch["input_ids"], attention_mask=batch.get("attention_mask"),
                     labels=batch.get("labels", batch["input_ids"]), position_ids=batch.get("position_ids"),
@@ -435,7 +488,7 @@ class SOTATrainer:
                     step_tokens = 0
                 with nvtx_range("h2d_batch"):
                     batch = self._to_device(batch)
-                step_tokens += int(batch["input_ids"].numel())
+                step_tokens += self._batch_tokens(batch)
                 sync = (step + 1) % gas == 0
                 if self.engine is not None:
                     if not getattr(self.engine, "pipelined", False):
@@ -454,7 +507,8 @@ class SOTATrainer:
                         last_gn = gn.detach()
                 loss_acc += loss.detach().float()
                 tok_acc += ntok.float() if torch.is_tensor(ntok) else float(ntok)
-                self.state.samples_seen += int(batch["input_ids"].shape[0]) * self._data_parallel_size()
+                self.state.samples_seen += int(next(v for v in batch.values() if torch.is_tensor(v)).shape[0]) * \
+                    self._data_parallel_size()
                 if not sync:
                     continue
                 self.scheduler.step()
@@ -522,6 +576,9 @@ class SOTATrainer:
         if self.engine is not None and self.is_main and hasattr(self.engine, "memory_summary"):
             line += " | " + self.engine.memory_summary()
         rec = {"step": step, "loss": loss, "ppl": ppl, "lr": lr, "grad_norm": gn, "tokens_per_second": tps, "mfu": mfu}
+        for k, v in (getattr(self, "last_preference_metrics", None) or {}).items():
+            rec[k] = float(v)          # reward accuracy / margin of the last micro-batch (already a log-time sync)
+            line += f" | {k} {rec[k]:.3f}"
         self._ctx.logs = {**rec, "line": line}
         self.callbacks.fire("on_log", self._ctx)
         return rec
