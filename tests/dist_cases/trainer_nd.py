@@ -151,7 +151,10 @@ def main():
         from trainscale_b200.ops import _lib
         _lib.raise_on_any_device_error()
         if rank == 0 and a.mode == "sp":
-            print("tp comm:", tr.engine.tp.comm)
+            from trainscale_b200.parallel import tp_fused
+            print("tp comm:", tr.engine.tp.comm, "fused kernel calls:", tp_fused.CALLS)
+            assert tp_fused.CALLS["gather_gemm"] > 0 and tp_fused.CALLS["gemm_reduce"] > 0, \
+                "the decoder did not reach the fused tensor-parallel GEMMs"
     if rank == 0:
         print(f"RESULT mode={a.mode} ok={flag.item() == 0}")
     dist.barrier()

@@ -93,3 +93,100 @@ def test_decoder_trains_with_fp8_projections():
         eng.step()
         losses.append(loss.item())
     assert all(l == l for l in losses) and losses[-1] < losses[0] - 0.3, losses
+
+
+# ------------------------------------------------------------------------------------------------ rowwise recipe
+@pytest.mark.parametrize("fmt", ["e4m3", "e5m2"])
+def test_rowwise_and_colwise_quant_match_pytorch(fmt):
+    from trainscale_b200.ops import fp8
+    torch.manual_seed(0)
+    fmax = {"e4m3": 448.0, "e5m2": 57344.0}[fmt]
+    for R, C in [(257, 384), (64, 9216), (1000, 2056)]:
+        x = torch.randn(R, C, device="cuda", dtype=torch.bfloat16) * torch.rand(R, 1, device="cuda").add(0.1).bfloat16()
+        q, s = fp8.quant_rowwise(x, fmt)
+        assert torch.allclose(s, x.float().abs().amax(1).clamp(min=1e-12) / fmax, rtol=1e-6)
+        back = fp8.dequant_rowwise(q, s, 0)
+        step = 2.0 ** (-3 if fmt == "e4m3" else -2)          # relative spacing of the format
+        assert ((back - x.float()).abs() <= step * x.float().abs().amax(1, keepdim=True)).all()
+        # the kernel multiplies by 1/s, the oracle divides: a value on a rounding boundary may land one step apart
+        same = q.view(torch.uint8) == (x.float() / s.view(-1, 1)).to(q.dtype).view(torch.uint8)
+        assert same.float().mean().item() > 0.995
+        qc, sc = fp8.quant_colwise(x, fmt)
+        assert torch.allclose(sc, x.float().abs().amax(0).clamp(min=1e-12) / fmax, rtol=1e-6)
+        same = qc.view(torch.uint8) == (x.float() / sc.view(1, -1)).to(qc.dtype).view(torch.uint8)
+        assert same.float().mean().item() > 0.995
+        backc = fp8.dequant_rowwise(qc, sc, 1)
+        assert ((backc - x.float()).abs() <= step * x.float().abs().amax(0, keepdim=True)).all()
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 256, 128), (300, 400, 528), (1000, 1072, 1040), (4096, 2048, 4096)])
+def test_rowwise_gemm_all_layouts_match_fp32_on_the_same_fp8_values(M, N, K):
+    """Forward (K-major x K-major), dgrad (K-major x MN-major) and wgrad (MN-major x MN-major) layouts, ragged shapes,
+    against fp32 matmuls of the dequantised operands; bf16 and fp32 outputs, accumulation."""
+    from trainscale_b200.ops import fp8, _lib
+    torch.manual_seed(1)
+    a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    b = (torch.randn(N, K, device="cuda") / K ** 0.5).to(torch.bfloat16)
+    aq, sa = fp8.quant_rowwise(a)
+    bq, sb = fp8.quant_rowwise(b)
+    ref = fp8.dequant_rowwise(aq, sa, 0) @ fp8.dequant_rowwise(bq, sb, 0).t()
+    y = fp8.gemm_rowwise(aq, sa, bq, sb, M, N, K)
+    tol = 1e-2 * max(ref.abs().max().item(), 1.0)
+    assert (y.float() - ref).abs().max().item() <= tol
+    y32 = torch.ones(M, N, device="cuda", dtype=torch.float32)
+    fp8.gemm_rowwise(aq, sa, bq, sb, M, N, K, out=y32, accumulate=True)
+    assert (y32 - 1.0 - ref).abs().max().item() <= 1e-3 * max(ref.abs().max().item(), 1.0)
+    # B stored [K][N] (MN-major), column scales: c[m][n] = sum_k a[m][k] bt[k][n]
+    bt = (torch.randn(K, N, device="cuda") / K ** 0.5).to(torch.bfloat16)
+    btq, sbt = fp8.quant_colwise(bt, "e4m3")
+    ref2 = fp8.dequant_rowwise(aq, sa, 0) @ fp8.dequant_rowwise(btq, sbt, 1)
+    y2 = fp8.gemm_rowwise(aq, sa, btq, sbt, M, N, K, b_mn=True)
+    assert (y2.float() - ref2).abs().max().item() <= 1e-2 * max(ref2.abs().max().item(), 1.0)
+    # both operands MN-major (wgrad): c[m][n] = sum_k at[k][m] bt[k][n], A in E5M2
+    at = torch.randn(K, M, device="cuda", dtype=torch.bfloat16)
+    atq, sat = fp8.quant_colwise(at, "e5m2")
+    ref3 = fp8.dequant_rowwise(atq, sat, 1).t() @ fp8.dequant_rowwise(btq, sbt, 1)
+    y3 = fp8.gemm_rowwise(atq, sat, btq, sbt, M, N, K, a_mn=True, b_mn=True)
+    assert (y3.float() - ref3).abs().max().item() <= 1e-2 * max(ref3.abs().max().item(), 1.0)
+    torch.cuda.synchronize()
+    assert _lib.device_error("fp8_rowwise")[0] == 0
+
+
+@pytest.mark.parametrize("grad_fmt,tol", [("e4m3", 0.06), ("e5m2", 0.12)])
+def test_fp8_rowwise_linear_forward_and_backward(grad_fmt, tol):
+    from trainscale_b200.ops import fp8
+    torch.manual_seed(2)
+    M, N, K = 512, 768, 1024
+    x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    w = (torch.randn(N, K, device="cuda") / K ** 0.5).to(torch.bfloat16).requires_grad_(True)
+    w.main_grad = torch.zeros(N, K, device="cuda", dtype=torch.float32)     # the engine's gradient buffer
+    w.grad_added = False
+    y = fp8.fp8_linear(x, w, recipe="rowwise", grad_format=grad_fmt)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    assert w.grad is None and w.grad_added
+    xr, wr = x.detach().float().requires_grad_(True), w.detach().float().requires_grad_(True)
+    yr = xr @ wr.t()
+    yr.backward(dy.float())
+    assert (y.float() - yr).abs().mean().item() <= 0.05 * yr.abs().mean().item()
+    for a, b in ((x.grad, xr.grad), (w.main_grad, wr.grad)):
+        assert (a.float() - b).abs().mean().item() <= tol * b.abs().mean().item() + 1e-3
+        assert (a.float() - b).abs().max().item() <= 3 * tol * b.abs().max().item()
+
+
+def test_decoder_trains_with_fp8_rowwise_and_e5m2_gradients():
+    from trainscale_b200.models.llama import LlamaConfig, build_model
+    from trainscale_b200.parallel.flat_engine import EngineConfig, FlatShardedEngine
+    cfg = LlamaConfig(vocab_size=512, hidden_size=256, intermediate_size=512, num_hidden_layers=2,
+                      num_attention_heads=4, num_key_value_heads=2, head_dim=64)
+    model = build_model(cfg, dtype=torch.bfloat16, device="cuda", seed=0)
+    model.enable_fp8(True, recipe="rowwise", grad_format="e5m2")
+    eng = FlatShardedEngine(model, EngineConfig(lr=3e-3, weight_decay=0.0), device=torch.device("cuda"))
+    ids = torch.randint(0, 512, (4, 256), device="cuda", generator=torch.Generator("cuda").manual_seed(0))
+    losses = []
+    for _ in range(8):
+        out = model(ids, labels=ids)
+        eng.backward(out.loss)
+        eng.step()
+        losses.append(float(out.loss.detach()))
+    assert losses[-1] < losses[0] - 0.5, losses

@@ -153,6 +153,54 @@ def bench_fp8(t, small):
     return out
 
 
+def bench_fp8_rowwise(t, small):
+    """Row-scaled fp8 GEMM (forward / dgrad / wgrad layouts) against this framework's bf16 GEMM on the same shapes,
+    the quantisation kernels, and the whole fp8 linear layer (quantise + 3 GEMMs) against the bf16 one."""
+    from .ops import fp8, gemm
+    out = []
+    shapes = [(4096, 4096, 4096)] if small else [(8192, 8192, 8192), (8192, 28672, 8192), (8192, 4096, 14336),
+                                                 (8192, 28672, 4096)]
+    for M, N, K in shapes:
+        x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+        w = (torch.randn(N, K, device="cuda") / K ** 0.5).to(torch.bfloat16)
+        dy = torch.randn(M, N, device="cuda", dtype=torch.bfloat16)
+        y = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        xq, sx = fp8.quant_rowwise(x)
+        wq, sw = fp8.quant_rowwise(w)
+        ms = t(lambda: fp8.gemm_rowwise(xq, sx, wq, sw, M, N, K, out=y))
+        base = t(lambda: gemm.matmul_nt(x, w, out=y))
+        out.append(dict(name=f"fp8_rowwise_gemm fwd {M}x{N}x{K}", ms=ms, baseline_ms=base,
+                        tflops=2 * M * N * K / ms / 1e9))
+        dq, sd = fp8.quant_rowwise(dy)
+        wc, swc = fp8.quant_colwise(w)
+        dx = torch.empty(M, K, device="cuda", dtype=torch.bfloat16)
+        ms = t(lambda: fp8.gemm_rowwise(dq, sd, wc, swc, M, K, N, b_mn=True, out=dx))
+        base = t(lambda: gemm.matmul_nn(dy, w, out=dx))
+        out.append(dict(name=f"fp8_rowwise_gemm dgrad {M}x{K}x{N}", ms=ms, baseline_ms=base,
+                        tflops=2 * M * N * K / ms / 1e9))
+        dc, sdc = fp8.quant_colwise(dy)
+        xc, sxc = fp8.quant_colwise(x)
+        dw = torch.empty(N, K, device="cuda", dtype=torch.bfloat16)
+        ms = t(lambda: fp8.gemm_rowwise(dc, sdc, xc, sxc, N, K, M, a_mn=True, b_mn=True, out=dw))
+        base = t(lambda: gemm.matmul_tn(dy, x, out=dw))
+        out.append(dict(name=f"fp8_rowwise_gemm wgrad {N}x{K}x{M}", ms=ms, baseline_ms=base,
+                        tflops=2 * M * N * K / ms / 1e9))
+        ms = t(lambda: fp8.quant_rowwise(dy))
+        out.append(dict(name=f"fp8_quant_rowwise {M}x{N}", ms=ms, baseline_ms=None, gbs=M * N * 3 / ms / 1e6))
+        ms = t(lambda: fp8.quant_colwise(dy))
+        out.append(dict(name=f"fp8_quant_colwise {M}x{N}", ms=ms, baseline_ms=None, gbs=M * N * 5 / ms / 1e6))
+        xg, wg = x.clone().requires_grad_(True), w.clone().requires_grad_(True)
+
+        def layer(fn):
+            xg.grad = wg.grad = None
+            fn(xg, wg).backward(dy)
+        ms = t(lambda: layer(lambda a, b: fp8.fp8_linear(a, b, recipe="rowwise")))
+        base = t(lambda: layer(gemm.linear))
+        out.append(dict(name=f"fp8_rowwise_linear fwd+bwd {M}x{N}x{K}", ms=ms, baseline_ms=base,
+                        tflops=6 * M * N * K / ms / 1e9))
+    return out
+
+
 def bench_moe(t, small):
     from .ops import moe
     out = []
@@ -181,7 +229,7 @@ def bench_layernorm(t, small):
     return out
 
 
-CASES = {"fp8": bench_fp8, "moe": bench_moe, "layernorm": bench_layernorm, "rmsnorm": bench_rmsnorm, "swiglu": bench_swiglu, "rope": bench_rope, "cross_entropy": bench_cross_entropy,
+CASES = {"fp8": bench_fp8, "fp8_rowwise": bench_fp8_rowwise, "moe": bench_moe, "layernorm": bench_layernorm, "rmsnorm": bench_rmsnorm, "swiglu": bench_swiglu, "rope": bench_rope, "cross_entropy": bench_cross_entropy,
          "gemm": bench_gemm, "attention": bench_attention, "adamw": bench_adamw}
 
 

@@ -297,6 +297,9 @@ class HardwareConfig:
     num_workers: int = 4
     pin_memory: bool = True
     prefetch_factor: int = 2
+    # fp8 precisions: "rowwise" = per-token / per-feature scales, forward + dgrad + wgrad in fp8 (precision fp8_e5m2
+    # keeps activations and weights in E4M3 and quantises gradients to E5M2); "block" = 1 x 128 / 128 x 128 scales
+    fp8_recipe: str = "rowwise"
 
 
 @dataclass

@@ -122,22 +122,56 @@ def preset_config(name: str, **overrides) -> LlamaConfig:
     return LlamaConfig(**d)
 
 
+_TP_FIRST, _TP_LAST = ("wqkv", "w_gate_up"), ("wo", "w_down")
+
+
 def _lin(mod, x, name: str):
-    """x @ W^T plus the low-rank adapter of that weight when one is attached.  With `mod.fp8` the product runs on the
-    block-scaled fp8 tensor-core kernel (forward and dgrad; wgrad and the master weights stay bf16 / fp32)."""
+    """x @ W^T plus the low-rank adapter of that weight when one is attached.
+
+    `mod.fp8`: the product runs on the fp8 tensor-core kernels (`mod.fp8_recipe`: "rowwise" = forward, dgrad and wgrad
+    in fp8 with per-token / per-feature scales; "block" = 1 x 128 / 128 x 128 scales, wgrad in bf16).
+    `mod.tp_ctx` (set by the tensor-parallel wrapper on the fused back-end, with sequence parallelism): `x` of the
+    block's first projection is this rank's token shard and the all-gather runs inside the GEMM kernel; the block's
+    last projection reduce-scatters its output over the token dimension from the GEMM epilogue."""
     w = getattr(mod, name)
+    tp = getattr(mod, "tp_ctx", None)
+    if tp is not None and x.is_cuda and x.dtype == torch.bfloat16 and mod.lora is None:
+        y = _tp_fused_lin(x, w, name, tp)
+        if y is not None:
+            return y
     has_lora = mod.lora is not None and name in mod.lora
     if has_lora and not getattr(mod, "fp8", False) and hasattr(mod.lora[name], "linear"):
         return mod.lora[name].linear(x, w)
     if getattr(mod, "fp8", False) and x.is_cuda and x.dtype == torch.bfloat16 and x.shape[-1] % 128 == 0 \
             and w.shape[0] % 8 == 0:
         from ..ops import fp8 as fp8_ops
-        y = fp8_ops.fp8_linear(x, w)
+        y = fp8_ops.fp8_linear(x, w, recipe=getattr(mod, "fp8_recipe", "rowwise"),
+                               grad_format=getattr(mod, "fp8_grad_format", "e4m3"))
     else:
         y = gemm.linear(x, w)
     if has_lora:
         y = y + mod.lora[name](x)
     return y
+
+
+def _tp_fused_lin(x, w, name, tp):
+    """First / last projection of a tensor-parallel block on the fused all-gather->GEMM / GEMM->reduce-scatter
+    kernels (one sequence, token-sharded).  None when the shape does not fit their tiling: the caller's wrapper then
+    gathers / scatters with library collectives around ordinary GEMMs."""
+    from ..parallel import tp_fused
+    if x.dim() != 3 or x.shape[0] != 1:
+        return None
+    if name in _TP_FIRST:
+        S_loc, K = x.shape[1], x.shape[2]
+        if S_loc % 128 != 0 or K % 64 != 0:
+            return None
+        return tp_fused.all_gather_linear(x.view(S_loc, K), w, tp).view(1, S_loc * tp.size, w.shape[0])
+    if name in _TP_LAST:
+        S, K = x.shape[1], x.shape[2]
+        if S % (128 * tp.size) != 0 or K % 64 != 0:
+            return None
+        return tp_fused.linear_reduce(x.reshape(S, K), w, tp, scatter=True).view(1, S // tp.size, w.shape[0])
+    return None
 
 
 class RMSNorm(nn.Module):
@@ -396,11 +430,14 @@ class LlamaForCausalLM(nn.Module):
         self.model.gradient_checkpointing = True
         self.model.checkpoint_every = max(1, every)
 
-    def enable_fp8(self, enabled: bool = True):
-        """Block-scaled fp8 (E4M3) GEMMs for the attention and MLP projections (the head and the embedding stay bf16)."""
+    def enable_fp8(self, enabled: bool = True, recipe: str = "rowwise", grad_format: str = "e4m3"):
+        """fp8 GEMMs for the attention and MLP projections (the head and the embedding stay bf16).  recipe "rowwise":
+        forward, dgrad and wgrad in fp8 with per-token / per-feature scales (gradients in `grad_format`, e4m3 or e5m2);
+        "block": 1 x 128 / 128 x 128 block scales, forward and dgrad in fp8."""
         for layer in self.model.layers:
-            layer.self_attn.fp8 = enabled
-            layer.mlp.fp8 = enabled
+            for blk in (layer.self_attn, layer.mlp):
+                blk = getattr(blk, "inner", blk)      # under tensor parallelism the block sits inside its wrapper
+                blk.fp8, blk.fp8_recipe, blk.fp8_grad_format = enabled, recipe, grad_format
 
     def op_selective_recompute(self, enabled: bool = True):
         """Operator-level selective recomputation: no layer is re-run, but norm and GLU outputs are rebuilt in

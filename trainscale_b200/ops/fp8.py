@@ -1,4 +1,10 @@
-"""Block-scaled fp8 (E4M3) ops on the sm_100a kernels: quantise / dequantise and the tcgen05 kind::f8f6f4 GEMM.
+"""fp8 ops on the sm_100a kernels: quantise / dequantise and the tcgen05 kind::f8f6f4 GEMMs.
+
+Two recipes.  "rowwise" (default of `fp8_linear`): every scale is constant along the reduction axis (one per token /
+per feature), applied in the GEMM epilogue; forward, dgrad AND wgrad run at the full fp8 tensor-core rate on the
+paired-CTA kernel of csrc/fp8_rowwise.cu, gradients optionally in E5M2.  "block": the 1 x 128 / 128 x 128 recipe below.
+
+Block recipe:
 
 Activations: one fp32 scale per 1 x 128 block (stored [K/128, M]); weights: one per 128 x 128 block ([N/128, K/128]).
 `fp8_linear` runs forward and dgrad in fp8 (the gradient w.r.t. the output is re-quantised along its own reduction
@@ -119,6 +125,122 @@ class _FP8LinearFn(torch.autograd.Function):
 
 
 def fp8_linear(x: torch.Tensor, w: torch.Tensor | None = None, wq: torch.Tensor | None = None,
-               ws: torch.Tensor | None = None) -> torch.Tensor:
-    """Linear layer with block-scaled fp8 operands (see module docstring)."""
+               ws: torch.Tensor | None = None, recipe: str = "block", grad_format: str = "e4m3") -> torch.Tensor:
+    """Linear layer with fp8 operands.  recipe "rowwise": fwd + dgrad + wgrad in fp8 at the full tensor-core rate
+    (falls back to "block" for shapes whose fp8 rows would not be 16-byte aligned); "block": 1 x 128 / 128 x 128
+    scales, fwd + dgrad in fp8, wgrad in bf16 (also the path of a frozen pre-quantised weight `wq` / `ws`)."""
+    if recipe == "rowwise" and wq is None and w is not None and rowwise_available(x, w):
+        return fp8_linear_rowwise(x, w, grad_format)
     return _FP8LinearFn.apply(x, w, wq, ws)
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# rowwise recipe (csrc/fp8_rowwise.cu)
+# ---------------------------------------------------------------------------------------------------------------
+_FMT = {"e4m3": 0, "e5m2": 1}
+_TORCH_FP8 = {"e4m3": torch.float8_e4m3fn, "e5m2": torch.float8_e5m2}
+_FMAX = {"e4m3": 448.0, "e5m2": 57344.0}
+
+
+def rowwise_available(x: torch.Tensor, w: torch.Tensor) -> bool:
+    """Every leading dimension of the three GEMMs must keep fp8 rows 16-byte aligned."""
+    T = x.numel() // x.shape[-1]
+    return (x.is_cuda and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[-1] % 16 == 0 and
+            w.shape[0] % 16 == 0 and T % 16 == 0)
+
+
+def quant_rowwise(x2: torch.Tensor, fmt: str = "e4m3"):
+    """x2 [R, C] bf16 -> (q fp8 [R, C], scale fp32 [R]): one scale per row."""
+    lib = _lib.load("fp8_rowwise")
+    R, C = x2.shape
+    if x2.stride(1) != 1 or x2.stride(0) % 8 != 0:
+        x2 = x2.contiguous()
+    q = torch.empty(R, C, dtype=_TORCH_FP8[fmt], device=x2.device)
+    s = torch.empty(R, dtype=torch.float32, device=x2.device)
+    _lib.check(lib.ts_fp8_quant_rowwise(_lib.ptr(x2), _ll(x2.stride(0)), _lib.ptr(q), _lib.ptr(s), _ll(R), C, _FMT[fmt],
+                                        _lib.stream_ptr()), "ts_fp8_quant_rowwise")
+    return q, s
+
+
+def quant_colwise(x2: torch.Tensor, fmt: str = "e4m3"):
+    """x2 [R, C] bf16 -> (q fp8 [R, C] in the same layout, scale fp32 [C]): one scale per column."""
+    lib = _lib.load("fp8_rowwise")
+    R, C = x2.shape
+    if x2.stride(1) != 1 or x2.stride(0) % 8 != 0:
+        x2 = x2.contiguous()
+    q = torch.empty(R, C, dtype=_TORCH_FP8[fmt], device=x2.device)
+    s = torch.empty(C, dtype=torch.float32, device=x2.device)
+    work = torch.empty(C, dtype=torch.int32, device=x2.device)
+    _lib.check(lib.ts_fp8_quant_colwise(_lib.ptr(x2), _ll(x2.stride(0)), _lib.ptr(q), _lib.ptr(s), _lib.ptr(work),
+                                        _ll(R), C, _FMT[fmt], _lib.stream_ptr()), "ts_fp8_quant_colwise")
+    return q, s
+
+
+def gemm_rowwise(a, sa, b, sb, M: int, N: int, K: int, a_mn: bool = False, b_mn: bool = False, out=None,
+                 out_dtype=torch.bfloat16, accumulate: bool = False) -> torch.Tensor:
+    """out[M, N] (+)= sa[m] * sb[n] * sum_k A[m, k] B[n, k].  a: [M, K] (a_mn False) or [K, M] (a_mn True) fp8;
+    b: [N, K] (b_mn False) or [K, N] (b_mn True) fp8; formats are read from the tensors' dtypes."""
+    lib = _lib.load("fp8_rowwise")
+    if out is None:
+        out = torch.empty(M, N, dtype=out_dtype, device=a.device)
+    fa = 1 if a.dtype == torch.float8_e5m2 else 0
+    fb = 1 if b.dtype == torch.float8_e5m2 else 0
+    rc = lib.ts_fp8_rowwise_gemm(_lib.ptr(a), _lib.ptr(sa), _lib.ptr(b), _lib.ptr(sb), _lib.ptr(out), M, N, K,
+                                 a.stride(0), b.stride(0), out.stride(0), int(a_mn), int(b_mn), fa, fb,
+                                 int(out.dtype == torch.float32), int(accumulate), _lib.stream_ptr())
+    _lib.check(rc, "ts_fp8_rowwise_gemm")
+    return out
+
+
+def dequant_rowwise(q: torch.Tensor, s: torch.Tensor, axis: int) -> torch.Tensor:
+    """fp32 values of a rowwise (axis 0) or colwise (axis 1) quantised matrix (test oracle)."""
+    return q.float() * (s.view(-1, 1) if axis == 0 else s.view(1, -1))
+
+
+class _FP8RowwiseLinearFn(torch.autograd.Function):
+    """y = x @ w^T with all three GEMMs in fp8.  Saved for backward: the column-scaled fp8 copy of x (half the bytes
+    of the bf16 activation) and the weight."""
+
+    @staticmethod
+    def forward(ctx, x, w, grad_fmt):
+        x2 = x.reshape(-1, x.shape[-1])
+        T, K = x2.shape
+        N = w.shape[0]
+        xq, sx = quant_rowwise(x2)
+        wq, sw = quant_rowwise(w)
+        y = gemm_rowwise(xq, sx, wq, sw, T, N, K)
+        need_dw = w.requires_grad
+        if need_dw:
+            xc, sxc = quant_colwise(x2)                  # operand of wgrad: scales per input feature, over all tokens
+        else:
+            xc = sxc = None
+        ctx.save_for_backward(xc, sxc, w)
+        ctx.x_shape, ctx.grad_fmt = x.shape, grad_fmt
+        return y.view(*x.shape[:-1], N)
+
+    @staticmethod
+    def backward(ctx, dy):
+        xc, sxc, w = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        T, N = dy2.shape
+        K = w.shape[1]
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            dq, sd = quant_rowwise(dy2, ctx.grad_fmt)    # scales per token
+            wc, swc = quant_colwise(w)                   # scales per input feature k; stored [N][K] = MN-major B
+            dx = gemm_rowwise(dq, sd, wc, swc, T, K, N, b_mn=True).view(ctx.x_shape)
+        if ctx.needs_input_grad[1]:
+            dc, sdc = quant_colwise(dy2, ctx.grad_fmt)   # scales per output feature n, over all tokens
+            main_grad = getattr(w, "main_grad", None)
+            if main_grad is not None:
+                gemm_rowwise(dc, sdc, xc, sxc, N, K, T, a_mn=True, b_mn=True, out=main_grad.view(w.shape),
+                             accumulate=getattr(w, "grad_added", False))
+                w.grad_added = True
+            else:
+                dw = gemm_rowwise(dc, sdc, xc, sxc, N, K, T, a_mn=True, b_mn=True, out_dtype=w.dtype)
+        return dx, dw, None
+
+
+def fp8_linear_rowwise(x: torch.Tensor, w: torch.Tensor, grad_format: str = "e4m3") -> torch.Tensor:
+    """Linear layer whose forward, dgrad and wgrad GEMMs all run in fp8 with row / column scales (module docstring)."""
+    return _FP8RowwiseLinearFn.apply(x, w, grad_format)

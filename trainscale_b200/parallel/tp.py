@@ -330,10 +330,26 @@ class _TPBlockIO(nn.Module):
     def __init__(self, inner: nn.Module, tp: TPContext):
         super().__init__()
         self.inner, self.tp = inner, tp
+        # fused back-end + sequence parallelism: the block's first projection gathers the token shards inside its GEMM
+        # kernel and its last projection reduce-scatters from the GEMM epilogue (models/llama.py `_lin`)
+        self.fused_sp = tp.sequence_parallel and tp.comm == "fused" and tp.heap is not None and \
+            not getattr(inner, "fp8", False)
+        if self.fused_sp:
+            inner.tp_ctx = tp
+
+    def _fits_fused(self, x) -> bool:
+        B, S, H = x.shape
+        return x.is_cuda and x.dtype == torch.bfloat16 and B == 1 and S % 128 == 0 and H % 64 == 0 and \
+            getattr(self.inner, "lora", None) is None and not getattr(self.inner, "fp8", False)
 
     def forward(self, x, *args, **kw):
         tp = self.tp
         if tp.sequence_parallel:
+            if self.fused_sp:
+                if self._fits_fused(x) and kw.get("kv_cache") is None:
+                    self.inner.tp_ctx = tp
+                    return self.inner(x, *args, **kw)
+                self.inner.tp_ctx = None       # this call goes through the library collectives below
             B, S, H = x.shape   # tokens are sharded along S; gather them (B must be 1 per shard row-block)
             xg = all_gather_from_sequence_parallel_region(x.reshape(B * S, H), tp).view(B, S * tp.size, H) if B == 1 else \
                 all_gather_from_sequence_parallel_region(x.transpose(0, 1).contiguous(), tp).transpose(0, 1)

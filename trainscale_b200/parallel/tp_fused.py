@@ -17,6 +17,7 @@ from ..ops import _lib
 from ..ops.gemm import matmul_tn
 
 _ll, _u = ctypes.c_longlong, ctypes.c_uint
+CALLS = {"gather_gemm": 0, "gemm_reduce": 0}     # launches of the fused kernels (tests check that they ran)
 
 
 class _Buffers:
@@ -59,6 +60,7 @@ def _launch(mode, tp, b, A, B, C, a_full, M, N, K, lda, ldb, ldc, b_mn):
 
 def _gather_gemm(x_shard, w, tp, b_mn):
     """(y [M, N], a_full [M, K]); w is [N, K] (b_mn False) or [K, N] (b_mn True)."""
+    CALLS["gather_gemm"] += 1
     Ms, K = x_shard.shape
     M = Ms * tp.size
     N = w.shape[1] if b_mn else w.shape[0]
@@ -85,6 +87,7 @@ REDUCE_MODE = os.environ.get("TS_TP_REDUCE", "tma")
 
 def _gemm_reduce(x, w, tp, b_mn):
     """y_shard [M/W, N] (bf16) = reduce_scatter(x @ w^T)."""
+    CALLS["gemm_reduce"] += 1
     M, K = x.shape
     N = w.shape[1] if b_mn else w.shape[0]
     Ms = M // tp.size

@@ -206,9 +206,11 @@ class SOTATrainer:
         if self.config.lora.enabled:
             from ..lora import apply_lora
             self.model = apply_lora(self.model, self.config.lora)
-        if getattr(self.config.hardware.precision, "value", self.config.hardware.precision) in ("fp8_e4m3", "fp8") \
-                and hasattr(self.model, "enable_fp8") and self.device.type == "cuda":
-            self.model.enable_fp8(True)      # bf16 parameters, fp8 tensor-core GEMMs for the layer projections
+        prec = getattr(self.config.hardware.precision, "value", self.config.hardware.precision)
+        if prec in ("fp8_e4m3", "fp8_e5m2", "fp8") and hasattr(self.model, "enable_fp8") and self.device.type == "cuda":
+            # bf16 parameters, fp8 tensor-core GEMMs for the layer projections
+            self.model.enable_fp8(True, recipe=self.config.hardware.fp8_recipe,
+                                  grad_format="e5m2" if prec == "fp8_e5m2" else "e4m3")
         d = self.config.distributed
         fc = dict(d.fsdp_config or {})
         use_ckpt = bool(fc.get("activation_checkpointing", d.gradient_checkpointing))
