@@ -50,6 +50,28 @@ def test_gemm_layouts_and_accumulate(M, N, K):
     assert rel_err(accb, a.float() @ bt.float() + 1) < 1e-2
 
 
+@pytest.mark.parametrize("M,N,K", [(8000, 4104, 1024), (2560, 2056, 520), (8192, 4096, 3584), (304, 264, 200)])
+def test_gemm_paired_cta_kernel_every_layout_against_fp32(M, N, K):
+    """bn=512 selects the cluster-of-two 256 x 256 kernel explicitly: forward (NT), dgrad (NN) and wgrad (TN) operand
+    layouts, M and N that are not multiples of 256 (partial tiles on both edges), K with a tail, fp32 accumulation."""
+    from trainscale_b200.ops import gemm
+    torch.manual_seed(5)
+    a = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
+    b = torch.randn(N, K, device=DEV, dtype=torch.bfloat16)
+    ref = a.float() @ b.float().t()
+    assert rel_err(gemm.matmul_nt(a, b, bn=512), ref) < 1e-2
+    bt = b.t().contiguous()                                         # [K, N]: MN-major B
+    assert rel_err(gemm.matmul_nn(a, bt, bn=512), ref) < 1e-2
+    at = a.t().contiguous()                                         # [K, M]: MN-major A
+    assert rel_err(gemm.matmul_tn(at, bt, bn=512), ref) < 1e-2
+    acc = torch.full((M, N), 2.0, device=DEV, dtype=torch.float32)
+    gemm.matmul_tn(at, bt, out=acc, accumulate=True, alpha=0.25, bn=512)
+    assert rel_err(acc, 0.25 * ref + 2) < 1e-4
+    # the default policy must pick the same kernel for the large shapes and agree bit for bit with the explicit choice
+    if (M + 255) // 256 * ((N + 255) // 256) >= 74:
+        assert torch.equal(gemm.matmul_nt(a, b), gemm.matmul_nt(a, b, bn=512))
+
+
 def test_linear_autograd_matches_torch():
     from trainscale_b200.ops import gemm
     torch.manual_seed(2)
