@@ -28,16 +28,27 @@ class Timer:
     def __init__(self, flush_mb: int = 256):
         self.flush = torch.empty(flush_mb * 2 ** 20, dtype=torch.int8, device="cuda")
 
-    def __call__(self, fn, iters: int = 10, warmup: int = 3) -> float:
+    def __call__(self, fn, iters: int = 10, warmup: int = 3, graph: bool = False) -> float:
+        """Mean device time of `fn` in ms.  `graph`: replay `fn` from a CUDA graph, so that the time between the two
+        events is the kernels' own (for kernels of a few tens of microseconds the host-side launch path is longer
+        than the kernel, and an event pair around a plain call measures the host)."""
         for _ in range(warmup):
             fn()
         torch.cuda.synchronize()
+        run = fn
+        if graph:
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                fn()
+            run = g.replay
+            run()
+            torch.cuda.synchronize()
         total = 0.0
         for _ in range(iters):
             self.flush.zero_()           # evict L2 (126 MB)
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a.record()
-            fn()
+            run()
             b.record()
             torch.cuda.synchronize()
             total += a.elapsed_time(b)
@@ -51,8 +62,8 @@ def bench_rmsnorm(t, small):
     for B, S, D in shapes:
         x = torch.randn(B * S, D, device="cuda", dtype=torch.bfloat16)
         w = torch.ones(D, device="cuda", dtype=torch.bfloat16)
-        ms = t(lambda: norm.rmsnorm(x, w))
-        base = t(lambda: F.rms_norm(x, (D,), w, 1e-5))
+        ms = t(lambda: norm.rmsnorm(x, w), graph=True)
+        base = t(lambda: F.rms_norm(x, (D,), w, 1e-5), graph=True)
         out.append(dict(name=f"rmsnorm B={B},S={S},D={D}", ms=ms, baseline_ms=base, gbs=2 * x.numel() * 2 / ms / 1e6))
     return out
 
@@ -62,8 +73,8 @@ def bench_swiglu(t, small):
     out = []
     for rows, I in ([(2048, 11008)] if small else [(2048, 11008), (8192, 14336)]):
         gu = torch.randn(rows, 2 * I, device="cuda", dtype=torch.bfloat16)
-        ms = t(lambda: activation.glu(gu))
-        base = t(lambda: F.silu(gu[:, :I]) * gu[:, I:])
+        ms = t(lambda: activation.glu(gu), graph=True)
+        base = t(lambda: F.silu(gu[:, :I]) * gu[:, I:], graph=True)
         out.append(dict(name=f"swiglu rows={rows},I={I}", ms=ms, baseline_ms=base, gbs=3 * rows * I * 2 / ms / 1e6))
     return out
 
@@ -75,9 +86,11 @@ def bench_rope(t, small):
         Hq, Hkv, D = 32, 8, 128
         cos, sin = rope.rope_tables(S, D, 500000.0, "cuda")
         qkv = torch.randn(1, S, (Hq + 2 * Hkv) * D, device="cuda", dtype=torch.bfloat16)
-        ms = t(lambda: rope.apply_rope_qkv(qkv, Hq + Hkv, D, cos, sin))
-        base = t(lambda: qkv.clone())
-        out.append(dict(name=f"rope S={S}", ms=ms, baseline_ms=base, gbs=2 * qkv.numel() * 2 / ms / 1e6))
+        ms = t(lambda: rope.apply_rope_qkv(qkv, Hq + Hkv, D, cos, sin), graph=True)
+        base = t(lambda: qkv.clone(), graph=True)
+        # bytes: the q and k heads are read and written in place (v is not touched), plus the cos / sin rows
+        out.append(dict(name=f"rope S={S}", ms=ms, baseline_ms=base,
+                        gbs=(2 * S * (Hq + Hkv) * D * 2 + 2 * S * D * 2) / ms / 1e6))
     return out
 
 
@@ -148,7 +161,7 @@ def bench_fp8(t, small):
         wq, ws = fp8.quant_block(w)
         ms = t(lambda: fp8.gemm_fp8(xq, xs, wq, ws, N))
         out.append(dict(name=f"fp8_gemm {M}x{N}x{K}", ms=ms, baseline_ms=None, tflops=2 * M * N * K / ms / 1e9))
-        ms = t(lambda: fp8.quant_act(x))
+        ms = t(lambda: fp8.quant_act(x), graph=True)
         out.append(dict(name=f"fp8_quant_act {M}x{K}", ms=ms, baseline_ms=None, gbs=M * K * 3 / ms / 1e6))
     return out
 
@@ -185,9 +198,9 @@ def bench_fp8_rowwise(t, small):
         base = t(lambda: gemm.matmul_tn(dy, x, out=dw))
         out.append(dict(name=f"fp8_rowwise_gemm wgrad {N}x{K}x{M}", ms=ms, baseline_ms=base,
                         tflops=2 * M * N * K / ms / 1e9))
-        ms = t(lambda: fp8.quant_rowwise(dy))
+        ms = t(lambda: fp8.quant_rowwise(dy), graph=True)
         out.append(dict(name=f"fp8_quant_rowwise {M}x{N}", ms=ms, baseline_ms=None, gbs=M * N * 3 / ms / 1e6))
-        ms = t(lambda: fp8.quant_colwise(dy))
+        ms = t(lambda: fp8.quant_colwise(dy), graph=True)
         out.append(dict(name=f"fp8_quant_colwise {M}x{N}", ms=ms, baseline_ms=None, gbs=M * N * 5 / ms / 1e6))
         xg, wg = x.clone().requires_grad_(True), w.clone().requires_grad_(True)
 
@@ -223,8 +236,8 @@ def bench_layernorm(t, small):
         x = torch.randn(rows, H, device="cuda", dtype=torch.bfloat16)
         w = torch.ones(H, device="cuda", dtype=torch.bfloat16)
         b = torch.zeros(H, device="cuda", dtype=torch.bfloat16)
-        ms = t(lambda: norm.layernorm(x, w, b))
-        base = t(lambda: F.layer_norm(x, (H,), w, b))
+        ms = t(lambda: norm.layernorm(x, w, b), graph=True)
+        base = t(lambda: F.layer_norm(x, (H,), w, b), graph=True)
         out.append(dict(name=f"layernorm_fwd {rows}x{H}", ms=ms, baseline_ms=base, gbs=rows * H * 4 / ms / 1e6))
     return out
 
@@ -311,8 +324,8 @@ def bench_gelu(t, small):
     out = []
     for n in ([1 << 24] if small else [1 << 24, 1 << 27]):
         x = torch.randn(n, device="cuda", dtype=torch.bfloat16)
-        ms = t(lambda: activation.gelu(x, "tanh"))
-        base = t(lambda: F.gelu(x, approximate="tanh"))
+        ms = t(lambda: activation.gelu(x, "tanh"), graph=True)
+        base = t(lambda: F.gelu(x, approximate="tanh"), graph=True)
         out.append(dict(name=f"gelu n={n}", ms=ms, baseline_ms=base, gbs=2 * n * 2 / ms / 1e6))
     return out
 

@@ -101,10 +101,19 @@ __global__ void __launch_bounds__(NORM_THREADS) rmsnorm_fwd_kernel(const __nv_bf
   }
 }
 
-// Warp-per-row forward for rows of up to 32 * VPL vectors (H <= 4096 with VPL = 16): the whole row sits in the
-// warp's registers, the reduction is shuffle-only, and a warp keeps VPL independent 16-byte loads in flight.  Warps
-// walk rows with a grid stride, so there is no per-row CTA launch.
-template <int VPL>
+// Warp-per-row forward for rows of up to 32 * VPL vectors (H <= 4096 with VPL = 16).  The row stays in the warp's
+// registers as the PACKED bf16 words that were loaded (4 registers per 16-byte vector, not 8 floats): that leaves room
+// for all VPL loads of a lane to be in flight at once, which is what the memory system needs from the few warps that
+// fit on an SM.  The reduction is shuffle-only; warps walk rows with a grid stride.
+__device__ __forceinline__ void unpack_u4(const uint4& r, float* f) {
+  const float2 a = unpack_bf16x2(r.x), b = unpack_bf16x2(r.y), c = unpack_bf16x2(r.z), d = unpack_bf16x2(r.w);
+  f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
+}
+__device__ __forceinline__ uint4 pack_u4(const float* f) {
+  return make_uint4(pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]), pack_bf16x2(f[4], f[5]), pack_bf16x2(f[6], f[7]));
+}
+
+template <int VPL, bool HAS_RES>
 __global__ void __launch_bounds__(128) rmsnorm_fwd_warp_kernel(const __nv_bfloat16* __restrict__ x,
                                                                const __nv_bfloat16* __restrict__ residual,
                                                                const __nv_bfloat16* __restrict__ w,
@@ -117,49 +126,65 @@ __global__ void __launch_bounds__(128) rmsnorm_fwd_warp_kernel(const __nv_bfloat
   const long long warps = static_cast<long long>(gridDim.x) * (blockDim.x >> 5);
   for (long long row = blockIdx.x * static_cast<long long>(blockDim.x >> 5) + (threadIdx.x >> 5); row < rows;
        row += warps) {
-    const __nv_bfloat16* xr = x + row * H;
-    float f[VPL][8];
-    float ss = 0.f;
+    const uint4* xr = reinterpret_cast<const uint4*>(x + row * H);
+    uint4 raw[VPL];
 #pragma unroll
     for (int c = 0; c < VPL; ++c) {
       const int i = lane + c * 32;
-      if (i < nvec) load8(xr + i * 8, f[c]);
+      raw[c] = i < nvec ? __ldcs(xr + i) : make_uint4(0u, 0u, 0u, 0u);
     }
-    if (residual) {
+    if constexpr (HAS_RES) {
+      const uint4* rr = reinterpret_cast<const uint4*>(residual + row * H);
+      uint4* ro = reinterpret_cast<uint4*>(res_out + row * H);
+      uint4 rres[VPL];
 #pragma unroll
       for (int c = 0; c < VPL; ++c) {
         const int i = lane + c * 32;
-        if (i < nvec) {
-          float r[8];
-          load8(residual + row * H + i * 8, r);
-#pragma unroll
-          for (int e = 0; e < 8; ++e) f[c][e] += r[e];
-          store8(res_out + row * H + i * 8, f[c]);
-          // the sum is rounded to bf16 exactly as the stored residual stream is
-#pragma unroll
-          for (int e = 0; e < 8; ++e) f[c][e] = __bfloat162float(__float2bfloat16(f[c][e]));
-        }
+        rres[c] = i < nvec ? __ldcs(rr + i) : make_uint4(0u, 0u, 0u, 0u);
       }
+#pragma unroll
+      for (int c = 0; c < VPL; ++c) {
+        const int i = lane + c * 32;
+        float a[8], b[8];
+        unpack_u4(raw[c], a);
+        unpack_u4(rres[c], b);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) a[e] += b[e];
+        raw[c] = pack_u4(a);          // the sum is rounded to bf16 exactly as the stored residual stream is
+        if (i < nvec) __stcs(ro + i, raw[c]);
+      }
+#pragma unroll
+      for (int c = 0; c < VPL; ++c)
+        asm volatile("" : "+r"(raw[c].x), "+r"(raw[c].y), "+r"(raw[c].z), "+r"(raw[c].w));
     }
+    float ss = 0.f;
 #pragma unroll
     for (int c = 0; c < VPL; ++c) {
-      if (lane + c * 32 < nvec) {
+      float a[8];
+      unpack_u4(raw[c], a);           // out-of-range vectors are zero and add nothing
 #pragma unroll
-        for (int e = 0; e < 8; ++e) ss += f[c][e] * f[c][e];
-      }
+      for (int e = 0; e < 8; ++e) ss += a[e] * a[e];
     }
     ss = warp_sum(ss);
     const float rstd = rsqrtf(ss / H + eps);
     if (lane == 0 && rstd_out) rstd_out[row] = rstd;
+    // the second pass unpacks the words again: without this the compiler keeps all 8 * VPL floats of the first pass
+    // alive, and the registers that costs are exactly the ones the in-flight loads need
+#pragma unroll
+    for (int c = 0; c < VPL; ++c)
+      asm volatile("" : "+r"(raw[c].x), "+r"(raw[c].y), "+r"(raw[c].z), "+r"(raw[c].w));
+    const uint4* wr = reinterpret_cast<const uint4*>(w);
+    uint4* yr = reinterpret_cast<uint4*>(y + row * H);
 #pragma unroll
     for (int c = 0; c < VPL; ++c) {
       const int i = lane + c * 32;
       if (i < nvec) {
-        float wv[8];
-        load8(w + i * 8, wv);
+        float a[8], wv[8];
+        unpack_u4(raw[c], a);
+        unpack_u4(__ldg(wr + i), wv);
 #pragma unroll
-        for (int e = 0; e < 8; ++e) f[c][e] = f[c][e] * rstd * (wv[e] + w_offset);
-        store8(y + row * H + i * 8, f[c]);
+        for (int e = 0; e < 8; ++e) a[e] = a[e] * rstd * (wv[e] + w_offset);
+        yr[i] = pack_u4(a);          // default caching: the next kernel (a GEMM) reads y out of L2
       }
     }
   }
@@ -876,12 +901,15 @@ extern "C" int ts_rmsnorm_fwd(const void* x, const void* residual, const void* w
     long long blocks = (rows + 3) / 4;
     const long long cap = static_cast<long long>(sm_count()) * 8;
     if (blocks > cap) blocks = cap;
-    if (H <= 2048)
-      rmsnorm_fwd_warp_kernel<8><<<(unsigned)blocks, 128, 0, ST(stream)>>>(
-          (const bf16*)x, (const bf16*)residual, (const bf16*)w, (bf16*)y, (bf16*)res_out, rstd, rows, H, eps, w_offset);
-    else
-      rmsnorm_fwd_warp_kernel<16><<<(unsigned)blocks, 128, 0, ST(stream)>>>(
-          (const bf16*)x, (const bf16*)residual, (const bf16*)w, (bf16*)y, (bf16*)res_out, rstd, rows, H, eps, w_offset);
+#define TS_RMS_WARP(VPL, RES)                                                                                     \
+  rmsnorm_fwd_warp_kernel<VPL, RES><<<(unsigned)blocks, 128, 0, ST(stream)>>>(                                    \
+      (const bf16*)x, (const bf16*)residual, (const bf16*)w, (bf16*)y, (bf16*)res_out, rstd, rows, H, eps, w_offset)
+    if (H <= 2048) {
+      if (residual) TS_RMS_WARP(8, true); else TS_RMS_WARP(8, false);
+    } else {
+      if (residual) TS_RMS_WARP(16, true); else TS_RMS_WARP(16, false);
+    }
+#undef TS_RMS_WARP
     return (int)cudaGetLastError();
   }
   rmsnorm_fwd_kernel<<<(unsigned)rows, NORM_THREADS, 0, ST(stream)>>>(

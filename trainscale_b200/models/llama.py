@@ -61,6 +61,17 @@ class LlamaConfig:
     def to_dict(self) -> dict:
         return asdict(self)
 
+    def tensor_parallel_local(self, tp: int) -> "LlamaConfig":
+        """The shapes ONE tensor-parallel rank holds: heads and FFN columns divided by `tp`, everything else equal.
+        A decoder built from it has exactly the parameters `shard_llama_state_for_tp` would leave on a rank."""
+        if self.num_attention_heads % tp or self.num_key_value_heads % tp or self.intermediate_size % tp:
+            raise ValueError(f"heads ({self.num_attention_heads}/{self.num_key_value_heads}) and FFN width "
+                             f"({self.intermediate_size}) must divide by the tensor-parallel size {tp}")
+        d = self.to_dict()
+        d.update(num_attention_heads=self.num_attention_heads // tp, num_key_value_heads=self.num_key_value_heads // tp,
+                 intermediate_size=self.intermediate_size // tp, head_dim=self.head_dim)
+        return LlamaConfig(**d)
+
     @classmethod
     def from_dict(cls, d: dict) -> "LlamaConfig":
         keys = {f for f in cls.__dataclass_fields__}
@@ -307,11 +318,13 @@ class CausalLMOutput:
 
 
 class LlamaModel(nn.Module):
-    def __init__(self, cfg: LlamaConfig):
+    def __init__(self, cfg: LlamaConfig, layer_range: range | None = None):
+        """`layer_range`: build only these decoder layers (one pipeline stage's); the others are placeholders."""
         super().__init__()
         self.cfg = cfg
         self.embed_tokens = nn.Embedding(cfg.vocab_size, cfg.hidden_size)
-        self.layers = nn.ModuleList(LlamaDecoderLayer(cfg) for _ in range(cfg.num_hidden_layers))
+        self.layers = nn.ModuleList(LlamaDecoderLayer(cfg) if (layer_range is None or i in layer_range) else nn.Identity()
+                                    for i in range(cfg.num_hidden_layers))
         self.norm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, cfg.norm_weight_offset)
         self.gradient_checkpointing = False
         self.checkpoint_every = 1
@@ -390,20 +403,26 @@ class LlamaForCausalLM(nn.Module):
     as in data_pipeline/trainer/trainers/sota_trainer.py:2044-2055) and returns the mean loss over
     non-ignored tokens."""
 
-    def __init__(self, cfg: LlamaConfig):
+    def __init__(self, cfg: LlamaConfig, layer_range: range | None = None, init: bool = True):
         super().__init__()
         self.config = cfg
-        self.model = LlamaModel(cfg)
+        self.model = LlamaModel(cfg, layer_range)
         self.lm_head = None if cfg.tie_word_embeddings else nn.Parameter(torch.empty(cfg.vocab_size, cfg.hidden_size))
         self.loss_chunk_tokens = cross_entropy.DEFAULT_CHUNK_TOKENS
-        self.reset_parameters()
+        if init:
+            self.reset_parameters()
 
     # ---------------------------------------------------------------- init / introspection
     @torch.no_grad()
-    def reset_parameters(self, seed: int | None = None):
+    def reset_parameters(self, seed: int | None = None, on_device: bool = False):
+        """Normal(0, initializer_range) weights (output projections scaled by 1/sqrt(2L)), unit norm weights.  With a
+        seed the values come from a CPU generator, so every device and every rank builds the same model; `on_device`
+        draws them with the parameters' own device generator instead (seconds instead of minutes for tens of billions
+        of parameters; the values then depend on the device type, not only on the seed)."""
         gen = None
-        if seed is not None:
+        if seed is not None and not on_device:
             gen = torch.Generator(device="cpu").manual_seed(seed)
+        dgen: dict = {}
         std = self.config.initializer_range
         for name, p in self.named_parameters():
             if name.endswith("bqkv"):
@@ -416,6 +435,11 @@ class LlamaForCausalLM(nn.Module):
                     s = std / math.sqrt(2 * self.config.num_hidden_layers)
                 if gen is not None:
                     p.copy_(torch.randn(p.shape, generator=gen) * s)
+                elif seed is not None:
+                    g = dgen.get(p.device)
+                    if g is None:
+                        g = dgen[p.device] = torch.Generator(device=p.device).manual_seed(seed)
+                    p.normal_(0.0, s, generator=g)
                 else:
                     p.normal_(0.0, s)
 
@@ -621,7 +645,10 @@ class LlamaForCausalLM(nn.Module):
                 "hidden_act": c.hidden_act, "torch_dtype": "bfloat16"}
 
 
-def build_model(cfg: LlamaConfig | str | dict, dtype=torch.bfloat16, device=None, seed: int | None = None) -> LlamaForCausalLM:
+def build_model(cfg: LlamaConfig | str | dict, dtype=torch.bfloat16, device=None, seed: int | None = None,
+                layer_range: range | None = None, init_on_device: bool = False) -> LlamaForCausalLM:
+    """Random-init decoder.  `layer_range`: only these layers are built (a pipeline stage); `init_on_device`: draw the
+    weights with the device's generator (see `reset_parameters`)."""
     if isinstance(cfg, str):
         cfg = preset_config(cfg)
     elif isinstance(cfg, dict):
@@ -631,11 +658,11 @@ def build_model(cfg: LlamaConfig | str | dict, dtype=torch.bfloat16, device=None
     try:
         if device is not None:
             with torch.device(device):
-                m = LlamaForCausalLM(cfg)
+                m = LlamaForCausalLM(cfg, layer_range, init=seed is None)
         else:
-            m = LlamaForCausalLM(cfg)
+            m = LlamaForCausalLM(cfg, layer_range, init=seed is None)
     finally:
         torch.set_default_dtype(prev)
     if seed is not None:
-        m.reset_parameters(seed)
+        m.reset_parameters(seed, on_device=init_on_device)
     return m

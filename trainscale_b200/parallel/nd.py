@@ -66,6 +66,8 @@ class NDEngine:
                                               next_rank=self.pp_ranks[stage + 1] if stage < P - 1 else None)
             self.pp_microbatches = int(p.pp_microbatches or 0)
             self.pipelined = True
+            if self.tp is not None and p.sp:
+                self.stage_module.sp_ctx = self.tp     # token-sharded activations inside and between the stages
             opt_model = self.stage_module
             overlap = False            # the schedule interleaves micro-batches: reduce once, in step()
             gas = gas * max(1, self.pp_microbatches or 1)
@@ -101,7 +103,8 @@ class NDEngine:
             raise ValueError(f"batch of {B} sequences does not split into {M} pipeline micro-batches")
         mbs = PP.split_into_microbatches({k: v for k, v in batch.items() if torch.is_tensor(v)}, M)
         H = self.stage_module.config.hidden_size
-        act_shape = (B // M, S, 2 * H)
+        sp = self.tp.size if (self.tp is not None and self.tp.sequence_parallel) else 1
+        act_shape = (B // M, S // sp, 2 * H)      # with sequence parallelism a rank exchanges only its token shard
         dev = batch["input_ids"].device
         loss = self.runtime.train_step(mbs, act_shape, self.trainer.dtype, dev, extra_scale=loss_scale)
         lc = self.trainer.config.loss
@@ -115,6 +118,9 @@ class NDEngine:
                                                           self.stage_module.config.tie_word_embeddings):
             PP.allreduce_tied_embedding_grads(self.stage_module, self.dims.group("pp"), self.pp_ranks[0],
                                               self.pp_ranks[-1])
+        if self.tp is not None and self.tp.sequence_parallel:
+            from . import tp as TP
+            TP.allreduce_sequence_parallel_grads(self.stage_module, self.tp)
         self.flat.micro_step += 1
         return out[0], ntok
 

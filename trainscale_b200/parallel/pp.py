@@ -237,14 +237,34 @@ class LlamaStage(nn.Module):
         else:
             H = x.shape[-1] // 2
             h, res = x[..., :H], x[..., H:]
-        cos, sin = self._rope.rope_tables(h.device, h.shape[1])
-        for layer in self.layers:
-            h, res = layer(h, res, cos, sin)
+        sp = getattr(self, "sp_ctx", None)
+        S_full = h.shape[1] * (sp.size if (sp is not None and not self.first) else 1)
+        cos, sin = self._rope.rope_tables(h.device, S_full)
+        if sp is not None and self.first:
+            # sequence parallelism: from here on (and between stages) every tensor-parallel rank holds S / tp tokens
+            from . import tp as TP
+            if h.shape[0] != 1:
+                raise ValueError("sequence-parallel pipeline stages take one sequence per micro-batch")
+            h = TP.scatter_to_sequence_parallel_region(h.view(S_full, -1), sp).view(1, S_full // sp.size, -1)
+        ckpt = self._rope.gradient_checkpointing and self.training and torch.is_grad_enabled()
+        every = max(1, getattr(self._rope, "checkpoint_every", 1))
+        for i, layer in enumerate(self.layers):
+            if ckpt and i % every == 0:
+                from torch.utils.checkpoint import checkpoint
+                h, res = checkpoint(layer, h, res, cos, sin, use_reentrant=False)
+            else:
+                h, res = layer(h, res, cos, sin)
         if not self.last:
             if res is None:
                 res = torch.zeros_like(h)
             return torch.cat((h, res), dim=-1)
         h, _ = self.norm(h, res)
+        if sp is not None:
+            from . import tp as TP
+            from ..models.llama import _ScaleGrad
+            # every rank computes the full loss on the gathered tokens; the gather's backward sums tp copies
+            h = TP.all_gather_from_sequence_parallel_region(h.view(S_full // sp.size, -1), sp).view(1, S_full, -1)
+            h = _ScaleGrad.apply(h, 1.0 / sp.size)
         if labels is None:
             return h
         tgt = torch.full_like(labels, -100)

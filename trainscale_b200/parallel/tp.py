@@ -366,8 +366,17 @@ def shard_model_for_tensor_parallel(model, tp: TPContext):
     all-reduce the norm-weight gradients over the TP group (`allreduce_sequence_parallel_grads`)."""
     if not tp.active:
         return model
-    shard_llama_state_for_tp(model, tp.size, tp.rank)
+    if getattr(model, "tp_presharded", 0) == tp.size:
+        # built with this rank's slice only (random init): the replicated parameters must still agree inside the group
+        with torch.no_grad():
+            for n, p in model.named_parameters():
+                if p.dim() == 1 or "embed_tokens" in n or "lm_head" in n:
+                    dist.broadcast(p.data, src=dist.get_global_rank(tp.group, 0), group=tp.group)
+    else:
+        shard_llama_state_for_tp(model, tp.size, tp.rank)
     for layer in model.model.layers:
+        if isinstance(layer, nn.Identity):      # another pipeline stage's layer
+            continue
         layer.self_attn = _TPBlockIO(layer.self_attn, tp)
         layer.mlp = _TPBlockIO(layer.mlp, tp)
     model.tp = tp

@@ -192,7 +192,24 @@ class SOTATrainer:
         cfg = preset_config(arch) if isinstance(arch, str) else LlamaConfig.from_dict(arch)
         if self.config.model.max_position_embeddings:
             cfg.max_position_embeddings = self.config.model.max_position_embeddings
-        return build_model(cfg, dtype=self.dtype, device=self.device, seed=self.config.training.seed)
+        seed = self.config.training.seed
+        big = cfg.num_parameters() > 2_000_000_000 and self.device.type == "cuda"
+        par = self.config.distributed.parallel
+        tp, pp = int(getattr(par, "tp", 1) or 1), int(getattr(par, "pp", 1) or 1)
+        if big and self.is_distributed and self.strategy in ("pipeline", "tensor_parallel", "nd") and (tp > 1 or pp > 1):
+            # A random-init model too large to be built whole on every rank: build only what this rank will hold (its
+            # tensor-parallel slice of every projection, its pipeline stage's layers), with weights drawn on the GPU.
+            from ..parallel.mesh import create_parallel_dims_from_config
+            from ..parallel.pp import split_layers
+            dims = create_parallel_dims_from_config(self.config.distributed)
+            local = cfg.tensor_parallel_local(tp) if tp > 1 else cfg
+            layers = split_layers(cfg.num_hidden_layers, pp)[dims.local_rank("pp")] if pp > 1 else None
+            model = build_model(local, dtype=self.dtype, device=self.device, layer_range=layers, init_on_device=True,
+                                seed=seed + 7919 * dims.local_rank("tp"))
+            model.config = cfg                       # the whole model's shape (FLOP accounting, checkpoint export)
+            model.tp_presharded = tp
+            return model
+        return build_model(cfg, dtype=self.dtype, device=self.device, seed=seed, init_on_device=big)
 
     def setup_model(self, model: nn.Module | None = None, model_init_fn: Callable[[], nn.Module] | None = None):
         if model is None and model_init_fn is not None:
