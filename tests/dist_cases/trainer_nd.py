@@ -39,7 +39,7 @@ def make_cfg(strategy, parallel, world, enabled):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--mode", default="pp", choices=["pp", "sp", "cp", "ulysses", "tp_dp"])
+    ap.add_argument("--mode", default="pp", choices=["pp", "sp", "cp", "ulysses", "tp_dp", "tp_pp"])
     ap.add_argument("--cuda", action="store_true", help="bf16 on GPUs through the CUDA kernels (fused TP path)")
     a = ap.parse_args()
     if CUDA:
@@ -60,6 +60,11 @@ def main():
     elif a.mode in ("cp", "ulysses"):
         par = {"cp": world, "dp_shard": 1, "cp_balancer": "head_tail" if a.mode == "cp" else "ulysses"}
         strategy, B = "context_parallel", 1
+    elif a.mode == "tp_pp":
+        # 2 pipeline stages x tensor-parallel pairs with sequence parallelism: token-sharded activations inside and
+        # between the stages, one sequence per pipeline micro-batch
+        par = {"tp": 2, "pp": world // 2, "dp_shard": 1, "sp": True, "pp_schedule": "1f1b", "pp_microbatches": 2}
+        strategy, B = "pipeline", 2
     elif a.mode == "tp_dp":
         # tensor parallel pairs x data parallel replicas: the clip must see the norm of the whole model, with the
         # parameters replicated inside a pair (norms, embedding, head) counted once

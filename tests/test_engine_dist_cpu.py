@@ -115,3 +115,12 @@ def test_tensor_parallel_pairs_times_data_parallel_clip_norm():
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
     assert "RESULT mode=tp_dp ok=True" in r.stdout
+
+
+def test_pipeline_stages_of_tensor_parallel_pairs_with_sequence_parallelism():
+    """pp=2 x tp=2 (+ sequence parallelism) on four gloo ranks reproduces the single-process losses and checkpoint."""
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=4", "--master-addr",
+           "127.0.0.1", "--master-port", "29626", str(ND_CASE), "--mode", "tp_pp"]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    assert "RESULT mode=tp_pp ok=True" in r.stdout

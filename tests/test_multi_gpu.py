@@ -102,3 +102,11 @@ def test_dpo_with_sharded_frozen_reference_on_two_gpus(comm, port):
     out = _launch("preference_equivalence.py", "--device", "cuda", "--comm", comm, port=port)
     assert "RESULT preference" in out and "ok=True" in out
     assert ("fused=True" in out) == (comm == "fused")
+
+
+def test_pipeline_of_tensor_parallel_pairs_on_four_gpus():
+    """pp=2 x tp=2 with sequence parallelism through the trainer: fused tensor-parallel GEMMs inside the stages,
+    token-sharded activations between them."""
+    _need(4)
+    out = _launch("trainer_nd.py", "--mode", "tp_pp", "--cuda", port=29781, nproc=4)
+    assert "RESULT mode=tp_pp ok=True" in out
