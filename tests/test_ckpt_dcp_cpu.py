@@ -66,3 +66,37 @@ def test_two_rank_save_single_process_load(tmp_path, strategy, port):
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=300)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
     assert f"RESULT dcp strategy={strategy} ok=True" in r.stdout
+
+
+def test_trainer_writes_and_resumes_dcp_checkpoints(tmp_path):
+    """`distributed.fsdp_config.checkpoint_format: dcp`: the trainer's checkpoint directory is a DCP directory, it
+    passes verification, and a new trainer resumes weights, optimizer state and step from it."""
+    from trainscale_b200.ckpt import verify_checkpoint
+    from trainscale_b200.config.sota_config import SOTAConfig
+    from trainscale_b200.trainer.sota_trainer import SOTATrainer
+
+    def make():
+        return SOTATrainer(SOTAConfig.from_dict({
+            "model": {"architecture": {"vocab_size": 128, "hidden_size": 64, "intermediate_size": 96, "num_hidden_layers": 2,
+                                       "num_attention_heads": 4, "num_key_value_heads": 2}},
+            "optimizer": {"type": "adamw", "learning_rate": 1e-2}, "scheduler": {"type": "constant", "warmup_steps": 0},
+            "distributed": {"enabled": False, "strategy": "fsdp2", "fsdp_config": {"checkpoint_format": "dcp"}},
+            "hardware": {"device": "cpu", "precision": "fp32"}, "data": {"max_seq_length": 16},
+            "training": {"output_dir": str(tmp_path), "max_steps": 3, "save_strategy": "no", "eval_strategy": "no"}}))
+    tr = make()
+    tr.setup_model()
+    ids = torch.randint(0, 128, (2, 16), generator=torch.Generator().manual_seed(0))
+    for _ in range(3):
+        tr.train_step({"input_ids": ids, "labels": ids})
+    ck = tr.save_checkpoint()
+    assert is_dcp_checkpoint(ck) and (ck / "trainer_state.pt").exists() and not (ck / "optim").exists()
+    assert verify_checkpoint(ck) == []
+    tr2 = make()
+    tr2.setup_model()
+    tr2.setup_optimizer()
+    tr2.setup_scheduler(3)
+    tr2.load_checkpoint(ck)
+    for (n, p), (_, q) in zip(tr2.model.named_parameters(), tr.model.named_parameters()):
+        assert torch.equal(p, q), n
+    assert tr2.state.global_step == 3 and tr2.engine.step_count == 3
+    assert torch.equal(tr2.engine.units[0].exp_avg_sq, tr.engine.units[0].exp_avg_sq)

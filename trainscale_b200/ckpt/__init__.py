@@ -6,6 +6,9 @@ data_pipeline/trainer/distributed/fsdp2.py:2317-2363:
   checkpoint-{step}/
     model.safetensors (+ config.json)   full weights in HuggingFace Llama naming, written by rank 0
     optim/shard-{rank:05d}-of-{world:05d}.pt   this rank's fp32 master / moment slices (flat engine)
+      -- or, with `distributed.fsdp_config.checkpoint_format: dcp`, instead of the two entries above --
+    .metadata + __{rank}_{n}.distcp     torch.distributed.checkpoint directory (ckpt/dcp.py): fp32 weights and AdamW
+                                        state under HuggingFace parameter names, the reference's `dcp_save` layout
     meta.pt            {epoch, step, api_version, config{sharding_strategy, mixed_precision, world_size}, extra{...}}
     trainer_state.pt   {optimizer|None, scheduler, state{...}, config, rng_state{python,numpy,torch,cuda}, meta{...}}
 
@@ -107,6 +110,21 @@ def save_training_checkpoint(trainer, path: Path) -> None:
         if trainer.is_distributed:
             dist.barrier()
         eng = trainer.engine
+        fmt = str((trainer.config.distributed.fsdp_config or {}).get("checkpoint_format", "")).lower()
+        if fmt == "dcp" and eng is not None and hasattr(eng, "units") and not hasattr(eng, "dims") \
+                and hasattr(trainer.model, "config"):
+            from .dcp import save_dcp_checkpoint
+            st = trainer.state
+            save_dcp_checkpoint(eng, trainer.model, path, st.epoch, st.global_step,
+                                {"best_metric": st.best_metric, "patience_counter": st.patience_counter,
+                                 "samples_seen": st.samples_seen})
+            if rank == 0:
+                _save_trainer_state(trainer, path, None, world, rank)
+                if hasattr(trainer.model, "hf_config_dict"):
+                    (path / "config.json").write_text(json.dumps(trainer.model.hf_config_dict(), indent=2))
+            if trainer.is_distributed:
+                dist.barrier()
+            return
         # FULL_SHARD keeps only shards between steps: every rank takes part in materialising the weights
         summon = eng.summon_full_params() if eng is not None and hasattr(eng, "summon_full_params") \
             else contextlib.nullcontext()
@@ -137,17 +155,22 @@ def save_training_checkpoint(trainer, path: Path) -> None:
             opt_sd = None
             if not sharded and trainer.optimizer is not None and hasattr(trainer.optimizer, "state_dict"):
                 opt_sd = _to_cpu(trainer.optimizer.state_dict())
-            ts = {"optimizer": opt_sd,
-                  "scheduler": trainer.scheduler.state_dict() if trainer.scheduler is not None else None,
-                  "state": asdict(st), "config": trainer.config.to_dict(), "rng_state": trainer._collect_rng_states(),
-                  "scaler": None,
-                  "meta": {"torch_version": torch.__version__, "world_size": world, "rank": rank,
-                           "distributed_strategy": trainer.strategy, "timestamp": time.time()}}
-            atomic_torch_save(ts, path / "trainer_state.pt")
+            _save_trainer_state(trainer, path, opt_sd, world, rank)
         if trainer.is_distributed:
             dist.barrier()
     except OSError as e:
         raise CheckpointSaveError(f"failed to write checkpoint {path}", cause=e)
+
+
+def _save_trainer_state(trainer, path: Path, opt_sd, world: int, rank: int) -> None:
+    st = trainer.state
+    ts = {"optimizer": opt_sd,
+          "scheduler": trainer.scheduler.state_dict() if trainer.scheduler is not None else None,
+          "state": asdict(st), "config": trainer.config.to_dict(), "rng_state": trainer._collect_rng_states(),
+          "scaler": None,
+          "meta": {"torch_version": torch.__version__, "world_size": world, "rank": rank,
+                   "distributed_strategy": trainer.strategy, "timestamp": time.time()}}
+    atomic_torch_save(ts, path / "trainer_state.pt")
 
 
 def reshard_optimizer_state(shards: list[dict], new_rank: int, new_world: int,
@@ -197,18 +220,25 @@ def load_training_checkpoint(trainer, path: Path) -> None:
         raise CheckpointLoadError(f"checkpoint {path} does not exist")
     try:
         eng = trainer.engine
+        from .dcp import is_dcp_checkpoint, load_dcp_checkpoint
+        dcp_dir = is_dcp_checkpoint(path) and eng is not None and hasattr(eng, "units") and not hasattr(eng, "dims")
+        if dcp_dir:
+            load_dcp_checkpoint(eng, trainer.model, path)
         summon = eng.summon_full_params() if eng is not None and hasattr(eng, "summon_full_params") \
             else contextlib.nullcontext()
-        with summon:
-            load_model_weights(trainer.model, path, strict=False, tp=getattr(eng, "tp", None))
-            if eng is not None and hasattr(eng, "units"):
+        with summon if not dcp_dir else contextlib.nullcontext():
+            if dcp_dir:
+                pass
+            else:
+                load_model_weights(trainer.model, path, strict=False, tp=getattr(eng, "tp", None))
+            if eng is not None and hasattr(eng, "units") and not dcp_dir:
                 # the flat buffers alias the parameters: refresh the shards and fp32 masters from the loaded weights
                 for u in eng.units:
                     src = u.flat_param[u.shard_start:u.shard_start + u.shard_numel]
                     if getattr(u, "resharded", False):
                         u.param_shard.copy_(src)
                     u.master.copy_(src)
-        if eng is not None and hasattr(eng, "units"):
+        if eng is not None and hasattr(eng, "units") and not dcp_dir:
             files = sorted((path / "optim").glob("shard-*.pt")) if (path / "optim").exists() else []
             if files:
                 saved_world = int(files[0].stem.split("-of-")[1])
@@ -270,6 +300,9 @@ def verify_checkpoint(path: Path, world_size: int | None = None) -> list[str]:
                     problems.append(f"weight shard {name} does not match its sha256")
         except (OSError, ValueError) as e:
             problems.append(f"weight index is unreadable: {e}")
+    elif (path / ".metadata").exists():
+        if not list(path.glob("*.distcp")):
+            problems.append("torch.distributed.checkpoint metadata without any .distcp data file")
     elif not (path / "model.safetensors").exists() and not (path / "model.pt").exists():
         problems.append("no model weights")
     shards = sorted((path / "optim").glob("shard-*.pt")) if (path / "optim").exists() else []

@@ -158,6 +158,7 @@ def load_dcp_checkpoint(engine, model, path, load_optimizer: bool = True) -> dic
     known = set(reader.read_metadata().state_dict_metadata.keys())
     try:
         step_seen = None
+        engine.drop_gathered()
         for u in engine.units:
             for key, dst in (("model", u.master), ("exp_avg", u.exp_avg), ("exp_avg_sq", u.exp_avg_sq)):
                 if dst is None or (key != "model" and not load_optimizer):

@@ -357,6 +357,22 @@ extern "C" int ts_symm_gather_pull(const unsigned long long* peer_ptrs, long lon
   return (int)cudaGetLastError();
 }
 
+// The same one-sided gather on the copy engines: one peer-to-peer cudaMemcpyAsync per remote shard (the peers' shards
+// are mapped into this process's address space) plus one local copy.  No SM runs a single instruction for it, so a
+// gather that is prefetched under a layer's GEMMs takes nothing from them but NVLink and HBM bandwidth.
+extern "C" int ts_symm_gather_ce(const unsigned long long* peer_ptrs, long long byte_offset, void* dst, int rank,
+                                 int world, long long shard_bytes, void* stream) {
+  if (world > MAX_WORLD || shard_bytes <= 0) return -10;
+  for (int pi = 0; pi < world; ++pi) {
+    const int pr = (rank + 1 + pi) % world;          // remote shards first, a different peer first on every rank
+    const void* src = reinterpret_cast<const void*>(peer_ptrs[pr] + byte_offset);
+    cudaError_t e = cudaMemcpyAsync(static_cast<char*>(dst) + static_cast<long long>(pr) * shard_bytes, src,
+                                    static_cast<size_t>(shard_bytes), cudaMemcpyDeviceToDevice, ST(stream));
+    if (e != cudaSuccess) return (int)e;
+  }
+  return 0;
+}
+
 // Single-GPU self-test of the bounded wait: one warp waits (system-scope acquire loads) on a flag that nothing
 // sets, with the given limit.  `status` becomes 1 when the wait gave up, and the library's error word records
 // ERR_FLAG_TIMEOUT; the context stays usable.

@@ -56,6 +56,7 @@ class EngineConfig:
     optimizer: str = "adamw"                        # adamw | lion
     comm: str = "auto"                              # auto | fused | nccl
     grad_slots: int = 3                             # FULL_SHARD on peer memory: gradient buffers in the slot ring
+    gather_engine: str = "ce"                       # FULL_SHARD on peer memory: "ce" copy engines | "sm" pull kernel
     overlap_grad_reduce: bool = True
     skip_nonfinite: bool = True
 
@@ -335,6 +336,7 @@ class FlatShardedEngine:
         if self.distributed:
             self._sync_initial_params()
         sharded = [u for u in self.units if u.resharded]
+        self._last_resharded = max((i for i, u in enumerate(self.units) if u.resharded), default=-1)
         store = None
         if sharded and self._symm is not None:
             # every unit's bf16 shard in ONE symmetric allocation (peers pull from it), and the gradient slot ring
@@ -424,6 +426,8 @@ class FlatShardedEngine:
     def _unit_post_forward(self, idx: int):
         if self._in_backward:
             return                          # recomputation: the backward of this unit follows immediately
+        if torch.is_grad_enabled() and idx == self._last_resharded:
+            return                          # backward starts with this unit: a re-gather would sit on the critical path
         self._release_params(idx)
 
     def _unit_pre_backward(self, idx: int):
@@ -472,7 +476,7 @@ class FlatShardedEngine:
             if self.is_cuda:
                 if self._symm is not None:
                     from . import fused_comm
-                    fused_comm.gather_pull(self._symm, u.param_shard, buf)
+                    fused_comm.gather_pull(self._symm, u.param_shard, buf, engine=self.cfg.gather_engine)
                 else:
                     dist.all_gather_into_tensor(buf, u.param_shard, group=self.pg)
                 u.gather_event = torch.cuda.Event()
@@ -520,6 +524,14 @@ class FlatShardedEngine:
                 self._release_params(i)
             if fence:
                 self._device_barrier()
+
+    def drop_gathered(self) -> None:
+        """Forget every gathered or in-flight copy of a re-sharded unit (call before the shards are rewritten from
+        outside a `summon_full_params` block: a prefetched copy would otherwise be used with the old values)."""
+        for i, u in enumerate(self.units):
+            if u.resharded and (u.gathered or u.gather_event is not None):
+                self._ensure_gathered(i)
+                self._release_params(i)
 
     def _device_barrier(self):
         from . import fused_comm
@@ -773,6 +785,12 @@ class FlatShardedEngine:
                 if self.step_count == 2:
                     self._symm.mark_warm()
         self.zero_grad()
+        if self.full_shard and self._symm is not None and self.model.training:
+            # the next forward starts with the first re-sharded unit: fetch it now, behind the host-side work between
+            # two steps, instead of in front of that forward
+            first = next((i for i, u in enumerate(self.units) if u.resharded), None)
+            if first is not None:
+                self._start_gather(first)
         return self.last_grad_norm
 
     def check_comm_status(self) -> None:
@@ -838,6 +856,7 @@ class FlatShardedEngine:
                 "param_groups": [dict(g) for g in self.param_groups]}
 
     def load_state_dict(self, sd: dict):
+        self.drop_gathered()
         self.step_count = sd["step"]
         for u in self.units:
             st = sd["units"][u.name]

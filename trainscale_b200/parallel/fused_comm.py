@@ -47,15 +47,22 @@ def all_gather_inplace(heap: SymmetricHeap, flat: torch.Tensor, shard_start: int
     _lib.check(rc, "ts_symm_all_gather")
 
 
-def gather_pull(heap: SymmetricHeap, shard: torch.Tensor, out_full: torch.Tensor, max_blocks: int = 0) -> None:
+def gather_pull(heap: SymmetricHeap, shard: torch.Tensor, out_full: torch.Tensor, max_blocks: int = 0,
+                engine: str = "ce") -> None:
     """out_full = concatenation over ranks of `shard` (a view into symmetric memory, same offset on every rank).
-    One-sided: reads the peers' shards with plain loads and waits for nobody; the caller guarantees that no rank is
-    writing its shard (shards change only inside the optimizer step, between the step's barriers)."""
+    One-sided: reads the peers' shards and waits for nobody; the caller guarantees that no rank is writing its shard
+    (shards change only inside the optimizer step, between the step's barriers).
+    engine "ce": peer-to-peer copies on the copy engines (no SM is used); "sm": a small grid of load/store CTAs."""
     buf, off = heap.lookup(shard)
     nbytes = shard.numel() * shard.element_size()
     if out_full.numel() * out_full.element_size() != nbytes * heap.world:
         raise ValueError("gather_pull: output must hold world x shard")
     lib = _lib.load("comm")
+    if engine == "ce":
+        rc = lib.ts_symm_gather_ce(buf.peer_ptrs, _ll(off), _lib.ptr(out_full), heap.rank, heap.world, _ll(nbytes),
+                                   _lib.stream_ptr())
+        _lib.check(rc, "ts_symm_gather_ce")
+        return
     rc = lib.ts_symm_gather_pull(buf.peer_ptrs, _ll(off), _lib.ptr(out_full), heap.rank, heap.world, _ll(nbytes),
                                  int(max_blocks), _lib.stream_ptr())
     _lib.check(rc, "ts_symm_gather_pull")
