@@ -76,6 +76,12 @@ class NDEngine:
                           max_grad_norm=cfg.optimizer.max_grad_norm, lr=cfg.optimizer.learning_rate,
                           betas=tuple(cfg.optimizer.betas), eps=cfg.optimizer.eps, weight_decay=cfg.optimizer.weight_decay,
                           comm="nccl")
+        fc = dict(cfg.distributed.fsdp_config or {})
+        gd = str(fc.get("grad_dtype", "")).lower()
+        if gd in ("bf16", "bfloat16"):
+            ec.grad_dtype = torch.bfloat16    # halves the gradient buffers; every micro-batch's addition rounds to bf16
+        elif gd in ("fp32", "float32"):
+            ec.grad_dtype = torch.float32
         if self.pipelined and ec.grad_dtype is None:
             ec.grad_dtype = torch.float32     # gradients of several micro-batches accumulate in the buffers
         # gradients are averaged over every rank that saw different tokens of the same weights: dp x cp

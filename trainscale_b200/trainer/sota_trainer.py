@@ -193,7 +193,8 @@ class SOTATrainer:
         if self.config.model.max_position_embeddings:
             cfg.max_position_embeddings = self.config.model.max_position_embeddings
         seed = self.config.training.seed
-        big = cfg.num_parameters() > 2_000_000_000 and self.device.type == "cuda"
+        big = (cfg.num_parameters() > 2_000_000_000 and self.device.type == "cuda") or \
+            os.environ.get("TS_BUILD_LOCAL_SLICE", "0") == "1"
         par = self.config.distributed.parallel
         tp, pp = int(getattr(par, "tp", 1) or 1), int(getattr(par, "pp", 1) or 1)
         if big and self.is_distributed and self.strategy in ("pipeline", "tensor_parallel", "nd") and (tp > 1 or pp > 1):
@@ -317,6 +318,20 @@ class SOTATrainer:
         dims = getattr(self.engine, "dims", None)
         if dims is not None:
             return max(1, dims.size("dp"))
+        return self.world_size
+
+    def data_rank(self) -> int:
+        """Index of the data shard this rank reads: ranks of one model replica (tensor / pipeline / context parallel
+        peers) must see the same samples, so it is the data-parallel coordinate, not the global rank."""
+        dims = getattr(self.engine, "dims", None)
+        return dims.local_rank("dp") if dims is not None else self.rank
+
+    def _token_multiplier(self) -> int:
+        """Whole-job tokens per token of this rank's (sharded) batch: data-parallel replicas, times the context-parallel
+        size (a context-parallel rank holds only its slice of every sequence)."""
+        dims = getattr(self.engine, "dims", None)
+        if dims is not None:
+            return max(1, dims.size("dp")) * (dims.size("cp") if dims.enabled("cp") else 1)
         return self.world_size
 
     def _flops_per_token(self) -> float:
