@@ -88,3 +88,26 @@ def test_lora_moe_fp8_entry_points():
     mgr = K.FP8ScaleManager()
     assert mgr.update("act", torch.tensor([2.0, -4.0])) == 448.0 / 4.0 and mgr.update("act", torch.tensor([1.0])) == 112.0
     assert K.FP8Linear(64, 32, dtype=torch.float32)(x).shape == (8, 32)
+
+
+def test_longrope_uses_its_factor_lists_and_refuses_to_guess():
+    import math
+
+    import pytest
+    import torch
+
+    from trainscale_b200.kernels import RoPEConfig, RoPEFrequencyCache, RoPEScalingType
+    from trainscale_b200.ops import rope
+    half = 32
+    lf = [1.0 + 0.1 * i for i in range(half)]
+    base = rope.rope_inv_freq(64, 10000.0)
+    inv = rope.rope_inv_freq(64, 10000.0, scaling="longrope", original_max_pos=128, max_pos=512, long_factor=lf)
+    assert torch.allclose(inv, base / torch.tensor(lf))
+    with pytest.raises(ValueError):
+        rope.rope_inv_freq(64, 10000.0, scaling="longrope", original_max_pos=128, max_pos=512)
+    cfg = RoPEConfig(dim=64, max_position=512, scaling_type=RoPEScalingType.LONGROPE, original_max_position=128,
+                     longrope_long_factor=lf)
+    cos, _ = RoPEFrequencyCache().get(cfg, 512)
+    m = math.sqrt(1 + math.log(4) / math.log(128))
+    want = torch.outer(torch.arange(512, dtype=torch.float32), base / torch.tensor(lf)).cos() * m
+    assert (cos - want).abs().max() < 1e-3

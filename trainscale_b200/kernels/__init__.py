@@ -12,7 +12,7 @@ from __future__ import annotations
 import math
 from dataclasses import dataclass
 from enum import Enum
-from typing import NamedTuple
+from typing import List, NamedTuple, Optional
 
 import torch
 import torch.nn as nn
@@ -378,6 +378,8 @@ class RoPEConfig:
     scaling_factor: float = 1.0
     original_max_position: int = 8192
     interleaved: bool = False
+    longrope_short_factor: Optional[List[float]] = None
+    longrope_long_factor: Optional[List[float]] = None
 
 
 def precompute_freqs_cis(dim: int, end: int, theta: float = 10000.0, scaling_factor: float = 1.0, device=None):
@@ -397,11 +399,9 @@ class RoPEFrequencyCache:
         cur = self._cache.get(key)
         if cur is None or cur[0].shape[0] < seq_len:
             n = max(seq_len, cfg.max_position)
-            kind = cfg.scaling_type.value if cfg.scaling_type is not RoPEScalingType.LONGROPE else "yarn"
-            inv = _rope.rope_inv_freq(cfg.dim, cfg.theta, scaling=kind, factor=cfg.scaling_factor,
-                                      original_max_pos=cfg.original_max_position, max_pos=n)
-            ang = torch.outer(torch.arange(n, dtype=torch.float32), inv)
-            cur = (ang.cos().to(device).contiguous(), ang.sin().to(device).contiguous())
+            cur = _rope.rope_tables(n, cfg.dim, cfg.theta, device, scaling=cfg.scaling_type.value,
+                                    factor=cfg.scaling_factor, original_max_pos=cfg.original_max_position,
+                                    long_factor=cfg.longrope_long_factor, short_factor=cfg.longrope_short_factor)
             self._cache[key] = cur
         return cur
 

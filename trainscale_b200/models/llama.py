@@ -343,6 +343,8 @@ class LlamaModel(nn.Module):
                           original_max_pos=sc.get("original_max_position_embeddings", 8192),
                           low_freq_factor=sc.get("low_freq_factor", 1.0),
                           high_freq_factor=sc.get("high_freq_factor", 4.0))
+                if str(kind).lower() == "longrope":
+                    kw.update(long_factor=sc.get("long_factor"), short_factor=sc.get("short_factor"))
             cached = rope.rope_tables(n, self.cfg.head_dim, self.cfg.rope_theta, device, **kw)
             self._rope_cache[key] = cached
         return cached

@@ -15,8 +15,13 @@ from . import _lib
 
 def rope_inv_freq(dim: int, theta: float = 10000.0, scaling: str = "none", factor: float = 1.0,
                   original_max_pos: int = 8192, max_pos: int | None = None, beta_fast: float = 32.0,
-                  beta_slow: float = 1.0, low_freq_factor: float = 1.0, high_freq_factor: float = 4.0) -> torch.Tensor:
-    """Inverse frequencies [dim/2] for none | linear | ntk | dynamic_ntk | yarn | llama3 scaling."""
+                  beta_slow: float = 1.0, low_freq_factor: float = 1.0, high_freq_factor: float = 4.0,
+                  long_factor=None, short_factor=None) -> torch.Tensor:
+    """Inverse frequencies [dim/2] for none | linear | ntk | dynamic_ntk | yarn | llama3 | longrope scaling.
+
+    longrope (data_pipeline/trainer/kernels/rope_kernels.py:298-313): every rotary dimension has its own searched
+    rescale factor; `long_factor` applies when the table covers more than `original_max_pos` positions, `short_factor`
+    otherwise (both [dim/2]).  Asking for it without the factor list it needs is an error, not a silent fallback."""
     half = dim // 2
     idx = torch.arange(0, half, dtype=torch.float64)
     scaling = (scaling or "none").lower()
@@ -26,6 +31,18 @@ def rope_inv_freq(dim: int, theta: float = 10000.0, scaling: str = "none", facto
             f = max(1.0, (factor * max_pos / original_max_pos) - (factor - 1))
         theta = theta * f ** (dim / max(dim - 2, 1))
     inv = 1.0 / (theta ** (2 * idx / dim))
+    if scaling == "longrope":
+        use_long = max_pos is not None and max_pos > original_max_pos
+        fac = long_factor if use_long else (short_factor if short_factor is not None else None)
+        if fac is None and not use_long:
+            return inv.float()               # inside the original window without short factors: plain RoPE
+        if fac is None:
+            raise ValueError("rope scaling 'longrope' beyond the original context needs `long_factor` "
+                             f"(a list of {half} per-dimension factors)")
+        fac = torch.as_tensor(fac, dtype=torch.float64).reshape(-1)
+        if fac.numel() < half:
+            raise ValueError(f"longrope factor list has {fac.numel()} entries, the rotary dimension needs {half}")
+        return (inv / fac[:half]).float()
     if scaling == "linear":
         inv = inv / factor
     elif scaling == "yarn":
@@ -46,11 +63,24 @@ def rope_inv_freq(dim: int, theta: float = 10000.0, scaling: str = "none", facto
     return inv.float()
 
 
+def longrope_attention_factor(max_pos: int, original_max_pos: int) -> float:
+    """Magnitude correction LongRoPE applies to cos / sin when the context is extended (sqrt(1 + ln s / ln L0))."""
+    s = max_pos / original_max_pos
+    return 1.0 if s <= 1.0 else math.sqrt(1.0 + math.log(s) / math.log(original_max_pos))
+
+
 def rope_tables(max_pos: int, dim: int, theta: float = 10000.0, device=None, **scaling) -> tuple[torch.Tensor, torch.Tensor]:
     """cos/sin tables, fp32 [max_pos, dim/2]."""
+    attention_factor = scaling.pop("attention_factor", None)
+    if str(scaling.get("scaling", "")).lower() in ("longrope", "dynamic_ntk"):
+        scaling.setdefault("max_pos", max_pos)
     inv = rope_inv_freq(dim, theta, **scaling)
     ang = torch.outer(torch.arange(max_pos, dtype=torch.float32), inv)
-    return ang.cos().to(device).contiguous(), ang.sin().to(device).contiguous()
+    cos, sin = ang.cos(), ang.sin()
+    if str(scaling.get("scaling", "")).lower() == "longrope":
+        m = attention_factor or longrope_attention_factor(max_pos, scaling.get("original_max_pos", 8192))
+        cos, sin = cos * m, sin * m
+    return cos.to(device).contiguous(), sin.to(device).contiguous()
 
 
 def _rope_reference(x, cos, sin, positions, interleaved, sign):
