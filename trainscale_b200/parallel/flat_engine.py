@@ -57,6 +57,7 @@ class EngineConfig:
     comm: str = "auto"                              # auto | fused | nccl
     grad_slots: int = 3                             # FULL_SHARD on peer memory: gradient buffers in the slot ring
     gather_engine: str = "ce"                       # FULL_SHARD on peer memory: "ce" copy engines | "sm" pull kernel
+    reshard_after_forward: bool = True              # FULL_SHARD: False keeps a unit gathered from forward to backward
     overlap_grad_reduce: bool = True
     skip_nonfinite: bool = True
 
@@ -426,8 +427,10 @@ class FlatShardedEngine:
     def _unit_post_forward(self, idx: int):
         if self._in_backward:
             return                          # recomputation: the backward of this unit follows immediately
-        if torch.is_grad_enabled() and idx == self._last_resharded:
-            return                          # backward starts with this unit: a re-gather would sit on the critical path
+        if torch.is_grad_enabled() and (idx == self._last_resharded or not self.cfg.reshard_after_forward):
+            # backward starts with the last unit (a re-gather would sit on the critical path); with
+            # reshard_after_forward off every unit stays gathered until its backward is done
+            return
         self._release_params(idx)
 
     def _unit_pre_backward(self, idx: int):

@@ -295,7 +295,9 @@ class SOTATrainer:
                                                    c.training.gradient_accumulation_steps)),
             max_grad_norm=float(fc.get("gradient_clipping_norm", c.optimizer.max_grad_norm) or 0.0),
             lr=c.optimizer.learning_rate, betas=betas, eps=c.optimizer.eps, weight_decay=c.optimizer.weight_decay,
-            optimizer="lion" if opt_type == "lion" else "adamw", comm=d.comm)
+            optimizer="lion" if opt_type == "lion" else "adamw", comm=d.comm,
+            reshard_after_forward=bool(fc.get("reshard_after_forward", True)),
+            gather_engine=str(fc.get("gather_engine", "ce")))
         c.training.gradient_accumulation_steps = ec.gradient_accumulation_steps
         par = d.parallel
         if self.is_distributed and strat == "fsdp" and int(getattr(par, "dp_replicate", 1) or 1) > 1:
