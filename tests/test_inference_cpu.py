@@ -210,3 +210,15 @@ def test_mixed_adapter_batch_matches_merged_models():
     import pytest
     with pytest.raises(ValueError):
         EngineCore(EngineConfig(model="custom", tokenizer="byte", device="cpu", dtype="float32"), model=m).load_adapters(adapters)
+
+
+def test_tensor_parallel_serving_matches_single_process():
+    import subprocess
+    import sys
+    from pathlib import Path
+    case = Path(__file__).parent / "dist_cases" / "inference_tp.py"
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+           "127.0.0.1", "--master-port", "29695", str(case)]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    assert "RESULT inference tp=2" in r.stdout and "ok=True" in r.stdout

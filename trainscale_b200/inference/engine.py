@@ -207,12 +207,26 @@ class StreamChunk:
 class ModelRunner:
     """Runs the framework decoder over a flattened token batch with a paged KV cache."""
 
-    def __init__(self, model, cache: PagedKVCache, device):
+    def __init__(self, model, cache: PagedKVCache, device, tp=None, use_graphs: bool = False):
+        """`tp`: tensor-parallel context of a model sharded with `shard_model_for_tensor_parallel` (every rank runs
+        the same batch; the attention and MLP outputs are all-reduced).  `use_graphs`: pure decode steps replay a CUDA
+        graph per (padded batch size, block-table width) instead of launching ~12 kernels per layer from Python."""
         self.model, self.cache, self.device = model.eval(), cache, torch.device(device)
         self.cfg = model.config
         self.cuda = self.device.type == "cuda" and next(model.parameters()).dtype == torch.bfloat16
         self.cos, self.sin = model.model.rope_tables(self.device, min(self.cfg.max_position_embeddings, 1 << 16))
         self.lora = None                 # multi_lora.BatchedLoRA when adapters are loaded
+        self.tp = tp if (tp is not None and tp.active) else None
+        ws = self.tp.size if self.tp is not None else 1
+        self.Hq, self.Hkv = self.cfg.num_attention_heads // ws, self.cfg.num_key_value_heads // ws
+        self.use_graphs = bool(use_graphs) and self.cuda
+        self.graphs: dict = {}
+        self.graph_replays = 0
+
+    def _reduce(self, x: torch.Tensor) -> torch.Tensor:
+        if self.tp is not None:
+            torch.distributed.all_reduce(x, group=self.tp.group)
+        return x
 
     def _lin(self, li: int, wname: str, w: torch.Tensor, x: torch.Tensor, adapter_ids) -> torch.Tensor:
         y = gemm.linear(x, w)
@@ -224,7 +238,7 @@ class ModelRunner:
 
     def _write_cache(self, layer: int, qkv2d: torch.Tensor, slots: torch.Tensor) -> None:
         c = self.cfg
-        Hq, Hkv, D = c.num_attention_heads, c.num_key_value_heads, c.head_dim
+        Hq, Hkv, D = self.Hq, self.Hkv, c.head_dim
         kw = Hkv * D
         if self.cuda:
             lib = _lib.load("decode")
@@ -242,14 +256,14 @@ class ModelRunner:
         s = self.cache.seqs[seq_id]
         idx = torch.tensor(s.blocks, device=self.device)
         c = self.cfg
-        k = self.cache.k[layer][idx].reshape(-1, c.num_key_value_heads, c.head_dim)[:s.num_tokens]
-        v = self.cache.v[layer][idx].reshape(-1, c.num_key_value_heads, c.head_dim)[:s.num_tokens]
+        k = self.cache.k[layer][idx].reshape(-1, self.Hkv, c.head_dim)[:s.num_tokens]
+        v = self.cache.v[layer][idx].reshape(-1, self.Hkv, c.head_dim)[:s.num_tokens]
         return k, v
 
     def _attend(self, layer: int, qkv2d: torch.Tensor, seq_ids: list[int], q_lens: list[int], fresh: bool,
-                block_table, seq_lens) -> torch.Tensor:
+                block_table, seq_lens, splits: int | None = None) -> torch.Tensor:
         c = self.cfg
-        Hq, Hkv, D = c.num_attention_heads, c.num_key_value_heads, c.head_dim
+        Hq, Hkv, D = self.Hq, self.Hkv, c.head_dim
         scale = 1.0 / math.sqrt(D)
         T = qkv2d.shape[0]
         if self.cuda and fresh and D in (64, 128):
@@ -260,9 +274,10 @@ class ModelRunner:
             return o.view(T, Hq * D)
         if self.cuda and all(n == 1 for n in q_lens) and D in (64, 128):
             lib = _lib.load("decode")
-            n = len(seq_ids)
+            n = qkv2d.shape[0]
             chunk = 512
-            splits = max(1, -(-int(seq_lens.max().item()) // chunk))
+            if splits is None:       # (a captured decode passes the split count of its block-table width)
+                splits = max(1, -(-int(seq_lens.max().item()) // chunk))
             out = torch.empty(n, Hq * D, dtype=qkv2d.dtype, device=self.device)
             po = torch.empty(n, Hq, splits, D, dtype=torch.float32, device=self.device)
             pl = torch.empty(n, Hq, splits, dtype=torch.float32, device=self.device)
@@ -283,38 +298,111 @@ class ModelRunner:
             off += n
         return torch.cat(outs)
 
-    @torch.no_grad()
-    def forward(self, token_ids: torch.Tensor, positions: torch.Tensor, slots: torch.Tensor, seq_ids: list[int],
-                q_lens: list[int], fresh: bool, adapter_ids: torch.Tensor | None = None) -> torch.Tensor:
-        """token_ids / positions / slots: [T]; returns the hidden state of each sequence's LAST token [n_seq, H].
-        `adapter_ids` [T]: LoRA adapter index of every token (requests with different adapters share the batch)."""
+    def _layers(self, token_ids, pos32, slots, seq_ids, q_lens, fresh, adapter_ids, block_table, seq_lens,
+                splits: int | None = None) -> torch.Tensor:
+        """The decoder over a flattened token batch; returns the final-norm hidden state of every token."""
         m, c = self.model.model, self.cfg
         x = m.embed_tokens(token_ids)
         if getattr(c, "scale_embeddings", False):
             x = x * torch.tensor(c.hidden_size ** 0.5, dtype=x.dtype)
         res = None
-        block_table, seq_lens = self.cache.block_table(seq_ids, self.device)
-        pos32 = positions.to(torch.int32)
         for li, layer in enumerate(m.layers):
+            attn, mlp = getattr(layer.self_attn, "inner", layer.self_attn), getattr(layer.mlp, "inner", layer.mlp)
             h, res = layer.input_layernorm(x, res)
-            qkv = self._lin(li, "wqkv", layer.self_attn.wqkv, h, adapter_ids)
-            if layer.self_attn.bqkv is not None:
-                qkv = qkv + layer.self_attn.bqkv
-            qkv = rope.apply_rope_qkv(qkv.unsqueeze(0), c.num_attention_heads + c.num_key_value_heads, c.head_dim,
-                                      self.cos, self.sin, pos32.unsqueeze(0), qkv.shape[0], 0, c.rope_interleaved)[0]
+            qkv = self._lin(li, "wqkv", attn.wqkv, h, adapter_ids)
+            if attn.bqkv is not None:
+                qkv = qkv + attn.bqkv
+            qkv = rope.apply_rope_qkv(qkv.unsqueeze(0), self.Hq + self.Hkv, c.head_dim, self.cos, self.sin,
+                                      pos32.unsqueeze(0), qkv.shape[0], 0, c.rope_interleaved)[0]
             self._write_cache(li, qkv, slots)
-            a = self._attend(li, qkv, seq_ids, q_lens, fresh, block_table, seq_lens)
-            a = self._lin(li, "wo", layer.self_attn.wo, a, adapter_ids)
+            a = self._attend(li, qkv, seq_ids, q_lens, fresh, block_table, seq_lens, splits)
+            a = self._reduce(self._lin(li, "wo", attn.wo, a, adapter_ids))
             h, res = layer.post_attention_layernorm(a, res)
-            if hasattr(layer.mlp, "router"):            # mixture of experts: the block routes by itself
+            if hasattr(mlp, "router"):            # mixture of experts: the block routes by itself
                 x = layer.mlp(h)
             else:
-                x = self._lin(li, "w_down", layer.mlp.w_down,
-                              activation.glu(self._lin(li, "w_gate_up", layer.mlp.w_gate_up, h, adapter_ids),
-                                             layer.mlp.act), adapter_ids)
+                x = self._reduce(self._lin(li, "w_down", mlp.w_down,
+                                           activation.glu(self._lin(li, "w_gate_up", mlp.w_gate_up, h, adapter_ids),
+                                                          mlp.act), adapter_ids))
         x, _ = m.norm(x, res)
+        return x
+
+    @torch.no_grad()
+    def forward(self, token_ids: torch.Tensor, positions: torch.Tensor, slots: torch.Tensor, seq_ids: list[int],
+                q_lens: list[int], fresh: bool, adapter_ids: torch.Tensor | None = None) -> torch.Tensor:
+        """token_ids / positions / slots: [T]; returns the hidden state of each sequence's LAST token [n_seq, H].
+        `adapter_ids` [T]: LoRA adapter index of every token (requests with different adapters share the batch)."""
+        block_table, seq_lens = self.cache.block_table(seq_ids, self.device)
+        x = self._layers(token_ids, positions.to(torch.int32), slots, seq_ids, q_lens, fresh, adapter_ids, block_table,
+                         seq_lens)
         last = torch.tensor(q_lens, device=self.device).cumsum(0) - 1
         return x[last]
+
+    # ---------------------------------------------------------------- CUDA-graph decode
+    def can_graph(self, q_lens: list[int]) -> bool:
+        c = self.cfg
+        return (self.use_graphs and self.lora is None and all(n == 1 for n in q_lens) and c.head_dim in (64, 128)
+                and getattr(c, "num_local_experts", 0) == 0 and len(q_lens) <= 256)
+
+    @torch.no_grad()
+    def decode_graphed(self, toks: list[int], pos: list[int], slots: list[int], seq_ids: list[int]) -> torch.Tensor:
+        """One decode step (one new token per sequence) replayed from a CUDA graph; returns fp32 logits [n, V].
+        The batch is padded to a power of two with rows that write to / read from the cache's spare block."""
+        n = len(seq_ids)
+        n_pad = 1
+        while n_pad < n:
+            n_pad *= 2
+        bt, sl = self.cache.block_table(seq_ids, None)
+        width = -(-bt.shape[1] // 32) * 32
+        key = (n_pad, width)
+        st = self.graphs.get(key)
+        if st is None:
+            st = self.graphs[key] = self._capture(n_pad, width)
+        bs, trash = self.cache.block_size, self.cache.trash_block
+        h = st["host"]
+        h["tok"].zero_()
+        h["pos"].zero_()
+        h["slots"].fill_(trash * bs)
+        h["sl"].fill_(1)
+        h["bt"].fill_(trash)
+        h["tok"][:n] = torch.tensor(toks)
+        h["pos"][:n] = torch.tensor(pos, dtype=torch.int32)
+        h["slots"][:n] = torch.tensor(slots)
+        h["sl"][:n] = sl
+        h["bt"][:n, :bt.shape[1]] = bt
+        for k in ("tok", "pos", "slots", "sl", "bt"):
+            st[k].copy_(h[k], non_blocking=True)
+        st["graph"].replay()
+        self.graph_replays += 1
+        return st["logits"][:n]
+
+    def _capture(self, n_pad: int, width: int) -> dict:
+        dev = self.device
+        bs, trash = self.cache.block_size, self.cache.trash_block
+        st = {"tok": torch.zeros(n_pad, dtype=torch.long, device=dev),
+              "pos": torch.zeros(n_pad, dtype=torch.int32, device=dev),
+              "slots": torch.full((n_pad,), trash * bs, dtype=torch.long, device=dev),
+              "sl": torch.ones(n_pad, dtype=torch.int32, device=dev),
+              "bt": torch.full((n_pad, width), trash, dtype=torch.int32, device=dev)}
+        st["host"] = {k: torch.empty_like(v, device="cpu").pin_memory() for k, v in st.items()}
+        splits = max(1, -(-(width * bs) // 512))
+        ids = list(range(n_pad))
+
+        def body():
+            x = self._layers(st["tok"], st["pos"], st["slots"], ids, [1] * n_pad, False, None, st["bt"], st["sl"], splits)
+            return self.model.logits(x).float()
+
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            body()                                  # lazy initialisation (library loads, attribute setup) outside capture
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize(dev)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            st["logits"] = body()
+        st["graph"] = g
+        return st
 
     @torch.no_grad()
     def logits(self, hidden: torch.Tensor) -> torch.Tensor:
@@ -361,6 +449,20 @@ class EngineCore:
                 from ..hub import load_pretrained
                 model = load_pretrained(config.model, dtype=dtype, device=self.device)
         self.model = model.to(self.device)
+        # tensor-parallel serving: every rank of the (already initialised) process group runs this engine on the same
+        # requests with its slice of every projection; sampling uses the same seeds, so all ranks emit the same tokens
+        self.tp = None
+        tps = int(config.parallel.tensor_parallel_size or 1)
+        if tps > 1:
+            import torch.distributed as dist
+            from ..parallel import tp as TP
+            if not dist.is_initialized() or dist.get_world_size() != tps:
+                raise ValueError(f"tensor_parallel_size={tps} needs a torch.distributed job of exactly {tps} ranks "
+                                 "(launch the engine under torchrun)")
+            if getattr(self.model, "tp", None) is None:
+                ctx = TP.TPContext.from_group(dist.group.WORLD, sequence_parallel=False, comm="nccl")
+                TP.shard_model_for_tensor_parallel(self.model, ctx)
+            self.tp = self.model.tp
         if tokenizer is None:
             tokenizer = create_tokenizer(name_or_path=config.tokenizer or ("byte" if config.model in PRESETS else config.model),
                                          padding=False, truncation=False)
@@ -369,16 +471,17 @@ class EngineCore:
         cc = config.cache
         nb = cc.num_gpu_blocks
         if nb is None:
-            per_block = 2 * c.num_hidden_layers * cc.block_size * c.num_key_value_heads * c.head_dim * (2 if dtype != torch.float32 else 4)
+            per_block = 2 * c.num_hidden_layers * cc.block_size * (c.num_key_value_heads // tps) * c.head_dim * \
+                (2 if dtype != torch.float32 else 4)
             if self.device.type == "cuda":
                 free, _ = torch.cuda.mem_get_info(self.device)
                 nb = max(64, int(free * cc.gpu_memory_utilization * 0.5) // per_block)
             else:
                 nb = 512
             nb = min(nb, max(64, cc.max_model_len * config.scheduler.max_num_seqs // cc.block_size + 64))
-        self.cache = PagedKVCache(c.num_hidden_layers, nb, cc.block_size, c.num_key_value_heads, c.head_dim, dtype,
+        self.cache = PagedKVCache(c.num_hidden_layers, nb, cc.block_size, c.num_key_value_heads // tps, c.head_dim, dtype,
                                   self.device, cc.enable_prefix_caching)
-        self.runner = ModelRunner(self.model, self.cache, self.device)
+        self.runner = ModelRunner(self.model, self.cache, self.device, tp=self.tp, use_graphs=not config.enforce_eager)
         self.waiting: deque[_Request] = deque()
         self.running: list[_Request] = []
         self.metrics = MetricsAggregator()
@@ -503,9 +606,14 @@ class EngineCore:
             q_lens.append(len(feed))
             fresh &= (start == 0)
         dev = self.device
-        hidden = self.runner.forward(torch.tensor(toks, device=dev), torch.tensor(pos, device=dev),
-                                     torch.tensor(slots, device=dev, dtype=torch.long), seq_ids, q_lens, fresh,
-                                     torch.tensor(ad, device=dev) if lora is not None else None)
+        graphed = self.runner.can_graph(q_lens)
+        if graphed:
+            all_logits = self.runner.decode_graphed(toks, pos, slots, seq_ids)     # [n, V] of every decode row
+            hidden = None
+        else:
+            hidden = self.runner.forward(torch.tensor(toks, device=dev), torch.tensor(pos, device=dev),
+                                         torch.tensor(slots, device=dev, dtype=torch.long), seq_ids, q_lens, fresh,
+                                         torch.tensor(ad, device=dev) if lora is not None else None)
         self.steps += 1
         # 4) sample for every request whose prompt is now complete
         sample_rows, sample_reqs = [], []
@@ -520,7 +628,8 @@ class EngineCore:
                 r.prefilled = start + len(feed)
         if not sample_reqs:
             return []
-        logits = self.runner.logits(hidden[torch.tensor(sample_rows, device=dev)])
+        rows = torch.tensor(sample_rows, device=dev)
+        logits = all_logits[rows] if graphed else self.runner.logits(hidden[rows])
         ps = [r.params for r in sample_reqs]
         logits = apply_penalties(logits, [r.output_ids for r in sample_reqs], [p.repetition_penalty for p in ps],
                                  [p.presence_penalty for p in ps], [p.frequency_penalty for p in ps])
@@ -779,11 +888,25 @@ def create_openai_server(engine: SOTAAsyncStreamEngine, model_name: str = "train
 
 
 # ------------------------------------------------------------------------------------------------ CLI
-def run_bench(engine: SOTAInferenceEngine, num_prompts: int = 50, input_len: int = 128, output_len: int = 128) -> dict:
+def run_bench(engine: SOTAInferenceEngine, num_prompts: int = 50, input_len: int = 128, output_len: int = 128,
+              warmup: bool = True) -> dict:
+    """Offline throughput / latency of the engine on random prompts (all requests arrive at t = 0): TTFT and TPOT
+    percentiles from the per-request metrics, output and total tokens per second over the whole run.  A short warm-up
+    with the same batch shape runs first, so that library loading and CUDA-graph capture are not in the numbers."""
     vocab = min(engine.core.model.config.vocab_size, 255)
     g = torch.Generator().manual_seed(0)
     prompts = [torch.randint(1, vocab, (input_len,), generator=g).tolist() for _ in range(num_prompts)]
     params = GenerationParams(max_tokens=output_len, temperature=0.0, ignore_eos=True)
+    if warmup:
+        wp = GenerationParams(max_tokens=min(8, output_len), temperature=0.0, ignore_eos=True)
+        for p in prompts:
+            engine.core.add_request([t % vocab + 1 for t in p[::-1]], wp)      # other tokens: no prefix-cache hits later
+        while engine.core.has_unfinished():
+            engine.core.step()
+        engine.core.metrics = MetricsAggregator()
+        engine.core.steps = 0
+    if torch.cuda.is_available():
+        torch.cuda.synchronize()
     t0 = time.perf_counter()
     for p in prompts:
         engine.core.add_request(p, params)
@@ -794,8 +917,48 @@ def run_bench(engine: SOTAInferenceEngine, num_prompts: int = 50, input_len: int
     dt = time.perf_counter() - t0
     s = engine.metrics_summary()
     s.update(seconds=dt, output_tokens_per_second=num_prompts * output_len / dt,
-             total_tokens_per_second=num_prompts * (input_len + output_len) / dt, engine_steps=engine.core.steps)
+             total_tokens_per_second=num_prompts * (input_len + output_len) / dt, engine_steps=engine.core.steps,
+             cuda_graph_replays=engine.core.runner.graph_replays, cuda_graphs=len(engine.core.runner.graphs),
+             tensor_parallel_size=engine.core.config.parallel.tensor_parallel_size)
     return s
+
+
+def run_hf_generate_baseline(model_cfg, num_prompts: int, input_len: int, output_len: int, batch_size: int = 64) -> dict:
+    """The same workload through HuggingFace `generate` on a random-init model of the same shape (the path the
+    reference's engine falls back to without vLLM, data_pipeline/trainer/inference.py:2177-2233): bf16, SDPA
+    attention, greedy, static batches of `batch_size` prompts.  TTFT = time of a 1-token generate of a batch
+    (prefill), TPOT = (full generate - prefill) / (output_len - 1)."""
+    from transformers import LlamaConfig as HFConfig, LlamaForCausalLM as HFModel
+    c = model_cfg
+    hf = HFConfig(vocab_size=c.vocab_size, hidden_size=c.hidden_size, intermediate_size=c.intermediate_size,
+                  num_hidden_layers=c.num_hidden_layers, num_attention_heads=c.num_attention_heads,
+                  num_key_value_heads=c.num_key_value_heads, head_dim=c.head_dim, rms_norm_eps=c.rms_norm_eps,
+                  rope_theta=c.rope_theta, max_position_embeddings=max(c.max_position_embeddings, input_len + output_len),
+                  tie_word_embeddings=c.tie_word_embeddings, attn_implementation="sdpa")
+    torch.manual_seed(0)
+    with torch.device("cuda"):
+        m = HFModel(hf).to(torch.bfloat16).eval()
+    vocab = min(c.vocab_size, 255)
+    g = torch.Generator().manual_seed(0)
+    ids = torch.stack([torch.randint(1, vocab, (input_len,), generator=g) for _ in range(num_prompts)]).cuda()
+    kw = dict(do_sample=False, pad_token_id=0, eos_token_id=None)
+    with torch.no_grad():
+        m.generate(ids[:min(batch_size, 4)], max_new_tokens=4, min_new_tokens=4, **kw)     # warm-up
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        m.generate(ids[:batch_size], max_new_tokens=1, min_new_tokens=1, **kw)
+        torch.cuda.synchronize()
+        ttft = time.perf_counter() - t0
+        t0 = time.perf_counter()
+        for s0 in range(0, num_prompts, batch_size):
+            m.generate(ids[s0:s0 + batch_size], max_new_tokens=output_len, min_new_tokens=output_len, **kw)
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+    nb = -(-num_prompts // batch_size)
+    return {"impl": "transformers generate (bf16, sdpa)", "seconds": dt, "batch_size": batch_size,
+            "output_tokens_per_second": num_prompts * output_len / dt,
+            "total_tokens_per_second": num_prompts * (input_len + output_len) / dt,
+            "ttft_first_batch_s": ttft, "tpot_s": max(0.0, dt / nb - ttft) / max(1, output_len - 1)}
 
 
 def main(argv: list[str] | None = None) -> int:
@@ -815,8 +978,27 @@ def main(argv: list[str] | None = None) -> int:
             p.add_argument("--num-prompts", type=int, default=50)
             p.add_argument("--input-len", type=int, default=128)
             p.add_argument("--output-len", type=int, default=128)
+            p.add_argument("--baseline", default=None, choices=["hf"], help="also time transformers generate")
+        p.add_argument("--tensor-parallel-size", type=int, default=1, help="launch under torchrun with this many ranks")
+        p.add_argument("--eager", action="store_true", help="no CUDA graphs in the decode loop")
+        p.add_argument("--max-num-seqs", type=int, default=64)
     a = ap.parse_args(argv)
-    cfg = EngineConfig(model=a.model)
+    cfg = EngineConfig(model=a.model, enforce_eager=a.eager)
+    cfg.parallel.tensor_parallel_size = a.tensor_parallel_size
+    cfg.scheduler.max_num_seqs = a.max_num_seqs
+    rank0 = True
+    if a.tensor_parallel_size > 1:
+        import os
+
+        import torch.distributed as dist
+        local = int(os.environ.get("LOCAL_RANK", "0"))
+        if torch.cuda.is_available():
+            torch.cuda.set_device(local)
+            cfg.device = f"cuda:{local}"
+            dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        else:
+            dist.init_process_group("gloo")
+        rank0 = dist.get_rank() == 0
     if a.cmd == "probe":
         print(json.dumps({"cuda": torch.cuda.is_available(),
                           "device": torch.cuda.get_device_name(0) if torch.cuda.is_available() else "cpu",
@@ -842,6 +1024,14 @@ def main(argv: list[str] | None = None) -> int:
         uvicorn.run(create_openai_server(SOTAAsyncStreamEngine(cfg), a.model), host=a.host, port=a.port)
         return 0
     if a.cmd == "bench":
-        print(json.dumps(run_bench(SOTAInferenceEngine(cfg), a.num_prompts, a.input_len, a.output_len)))
+        eng = SOTAInferenceEngine(cfg)
+        out = run_bench(eng, a.num_prompts, a.input_len, a.output_len)
+        if a.baseline == "hf" and rank0 and torch.cuda.is_available():
+            mcfg = eng.core.model.config
+            del eng
+            torch.cuda.empty_cache()
+            out["baseline"] = run_hf_generate_baseline(mcfg, a.num_prompts, a.input_len, a.output_len, a.max_num_seqs)
+        if rank0:
+            print(json.dumps(out))
         return 0
     return 1

@@ -65,7 +65,10 @@ class PagedKVCache:
                  enable_prefix_caching: bool = True):
         self.block_size, self.num_layers = block_size, num_layers
         self.alloc = BlockAllocator(num_blocks)
-        shape = (num_blocks, block_size, n_kv_heads, head_dim)
+        # one block beyond the allocator's range: padding rows of a fixed-shape (CUDA-graph) decode batch write their
+        # key / value there and read it back as their one-token "sequence"
+        self.trash_block = num_blocks
+        shape = (num_blocks + 1, block_size, n_kv_heads, head_dim)
         self.k = [torch.zeros(shape, dtype=dtype, device=device) for _ in range(num_layers)]
         self.v = [torch.zeros(shape, dtype=dtype, device=device) for _ in range(num_layers)]
         self.seqs: dict[int, SequenceBlocks] = {}
@@ -141,6 +144,8 @@ class PagedKVCache:
             b = self.seqs[i].blocks
             bt[r, :len(b)] = torch.tensor(b, dtype=torch.int32)
         lens = torch.tensor([self.seqs[i].num_tokens for i in seq_ids], dtype=torch.int32)
+        if device is None:
+            return bt, lens
         return bt.to(device), lens.to(device)
 
     def utilization(self) -> float:
