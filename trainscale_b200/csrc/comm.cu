@@ -102,7 +102,7 @@ __global__ void __launch_bounds__(512)
 symm_reduce_scatter_kernel(PeerTable peers, PadTable pads, const void* mc_base, int rank, int world,
                            long long shard_start, long long shard_numel, float* __restrict__ out, float scale,
                            float* __restrict__ sumsq, float* __restrict__ nonfinite, unsigned int slot0,
-                           unsigned int epoch, long long wait_cycles, unsigned int* status) {
+                           unsigned int epoch, long long wait_cycles, unsigned int* status, long long buf_elems) {
   __shared__ float scratch[32];
   __shared__ int s_ok;
   // entry barrier: every rank's gradient buffer is complete before anyone reads it
@@ -122,6 +122,10 @@ symm_reduce_scatter_kernel(PeerTable peers, PadTable pads, const void* mc_base, 
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
     const long long e = shard_start + (i << 3);
     float acc[8];
+    // debug build: the 8 elements must lie inside the symmetric buffer every rank registered (buf_elems of T)
+    if (!TS_IN_BOUNDS(reinterpret_cast<const T*>(peers.ptr[rank]) + e, 8 * sizeof(T), peers.ptr[rank],
+                      static_cast<size_t>(buf_elems) * sizeof(T), 7200))
+      continue;
     if (mc_base) {
       if constexpr (sizeof(T) == 2) {
         multimem_ld_reduce_bf16x8(reinterpret_cast<const T*>(mc_base) + e, acc);
@@ -285,8 +289,9 @@ extern "C" int ts_symm_reduce_scatter(const unsigned long long* peer_ptrs, const
                                       int world, long long shard_start, long long shard_numel, float* out,
                                       float scale, float* sumsq, float* nonfinite, unsigned int slot0,
                                       unsigned int epoch, long long wait_cycles, unsigned int* status, int max_blocks,
-                                      void* stream) {
-  if (world > MAX_WORLD || shard_numel % 8 != 0) return -10;
+                                      long long buf_elems, void* stream) {
+  // buf_elems: elements (of the gradient dtype) from byte_offset to the end of the symmetric allocation
+  if (world > MAX_WORLD || shard_numel % 8 != 0 || shard_start < 0 || shard_start + shard_numel > buf_elems) return -10;
   PeerTable pt; PadTable pd;
   fill_tables(pt, pd, peer_ptrs, pad_ptrs, world, byte_offset);
   const void* mc = mc_ptr ? reinterpret_cast<const void*>(mc_ptr + byte_offset) : nullptr;
@@ -297,11 +302,11 @@ extern "C" int ts_symm_reduce_scatter(const unsigned long long* peer_ptrs, const
   if (is_bf16)
     symm_reduce_scatter_kernel<__nv_bfloat16><<<(unsigned)blocks, 512, 0, ST(stream)>>>(
         pt, pd, mc, rank, world, shard_start, shard_numel, out, scale, sumsq, nonfinite, slot0, epoch, wait_cycles,
-        status);
+        status, buf_elems);
   else
     symm_reduce_scatter_kernel<float><<<(unsigned)blocks, 512, 0, ST(stream)>>>(
         pt, pd, mc, rank, world, shard_start, shard_numel, out, scale, sumsq, nonfinite, slot0, epoch, wait_cycles,
-        status);
+        status, buf_elems);
   return (int)cudaGetLastError();
 }
 

@@ -24,6 +24,7 @@ enum ErrorCode : unsigned int {
   ERR_FLAG_TIMEOUT = 2,      // a global / peer flag wait ran out of cycles
   ERR_BAD_ARGUMENT = 3,      // a launcher rejected its arguments
   ERR_TMEM = 4,              // TMEM allocation failed / returned a bad address
+  ERR_BOUNDS = 5,            // debug build: a store / load would have left the tensor it belongs to (it was skipped)
 };
 
 // One copy per shared library (each .cu of this directory is built as its own library).
@@ -36,6 +37,23 @@ __device__ __forceinline__ void ts_report_error(unsigned int code, unsigned int 
     g_ts_error[3] = extra;
   }
 }
+
+// Debug build (-DTS_DEBUG=1, `TS_DEBUG=1 python -m trainscale_b200.ops.build`): every epilogue store and every
+// peer-memory access is checked against the extent of the tensor it belongs to.  An access outside it is NOT made: the
+// first one is recorded in the error word (code ERR_BOUNDS, the site id, the offending byte offset / 16) and the kernel
+// carries on, so a wrong index shows up as a host-readable status instead of silent corruption or a fault.
+#ifdef TS_DEBUG
+__device__ __forceinline__ bool ts_in_bounds(const void* p, size_t access_bytes, const void* base, size_t extent_bytes,
+                                             unsigned int site) {
+  const uintptr_t a = reinterpret_cast<uintptr_t>(p), b = reinterpret_cast<uintptr_t>(base);
+  if (a >= b && a + access_bytes <= b + extent_bytes) return true;
+  ts_report_error(ERR_BOUNDS, site, static_cast<unsigned int>((a - b) >> 4));
+  return false;
+}
+#define TS_IN_BOUNDS(p, bytes, base, extent, site) ts::ts_in_bounds((p), (bytes), (base), (extent), (site))
+#else
+#define TS_IN_BOUNDS(p, bytes, base, extent, site) (true)
+#endif
 
 #ifndef TS_WAIT_LIMIT_CYCLES
 #define TS_WAIT_LIMIT_CYCLES (4000000000ll)   // about two seconds at B200 clocks

@@ -163,6 +163,7 @@ struct R8Params {
   const float* sa;           // [M]
   const float* sb;           // [N]
   void* C;
+  size_t c_bytes;            // extent of C in bytes (checked per store in the debug build)
   int k_blocks;
 };
 
@@ -181,6 +182,12 @@ __device__ __forceinline__ void umma_f8_ss_2cta(uint32_t d_tmem, uint64_t a_desc
 // 32 accumulator columns of one output row: apply sa[row] * sb[col], optionally add C, convert, store.
 __device__ __forceinline__ void r8_store_chunk(const R8Params& p, const uint32_t* r, size_t row, int col0, float sa) {
   const bool full = (col0 + 32 <= p.N);
+  {
+    const size_t esz = p.out_fp32 ? 4 : 2;
+    const int ncols = full ? 32 : p.N - col0;
+    if (!TS_IN_BOUNDS(static_cast<const char*>(p.C) + (row * p.ldc + col0) * esz, ncols * esz, p.C, p.c_bytes, 7100))
+      return;
+  }
   float v[32];
   if (full && ((reinterpret_cast<uintptr_t>(p.sb + col0) & 15u) == 0)) {
 #pragma unroll
@@ -452,6 +459,7 @@ extern "C" int ts_fp8_rowwise_gemm(const void* A, const float* sa, const void* B
   p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.a_mn = a_mn; p.b_mn = b_mn; p.a_fmt = a_fmt; p.b_fmt = b_fmt;
   p.out_fp32 = out_fp32; p.accumulate = accumulate; p.sa = sa; p.sb = sb; p.C = C;
   p.k_blocks = (K + 127) / 128;
+  p.c_bytes = (static_cast<size_t>(M - 1) * ldc + N) * (out_fp32 ? 4 : 2);
   const int tiles = ((M + 255) / 256) * ((N + 255) / 256);
   int clusters = sm_count() / 2;
   if (tiles < clusters) clusters = tiles;

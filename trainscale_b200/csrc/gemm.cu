@@ -14,6 +14,8 @@
 // Replaces the library GEMMs behind F.linear in the reference
 // (data_pipeline/trainer/distributed/tensor_parallel.py:1061,1214) and the zero-bubble split-backward
 // GEMMs (data_pipeline/trainer/distributed/zbpp.py:202,232).
+#include <stdlib.h>
+
 #include "common.cuh"
 #include "host_common.h"
 
@@ -35,6 +37,7 @@ struct GemmParams {
   int num_m_tiles, num_n_tiles, k_blocks;
   // grouped (mixture-of-experts) modes
   const int* tile_expert;   // MODE 1: expert of every 128-row tile of A / C (-1: tile unused)
+  size_t c_bytes;           // extent of C in bytes (checked per store in the debug build)
   const int* seg_start;     // MODE 2: [E + 1] first row of every expert's (128-aligned) segment along the K axis
   int group_rows;           // MODE 1: rows (K-major B) or K extent (MN-major B) of one expert inside the stacked B
   int num_groups;           // MODE 2: E; C is [E][M][ldc]
@@ -43,6 +46,12 @@ struct GemmParams {
 // 32 consecutive fp32 accumulator columns of one output row: scale, optionally add to C, convert, store.
 __device__ __forceinline__ void gemm_store_chunk(const GemmParams& p, const uint32_t* r, size_t row, int col0) {
   const bool full = (col0 + 32 <= p.N);
+  {
+    const size_t esz = p.out_fp32 ? 4 : 2;
+    const int ncols = full ? 32 : p.N - col0;
+    if (!TS_IN_BOUNDS(static_cast<const char*>(p.C) + (row * p.ldc + col0) * esz, ncols * esz, p.C, p.c_bytes, 7000))
+      return;
+  }
   if (p.out_fp32) {
     float* dst = reinterpret_cast<float*>(p.C) + row * p.ldc + col0;
     if (full && ((reinterpret_cast<uintptr_t>(dst) & 15u) == 0)) {
@@ -572,6 +581,15 @@ extern "C" int ts_gemm_bf16(const void* A, const void* B, void* C, int M, int N,
   p.num_n_tiles = (N + bn - 1) / bn;
   p.k_blocks = (K + GEMM_BK - 1) / GEMM_BK;
   p.tile_expert = nullptr; p.seg_start = nullptr; p.group_rows = 0; p.num_groups = 1;
+  p.c_bytes = (static_cast<size_t>(M - 1) * ldc + N) * (out_fp32 ? 4 : 2);
+#ifdef TS_DEBUG
+  // test hook of the debug build: pretend C ends `TS_DEBUG_SHRINK_C_ROWS` rows early, so that the bounds check (and
+  // nothing else) keeps the kernel from writing them
+  if (const char* e = getenv("TS_DEBUG_SHRINK_C_ROWS")) {
+    const long long cut = atoll(e);
+    if (cut > 0 && cut < M) p.c_bytes = (static_cast<size_t>(M - cut - 1) * ldc + N) * (out_fp32 ? 4 : 2);
+  }
+#endif
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   if (two_cta) return launch_gemm_2cta(tmA, tmB, p, st);
   if (bn == 256) return launch_gemm<256>(tmA, tmB, p, st);
@@ -618,6 +636,8 @@ extern "C" int ts_gemm_grouped_bf16(const void* A, const void* B, void* C, int m
   p.seg_start = (mode == 2) ? groups : nullptr;
   p.group_rows = b_mn ? K : N;
   p.num_groups = num_groups;
+  p.c_bytes = (static_cast<size_t>((mode == 2 ? num_groups : 1)) * M - 1) * ldc * (out_fp32 ? 4 : 2) +
+              static_cast<size_t>(N) * (out_fp32 ? 4 : 2);
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   if (mode == 1) {
     if (bn == 256) return launch_gemm<256, 1>(tmA, tmB, p, st);

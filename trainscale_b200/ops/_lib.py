@@ -12,7 +12,8 @@ import torch
 
 from .build import build_all, lib_path
 
-_ERR_NAMES = {0: "none", 1: "mbarrier wait timed out", 2: "flag wait timed out", 3: "bad argument", 4: "tmem"}
+_ERR_NAMES = {0: "none", 1: "mbarrier wait timed out", 2: "flag wait timed out", 3: "bad argument", 4: "tmem",
+              5: "access outside its tensor (debug build: skipped)"}
 
 
 class KernelError(RuntimeError):

@@ -2,6 +2,11 @@
 
 Each ``csrc/<name>.cu`` becomes ``lib/libts_<name>.so`` (plain ``extern "C"`` entry points, loaded with
 ctypes, no torch headers, so a full rebuild takes seconds).  ``nvcc`` cross-compiles without a GPU.
+
+Debug build: ``TS_DEBUG=1`` selects ``lib_debug/`` (built with ``-DTS_DEBUG=1``): every GEMM epilogue store and every
+peer read of the fused reduce-scatter is checked against the extent of its tensor, an access outside it is skipped and
+recorded in the library's error word (`ops/_lib.raise_on_any_device_error`), and `parallel.symm.SymmetricHeap` puts
+canary words around every symmetric buffer.  Slower; for chasing an indexing bug or a suspected overrun.
 """
 from __future__ import annotations
 
@@ -13,7 +18,8 @@ from pathlib import Path
 
 PKG_DIR = Path(__file__).resolve().parent.parent
 CSRC_DIR = PKG_DIR / "csrc"
-LIB_DIR = PKG_DIR / "lib"
+DEBUG = os.environ.get("TS_DEBUG", "0") == "1"
+LIB_DIR = PKG_DIR / ("lib_debug" if DEBUG else "lib")
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -46,20 +52,23 @@ def _stale(src: Path, out: Path) -> bool:
     return out.stat().st_mtime < newest
 
 
-def build_all(force: bool = False, verbose: bool = False) -> list[Path]:
-    """Compile every stale library; returns the list of library paths. Raises on a compile error."""
+def build_all(force: bool = False, verbose: bool = False, debug: bool | None = None) -> list[Path]:
+    """Compile every stale library; returns the list of library paths. Raises on a compile error.
+    `debug`: build the checked variant into lib_debug/ (default: what TS_DEBUG selected for this process)."""
     nvcc = find_nvcc()
-    LIB_DIR.mkdir(exist_ok=True)
+    debug = DEBUG if debug is None else debug
+    lib_dir = PKG_DIR / ("lib_debug" if debug else "lib")
+    lib_dir.mkdir(exist_ok=True)
     outs = []
     procs = []
     for src in sources():
-        out = lib_path(src.stem)
+        out = lib_dir / f"libts_{src.stem}.so"
         outs.append(out)
         if not force and not _stale(src, out):
             continue
         if nvcc is None:
             raise RuntimeError(f"nvcc not found and {out.name} is missing or stale")
-        cmd = [nvcc, *NVCC_FLAGS, "-o", str(out), str(src)]
+        cmd = [nvcc, *NVCC_FLAGS, *(["-DTS_DEBUG=1"] if debug else []), "-o", str(out), str(src)]
         if verbose:
             cmd.insert(1, "-Xptxas=-v")
             print(" ".join(cmd), file=sys.stderr)

@@ -18,11 +18,14 @@ def reduce_scatter_fp32(heap: SymmetricHeap, flat_grad: torch.Tensor, out_shard:
     """out_shard[i] = scale * sum_r grad_r[shard_start + i]; sumsq += sum(out^2). Reads peers inside the kernel."""
     buf, off = heap.lookup(flat_grad)
     lib = _lib.load("comm")
+    # what is left of the symmetric allocation behind `flat_grad`, in elements: the launcher refuses a shard that would
+    # run past it on this rank or (same layout everywhere) on a peer
+    room = (buf.tensor.numel() * buf.tensor.element_size() - off) // flat_grad.element_size()
     rc = lib.ts_symm_reduce_scatter(buf.peer_ptrs, buf.pad_ptrs, ctypes.c_ulonglong(buf.multicast_ptr), _ll(off),
                                     int(flat_grad.dtype == torch.bfloat16), heap.rank, heap.world, _ll(shard_start),
                                     _ll(out_shard.numel()), _lib.ptr(out_shard), _f(scale), _lib.ptr(sumsq),
                                     _lib.ptr(nonfinite), _u(SLOT_RS), _u(buf.next_epoch("rs")), _ll(heap.wait_cycles),
-                                    _lib.ptr(heap.status), max_blocks, _lib.stream_ptr())
+                                    _lib.ptr(heap.status), max_blocks, _ll(room), _lib.stream_ptr())
     _lib.check(rc, "ts_symm_reduce_scatter")
 
 

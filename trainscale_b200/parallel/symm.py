@@ -73,8 +73,13 @@ class SymmetricHeap:
                 print(f"[trainscale_b200] symmetric memory unavailable ({type(e).__name__}: {e}); using NCCL path")
             return None
 
+    GUARD_BYTES = 256
+    CANARY = 0xC5
+
     def alloc(self, numel: int, dtype: torch.dtype) -> torch.Tensor:
         import torch.distributed._symmetric_memory as symm_mem
+        if os.environ.get("TS_DEBUG", "0") == "1":
+            return self._alloc_guarded(numel, dtype)
         t = symm_mem.empty(numel, dtype=dtype, device=self.device)
         h = symm_mem.rendezvous(t, self.group)
         t.zero_()
@@ -84,6 +89,44 @@ class SymmetricHeap:
         self._by_ptr[t.data_ptr()] = buf
         self.bytes_allocated = getattr(self, "bytes_allocated", 0) + numel * t.element_size()
         return t
+
+    def _alloc_guarded(self, numel: int, dtype: torch.dtype) -> torch.Tensor:
+        """Debug build: the buffer sits between two 256-byte guard zones filled with a canary byte.  The kernels get
+        the addresses of the inner part, so a store that runs past either end of a (local or peer) buffer lands in a
+        guard zone, where `check_canaries` finds it."""
+        import torch.distributed._symmetric_memory as symm_mem
+        esz = torch.empty(0, dtype=dtype).element_size()
+        g = self.GUARD_BYTES
+        nbytes = numel * esz
+        raw = symm_mem.empty(nbytes + 2 * g, dtype=torch.uint8, device=self.device)
+        h = symm_mem.rendezvous(raw, self.group)
+        raw.zero_()
+        raw[:g].fill_(self.CANARY)
+        raw[g + nbytes:].fill_(self.CANARY)
+        t = raw[g:g + nbytes].view(dtype)
+        arr = ctypes.c_ulonglong * self.world
+        mc = int(getattr(h, "multicast_ptr", 0) or 0) if self.use_multicast else 0
+        buf = SymmBuffer(t, h, arr(*[int(p) + g for p in h.buffer_ptrs]), arr(*[int(p) for p in h.signal_pad_ptrs]),
+                         mc + g if mc else 0, {})
+        buf.raw = raw
+        self._by_ptr[t.data_ptr()] = buf
+        self.bytes_allocated = getattr(self, "bytes_allocated", 0) + nbytes + 2 * g
+        return t
+
+    def check_canaries(self) -> None:
+        """Debug build: raises when any guard zone around a symmetric buffer of this rank was written."""
+        bad = []
+        for buf in self._by_ptr.values():
+            raw = getattr(buf, "raw", None)
+            if raw is None:
+                continue
+            g = self.GUARD_BYTES
+            if not (bool((raw[:g] == self.CANARY).all()) and bool((raw[-g:] == self.CANARY).all())):
+                bad.append(hex(buf.tensor.data_ptr()))
+        if bad:
+            from ..core.errors import CommunicationError
+            raise CommunicationError(f"guard zone of symmetric buffer(s) {bad} was overwritten", rank=self.rank,
+                                     world=self.world)
 
     def lookup(self, t: torch.Tensor) -> tuple[SymmBuffer, int]:
         """(buffer, byte offset) of a tensor that is a view into a symmetric allocation."""
