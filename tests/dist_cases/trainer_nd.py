@@ -39,7 +39,7 @@ def make_cfg(strategy, parallel, world, enabled):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--mode", default="pp", choices=["pp", "sp", "cp", "ulysses", "tp_dp", "tp_pp"])
+    ap.add_argument("--mode", default="pp", choices=["pp", "sp", "cp", "ulysses", "tp_dp", "tp_pp", "ep"])
     ap.add_argument("--cuda", action="store_true", help="bf16 on GPUs through the CUDA kernels (fused TP path)")
     a = ap.parse_args()
     if CUDA:
@@ -53,7 +53,8 @@ def main():
     dt = torch.bfloat16 if CUDA else torch.float32
     S = 512 if CUDA else 32
     mcfg = LlamaConfig(vocab_size=256, hidden_size=256 if CUDA else 64, intermediate_size=512 if CUDA else 128,
-                       num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=2, head_dim=64 if CUDA else 16)
+                       num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=2, head_dim=64 if CUDA else 16,
+                       **(dict(num_local_experts=4, num_experts_per_tok=2) if a.mode == "ep" else {}))
     if a.mode == "pp":
         par = {"pp": world, "dp_shard": 1, "pp_schedule": "1f1b", "pp_microbatches": 2}
         strategy, B = "pipeline", 4
@@ -65,6 +66,10 @@ def main():
         # between the stages, one sequence per pipeline micro-batch
         par = {"tp": 2, "pp": world // 2, "dp_shard": 1, "sp": True, "pp_schedule": "1f1b", "pp_microbatches": 2}
         strategy, B = "pipeline", 2
+    elif a.mode == "ep":
+        # data parallel ranks in expert-parallel pairs: each rank keeps 2 of the 4 experts of every layer
+        par = {"ep": 2}
+        strategy, B = "fsdp2", world
     elif a.mode == "tp_dp":
         # tensor parallel pairs x data parallel replicas: the clip must see the norm of the whole model, with the
         # parameters replicated inside a pair (norms, embedding, head) counted once
@@ -97,21 +102,22 @@ def main():
     ok = True
     for step in range(3):
         ids = torch.randint(0, 256, (B, S), generator=g)
-        mine = ids[rank // 2:rank // 2 + 1] if a.mode == "tp_dp" else ids
+        mine = ids[rank // 2:rank // 2 + 1] if a.mode == "tp_dp" else (ids[rank:rank + 1] if a.mode == "ep" else ids)
         l1 = tr.train_step({"input_ids": mine, "labels": mine})
         try:
             dist.is_initialized = lambda: False
             l0 = ref.train_step({"input_ids": ids, "labels": ids})
         finally:
             dist.is_initialized = saved_init
-        if a.mode in ("cp", "ulysses", "tp_dp"):
+        if a.mode in ("cp", "ulysses", "tp_dp", "ep"):
             # every rank reports the mean over ITS tokens; the shards are equal up to the one ignored last label
             t = torch.tensor([l1], device=dev)
             dist.all_reduce(t)
             l1 = float(t) / world
         good = abs(l1 - l0) < (3e-2 if CUDA else 2e-3) * max(1.0, abs(l0))
-        if a.mode == "tp_dp":
-            n1, n0 = float(tr.engine.flat.last_grad_norm), float(ref.engine.last_grad_norm)
+        if a.mode in ("tp_dp", "ep"):
+            n1 = float(tr.engine.flat.last_grad_norm if a.mode == "tp_dp" else tr.engine.last_grad_norm)
+            n0 = float(ref.engine.last_grad_norm)
             good &= abs(n1 - n0) < (3e-2 if CUDA else 1e-3) * max(1.0, n0)
             if rank == 0:
                 print(f"step {step} grad_norm={n1:.5f} oracle={n0:.5f}", flush=True)
@@ -137,7 +143,7 @@ def main():
             good = same_keys and shapes and worst < (6e-2 if CUDA else 2e-3)
             ok &= good
             print(f"checkpoint {d.name}: keys={same_keys} shapes={shapes} max|diff|={worst:.2e} ok={good}", flush=True)
-    own = tr.engine.stage_module if tr.engine.pipelined else tr.model     # a stage trains only its own layers
+    own = tr.engine.stage_module if getattr(tr.engine, "pipelined", False) else tr.model     # a stage trains only its own layers
     before = {n: q.detach().clone() for n, q in own.named_parameters()}
     with torch.no_grad():
         for q in own.parameters():

@@ -124,3 +124,14 @@ def test_pipeline_stages_of_tensor_parallel_pairs_with_sequence_parallelism():
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
     assert "RESULT mode=tp_pp ok=True" in r.stdout
+
+
+def test_expert_parallelism_from_the_config_matches_single_process():
+    """`distributed.parallel.ep: 2` on four gloo ranks (two expert-parallel pairs x two replicas of every expert):
+    losses, the one global gradient norm both engines clip with, the HuggingFace-layout checkpoint (experts gathered)
+    and a resume, against the single-process trainer on the same mixture-of-experts decoder."""
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=4", "--master-addr",
+           "127.0.0.1", "--master-port", "29627", str(ND_CASE), "--mode", "ep"]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    assert "RESULT mode=ep ok=True" in r.stdout

@@ -110,3 +110,10 @@ def test_pipeline_of_tensor_parallel_pairs_on_four_gpus():
     _need(4)
     out = _launch("trainer_nd.py", "--mode", "tp_pp", "--cuda", port=29781, nproc=4)
     assert "RESULT mode=tp_pp ok=True" in out
+
+
+def test_expert_parallel_trainer_on_four_gpus():
+    """`distributed.parallel.ep: 2` through the trainer on the CUDA kernels (grouped expert GEMMs, device-side routing)."""
+    _need(4)
+    out = _launch("trainer_nd.py", "--mode", "ep", "--cuda", port=29782, nproc=4)
+    assert "RESULT mode=ep ok=True" in out

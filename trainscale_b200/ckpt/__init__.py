@@ -135,6 +135,14 @@ def save_training_checkpoint(trainer, path: Path) -> None:
                 if trainer.is_distributed:
                     dist.barrier()
                 save_model_parallel_weights(trainer, path)
+            elif eng is not None and hasattr(eng, "ep_group"):
+                # expert parallelism: every rank takes part in gathering the experts, rank 0 writes
+                from ..hub import ModelSerializer
+                sd = trainer.model.to_hf_state_dict()
+                if rank == 0:
+                    ModelSerializer().save(sd, path)
+                    (path / "config.json").write_text(json.dumps(trainer.model.hf_config_dict(), indent=2))
+                del sd
             elif rank == 0:
                 save_model_weights(trainer.model, path)
         if trainer.is_distributed:

@@ -610,7 +610,14 @@ class LlamaForCausalLM(nn.Module):
             put(attn.wo, [get(p + "self_attn.o_proj.weight", 1)])
             if attn.bqkv is not None:
                 put(attn.bqkv, [get(p + f"self_attn.{n}_proj.bias", 0) for n in "qkv"])
-            if isinstance(mlp, LlamaMoEMLP):
+            if hasattr(mlp, "full_expert_weights"):
+                # expert-parallel block: this rank's experts are a contiguous slice of the stacked expert tensors
+                El, r_ep = mlp.w_gate_up.shape[0], mlp.dispatcher.rank
+                put(mlp.router, [get(p + "mlp.gate.weight")])
+                gu, dn = get(p + "mlp.experts.gate_up_proj"), get(p + "mlp.experts.down_proj")
+                put(mlp.w_gate_up, [None if gu is None else gu[r_ep * El:(r_ep + 1) * El]])
+                put(mlp.w_down, [None if dn is None else dn[r_ep * El:(r_ep + 1) * El]])
+            elif isinstance(mlp, LlamaMoEMLP):
                 put(mlp.router, [get(p + "mlp.gate.weight")])
                 if p + "mlp.experts.gate_up_proj" in sd or p + "mlp.experts.0.w1.weight" not in sd:
                     put(mlp.w_gate_up, [get(p + "mlp.experts.gate_up_proj")])

@@ -12,6 +12,8 @@ slices are exchanged with `all_to_all_single` using exact (not capacity-padded) 
 """
 from __future__ import annotations
 
+import contextlib
+
 import math
 from dataclasses import dataclass
 
@@ -429,3 +431,113 @@ def shard_model_for_expert_parallel(model, group) -> int:
             layer.mlp = ExpertParallelDecoderMoE(layer.mlp, group)
             n += 1
     return n
+
+
+# ------------------------------------------------------------------------------------------------ trainer engine
+class ExpertParallelEngine:
+    """Data parallelism with the decoder's experts sharded over expert-parallel groups, behind the engine surface
+    SOTATrainer drives (`backward`, `step`, `zero_grad`, `param_groups`, `state_dict`, ...).
+
+    `distributed.parallel.ep = k` cuts the W data-parallel ranks into W / k groups of k consecutive ranks; inside a
+    group every rank keeps E / k experts of every mixture-of-experts layer and tokens travel to their experts and
+    back (data_pipeline/trainer/distributed/expert_parallel.py:219-454,1693; mesh keys :1049-1057 of parallel_dims.py).
+    Two flat engines share the model and its autograd graph:
+      dense   every parameter that is replicated on all W ranks (attention, norms, routers, embeddings): reduced over W
+      expert  the expert weights: the W / k ranks that hold the same experts reduce among themselves; a gradient
+              already holds the contributions of the k ranks whose tokens visited the expert, so it is scaled by 1 / k
+              to make the update the gradient of the global mean loss
+    and they clip with ONE norm: dense norm^2 + expert norm^2 summed over the k different expert shards."""
+
+    def __init__(self, model, cfg, ep_size: int, device, sharding: str = "SHARD_GRAD_OP"):
+        import copy as _copy
+
+        from .flat_engine import FlatShardedEngine
+        W, rank = dist.get_world_size(), dist.get_rank()
+        if W % ep_size:
+            raise ValueError(f"expert-parallel size {ep_size} must divide the data-parallel size {W}")
+        self.ep_size = ep_size
+        self.ep_group = self.edp_group = None
+        for g in range(W // ep_size):            # every rank creates every group, in the same order
+            grp = dist.new_group(list(range(g * ep_size, (g + 1) * ep_size)))
+            if rank // ep_size == g:
+                self.ep_group = grp
+        for j in range(ep_size):
+            grp = dist.new_group(list(range(j, W, ep_size)))
+            if rank % ep_size == j:
+                self.edp_group = grp
+        self.converted = shard_model_for_expert_parallel(model, self.ep_group)
+        if self.converted == 0:
+            raise ValueError("distributed.parallel.ep > 1 but the model has no mixture-of-experts layer")
+        expert_ids = {id(p) for p in model.parameters() if getattr(p, "expert_parallel", False)}
+        dense_cfg = _copy.copy(cfg)
+        dense_cfg.sharding_strategy = sharding if sharding != "FULL_SHARD" else "SHARD_GRAD_OP"
+        self.dense = FlatShardedEngine(model, dense_cfg, device=device, param_filter=lambda p: id(p) not in expert_ids)
+        exp_cfg = _copy.copy(cfg)
+        exp_cfg.sharding_strategy, exp_cfg.comm, exp_cfg.grad_mul = dense_cfg.sharding_strategy, "nccl", 1.0 / ep_size
+        self.expert = FlatShardedEngine(model, exp_cfg, process_group=self.edp_group, device=device,
+                                        solo=W // ep_size == 1, param_filter=lambda p: id(p) in expert_ids)
+        self.param_groups = self.dense.param_groups
+        self.cfg = dense_cfg
+        self.model = model
+
+    @property
+    def micro_step(self):
+        return self.dense.micro_step
+
+    @micro_step.setter
+    def micro_step(self, v):
+        self.dense.micro_step = self.expert.micro_step = v
+
+    @property
+    def units(self):
+        return self.dense.units + self.expert.units
+
+    @property
+    def last_grad_norm(self):
+        return self.dense.last_grad_norm
+
+    def backward(self, loss):
+        sync = self.dense.backward(loss)       # one backward over the shared graph; both engines' hooks fire in it
+        self.expert.after_backward()
+        return sync
+
+    def step(self, lr=None):
+        d, e = self.dense, self.expert
+        e.param_groups[0].update(d.param_groups[0])
+        d.reduce_and_norm()
+        e.reduce_and_norm()
+        ex = e.norm_sq.clone()
+        nf = e.nonfinite.clone()
+        dist.all_reduce(ex, group=self.ep_group)                     # the k ranks of a group hold different experts
+        dist.all_reduce(nf, op=dist.ReduceOp.MAX, group=self.ep_group)
+        total = d.norm_sq + ex
+        flag = torch.maximum(d.nonfinite, nf)
+        for eng in (d, e):
+            eng.norm_sq.copy_(total)
+            eng.nonfinite.copy_(flag)
+        gn = d.apply_update(lr)
+        e.apply_update(lr)
+        return gn
+
+    def zero_grad(self):
+        self.dense.zero_grad()
+        self.expert.zero_grad()
+
+    def check_comm_status(self):
+        self.dense.check_comm_status()
+        self.expert.check_comm_status()
+
+    @contextlib.contextmanager
+    def summon_full_params(self):
+        with self.dense.summon_full_params(), self.expert.summon_full_params():
+            yield
+
+    def state_dict(self):
+        return {"dense": self.dense.state_dict(), "expert": self.expert.state_dict(), "ep_size": self.ep_size}
+
+    def load_state_dict(self, sd):
+        self.dense.load_state_dict(sd["dense"])
+        self.expert.load_state_dict(sd["expert"])
+
+    def memory_summary(self):
+        return f"ep={self.ep_size} | dense: {self.dense.memory_summary()} | experts: {self.expert.memory_summary()}"

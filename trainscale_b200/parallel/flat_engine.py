@@ -58,6 +58,7 @@ class EngineConfig:
     grad_slots: int = 3                             # FULL_SHARD on peer memory: gradient buffers in the slot ring
     gather_engine: str = "ce"                       # FULL_SHARD on peer memory: "ce" copy engines | "sm" pull kernel
     reshard_after_forward: bool = True              # FULL_SHARD: False keeps a unit gathered from forward to backward
+    grad_mul: float = 1.0                           # extra factor on every reduced gradient (expert parallelism: 1/ep)
     overlap_grad_reduce: bool = True
     skip_nonfinite: bool = True
 
@@ -261,9 +262,11 @@ class FlatShardedEngine:
 
     def __init__(self, model: nn.Module, cfg: EngineConfig, process_group=None, device=None,
                  unit_modules: list[tuple[str, nn.Module]] | None = None, solo: bool = False,
-                 replicate_group=None, frozen: bool = False):
+                 replicate_group=None, frozen: bool = False, param_filter: Callable | None = None):
         """`frozen`: hold the model's parameters only (sharded and re-gathered unit by unit like a trained model's, but
         with no gradient buffers and no optimizer state): the frozen reference model of preference training.
+        `param_filter(p) -> bool`: manage only these parameters of `model` (a second engine with another process
+        group takes the rest: expert weights under expert parallelism).
         `solo`: this rank shares its parameters with nobody (a data-parallel group of one inside a larger job,
         e.g. pure pipeline or tensor parallelism): no collective is ever issued.
         `replicate_group`: hybrid sharding - `process_group` is the shard group (inside a node, say) and the ranks of
@@ -310,7 +313,8 @@ class FlatShardedEngine:
         self.units: list[FlatUnit] = []
         self._unit_of_module: dict[int, int] = {}
         for name, mod in unit_modules:
-            named = [(f"{name}.{n}" if name else n, p) for n, p in mod.named_parameters() if id(p) not in seen]
+            named = [(f"{name}.{n}" if name else n, p) for n, p in mod.named_parameters()
+                     if id(p) not in seen and (param_filter is None or param_filter(p))]
             if not named:
                 continue
             seen.update(id(p) for _, p in named)
@@ -321,7 +325,8 @@ class FlatShardedEngine:
             self.units.append(FlatUnit(name or "root", named, cfg, self.rank, self.world, self.device, gd,
                                        None if (resharded or frozen) else self._alloc_fn(), resharded=resharded,
                                        frozen=frozen))
-        rest = [(n, p) for n, p in model.named_parameters() if id(p) not in seen]
+        rest = [(n, p) for n, p in model.named_parameters()
+                if id(p) not in seen and (param_filter is None or param_filter(p))]
         if rest:
             self.units.append(FlatUnit("root", rest, cfg, self.rank, self.world, self.device, torch.float32,
                                        None if frozen else self._alloc_fn(), frozen=frozen))
@@ -575,6 +580,11 @@ class FlatShardedEngine:
             loss.backward()
         finally:
             self._in_backward = False
+        return self.after_backward()
+
+    def after_backward(self) -> bool:
+        """What follows `loss.backward()` (a second engine that shares the autograd graph calls only this)."""
+        self._in_backward = False
         for u in self._deferred_reduce:
             self._launch_reduce(u)
         self._deferred_reduce.clear()
@@ -708,9 +718,14 @@ class FlatShardedEngine:
     def step(self, lr: float | None = None) -> torch.Tensor:
         """Reduce what is not reduced yet, clip by global norm, update, re-gather. Returns the grad norm
         as a device tensor (reading it is the caller's choice; nothing here synchronises the host)."""
+        self.reduce_and_norm()
+        return self.apply_update(lr)
+
+    def reduce_and_norm(self) -> torch.Tensor:
+        """First half of `step`: finish the gradient reduction and leave the squared global gradient norm of THIS
+        engine's parameters in `self.norm_sq` (and the skip flag in `self.nonfinite`).  Engines that share one model
+        (dense + expert parameters) add their norms between the two halves so that both clip with the same factor."""
         cfg = self.cfg
-        if lr is None:
-            lr = self.param_groups[0]["lr"]
         cur = torch.cuda.current_stream() if self.is_cuda else None
         fused_norm = self._symm is not None and self.world > 1 and cfg.sharding_strategy != "NO_SHARD"
         if self.world == 1:
@@ -728,7 +743,7 @@ class FlatShardedEngine:
             self.nonfinite.zero_()
         for u in self.units:
             if not (fused_norm and getattr(u, "norm_in_reduce", False)):
-                optim_ops.sumsq_(self.norm_sq, self._shard_grad_view(u), self.nonfinite)
+                optim_ops.sumsq_(self.norm_sq, self._shard_grad_view(u), self.nonfinite, cfg.grad_mul)
         if self._symm is not None:
             # a fused collective that gave up waiting for a peer left its output unwritten: the update is skipped
             # on every rank (the flag joins the non-finite word, reduced with MAX below); the host learns of it
@@ -751,6 +766,14 @@ class FlatShardedEngine:
             # of the whole model
             dist.all_reduce(self.norm_sq, group=g)
             dist.all_reduce(self.nonfinite, op=dist.ReduceOp.MAX, group=g)
+        return self.norm_sq
+
+    def apply_update(self, lr: float | None = None) -> torch.Tensor:
+        """Second half of `step`: clip with `self.norm_sq`, update this rank's shard, publish the new parameters."""
+        cfg = self.cfg
+        if lr is None:
+            lr = self.param_groups[0]["lr"]
+        fused_norm = self._symm is not None and self.world > 1 and cfg.sharding_strategy != "NO_SHARD"
         self.last_grad_norm = self.norm_sq.sqrt()
         self.step_count += 1
         b1, b2 = self.param_groups[0]["betas"]
@@ -771,12 +794,12 @@ class FlatShardedEngine:
                     continue
                 if cfg.optimizer == "lion":
                     optim_ops.lion_flat_(u.master[sl], u.exp_avg[sl], g[sl], out, lr=lr, beta1=b1, beta2=b2,
-                                         weight_decay=seg.weight_decay)
+                                         weight_decay=seg.weight_decay, grad_mul=cfg.grad_mul)
                 else:
                     optim_ops.adamw_flat_(u.master[sl], u.exp_avg[sl], u.exp_avg_sq[sl], g[sl], out, lr=lr, beta1=b1,
                                           beta2=b2, eps=self.param_groups[0]["eps"], weight_decay=seg.weight_decay,
-                                          step=self.step_count, sumsq=self.norm_sq, max_norm=cfg.max_grad_norm,
-                                          skip_flag=skip)
+                                          step=self.step_count, grad_mul=cfg.grad_mul, sumsq=self.norm_sq,
+                                          max_norm=cfg.max_grad_norm, skip_flag=skip)
         if self.world > 1 and cfg.sharding_strategy != "NO_SHARD":
             if not (fused_norm and cfg.optimizer == "adamw"):
                 self._all_gather_params()

@@ -248,7 +248,13 @@ class SOTATrainer:
             # parameters at its flat buffers
             import copy
             ref_model = copy.deepcopy(self.model).eval()
-        if strat in ("single", "ddp", "fsdp") and all(p.requires_grad for p in self.model.parameters()) \
+        ep = int(getattr(d.parallel, "ep", 1) or 1)
+        if ep > 1 and self.is_distributed and strat in ("ddp", "fsdp") and self._flat_engine_ok():
+            # expert parallelism inside data parallelism: experts sharded over groups of `ep` ranks
+            from ..parallel.ep import ExpertParallelEngine
+            proto = self._build_flat_engine_config(strat)
+            self.engine = ExpertParallelEngine(self.model, proto, ep, self.device, proto.sharding_strategy)
+        elif strat in ("single", "ddp", "fsdp") and all(p.requires_grad for p in self.model.parameters()) \
                 and self._flat_engine_ok():
             self.engine = self._build_flat_engine(strat)
             if ref_model is not None:
@@ -277,9 +283,8 @@ class SOTATrainer:
         t = getattr(self.config.optimizer.type, "value", self.config.optimizer.type)
         return t in ("adamw", "fused_adamw", "lion")
 
-    def _build_flat_engine(self, strat: str, model: nn.Module | None = None, frozen: bool = False) -> FlatShardedEngine:
+    def _build_flat_engine_config(self, strat: str) -> EngineConfig:
         c, d = self.config, self.config.distributed
-        model = self.model if model is None else model
         fc = dict(d.fsdp_config or {})
         if strat == "ddp":
             sharding = "NO_SHARD"
@@ -299,6 +304,12 @@ class SOTATrainer:
             reshard_after_forward=bool(fc.get("reshard_after_forward", True)),
             gather_engine=str(fc.get("gather_engine", "ce")))
         c.training.gradient_accumulation_steps = ec.gradient_accumulation_steps
+        return ec
+
+    def _build_flat_engine(self, strat: str, model: nn.Module | None = None, frozen: bool = False) -> FlatShardedEngine:
+        d = self.config.distributed
+        model = self.model if model is None else model
+        ec = self._build_flat_engine_config(strat)
         par = d.parallel
         if self.is_distributed and strat == "fsdp" and int(getattr(par, "dp_replicate", 1) or 1) > 1:
             # hybrid sharding: shard inside groups of world / dp_replicate ranks, replicate across them
@@ -739,9 +750,13 @@ class SOTATrainer:
         summon = eng.summon_full_params() if eng is not None and hasattr(eng, "summon_full_params") \
             else contextlib.nullcontext()
         with summon:       # FULL_SHARD keeps only shards between steps; every rank materialises, rank 0 writes
+            model = self.model
+            if eng is not None and hasattr(eng, "ep_group"):
+                # expert parallelism: gathering the experts is a collective of every rank; rank 0 writes the result
+                model = _GatheredWeights(self.model, self.model.to_hf_state_dict())
             if not self.is_main:
                 return None
-            return export_model(self.model, out, fmt, tokenizer=tokenizer, merge_lora=e.merge_lora)
+            return export_model(model, out, fmt, tokenizer=tokenizer, merge_lora=e.merge_lora)
 
     def cleanup(self) -> None:
         self.engine = None
@@ -753,6 +768,22 @@ class SOTATrainer:
         if self._own_pg and dist.is_initialized():
             dist.destroy_process_group()
             self._own_pg = False
+
+
+class _GatheredWeights:
+    """Stands in for a model whose full state dict has already been assembled (by a collective of all ranks)."""
+
+    def __init__(self, model, state_dict):
+        self._model, self._sd = model, state_dict
+
+    def to_hf_state_dict(self):
+        return self._sd
+
+    def hf_config_dict(self):
+        return self._model.hf_config_dict()
+
+    def named_parameters(self):
+        return self._model.named_parameters()
 
 
 def create_trainer(config: str | os.PathLike | dict | SOTAConfig, **kw) -> SOTATrainer:
