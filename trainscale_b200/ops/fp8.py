@@ -197,6 +197,32 @@ def dequant_rowwise(q: torch.Tensor, s: torch.Tensor, axis: int) -> torch.Tensor
     return q.float() * (s.view(-1, 1) if axis == 0 else s.view(1, -1))
 
 
+# Weights change only in the optimizer step, but a step quantises each of them once per forward (row scales) and once
+# per backward (column scales) of every micro-batch.  The engines bump WEIGHT_EPOCH when they update (or reload) the
+# parameters; inside one epoch both quantised copies of a weight are made once and reused.  (The optimizer kernels write
+# through raw pointers, so torch's own version counter cannot be the key.)
+WEIGHT_EPOCH = [0]
+_W_CACHE: dict = {}
+
+
+def bump_weight_epoch() -> None:
+    WEIGHT_EPOCH[0] += 1
+    _W_CACHE.clear()
+
+
+def _quant_weight(w: torch.Tensor):
+    """(row-scaled copy, row scales, column-scaled copy, column scales) of a weight, cached per weight epoch."""
+    import weakref
+    key = (id(w), w._version)       # (a re-gathered ZeRO-3 weight keeps its identity and its values inside an epoch)
+    hit = _W_CACHE.get(key)
+    if hit is not None and hit[0] == WEIGHT_EPOCH[0] and hit[2]() is w:
+        return hit[1]
+    wq, sw = quant_rowwise(w)
+    wc, swc = quant_colwise(w)
+    _W_CACHE[key] = (WEIGHT_EPOCH[0], (wq, sw, wc, swc), weakref.ref(w))
+    return wq, sw, wc, swc
+
+
 class _FP8RowwiseLinearFn(torch.autograd.Function):
     """y = x @ w^T with all three GEMMs in fp8.  Saved for backward: the column-scaled fp8 copy of x (half the bytes
     of the bf16 activation) and the weight."""
@@ -207,7 +233,10 @@ class _FP8RowwiseLinearFn(torch.autograd.Function):
         T, K = x2.shape
         N = w.shape[0]
         xq, sx = quant_rowwise(x2)
-        wq, sw = quant_rowwise(w)
+        if w.requires_grad:
+            wq, sw, _, _ = _quant_weight(w)
+        else:
+            wq, sw = quant_rowwise(w)
         y = gemm_rowwise(xq, sx, wq, sw, T, N, K)
         need_dw = w.requires_grad
         if need_dw:
@@ -227,7 +256,7 @@ class _FP8RowwiseLinearFn(torch.autograd.Function):
         dx = dw = None
         if ctx.needs_input_grad[0]:
             dq, sd = quant_rowwise(dy2, ctx.grad_fmt)    # scales per token
-            wc, swc = quant_colwise(w)                   # scales per input feature k; stored [N][K] = MN-major B
+            _, _, wc, swc = _quant_weight(w)             # scales per input feature k; stored [N][K] = MN-major B
             dx = gemm_rowwise(dq, sd, wc, swc, T, K, N, b_mn=True).view(ctx.x_shape)
         if ctx.needs_input_grad[1]:
             dc, sdc = quant_colwise(dy2, ctx.grad_fmt)   # scales per output feature n, over all tokens

@@ -776,6 +776,9 @@ class FlatShardedEngine:
         fused_norm = self._symm is not None and self.world > 1 and cfg.sharding_strategy != "NO_SHARD"
         self.last_grad_norm = self.norm_sq.sqrt()
         self.step_count += 1
+        if self.is_cuda:
+            from ..ops import fp8 as fp8_ops
+            fp8_ops.bump_weight_epoch()        # quantised copies of the weights are stale from here on
         b1, b2 = self.param_groups[0]["betas"]
         skip = self.nonfinite if cfg.skip_nonfinite else None
         for u in self.units:
@@ -883,6 +886,9 @@ class FlatShardedEngine:
 
     def load_state_dict(self, sd: dict):
         self.drop_gathered()
+        if self.is_cuda:
+            from ..ops import fp8 as fp8_ops
+            fp8_ops.bump_weight_epoch()
         self.step_count = sd["step"]
         for u in self.units:
             st = sd["units"][u.name]
