@@ -203,11 +203,16 @@ def dequant_rowwise(q: torch.Tensor, s: torch.Tensor, axis: int) -> torch.Tensor
 # through raw pointers, so torch's own version counter cannot be the key.)
 WEIGHT_EPOCH = [0]
 _W_CACHE: dict = {}
+_W_CACHE_BYTES = [0]
+# the two fp8 copies take as many bytes as the bf16 weight itself: the cache stops growing at this size (the weights
+# that do not fit are simply re-quantised on every use)
+W_CACHE_LIMIT_BYTES = int(float(__import__("os").environ.get("TS_FP8_WEIGHT_CACHE_GB", "8")) * 2 ** 30)
 
 
 def bump_weight_epoch() -> None:
     WEIGHT_EPOCH[0] += 1
     _W_CACHE.clear()
+    _W_CACHE_BYTES[0] = 0
 
 
 def _quant_weight(w: torch.Tensor):
@@ -219,7 +224,9 @@ def _quant_weight(w: torch.Tensor):
         return hit[1]
     wq, sw = quant_rowwise(w)
     wc, swc = quant_colwise(w)
-    _W_CACHE[key] = (WEIGHT_EPOCH[0], (wq, sw, wc, swc), weakref.ref(w))
+    if _W_CACHE_BYTES[0] + 2 * w.numel() <= W_CACHE_LIMIT_BYTES:
+        _W_CACHE[key] = (WEIGHT_EPOCH[0], (wq, sw, wc, swc), weakref.ref(w))
+        _W_CACHE_BYTES[0] += 2 * w.numel()
     return wq, sw, wc, swc
 
 
