@@ -215,19 +215,23 @@ def bump_weight_epoch() -> None:
     _W_CACHE_BYTES[0] = 0
 
 
-def _quant_weight(w: torch.Tensor):
-    """(row-scaled copy, row scales, column-scaled copy, column scales) of a weight, cached per weight epoch."""
+def _quant_weight(w: torch.Tensor, which: str):
+    """Row-scaled (`which` "row": forward) or column-scaled ("col": dgrad) fp8 copy of a weight and its scales.  Both
+    copies are made together and cached per weight epoch while the cache has room; beyond that only the requested one
+    is made."""
     import weakref
     key = (id(w), w._version)       # (a re-gathered ZeRO-3 weight keeps its identity and its values inside an epoch)
     hit = _W_CACHE.get(key)
     if hit is not None and hit[0] == WEIGHT_EPOCH[0] and hit[2]() is w:
-        return hit[1]
+        wq, sw, wc, swc = hit[1]
+        return (wq, sw) if which == "row" else (wc, swc)
+    if _W_CACHE_BYTES[0] + 2 * w.numel() > W_CACHE_LIMIT_BYTES:
+        return quant_rowwise(w) if which == "row" else quant_colwise(w)
     wq, sw = quant_rowwise(w)
     wc, swc = quant_colwise(w)
-    if _W_CACHE_BYTES[0] + 2 * w.numel() <= W_CACHE_LIMIT_BYTES:
-        _W_CACHE[key] = (WEIGHT_EPOCH[0], (wq, sw, wc, swc), weakref.ref(w))
-        _W_CACHE_BYTES[0] += 2 * w.numel()
-    return wq, sw, wc, swc
+    _W_CACHE[key] = (WEIGHT_EPOCH[0], (wq, sw, wc, swc), weakref.ref(w))
+    _W_CACHE_BYTES[0] += 2 * w.numel()
+    return (wq, sw) if which == "row" else (wc, swc)
 
 
 class _FP8RowwiseLinearFn(torch.autograd.Function):
@@ -240,10 +244,7 @@ class _FP8RowwiseLinearFn(torch.autograd.Function):
         T, K = x2.shape
         N = w.shape[0]
         xq, sx = quant_rowwise(x2)
-        if w.requires_grad:
-            wq, sw, _, _ = _quant_weight(w)
-        else:
-            wq, sw = quant_rowwise(w)
+        wq, sw = _quant_weight(w, "row") if w.requires_grad else quant_rowwise(w)
         y = gemm_rowwise(xq, sx, wq, sw, T, N, K)
         need_dw = w.requires_grad
         if need_dw:
@@ -263,7 +264,7 @@ class _FP8RowwiseLinearFn(torch.autograd.Function):
         dx = dw = None
         if ctx.needs_input_grad[0]:
             dq, sd = quant_rowwise(dy2, ctx.grad_fmt)    # scales per token
-            _, _, wc, swc = _quant_weight(w)             # scales per input feature k; stored [N][K] = MN-major B
+            wc, swc = _quant_weight(w, "col")            # scales per input feature k; stored [N][K] = MN-major B
             dx = gemm_rowwise(dq, sd, wc, swc, T, K, N, b_mn=True).view(ctx.x_shape)
         if ctx.needs_input_grad[1]:
             dc, sdc = quant_colwise(dy2, ctx.grad_fmt)   # scales per output feature n, over all tokens
