@@ -214,6 +214,71 @@ def bench_fp8_rowwise(t, small):
     return out
 
 
+def bench_comm(t, small):
+    """The fused collective kernels of csrc/comm.cu on symmetric memory.  Under torchrun (one rank per GPU) the peer
+    traffic crosses NVLink and the rates are per-GPU NVLink rates; in a single process the only "peer" is this GPU, so
+    the same kernels run against local HBM (what an ncu capture of one GPU can show).  Bytes counted: reduce-scatter
+    reads W shards of the gradient dtype and writes one fp32 shard; AdamW + broadcast reads 4 fp32 streams, writes 3 and
+    stores W bf16 copies; the gather moves W - 1 remote shards (W = 1: one local copy)."""
+    import torch.distributed as dist
+
+    from .parallel import fused_comm
+    from .parallel.symm import SymmetricHeap
+    own = False
+    if not dist.is_initialized():
+        import os
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29555")
+        dist.init_process_group("nccl", rank=0, world_size=1, device_id=torch.device("cuda", torch.cuda.current_device()))
+        own = True
+    W, rank = dist.get_world_size(), dist.get_rank()
+    dev = torch.device("cuda", torch.cuda.current_device())
+    heap = SymmetricHeap.try_create(None, dev)
+    out = []
+    if heap is None:
+        return out
+    n = (1 << 26 if small else 1 << 28) // W * W            # bf16 elements of one layer-sized gradient buffer
+    shard = n // W
+    grad = heap.alloc(n, torch.bfloat16)
+    grad.normal_()
+    param = heap.alloc(n, torch.bfloat16)
+    red = torch.empty(shard, dtype=torch.float32, device=dev)
+    ss, nf = torch.zeros(1, device=dev), torch.zeros(1, device=dev)
+    master, m, v = (torch.zeros(shard, dtype=torch.float32, device=dev) for _ in range(3))
+    full = torch.empty(n, dtype=torch.bfloat16, device=dev)
+    store = heap.alloc(shard, torch.bfloat16)
+
+    def timed(fn):
+        ms = t(fn, iters=5)
+        x = torch.tensor([ms], device=dev)
+        if W > 1:
+            dist.all_reduce(x, op=dist.ReduceOp.MAX)       # multi-GPU numbers are the maximum over ranks
+        return float(x)
+    ms = timed(lambda: fused_comm.reduce_scatter_fp32(heap, grad, red, rank * shard, 1.0 / W, ss, nf))
+    out.append(dict(name=f"symm_reduce_scatter W={W} n={n}", ms=ms, baseline_ms=None,
+                    gbs=(W * shard * 2 + shard * 4) / ms / 1e6, nvlink_gbs=((W - 1) * shard * 2) / ms / 1e6))
+    ms = timed(lambda: fused_comm.adamw_bcast(heap, param, rank * shard, master, m, v, red, lr=1e-4, beta1=0.9,
+                                              beta2=0.95, eps=1e-8, weight_decay=0.0, step=1))
+    out.append(dict(name=f"symm_adamw_bcast W={W} n={n}", ms=ms, baseline_ms=None,
+                    gbs=(shard * 4 * 7 + W * shard * 2) / ms / 1e6, nvlink_gbs=((W - 1) * shard * 2) / ms / 1e6))
+    for eng in ("ce", "sm"):
+        ms = timed(lambda: fused_comm.gather_pull(heap, store, full, engine=eng))
+        out.append(dict(name=f"gather_pull[{eng}] W={W} n={n}", ms=ms, baseline_ms=None,
+                        gbs=2 * n * 2 / ms / 1e6, nvlink_gbs=((W - 1) * shard * 2) / ms / 1e6))
+    if W > 1:
+        ms = timed(lambda: dist.reduce_scatter_tensor(full[:shard], grad, op=dist.ReduceOp.AVG))
+        out.append(dict(name=f"nccl reduce_scatter W={W} n={n}", ms=ms, baseline_ms=None,
+                        gbs=(W * shard * 2 + shard * 2) / ms / 1e6, nvlink_gbs=((W - 1) * shard * 2) / ms / 1e6))
+        ms = timed(lambda: dist.all_gather_into_tensor(full, store))
+        out.append(dict(name=f"nccl all_gather W={W} n={n}", ms=ms, baseline_ms=None, gbs=2 * n * 2 / ms / 1e6,
+                        nvlink_gbs=((W - 1) * shard * 2) / ms / 1e6))
+    torch.cuda.synchronize()
+    heap.check_status()
+    if own:
+        dist.destroy_process_group()
+    return out
+
+
 def bench_moe(t, small):
     from .ops import moe
     out = []
@@ -242,7 +307,7 @@ def bench_layernorm(t, small):
     return out
 
 
-CASES = {"fp8": bench_fp8, "fp8_rowwise": bench_fp8_rowwise, "moe": bench_moe, "layernorm": bench_layernorm, "rmsnorm": bench_rmsnorm, "swiglu": bench_swiglu, "rope": bench_rope, "cross_entropy": bench_cross_entropy,
+CASES = {"fp8": bench_fp8, "fp8_rowwise": bench_fp8_rowwise, "comm": bench_comm, "moe": bench_moe, "layernorm": bench_layernorm, "rmsnorm": bench_rmsnorm, "swiglu": bench_swiglu, "rope": bench_rope, "cross_entropy": bench_cross_entropy,
          "gemm": bench_gemm, "attention": bench_attention, "adamw": bench_adamw}
 
 
@@ -314,6 +379,8 @@ class BenchmarkSuite:
         for r in self.results:
             frac = r["gbs"] / pk["hbm_gbs"] if "gbs" in r else r["tflops"] / pk["bf16_tflops"]
             rate = f"{r['gbs']:.0f} GB/s" if "gbs" in r else f"{r['tflops']:.0f} TFLOPS"
+        if r.get("nvlink_gbs"):
+            rate += f" ({r['nvlink_gbs']:.0f} GB/s in over NVLink)"
             sp = f"{r['baseline_ms'] / r['ms']:.2f}x" if r.get("baseline_ms") else "-"
             lines.append(f"{r['name']:<40s} {r['ms']:8.3f} ms  {sp:>7s}  {rate:>12s}  {frac:5.2f} {tag}")
         return "\n".join(lines)
@@ -384,19 +451,30 @@ def main(argv=None) -> int:
     if not torch.cuda.is_available():
         print("no CUDA device")
         return 0
+    import os
+    world, rank = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0"))
+    if "LOCAL_RANK" in os.environ:
+        torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
+    if world > 1:      # `torchrun ... -m trainscale_b200.benchmark_suite --only comm`: one rank per GPU
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", torch.cuda.current_device()))
     pk = peaks()
     t = Timer(64 if a.small else 256)
     rows = []
     for name, fn in CASES.items():
-        if a.only and name != a.only:
-            continue
+        if (a.only and name != a.only) or (not a.only and name == "comm"):
+            continue                   # the collective case needs symmetric memory and runs only when asked for
         rows += fn(t, a.small)
+    if rank != 0:
+        return 0
     tag = "of fallback" if pk.get("fallback") else "of measured"
     for r in rows:
         frac = r["gbs"] / pk["hbm_gbs"] if "gbs" in r else r["tflops"] / pk["bf16_tflops"]
         r["fraction_of_peak"] = frac
         sp = f"{r['baseline_ms'] / r['ms']:.2f}x" if r.get("baseline_ms") else "  -  "
         rate = f"{r['gbs']:.0f} GB/s" if "gbs" in r else f"{r['tflops']:.0f} TFLOPS"
+        if r.get("nvlink_gbs"):
+            rate += f" ({r['nvlink_gbs']:.0f} GB/s in over NVLink)"
         print(f"{r['name']:<40s} {r['ms']:8.3f} ms  baseline {r.get('baseline_ms') or float('nan'):8.3f} ms  {sp:>7s}  "
               f"{rate:>12s}  {frac:5.2f} {tag}")
     if a.json:
