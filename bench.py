@@ -297,7 +297,7 @@ def main():
     ap.add_argument("--seq", type=int, default=SEQ)
     ap.add_argument("--micro-batch", type=int, default=MICRO_BATCH)
     ap.add_argument("--ac", default="auto", choices=["auto", "full", "half", "op_selective", "none"])
-    ap.add_argument("--sharding", default="shard_grad_op", choices=["full", "full_shard", "shard_grad_op", "no_shard"])
+    ap.add_argument("--sharding", default="full_shard", choices=["full", "full_shard", "shard_grad_op", "no_shard"])
     ap.add_argument("--comm", default="auto", choices=["auto", "fused", "nccl"])
     ap.add_argument("--no-secondary", action="store_true", help="skip the measurement of the other sharding mode")
     ap.add_argument("--secondary-timeout", type=float, default=300.0)

@@ -461,6 +461,8 @@ class LlamaForCausalLM(nn.Module):
         forward, dgrad and wgrad in fp8 with per-token / per-feature scales (gradients in `grad_format`, e4m3 or e5m2);
         "block": 1 x 128 / 128 x 128 block scales, forward and dgrad in fp8."""
         for layer in self.model.layers:
+            if isinstance(layer, nn.Identity):        # another pipeline stage's layer (not built on this rank)
+                continue
             for blk in (layer.self_attn, layer.mlp):
                 blk = getattr(blk, "inner", blk)      # under tensor parallelism the block sits inside its wrapper
                 blk.fp8, blk.fp8_recipe, blk.fp8_grad_format = enabled, recipe, grad_format
@@ -469,7 +471,8 @@ class LlamaForCausalLM(nn.Module):
         """Operator-level selective recomputation: no layer is re-run, but norm and GLU outputs are rebuilt in
         backward instead of stored (see ops/fused_blocks.py)."""
         for layer in self.model.layers:
-            layer.op_selective = enabled
+            if not isinstance(layer, nn.Identity):
+                layer.op_selective = enabled
 
     def gradient_checkpointing_disable(self):
         self.model.gradient_checkpointing = False

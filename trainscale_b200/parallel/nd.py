@@ -61,7 +61,11 @@ class NDEngine:
             for i, layer in enumerate(model.model.layers):     # other stages' layers are dropped on this rank
                 if id(layer) not in mine:
                     model.model.layers[i] = torch.nn.Identity()
-            self.runtime = PP.PipelineRuntime(self.stage_module, stage, P, group=None, schedule=p.pp_schedule,
+            # one communicator per direction (activations down the pipeline, gradients up): see PipelineRuntime
+            world = list(range(dist.get_world_size()))
+            self._pp_act_group, self._pp_grad_group = dist.new_group(world), dist.new_group(world)
+            self.runtime = PP.PipelineRuntime(self.stage_module, stage, P, group=self._pp_act_group,
+                                              schedule=p.pp_schedule, grad_group=self._pp_grad_group,
                                               prev_rank=self.pp_ranks[stage - 1] if stage > 0 else None,
                                               next_rank=self.pp_ranks[stage + 1] if stage < P - 1 else None)
             self.pp_microbatches = int(p.pp_microbatches or 0)

@@ -293,22 +293,27 @@ class PipelineRuntime:
     """Executes one schedule on this rank's stage. Activations travel as one packed tensor [mb, S, 2H]."""
 
     def __init__(self, stage_module: nn.Module, stage: int, num_stages: int, group=None, schedule: str = "1f1b",
-                 prev_rank: int | None = None, next_rank: int | None = None):
+                 prev_rank: int | None = None, next_rank: int | None = None, grad_group=None):
+        """`group` carries the activations (stage s -> s + 1), `grad_group` the activation gradients (s + 1 -> s).
+        On NCCL the two directions need their own communicators: in 1F1B a stage sends its next activation while its
+        neighbour sends a gradient back; on ONE communicator each send waits for the matching receive, which is queued
+        behind the other rank's own send, and large messages (no eager buffering) dead-lock."""
         self.mod, self.stage, self.P, self.group, self.schedule_name = stage_module, stage, num_stages, group, schedule
+        self.grad_group = grad_group if grad_group is not None else group
         self.prev_rank = prev_rank if prev_rank is not None else stage - 1
         self.next_rank = next_rank if next_rank is not None else stage + 1
         self.first, self.last = stage == 0, stage == num_stages - 1
         self.wq = WgradQueue()
         self.stats = {"sent_bytes": 0, "recv_bytes": 0}
 
-    def _send(self, t: torch.Tensor, dst: int):
+    def _send(self, t: torch.Tensor, dst: int, grad: bool = False):
         self.stats["sent_bytes"] += t.numel() * t.element_size()
-        return dist.isend(t.contiguous(), dst, group=self.group)
+        return dist.isend(t.contiguous(), dst, group=self.grad_group if grad else self.group)
 
-    def _recv(self, shape, dtype, device, src: int):
+    def _recv(self, shape, dtype, device, src: int, grad: bool = False):
         buf = torch.empty(shape, dtype=dtype, device=device)
         self.stats["recv_bytes"] += buf.numel() * buf.element_size()
-        return buf, dist.irecv(buf, src, group=self.group)
+        return buf, dist.irecv(buf, src, group=self.grad_group if grad else self.group)
 
     def train_step(self, microbatches: Sequence[dict], act_shape: tuple, act_dtype, device,
                    extra_scale: float = 1.0) -> torch.Tensor | None:
@@ -345,7 +350,7 @@ class PipelineRuntime:
                 if self.last:
                     grad = None
                 else:
-                    grad, work = self._recv(act_shape, act_dtype, device, self.next_rank)
+                    grad, work = self._recv(act_shape, act_dtype, device, self.next_rank, grad=True)
                     work.wait()
                 before = len(self.wq)
                 if split:
@@ -356,7 +361,7 @@ class PipelineRuntime:
                     torch.autograd.backward(out, grad)
                 x = inputs.pop(a.mb)
                 if not self.first:
-                    pending.append(self._send(x.grad, self.prev_rank))
+                    pending.append(self._send(x.grad, self.prev_rank, grad=True))
             else:   # W: retire the weight-gradient GEMMs parked by B of this micro-batch
                 self.wq.run(w_marks.pop(a.mb, None))
         self.wq.run()
