@@ -55,12 +55,19 @@ def test_noalloc_entry_point_matches_existing_twice_in_a_row():
     # outputs are allocated before the calls: the entry point itself must not need any allocation
     cases = [(_inputs(1000, 4096, 1)), (_inputs(333, 1024, 2))]
     outs = [(torch.empty_like(c[0]), torch.empty(c[0].shape[1], dtype=torch.float32, device="cuda")) for c in cases]
+    # the set-up call (address look-up of the built-in workspace, lazy loading of the kernels) is made first, so the
+    # driver-level free-memory figure below sees only what the two measured calls do
+    (x, dy, dres, w, rstd), (dx, dw) = cases[0], outs[0]
+    assert _run_noalloc(lib, x, dy, dres, w, rstd, dx, dw) == 0
     torch.cuda.synchronize()
     before = torch.cuda.memory_allocated()
+    free_before = torch.cuda.mem_get_info()[0]
     for (x, dy, dres, w, rstd), (dx, dw) in zip(cases, outs):      # two calls in a row, second one smaller
         assert _run_noalloc(lib, x, dy, dres, w, rstd, dx, dw) == 0
     torch.cuda.synchronize()
     assert torch.cuda.memory_allocated() == before
+    # a raw cudaMalloc inside the library would not show in PyTorch's counter, but it does lower the device's free bytes
+    assert torch.cuda.mem_get_info()[0] >= free_before
     for (x, dy, dres, w, rstd), (dx, dw) in zip(cases, outs):
         rdx, rdw = _run_existing(lib, x, dy, dres, w, rstd)
         torch.cuda.synchronize()

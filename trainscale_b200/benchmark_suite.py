@@ -86,7 +86,8 @@ def bench_rope(t, small):
         Hq, Hkv, D = 32, 8, 128
         cos, sin = rope.rope_tables(S, D, 500000.0, "cuda")
         qkv = torch.randn(1, S, (Hq + 2 * Hkv) * D, device="cuda", dtype=torch.bfloat16)
-        ms = t(lambda: rope.apply_rope_qkv(qkv, Hq + Hkv, D, cos, sin), graph=True)
+        # the decoder's form: q|k rotated where the projection wrote them (no copy)
+        ms = t(lambda: rope.apply_rope_qkv(qkv, Hq + Hkv, D, cos, sin, inplace=True), graph=True)
         base = t(lambda: qkv.clone(), graph=True)
         # bytes: the q and k heads are read and written in place (v is not touched), plus the cos / sin rows
         out.append(dict(name=f"rope S={S}", ms=ms, baseline_ms=base,

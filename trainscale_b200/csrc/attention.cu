@@ -47,22 +47,6 @@ __device__ __forceinline__ float fast_tanh(float x) {
   return y;
 }
 
-// 2^x on the FMA pipe (no special-function unit): round-to-nearest split x = n + f with the 1.5 * 2^23 trick, a cubic
-// for 2^f on [-0.5, 0.5] (max relative error 1.0e-4, far inside the bf16 rounding of P) and n added into the exponent
-// field.  The forward softmax spends one `ex2.approx` per score, and the special-function unit (16 per clock per SM)
-// then needs as many cycles per tile as the two MMAs of the tile; moving a quarter of the exponentials here takes it
-// off the critical path.  Arguments below -126 (masked scores are -inf) give exactly 0.
-__device__ __forceinline__ float poly_ex2(float x) {
-  const float xc = fmaxf(x, -126.f);
-  const float t = xc + 12582912.f;
-  const float f = xc - (t - 12582912.f);
-  float p = fmaf(f, 0.05592204f, 0.24264008f);
-  p = fmaf(p, f, 0.69312102f);
-  p = fmaf(p, f, 0.99992448f);
-  const float r = __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
-  return x < -126.f ? 0.f : r;
-}
-
 __device__ __forceinline__ void seq_bounds(const AttnParams& p, int b, int& start, int& len) {
   if (p.cu_seqlens) {
     start = p.cu_seqlens[b];
@@ -307,11 +291,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         uint32_t pk[16];
 #pragma unroll
         for (int j = 0; j < 32; j += 2) {
-          const float x0 = fmaf(__uint_as_float(v[c * 32 + j]), sc, -m_sub);
-          const float x1 = fmaf(__uint_as_float(v[c * 32 + j + 1]), sc, -m_sub);
-          // one pair in four goes through the FMA-pipe cubic instead of the special-function unit
-          const float p0 = ((j & 6) == 6) ? poly_ex2(x0) : fast_ex2(x0);
-          const float p1 = ((j & 6) == 6) ? poly_ex2(x1) : fast_ex2(x1);
+          const float p0 = fast_ex2(fmaf(__uint_as_float(v[c * 32 + j]), sc, -m_sub));
+          const float p1 = fast_ex2(fmaf(__uint_as_float(v[c * 32 + j + 1]), sc, -m_sub));
           l0 += p0;
           l1 += p1;
           pk[j >> 1] = pack_bf16x2(p0, p1);

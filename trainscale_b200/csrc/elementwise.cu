@@ -47,64 +47,6 @@ __device__ __forceinline__ void store8(__nv_bfloat16* p, const float* f) {
 constexpr int NORM_THREADS = 256;
 constexpr int NORM_MAXV = 4;   // 256 threads * 4 vectors * 8 = rows up to 8192 wide stay in registers
 
-__global__ void __launch_bounds__(NORM_THREADS) rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x,
-                                                                   const __nv_bfloat16* __restrict__ residual,
-                                                                   const __nv_bfloat16* __restrict__ w,
-                                                                   __nv_bfloat16* __restrict__ y,
-                                                                   __nv_bfloat16* __restrict__ res_out,
-                                                                   float* __restrict__ rstd_out, int H, float eps,
-                                                                   float w_offset) {
-  __shared__ float scratch[32];
-  const size_t row = blockIdx.x;
-  const __nv_bfloat16* xr = x + row * H;
-  const int nvec = H >> 3;
-  float cache[NORM_MAXV][8];
-  float ss = 0.f;
-  int c = 0;
-  for (int i = threadIdx.x; i < nvec; i += NORM_THREADS, ++c) {
-    float f[8];
-    load8(xr + i * 8, f);
-    if (residual) {
-      float r[8];
-      load8(residual + row * H + i * 8, r);
-#pragma unroll
-      for (int e = 0; e < 8; ++e) f[e] += r[e];
-      // the sum is rounded to bf16 exactly as the stored residual stream is
-      store8(res_out + row * H + i * 8, f);
-#pragma unroll
-      for (int e = 0; e < 8; ++e) f[e] = __bfloat162float(__float2bfloat16(f[e]));
-    }
-#pragma unroll
-    for (int e = 0; e < 8; ++e) ss += f[e] * f[e];
-    if (c < NORM_MAXV) {
-#pragma unroll
-      for (int e = 0; e < 8; ++e) cache[c][e] = f[e];
-    }
-  }
-  ss = block_sum(ss, scratch);
-  const float rstd = rsqrtf(ss / H + eps);
-  if (threadIdx.x == 0 && rstd_out) rstd_out[row] = rstd;
-  c = 0;
-  const __nv_bfloat16* src = residual ? res_out + row * H : xr;
-  for (int i = threadIdx.x; i < nvec; i += NORM_THREADS, ++c) {
-    float f[8], wv[8];
-    if (c < NORM_MAXV) {
-#pragma unroll
-      for (int e = 0; e < 8; ++e) f[e] = cache[c][e];
-    } else {
-      load8(src + i * 8, f);
-    }
-    load8(w + i * 8, wv);
-#pragma unroll
-    for (int e = 0; e < 8; ++e) f[e] = f[e] * rstd * (wv[e] + w_offset);
-    store8(y + row * H + i * 8, f);
-  }
-}
-
-// Warp-per-row forward for rows of up to 32 * VPL vectors (H <= 4096 with VPL = 16).  The row stays in the warp's
-// registers as the PACKED bf16 words that were loaded (4 registers per 16-byte vector, not 8 floats): that leaves room
-// for all VPL loads of a lane to be in flight at once, which is what the memory system needs from the few warps that
-// fit on an SM.  The reduction is shuffle-only; warps walk rows with a grid stride.
 __device__ __forceinline__ void unpack_u4(const uint4& r, float* f) {
   const float2 a = unpack_bf16x2(r.x), b = unpack_bf16x2(r.y), c = unpack_bf16x2(r.z), d = unpack_bf16x2(r.w);
   f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
@@ -113,6 +55,91 @@ __device__ __forceinline__ uint4 pack_u4(const float* f) {
   return make_uint4(pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]), pack_bf16x2(f[4], f[5]), pack_bf16x2(f[6], f[7]));
 }
 
+__global__ void __launch_bounds__(NORM_THREADS) rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x,
+                                                                   const __nv_bfloat16* __restrict__ residual,
+                                                                   const __nv_bfloat16* __restrict__ w,
+                                                                   __nv_bfloat16* __restrict__ y,
+                                                                   __nv_bfloat16* __restrict__ res_out,
+                                                                   float* __restrict__ rstd_out, int H, float eps,
+                                                                   float w_offset) {
+  // One CTA per row.  A thread's share of the row (up to NORM_MAXV 16-byte vectors: rows of up to 8192 values) stays in
+  // registers as the packed words that were loaded, all loads are issued before the first use, and the second pass
+  // unpacks again (see rmsnorm_fwd_warp_kernel); wider rows re-read the part that does not fit.
+  __shared__ float scratch[32];
+  const size_t row = blockIdx.x;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + row * H);
+  const uint4* rr = residual ? reinterpret_cast<const uint4*>(residual + row * H) : nullptr;
+  uint4* ro = residual ? reinterpret_cast<uint4*>(res_out + row * H) : nullptr;
+  const int nvec = H >> 3;
+  const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+  uint4 raw[NORM_MAXV], rres[NORM_MAXV];
+#pragma unroll
+  for (int c = 0; c < NORM_MAXV; ++c) {
+    const int i = threadIdx.x + c * NORM_THREADS;
+    raw[c] = i < nvec ? __ldcs(xr + i) : zero;
+    rres[c] = (rr && i < nvec) ? __ldcs(rr + i) : zero;
+  }
+  float ss = 0.f;
+  auto add_sq = [&](const uint4& v) {
+    float a[8];
+    unpack_u4(v, a);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) ss += a[e] * a[e];
+  };
+  auto summed = [&](const uint4& xv, const uint4& rv) {     // residual add, rounded to bf16 as the stored stream is
+    float a[8], b[8];
+    unpack_u4(xv, a);
+    unpack_u4(rv, b);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) a[e] += b[e];
+    return pack_u4(a);
+  };
+#pragma unroll
+  for (int c = 0; c < NORM_MAXV; ++c) {
+    const int i = threadIdx.x + c * NORM_THREADS;
+    if (rr) {
+      raw[c] = summed(raw[c], rres[c]);
+      if (i < nvec) ro[i] = raw[c];
+    }
+    add_sq(raw[c]);
+  }
+  for (int i = threadIdx.x + NORM_MAXV * NORM_THREADS; i < nvec; i += NORM_THREADS) {   // rows wider than 8192
+    uint4 v = xr[i];
+    if (rr) {
+      v = summed(v, rr[i]);
+      ro[i] = v;
+    }
+    add_sq(v);
+  }
+  ss = block_sum(ss, scratch);
+  const float rstd = rsqrtf(ss / H + eps);
+  if (threadIdx.x == 0 && rstd_out) rstd_out[row] = rstd;
+#pragma unroll
+  for (int c = 0; c < NORM_MAXV; ++c)
+    asm volatile("" : "+r"(raw[c].x), "+r"(raw[c].y), "+r"(raw[c].z), "+r"(raw[c].w));
+  const uint4* wr = reinterpret_cast<const uint4*>(w);
+  uint4* yr = reinterpret_cast<uint4*>(y + row * H);
+  auto emit = [&](int i, const uint4& v) {
+    float a[8], wv[8];
+    unpack_u4(v, a);
+    unpack_u4(__ldg(wr + i), wv);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) a[e] = a[e] * rstd * (wv[e] + w_offset);
+    yr[i] = pack_u4(a);
+  };
+#pragma unroll
+  for (int c = 0; c < NORM_MAXV; ++c) {
+    const int i = threadIdx.x + c * NORM_THREADS;
+    if (i < nvec) emit(i, raw[c]);
+  }
+  const uint4* src = rr ? reinterpret_cast<const uint4*>(res_out + row * H) : xr;
+  for (int i = threadIdx.x + NORM_MAXV * NORM_THREADS; i < nvec; i += NORM_THREADS) emit(i, src[i]);
+}
+
+// Warp-per-row forward for rows of up to 32 * VPL vectors (H <= 4096 with VPL = 16).  The row stays in the warp's
+// registers as the PACKED bf16 words that were loaded (4 registers per 16-byte vector, not 8 floats): that leaves room
+// for all VPL loads of a lane to be in flight at once, which is what the memory system needs from the few warps that
+// fit on an SM.  The reduction is shuffle-only; warps walk rows with a grid stride.
 template <int VPL, bool HAS_RES>
 __global__ void __launch_bounds__(128) rmsnorm_fwd_warp_kernel(const __nv_bfloat16* __restrict__ x,
                                                                const __nv_bfloat16* __restrict__ residual,
@@ -927,7 +954,8 @@ extern "C" int ts_rmsnorm_bwd_parts(long long rows) {
 extern "C" int ts_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, const void* dres,
                               void* dx, float* dw_partial, float* dw_f32, void* dw_bf16, int accumulate_dw,
                               long long rows, int H, float w_offset, void* stream) {
-  if (H % 8 != 0 || H > NORM_THREADS * NORM_MAXV * 8 || rows <= 0) return -10;
+  // the kernels index rows with 32-bit integers
+  if (H % 8 != 0 || H > NORM_THREADS * NORM_MAXV * 8 || rows <= 0 || rows > 2147483647LL) return -10;
   const int parts = ts_rmsnorm_bwd_parts(rows);
   if (H <= NORM_THREADS * 2 * 8)
     rmsnorm_bwd_kernel<2><<<parts, NORM_THREADS, 0, ST(stream)>>>((const bf16*)dy, (const bf16*)x, (const bf16*)w, rstd,
@@ -953,7 +981,7 @@ extern "C" int ts_layernorm_fwd(const void* x, const void* w, const void* b, voi
 // partial: fp32 workspace of ts_rmsnorm_bwd_parts(rows) * 2 * H floats; dw / db: fp32 [H]
 extern "C" int ts_layernorm_bwd(const void* dy, const void* x, const void* w, const float* mean, const float* rstd,
                                 void* dx, float* partial, float* dw, float* db, long long rows, int H, void* stream) {
-  if (H % 8 != 0 || H > NORM_THREADS * NORM_MAXV * 8 || rows <= 0) return -10;
+  if (H % 8 != 0 || H > NORM_THREADS * NORM_MAXV * 8 || rows <= 0 || rows > 2147483647LL) return -10;
   const int parts = ts_rmsnorm_bwd_parts(rows);
   layernorm_bwd_kernel<<<parts, NORM_THREADS, 0, ST(stream)>>>((const bf16*)dy, (const bf16*)x, (const bf16*)w, mean,
                                                                rstd, (bf16*)dx, partial, (int)rows, H);
@@ -1143,10 +1171,10 @@ int noalloc_workspace(float** out) {
 extern "C" int ts_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void* w, const float* rstd, const void* dres,
                                       void* dx, float* dw_f32, void* dw_bf16, int accumulate_dw, long long rows, int H,
                                       float w_offset, void* stream) {
-  if (rows <= 0 || H <= 0 || H % 8 != 0 || H > TS_NOALLOC_MAX_H) {
+  if (rows <= 0 || rows > 2147483647LL || H <= 0 || H % 8 != 0 || H > TS_NOALLOC_MAX_H) {
     fprintf(stderr,
-            "[trainscale_b200] ts_rmsnorm_bwd_noalloc: rows=%lld H=%d rejected (need rows > 0, H %% 8 == 0, H <= %d: "
-            "the built-in workspace holds %d x %d floats)\n",
+            "[trainscale_b200] ts_rmsnorm_bwd_noalloc: rows=%lld H=%d rejected (need 0 < rows < 2^31, H %% 8 == 0, "
+            "H <= %d: the built-in workspace holds %d x %d floats)\n",
             rows, H, TS_NOALLOC_MAX_H, TS_NOALLOC_MAX_PARTS, TS_NOALLOC_MAX_H);
     return -20;
   }

@@ -29,7 +29,7 @@ extern "C" {
 // dy / x / w / dres / dx / dw_bf16 are bf16, rstd / dw_f32 fp32.  H must be a multiple of 8.
 //
 // Returns 0 on success.  Returns -20 (and prints one line to stderr) when H > TS_NOALLOC_MAX_H, H % 8 != 0 or
-// rows <= 0; the workspace is never exceeded.  Returns a positive cudaError_t value if the CUDA runtime refuses
+// rows <= 0 or rows >= 2^31; the workspace is never exceeded.  Returns a positive cudaError_t value if the CUDA runtime refuses
 // the set-up or a launch.
 //
 // Set-up: the first call on each device looks up the device address of the built-in workspace

@@ -216,7 +216,7 @@ class LlamaAttention(nn.Module):
         """Everything after the fused q|k|v projection: rotary embedding, attention, output projection."""
         offset = 0 if kv_cache is None else kv_cache.seq_len
         qkv = rope.apply_rope_qkv(qkv, self.n_heads + self.n_kv, self.hd, cos, sin, position_ids, qkv.shape[-2], offset,
-                                  self.cfg.rope_interleaved)
+                                  self.cfg.rope_interleaved, inplace=True)
         if kv_cache is not None:
             o = kv_cache.attend(qkv, self)
         elif self.cp_group is not None:

@@ -21,10 +21,10 @@ class _NormLinearFn(torch.autograd.Function):
         x2 = norm._rows(x, H)
         r2 = None if residual is None else norm._rows(residual, H)
         y, h, rstd = norm.rmsnorm_fwd_raw(x2, r2, norm_w, eps, w_offset)
-        out = gemm.matmul_nt(y, w)
+        out = torch.empty(*x.shape[:-1], w.shape[0], dtype=x.dtype, device=x.device)     # final shape, not a view
+        gemm.matmul_nt(y, w, out=out.view(-1, w.shape[0]))
         ctx.save_for_backward(h, norm_w, rstd, w)
         ctx.eps, ctx.w_offset, ctx.has_res, ctx.shape = eps, w_offset, residual is not None, x.shape
-        out = out.view(*x.shape[:-1], w.shape[0])
         if residual is None:
             return out
         return out, h.view(x.shape)

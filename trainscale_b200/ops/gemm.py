@@ -163,8 +163,11 @@ class _LinearFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w):
         ctx.save_for_backward(x, w)
-        y = matmul_nt(x, w)
-        return y.view(*x.shape[:-1], w.shape[0])
+        # the result is allocated in its final shape (not returned as a view of a 2-D buffer), so that a following
+        # in-place op (the rotary embedding on q|k) is legal for autograd
+        y = torch.empty(*x.shape[:-1], w.shape[0], dtype=x.dtype, device=x.device)
+        matmul_nt(x, w, out=y.view(-1, w.shape[0]))
+        return y
 
     @staticmethod
     def backward(ctx, dy):

@@ -120,9 +120,11 @@ def _apply_inplace(buf2d, n_heads, D, cos, sin, positions, seq, offset, interlea
 
 
 class _RopeFn(torch.autograd.Function):
+    """Out-of-place form: rotates a copy (the input may be a view, a leaf, or needed by somebody else)."""
+
     @staticmethod
     def forward(ctx, qkv, n_heads, D, cos, sin, positions, seq, offset, interleaved):
-        out = qkv.clone() if qkv.requires_grad or True else qkv
+        out = qkv.clone()
         buf = out.view(-1, out.shape[-1])
         _apply_inplace(buf, n_heads, D, cos, sin, positions, seq, offset, interleaved, False)
         ctx.args = (n_heads, D, seq, offset, interleaved)
@@ -133,21 +135,51 @@ class _RopeFn(torch.autograd.Function):
     def backward(ctx, g):
         cos, sin, positions = ctx.saved_tensors
         n_heads, D, seq, offset, interleaved = ctx.args
-        g = g.clone() if not g.is_contiguous() else g.clone()
+        g = g.clone()
+        _apply_inplace(g.view(-1, g.shape[-1]), n_heads, D, cos, sin, positions, seq, offset, interleaved, True)
+        return g, None, None, None, None, None, None, None, None
+
+
+class _RopeInplaceFn(torch.autograd.Function):
+    """In-place form for the projection output that only the attention reads: no copy in forward (the buffer is
+    marked dirty for autograd) and none in backward (the incoming gradient, produced for this node alone by the
+    attention backward, is rotated where it is).  One pass over the q|k heads instead of a copy of q|k|v plus a pass."""
+
+    @staticmethod
+    def forward(ctx, qkv, n_heads, D, cos, sin, positions, seq, offset, interleaved):
+        ctx.mark_dirty(qkv)
+        _apply_inplace(qkv.view(-1, qkv.shape[-1]), n_heads, D, cos, sin, positions, seq, offset, interleaved, False)
+        ctx.args = (n_heads, D, seq, offset, interleaved)
+        ctx.save_for_backward(cos, sin, positions)
+        return qkv
+
+    @staticmethod
+    def backward(ctx, g):
+        cos, sin, positions = ctx.saved_tensors
+        n_heads, D, seq, offset, interleaved = ctx.args
+        if not g.is_contiguous():
+            g = g.contiguous()
         _apply_inplace(g.view(-1, g.shape[-1]), n_heads, D, cos, sin, positions, seq, offset, interleaved, True)
         return g, None, None, None, None, None, None, None, None
 
 
 def apply_rope_qkv(qkv: torch.Tensor, n_rot_heads: int, head_dim: int, cos: torch.Tensor, sin: torch.Tensor,
                    positions: torch.Tensor | None = None, seq_len: int | None = None, offset: int = 0,
-                   interleaved: bool = False) -> torch.Tensor:
+                   interleaved: bool = False, inplace: bool = False) -> torch.Tensor:
     """Rotate the first `n_rot_heads` heads (q heads then k heads) of a fused [..., (Hq+2Hkv)*D] buffer.
 
     Each k head is rotated once (no per-q-head redundant writes as in the reference's GQA path).
     `positions` ([..., seq] ints) overrides `arange(seq) + offset` for packed documents / CP shards.
+    `inplace`: the caller owns `qkv` (a projection output nobody else reads) and allows it to be rotated where it is;
+    honoured only when autograd permits it (see below), otherwise a copy is rotated as without the flag.
     """
     seq = seq_len if seq_len is not None else qkv.shape[-2]
-    return _RopeFn.apply(qkv, n_rot_heads, head_dim, cos, sin, positions, seq, offset, interleaved)
+    # in place when the buffer is a fresh, contiguous result (not a view of something else, not a leaf that wants a
+    # gradient) on the CUDA path; anything else is rotated in a copy
+    inplace = (inplace and qkv.is_cuda and qkv.dtype == torch.bfloat16 and qkv._base is None and qkv.is_contiguous()
+               and not (qkv.is_leaf and qkv.requires_grad) and not torch.is_inference(qkv))
+    fn = _RopeInplaceFn if inplace else _RopeFn
+    return fn.apply(qkv, n_rot_heads, head_dim, cos, sin, positions, seq, offset, interleaved)
 
 
 def apply_rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, positions: torch.Tensor | None = None,
