@@ -218,6 +218,30 @@ def reshard_optimizer_state(shards: list[dict], new_rank: int, new_world: int,
     return out
 
 
+def select_model_parallel_shards(shards: list[dict], mesh: dict) -> list[dict]:
+    """Of the optimizer shards of a tensor- / pipeline-parallel run, those that hold the SAME parameters as the rank
+    whose mesh coordinates are `mesh` ({axis: [rank, size]}, `NDEngine.mesh_coordinates`): equal tp and pp
+    coordinates.  They form one data-parallel group and can be re-sliced among themselves; shards of another tp rank
+    or pipeline stage hold other parameters under the same unit names and must never be concatenated with them.
+    A checkpoint whose tp or pp size differs from the running layout, or whose shards carry no coordinates, is
+    refused."""
+    if any("mesh" not in s for s in shards):
+        raise CheckpointLoadError("optimizer shards of this checkpoint carry no mesh coordinates: they can only be "
+                                  "resumed at the world size and parallel layout they were written at")
+    saved = shards[0]["mesh"]
+    for axis in ("tp", "pp"):
+        if int(saved[axis][1]) != int(mesh[axis][1]):
+            raise CheckpointLoadError(f"the checkpoint was written with {axis}={saved[axis][1]}, this run uses "
+                                      f"{axis}={mesh[axis][1]}: optimizer shards are re-sliced along the data-parallel "
+                                      f"axis only; load the weights alone or resume with the saved {axis} size")
+    mine = [s for s in shards if all(int(s["mesh"][a][0]) == int(mesh[a][0]) for a in ("tp", "pp"))]
+    want = int(saved["dp_cp"][1])
+    if len(mine) != want:
+        raise CheckpointLoadError(f"found {len(mine)} optimizer shards for tp rank {mesh['tp'][0]}, pp stage "
+                                  f"{mesh['pp'][0]}; the checkpoint was written by {want} data-parallel ranks")
+    return sorted(mine, key=lambda s: int(s["mesh"]["dp_cp"][0]))
+
+
 def engine_layout(engine) -> dict[str, tuple[int, int, int]]:
     return {u.name: (u.numel, u.shard_start, u.shard_numel) for u in engine.units}
 
@@ -252,7 +276,20 @@ def load_training_checkpoint(trainer, path: Path) -> None:
                 saved_world = int(files[0].stem.split("-of-")[1])
                 mine = path / "optim" / f"shard-{trainer.rank:05d}-of-{trainer.world_size:05d}.pt"
                 if saved_world == trainer.world_size and mine.exists():
-                    eng.load_state_dict(torch.load(mine, map_location="cpu", weights_only=False))
+                    sd = torch.load(mine, map_location="cpu", weights_only=False)
+                    if hasattr(eng, "mesh_coordinates") and "mesh" in sd and \
+                            {k: list(v) for k, v in sd["mesh"].items()} != eng.mesh_coordinates():
+                        raise CheckpointLoadError(f"the checkpoint's parallel layout {sd['mesh']} differs from this "
+                                                  f"run's {eng.mesh_coordinates()} at the same world size")
+                    eng.load_state_dict(sd)
+                elif hasattr(eng, "ep_group"):
+                    raise CheckpointLoadError("optimizer shards of an expert-parallel run can only be resumed at the "
+                                              f"world size they were written at ({saved_world})")
+                elif hasattr(eng, "mesh_coordinates"):
+                    shards = select_model_parallel_shards(
+                        [torch.load(f, map_location="cpu", weights_only=False) for f in files], eng.mesh_coordinates())
+                    flat = eng.flat
+                    eng.load_state_dict(reshard_optimizer_state(shards, flat.rank, flat.world, engine_layout(eng)))
                 elif eng.cfg.sharding_strategy == "NO_SHARD" and saved_world == trainer.world_size:
                     eng.load_state_dict(torch.load(files[0], map_location="cpu", weights_only=False))
                 else:
@@ -272,6 +309,8 @@ def load_training_checkpoint(trainer, path: Path) -> None:
                 trainer.optimizer.load_state_dict(ts["optimizer"])
             if ts.get("rng_state") and ts.get("meta", {}).get("world_size") == trainer.world_size:
                 trainer._restore_rng_states(ts["rng_state"])
+    except CheckpointLoadError:
+        raise
     except (OSError, KeyError, RuntimeError) as e:
         raise CheckpointLoadError(f"failed to load checkpoint {path}", cause=e)
 

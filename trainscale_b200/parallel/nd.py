@@ -174,8 +174,16 @@ class NDEngine:
     def micro_step(self, v):
         self.flat.micro_step = v
 
+    def mesh_coordinates(self) -> dict:
+        """{axis: [rank on that axis, size of that axis]} for the axes that decide WHICH parameters this rank's
+        optimizer shard holds (tp: a slice of every projection, pp: a stage's layers) and for the data axis the shard
+        is cut along."""
+        return {a: [self.dims.local_rank(a), self.dims.size(a)] for a in ("tp", "pp", "dp_cp")}
+
     def state_dict(self):
-        return self.flat.state_dict()
+        sd = self.flat.state_dict()
+        sd["mesh"] = self.mesh_coordinates()
+        return sd
 
     def load_state_dict(self, sd):
         self.flat.load_state_dict(sd)
