@@ -169,3 +169,92 @@ def test_moe_decoder_on_gpu_matches_expert_loop():
     assert errs["w_down"][0] < 4e-2 and errs["w_gate_up"][0] < 4e-2 and errs["router"][0] < 0.15, errs
     assert all(worst < 0.25 for _, worst in errs.values()), errs
     _lib.raise_on_any_device_error()
+
+
+@pytest.mark.parametrize("W,T,H,I,E,k", [(2, 200, 256, 128, 4, 2), (4, 333, 128, 256, 8, 2), (4, 64, 256, 128, 16, 1)])
+def test_expert_parallel_peer_kernels_with_virtual_ranks_on_one_gpu(W, T, H, I, E, k):
+    """The dispatch / combine kernels of the peer-memory expert-parallel path, driven for W "ranks" whose buffers all
+    live on this GPU (no kernel of that path waits on another, so running the ranks' launches one after the other in
+    stream order stands in for the barriers).  Every rank's output must equal the expert loop over ALL experts on its
+    own tokens; the scaled push followed by an unweighted pull must give back the pushed rows times the weight sum."""
+    from trainscale_b200.ops import moe, _lib
+    from trainscale_b200.parallel import ep_peer
+    torch.manual_seed(1)
+    dev = torch.device("cuda")
+    El = E // W
+    wgu = (torch.randn(E, 2 * I, H, device=dev) / H ** 0.5).to(torch.bfloat16)
+    wd = (torch.randn(E, H, I, device=dev) / I ** 0.5).to(torch.bfloat16)
+    xs, idss, ws = [], [], []
+    for r in range(W):
+        n_tok = T - 7 * r if r % 2 else T                   # the kernels do not need equal token counts
+        xs.append(torch.randn(n_tok, H, device=dev, dtype=torch.bfloat16))
+        logits = torch.randn(n_tok, E, device=dev)
+        if E >= 8:
+            logits[:, 3] = -1e9                             # an expert nobody routes to
+        w, ids = torch.softmax(logits, -1).topk(k, dim=-1)
+        ws.append((w / w.sum(-1, keepdim=True)).float().contiguous())
+        idss.append(ids)
+    cap = ep_peer.padded_rows(W * T * k, El)
+    tables = [torch.zeros(W * E, dtype=torch.int32, device=dev) for _ in range(W)]
+    xbufs = [torch.full((cap, H), float("nan"), dtype=torch.bfloat16, device=dev) for _ in range(W)]
+    ybufs = [torch.full((cap, H), float("nan"), dtype=torch.bfloat16, device=dev) for _ in range(W)]
+    arr = lambda ts: ep_peer._arr([t.data_ptr() for t in ts])   # noqa: E731
+    t_ptrs, x_ptrs, y_ptrs = arr(tables), arr(xbufs), arr(ybufs)
+    overflow = torch.zeros(1, dtype=torch.int32, device=dev)
+    local = [ep_peer.local_ranks(idss[r], E) for r in range(W)]
+    for r in range(W):
+        ep_peer.counts_push(t_ptrs, local[r][2], r, W, E)
+    routes = [ep_peer.make_route(tables[r], local[r][0], local[r][1], r, W, E, cap, idss[r].shape[0], k, overflow)
+              for r in range(W)]
+    for r in range(W):
+        ep_peer.push_rows(x_ptrs, xs[r], routes[r], W, record_rows=True)
+    outs = []
+    for r in range(W):
+        rt = routes[r]
+        xr = ep_peer.finalize(xbufs[r], rt, H)
+        h = moe.grouped_linear(xr, wgu[r * El:(r + 1) * El].contiguous(), rt.plan)
+        from trainscale_b200.ops import activation
+        y = moe.grouped_linear(activation.glu(h, "silu"), wd[r * El:(r + 1) * El].contiguous(), rt.plan)
+        ep_peer.copy_used(y, ybufs[r], rt, H)
+        # received rows per local expert = what all ranks routed there
+        want_real = torch.stack([sum((idss[s] == r * El + l).sum() for s in range(W)) for l in range(El)])
+        assert torch.equal(rt.seg_real.long(), want_real.long())
+    for r in range(W):
+        out, ys = ep_peer.pull_combine(y_ptrs, routes[r], H, W, ws[r].reshape(-1), True, dev)
+        outs.append(out)
+        assert ys.shape == (idss[r].numel(), H)
+    torch.cuda.synchronize()
+    assert int(overflow.item()) == 0
+    for r in range(W):
+        ref = _reference(xs[r], idss[r], ws[r], wgu, wd)
+        err = (outs[r].float() - ref).abs().max().item()
+        assert err <= 3e-2 * max(ref.abs().max().item(), 1.0), (r, err)
+    # backward-direction moves: scaled push of g, then an unweighted pull of the same rows
+    gs = [torch.randn_like(x) for x in xs]
+    for r in range(W):
+        ep_peer.push_rows(x_ptrs, gs[r], routes[r], W, scale=ws[r].reshape(-1))
+    for r in range(W):
+        dy = ep_peer.finalize(xbufs[r], routes[r], H)
+        used = int(routes[r].plan.seg_start[-1].item())
+        assert torch.isfinite(dy[:used].float()).all()          # pad rows were zeroed, real rows overwritten
+        ep_peer.copy_used(dy, ybufs[r], routes[r], H)
+    for r in range(W):
+        back, _ = ep_peer.pull_combine(y_ptrs, routes[r], H, W, None, False, dev)
+        want = gs[r].float() * ws[r].to(torch.bfloat16).float().sum(-1, keepdim=True)
+        assert (back.float() - want).abs().max().item() <= 3e-2 * max(want.abs().max().item(), 1.0)
+    torch.cuda.synchronize()
+    _lib.raise_on_any_device_error()
+
+
+def test_expert_parallel_block_on_the_peer_dispatcher_single_rank():
+    """The whole autograd path of the peer-memory expert-parallel block (route, dispatch, grouped GEMMs, combine and
+    their backward moves) in a one-rank process group, against the local block and the all-to-all block."""
+    import subprocess
+    import sys
+    from pathlib import Path
+    case = Path(__file__).parent / "dist_cases" / "ep_peer_equivalence.py"
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=1", "--master-addr",
+           "127.0.0.1", "--master-port", "29781", str(case)]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert "arm=peer" in r.stdout and "ok=False" not in r.stdout

@@ -117,3 +117,11 @@ def test_expert_parallel_trainer_on_four_gpus():
     _need(4)
     out = _launch("trainer_nd.py", "--mode", "ep", "--cuda", port=29782, nproc=4)
     assert "RESULT mode=ep ok=True" in out
+
+
+@pytest.mark.parametrize("nproc", [2, 4])
+def test_expert_parallel_dispatch_over_peer_memory(nproc):
+    """Peer-memory dispatch / combine kernels against the library all-to-all and the all-experts-local block."""
+    _need(nproc)
+    out = _launch("ep_peer_equivalence.py", port=29782 + nproc, nproc=nproc)
+    assert "arm=peer" in out and "ok=False" not in out

@@ -280,6 +280,69 @@ def bench_comm(t, small):
     return out
 
 
+def bench_ep(t, small):
+    """One expert-parallel mixture-of-experts block, forward + backward, per rank: tokens dispatched and combined by the
+    peer-memory kernels of csrc/ep_comm.cu (`parallel/ep_peer.py`: no host synchronisation, grouped GEMMs) against the
+    same block on the library all-to-all (`baseline`: host-side split sizes, one GEMM pair per expert).  Run under
+    torchrun with one rank per GPU; in a single process the "peers" are this GPU.  TFLOP/s counts the three expert
+    GEMMs of the rank's own tokens, forward + backward (3x forward)."""
+    import copy
+
+    import torch.distributed as dist
+
+    from .models.llama import LlamaMoEMLP, preset_config
+    from .parallel.ep import ExpertParallelDecoderMoE, make_peer_dispatcher
+    own = False
+    if not dist.is_initialized():
+        import os
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29556")
+        dist.init_process_group("nccl", rank=0, world_size=1, device_id=torch.device("cuda", torch.cuda.current_device()))
+        own = True
+    W, rank = dist.get_world_size(), dist.get_rank()
+    dev = torch.device("cuda", torch.cuda.current_device())
+    out = []
+    T, H, I, E, k = (2048, 2048, 1024, 8, 2) if small else (8192, 4096, 14336, 8, 2)
+    peer = make_peer_dispatcher(dist.group.WORLD, E, dev)
+    if peer is None or E % W:
+        return out
+    cfg = preset_config("moe-tiny", hidden_size=H, intermediate_size=I, num_local_experts=E, num_experts_per_tok=k)
+    torch.manual_seed(0)
+    with torch.device(dev):
+        base = LlamaMoEMLP(cfg).to(torch.bfloat16)
+    for p in base.parameters():
+        torch.nn.init.normal_(p, std=0.02)
+    blocks = {"peer": ExpertParallelDecoderMoE(base, dist.group.WORLD, peer),
+              "nccl": ExpertParallelDecoderMoE(base, dist.group.WORLD, None)}
+    del base
+    gen = torch.Generator(device="cpu").manual_seed(rank)
+    x = torch.randn(T, H, generator=gen).to(dev, torch.bfloat16).requires_grad_(True)
+    g = torch.randn(T, H, generator=gen).to(dev, torch.bfloat16)
+
+    def step(blk):
+        for p in blk.parameters():
+            p.grad = None
+        x.grad = None
+        blk(x).backward(g)
+
+    ms = {}
+    for name, blk in blocks.items():
+        v = torch.tensor([t(lambda: step(blk), iters=5)], device=dev)
+        if W > 1:
+            dist.all_reduce(v, op=dist.ReduceOp.MAX)
+        ms[name] = float(v)
+    flops = 3 * (T * k) * 3 * 2 * H * I
+    out.append(dict(name=f"ep moe block fwd+bwd W={W} T={T} H={H} I={I} E={E} k={k}", ms=ms["peer"],
+                    baseline_ms=ms["nccl"], tflops=flops / ms["peer"] / 1e9,
+                    nvlink_gbs=4 * (T * k) * (W - 1) / W * H * 2 / ms["peer"] / 1e6 if W > 1 else None))
+    torch.cuda.synchronize()
+    peer.heap.check_status()
+    peer.check()
+    if own:
+        dist.destroy_process_group()
+    return out
+
+
 def bench_moe(t, small):
     from .ops import moe
     out = []
@@ -308,7 +371,7 @@ def bench_layernorm(t, small):
     return out
 
 
-CASES = {"fp8": bench_fp8, "fp8_rowwise": bench_fp8_rowwise, "comm": bench_comm, "moe": bench_moe, "layernorm": bench_layernorm, "rmsnorm": bench_rmsnorm, "swiglu": bench_swiglu, "rope": bench_rope, "cross_entropy": bench_cross_entropy,
+CASES = {"fp8": bench_fp8, "fp8_rowwise": bench_fp8_rowwise, "comm": bench_comm, "ep": bench_ep, "moe": bench_moe, "layernorm": bench_layernorm, "rmsnorm": bench_rmsnorm, "swiglu": bench_swiglu, "rope": bench_rope, "cross_entropy": bench_cross_entropy,
          "gemm": bench_gemm, "attention": bench_attention, "adamw": bench_adamw}
 
 
@@ -456,15 +519,15 @@ def main(argv=None) -> int:
     world, rank = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0"))
     if "LOCAL_RANK" in os.environ:
         torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
-    if world > 1:      # `torchrun ... -m trainscale_b200.benchmark_suite --only comm`: one rank per GPU
+    if world > 1:      # `torchrun ... -m trainscale_b200.benchmark_suite --only comm|ep`: one rank per GPU
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=torch.device("cuda", torch.cuda.current_device()))
     pk = peaks()
     t = Timer(64 if a.small else 256)
     rows = []
     for name, fn in CASES.items():
-        if (a.only and name != a.only) or (not a.only and name == "comm"):
-            continue                   # the collective case needs symmetric memory and runs only when asked for
+        if (a.only and name != a.only) or (not a.only and name in ("comm", "ep")):
+            continue                   # the collective cases need symmetric memory and run only when asked for
         rows += fn(t, a.small)
     if rank != 0:
         return 0

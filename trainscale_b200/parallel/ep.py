@@ -357,10 +357,13 @@ class ExpertParallelDecoderMoE(nn.Module):
     routing weights.  Gradients of the local experts are complete on their owner (every token that chose them was
     there); the router's gradient is a data-parallel gradient like any replicated parameter."""
 
-    def __init__(self, mlp, group):
+    def __init__(self, mlp, group, peer=None):
         super().__init__()
         E = mlp.router.shape[0]
         self.dispatcher = AllToAllDispatcher(group, E)
+        # `ep_peer.PeerDispatcher` of the group (shared by all layers) or None: tokens then travel through the
+        # library all-to-all above
+        self.peer = peer
         El, r = self.dispatcher.local_experts, self.dispatcher.rank
         self.act, self.top_k, self.norm_topk, self.aux_coef = mlp.act, mlp.top_k, mlp.norm_topk, mlp.aux_coef
         self.num_experts = E
@@ -387,6 +390,12 @@ class ExpertParallelDecoderMoE(nn.Module):
         x2 = x.reshape(-1, shape[-1])
         logits = F.linear(x2, self.router)
         w, ids, probs = moe_ops.topk_softmax(logits, self.top_k, self.norm_topk)
+        if self.peer is not None and moe_ops.available(x2):
+            # peer-memory path: no host synchronisation, permutation fused into the transfers, grouped GEMMs
+            from .ep_peer import expert_parallel_ffn
+            y = expert_parallel_ffn(x2.contiguous(), ids, w.to(x2.dtype), self.w_gate_up, self.w_down, self.peer, self.act)
+            self._aux(ids, probs, x)
+            return y.view(shape)
         d = self.dispatcher
         xs, order, counts = permute_tokens(x2, ids, self.num_experts)
         recv, recv_counts, book = d.dispatch(xs, counts)
@@ -405,11 +414,14 @@ class ExpertParallelDecoderMoE(nn.Module):
         back = back.index_copy(0, gather_idx, ye.to(back.dtype)) if o > 0 else back
         ys = d.combine(back, book)
         y = unpermute_tokens(ys, order, w.to(ys.dtype), x2.shape[0])
+        self._aux(ids, probs, x)
+        return y.view(shape)
+
+    def _aux(self, ids, probs, x) -> None:
         if self.aux_coef > 0 and self.training:
             frac = torch.zeros(self.num_experts, device=x.device).index_add_(
                 0, ids.reshape(-1).long(), torch.ones(ids.numel(), device=x.device)) / ids.numel()
             self.aux_loss = self.num_experts * (frac * probs.mean(0)).sum()
-        return y.view(shape)
 
     def full_expert_weights(self):
         """(w_gate_up [E, 2I, H], w_down [E, H, I]) gathered over the group (collective)."""
@@ -421,16 +433,35 @@ class ExpertParallelDecoderMoE(nn.Module):
         return tuple(out)
 
 
-def shard_model_for_expert_parallel(model, group) -> int:
+def make_peer_dispatcher(group, num_experts: int, device):
+    """`ep_peer.PeerDispatcher` over a symmetric-memory heap of `group`, or None where peer memory is not available
+    (CPU, no peer access, TS_DISABLE_SYMM=1).  Collective over the group."""
+    device = torch.device(device)
+    if device.type != "cuda":
+        return None
+    from .ep_peer import PeerDispatcher
+    from .symm import SymmetricHeap
+    heap = SymmetricHeap.try_create(group, device)
+    return None if heap is None else PeerDispatcher(heap, num_experts)
+
+
+def shard_model_for_expert_parallel(model, group, comm: str = "nccl", device=None) -> int:
     """Replace every mixture-of-experts MLP of a framework decoder by its expert-parallel form.  Returns the number of
-    layers converted.  Call before the data-parallel engine is built (parameters are re-created)."""
+    layers converted.  Call before the data-parallel engine is built (parameters are re-created).
+    `comm`: "nccl" moves tokens with the library all-to-all; "auto" / "fused" with the peer-memory kernels of
+    `ep_peer` when the group has symmetric memory ("fused" raises when it has not)."""
     from ..models.llama import LlamaMoEMLP
-    n = 0
-    for layer in model.model.layers:
-        if isinstance(layer.mlp, LlamaMoEMLP):
-            layer.mlp = ExpertParallelDecoderMoE(layer.mlp, group)
-            n += 1
-    return n
+    moe_layers = [layer for layer in model.model.layers if isinstance(layer.mlp, LlamaMoEMLP)]
+    peer = None
+    if moe_layers and comm in ("auto", "fused"):
+        device = device if device is not None else next(model.parameters()).device
+        peer = make_peer_dispatcher(group, moe_layers[0].mlp.router.shape[0], device)
+        if peer is None and comm == "fused":
+            raise RuntimeError("distributed.comm: fused needs symmetric memory over the expert-parallel group")
+    for layer in moe_layers:
+        layer.mlp = ExpertParallelDecoderMoE(layer.mlp, group, peer)
+    model.ep_peer = peer
+    return len(moe_layers)
 
 
 # ------------------------------------------------------------------------------------------------ trainer engine
@@ -465,7 +496,8 @@ class ExpertParallelEngine:
             grp = dist.new_group(list(range(j, W, ep_size)))
             if rank % ep_size == j:
                 self.edp_group = grp
-        self.converted = shard_model_for_expert_parallel(model, self.ep_group)
+        self.converted = shard_model_for_expert_parallel(model, self.ep_group, getattr(cfg, "comm", "nccl"), device)
+        self.peer = getattr(model, "ep_peer", None)
         if self.converted == 0:
             raise ValueError("distributed.parallel.ep > 1 but the model has no mixture-of-experts layer")
         expert_ids = {id(p) for p in model.parameters() if getattr(p, "expert_parallel", False)}
@@ -526,6 +558,9 @@ class ExpertParallelEngine:
     def check_comm_status(self):
         self.dense.check_comm_status()
         self.expert.check_comm_status()
+        if self.peer is not None:
+            self.peer.heap.check_status()
+            self.peer.check()
 
     @contextlib.contextmanager
     def summon_full_params(self):
