@@ -79,7 +79,7 @@ class ClockSampler:
 def baseline_value(n_gpus: int = 1) -> float | None:
     """The number `vs_baseline` divides by: a published value from BASELINE.json when the reference publishes one (it
     does not), else the reference's own throughput measured on this pool's B200s at the same GPU count
-    (baseline/measured_reference.json, also tabulated in BASELINE.md)."""
+    (baseline/measured_reference.json)."""
     try:
         pub = json.loads((ROOT / "BASELINE.json").read_text()).get("published", {})
         for v in pub.values():

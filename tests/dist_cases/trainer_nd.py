@@ -18,6 +18,9 @@ from trainscale_b200.trainer.sota_trainer import SOTATrainer  # noqa: E402
 CUDA = "--cuda" in sys.argv
 
 
+COMM = sys.argv[sys.argv.index("--comm") + 1] if "--comm" in sys.argv else ("auto" if CUDA else "nccl")
+
+
 def make_cfg(strategy, parallel, world, enabled):
     return SOTAConfig.from_dict({
         "training_mode": "full",
@@ -27,7 +30,7 @@ def make_cfg(strategy, parallel, world, enabled):
         "loss": {"type": "chunked_ce"},
         "distributed": {"enabled": enabled, "backend": "nccl" if CUDA else "gloo", "strategy": strategy,
                         "world_size": world, "gradient_checkpointing": False, "parallel": parallel,
-                        "comm": "auto" if CUDA else "nccl"},
+                        "comm": COMM},
         "hardware": {"precision": "bf16" if CUDA else "fp32", "device": "cuda" if CUDA else "cpu",
                      "device_id": int(os.environ.get("LOCAL_RANK", "0"))},
         "data": {"max_seq_length": 512 if CUDA else 32},
@@ -41,6 +44,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--mode", default="pp", choices=["pp", "sp", "cp", "ulysses", "tp_dp", "tp_pp", "ep"])
     ap.add_argument("--cuda", action="store_true", help="bf16 on GPUs through the CUDA kernels (fused TP path)")
+    ap.add_argument("--comm", default=None, help="distributed.comm (default: auto on GPUs, nccl on CPU)")
     a = ap.parse_args()
     if CUDA:
         lr_ = int(os.environ["LOCAL_RANK"])
@@ -124,6 +128,10 @@ def main():
         ok &= good
         if rank == 0:
             print(f"step {step} mode={a.mode} loss={l1:.5f} oracle={l0:.5f} ok={good}", flush=True)
+    if a.mode == "ep":
+        peer = getattr(tr.engine, "peer", None)
+        print(f"RESULT rank={rank} ep_peer_calls={0 if peer is None else peer.calls}", flush=True)
+        tr.engine.check_comm_status()
     # one HuggingFace-layout checkpoint out of the model-parallel ranks: equal to the oracle's weights, and a resume
     # from it leaves every rank's shard / stage as it was
     import tempfile

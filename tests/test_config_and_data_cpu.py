@@ -1,4 +1,5 @@
 """Config schema, Result type, tokenizer, prompt engine stages, length manager, packing, collate, DataPipeline."""
+import os
 import pytest
 import torch
 import yaml
@@ -197,7 +198,11 @@ def test_every_shipped_yaml_parses_and_resolves_its_mesh():
 def _reference_example_yamls():
     from pathlib import Path
     here = Path(__file__).resolve().parent.parent
-    for root in (here / "baseline" / "_ref" / "data_pipeline" / "examples", Path("/root/reference/data_pipeline/examples")):
+    # the reference as installed for the comparison arm of bench.py, or a checkout named by TRAINSCALE_REFERENCE
+    roots = [here / "baseline" / "_ref" / "data_pipeline" / "examples"]
+    if os.environ.get("TRAINSCALE_REFERENCE"):
+        roots.append(Path(os.environ["TRAINSCALE_REFERENCE"]) / "data_pipeline" / "examples")
+    for root in roots:
         found = sorted(root.glob("*.yaml")) if root.is_dir() else []
         if found:
             return found

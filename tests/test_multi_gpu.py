@@ -112,11 +112,16 @@ def test_pipeline_of_tensor_parallel_pairs_on_four_gpus():
     assert "RESULT mode=tp_pp ok=True" in out
 
 
-def test_expert_parallel_trainer_on_four_gpus():
-    """`distributed.parallel.ep: 2` through the trainer on the CUDA kernels (grouped expert GEMMs, device-side routing)."""
-    _need(4)
-    out = _launch("trainer_nd.py", "--mode", "ep", "--cuda", port=29782, nproc=4)
+@pytest.mark.parametrize("nproc,comm,port", [(2, "auto", 29790), (4, "auto", 29782), (4, "nccl", 29791)])
+def test_expert_parallel_trainer(nproc, comm, port):
+    """`distributed.parallel.ep: 2` through the trainer on the CUDA kernels (device-side routing, grouped expert
+    GEMMs): losses, gradient norms, checkpoint and export against the single-process oracle, with the tokens moved by
+    the peer-memory dispatcher (`auto`) or by the library all-to-all (`nccl`)."""
+    _need(nproc)
+    out = _launch("trainer_nd.py", "--mode", "ep", "--cuda", "--comm", comm, port=port, nproc=nproc)
     assert "RESULT mode=ep ok=True" in out
+    used_peer = "ep_peer_calls=0" not in out
+    assert used_peer == (comm == "auto"), out[-2000:]
 
 
 @pytest.mark.parametrize("nproc", [2, 4])
