@@ -384,3 +384,74 @@ def test_every_optimizer_of_the_zoo_reduces_a_least_squares_loss(name):
     # AdaFactor's relative step (1e-2 x RMS of the weights) is slow by construction on weights this small
     bound = 0.8 if name == "adafactor" else 0.5
     assert bool(torch.isfinite(w).all()) and last < bound * first, (name, first, last)
+
+
+def test_ranking_segmentation_and_distillation_losses_against_direct_formulas():
+    """The losses of losses/extra.py against loop-form restatements of their definitions."""
+    import math
+
+    import torch
+    import torch.nn.functional as F
+
+    from trainscale_b200 import losses as L
+    torch.manual_seed(0)
+    scores, rel = torch.randn(3, 6, requires_grad=True), torch.randint(0, 4, (3, 6)).float()
+    # ListMLE: -sum_i log softmax over the remaining items, in ideal order
+    want = 0.0
+    for b in range(3):
+        order = sorted(range(6), key=lambda i: (-rel[b, i].item(), i))
+        s = scores[b, order]
+        want += -sum(s[i] - torch.logsumexp(s[i:], 0) for i in range(6))
+    got = L.ListMLELoss()(scores, rel)
+    assert abs(float(got) - float(want) / 3) < 1e-5
+    got.backward()
+    assert scores.grad.abs().sum() > 0
+    # LambdaRank: pair loop
+    ranks = scores.detach().argsort(1, descending=True).argsort(1)
+    tot = 0.0
+    for b in range(3):
+        gains = 2.0 ** rel[b] - 1
+        disc = 1 / torch.log2(ranks[b].float() + 2)
+        idcg = (gains.sort(descending=True).values / torch.log2(torch.arange(6).float() + 2)).sum().clamp(min=1e-8)
+        acc = 0.0
+        for i in range(6):
+            for j in range(i + 1, 6):
+                d = abs(gains[i] * (disc[j] - disc[i]) + gains[j] * (disc[i] - disc[j])) / idcg
+                sgn = math.copysign(1.0, rel[b, i] - rel[b, j]) if rel[b, i] != rel[b, j] else 0.0
+                acc += d * math.log1p(math.exp(-sgn * float(scores[b, i] - scores[b, j])))
+        tot += acc / 15
+    assert abs(float(L.LambdaRankLoss()(scores.detach(), rel)) - float(tot) / 3) < 1e-5
+    # segmentation
+    p, t = torch.rand(2, 3, 4, 4), (torch.rand(2, 3, 4, 4) > 0.5).float()
+    inter = (p * t).flatten(2).sum(-1)
+    union = p.flatten(2).sum(-1) + t.flatten(2).sum(-1) - inter
+    assert torch.allclose(L.IoULoss()(p, t), (1 - (inter + 1) / (union + 1)).mean())
+    fp, fn = (p * (1 - t)).flatten(2).sum(-1), ((1 - p) * t).flatten(2).sum(-1)
+    tv = (inter + 1) / (inter + 0.7 * fp + 0.3 * fn + 1)
+    assert torch.allclose(L.FocalTverskyLoss()(p, t), ((1 - tv) ** 0.75).mean())
+    assert torch.allclose(L.BoundaryLoss()(p, t - 0.5), (p * (t - 0.5)).sum((2, 3)).mean())
+    assert torch.allclose(L.CharbonnierLoss(1e-3)(p, t), torch.sqrt((p - t) ** 2 + 1e-6).mean())
+    # GHM-C: with one bin every weight is 1, so the loss is plain cross-entropy; with many bins it is a reweighting
+    logits, y = torch.randn(32, 5), torch.randint(0, 5, (32,))
+    assert torch.allclose(L.GHMCLoss(bins=1)(logits, y), F.cross_entropy(logits, y), atol=1e-6)
+    g = 1 - F.softmax(logits, 1).gather(1, y[:, None]).squeeze(1)
+    idx = (g * 10).floor().clamp(max=9).long()
+    w = 32 / (torch.bincount(idx, minlength=10).clamp(min=1).float() * 10)
+    assert torch.allclose(L.GHMCLoss(bins=10)(logits, y), (F.cross_entropy(logits, y, reduction="none") * w[idx]).mean(),
+                          atol=1e-6)
+    yb = (torch.rand(32) > 0.5).float()
+    assert torch.isfinite(L.GHMCLoss(bins=5, momentum=0.5)(logits[:, 0], yb, mask=torch.rand(32) > 0.2))
+    # distillation
+    s, tt = torch.randn(2, 7, 16), torch.randn(2, 7, 24)
+    fd = L.FeatureDistillationLoss("cosine")
+    assert fd(s, tt).shape == () and fd.projection.weight.shape == (24, 16)
+    a, b = torch.randn(2, 2, 5, 5), torch.randn(2, 2, 5, 5)
+    kl = L.AttentionDistillationLoss("kl", 2.0)(a, b)
+    want = F.kl_div(F.log_softmax(a.reshape(-1, 5) / 2, -1), F.softmax(b.reshape(-1, 5) / 2, -1), reduction="batchmean")
+    assert torch.allclose(kl, want)
+    pl = L.PerceptualLoss(torch.nn.Conv2d(3, 4, 3), normalize=False)
+    assert float(pl(p, p)) == 0.0 and float(pl(p, t)) > 0
+    m = L.create_label_smoothing_matrix(10, 0.1)
+    assert m.shape == (10, 10) and abs(float(m[3, 3]) - 0.9) < 1e-6 and abs(float(m[3, 4]) - 0.01) < 1e-6
+    out = L.LossOutput(torch.tensor(1.0), {"ppl": 2.7})
+    assert out.aux_loss is None and L.create_loss("iou").__class__ is L.IoULoss

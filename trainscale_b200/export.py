@@ -80,3 +80,25 @@ def export_model(model, out_dir, fmt: str = "safetensors", tokenizer=None, merge
     if hub_model_id:
         push_to_hub(out, hub_model_id, hub_token)
     return out
+
+
+def prepare_for_vllm(model_path: str, tensor_parallel_size: int = 1, dtype: str = "auto") -> dict:
+    """Keyword arguments for `vllm.LLM(...)` serving an exported directory (data_pipeline/trainer/export.py:278-296)."""
+    return {"model": str(model_path), "tensor_parallel_size": int(tensor_parallel_size), "dtype": dtype,
+            "trust_remote_code": True, "gpu_memory_utilization": 0.9}
+
+
+def unmerge_lora_weights(model, lora_state_dict: dict):
+    """Undo a merge: subtract scaling * B @ A from every module whose adapter tensors are in `lora_state_dict`
+    (`<module>.lora_A.weight`, `<module>.lora_B.weight`, optional `<module>.scaling`), in place
+    (data_pipeline/trainer/export.py:111-130)."""
+    import torch
+    with torch.no_grad():
+        for name, module in model.named_modules():
+            a, b = lora_state_dict.get(f"{name}.lora_A.weight"), lora_state_dict.get(f"{name}.lora_B.weight")
+            w = getattr(module, "weight", None)
+            if a is None or b is None or w is None:
+                continue
+            scale = float(lora_state_dict.get(f"{name}.scaling", 1.0))
+            w.sub_((scale * (b.float() @ a.float())).to(w.dtype).to(w.device))
+    return model

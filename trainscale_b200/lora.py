@@ -9,6 +9,7 @@ HF target names (q_proj, k_proj, v_proj, o_proj, gate_proj, up_proj, down_proj) 
 from __future__ import annotations
 
 import math
+from dataclasses import dataclass, field
 
 import torch
 import torch.nn as nn
@@ -254,3 +255,54 @@ def load_adapter(model, path, strict: bool = True) -> list[str]:
                 elif strict:
                     raise KeyError(f"adapter checkpoint has no {k}")
     return sorted(set(sd) - used)
+
+
+# ------------------------------------------------------------------------------------------------ names of the reference
+@dataclass
+class LoraConfig:
+    """Adapter hyper-parameters (data_pipeline/trainer/lora.py:27-62); `apply_lora(model, LoraConfig(...))` applies
+    them.  `scaling` = alpha / r, or alpha / sqrt(r) with rank-stabilised LoRA."""
+    r: int = 16
+    lora_alpha: float = 32
+    lora_dropout: float = 0.0
+    target_modules: list = field(default_factory=lambda: ["q_proj", "k_proj", "v_proj", "o_proj", "gate_proj",
+                                                          "up_proj", "down_proj"])
+    modules_to_save: list = field(default_factory=lambda: ["embed_tokens", "lm_head"])
+    bias: str = "none"
+    use_rslora: bool = False
+    use_dora: bool = False
+    init_lora_weights: bool | str = True
+    rank_pattern: dict = field(default_factory=dict)
+
+    @property
+    def scaling(self) -> float:
+        return self.lora_alpha / math.sqrt(self.r) if self.use_rslora else self.lora_alpha / self.r
+
+
+def get_trainable_parameters(model) -> tuple[int, int, float]:
+    """(trainable, total, percentage)."""
+    trainable, total = count_trainable(model)
+    return trainable, total, (100.0 * trainable / total if total else 0.0)
+
+
+def print_trainable_parameters(model) -> None:
+    t, n, pct = get_trainable_parameters(model)
+    print(f"trainable params: {t:,d} || all params: {n:,d} || trainable%: {pct:.4f}")
+
+
+def get_lora_state_dict(model) -> dict[str, torch.Tensor]:
+    """The adapter tensors alone, by parameter name (data_pipeline/trainer/lora.py:298-304)."""
+    return {n: p.data for n, p in model.named_parameters() if "lora_" in n}
+
+
+def load_lora_weights(model, lora_weights: dict) -> int:
+    """Copy adapter tensors (as `get_lora_state_dict` returns them) into a model that already has the adapters;
+    returns the number of tensors loaded.  Names the model does not have are ignored, shapes must match."""
+    own = dict(model.named_parameters())
+    n = 0
+    with torch.no_grad():
+        for name, w in lora_weights.items():
+            if name in own:
+                own[name].copy_(w.to(own[name].dtype))
+                n += 1
+    return n

@@ -476,6 +476,11 @@ class TverskyLoss(nn.Module):
 class BCEWithLogitsLoss(nn.BCEWithLogitsLoss): ...
 
 
+from .extra import (AttentionDistillationLoss, BoundaryLoss, CharbonnierLoss, FeatureDistillationLoss,  # noqa: E402
+                    FocalTverskyLoss, GHMCLoss, IoULoss, LambdaRankLoss, ListMLELoss, LossOutput, PerceptualLoss,
+                    create_label_smoothing_matrix)
+
+
 # ------------------------------------------------------------------------------------------------ registry / composition
 class LossRegistry:
     _losses: dict[str, Callable[..., nn.Module]] = {}
@@ -510,7 +515,10 @@ for _n, _c in {"cross_entropy": CrossEntropyLoss, "fused_cross_entropy": FusedCr
                "load_balancing": LoadBalancingLoss, "expert_entropy": ExpertEntropyLoss, "mse": MSELoss, "mae": MAELoss,
                "huber": HuberLoss, "smooth_l1": SmoothL1Loss, "log_cosh": LogCoshLoss, "quantile": QuantileLoss,
                "margin_ranking": MarginRankingLoss, "listnet": ListNetLoss, "pairwise_reward": PairwiseRewardLoss,
-               "dice": DiceLoss, "tversky": TverskyLoss, "bce": BCEWithLogitsLoss}.items():
+               "dice": DiceLoss, "tversky": TverskyLoss, "bce": BCEWithLogitsLoss,
+               "feature_distillation": FeatureDistillationLoss, "attention_distillation": AttentionDistillationLoss,
+               "charbonnier": CharbonnierLoss, "list_mle": ListMLELoss, "lambda_rank": LambdaRankLoss,
+               "focal_tversky": FocalTverskyLoss, "ghmc": GHMCLoss, "iou": IoULoss, "boundary": BoundaryLoss}.items():
     LossRegistry.register(_n, _c)
 
 

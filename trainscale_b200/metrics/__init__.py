@@ -59,9 +59,22 @@ class DistributedMetricBuffer:
 
 
 class Metric:
+    """update / compute / reset; calling a metric resets it, feeds one batch and returns the value
+    (data_pipeline/trainer/metrics/__init__.py:16-40).  `name` is the key under which a collection reports it."""
+    name: str = ""
+
     def update(self, preds, targets): raise NotImplementedError
     def compute(self) -> float: raise NotImplementedError
     def reset(self): raise NotImplementedError
+
+    def __call__(self, preds, targets):
+        self.reset()
+        self.update(preds, targets)
+        return self.compute()
+
+    def named(self, name: str) -> "Metric":
+        self.name = name
+        return self
 
 
 class _Counts(Metric):
@@ -356,3 +369,85 @@ class TrainingMetrics:
 
     def state_dict(self):
         return {"loss": self.loss.state_dict(), "grad": self.grad.state_dict(), "throughput": self.throughput.state_dict()}
+
+
+# ------------------------------------------------------------------------------------------------ names of the reference
+for _cls, _name in ((Accuracy, "accuracy"), (Precision, "precision"), (Recall, "recall"), (F1Score, "f1"),
+                    (AUROC, "auroc"), (Perplexity, "perplexity"), (BLEU, "bleu"), (ROUGE, "rouge"), (MSE, "mse"),
+                    (MAE, "mae"), (R2Score, "r2")):
+    _cls.name = _name
+
+BLEUScore = BLEU
+MeanSquaredError = MSE
+MeanAbsoluteError = MAE
+
+
+class ROUGEScore(ROUGE):
+    """ROUGE-L F-measure as one number (data_pipeline/trainer/metrics/__init__.py:310-343); `ROUGE` reports
+    ROUGE-1 / -2 / -L together."""
+    name = "rouge_l"
+
+    def compute(self) -> float:
+        return super().compute()["rougeL"]
+
+
+class MetricCollection:
+    """Several metrics fed with the same batches; `compute()` returns {metric name: value}
+    (data_pipeline/trainer/metrics/__init__.py:415-434)."""
+
+    def __init__(self, metrics: Sequence[Metric] = ()):
+        self.metrics: dict[str, Metric] = {}
+        for m in metrics:
+            self.add(m)
+
+    def add(self, metric: Metric) -> None:
+        self.metrics[metric.name or type(metric).__name__.lower()] = metric
+
+    def update(self, preds, targets) -> None:
+        for m in self.metrics.values():
+            m.update(preds, targets)
+
+    def compute(self) -> dict:
+        return {n: m.compute() for n, m in self.metrics.items()}
+
+    def reset(self) -> None:
+        for m in self.metrics.values():
+            m.reset()
+
+
+def compute_accuracy(preds, targets) -> float:
+    return Accuracy()(preds, targets)
+
+
+def compute_f1(preds, targets, average: str = "macro") -> float:
+    return F1Score(average=average)(preds, targets)
+
+
+def compute_perplexity(preds, targets) -> float:
+    return Perplexity()(preds, targets)
+
+
+def create_training_metrics(distributed: bool = False, model=None, log_prefix: str = "train") -> TrainingMetrics:
+    """`TrainingMetrics` with the model's parameter count turned into FLOPs per token (6 N) for the MFU figure
+    (data_pipeline/trainer/metrics/training.py:337-360)."""
+    n = sum(p.numel() for p in model.parameters()) if model is not None else 0
+    world = dist.get_world_size() if distributed and dist.is_available() and dist.is_initialized() else 1
+    tm = TrainingMetrics(flops_per_token=6.0 * n, world_size=world)
+    tm.log_prefix, tm.distributed = log_prefix, distributed
+    return tm
+
+
+def is_distributed() -> bool:
+    return dist.is_available() and dist.is_initialized()
+
+
+def get_world_size() -> int:
+    return dist.get_world_size() if is_distributed() else 1
+
+
+def get_rank() -> int:
+    return dist.get_rank() if is_distributed() else 0
+
+
+def is_main_process() -> bool:
+    return get_rank() == 0

@@ -9,7 +9,8 @@ matmul, which is also the oracle.
 """
 from __future__ import annotations
 
-from dataclasses import dataclass
+from dataclasses import dataclass, field
+from enum import Enum
 
 import torch
 import torch.nn as nn
@@ -19,13 +20,93 @@ from .ops import gemm
 FP8_MAX = {torch.float8_e4m3fn: 448.0, torch.float8_e5m2: 57344.0}
 
 
+class QuantizationType(Enum):
+    """Weight formats a model can be held in (data_pipeline/trainer/quantization.py:29-37)."""
+    NONE = "none"
+    INT8 = "int8"
+    INT4 = "int4"
+    FP8_E4M3 = "fp8_e4m3"
+    FP8_E5M2 = "fp8_e5m2"
+    DYNAMIC = "dynamic"
+
+
+class QuantizationFormat(Enum):
+    """4-bit code books (data_pipeline/trainer/quantization.py:39-43)."""
+    NF4 = "nf4"
+    FP4 = "fp4"
+    INT4 = "int4"
+
+
 @dataclass
 class QuantizationConfig:
-    bits: int = 8
+    """How the base weights are stored.  The `load_in_*` / `bnb_*` / `llm_int8_*` fields are the reference's
+    (data_pipeline/trainer/quantization.py:47-100); `format`, `block_size`, `per_row_activations` and
+    `amax_history_len` steer this framework's own fp8 path (`FP8Linear`, `ops/fp8.py`)."""
+    bits_override: int | None = None
     format: str = "fp8_e4m3"       # fp8_e4m3 | fp8_e5m2 | int8 | nf4
     block_size: int = 128
     per_row_activations: bool = True
     amax_history_len: int = 16
+    load_in_4bit: bool = False
+    load_in_8bit: bool = False
+    load_in_fp8: bool = False
+    bnb_4bit_quant_type: str = "nf4"
+    bnb_4bit_compute_dtype: torch.dtype = torch.bfloat16
+    bnb_4bit_use_double_quant: bool = True
+    fp8_format: str = "e4m3"
+    llm_int8_threshold: float = 6.0
+    llm_int8_skip_modules: list = field(default_factory=lambda: ["lm_head"])
+    llm_int8_has_fp16_weight: bool = False
+
+    def __post_init__(self):
+        if self.load_in_4bit + self.load_in_8bit + self.load_in_fp8 > 1:
+            raise ValueError("only one of load_in_4bit / load_in_8bit / load_in_fp8 can be set")
+        if self.bnb_4bit_quant_type not in ("nf4", "fp4"):
+            raise ValueError(f"invalid 4-bit quant type {self.bnb_4bit_quant_type!r}")
+        if self.fp8_format not in ("e4m3", "e5m2"):
+            raise ValueError(f"invalid fp8 format {self.fp8_format!r}")
+        if self.load_in_fp8:
+            self.format = f"fp8_{self.fp8_format}"
+        elif self.load_in_4bit:
+            self.format = self.bnb_4bit_quant_type
+        elif self.load_in_8bit:
+            self.format = "int8"
+
+    @property
+    def is_quantized(self) -> bool:
+        return self.load_in_4bit or self.load_in_8bit or self.load_in_fp8
+
+    @property
+    def bits(self) -> int:
+        if self.bits_override is not None:
+            return self.bits_override
+        return 4 if self.load_in_4bit else (8 if self.load_in_8bit or self.load_in_fp8 else 16)
+
+    def to_bnb_config(self) -> dict:
+        return {"load_in_4bit": self.load_in_4bit, "load_in_8bit": self.load_in_8bit,
+                "bnb_4bit_quant_type": self.bnb_4bit_quant_type,
+                "bnb_4bit_compute_dtype": self.bnb_4bit_compute_dtype,
+                "bnb_4bit_use_double_quant": self.bnb_4bit_use_double_quant,
+                "llm_int8_threshold": self.llm_int8_threshold, "llm_int8_skip_modules": list(self.llm_int8_skip_modules)}
+
+
+def get_4bit_config(compute_dtype: torch.dtype = torch.bfloat16, quant_type: str = "nf4",
+                    double_quant: bool = True) -> QuantizationConfig:
+    return QuantizationConfig(load_in_4bit=True, bnb_4bit_quant_type=quant_type, bnb_4bit_compute_dtype=compute_dtype,
+                              bnb_4bit_use_double_quant=double_quant)
+
+
+def get_8bit_config(threshold: float = 6.0, skip_modules: list | None = None) -> QuantizationConfig:
+    return QuantizationConfig(load_in_8bit=True, llm_int8_threshold=threshold,
+                              llm_int8_skip_modules=skip_modules or ["lm_head"])
+
+
+def get_fp8_config(format: str = "e4m3") -> QuantizationConfig:      # noqa: A002 - the reference's keyword
+    return QuantizationConfig(load_in_fp8=True, fp8_format=format)
+
+
+def get_16bit_config(dtype: torch.dtype = torch.bfloat16) -> QuantizationConfig:
+    return QuantizationConfig(bnb_4bit_compute_dtype=dtype)
 
 
 def block_quantize_fp8(w: torch.Tensor, block: int = 128, dtype=torch.float8_e4m3fn):
@@ -149,3 +230,74 @@ def estimate_memory_usage(n_params: float, weight_bits: int = 16, trainable_frac
     opt = n_params * trainable_fraction * optimizer_bytes_per_param
     return {"weights_gb": weights * gb, "gradients_gb": grads * gb, "optimizer_gb": opt * gb,
             "total_gb": (weights + grads + opt) * gb}
+
+
+@dataclass
+class QuantState:
+    """Block-quantisation state of a 4-bit tensor: per-block absmax, the code book, and (double quantisation) the
+    state the absmax values themselves were quantised with (data_pipeline/trainer/quantization.py:159-167)."""
+    absmax: torch.Tensor
+    code: torch.Tensor
+    blocksize: int = 64
+    dtype: torch.dtype = torch.bfloat16
+    shape: tuple | None = None
+    offset: torch.Tensor | None = None
+    state2: "QuantState | None" = None
+
+
+def get_quant_state(weight: torch.Tensor) -> QuantState | None:
+    """`QuantState` of a weight that carries one (`weight.quant_state`, as bitsandbytes parameters and the tensors
+    packed by `quantize_nf4_param` do), else None."""
+    qs = getattr(weight, "quant_state", None)
+    if qs is None:
+        return None
+    if isinstance(qs, QuantState):
+        return qs
+    return QuantState(absmax=getattr(qs, "absmax", None), code=getattr(qs, "code", None),
+                      blocksize=getattr(qs, "blocksize", 64), dtype=getattr(qs, "dtype", torch.bfloat16),
+                      shape=getattr(qs, "shape", None), offset=getattr(qs, "offset", None))
+
+
+def quantize_nf4_param(w: torch.Tensor, block: int = 64) -> torch.Tensor:
+    """Pack `w` to NF4 and return the packed uint8 tensor with its `quant_state` attached, so that
+    `get_quant_state` / `fast_dequantize(packed, qs.absmax, qs.shape)` can restore it."""
+    packed, absmax, shape = quantize_nf4(w, block)
+    packed.quant_state = QuantState(absmax=absmax, code=NF4_LEVELS.clone(), blocksize=block, dtype=w.dtype,
+                                    shape=tuple(shape))
+    return packed
+
+
+def prepare_model_for_quantization(model: nn.Module, config: QuantizationConfig) -> nn.Module:
+    """Get a model ready for training on quantised base weights (data_pipeline/trainer/quantization.py:223-249):
+    activation checkpointing on where the model offers it, and - when the base is quantised - every remaining
+    half-precision parameter that is still trainable (norms, biases, embeddings) promoted to fp32, and inputs made
+    to require grad so that checkpointed blocks behind frozen embeddings still back-propagate."""
+    if hasattr(model, "gradient_checkpointing_enable"):
+        model.gradient_checkpointing_enable()
+    if config.is_quantized:
+        for p in model.parameters():
+            if p.requires_grad and p.dtype in (torch.float16, torch.bfloat16) and p.dim() <= 1:
+                p.data = p.data.float()
+        if hasattr(model, "enable_input_require_grads"):
+            model.enable_input_require_grads()
+    return model
+
+
+_LORA_TARGETS = {
+    "phi": ["q_proj", "k_proj", "v_proj", "dense", "fc1", "fc2"],
+    "gpt2": ["c_attn", "c_proj", "c_fc"],
+    "falcon": ["query_key_value", "dense", "dense_h_to_4h", "dense_4h_to_h"],
+}
+
+
+def get_target_modules(model_type: str) -> list[str]:
+    """Default LoRA target modules of a model family (data_pipeline/trainer/quantization.py:252-261): the seven
+    projections for the Llama-shaped families, family-specific names otherwise, q/v for unknown types."""
+    mt = (model_type or "").lower()
+    for fam in ("llama", "qwen", "gemma", "mistral", "mixtral", "yi", "deepseek"):
+        if fam in mt:
+            return ["q_proj", "k_proj", "v_proj", "o_proj", "gate_proj", "up_proj", "down_proj"]
+    for fam, t in _LORA_TARGETS.items():
+        if fam in mt:
+            return list(t)
+    return ["q_proj", "v_proj"]

@@ -188,3 +188,39 @@ class PreferenceTrainer:
             loss.backward()
             gn = None
         return loss.detach(), metrics, gn
+
+
+# ------------------------------------------------------------------------------------------------ reward / batch helpers
+def clip_rewards(rewards: torch.Tensor, clip_value: float | None = 10.0) -> torch.Tensor:
+    """Clamp rewards to [-clip_value, clip_value] (data_pipeline/trainer/rl_training.py:272)."""
+    return rewards if clip_value is None else rewards.clamp(-clip_value, clip_value)
+
+
+def apply_length_penalty(rewards: torch.Tensor, lengths: torch.Tensor, alpha: float = 1.0) -> torch.Tensor:
+    """rewards * (length / longest length)^alpha: short completions earn less (rl_training.py:282)."""
+    return rewards * (lengths.float() / lengths.max().clamp(min=1).float()) ** alpha
+
+
+def calculate_pad_tokens_in_prompt(input_ids: torch.Tensor, logits_to_keep: int, pad_token_id: int) -> torch.Tensor:
+    """Pad tokens in the prompt part (everything but the last `logits_to_keep` positions) of every row."""
+    return (input_ids[:, :-logits_to_keep] == pad_token_id).sum(-1)
+
+
+def create_completion_attention_mask(input_ids: torch.Tensor, pad_token_id: int) -> torch.Tensor:
+    return (input_ids != pad_token_id).long()
+
+
+def autotune_batch_and_chunks(total_rows: int, seq_len: int, hidden_dim: int, vocab_dim: int, dtype_bytes: int = 16,
+                              multiplier: int | None = None, budget_bytes: int | None = None) -> tuple[int, int]:
+    """(rows per pass, number of vocabulary chunks) for a chunked log-softmax over `total_rows` sequences
+    (rl_training.py:198-238).  A pass holds rows x seq_len hidden states and one chunk of the logits, rows x seq_len x
+    vocab / chunks in fp32; rows is the largest divisor of `total_rows` that fits the budget (default 4 GiB; on a
+    180 GB part pass `budget_bytes`), chunks defaults to max(4, seq_len / 4096).  `dtype_bytes` is in BITS, as in the
+    reference."""
+    chunks = multiplier if multiplier is not None else max(4, seq_len // 4096)
+    budget = budget_bytes if budget_bytes is not None else 4 * 2 ** 30
+    per_row = seq_len * hidden_dim * dtype_bytes / 8 + seq_len * vocab_dim * 4 / chunks
+    rows = int(max(1, min(total_rows, budget // max(per_row, 1))))
+    while total_rows % rows:
+        rows -= 1
+    return rows, chunks

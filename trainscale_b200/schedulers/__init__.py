@@ -176,10 +176,53 @@ class OneCycleScheduler(BaseScheduler):
         return fin + (hi - fin) * 0.5 * (1 + math.cos(math.pi * p))
 
 
+class CosineRestartsScheduler(BaseScheduler):
+    """Cosine annealing with warm restarts, parameterised by the NUMBER of cycles over the decay span
+    (data_pipeline/trainer/schedulers/__init__.py:274-320): cycle c starts at base * cycle_decay^c and anneals to the
+    floor; `restart_warmup_steps` ramps linearly into every cycle after the first.  `CosineRestartScheduler` is the
+    form parameterised by cycle length."""
+
+    def __init__(self, optimizer, num_training_steps, warmup_steps=0, min_lr_ratio=0.0, num_cycles: float = 1.0,
+                 cycle_decay: float = 1.0, restart_warmup_steps: int = 0, **kw):
+        self.num_cycles, self.cycle_decay, self.restart_warmup_steps = num_cycles, cycle_decay, restart_warmup_steps
+        super().__init__(optimizer, num_training_steps, warmup_steps, min_lr_ratio, **kw)
+
+    def decay(self, s):
+        total = max(1, self.num_training_steps - self.warmup_steps)
+        if s >= total:
+            return 0.0
+        x = s / total * self.num_cycles
+        cycle = math.floor(x)
+        amp = self.cycle_decay ** cycle * 0.5 * (1.0 + math.cos(math.pi * (x - cycle)))
+        if cycle > 0 and self.restart_warmup_steps > 0:
+            into = s - cycle * total / self.num_cycles            # steps since this cycle began
+            amp *= min(1.0, (into + 1) / self.restart_warmup_steps)
+        return amp
+
+
+# names of the reference's first-generation schedulers (data_pipeline/trainer/schedulers/__init__.py:348,390) and the
+# base class of its second generation (sota_schedulers.py:26)
+PolynomialScheduler = PolynomialDecayScheduler
+InverseSqrtScheduler = InverseSquareRootScheduler
+BaseEnhancedScheduler = BaseScheduler
+
+
+def get_cosine_schedule_with_warmup(optimizer, num_warmup_steps: int, num_training_steps: int,
+                                    min_lr_ratio: float = 0.0) -> CosineScheduler:
+    """Linear warm-up, cosine decay to min_lr_ratio * base (data_pipeline/trainer/schedulers/__init__.py:579)."""
+    return CosineScheduler(optimizer, num_training_steps, warmup_steps=num_warmup_steps, min_lr_ratio=min_lr_ratio)
+
+
+def get_linear_schedule_with_warmup(optimizer, num_warmup_steps: int, num_training_steps: int) -> LinearScheduler:
+    """Linear warm-up, linear decay to zero (data_pipeline/trainer/schedulers/__init__.py:599)."""
+    return LinearScheduler(optimizer, num_training_steps, warmup_steps=num_warmup_steps, min_lr_ratio=0.0)
+
+
 _REGISTRY: dict[str, Callable] = {
     "cosine": CosineScheduler, "linear": LinearScheduler, "constant": ConstantScheduler, "wsd": WSDScheduler,
     "polynomial": PolynomialDecayScheduler, "inverse_sqrt": InverseSquareRootScheduler, "rex": REXScheduler,
-    "cosine_restart": CosineRestartScheduler, "cosine_restarts": CosineRestartScheduler, "onecycle": OneCycleScheduler,
+    "cosine_restart": CosineRestartScheduler, "cosine_restarts": CosineRestartScheduler,
+    "cosine_with_restarts": CosineRestartsScheduler, "onecycle": OneCycleScheduler,
     "one_cycle": OneCycleScheduler,
 }
 
