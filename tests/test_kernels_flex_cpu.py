@@ -1,0 +1,98 @@
+"""The flex-style attention front end (kernels/flex.py) against direct softmax(QK^T)V math; on CPU every path runs the
+fp32 reference of the flash kernels, so this checks the mask / scale / soft-cap / GQA plumbing."""
+import math
+
+import torch
+
+from trainscale_b200 import kernels as K
+
+
+def _direct(Q, Kt, V, allow, scale, softcap=0.0):
+    g = Q.shape[1] // Kt.shape[1]
+    Kt, V = Kt.repeat_interleave(g, 1), V.repeat_interleave(g, 1)
+    s = (Q.float() @ Kt.float().transpose(-1, -2)) * scale
+    if softcap:
+        s = softcap * torch.tanh(s / softcap)
+    s = s.masked_fill(~allow, float("-inf"))
+    return torch.softmax(s, -1) @ V.float()
+
+
+def _merge(o):
+    return o.transpose(1, 2).reshape(o.shape[0], o.shape[2], -1)
+
+
+def test_block_masks_are_recognised_and_forwards_match_direct_math():
+    torch.manual_seed(0)
+    B, H, Hkv, S, D = 2, 4, 2, 24, 16
+    Q, Kt, V = torch.randn(B, H, S, D), torch.randn(B, Hkv, S, D), torch.randn(B, Hkv, S, D)
+    i = torch.arange(S)
+    causal = i[:, None] >= i[None, :]
+    cfg = K.FlexAttentionConfig(num_attention_heads=H, num_key_value_heads=Hkv, head_dim=D,
+                                attn_logit_softcapping=5.0, query_pre_attn_scalar=float(D))
+    assert cfg.num_kv_groups == 2 and cfg.hidden_size == H * D and cfg.softcap == 5.0
+    scale = 1 / math.sqrt(D)
+
+    bm = K.create_flex_attention_causal_mask(S)
+    assert bm.kind == "causal"
+    out = K.flex_attention_forward(Q, Kt, V, bm, cfg)
+    assert out.shape == (B, S, H * D)
+    assert torch.allclose(out, _merge(_direct(Q, Kt, V, causal, scale, 5.0)), atol=2e-5)
+
+    sw = K.create_flex_attention_sliding_window_mask(S, sliding_window=5)
+    assert sw.kind == "sliding_window" and sw.window == 5
+    win = causal & (i[:, None] - i[None, :] < 5)
+    assert torch.equal(sw.to_bool(), win)
+    assert torch.allclose(K.flex_attention_forward(Q, Kt, V, sw, cfg), _merge(_direct(Q, Kt, V, win, scale, 5.0)),
+                          atol=2e-5)
+
+    # a hand-written function for ints is evaluated pair by pair; a causal one is recognised by value
+    assert K.create_block_mask(lambda b, h, q, k: q >= k and True, 8).kind == "causal"
+    odd = K.create_block_mask(lambda b, h, q, k: (q >= k) and ((q - k) % 2 == 0), S)
+    assert odd.kind == "dense"
+    allow = causal & ((i[:, None] - i[None, :]) % 2 == 0)
+    assert torch.allclose(K.flex_attention_forward(Q, Kt, V, odd, cfg), _merge(_direct(Q, Kt, V, allow, scale, 5.0)),
+                          atol=2e-5)
+    per_head = K.CausalSlidingWindowMasker({0: 3}, default_window=7)
+    assert K.create_block_mask(per_head, S, num_heads=H).dense.shape == (H, S, S)
+    assert K.create_block_mask(K.CausalSlidingWindowMasker(default_window=7), S, num_heads=H).kind == "sliding_window"
+
+    plain = K.FlexAttentionConfig(num_attention_heads=H, num_key_value_heads=Hkv, head_dim=D)
+    assert torch.allclose(K.flash_attention_forward(Q, Kt, V, plain, causal=True), _merge(_direct(Q, Kt, V, causal, scale)),
+                          atol=2e-5)
+    full = torch.ones(S, S, dtype=torch.bool)
+    assert torch.allclose(K.sdpa_attention_forward(Q, Kt, V, plain, is_causal=False), _merge(_direct(Q, Kt, V, full, scale)),
+                          atol=2e-5)
+    add = torch.zeros(S, S).masked_fill(~win, float("-inf"))
+    assert torch.allclose(K.sdpa_attention_forward(Q, Kt, V, plain, attn_mask=add), _merge(_direct(Q, Kt, V, win, scale)),
+                          atol=2e-5)
+    # no block mask = full attention, as with torch's flex_attention
+    fn = K.get_flex_attention(float(D), 0.0)
+    assert torch.allclose(fn(Q, Kt, V), _direct(Q, Kt, V, full, scale), atol=2e-5)
+
+
+def test_generation_step_variants_and_modifiers():
+    torch.manual_seed(1)
+    B, H, Hkv, S, D = 1, 4, 1, 12, 8
+    Kt, V = torch.randn(B, Hkv, S, D), torch.randn(B, Hkv, S, D)
+    q1 = torch.randn(B, H, 1, D)
+    cfg = K.FlexAttentionConfig(num_attention_heads=H, num_key_value_heads=Hkv, head_dim=D, attn_logit_softcapping=3.0)
+    mask = torch.zeros(1, S)                     # the single new token sees the whole cache
+    got = K.inference_attention_softcapping(q1, Kt, V, mask, cfg)
+    want = _merge(_direct(q1, Kt, V, torch.ones(1, S, dtype=torch.bool), 1 / math.sqrt(D), 3.0))
+    assert got.shape == (B, 1, H * D) and torch.allclose(got, want, atol=2e-5)
+    assert torch.allclose(K.slow_inference_attention_softcapping(q1, Kt, V, mask, cfg, B, 1), want, atol=2e-5)
+    assert torch.allclose(K.attention_sliding_window_compiled(q1, Kt, V, mask, 1.0, 3.0, H, Hkv, D), want, atol=2e-5)
+    # a decode step through the flex callable: causal block mask, one query against S keys
+    fn = K.get_flex_attention(1.0, 3.0)
+    assert torch.allclose(_merge(fn(q1, Kt, V, K.create_flex_attention_causal_mask(S))), want, atol=2e-5)
+
+    s = torch.randn(4, 4) * 10
+    assert torch.allclose(K.apply_softcap_stable(s, 2.0), 2 * torch.tanh(s / 2))
+    assert torch.allclose(K.apply_softcap_inplace(s.clone(), 2.0), 2 * torch.tanh(s / 2))
+    assert torch.allclose(K.generate_tanh_softcap(2.0)(s, 0, 0, 0, 0), 2 * torch.tanh(s / 2), atol=1e-4)
+    assert torch.allclose(K.generate_combined_modifier(0.5, 2.0)(s, 0, 0, 0, 0), 2 * torch.tanh(s / 4), atol=1e-4)
+    assert torch.equal(K.generate_scale_modifier(0.5)(s, 0, 0, 0, 0), s * 0.5)
+    k2, v2 = K.expand_kv_for_gqa_contiguous(Kt, V, 4)
+    assert k2.shape == (B, 4, S, D) and k2.is_contiguous() and torch.equal(k2[:, 3], Kt[:, 0])
+    assert K.get_causal_mask_slice(torch.ones(8, 8), 2, 5).shape == (2, 5)
+    assert K.causal_masker(0, 0, 3, 2) and not K.get_sliding_window_masker(2)(0, 0, 5, 2)

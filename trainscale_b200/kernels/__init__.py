@@ -220,8 +220,44 @@ class FlashAttentionConfig:
 
 @dataclass
 class FlexAttentionConfig(FlashAttentionConfig):
+    """`mask_type` / `backend` select the kernel switches of `FlexAttention`; the remaining fields are the reference's
+    (data_pipeline/trainer/kernels/flex_attention.py:58-99) and are what the functions of `kernels/flex.py` read."""
     mask_type: AttentionMaskType = AttentionMaskType.CAUSAL
     backend: AttentionBackend | None = None
+    num_attention_heads: int | None = None
+    num_key_value_heads: int | None = None
+    head_dim: int | None = None
+    query_pre_attn_scalar: float = 1.0
+    attn_logit_softcapping: float = 0.0
+    sliding_window_size: int | None = None
+    max_seq_length: int = 8192
+    precision_mode: "PrecisionMode" = None
+    use_flash_attention: bool = True
+    use_triton_kernels: bool = False
+    enable_kv_cache: bool = True
+    page_size: int = 16
+    block_size: int = 128
+    dropout_p: float = 0.0
+    deterministic: bool = True
+
+    def __post_init__(self):
+        if self.num_attention_heads and self.num_key_value_heads and \
+                self.num_attention_heads % self.num_key_value_heads:
+            raise ValueError("num_attention_heads must be divisible by num_key_value_heads")
+        if self.precision_mode is None:
+            self.precision_mode = PrecisionMode.BF16
+        if self.attn_logit_softcapping and not self.softcap:
+            self.softcap = self.attn_logit_softcapping
+        if self.sliding_window_size and not self.window_size:
+            self.window_size = self.sliding_window_size
+
+    @property
+    def num_kv_groups(self) -> int:
+        return (self.num_attention_heads or 1) // (self.num_key_value_heads or self.num_attention_heads or 1)
+
+    @property
+    def hidden_size(self) -> int:
+        return (self.num_attention_heads or 0) * (self.head_dim or 0)
 
 
 @dataclass
@@ -616,3 +652,13 @@ class FP8Linear(nn.Module):
         y = _fp8.fp8_linear(x, self.weight) if _fp8.available(x) and self.weight.shape[0] % 8 == 0 \
             else _gemm.linear(x, self.weight)
         return y if self.bias is None else y + self.bias
+
+
+# ------------------------------------------------------------------------------------------------ flex-style front end
+from .flex import (BlockMask, CausalSlidingWindowMasker, SlidingWindowMasker, apply_softcap_inplace,  # noqa: E402,F401
+                   apply_softcap_stable, attention_sliding_window_compiled, causal_masker, create_block_mask,
+                   create_flex_attention_causal_mask, create_flex_attention_sliding_window_mask, expand_kv_for_gqa,
+                   expand_kv_for_gqa_contiguous, flash_attention_forward, flex_attention_forward,
+                   generate_combined_modifier, generate_scale_modifier, generate_tanh_softcap, get_causal_mask_slice,
+                   get_flex_attention, get_sliding_window_masker, inference_attention_softcapping,
+                   sdpa_attention_forward, slow_inference_attention_softcapping)
