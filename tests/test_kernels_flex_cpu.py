@@ -96,3 +96,50 @@ def test_generation_step_variants_and_modifiers():
     assert k2.shape == (B, 4, S, D) and k2.is_contiguous() and torch.equal(k2[:, 3], Kt[:, 0])
     assert K.get_causal_mask_slice(torch.ones(8, 8), 2, 5).shape == (2, 5)
     assert K.causal_masker(0, 0, 3, 2) and not K.get_sliding_window_masker(2)(0, 0, 5, 2)
+
+
+def test_moe_block_router_and_grouped_gemm_functionals():
+    import torch.nn.functional as F
+    torch.manual_seed(2)
+    H, I, E, k = 32, 48, 4, 2
+    blk = K.create_moe_block(H, I, num_experts=E, top_k=k).eval()
+    x = torch.randn(2, 9, H)
+    out, aux = blk(x)
+    assert out.shape == x.shape and float(aux["total_loss"]) == 0.0
+    # against a direct loop over tokens
+    flat = x.reshape(-1, H)
+    probs = torch.softmax(blk.router.gate(flat).float(), -1)
+    w, idx = probs.topk(k, -1)
+    w = w / w.sum(-1, keepdim=True)
+    want = torch.zeros_like(flat)
+    for t in range(flat.shape[0]):
+        for j in range(k):
+            e = int(idx[t, j])
+            g, u = (flat[t] @ blk.gate_up_proj[e].t()).chunk(2)
+            want[t] += w[t, j] * ((F.silu(g) * u) @ blk.down_proj[e].t())
+    assert torch.allclose(out.reshape(-1, H), want, atol=1e-4)
+    blk.train()
+    _, aux = blk(x)
+    assert float(aux["aux_loss"]) > 0 and float(aux["z_loss"]) > 0 and float(blk.get_aux_loss()) > 0
+    out2, total = K.moe_forward(x, (blk.gate_up_proj, blk.down_proj), blk.router.eval())
+    assert torch.allclose(out2, out, atol=1e-5) and float(total) == 0.0
+
+    # the reference's calling convention: cumulative offsets + argsort indices
+    rw, sel, offsets, gather, _ = blk.router(x)
+    assert offsets[-1] == flat.shape[0] * k and torch.equal(sel.reshape(-1)[gather], sel.reshape(-1)[gather].sort().values)
+    W1 = blk.gate_up_proj.detach().clone().requires_grad_(True)
+    xin = flat.detach().clone().requires_grad_(True)
+    gu = K.MoEGroupedGEMMFunction.apply(xin, W1, k, offsets, gather, None, True, False, False)
+    act = F.silu(gu[:, :I]) * gu[:, I:]
+    y = K.moe_grouped_gemm_forward(act, blk.down_proj, k, offsets, gather, rw, False, True, True)
+    assert torch.allclose(y.view(-1, k, H).sum(1), want, atol=1e-4)
+    dgu = torch.randn_like(gu)
+    gu.backward(dgu)
+    dx = K.moe_grouped_gemm_backward_dx(dgu, W1.detach(), k, offsets, gather, permute_x=True, num_tokens=flat.shape[0])
+    dw = K.moe_grouped_gemm_backward_dw(flat, dgu, k, offsets, gather, permute_x=True, num_experts=E)
+    assert torch.allclose(dx, xin.grad, atol=1e-4) and torch.allclose(dw, W1.grad, atol=1e-4)
+    assert K.get_num_sms() >= 1 and K.get_max_shared_memory() >= 49152 and K.get_l2_cache_size() >= 0
+    assert len(K.MoEAutotuneConfig().generate_configs()) == 1
+    e = K.ExpertMLPLayer(H, I)
+    g_, u_ = e.gate_proj(flat), e.up_proj(flat)
+    assert torch.allclose(e(flat), e.down_proj(F.silu(g_) * u_), atol=1e-5)

@@ -662,3 +662,8 @@ from .flex import (BlockMask, CausalSlidingWindowMasker, SlidingWindowMasker, ap
                    generate_combined_modifier, generate_scale_modifier, generate_tanh_softcap, get_causal_mask_slice,
                    get_flex_attention, get_sliding_window_masker, inference_attention_softcapping,
                    sdpa_attention_forward, slow_inference_attention_softcapping)
+
+from .moe import (ExpertMLPLayer, MoEAutotuneConfig, MoEGroupedGEMMFunction, MoERouter, RouterConfig,  # noqa: E402,F401
+                  SparseMoEBlock, benchmark_moe_kernel, create_moe_block, get_l2_cache_size, get_max_shared_memory,
+                  get_num_sms, moe_forward, moe_grouped_gemm_backward_dw, moe_grouped_gemm_backward_dx,
+                  moe_grouped_gemm_forward)
