@@ -143,3 +143,92 @@ def test_moe_block_router_and_grouped_gemm_functionals():
     e = K.ExpertMLPLayer(H, I)
     g_, u_ = e.gate_proj(flat), e.up_proj(flat)
     assert torch.allclose(e(flat), e.down_proj(F.silu(g_) * u_), atol=1e-5)
+
+
+def test_remaining_kernel_layer_names_against_plain_math():
+    import torch.nn as nn
+    import torch.nn.functional as F
+    torch.manual_seed(3)
+    # rotary
+    B, S, H, D = 2, 10, 3, 16
+    q, k = torch.randn(B, S, H, D), torch.randn(B, S, 1, D)
+    rot = K.RotaryEmbedding(D, max_seq_len=8, scaling_type="pi", scaling_factor=2.0)
+    q2, k2 = rot.forward_qk(q, k, position_offset=3)
+    cos, sin = rot.get_freqs(S + 3)
+    assert cos.shape == (S + 3, D // 2)
+    c, s_ = cos[3:3 + S][None, :, None, :], sin[3:3 + S][None, :, None, :]
+    a, b = q[..., :D // 2], q[..., D // 2:]
+    assert torch.allclose(q2, torch.cat((a * c - b * s_, b * c + a * s_), -1), atol=1e-5)
+    q3, _ = K.apply_rope_qk(q, k, cos, sin, position_offset=3)
+    assert torch.allclose(q3, q2) and torch.allclose(K.RoPEFunction.apply(q, cos, sin, None, 3, False, False), q2)
+    assert torch.allclose(rot(q, position_offset=3), q2) and k2.shape == k.shape
+    cfg = K.RoPEConfig(dim=D, scaling_type=K.RoPEScalingType.NTK, scaling_factor=4.0)
+    assert K.compute_rope_frequencies(cfg, 32)[0].shape == (32, D // 2)
+    assert K.get_optimal_block_size(96) == 128 and K.calculate_settings(4096) == (4096, 8)
+    assert K.calculate_multi_row_settings(256, 1000)[1] == 8 and K.get_layernorm_info()["max_fused_size"] == 65536
+    # norms
+    x, r, w = torch.randn(4, 6, 32), torch.randn(4, 6, 32), torch.rand(32) + 0.5
+    want = lambda t: t * torch.rsqrt(t.pow(2).mean(-1, keepdim=True) + 1e-6) * w   # noqa: E731
+    assert torch.allclose(K.rms_layernorm(x, w), want(x), atol=1e-5)
+    y, h = K.FusedAddRMSLayerNormFunction.apply(x, r, w, 1e-6, True)
+    assert torch.allclose(h, x + r) and torch.allclose(y, want(x + r), atol=1e-5)
+    m = K.FusedRMSNorm(32)
+    assert torch.allclose(m(x, r), (x + r) * torch.rsqrt((x + r).pow(2).mean(-1, keepdim=True) + 1e-6), atol=1e-5)
+    ln = K.LayerNorm(32)
+    assert torch.allclose(ln(x), F.layer_norm(x, (32,)), atol=1e-5)
+    assert torch.allclose(K.fused_add_layernorm(x, r, ln.weight, ln.bias), F.layer_norm(x + r, (32,)), atol=1e-5)
+    assert torch.allclose(K.LayerNormFunction.apply(x, None, None), F.layer_norm(x, (32,)), atol=1e-5)
+    # fp8
+    spec = K.get_fp8_spec(K.FP8Format.E5M2)
+    assert spec.max_val == 57344.0 and spec.exponent_bits == 5
+    meta = K.FP8TensorMeta(K.get_fp8_spec("e4m3"), history_len=4)
+    for v in (1.0, 8.0, 2.0):
+        meta.update_amax(torch.tensor(v))
+    sc, inv = meta.compute_scale()
+    assert abs(float(sc) - 8.0 / 448.0) < 1e-9 and abs(float(inv) * float(sc) - 1) < 1e-6
+    lin = nn.Linear(256, 128)
+    net = K.convert_model_to_fp8(nn.Sequential(lin, nn.ReLU(), nn.Linear(128, 128, bias=False)), exclude_layers=["2"])
+    xin = torch.randn(5, 256)
+    ref = F.linear(xin, lin.weight, lin.bias)
+    assert isinstance(net[2], nn.Linear) and not isinstance(net[0], nn.Linear)
+    assert (net[0](xin) - ref).abs().max() < 0.05 * ref.abs().max()
+    from trainscale_b200.quantization import block_quantize_fp8
+    wq, ws = block_quantize_fp8(lin.weight.detach())
+    assert (K.fp8_linear_forward(xin, wq, ws, lin.bias) - ref).abs().max() < 0.05 * ref.abs().max()
+    assert K.get_fp8_capability()["recommended_block_size"] == 128
+    # attention names
+    Q, Kt, V = torch.randn(1, 4, 12, 8), torch.randn(1, 2, 12, 8), torch.randn(1, 2, 12, 8)
+    i = torch.arange(12)
+    o = K.FlashAttentionTritonFunction.apply(Q, Kt, V, True, None, None, 2)
+    assert torch.allclose(o, _direct(Q, Kt, V, i[:, None] >= i[None, :], 8 ** -0.5), atol=2e-5)
+    assert K.get_attention_backend() in ("tcgen05_flash", "reference") and K.get_flash_attn_version() is None
+    # LoRA wrappers
+    class L(nn.Module):
+        def __init__(s, i, o):
+            super().__init__()
+            s.weight = nn.Parameter(torch.randn(o, i) * 0.1)
+            s.lora_A, s.lora_B, s.scaling = nn.Parameter(torch.randn(4, i) * 0.1), nn.Parameter(torch.randn(o, 4) * 0.1), 0.5
+    g_, u_, d_ = L(16, 24), L(16, 24), L(24, 16)
+    f = lambda m, t: t @ m.weight.t() + 0.5 * (t @ m.lora_A.t()) @ m.lora_B.t()   # noqa: E731
+    xx = torch.randn(7, 16)
+    assert torch.allclose(K.FusedLoRAMLP(g_, u_, d_)(xx), f(d_, F.silu(f(g_, xx)) * f(u_, xx)), atol=1e-5)
+    assert torch.allclose(K.FusedLoRAQKV(g_, u_, g_)(xx)[1], f(u_, xx), atol=1e-5)
+    x24 = torch.randn(3, 24)
+    assert torch.allclose(K.apply_lora_o(d_, x24), f(d_, x24), atol=1e-5)
+    gate, up, dH = torch.randn(5, 8, requires_grad=True), torch.randn(5, 8, requires_grad=True), torch.randn(5, 8)
+    (F.silu(gate) * up).backward(dH)
+    hh, d_up, d_gate = K.swiglu_backward(dH, gate.detach(), up.detach())
+    assert torch.allclose(d_up, up.grad, atol=1e-6) and torch.allclose(d_gate, gate.grad, atol=1e-6)
+    dg2, du2 = K.swiglu_backward_triton(dH, gate.detach(), up.detach())
+    assert torch.allclose(dg2, gate.grad, atol=1e-6) and torch.allclose(du2, up.grad, atol=1e-6)
+    assert K.dequantize_weight(xx, None) is xx
+    # compiler surface: on CPU the wrapper runs eagerly and counts
+    @K.compiled()
+    def twice(t):
+        return t * 2
+    assert torch.equal(twice(xx), xx * 2) and twice.stats["eager_calls"] == 1
+    with K.compilation_context(disable=True):
+        assert torch.equal(K.compile_function(lambda t: t + 1, backend="eager")(xx), xx + 1)
+    assert K.get_compiler() is K.get_compiler()
+    K.clear_compilation_cache()
+    assert K.CUDAGraphConfig().warmup_iterations == 3 and K.InductorConfig().max_autotune and K.DynamicShapeConfig().enabled

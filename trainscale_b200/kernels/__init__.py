@@ -667,3 +667,15 @@ from .moe import (ExpertMLPLayer, MoEAutotuneConfig, MoEGroupedGEMMFunction, MoE
                   SparseMoEBlock, benchmark_moe_kernel, create_moe_block, get_l2_cache_size, get_max_shared_memory,
                   get_num_sms, moe_forward, moe_grouped_gemm_backward_dw, moe_grouped_gemm_backward_dx,
                   moe_grouped_gemm_forward)
+
+from .compat import (CUDAGraphConfig, CompiledFunctionWrapper, DynamicShapeConfig, FP8LinearFunction,  # noqa: E402,F401
+                     FP8Spec, FP8TensorMeta, Fast_RoPE, FlashAttentionTritonFunction, FusedAddRMSLayerNormFunction,
+                     FusedLoRAMLP, FusedLoRAQKV, FusedRMSNorm, FusedRoPEQKFunction, InductorConfig, LayerNorm,
+                     LayerNormFunction, RMSLayerNormFunction, RoPEFunction, RotaryEmbedding, apply_lora_o, apply_rope_qk,
+                     benchmark_attention, benchmark_rope, calculate_multi_row_settings, calculate_settings,
+                     clear_compilation_cache, compilation_context, compile_function, compiled, compute_rope_frequencies,
+                     convert_model_to_fp8, dequantize_weight, fp8_linear_forward, fused_add_layernorm,
+                     get_attention_backend, get_compiler, get_cuda_capability, get_device_capability,
+                     get_flash_attn_version, get_fp8_capability, get_fp8_spec, get_layernorm_info,
+                     get_optimal_block_size, is_flash_attn_triton_available, rms_layernorm, supports_bf16,
+                     swiglu_backward, swiglu_backward_triton, triton_flash_attention)
