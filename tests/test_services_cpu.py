@@ -455,3 +455,56 @@ def test_ranking_segmentation_and_distillation_losses_against_direct_formulas():
     assert m.shape == (10, 10) and abs(float(m[3, 3]) - 0.9) < 1e-6 and abs(float(m[3, 4]) - 0.01) < 1e-6
     out = L.LossOutput(torch.tensor(1.0), {"ppl": 2.7})
     assert out.aux_loss is None and L.create_loss("iou").__class__ is L.IoULoss
+
+
+def test_checkpoint_catalogue_contracts_and_layer_patches():
+    import torch
+    import torch.nn as nn
+    import torch.nn.functional as F
+
+    from trainscale_b200 import registry as R
+    n = R.register_llama_models()
+    assert n > 0 and R.register_llama_models() == 0                       # idempotent
+    info = R.get_checkpoint_info("meta-llama/Llama-3.1-8B-Instruct")
+    assert isinstance(info, R.LlamaModelInfo) and info.mlp_class == "LlamaMLP" and info.model_path.endswith("Instruct")
+    assert R.get_checkpoint_info("unsloth/Llama-3.1-8B-Instruct-bnb-4bit").quant_type is R.QuantType.BNB_4BIT
+    total = R.register_all_models()
+    assert total > 100 and len(R.CHECKPOINT_REGISTRY) == n + total
+    assert all(i.is_multimodal for i in R.search_models(is_multimodal=True)) and R.search_models(is_multimodal=True)
+    assert {i.size for i in R.search_models(base_name="gemma", quant_type=R.QuantType.NONE, org="google")} >= {"2", "9", "27"}
+    assert R.register_model(R.CheckpointInfo, "me", "Tiny", "1", "0.1").model_path == "me/Tiny-1-0.1B"
+    assert R.register_model(R.CheckpointInfo, "me", "Tiny", "1", "0.1") is None
+    assert R.CheckpointInfo.construct_model_name("DeepSeek", "V3", "default", R.QuantType.BF16, "Chat") == "DeepSeek-V3-Chat-bf16"
+
+    # contracts
+    c = R.BaseModuleContract("needs_tcgen05", _hardware_requirements=frozenset({R.Capability.TCGEN05}),
+                             _dependencies=frozenset({"gemm_tcgen05", "nowhere"}))
+    cpu = R.HardwareCapability("cpu", (0, 0), 0, 0.0, frozenset())
+    errs = c.validate(cpu, known={"gemm_tcgen05"})
+    assert [type(e) for e in errs] == [R.HardwareError, R.DependencyError] and errs[1].missing_deps == ("nowhere",)
+    b200 = R.HardwareCapability("b200", (10, 0), 148, 180.0, frozenset({R.Capability.TCGEN05}))
+    assert c.validate(b200) == [] and c.to_contract().requires == (R.Capability.TCGEN05,)
+    assert R.get_registry_validator() is R.get_registry_validator() and R.get_registry_validator().validate() == []
+
+    @R.requires_capability(R.Capability.TCGEN05)
+    def only_on_blackwell():
+        return 1
+    if not R.has_capability(R.Capability.TCGEN05):
+        import pytest
+        with pytest.raises(RuntimeError, match="TCGEN05"):
+            only_on_blackwell()
+
+    # layer patches by class name
+    class GemmaMLP(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.gate_proj, self.up_proj, self.down_proj = nn.Linear(8, 16, bias=False), nn.Linear(8, 16, bias=False), nn.Linear(16, 8, bias=False)
+
+        def forward(self, x):
+            raise AssertionError("the patched forward must run")
+    net = nn.Sequential(GemmaMLP())
+    assert R.apply_layer_patches(net) == ["0"]
+    x = torch.randn(3, 8)
+    m = net[0]
+    want = m.down_proj(F.gelu(m.gate_proj(x), approximate="tanh") * m.up_proj(x))
+    assert torch.allclose(net(x), want, atol=1e-5)

@@ -466,3 +466,16 @@ def auto_patch_attention(model: nn.Module, name: str = "trainscale_flash") -> in
             m.config._attn_implementation = name
             n += 1
     return n
+
+
+# ------------------------------------------------------------------------------------------------ checkpoint catalogue
+from .catalog import (CHECKPOINT_REGISTRY, LAYER_PATCHES, QUANT_TAG_MAP, BaseModuleContract, CheckpointInfo,  # noqa: E402,F401
+                      ContractError, DeepSeekModelInfo, DependencyError, FamilyMeta, GemmaModelInfo, HardwareError,
+                      LlamaModelInfo, MistralModelInfo, QuantType, QwenModelInfo, RegistrationError,
+                      apply_layer_patches, auto_patch_mlp_geglu, auto_patch_mlp_swiglu, get_checkpoint_info,
+                      get_registry_validator, has_capability, register_all_models, register_code_models,
+                      register_cohere_granite_models, register_deepseek_models, register_falcon_models,
+                      register_family, register_gemma_models, register_layer_patch, register_llama_models,
+                      register_mistral_models, register_model, register_moe_models, register_phi_models,
+                      register_qwen_models, register_vision_models, register_yi_models, requires_capability,
+                      search_models)
