@@ -369,3 +369,67 @@ def test_ulysses_attention_matches_full_attention(nproc, port):
     r = launch("ulysses.py", nproc, port)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
     assert "RESULT ok=True" in r.stdout
+
+
+def test_activation_checkpoint_reference_surface():
+    import torch
+    import torch.nn as nn
+
+    from trainscale_b200.models.llama import LlamaConfig, build_model
+    from trainscale_b200.parallel import activation as A
+    # the decoder obeys no_checkpoint / force_checkpoint
+    m = build_model(LlamaConfig(vocab_size=64, hidden_size=32, intermediate_size=64, num_hidden_layers=2,
+                                num_attention_heads=2, num_key_value_heads=2, head_dim=16), dtype=torch.float32,
+                    device="cpu", seed=0)
+    m.gradient_checkpointing_enable(1)
+    ids = torch.randint(0, 64, (1, 8))
+    calls = []
+    import trainscale_b200.models.llama as L
+    real = L.checkpoint
+    L.checkpoint = lambda fn, *a, **k: (calls.append(1), real(fn, *a, **k))[1]
+    try:
+        m.train()
+        base = m(ids, labels=ids).loss
+        assert len(calls) == 2
+        with A.no_checkpoint():
+            assert torch.allclose(m(ids, labels=ids).loss, base) and len(calls) == 2
+        m.eval()
+        m(ids, labels=ids)
+        assert len(calls) == 2
+        with A.force_checkpoint():
+            m(ids, labels=ids)
+        assert len(calls) == 4
+    finally:
+        L.checkpoint = real
+    # functional checkpoint with keyword arguments, segments, operation contexts
+    lin = nn.Linear(4, 4)
+    x = torch.randn(3, 4, requires_grad=True)
+    y = A.checkpoint(lambda t, scale=1.0: lin(t) * scale, x, scale=2.0)
+    y.sum().backward()
+    assert torch.allclose(y, lin(x) * 2) and x.grad is not None
+    layers = nn.ModuleList(nn.Linear(4, 4) for _ in range(6))
+    seg = A.CheckpointSegment(0, 0, 6, level=1)
+    kids = seg.split(4)
+    assert [len(k) for k in kids] == [1, 2, 1, 2] and 3 in kids[2] and kids[0].level == 0
+    want = x
+    for l_ in layers:
+        want = l_(want)
+    assert torch.allclose(seg.run(layers, x), want, atol=1e-6)
+    with A.OperationCheckpointContext(None, "layernorm") as ctx:
+        assert A.OperationCheckpointContext.active() == ["layernorm"] and ctx.should_checkpoint()
+        assert torch.allclose(ctx.run(torch.nn.functional.layer_norm, x, (4,)), torch.nn.functional.layer_norm(x, (4,)))
+        with A.no_checkpoint():
+            assert torch.allclose(ctx.run(lin, x), lin(x))
+    assert not A.OperationCheckpointContext(None, "attention").should_checkpoint()
+    # records
+    h = A.OffloadHandle.offload(7, x.detach(), A.OffloadTarget.CPU_PAGED)
+    assert torch.equal(h.restore(), x.detach()) and h.shape == (3, 4)
+    import pytest
+    with pytest.raises(ValueError):
+        A.OffloadHandle(1, (1,), torch.float32, torch.device("cpu"), A.OffloadTarget.NVME)
+    snap = A.MemorySnapshot.take()
+    assert snap.timestamp_ns > 0 and A.CheckpointImpl.NO_REENTRANT.value == "no_reentrant"
+    assert A.LayerProfile("l0", A.OperationType.FFN, 1, 2, 0.5, False, True).is_ffn
+    assert A.CheckpointMetrics("l0", 1, 2, 3, 4, 5).memory_saved_bytes == 3
+    ac = A.create_activation_checkpoint("selective", frequency=3)
+    assert ac.cfg.frequency == 3 and A.create_activation_checkpoint("op_selective").cfg.mode == A.CheckpointMode.OP_SELECTIVE

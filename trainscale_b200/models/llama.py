@@ -21,6 +21,7 @@ import torch.nn.functional as F
 from torch.utils.checkpoint import checkpoint
 
 from ..ops import activation, attention, cross_entropy, fused_blocks, gemm, norm, rope
+from ..utils import recompute as _recompute_switch
 
 
 @dataclass
@@ -372,7 +373,7 @@ class LlamaModel(nn.Module):
             cache = None if kv_caches is None else kv_caches[i]
             ck = getattr(self, "checkpoint_layers", None)
             recompute = (i in ck) if ck is not None else (i % self.checkpoint_every == 0)
-            if self.gradient_checkpointing and self.training and recompute:
+            if _recompute_switch.wanted(self.gradient_checkpointing and recompute, self.training):
                 x, residual = checkpoint(layer, x, residual, cos, sin, position_ids, cu_seqlens, doc_ids, None,
                                          use_reentrant=False)
             else:

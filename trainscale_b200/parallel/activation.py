@@ -9,6 +9,7 @@ from __future__ import annotations
 import contextlib
 from dataclasses import dataclass, field
 from enum import Enum
+from typing import NamedTuple
 
 import torch
 import torch.nn as nn
@@ -298,3 +299,217 @@ class HierarchicalCheckpointManager:
         return x
 
     __call__ = forward
+
+
+# ------------------------------------------------------------------------------------------------ reference surface
+class CheckpointImpl(Enum):
+    """Which checkpoint mechanism wraps a layer (data_pipeline/trainer/distributed/activation_checkpoint.py:109)."""
+    NO_REENTRANT = "no_reentrant"
+    REENTRANT = "reentrant"
+    CUSTOM = "custom"
+
+
+class OffloadTarget(Enum):
+    GPU = "gpu"
+    CPU_PINNED = "cpu_pinned"
+    CPU_PAGED = "cpu_paged"
+    NVME = "nvme"
+
+
+class OperationType(Enum):
+    """Kinds of operation a selective policy distinguishes: keep what is expensive to recompute (attention, GEMMs),
+    recompute what is cheap and large (norms, activations, residual adds)."""
+    ATTENTION = "attention"
+    FFN = "ffn"
+    LAYERNORM = "layernorm"
+    EMBEDDING = "embedding"
+    ACTIVATION = "activation"
+    LINEAR = "linear"
+    RESIDUAL = "residual"
+    CUSTOM = "custom"
+
+
+CHEAP_TO_RECOMPUTE = frozenset({OperationType.LAYERNORM, OperationType.ACTIVATION, OperationType.RESIDUAL})
+
+
+class MemorySnapshot(NamedTuple):
+    total_bytes: int
+    allocated_bytes: int
+    reserved_bytes: int
+    free_bytes: int
+    fragmentation_ratio: float
+    timestamp_ns: int
+
+    @classmethod
+    def take(cls, device=None) -> "MemorySnapshot":
+        import time
+        if not torch.cuda.is_available():
+            return cls(0, 0, 0, 0, 0.0, time.monotonic_ns())
+        free, total = torch.cuda.mem_get_info(device)
+        alloc, res = torch.cuda.memory_allocated(device), torch.cuda.memory_reserved(device)
+        return cls(total, alloc, res, free, (res - alloc) / res if res else 0.0, time.monotonic_ns())
+
+
+class CheckpointMetrics(NamedTuple):
+    layer_name: str
+    forward_time_ns: int
+    recompute_time_ns: int
+    memory_saved_bytes: int
+    tensors_checkpointed: int
+    tensors_recomputed: int
+
+
+class LayerProfile(NamedTuple):
+    name: str
+    operation_type: OperationType
+    activation_memory_bytes: int
+    compute_flops: int
+    recompute_cost: float
+    is_attention: bool
+    is_ffn: bool
+
+
+@dataclass
+class OffloadHandle:
+    """Where an offloaded activation lives and how it comes back."""
+    tensor_id: int
+    shape: tuple
+    dtype: torch.dtype
+    device: torch.device
+    target: OffloadTarget
+    cpu_tensor: torch.Tensor | None = None
+    nvme_path: str | None = None
+    is_prefetching: bool = False
+    prefetch_stream: object = None
+    prefetch_event: object = None
+
+    def __post_init__(self):
+        if self.target is OffloadTarget.NVME and self.nvme_path is None:
+            raise ValueError("an NVMe offload handle needs `nvme_path`")
+        if self.target in (OffloadTarget.CPU_PINNED, OffloadTarget.CPU_PAGED) and self.cpu_tensor is None:
+            raise ValueError("a CPU offload handle needs `cpu_tensor`")
+
+    @classmethod
+    def offload(cls, tensor_id: int, t: torch.Tensor, target: OffloadTarget = OffloadTarget.CPU_PINNED,
+                nvme_path: str | None = None) -> "OffloadHandle":
+        if target is OffloadTarget.NVME:
+            torch.save(t.detach().cpu(), nvme_path)
+            return cls(tensor_id, tuple(t.shape), t.dtype, t.device, target, nvme_path=nvme_path)
+        if target is OffloadTarget.GPU:
+            return cls(tensor_id, tuple(t.shape), t.dtype, t.device, target, cpu_tensor=None)
+        host = torch.empty(t.shape, dtype=t.dtype, pin_memory=target is OffloadTarget.CPU_PINNED and t.is_cuda)
+        host.copy_(t.detach(), non_blocking=t.is_cuda)
+        return cls(tensor_id, tuple(t.shape), t.dtype, t.device, target, cpu_tensor=host)
+
+    def restore(self) -> torch.Tensor:
+        if self.target is OffloadTarget.NVME:
+            return torch.load(self.nvme_path, weights_only=True).to(self.device)
+        return self.cpu_tensor.to(self.device, non_blocking=True)
+
+
+class CheckpointSegment:
+    """Layers [start_layer, end_layer) treated as one recomputation unit at `level` of a hierarchy (0 = finest)."""
+
+    def __init__(self, segment_id: int, start_layer: int, end_layer: int, level: int = 0):
+        if end_layer <= start_layer:
+            raise ValueError("a segment needs at least one layer")
+        self.segment_id, self.start_layer, self.end_layer, self.level = segment_id, start_layer, end_layer, level
+        self.children: list[CheckpointSegment] = []
+
+    def __len__(self) -> int:
+        return self.end_layer - self.start_layer
+
+    def __contains__(self, layer: int) -> bool:
+        return self.start_layer <= layer < self.end_layer
+
+    def split(self, parts: int) -> list["CheckpointSegment"]:
+        """Cut into `parts` nearly equal child segments one level down."""
+        n, parts = len(self), max(1, min(parts, len(self)))
+        cuts = [self.start_layer + (n * i) // parts for i in range(parts + 1)]
+        self.children = [CheckpointSegment(self.segment_id * parts + i, a, b, max(0, self.level - 1))
+                         for i, (a, b) in enumerate(zip(cuts, cuts[1:]))]
+        return self.children
+
+    def run(self, layers, x, *args, use_reentrant: bool = False):
+        """Run the segment's layers as one checkpointed unit (plainly when recomputation is switched off)."""
+        def body(h, *a):
+            for layer in layers[self.start_layer:self.end_layer]:
+                h = layer(h, *a)
+            return h
+        return checkpoint(body, x, *args, use_reentrant=use_reentrant)
+
+
+class OperationCheckpointContext:
+    """`with OperationCheckpointContext(policy, "attention") as ctx: y = ctx.run(fn, x)`: runs `fn` under a checkpoint
+    when the operation kind is cheap to recompute (or the policy says so), plainly otherwise; contexts nest and the
+    stack of active operation names is kept per thread."""
+    _active: dict = {}
+
+    def __init__(self, policy=None, op_name: str = "custom", enabled: bool = True):
+        self.policy, self.op_name, self.enabled = policy, op_name, enabled
+        try:
+            self.op_type = OperationType(op_name.lower())
+        except ValueError:
+            self.op_type = OperationType.CUSTOM
+
+    def should_checkpoint(self) -> bool:
+        if not self.enabled or not torch.is_grad_enabled():
+            return False
+        decide = getattr(self.policy, "should_checkpoint_op", None)
+        return bool(decide(self.op_type)) if decide is not None else self.op_type in CHEAP_TO_RECOMPUTE
+
+    def run(self, fn, *args, **kwargs):
+        return checkpoint(fn, *args, **kwargs) if self.should_checkpoint() else fn(*args, **kwargs)
+
+    @classmethod
+    def active(cls) -> list[str]:
+        import threading
+        return [c.op_name for c in cls._active.get(threading.get_ident(), [])]
+
+    def __enter__(self):
+        import threading
+        self._active.setdefault(threading.get_ident(), []).append(self)
+        return self
+
+    def __exit__(self, *exc):
+        import threading
+        self._active[threading.get_ident()].pop()
+        return False
+
+
+def checkpoint(function, *args, use_reentrant: bool = False, preserve_rng_state: bool = True, **kwargs):
+    """torch's activation checkpoint with keyword arguments allowed for `function`, obeying `no_checkpoint()`."""
+    from ..utils import recompute
+    if recompute.override() is False or not torch.is_grad_enabled():
+        return function(*args, **kwargs)
+    from torch.utils.checkpoint import checkpoint as _ckpt
+    fn = (lambda *a: function(*a, **kwargs)) if kwargs else function
+    return _ckpt(fn, *args, use_reentrant=use_reentrant, preserve_rng_state=preserve_rng_state)
+
+
+def no_checkpoint():
+    """Context manager: layers configured for recomputation run plainly (framework decoder, `checkpoint` above,
+    `CheckpointSegment`, `OperationCheckpointContext`)."""
+    from ..utils import recompute
+    return recompute.scoped(False)
+
+
+def force_checkpoint():
+    """Context manager: layers configured for recomputation are checkpointed even when the model is in eval mode
+    (gradients must be enabled for a checkpoint to mean anything)."""
+    from ..utils import recompute
+    return recompute.scoped(True)
+
+
+def create_activation_checkpoint(mode: str = "selective", frequency: int = 2, memory_budget: float = 0.7,
+                                 **kwargs) -> ActivationCheckpoint:
+    """`ActivationCheckpoint` from a mode name: none | full | selective | memory_budget | op_selective | hierarchical |
+    offload.  `memory_budget` is the fraction of the device's memory activations may use (memory_budget mode)."""
+    cfg = ActivationCheckpointConfig(CheckpointMode(mode), int(frequency))
+    if CheckpointMode(mode) is CheckpointMode.MEMORY_BUDGET:
+        total = torch.cuda.mem_get_info()[1] if torch.cuda.is_available() else 0
+        cfg.memory_budget_gb = kwargs.pop("memory_budget_gb", memory_budget * total / 2 ** 30 if total else None)
+    for k, v in kwargs.items():
+        if hasattr(cfg, k):
+            setattr(cfg, k, v)
+    return ActivationCheckpoint(cfg)
