@@ -433,3 +433,40 @@ def test_activation_checkpoint_reference_surface():
     assert A.CheckpointMetrics("l0", 1, 2, 3, 4, 5).memory_saved_bytes == 3
     ac = A.create_activation_checkpoint("selective", frequency=3)
     assert ac.cfg.frequency == 3 and A.create_activation_checkpoint("op_selective").cfg.mode == A.CheckpointMode.OP_SELECTIVE
+
+
+def test_mesh_topology_records_and_tensor_parallel_helpers():
+    import torch
+
+    from trainscale_b200.parallel import mesh as M
+    from trainscale_b200.parallel import tp as T
+    r = M.create_parallel_dims(16, tp=2, pp=2, cp=2, rank=5)
+    assert r.is_ok() and r.unwrap().sizes == {"pp": 2, "dp_replicate": 1, "dp_shard": 2, "cp": 2, "tp": 2}
+    assert M.create_parallel_dims(6, tp=4).is_err()
+    specs = {d.name: d for d in M.DimensionSpec.of(M.ParallelDimsConfig(tp=2, world_size=8))}
+    assert specs["dp_shard"].degree == 4 and specs["tp"].is_sharding and not specs["pp"].requires_comm
+    import pytest
+    with pytest.raises(ValueError):
+        M.DimensionSpec("bogus", 2, M.ParallelDimType.DATA)
+    topo = M.detect_cluster_topology()
+    assert topo.num_nodes >= 1 and topo.nodes[0].num_gpus == topo.gpus_per_node
+    assert M.GPUArchitecture.from_compute_capability((10, 0)) is M.GPUArchitecture.BLACKWELL
+    assert M.GPUArchitecture.from_compute_capability((9, 0)) is M.GPUArchitecture.HOPPER
+    assert M.InterconnectType.NVLINK5 == 4 and M.CommunicationAlgorithm.RING == 1 and M.HardwareVendor.NVIDIA == 1
+    assert M.ParallelDimsMetrics(num_cache_hits=3, num_cache_misses=1).to_dict()["cache_hit_rate"] == 0.75
+
+    with T.tensor_parallel_context(T.TensorParallelConfig()) as mgr:
+        assert mgr.initialized and T.get_tensor_parallel_world_size() == 1 and T.get_sequence_parallel_rank() == 0
+        assert not T.is_sequence_parallel_enabled() and T.get_tensor_parallel_group() is None
+        net = torch.nn.Sequential(T.FusedColumnParallelLinearWithGELU(8, 16),
+                                  T.FusedRowParallelLinearWithDropout(16, 8, dropout_prob=0.1), torch.nn.LayerNorm(8)).eval()
+        x = torch.randn(3, 8)
+        F = torch.nn.functional
+        want = F.linear(F.gelu(F.linear(x, net[0].linear.weight, net[0].linear.bias), approximate="tanh"),
+                        net[1].linear.weight, net[1].linear.bias)
+        assert torch.allclose(net[1](net[0](x)), want, atol=1e-5)
+        counts = T.compute_parameter_count(net)
+        assert counts["parallel_params"] == 280 and counts["replicated_params"] == 16 and counts["total_params"] == 296
+    with pytest.raises(ValueError):
+        T.TensorParallelConfig(tensor_parallel_size=3)
+    assert T.CommStats(1, 2, 3, "all_reduce").latency_ns == 3

@@ -354,3 +354,206 @@ class CommAlgorithmSelector:
         """Gradient bucket size: collective cost on NVSwitch is latency- not link-bound, so buckets only need to
         amortise a launch (tens of MB)."""
         return (80 << 20) if self.nvswitch else (25 << 20)
+
+
+# ------------------------------------------------------------------------------------------------ typed topology records
+from enum import IntEnum  # noqa: E402
+from typing import NamedTuple  # noqa: E402
+
+
+class HardwareVendor(IntEnum):
+    UNKNOWN = 0
+    NVIDIA = 1
+    AMD = 2
+    INTEL = 3
+    CPU = 4
+
+
+class InterconnectType(IntEnum):
+    UNKNOWN = 0
+    PCIE = 1
+    NVLINK3 = 2
+    NVLINK4 = 3
+    NVLINK5 = 4
+    INFINITY_FABRIC = 5
+    INTEL_FABRIC = 6
+    INFINIBAND_HDR = 7
+    INFINIBAND_NDR = 8
+    ROCE_V2 = 9
+    ETHERNET = 10
+
+
+class GPUArchitecture(IntEnum):
+    UNKNOWN = 0
+    AMPERE = 1
+    ADA = 2
+    HOPPER = 3
+    BLACKWELL = 4
+    CDNA2 = 10
+    CDNA3 = 11
+    CDNA4 = 12
+    GAUDI2 = 20
+    GAUDI3 = 21
+
+    @classmethod
+    def from_compute_capability(cls, cc: tuple) -> "GPUArchitecture":
+        return {(8, 0): cls.AMPERE, (8, 6): cls.AMPERE, (8, 9): cls.ADA, (9, 0): cls.HOPPER}.get(
+            tuple(cc), cls.BLACKWELL if cc[0] in (10, 12) else cls.UNKNOWN)
+
+
+class ParallelDimType(IntEnum):
+    DATA = 0
+    TENSOR = 1
+    PIPELINE = 2
+    CONTEXT = 3
+    EXPERT = 4
+    SEQUENCE = 5
+
+
+class CommunicationAlgorithm(IntEnum):
+    AUTO = 0
+    RING = 1
+    TREE = 2
+    RECURSIVE_HALVING = 3
+    BUCKET = 4
+    NCCL_AUTO = 5
+
+
+class NUMATopology(NamedTuple):
+    num_nodes: int
+    gpus_per_node: list          # NUMA node -> GPU indices
+    cpu_affinity: dict           # GPU index -> CPU cores
+
+
+class GPUInfo(NamedTuple):
+    index: int
+    name: str
+    vendor: HardwareVendor
+    architecture: GPUArchitecture
+    compute_capability: tuple
+    memory_bytes: int
+    nvlink_connected: list
+    pcie_bus_id: str
+    numa_node: int
+
+
+class NodeTopology(NamedTuple):
+    hostname: str
+    num_gpus: int
+    gpu_info: list
+    intra_node_interconnect: InterconnectType
+    numa_topology: NUMATopology | None
+    has_nvswitch: bool
+
+
+class ClusterTopology(NamedTuple):
+    num_nodes: int
+    gpus_per_node: int
+    total_gpus: int
+    inter_node_interconnect: InterconnectType
+    nodes: list
+    is_homogeneous: bool
+
+
+_NVLINK_BY_ARCH = {GPUArchitecture.AMPERE: InterconnectType.NVLINK3, GPUArchitecture.HOPPER: InterconnectType.NVLINK4,
+                   GPUArchitecture.BLACKWELL: InterconnectType.NVLINK5}
+
+
+def detect_node_topology() -> NodeTopology:
+    """This node as typed records (data_pipeline/trainer/distributed/parallel_dims.py:258-292), from the same probes
+    as `HardwareDetector.detect()`: a GPU that can reach peers directly is taken to be NVLink-connected to them, all-to-all
+    reachability on more than two GPUs to mean a switch."""
+    import socket
+    raw = HardwareDetector.detect()
+    n = raw["num_gpus"]
+    gpus = []
+    for i in range(n):
+        p = torch.cuda.get_device_properties(i)
+        cc = (p.major, p.minor)
+        peers = [j for j in range(n) if j != i and raw["peer_access"][i][j]]
+        gpus.append(GPUInfo(i, p.name, HardwareVendor.NVIDIA, GPUArchitecture.from_compute_capability(cc), cc,
+                            p.total_memory, peers, str(getattr(p, "pci_bus_id", "")), raw["numa"].get(i, -1)))
+    numa = None
+    if raw["numa"]:
+        nodes = sorted(set(raw["numa"].values()))
+        numa = NUMATopology(len(nodes), [[g for g, nd in raw["numa"].items() if nd == k] for k in nodes], {})
+    if n == 0:
+        link = InterconnectType.UNKNOWN
+    elif any(g.nvlink_connected for g in gpus):
+        link = _NVLINK_BY_ARCH.get(gpus[0].architecture, InterconnectType.UNKNOWN)
+    else:
+        link = InterconnectType.PCIE
+    return NodeTopology(socket.gethostname(), n, gpus, link, numa, bool(raw["nvswitch"]))
+
+
+def detect_cluster_topology(num_nodes: int | None = None) -> ClusterTopology:
+    """One node probed, the others assumed alike (the world size tells how many there are); the fabric between nodes
+    cannot be seen from a process and is reported as UNKNOWN unless there is a single node."""
+    node = detect_node_topology()
+    world = dist.get_world_size() if dist.is_initialized() else max(node.num_gpus, 1)
+    nodes = num_nodes or max(1, world // max(node.num_gpus, 1))
+    return ClusterTopology(nodes, node.num_gpus, nodes * node.num_gpus,
+                           InterconnectType.UNKNOWN if nodes > 1 else node.intra_node_interconnect, [node] * nodes, True)
+
+
+@dataclass
+class ParallelDimsMetrics:
+    mesh_build_ns: int = 0
+    mesh_slice_ns: int = 0
+    topology_detect_ns: int = 0
+    num_mesh_accesses: int = 0
+    num_cache_hits: int = 0
+    num_cache_misses: int = 0
+
+    def compute_cache_hit_rate(self) -> float:
+        total = self.num_cache_hits + self.num_cache_misses
+        return self.num_cache_hits / total if total else 0.0
+
+    def to_dict(self) -> dict:
+        return {"mesh_build_ms": self.mesh_build_ns / 1e6, "mesh_slice_us": self.mesh_slice_ns / 1e3,
+                "topology_detect_ms": self.topology_detect_ns / 1e6, "cache_hit_rate": self.compute_cache_hit_rate(),
+                "total_mesh_accesses": self.num_mesh_accesses}
+
+
+_DIM_TYPES = {"dp_replicate": ParallelDimType.DATA, "dp_shard": ParallelDimType.DATA, "cp": ParallelDimType.CONTEXT,
+              "tp": ParallelDimType.TENSOR, "pp": ParallelDimType.PIPELINE, "ep": ParallelDimType.EXPERT,
+              "etp": ParallelDimType.EXPERT, "sp": ParallelDimType.SEQUENCE}
+
+
+@dataclass(frozen=True)
+class DimensionSpec:
+    """One mesh dimension: name, degree (>= 1), kind, whether it communicates and whether it shards data or weights."""
+    name: str
+    degree: int
+    dim_type: ParallelDimType
+    requires_comm: bool = True
+    is_sharding: bool = False
+
+    def __post_init__(self):
+        if self.degree < 1:
+            raise ValueError(f"dimension {self.name} degree must be >= 1, got {self.degree}")
+        if self.name not in _DIM_TYPES:
+            raise ValueError(f"unknown dimension name: {self.name}")
+
+    @classmethod
+    def of(cls, cfg: ParallelDimsConfig) -> list["DimensionSpec"]:
+        c = cfg.resolve()
+        return [cls(n, int(getattr(c, n)), _DIM_TYPES[n], int(getattr(c, n)) > 1, n in ("dp_shard", "tp", "cp", "ep", "etp"))
+                for n in ("pp", "dp_replicate", "dp_shard", "cp", "tp", "ep", "etp")]
+
+
+def create_parallel_dims(world_size: int, dp_replicate: int = 1, dp_shard: int = -1, cp: int = 1, tp: int = 1,
+                         pp: int = 1, ep: int = 1, etp: int = 1, sp: int = 1, rank: int | None = None,
+                         create_groups: bool | None = None):
+    """Validated `ParallelDims` as a Result (data_pipeline/trainer/distributed/parallel_dims.py:1640-1678): Ok(dims) or
+    Err(ValueError) when the degrees do not multiply to the world size.  Process groups are created only when a
+    process group of that world size is initialised (or `create_groups` says so)."""
+    from ..core.types import Err, Ok
+    try:
+        cfg = ParallelDimsConfig(dp_replicate, dp_shard, cp, tp, pp, ep, etp, bool(sp and sp > 1), world_size).resolve()
+        if create_groups is None:
+            create_groups = dist.is_initialized() and dist.get_world_size() == world_size
+        return Ok(ParallelDims(cfg, rank=rank if rank is not None else (dist.get_rank() if dist.is_initialized() else 0),
+                               create_groups=create_groups))
+    except ValueError as e:
+        return Err(e)

@@ -13,6 +13,7 @@ GEMM's epilogue over peer memory).
 """
 from __future__ import annotations
 
+import contextlib
 import math
 from dataclasses import dataclass
 
@@ -561,3 +562,139 @@ class ParallelSelfAttention(nn.Module):
         o = o.reshape(B, S, self.h_loc * self.head_dim)
         y = self.o_proj(o.reshape(-1, o.shape[-1]) if sp else o)
         return y.view(B, -1, y.shape[-1]) if sp else y
+
+
+# ------------------------------------------------------------------------------------------------ reference surface
+from typing import NamedTuple  # noqa: E402
+
+
+class CommStats(NamedTuple):
+    """One collective as a profiling record (data_pipeline/trainer/distributed/tensor_parallel.py:121)."""
+    bytes_sent: int
+    bytes_received: int
+    latency_ns: int
+    operation: str
+
+
+@dataclass(frozen=True)
+class TensorParallelConfig:
+    """Switches of a tensor-parallel run (data_pipeline/trainer/distributed/tensor_parallel.py:88-118).  Here
+    `async_communication` / `use_ring_allreduce` / `memory_efficient_linear` describe the library path; the fused
+    path (`comm="fused"` on the TP context) overlaps transfer and GEMM inside one kernel instead."""
+    tensor_parallel_size: int = 1
+    pipeline_parallel_size: int = 1
+    sequence_parallel_enabled: bool = True
+    async_communication: bool = True
+    gradient_accumulation_fusion: bool = True
+    use_ring_allreduce: bool = True
+    fp8_communication: bool = False
+    memory_efficient_linear: bool = True
+    cache_line_aligned: bool = True
+
+    def __post_init__(self):
+        if self.tensor_parallel_size < 1 or self.pipeline_parallel_size < 1:
+            raise ValueError("tensor / pipeline parallel sizes must be >= 1")
+        if self.tensor_parallel_size & (self.tensor_parallel_size - 1):
+            raise ValueError("tensor_parallel_size must be a power of two")
+
+
+def _mgr() -> ProcessGroupManager:
+    return ProcessGroupManager.get()
+
+
+def get_tensor_parallel_rank() -> int:
+    return _mgr().tp_rank if _mgr().initialized else 0
+
+
+def get_tensor_parallel_world_size() -> int:
+    return _mgr().tp_size if _mgr().initialized else 1
+
+
+def get_tensor_parallel_group():
+    return _mgr().tp_group
+
+
+def get_sequence_parallel_rank() -> int:
+    return get_tensor_parallel_rank()          # sequence parallelism shares the tensor group
+
+
+def get_sequence_parallel_world_size() -> int:
+    return get_tensor_parallel_world_size()
+
+
+def is_sequence_parallel_enabled() -> bool:
+    cfg = getattr(_mgr(), "config", None)
+    return bool(cfg is not None and cfg.sequence_parallel_enabled and _mgr().tp_size > 1)
+
+
+@contextlib.contextmanager
+def tensor_parallel_context(config: TensorParallelConfig):
+    """Initialise the process-group registry for `config` (collective when a process group exists) and yield it; on
+    exit the registry is forgotten, the torch process groups stay alive with the job."""
+    mgr = ProcessGroupManager.get()
+    mgr.config = config
+    if dist.is_available() and dist.is_initialized():
+        mgr.initialize(config.tensor_parallel_size, config.pipeline_parallel_size)
+    elif config.tensor_parallel_size * config.pipeline_parallel_size == 1:
+        mgr.initialize(1, 1)
+    try:
+        yield mgr
+    finally:
+        mgr.destroy()
+
+
+def compute_parameter_count(model: nn.Module, include_parallel_factor: bool = True) -> dict:
+    """Local / trainable / tensor-parallel / replicated parameter counts of a tensor-parallel model and, with
+    `include_parallel_factor`, the size of the whole model (parallel parameters x TP size + replicated ones)."""
+    tp = get_tensor_parallel_world_size() if include_parallel_factor else 1
+    parallel = replicated = 0
+    for m in model.modules():
+        own = sum(p.numel() for p in m.parameters(recurse=False))
+        if isinstance(m, (ColumnParallelLinear, RowParallelLinear, VocabParallelEmbedding)) or \
+                getattr(m, "_is_tensor_parallel", False):
+            size = getattr(getattr(m, "tp", None), "size", None)
+            tp = max(tp, size) if include_parallel_factor and size else tp
+            parallel += own
+        else:
+            replicated += own
+    local = parallel + replicated
+    return {"local_params": local, "local_trainable": sum(p.numel() for p in model.parameters() if p.requires_grad),
+            "parallel_params": parallel, "replicated_params": replicated, "tp_world_size": tp,
+            "total_params": parallel * tp + replicated}
+
+
+class FusedColumnParallelLinearWithGELU(nn.Module):
+    """Column-parallel projection followed by GELU (the first half of a classic transformer MLP); the activation runs
+    on the fused elementwise kernel over the local columns, so no gathered pre-activation exists."""
+
+    def __init__(self, in_features: int, out_features: int, tp: TPContext | None = None, *, bias: bool = True,
+                 gather_output: bool = False, sequence_parallel: bool = False, approximate: str = "tanh", dtype=None,
+                 device=None):
+        super().__init__()
+        tp = tp if tp is not None else _mgr().tp_context(sequence_parallel)
+        self.linear = ColumnParallelLinear(in_features, out_features, tp, bias=bias, gather_output=False, dtype=dtype,
+                                           device=device)
+        self.gather_output, self.approximate = gather_output, approximate
+
+    def forward(self, x):
+        from ..ops import activation
+        y = activation.gelu(self.linear(x), self.approximate)
+        return gather_from_tensor_parallel_region(y, self.linear.tp) if self.gather_output else y
+
+
+class FusedRowParallelLinearWithDropout(nn.Module):
+    """Row-parallel projection, reduction over the group, bias, then dropout - in that order, so that the bias is added
+    once and every rank draws the dropout mask on the reduced tensor."""
+
+    def __init__(self, in_features: int, out_features: int, tp: TPContext | None = None, *, bias: bool = True,
+                 input_is_parallel: bool = True, sequence_parallel: bool = False, dropout_prob: float = 0.0, dtype=None,
+                 device=None):
+        super().__init__()
+        tp = tp if tp is not None else _mgr().tp_context(sequence_parallel)
+        self.linear = RowParallelLinear(in_features, out_features, tp, bias=bias, input_is_parallel=input_is_parallel,
+                                        dtype=dtype, device=device)
+        self.dropout_prob = dropout_prob
+
+    def forward(self, x):
+        y = self.linear(x)
+        return torch.nn.functional.dropout(y, self.dropout_prob, self.training) if self.dropout_prob > 0 else y
