@@ -470,3 +470,52 @@ def test_mesh_topology_records_and_tensor_parallel_helpers():
     with pytest.raises(ValueError):
         T.TensorParallelConfig(tensor_parallel_size=3)
     assert T.CommStats(1, 2, 3, "all_reduce").latency_ns == 3
+
+
+def test_dist_utils_expert_parallel_and_ddp_reference_names(tmp_path):
+    import pytest
+    import torch
+
+    from trainscale_b200.parallel import ddp as D
+    from trainscale_b200.parallel import dist_utils as U
+    from trainscale_b200.parallel import ep as E
+    T_ = U.DistributedStateTransition
+    assert T_.allowed(U.StatePhase.INITIALIZING, U.StatePhase.READY) and T_.allowed(U.StatePhase.READY, U.StatePhase.ERROR)
+    assert not T_.allowed(U.StatePhase.READY, U.StatePhase.INITIALIZING)
+    assert U.GradientConfig().max_norm == 1.0 and U.DistributedStrategy.FSDP2.value == "fsdp2"
+    t = torch.ones(2)
+    assert U.dist_scatter(t) is t and U.prepare_scheduler_for_distributed("s") == "s"
+    opt = torch.optim.SGD([torch.nn.Parameter(t)], lr=0.1)
+    assert U.prepare_optimizer_for_distributed(opt, None) is opt
+    with pytest.raises(ValueError):
+        U.prepare_optimizer_for_distributed(opt, None, U.DistributedStrategy.FSDP2)
+    with U.mixed_precision_context(dtype=torch.bfloat16):
+        assert torch.nn.functional.linear(torch.randn(2, 4), torch.randn(3, 4)).dtype == torch.bfloat16
+    U.print_rank_0("rank 0 prints")
+
+    cfg = E.ExpertParallelConfig(num_experts=4, top_k=2, hidden_size=16, capacity_factor=1.0, min_capacity=1)
+    out = E.RouterBase(cfg)(torch.randn(2, 6, 16))
+    T, C = 12, out.metadata["capacity"]
+    assert out.dispatch_mask.shape == (T, 4, C) and out.expert_indices.shape == (T, 2)
+    assert int(out.dispatch_mask.sum()) + out.metadata["dropped"] == T * 2
+    assert out.dispatch_mask.sum(0).max() <= 1                      # one token per (expert, slot)
+    kept = out.dispatch_mask.any(-1)
+    assert torch.allclose(out.combine_weights.sum(-1)[kept], torch.zeros(T, 4).scatter(1, out.expert_indices, out.expert_weights)[kept])
+    probs = torch.softmax(out.router_logits, -1)
+    sw = E.load_balance_loss(E.LoadBalanceLossType.SWITCH, probs, out.expert_indices)
+    st = E.load_balance_loss(E.LoadBalanceLossType.STMOE, probs, out.expert_indices, out.router_logits)
+    assert float(st) > float(sw) > 0 and float(E.load_balance_loss(E.LoadBalanceLossType.VMOE, probs, out.expert_indices)) >= 0
+    assert E.get_expert_parallel_rank() == 0 and E.get_expert_parallel_world_size() == 1
+    assert E.RoutingStrategy.EXPERT_CHOICE.value == "expert_choice"
+
+    class Half(D.GradientCompressionHook):
+        def compress(self, bucket):
+            return bucket.half()
+    b = torch.tensor([1.0, 2.0, 3.0])
+    assert torch.equal(Half()(None, b), torch.tensor([1.0, 2.0, 3.0]))
+    assert D.BucketSchedule.REVERSE == 1 and D.AllReduceAlgorithm.NCCL_AUTO == 3
+    y = tmp_path / "ddp.yaml"
+    y.write_text("distributed:\n  ddp:\n    bucket_cap_mb: 64\n    gradient_compression: bf16\n")
+    r = D.create_ddp_from_yaml(str(y))
+    assert r.is_ok() and r.unwrap().config.bucket_cap_mb == 64
+    assert D.create_ddp_from_yaml(str(tmp_path / "missing.yaml")).is_err()

@@ -427,3 +427,62 @@ def create_ddp_engine(**kw) -> Result:
         return Ok(SOTADDPEngine(**kw))
     except (TypeError, ValueError) as e:
         return Err(e)
+
+
+# ------------------------------------------------------------------------------------------------ reference surface
+from enum import IntEnum  # noqa: E402
+
+
+class AllReduceAlgorithm(IntEnum):
+    RING = 0
+    RECURSIVE_HALVING = 1
+    BUCKET_RECURSIVE = 2
+    NCCL_AUTO = 3
+
+
+class BucketSchedule(IntEnum):
+    """Order in which gradient buckets are reduced: as they fill (FIFO), last layer first (REVERSE: the order backward
+    produces them), largest first, or intra-node before inter-node."""
+    FIFO = 0
+    REVERSE = 1
+    SIZE_PRIORITY = 2
+    TOPOLOGY_AWARE = 3
+
+
+class GradientCompressionHook:
+    """Base of the bucket hooks: `hook(group, bucket) -> averaged bucket`.  Subclasses override `compress` /
+    `decompress`; the base implementation all-reduces the compressed form and averages
+    (data_pipeline/trainer/distributed/ddp.py:796-830)."""
+
+    def __init__(self, process_group=None):
+        ready = dist.is_available() and dist.is_initialized()
+        self._process_group = process_group or (dist.group.WORLD if ready else None)
+        self._world_size = dist.get_world_size(self._process_group) if ready else 1
+        self._rank = dist.get_rank(self._process_group) if ready else 0
+        self._metrics = DDPMetrics()
+        self.__name__ = type(self).__name__
+
+    def compress(self, bucket: torch.Tensor) -> torch.Tensor:
+        return bucket
+
+    def decompress(self, payload: torch.Tensor, like: torch.Tensor) -> torch.Tensor:
+        return payload.to(like.dtype)
+
+    def __call__(self, group, bucket: torch.Tensor) -> torch.Tensor:
+        group = group if group is not None else self._process_group
+        payload = self.compress(bucket)
+        if self._world_size > 1:
+            dist.all_reduce(payload, group=group)
+        bucket.copy_(self.decompress(payload, bucket).div_(self._world_size))
+        return bucket
+
+
+def create_ddp_from_yaml(config_path: str):
+    """`SOTADDPEngine` from the `distributed.ddp` section of a YAML file, as a Result."""
+    try:
+        import yaml
+        with open(config_path) as f:
+            section = (yaml.safe_load(f) or {}).get("distributed", {}).get("ddp", {})
+        return create_ddp_engine(**section)
+    except Exception as e:   # noqa: BLE001 - reported through the Result
+        return Err(e)

@@ -15,6 +15,7 @@ import random
 import time
 from dataclasses import dataclass
 from enum import Enum
+from typing import NamedTuple
 
 import numpy as np
 import torch
@@ -668,3 +669,84 @@ class FaultInjector:
         """Heartbeat unless this rank has been muted."""
         if not self.muted:
             monitor.beat()
+
+
+# ------------------------------------------------------------------------------------------------ reference surface
+class StatePhase(Enum):
+    """Lifecycle of the distributed state (data_pipeline/trainer/distributed/sota_utils.py:655)."""
+    UNINITIALIZED = 0
+    INITIALIZING = 1
+    READY = 2
+    SHUTTING_DOWN = 3
+    TERMINATED = 4
+    ERROR = 5
+
+
+class DistributedStateTransition(Enum):
+    UNINITIALIZED_TO_INITIALIZING = (StatePhase.UNINITIALIZED, StatePhase.INITIALIZING)
+    INITIALIZING_TO_READY = (StatePhase.INITIALIZING, StatePhase.READY)
+    READY_TO_SHUTTING_DOWN = (StatePhase.READY, StatePhase.SHUTTING_DOWN)
+    SHUTTING_DOWN_TO_TERMINATED = (StatePhase.SHUTTING_DOWN, StatePhase.TERMINATED)
+    ANY_TO_ERROR = (None, StatePhase.ERROR)
+
+    @classmethod
+    def allowed(cls, src: StatePhase, dst: StatePhase) -> bool:
+        return dst is StatePhase.ERROR or any(t.value == (src, dst) for t in cls)
+
+
+class DistributedStrategy(Enum):
+    NONE = "none"
+    DDP = "ddp"
+    FSDP = "fsdp"
+    FSDP2 = "fsdp2"
+    TENSOR_PARALLEL = "tensor_parallel"
+    PIPELINE = "pipeline"
+
+
+class GradientConfig(NamedTuple):
+    max_norm: float = 1.0
+    norm_type: float = 2.0
+    clip_algorithm: str = "global"
+    compression: str | None = None
+    sync_before_clip: bool = False
+
+
+def dist_scatter(tensor: torch.Tensor, scatter_list=None, src: int = 0, process_group=None) -> torch.Tensor:
+    """Rank `src` hands element r of `scatter_list` to rank r; returns `tensor` (unchanged without a process group)."""
+    if dist.is_available() and dist.is_initialized():
+        dist.scatter(tensor, scatter_list=scatter_list if dist.get_rank(process_group) == src else None, src=src,
+                     group=process_group)
+    return tensor
+
+
+@contextlib.contextmanager
+def mixed_precision_context(enabled: bool = True, dtype: torch.dtype = torch.bfloat16, cache_enabled: bool = True):
+    """torch autocast for modules OUTSIDE the framework (its own kernels compute in the dtype of their inputs and
+    ignore autocast)."""
+    if not enabled:
+        yield
+        return
+    with torch.autocast("cuda" if torch.cuda.is_available() else "cpu", dtype=dtype, cache_enabled=cache_enabled):
+        yield
+
+
+def prepare_optimizer_for_distributed(optimizer, model, strategy=DistributedStrategy.DDP):
+    """An optimizer built on the module's parameters needs nothing under DDP.  Under the sharded engine the ENGINE owns
+    the update (fp32 master shards, fused AdamW): a torch optimizer passed here would update full-size parameters
+    the engine overwrites, so that combination is refused."""
+    kind = getattr(strategy, "value", strategy)
+    if kind in ("fsdp", "fsdp2") and not hasattr(optimizer, "engine"):
+        raise ValueError("with the sharded engine the optimizer step is engine.step(); build the engine with the "
+                         "optimizer's hyper-parameters instead of wrapping a torch optimizer")
+    return optimizer
+
+
+def prepare_scheduler_for_distributed(scheduler, state=None):
+    """Schedules depend on the step count only, which every rank shares: returned unchanged."""
+    return scheduler
+
+
+def print_rank_0(*args, flush: bool = True, **kwargs) -> None:
+    if dist.is_available() and dist.is_initialized() and dist.get_rank() != 0:
+        return
+    print(*args, flush=flush, **kwargs)

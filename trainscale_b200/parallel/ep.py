@@ -576,3 +576,95 @@ class ExpertParallelEngine:
 
     def memory_summary(self):
         return f"ep={self.ep_size} | dense: {self.dense.memory_summary()} | experts: {self.expert.memory_summary()}"
+
+
+# ------------------------------------------------------------------------------------------------ reference surface
+from enum import Enum  # noqa: E402
+from typing import NamedTuple  # noqa: E402
+
+
+class RoutingStrategy(Enum):
+    TOP_K = "top_k"
+    EXPERT_CHOICE = "expert_choice"
+    SOFT_MOE = "soft"
+    HASH_ROUTING = "hash"
+
+
+class LoadBalanceLossType(Enum):
+    SWITCH = "switch"        # E * sum_e f_e P_e
+    GSHARD = "gshard"        # the same on the top-1 assignment only
+    STMOE = "stmoe"          # Switch term + z-loss
+    VMOE = "vmoe"            # squared coefficient of variation of importance and of load
+
+
+class RoutingOutput(NamedTuple):
+    """Dense (capacity-slotted) view of a routing decision (data_pipeline/trainer/distributed/expert_parallel.py:67)."""
+    dispatch_mask: torch.Tensor       # [T, E, C] bool
+    combine_weights: torch.Tensor     # [T, E, C]
+    expert_indices: torch.Tensor      # [T, k]
+    expert_weights: torch.Tensor      # [T, k]
+    router_logits: torch.Tensor       # [T, E]
+    auxiliary_loss: torch.Tensor
+    metadata: dict
+
+
+def get_expert_parallel_rank(group=None) -> int:
+    return dist.get_rank(group=group) if dist.is_available() and dist.is_initialized() else 0
+
+
+def get_expert_parallel_world_size(group=None) -> int:
+    return dist.get_world_size(group=group) if dist.is_available() and dist.is_initialized() else 1
+
+
+def load_balance_loss(kind: LoadBalanceLossType, probs: torch.Tensor, expert_indices: torch.Tensor,
+                      logits: torch.Tensor | None = None, z_weight: float = 1e-3) -> torch.Tensor:
+    """Auxiliary loss of the chosen flavour from router probabilities [T, E] and chosen experts [T, k]."""
+    E = probs.shape[1]
+    hot = F.one_hot(expert_indices, E).float()
+    if kind is LoadBalanceLossType.GSHARD:
+        hot = hot[:, :1]
+    f = hot.sum(1).mean(0) / hot.shape[1]
+    P = probs.mean(0)
+    if kind is LoadBalanceLossType.VMOE:
+        cv2 = lambda v: v.var() / v.mean().clamp(min=1e-9) ** 2      # noqa: E731
+        return cv2(probs.sum(0)) + cv2(hot.sum((0, 1)))
+    loss = E * (f * P).sum()
+    if kind is LoadBalanceLossType.STMOE and logits is not None:
+        loss = loss + z_weight * torch.logsumexp(logits.float(), -1).pow(2).mean()
+    return loss
+
+
+class RouterBase(nn.Module):
+    """Common part of a router: the projection hidden -> experts (small initial weights), the auxiliary loss, and the
+    conversion of a top-k decision into the dense capacity-slotted `RoutingOutput`.  Subclasses implement `route`."""
+
+    def __init__(self, config: ExpertParallelConfig, loss_type: LoadBalanceLossType = LoadBalanceLossType.SWITCH):
+        super().__init__()
+        self.config, self.loss_type = config, loss_type
+        self.router = nn.Linear(config.hidden_size, config.num_experts, bias=False)
+        nn.init.normal_(self.router.weight, std=0.01)
+
+    def route(self, logits: torch.Tensor):
+        """logits [T, E] -> (weights [T, k], experts [T, k], probs [T, E]); top-k soft-max by default."""
+        from ..ops import moe as moe_ops
+        return moe_ops.topk_softmax(logits, self.config.top_k, self.config.normalize_topk)
+
+    def forward(self, x: torch.Tensor) -> RoutingOutput:
+        cfg = self.config
+        flat = x.reshape(-1, x.shape[-1])
+        logits = self.router(flat).float()
+        w, idx, probs = self.route(logits)
+        T, E = probs.shape
+        C = moe_capacity(T, E, cfg.top_k, cfg.capacity_factor, cfg.min_capacity)
+        # slot of every (token, choice) inside its expert: rank among the earlier slots routed to the same expert
+        hot = F.one_hot(idx.reshape(-1), E)                                        # [T*k, E]
+        slot = (hot.cumsum(0) - hot).gather(1, idx.reshape(-1, 1)).reshape(T, cfg.top_k)
+        keep = slot < C
+        dispatch = torch.zeros(T, E, C, dtype=torch.bool, device=x.device)
+        combine = torch.zeros(T, E, C, dtype=w.dtype, device=x.device)
+        t = torch.arange(T, device=x.device)[:, None].expand_as(idx)
+        dispatch[t[keep], idx[keep], slot[keep]] = True
+        combine[t[keep], idx[keep], slot[keep]] = w[keep]
+        aux = cfg.aux_loss_weight * load_balance_loss(self.loss_type, probs, idx, logits, cfg.z_loss_weight)
+        meta = {"capacity": C, "dropped": int((~keep).sum()), "tokens_per_expert": hot.sum(0)}
+        return RoutingOutput(dispatch, combine, idx, w, logits, aux, meta)
