@@ -508,3 +508,78 @@ def test_checkpoint_catalogue_contracts_and_layer_patches():
     m = net[0]
     want = m.down_proj(F.gelu(m.gate_proj(x), approximate="tanh") * m.up_proj(x))
     assert torch.allclose(net(x), want, atol=1e-5)
+
+
+def test_optimizer_helpers_core_records_and_presets():
+    import os
+
+    import pytest
+    import torch
+
+    from trainscale_b200 import optim as O
+    from trainscale_b200.config import sota_config as S
+    from trainscale_b200.config import training_args as T
+    from trainscale_b200.core.errors import DeviceNotAvailableError, EarlyStoppingError, TrainingLoopError
+    from trainscale_b200.core.types import CheckpointStrategy, GradientInfo, StepMetrics, WarmupType
+    m = torch.nn.Linear(256, 256)
+    m(torch.randn(4, 256)).sum().backward()
+    total, mx, mn = O.compute_grad_norm(m.parameters())
+    want = torch.sqrt(m.weight.grad.pow(2).sum() + m.bias.grad.pow(2).sum())
+    assert abs(total - float(want)) < 1e-2 and mx >= mn > 0
+    info = O.clip_grad_value_(m.parameters(), 0.01)
+    assert isinstance(info, GradientInfo) and info.clipped and float(m.weight.grad.abs().max()) <= 0.01
+    opt = O.create_adafactor_for_llm(m.parameters(), "70b")
+    opt.step()
+    assert opt.param_groups[0]["clip_threshold"] == 0.5
+    fp = O.get_optimizer_memory_footprint(opt)
+    assert fp["compression_ratio"] > 50 and fp["total_bytes"] > 0          # factored moments: rows + columns
+    assert O.check_optimizer_compatibility(opt, m)["is_compatible"]
+    extra = torch.nn.Linear(2, 2)
+    bad = O.check_optimizer_compatibility(opt, torch.nn.Sequential(m, extra))
+    assert not bad["is_compatible"] and any("not in the optimizer" in w for w in bad["warnings"])
+    assert O.determine_factorization((4096, 4096)) is O.FactorizationMode.BLOCK
+    assert O.determine_factorization((512, 512)) is O.FactorizationMode.ROW_COL
+    assert O.determine_factorization((64, 4096)) is O.FactorizationMode.NONE
+    assert O.compute_rho_jit(0, -0.8) == 0.0 and O.compute_rho_jit(10 ** 6, -0.8) == 0.999
+    assert abs(O.compute_rms_jit(torch.full((10,), 3.0)) - 3.0) < 1e-6
+
+    class SignSGD(O.BaseOptimizer):
+        def __init__(self, params, lr=0.1):
+            super().__init__(params, dict(lr=lr, max_grad_norm=1.0))
+
+        def _update(self, p, g, st, grp):
+            p.add_(g.sign(), alpha=-grp["lr"])
+    w0 = m.weight.detach().clone()
+    o2 = SignSGD(m.parameters())
+    o2.step()
+    assert abs(float((m.weight - w0).abs().max()) - 0.1) < 1e-6 and o2.metrics.total_steps == 1
+    assert o2.lifecycle is O.OptimizerState.STEPPED and o2.state[m.weight]["step"] == 1
+    k = O.KahanAccumulator()
+    for _ in range(10):
+        k.add(0.1)
+    assert k.value == 1.0
+    st = O.AdaFactorState((8, 16), "cpu", torch.float32, True, True).initialize()
+    assert st.memory_bytes() == (8 + 16 + 128) * 4 and st.snapshot().exp_avg_sq is None
+    assert O.AdaFactorConfig(lr=1e-3, relative_step=False).build(m.parameters()).defaults["lr"] == 1e-3
+    assert O.create_lamb(m.parameters(), max_trust_ratio=5.0).defaults["clamp_trust"] == (0.0, 5.0)
+    assert O.create_adamw(m.parameters(), max_grad_norm=1.0).max_grad_norm == 1.0 and O.get_triton_version() is None
+    x = torch.randn(3, 5)
+    assert torch.allclose(O.stable_softmax(x), torch.softmax(x, -1), atol=1e-6)
+
+    e = EarlyStoppingError(metric_name="loss", metric_value=1.0, patience=3)
+    assert isinstance(e, TrainingLoopError) and e.patience == 3 and "patience=3" in str(e)
+    assert DeviceNotAvailableError("no gpu", "cuda", ("cpu",)).available_devices == ("cpu",)
+    assert WarmupType("linear") is WarmupType.LINEAR and CheckpointStrategy.BEST_AND_LAST.value == "best_and_last"
+    assert StepMetrics(1.0, 1e-4, 0.5, 1e4, 100.0, 12.0).component_losses is None
+
+    c = S.get_dpo_preset("m")
+    assert c.loss.type is S.LossType.DPO and c.rl.algorithm is S.RLAlgorithm.DPO and c.rl.enabled
+    assert S.get_export_gguf_preset("/o", "q8_0").format is S.ExportFormat.GGUF_Q8
+    with pytest.raises(ValueError):
+        S.get_export_gguf_preset("/o", "q3")
+    assert T.get_qlora_config("m", r=8).lora_alpha == 16 and T.get_pretraining_config("m").pack_sequences
+    assert T.get_full_finetune_config("m").to_sota_dict()["optimizer"]["learning_rate"] == 1e-5
+    os.environ["TS_TEST_OUT"] = "/tmp/ts_x"
+    assert T.load_training_config_from_dict({"output_dir": "${TS_TEST_OUT}"}).output_dir == "/tmp/ts_x"
+    with pytest.raises(ValueError, match="learning_rate"):
+        T.load_training_config_from_dict({"learning_rate": "abc"})

@@ -516,3 +516,22 @@ def get_pretrain_preset(model: str = "") -> SOTAConfig:
     return SOTAConfig(training_mode=TrainingMode.PRETRAIN, model=ModelConfig(name_or_path=model),
                       lora=LoRAConfig(enabled=False), optimizer=OptimizerConfig(learning_rate=3e-4, weight_decay=0.1),
                       scheduler=SchedulerConfig(type=SchedulerType.WSD, warmup_ratio=0.01))
+
+
+def get_dpo_preset(model: str = "") -> SOTAConfig:
+    """Preference optimisation with the DPO loss (beta 0.1) against a frozen copy of the starting weights."""
+    return SOTAConfig(training_mode=TrainingMode.RL, model=ModelConfig(name_or_path=model),
+                      rl=RLConfig(enabled=True, algorithm=RLAlgorithm.DPO),
+                      loss=LossConfig(type=LossType.DPO, dpo_beta=0.1), optimizer=OptimizerConfig(learning_rate=5e-7))
+
+
+_GGUF_FORMATS = {"q4_k_m": ExportFormat.GGUF_Q4, "q5_k_m": ExportFormat.GGUF_Q5, "q8_0": ExportFormat.GGUF_Q8,
+                 "f16": ExportFormat.GGUF_F16}
+
+
+def get_export_gguf_preset(output_dir: str, quant: str = "q4_k_m") -> ExportConfig:
+    """Export section for a GGUF file of the given quantisation (adapters merged first)."""
+    if quant not in _GGUF_FORMATS:
+        raise ValueError(f"unknown GGUF quantisation {quant!r}; choose from {sorted(_GGUF_FORMATS)}")
+    return ExportConfig(enabled=True, output_dir=output_dir, format=_GGUF_FORMATS[quant], gguf_quantization=quant,
+                        merge_lora=True)

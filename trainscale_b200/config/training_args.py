@@ -190,3 +190,41 @@ def get_memory_efficient_config() -> TrainingConfig:
 
 def get_high_throughput_config() -> TrainingConfig:
     return TrainingConfig(batch_size=8, gradient_accumulation_steps=1, strategy="fsdp2", gradient_checkpointing=False)
+
+
+def get_qlora_config(model_name: str, r: int = 16, max_seq_length: int = 2048) -> TrainingConfig:
+    """Adapters of rank r (alpha 2r) on a quantised base, packed sequences
+    (data_pipeline/trainer/training_config.py:230)."""
+    c = TrainingConfig(model_name=model_name, use_lora=True, lora_r=r, max_seq_length=max_seq_length,
+                       learning_rate=2e-4, strategy="ddp")
+    c.load_in_4bit, c.lora_alpha, c.pack_sequences = True, 2 * r, True
+    return c
+
+
+def get_full_finetune_config(model_name: str, max_seq_length: int = 2048) -> TrainingConfig:
+    c = TrainingConfig(model_name=model_name, use_lora=False, max_seq_length=max_seq_length, learning_rate=1e-5,
+                       precision="bf16", strategy="fsdp2", gradient_checkpointing=True)
+    c.load_in_4bit, c.pack_sequences = False, False
+    return c
+
+
+def get_pretraining_config(model_name: str, max_seq_length: int = 4096) -> TrainingConfig:
+    c = TrainingConfig(model_name=model_name, use_lora=False, max_seq_length=max_seq_length, learning_rate=3e-4,
+                       warmup_ratio=0.01, precision="bf16", strategy="fsdp2", gradient_checkpointing=True)
+    c.load_in_4bit, c.pack_sequences = False, True
+    return c
+
+
+def load_training_config_from_dict(config_dict: Dict[str, Any], *, interpolate_env: bool = True) -> TrainingArguments:
+    """Validated `TrainingArguments` from a dictionary; `${VAR}` / `${VAR:default}` strings are replaced from the
+    environment first.  Validation problems are raised as one ValueError that lists every offending field."""
+    raw = interpolate_env_vars(config_dict) if interpolate_env else config_dict
+    raw = raw.get("training_arguments", raw)
+    try:
+        return TrainingArguments(**raw)
+    except Exception as e:    # noqa: BLE001 - pydantic's ValidationError, re-worded
+        details = getattr(e, "errors", None)
+        if callable(details):
+            lines = [f"{'.'.join(str(p) for p in d.get('loc', ()))}: {d.get('msg')}" for d in details()]
+            raise ValueError("invalid training configuration:\n  " + "\n  ".join(lines)) from e
+        raise

@@ -107,3 +107,47 @@ def flat_map(r, fn: Callable):
 
 def map_err(r, fn: Callable):
     return Err(fn(r.error)) if isinstance(r, Err) else r
+
+
+# ------------------------------------------------------------------------------------------------ training records
+import enum  # noqa: E402
+from typing import Dict, Optional  # noqa: E402
+
+
+class WarmupType(str, enum.Enum):
+    """How the learning rate ramps up (data_pipeline/trainer/core/types.py:440)."""
+    NONE = "none"
+    LINEAR = "linear"
+    EXPONENTIAL = "exponential"
+    CONSTANT = "constant"
+
+
+class CheckpointStrategy(str, enum.Enum):
+    STEPS = "steps"
+    EPOCH = "epoch"
+    BEST = "best"
+    BEST_AND_LAST = "best_and_last"
+    NO = "no"
+
+
+@dataclass(frozen=True)
+class GradientInfo:
+    """Gradient statistics of one step (data_pipeline/trainer/core/types.py:652)."""
+    global_norm: float
+    max_norm: float
+    min_norm: float
+    clipped: bool
+    overflow: bool
+    scale_factor: float = 1.0
+    layer_norms: Optional[Dict[str, float]] = None
+
+
+@dataclass(frozen=True)
+class StepMetrics:
+    loss: float
+    lr: float
+    grad_norm: float
+    throughput: float
+    gpu_memory_mb: float
+    step_time_ms: float
+    component_losses: Optional[Dict[str, float]] = None

@@ -738,3 +738,333 @@ def create_optimizer(params, config=None, name: str | None = None, **kw) -> Opti
     if name not in _OPTIMIZERS:
         raise ValueError(f"unknown optimizer {name!r}; choose from {sorted(_OPTIMIZERS)}")
     return _OPTIMIZERS[name](params, **kw)
+
+
+# ------------------------------------------------------------------------------------------------ reference surface
+import math as _math  # noqa: E402
+from dataclasses import dataclass as _dataclass, field as _field  # noqa: E402
+from enum import Enum as _Enum, IntEnum as _IntEnum  # noqa: E402
+from typing import NamedTuple as _NamedTuple  # noqa: E402
+
+
+class FactorizationMode(_IntEnum):
+    NONE = 1
+    ROW_COL = 2
+    BLOCK = 3
+
+
+class QuantizationMode(_Enum):
+    NONE = "none"
+    DYNAMIC_8BIT = "dynamic_8bit"
+    BLOCK_WISE_8BIT = "block_wise_8bit"
+    STOCHASTIC_8BIT = "stochastic_8bit"
+
+
+class OptimizerState(_Enum):
+    UNINITIALIZED = "uninitialized"
+    INITIALIZED = "initialized"
+    STEPPED = "stepped"
+    CLOSED = "closed"
+
+
+@_dataclass(frozen=True)
+class AdaFactorConfig:
+    """Hyper-parameters of `AdaFactor` as one immutable record (data_pipeline/trainer/optimizers/adafactor.py:117);
+    `build(params)` makes the optimizer."""
+    lr: float | None = None
+    eps1: float = 1e-30
+    eps2: float = 1e-3
+    clip_threshold: float = 1.0
+    decay_rate: float = -0.8
+    beta1: float | None = None
+    weight_decay: float = 0.0
+    scale_parameter: bool = True
+    relative_step: bool = True
+    warmup_init: bool = False
+    warmup_steps: int = 10000
+    min_lr: float = 1e-6
+    max_lr: float = 1.0
+    factorization_threshold: int = 128
+
+    def build(self, params) -> "AdaFactor":
+        return AdaFactor(params, lr=self.lr, eps=(self.eps1, self.eps2), clip_threshold=self.clip_threshold,
+                         decay_rate=self.decay_rate, beta1=self.beta1, weight_decay=self.weight_decay,
+                         scale_parameter=self.scale_parameter, relative_step=self.relative_step,
+                         warmup_init=self.warmup_init)
+
+
+class ParamState(_NamedTuple):
+    step: int
+    factored: bool
+    exp_avg: torch.Tensor | None
+    exp_avg_sq: torch.Tensor | None
+    exp_avg_sq_row: torch.Tensor | None
+    exp_avg_sq_col: torch.Tensor | None
+    kahan_comp: torch.Tensor | None = None
+
+
+class AdaFactorState:
+    """State of one parameter, allocated on first use: factored row / column second moments for matrices, a full
+    second moment otherwise, optional first moment and Kahan compensation.  `snapshot()` gives a `ParamState`."""
+
+    def __init__(self, shape, device, dtype, factored: bool, use_momentum: bool, use_kahan: bool = False):
+        self.step, self.factored, self.shape, self.device, self.dtype = 0, factored and len(shape) >= 2, tuple(shape), device, dtype
+        self.use_momentum, self.use_kahan = use_momentum, use_kahan
+        self.exp_avg = self.exp_avg_sq = self.exp_avg_sq_row = self.exp_avg_sq_col = self.kahan_comp = None
+        self.is_initialized = False
+
+    def initialize(self) -> "AdaFactorState":
+        z = lambda s: torch.zeros(s, device=self.device, dtype=torch.float32)      # noqa: E731
+        if self.factored:
+            self.exp_avg_sq_row, self.exp_avg_sq_col = z(self.shape[:-1]), z(self.shape[:-2] + self.shape[-1:])
+        else:
+            self.exp_avg_sq = z(self.shape)
+        if self.use_momentum:
+            self.exp_avg = z(self.shape)
+        if self.use_kahan:
+            self.kahan_comp = z(self.shape)
+        self.is_initialized = True
+        return self
+
+    def memory_bytes(self) -> int:
+        return sum(t.numel() * t.element_size() for t in (self.exp_avg, self.exp_avg_sq, self.exp_avg_sq_row,
+                                                          self.exp_avg_sq_col, self.kahan_comp) if t is not None)
+
+    def snapshot(self) -> ParamState:
+        return ParamState(self.step, self.factored, self.exp_avg, self.exp_avg_sq, self.exp_avg_sq_row,
+                          self.exp_avg_sq_col, self.kahan_comp)
+
+
+@_dataclass
+class ProfilingStats:
+    total_step_time_ns: int = 0
+    kernel_time_ns: int = 0
+    memory_allocated_bytes: int = 0
+    memory_peak_bytes: int = 0
+    num_factorized_params: int = 0
+    num_full_params: int = 0
+    triton_kernel_calls: int = 0
+    fused_updates: int = 0
+
+
+@_dataclass
+class OptimizerMetrics:
+    total_steps: int = 0
+    total_params: int = 0
+    kernel_time_ns: int = 0
+    memory_allocated_bytes: int = 0
+    grad_norm_history: list = _field(default_factory=list)
+
+    def record_step(self, grad_norm: float, kernel_time_ns: int = 0) -> None:
+        self.total_steps += 1
+        self.kernel_time_ns += kernel_time_ns
+        if len(self.grad_norm_history) < 1000:
+            self.grad_norm_history.append(float(grad_norm))
+
+
+def compute_rms_jit(tensor: torch.Tensor, eps: float = 1e-30) -> float:
+    return float(torch.sqrt(tensor.float().pow(2).mean().clamp(min=eps)))
+
+
+def compute_rho_jit(step: int, decay_rate: float, max_rho: float = 0.999) -> float:
+    """Second-moment decay of AdaFactor at `step`: min(1 - (step + 1)^decay_rate, max_rho)."""
+    return min(1.0 - _math.pow(float(step + 1), decay_rate), max_rho)
+
+
+def determine_factorization(shape, threshold: int = 128) -> FactorizationMode:
+    """NONE for vectors and for matrices with a side below `threshold`; ROW_COL for matrices; BLOCK above 10M values."""
+    if len(shape) < 2 or shape[-1] < threshold or shape[-2] < threshold:
+        return FactorizationMode.NONE
+    return FactorizationMode.BLOCK if _math.prod(shape) > 10_000_000 else FactorizationMode.ROW_COL
+
+
+def get_triton_block_config(numel: int, dtype=None) -> tuple[int, int, int]:
+    """(block, warps, stages) the reference's Triton update kernels would pick; informational (the CUDA update kernels
+    here use fixed 256-thread blocks with 16-byte accesses)."""
+    return (256, 2, 2) if numel < 1024 else (512, 4, 2) if numel < 16384 else (1024, 8, 3) if numel < 131072 else (2048, 8, 4)
+
+
+def get_triton_version():
+    """Triton is not used by this framework."""
+    return None
+
+
+def create_adamw(params, lr: float = 1e-3, betas=(0.9, 0.999), eps: float = 1e-8, weight_decay: float = 0.01,
+                 amsgrad: bool = False, max_grad_norm: float | None = None, use_triton: bool = True) -> AdamW:
+    opt = AdamW(params, lr=lr, betas=betas, eps=eps, weight_decay=weight_decay, amsgrad=amsgrad, fused=True)
+    opt.max_grad_norm = max_grad_norm
+    return opt
+
+
+def create_lion(params, lr: float = 1e-4, betas=(0.9, 0.99), weight_decay: float = 0.0, use_triton: bool = True) -> Lion:
+    return Lion(params, lr=lr, betas=betas, weight_decay=weight_decay)
+
+
+def create_lamb(params, lr: float = 1e-3, betas=(0.9, 0.999), eps: float = 1e-6, weight_decay: float = 0.01,
+                max_trust_ratio: float = 10.0) -> LAMB:
+    return LAMB(params, lr=lr, betas=betas, eps=eps, weight_decay=weight_decay, clamp_trust=(0.0, max_trust_ratio))
+
+
+def create_adafactor(params, lr: float | None = None, eps=(1e-30, 1e-3), clip_threshold: float = 1.0,
+                     decay_rate: float = -0.8, beta1: float | None = None, weight_decay: float = 0.0,
+                     scale_parameter: bool = True, relative_step: bool = True, warmup_init: bool = False,
+                     **_ignored) -> AdaFactor:
+    return AdaFactor(params, lr=lr, eps=eps, clip_threshold=clip_threshold, decay_rate=decay_rate, beta1=beta1,
+                     weight_decay=weight_decay, scale_parameter=scale_parameter, relative_step=relative_step,
+                     warmup_init=warmup_init)
+
+
+_ADAFACTOR_BY_SIZE = {"1b": dict(clip_threshold=1.0), "7b": dict(clip_threshold=1.0), "13b": dict(clip_threshold=0.8),
+                      "70b": dict(clip_threshold=0.5), "175b": dict(clip_threshold=0.3)}
+
+
+def create_adafactor_for_llm(params, model_size: str = "7b", **kwargs) -> AdaFactor:
+    """AdaFactor with relative step, parameter scaling and warm-up initialisation, and an update clip that tightens with
+    model size (1.0 up to 7B, 0.8 at 13B, 0.5 at 70B, 0.3 at 175B)."""
+    cfg = dict(_ADAFACTOR_BY_SIZE.get(model_size.lower(), _ADAFACTOR_BY_SIZE["7b"]))
+    cfg.update(kwargs)
+    return create_adafactor(params, lr=None, relative_step=True, scale_parameter=True, warmup_init=True, **cfg)
+
+
+class KahanAccumulator:
+    """Compensated running sum of floats."""
+    __slots__ = ("_sum", "_compensation")
+
+    def __init__(self, initial: float = 0.0):
+        self._sum, self._compensation = float(initial), 0.0
+
+    def add(self, value: float) -> None:
+        y = value - self._compensation
+        t = self._sum + y
+        self._compensation = (t - self._sum) - y
+        self._sum = t
+
+    @property
+    def value(self) -> float:
+        return self._sum
+
+
+def stable_softmax(x: torch.Tensor, dim: int = -1) -> torch.Tensor:
+    e = torch.exp(x - x.max(dim=dim, keepdim=True).values)
+    return e / e.sum(dim=dim, keepdim=True)
+
+
+def safe_sqrt(x: torch.Tensor, eps: float = 1e-8) -> torch.Tensor:
+    return torch.sqrt(x + eps)
+
+
+def rms_norm(x: torch.Tensor, eps: float = 1e-8) -> torch.Tensor:
+    return torch.sqrt(torch.mean(x * x) + eps)
+
+
+class GradScalerProtocol:
+    """What an optimizer expects of a loss scaler: `get_scale()` and `update(new_scale=None)`
+    (`parallel.dist_utils.GradScaler` and `torch.amp.GradScaler` both qualify)."""
+
+    def get_scale(self) -> float: ...
+    def update(self, new_scale: float | None = None) -> None: ...
+
+
+class BaseOptimizer(Optimizer):
+    """Base for optimizers written as one `_update(p, grad, state, group)` rule: lazy per-parameter state, optional
+    global-norm clipping before the update (`max_grad_norm` in the defaults), step metrics.
+    (data_pipeline/trainer/optimizers/base.py:248, sota_optimizers.py:539)"""
+
+    def __init__(self, params, defaults: dict, *, foreach=None, differentiable: bool = False):
+        defaults = dict(defaults)
+        defaults.setdefault("max_grad_norm", None)
+        super().__init__(params, defaults)
+        self.metrics = OptimizerMetrics(total_params=sum(p.numel() for g in self.param_groups for p in g["params"]))
+        self.lifecycle = OptimizerState.INITIALIZED
+
+    def _init_state(self, p: torch.Tensor, group: dict) -> dict:
+        return {"step": 0}
+
+    def _update(self, p: torch.Tensor, grad: torch.Tensor, state: dict, group: dict) -> None:
+        raise NotImplementedError
+
+    @torch.no_grad()
+    def step(self, closure=None):
+        loss = None
+        if closure is not None:
+            with torch.enable_grad():
+                loss = closure()
+        norm = 0.0
+        for g in self.param_groups:
+            ps = [p for p in g["params"] if p.grad is not None]
+            if g.get("max_grad_norm"):
+                norm = float(clip_grad_norm_(ps, g["max_grad_norm"]))
+            for p in ps:
+                st = self.state[p]
+                if not st:
+                    st.update(self._init_state(p, g))
+                st["step"] = st.get("step", 0) + 1
+                self._update(p, p.grad, st, g)
+        self.metrics.record_step(norm)
+        self.lifecycle = OptimizerState.STEPPED
+        return loss
+
+
+BaseApexOptimizer = BaseOptimizer
+
+
+def compute_grad_norm(parameters, norm_type: float = 2.0) -> tuple[float, float, float]:
+    """(global norm, largest per-parameter norm, smallest per-parameter norm) of the gradients present."""
+    norms = [torch.linalg.vector_norm(p.grad.detach().float(), norm_type) for p in parameters if p.grad is not None]
+    if not norms:
+        return 0.0, 0.0, 0.0
+    stacked = torch.stack(norms)
+    total = stacked.max() if norm_type == float("inf") else torch.linalg.vector_norm(stacked, norm_type)
+    return float(total), float(stacked.max()), float(stacked.min())
+
+
+def clip_grad_value_(parameters, clip_value: float):
+    """Clamp every gradient element to [-clip_value, clip_value] in place; returns `core.types.GradientInfo` with the
+    norms BEFORE clamping."""
+    from ..core.types import GradientInfo
+    ps = [p for p in parameters if p.grad is not None]
+    total, mx, mn = compute_grad_norm(ps)
+    clipped = any(bool((p.grad.abs() > clip_value).any()) for p in ps)
+    overflow = any(not bool(torch.isfinite(p.grad).all()) for p in ps)
+    for p in ps:
+        p.grad.clamp_(-clip_value, clip_value)
+    return GradientInfo(total, mx, mn, clipped, overflow)
+
+
+def get_optimizer_memory_footprint(optimizer: Optimizer, param_bytes: int = 4) -> dict:
+    """Bytes held in optimizer state, per state key, and the ratio to the two fp32 moments of plain Adam."""
+    by_key: dict[str, int] = {}
+    n_params = 0
+    for g in optimizer.param_groups:
+        for p in g["params"]:
+            n_params += p.numel()
+            for k, v in optimizer.state.get(p, {}).items():
+                if torch.is_tensor(v):
+                    by_key[k] = by_key.get(k, 0) + v.numel() * v.element_size()
+    total = sum(by_key.values())
+    return {"total_bytes": total, "state_bytes": by_key, "param_bytes": n_params * param_bytes,
+            "compression_ratio": (2 * 4 * n_params) / total if total else float("inf")}
+
+
+def check_optimizer_compatibility(optimizer: Optimizer, model) -> dict:
+    """Things that make an optimizer / model pair fail or waste memory: sparse or meta parameters, trainable parameters
+    the optimizer does not hold, parameters it holds that the model does not have, half-precision parameters without
+    fp32 masters."""
+    warnings, recommendations = [], []
+    held = {id(p) for g in optimizer.param_groups for p in g["params"]}
+    own = {id(p): n for n, p in model.named_parameters()}
+    for n, p in model.named_parameters():
+        if p.is_sparse:
+            warnings.append(f"sparse parameter: {n}")
+        if p.device.type == "meta":
+            warnings.append(f"meta-device parameter: {n}")
+        if p.requires_grad and id(p) not in held:
+            warnings.append(f"trainable parameter not in the optimizer: {n}")
+    stray = len([i for i in held if i not in own])
+    if stray:
+        warnings.append(f"{stray} optimizer parameter(s) do not belong to the model")
+    if any(p.dtype in (torch.float16, torch.bfloat16) and p.requires_grad for p in model.parameters()):
+        recommendations.append("half-precision trainable parameters: use the sharded engine (fp32 master shards) or "
+                               "keep fp32 master weights")
+    blocking = [w for w in warnings if w.startswith(("meta", "trainable", "sparse"))]
+    return {"is_compatible": not blocking, "warnings": warnings, "recommendations": recommendations}
