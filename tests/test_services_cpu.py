@@ -583,3 +583,65 @@ def test_optimizer_helpers_core_records_and_presets():
     assert T.load_training_config_from_dict({"output_dir": "${TS_TEST_OUT}"}).output_dir == "/tmp/ts_x"
     with pytest.raises(ValueError, match="learning_rate"):
         T.load_training_config_from_dict({"learning_rate": "abc"})
+
+
+def test_inference_hub_and_introspection_reference_names(tmp_path):
+    import torch
+
+    from trainscale_b200 import hub as H
+    from trainscale_b200 import introspection as I
+    from trainscale_b200.inference import engine as E
+    cfg = E.EngineConfig(model="tiny", device="cpu", dtype="float32")
+    probe = E.HardwareProbe.probe()
+    assert probe["gpu_count"] == len(probe["devices"]) and "recommended_attention" in probe
+    out = E.run_batch_demo(cfg, ["hello", "abc"], E.GenerationParams(max_tokens=3, temperature=0.0))
+    assert len(out) == 2 and all(r.metrics.completion_tokens == 3 for r in out)
+    eng = E.SOTAInferenceEngine(cfg)
+    assert E.ResultStatus.of(eng.generate("x", E.GenerationParams(max_tokens=2))) is E.ResultStatus.OK
+    assert E.ResultStatus.of(eng.generate("x", E.GenerationParams(max_tokens=0))) is E.ResultStatus.ERR
+    req = E.InferenceRequest("hi", params=E.GenerationParams(max_tokens=2, temperature=0.0))
+    queued = req.submit(eng)
+    while eng.core.has_unfinished():
+        eng.core.step()
+    assert len(queued.output_ids) == 2 and req.metrics is queued.metrics and len(req.request_id) == 32
+    assert E.run_benchmark(cfg, 2, 8, 4)["output_tokens_per_second"] > 0
+    assert E.SchedulerPolicy("fcfs") is E.SchedulerPolicy.FCFS and E.QuantizationMethod.FP8.value == "fp8"
+    assert E.ParallelStrategy.TENSOR.value == "tensor"
+
+    hc = H.HubConfig(shard_size_bytes=4096, repo_id="me/x", token="t")
+    hc.serializer().save({"a": torch.randn(32, 32), "b": torch.randn(32, 32), "c": torch.randn(8)}, tmp_path / "m")
+    res = H.SerializationResult.describe(tmp_path / "m")
+    assert len(res.shards) == 3 and res.format == "safetensors" and res.shards[0].tensor_names == ("a",)
+    assert res.total_bytes == sum(s.byte_size for s in res.shards) and res.shards[1].byte_offset == res.shards[0].byte_size
+    assert hc.manager().repo_id == "me/x" and hc.manager().policy.max_attempts == 3
+    cm = H.CheckpointManager(tmp_path / "ck")
+    p = cm.save(5, lambda t: (t / "x").write_text("1"), {"loss": 1.5, "epoch": 2})
+    meta = H.CheckpointMetadata.read(p)
+    assert (meta.step, meta.epoch, meta.loss) == (5, 2, 1.5) and len(meta.sha256) == 64 and meta.path == p
+    b = H.CircuitBreaker(failure_threshold=1)
+    assert H.CircuitState.of(b) is H.CircuitState.CLOSED
+    b.record_failure()
+    assert H.CircuitState.of(b) is H.CircuitState.OPEN
+    assert H.classify_hub_error(TimeoutError()) is H.HubErrorCode.TIMEOUT
+    assert H.classify_hub_error(ConnectionError()) in H.RETRIABLE and H.classify_hub_error(ValueError()) not in H.RETRIABLE
+    g = H.HubMetrics()
+    g.record_upload(10, 2_000_000, True)
+    g.record_upload(10, 4_000_000, False)
+    g.record_retry()
+    s = g.summary()
+    assert (s["uploads_total"], s["uploads_failed"], s["bytes_uploaded"], s["retries_total"]) == (2, 1, 10, 1)
+    assert H.get_hub_metrics() is H.get_hub_metrics()
+
+    rows = {"train": [{"question": "q", "answer": "a", "tags": ["x"], "meta": {"k": 1}}], "test": []}
+    md = I.discover_dataset(rows).unwrap()
+    assert I.get_default_split(rows).unwrap() == "train" and I.get_default_split(md).unwrap() == "train"
+    assert I.describe_dataset(md)[0].splits[0] == I.SplitInfo("train", 1)
+    feats = {f.name: f for f in I.describe_features(rows["train"])}
+    assert feats["tags"].is_list and feats["meta"].is_nested and not feats["question"].is_list
+    assert I.fuzzy_match_columns(["question", "answer", "Txt"], ["prompt", "completion", "text"]).unwrap() == \
+        {"prompt": "question", "completion": "answer", "text": "Txt"}
+    kinds = [m.match_type for m in I.match_columns(["question", "answr", "text"], ["prompt", "answer", "text"])]
+    assert kinds == ["pattern", "fuzzy", "exact"]
+    assert I.fuzzy_match_columns(["a"], ["prompt"]).is_err()
+    assert I.fuzzy_match_columns(["a"], ["prompt"], {"prompt": "a"}).unwrap() == {"prompt": "a"}
+    assert abs(I.normalized_similarity("Prompt", "prompts") - 6 / 7) < 1e-9 and I.get_introspector() is I.get_introspector()

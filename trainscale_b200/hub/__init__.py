@@ -309,3 +309,198 @@ class CheckpointManager:
         for p in self.list():
             if p.name not in keep:
                 shutil.rmtree(p, ignore_errors=True)
+
+
+# ------------------------------------------------------------------------------------------------ reference surface
+import threading as _threading  # noqa: E402
+from datetime import datetime as _datetime  # noqa: E402
+from enum import Enum as _Enum  # noqa: E402
+
+
+class HubErrorCode(_Enum):
+    """Failure modes of a hub operation (data_pipeline/trainer/hub/__init__.py:80); `classify_hub_error` maps an
+    exception onto one, and `RETRIABLE` says which are worth another attempt."""
+    NETWORK_FAILURE = "network_failure"
+    AUTHENTICATION_FAILED = "authentication_failed"
+    REPOSITORY_NOT_FOUND = "repository_not_found"
+    PERMISSION_DENIED = "permission_denied"
+    QUOTA_EXCEEDED = "quota_exceeded"
+    VALIDATION_ERROR = "validation_error"
+    SERIALIZATION_ERROR = "serialization_error"
+    INTEGRITY_CHECK_FAILED = "integrity_check_failed"
+    CIRCUIT_OPEN = "circuit_open"
+    DEPENDENCY_MISSING = "dependency_missing"
+    TIMEOUT = "timeout"
+    RESOURCE_EXHAUSTED = "resource_exhausted"
+    INTERNAL_ERROR = "internal_error"
+
+
+RETRIABLE = frozenset({HubErrorCode.NETWORK_FAILURE, HubErrorCode.TIMEOUT})
+
+
+def classify_hub_error(exc: BaseException) -> HubErrorCode:
+    status = getattr(getattr(exc, "response", None), "status_code", None)
+    by_status = {401: HubErrorCode.AUTHENTICATION_FAILED, 403: HubErrorCode.PERMISSION_DENIED,
+                 404: HubErrorCode.REPOSITORY_NOT_FOUND, 413: HubErrorCode.QUOTA_EXCEEDED,
+                 429: HubErrorCode.QUOTA_EXCEEDED}
+    if status in by_status:
+        return by_status[status]
+    if isinstance(exc, TimeoutError):
+        return HubErrorCode.TIMEOUT
+    if isinstance(exc, (ImportError, ModuleNotFoundError)):
+        return HubErrorCode.DEPENDENCY_MISSING
+    if isinstance(exc, MemoryError) or (isinstance(exc, OSError) and getattr(exc, "errno", None) == 28):
+        return HubErrorCode.RESOURCE_EXHAUSTED
+    if isinstance(exc, (ConnectionError, OSError)):
+        return HubErrorCode.NETWORK_FAILURE
+    if isinstance(exc, (ValueError, TypeError)):
+        return HubErrorCode.VALIDATION_ERROR
+    return HubErrorCode.INTERNAL_ERROR
+
+
+class CircuitState(_Enum):
+    CLOSED = "closed"
+    OPEN = "open"
+    HALF_OPEN = "half_open"
+
+    @classmethod
+    def of(cls, breaker: CircuitBreaker) -> "CircuitState":
+        breaker.allow()                      # lets an expired open state move to half-open
+        return cls(breaker.state)
+
+
+@dataclass
+class HubConfig:
+    """Options of hub traffic; the token falls back to HF_TOKEN / HUGGING_FACE_HUB_TOKEN."""
+    shard_size_bytes: int = 5 * 2 ** 30
+    upload_timeout_s: float = 3600.0
+    download_timeout_s: float = 3600.0
+    repo_id: str | None = None
+    token: str | None = None
+    cache_dir: str | None = None
+    max_workers: int = 4
+    max_retries: int = 3
+    private: bool = False
+    verify_integrity: bool = True
+    prefer_safetensors: bool = True
+
+    def __post_init__(self):
+        if self.token is None:
+            self.token = os.environ.get("HF_TOKEN") or os.environ.get("HUGGING_FACE_HUB_TOKEN")
+        if self.shard_size_bytes <= 0 or self.max_retries < 0:
+            raise ValueError("shard_size_bytes must be positive and max_retries non-negative")
+
+    def manager(self) -> HubManager:
+        return HubManager(self.repo_id, self.token, self.private, RetryPolicy(max_attempts=max(1, self.max_retries)))
+
+    def serializer(self) -> ModelSerializer:
+        return ModelSerializer(self.shard_size_bytes)
+
+
+class HubMetrics:
+    """Counters and latency samples of uploads / downloads, safe to update from several threads."""
+
+    def __init__(self):
+        self._lock = _threading.Lock()
+        self.uploads_total = self.uploads_failed = self.downloads_total = self.downloads_failed = 0
+        self.bytes_uploaded = self.bytes_downloaded = self.retries_total = 0
+        self._up_ns: list[int] = []
+        self._down_ns: list[int] = []
+
+    def record_upload(self, bytes_count: int, latency_ns: int, success: bool) -> None:
+        with self._lock:
+            self.uploads_total += 1
+            self.uploads_failed += not success
+            self.bytes_uploaded += bytes_count if success else 0
+            self._up_ns.append(latency_ns)
+
+    def record_download(self, bytes_count: int, latency_ns: int, success: bool) -> None:
+        with self._lock:
+            self.downloads_total += 1
+            self.downloads_failed += not success
+            self.bytes_downloaded += bytes_count if success else 0
+            self._down_ns.append(latency_ns)
+
+    def record_retry(self) -> None:
+        with self._lock:
+            self.retries_total += 1
+
+    @staticmethod
+    def _pct(xs: list[int], q: float) -> float:
+        if not xs:
+            return 0.0
+        s = sorted(xs)
+        return s[min(len(s) - 1, int(q * len(s)))] / 1e6
+
+    def summary(self) -> dict:
+        with self._lock:
+            return {"uploads_total": self.uploads_total, "uploads_failed": self.uploads_failed,
+                    "downloads_total": self.downloads_total, "downloads_failed": self.downloads_failed,
+                    "bytes_uploaded": self.bytes_uploaded, "bytes_downloaded": self.bytes_downloaded,
+                    "retries_total": self.retries_total, "upload_p50_ms": self._pct(self._up_ns, 0.5),
+                    "upload_p99_ms": self._pct(self._up_ns, 0.99), "download_p50_ms": self._pct(self._down_ns, 0.5)}
+
+
+_HUB_METRICS = HubMetrics()
+
+
+def get_hub_metrics() -> HubMetrics:
+    return _HUB_METRICS
+
+
+@dataclass(frozen=True)
+class ShardInfo:
+    filename: str
+    byte_offset: int
+    byte_size: int
+    sha256: str
+    tensor_names: tuple
+
+
+@dataclass(frozen=True)
+class SerializationResult:
+    shards: tuple
+    total_bytes: int
+    format: str
+    metadata: dict
+
+    @classmethod
+    def describe(cls, out_dir: str | os.PathLike) -> "SerializationResult":
+        """What `ModelSerializer.save` left in `out_dir`, from the index (or the single file)."""
+        out = Path(out_dir)
+        idx = out / "model.safetensors.index.json"
+        if idx.exists():
+            index = json.loads(idx.read_text())
+            by_file: dict[str, list[str]] = {}
+            for k, f in index["weight_map"].items():
+                by_file.setdefault(f, []).append(k)
+            hashes = index.get("metadata", {}).get("sha256", {})
+        else:
+            single = [p.name for p in (out / "model.safetensors", out / "model.pt") if p.exists()]
+            by_file, hashes = {f: [] for f in single}, {}
+        shards, off = [], 0
+        for f in sorted(by_file):
+            size = (out / f).stat().st_size
+            shards.append(ShardInfo(f, off, size, hashes.get(f) or compute_sha256(out / f), tuple(by_file[f])))
+            off += size
+        fmt = "safetensors" if any(s.filename.endswith(".safetensors") for s in shards) else "pytorch"
+        return cls(tuple(shards), off, fmt, {"num_shards": len(shards)})
+
+
+@dataclass(frozen=True)
+class CheckpointMetadata:
+    step: int
+    epoch: int
+    loss: float
+    timestamp: _datetime
+    sha256: str
+    path: Path
+
+    @classmethod
+    def read(cls, checkpoint_dir: str | os.PathLike) -> "CheckpointMetadata":
+        """From the `checkpoint_meta.json` a `CheckpointManager` writes; the hash covers that file."""
+        d = Path(checkpoint_dir)
+        meta = json.loads((d / "checkpoint_meta.json").read_text())
+        m = meta.get("metrics", {})
+        return cls(int(meta.get("step", 0)), int(m.get("epoch", 0)), float(m.get("loss", m.get("eval_loss", float("nan")))),
+                   _datetime.fromtimestamp(meta.get("time", 0.0)), compute_sha256(d / "checkpoint_meta.json"), d)

@@ -1035,3 +1035,128 @@ def main(argv: list[str] | None = None) -> int:
             print(json.dumps(out))
         return 0
     return 1
+
+
+# ------------------------------------------------------------------------------------------------ reference surface
+from enum import Enum  # noqa: E402
+
+
+class QuantizationMethod(Enum):
+    """Weight formats a serving engine may be asked for (data_pipeline/trainer/inference.py:184).  This engine serves
+    bf16 and block-scaled fp8; the others are accepted in configurations and refused at build time."""
+    NONE = "none"
+    GPTQ = "gptq"
+    AWQ = "awq"
+    AUTOROUND = "autoround"
+    FP8 = "fp8"
+    INT8 = "compressed-tensors"
+    BITSANDBYTES = "bitsandbytes"
+    SQUEEZELLM = "squeezellm"
+    MARLIN = "marlin"
+
+
+class ParallelStrategy(Enum):
+    NONE = "none"
+    TENSOR = "tensor"
+    PIPELINE = "pipeline"
+    TENSOR_PIPELINE = "tensor_pipeline"
+    DATA = "data"
+
+
+class SchedulerPolicy(Enum):
+    FCFS = "fcfs"
+    PRIORITY = "priority"
+
+
+class ResultStatus(Enum):
+    OK = "ok"
+    ERR = "err"
+
+    @classmethod
+    def of(cls, result) -> "ResultStatus":
+        return cls.OK if result.is_ok() else cls.ERR
+
+
+@dataclass
+class InferenceRequest:
+    """A prompt with its sampling parameters, optional adapter and metrics; `submit(engine)` queues it."""
+    prompt: str
+    request_id: str = ""
+    params: GenerationParams = field(default_factory=GenerationParams)
+    lora_name: str | None = None
+    lora_path: str | None = None
+    lora_id: int | None = None
+    _metrics: RequestMetrics = field(default_factory=RequestMetrics)
+
+    def __post_init__(self):
+        if not self.request_id:
+            import uuid
+            self.request_id = uuid.uuid4().hex
+        self._metrics.request_id = self.request_id
+        if self.lora_name and not self.params.lora_name:
+            self.params.lora_name = self.lora_name
+
+    @property
+    def metrics(self) -> RequestMetrics:
+        return self._metrics
+
+    def submit(self, engine: "SOTAInferenceEngine"):
+        req = engine.core.add_request(self.prompt, self.params)
+        self._metrics = req.metrics
+        return req
+
+
+class HardwareProbe:
+    """What the serving engine can count on: devices, memory, compute capability, peer access, the dtype and attention
+    path it will pick (data_pipeline/trainer/inference.py:702)."""
+
+    @staticmethod
+    def probe() -> dict:
+        info: dict = {"cuda_available": torch.cuda.is_available(), "gpu_count": 0, "devices": [],
+                      "total_gpu_memory_gb": 0.0, "recommended_dtype": "float32", "recommended_attention": "reference",
+                      "nvlink_p2p": False}
+        if not torch.cuda.is_available():
+            return info
+        n = torch.cuda.device_count()
+        info["gpu_count"] = n
+        for i in range(n):
+            p = torch.cuda.get_device_properties(i)
+            info["devices"].append({"index": i, "name": p.name, "compute_capability": f"{p.major}.{p.minor}",
+                                    "memory_gb": round(p.total_memory / 2 ** 30, 1), "sm_count": p.multi_processor_count})
+            info["total_gpu_memory_gb"] += p.total_memory / 2 ** 30
+        major = torch.cuda.get_device_capability(0)[0]
+        info["recommended_dtype"] = "bfloat16" if major >= 8 else "float16"
+        info["recommended_attention"] = "tcgen05_flash" if major == 10 else "reference"
+        info["cuda_graphs"] = True
+        if n > 1:
+            try:
+                info["nvlink_p2p"] = all(torch.cuda.can_device_access_peer(0, j) for j in range(1, n))
+            except RuntimeError:
+                pass
+        info["recommended_tensor_parallel_size"] = n if info["nvlink_p2p"] else 1
+        return info
+
+
+def run_hardware_probe() -> dict:
+    info = HardwareProbe.probe()
+    print(json.dumps(info, indent=2))
+    return info
+
+
+def run_batch_demo(config: EngineConfig, prompts: list[str], params: GenerationParams | None = None) -> list:
+    """Generate for a batch of prompts and print every completion with its latency figures and the engine summary."""
+    engine = SOTAInferenceEngine(config)
+    params = params or GenerationParams(max_tokens=256, temperature=0.7, top_p=0.95)
+    responses = engine.generate(list(prompts), params).unwrap()
+    for r in responses:
+        m = r.metrics
+        print(f"[{r.request_id[:8]}] {r.finish_reason:6s} {m.completion_tokens:4d} tok  {r.text!r}")
+    print(json.dumps(engine.metrics_summary(), indent=2, default=str))
+    return responses
+
+
+def run_benchmark(config: EngineConfig, num_prompts: int = 100, prompt_len: int = 128, output_len: int = 128) -> dict:
+    """Throughput and TTFT / TPOT percentiles of an engine built from `config` (`run_bench` on a fresh engine)."""
+    out = run_bench(SOTAInferenceEngine(config), num_prompts, prompt_len, output_len)
+    print(json.dumps(out, indent=2, default=str))
+    return out

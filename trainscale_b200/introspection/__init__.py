@@ -144,3 +144,126 @@ class ColumnMapper:
         if missing:
             return Err(ColumnNotFoundError(f"no column matches {missing}", available=list(available)))
         return Ok(out)
+
+
+# ------------------------------------------------------------------------------------------------ reference surface
+@dataclass(frozen=True)
+class FeatureInfo:
+    """One column: name, dtype name, whether its values are lists and whether they nest mappings."""
+    name: str
+    dtype: str
+    is_list: bool = False
+    is_nested: bool = False
+
+    @classmethod
+    def of(cls, name: str, value: Any) -> "FeatureInfo":
+        is_list = isinstance(value, (list, tuple))
+        inner = value[0] if is_list and value else value
+        return cls(name, type(inner).__name__ if is_list else type(value).__name__, is_list, isinstance(inner, Mapping))
+
+
+@dataclass(frozen=True)
+class SplitInfo:
+    name: str
+    num_examples: int | None = None
+    num_bytes: int | None = None
+
+
+@dataclass(frozen=True)
+class ConfigInfo:
+    name: str
+    splits: tuple = ()
+    description: str | None = None
+
+
+@dataclass(frozen=True)
+class ColumnMatch:
+    """How a required column was matched: exact name, known alias ("pattern") or edit distance ("fuzzy")."""
+    source: str
+    target: str
+    confidence: float
+    match_type: str
+
+
+def normalized_similarity(s1: str, s2: str) -> float:
+    """1 - edit distance / longer length, case-insensitive; 1.0 for two empty strings."""
+    if not s1 and not s2:
+        return 1.0
+    if not s1 or not s2:
+        return 0.0
+    return 1.0 - levenshtein_distance(s1.lower(), s2.lower()) / max(len(s1), len(s2))
+
+
+def describe_dataset(md: DatasetMetadata, sample_row: Mapping[str, Any] | None = None) -> tuple[ConfigInfo, ...]:
+    """`DatasetMetadata` as typed records: one `ConfigInfo` per configuration (a single "default" one when the dataset
+    has none), each with its `SplitInfo`s."""
+    splits = tuple(SplitInfo(k, v) for k, v in md.splits.items())
+    return tuple(ConfigInfo(c, splits) for c in (md.configs or ["default"]))
+
+
+def describe_features(rows: Sequence[Mapping[str, Any]]) -> tuple[FeatureInfo, ...]:
+    seen: dict[str, FeatureInfo] = {}
+    for r in rows[:16]:
+        for k, v in r.items():
+            seen.setdefault(k, FeatureInfo.of(k, v))
+    return tuple(seen.values())
+
+
+def match_columns(source_columns: Sequence[str], target_schema: Sequence[str], min_score: float = 0.7) -> list[ColumnMatch]:
+    """Best source column for every target column with how it was found; targets without a match above `min_score`
+    are left out."""
+    mapper = ColumnMapper(max_distance=10 ** 6)
+    out = []
+    for t in target_schema:
+        exact = next((s for s in source_columns if s.lower() == t.lower()), None)
+        if exact is not None:
+            out.append(ColumnMatch(exact, t, 1.0, "exact"))
+            continue
+        alias = next((s for s in source_columns if s.lower() in mapper.ALIASES.get(t.lower(), ())), None)
+        if alias is not None:
+            out.append(ColumnMatch(alias, t, 0.9, "pattern"))
+            continue
+        best = max(source_columns, key=lambda s: normalized_similarity(s, t), default=None)
+        if best is not None and normalized_similarity(best, t) >= min_score:
+            out.append(ColumnMatch(best, t, normalized_similarity(best, t), "fuzzy"))
+    return out
+
+
+def fuzzy_match_columns(source_columns: Sequence[str], target_schema: Sequence[str],
+                        explicit_mapping: Mapping[str, str] | None = None, min_score: float = 0.7) -> Result:
+    """{target column: source column} as a Result; explicit mappings win, every other target needs a match of at least
+    `min_score` (data_pipeline/introspection/column_mapper.py:337)."""
+    out: dict[str, str] = {}
+    for t, s in (explicit_mapping or {}).items():
+        if s not in source_columns:
+            return Err(ColumnNotFoundError(f"mapped column {s!r} does not exist", available=list(source_columns)))
+        out[t] = s
+    rest = [t for t in target_schema if t not in out]
+    found = {m.target: m.source for m in match_columns(source_columns, rest, min_score)}
+    missing = [t for t in rest if t not in found]
+    if missing:
+        return Err(ColumnNotFoundError(f"no column matches {missing}", available=list(source_columns)))
+    out.update(found)
+    return Ok(out)
+
+
+_INTROSPECTOR: list = [None]
+
+
+def get_introspector(token: str | None = None) -> DatasetIntrospector:
+    if _INTROSPECTOR[0] is None:
+        _INTROSPECTOR[0] = DatasetIntrospector(token=token)
+    return _INTROSPECTOR[0]
+
+
+def discover_dataset(dataset_id, token: str | None = None) -> Result:
+    return get_introspector(token).discover(dataset_id)
+
+
+def get_default_split(dataset_id, config: str | None = None, token: str | None = None) -> Result:
+    """Preferred split (train first) of a dataset given by id, path, rows or an already discovered `DatasetMetadata`."""
+    intro = get_introspector(token)
+    if isinstance(dataset_id, DatasetMetadata):
+        return intro.get_default_split(dataset_id)
+    md = intro.discover(dataset_id, config)
+    return md if md.is_err() else intro.get_default_split(md.unwrap())
