@@ -1,0 +1,109 @@
+"""Every public class / function name of the reference's package has a counterpart of the same name somewhere in this
+package (a class, a function or a module-level alias).  The reference is read as text (its installed copy for the
+comparison arm of bench.py, or a checkout named by TRAINSCALE_REFERENCE); the test is skipped where neither exists."""
+import ast
+import os
+from pathlib import Path
+
+import pytest
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def _reference_root():
+    for cand in (ROOT / "baseline" / "_ref" / "data_pipeline",
+                 Path(os.environ.get("TRAINSCALE_REFERENCE", "/nonexistent")) / "data_pipeline"):
+        if cand.is_dir():
+            return cand
+    return None
+
+
+def _public_defs(root: Path) -> dict[str, str]:
+    out = {}
+    for p in root.rglob("*.py"):
+        if "examples" in p.parts:
+            continue
+        try:
+            tree = ast.parse(p.read_text())
+        except SyntaxError:
+            continue
+        for node in tree.body:
+            if isinstance(node, (ast.ClassDef, ast.FunctionDef)) and not node.name.startswith("_"):
+                out.setdefault(node.name, str(p.relative_to(root)))
+    return out
+
+
+def _our_names(root: Path) -> set[str]:
+    """Module-level classes, functions, assigned names and imported names of every file of the package."""
+    names: set[str] = set()
+    for p in root.rglob("*.py"):
+        try:
+            tree = ast.parse(p.read_text())
+        except SyntaxError:
+            continue
+        for node in tree.body:
+            if isinstance(node, (ast.ClassDef, ast.FunctionDef)):
+                names.add(node.name)
+            elif isinstance(node, (ast.Assign, ast.AnnAssign)):
+                targets = node.targets if isinstance(node, ast.Assign) else [node.target]
+                for t in targets:
+                    for n in ast.walk(t):
+                        if isinstance(n, ast.Name):
+                            names.add(n.id)
+    return names
+
+
+def test_every_public_name_of_the_reference_exists_here():
+    ref = _reference_root()
+    if ref is None:
+        pytest.skip("the reference package is not on this machine")
+    ours = _our_names(ROOT / "trainscale_b200")
+    missing = {n: f for n, f in _public_defs(ref).items() if n not in ours}
+    assert not missing, f"{len(missing)} names without a counterpart: {sorted(missing.items())[:20]}"
+
+
+def test_last_helpers_behave():
+    import torch
+
+    from trainscale_b200 import benchmark_suite as BS
+    from trainscale_b200.core.types import Err, Ok
+    from trainscale_b200.data import length_manager as LM
+    from trainscale_b200.data import packing as P
+    from trainscale_b200.data import prompt_engine as PE
+    from trainscale_b200.data import tokenization as TK
+    from trainscale_b200.parallel import activation as A
+    from trainscale_b200.parallel import cp as C
+    from trainscale_b200.parallel import dist_utils as U
+    from trainscale_b200.trainer import base as B
+    from trainscale_b200.trainer.sota_trainer import SOTATrainer, create_trainer_from_config
+    m = torch.nn.Sequential(torch.nn.Linear(4, 4), torch.nn.ReLU(), torch.nn.Linear(4, 4))
+    ref = m(torch.ones(2, 4)).detach()
+    A.wrap_activation_checkpointing(m, torch.nn.Linear)
+    x = torch.ones(2, 4, requires_grad=True)
+    y = m(x)
+    y.sum().backward()
+    assert torch.allclose(y, ref) and x.grad is not None and m[0]._ts_checkpointed
+    g = A.OffloadTensorGroup("mlp")
+    g.add("h", torch.arange(6.0).view(2, 3))
+    assert g.offload_all(A.OffloadTarget.CPU_PAGED) == 24 and torch.equal(g.get("h"), torch.arange(6.0).view(2, 3))
+    assert A.ActivationOffloadConfig(min_offload_tensor_size=1024).build().min_bytes == 2048
+    with U.no_sync(m):
+        pass
+    U.allreduce_conditional_embedding_grads(m, None)                  # no pipeline group: nothing to do
+    assert LM.saturating_sub(3, 5) == 0 and LM.clamp(7, 0, 5) == 5 and LM.is_tokenizer(TK.ByteTokenizer())
+    assert P.calculate_packing_efficiency([3, 4, 5], [[0, 1], [2]], 8) == 0.75
+    assert TK.ensure_tokenizer_padding(TK.ByteTokenizer()) >= 0
+    oks, errs = PE.extract_successful([Ok(1), Err(ValueError("x")), Ok(2)])
+    assert oks == [1, 2] and isinstance(errs[0], ValueError)
+    out = B.TrainOutput.from_summary({"global_step": 3, "train_loss": 1.25})
+    assert out.global_step == 3 and "1.250000" in repr(out) and B.PredictionOutput(torch.zeros(1)).label_ids is None
+    s = C.BalancerStrategy("head_tail")
+    t = torch.arange(16).view(1, 16)
+    parts = [s.partition(t, r, 2, 1) for r in range(2)]
+    assert parts[0].tolist() == [[0, 1, 2, 3, 12, 13, 14, 15]] and torch.equal(s.unpartition(parts, 1), t)
+    row = BS.BenchmarkResult.from_row({"name": "k", "ms": 1.0, "baseline_ms": 2.0, "gbs": 100.0})
+    assert row.speedup == 2.0 and row.baseline_metric == 50.0 and row.metric_name == "GB/s"
+    tr = create_trainer_from_config({"model": {"architecture": "llama-tiny"},
+                                     "hardware": {"device": "cpu", "precision": "fp32"},
+                                     "distributed": {"enabled": False}})
+    assert isinstance(tr, SOTATrainer)

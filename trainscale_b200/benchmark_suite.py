@@ -10,6 +10,7 @@ from __future__ import annotations
 import argparse
 import json
 from pathlib import Path
+from typing import NamedTuple
 
 import torch
 import torch.nn.functional as F
@@ -550,3 +551,42 @@ def main(argv=None) -> int:
 
 if __name__ == "__main__":
     raise SystemExit(main())
+
+
+class BenchmarkResult(NamedTuple):
+    """One benchmark row in the reference's record form (data_pipeline/trainer/kernels/benchmark_suite.py:88)."""
+    name: str
+    kernel_ms: float
+    baseline_ms: float
+    speedup: float
+    metric_name: str
+    kernel_metric: float
+    baseline_metric: float
+
+    @classmethod
+    def from_row(cls, row: dict) -> "BenchmarkResult":
+        """From a row dictionary of this suite ({name, ms, baseline_ms, gbs | tflops})."""
+        metric = "GB/s" if "gbs" in row else "TFLOPS"
+        val = row.get("gbs", row.get("tflops", 0.0))
+        base = row.get("baseline_ms") or float("nan")
+        return cls(row["name"], row["ms"], base, base / row["ms"], metric, val, val * row["ms"] / base)
+
+
+def do_bench_fallback(fn, warmup: int = 25, rep: int = 100, quantiles=None, return_mode: str = "mean"):
+    """CUDA-event timing of `fn` in ms without Triton's helper: `rep` timed calls after `warmup`; returns the mean (or
+    min / max / median by `return_mode`), or the requested quantiles as a list."""
+    fn()
+    torch.cuda.synchronize()
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    pairs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(rep)]
+    for a, b in pairs:
+        a.record()
+        fn()
+        b.record()
+    torch.cuda.synchronize()
+    times = torch.tensor([a.elapsed_time(b) for a, b in pairs])
+    if quantiles is not None:
+        return torch.quantile(times, torch.tensor(quantiles, dtype=torch.float32)).tolist()
+    return float(getattr(times, return_mode)())

@@ -353,3 +353,24 @@ def create_content_distributor(mode="proportional", max_length: int = 2048, colu
     cols = [ColumnContentConfig(n, priority=(priorities or {}).get(n, 0), ratio=(column_ratios or {}).get(n),
                                 is_label=n in label_columns) for n in names]
     return TokenAwareContentDistributor(ContentDistributionMode(mode), max_length, cols, special_tokens_budget, tokenizer)
+
+
+def saturating_sub(a: int, b: int) -> int:
+    """a - b, never below zero."""
+    return a - b if a > b else 0
+
+
+def clamp(value: int, lo: int, hi: int) -> int:
+    return lo if value < lo else hi if value > hi else value
+
+
+class TokenizerProtocol:
+    """What token estimation needs of a tokenizer: `encode(text, add_special_tokens=False) -> list[int]`
+    (structural: any object with that method qualifies, see `is_tokenizer`)."""
+
+    def encode(self, text: str, *, add_special_tokens: bool = False) -> list:
+        raise NotImplementedError
+
+
+def is_tokenizer(obj) -> bool:
+    return callable(getattr(obj, "encode", None))

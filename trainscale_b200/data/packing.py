@@ -109,3 +109,9 @@ def get_packing_stats(lengths: Sequence[int], max_length: int) -> dict:
     return {"num_sequences": len(lengths), "num_packed": len(bins), "efficiency": used / max(1, len(bins) * max_length),
             "padding_efficiency": used / max(1, len(lengths) * max_length),
             "compression_ratio": len(lengths) / max(1, len(bins))}
+
+
+def calculate_packing_efficiency(lengths: Sequence[int], bins: Sequence[Sequence[int]], max_capacity: int) -> float:
+    """Used tokens / capacity of the bins (1.0 = no padding)."""
+    total = len(bins) * max_capacity
+    return sum(lengths) / total if total > 0 else 0.0

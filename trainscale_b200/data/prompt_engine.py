@@ -624,3 +624,14 @@ def create_rl_engine(tokenizer, max_length=2048, algorithm="dpo", **rl_kw) -> Pr
     from ..config.data_schema import RLConfig
     rl = RLConfig(algorithm=RLAlgorithm(algorithm), **rl_kw)
     return PromptEngine(PromptEngineConfig(stage=TrainingStage.POST_TRAINING, max_length=max_length, rl=rl), tokenizer)
+
+
+def extract_successful(results):
+    """Split a list of Results into (ok values, errors), keeping order."""
+    oks, errs = [], []
+    for r in results:
+        if r.is_ok():
+            oks.append(r.unwrap())
+        else:
+            errs.append(r.error)
+    return oks, errs

@@ -279,3 +279,12 @@ def create_tokenizer(config=None, name_or_path: str | None = None, token: str | 
 
 def wrap_tokenizer(tokenizer, **kw) -> TokenizerWrapper:
     return tokenizer if isinstance(tokenizer, TokenizerWrapper) else TokenizerWrapper(tokenizer, **kw)
+
+
+def ensure_tokenizer_padding(tokenizer) -> int:
+    """Give a raw tokenizer a pad token if it has none (eos, then unk, else a new '<pad>') and return its id."""
+    _ensure_pad_token(tokenizer)
+    pid = getattr(tokenizer, "pad_token_id", None)
+    if pid is None and hasattr(tokenizer, "convert_tokens_to_ids"):
+        pid = tokenizer.convert_tokens_to_ids(tokenizer.pad_token)
+    return int(pid if pid is not None else 0)

@@ -513,3 +513,87 @@ def create_activation_checkpoint(mode: str = "selective", frequency: int = 2, me
         if hasattr(cfg, k):
             setattr(cfg, k, v)
     return ActivationCheckpoint(cfg)
+
+
+def activation_checkpoint(fn, *args, use_reentrant: bool = False, **kwargs):
+    """Run `fn(*args, **kwargs)` under a checkpoint (data_pipeline/trainer/distributed/__init__.py:629)."""
+    return checkpoint(fn, *args, use_reentrant=use_reentrant, **kwargs)
+
+
+def wrap_activation_checkpointing(model: nn.Module, layer_cls) -> nn.Module:
+    """Every submodule of type `layer_cls` recomputes its forward in backward from now on; obeys `no_checkpoint()`."""
+    import functools
+    for module in model.modules():
+        if isinstance(module, layer_cls) and not getattr(module, "_ts_checkpointed", False):
+            original = module.forward
+
+            @functools.wraps(original)
+            def checkpointed_forward(*a, _original=original, **k):
+                return activation_checkpoint(_original, *a, **k)
+            module.forward = checkpointed_forward
+            module._ts_checkpointed = True
+    return model
+
+
+@dataclass
+class ActivationOffloadConfig:
+    """Options of activation offload (data_pipeline/trainer/distributed/activation_offload.py:67): tensors below
+    `min_offload_tensor_size` ELEMENTS stay on the GPU, `offload_margin` trailing groups are never offloaded (they are
+    needed again at once when backward starts)."""
+    min_offload_tensor_size: int = 1 << 20
+    use_pinned_memory: bool = True
+    offload_margin: int = 0
+    enable_warmup_stats: bool = True
+
+    def build(self, bytes_per_element: int = 2) -> ActivationOffloader:
+        return ActivationOffloader(self.min_offload_tensor_size * bytes_per_element)
+
+
+class OffloadTensorGroup:
+    """Tensors offloaded and reloaded together (one group per layer part: "attention", "mlp", ...), with one event per
+    direction so that a consumer waits once per group."""
+
+    def __init__(self, name: str, offload: bool = True):
+        self.name, self.offload = name, offload
+        self._tensors: dict = {}
+        self._handles: dict = {}
+        self.total_offload_bytes = 0
+        self.total_tensor_count = 0
+        cuda = torch.cuda.is_available()
+        self._offload_event = torch.cuda.Event() if cuda else None
+        self._reload_event = torch.cuda.Event() if cuda else None
+
+    def add(self, key, t: torch.Tensor) -> None:
+        self._tensors[key] = t
+        self.total_tensor_count += 1
+
+    def offload_all(self, target: OffloadTarget = OffloadTarget.CPU_PINNED, min_elements: int = 0) -> int:
+        """Move the group's tensors (those of at least `min_elements`) to the host; returns the bytes moved."""
+        if not self.offload:
+            return 0
+        moved = 0
+        for i, (key, t) in enumerate(list(self._tensors.items())):
+            if t.numel() < min_elements:
+                continue
+            self._handles[key] = OffloadHandle.offload(i, t, target)
+            moved += t.numel() * t.element_size()
+            del self._tensors[key]
+        if self._offload_event is not None:
+            self._offload_event.record()
+        self.total_offload_bytes += moved
+        return moved
+
+    def reload_all(self) -> dict:
+        if self._offload_event is not None:
+            self._offload_event.synchronize()
+        for key, h in list(self._handles.items()):
+            self._tensors[key] = h.restore()
+            del self._handles[key]
+        if self._reload_event is not None:
+            self._reload_event.record()
+        return dict(self._tensors)
+
+    def get(self, key) -> torch.Tensor:
+        if key in self._handles:
+            self.reload_all()
+        return self._tensors[key]

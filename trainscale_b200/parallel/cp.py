@@ -939,3 +939,26 @@ def ulysses_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, group, 
     qkv = torch.cat((qh.reshape(B, S, -1), kh.reshape(B, S, -1), vh.reshape(B, S, -1)), -1)
     o = A.attention_qkv(qkv, Hq // P, Hkv // P, D, causal, scale, window, softcap).view(B, S, Hq // P, D)
     return _heads_to_seq(o, group, P)
+
+
+class LoadBalancerStrategy:
+    """Interface of a sequence partitioner for context parallelism (data_pipeline/trainer/distributed/
+    context_parallel.py:980): `partition(tensor, cp_rank, cp_world_size, seq_dim)` returns the rank's part and
+    `unpartition(parts, seq_dim)` restores the order.  `BalancerStrategy(name)` adapts the balancers of this module."""
+
+    def partition(self, tensor: torch.Tensor, cp_rank: int, cp_world_size: int, seq_dim: int) -> torch.Tensor:
+        raise NotImplementedError
+
+    def unpartition(self, parts: list[torch.Tensor], seq_dim: int) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class BalancerStrategy(LoadBalancerStrategy):
+    def __init__(self, name: str = "head_tail"):
+        self.name = name
+
+    def partition(self, tensor, cp_rank, cp_world_size, seq_dim):
+        return create_balancer(self.name, cp_world_size, cp_rank).shard(tensor, seq_dim)
+
+    def unpartition(self, parts, seq_dim):
+        return create_balancer(self.name, len(parts), 0).unshard(parts, seq_dim)

@@ -750,3 +750,43 @@ def print_rank_0(*args, flush: bool = True, **kwargs) -> None:
     if dist.is_available() and dist.is_initialized() and dist.get_rank() != 0:
         return
     print(*args, flush=flush, **kwargs)
+
+
+@contextlib.contextmanager
+def no_sync(model):
+    """Suspend gradient synchronisation for the micro-batches of an accumulation window: uses the `no_sync()` of a
+    torch DDP module or of this framework's engines (found on the object or on its `engine` attribute); a plain module
+    needs nothing."""
+    target = model if hasattr(model, "no_sync") else getattr(model, "engine", None)
+    if target is not None and hasattr(target, "no_sync"):
+        with target.no_sync():
+            yield
+    else:
+        yield
+
+
+def allreduce_conditional_embedding_grads(model, pp_group=None) -> None:
+    """Parameters replicated on every pipeline stage (marked `pipeline_parallel = True`: timestep / label embedders of
+    diffusion transformers) get their gradients summed over the stages.  `model` is a module or a list of module chunks
+    (interleaved schedules); a name that occurs in several local chunks is summed locally first, reduced once and
+    copied back to the other chunks (data_pipeline/trainer/distributed/finalize_grads.py:87)."""
+    if pp_group is None or not dist.is_initialized() or dist.get_world_size(pp_group) <= 1:
+        return
+    chunks = list(model) if isinstance(model, (list, tuple)) else [model]
+    by_name: dict[str, list[torch.Tensor]] = {}
+    for chunk in chunks:
+        for name, p in chunk.named_parameters():
+            if not (p.requires_grad and getattr(p, "pipeline_parallel", False)):
+                continue
+            g = getattr(p, "main_grad", None)
+            g = g if g is not None else p.grad
+            if g is None:
+                continue
+            if name in by_name:
+                by_name[name][0].add_(g)
+            by_name.setdefault(name, []).append(g)
+    for name in sorted(by_name):
+        first = by_name[name][0]
+        dist.all_reduce(first, group=pp_group)
+        for other in by_name[name][1:]:
+            other.copy_(first)

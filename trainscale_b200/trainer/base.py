@@ -9,6 +9,7 @@ from __future__ import annotations
 
 import copy
 import math
+from dataclasses import dataclass, field
 from typing import Any, Callable, Iterable
 
 import torch
@@ -219,3 +220,28 @@ class TextGenerationTrainer(Trainer):
             if eos_token_id is not None and bool((nxt == eos_token_id).all()):
                 break
         return ids
+
+
+@dataclass
+class TrainOutput:
+    """What a training run produced (data_pipeline/trainer/base.py:103)."""
+    global_step: int
+    training_loss: float
+    metrics: dict = field(default_factory=dict)
+
+    def __repr__(self) -> str:
+        return f"TrainOutput(global_step={self.global_step}, training_loss={self.training_loss:.6f}, metrics={self.metrics})"
+
+    @classmethod
+    def from_summary(cls, summary: dict) -> "TrainOutput":
+        """From the dictionary `Trainer.train()` returns."""
+        loss = summary.get("train_loss", summary.get("training_loss", float("nan")))
+        return cls(int(summary.get("global_step", 0)), float(loss),
+                   {k: v for k, v in summary.items() if k not in ("global_step",)})
+
+
+@dataclass
+class PredictionOutput:
+    predictions: torch.Tensor
+    label_ids: torch.Tensor | None = None
+    metrics: dict = field(default_factory=dict)

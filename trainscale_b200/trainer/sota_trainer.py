@@ -794,3 +794,13 @@ def create_trainer(config: str | os.PathLike | dict | SOTAConfig, **kw) -> SOTAT
     else:
         cfg = SOTAConfig.from_yaml(config)
     return SOTATrainer(cfg, **kw)
+
+
+def create_trainer_from_config(config) -> "SOTATrainer":
+    """Trainer from an already built `SOTAConfig` (a dict or a YAML path is accepted too)."""
+    from ..config.sota_config import SOTAConfig
+    if isinstance(config, dict):
+        config = SOTAConfig.from_dict(config)
+    elif isinstance(config, (str, os.PathLike)):
+        config = SOTAConfig.from_yaml(config)
+    return SOTATrainer(config)
