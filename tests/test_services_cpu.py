@@ -645,3 +645,94 @@ def test_inference_hub_and_introspection_reference_names(tmp_path):
     assert I.fuzzy_match_columns(["a"], ["prompt"]).is_err()
     assert I.fuzzy_match_columns(["a"], ["prompt"], {"prompt": "a"}).unwrap() == {"prompt": "a"}
     assert abs(I.normalized_similarity("Prompt", "prompts") - 6 / 7) < 1e-9 and I.get_introspector() is I.get_introspector()
+
+
+def test_training_trackers_full_surface():
+    import math
+    import time
+
+    import torch
+
+    from trainscale_b200.metrics import (AccuracyTracker, GradientTracker, LossTracker, ThroughputTracker,
+                                         TrainingMetrics, create_training_metrics)
+    lt = LossTracker()
+    lt.update(2.0, num_tokens=10, num_samples=2)
+    lt.update(1.0, num_tokens=30, accumulation_steps=4)          # the loss had been divided by 4
+    assert lt.compute_avg() == (2.0 * 10 + 4.0 * 30) / 40 and lt.last_loss == 4.0 and lt.step_count == 2
+    assert lt.total_tokens == 40 and lt.total_samples == 3 and lt.get_history(1) == [4.0]
+    assert abs(lt.compute_ema() - (0.99 * 2.0 + 0.01 * 4.0)) < 1e-12 and lt.compute_variance() == 2.0
+    assert abs(lt.compute_ppl() - math.exp(3.5)) < 1e-9 and lt.sync() == 3.5
+    logits, labels = torch.randn(2, 5, 7), torch.randint(0, 7, (2, 5))
+    labels[0, 1] = -100
+    want = torch.nn.functional.cross_entropy(logits[:, :-1].reshape(-1, 7), labels[:, 1:].reshape(-1), ignore_index=-100)
+    lt2 = LossTracker()
+    assert abs(lt2.update_from_logits(logits, labels) - float(want)) < 1e-5 and lt2.total_tokens == 7
+    sd = lt.state_dict()
+    lt3 = LossTracker()
+    lt3.load_state_dict(sd)
+    assert lt3.compute_avg() == 3.5 and lt3.step_count == 2
+    lt.reset()
+    assert lt.total_tokens == 0 and lt.compute_avg() == 0.0
+
+    acc = AccuracyTracker()
+    a = acc.update_from_logits(logits, labels)
+    pred = logits[:, :-1].argmax(-1)
+    m = labels[:, 1:] != -100
+    assert acc.total == 7 and abs(a - float(((pred == labels[:, 1:]) & m).sum()) / 7) < 1e-9
+    acc.update(3, 3)
+    assert acc.total == 10 and acc.sync() == acc.compute() == acc.accuracy
+
+    net = torch.nn.Sequential(torch.nn.Linear(4, 3), torch.nn.Linear(3, 2))
+    net(torch.randn(5, 4)).sum().backward()
+    gt = GradientTracker(max_norm=1e-3)
+    n = gt.update(net.parameters())
+    want = math.sqrt(sum(float(p.grad.pow(2).sum()) for p in net.parameters()))
+    assert abs(n - want) < 1e-5 and gt.compute_norm() == n and gt.is_anomaly() and not gt.has_nan_or_inf()
+    allg = torch.cat([p.grad.reshape(-1) for p in net.parameters()])
+    assert abs(gt.compute_mean() - float(allg.mean())) < 1e-6 and abs(gt.compute_std() - float(allg.std(unbiased=False))) < 1e-5
+    gt.update_from_model(net)
+    top = gt.get_top_layers(2)
+    assert len(gt.get_layer_norms()) == 4 and top[0][1] >= top[1][1] and gt.step_count == 2
+    net[0].weight.grad[0, 0] = float("nan")
+    gt.update(net)
+    assert gt.has_nan() and not gt.has_inf() and gt.nan_count == 1
+    gt.update(0.5)                                                  # a norm computed elsewhere
+    assert gt.compute_norm() == 0.5 and set(gt.histogram()) == {"p10", "p25", "p50", "p75", "p90", "max"}
+    assert "gradient/norm_ema" in gt.log_dict()
+    g2 = GradientTracker()
+    g2.load_state_dict(gt.state_dict())
+    assert g2.step_count == gt.step_count and abs(g2.compute_ema_norm() - gt.compute_ema_norm()) < 1e-12
+
+    tt = ThroughputTracker(flops_per_token=6e3, peak_tflops=1e-6, use_cuda_events=False)
+    tt.start()
+    time.sleep(0.02)
+    tt.update(samples=2, tokens=1000)
+    time.sleep(0.02)
+    tt.update(samples=2, tokens=1000)
+    assert tt.total_tokens == 2000 and tt.total_samples == 4 and tt.step_count == 2 and tt.elapsed_seconds() >= 0.04
+    assert 0 < tt.tokens_per_sec() < 1e5 and tt.samples_per_sec() > 0 and tt.tokens_per_sec_window() > 0
+    assert abs(tt.compute_tflops() / (tt.tokens_per_sec() * 6e3 / 1e12) - 1) < 0.05 and tt.compute_mfu() > 0   # the clock runs
+    assert tt.compute_mfu(model_params=1000) > 0 and "throughput/mfu" in tt.log_dict()
+    tt.sync()
+    tt.reset()
+    assert tt.total_tokens == 0 and tt.step_count == 0
+
+    tm = create_training_metrics(model=net, log_prefix="train")
+    assert tm.model_params == sum(p.numel() for p in net.parameters())
+    tm.start()
+    tm.new_epoch(1)
+    time.sleep(0.01)
+    tm.update_step(torch.tensor(2.0), logits=logits, labels=labels, batch_size=2, num_tokens=8, lr=1e-4, grad_norm=0.7)
+    tm.update_step(1.0, model=net, batch_size=2, num_tokens=8)
+    out = tm.compute()
+    assert out["global_step"] == 2 and out["epoch"] == 1 and out["loss"] == 1.5 and out["lr"] == 1e-4
+    assert out["total_tokens"] == 16 and 0.0 <= out["accuracy"] <= 1.0
+    assert set(tm.log_dict()) >= {"train/loss", "train/ppl", "train/step", "train/mfu"}
+    assert tm.format_log_string().startswith("step=2 | loss=1.5000 | ppl=")
+    tm2 = TrainingMetrics()
+    tm2.load_state_dict(tm.state_dict())
+    assert tm2.compute(sync=False)["global_step"] == 2 and "tokens_per_second" in tm.summary()
+    tm.reset()
+    assert tm.loss.total_tokens == 0 and tm.compute()["global_step"] == 2
+    tm.reset_all()
+    assert tm.compute()["global_step"] == 0

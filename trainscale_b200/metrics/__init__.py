@@ -284,91 +284,7 @@ class R2Score(_Regression):
         return float(1 - ((p - t) ** 2).sum() / ((t - t.mean()) ** 2).sum().clamp(min=1e-12))
 
 
-class LossTracker:
-    """EMA loss (decay 0.99), token-weighted mean, perplexity; `sync()` reduces over ranks."""
-
-    def __init__(self, ema_decay: float = 0.99, window: int = 100):
-        self.decay, self.ema = ema_decay, None
-        self.sum, self.tokens = 0.0, 0
-        self.window = deque(maxlen=window)
-
-    def update(self, loss, num_tokens: int = 1):
-        l = float(loss)
-        if not math.isfinite(l):
-            return
-        self.ema = l if self.ema is None else self.decay * self.ema + (1 - self.decay) * l
-        self.sum += l * num_tokens
-        self.tokens += num_tokens
-        self.window.append(l)
-
-    @property
-    def mean(self): return self.sum / max(self.tokens, 1)
-    @property
-    def perplexity(self): return math.exp(min(self.mean, 50.0))
-    @property
-    def windowed(self): return sum(self.window) / max(len(self.window), 1)
-
-    def sync(self, group=None):
-        tot = sync_metrics({"sum": self.sum, "tokens": float(self.tokens)}, "sum", group)
-        return tot["sum"] / max(tot["tokens"], 1.0)
-
-    def state_dict(self): return {"ema": self.ema, "sum": self.sum, "tokens": self.tokens}
-
-    def load_state_dict(self, sd):
-        self.ema, self.sum, self.tokens = sd["ema"], sd["sum"], sd["tokens"]
-
-
-class AccuracyTracker:
-    """Next-token accuracy with the causal shift (logits[..., :-1] vs labels[..., 1:])."""
-
-    def __init__(self, ignore_index: int = -100):
-        self.ignore_index, self.correct, self.total = ignore_index, 0, 0
-
-    def update_from_logits(self, logits, labels):
-        p = logits[..., :-1, :].argmax(-1)
-        t = labels[..., 1:]
-        m = t != self.ignore_index
-        self.correct += int(((p == t) & m).sum())
-        self.total += int(m.sum())
-
-    @property
-    def accuracy(self): return self.correct / max(self.total, 1)
-
-
-class GradientTracker:
-    def __init__(self, window: int = 100, explode_threshold: float = 1e6):
-        self.norms = deque(maxlen=window)
-        self.nan_count, self.threshold, self.clipped = 0, explode_threshold, 0
-
-    def update(self, grad_norm, max_norm: float | None = None):
-        g = float(grad_norm)
-        if not math.isfinite(g):
-            self.nan_count += 1
-            return
-        self.norms.append(g)
-        if max_norm and g > max_norm:
-            self.clipped += 1
-
-    @property
-    def mean(self): return sum(self.norms) / max(len(self.norms), 1)
-    def exploding(self) -> bool: return bool(self.norms) and self.norms[-1] > self.threshold
-    def state_dict(self): return {"norms": list(self.norms), "nan_count": self.nan_count, "clipped": self.clipped}
-
-
-class TrainingMetrics:
-    """Bundle of the trackers a training loop updates."""
-
-    def __init__(self, flops_per_token: float = 0.0, world_size: int = 1):
-        self.loss, self.acc, self.grad = LossTracker(), AccuracyTracker(), GradientTracker()
-        self.throughput = ThroughputTracker(flops_per_token, world_size=world_size)
-
-    def summary(self) -> dict:
-        return {"loss": self.loss.mean, "loss_ema": self.loss.ema, "ppl": self.loss.perplexity, "acc": self.acc.accuracy,
-                "grad_norm": self.grad.mean, "tokens_per_second": self.throughput.tokens_per_second(),
-                "mfu": self.throughput.compute_mfu()}
-
-    def state_dict(self):
-        return {"loss": self.loss.state_dict(), "grad": self.grad.state_dict(), "throughput": self.throughput.state_dict()}
+from .trackers import AccuracyTracker, GradientTracker, LossTracker, TrainingMetrics  # noqa: E402,F401
 
 
 # ------------------------------------------------------------------------------------------------ names of the reference
@@ -432,9 +348,8 @@ def create_training_metrics(distributed: bool = False, model=None, log_prefix: s
     (data_pipeline/trainer/metrics/training.py:337-360)."""
     n = sum(p.numel() for p in model.parameters()) if model is not None else 0
     world = dist.get_world_size() if distributed and dist.is_available() and dist.is_initialized() else 1
-    tm = TrainingMetrics(flops_per_token=6.0 * n, world_size=world)
-    tm.log_prefix, tm.distributed = log_prefix, distributed
-    return tm
+    return TrainingMetrics(flops_per_token=6.0 * n, world_size=world, distributed=distributed, log_prefix=log_prefix,
+                           model_params=n or None)
 
 
 def is_distributed() -> bool:

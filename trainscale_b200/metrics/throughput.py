@@ -41,8 +41,11 @@ class ThroughputTracker:
         self.window = deque(maxlen=window)
         self.total_tokens = 0
         self.total_seconds = 0.0
+        self.total_samples = 0
+        self.step_count = 0
         self._pending: list[tuple] = []
         self._t0 = None
+        self._started = self._last = None
 
     def start_step(self):
         if self.cuda:
@@ -86,12 +89,78 @@ class ThroughputTracker:
     def tflops(self) -> float:
         return self.tokens_per_second() * self.flops_per_token / 1e12
 
-    def compute_mfu(self) -> float:
-        denom = self.peak * self.world_size
+    def compute_mfu(self, model_params: int | None = None, peak_tflops: float | None = None) -> float:
+        """Achieved FLOP/s over the peak of all GPUs.  FLOPs per token: the tracker's own figure, or 6 x `model_params`
+        (forward + backward of a dense decoder, attention not counted) when that is given."""
+        denom = (peak_tflops if peak_tflops is not None else self.peak) * self.world_size
+        if model_params:
+            rate = self.tokens_per_second() or self.tokens_per_sec()
+            return rate * 6.0 * model_params / 1e12 / denom if denom > 0 else 0.0
         return self.tflops() / denom if denom > 0 else 0.0
 
     def state_dict(self):
-        return {"total_tokens": self.total_tokens, "total_seconds": self.total_seconds}
+        return {"total_tokens": self.total_tokens, "total_seconds": self.total_seconds,
+                "total_samples": self.total_samples, "step_count": self.step_count}
 
     def load_state_dict(self, sd):
         self.total_tokens, self.total_seconds = sd["total_tokens"], sd["total_seconds"]
+        self.total_samples, self.step_count = sd.get("total_samples", 0), sd.get("step_count", 0)
+
+    # ---- wall-clock interface of the reference (data_pipeline/trainer/metrics/throughput.py:137-360): `start()`,
+    # then `update(samples, tokens)` once per step; rates are totals over the time since `start()`, or over the last
+    # `window` steps.  The CUDA-event interface above (`start_step` / `end_step`) feeds the same totals.
+    def reset(self) -> None:
+        self.window.clear()
+        self.total_tokens, self.total_seconds, self.total_samples, self.step_count = 0, 0.0, 0, 0
+        self._pending, self._t0, self._started, self._last = [], None, None, None
+
+    def start(self) -> None:
+        self._started = self._last = time.perf_counter()
+
+    def update(self, samples: int = 0, tokens: int = 0, flops: float = 0.0) -> None:
+        now = time.perf_counter()
+        if self._started is None:
+            self.start()
+            now = self._started
+        dt = now - self._last
+        self._last = now
+        self.total_samples += samples * self.world_size
+        self.step_count += 1
+        if dt > 0:
+            self._add(dt, tokens)
+        else:
+            self.total_tokens += tokens * self.world_size
+
+    def elapsed_seconds(self) -> float:
+        return (time.perf_counter() - self._started) if self._started is not None else self.total_seconds
+
+    def samples_per_sec(self) -> float:
+        s = self.elapsed_seconds()
+        return self.total_samples / s if s > 0 else 0.0
+
+    def tokens_per_sec(self) -> float:
+        self.flush()
+        s = self.elapsed_seconds() if self._started is not None else self.total_seconds
+        return self.total_tokens / s if s > 0 else 0.0
+
+    def tokens_per_sec_window(self) -> float:
+        return self.tokens_per_second()
+
+    def compute_tflops(self, flops_per_token: float | None = None) -> float:
+        f = self.flops_per_token if flops_per_token is None else flops_per_token
+        return self.tokens_per_sec() * f / 1e12
+
+    def sync(self, process_group=None) -> None:
+        """No-op when totals already count all ranks (`world_size` > 1 at construction); otherwise sum them."""
+        import torch.distributed as dist
+        if self.world_size > 1 or not (dist.is_available() and dist.is_initialized()):
+            return
+        dev = torch.device("cuda", torch.cuda.current_device()) if dist.get_backend(process_group) == "nccl" else "cpu"
+        t = torch.tensor([float(self.total_tokens), float(self.total_samples)], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, group=process_group)
+        self.total_tokens, self.total_samples = int(t[0]), int(t[1])
+
+    def log_dict(self) -> dict:
+        return {"throughput/tokens_per_sec": self.tokens_per_sec(), "throughput/samples_per_sec": self.samples_per_sec(),
+                "throughput/tokens_per_sec_window": self.tokens_per_sec_window(), "throughput/mfu": self.compute_mfu(),
+                "throughput/total_tokens": float(self.total_tokens), "throughput/elapsed_seconds": self.elapsed_seconds()}
