@@ -519,3 +519,71 @@ def test_dist_utils_expert_parallel_and_ddp_reference_names(tmp_path):
     r = D.create_ddp_from_yaml(str(y))
     assert r.is_ok() and r.unwrap().config.bucket_cap_mb == 64
     assert D.create_ddp_from_yaml(str(tmp_path / "missing.yaml")).is_err()
+
+
+def test_parallel_dims_state_pool_timer_and_manager_accessors():
+    import torch
+
+    from trainscale_b200.parallel import dist_utils as U
+    from trainscale_b200.parallel import mesh as M
+    from trainscale_b200.parallel import tp as T
+    d = M.ParallelDims.create(16, tp=2, cp=2, pp=2, rank=3).unwrap()
+    assert d.tp_enabled and d.cp_enabled and d.pp_enabled and d.dp_shard_enabled and not d.ep_enabled
+    assert d.fsdp_gradient_divide_factor == 4 and d.non_data_parallel_size == 8 and d.seq_len_divisor == 8
+    assert d.config.tp == 2 and d.device_type in ("cpu", "cuda")
+    views = d.build_mesh().unwrap()
+    assert views["dense"].shape == (2, 1, 4, 2) and d.build_mesh().unwrap() is views
+    assert d.get_mesh(["dp_shard", "tp"]).shape == (2, 2) and d.get_optional_mesh("ep") is None
+    assert sorted(d.get_all_1d_meshes()) == ["cp", "dp_shard", "pp", "tp"] and d.world_mesh.size() == 16
+    import pytest
+    with pytest.raises(ValueError):
+        d.get_mesh("dp_replicate")
+    with pytest.raises(ValueError):
+        d.get_optional_mesh("bogus")
+    d.get_mesh("tp")
+    d.get_mesh("tp")
+    assert d.metrics.num_cache_hits >= 1 and d.metrics.compute_cache_hit_rate() > 0
+    assert isinstance(d.get_communication_algorithm(1 << 20), M.CommunicationAlgorithm)
+    assert d.estimate_memory_per_gpu(8_000_000_000, 16, 8192, 4096, 32) > 2 ** 30
+    assert isinstance(M.HardwareDetector.detect_architecture(), M.GPUArchitecture)
+    assert M.HardwareDetector.get_optimal_device_order() == list(range(M.HardwareDetector.detect()["num_gpus"]))
+    M.MeshCache.set_global("dense", d.world_mesh)
+    assert M.MeshCache.get_global("dense") is not None and M.MeshCache.get_world() is None
+    M.MeshCache.clear()
+
+    st = U.DistributedState.from_environment()
+    assert st.is_main_process and st.is_local_main and not st.is_distributed and st.is_initialized and st.num_nodes == 1
+    t = torch.ones(3)
+    assert st.all_reduce(t, "mean") is t and st.broadcast(t) is t and st.get_data_parallel_group() is None
+    pool = st.tensor_pool
+    a = pool.acquire((3, 5))
+    pool.release(a)
+    b = pool.acquire(15)
+    assert a.data_ptr() == b.data_ptr() and pool.get_stats()["hit_rate"] == 0.5
+    pool.free()
+    assert pool.get_stats()["pooled_bytes"] == 0
+    tm = U.NanoTimer().start()
+    sum(range(10000))
+    assert tm.stop().elapsed_ns() > 0 and abs(tm.elapsed_ms() * 1e3 - tm.elapsed_us()) < 1e-6
+    with U.CUDATimer() as t2:
+        pass
+    assert t2.sync_and_elapsed_ms() >= 0
+    m = torch.nn.Linear(2, 2)
+    m(torch.ones(1, 2)).sum().backward()
+    g0 = m.weight.grad.clone()
+    gs = U.GradScaler(init_scale=4.0, growth_interval=1)
+    assert gs.unscale_(parameters=m.parameters()) and torch.allclose(m.weight.grad, g0 / 4)
+    gs.update()
+    assert gs.get_scale() == 8.0
+    m.weight.grad[0, 0] = float("inf")
+    assert not gs.unscale_(parameters=m.parameters())
+    gs.update()
+    assert gs.get_scale() == 4.0
+    assert U.DistributedManager.get_instance() is U.DistributedManager()
+    assert U.DeviceManager.auto_detect().compute_capability >= (0, 0)
+    mgr = T.ProcessGroupManager.get_instance().initialize(1, 1)
+    assert mgr.is_initialized() and mgr.get_world_size("tensor") == 1 and mgr.get_rank("data") == 0
+    assert mgr.get_group("sequence") is None
+    buf = mgr.acquire_buffer((4, 4))
+    mgr.release_buffer(buf)
+    mgr.destroy()

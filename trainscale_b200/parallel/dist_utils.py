@@ -10,6 +10,7 @@ from __future__ import annotations
 import contextlib
 import datetime
 import logging
+import math
 import os
 import random
 import time
@@ -83,9 +84,73 @@ class DistributedState:
     def device(self) -> torch.device:
         return torch.device("cuda", self.local_rank) if torch.cuda.is_available() else torch.device("cpu")
 
-    def barrier(self):
+    def barrier(self, group=None):
         if dist.is_initialized():
-            dist.barrier()
+            dist.barrier(group=group)
+
+    # ---- the reference's accessors (data_pipeline/trainer/distributed/__init__.py:176-262, sota_utils.py:666-1060)
+    is_main_process = property(lambda self: self.rank == 0)
+    is_local_main = property(lambda self: self.local_rank == 0)
+    is_local_main_process = property(lambda self: self.local_rank == 0)
+    is_distributed = property(lambda self: self.world_size > 1)
+    is_initialized = property(lambda self: self.world_size == 1 or (dist.is_available() and dist.is_initialized()))
+    initialized = property(lambda self: self.is_initialized)
+    num_nodes = property(lambda self: max(1, self.world_size // max(1, self.local_world_size)))
+    node_rank = property(lambda self: self.rank // max(1, self.local_world_size))
+
+    @property
+    def tensor_pool(self) -> "TensorPool":
+        if "_pool" not in self.__dict__:
+            self.__dict__["_pool"] = TensorPool(self.device)
+        return self.__dict__["_pool"]
+
+    def broadcast(self, tensor: torch.Tensor, src: int = 0, group=None, async_op: bool = False):
+        if not (self.is_distributed and dist.is_initialized()):
+            return tensor
+        work = dist.broadcast(tensor, src=src, group=group, async_op=async_op)
+        return work if async_op else tensor
+
+    def all_reduce(self, tensor: torch.Tensor, op: str = "sum", group=None, async_op: bool = False):
+        """In-place all-reduce; `op` sum | mean | max | min | prod (a `dist.ReduceOp` works too).  With `async_op` the
+        work handle is returned and a mean still has to be divided by the caller after `wait()`."""
+        if not (self.is_distributed and dist.is_initialized()):
+            return tensor
+        name = op if isinstance(op, str) else str(getattr(op, "name", op))
+        name = name.lower().split(".")[-1]
+        table = {"sum": dist.ReduceOp.SUM, "mean": dist.ReduceOp.SUM, "avg": dist.ReduceOp.SUM,
+                 "max": dist.ReduceOp.MAX, "min": dist.ReduceOp.MIN, "prod": dist.ReduceOp.PRODUCT,
+                 "product": dist.ReduceOp.PRODUCT}
+        work = dist.all_reduce(tensor, op=table[name], group=group, async_op=async_op)
+        if async_op:
+            return work
+        if name in ("mean", "avg"):
+            tensor.div_(dist.get_world_size(group))
+        return tensor
+
+    def get_process_group(self, name: str, ranks: list | None = None):
+        """Named process group, created once (collectively: every rank must ask for the same groups in the same
+        order); None without an initialised job."""
+        groups = self.__dict__.setdefault("_groups", {})
+        if name not in groups:
+            if not (dist.is_available() and dist.is_initialized()):
+                return None
+            groups[name] = dist.new_group(ranks=ranks if ranks is not None else list(range(self.world_size)))
+        return groups[name]
+
+    def get_data_parallel_group(self):
+        return self.get_process_group("data_parallel")
+
+    def get_tensor_parallel_group(self, tp_size: int):
+        """Group of this rank among groups of `tp_size` consecutive ranks (all groups are created, in rank order)."""
+        if self.world_size % tp_size:
+            raise ValueError(f"world size {self.world_size} is not divisible by tp_size {tp_size}")
+        mine = None
+        for g in range(self.world_size // tp_size):
+            ranks = list(range(g * tp_size, (g + 1) * tp_size))
+            grp = self.get_process_group(f"tensor_parallel_{tp_size}_{g}", ranks)
+            if self.rank in ranks:
+                mine = grp
+        return mine
 
     def shutdown(self):
         if self.initialized_here and dist.is_initialized():
@@ -133,8 +198,108 @@ class NanoTimer:
         self.flush()
         return {k: self.totals[k] / self.counts[k] for k in self.totals}
 
+    # ---- single-interval interface (data_pipeline/trainer/distributed/sota_utils.py NanoTimer, context_parallel.py
+    # CUDATimer): start() ... stop(), then elapsed_*; on CUDA the interval is measured with two events on the current
+    # stream and reading it waits for the second event only.
+    def start(self) -> "NanoTimer":
+        if self.cuda:
+            self._a, self._b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            self._a.record()
+        else:
+            self._a, self._b = time.perf_counter_ns(), None
+        return self
+
+    def stop(self) -> "NanoTimer":
+        if self.cuda:
+            self._b.record()
+        else:
+            self._b = time.perf_counter_ns()
+        return self
+
+    def elapsed_ns(self) -> int:
+        if getattr(self, "_b", None) is None:
+            return 0
+        if self.cuda:
+            self._b.synchronize()
+            return int(self._a.elapsed_time(self._b) * 1e6)
+        return int(self._b - self._a)
+
+    def elapsed_us(self) -> float:
+        return self.elapsed_ns() / 1e3
+
+    def elapsed_ms(self) -> float:
+        return self.elapsed_ns() / 1e6
+
+    sync_and_elapsed_ms = elapsed_ms
+
+    def __enter__(self):
+        return self.start()
+
+    def __exit__(self, *exc):
+        self.stop()
+        return False
+
 
 CUDATimer = NanoTimer
+Timer = NanoTimer
+
+
+class TensorPool:
+    """Recycles scratch tensors by size class (powers of two of the byte count), per dtype, so that collectives and
+    staging copies do not hit the allocator every step (data_pipeline/trainer/distributed/sota_utils.py:511-640).
+    `acquire(shape, dtype)` returns a view of a pooled buffer, `release(t)` gives it back."""
+
+    def __init__(self, device=None, max_bytes: int = 4 * 2 ** 30):
+        self.device = torch.device(device) if device is not None else torch.device("cpu")
+        self.max_bytes = max_bytes
+        self._free: dict[tuple, list[torch.Tensor]] = {}
+        self._owner: dict[int, torch.Tensor] = {}
+        self._held = 0
+        self._stats = {"acquires": 0, "hits": 0, "releases": 0, "dropped": 0}
+
+    @staticmethod
+    def _size_class(nbytes: int) -> int:
+        return 1 << max(9, (max(nbytes, 1) - 1).bit_length())          # 512 B granularity at the bottom
+
+    def acquire(self, shape, dtype: torch.dtype = torch.float32, zero: bool = False) -> torch.Tensor:
+        shape = (shape,) if isinstance(shape, int) else tuple(shape)
+        n = math.prod(shape)
+        esz = torch.empty(0, dtype=dtype).element_size()
+        cls_bytes = self._size_class(n * esz)
+        self._stats["acquires"] += 1
+        lst = self._free.get((cls_bytes, dtype))
+        if lst:
+            buf = lst.pop()
+            self._held -= cls_bytes
+            self._stats["hits"] += 1
+        else:
+            buf = torch.empty(cls_bytes // esz, dtype=dtype, device=self.device)
+        out = buf[:n].view(shape)
+        self._owner[out.data_ptr()] = buf
+        return out.zero_() if zero else out
+
+    def release(self, tensor: torch.Tensor) -> None:
+        buf = self._owner.pop(tensor.data_ptr(), None)
+        if buf is None:
+            return                                   # not from this pool
+        nbytes = buf.numel() * buf.element_size()
+        self._stats["releases"] += 1
+        if self._held + nbytes > self.max_bytes:
+            self._stats["dropped"] += 1
+            return
+        self._free.setdefault((nbytes, buf.dtype), []).append(buf)
+        self._held += nbytes
+
+    def free(self) -> None:
+        """Drop every pooled buffer (outstanding tensors stay valid)."""
+        self._free.clear()
+        self._held = 0
+
+    reset = free
+
+    def get_stats(self) -> dict:
+        a = self._stats["acquires"]
+        return dict(self._stats, pooled_bytes=self._held, hit_rate=self._stats["hits"] / a if a else 0.0)
 
 
 @torch.no_grad()
@@ -212,6 +377,35 @@ class GradScaler:
             self.scale_value *= self.backoff
             self._good = 0
         return finite
+
+    def unscale_(self, optimizer=None, parameters=None) -> bool:
+        """Divide the gradients by the scale in place; returns whether they are all finite (the verdict `update` uses)."""
+        if not self.enabled:
+            return True
+        params = list(parameters) if parameters is not None else [p for g in optimizer.param_groups for p in g["params"]]
+        params = [p for p in params if p.grad is not None]
+        self._finite = all(bool(torch.isfinite(p.grad).all()) for p in params)
+        if self._finite:
+            for p in params:
+                p.grad.div_(self.scale_value)
+        return self._finite
+
+    def update(self, new_scale: float | None = None) -> None:
+        """Grow the scale after `growth_interval` finite steps in a row, back off after a non-finite one
+        (the verdict of the last `unscale_`); or set it."""
+        if new_scale is not None:
+            self.scale_value = float(new_scale)
+            return
+        if getattr(self, "_finite", True):
+            self._good += 1
+            if self._good % self.interval == 0:
+                self.scale_value *= self.growth
+        else:
+            self.scale_value *= self.backoff
+            self._good = 0
+
+    def get_scale(self) -> float:
+        return self.scale_value
 
     def state_dict(self):
         return {"scale": self.scale_value, "good": self._good}
@@ -352,6 +546,19 @@ class DistributedManager:
             cls._instance.state = None
         return cls._instance
 
+    @classmethod
+    def get_instance(cls) -> "DistributedManager":
+        return cls()
+
+    def barrier(self, group=None) -> None:
+        if dist.is_available() and dist.is_initialized():
+            dist.barrier(group=group)
+
+    def destroy_process_group(self) -> None:
+        if dist.is_available() and dist.is_initialized():
+            dist.destroy_process_group()
+        self.state = None
+
     def init_process_group(self, backend: str | None = None) -> "DistributedState":
         self.state = DistributedState.from_environment()
         self.state.initialize(backend)
@@ -449,6 +656,17 @@ class DeviceManager:
 
     def supports_bf16(self) -> bool:
         return (not self.cuda) or torch.cuda.get_device_capability(self.device)[0] >= 8
+
+    @classmethod
+    def auto_detect(cls) -> "DeviceManager":
+        return cls()
+
+    @property
+    def compute_capability(self) -> tuple:
+        return torch.cuda.get_device_capability(self.device) if self.cuda else (0, 0)
+
+    def supports_fp8(self) -> bool:
+        return self.cuda and self.compute_capability >= (8, 9)
 
     def memory_stats(self) -> dict[str, float]:
         if not self.cuda:

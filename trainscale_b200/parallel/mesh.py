@@ -158,6 +158,112 @@ class ParallelDims:
     def describe(self) -> str:
         return " x ".join(f"{d}={self.sizes[d]}" for d in DIM_ORDER) + f" | rank {self.rank} at {self.coords}"
 
+    # ---------------------------------------------------------------- the reference's accessors
+    # (data_pipeline/trainer/distributed/parallel_dims.py:1168-1640).  Meshes are `MeshView`s (names, sizes, this rank's
+    # coordinates, process groups created on demand) instead of torch DeviceMesh objects.
+    @classmethod
+    def create(cls, world_size: int, dp_replicate: int = 1, dp_shard: int = -1, cp: int = 1, tp: int = 1, pp: int = 1,
+               ep: int = 1, etp: int = 1, sp: int = 1, **kwargs):
+        return create_parallel_dims(world_size, dp_replicate, dp_shard, cp, tp, pp, ep, etp, sp, **kwargs)
+
+    @property
+    def config(self) -> ParallelDimsConfig:
+        return self.cfg
+
+    def build_mesh(self):
+        """Ok({view name: MeshView}) for the dataloading / loss / dense / sparse views (built once)."""
+        from ..core.types import Err, Ok
+        import time
+        try:
+            if getattr(self, "_views", None) is None:
+                t0 = time.perf_counter_ns()
+                self._views = build_mesh(self)
+                self.metrics.mesh_build_ns += time.perf_counter_ns() - t0
+            return Ok(self._views)
+        except (RuntimeError, ValueError) as e:
+            return Err(e)
+
+    def get_optional_mesh(self, dims):
+        """`MeshView` over one dimension name or a list of them; None when every named dimension has size 1."""
+        names = [dims] if isinstance(dims, str) else list(dims)
+        valid = set(DIM_ORDER) | set(self._FLAT) | {"ep", "etp"}
+        for n in names:
+            if n not in valid:
+                raise ValueError(f"invalid mesh dim {n!r}; valid: {sorted(valid)}")
+        m = self.metrics
+        m.num_mesh_accesses += 1
+        key = tuple(names)
+        cache = self.__dict__.setdefault("_mesh_cache", {})
+        if key in cache:
+            m.num_cache_hits += 1
+            return cache[key]
+        m.num_cache_misses += 1
+        sized = {n: (getattr(self.cfg, n) if n in ("ep", "etp") else self.size(n)) for n in names}
+        view = None if all(v == 1 for v in sized.values()) else MeshView("x".join(names), self, [n for n in names])
+        cache[key] = view
+        return view
+
+    def get_mesh(self, dims):
+        view = self.get_optional_mesh(dims)
+        if view is None:
+            raise ValueError(f"mesh {dims!r} is not available (every named dimension has size 1)")
+        return view
+
+    def get_all_1d_meshes(self) -> dict:
+        out = {}
+        for n in ("pp", "dp_replicate", "dp_shard", "cp", "tp"):
+            if self.sizes[n] > 1:
+                out[n] = self.get_mesh(n)
+        return out
+
+    @property
+    def world_mesh(self) -> "MeshView":
+        return MeshView("world", self, DIM_ORDER)
+
+    dp_replicate_enabled = property(lambda self: self.cfg.dp_replicate > 1)
+    dp_shard_enabled = property(lambda self: self.cfg.dp_shard > 1)
+    dp_enabled = property(lambda self: self.cfg.dp_replicate > 1 or self.cfg.dp_shard > 1)
+    fsdp_enabled = property(lambda self: self.cfg.dp_shard > 1 or self.cfg.cp > 1)
+    cp_enabled = property(lambda self: self.cfg.cp > 1)
+    tp_enabled = property(lambda self: self.cfg.tp > 1)
+    pp_enabled = property(lambda self: self.cfg.pp > 1)
+    ep_enabled = property(lambda self: self.cfg.ep > 1)
+    etp_enabled = property(lambda self: self.cfg.etp > 1)
+    sp_enabled = property(lambda self: bool(self.cfg.sp))
+    fsdp_gradient_divide_factor = property(lambda self: self.cfg.dp_replicate * self.cfg.dp_shard * self.cfg.cp)
+    non_data_parallel_size = property(lambda self: self.cfg.cp * self.cfg.tp * self.cfg.pp)
+    # tokens per sequence must divide by tp (sequence parallelism) and by 2 * cp (head-tail balanced context shards)
+    seq_len_divisor = property(lambda self: self.cfg.tp * self.cfg.cp * 2)
+    device_type = property(lambda self: "cuda" if torch.cuda.is_available() else "cpu")
+    hardware_vendor = property(lambda self: HardwareDetector.detect_vendor())
+    architecture = property(lambda self: HardwareDetector.detect_architecture())
+    intra_node_interconnect = property(lambda self: HardwareDetector.detect_intra_node_interconnect())
+
+    @property
+    def metrics(self) -> "ParallelDimsMetrics":
+        if "_metrics" not in self.__dict__:
+            self.__dict__["_metrics"] = ParallelDimsMetrics()
+        return self.__dict__["_metrics"]
+
+    def get_communication_algorithm(self, message_size_bytes: int, dim_name: str = "dp_shard") -> "CommunicationAlgorithm":
+        """What an all-reduce of that size along `dim_name` should use.  On an NVSwitch node every peer is one hop away,
+        so small messages go through one-shot peer kernels and large ones through the in-switch reduction; both are
+        reported as NCCL_AUTO / TREE / RING in the reference's vocabulary."""
+        n = self.size(dim_name) if dim_name in set(DIM_ORDER) | set(self._FLAT) else 1
+        if n <= 1:
+            return CommunicationAlgorithm.NCCL_AUTO
+        kind = CommAlgorithmSelector(n, nvswitch=HardwareDetector.detect().get("nvswitch", False)).all_reduce(
+            message_size_bytes)
+        return {"one_shot_p2p": CommunicationAlgorithm.TREE, "multimem": CommunicationAlgorithm.NCCL_AUTO,
+                "ring": CommunicationAlgorithm.RING}.get(kind, CommunicationAlgorithm.NCCL_AUTO)
+
+    def estimate_memory_per_gpu(self, model_params: int, batch_size: int, seq_len: int, hidden_dim: int, num_layers: int,
+                                use_activation_checkpointing: bool = False, precision_bytes: int = 2) -> int:
+        c = self.cfg
+        return MemoryEstimator.estimate_per_gpu_memory(
+            model_params, max(1, batch_size // max(1, c.dp_replicate * c.dp_shard)), seq_len, hidden_dim, num_layers,
+            c.tp, c.pp, c.cp, c.dp_shard * c.dp_replicate, use_activation_checkpointing, precision_bytes)
+
 
 class MeshView:
     """One named view of the mesh: ordered dimension names (outer first), their sizes, this rank's coordinates and
@@ -199,12 +305,20 @@ def build_mesh(dims: "ParallelDims") -> dict[str, MeshView]:
             "sparse": MeshView("sparse", dims, ("pp", "dp_replicate", "fsdp", "tp"))}
 
 
+class ParallelDimsMetricsLite:
+    """Access counters of `MeshCache` (the full record, `ParallelDimsMetrics`, is defined further down)."""
+
+    def __init__(self):
+        self.num_mesh_accesses = self.num_cache_hits = self.num_cache_misses = 0
+
+
 class MeshCache:
     """Process groups are expensive to create and must be created by all ranks in the same order: one ParallelDims
     (with its lazily created groups and views) per distinct configuration, shared by every engine of the process."""
 
     _cache: dict[tuple, "ParallelDims"] = {}
     _views: dict[tuple, dict[str, MeshView]] = {}
+    metrics = ParallelDimsMetricsLite()
 
     @staticmethod
     def _key(cfg: ParallelDimsConfig) -> tuple:
@@ -229,6 +343,44 @@ class MeshCache:
     def clear(cls) -> None:
         cls._cache.clear()
         cls._views.clear()
+        cls._named.clear()
+        cls.metrics = ParallelDimsMetricsLite()
+
+    # name -> mesh store of the reference (parallel_dims.py:600-700): 1-D meshes by dimension name, the flattened
+    # "global" meshes (dataloading / dense / sparse) and the world mesh
+    _named: dict = {}
+
+    @classmethod
+    def set(cls, name: str, mesh) -> None:
+        cls._named[("dim", name)] = mesh
+
+    @classmethod
+    def set_global(cls, name: str, mesh) -> None:
+        cls._named[("global", name)] = mesh
+
+    @classmethod
+    def get_global(cls, name: str):
+        return cls._lookup(("global", name))
+
+    @classmethod
+    def set_world(cls, mesh) -> None:
+        cls._named[("world", "")] = mesh
+
+    @classmethod
+    def get_world(cls):
+        return cls._lookup(("world", ""))
+
+    @classmethod
+    def get_named(cls, name: str):
+        return cls._lookup(("dim", name))
+
+    @classmethod
+    def _lookup(cls, key):
+        cls.metrics.num_mesh_accesses += 1
+        hit = key in cls._named
+        cls.metrics.num_cache_hits += hit
+        cls.metrics.num_cache_misses += not hit
+        return cls._named.get(key)
 
 
 def create_parallel_dims_from_config(dist_cfg, world_size: int | None = None, rank: int | None = None) -> ParallelDims:
@@ -299,6 +451,35 @@ class HardwareDetector:
             except Exception:
                 pass
         return info
+
+
+def _hd_cc(device: int = 0) -> tuple:
+    return torch.cuda.get_device_capability(device) if torch.cuda.is_available() else (0, 0)
+
+
+def _hd_install():
+    """Typed single-fact probes of the reference (parallel_dims.py:294-700) as static methods of `HardwareDetector`,
+    all derived from `detect()` / `detect_node_topology()`."""
+    H = HardwareDetector
+    H.detect_vendor = staticmethod(lambda: HardwareVendor.NVIDIA if torch.cuda.is_available() else HardwareVendor.CPU)
+    H.detect_compute_capability = staticmethod(_hd_cc)
+    H.detect_architecture = staticmethod(lambda device=0: GPUArchitecture.from_compute_capability(_hd_cc(device))
+                                         if torch.cuda.is_available() else GPUArchitecture.UNKNOWN)
+    H.detect_node_topology = staticmethod(lambda: detect_node_topology())
+    H.detect_numa_topology = staticmethod(lambda: detect_node_topology().numa_topology)
+    H.detect_intra_node_interconnect = staticmethod(lambda: detect_node_topology().intra_node_interconnect)
+    H.detect_inter_node_interconnect = staticmethod(lambda: detect_cluster_topology().inter_node_interconnect)
+    H.detect_nvlink_topology = staticmethod(lambda: {g.index: list(g.nvlink_connected)
+                                                     for g in detect_node_topology().gpu_info})
+
+    def get_optimal_device_order() -> list:
+        """GPU indices ordered so that neighbours in the list are neighbours in hardware: grouped by NUMA node, inside
+        a node by index.  With a switch every order is equally good and the natural order is returned."""
+        node = detect_node_topology()
+        if node.has_nvswitch or node.numa_topology is None:
+            return list(range(node.num_gpus))
+        return [g for grp in node.numa_topology.gpus_per_node for g in sorted(grp)]
+    H.get_optimal_device_order = staticmethod(get_optimal_device_order)
 
 
 class MemoryEstimator:
@@ -557,3 +738,6 @@ def create_parallel_dims(world_size: int, dp_replicate: int = 1, dp_shard: int =
                                create_groups=create_groups))
     except ValueError as e:
         return Err(e)
+
+
+_hd_install()

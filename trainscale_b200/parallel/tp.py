@@ -452,6 +452,55 @@ class ProcessGroupManager:
     def destroy(self) -> None:
         type(self)._instance = None
 
+    # ---- accessors by mode name (data_pipeline/trainer/distributed/tensor_parallel.py:133-395): "tensor" |
+    # "sequence" (the tensor group) | "pipeline" | "data"
+    config = None
+
+    @classmethod
+    def get_instance(cls) -> "ProcessGroupManager":
+        return cls.get()
+
+    def is_initialized(self) -> bool:
+        return self.initialized
+
+    @staticmethod
+    def _mode(mode) -> str:
+        m = str(getattr(mode, "name", mode)).lower()
+        return {"tensor": "tp", "tp": "tp", "sequence": "tp", "sp": "tp", "pipeline": "pp", "pp": "pp", "data": "dp",
+                "dp": "dp"}[m]
+
+    def get_group(self, mode="tensor"):
+        return getattr(self, self._mode(mode) + "_group")
+
+    def get_rank(self, mode="tensor") -> int:
+        return getattr(self, self._mode(mode) + "_rank")
+
+    def get_world_size(self, mode="tensor") -> int:
+        return getattr(self, self._mode(mode) + "_size")
+
+    def get_stream(self, mode="tensor"):
+        """A side stream per mode for library collectives that should overlap compute (None without CUDA)."""
+        if not torch.cuda.is_available():
+            return None
+        streams = self.__dict__.setdefault("_streams", {})
+        key = self._mode(mode)
+        if key not in streams:
+            streams[key] = torch.cuda.Stream()
+        return streams[key]
+
+    def acquire_buffer(self, shape, dtype=torch.float32, device=None) -> torch.Tensor:
+        from .dist_utils import TensorPool
+        pools = self.__dict__.setdefault("_pools", {})
+        dev = torch.device(device) if device is not None else (
+            torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu"))
+        if dev not in pools:
+            pools[dev] = TensorPool(dev)
+        return pools[dev].acquire(shape, dtype)
+
+    def release_buffer(self, tensor: torch.Tensor) -> None:
+        for pool in self.__dict__.get("_pools", {}).values():
+            pool.release(tensor)
+
 
 class ParallelEmbedding(nn.Module):
     """Embedding table split along the HIDDEN dimension: every rank looks up all tokens in its slice of columns and the
