@@ -1,0 +1,290 @@
+"""Behaviour of the members that classes share with the reference by name: builders, tokenizer wrapper, DDP engine
+records, training configuration, serving engines, hub manager, length manager, callbacks, LoRA layer, trainer."""
+import asyncio
+import os
+
+import pytest
+import torch
+import torch.nn as nn
+
+
+def test_dataloader_builder_fluent_chain():
+    from trainscale_b200.data.dataloader_factory import DataLoaderBuilder
+    ds = [{"input_ids": torch.arange(n + 1), "labels": torch.arange(n + 1)} for n in range(10)]
+    dl = (DataLoaderBuilder().with_dataset(ds).with_batch_size(4).with_shuffle(False).with_seed(3).with_num_workers(0)
+          .with_pin_memory(False).with_drop_last(True).with_padding(pad_token_id=7, label_pad_token_id=-100).build())
+    batches = list(dl)
+    assert len(batches) == 2                                  # 10 rows, batch 4, last dropped
+    b = batches[0]
+    assert b["input_ids"].shape == (4, 4) and b["input_ids"][0, 1:].tolist() == [7, 7, 7]
+    assert b["labels"][0, 1:].tolist() == [-100, -100, -100]
+
+
+def test_tokenizer_wrapper_vocabulary_members():
+    from trainscale_b200.data.tokenization import ByteTokenizer, TokenizerWrapper
+    w = TokenizerWrapper(ByteTokenizer())
+    assert len(w) == w.vocab_size and w.original_vocab_size <= w.vocab_size
+    assert w.num_added_tokens == w.vocab_size - w.original_vocab_size
+    assert w.vocab_was_modified == (w.num_added_tokens > 0)
+    ids = w.encode_raw("hi there")
+    assert w.decode_batch([ids, ids]) == [w.decode(ids)] * 2
+    toks = w.convert_ids_to_tokens(list(ids))
+    assert w.convert_tokens_to_ids(toks) == list(ids)
+    info = w.get_special_tokens_info()
+    assert set(w.get_all_special_token_ids()) >= {v for v in (info.get("pad_token_id"), info.get("eos_token_id"))
+                                                   if v is not None}
+
+
+def test_ddp_metrics_and_pressure_monitor():
+    from trainscale_b200.parallel.ddp import DDPMetrics, MemoryPressureMonitor
+    m = DDPMetrics()
+    for _ in range(4):
+        m.record_allreduce(4 * 10 ** 9, 2.0)
+        m.steps += 1
+    assert m.compute_avg_latency_ms() == pytest.approx(2.0)
+    assert m.compute_bandwidth_gbps() == pytest.approx(16 / 0.008)
+    m.reset()
+    assert m.steps == 0 and m.compute_avg_latency_ms() == 0.0 and m.compute_bandwidth_gbps() == 0.0
+    used = [10]
+    mon = MemoryPressureMonitor(probe=lambda: (used[0], 100))
+    assert mon.get_pressure_level() == 0
+    used[0] = 90
+    assert mon.get_pressure_level() == 1
+    used[0] = 99
+    assert mon.get_pressure_level() == 2
+    assert mon.allocated_bytes >= 0 and mon.reserved_bytes >= 0 and mon.emergency_free() >= 0
+
+
+def test_training_config_reference_fields_and_aliases():
+    from trainscale_b200.config.sota_config import SOTAConfig
+    from trainscale_b200.config.training_args import TrainingConfig, TrainingMode, get_qlora_config
+    c = TrainingConfig(model_name="tiny", batch_size=2, gradient_accumulation_steps=4)
+    assert c.model_name_or_path == "tiny" and c.per_device_train_batch_size == 2
+    assert c.effective_batch_size == 8
+    q = get_qlora_config("tiny", r=8)
+    assert q.training_mode == TrainingMode.QLORA and q.load_in_4bit and q.to_lora_config().r == 8
+    assert q.to_quant_config().load_in_4bit
+    again = TrainingConfig.from_dict(q.to_dict())
+    assert again.to_dict() == q.to_dict()
+    s = SOTAConfig.from_dict(q.to_sota_dict())
+    assert s.lora.enabled and s.lora.r == 8
+
+
+def _cpu_engine_config(preset):
+    preset.device = "cpu"
+    preset.cache.num_gpu_blocks = 64
+    return preset
+
+
+def test_engine_presets_profiles():
+    from trainscale_b200.inference.engine import EnginePresets
+    hi, lo = EnginePresets.high_throughput_batch("tiny"), EnginePresets.low_latency_interactive("tiny")
+    assert hi.scheduler.max_num_seqs > lo.scheduler.max_num_seqs
+    assert hi.scheduler.max_num_batched_tokens > lo.scheduler.max_num_batched_tokens
+    sp = EnginePresets.speculative_fast_decode("tiny", draft_model="tiny", num_speculative_tokens=3)
+    assert sp.speculative.enabled and sp.speculative.num_speculative_tokens == 3
+    assert EnginePresets.quantized_memory_efficient("tiny", "fp8").quantization.method == "fp8"
+    big = EnginePresets.multi_gpu_large_model("tiny", tp_size=4, pp_size=2)
+    assert big.parallel.tensor_parallel_size == 4 and big.parallel.pipeline_parallel_size == 2
+    ml = EnginePresets.multi_lora_serving("tiny", max_lora_rank=32, max_concurrent_loras=2)
+    assert ml.lora.enabled and ml.lora.max_loras == 2 and ml.lora.max_lora_rank == 32
+
+
+def test_generate_with_lora_loads_adapter_directory(tmp_path):
+    from trainscale_b200 import lora as L
+    from trainscale_b200.inference.engine import EnginePresets, GenerationParams, SOTAInferenceEngine
+    from trainscale_b200.models.llama import build_model
+    m = L.get_peft_model(build_model("tiny", dtype=torch.float32, device="cpu", seed=0), L.LoraConfig(r=4))
+    e = SOTAInferenceEngine(_cpu_engine_config(EnginePresets.multi_lora_serving("tiny")), model=m)
+    gp = GenerationParams(max_tokens=4, temperature=0.0)
+    base = e.generate_single("hello", gp).unwrap().token_ids
+    for n, p in m.named_parameters():
+        if "lora_B" in n:
+            nn.init.normal_(p, std=0.5)
+    L.save_adapter(m, tmp_path)
+    for n, p in m.named_parameters():                     # the model itself goes back to a no-op adapter
+        if "lora_B" in n:
+            nn.init.zeros_(p)
+    tuned = e.generate_with_lora("hello", "a1", str(tmp_path), params=gp).unwrap().token_ids
+    assert tuned != base
+    assert e.generate_single("hello", gp).unwrap().token_ids == base        # requests without an adapter are unchanged
+    assert e.generate_with_lora("hello", "a1", params=gp).unwrap().token_ids == tuned   # found by name the second time
+    assert e.generate_with_lora("x", "unknown").is_err()
+    assert e.get_metrics_summary()["requests"] == 4 and e.engine is e.core and e.metrics is e.core.metrics
+
+
+def test_async_engine_generate_batch_and_shutdown():
+    from trainscale_b200.inference.engine import (EnginePresets, GenerationParams, SOTAAsyncStreamEngine,
+                                                  SOTAInferenceEngine)
+    cfg = _cpu_engine_config(EnginePresets.low_latency_interactive("tiny"))
+    gp = GenerationParams(max_tokens=3, temperature=0.0)
+    a = SOTAAsyncStreamEngine(cfg)
+    sync_ids = SOTAInferenceEngine(cfg, model=a.core.model).generate_single("abc", gp).unwrap().token_ids
+
+    async def main():
+        one = (await a.generate("abc", gp)).unwrap()
+        many = (await a.generate_batch(["a", "bb", "ccc"], gp)).unwrap()
+        assert a.active_request_count == 0
+        await a.shutdown()
+        return one, many
+
+    one, many = asyncio.run(main())
+    assert one.token_ids == sync_ids and len(many) == 3 and all(len(r.token_ids) == 3 for r in many)
+    assert a.get_metrics_summary()["requests"] == 4
+
+
+def test_request_metrics_marks():
+    from trainscale_b200.inference.engine import RequestMetrics
+    m = RequestMetrics("r")
+    m.mark_submitted()
+    m.mark_first_token()
+    first = m.first_token
+    m.mark_first_token()
+    assert m.first_token == first                         # only the first call counts
+    m.mark_complete(5)
+    assert m.completion_tokens == 5 and m.e2e >= m.ttft >= 0 and m.tpot is not None
+
+
+def test_hub_manager_round_trip_through_a_local_folder(tmp_path):
+    from trainscale_b200.hub import HubConfig, HubErrorCode, HubManager, ModelSerializer
+    src, dst = nn.Linear(64, 64), nn.Linear(64, 64)
+    h = HubManager(HubConfig(repo_id="someone/model", token="", shard_size_bytes=8 * 1024))
+    seen = []
+    r = h.push_to_hub(src, local_dir=tmp_path, progress_callback=lambda a, b: seen.append((a, b)))
+    # no network / token here: the upload itself fails with a classified error, the folder is complete
+    assert r.is_err() and r.error.context["code"] == HubErrorCode.DEPENDENCY_MISSING
+    assert (tmp_path / "README.md").exists() and seen and seen[0][0] == 0
+    assert h.load_from_hub(dst, str(tmp_path)).is_ok()
+    assert torch.equal(src.weight, dst.weight) and torch.equal(src.bias, dst.bias)
+    assert h.get_metrics()["uploads_failed"] >= 1 and h.config.repo_id == "someone/model"
+    assert HubManager().push_to_hub(src).error.context["code"] == HubErrorCode.VALIDATION_ERROR
+    assert HubManager().pull_from_hub().is_err()
+    ser = ModelSerializer(8 * 1024)
+    res = ser.serialize(src, tmp_path / "again").unwrap()
+    assert res.total_bytes > 0 and len(res.shards) >= 1 and isinstance(ser.safetensors_available, bool)
+
+
+def test_length_manager_column_limits():
+    from trainscale_b200.data.length_manager import (ColumnLengthConfig, LengthManager, LengthManagerConfig,
+                                                     TokenEstimator)
+    lm = LengthManager(LengthManagerConfig(max_total_length=64, per_column={"a": ColumnLengthConfig("a", max_length=5)}))
+    assert lm.max_length == 64 and lm.padding_strategy == lm.config.padding_strategy
+    assert lm.get_column_config("a").max_tokens == 5 and lm.get_column_config("zzz").max_tokens is None
+    lm.set_column_config("b", ColumnLengthConfig(max_chars=7))
+    assert lm.preprocess_text("hello world this is long", "b") == "hello w"
+    assert len(lm.preprocess_text("x" * 100, "a")) == lm.estimator.tokens_to_chars(5)
+    assert lm.preprocess_text("x" * 100, "a", max_chars=3) == "xxx"          # the explicit limit wins
+    assert len(lm.preprocess_text("y" * 1000)) == lm.estimator.tokens_to_chars(64)
+    assert lm.preprocess_text("", "a") == ""
+    te = TokenEstimator(chars_per_token=4.0)
+    assert te.estimate_tokens("") == 0 and te.estimate_tokens("abcdefgh") == 2 and te.tokens_to_chars(10) == 40
+
+    class Tok:
+        def encode(self, text):
+            return text.split()
+    assert TokenEstimator(Tok()).estimate_tokens("a b c") == 3
+
+
+def test_callback_handler_trigger_stops_at_should_stop():
+    from trainscale_b200.callbacks import Callback, CallbackContext, CallbackHandler
+    calls = []
+
+    class A(Callback):
+        order = 0
+        def on_step_end(self, ctx):
+            calls.append("a")
+            ctx.should_stop = True
+
+    class B(Callback):
+        order = 1
+        def on_step_end(self, ctx):
+            calls.append("b")
+
+    h = CallbackHandler()
+    h.add_callback(B())
+    h.add_callback(A())
+    h.set_trainer("trainer")
+    assert all(c.trainer == "trainer" for c in h.callbacks) and h.callbacks[0].priority == 0
+    h.trigger("on_step_end", CallbackContext())
+    assert calls == ["a"]                                  # B is skipped once A asked to stop
+    h.fire("on_step_end", CallbackContext())
+    assert calls == ["a", "a", "b"]
+    h.remove_callback(A)
+    assert [type(c) for c in h.callbacks] == [B]
+    with pytest.raises(ValueError):
+        h.trigger("no_such_hook", CallbackContext())
+
+
+def test_lora_linear_from_linear_and_merge():
+    from trainscale_b200.lora import LoRALinear
+    torch.manual_seed(0)
+    lin = nn.Linear(16, 8)
+    m = LoRALinear.from_linear(lin, r=4, lora_alpha=8)
+    x = torch.randn(3, 16)
+    assert torch.allclose(m(x), lin(x), atol=1e-6)          # B = 0: identical to the base layer
+    nn.init.normal_(m.lora_B)
+    assert not torch.allclose(m(x), lin(x), atol=1e-3)
+    assert torch.allclose(m(x), x @ m.merge_weights().T + lin.bias, atol=1e-5)
+    assert not m.weight.requires_grad and m.lora_A.requires_grad
+    m.reset_lora_parameters()
+    assert float(m.lora_B.detach().abs().sum()) == 0.0
+    with pytest.raises(ValueError):
+        LoRALinear(16, 8).merge_weights()
+
+
+def test_trainer_builds_loaders_from_datasets_and_reloads_weights(tmp_path):
+    from trainscale_b200.config.training_args import TrainingArguments
+    from trainscale_b200.core.errors import ConfigurationError
+    from trainscale_b200.trainer.base import Trainer
+
+    class M(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.l = nn.Linear(4, 1)
+
+    args = TrainingArguments(per_device_train_batch_size=4, gradient_accumulation_steps=2, world_size=8,
+                             num_train_epochs=1, output_dir=str(tmp_path))
+    assert args.effective_batch_size == 64 and args.output_path == tmp_path
+    with pytest.raises(ValueError):
+        TrainingArguments(push_to_hub=True)
+    ds = [{"x": torch.randn(4), "y": torch.randn(1)} for _ in range(16)]
+    t = Trainer(M(), args, train_dataset=ds, eval_dataset=ds,
+                compute_loss=lambda m, b: ((m.l(b["x"]) - b["y"]) ** 2).mean())
+    assert len(t.get_train_dataloader()) == 4 and len(t.get_eval_dataloader()) == 2
+    first = [b["x"] for b in t.get_train_dataloader()]
+    assert all(torch.equal(a, b) for a, b in zip(first, [b["x"] for b in t.get_train_dataloader()]))   # seeded shuffle
+    assert t.train()["global_step"] == 2
+    t.save_model(str(tmp_path / "w"))
+    w = t.model.l.weight.detach().clone()
+    nn.init.zeros_(t.model.l.weight)
+    t.load_model(str(tmp_path / "w"))
+    assert torch.equal(w, t.model.l.weight)
+    with pytest.raises(ConfigurationError):
+        Trainer(M(), args).get_train_dataloader()
+
+
+def test_preprocessed_dataset_select_and_stage_splits():
+    from trainscale_b200.config.data_schema import SplitSpec, StageConfig
+    from trainscale_b200.data.dataset_wrappers import PreprocessedDataset
+
+    class Ex:
+        def __init__(self, row):
+            self.row = row
+        def to_dict(self):
+            return {"input_ids": [self.row["v"]]}
+
+    class Engine:
+        calls = 0
+        def process(self, row):
+            Engine.calls += 1
+            return Ex(row)
+
+    d = PreprocessedDataset([{"v": i} for i in range(6)], Engine())
+    assert int(d[2]["input_ids"][0]) == 2 and int(d[2]["input_ids"][0]) == 2 and Engine.calls == 1   # second read cached
+    d.clear_cache()
+    d[2]
+    assert Engine.calls == 2 and d.features is None
+    sub = d.select([4, 1])
+    assert len(sub) == 2 and int(sub[0]["input_ids"][0]) == 4
+    st = StageConfig("s1", {"extra": SplitSpec("extra"), "train": SplitSpec("train")})
+    assert list(st.all_splits()) == ["train", "extra"] and st.get_split("train") is st.train and st.get_split("nope") is None

@@ -42,8 +42,17 @@ class CallbackContext:
 
 
 class Callback:
-    """Override any of the hooks; each receives the shared CallbackContext."""
+    """Override any of the hooks; each receives the shared CallbackContext.  Callbacks run in ascending `order`
+    (`priority` is the reference's name for the same number)."""
     order = 0
+    trainer: Any = None
+
+    @property
+    def priority(self) -> int:
+        return self.order
+
+    def set_trainer(self, trainer) -> None:
+        self.trainer = trainer
 
     def on_init_end(self, ctx): ...
     def on_train_begin(self, ctx): ...
@@ -77,6 +86,27 @@ class CallbackHandler:
             raise ValueError(f"unknown hook {hook}")
         for c in self.callbacks:
             getattr(c, hook)(ctx)
+        return ctx
+
+    # the reference's method names (data_pipeline/trainer/callbacks/__init__.py:176-217)
+    add_callback = add
+    remove_callback = remove
+
+    def set_trainer(self, trainer) -> None:
+        for c in self.callbacks:
+            if hasattr(c, "set_trainer"):
+                c.set_trainer(trainer)
+
+    def trigger(self, event: str, ctx: CallbackContext) -> CallbackContext:
+        """Like `fire`, but later callbacks are skipped once one of them has set `ctx.should_stop`."""
+        if event not in HOOKS:
+            raise ValueError(f"unknown hook {event}")
+        for c in self.callbacks:
+            handler = getattr(c, event, None)
+            if handler is not None:
+                handler(ctx)
+                if ctx.should_stop:
+                    break
         return ctx
 
     def __getattr__(self, name):

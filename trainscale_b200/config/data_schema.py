@@ -102,6 +102,26 @@ class StageConfig:
     splits: Mapping[str, SplitSpec] = field(default_factory=dict)
     weight: float = 1.0
 
+    def get_split(self, name: str) -> Optional[SplitSpec]:
+        return self.splits.get(name)
+
+    def all_splits(self) -> Dict[str, SplitSpec]:
+        """train / test / eval first (when present), then the other splits in their declared order."""
+        head = {k: self.splits[k] for k in ("train", "test", "eval") if k in self.splits}
+        return {**head, **{k: v for k, v in self.splits.items() if k not in head}}
+
+    @property
+    def train(self) -> Optional[SplitSpec]:
+        return self.splits.get("train")
+
+    @property
+    def test(self) -> Optional[SplitSpec]:
+        return self.splits.get("test")
+
+    @property
+    def eval(self) -> Optional[SplitSpec]:
+        return self.splits.get("eval")
+
 
 @dataclass(frozen=True)
 class DatasetConfig:

@@ -13,7 +13,7 @@ from pathlib import Path
 from typing import Any, Dict, List, Optional
 
 import yaml
-from pydantic import BaseModel, Field, field_validator
+from pydantic import BaseModel, Field, field_validator, model_validator
 
 from .data_schema import interpolate_env_vars
 
@@ -94,6 +94,12 @@ class TrainingArguments(BaseModel):
     eval_steps: Optional[int] = None
     detect_anomaly: bool = False
     dataloader_num_workers: int = 0
+    dataloader_pin_memory: bool = True
+    dataloader_drop_last: bool = False
+    world_size: int = 1
+    overwrite_output_dir: bool = False
+    push_to_hub: bool = False
+    hub_model_id: Optional[str] = None
     checkpoint: CheckpointConfig = Field(default_factory=CheckpointConfig)
     logging: LoggingConfig = Field(default_factory=LoggingConfig)
 
@@ -110,6 +116,28 @@ class TrainingArguments(BaseModel):
         if v < 1:
             raise ValueError("must be >= 1")
         return v
+
+    @property
+    def effective_batch_size(self) -> int:
+        """per-device batch x accumulation steps x world size (data_pipeline/trainer/core/config.py:312-323)."""
+        return self.per_device_train_batch_size * self.gradient_accumulation_steps * max(1, self.world_size)
+
+    @property
+    def per_device_batch_size(self) -> int:
+        return self.per_device_train_batch_size
+
+    @property
+    def output_path(self) -> Path:
+        return Path(self.output_dir)
+
+    @model_validator(mode="after")
+    def validate_arguments(self) -> "TrainingArguments":
+        """Cross-field checks: a hub upload needs its repository name; bf16 and fp16 exclude each other."""
+        if self.push_to_hub and not self.hub_model_id:
+            raise ValueError("hub_model_id is required when push_to_hub=True")
+        if self.bf16 and self.fp16:
+            raise ValueError("bf16 and fp16 are mutually exclusive")
+        return self
 
     def to_sota_dict(self) -> Dict[str, Any]:
         """The same settings expressed in the SOTAConfig key schema."""
@@ -151,33 +179,163 @@ def load_training_config(path, overrides: Dict[str, Any] | None = None) -> Train
     return TrainingArguments(**merge_configs(raw, overrides or {}))
 
 
+class TrainingMode(str, Enum):
+    """What is trained (data_pipeline/trainer/training_config.py)."""
+    FULL_FINETUNE = "full"
+    LORA = "lora"
+    QLORA = "qlora"
+    PRETRAINING = "pretrain"
+    RL = "rl"
+
+
 @dataclass
 class TrainingConfig:
-    model_name: str = ""
+    """Flat, script-friendly training configuration with the reference's field names
+    (data_pipeline/trainer/training_config.py:40-224) plus the short spellings this framework's presets use
+    (`model_name`, `batch_size`, `num_epochs`, `use_lora`, `precision`, `strategy`), which are kept in step with their
+    long forms.  `to_sota_dict()` turns it into the nested dictionary `SOTAConfig.from_dict` reads."""
     output_dir: str = "./outputs"
-    learning_rate: float = 2e-5
-    batch_size: int = 4
+    model_name_or_path: str = ""
+    training_mode: TrainingMode | None = None
+    num_train_epochs: int = 3
+    max_steps: int = -1
+    per_device_train_batch_size: int = 4
+    per_device_eval_batch_size: int = 4
     gradient_accumulation_steps: int = 4
-    num_epochs: int = 3
-    max_seq_length: int = 4096
-    warmup_ratio: float = 0.1
+    learning_rate: float = 2e-5
     weight_decay: float = 0.01
-    use_lora: bool = False
+    warmup_ratio: float = 0.1
+    warmup_steps: int = 0
+    max_seq_length: int = 4096
+    load_in_4bit: bool = False
+    load_in_8bit: bool = False
+    load_in_fp8: bool = False
+    bnb_4bit_quant_type: str = "nf4"
+    bnb_4bit_compute_dtype: str = "bfloat16"
+    bnb_4bit_use_double_quant: bool = True
     lora_r: int = 16
-    precision: str = "bf16"
-    strategy: str = "ddp"
+    lora_alpha: int = 32
+    lora_dropout: float = 0.0
+    lora_target_modules: list = field(default_factory=lambda: ["q_proj", "k_proj", "v_proj", "o_proj", "gate_proj",
+                                                               "up_proj", "down_proj"])
+    use_rslora: bool = False
+    use_dora: bool = False
+    pack_sequences: bool = False
+    padding_free: bool = True
+    fp16: bool = False
+    bf16: bool = True
+    tf32: bool = True
     gradient_checkpointing: bool = True
+    use_flash_attention: bool = True
+    use_triton_kernels: bool = False
+    optim: str = "adamw"
+    adam_beta1: float = 0.9
+    adam_beta2: float = 0.999
+    adam_epsilon: float = 1e-8
+    max_grad_norm: float = 1.0
+    lr_scheduler_type: str = "cosine"
+    logging_steps: int = 10
+    save_steps: int = 500
+    eval_steps: int = 500
+    save_total_limit: int = 3
+    report_to: str = "tensorboard"
+    push_to_hub: bool = False
+    hub_model_id: str | None = None
+    distributed_strategy: str = "ddp"
+    num_pipeline_stages: int = 4
+    num_microbatches: int = 8
+    pipeline_memory_limit_gb: float = 4.0
+    seed: int = 42
+    data_seed: int = 42
+    # short spellings (None = take the long form)
+    model_name: str | None = None
+    batch_size: int | None = None
+    num_epochs: int | None = None
+    use_lora: bool | None = None
+    precision: str | None = None
+    strategy: str | None = None
+
+    def __post_init__(self):
+        if isinstance(self.training_mode, str):
+            self.training_mode = TrainingMode(self.training_mode)
+        if self.model_name is not None:
+            self.model_name_or_path = self.model_name
+        if self.batch_size is not None:
+            self.per_device_train_batch_size = self.batch_size
+        if self.num_epochs is not None:
+            self.num_train_epochs = self.num_epochs
+        if self.strategy is not None:
+            self.distributed_strategy = self.strategy
+        if self.precision is not None:
+            self.bf16, self.fp16 = self.precision == "bf16", self.precision == "fp16"
+            self.load_in_fp8 = self.load_in_fp8 or self.precision.startswith("fp8")
+        if self.training_mode is None:
+            self.training_mode = (TrainingMode.QLORA if self.load_in_4bit else TrainingMode.LORA) if self.use_lora \
+                else TrainingMode.FULL_FINETUNE
+        if self.use_lora is None:
+            self.use_lora = self.training_mode in (TrainingMode.LORA, TrainingMode.QLORA)
+        if self.training_mode is TrainingMode.QLORA:
+            self.load_in_4bit = True
+        elif self.training_mode is TrainingMode.FULL_FINETUNE:
+            self.load_in_4bit = self.load_in_8bit = False
+        elif self.training_mode is TrainingMode.PRETRAINING:
+            self.pack_sequences = self.gradient_checkpointing = True
+        self.model_name, self.batch_size = self.model_name_or_path, self.per_device_train_batch_size
+        self.num_epochs, self.strategy = self.num_train_epochs, self.distributed_strategy
+        self.precision = self.precision or ("bf16" if self.bf16 else "fp16" if self.fp16 else "fp32")
+
+    @property
+    def compute_dtype(self) -> "torch.dtype":
+        import torch
+        return {"float16": torch.float16, "bfloat16": torch.bfloat16, "float32": torch.float32}.get(
+            self.bnb_4bit_compute_dtype, torch.bfloat16)
+
+    @property
+    def effective_batch_size(self) -> int:
+        return self.per_device_train_batch_size * self.gradient_accumulation_steps
+
+    def to_lora_config(self):
+        from ..lora import LoraConfig
+        return LoraConfig(r=self.lora_r, lora_alpha=self.lora_alpha, lora_dropout=self.lora_dropout,
+                          target_modules=list(self.lora_target_modules), use_rslora=self.use_rslora,
+                          use_dora=self.use_dora)
+
+    def to_quant_config(self):
+        from ..quantization import QuantizationConfig
+        return QuantizationConfig(load_in_4bit=self.load_in_4bit, load_in_8bit=self.load_in_8bit,
+                                  load_in_fp8=self.load_in_fp8, bnb_4bit_quant_type=self.bnb_4bit_quant_type,
+                                  bnb_4bit_compute_dtype=self.compute_dtype,
+                                  bnb_4bit_use_double_quant=self.bnb_4bit_use_double_quant)
+
+    def to_dict(self) -> Dict[str, Any]:
+        return {k: (v.value if isinstance(v, Enum) else v) for k, v in self.__dict__.items()}
+
+    @classmethod
+    def from_dict(cls, d: Dict[str, Any]) -> "TrainingConfig":
+        known = {f for f in cls.__dataclass_fields__}
+        return cls(**{k: v for k, v in d.items() if k in known})
 
     def to_sota_dict(self) -> Dict[str, Any]:
-        return {"training_mode": "lora" if self.use_lora else "full", "model": {"name_or_path": self.model_name},
-                "lora": {"enabled": self.use_lora, "r": self.lora_r},
-                "optimizer": {"learning_rate": self.learning_rate, "weight_decay": self.weight_decay},
-                "scheduler": {"warmup_ratio": self.warmup_ratio},
-                "distributed": {"strategy": self.strategy, "gradient_checkpointing": self.gradient_checkpointing},
-                "hardware": {"precision": self.precision}, "data": {"max_seq_length": self.max_seq_length},
-                "training": {"output_dir": self.output_dir, "num_train_epochs": self.num_epochs,
-                             "per_device_train_batch_size": self.batch_size,
-                             "gradient_accumulation_steps": self.gradient_accumulation_steps}}
+        mode = {TrainingMode.FULL_FINETUNE: "full", TrainingMode.LORA: "lora", TrainingMode.QLORA: "qlora",
+                TrainingMode.PRETRAINING: "pretrain", TrainingMode.RL: "rl"}[self.training_mode]
+        return {"training_mode": mode, "model": {"name_or_path": self.model_name_or_path},
+                "lora": {"enabled": bool(self.use_lora), "r": self.lora_r, "lora_alpha": self.lora_alpha,
+                         "lora_dropout": self.lora_dropout, "target_modules": list(self.lora_target_modules),
+                         "use_rslora": self.use_rslora},
+                "optimizer": {"learning_rate": self.learning_rate, "weight_decay": self.weight_decay,
+                              "max_grad_norm": self.max_grad_norm, "betas": [self.adam_beta1, self.adam_beta2],
+                              "eps": self.adam_epsilon},
+                "scheduler": {"type": self.lr_scheduler_type, "warmup_ratio": self.warmup_ratio,
+                              "warmup_steps": self.warmup_steps},
+                "distributed": {"strategy": self.distributed_strategy, "gradient_checkpointing": self.gradient_checkpointing},
+                "hardware": {"precision": self.precision}, "data": {"max_seq_length": self.max_seq_length,
+                                                                    "packing": self.pack_sequences},
+                "training": {"output_dir": self.output_dir, "num_train_epochs": self.num_train_epochs,
+                             "max_steps": self.max_steps,
+                             "per_device_train_batch_size": self.per_device_train_batch_size,
+                             "gradient_accumulation_steps": self.gradient_accumulation_steps,
+                             "logging_steps": self.logging_steps, "save_steps": self.save_steps,
+                             "save_total_limit": self.save_total_limit, "seed": self.seed}}
 
 
 def get_quick_test_config() -> TrainingConfig:
@@ -195,24 +353,18 @@ def get_high_throughput_config() -> TrainingConfig:
 def get_qlora_config(model_name: str, r: int = 16, max_seq_length: int = 2048) -> TrainingConfig:
     """Adapters of rank r (alpha 2r) on a quantised base, packed sequences
     (data_pipeline/trainer/training_config.py:230)."""
-    c = TrainingConfig(model_name=model_name, use_lora=True, lora_r=r, max_seq_length=max_seq_length,
-                       learning_rate=2e-4, strategy="ddp")
-    c.load_in_4bit, c.lora_alpha, c.pack_sequences = True, 2 * r, True
-    return c
+    return TrainingConfig(model_name=model_name, training_mode=TrainingMode.QLORA, lora_r=r, lora_alpha=2 * r,
+                          max_seq_length=max_seq_length, learning_rate=2e-4, strategy="ddp", pack_sequences=True)
 
 
 def get_full_finetune_config(model_name: str, max_seq_length: int = 2048) -> TrainingConfig:
-    c = TrainingConfig(model_name=model_name, use_lora=False, max_seq_length=max_seq_length, learning_rate=1e-5,
-                       precision="bf16", strategy="fsdp2", gradient_checkpointing=True)
-    c.load_in_4bit, c.pack_sequences = False, False
-    return c
+    return TrainingConfig(model_name=model_name, training_mode=TrainingMode.FULL_FINETUNE, max_seq_length=max_seq_length,
+                          learning_rate=1e-5, precision="bf16", strategy="fsdp2", gradient_checkpointing=True)
 
 
 def get_pretraining_config(model_name: str, max_seq_length: int = 4096) -> TrainingConfig:
-    c = TrainingConfig(model_name=model_name, use_lora=False, max_seq_length=max_seq_length, learning_rate=3e-4,
-                       warmup_ratio=0.01, precision="bf16", strategy="fsdp2", gradient_checkpointing=True)
-    c.load_in_4bit, c.pack_sequences = False, True
-    return c
+    return TrainingConfig(model_name=model_name, training_mode=TrainingMode.PRETRAINING, max_seq_length=max_seq_length,
+                          learning_rate=3e-4, warmup_ratio=0.01, precision="bf16", strategy="fsdp2")
 
 
 def load_training_config_from_dict(config_dict: Dict[str, Any], *, interpolate_env: bool = True) -> TrainingArguments:

@@ -15,7 +15,7 @@ from ..core.errors import DataLoadingError
 
 
 class DataLoaderBuilder:
-    def __init__(self, dataset):
+    def __init__(self, dataset=None):
         self.dataset = dataset
         self._batch_size, self._shuffle, self._seed = 8, False, 42
         self._num_workers, self._pin, self._drop_last = 0, False, False
@@ -53,7 +53,80 @@ class DataLoaderBuilder:
         self._dist, self._rank, self._world = world_size > 1, rank, world_size
         return self
 
+    # ---- `with_*` spelling of the reference's builder (data_pipeline/data/dataloader_factory.py:89-176)
+    def with_dataset(self, dataset):
+        self.dataset = dataset
+        return self
+
+    def with_batch_size(self, batch_size: int):
+        return self.batch_size(batch_size)
+
+    def with_shuffle(self, shuffle: bool):
+        self._shuffle = bool(shuffle)
+        return self
+
+    def with_seed(self, seed: int):
+        self._seed = int(seed)
+        return self
+
+    def with_num_workers(self, num_workers: int):
+        self._num_workers = int(num_workers)
+        return self
+
+    def with_pin_memory(self, pin_memory: bool):
+        return self.pin_memory(pin_memory)
+
+    def with_drop_last(self, drop_last: bool):
+        return self.drop_last(drop_last)
+
+    def with_distributed(self, rank: int, world_size: int):
+        return self.distributed(rank, world_size)
+
+    def with_collate_fn(self, collate_fn: Callable):
+        return self.collate(collate_fn)
+
+    def with_sampler(self, sampler):
+        """A sampler given here wins over the shuffle / distributed settings."""
+        self._sampler = sampler
+        return self
+
+    def with_padding(self, pad_token_id: int, label_pad_token_id: int = -100, padding_side: str = "right",
+                     max_length: int | None = None):
+        """Pad batches with the framework collate function (`data.collate.create_collate_fn`) unless a collate function
+        is set explicitly."""
+        self._padding = dict(pad_token_id=pad_token_id, label_pad_token_id=label_pad_token_id,
+                             padding_side=padding_side, max_length=max_length)
+        return self
+
+    def with_output_schema(self, schema):
+        self._schema = schema
+        return self
+
+    def with_config(self, config):
+        """Take batch size, workers, pinning, drop_last, shuffle, prefetch and worker persistence from a loader
+        configuration object (attributes missing on it keep their current values)."""
+        g = lambda name, cur: getattr(config, name, cur)      # noqa: E731
+        self._batch_size, self._num_workers = g("batch_size", self._batch_size), g("num_workers", self._num_workers)
+        self._pin, self._drop_last = g("pin_memory", self._pin), g("drop_last", self._drop_last)
+        self._shuffle, self._prefetch = g("shuffle", self._shuffle), g("prefetch_factor", self._prefetch)
+        self._persistent = g("persistent_workers", self._persistent)
+        return self
+
+    def _padding_collate(self):
+        pad = getattr(self, "_padding", None)
+        if pad is None:
+            return None
+        from .collate import create_collate_fn
+        import inspect
+        accepted = set(inspect.signature(create_collate_fn).parameters)
+        kw = {k: v for k, v in pad.items() if k in accepted and v is not None}
+        if getattr(self, "_schema", None) is not None and "output_schema" in accepted:
+            kw["output_schema"] = self._schema
+        return create_collate_fn(**kw)
+
     def _create_sampler(self):
+        if getattr(self, "_sampler", None) is not None:
+            return self._sampler
         if isinstance(self.dataset, IterableDataset):
             return None
         if self._dist:
@@ -65,7 +138,8 @@ class DataLoaderBuilder:
 
     def build(self) -> DataLoader:
         kw = dict(batch_size=self._batch_size, sampler=self._create_sampler(), num_workers=self._num_workers,
-                  pin_memory=self._pin and torch.cuda.is_available(), drop_last=self._drop_last, collate_fn=self._collate)
+                  pin_memory=self._pin and torch.cuda.is_available(), drop_last=self._drop_last,
+                  collate_fn=self._collate if self._collate is not None else self._padding_collate())
         if self._num_workers > 0:
             if self._prefetch:
                 kw["prefetch_factor"] = self._prefetch

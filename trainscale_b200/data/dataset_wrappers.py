@@ -58,6 +58,21 @@ class PreprocessedDataset(Dataset):
             self.cache[i] = item
         return item
 
+    def clear_cache(self) -> None:
+        if self.cache is not None:
+            self.cache.clear()
+
+    @property
+    def features(self):
+        """Feature description of the wrapped dataset (None when it has none)."""
+        return getattr(self.dataset, "features", None)
+
+    def select(self, indices) -> "PreprocessedDataset":
+        """The same preprocessing over a subset of rows (data_pipeline/data/dataset_wrappers.py:179-196)."""
+        indices = list(indices)
+        sub = self.dataset.select(indices) if hasattr(self.dataset, "select") else [self.dataset[i] for i in indices]
+        return PreprocessedDataset(sub, self.engine, self.mapping, self.cache is not None, self.max_cache_items)
+
 
 class StreamingPreprocessedDataset(IterableDataset):
     def __init__(self, iterable: Iterable, engine, column_mapping: Mapping[str, str] | None = None, rank: int = 0,

@@ -12,6 +12,7 @@ Behaviour after data_pipeline/preprocessing/length_manager.py:92-1765:
 from __future__ import annotations
 
 import bisect
+import math
 import re
 from dataclasses import dataclass, field
 from typing import Callable, Mapping, Sequence
@@ -52,9 +53,23 @@ class ColumnContentConfig:
 
 @dataclass
 class ColumnLengthConfig:
-    name: str
+    """Limits of one text column (data_pipeline/preprocessing/length_manager.py:231-257).  `max_length` and
+    `max_tokens` are the same limit in tokens; `max_chars` is a hard limit in characters and wins over both."""
+    name: str = ""
     max_length: int | None = None
     truncation: TruncationStrategy = TruncationStrategy.RIGHT
+    max_chars: int | None = None
+    max_tokens: int | None = None
+    preserve_ratio: float = 0.0
+    priority: int = 0
+
+    def __post_init__(self):
+        if self.max_tokens is None:
+            self.max_tokens = self.max_length
+        elif self.max_length is None:
+            self.max_length = self.max_tokens
+        if not 0.0 <= self.preserve_ratio <= 1.0:
+            raise ValueError("preserve_ratio must lie in [0, 1]")
 
 
 @dataclass
@@ -67,6 +82,19 @@ class LengthManagerConfig:
     chars_per_token: float = CHARS_PER_TOKEN
     per_column: Mapping[str, ColumnLengthConfig] = field(default_factory=dict)
     pad_to_multiple_of: int | None = None
+
+    # the reference's field names for the same settings
+    @property
+    def total_max_length(self) -> int:
+        return self.max_total_length
+
+    @property
+    def default_truncation(self) -> TruncationStrategy:
+        return self.truncation_strategy
+
+    @property
+    def chars_per_token_estimate(self) -> float:
+        return self.chars_per_token
 
 
 _SENT = re.compile(r"[.!?]['\")\]]*\s")
@@ -131,6 +159,26 @@ class TokenEstimator:
 
     def chars_for(self, tokens: int) -> int:
         return int(tokens * self.cpt)
+
+    def estimate_tokens(self, text: str) -> int:
+        """Token count of `text`: the tokenizer's when one is attached (any of count_tokens / encode / __call__),
+        else the characters-per-token estimate."""
+        if not text:
+            return 0
+        tk = self.tokenizer
+        if tk is not None:
+            try:
+                if hasattr(tk, "count_tokens"):
+                    return max(1, int(tk.count_tokens(text)))
+                if hasattr(tk, "encode"):
+                    ids = tk.encode(text)
+                    return max(1, len(ids["input_ids"] if isinstance(ids, dict) else ids))
+            except Exception:   # noqa: BLE001 - an unusable tokenizer falls back to the estimate
+                pass
+        return max(1, int(len(text) / self.cpt + 0.5))
+
+    def tokens_to_chars(self, tokens: int) -> int:
+        return 0 if tokens <= 0 else int(math.ceil(tokens * self.cpt))
 
 
 class TokenAwareContentDistributor:
@@ -247,13 +295,42 @@ class LengthManager:
     def __init__(self, config: LengthManagerConfig | None = None, tokenizer=None):
         self.config = config or LengthManagerConfig()
         self.estimator = TokenEstimator(tokenizer, self.config.chars_per_token)
+        self._column_configs: dict[str, ColumnLengthConfig] = dict(self.config.per_column)
+
+    @property
+    def max_length(self) -> int:
+        return self.config.max_total_length
+
+    @property
+    def padding_strategy(self) -> PaddingStrategy:
+        return self.config.padding_strategy
+
+    def get_column_config(self, column: str | None) -> ColumnLengthConfig:
+        """The column's limits; defaults for a column that has none."""
+        if column is None or column not in self._column_configs:
+            return ColumnLengthConfig(column or "", truncation=self.config.truncation_strategy)
+        return self._column_configs[column]
+
+    def set_column_config(self, column: str, config: ColumnLengthConfig) -> None:
+        self._column_configs[column] = config
+
+    def preprocess_text(self, text: str, column: str | None = None, max_chars: int | None = None) -> str:
+        """Truncate one field.  The limit is the first of: `max_chars`, the column's max_chars, the column's
+        max_tokens in characters, the total length in characters."""
+        if not text:
+            return ""
+        cc = self.get_column_config(column)
+        if max_chars is None:
+            max_chars = cc.max_chars if cc.max_chars is not None else self.estimator.tokens_to_chars(
+                cc.max_tokens if cc.max_tokens is not None else self.config.max_total_length)
+        return smart_truncate(text, max_chars, cc.truncation)
 
     def preprocess_example(self, example: Mapping[str, str]) -> dict[str, str]:
         """Per-column limits first, then priority trimming until the total fits."""
         out = dict(example)
-        for name, cc in self.config.per_column.items():
-            if isinstance(out.get(name), str) and cc.max_length is not None:
-                out[name] = smart_truncate(out[name], self.estimator.chars_for(cc.max_length), cc.truncation)
+        for name, cc in self._column_configs.items():
+            if isinstance(out.get(name), str) and (cc.max_length is not None or cc.max_chars is not None):
+                out[name] = self.preprocess_text(out[name], name)
         return self._priority_trim(out)
 
     def _priority_trim(self, example: dict) -> dict:

@@ -533,6 +533,14 @@ class PromptEngine:
         else:
             self.processor = _RLProcessor(config, self.enc)
 
+    @property
+    def stage(self) -> TrainingStage:
+        return TrainingStage(self.config.stage)
+
+    @property
+    def max_length(self) -> int:
+        return self.config.max_length
+
     @classmethod
     def from_config(cls, config: PromptEngineConfig, tokenizer, distributor=None, template=None) -> "PromptEngine":
         return cls(config, tokenizer, distributor, template)

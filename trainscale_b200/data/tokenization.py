@@ -57,9 +57,14 @@ class ByteTokenizer:
     def convert_tokens_to_ids(self, tok):
         if isinstance(tok, (list, tuple)):
             return [self.convert_tokens_to_ids(t) for t in tok]
-        return self.special.get(tok, self.added.get(tok, self.unk_token_id))
+        if tok in self.special or tok in self.added:
+            return self.special.get(tok, self.added.get(tok))
+        # byte tokens are spelled as the character of that code (the inverse of convert_ids_to_tokens)
+        return ord(tok) if isinstance(tok, str) and len(tok) == 1 and ord(tok) < 256 else self.unk_token_id
 
     def convert_ids_to_tokens(self, i):
+        if isinstance(i, (list, tuple)):
+            return [self.convert_ids_to_tokens(x) for x in i]
         inv = {v: k for k, v in {**self.special, **self.added}.items()}
         return inv.get(i, chr(i) if i < 256 else "<unk>")
 
@@ -243,6 +248,50 @@ class TokenizerWrapper:
                                getattr(self.tokenizer, "unk_token_id", None)) if i is not None}
         special |= set(getattr(self.tokenizer, "all_special_ids", []) or [])
         return [1 if int(i) in special else 0 for i in ids]
+
+    # ---- vocabulary bookkeeping and conversions (data_pipeline/preprocessing/tokenization.py:332-356, 565-667)
+    original_vocab_size = property(lambda self: self._initial_vocab)
+    num_added_tokens = property(lambda self: max(0, len(self.tokenizer) - self._initial_vocab))
+    vocab_was_modified = property(lambda self: len(self.tokenizer) != self._initial_vocab)
+
+    def decode_batch(self, batch_token_ids, *, skip_special_tokens: bool = True) -> list[str]:
+        return [self.decode(ids, skip_special_tokens) for ids in batch_token_ids]
+
+    def get_all_special_token_ids(self) -> frozenset:
+        """Every special token id the tokenizer knows (label masking: these positions usually get -100)."""
+        ids = set(getattr(self.tokenizer, "all_special_ids", []) or [])
+        for attr in ("pad", "eos", "bos", "unk", "sep", "cls", "mask"):
+            i = getattr(self.tokenizer, f"{attr}_token_id", None)
+            if i is not None:
+                ids.add(int(i))
+        return frozenset(ids)
+
+    def get_special_tokens_info(self) -> dict:
+        """{attribute: {"string": token, "id": id} or None} for the canonical special tokens."""
+        info = {}
+        for attr in ("pad_token", "eos_token", "bos_token", "unk_token", "sep_token", "cls_token", "mask_token"):
+            tok = getattr(self.tokenizer, attr, None)
+            info[attr] = None if tok is None else {"string": tok, "id": getattr(self.tokenizer, f"{attr}_id", None)}
+        return info
+
+    def convert_tokens_to_ids(self, tokens):
+        fn = getattr(self.tokenizer, "convert_tokens_to_ids", None)
+        if fn is not None:
+            return fn(tokens)
+        one = isinstance(tokens, str)
+        out = [_resolve_token_id(self.tokenizer, t) for t in ([tokens] if one else tokens)]
+        return out[0] if one else out
+
+    def convert_ids_to_tokens(self, ids):
+        fn = getattr(self.tokenizer, "convert_ids_to_tokens", None)
+        if fn is not None:
+            return fn(ids)
+        one = isinstance(ids, int)
+        out = [self.tokenizer.decode([i], skip_special_tokens=False) for i in ([ids] if one else ids)]
+        return out[0] if one else out
+
+    def __len__(self) -> int:
+        return self.vocab_size
 
     def apply_chat_template(self, messages: list[dict], add_generation_prompt: bool = False) -> str:
         tok = self.tokenizer

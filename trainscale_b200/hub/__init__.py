@@ -99,8 +99,29 @@ def compute_sha256(path: str | os.PathLike, chunk: int = 1 << 22) -> str:
 class ModelSerializer:
     """state dict -> `model.safetensors` or `model-0000i-of-0000n.safetensors` + `model.safetensors.index.json`."""
 
-    def __init__(self, max_shard_bytes: int = 5 * 2 ** 30):
-        self.max_shard_bytes = max_shard_bytes
+    def __init__(self, max_shard_bytes: int = 5 * 2 ** 30, prefer_safetensors: bool = True):
+        if max_shard_bytes <= 0:
+            raise ValueError("max_shard_bytes must be positive")
+        self.max_shard_bytes, self.prefer_safetensors = max_shard_bytes, prefer_safetensors
+
+    @property
+    def shard_size_bytes(self) -> int:
+        return self.max_shard_bytes
+
+    @property
+    def safetensors_available(self) -> bool:
+        return HAVE_SAFETENSORS
+
+    def serialize(self, model, output_dir: str | os.PathLike, model_id: str | None = None):
+        """`model.state_dict()` written under `output_dir`; Ok(SerializationResult) or Err(HubError)
+        (data_pipeline/trainer/hub/__init__.py:522-567)."""
+        from ..core.types import Err, Ok
+        try:
+            self.save(model.state_dict(), output_dir)
+            return Ok(SerializationResult.describe(output_dir))
+        except Exception as e:   # noqa: BLE001
+            return Err(HubError(f"failed to serialise model: {e}", code=HubErrorCode.SERIALIZATION_ERROR,
+                                model_id=model_id, output_dir=str(output_dir)))
 
     def plan(self, sd: dict[str, torch.Tensor]) -> list[list[str]]:
         shards, cur, size = [], [], 0
@@ -118,7 +139,7 @@ class ModelSerializer:
     def save(self, sd: dict[str, torch.Tensor], out_dir: str | os.PathLike) -> dict:
         out = Path(out_dir)
         out.mkdir(parents=True, exist_ok=True)
-        if not HAVE_SAFETENSORS:
+        if not (HAVE_SAFETENSORS and getattr(self, "prefer_safetensors", True)):
             sd = {k: v.detach().cpu().contiguous() for k, v in sd.items()}
             tmp = out / "model.pt.tmp"
             torch.save(sd, tmp)
@@ -222,10 +243,120 @@ def generate_model_card(model_name: str, base_model: str = "", config: dict | No
 class HubManager:
     """Thin wrapper over `huggingface_hub` with retry + circuit breaker; a no-op target directory when offline."""
 
-    def __init__(self, repo_id: str | None = None, token: str | None = None, private: bool = False,
+    def __init__(self, repo_id: "str | HubConfig | None" = None, token: str | None = None, private: bool = False,
                  policy: RetryPolicy | None = None):
+        self._config = None
+        if repo_id is not None and not isinstance(repo_id, str):       # HubManager(HubConfig(...)), the reference's form
+            self._config = cfg = repo_id
+            repo_id, token, private = cfg.repo_id, token or cfg.token, cfg.private
+            policy = policy or RetryPolicy(max_attempts=max(1, cfg.max_retries))
         self.repo_id, self.token, self.private = repo_id, token or os.environ.get("HF_TOKEN"), private
         self.policy, self.breaker = policy or RetryPolicy(), CircuitBreaker()
+        self._api = None
+
+    # ---- model-level operations returning Result (data_pipeline/trainer/hub/__init__.py:917-1247)
+    @property
+    def config(self) -> "HubConfig":
+        if self._config is None:
+            self._config = HubConfig(repo_id=self.repo_id, token=self.token, private=self.private,
+                                     max_retries=self.policy.max_attempts)
+        return self._config
+
+    @property
+    def api(self):
+        """The `huggingface_hub.HfApi` client, created on first use; ImportError when the package is absent."""
+        if self._api is None:
+            from huggingface_hub import HfApi
+            self._api = HfApi(token=self.token)
+        return self._api
+
+    def _fail(self, exc: BaseException, **ctx):
+        from ..core.types import Err
+        return Err(HubError(str(exc), code=classify_hub_error(exc), **ctx))
+
+    def push_to_hub(self, model, repo_id: str | None = None, commit_message: str = "Upload model",
+                    model_card: str | None = None, tags: list[str] | None = None, progress_callback=None,
+                    local_dir: str | os.PathLike | None = None):
+        """Serialise `model` (sharded safetensors + index, config.json when the model has a config, README.md) and
+        upload the folder.  `local_dir` keeps the serialised folder; otherwise a temporary one is used.  Ok(url) or
+        Err(HubError with a `code` of HubErrorCode)."""
+        import tempfile
+        from ..core.types import Err, Ok
+        repo = repo_id or self.repo_id
+        if not repo:
+            return Err(HubError("repo_id required for push operation", code=HubErrorCode.VALIDATION_ERROR))
+        t0 = time.time_ns()
+        tmp = None if local_dir is not None else tempfile.TemporaryDirectory(prefix="ts_hub_")
+        out = Path(local_dir if local_dir is not None else tmp.name)
+        nbytes = 0
+        try:
+            res = ModelSerializer(self.config.shard_size_bytes, self.config.prefer_safetensors).serialize(model, out, repo)
+            if res.is_err():
+                return res
+            nbytes = res.unwrap().total_bytes
+            cfg = getattr(model, "config", None)
+            if cfg is not None:
+                d = cfg.to_dict() if hasattr(cfg, "to_dict") else {k: v for k, v in vars(cfg).items()
+                                                                   if isinstance(v, (int, float, str, bool, list, type(None)))}
+                (out / "config.json").write_text(json.dumps(d, indent=2, default=str))
+            (out / "README.md").write_text(model_card or generate_model_card(repo.split("/")[-1], tags=tags))
+            if progress_callback is not None:
+                progress_callback(0, nbytes)
+            old_repo, self.repo_id = self.repo_id, repo
+            try:
+                if not self.available():
+                    raise ImportError("huggingface_hub with a token is needed to upload (offline: the folder is in local_dir)")
+                url = self.push(out, commit_message)
+            finally:
+                self.repo_id = old_repo
+            if progress_callback is not None:
+                progress_callback(nbytes, nbytes)
+            _HUB_METRICS.record_upload(nbytes, time.time_ns() - t0, True)
+            return Ok(url)
+        except Exception as e:   # noqa: BLE001 - every failure becomes a classified Err
+            _HUB_METRICS.record_upload(nbytes, time.time_ns() - t0, False)
+            return self._fail(e, repo_id=repo)
+        finally:
+            if tmp is not None:
+                tmp.cleanup()
+
+    def pull_from_hub(self, repo_id: str | None = None, revision: str = "main", cache_dir: str | None = None):
+        """Ok(path of the snapshot) or Err.  A `repo_id` that is an existing local directory is returned as it is, so
+        that offline hosts can point at a folder written by `push_to_hub(local_dir=...)`."""
+        from ..core.types import Err, Ok
+        repo = repo_id or self.repo_id
+        if not repo:
+            return Err(HubError("repo_id required for pull operation", code=HubErrorCode.VALIDATION_ERROR))
+        if Path(repo).is_dir():
+            return Ok(Path(repo))
+        t0 = time.time_ns()
+        try:
+            from huggingface_hub import snapshot_download
+            path = Path(execute_with_retry(lambda: snapshot_download(repo, revision=revision, token=self.token,
+                                                                     cache_dir=cache_dir or self.config.cache_dir),
+                                           self.policy, self.breaker))
+            size = sum(f.stat().st_size for f in path.rglob("*") if f.is_file())
+            _HUB_METRICS.record_download(size, time.time_ns() - t0, True)
+            return Ok(path)
+        except Exception as e:   # noqa: BLE001
+            _HUB_METRICS.record_download(0, time.time_ns() - t0, False)
+            return self._fail(e, repo_id=repo, revision=revision)
+
+    def load_from_hub(self, model, repo_id: str | None = None, revision: str = "main", strict: bool = True):
+        """Weights of the repository (or local folder) loaded into `model`: Ok(model) or Err."""
+        from ..core.types import Ok
+        got = self.pull_from_hub(repo_id, revision)
+        if got.is_err():
+            return got
+        try:
+            sd = ModelDeserializer(self.config.verify_integrity, self.config.max_workers).load(got.unwrap())
+            model.load_state_dict(sd, strict=strict)
+            return Ok(model)
+        except Exception as e:   # noqa: BLE001
+            return self._fail(e, strict=strict)
+
+    def get_metrics(self) -> dict:
+        return _HUB_METRICS.summary()
 
     def available(self) -> bool:
         try:

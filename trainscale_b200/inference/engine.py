@@ -148,6 +148,18 @@ class RequestMetrics:
     def e2e(self) -> float | None:
         return None if self.finished is None else self.finished - self.arrival
 
+    def mark_submitted(self) -> None:
+        self.arrival = time.perf_counter()
+
+    def mark_first_token(self) -> None:
+        if self.first_token is None:
+            self.first_token = time.perf_counter()
+
+    def mark_complete(self, completion_tokens: int | None = None) -> None:
+        self.finished = time.perf_counter()
+        if completion_tokens is not None:
+            self.completion_tokens = completion_tokens
+
 
 class MetricsAggregator:
     def __init__(self):
@@ -435,6 +447,7 @@ class EngineCore:
         from ..data.tokenization import TokenizerWrapper, create_tokenizer
         from ..models.llama import PRESETS, build_model
         self.config = config
+        self.adapter_states: dict[str, dict[str, torch.Tensor]] = {}   # registry behind `load_adapters`
         dev = config.device
         if dev == "auto":
             dev = "cuda" if torch.cuda.is_available() else "cpu"
@@ -519,6 +532,7 @@ class EngineCore:
         if limit and len(adapters) > limit:
             raise ValueError(f"{len(adapters)} adapters exceed lora.max_loras = {limit}")
         self.runner.lora = BatchedLoRA(self.model, adapters)
+        self.adapter_states = dict(adapters)
 
     def _salt(self, r: "_Request") -> bytes:
         """Prefix-cache namespace of a request: K/V computed under one adapter are not valid under another."""
@@ -731,6 +745,38 @@ class SOTAInferenceEngine:
     def metrics_summary(self) -> dict:
         return self.core.metrics.summary()
 
+    get_metrics_summary = metrics_summary
+
+    @property
+    def engine(self) -> "EngineCore":
+        """The scheduler / model-runner core (what the reference exposes as its underlying LLM engine)."""
+        return self.core
+
+    @property
+    def metrics(self) -> "MetricsAggregator":
+        return self.core.metrics
+
+    def generate_single(self, prompt: str, params: GenerationParams | None = None) -> Result:
+        return self.generate(prompt, params)
+
+    def generate_with_lora(self, prompts: str | Iterable[str], lora_name: str, lora_path: str | None = None,
+                           lora_id: int | None = None, params: GenerationParams | None = None) -> Result:
+        """Generate with the named adapter.  `lora_path`: a directory written by `lora.save_adapter`, loaded on first
+        use; adapters registered earlier with `EngineCore.load_adapters` are found by name alone."""
+        import copy as _copy
+        try:
+            known = self.core.adapter_states
+            if lora_name not in known:
+                if lora_path is None:
+                    raise ValueError(f"adapter {lora_name!r} is not loaded and no lora_path was given")
+                from ..lora import adapter_state_from_dir
+                self.core.load_adapters({**known, lora_name: adapter_state_from_dir(self.core.model, lora_path)})
+        except (ValueError, OSError, RuntimeError, KeyError) as e:
+            return Err(e)
+        p = _copy.copy(params) if params is not None else GenerationParams()
+        p.lora_name = lora_name
+        return self.generate(prompts, p)
+
 
 class SOTAAsyncStreamEngine:
     """Single background loop stepping the core; each request gets an asyncio queue of StreamChunks."""
@@ -777,6 +823,50 @@ class SOTAAsyncStreamEngine:
             await q.put(StreamChunk(request_id, "", -1, True, "abort"))
         return ok
 
+    @property
+    def engine(self) -> "EngineCore":
+        return self.core
+
+    @property
+    def active_request_count(self) -> int:
+        return len(self._queues)
+
+    async def generate(self, prompt: str, params: GenerationParams | None = None, request_id: str | None = None) -> Result:
+        """Non-streaming form: runs the streaming path and returns the whole completion."""
+        try:
+            text, ids, reason, rid = [], [], None, request_id
+            async for c in self.generate_stream(prompt, params, request_id):
+                rid = c.request_id
+                text.append(c.text)
+                if c.token_id is not None and c.token_id >= 0:
+                    ids.append(c.token_id)
+                reason = c.finish_reason or reason
+            m = next((x for x in reversed(self.core.metrics.records) if x.request_id == rid), RequestMetrics(rid or ""))
+            return Ok(InferenceResponse(rid or "", prompt, "".join(text), ids, reason or "stop", m, None))
+        except (ValueError, MemoryError, RuntimeError) as e:
+            return Err(e)
+
+    async def generate_batch(self, prompts: list[str], params: GenerationParams | None = None) -> Result:
+        """All prompts are queued at once, so the scheduler batches them continuously."""
+        results = await asyncio.gather(*(self.generate(p, params) for p in prompts))
+        bad = next((r for r in results if r.is_err()), None)
+        return bad if bad is not None else Ok([r.unwrap() for r in results])
+
+    async def shutdown(self) -> None:
+        for rid in list(self._queues):
+            await self.abort_request(rid)
+        if self._task is not None:
+            try:
+                await self._task
+            except Exception:   # noqa: BLE001 - the loop ends with the aborted requests
+                pass
+        self._queues.clear()
+
+    def get_metrics_summary(self) -> dict:
+        out = self.core.metrics.summary()
+        out["active_requests"] = self.active_request_count
+        return out
+
 
 class EnginePresets:
     @staticmethod
@@ -786,6 +876,51 @@ class EnginePresets:
     @staticmethod
     def high_throughput(model: str = "tiny") -> EngineConfig:
         return EngineConfig(model=model, scheduler=SchedulerConfig(max_num_seqs=256, max_num_batched_tokens=16384))
+
+    # ---- deployment profiles under the reference's names (data_pipeline/trainer/inference.py:1549-1810)
+    @staticmethod
+    def _base(model, tp_size, pp_size, max_model_len, seqs, tokens, util, chunked=True) -> EngineConfig:
+        return EngineConfig(model=model, enforce_eager=False,
+                            scheduler=SchedulerConfig(max_num_seqs=seqs, max_num_batched_tokens=tokens,
+                                                      enable_chunked_prefill=chunked),
+                            cache=CacheConfig(gpu_memory_utilization=util, enable_prefix_caching=True,
+                                              max_model_len=max_model_len),
+                            parallel=ParallelConfig(tensor_parallel_size=tp_size, pipeline_parallel_size=pp_size))
+
+    @staticmethod
+    def high_throughput_batch(model: str = "tiny", tp_size: int = 1, max_model_len: int = 8192) -> EngineConfig:
+        return EnginePresets._base(model, tp_size, 1, max_model_len, 256, 32768, 0.95)
+
+    @staticmethod
+    def low_latency_interactive(model: str = "tiny", tp_size: int = 1, max_model_len: int = 4096) -> EngineConfig:
+        return EnginePresets._base(model, tp_size, 1, max_model_len, 32, 4096, 0.90)
+
+    @staticmethod
+    def speculative_fast_decode(model: str = "tiny", draft_model: str | None = None, tp_size: int = 1,
+                                num_speculative_tokens: int = 5, max_model_len: int = 4096) -> EngineConfig:
+        c = EnginePresets._base(model, tp_size, 1, max_model_len, 64, 8192, 0.90, chunked=False)
+        c.speculative = SpeculativeConfig(enabled=True, draft_model=draft_model,
+                                          num_speculative_tokens=num_speculative_tokens)
+        return c
+
+    @staticmethod
+    def quantized_memory_efficient(model: str = "tiny", quant_method="fp8", bits: int = 8, tp_size: int = 1,
+                                   max_model_len: int = 8192) -> EngineConfig:
+        c = EnginePresets._base(model, tp_size, 1, max_model_len, 128, 16384, 0.92)
+        c.quantization = QuantizationConfig(method=str(getattr(quant_method, "value", quant_method)))
+        return c
+
+    @staticmethod
+    def multi_gpu_large_model(model: str = "tiny", tp_size: int = 4, pp_size: int = 1,
+                              max_model_len: int = 16384) -> EngineConfig:
+        return EnginePresets._base(model, tp_size, pp_size, max_model_len, 128, 16384, 0.92)
+
+    @staticmethod
+    def multi_lora_serving(model: str = "tiny", max_lora_rank: int = 64, max_concurrent_loras: int = 4,
+                           tp_size: int = 1, max_model_len: int = 4096) -> EngineConfig:
+        c = EnginePresets._base(model, tp_size, 1, max_model_len, 64, 8192, 0.88)
+        c.lora = LoRAServingConfig(enabled=True, max_loras=max_concurrent_loras, max_lora_rank=max_lora_rank)
+        return c
 
     @staticmethod
     def long_context(model: str = "tiny", max_len: int = 131072) -> EngineConfig:

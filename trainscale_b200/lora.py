@@ -29,10 +29,43 @@ class LoRALinear(nn.Module):
         self.lora_A = nn.Parameter(torch.empty(r, in_features, dtype=dtype, device=device))
         self.lora_B = nn.Parameter(torch.zeros(rows, r, dtype=dtype, device=device))
         self.dropout = nn.Dropout(dropout) if dropout > 0 else None
-        if init == "gaussian":
-            nn.init.normal_(self.lora_A, std=1.0 / r)
+        self._init = init
+        self.weight = None            # frozen base weight: only when built by `from_linear` (stand-alone layer)
+        self.bias_param = None
+        self.reset_lora_parameters()
+
+    def reset_lora_parameters(self) -> None:
+        """A: Kaiming-uniform (or N(0, 1/r) for init='gaussian'); B: zero, so the adapter starts as a no-op."""
+        if self._init == "gaussian":
+            nn.init.normal_(self.lora_A, std=1.0 / self.r)
         else:
             nn.init.kaiming_uniform_(self.lora_A, a=math.sqrt(5))
+        nn.init.zeros_(self.lora_B)
+
+    @classmethod
+    def from_linear(cls, linear: nn.Linear, r: int = 16, lora_alpha: float = 32.0, lora_dropout: float = 0.0,
+                    use_rslora: bool = False) -> "LoRALinear":
+        """A stand-alone adapted layer around an existing nn.Linear, whose weight is shared and frozen
+        (data_pipeline/trainer/lora.py:148-174)."""
+        m = cls(linear.in_features, linear.out_features, r, lora_alpha, lora_dropout, use_rslora,
+                dtype=linear.weight.dtype, device=linear.weight.device)
+        m.weight = nn.Parameter(linear.weight.data, requires_grad=False)
+        if linear.bias is not None:
+            m.bias_param = nn.Parameter(linear.bias.data.clone())
+        return m
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        """y = x W^T (+ b) + scaling * (x A^T) B^T; without a base weight, the low-rank term alone."""
+        if self.weight is None:
+            return self.delta(x)
+        y = gemm.linear(x, self.weight) + self.delta(x)
+        return y if self.bias_param is None else y + self.bias_param
+
+    def merge_weights(self) -> torch.Tensor:
+        """W + scaling * B A, as a new tensor in the base weight's dtype."""
+        if self.weight is None:
+            raise ValueError("no base weight to merge into")
+        return (self.weight.float() + self.delta_weight()).to(self.weight.dtype)
 
     def delta(self, x: torch.Tensor) -> torch.Tensor:
         if self.dropout is not None:
@@ -127,7 +160,15 @@ def _targets_for(model_cfg) -> dict:
 def get_peft_model(model, r: int = 16, lora_alpha: float = 32.0, lora_dropout: float = 0.0,
                    target_modules: list[str] | None = None, use_rslora: bool = True, modules_to_save: list[str] | None = None,
                    init_lora_weights: bool | str = True, rank_pattern: dict | None = None):
-    """Freeze the base weights and attach adapters. Returns the same model object."""
+    """Freeze the base weights and attach adapters. Returns the same model object.  `r` may also be a `LoraConfig`
+    (the peft calling form `get_peft_model(model, config)`), whose fields then replace the keyword arguments."""
+    if not isinstance(r, int):
+        cfg = r
+        r, lora_alpha, lora_dropout = cfg.r, cfg.lora_alpha, cfg.lora_dropout
+        target_modules, use_rslora = list(cfg.target_modules), cfg.use_rslora
+        init_lora_weights, rank_pattern = cfg.init_lora_weights, dict(cfg.rank_pattern) or None
+        # embeddings and the head stay frozen unless the caller names them: a LoraConfig's default lists both
+        modules_to_save = modules_to_save
     targets = _targets_for(model.config)
     wanted = [t for t in (target_modules or list(targets)) if t in targets]
     for p in model.parameters():
@@ -231,9 +272,7 @@ def save_adapter(model, path, adapter_config: dict | None = None) -> None:
     (path / "adapter_config.json").write_text(json.dumps(cfg, indent=2))
 
 
-def load_adapter(model, path, strict: bool = True) -> list[str]:
-    """Loads adapter weights saved by `save_adapter` (or by peft, same key layout) into a model that already carries
-    adapters of the same shapes (`get_peft_model` first).  Returns the keys that found no adapter."""
+def _read_adapter_file(path) -> dict[str, torch.Tensor]:
     from pathlib import Path
     path = Path(path)
     f = path / "adapter_model.safetensors"
@@ -243,7 +282,28 @@ def load_adapter(model, path, strict: bool = True) -> list[str]:
     else:
         sd = torch.load(path / "adapter_model.bin", map_location="cpu", weights_only=True)
     # peft inserts the adapter name ("default") before ".weight"
-    sd = {k.replace(".lora_A.default.", ".lora_A.").replace(".lora_B.default.", ".lora_B."): v for k, v in sd.items()}
+    return {k.replace(".lora_A.default.", ".lora_A.").replace(".lora_B.default.", ".lora_B."): v for k, v in sd.items()}
+
+
+def adapter_state_from_dir(model, path) -> dict[str, torch.Tensor]:
+    """An adapter directory (`save_adapter` / peft layout) as {parameter name of `model`: tensor}, the form of
+    `lora_state_dict` that the serving engine's adapter registry takes; the model's own adapters are not touched."""
+    sd = _read_adapter_file(path)
+    names = {id(p): n for n, p in model.named_parameters()}
+    out = {}
+    for stem, part in _adapter_items(model):
+        for kind in ("lora_A", "lora_B"):
+            k = f"{stem}.{kind}.weight"
+            if k not in sd:
+                raise KeyError(f"adapter checkpoint has no {k}")
+            out[names[id(getattr(part, kind))]] = sd[k]
+    return out
+
+
+def load_adapter(model, path, strict: bool = True) -> list[str]:
+    """Loads adapter weights saved by `save_adapter` (or by peft, same key layout) into a model that already carries
+    adapters of the same shapes (`get_peft_model` first).  Returns the keys that found no adapter."""
+    sd = _read_adapter_file(path)
     used = set()
     with torch.no_grad():
         for stem, p in _adapter_items(model):

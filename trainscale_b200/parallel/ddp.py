@@ -101,6 +101,8 @@ class PowerSGDHook:
         self.state.clear()
         self.iter = 0
 
+    reset_state = reset
+
     def __call__(self, group, bucket: torch.Tensor, key: int = 0) -> torch.Tensor:
         self.iter += 1
         w = dist.get_world_size(group)
@@ -136,6 +138,9 @@ class TopKSparsificationHook:
     def __init__(self, ratio: float = 0.01):
         self.ratio = ratio
         self.err: dict[int, torch.Tensor] = {}
+
+    def reset_state(self) -> None:
+        self.err.clear()
 
     def __call__(self, group, bucket: torch.Tensor, key: int = 0) -> torch.Tensor:
         w = dist.get_world_size(group)
@@ -295,6 +300,16 @@ class DDPMetrics:
     def to_dict(self) -> dict:
         return dict(self.__dict__)
 
+    def compute_avg_latency_ms(self) -> float:
+        return self.allreduce_ms / self.steps if self.steps else 0.0
+
+    def compute_bandwidth_gbps(self) -> float:
+        """Payload bytes per second of all-reduce time, in GB/s."""
+        return self.bytes_reduced / (self.allreduce_ms * 1e6) if self.allreduce_ms > 0 else 0.0
+
+    def reset(self) -> None:
+        self.__init__()
+
 
 class MemoryPressureMonitor:
     """Watches allocated / total device memory; above `high` it asks for relief (smaller buckets, cache release),
@@ -329,6 +344,28 @@ class MemoryPressureMonitor:
         if lvl == "critical" and torch.cuda.is_available() and self._probe is None:
             torch.cuda.empty_cache()
         return lvl
+
+    def get_pressure_level(self) -> int:
+        """0 normal, 1 high, 2 critical."""
+        return {"normal": 0, "high": 1, "critical": 2}[self.level()]
+
+    @property
+    def allocated_bytes(self) -> int:
+        return torch.cuda.memory_allocated(self.device) if torch.cuda.is_available() else 0
+
+    @property
+    def reserved_bytes(self) -> int:
+        return torch.cuda.memory_reserved(self.device) if torch.cuda.is_available() else 0
+
+    def emergency_free(self) -> int:
+        """Release the allocator's cached blocks; returns the bytes that went back to the driver."""
+        import gc
+        gc.collect()
+        if not torch.cuda.is_available():
+            return 0
+        before = torch.cuda.memory_reserved(self.device)
+        torch.cuda.empty_cache()
+        return before - torch.cuda.memory_reserved(self.device)
 
     def suggested_bucket_mb(self, base_mb: int) -> int:
         return {"normal": base_mb, "high": max(1, base_mb // 2), "critical": max(1, base_mb // 4)}[self.level()]
@@ -386,6 +423,46 @@ class SOTADDPEngine:
     def no_sync(self):
         with (self.engine.no_sync() if self.engine is not None else contextlib.nullcontext()):
             yield
+
+    # ---- accessors of the reference's engine (data_pipeline/trainer/distributed/ddp.py:1587-1672)
+    rank = property(lambda self: dist.get_rank() if dist.is_available() and dist.is_initialized() else 0)
+    world_size = property(lambda self: dist.get_world_size() if dist.is_available() and dist.is_initialized() else 1)
+    is_rank_zero = property(lambda self: self.rank == 0)
+
+    def _need_engine(self):
+        if self.engine is None:
+            raise RuntimeError("call wrap_model() first")
+        return self.engine
+
+    def get_module(self) -> nn.Module:
+        """The module that was wrapped (the engine aliases its parameters; there is no wrapper module to peel off)."""
+        return self._need_engine().model
+
+    def clip_grad_norm_(self, max_norm: float, norm_type: float = 2.0) -> torch.Tensor:
+        """Clip the gradients the engine holds; the engine's own `step()` already clips to its configured
+        `max_grad_norm` on the device, this is for loops that step another optimizer."""
+        eng = self._need_engine()
+        params = [p for p in eng.model.parameters() if p.grad is not None or getattr(p, "main_grad", None) is not None]
+        for p in params:
+            if p.grad is None:
+                p.grad = p.main_grad
+        return torch.nn.utils.clip_grad_norm_(params, max_norm, norm_type)
+
+    def get_metrics(self) -> "DDPMetrics":
+        m = self.__dict__.setdefault("_metrics", DDPMetrics())
+        if self.engine is not None:
+            m.steps = getattr(self.engine, "step_count", m.steps)
+        return m
+
+    def reset_metrics(self) -> None:
+        self.__dict__["_metrics"] = DDPMetrics()
+
+    def reset_compression_state(self) -> None:
+        """Forget the error-feedback / low-rank state of a compression hook (after loading a checkpoint the residuals of
+        the old trajectory no longer apply)."""
+        reset = getattr(self.hook, "reset_state", None)
+        if reset is not None:
+            reset()
 
     def check_health(self, timeout_s: float = 30.0) -> bool:
         if not dist.is_initialized():

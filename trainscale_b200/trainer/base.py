@@ -30,8 +30,14 @@ class _State:
 class Trainer:
     def __init__(self, model: nn.Module, args: TrainingArguments | None = None, train_dataloader: Iterable | None = None,
                  eval_dataloader: Iterable | None = None, optimizer=None, scheduler=None, callbacks: list | None = None,
-                 compute_loss: Callable | None = None, compute_metrics: Callable | None = None):
+                 compute_loss: Callable | None = None, compute_metrics: Callable | None = None,
+                 train_dataset=None, eval_dataset=None, data_collator: Callable | None = None):
         self.model, self.args = model, args or TrainingArguments()
+        self.train_dataset, self.eval_dataset, self.data_collator = train_dataset, eval_dataset, data_collator
+        if train_dataloader is None and train_dataset is not None:
+            train_dataloader = self.get_train_dataloader()
+        if eval_dataloader is None and eval_dataset is not None:
+            eval_dataloader = self.get_eval_dataloader()
         self.train_dataloader, self.eval_dataloader = train_dataloader, eval_dataloader
         self.optimizer, self.scheduler = optimizer, scheduler
         self.callbacks = CallbackHandler(callbacks or [])
@@ -40,6 +46,29 @@ class Trainer:
         self.device = next(model.parameters()).device
         self.ctx = CallbackContext(trainer=self, state=self.state, config=self.args, model=model)
         self.callbacks.fire("on_init_end", self.ctx)
+
+    def _loader(self, dataset, batch_size: int, shuffle: bool, drop_last: bool):
+        from torch.utils.data import DataLoader
+        a = self.args
+        g = torch.Generator().manual_seed(a.seed) if shuffle else None
+        return DataLoader(dataset, batch_size=batch_size, shuffle=shuffle, num_workers=a.dataloader_num_workers,
+                          pin_memory=a.dataloader_pin_memory and torch.cuda.is_available(), drop_last=drop_last,
+                          collate_fn=self.data_collator, generator=g)
+
+    def get_train_dataloader(self):
+        """Shuffled loader over `train_dataset` (data_pipeline/trainer/base.py:333-345); the shuffle is seeded by
+        `args.seed`."""
+        if self.train_dataset is None:
+            from ..core.errors import ConfigurationError
+            raise ConfigurationError("training dataset not provided")
+        return self._loader(self.train_dataset, self.args.per_device_train_batch_size, True, self.args.dataloader_drop_last)
+
+    def get_eval_dataloader(self):
+        if self.eval_dataset is None:
+            from ..core.errors import ConfigurationError
+            raise ConfigurationError("evaluation dataset not provided")
+        return self._loader(self.eval_dataset, self.args.per_device_eval_batch_size or self.args.per_device_train_batch_size,
+                            False, False)
 
     def create_optimizer(self):
         a = self.args
@@ -142,6 +171,16 @@ class Trainer:
         from pathlib import Path
         save_model_weights(self.model, Path(output_dir))
         self.callbacks.fire("on_save", self.ctx)
+
+    def load_model(self, checkpoint_dir: str) -> None:
+        """Weights written by `save_model` (safetensors, sharded or not), or a plain `model.pt` state dict."""
+        from pathlib import Path
+        d = Path(checkpoint_dir)
+        if (d / "model.pt").exists() and not any(d.glob("*.safetensors")):
+            self.model.load_state_dict(torch.load(d / "model.pt", map_location=self.device, weights_only=True))
+            return
+        from ..ckpt import load_model_weights
+        load_model_weights(self.model, d)
 
 
 class PretrainingTrainer(Trainer):
