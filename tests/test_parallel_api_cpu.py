@@ -587,3 +587,155 @@ def test_parallel_dims_state_pool_timer_and_manager_accessors():
     buf = mgr.acquire_buffer((4, 4))
     mgr.release_buffer(buf)
     mgr.destroy()
+
+
+# ------------------------------------------------------------------------------------------------ offload protocol, policy members
+def test_pipeline_offload_manager_schedule_protocol():
+    """Chunks are offloaded in forward and brought back in backward with gradients equal to the plain run; the
+    backward order is learnt in the first iteration and replayed; disabling offload keeps everything in place."""
+    import torch
+    from trainscale_b200.parallel.activation import PipelineOffloadManager
+    PipelineOffloadManager.reset_instance()
+    m = PipelineOffloadManager.get_instance()
+    assert m is PipelineOffloadManager.get_instance()
+    lin = torch.nn.Linear(64, 64)
+
+    def iteration():
+        outs, grads = [], []
+        for _ in range(3):
+            m.init_model_chunk_offload_handler(min_offload_tensor_size=128)
+            m.cur_forward_chunk().begin_group("mlp")
+            x = torch.randn(8, 64, requires_grad=True)
+            with m:
+                outs.append((x, (lin(x).relu() ** 2).sum()))
+        for x, y in outs:
+            m.pop_backward_chunk("mlp")
+            y.backward()
+            if m.cur_backward_chunk() is not None:
+                assert m.cur_backward_chunk().finish_all_groups("mlp")
+            grads.append(x.grad.clone())
+        return outs, grads
+
+    outs, grads = iteration()
+    first = m.offload_summary_total_bytes
+    assert first > 0 and m.offload_summary_bytes == {"mlp": first}
+    x = outs[0][0].detach().clone().requires_grad_(True)
+    (lin(x).relu() ** 2).sum().backward()
+    assert torch.allclose(x.grad, grads[0])
+    m.reset()
+    iteration()
+    assert len(m._forward) == 3 and m.offload_summary_total_bytes == 2 * first     # same three chunks, replayed
+    m.disable_offload()
+    m.reset()
+    iteration()
+    assert m.offload_summary_total_bytes == 2 * first
+    m.enable_offload()
+    assert m.cpu_tensor_pool is m.cur_forward_chunk().cpu_tensor_pool
+    # interleaved (virtual) stages: within one round the later virtual stage goes to backward first
+    PipelineOffloadManager.reset_instance()
+    m = PipelineOffloadManager.get_instance()
+    for _ in range(2):
+        for stage in range(2):
+            m.init_model_chunk_offload_handler(2, stage)
+    m._flush(final=True)
+    assert [(h.vpp_rank, h.chunk_id) for h in m._backward] == [(1, 1), (0, 0), (1, 3), (0, 2)]
+    PipelineOffloadManager.reset_instance()
+
+
+def test_chunk_handler_tags_and_group_bookkeeping():
+    import pytest
+    import torch
+    from trainscale_b200.parallel.activation import ChunkOffloadHandler, OffloadTensorGroup
+    h = ChunkOffloadHandler(min_offload_tensor_size=16)
+    assert h.is_empty_chunk() and h.finish_all_groups()
+    h.begin_group("attn")
+    small, big = torch.ones(4), torch.arange(64.0)
+    s1, s2 = h.tensor_push(small), h.tensor_push(big)
+    assert s1[0] == "direct" and s2[0] == "offloaded" and not h.is_empty_chunk("attn") and h.is_empty_chunk("mlp")
+    assert not h.finish_all_groups("attn")
+    assert h.tensor_pop(s1) is small and torch.equal(h.tensor_pop(s2), big)
+    assert h.finish_all_groups("attn") and h.get_max_deduplicated_groups() == 1
+    with pytest.raises(ValueError):
+        h.tensor_pop(("bogus", None))
+    h.reset()
+    assert h.is_empty_chunk()
+    g = OffloadTensorGroup("g")
+    g.push_tensor("k", small)
+    g.update_stats(small)
+    assert g.pop_tensor("k") is small and g.total_offload_bytes == 16 and g.total_tensor_count == 1
+
+
+def test_activation_policy_members():
+    import torch
+    import torch.nn as nn
+    from trainscale_b200.models.llama import build_model
+    from trainscale_b200.parallel.activation import (ActivationCheckpoint, ActivationCheckpointConfig, ActivationOffloader,
+                                                     ActivationPool, CheckpointMetrics, HierarchicalCheckpointManager,
+                                                     LayerProfile, MemoryProfiler, OperationCheckpointContext,
+                                                     OperationType, SelectiveCheckpointPolicy)
+    mp = MemoryProfiler()
+    mp.clear()
+    flash = mp.estimate_activation_memory(1, 4096, 4096, 32, 32, 14336, torch.bfloat16, 8)
+    dense = mp.estimate_activation_memory(1, 4096, 4096, 32, 32, 14336, torch.bfloat16, 8, flash_attention=False)
+    # per token and layer: 5 H + (nh + 2 nkv) d + 3 I elements
+    per_token = (5 * 4096 + 48 * 128 + 3 * 14336) * 2
+    assert flash == int((4096 * per_token + 32 * 4096 * 4) * 32 * 1.1)
+    assert abs((dense - flash) - 32 * 4096 * (4096 * 2 - 4) * 32 * 1.1) <= 2      # the S x S probabilities
+
+    class MLP(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.a, self.b = nn.Linear(16, 64), nn.Linear(64, 16)
+        def forward(self, x):
+            return self.b(torch.relu(self.a(x)))
+
+    prof = mp.profile_layer(MLP(), "mlp0", torch.randn(2, 8, 16))
+    assert prof.operation_type is OperationType.FFN and prof.is_ffn
+    assert prof.activation_memory_bytes == (2 * 8 * 16 + 2 * 8 * 64) * 4          # the input and the ReLU output
+    mp.record_checkpoint_metrics(CheckpointMetrics("l", 1, 2, 100, 1, 1))
+    st = mp.get_statistics()
+    assert st["profiled_layers"] == 1 and st["total_memory_saved_bytes"] == 100 and st["total_recompute_time_ns"] == 2
+    mp.clear()
+    assert mp.get_statistics()["checkpoint_operations"] == 0
+
+    pol = SelectiveCheckpointPolicy()
+    assert pol.should_checkpoint("self_attn") and not pol.should_checkpoint("input_layernorm")
+    assert not pol.should_checkpoint("mlp", recompute_cost=0.01)                  # switched on, but trivially cheap
+    assert pol.should_checkpoint("other", activation_size_bytes=10 ** 9)
+    assert pol.should_checkpoint("other", 10, 0.5, memory_pressure=0.9)
+    assert not pol.should_checkpoint("other", 10, 0.5, memory_pressure=0.1)
+    pol.update_from_profile(LayerProfile("other", OperationType.CUSTOM, 10 ** 9, 0, 0.5, False, False))
+    assert pol.should_checkpoint("other", 10, 0.5, memory_pressure=0.1)
+
+    h = HierarchicalCheckpointManager(ActivationCheckpointConfig(segment_size=4, hierarchy_levels=3), 20)
+    assert [(s.start_layer, s.end_layer) for s in h._level(1)] == [(0, 8), (8, 16), (16, 20)]
+    assert h.should_checkpoint_layer(3) and not h.should_checkpoint_layer(4)
+    assert h.adjust_level_for_memory(0.5) == 2 and h.should_checkpoint_layer(15) and not h.should_checkpoint_layer(7)
+    assert h.adjust_level_for_memory(0.9) == 1 and h.adjust_level_for_memory(0.99) == 0
+    assert h.get_segment_for_layer(19, level=0).start_layer == 16
+
+    pool = ActivationPool()
+    t = pool.acquire((4, 4), torch.float32)
+    pool.release(t)
+    assert pool.acquire((4, 4), torch.float32) is not None and pool.hit_rate == 0.5 and pool.get_stats()["hits"] == 1
+
+    off = ActivationOffloader()
+    x = torch.randn(8, 8)
+    hid = off.offload(x)
+    off.prefetch(hid)
+    assert torch.equal(off.reload(hid), x)
+    off.release(hid)
+    off.clear()
+
+    m = build_model("tiny", dtype=torch.float32, device="cpu")
+    L = len(m.model.layers)
+    assert ActivationCheckpoint.apply_full(m)._ts_checkpointed_layers == list(range(L))
+    assert ActivationCheckpoint.apply_selective(m, 2)._ts_checkpointed_layers == list(range(0, L, 2))
+    assert ActivationCheckpoint.apply_hierarchical(m, 2, 2)._ts_checkpointed_layers == [i for i in range(L) if i % 2 == 0]
+    assert ActivationCheckpoint.apply_memory_budget(m, 0.7, 1, 128, total_bytes=1 << 24)._ts_checkpointed_layers == list(range(L))
+    huge = ActivationCheckpoint.apply_memory_budget(m, 0.7, 1, 128, total_bytes=1 << 40)
+    assert huge._ts_checkpointed_layers == [] and huge._ts_activation_checkpoint.get_statistics()["config"]["mode"] == "MEMORY_BUDGET"
+
+    with OperationCheckpointContext(pol, "attention") as c:
+        assert OperationCheckpointContext.get_current() is c and c.checkpointing
+    assert OperationCheckpointContext.get_current() is None

@@ -33,6 +33,21 @@ class ActivationCheckpointConfig:
     bytes_per_layer: float | None = None
     offload_min_bytes: int = 1 << 20
     hierarchical_group: int = 4
+    # operation-level policy and hierarchy (data_pipeline/trainer/distributed/activation_checkpoint.py:219-378)
+    memory_budget_fraction: float = 0.70
+    checkpoint_attention: bool = True
+    checkpoint_ffn: bool = True
+    checkpoint_layernorm: bool = False
+    checkpoint_residual: bool = False
+    min_recompute_cost_threshold: float = 0.1
+    max_memory_threshold_bytes: int = 100 * 2 ** 20
+    hierarchy_levels: int = 2
+    segment_size: int = 4
+    use_reentrant: bool = False
+
+    def with_mode(self, mode) -> "ActivationCheckpointConfig":
+        import dataclasses
+        return dataclasses.replace(self, mode=CheckpointMode(mode))
 
 
 class MemoryProfiler:
@@ -59,10 +74,121 @@ class MemoryProfiler:
         free, total = torch.cuda.mem_get_info()
         return 1.0 - free / total
 
+    get_memory_pressure = pressure
+
+    @staticmethod
+    def estimate_activation_memory(batch_size: int, seq_len: int, hidden_size: int, num_layers: int,
+                                   num_attention_heads: int, intermediate_size: int,
+                                   dtype: torch.dtype = torch.bfloat16, num_kv_heads: int | None = None,
+                                   flash_attention: bool = True) -> int:
+        """Bytes that a decoder of this shape keeps for backward without recomputation, +10 % for temporaries.
+        Per layer and token: the residual stream into each of the two norms (2 H), the two normalised inputs (2 H),
+        q / k / v after RoPE ((nh + 2 nkv) d), the attention output (H), gate and up (2 I) and the GLU product (I).
+        With `flash_attention` the S x S probabilities are not kept (only a per-row log-sum-exp, 4 bytes per head and
+        token); without it they are, which is the term that dominates the reference's estimate
+        (data_pipeline/trainer/distributed/activation_checkpoint.py:487-570)."""
+        e = torch.finfo(dtype).bits // 8 if dtype.is_floating_point else torch.iinfo(dtype).bits // 8
+        nh, nkv = num_attention_heads, num_kv_heads or num_attention_heads
+        d = hidden_size // nh
+        tokens = batch_size * seq_len
+        per_token = (5 * hidden_size + (nh + 2 * nkv) * d + 3 * intermediate_size) * e
+        attn = batch_size * nh * seq_len * (4 if flash_attention else seq_len * e)
+        return int((tokens * per_token + attn) * num_layers * 1.1)
+
+    def profile_layer(self, module: nn.Module, name: str, input_tensor: torch.Tensor) -> "LayerProfile":
+        """Measures what `module` keeps for backward on `input_tensor` (saved-tensor hooks around one forward; weights
+        excluded) and classifies it by its class name; when the forward cannot be run with this input alone the
+        estimate is twice the input's size."""
+        cls = type(module).__name__.lower()
+        kind = (OperationType.ATTENTION if "attn" in cls or "attention" in cls else
+                OperationType.FFN if any(k in cls for k in ("mlp", "ffn", "feedforward", "moe")) else
+                OperationType.LAYERNORM if "norm" in cls else
+                OperationType.EMBEDDING if "embed" in cls else OperationType.CUSTOM)
+        weights = {p.data_ptr() for p in module.parameters()}      # by address: autograd saves views of weights
+        seen, saved = set(), [0]
+
+        def pack(t):
+            if t.data_ptr() not in weights and t.data_ptr() not in seen:
+                seen.add(t.data_ptr())
+                saved[0] += t.numel() * t.element_size()
+            return t
+
+        try:
+            with torch.enable_grad(), torch.autograd.graph.saved_tensors_hooks(pack, lambda t: t):
+                module(input_tensor.detach().requires_grad_(input_tensor.is_floating_point()))
+            act = saved[0]
+        except Exception:   # noqa: BLE001 - modules that need more than one input
+            act = 2 * input_tensor.numel() * input_tensor.element_size()
+        params = sum(p.numel() for p in module.parameters())
+        tokens = input_tensor.numel() // max(1, input_tensor.shape[-1]) if input_tensor.dim() > 1 else input_tensor.numel()
+        cost = {OperationType.ATTENTION: 0.8, OperationType.FFN: 0.6, OperationType.LAYERNORM: 0.05,
+                OperationType.ACTIVATION: 0.02}.get(kind, 0.5)
+        prof = LayerProfile(name, kind, act, 2 * params * tokens, cost, kind is OperationType.ATTENTION,
+                            kind is OperationType.FFN)
+        self.__dict__.setdefault("layer_profiles", {})[name] = prof
+        return prof
+
+    def record_checkpoint_metrics(self, metrics: "CheckpointMetrics") -> None:
+        lst = self.__dict__.setdefault("checkpoint_metrics", [])
+        lst.append(metrics)
+        if len(lst) > 10000:
+            del lst[:5000]
+
+    def get_statistics(self) -> dict:
+        ms = self.__dict__.get("checkpoint_metrics", [])
+        return {"peak_memory_bytes": max((x["peak"] for x in self.snapshots), default=0),
+                "snapshot_count": len(self.snapshots), "profiled_layers": len(self.__dict__.get("layer_profiles", {})),
+                "checkpoint_operations": len(ms), "total_memory_saved_bytes": sum(m.memory_saved_bytes for m in ms),
+                "total_recompute_time_ns": sum(m.recompute_time_ns for m in ms)}
+
+    def clear(self) -> None:
+        self.snapshots.clear()
+        self.__dict__.get("layer_profiles", {}).clear()
+        self.__dict__.get("checkpoint_metrics", []).clear()
+
 
 class SelectiveCheckpointPolicy:
-    def __init__(self, cfg: ActivationCheckpointConfig, num_layers: int):
-        self.cfg, self.L = cfg, num_layers
+    """Which layers are recomputed (`layers_to_checkpoint`) and, inside a layer, which kinds of operation
+    (`should_checkpoint`, `should_checkpoint_op`)."""
+
+    _KINDS = {"attention": ("attention", "attn"), "ffn": ("mlp", "ffn", "feed_forward", "feedforward"),
+              "layernorm": ("layernorm", "layer_norm", "rmsnorm", "rms_norm"), "residual": ("residual", "skip")}
+
+    def __init__(self, cfg: ActivationCheckpointConfig | None = None, num_layers: int = 0):
+        self.cfg, self.L = cfg or ActivationCheckpointConfig(), num_layers
+        self.config = self.cfg
+        self._decisions: dict[str, bool] = {}
+        for kind, words in self._KINDS.items():
+            for w in words:
+                self._decisions[w] = bool(getattr(self.cfg, f"checkpoint_{kind}"))
+
+    def should_checkpoint(self, op_name: str, activation_size_bytes: int = 0, recompute_cost: float = 0.5,
+                          memory_pressure: float | None = None) -> bool:
+        """A named operation is recomputed when its kind is switched on and it is not trivially cheap; an operation of
+        no known kind when it keeps more than `max_memory_threshold_bytes`, or - unless cheap - when device memory is
+        more than 85 % in use (data_pipeline/trainer/distributed/activation_checkpoint.py:1283-1324)."""
+        low = op_name.lower()
+        cheap = recompute_cost < self.cfg.min_recompute_cost_threshold
+        for word in sorted(self._decisions, key=len, reverse=True):
+            if word in low:
+                return self._decisions[word] and not cheap
+        if activation_size_bytes > self.cfg.max_memory_threshold_bytes:
+            return True
+        if cheap:
+            return False
+        pressure = MemoryProfiler().pressure() if memory_pressure is None else memory_pressure
+        return pressure > 0.85
+
+    def should_checkpoint_op(self, op_type) -> bool:
+        return self.should_checkpoint(getattr(op_type, "value", str(op_type)))
+
+    def update_from_profile(self, layer_profile) -> None:
+        """A layer seen to keep more than twice the size threshold is always recomputed from now on; one whose
+        recomputation is nearly free never is."""
+        if layer_profile.activation_memory_bytes > 2 * self.cfg.max_memory_threshold_bytes:
+            self._decisions[layer_profile.name.lower()] = True
+        elif layer_profile.recompute_cost < self.cfg.min_recompute_cost_threshold / 2:
+            self._decisions[layer_profile.name.lower()] = False
 
     def layers_to_checkpoint(self) -> list[int]:
         m = CheckpointMode(self.cfg.mode)
@@ -83,6 +209,58 @@ class SelectiveCheckpointPolicy:
 class ActivationCheckpoint:
     def __init__(self, cfg: ActivationCheckpointConfig | None = None):
         self.cfg = cfg or ActivationCheckpointConfig()
+        self.config = self.cfg
+        self.profiler = MemoryProfiler()
+        self._stats = {"layers_wrapped": 0, "applications": 0}
+
+    # ---- one-call forms (data_pipeline/trainer/distributed/activation_checkpoint.py:2079-2170): return the model
+    @staticmethod
+    def _applied(model, cfg: ActivationCheckpointConfig):
+        ac = ActivationCheckpoint(cfg)
+        model._ts_checkpointed_layers = ac.apply(model)
+        model._ts_activation_checkpoint = ac
+        return model
+
+    @staticmethod
+    def apply_full(model):
+        return ActivationCheckpoint._applied(model, ActivationCheckpointConfig(CheckpointMode.FULL))
+
+    @staticmethod
+    def apply_selective(model, frequency: int = 2):
+        return ActivationCheckpoint._applied(model, ActivationCheckpointConfig(CheckpointMode.SELECTIVE, int(frequency)))
+
+    @staticmethod
+    def apply_memory_budget(model, budget: float = 0.7, batch_size: int = 1, seq_len: int = 4096,
+                            total_bytes: int | None = None):
+        """Recompute as many of the earliest layers as needed for the kept activations to fit `budget` x device memory
+        (`total_bytes` replaces the device's size, e.g. off-GPU) after the weights; the per-layer size comes from
+        `MemoryProfiler.estimate_activation_memory` for the model's own shape."""
+        c = model.config
+        per_layer = MemoryProfiler.estimate_activation_memory(batch_size, seq_len, c.hidden_size, 1, c.num_attention_heads,
+                                                              c.intermediate_size, torch.bfloat16,
+                                                              getattr(c, "num_key_value_heads", None))
+        if total_bytes is None:
+            total_bytes = torch.cuda.mem_get_info()[1] if torch.cuda.is_available() else 0
+        weights = sum(p.numel() * p.element_size() for p in model.parameters())
+        room = max(0.0, budget * total_bytes - weights)
+        cfg = ActivationCheckpointConfig(CheckpointMode.MEMORY_BUDGET, memory_budget_gb=max(room, 1.0) / 2 ** 30,
+                                         bytes_per_layer=per_layer, memory_budget_fraction=budget)
+        return ActivationCheckpoint._applied(model, cfg)
+
+    @staticmethod
+    def apply_hierarchical(model, levels: int = 2, segment_size: int = 4):
+        cfg = ActivationCheckpointConfig(CheckpointMode.HIERARCHICAL, hierarchical_group=int(segment_size),
+                                         hierarchy_levels=int(levels), segment_size=int(segment_size))
+        return ActivationCheckpoint._applied(model, cfg)
+
+    def get_statistics(self) -> dict:
+        return {**self._stats, "profiler_stats": self.profiler.get_statistics(),
+                "config": {"mode": CheckpointMode(self.cfg.mode).name, "frequency": self.cfg.frequency,
+                           "memory_budget_fraction": self.cfg.memory_budget_fraction}}
+
+    def clear_profiling_data(self) -> None:
+        self.profiler.clear()
+        self._stats = {"layers_wrapped": 0, "applications": 0}
 
     def apply(self, model) -> list[int]:
         """Configure the framework decoder (it recomputes layer i when i % checkpoint_every == 0) or wrap generic
@@ -97,6 +275,8 @@ class ActivationCheckpoint:
                 inner.gradient_checkpointing = False
             return []
         chosen = SelectiveCheckpointPolicy(self.cfg, len(layers)).layers_to_checkpoint()
+        self._stats["layers_wrapped"] += len(chosen)
+        self._stats["applications"] += 1
         if hasattr(inner, "gradient_checkpointing"):
             inner.gradient_checkpointing = bool(chosen)
             inner.checkpoint_layers = set(chosen)
@@ -187,27 +367,227 @@ class ActivationOffloader:
         return (f"offloaded {self.offloaded_bytes / 2 ** 30:.2f} GiB, restored {self.restored_bytes / 2 ** 30:.2f} GiB, "
                 f"pinned pool {self.pool.bytes_allocated / 2 ** 30:.2f} GiB")
 
+    # ---- explicit, handle-addressed use (data_pipeline/trainer/distributed/activation_checkpoint.py:860-1056)
+    def offload(self, tensor: torch.Tensor) -> int:
+        """Copy `tensor` to a pooled host buffer (on the copy stream for a device tensor); returns the handle id."""
+        table = self.__dict__.setdefault("_handles", {})
+        hid = self.__dict__["_next_id"] = self.__dict__.get("_next_id", 0) + 1
+        host = self.pool.get(tensor.shape, tensor.dtype)
+        ev = None
+        if tensor.is_cuda:
+            self.d2h.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(self.d2h):
+                host.copy_(tensor.detach(), non_blocking=True)
+                ev = torch.cuda.Event()
+                ev.record(self.d2h)
+            tensor.record_stream(self.d2h)
+        else:
+            host.copy_(tensor.detach())
+        table[hid] = {"host": host, "event": ev, "device": tensor.device, "ready": None}
+        self.offloaded_bytes += tensor.numel() * tensor.element_size()
+        return hid
+
+    def prefetch(self, handle_id: int) -> None:
+        """Start bringing the tensor back on the host-to-device stream; `reload` then only waits for it."""
+        h = self._handles[handle_id]
+        if h["ready"] is not None:
+            return
+        if h["device"].type == "cuda":
+            if h["event"] is not None:
+                self.h2d.wait_event(h["event"])
+            with torch.cuda.stream(self.h2d):
+                out = h["host"].to(h["device"], non_blocking=True)
+                done = torch.cuda.Event()
+                done.record(self.h2d)
+            h["ready"] = (out, done)
+        else:
+            h["ready"] = (h["host"].clone(), None)
+
+    def reload(self, handle_id: int) -> torch.Tensor:
+        self.prefetch(handle_id)
+        out, done = self._handles[handle_id]["ready"]
+        if done is not None:
+            torch.cuda.current_stream().wait_event(done)
+            out.record_stream(torch.cuda.current_stream())
+        self.restored_bytes += out.numel() * out.element_size()
+        return out
+
+    def release(self, handle_id: int) -> None:
+        """Give the host buffer back to the pool.  A reload in flight is waited for first."""
+        h = self.__dict__.get("_handles", {}).pop(handle_id, None)
+        if h is None:
+            return
+        if h["ready"] is not None and h["ready"][1] is not None:
+            h["ready"][1].synchronize()
+        elif h["event"] is not None:
+            h["event"].synchronize()
+        self.pool.put(h["host"])
+
+    def clear(self) -> None:
+        for hid in list(self.__dict__.get("_handles", {})):
+            self.release(hid)
+
 
 class ChunkOffloadHandler(ActivationOffloader):
     """Offloads the saved activations of one model chunk (a pipeline stage's micro-batch, a group of layers) and
     keeps per-chunk accounting, so that a pipeline schedule can offload chunk k while chunk k+1 computes and bring it
-    back just before its backward (data_pipeline/trainer/distributed/activation_offload.py:358)."""
+    back just before its backward (data_pipeline/trainer/distributed/activation_offload.py:358).
 
-    def __init__(self, chunk_id: int = 0, min_bytes: int = 1 << 20):
+    `tensor_push` / `tensor_pop` are the pack / unpack pair of saved-tensor hooks: a tensor below
+    `min_offload_tensor_size` ELEMENTS travels as ("direct", tensor); a larger one is copied to a pooled host buffer on
+    the device-to-host stream and travels as ("offloaded", state).  Host tensors take the same path without streams, so
+    the bookkeeping is testable without a GPU.  Tensors are filed under the group opened last by `begin_group`."""
+
+    def __init__(self, chunk_id: int = 0, min_bytes: int = 1 << 20, min_offload_tensor_size: int | None = None,
+                 cpu_tensor_pool: "PinnedTensorPool | None" = None, d2h_stream=None, h2d_stream=None):
         super().__init__(min_bytes)
         self.chunk_id = chunk_id
+        self.min_offload_tensor_size = min_offload_tensor_size if min_offload_tensor_size is not None else max(1, min_bytes // 2)
+        if cpu_tensor_pool is not None:
+            self.pool = cpu_tensor_pool
+        if d2h_stream is not None:
+            self.d2h = d2h_stream
+        if h2d_stream is not None:
+            self.h2d = h2d_stream
+        self.cpu_tensor_pool = self.pool
+        self.do_offload = True
+        self.vpp_rank = 0
+        self.is_warmup = True
+        self.offload_groups: list[OffloadTensorGroup] = []
+        self._reloaded: set[int] = set()          # ids of groups whose tensors have all come back
+        self._pending: dict[int, int] = {}        # group id -> tensors still on the host
+        self.torch_tensor_count = 0
+
+    @property
+    def d2h_stream(self):
+        return self.d2h
+
+    @property
+    def h2d_stream(self):
+        return self.h2d
+
+    def begin_group(self, name: str) -> "OffloadTensorGroup":
+        g = OffloadTensorGroup(name)
+        self.offload_groups.append(g)
+        return g
+
+    def reset(self) -> None:
+        """Forget the groups of the finished iteration; the host pool keeps its buffers."""
+        self.offload_groups, self._reloaded, self._pending = [], set(), {}
+        self.torch_tensor_count = 0
+
+    def offload_tensor(self, src: torch.Tensor, use_cpu_pool: bool = True):
+        """Copy `src` to the host; returns the state that `reload_tensor` takes: (device, host tensor, pooled, group)."""
+        host = self.pool.get(src.shape, src.dtype) if use_cpu_pool else torch.empty(src.shape, dtype=src.dtype)
+        ev = None
+        if src.is_cuda:
+            self.d2h.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(self.d2h):
+                host.copy_(src.detach(), non_blocking=True)
+                ev = torch.cuda.Event()
+                ev.record(self.d2h)
+            src.record_stream(self.d2h)
+        else:
+            host.copy_(src.detach())
+        g = self.offload_groups[-1] if self.offload_groups else self.begin_group("default")
+        g.update_stats(src)
+        self._pending[id(g)] = self._pending.get(id(g), 0) + 1
+        self.offloaded_bytes += src.numel() * src.element_size()
+        return (src.device, host, use_cpu_pool, g, ev)
+
+    def reload_tensor(self, state) -> torch.Tensor:
+        dev, host, pooled, g, ev = state
+        if ev is not None:
+            ev.synchronize()
+        if dev.type == "cuda":
+            with torch.cuda.stream(self.h2d):
+                out = host.to(dev, non_blocking=True)
+            torch.cuda.current_stream().wait_stream(self.h2d)
+        else:
+            out = host.clone()
+        if pooled:
+            self.pool.put(host)
+        self.restored_bytes += out.numel() * out.element_size()
+        left = self._pending.get(id(g), 1) - 1
+        self._pending[id(g)] = left
+        if left <= 0:
+            self._reloaded.add(id(g))
+        return out
+
+    def tensor_push(self, tensor: torch.Tensor):
+        self.torch_tensor_count += 1
+        if (not self.do_offload or tensor.numel() < self.min_offload_tensor_size or isinstance(tensor, nn.Parameter)
+                or getattr(tensor, "_ts_unit", None) is not None):
+            return ("direct", tensor)
+        return ("offloaded", self.offload_tensor(tensor.contiguous()))
+
+    def tensor_pop(self, saved_state) -> torch.Tensor:
+        tag, data = saved_state
+        if tag == "direct":
+            return data
+        if tag == "offloaded":
+            return self.reload_tensor(data)
+        raise ValueError(f"unknown saved-state tag {tag!r}")
+
+    def is_empty_chunk(self, name: str | None = None) -> bool:
+        groups = [g for g in self.offload_groups if name is None or g.name == name]
+        return not any(g.total_tensor_count for g in groups)
+
+    def finish_all_groups(self, name: str | None = None) -> bool:
+        """True when every group (of that name) that offloaded something has been reloaded in full."""
+        return all(id(g) in self._reloaded for g in self.offload_groups
+                   if (name is None or g.name == name) and g.total_tensor_count)
+
+    def get_max_deduplicated_groups(self) -> int:
+        return len({g.name for g in self.offload_groups})
 
 
 class PipelineOffloadManager:
-    """One `ChunkOffloadHandler` per in-flight micro-batch of a pipeline stage
-    (data_pipeline/trainer/distributed/activation_offload.py:531)."""
+    """Activation offload for a pipeline stage: one `ChunkOffloadHandler` per in-flight micro-batch (and virtual stage),
+    all sharing two copy streams and one pinned host pool (data_pipeline/trainer/distributed/activation_offload.py:531).
+
+    Two ways to use it.  `with mgr.scope(mb):` around a micro-batch's forward (handlers keyed by micro-batch).  Or the
+    schedule-driven protocol: `init_model_chunk_offload_handler(vp_size, vp_stage)` before each forward chunk,
+    `with mgr:` around its forward, `pop_backward_chunk()` before each backward chunk, `reset()` between iterations.
+    The order in which chunks are handed to backward is learnt in the first iteration: per virtual stage in forward
+    order, later virtual stages first."""
+
+    _instance: "PipelineOffloadManager | None" = None
+
+    @classmethod
+    def get_instance(cls) -> "PipelineOffloadManager":
+        if cls._instance is None:
+            cls._instance = cls()
+        return cls._instance
+
+    @classmethod
+    def reset_instance(cls) -> None:
+        cls._instance = None
 
     def __init__(self, min_bytes: int = 1 << 20):
         self.min_bytes = min_bytes
         self.handlers: dict[int, ChunkOffloadHandler] = {}
+        cuda = torch.cuda.is_available()
+        self._d2h = torch.cuda.Stream() if cuda else None
+        self._h2d = torch.cuda.Stream() if cuda else None
+        self._pool = PinnedTensorPool()
+        self.do_offload = True
+        self._warm = True
+        self._vpp = 1
+        self._stages: list[list[ChunkOffloadHandler]] | None = None
+        self._forward: list[ChunkOffloadHandler] = []       # chunks in forward order (learnt in the first iteration)
+        self._backward: list[ChunkOffloadHandler] = []      # the same chunks in backward order
+        self._fi = self._bi = 0
+        self._cur_f: ChunkOffloadHandler | None = None
+        self._cur_b: ChunkOffloadHandler | None = None
+        self._hooks = None
 
+    # ---- keyed use
     def scope(self, micro_batch: int):
-        h = self.handlers.setdefault(micro_batch, ChunkOffloadHandler(micro_batch, self.min_bytes))
+        h = self.handlers.get(micro_batch)
+        if h is None:
+            h = self.handlers[micro_batch] = ChunkOffloadHandler(micro_batch, self.min_bytes, cpu_tensor_pool=self._pool,
+                                                                 d2h_stream=self._d2h, h2d_stream=self._h2d)
         return h.scope()
 
     def release(self, micro_batch: int) -> None:
@@ -215,6 +595,126 @@ class PipelineOffloadManager:
 
     def summary(self) -> str:
         return "; ".join(f"mb{k}: {h.summary()}" for k, h in sorted(self.handlers.items()))
+
+    # ---- shared resources and totals
+    @property
+    def d2h_stream(self):
+        return self._d2h
+
+    @property
+    def h2d_stream(self):
+        return self._h2d
+
+    @property
+    def cpu_tensor_pool(self) -> PinnedTensorPool:
+        return self._pool
+
+    def _all_chunks(self):
+        return list(self.handlers.values()) + self._forward
+
+    @property
+    def offload_summary_bytes(self) -> dict[str, int]:
+        """Bytes offloaded so far per group name."""
+        out: dict[str, int] = {}
+        for h in self._all_chunks():
+            for g in h.offload_groups:
+                out[g.name] = out.get(g.name, 0) + g.total_offload_bytes
+        return out
+
+    @property
+    def offload_summary_total_bytes(self) -> int:
+        return sum(h.offloaded_bytes for h in self._all_chunks())
+
+    def disable_offload(self) -> None:
+        self.do_offload = False
+        for h in self._all_chunks():
+            h.do_offload = False
+
+    def enable_offload(self) -> None:
+        self.do_offload = True
+        for h in self._all_chunks():
+            h.do_offload = True
+
+    # ---- schedule-driven protocol
+    def reset(self) -> None:
+        """Between iterations: the chunk order learnt in the first iteration is kept and replayed."""
+        if self._hooks is not None:
+            self.__exit__(None, None, None)
+        if self._warm and self._forward:
+            self._flush(final=True)
+            self._warm = False
+            for h in self._forward:
+                h.is_warmup = False
+        self._fi = self._bi = 0
+        self._cur_f = self._cur_b = None
+        for h in self._forward:
+            h.reset()
+
+    def _flush(self, final: bool = False) -> None:
+        st = self._stages
+        if st is None or not any(st):
+            return
+        if not final and len({len(x) for x in st}) != 1:
+            return                                            # a round over the virtual stages is not complete yet
+        for chunks in reversed(st):
+            self._backward.extend(chunks)
+        self._stages = [[] for _ in range(self._vpp)]
+
+    def init_model_chunk_offload_handler(self, vp_size: int | None = None, vp_stage: int | None = None,
+                                         min_offload_tensor_size: int = 1 << 20) -> None:
+        if not self._warm:                                    # replay: next chunk of the learnt forward order
+            self._cur_f = self._forward[self._fi % len(self._forward)]
+            self._fi += 1
+            return
+        vp = 1 if vp_size is None else int(vp_size)
+        if self._stages is None:
+            self._vpp, self._stages = vp, [[] for _ in range(vp)]
+        rank = 0 if vp_stage is None else int(vp_stage)
+        if not 0 <= rank < self._vpp:
+            raise ValueError(f"vp_stage {rank} outside [0, {self._vpp})")
+        h = ChunkOffloadHandler(len(self._forward), min_offload_tensor_size=min_offload_tensor_size,
+                                cpu_tensor_pool=self._pool, d2h_stream=self._d2h, h2d_stream=self._h2d)
+        h.vpp_rank, h.do_offload = rank, self.do_offload
+        self._stages[rank].append(h)
+        if rank == self._vpp - 1:
+            self._flush()
+        self._cur_f = h
+        self._forward.append(h)
+
+    def pop_backward_chunk(self, name: str | None = None) -> None:
+        """Make the next chunk that holds tensors (of group `name`) the current backward chunk."""
+        if self._warm:
+            self._flush(final=True)
+        self._cur_b = None
+        if not self.do_offload:
+            return                                            # nothing was offloaded: there is no chunk to wait for
+        while self._bi < len(self._backward):
+            h = self._backward[self._bi]
+            self._bi += 1
+            if not h.is_empty_chunk(name):
+                self._cur_b = h
+                return
+        raise RuntimeError("no non-empty backward chunk left")
+
+    def cur_forward_chunk(self) -> "ChunkOffloadHandler | None":
+        return self._cur_f
+
+    def cur_backward_chunk(self) -> "ChunkOffloadHandler | None":
+        return self._cur_b
+
+    def __enter__(self) -> "PipelineOffloadManager":
+        h = self._cur_f
+        if h is None or not h.do_offload:
+            return self
+        self._hooks = torch.autograd.graph.saved_tensors_hooks(
+            h.tensor_push, lambda st: st if isinstance(st, torch.Tensor) else h.tensor_pop(st))
+        self._hooks.__enter__()
+        return self
+
+    def __exit__(self, *exc) -> None:
+        if self._hooks is not None:
+            hooks, self._hooks = self._hooks, None
+            hooks.__exit__(*exc)
 
 
 def print_offload_summary(manager: "PipelineOffloadManager | ActivationOffloader") -> None:
@@ -254,6 +754,20 @@ class ActivationPool:
         self._free.clear()
         self.bytes_cached = 0
 
+    def acquire(self, shape, dtype: torch.dtype = torch.bfloat16, device="cpu") -> torch.Tensor:
+        return self.get(shape, dtype, device)
+
+    release = put
+
+    @property
+    def hit_rate(self) -> float:
+        n = self.hits + self.misses
+        return self.hits / n if n else 0.0
+
+    def get_stats(self) -> dict:
+        return {"hits": self.hits, "misses": self.misses, "hit_rate": self.hit_rate, "bytes_cached": self.bytes_cached,
+                "max_bytes": self.max_bytes, "buffers_cached": sum(len(v) for v in self._free.values())}
+
 
 def _checkpoint_function():
     from .pipeline import CheckpointFunction as F
@@ -272,12 +786,51 @@ class HierarchicalCheckpointManager:
     keeps only ITS input (g tensors), re-running itself when its turn comes.  Peak kept activations are about
     L / g + g layer inputs (minimal at g = sqrt(L)) for two extra forwards."""
 
-    def __init__(self, layers, group_size: int | None = None, use_reentrant: bool = False):
-        self.layers = list(layers)
-        L = len(self.layers)
+    def __init__(self, layers, group_size: int | None = None, use_reentrant: bool = False, levels: int | None = None):
+        """`layers`: the modules of the chain.  The planning-only form `HierarchicalCheckpointManager(config,
+        num_layers)` (data_pipeline/trainer/distributed/activation_checkpoint.py:1466) builds the segment hierarchy
+        without modules: `segment_size` x 2^level layers per segment at each of `hierarchy_levels` levels."""
+        if isinstance(layers, ActivationCheckpointConfig):
+            cfg, L = layers, int(group_size or 0)
+            self.layers, group_size, levels = [], cfg.segment_size, cfg.hierarchy_levels
+            use_reentrant = cfg.use_reentrant
+        else:
+            self.layers = list(layers)
+            L = len(self.layers)
+        self.num_layers = L
         self.group_size = group_size or max(1, int(round(L ** 0.5)))
         self.use_reentrant = use_reentrant
         self.groups = [self.layers[i:i + self.group_size] for i in range(0, L, self.group_size)]
+        self.hierarchy_levels = max(1, levels or 2)
+        self.segments: dict[int, list] = {}
+        self.active_level = 0
+
+    def _level(self, level: int) -> list:
+        if level not in self.segments:
+            size = self.group_size * 2 ** level
+            base = sum(-(-self.num_layers // (self.group_size * 2 ** l)) for l in range(level))
+            self.segments[level] = [CheckpointSegment(base + i, a, min(a + size, self.num_layers), level)
+                                    for i, a in enumerate(range(0, self.num_layers, size))]
+        return self.segments[level]
+
+    def get_segment_for_layer(self, layer_idx: int, level: int | None = None) -> "CheckpointSegment":
+        level = self.active_level if level is None else level
+        if not 0 <= level < self.hierarchy_levels:
+            raise ValueError(f"level {level} outside [0, {self.hierarchy_levels})")
+        for seg in self._level(level):
+            if layer_idx in seg:
+                return seg
+        raise ValueError(f"no segment holds layer {layer_idx} at level {level}")
+
+    def should_checkpoint_layer(self, layer_idx: int) -> bool:
+        """True for the last layer of each segment at the active level: its output is what the forward keeps."""
+        return layer_idx == self.get_segment_for_layer(layer_idx).end_layer - 1
+
+    def adjust_level_for_memory(self, pressure: float | None = None) -> int:
+        """Finest segments above 95 % memory in use, the middle level above 85 %, the coarsest otherwise."""
+        p = MemoryProfiler().pressure() if pressure is None else pressure
+        self.active_level = 0 if p > 0.95 else min(1, self.hierarchy_levels - 1) if p > 0.85 else self.hierarchy_levels - 1
+        return self.active_level
 
     def kept_tensors(self) -> int:
         return len(self.groups) + self.group_size
@@ -466,6 +1019,17 @@ class OperationCheckpointContext:
         import threading
         return [c.op_name for c in cls._active.get(threading.get_ident(), [])]
 
+    @property
+    def checkpointing(self) -> bool:
+        return self.should_checkpoint()
+
+    @classmethod
+    def get_current(cls) -> "OperationCheckpointContext | None":
+        """The innermost context entered by this thread."""
+        import threading
+        stack = cls._active.get(threading.get_ident(), [])
+        return stack[-1] if stack else None
+
     def __enter__(self):
         import threading
         self._active.setdefault(threading.get_ident(), []).append(self)
@@ -597,3 +1161,32 @@ class OffloadTensorGroup:
         if key in self._handles:
             self.reload_all()
         return self._tensors[key]
+
+    # ---- tag-addressed storage and per-direction events (data_pipeline/trainer/distributed/activation_offload.py:324-355)
+    def push_tensor(self, tag, tensor: torch.Tensor) -> None:
+        self._tensors[tag] = tensor
+
+    def pop_tensor(self, tag) -> torch.Tensor:
+        if tag in self._handles:
+            self.reload_all()
+        return self._tensors.pop(tag)
+
+    def record_offload_event(self, stream) -> None:
+        if self._offload_event is not None:
+            self._offload_event.record(stream)
+
+    def wait_offload_event(self, stream) -> None:
+        if self._offload_event is not None:
+            stream.wait_event(self._offload_event)
+
+    def record_reload_event(self, stream) -> None:
+        if self._reload_event is not None:
+            self._reload_event.record(stream)
+
+    def wait_reload_event(self, stream) -> None:
+        if self._reload_event is not None:
+            stream.wait_event(self._reload_event)
+
+    def update_stats(self, tensor: torch.Tensor) -> None:
+        self.total_offload_bytes += tensor.numel() * tensor.element_size()
+        self.total_tensor_count += 1
