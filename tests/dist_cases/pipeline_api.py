@@ -52,6 +52,25 @@ def main():
             good = good and float(loss) > 0
         ok &= good
         print(f"rank {rank} {sched}: max grad diff {worst:.2e} loss {float(loss):.5f} ok={good}", flush=True)
+    # neighbour-addressed sends: activations go down the pipe, gradients come back up; ends are no-ops
+    from trainscale_b200.parallel.pipeline import P2PCommunicator
+    comm = P2PCommunicator(ctx)
+    good = comm.stage_id == rank and comm.prev_rank == (rank - 1 if rank else None) \
+        and comm.next_rank == (rank + 1 if rank < P - 1 else None)
+    act = torch.full((4, 3), float(rank))
+    sent = comm.send_activation_async(act, 0)
+    w, got = comm.recv_activation_async((4, 3), torch.float32, 0)
+    good &= (sent is None) == (rank == P - 1) and (w is None) == (rank == 0)
+    comm.synchronize_pending()
+    if w is not None:
+        good &= bool((got == rank - 1).all())
+    comm.send_grad_async(torch.full((2,), 10.0 + rank), 0)
+    w, got = comm.recv_grad_async(microbatch_id=0)
+    comm.synchronize_pending()
+    if w is not None:
+        good &= bool((got == 11.0 + rank).all())
+    ok &= bool(good)
+    print(f"rank {rank} neighbour p2p ok={bool(good)}", flush=True)
     flag = torch.tensor([0.0 if ok else 1.0])
     dist.all_reduce(flag)
     if rank == 0:

@@ -288,3 +288,96 @@ def test_preprocessed_dataset_select_and_stage_splits():
     assert len(sub) == 2 and int(sub[0]["input_ids"][0]) == 4
     st = StageConfig("s1", {"extra": SplitSpec("extra"), "train": SplitSpec("train")})
     assert list(st.all_splits()) == ["train", "extra"] and st.get_split("train") is st.train and st.get_split("nope") is None
+
+
+def test_registry_incremental_registration_and_reports():
+    from trainscale_b200.models.llama import build_model
+    from trainscale_b200.registry import (MODEL_REGISTRY, Capability, DependencyGraph, HardwareCapability, KernelPatcher,
+                                          ModelInfo, ModuleContract, RegistryValidator)
+    from trainscale_b200.registry.catalog import BaseModuleContract
+    cpu = HardwareCapability("cpu", (0, 0), 0, 0.0, frozenset())
+    b200 = HardwareCapability("b200", (10, 0), 148, 180.0, frozenset(Capability))
+    v = RegistryValidator(hardware=b200)
+    assert v.register(ModuleContract("gemm_torch")).is_ok()
+    assert v.register(ModuleContract("gemm_tcgen05", (Capability.TCGEN05,), fallback="gemm_torch")).is_ok()
+    assert v.register(ModuleContract("attn", (Capability.TCGEN05,), ("gemm_tcgen05",))).is_ok()
+    missing = v.register(ModuleContract("x", (), ("nope",)))
+    assert missing.is_err() and missing.error.missing_deps == ("nope",)
+    assert v.register(ModuleContract("attn")).error.reason == "duplicate_registration"
+    order = v.get_registration_order().unwrap()
+    assert order.index("gemm_tcgen05") < order.index("attn")
+    rep = v.get_capabilities_report()
+    assert rep["total_registered"] == 3 and rep["validation_failed"] == 0 and "tcgen05" in rep["hardware_capabilities"]
+    off_gpu = RegistryValidator(v.matrix, cpu)
+    rep = off_gpu.get_capabilities_report()
+    assert rep["available_kernels"] == ["gemm_torch"] and rep["validation_failed"] == 2
+    assert off_gpu.validate_contract(ModuleContract("needs_fp8", (Capability.FP8,))).is_err()
+    assert v.matrix.get_optimal_kernel("gemm_tcgen05", cpu).name == "gemm_torch"
+    assert v.matrix.get_optimal_kernel("gemm_tcgen05", b200).name == "gemm_tcgen05"
+    b = BaseModuleContract("b", (2, 1, 0), frozenset(), frozenset({Capability.FP8}))
+    assert b.version_string() == "2.1.0" and b.get_fallback() is None
+    assert v.matrix.register_kernel(b, ["gemm_torch"]).is_ok()
+    assert v.matrix.get_optimal_kernel("b", cpu).name == "gemm_torch" and "b" in v.matrix.get_all_kernels()
+    assert "b" in v.matrix.get_available_kernels(b200) and "b" not in v.matrix.get_available_kernels(cpu)
+
+    g = DependencyGraph()
+    g.add_module("a", {"b"})
+    assert g.validate_dependencies("a").error.missing_deps == ("b",)
+    g.add_module("b", {"a"})
+    assert g.topological_sort().is_err() and g.get_dependencies("a") == frozenset({"b"})
+    g.remove_module("b")
+    assert g.topological_sort().unwrap() == ["b", "a"] and g.validate_dependencies("a").is_err()
+
+    mc = ModuleContract("k", (Capability.FP8,), ("d",), "f")
+    assert mc.validate(cpu).is_err() and mc.validate(b200).is_ok() and mc.get_fallback() == "f"
+    assert mc.dependencies == frozenset({"d"}) and mc.hardware_requirements == frozenset({Capability.FP8})
+    assert ModelInfo.construct_model_name("Llama", "3.1", "8", instruct_tag="Instruct") == "Llama-3.1-8B-Instruct"
+    assert MODEL_REGISTRY["llama"].model_path == "meta-llama/llama"
+    stats = KernelPatcher().get_stats(build_model("tiny", dtype=torch.float32, device="cpu"))
+    assert stats["attention_total"] == stats["attention_patched"] > 0 and stats["mlp_total"] == stats["mlp_patched"] > 0
+
+    class Foreign(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.norm = nn.LayerNorm(8)
+
+    assert KernelPatcher().get_stats(Foreign()) == {**{k: 0 for k in stats}, "layernorm_total": 1}
+
+
+def test_attention_config_and_backend_capabilities():
+    from trainscale_b200.kernels import (AttentionBackend, AttentionMaskType, BackendCapabilities, FlashAttentionConfig,
+                                         FlexAttentionConfig)
+    c = FlashAttentionConfig(head_dim=64, num_heads=8, num_kv_heads=2)
+    assert c.scale == 0.125 and c.num_kv_groups == 4 and c.is_gqa and c.mask_type is AttentionMaskType.CAUSAL
+    assert FlashAttentionConfig(softmax_scale=0.5).scale == 0.5
+    assert FlashAttentionConfig(sliding_window=5).mask_type is AttentionMaskType.SLIDING_WINDOW
+    assert FlashAttentionConfig(sliding_window=5).window_size == 5
+    assert FlashAttentionConfig(causal=False).mask_type is AttentionMaskType.FULL
+    assert not FlashAttentionConfig(head_dim=64, num_heads=8).is_gqa
+    with pytest.raises(ValueError):
+        FlashAttentionConfig(num_heads=8, num_kv_heads=3)
+    with pytest.raises(ValueError):
+        FlashAttentionConfig().scale
+    caps = BackendCapabilities(AttentionBackend.TCGEN05_FLASH)
+    assert caps.has_flex_attention and caps.has_flash_attention_2 and not caps.has_triton
+    f = FlexAttentionConfig(num_attention_heads=8, num_key_value_heads=4, head_dim=64)
+    assert caps.select_optimal_backend(f) is AttentionBackend.TCGEN05_FLASH
+    assert caps.select_optimal_backend(FlexAttentionConfig(head_dim=96)) is AttentionBackend.REFERENCE
+    here = BackendCapabilities.detect()
+    if not torch.cuda.is_available():
+        assert here.cuda_capability is None and not here.supports_fp8 and not here.supports_bf16
+        assert here.select_optimal_backend(f) is AttentionBackend.REFERENCE
+    assert callable(here.flex_attention_fn) and callable(here.create_block_mask_fn)
+
+
+def test_activation_memory_manager_named_storage():
+    from trainscale_b200.parallel.pipeline import ActivationMemoryManager
+    m = ActivationMemoryManager()
+    a, b = torch.ones(4, 4), torch.zeros(2)
+    m.store_activation(0, "x", a)
+    m.store_activation(0, "y", b)
+    m.store_activation(1, "x", b)
+    assert m.retrieve_activation(0, "x") is a and m.retrieve_activation(5, "x") is None
+    assert m.current_memory_mb == pytest.approx((64 + 8 + 8) / 2 ** 20)
+    assert m.release_activation(0) == 2 and m.retrieve_activation(0, "x") is None
+    assert m.retrieve_activation(1, "x") is b and m.current_memory_mb == pytest.approx(8 / 2 ** 20)

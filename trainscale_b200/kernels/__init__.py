@@ -216,6 +216,39 @@ class FlashAttentionConfig:
     window_size: int | None = None
     softcap: float = 0.0
     dropout: float = 0.0                  # not supported by the kernel; must stay 0
+    head_dim: int | None = None
+    num_heads: int | None = None
+    num_kv_heads: int | None = None       # fewer than num_heads: grouped-query / multi-query attention
+    sliding_window: int | None = None     # the reference's name for window_size
+
+    def __post_init__(self):
+        if self.sliding_window is not None and self.window_size is None:
+            self.window_size = self.sliding_window
+        self.sliding_window = self.window_size
+        if self.num_heads and self.num_kv_heads and self.num_heads % self.num_kv_heads:
+            raise ValueError("num_heads must be divisible by num_kv_heads")
+
+    @property
+    def scale(self) -> float:
+        """softmax_scale, or 1 / sqrt(head_dim) (data_pipeline/trainer/kernels/flash_attention.py:98-100)."""
+        if self.softmax_scale:
+            return self.softmax_scale
+        if not self.head_dim:
+            raise ValueError("scale needs softmax_scale or head_dim")
+        return 1.0 / math.sqrt(self.head_dim)
+
+    @property
+    def num_kv_groups(self) -> int:
+        return 1 if not (self.num_heads and self.num_kv_heads) else self.num_heads // self.num_kv_heads
+
+    @property
+    def is_gqa(self) -> bool:
+        return bool(self.num_heads and self.num_kv_heads and self.num_kv_heads < self.num_heads)
+
+    @property
+    def mask_type(self) -> "AttentionMaskType":
+        return (AttentionMaskType.SLIDING_WINDOW if self.window_size else
+                AttentionMaskType.CAUSAL if self.causal else AttentionMaskType.FULL)
 
 
 @dataclass
@@ -241,6 +274,7 @@ class FlexAttentionConfig(FlashAttentionConfig):
     deterministic: bool = True
 
     def __post_init__(self):
+        super().__post_init__()
         if self.num_attention_heads and self.num_key_value_heads and \
                 self.num_attention_heads % self.num_key_value_heads:
             raise ValueError("num_attention_heads must be divisible by num_key_value_heads")
@@ -272,6 +306,54 @@ class BackendCapabilities:
     @classmethod
     def detect(cls) -> "BackendCapabilities":
         return cls(AttentionBackend.TCGEN05_FLASH if supports_tcgen05() else AttentionBackend.REFERENCE)
+
+    # ---- the reference's probes (data_pipeline/trainer/kernels/flex_attention.py:199-258).  The `has_*` names
+    # describe CAPABILITIES of this framework's own kernels; no flash-attn, Triton or xformers package is on any path.
+    @property
+    def has_flex_attention(self) -> bool:
+        """Block-mask attention (`kernels.flex`) is always present: tcgen05 kernels on sm_100, fp32 maths elsewhere."""
+        return True
+
+    @property
+    def has_flash_attention_2(self) -> bool:
+        return self.backend is AttentionBackend.TCGEN05_FLASH
+
+    has_flash_attention_3 = has_flash_attention_2
+
+    @property
+    def has_triton(self) -> bool:
+        return False
+
+    @property
+    def cuda_capability(self) -> tuple | None:
+        return torch.cuda.get_device_capability() if torch.cuda.is_available() else None
+
+    @property
+    def supports_fp8(self) -> bool:
+        cap = self.cuda_capability
+        return cap is not None and cap >= (8, 9)
+
+    @property
+    def supports_bf16(self) -> bool:
+        cap = self.cuda_capability
+        return cap is not None and cap >= (8, 0)
+
+    @property
+    def flex_attention_fn(self):
+        from .flex import flex_attention_forward
+        return flex_attention_forward
+
+    @property
+    def create_block_mask_fn(self):
+        from .flex import create_block_mask
+        return create_block_mask
+
+    def select_optimal_backend(self, config=None) -> AttentionBackend:
+        """The tcgen05 flash kernels when the device has them and the head dimension is one they are built for
+        (soft-capping, windows, GQA and packed documents are all switches of the same kernels); fp32 maths otherwise."""
+        hd = getattr(config, "head_dim", None)
+        ok = self.backend is AttentionBackend.TCGEN05_FLASH and (hd is None or hd in self.head_dims)
+        return AttentionBackend.TCGEN05_FLASH if ok else AttentionBackend.REFERENCE
 
 
 def is_flash_attn_available() -> bool:

@@ -258,6 +258,36 @@ class ActivationMemoryManager:
     def has(self, key: tuple) -> bool:
         return key in self._stash
 
+    # ---- per-micro-batch, named storage (data_pipeline/trainer/distributed/zbpp.py:458-495)
+    def store_activation(self, microbatch_id: int, name: str, tensor: torch.Tensor, limit_bytes: int | None = None) -> None:
+        """Keep `tensor` under (microbatch_id, name).  When the stash would exceed `limit_bytes` the tensor is kept on
+        the host instead (pinned when it comes from a GPU) and comes back in `retrieve_activation`."""
+        nb = self._nbytes(tensor)
+        if limit_bytes is not None and self._cur + nb > limit_bytes and tensor.is_cuda:
+            host = torch.empty(tensor.shape, dtype=tensor.dtype, pin_memory=True)
+            host.copy_(tensor, non_blocking=True)
+            tensor = (host, tensor.device, torch.cuda.current_stream().record_event())
+            nb = 0                                         # host copies do not count against the device stash
+        self._stash[("mb", microbatch_id, name)] = tensor
+        self._cur += nb
+        self._peak = max(self._peak, self._cur)
+
+    def retrieve_activation(self, microbatch_id: int, name: str):
+        v = self._stash.get(("mb", microbatch_id, name))
+        if isinstance(v, tuple) and len(v) == 3 and torch.is_tensor(v[0]):
+            host, dev, ev = v
+            ev.synchronize()
+            return host.to(dev, non_blocking=True)
+        return v
+
+    def release_activation(self, microbatch_id: int) -> int:
+        """Drop everything stored for the micro-batch (after its weight-gradient pass); returns how many entries."""
+        keys = [k for k in self._stash if len(k) == 3 and k[0] == "mb" and k[1] == microbatch_id]
+        for k in keys:
+            v = self._stash.pop(k)
+            self._cur -= self._nbytes(v) if torch.is_tensor(v) else 0
+        return len(keys)
+
     def clear(self) -> None:
         self._stash.clear()
         self._cur = 0
@@ -345,6 +375,44 @@ class P2PCommunicator:
         for w, _ in self._pending:
             w.wait()
         self._pending.clear()
+
+    # ---- neighbour-addressed form (data_pipeline/trainer/distributed/zbpp.py:691-830): the peer is implied by the
+    # direction, a missing neighbour (first / last stage) makes the call a no-op that returns None
+    @property
+    def stage_id(self) -> int:
+        return self.ctx.pipeline_parallel_rank
+
+    @property
+    def prev_rank(self) -> int | None:
+        return self.ctx.get_prev_rank()
+
+    @property
+    def next_rank(self) -> int | None:
+        return self.ctx.get_next_rank()
+
+    def send_activation_async(self, tensor: torch.Tensor, microbatch_id: int = 0):
+        return None if self.next_rank is None else self.send_async(tensor, self.next_rank, "act")
+
+    def recv_activation_async(self, shape=None, dtype: torch.dtype | None = None, microbatch_id: int = 0):
+        """(work, buffer).  The shape travels in the link's header (once with `static_shapes`); `shape` / `dtype`, when
+        given, are checked against it."""
+        return (None, torch.empty(0)) if self.prev_rank is None else self._recv_checked(self.prev_rank, "act", shape, dtype)
+
+    def _recv_checked(self, src: int, kind: str, shape, dtype):
+        buf, w = self.recv_async(src, kind)
+        if (shape is not None and tuple(shape) != tuple(buf.shape)) or (dtype is not None and dtype != buf.dtype):
+            raise ValueError(f"expected {tuple(shape) if shape is not None else '?'} {dtype} from rank {src}, "
+                             f"the sender announced {tuple(buf.shape)} {buf.dtype}")
+        self._pending.append((w, buf))
+        return w, buf
+
+    def send_grad_async(self, grad: torch.Tensor, microbatch_id: int = 0):
+        return None if self.prev_rank is None else self.send_async(grad, self.prev_rank, "grad")
+
+    def recv_grad_async(self, shape=None, dtype: torch.dtype | None = None, microbatch_id: int = 0):
+        return (None, torch.empty(0)) if self.next_rank is None else self._recv_checked(self.next_rank, "grad", shape, dtype)
+
+    synchronize_pending = wait_all
 
 
 class GradientBucket:

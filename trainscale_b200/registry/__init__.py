@@ -70,19 +70,78 @@ class ModuleContract:
     depends_on: tuple[str, ...] = ()
     fallback: str | None = None
     factory: Callable | None = None
+    version: tuple = (1, 0, 0)
 
     def satisfied_by(self, hw: HardwareCapability) -> bool:
         return all(hw.has(c) for c in self.requires)
+
+    # ---- the protocol of data_pipeline/trainer/registry/__init__.py:252-300
+    @property
+    def dependencies(self) -> frozenset:
+        return frozenset(self.depends_on)
+
+    @property
+    def hardware_requirements(self) -> frozenset:
+        return frozenset(self.requires)
+
+    def validate(self, hardware: "HardwareCapability | None" = None):
+        """Ok(None) when the device has every required capability, else Err(HardwareError) naming what is missing."""
+        from ..core.types import Err, Ok
+        from .catalog import HardwareError
+        hw = hardware if hardware is not None else detect_capabilities()
+        missing = tuple(c for c in self.requires if not hw.has(c))
+        if missing:
+            return Err(HardwareError(f"{self.name} needs {[c.value for c in missing]}", self.name, required=missing,
+                                     available=tuple(hw.capabilities)))
+        return Ok(None)
+
+    def get_fallback(self) -> str | None:
+        """NAME of the contract to use when this one's requirements are not met (the matrix resolves names)."""
+        return self.fallback
 
 
 class DependencyGraph:
     def __init__(self):
         self.edges: dict[str, set[str]] = {}
+        self.declared: set[str] = set()       # nodes added themselves, as opposed to only named as a dependency
 
     def add(self, node: str, deps: Iterable[str] = ()):
+        deps = list(deps)
+        self.declared.add(node)
         self.edges.setdefault(node, set()).update(deps)
         for d in deps:
             self.edges.setdefault(d, set())
+
+    # ---- data_pipeline/trainer/registry/__init__.py:394-525
+    add_module = add
+
+    def remove_module(self, name: str) -> None:
+        """Forget the module's own edges; it stays as a (now undeclared) node while others still depend on it."""
+        self.declared.discard(name)
+        if any(name in d for n, d in self.edges.items() if n != name):
+            self.edges[name] = set()
+        else:
+            self.edges.pop(name, None)
+
+    def get_dependencies(self, name: str) -> frozenset:
+        return frozenset(self.edges.get(name, ()))
+
+    def topological_sort(self):
+        """Ok(order with every module after its dependencies) or Err(DependencyError with the first cycle)."""
+        from ..core.types import Err, Ok
+        from .catalog import DependencyError
+        cycles = self.find_cycles()
+        if cycles:
+            return Err(DependencyError(f"circular dependencies: {sorted(cycles[0])}", cycle_path=tuple(sorted(cycles[0]))))
+        return Ok(self.topological_order())
+
+    def validate_dependencies(self, name: str):
+        from ..core.types import Err, Ok
+        from .catalog import DependencyError
+        missing = tuple(sorted(d for d in self.edges.get(name, ()) if d not in self.declared))
+        if missing:
+            return Err(DependencyError(f"missing dependencies of {name!r}: {list(missing)}", name, missing_deps=missing))
+        return Ok(None)
 
     def strongly_connected_components(self) -> list[list[str]]:
         """Tarjan's algorithm (iterative)."""
@@ -170,6 +229,37 @@ class KernelCapabilityMatrix:
     def available(self, hw: HardwareCapability) -> dict[str, bool]:
         return {n: c.satisfied_by(hw) for n, c in self.contracts.items()}
 
+    # ---- data_pipeline/trainer/registry/__init__.py:541-610
+    def register_kernel(self, contract, fallback_chain: list[str] | None = None):
+        """Ok(None), or Err(RegistrationError) when the name is taken.  `contract`: a ModuleContract or a
+        catalog.BaseModuleContract; `fallback_chain`: names tried in order when its requirements are not met."""
+        from ..core.types import Err, Ok
+        from .catalog import RegistrationError
+        c = contract.to_contract() if hasattr(contract, "to_contract") else contract
+        if c.name in self.contracts:
+            return Err(RegistrationError(f"kernel {c.name!r} already registered", c.name, reason="duplicate_registration"))
+        self.contracts[c.name] = c
+        if fallback_chain:
+            self.__dict__.setdefault("chains", {})[c.name] = list(fallback_chain)
+        return Ok(None)
+
+    def get_optimal_kernel(self, kernel_name: str, hw: HardwareCapability | None = None) -> "ModuleContract | None":
+        """The first usable contract among the named one, its explicit fallback chain, and its `fallback` links."""
+        hw = hw if hw is not None else detect_capabilities()
+        for name in [kernel_name] + self.__dict__.get("chains", {}).get(kernel_name, []):
+            c = self.contracts.get(name)
+            if c is not None and c.satisfied_by(hw):
+                return c
+        got = self.resolve(kernel_name, hw)
+        return self.contracts[got] if got else None
+
+    def get_all_kernels(self) -> dict:
+        return dict(self.contracts)
+
+    def get_available_kernels(self, hw: HardwareCapability | None = None) -> list[str]:
+        hw = hw if hw is not None else detect_capabilities()
+        return [n for n, c in self.contracts.items() if c.satisfied_by(hw)]
+
 
 DEFAULT_CONTRACTS = [
     ModuleContract("gemm_tcgen05", (Capability.TCGEN05, Capability.TMA), fallback="gemm_torch"),
@@ -183,8 +273,63 @@ DEFAULT_CONTRACTS = [
 
 
 class RegistryValidator:
-    def __init__(self, matrix: KernelCapabilityMatrix):
-        self.matrix = matrix
+    def __init__(self, matrix: KernelCapabilityMatrix | None = None, hardware: HardwareCapability | None = None):
+        self.matrix = matrix if matrix is not None else KernelCapabilityMatrix()
+        self.hardware = hardware                      # None: probed when needed
+        self.graph = DependencyGraph()
+        for c in self.matrix.contracts.values():
+            self.graph.add(c.name, c.depends_on)
+
+    def _hw(self) -> HardwareCapability:
+        return self.hardware if self.hardware is not None else detect_capabilities()
+
+    # ---- incremental registration (data_pipeline/trainer/registry/__init__.py:630-775)
+    def validate_contract(self, contract):
+        """Hardware first, then that every dependency is registered, then that no cycle would appear."""
+        from ..core.types import Err, Ok
+        from .catalog import DependencyError
+        c = contract.to_contract() if hasattr(contract, "to_contract") else contract
+        r = c.validate(self._hw())
+        if r.is_err():
+            return r
+        missing = tuple(sorted(d for d in c.depends_on if d not in self.matrix.contracts))
+        if missing:
+            return Err(DependencyError(f"missing dependencies: {list(missing)}", c.name, missing_deps=missing))
+        before = {n: set(d) for n, d in self.graph.edges.items()}, set(self.graph.declared)
+        self.graph.add(c.name, c.depends_on)
+        cycles = self.graph.find_cycles()
+        self.graph.edges, self.graph.declared = before
+        if cycles:
+            return Err(DependencyError(f"would introduce a circular dependency: {sorted(cycles[0])}", c.name,
+                                       cycle_path=tuple(sorted(cycles[0]))))
+        return Ok(None)
+
+    def register(self, contract, *, skip_validation: bool = False):
+        from ..core.types import Ok
+        c = contract.to_contract() if hasattr(contract, "to_contract") else contract
+        if not skip_validation:
+            r = self.validate_contract(c)
+            if r.is_err():
+                return r
+        r = self.matrix.register_kernel(c)
+        if r.is_err():
+            return r
+        self.graph.add(c.name, c.depends_on)
+        return Ok(None)
+
+    def get_registration_order(self):
+        return self.graph.topological_sort()
+
+    def validate_all(self) -> dict:
+        hw = self._hw()
+        return {n: c.validate(hw) for n, c in self.matrix.contracts.items()}
+
+    def get_capabilities_report(self) -> dict:
+        hw, results = self._hw(), self.validate_all()
+        return {"hardware_capabilities": sorted(getattr(c, "value", str(c)) for c in hw.capabilities),
+                "available_kernels": self.matrix.get_available_kernels(hw), "total_registered": len(results),
+                "validation_passed": sum(r.is_ok() for r in results.values()),
+                "validation_failed": sum(r.is_err() for r in results.values())}
 
     def validate(self) -> list[str]:
         problems = []
@@ -213,6 +358,19 @@ class ModelInfo:
     rope: str = "default"
     supported: bool = True          # convertible to the framework decoder
     notes: str = ""
+
+    @classmethod
+    def construct_model_name(cls, base_name: str, version: str, size: str, quant_type=None,
+                             instruct_tag: str | None = None) -> str:
+        """Checkpoint name from its parts, e.g. ("Llama", "3.1", "8", instruct_tag="Instruct") -> Llama-3.1-8B-Instruct
+        (the rule of `catalog.CheckpointInfo`, data_pipeline/trainer/registry/__init__.py:841-858)."""
+        from .catalog import CheckpointInfo, QuantType
+        return CheckpointInfo.construct_model_name(base_name, version, size, quant_type or QuantType.NONE, instruct_tag)
+
+    @property
+    def model_path(self) -> str:
+        """Hub prefix of the family: "<org>/<family>"; single checkpoints are `catalog.CheckpointInfo.model_path`."""
+        return f"{self.org}/{self.family}"
 
 
 MODEL_REGISTRY: dict[str, ModelInfo] = {}
@@ -305,6 +463,27 @@ class KernelPatcher:
                 not any(k.endswith("o_proj.bias") for k in model.state_dict()):
             return convert_hf_llama(model, dtype, device)
         return model
+
+
+def _patch_stats(model) -> dict:
+    """How many norm / MLP / attention / rotary modules of `model` run on the framework's ops, and how many there are.
+    The framework decoder counts as patched throughout; for other models a module counts once an `auto_patch_*`
+    function has rewired it (data_pipeline/trainer/registry/__init__.py:1420-1450)."""
+    from ..models.llama import LlamaForCausalLM
+    native = isinstance(model, LlamaForCausalLM)
+    stats = {f"{k}_{w}": 0 for k in ("layernorm", "mlp", "attention", "rope") for w in ("patched", "total")}
+    for _, m in model.named_modules():
+        cls = type(m).__name__
+        kind = ("layernorm" if cls.endswith(("RMSNorm", "LayerNorm")) else "mlp" if cls.endswith(("MLP", "MoE")) else
+                "attention" if cls.endswith("Attention") else "rope" if cls.endswith("RotaryEmbedding") else None)
+        if kind is None:
+            continue
+        stats[f"{kind}_total"] += 1
+        stats[f"{kind}_patched"] += bool(native or getattr(m, "_ts_patched", False))
+    return stats
+
+
+KernelPatcher.get_stats = lambda self, model: _patch_stats(model)
 
 
 def patch_model(model, **kw):

@@ -307,6 +307,12 @@ class BaseModuleContract:
                                               missing_deps=missing))
         return errors
 
+    def get_fallback(self) -> Optional["BaseModuleContract"]:
+        return self._fallback
+
+    def version_string(self) -> str:
+        return ".".join(str(v) for v in self._version)
+
     def to_contract(self):
         from . import ModuleContract
         return ModuleContract(self._name, tuple(self._hardware_requirements), tuple(sorted(self._dependencies)),
