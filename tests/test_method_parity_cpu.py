@@ -381,3 +381,144 @@ def test_activation_memory_manager_named_storage():
     assert m.current_memory_mb == pytest.approx((64 + 8 + 8) / 2 ** 20)
     assert m.release_activation(0) == 2 and m.retrieve_activation(0, "x") is None
     assert m.retrieve_activation(1, "x") is b and m.current_memory_mb == pytest.approx(8 / 2 ** 20)
+
+
+def test_base_optimizer_grad_scale_step_count_and_close():
+    from trainscale_b200.optim import BaseOptimizer, OptimizerState
+
+    class SGD(BaseOptimizer):
+        def __init__(self, params, lr=0.1):
+            super().__init__(params, {"lr": lr})
+        def _update(self, p, grad, state, group):
+            p.add_(grad, alpha=-group["lr"])
+
+    w = nn.Parameter(torch.ones(3))
+    o = SGD([w])
+    w.grad = torch.full((3,), 4.0)
+    o.set_grad_scale(4.0)                                  # the loss was scaled by 4: the true gradient is 1
+    o.step()
+    assert torch.allclose(w.data, torch.full((3,), 0.9)) and o.step_count == 1 and o.get_grad_scale() == 4.0
+    assert o.get_metrics() is o.metrics
+    w.grad = torch.full((3,), 10.0)
+    before = o.clip_grad_norm_(1.0)
+    assert float(before) == pytest.approx(300 ** 0.5) and float(w.grad.norm()) == pytest.approx(1.0, abs=1e-5)
+    o.close()
+    assert o.lifecycle is OptimizerState.CLOSED and len(o.state) == 0
+    with pytest.raises(RuntimeError):
+        o.step()
+    with pytest.raises(ValueError):
+        o.set_grad_scale(0.0)
+
+
+def test_adafactor_footprint_and_state_round_trip():
+    from trainscale_b200.optim import AdaFactor, AdaFactorState
+    w, b = nn.Parameter(torch.randn(8, 4)), nn.Parameter(torch.randn(4))
+    o = AdaFactor([w, b])
+    w.grad, b.grad = torch.randn(8, 4), torch.randn(4)
+    o.step()
+    fp = o.memory_footprint()
+    assert fp["state_bytes"] == (8 + 4 + 4) * 4 and fp["total_bytes"] == fp["state_bytes"] + fp["buffer_bytes"]
+    ps = o.profiling_stats
+    assert ps.num_factorized_params == 1 and ps.num_full_params == 1 and ps.total_step_time_ns > 0
+    s = AdaFactorState((8, 4), "cpu", torch.float32, True, True).initialize()
+    s.step = 3
+    s.exp_avg.fill_(2.0)
+    back = AdaFactorState.from_dict(s.to_dict())
+    assert back.step == 3 and back.factored and back.is_initialized and torch.equal(back.exp_avg, s.exp_avg)
+    assert back.exp_avg is not s.exp_avg and back.memory_footprint() == s.memory_bytes() == (8 * 4 + 8 + 4) * 4
+
+
+def test_cp_balancers_stateless_forms_and_ring_step():
+    from trainscale_b200.parallel.cp import (BalancerStrategy, HeadTailBalancer, PTRRBalancer, RingCommunicator,
+                                             ZigZagBalancer)
+    x = torch.arange(32).view(1, 32)
+    for cls in (HeadTailBalancer, ZigZagBalancer, PTRRBalancer):
+        b = cls(4, 0)
+        parts = [b.partition(x, r, 4, 1) for r in range(4)]
+        assert torch.equal(b.gather(parts, 4, 1), x)
+        for r in range(4):                                  # global positions ARE the values of arange at those places
+            assert torch.equal(b.compute_global_positions(8, r, 4, 32), parts[r][0])
+        with pytest.raises(ValueError):
+            b.compute_global_positions(7, 0, 4, 32)
+    assert HeadTailBalancer(4, 0).compute_global_positions(8, 1, 4).tolist() == [4, 5, 6, 7, 24, 25, 26, 27]
+    st = BalancerStrategy("zigzag")
+    assert torch.equal(st.gather([st.partition(x, r, 4, 1) for r in range(4)], 4, 1), x)
+    assert st.compute_global_positions(8, 1, 4, 32).tolist() == [1, 6, 9, 14, 17, 22, 25, 30]
+    ring = RingCommunicator()
+    k, v = torch.randn(2, 3), torch.randn(2, 3)
+    with ring.ring_step_context(k, v) as (kn, vn):
+        pass
+    assert torch.equal(kn, k) and torch.equal(vn, v)        # a ring of one rank hands back its own blocks
+
+
+def test_fp8_scale_manager_and_linear_members():
+    from trainscale_b200.kernels import FP8Config, FP8Linear, FP8ScaleManager
+    lin = nn.Linear(256, 128)
+    m = FP8Linear.from_linear(lin)
+    x = torch.randn(4, 256)
+    assert torch.allclose(m(x), lin(x), atol=1e-4) and (m.in_features, m.out_features) == (256, 128)
+    q, sc = m.quantize_weight(lin.weight.data)
+    assert q.dtype == torch.float8_e4m3fn and tuple(sc.shape) == (1, 2)
+    with pytest.raises(ValueError):
+        m.quantize_weight(torch.zeros(3, 3))
+    mgr = FP8ScaleManager(FP8Config(amax_history_len=4))
+    s, si = mgr.update_and_get_scale(torch.tensor([1.0, -2.0]), "act")
+    assert float(s) == pytest.approx(2 / 448) and float(si) == pytest.approx(224.0)
+    mgr.step()
+    s, _ = mgr.update_and_get_scale(torch.tensor([0.5]), "act")
+    assert float(s) == pytest.approx(2 / 448)                # the history still holds the earlier amax of 2
+    assert mgr.get_meta("act") is mgr.get_meta("act")
+    assert FP8Config().forward_spec.max_val == 448.0 and FP8Config().backward_spec.max_val == 57344.0
+
+
+def test_function_classes_expose_forward_backward_pair():
+    import types
+    from trainscale_b200.kernels import FusedRoPEQKFunction, RMSLayerNormFunction, RoPEConfig, RoPEFrequencyCache
+    x, w = torch.randn(2, 5, 16), torch.randn(16)
+    ctx = types.SimpleNamespace()
+    y = RMSLayerNormFunction.forward(ctx, x, w, 1e-6, True)
+    gx, gw, g_eps, g_flag = RMSLayerNormFunction.backward(ctx, torch.ones_like(y))
+    xr, wr = x.clone().requires_grad_(True), w.clone().requires_grad_(True)
+    RMSLayerNormFunction.apply(xr, wr, 1e-6, True).sum().backward()
+    assert torch.allclose(gx, xr.grad) and torch.allclose(gw, wr.grad) and g_eps is None and g_flag is None
+
+    class Mine(torch.autograd.Function):
+        @staticmethod
+        def forward(ctx, a, b):
+            return RMSLayerNormFunction.forward(ctx, a, b)
+        @staticmethod
+        def backward(ctx, g):
+            return RMSLayerNormFunction.backward(ctx, g)
+
+    x2 = x.clone().requires_grad_(True)
+    Mine.apply(x2, w).sum().backward()
+    assert torch.allclose(x2.grad, xr.grad)
+    cos, sin = RoPEFrequencyCache.get_freqs(RoPEConfig(dim=8), 5, "cpu", torch.float32)
+    assert cos.shape == (5, 4)
+    q, k = torch.randn(1, 5, 2, 8), torch.randn(1, 5, 2, 8)
+    ctx = types.SimpleNamespace()
+    q2, k2 = FusedRoPEQKFunction.forward(ctx, q, k, cos, sin)
+    grads = FusedRoPEQKFunction.backward(ctx, torch.ones_like(q2), torch.ones_like(k2))
+    assert grads[0].shape == q.shape and grads[1].shape == k.shape
+    # rotation preserves norms, and so does its transpose applied to the gradient
+    assert torch.allclose(q2.norm(dim=-1), q.norm(dim=-1), atol=1e-5)
+    RoPEFrequencyCache.clear_cache()
+    assert len(RoPEFrequencyCache._shared._cache) == 0
+
+
+def test_distributed_metric_buffer_local_views():
+    from trainscale_b200.metrics import DistributedMetricBuffer
+    b = DistributedMetricBuffer()
+    b.add("loss", 1.0)
+    b.add("loss", torch.tensor(3.0))
+    b.add("acc", 0.5)
+    assert b.counts() == {"loss": 2, "acc": 1} and b.local_sums() == {"loss": 4.0, "acc": 0.5}
+    assert b.local_means() == {"loss": 2.0, "acc": 0.5} and b.reduce_all() == {"loss": 2.0, "acc": 0.5}
+    s = DistributedMetricBuffer("sum")
+    s.add("tokens", 5)
+    s.add("tokens", 7)
+    assert s.reduce_all() == {"tokens": 12.0}
+    b.clear()
+    assert b.counts() == {} and b.reduce_all() == {}
+    with pytest.raises(ValueError):
+        DistributedMetricBuffer("max")

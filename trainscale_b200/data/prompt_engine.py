@@ -179,6 +179,23 @@ class _Encoder:
     def apply_chat_template(self, messages: list[dict], add_generation_prompt=False) -> str:
         return self.tok.apply_chat_template(messages, add_generation_prompt)
 
+    # ---- small accessors (data_pipeline/preprocessing/prompt_engine.py:_Encoder)
+    pad_token_id = property(lambda self: self.tok.pad_token_id)
+    eos_token_id = property(lambda self: self.tok.eos_token_id)
+    eos_token = property(lambda self: getattr(self.tok.tokenizer, "eos_token", None) or "")
+    bos_token = property(lambda self: getattr(self.tok.tokenizer, "bos_token", None) or "")
+
+    def encode(self, text: str, add_special_tokens: bool = False) -> list[int]:
+        return self.tok.encode_raw(text, add_special_tokens=add_special_tokens)
+
+    def token_count(self, text: str) -> int:
+        return len(self.ids(text))
+
+    def encode_padded(self, text: str, max_length: int | None = None) -> tuple[list[int], list[int]]:
+        """(input_ids, attention_mask), truncated and padded to `max_length`."""
+        ids, mask, _ = self.finish(self.ids(text), None, max_length, pad=True)
+        return ids, mask
+
 
 # ------------------------------------------------------------------------------------------------ packing
 def _greedy_pack(lengths: Sequence[int], capacity: int, max_per_pack: int = 0) -> list[list[int]]:

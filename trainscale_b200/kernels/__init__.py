@@ -523,6 +523,23 @@ class RoPEFrequencyCache:
             self._cache[key] = cur
         return cur
 
+    # ---- class-level form (data_pipeline/trainer/kernels/rope_kernels.py:116-143): one shared cache, tables cut to
+    # `seq_len` rows and cast to `dtype`
+    _shared: "RoPEFrequencyCache | None" = None
+
+    @classmethod
+    def get_freqs(cls, config: RoPEConfig, seq_len: int, device=None, dtype: torch.dtype | None = None):
+        if cls._shared is None:
+            cls._shared = cls()
+        cos, sin = cls._shared.get(config, seq_len, device)
+        cos, sin = cos[:seq_len], sin[:seq_len]
+        return (cos.to(dtype), sin.to(dtype)) if dtype is not None else (cos, sin)
+
+    @classmethod
+    def clear_cache(cls) -> None:
+        if cls._shared is not None:
+            cls._shared._cache.clear()
+
 
 def fast_rope_embedding(q, k, cos, sin, positions=None, interleaved: bool = False):
     """q [B, S, Hq, D], k [B, S, Hkv, D], tables [max_pos, D/2] -> rotated (q, k)."""
@@ -671,6 +688,19 @@ class FP8Config:
     block_size: int = 128
     amax_history_len: int = 16
     margin: int = 0
+    forward_format: FP8Format = FP8Format.E4M3        # activations and weights: more mantissa
+    backward_format: FP8Format = FP8Format.E5M2       # gradients: more range
+    scale_update_interval: int = 1
+
+    @property
+    def forward_spec(self):
+        from .compat import get_fp8_spec
+        return get_fp8_spec(self.forward_format)
+
+    @property
+    def backward_spec(self):
+        from .compat import get_fp8_spec
+        return get_fp8_spec(self.backward_format)
 
 
 def row_quantize_fp8(x2):
@@ -719,6 +749,27 @@ class FP8ScaleManager:
         amax = max(h) if h else 1.0
         return (self.FMAX[self.config.format] / (2 ** self.config.margin)) / max(amax, 1e-12)
 
+    # ---- tensor-valued state per name (data_pipeline/trainer/kernels/fp8_kernels.py:170-196): the scale stays on the
+    # tensor's device, so nothing is read back to the host in the training loop
+    def get_meta(self, name: str, fp8_format: FP8Format = FP8Format.E4M3, device=None):
+        from .compat import FP8TensorMeta, get_fp8_spec
+        metas = self.__dict__.setdefault("_metas", {})
+        if name not in metas:
+            metas[name] = FP8TensorMeta(get_fp8_spec(fp8_format), device, self.config.amax_history_len)
+        return metas[name]
+
+    def update_and_get_scale(self, tensor: torch.Tensor, name: str, fp8_format: FP8Format = FP8Format.E4M3):
+        """Record the tensor's amax and return (scale, 1 / scale) with scale = amax_history.max() / fmax * 2^margin, so
+        that tensor / scale fills the format's range; the scale is refreshed every `scale_update_interval` steps."""
+        meta = self.get_meta(name, fp8_format, tensor.device)
+        meta.update_amax(tensor.detach().abs().max())
+        if self.__dict__.get("_steps", 0) % max(1, self.config.scale_update_interval) == 0:
+            meta.compute_scale(self.config.margin)
+        return meta.scale, meta.scale_inv
+
+    def step(self) -> None:
+        self.__dict__["_steps"] = self.__dict__.get("_steps", 0) + 1
+
 
 class FP8Linear(nn.Module):
     """Linear layer whose forward and input-gradient products run on the block-scaled fp8 kernel (bf16 CUDA inputs
@@ -734,6 +785,39 @@ class FP8Linear(nn.Module):
         y = _fp8.fp8_linear(x, self.weight) if _fp8.available(x) and self.weight.shape[0] % 8 == 0 \
             else _gemm.linear(x, self.weight)
         return y if self.bias is None else y + self.bias
+
+    @property
+    def in_features(self) -> int:
+        return self.weight.shape[1]
+
+    @property
+    def out_features(self) -> int:
+        return self.weight.shape[0]
+
+    @classmethod
+    def from_linear(cls, linear: nn.Linear, block_size: int = 128) -> "FP8Linear":
+        """The same weights (and bias) in a layer whose products run in fp8.  The parameters stay in the source dtype
+        and trainable: quantisation happens per call, on the current values."""
+        if block_size != 128:
+            raise ValueError("the block-scaled fp8 GEMM uses 128 x 128 weight blocks")
+        m = cls(linear.in_features, linear.out_features, linear.bias is not None, linear.weight.dtype, linear.weight.device)
+        m.quantize_weight(linear.weight.data)
+        if linear.bias is not None:
+            m.bias.data.copy_(linear.bias.data)
+        return m
+
+    def quantize_weight(self, weight: torch.Tensor):
+        """Load `weight` and return its block-scaled image (e4m3 values, one fp32 scale per 128 x 128 block) - what the
+        GEMM will see; useful to inspect the quantisation error."""
+        if tuple(weight.shape) != tuple(self.weight.shape):
+            raise ValueError(f"weight shape {tuple(weight.shape)} != {tuple(self.weight.shape)}")
+        with torch.no_grad():
+            self.weight.copy_(weight)
+        from ..quantization import block_quantize_fp8 as _bq
+        return _bq(self.weight.detach(), 128)
+
+    def extra_repr(self) -> str:
+        return f"in={self.in_features}, out={self.out_features}, bias={self.bias is not None}"
 
 
 # ------------------------------------------------------------------------------------------------ flex-style front end

@@ -26,6 +26,34 @@ from ..ops import rope as _rope
 DEFAULT_EPS_RMS, DEFAULT_EPS_LN, MAX_FUSED_SIZE = 1e-6, 1e-5, 65536
 
 
+# ------------------------------------------------------------------------------------------------ forward / backward pair
+class _FunctionPair:
+    """Gives an `apply`-style adapter the `forward(ctx, ...)` / `backward(ctx, *grad_outputs)` statics of a
+    `torch.autograd.Function`, for code that embeds the op in its own autograd function.  `forward` runs `apply` on
+    detached copies of the tensor arguments with gradients enabled and keeps that small graph on `ctx`; `backward`
+    differentiates it and returns one gradient (or None) per positional argument.  `ctx` may be any object."""
+
+    @classmethod
+    def forward(cls, ctx, *args, **kwargs):
+        leaves = [a.detach().requires_grad_(True) if torch.is_tensor(a) and a.is_floating_point() else a for a in args]
+        with torch.enable_grad():
+            out = cls.apply(*leaves, **kwargs)
+        ctx._ts_leaves, ctx._ts_out = leaves, out
+        if torch.is_tensor(out):
+            return out.detach()
+        return tuple(o.detach() if torch.is_tensor(o) else o for o in out)
+
+    @classmethod
+    def backward(cls, ctx, *grad_outputs):
+        out = ctx._ts_out
+        outs = [out] if torch.is_tensor(out) else [o for o in out if torch.is_tensor(o)]
+        pairs = [(o, g) for o, g in zip(outs, grad_outputs) if g is not None and o.requires_grad]
+        ins = [a for a in ctx._ts_leaves if torch.is_tensor(a) and a.requires_grad]
+        got = iter(torch.autograd.grad([o for o, _ in pairs], ins, [g for _, g in pairs], allow_unused=True)
+                   if pairs and ins else [None] * len(ins))
+        return tuple(next(got) if torch.is_tensor(a) and a.requires_grad else None for a in ctx._ts_leaves)
+
+
 # ------------------------------------------------------------------------------------------------ device queries
 def get_device_capability(device_id: int = 0) -> tuple[int, int]:
     return torch.cuda.get_device_capability(device_id) if torch.cuda.is_available() else (0, 0)
@@ -84,7 +112,7 @@ def _tables32(cos, sin):
     return cos.float().contiguous(), sin.float().contiguous()
 
 
-class RoPEFunction:
+class RoPEFunction(_FunctionPair):
     """`apply(x, cos, sin, position_ids, position_offset, interleaved, inplace)` on x [B, S, H, D]."""
 
     @staticmethod
@@ -98,7 +126,7 @@ class RoPEFunction:
         return out
 
 
-class FusedRoPEQKFunction:
+class FusedRoPEQKFunction(_FunctionPair):
     """`apply(Q, K, cos, sin, position_offset, interleaved)` -> (Q', K'); both [B, S, H, D]."""
 
     @staticmethod
@@ -176,7 +204,7 @@ def benchmark_rope(batch_size: int = 4, seq_len: int = 2048, n_heads: int = 32, 
 
 
 # ------------------------------------------------------------------------------------------------ normalisation
-class RMSLayerNormFunction:
+class RMSLayerNormFunction(_FunctionPair):
     """`apply(X, weight, eps, compute_weight_grad)`; the weight gradient is always formed when the weight wants one."""
 
     @staticmethod
@@ -184,7 +212,7 @@ class RMSLayerNormFunction:
         return _norm.rmsnorm(X, weight if compute_weight_grad else weight.detach(), eps)[0]
 
 
-class LayerNormFunction:
+class LayerNormFunction(_FunctionPair):
     @staticmethod
     def apply(X, weight=None, bias=None, eps: float = DEFAULT_EPS_LN, compute_weight_grad: bool = True):
         if weight is None:
@@ -194,7 +222,7 @@ class LayerNormFunction:
         return _norm.layernorm(X, weight, bias, eps)
 
 
-class FusedAddRMSLayerNormFunction:
+class FusedAddRMSLayerNormFunction(_FunctionPair):
     """`apply(X, residual, weight, eps, store_residual)` -> (norm(X + residual), X + residual or None): the sum is
     formed inside the norm kernel."""
 
@@ -312,7 +340,7 @@ def fp8_linear_forward(X, weight_fp8, weight_scale, bias=None, block_size: int =
     return y if bias is None else y + bias
 
 
-class FP8LinearFunction:
+class FP8LinearFunction(_FunctionPair):
     apply = staticmethod(fp8_linear_forward)
 
 
@@ -361,7 +389,7 @@ def triton_flash_attention(q, k, v, causal: bool = True, scale: float | None = N
                            sliding_window).transpose(1, 2)
 
 
-class FlashAttentionTritonFunction:
+class FlashAttentionTritonFunction(_FunctionPair):
     @staticmethod
     def apply(q, k, v, causal: bool = True, scale: float | None = None, sliding_window: int | None = None,
               num_kv_groups: int = 1):
@@ -537,6 +565,11 @@ class CompiledFunctionWrapper:
                 self.manager.clear()
         self.stats["eager_calls"] += 1
         return self.func(*args, **kwargs)
+
+    def reset(self) -> None:
+        """Forget captured graphs, counters and a remembered failure: the next call tries graph replay again."""
+        self.manager.clear()
+        self.stats = {"calls": 0, "graph_replays": 0, "eager_calls": 0, "failed": False}
 
 
 def compile_function(func: Callable, fullgraph: bool = False, dynamic: bool = True, mode: str = "max-autotune",

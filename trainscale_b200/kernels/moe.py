@@ -20,6 +20,7 @@ import torch.nn.functional as F
 from ..ops import activation as _act
 from ..ops import gemm as _gemm
 from ..ops import moe as _moe
+from .compat import _FunctionPair
 
 
 # ------------------------------------------------------------------------------------------------ device queries
@@ -280,7 +281,7 @@ def moe_grouped_gemm_backward_dw(X, dY, topk: int, expert_offsets, gather_indice
     return dW.to(X.dtype)
 
 
-class MoEGroupedGEMMFunction:
+class MoEGroupedGEMMFunction(_FunctionPair):
     """`apply(X, W, topk, expert_offsets, gather_indices, topk_weights, permute_x, permute_y, fuse_topk_weights,
     fwd_config=None, bwd_config=None)`: the reference's autograd-function entry point.  The forward functional is built
     from differentiable framework ops, so autograd derives the backward; the two explicit backward functionals above

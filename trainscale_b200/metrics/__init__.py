@@ -43,12 +43,36 @@ def sync_metrics(values: dict[str, float], op: str = "mean", group=None) -> dict
 class DistributedMetricBuffer:
     """Accumulate named sums locally; one all-reduce when read."""
 
-    def __init__(self):
+    def __init__(self, operation: str = "mean"):
+        if operation not in ("mean", "sum"):
+            raise ValueError("operation must be 'mean' or 'sum'")
+        self.operation = operation
         self.sums: dict[str, float] = {}
+        self._counts: dict[str, int] = {}
 
-    def add(self, name: str, value: float, weight: float = 1.0):
+    def add(self, name: str, value, weight: float = 1.0):
+        if torch.is_tensor(value):
+            value = value.detach().item()
         self.sums[name] = self.sums.get(name, 0.0) + float(value) * weight
         self.sums[name + "/weight"] = self.sums.get(name + "/weight", 0.0) + weight
+        self._counts[name] = self._counts.get(name, 0) + 1
+
+    # ---- data_pipeline/trainer/metrics/distributed.py:205-255
+    def counts(self) -> dict[str, int]:
+        return dict(self._counts)
+
+    def local_sums(self) -> dict[str, float]:
+        return {k: v for k, v in self.sums.items() if not k.endswith("/weight")}
+
+    def local_means(self) -> dict[str, float]:
+        return {k: v / max(self.sums[k + "/weight"], 1e-12) for k, v in self.local_sums().items()}
+
+    def reduce_all(self, process_group=None) -> dict[str, float]:
+        """One all-reduce for every buffered name.  'mean' is the mean over ALL values of all ranks (weighted by how
+        many each rank added), not the mean of the ranks' means; 'sum' the total."""
+        if self.operation == "mean":
+            return self.compute(process_group)
+        return sync_metrics(self.local_sums(), "sum", process_group)
 
     def compute(self, group=None) -> dict[str, float]:
         tot = sync_metrics(self.sums, "sum", group)
@@ -56,6 +80,9 @@ class DistributedMetricBuffer:
 
     def reset(self):
         self.sums.clear()
+        self._counts.clear()
+
+    clear = reset
 
 
 class Metric:

@@ -233,8 +233,46 @@ class AdaFactor(Optimizer):
     def _rms(x):
         return x.norm() / math.sqrt(max(1, x.numel()))
 
+    def memory_footprint(self) -> dict:
+        """Bytes held per kind: `state_bytes` (second moments, factored or full, and first moments) and `buffer_bytes`
+        (work buffers of the device path); data_pipeline/trainer/optimizers/adafactor.py:1420-1440."""
+        state = buf = 0
+        for st in self.state.values():
+            for k, v in st.items():
+                if torch.is_tensor(v):
+                    nb = v.numel() * v.element_size()
+                    if k in ("u", "sums", "col_tmp"):
+                        buf += nb
+                    else:
+                        state += nb
+        return {"state_bytes": state, "buffer_bytes": buf, "total_bytes": state + buf}
+
+    @property
+    def profiling_stats(self) -> "ProfilingStats":
+        """Counts since construction: steps' wall time, how many parameters use factored / full second moments, how
+        many updates ran as one device kernel."""
+        ps = self.__dict__.get("_prof")
+        if ps is None:
+            ps = self.__dict__["_prof"] = ProfilingStats()
+        ps.num_factorized_params = sum(1 for st in self.state.values() if "row" in st)
+        ps.num_full_params = sum(1 for st in self.state.values() if "v" in st)
+        ps.memory_allocated_bytes = self.memory_footprint()["total_bytes"]
+        ps.memory_peak_bytes = max(ps.memory_peak_bytes, ps.memory_allocated_bytes)
+        return ps
+
     @torch.no_grad()
     def step(self, closure=None):
+        import time as _time
+        t0 = _time.perf_counter_ns()
+        try:
+            return self._step(closure)
+        finally:
+            ps = self.__dict__.get("_prof")
+            if ps is None:
+                ps = self.__dict__["_prof"] = ProfilingStats()
+            ps.total_step_time_ns += _time.perf_counter_ns() - t0
+
+    def _step(self, closure=None):
         loss = closure() if closure is not None else None
         for g in self.param_groups:
             for p in g["params"]:
@@ -269,6 +307,7 @@ class AdaFactor(Optimizer):
                     K.adafactor_(p, p.grad, st, lr=lr, beta2=beta2, eps0=g["eps"][0], eps1=g["eps"][1],
                                  clip=g["clip_threshold"], scale_parameter=g["scale_parameter"], beta1=g["beta1"],
                                  weight_decay=g["weight_decay"])
+                    self.__dict__.setdefault("_prof", ProfilingStats()).fused_updates += 1
                     continue
                 gf = p.grad.float()
                 pf = p.float()
@@ -834,6 +873,32 @@ class AdaFactorState:
         return ParamState(self.step, self.factored, self.exp_avg, self.exp_avg_sq, self.exp_avg_sq_row,
                           self.exp_avg_sq_col, self.kahan_comp)
 
+    memory_footprint = memory_bytes
+
+    _TENSORS = ("exp_avg", "exp_avg_sq", "exp_avg_sq_row", "exp_avg_sq_col", "kahan_comp")
+
+    def to_dict(self) -> dict:
+        """Plain-dict form for a checkpoint: the step, the layout flags and clones of the tensors that exist."""
+        d = {"step": self.step, "factored": self.factored, "shape": list(self.shape), "dtype": str(self.dtype),
+             "use_momentum": self.use_momentum, "use_kahan": self.use_kahan}
+        for k in self._TENSORS:
+            t = getattr(self, k)
+            if t is not None:
+                d[k] = t.detach().clone()
+        return d
+
+    @classmethod
+    def from_dict(cls, d: dict, device=None) -> "AdaFactorState":
+        dtype = getattr(torch, str(d.get("dtype", "torch.float32")).replace("torch.", ""))
+        st = cls(tuple(d["shape"]), device, dtype, bool(d["factored"]), bool(d.get("use_momentum", "exp_avg" in d)),
+                 bool(d.get("use_kahan", "kahan_comp" in d)))
+        st.step = int(d.get("step", 0))
+        for k in cls._TENSORS:
+            if k in d:
+                setattr(st, k, d[k].to(device) if device is not None else d[k].clone())
+        st.is_initialized = any(k in d for k in cls._TENSORS)
+        return st
+
 
 @_dataclass
 class ProfilingStats:
@@ -976,6 +1041,38 @@ class BaseOptimizer(Optimizer):
         super().__init__(params, defaults)
         self.metrics = OptimizerMetrics(total_params=sum(p.numel() for g in self.param_groups for p in g["params"]))
         self.lifecycle = OptimizerState.INITIALIZED
+        self._grad_scale = 1.0
+        self._step_count = 0
+
+    # ---- data_pipeline/trainer/optimizers/adamw.py:1001-1152, sota_optimizers.py:600-640
+    @property
+    def step_count(self) -> int:
+        return self._step_count
+
+    def set_grad_scale(self, scale: float) -> None:
+        """The factor the loss was multiplied by (fp16 loss scaling): gradients are divided by it before the update."""
+        if not scale > 0:
+            raise ValueError("grad scale must be positive")
+        self._grad_scale = float(scale)
+
+    def get_grad_scale(self) -> float:
+        return self._grad_scale
+
+    def get_metrics(self) -> "OptimizerMetrics":
+        return self.metrics
+
+    @torch.no_grad()
+    def clip_grad_norm_(self, max_norm: float, norm_type: float = 2.0, error_if_nonfinite: bool = False) -> torch.Tensor:
+        """Clip over ALL parameter groups together; returns the norm before clipping."""
+        ps = [p for g in self.param_groups for p in g["params"] if p.grad is not None]
+        if not ps:
+            return torch.zeros(())
+        return torch.nn.utils.clip_grad_norm_(ps, max_norm, norm_type, error_if_nonfinite=error_if_nonfinite)
+
+    def close(self) -> None:
+        """Drop the per-parameter state (frees its memory); the optimizer takes no further steps."""
+        self.state.clear()
+        self.lifecycle = OptimizerState.CLOSED
 
     def _init_state(self, p: torch.Tensor, group: dict) -> dict:
         return {"step": 0}
@@ -989,9 +1086,13 @@ class BaseOptimizer(Optimizer):
         if closure is not None:
             with torch.enable_grad():
                 loss = closure()
+        if self.lifecycle is OptimizerState.CLOSED:
+            raise RuntimeError("step() on a closed optimizer")
         norm = 0.0
         for g in self.param_groups:
             ps = [p for p in g["params"] if p.grad is not None]
+            if self._grad_scale != 1.0:
+                torch._foreach_div_([p.grad for p in ps], self._grad_scale)
             if g.get("max_grad_norm"):
                 norm = float(clip_grad_norm_(ps, g["max_grad_norm"]))
             for p in ps:
@@ -1002,6 +1103,7 @@ class BaseOptimizer(Optimizer):
                 self._update(p, p.grad, st, g)
         self.metrics.record_step(norm)
         self.lifecycle = OptimizerState.STEPPED
+        self._step_count += 1
         return loss
 
 

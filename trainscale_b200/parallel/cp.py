@@ -22,6 +22,8 @@ from dataclasses import dataclass
 
 from enum import IntEnum
 
+import contextlib
+
 import torch
 import torch.distributed as dist
 import torch.nn as nn
@@ -56,6 +58,23 @@ class HeadTailBalancer:
         inv = torch.empty_like(order)
         inv[order] = torch.arange(full_len)
         return torch.cat(parts, dim=dim).index_select(dim, inv.to(parts[0].device))
+
+    # ---- stateless forms with the rank and the degree as arguments
+    # (data_pipeline/trainer/distributed/context_parallel.py:980-1010); every balancer of this module inherits them
+    def partition(self, tensor: torch.Tensor, cp_rank: int, cp_world_size: int, seq_dim: int = 1) -> torch.Tensor:
+        return type(self)(cp_world_size, cp_rank).shard(tensor, seq_dim)
+
+    def gather(self, shards: list[torch.Tensor], cp_world_size: int | None = None, seq_dim: int = 1) -> torch.Tensor:
+        return type(self)(cp_world_size or len(shards), 0).unshard(list(shards), seq_dim)
+
+    def compute_global_positions(self, local_len: int, cp_rank: int, cp_world_size: int,
+                                 total_len: int | None = None) -> torch.Tensor:
+        """Position in the full sequence of each of the rank's `local_len` tokens (what RoPE and the causal mask need)."""
+        total = total_len if total_len is not None else local_len * cp_world_size
+        idx = type(self)(cp_world_size, cp_rank).indices(total)
+        if idx.numel() != local_len:
+            raise ValueError(f"rank {cp_rank} of {cp_world_size} owns {idx.numel()} of {total} tokens, not {local_len}")
+        return idx
 
 
 class ZigZagBalancer(HeadTailBalancer):
@@ -778,6 +797,18 @@ class RingCommunicator:
         for h in handles:
             h.wait()
 
+    @contextlib.contextmanager
+    def ring_step_context(self, k_local: torch.Tensor, v_local: torch.Tensor):
+        """`with ring.ring_step_context(k, v) as (k_next, v_next):` - the exchange with the neighbours runs while the
+        body computes on the CURRENT k / v; on exit the received blocks are complete.  k and v travel as one message."""
+        send = torch.stack((k_local, v_local))
+        recv = torch.empty_like(send)
+        handles = self.start_send_recv(send, recv)
+        try:
+            yield recv[0], recv[1]
+        finally:
+            self.wait_recv(handles)
+
 
 class ContextParallelEngine:
     """Shards a batch over the context-parallel group, runs exact causal ring attention on the shards (forward and
@@ -951,6 +982,15 @@ class LoadBalancerStrategy:
 
     def unpartition(self, parts: list[torch.Tensor], seq_dim: int) -> torch.Tensor:
         raise NotImplementedError
+
+    def gather(self, shards: list[torch.Tensor], cp_world_size: int | None = None, seq_dim: int = 1) -> torch.Tensor:
+        return self.unpartition(list(shards), seq_dim)
+
+    def compute_global_positions(self, local_len: int, cp_rank: int, cp_world_size: int,
+                                 total_len: int | None = None) -> torch.Tensor:
+        """Derived from `partition` applied to the positions 0 .. total-1 themselves."""
+        total = total_len if total_len is not None else local_len * cp_world_size
+        return self.partition(torch.arange(total).unsqueeze(0), cp_rank, cp_world_size, 1).squeeze(0)
 
 
 class BalancerStrategy(LoadBalancerStrategy):

@@ -271,6 +271,26 @@ class CUDATimer:
             return self._a.elapsed_time(self._b) if self._b is not None and self._b.query() else None
         return self._dt
 
+    def sync_and_elapsed_ms(self) -> float:
+        """Waits for the stop event, then reads (the blocking form, for measurements outside the training loop)."""
+        if self.cuda and self._b is not None:
+            self._b.synchronize()
+        return float(self.elapsed_ms() or 0.0)
+
+    def elapsed_us(self) -> float | None:
+        ms = self.elapsed_ms()
+        return None if ms is None else ms * 1e3
+
+    def elapsed_ns(self) -> int | None:
+        ms = self.elapsed_ms()
+        return None if ms is None else int(ms * 1e6)
+
+    def __enter__(self) -> "CUDATimer":
+        return self.start()
+
+    def __exit__(self, *exc) -> None:
+        self.stop()
+
     __enter__ = start
 
     def __exit__(self, *exc):

@@ -59,6 +59,50 @@ class CUDAGraphManager:
     def clear(self):
         self.graphs.clear()
         self.pool = None
+        self.__dict__.get("_keyed", {}).clear()
+
+    # ---- explicit two-step form (data_pipeline/trainer/kernels/compiler.py:308-400)
+    def capture(self, func: Callable, *args: torch.Tensor, key: str | None = None, **kwargs):
+        """Capture `func(*args, **kwargs)` under `key` (default: the function's identity).  Returns (graph, static
+        inputs, static outputs); a second call with the same key returns the stored triple.  Needs a CUDA device."""
+        if not torch.cuda.is_available():
+            raise RuntimeError("CUDA required for graph capture")
+        keyed = self.__dict__.setdefault("_keyed", {})
+        key = key or str(id(func))
+        if key in keyed:
+            return keyed[key]
+        static = [a.clone() for a in args if torch.is_tensor(a)]
+        s = torch.cuda.Stream()
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            for _ in range(self.config.warmup_iters):
+                func(*static, **kwargs)
+        torch.cuda.current_stream().wait_stream(s)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, pool=self.pool):
+            out = func(*static, **kwargs)
+        if self.config.pool_shared and self.pool is None:
+            self.pool = g.pool()
+        outs = [out] if torch.is_tensor(out) else [o for o in out if torch.is_tensor(o)]
+        keyed[key] = (g, static, outs)
+        return keyed[key]
+
+    def replay(self, key: str, *args: torch.Tensor):
+        """Copy `args` into the static inputs of the graph captured under `key`, replay it, and return its static
+        outputs (one tensor, or a list).  The outputs are overwritten by the next replay: clone what must be kept."""
+        keyed = self.__dict__.get("_keyed", {})
+        if key not in keyed:
+            raise KeyError(f"no graph captured under {key!r}")
+        g, static, outs = keyed[key]
+        new = [a for a in args if torch.is_tensor(a)]
+        if len(new) != len(static):
+            raise ValueError(f"graph {key!r} takes {len(static)} tensors, got {len(new)}")
+        for dst, src in zip(static, new):
+            if dst.shape != src.shape or dst.dtype != src.dtype:
+                raise ValueError(f"graph {key!r} was captured for {tuple(dst.shape)} {dst.dtype}")
+            dst.copy_(src)
+        g.replay()
+        return outs[0] if len(outs) == 1 else outs
 
 
 def compile_model(model, config: CompilationConfig | None = None):
@@ -103,6 +147,14 @@ class ModelCompiler:
 
     def for_training(self, model, checkpoint_every: int = 2):
         return optimize_for_training(model, checkpoint_every)
+
+    @property
+    def cuda_graph_manager(self) -> CUDAGraphManager:
+        return self.graphs
+
+    def reset(self) -> None:
+        """Drop every captured graph (their memory pool with them)."""
+        self.graphs.clear()
 
 
 class InductorConfigManager:
