@@ -62,6 +62,73 @@ def test_every_public_name_of_the_reference_exists_here():
     assert not missing, f"{len(missing)} names without a counterpart: {sorted(missing.items())[:20]}"
 
 
+def _reference_methods(root: Path) -> dict[str, set[str]]:
+    """{class name: public method names} over every module-level class of the reference (same-named classes of
+    different files are merged)."""
+    out: dict[str, set[str]] = {}
+    for p in root.rglob("*.py"):
+        if "examples" in p.parts:
+            continue
+        try:
+            tree = ast.parse(p.read_text())
+        except SyntaxError:
+            continue
+        for node in tree.body:
+            if isinstance(node, ast.ClassDef):
+                out.setdefault(node.name, set()).update(
+                    n.name for n in node.body
+                    if isinstance(n, (ast.FunctionDef, ast.AsyncFunctionDef)) and not n.name.startswith("_"))
+    return out
+
+
+def _our_classes() -> dict[str, set]:
+    import importlib
+    import inspect
+    import pkgutil
+
+    import trainscale_b200
+    found: dict[str, set] = {}
+    for m in pkgutil.walk_packages(trainscale_b200.__path__, "trainscale_b200."):
+        if m.name.endswith("__main__"):
+            continue
+        try:
+            mod = importlib.import_module(m.name)
+        except Exception:   # noqa: BLE001 - optional dependencies of single modules
+            continue
+        for n, v in vars(mod).items():
+            if inspect.isclass(v) and v.__module__.startswith("trainscale_b200"):
+                found.setdefault(n, set()).add(v)
+    return found
+
+
+def _has_member(cls, name: str) -> bool:
+    import inspect
+    if hasattr(cls, name) or name in getattr(cls, "__annotations__", {}) or name in getattr(cls, "__dataclass_fields__", {}):
+        return True
+    try:                                              # attributes that exist per instance (set in __init__)
+        src = inspect.getsource(cls)
+    except (OSError, TypeError):
+        return False
+    return any(f"self.{name}{tail}" in src for tail in (" =", "=", ",", " :")) or f", self.{name}" in src
+
+
+def test_every_public_method_of_a_shared_class_exists_here():
+    """For every class that exists under the same name on both sides, each public method / property of the reference's
+    class is an attribute of ours (a method, a property, a field or an alias)."""
+    ref = _reference_root()
+    if ref is None:
+        pytest.skip("the reference package is not on this machine")
+    ours = _our_classes()
+    missing = {}
+    for cname, methods in _reference_methods(ref).items():
+        if cname not in ours:
+            continue
+        lack = sorted(m for m in methods if not any(_has_member(c, m) for c in ours[cname]))
+        if lack:
+            missing[cname] = lack
+    assert not missing, f"{sum(map(len, missing.values()))} members missing: {sorted(missing.items())[:15]}"
+
+
 def test_last_helpers_behave():
     import torch
 

@@ -522,3 +522,184 @@ def test_distributed_metric_buffer_local_views():
     assert b.counts() == {} and b.reduce_all() == {}
     with pytest.raises(ValueError):
         DistributedMetricBuffer("max")
+
+
+def test_hub_policy_members_and_result_map_err(tmp_path):
+    from trainscale_b200.core.errors import HubError
+    from trainscale_b200.core.types import Err, Ok
+    from trainscale_b200.hub import CheckpointManager, CircuitBreaker, HubErrorCode, HubMetrics, RetryPolicy
+    assert HubError("x", code=HubErrorCode.TIMEOUT).is_retriable
+    assert not HubError("x", code=HubErrorCode.VALIDATION_ERROR).is_retriable and not HubError("y").is_retriable
+    assert Ok(1).map_err(str) == Ok(1) and Err(2).map_err(lambda e: e * 2) == Err(4)
+    now = [0.0]
+    cb = CircuitBreaker(1, 10.0, clock=lambda: now[0])
+    assert cb.can_execute().is_ok()
+    cb.record_failure()
+    r = cb.can_execute()
+    assert r.is_err() and r.error.code is HubErrorCode.CIRCUIT_OPEN and r.error.context["retry_after_s"] == 10.0
+    now[0] = 11.0
+    assert cb.can_execute().is_ok()                          # half-open: one trial request may pass
+    assert RetryPolicy(jitter=0).compute_delay_ms(2) == 2000
+    m = HubMetrics()
+    m.record_upload(10, 5_000_000, True)
+    m.record_upload(10, 9_000_000, False)
+    assert m.get_percentile_latency_ns(50) == 9_000_000 and m.get_percentile_latency_ns(50, "download") is None
+    snap = m.snapshot()
+    assert snap["uploads"] == {"total": 2, "failed": 1, "bytes": 10, "p50_latency_ms": 9.0, "p99_latency_ms": 9.0}
+    cm = CheckpointManager(tmp_path)
+    for step, loss in ((1, 2.0), (2, 1.0), (3, 1.5)):
+        cm.save(step, lambda p: None, {"eval_loss": loss})
+    assert cm.get_latest_checkpoint().step == 3
+    best = cm.get_best_checkpoint()
+    assert best.step == 2 and best.loss == 1.0
+    assert CheckpointManager(tmp_path / "empty").get_best_checkpoint() is None
+
+
+def test_grpo_compute_log_probs_match_full_logits():
+    from trainscale_b200.models.llama import build_model
+    from trainscale_b200.rl import GRPOCompute
+    torch.manual_seed(0)
+    m = build_model("tiny", dtype=torch.float32, device="cpu")
+    g = GRPOCompute(group_size=2, model=m, reward_clip=0.8)
+    ids = torch.randint(0, 1000, (4, 9))
+    mask = torch.ones_like(ids)
+    mask[0, 6:] = 0
+    lp = g.compute_log_probs(ids, mask)
+    with torch.no_grad():
+        ref = torch.log_softmax(m(input_ids=ids).logits.float(), -1)[:, :-1].gather(-1, ids[:, 1:, None]).squeeze(-1)
+    assert lp.shape == (4, 8) and torch.allclose(lp[1:], ref[1:], atol=1e-4)
+    assert torch.allclose(lp[0, :5], ref[0, :5], atol=1e-4) and float(lp[0, 5:].abs().sum()) == 0.0   # padding targets
+    loss, stats = g.compute_grpo_loss(lp, ref - 0.1, torch.tensor([1.0, 0.0, 0.5, 0.2]), mask[:, 1:].float())
+    loss.backward()
+    assert stats["reward_mean"] == pytest.approx(0.375) and stats["kl"] > 0      # the reward of 1.0 was clipped to 0.8
+    assert m.head_weight.grad is not None
+
+
+def test_small_members_of_configs_and_records():
+    from trainscale_b200.callbacks import HOOKS, Callback
+    from trainscale_b200.config.data_schema import DatasetConfig, PromptTemplate, SplitSpec, StageConfig
+    from trainscale_b200.config.sota_config import SchedulerConfig
+    from trainscale_b200.data.dataset_wrappers import StreamingPreprocessedDataset
+    from trainscale_b200.data.length_manager import TokenAwareContentDistributor
+    from trainscale_b200.inference.engine import GenerationParams, InferenceRequest, MetricsAggregator, RequestMetrics
+    from trainscale_b200.introspection import ColumnMapper, DatasetIntrospector
+    from trainscale_b200.kernels import FlexAttentionConfig
+    from trainscale_b200.losses import CLIPLoss, LossRegistry
+    from trainscale_b200.optim import KahanAccumulator, Prodigy
+    from trainscale_b200.parallel.activation import CheckpointSegment, OffloadHandle, OffloadTarget
+    from trainscale_b200.parallel.cp import BalancedCPScheduler, HybridCPConfig
+    from trainscale_b200.parallel.ddp import DDPConfig, GradientCompression, GradientCompressionHook
+    from trainscale_b200.parallel.dist_kernels import CommStreamManager, DistributedBackend, DistributedConfig
+    from trainscale_b200.parallel.dist_utils import GradientSynchronizer, HardwareTopology
+    from trainscale_b200.parallel.fsdp2 import ComputeCapability
+    from trainscale_b200.parallel.mesh import (CommAlgorithmSelector, CommunicationAlgorithm, InterconnectType,
+                                               MemoryEstimator)
+    from trainscale_b200.trainer.sota_trainer import TrainingState
+
+    st = TrainingState(global_step=3)
+    st2 = st.with_update(global_step=4, epoch=1)
+    assert (st.global_step, st2.global_step, st2.epoch) == (3, 4, 1)
+    assert TokenAwareContentDistributor(max_length=100, special_tokens_budget=10).available_tokens == 90
+    assert SchedulerConfig(warmup_steps=0, warmup_ratio=0.1).compute_warmup_steps(1000) == 100
+    assert SchedulerConfig(warmup_steps=7).compute_warmup_steps(1000) == 7
+    d = GenerationParams(max_tokens=5, top_k=0, seed=3, stop=["x"]).to_sampling_params()
+    assert d["top_k"] == -1 and d["seed"] == 3 and d["stop"] == ["x"] and "logprobs" not in d
+    with pytest.raises(ValueError):
+        GenerationParams(n=0).to_sampling_params()
+    assert InferenceRequest("p", lora_name="a", lora_path="/x", lora_id=2).get_lora_request()["lora_int_id"] == 2
+    assert InferenceRequest("p", lora_name="a").get_lora_request() is None
+    agg = MetricsAggregator()
+    assert agg.summarize() == {"status": "no_requests_completed"}
+    agg.record(RequestMetrics("r", 3, 4))
+    assert agg.summarize()["requests"] == 1
+    md = DatasetIntrospector().discover({"train": [{"question": "q", "answer": "a"}], "test": []}).unwrap()
+    assert md.get_all_splits() == ["train", "test"] and md.get_config("default").splits[0].num_examples == 1
+    assert md.get_config("nope") is None and md.get_all_splits("nope") == []
+    sug = {m.target: m.source for m in ColumnMapper().suggest_mappings(["question", "answer", "id"])}
+    assert sug == {"prompt": "question", "completion": "answer"}
+    ds = DatasetConfig("d", stages={"s1": StageConfig("s1", {"train": SplitSpec("train")})})
+    assert ds.is_staged() and ds.get_split_spec("train", "s1").name == "train" and ds.get_split_spec("train") is None
+    assert not DatasetConfig("d").is_staged()
+    assert PromptTemplate(input_columns=("a", "b"), label_column="b").get_required_columns() == ["a", "b"]
+    assert PromptTemplate(input_columns=("a",), label_column="y").get_required_columns() == ["a", "y"]
+    assert FlexAttentionConfig(num_attention_heads=8, num_key_value_heads=2, head_dim=64).kv_hidden_size == 128
+    assert float(CLIPLoss(0.07).temperature) == pytest.approx(0.07, rel=1e-5)
+    assert type(LossRegistry.get("focal")).__name__ == "FocalLoss" and "dpo" in LossRegistry.list_available()
+    k = KahanAccumulator()
+    k.add(1.0)
+    k.reset()
+    assert k.value == 0.0
+    assert Prodigy([nn.Parameter(torch.zeros(2))], d0=1e-5).d == 1e-5
+    assert OffloadHandle(0, (2, 3), torch.bfloat16, torch.device("cpu"), OffloadTarget.GPU).memory_bytes == 12
+    assert CheckpointSegment(0, 2, 7).num_layers == 5
+    assert MemoryEstimator.check_memory_fit(100, 80).is_ok() and MemoryEstimator.check_memory_fit(100, 95).is_err()
+    assert "on_load" in HOOKS and Callback().on_load(None) is None
+    assert ComputeCapability(10, 0).supports_flash_attention_v2 and not ComputeCapability(7, 5).supports_flash_attention_v2
+    assert DistributedBackend.NCCL.to_torch_backend() == "nccl" and DistributedBackend.NONE.to_torch_backend() is None
+    DistributedConfig(tp_size=2, pp_size=2, dp_size=2).validate_topology(8)
+    with pytest.raises(ValueError):
+        DistributedConfig(tp_size=2).validate_topology(8)
+    assert DDPConfig.from_dict({"gradient_compression": "POWERSGD", "powersgd_rank": 8}).unwrap().gradient_compression \
+        is GradientCompression.POWERSGD
+    assert DDPConfig.from_dict({"no_such_option": 1}).is_err()
+    hook = GradientCompressionHook()
+    hook(None, torch.ones(8))
+    assert hook.metrics.bytes_reduced == 32 and hook.metrics.compression_ratio == 1.0
+    sel = CommAlgorithmSelector
+    assert sel.select_allreduce_algorithm(1 << 10, 8, None, True) is CommunicationAlgorithm.NCCL_AUTO
+    assert sel.select_allreduce_algorithm(1 << 10, 8) is CommunicationAlgorithm.TREE
+    assert sel.select_allreduce_algorithm(1 << 26, 8) is CommunicationAlgorithm.RING
+    env = sel.get_nccl_env_vars(CommunicationAlgorithm.RING, InterconnectType.NVLINK5)
+    assert env == {"NCCL_P2P_LEVEL": "NVL", "NCCL_ALGO": "Ring"}
+    assert sel.get_nccl_env_vars(CommunicationAlgorithm.NCCL_AUTO) == {}
+    topo = HardwareTopology(2, "x", 1.0, 1, ((True, True), (True, True)))
+    assert topo.total_gpus == 2 and topo.has_nvlink and not HardwareTopology(1, "x", 1.0, 1, ((True,),)).has_nvlink
+    mgr = CommStreamManager(device="cpu")
+    assert mgr.record_compute_event() is None and mgr.sync_back_to_compute() is None
+    lin = nn.Linear(2, 2)
+    lin(torch.ones(1, 2)).sum().backward()
+    GradientSynchronizer(lin).sync_gradients()                # single process: gradients stay as they are
+    assert lin.weight.grad is not None
+
+    sched = BalancedCPScheduler(HybridCPConfig(max_tokens_per_rank=100, world_size=4))
+    groups, ids = sched.get_groups_and_subsamples([(10, 400), (11, 90), (12, 100), (13, 180), (14, 50)])
+    assert sorted(i for g in ids for gpu in g for i in gpu if True) .count(10) == 4      # 400 tokens: all four GPUs
+    assert {i for g in ids for gpu in g for i in gpu} == {10, 11, 12, 13, 14}
+    assert all(len(g) == 4 for g in groups) and groups[0][0][0] == (10, 4)
+
+    class Ex:
+        def __init__(self, row):
+            self.row = row
+        def to_dict(self):
+            return {"input_ids": [self.row["v"]]}
+
+    class Engine:
+        def process(self, row):
+            return Ex(row)
+
+    stream = StreamingPreprocessedDataset([{"v": i} for i in range(50)], Engine())
+    a = [int(x["input_ids"][0]) for x in stream.shuffle(buffer_size=8, seed=1)]
+    b = [int(x["input_ids"][0]) for x in stream.shuffle(buffer_size=8, seed=1)]
+    assert sorted(a) == list(range(50)) and a != list(range(50)) and a == b
+
+
+def test_seq2seq_trainer_greedy_generate():
+    from trainscale_b200.config.training_args import TrainingArguments
+    from trainscale_b200.trainer.base import PretrainingTrainer, Seq2SeqTrainer
+
+    class Toy(nn.Module):
+        """Next decoder token = previous token + 1 (mod 6), whatever the encoder input."""
+        def __init__(self):
+            super().__init__()
+            self.p = nn.Parameter(torch.zeros(1))
+        def forward(self, input_ids, decoder_input_ids, **kw):
+            nxt = (decoder_input_ids + 1) % 6
+            return (torch.nn.functional.one_hot(nxt, 6).float() + self.p,)
+
+    t = Seq2SeqTrainer(Toy(), TrainingArguments())
+    out = t.generate({"input_ids": torch.zeros(2, 3, dtype=torch.long)}, max_length=8, eos_token_id=4)
+    assert out.tolist() == [[1, 2, 3, 4]] * 2                 # stops once every row has produced the end token
+    out = t.generate({"input_ids": torch.zeros(1, 3, dtype=torch.long)}, max_length=4)
+    assert out.tolist() == [[1, 2, 3, 4]]
+    pt = PretrainingTrainer(Toy(), TrainingArguments(), ema_decay=0.9)
+    assert pt.ema_model is pt.ema and pt.ema_model is not pt.model

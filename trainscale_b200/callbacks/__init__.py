@@ -22,7 +22,7 @@ from typing import Any
 logger = logging.getLogger("trainscale_b200")
 
 HOOKS = ("on_init_end", "on_train_begin", "on_train_end", "on_epoch_begin", "on_epoch_end", "on_step_begin",
-         "on_step_end", "on_evaluate", "on_save", "on_log", "on_prediction_step")
+         "on_step_end", "on_evaluate", "on_save", "on_load", "on_log", "on_prediction_step")
 
 
 @dataclass
@@ -63,6 +63,7 @@ class Callback:
     def on_step_end(self, ctx): ...
     def on_evaluate(self, ctx): ...
     def on_save(self, ctx): ...
+    def on_load(self, ctx): ...
     def on_log(self, ctx): ...
     def on_prediction_step(self, ctx): ...
 

@@ -136,6 +136,16 @@ class DatasetConfig:
     data_files: Optional[Any] = None
     path: Optional[str] = None          # local json/jsonl/parquet/csv/txt file or directory
 
+    def is_staged(self) -> bool:
+        """True when the dataset is configured as named stages (curriculum) rather than one set of splits."""
+        return bool(self.stages)
+
+    def get_split_spec(self, split_name: str, stage_name: Optional[str] = None) -> Optional[SplitSpec]:
+        if stage_name is not None:
+            stage = self.stages.get(stage_name)
+            return stage.get_split(split_name) if stage is not None else None
+        return self.splits.get(split_name)
+
 
 @dataclass(frozen=True)
 class TokenizerConfig:
@@ -162,6 +172,13 @@ class PromptTemplate:
     mask_input: bool = True
     add_bos: bool = False
     add_eos: bool = True
+
+    def get_required_columns(self) -> List[str]:
+        """Input columns plus the label column, each once, in that order."""
+        cols = list(self.input_columns)
+        if self.label_column and self.label_column not in cols:
+            cols.append(self.label_column)
+        return cols
 
 
 @dataclass(frozen=True)

@@ -189,6 +189,12 @@ class SchedulerConfig:
     power: float = 1.0
     max_lr_ratio: float = 10.0
 
+    def compute_warmup_steps(self, num_training_steps: int) -> int:
+        """Explicit `warmup_steps` when set, else `warmup_ratio` of the run (data_pipeline/trainer/core/types.py:517)."""
+        if self.warmup_steps > 0:
+            return self.warmup_steps
+        return int(self.warmup_ratio * max(0, num_training_steps))
+
 
 @dataclass
 class LossConfig:

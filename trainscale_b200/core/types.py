@@ -36,6 +36,9 @@ class Ok(Generic[T]):
     def and_then(self, fn):
         return fn(self.value)
 
+    def map_err(self, fn):
+        return self
+
     def __repr__(self):
         return f"Ok({self.value!r})"
 
@@ -63,6 +66,9 @@ class Err(Generic[E]):
 
     def and_then(self, fn):
         return self
+
+    def map_err(self, fn):
+        return Err(fn(self.error))
 
     def __repr__(self):
         return f"Err({self.error!r})"

@@ -74,12 +74,44 @@ class PreprocessedDataset(Dataset):
         return PreprocessedDataset(sub, self.engine, self.mapping, self.cache is not None, self.max_cache_items)
 
 
+class _BufferShuffle:
+    """Iterable that yields the rows of `source` through a buffer of `buffer_size` rows, picking a random one each
+    time (the usual approximate shuffle of a stream); a fresh pass re-seeds, so every pass has the same order."""
+
+    def __init__(self, source, buffer_size: int, seed: int = 0):
+        self.source, self.buffer_size, self.seed = source, max(1, buffer_size), seed
+
+    def __iter__(self):
+        import random
+        rng, buf = random.Random(self.seed), []
+        for row in self.source:
+            if len(buf) < self.buffer_size:
+                buf.append(row)
+                continue
+            i = rng.randrange(len(buf))
+            yield buf[i]
+            buf[i] = row
+        rng.shuffle(buf)
+        yield from buf
+
+
 class StreamingPreprocessedDataset(IterableDataset):
     def __init__(self, iterable: Iterable, engine, column_mapping: Mapping[str, str] | None = None, rank: int = 0,
                  world_size: int = 1, skip_errors: bool = True, max_items: int | None = None):
         self.iterable, self.engine, self.mapping = iterable, engine, dict(column_mapping or {})
         self.rank, self.world, self.skip_errors, self.max_items = rank, world_size, skip_errors, max_items
         self.num_errors = 0
+
+    def shuffle(self, buffer_size: int = 1000, seed: int = 0) -> "StreamingPreprocessedDataset":
+        """The same stream in shuffled order: the source's own `shuffle(buffer_size=..., seed=...)` when it has one
+        (HuggingFace iterable datasets), else a reservoir of `buffer_size` rows drawn from at random."""
+        src = self.iterable
+        if hasattr(src, "shuffle"):
+            shuffled = src.shuffle(buffer_size=buffer_size, seed=seed)
+        else:
+            shuffled = _BufferShuffle(src, buffer_size, seed)
+        return StreamingPreprocessedDataset(shuffled, self.engine, self.mapping, self.rank, self.world, self.skip_errors,
+                                            self.max_items)
 
     def __iter__(self):
         info = get_worker_info()

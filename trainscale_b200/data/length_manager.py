@@ -195,6 +195,11 @@ class TokenAwareContentDistributor:
     def _cfg(self, name: str) -> ColumnContentConfig:
         return self.columns.get(name) or ColumnContentConfig(name)
 
+    @property
+    def available_tokens(self) -> int:
+        """Token budget left for content once the special tokens' headroom is taken out."""
+        return max(0, self.max_length - self.special)
+
     def allocate(self, lengths: Mapping[str, int]) -> dict[str, int]:
         """lengths: estimated tokens per column -> allotted tokens per column (sum <= budget)."""
         budget = max(0, self.max_length - self.special)

@@ -89,6 +89,11 @@ class DataPipeline:
         md = self.discover()
         return list(md.unwrap().splits) if md.is_ok() else []
 
+    def get_stage_splits(self, stage: str) -> list[str]:
+        """Split names of one curriculum stage; empty for an unknown stage or a dataset without stages."""
+        st = self.config.dataset.stages.get(stage) if self.config.dataset.stages else None
+        return list(st.splits) if st is not None else []
+
     def load_dataset(self, split: str = "train") -> Result:
         ds = self.config.dataset
         spec = ds.splits.get(split)

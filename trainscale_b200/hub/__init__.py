@@ -41,6 +41,15 @@ class CircuitBreaker:
             self.state = "half_open"
         return self.state != "open"
 
+    def can_execute(self):
+        """`allow()` as a Result: Ok(True), or Err(HubError with code CIRCUIT_OPEN and the seconds left to wait)."""
+        from ..core.types import Err, Ok
+        if self.allow():
+            return Ok(True)
+        left = self.reset_timeout - (self.clock() - self.opened_at)
+        return Err(HubError(f"circuit open, retry after {left:.1f}s", code=HubErrorCode.CIRCUIT_OPEN,
+                            failures=self.failures, retry_after_s=left))
+
     def record_success(self):
         self.failures, self.state, self.opened_at = 0, "closed", None
 
@@ -62,6 +71,10 @@ class RetryPolicy:
     def delay(self, attempt: int) -> float:
         d = min(self.max_delay, self.base_delay * self.backoff ** attempt)
         return d * (1.0 + random.uniform(-self.jitter, self.jitter))
+
+    def compute_delay_ms(self, attempt: int) -> int:
+        """`delay(attempt)` in whole milliseconds (attempt is 0-based)."""
+        return int(round(self.delay(attempt) * 1e3))
 
 
 def execute_with_retry(fn: Callable, policy: RetryPolicy | None = None, breaker: CircuitBreaker | None = None,
@@ -430,6 +443,19 @@ class CheckpointManager:
         f = self.root / "best"
         return self.root / f.read_text().strip() if f.exists() else None
 
+    def get_latest_checkpoint(self) -> "CheckpointMetadata | None":
+        p = self.latest()
+        return CheckpointMetadata.read(p) if p is not None and (p / "checkpoint_meta.json").exists() else None
+
+    def get_best_checkpoint(self) -> "CheckpointMetadata | None":
+        """The checkpoint `best` points at (best value of the tracked metric), else the one with the lowest loss."""
+        p = self.best()
+        if p is not None and (p / "checkpoint_meta.json").exists():
+            return CheckpointMetadata.read(p)
+        metas = [CheckpointMetadata.read(d) for d in self.list() if (d / "checkpoint_meta.json").exists()]
+        metas = [m for m in metas if m.loss == m.loss]          # drop NaN (no loss recorded)
+        return min(metas, key=lambda m: m.loss) if metas else None
+
     def _prune_old_checkpoints(self):
         if not self.limit or self.limit <= 0:
             return
@@ -562,6 +588,22 @@ class HubMetrics:
             return 0.0
         s = sorted(xs)
         return s[min(len(s) - 1, int(q * len(s)))] / 1e6
+
+    def get_percentile_latency_ns(self, percentile: float, operation: str = "upload") -> int | None:
+        """`percentile` in [0, 100]; None before the first sample."""
+        with self._lock:
+            xs = sorted(self._up_ns if operation == "upload" else self._down_ns)
+        return xs[min(len(xs) - 1, int(len(xs) * percentile / 100.0))] if xs else None
+
+    def snapshot(self) -> dict:
+        """Nested form of `summary()` (data_pipeline/trainer/hub/__init__.py:241-262)."""
+        ms = lambda p, op: (self.get_percentile_latency_ns(p, op) or 0) / 1e6      # noqa: E731
+        return {"uploads": {"total": self.uploads_total, "failed": self.uploads_failed, "bytes": self.bytes_uploaded,
+                            "p50_latency_ms": ms(50, "upload"), "p99_latency_ms": ms(99, "upload")},
+                "downloads": {"total": self.downloads_total, "failed": self.downloads_failed,
+                              "bytes": self.bytes_downloaded, "p50_latency_ms": ms(50, "download"),
+                              "p99_latency_ms": ms(99, "download")},
+                "retries_total": self.retries_total}
 
     def summary(self) -> dict:
         with self._lock:

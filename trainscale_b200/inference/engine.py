@@ -122,6 +122,26 @@ class GenerationParams:
             raise ValueError("temperature must be >= 0")
         if not 0 < self.top_p <= 1:
             raise ValueError("top_p must be in (0, 1]")
+        if self.n < 1:
+            raise ValueError("n must be >= 1")
+
+    def to_sampling_params(self) -> dict:
+        """Validated keyword form of the sampling settings, as the sampler of this engine (or an external one with the
+        same vocabulary of options, e.g. vllm.SamplingParams(**d)) takes them; unset options are left out."""
+        self.validate()
+        d = {"max_tokens": self.max_tokens, "temperature": self.temperature, "top_p": self.top_p,
+             "top_k": self.top_k if self.top_k > 0 else -1, "min_p": self.min_p,
+             "repetition_penalty": self.repetition_penalty, "frequency_penalty": self.frequency_penalty,
+             "presence_penalty": self.presence_penalty, "n": self.n, "ignore_eos": self.ignore_eos}
+        if self.seed is not None:
+            d["seed"] = self.seed
+        if self.stop:
+            d["stop"] = list(self.stop)
+        if self.stop_token_ids:
+            d["stop_token_ids"] = list(self.stop_token_ids)
+        if self.logprobs:
+            d["logprobs"] = 1
+        return d
 
 
 @dataclass
@@ -167,6 +187,12 @@ class MetricsAggregator:
 
     def add(self, m: RequestMetrics) -> None:
         self.records.append(m)
+
+    record = add
+
+    def summarize(self) -> dict:
+        """`summary()`, or {"status": "no_requests_completed"} before the first finished request."""
+        return self.summary() if self.records else {"status": "no_requests_completed"}
 
     @staticmethod
     def _pct(vals: list[float], p: float) -> float | None:
@@ -1234,6 +1260,12 @@ class InferenceRequest:
     @property
     def metrics(self) -> RequestMetrics:
         return self._metrics
+
+    def get_lora_request(self) -> dict | None:
+        """{"lora_name", "lora_int_id", "lora_path"} when the request names an adapter completely, else None."""
+        if self.lora_name and self.lora_path and self.lora_id is not None:
+            return {"lora_name": self.lora_name, "lora_int_id": self.lora_id, "lora_path": self.lora_path}
+        return None
 
     def submit(self, engine: "SOTAInferenceEngine"):
         req = engine.core.add_request(self.prompt, self.params)

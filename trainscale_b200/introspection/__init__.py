@@ -36,6 +36,20 @@ class DatasetMetadata:
     splits: dict[str, int | None] = field(default_factory=dict)     # split -> rows (None if unknown)
     columns: dict[str, str] = field(default_factory=dict)           # column -> dtype name
     source: str = "memory"
+    default_config: str | None = None
+
+    def get_config(self, name: str) -> "ConfigInfo | None":
+        """Typed record of one configuration ("default" names the only one of a dataset without configurations)."""
+        if name in self.configs or (not self.configs and name == "default"):
+            return ConfigInfo(name, tuple(SplitInfo(k, v) for k, v in self.splits.items()))
+        return None
+
+    def get_all_splits(self, config: str | None = None) -> list[str]:
+        """Split names in their declared order.  Splits are recorded for the configuration that was discovered, so an
+        unknown `config` yields an empty list."""
+        if config is not None and self.get_config(config) is None:
+            return []
+        return list(self.splits)
 
 
 class DatasetIntrospector:
@@ -43,8 +57,23 @@ class DatasetIntrospector:
 
     def __init__(self, token: str | None = None):
         self.token = token
+        self._cache: dict = {}
+
+    def clear_cache(self) -> None:
+        self._cache.clear()
 
     def discover(self, name_or_data, config_name: str | None = None) -> Result:
+        """Metadata of rows in memory, of a local file / directory, or of a hub dataset.  Hub and path look-ups are
+        cached per (name, config) until `clear_cache()`."""
+        key = (str(name_or_data), config_name) if isinstance(name_or_data, (str, Path)) else None
+        if key is not None and key in self._cache:
+            return Ok(self._cache[key])
+        r = self._discover(name_or_data, config_name)
+        if key is not None and r.is_ok():
+            self._cache[key] = r.unwrap()
+        return r
+
+    def _discover(self, name_or_data, config_name: str | None = None) -> Result:
         try:
             if isinstance(name_or_data, Mapping):   # {"split": rows}
                 return Ok(self._from_memory("memory", dict(name_or_data)))
@@ -144,6 +173,14 @@ class ColumnMapper:
         if missing:
             return Err(ColumnNotFoundError(f"no column matches {missing}", available=list(available)))
         return Ok(out)
+
+    STANDARD_SCHEMA = ("text", "prompt", "completion", "chosen", "rejected", "messages")
+
+    def suggest_mappings(self, source_columns: Sequence[str], target_schema: Sequence[str] | None = None) -> list:
+        """`ColumnMatch` for every target column (the standard training columns by default) that some source column
+        matches; nothing is required, so an unknown dataset can be explored
+        (data_pipeline/introspection/column_mapper.py:305-330)."""
+        return match_columns(source_columns, list(target_schema or self.STANDARD_SCHEMA))
 
 
 # ------------------------------------------------------------------------------------------------ reference surface

@@ -27,6 +27,7 @@ from ..ops import moe as _moe
 from ..ops import norm as _norm
 from ..ops import rope as _rope
 from ..losses import Fast_CrossEntropyLoss, FusedCrossEntropyFunction  # noqa: F401
+from ..utils.explicit_backward import ExplicitBackward as _ExplicitBackward
 from ..parallel.dist_kernels import (DistributedBackend, DistributedConfig, DistributedKernels,  # noqa: F401
                                      get_distributed_backend, get_world_info, pinned_memory_transfer)
 from ..utils.cuda_graphs import CompilationConfig, compile_model  # noqa: F401
@@ -292,6 +293,10 @@ class FlexAttentionConfig(FlashAttentionConfig):
     @property
     def hidden_size(self) -> int:
         return (self.num_attention_heads or 0) * (self.head_dim or 0)
+
+    @property
+    def kv_hidden_size(self) -> int:
+        return (self.num_key_value_heads or self.num_attention_heads or 0) * (self.head_dim or 0)
 
 
 @dataclass
@@ -588,7 +593,7 @@ def apply_lora_mlp_swiglu(x, Wg, Wu, Wd, Ag=None, Bg=None, Au=None, Bu=None, Ad=
     return matmul_lora(h, Wd, Ad, Bd, s)
 
 
-class _LoRABlock(nn.Module):
+class _LoRABlock(_ExplicitBackward, nn.Module):
     def _adapter(self, name, out_f, in_f, r, dtype, device):
         A = nn.Parameter(torch.empty(r, in_f, dtype=dtype, device=device))
         B = nn.Parameter(torch.zeros(out_f, r, dtype=dtype, device=device))

@@ -18,6 +18,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from ..ops import cross_entropy as ce_ops
+from ..utils.explicit_backward import ExplicitBackward as _ExplicitBackward
 
 
 # ------------------------------------------------------------------------------------------------ helpers
@@ -74,7 +75,7 @@ class CrossEntropyLoss(nn.Module):
         return loss
 
 
-class FusedCrossEntropyLoss(CrossEntropyLoss):
+class FusedCrossEntropyLoss(_ExplicitBackward, CrossEntropyLoss):
     """Same contract; CUDA bf16 logits go through the row kernel (loss + lse in one pass)."""
 
     def forward(self, logits, labels):
@@ -322,6 +323,11 @@ class CLIPLoss(nn.Module):
         t = torch.tensor(math.log(1 / init_temperature))
         self.logit_scale = nn.Parameter(t) if learnable else t
 
+    @property
+    def temperature(self) -> torch.Tensor:
+        """Current soft-max temperature, 1 / exp(logit_scale) (the scale itself is capped at 100)."""
+        return 1.0 / self.logit_scale.exp().clamp(max=100)
+
     def forward(self, image_emb, text_emb):
         a, b = F.normalize(image_emb.float(), dim=-1), F.normalize(text_emb.float(), dim=-1)
         logits = self.logit_scale.exp().clamp(max=100) * a @ b.t()
@@ -505,6 +511,10 @@ class LossRegistry:
     @classmethod
     def available(cls) -> list[str]:
         return sorted(cls._losses)
+
+    # the reference's names for the same two calls (data_pipeline/trainer/loss/sota_losses.py:2909-3000)
+    get = create
+    list_available = available
 
 
 for _n, _c in {"cross_entropy": CrossEntropyLoss, "fused_cross_entropy": FusedCrossEntropyLoss,

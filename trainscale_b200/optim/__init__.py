@@ -532,6 +532,11 @@ class Prodigy(Optimizer):
         super().__init__(params, dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay, d=d0, d0=d0, d_coef=d_coef,
                                       growth_rate=growth_rate, k=0, d_numerator=0.0))
 
+    @property
+    def d(self) -> float:
+        """Current estimate of the step-size scale D."""
+        return float(self.param_groups[0]["d"])
+
     @torch.no_grad()
     def step(self, closure=None):
         loss = closure() if closure is not None else None
@@ -1007,6 +1012,9 @@ class KahanAccumulator:
     @property
     def value(self) -> float:
         return self._sum
+
+    def reset(self, initial: float = 0.0) -> None:
+        self._sum, self._compensation = float(initial), 0.0
 
 
 def stable_softmax(x: torch.Tensor, dim: int = -1) -> torch.Tensor:

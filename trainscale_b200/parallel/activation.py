@@ -954,6 +954,13 @@ class OffloadHandle:
         host.copy_(t.detach(), non_blocking=t.is_cuda)
         return cls(tensor_id, tuple(t.shape), t.dtype, t.device, target, cpu_tensor=host)
 
+    @property
+    def memory_bytes(self) -> int:
+        n = 1
+        for s in self.shape:
+            n *= s
+        return n * torch.empty((), dtype=self.dtype).element_size()
+
     def restore(self) -> torch.Tensor:
         if self.target is OffloadTarget.NVME:
             return torch.load(self.nvme_path, weights_only=True).to(self.device)
@@ -970,6 +977,10 @@ class CheckpointSegment:
         self.children: list[CheckpointSegment] = []
 
     def __len__(self) -> int:
+        return self.end_layer - self.start_layer
+
+    @property
+    def num_layers(self) -> int:
         return self.end_layer - self.start_layer
 
     def __contains__(self, layer: int) -> bool:

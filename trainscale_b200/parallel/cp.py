@@ -558,6 +558,24 @@ class BalancedCPScheduler:
             i += 1
         return out, i
 
+    def get_groups_and_subsamples(self, sample_id_seqlens: list[tuple[int, int]], config: "HybridCPConfig | None" = None):
+        """Cut a batch of (sample id, length) into successive groups that each fill the world once; inside a group
+        the samples are balanced over the GPUs by `schedule`.  Returns (groups, sample_id_groups): groups[g][gpu] is
+        that GPU's list of (sample id, cp degree) in group g, sample_id_groups[g][gpu] the sample ids alone
+        (data_pipeline/trainer/distributed/hybrid_cp_scheduler.py:580-621)."""
+        sched = self if config is None else BalancedCPScheduler(config)
+        items = sorted(sample_id_seqlens, key=lambda t: -t[1])              # longest first packs best
+        lengths = [l for _, l in items]
+        groups, id_groups, start = [], [], 0
+        while start < len(items):
+            chosen, nxt = sched.next_hdp_group(lengths, start)
+            idx = [i for i, _ in chosen]
+            plan = sched.schedule([lengths[i] for i in idx])
+            groups.append([[(items[idx[j]][0], cp) for j, cp in gpu] for gpu in plan])
+            id_groups.append([[sid for sid, _ in gpu] for gpu in groups[-1]])
+            start = nxt
+        return groups, id_groups
+
     def _trim_overloaded(self, plan: list[list[tuple[int, int]]], lengths: list[int], tolerance: float = 1.25):
         """Moves single-GPU sequences off GPUs whose load exceeds tolerance x mean onto the least loaded GPU."""
         def load(g):

@@ -68,6 +68,25 @@ class DDPConfig:
     def resolved_bucket_mb(self) -> int:
         return self.bucket_cap_mb or BUCKET_MB[detect_gpu_topology()][0]
 
+    @classmethod
+    def from_dict(cls, config_dict: dict) -> "Result":
+        """Ok(DDPConfig) from a plain mapping (YAML section): enum fields accept their names or values in any case,
+        unknown keys are an Err(ValueError) rather than silently dropped."""
+        import dataclasses
+        fields = {f.name: f for f in dataclasses.fields(cls)}
+        unknown = sorted(set(config_dict) - set(fields))
+        if unknown:
+            return Err(ValueError(f"unknown DDP options: {unknown}"))
+        kw = dict(config_dict)
+        try:
+            if isinstance(kw.get("gradient_compression"), str):
+                v = kw["gradient_compression"]
+                kw["gradient_compression"] = (GradientCompression[v.upper()] if v.upper() in GradientCompression.__members__
+                                              else GradientCompression(v.lower()))
+            return Ok(cls(**kw))
+        except (KeyError, ValueError, TypeError) as e:
+            return Err(ValueError(f"invalid DDP configuration: {e}"))
+
 
 # ------------------------------------------------------------------------------------------------ hooks: bucket -> averaged bucket
 def allreduce_hook(group, bucket: torch.Tensor) -> torch.Tensor:
@@ -417,6 +436,18 @@ class HierarchicalAllReduceManager:
         dist.broadcast(t, self.leader, group=self.intra)
         return t.div_(self.world)
 
+    def create_comm_hook(self):
+        """Two forms of the same reduction.  `hook(group, flat_bucket) -> averaged bucket` is what the bucket engines of
+        this module take; `hook(state, bucket)` with a torch `GradBucket` returns a completed Future of the averaged
+        buffer, the signature of `DistributedDataParallel.register_comm_hook`."""
+        def hook(state, bucket):
+            if torch.is_tensor(bucket):
+                return self.all_reduce(bucket)
+            fut = torch.futures.Future()
+            fut.set_result(self.all_reduce(bucket.buffer()))
+            return fut
+        return hook
+
 
 class SOTADDPEngine:
     def __init__(self, config: DDPConfig | None = None, **kw):
@@ -518,6 +549,14 @@ class DDPInitializer:
         except Exception as e:   # noqa: BLE001
             return Err(e)
 
+    @staticmethod
+    def destroy_process_group() -> None:
+        """Tear the default group down if there is one (after a barrier-free wait for this rank's own work)."""
+        if dist.is_available() and dist.is_initialized():
+            if torch.cuda.is_available():
+                torch.cuda.synchronize()
+            dist.destroy_process_group()
+
 
 def create_ddp_engine(**kw) -> Result:
     try:
@@ -565,9 +604,17 @@ class GradientCompressionHook:
     def decompress(self, payload: torch.Tensor, like: torch.Tensor) -> torch.Tensor:
         return payload.to(like.dtype)
 
+    @property
+    def metrics(self) -> DDPMetrics:
+        """Bytes put on the wire (after compression) and the compression ratio of the last bucket."""
+        return self._metrics
+
     def __call__(self, group, bucket: torch.Tensor) -> torch.Tensor:
         group = group if group is not None else self._process_group
         payload = self.compress(bucket)
+        sent = payload.numel() * payload.element_size()
+        self._metrics.record_allreduce(sent, None)
+        self._metrics.compression_ratio = bucket.numel() * bucket.element_size() / max(sent, 1)
         if self._world_size > 1:
             dist.all_reduce(payload, group=group)
         bucket.copy_(self.decompress(payload, bucket).div_(self._world_size))

@@ -25,6 +25,10 @@ class DistributedBackend(Enum):
     GLOO = "gloo"
     NONE = "none"
 
+    def to_torch_backend(self) -> str | None:
+        """Name for `torch.distributed.init_process_group` (None for NONE: no process group)."""
+        return None if self is DistributedBackend.NONE else self.value
+
 
 @dataclass
 class DistributedConfig:
@@ -35,6 +39,17 @@ class DistributedConfig:
     powersgd_rank: int = 4
     topk_ratio: float = 0.01
     average: bool = True
+    tp_size: int = 1
+    pp_size: int = 1
+    dp_size: int = 1
+
+    def validate_topology(self, world_size: int | None = None) -> None:
+        """tp x pp x dp must equal the world size (the job's, when not given); ValueError otherwise."""
+        w = world_size if world_size is not None else (dist.get_world_size() if _on() else 1)
+        if min(self.tp_size, self.pp_size, self.dp_size) < 1:
+            raise ValueError("parallel sizes must be >= 1")
+        if self.tp_size * self.pp_size * self.dp_size != w:
+            raise ValueError(f"tp ({self.tp_size}) x pp ({self.pp_size}) x dp ({self.dp_size}) != world size ({w})")
 
 
 def _on() -> bool:
@@ -86,6 +101,24 @@ class CommStreamManager:
     def synchronize_all(self) -> None:
         for s in self._streams:
             torch.cuda.current_stream(self.device).wait_stream(s)
+
+    # ---- event form of the same two edges, for code that picks its own stream
+    def record_compute_event(self):
+        """Mark "compute has produced its data" on the current stream; a side stream then waits for the returned event
+        (`stream.wait_event(ev)`) instead of for the whole stream.  None without a GPU."""
+        if not self._streams:
+            return None
+        ev = torch.cuda.Event()
+        ev.record(torch.cuda.current_stream(self.device))
+        return ev
+
+    def sync_back_to_compute(self, stream=None) -> None:
+        """The current (compute) stream waits for what was queued on `stream` (default: every side stream)."""
+        if not self._streams:
+            return
+        cur = torch.cuda.current_stream(self.device)
+        for s in ([stream] if stream is not None else self._streams):
+            cur.wait_stream(s)
 
 
 _MANAGER: CommStreamManager | None = None

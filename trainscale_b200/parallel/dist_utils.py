@@ -533,6 +533,30 @@ class GradientSynchronizer:
             return contextlib.nullcontext()
         return self.engine.no_sync()
 
+    def sync_gradients(self, group=None, average: bool = True) -> None:
+        """Reduce the gradients now.  An engine with its own reduction (`reduce_gradients` / `sync_gradients`) does it;
+        for a plain module the gradients are flattened per dtype, all-reduced in one call each and averaged."""
+        for name in ("reduce_gradients", "sync_gradients", "finish_gradient_synchronization"):
+            fn = getattr(self.engine, name, None)
+            if callable(fn):
+                fn()
+                return
+        if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size(group) == 1:
+            return
+        by_dtype: dict = {}
+        for p in self.engine.parameters():
+            if p.grad is not None:
+                by_dtype.setdefault(p.grad.dtype, []).append(p.grad)
+        for grads in by_dtype.values():
+            flat = torch.cat([g.reshape(-1) for g in grads])
+            dist.all_reduce(flat, group=group)
+            if average:
+                flat /= dist.get_world_size(group)
+            off = 0
+            for g in grads:
+                g.copy_(flat[off:off + g.numel()].view_as(g))
+                off += g.numel()
+
 
 class DistributedManager:
     """Process-wide entry point: process-group initialisation, model wrapping into the flat engine, thin collective
@@ -707,6 +731,15 @@ class HardwareTopology:
     def fully_connected(self) -> bool:
         return self.num_gpus > 1 and all(all(r) for r in self.peer_access)
 
+    @property
+    def total_gpus(self) -> int:
+        return self.num_gpus
+
+    @property
+    def has_nvlink(self) -> bool:
+        """Some pair of GPUs reads each other's memory directly (peer access), which on these machines is NVLink."""
+        return any(ok for i, row in enumerate(self.peer_access) for j, ok in enumerate(row) if i != j)
+
     def recommended_bucket_mb(self) -> int:
         from .ddp import BUCKET_MB, detect_gpu_topology
         return BUCKET_MB[detect_gpu_topology()][0]
@@ -736,6 +769,11 @@ class DistributedLogger:
 
     def warning(self, msg: str, *a) -> None:
         self._emit(logging.WARNING, msg, *a)
+
+    def metric(self, name: str, value: float, unit: str = "") -> None:
+        """One machine-readable line: METRIC|<ns timestamp>|<name>|<value>|<unit>|rank=<r>."""
+        import time
+        self._emit(logging.INFO, "METRIC|%d|%s|%s|%s|rank=%d", time.time_ns(), name, value, unit, self._rank())
 
     def error(self, msg: str, *a) -> None:          # errors are never silenced
         self._log.error(f"[rank {self._rank()}] {msg}", *a)

@@ -40,6 +40,21 @@ class ExpertParallelConfig:
     num_shared_experts: int = 0
     normalize_topk: bool = True
     jitter: float = 0.0
+    expert_parallel_group: object = None   # process group the experts are spread over (None: the default group)
+    use_fp32_router: bool = True
+
+    @property
+    def num_local_experts(self) -> int:
+        """Experts held by each rank of the expert-parallel group."""
+        w = get_expert_parallel_world_size(self.expert_parallel_group)
+        if self.num_experts % w:
+            raise ValueError(f"num_experts ({self.num_experts}) must be divisible by the group size ({w})")
+        return self.num_experts // w
+
+    @property
+    def local_expert_offset(self) -> int:
+        """Global index of this rank's first expert."""
+        return get_expert_parallel_rank(self.expert_parallel_group) * self.num_local_experts
 
 
 def moe_capacity(tokens: int, num_experts: int, top_k: int, capacity_factor: float, min_capacity: int = 4) -> int:
@@ -318,7 +333,13 @@ class ExpertParallelMoE(MoELayer):
         y = self.route_and_run(x2, self._distributed)
         for s in self.shared:
             y = y + s(x2)
+        self.__dict__["_forward_count"] = self.__dict__.get("_forward_count", 0) + 1
         return y.view(shp)
+
+    def get_routing_statistics(self) -> dict:
+        return {"forward_count": self.__dict__.get("_forward_count", 0), "num_experts": self.cfg.num_experts,
+                "num_local_experts": self.dispatcher.local_experts, "top_k": self.cfg.top_k,
+                "aux_loss": float(self.aux_loss.detach()) if torch.is_tensor(self.aux_loss) else float(self.aux_loss)}
 
 
 class HierarchicalMoE(nn.Module):
@@ -648,6 +669,36 @@ class RouterBase(nn.Module):
         """logits [T, E] -> (weights [T, k], experts [T, k], probs [T, E]); top-k soft-max by default."""
         from ..ops import moe as moe_ops
         return moe_ops.topk_softmax(logits, self.config.top_k, self.config.normalize_topk)
+
+    def compute_router_logits(self, hidden_states: torch.Tensor) -> torch.Tensor:
+        """[..., H] -> [..., E]; in fp32 (input and weight upcast) when `use_fp32_router`: the soft-max over experts is
+        sensitive to bf16 rounding of near-tied logits."""
+        if getattr(self.config, "use_fp32_router", True) and hidden_states.dtype != torch.float32:
+            return F.linear(hidden_states.float(), self.router.weight.float())
+        return self.router(hidden_states)
+
+    def compute_auxiliary_loss(self, router_logits: torch.Tensor, expert_mask: torch.Tensor, num_experts: int | None = None):
+        """(weighted total, {name: unweighted term}) from raw logits [T, E] and the 0/1 mask of chosen experts [T, E]:
+        `load_balance` = E sum_e f_e P_e always; `router_z_loss` = mean logsumexp^2 for ST-MoE and GShard;
+        `importance_loss` = CV^2 of the per-expert probability mass for GShard and V-MoE
+        (data_pipeline/trainer/distributed/expert_parallel.py:548-610)."""
+        cfg, kind = self.config, self.loss_type
+        E = num_experts or router_logits.shape[-1]
+        logits = router_logits.float().reshape(-1, router_logits.shape[-1])
+        probs = logits.softmax(-1)
+        f = expert_mask.float().reshape(-1, expert_mask.shape[-1]).sum(0) / max(logits.shape[0], 1)
+        terms = {"load_balance": E * (f * probs.mean(0)).sum()}
+        if kind in (LoadBalanceLossType.STMOE, LoadBalanceLossType.GSHARD):
+            terms["router_z_loss"] = torch.logsumexp(logits, -1).pow(2).mean()
+        if kind in (LoadBalanceLossType.GSHARD, LoadBalanceLossType.VMOE):
+            imp = probs.sum(0)
+            terms["importance_loss"] = (imp.std() / (imp.mean() + 1e-9)) ** 2
+        total = cfg.aux_loss_weight * terms["load_balance"]
+        if "router_z_loss" in terms:
+            total = total + cfg.z_loss_weight * terms["router_z_loss"]
+        if "importance_loss" in terms:
+            total = total + cfg.aux_loss_weight * terms["importance_loss"]
+        return total, terms
 
     def forward(self, x: torch.Tensor) -> RoutingOutput:
         cfg = self.config

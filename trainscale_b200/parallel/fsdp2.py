@@ -48,6 +48,11 @@ class ComputeCapability(NamedTuple):
         return self.major >= 9
 
     @property
+    def supports_flash_attention_v2(self) -> bool:
+        """Flash-style attention needs Ampere or newer; the framework's own tcgen05 kernels need major == 10."""
+        return self.major >= 8
+
+    @property
     def supports_tcgen05(self) -> bool:
         return self.major == 10
 
@@ -71,6 +76,11 @@ class HardwareInfo:
     @property
     def is_blackwell(self) -> bool:
         return self.capability.major == 10
+
+    @property
+    def is_amd(self) -> bool:
+        """Always False: this framework is written for NVIDIA sm_100a only."""
+        return False
 
 
 def detect_hardware(device_id: int = 0) -> Result:

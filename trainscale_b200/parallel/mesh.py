@@ -508,6 +508,16 @@ class MemoryEstimator:
     def fits(bytes_needed: int, capacity_gb: float = 180.0, headroom: float = 0.92) -> bool:
         return bytes_needed <= capacity_gb * 2 ** 30 * headroom
 
+    @staticmethod
+    def check_memory_fit(available_memory_bytes: int, estimated_memory_bytes: int, safety_margin: float = 0.9):
+        """Ok(None) when the estimate fits `safety_margin` of the available bytes, else Err(MemoryError) with both."""
+        from ..core.types import Err, Ok
+        usable = int(available_memory_bytes * safety_margin)
+        if estimated_memory_bytes > usable:
+            return Err(MemoryError(f"estimated {estimated_memory_bytes / 2 ** 30:.2f} GiB exceeds the usable "
+                                   f"{usable / 2 ** 30:.2f} GiB"))
+        return Ok(None)
+
 
 class CommAlgorithmSelector:
     """Which implementation a collective of a given size should use on an NVSwitch box: small messages are launch-bound
@@ -535,6 +545,38 @@ class CommAlgorithmSelector:
         """Gradient bucket size: collective cost on NVSwitch is latency- not link-bound, so buckets only need to
         amortise a launch (tens of MB)."""
         return (80 << 20) if self.nvswitch else (25 << 20)
+
+    # ---- library-level choice (data_pipeline/trainer/distributed/parallel_dims.py:969-1040).  Nothing is set here:
+    # `get_nccl_env_vars` RETURNS the variables a launcher may export before the process group is created.
+    @staticmethod
+    def select_allreduce_algorithm(message_size_bytes: int, num_devices: int, interconnect=None,
+                                   has_nvswitch: bool = False) -> "CommunicationAlgorithm":
+        """Behind a switch the library's own choice stands (it reduces inside the switch when it can, which beats any
+        ring or tree).  Without one: a tree for latency-bound messages (< 256 KiB) or many devices, a ring for
+        bandwidth-bound ones (> 4 MiB), the library's choice in between."""
+        if num_devices <= 1:
+            return CommunicationAlgorithm.AUTO
+        if has_nvswitch:
+            return CommunicationAlgorithm.NCCL_AUTO
+        if message_size_bytes < 256 * 1024:
+            return CommunicationAlgorithm.TREE
+        if message_size_bytes > 4 * 1024 * 1024:
+            return CommunicationAlgorithm.RING
+        return CommunicationAlgorithm.NCCL_AUTO
+
+    @staticmethod
+    def get_nccl_env_vars(algorithm: "CommunicationAlgorithm", interconnect=None) -> dict:
+        env: dict[str, str] = {}
+        if interconnect in (InterconnectType.NVLINK3, InterconnectType.NVLINK4, InterconnectType.NVLINK5):
+            env["NCCL_P2P_LEVEL"] = "NVL"
+        if interconnect in (InterconnectType.INFINIBAND_HDR, InterconnectType.INFINIBAND_NDR):
+            env["NCCL_IB_DISABLE"] = "0"
+            env["NCCL_NET_GDR_LEVEL"] = "5"
+        if algorithm == CommunicationAlgorithm.RING:
+            env["NCCL_ALGO"] = "Ring"
+        elif algorithm == CommunicationAlgorithm.TREE:
+            env["NCCL_ALGO"] = "Tree"
+        return env
 
 
 # ------------------------------------------------------------------------------------------------ typed topology records

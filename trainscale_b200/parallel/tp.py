@@ -23,6 +23,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from ..ops import gemm
+from ..utils.explicit_backward import ExplicitBackward as _ExplicitBackward
 
 
 @dataclass
@@ -283,7 +284,7 @@ def vocab_parallel_cross_entropy(logits_local: torch.Tensor, labels: torch.Tenso
     return _VocabParallelCE.apply(logits_local, labels, tp, vocab_start, ignore_index)
 
 
-class VocabParallelCrossEntropyLoss(nn.Module):
+class VocabParallelCrossEntropyLoss(_ExplicitBackward, nn.Module):
     def __init__(self, tp: TPContext, vocab_start: int, ignore_index: int = -100, reduction: str = "mean"):
         super().__init__()
         self.tp, self.vocab_start, self.ignore_index, self.reduction = tp, vocab_start, ignore_index, reduction

@@ -82,8 +82,39 @@ def left_pack_padding(ids: torch.Tensor, mask: torch.Tensor, pad_id: int = 0):
 
 
 class GRPOCompute:
-    def __init__(self, group_size: int = 8, clip: float = 0.2, beta: float = 0.01, variant: str = "grpo"):
+    def __init__(self, group_size: int = 8, clip: float = 0.2, beta: float = 0.01, variant: str = "grpo",
+                 model: nn.Module | None = None, reward_clip: float | None = None, chunk_tokens: int = 4096):
         self.group_size, self.clip, self.beta, self.variant = group_size, clip, beta, variant
+        self.model, self.reward_clip, self.chunk_tokens = model, reward_clip, chunk_tokens
+
+    def compute_log_probs(self, input_ids: torch.Tensor, attention_mask: torch.Tensor | None = None,
+                          model: nn.Module | None = None) -> torch.Tensor:
+        """log p(token t+1 | tokens <= t) for every position, [B, S-1] (0 where the target is padding), without ever
+        forming [B, S, V] logits: the decoder's hidden states go through the chunked fused head
+        (data_pipeline/trainer/rl_training.py:509-552)."""
+        model = model if model is not None else self.model
+        if model is None:
+            raise ValueError("compute_log_probs needs a model (argument or constructor)")
+        out = model(input_ids=input_ids, return_logits=False)
+        labels = input_ids[:, 1:]
+        if attention_mask is not None:
+            labels = labels.masked_fill(attention_mask[:, 1:] == 0, -100)
+        return chunked_log_softmax(out.hidden_states[:, :-1], model.head_weight, labels, self.chunk_tokens)
+
+    def compute_grpo_loss(self, policy_log_probs, ref_log_probs, rewards, mask, old_log_probs=None):
+        """(loss, {"reward_mean", "reward_std", "advantage_abs_mean", "kl"}) for the configured variant.  Without
+        `old_log_probs` the policy's own (detached) values are the behaviour policy: one optimisation step per batch."""
+        if self.reward_clip:
+            rewards = rewards.clamp(-self.reward_clip, self.reward_clip)
+        old = policy_log_probs.detach() if old_log_probs is None else old_log_probs
+        loss = self(policy_log_probs, old, ref_log_probs, rewards, mask)
+        adv = compute_advantages(rewards, self.group_size, scale=self.variant != "drgrpo")
+        stats = {"reward_mean": float(rewards.float().mean()), "reward_std": float(rewards.float().std()),
+                 "advantage_abs_mean": float(adv.abs().mean())}
+        if ref_log_probs is not None:
+            d = (ref_log_probs - policy_log_probs).detach()
+            stats["kl"] = float(_masked_mean(torch.exp(d) - d - 1, mask))
+        return loss, stats
 
     def __call__(self, logp, old_logp, ref_logp, rewards, mask):
         adv = compute_advantages(rewards, self.group_size, scale=self.variant != "drgrpo")

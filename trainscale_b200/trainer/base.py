@@ -192,6 +192,11 @@ class PretrainingTrainer(Trainer):
         self.ema = copy.deepcopy(self.model).eval() if ema_decay else None
         self.curriculum = curriculum   # (start_len, end_len, ramp_steps)
 
+    @property
+    def ema_model(self):
+        """The exponential-moving-average copy of the weights (None when `ema_decay` is not set)."""
+        return self.ema
+
     def current_seq_len(self) -> int | None:
         if not self.curriculum:
             return None
@@ -241,6 +246,31 @@ class Seq2SeqTrainer(Trainer):
             return out.loss
         logits = out.logits if hasattr(out, "logits") else out
         return F.cross_entropy(logits.reshape(-1, logits.shape[-1]).float(), batch["labels"].reshape(-1), ignore_index=-100)
+
+    @torch.no_grad()
+    def generate(self, inputs: dict, max_length: int = 128, num_beams: int | None = None,
+                 decoder_start_token_id: int = 1, eos_token_id: int | None = None) -> torch.Tensor:
+        """Decoder ids for an encoder-decoder model: the model's own `generate` when it has one (beam search and the
+        rest), else greedy decoding that feeds `decoder_input_ids` back (data_pipeline/trainer/trainers/__init__.py:242)."""
+        self.model.eval()
+        inputs = self._to_device(inputs)
+        if hasattr(self.model, "generate"):
+            kw = {"num_beams": num_beams} if num_beams else {}
+            return self.model.generate(**inputs, max_length=max_length, **kw)
+        B = inputs["input_ids"].shape[0]
+        dec = torch.full((B, 1), decoder_start_token_id, dtype=torch.long, device=self.device)
+        done = torch.zeros(B, dtype=torch.bool, device=self.device)
+        for _ in range(max_length - 1):
+            out = self.model(**inputs, decoder_input_ids=dec)
+            logits = out.logits if hasattr(out, "logits") else out[0] if isinstance(out, tuple) else out
+            nxt = logits[:, -1].argmax(-1)
+            if eos_token_id is not None:
+                nxt = torch.where(done, torch.full_like(nxt, eos_token_id), nxt)
+                done |= nxt == eos_token_id
+            dec = torch.cat((dec, nxt[:, None]), 1)
+            if eos_token_id is not None and bool(done.all()):
+                break
+        return dec
 
 
 class TextGenerationTrainer(Trainer):

@@ -69,6 +69,11 @@ class TrainingState:
     max_steps: int = 0
     tokens_seen: int = 0
 
+    def with_update(self, **kwargs) -> "TrainingState":
+        """A copy with the given fields replaced (the state object of a running trainer is not touched)."""
+        import dataclasses
+        return dataclasses.replace(self, **kwargs)
+
 
 def set_seed(seed: int, rank: int = 0, deterministic: bool = False) -> None:
     """seed + rank for python / numpy / torch (data_pipeline/trainer/distributed/sota_utils.py:1731-1768)."""
