@@ -21,7 +21,7 @@ def test_norms_activations_losses_match_torch():
     x, r, w, b = torch.randn(6, 64), torch.randn(6, 64), torch.rand(64) + 0.5, torch.randn(64)
     rms = lambda t: t * torch.rsqrt(t.pow(2).mean(-1, keepdim=True) + 1e-6) * w      # noqa: E731
     torch.testing.assert_close(K.fast_rms_layernorm(x, w), rms(x))
-    y, res = K.fused_add_rms_layernorm(x, r, w)
+    y, res = K.fused_add_rms_layernorm(x, r, w, return_residual=True)
     torch.testing.assert_close(res, x + r)
     torch.testing.assert_close(y, rms(x + r))
     torch.testing.assert_close(K.fused_layer_norm(x, w, b), F.layer_norm(x, (64,), w, b))

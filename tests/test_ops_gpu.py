@@ -436,7 +436,7 @@ def test_kernel_layer_entry_points_on_gpu():
     x, r = torch.randn(512, 1024, device=dev, dtype=dt), torch.randn(512, 1024, device=dev, dtype=dt)
     w = (torch.rand(1024, device=dev) + 0.5).to(dt)
     xf, rf, wf = x.float(), r.float(), w.float()
-    y, res = K.fused_add_rms_layernorm(x, r, w)
+    y, res = K.fused_add_rms_layernorm(x, r, w, return_residual=True)
     h = xf + rf
     torch.testing.assert_close(y.float(), h * torch.rsqrt(h.pow(2).mean(-1, keepdim=True) + 1e-6) * wf, rtol=2e-2, atol=2e-2)
     torch.testing.assert_close(K.fused_softmax(x).float(), torch.softmax(xf, -1), rtol=2e-2, atol=1e-4)

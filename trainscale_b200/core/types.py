@@ -7,6 +7,7 @@ from __future__ import annotations
 
 from dataclasses import dataclass
 from typing import Callable, Generic, TypeVar, Union
+from ..utils.refargs import ANY, reference_kwargs
 
 T = TypeVar("T")
 U = TypeVar("U")
@@ -77,40 +78,49 @@ class Err(Generic[E]):
 Result = Union[Ok[T], Err[E]]
 
 
+@reference_kwargs(result="r")
 def is_ok(r) -> bool:
     return isinstance(r, Ok)
 
 
+@reference_kwargs(result="r")
 def is_err(r) -> bool:
     return isinstance(r, Err)
 
 
+@reference_kwargs(result="r")
 def unwrap(r):
     return r.unwrap()
 
 
+@reference_kwargs(result="r")
 def unwrap_err(r):
     if isinstance(r, Err):
         return r.error
     raise ValueError(f"called unwrap_err on Ok: {r.value!r}")
 
 
+@reference_kwargs(result="r")
 def unwrap_or(r, default):
     return r.value if isinstance(r, Ok) else default
 
 
+@reference_kwargs(result="r", f="fn")
 def unwrap_or_else(r, fn: Callable):
     return r.value if isinstance(r, Ok) else fn(r.error)
 
 
+@reference_kwargs(result="r", f="fn")
 def map_result(r, fn: Callable):
     return Ok(fn(r.value)) if isinstance(r, Ok) else r
 
 
+@reference_kwargs(result="r", f="fn")
 def flat_map(r, fn: Callable):
     return fn(r.value) if isinstance(r, Ok) else r
 
 
+@reference_kwargs(result="r", f="fn")
 def map_err(r, fn: Callable):
     return Err(fn(r.error)) if isinstance(r, Err) else r
 

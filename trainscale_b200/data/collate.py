@@ -8,10 +8,12 @@ from __future__ import annotations
 from typing import Mapping, Sequence
 
 import torch
+from ..utils.refargs import ANY, reference_kwargs
 
 from ..core.errors import CollationError
 
 
+@reference_kwargs(sequences="seqs", padding_value="pad_value")
 def pad_sequence_right(seqs: Sequence[torch.Tensor], pad_value: int, max_length: int | None = None) -> torch.Tensor:
     n = max_length or max(len(s) for s in seqs)
     out = torch.full((len(seqs), n), pad_value, dtype=seqs[0].dtype)
@@ -21,6 +23,7 @@ def pad_sequence_right(seqs: Sequence[torch.Tensor], pad_value: int, max_length:
     return out
 
 
+@reference_kwargs(sequences="seqs", padding_value="pad_value")
 def pad_sequence_left(seqs: Sequence[torch.Tensor], pad_value: int, max_length: int | None = None) -> torch.Tensor:
     n = max_length or max(len(s) for s in seqs)
     out = torch.full((len(seqs), n), pad_value, dtype=seqs[0].dtype)

@@ -19,6 +19,8 @@ from typing import Callable, Mapping, Sequence
 
 import torch
 
+from ..utils.refargs import ANY, reference_kwargs
+
 from ..config.data_schema import ContentDistributionMode, PaddingStrategy, TruncationStrategy
 
 DEFAULT_BUCKETS = (64, 128, 256, 512, 1024, 2048, 4096)
@@ -109,14 +111,17 @@ def _last_boundary(text: str, pattern: re.Pattern, limit: int) -> int:
     return pos
 
 
+@reference_kwargs(max_chars="limit")
 def find_sentence_boundary(text: str, limit: int) -> int:
     return _last_boundary(text, _SENT, limit)
 
 
+@reference_kwargs(max_chars="limit")
 def find_clause_boundary(text: str, limit: int) -> int:
     return _last_boundary(text, _CLAUSE, limit)
 
 
+@reference_kwargs(max_chars="limit")
 def find_word_boundary(text: str, limit: int) -> int:
     return _last_boundary(text, _WORD, limit)
 
@@ -383,11 +388,16 @@ class LengthManager:
         return n
 
 
+@reference_kwargs(label_pad_token_id="label_pad")
 def create_dynamic_collate_fn(length_manager: LengthManager, pad_token_id: int = 0, label_pad: int = -100,
-                              padding_side: str = "right") -> Callable:
-    """Collate that pads (or crops) every `*input_ids / *attention_mask / *labels` key to the batch's effective length."""
+                              padding_side: str = "right", additional_pad_keys: Mapping[str, int] | None = None) -> Callable:
+    """Collate that pads (or crops) every `*input_ids / *attention_mask / *labels` key to the batch's effective length;
+    `additional_pad_keys` = {key: fill value} for other sequence-valued keys (e.g. token_type_ids)."""
+    extra = dict(additional_pad_keys or {})
 
     def pad_value(key: str) -> int:
+        if key in extra:
+            return extra[key]
         if key.endswith("labels"):
             return label_pad
         if key.endswith("attention_mask"):
@@ -428,13 +438,24 @@ def create_length_manager(max_total_length: int = 2048, padding_strategy="max_le
     return LengthManager(cfg, tokenizer)
 
 
+@reference_kwargs(distribution_mode="mode")
 def create_content_distributor(mode="proportional", max_length: int = 2048, column_ratios: Mapping[str, float] | None = None,
                                label_columns: Sequence[str] = (), priorities: Mapping[str, int] | None = None,
-                               special_tokens_budget: int = 10, tokenizer=None) -> TokenAwareContentDistributor:
+                               special_tokens_budget: int = 10, tokenizer=None,
+                               column_configs: Mapping[str, ColumnContentConfig] | None = None,
+                               default_truncation: TruncationStrategy | str | None = None,
+                               chars_per_token: float = CHARS_PER_TOKEN) -> TokenAwareContentDistributor:
+    """`column_configs` ({name: ColumnContentConfig}) gives full per-column settings and wins over the short forms
+    (ratios, label columns, priorities); `default_truncation` applies to columns built from the short forms."""
     names = set(column_ratios or {}) | set(label_columns) | set(priorities or {})
-    cols = [ColumnContentConfig(n, priority=(priorities or {}).get(n, 0), ratio=(column_ratios or {}).get(n),
-                                is_label=n in label_columns) for n in names]
-    return TokenAwareContentDistributor(ContentDistributionMode(mode), max_length, cols, special_tokens_budget, tokenizer)
+    trunc = TruncationStrategy(default_truncation) if default_truncation is not None else TruncationStrategy.SMART
+    cols = {n: ColumnContentConfig(n, priority=(priorities or {}).get(n, 0), ratio=(column_ratios or {}).get(n),
+                                   is_label=n in label_columns, truncation=trunc) for n in names}
+    for n, c in (column_configs or {}).items():
+        cols[n] = c if c.name == n else ColumnContentConfig(**{**c.__dict__, "name": n})
+    mode = getattr(mode, "value", mode)
+    return TokenAwareContentDistributor(ContentDistributionMode(mode), max_length, list(cols.values()),
+                                        special_tokens_budget, tokenizer, chars_per_token)
 
 
 def saturating_sub(a: int, b: int) -> int:

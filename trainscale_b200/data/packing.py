@@ -10,9 +10,11 @@ from __future__ import annotations
 from typing import Sequence
 
 import torch
+from ..utils.refargs import ANY, reference_kwargs
 from torch.utils.data import Dataset
 
 
+@reference_kwargs(max_capacity="max_length")
 def first_fit_decreasing(lengths: Sequence[int], max_length: int) -> list[list[int]]:
     order = sorted(range(len(lengths)), key=lambda i: -lengths[i])
     bins, free = [], []
@@ -29,8 +31,22 @@ def first_fit_decreasing(lengths: Sequence[int], max_length: int) -> list[list[i
     return bins
 
 
-def pack_sequences(sequences: Sequence[dict], max_length: int, pad_token_id: int = 0, label_pad: int = -100) -> list[dict]:
-    """Each input dict holds 1-D `input_ids` (and optionally `labels`); returns packed dicts of tensors."""
+@reference_kwargs(max_seq_len="max_length", label_pad_id="label_pad")
+def pack_sequences(sequences: Sequence[dict] | None = None, max_length: int = 2048, pad_token_id: int = 0,
+                   label_pad: int = -100, *, input_ids=None, attention_mask=None, labels=None) -> list[dict]:
+    """Each input dict holds 1-D `input_ids` (and optionally `labels`); returns packed dicts of tensors.  The
+    reference's column form is taken too: `input_ids` / `attention_mask` / `labels` as lists (or padded [N, L] tensors)
+    of the N sequences, the mask giving each row's real length."""
+    if sequences is None or input_ids is not None or (torch.is_tensor(sequences) and sequences.dim() == 2):
+        ids = input_ids if input_ids is not None else sequences
+        rows = []
+        for i in range(len(ids)):
+            n = int(torch.as_tensor(attention_mask[i]).sum()) if attention_mask is not None else len(ids[i])
+            row = {"input_ids": torch.as_tensor(ids[i])[:n]}
+            if labels is not None:
+                row["labels"] = torch.as_tensor(labels[i])[:n]
+            rows.append(row)
+        sequences = rows
     lengths = [min(len(s["input_ids"]), max_length) for s in sequences]
     out = []
     for b in first_fit_decreasing(lengths, max_length):
@@ -58,6 +74,7 @@ def pack_sequences(sequences: Sequence[dict], max_length: int, pad_token_id: int
     return out
 
 
+@reference_kwargs(max_seq_len="total_length")
 def create_packed_attention_mask(cu_seqlens: torch.Tensor, total_length: int, dtype=torch.float32) -> torch.Tensor:
     """Block-diagonal causal additive mask [L, L]: 0 where attention is allowed, -inf elsewhere."""
     m = torch.full((total_length, total_length), float("-inf"), dtype=dtype)
@@ -68,9 +85,15 @@ def create_packed_attention_mask(cu_seqlens: torch.Tensor, total_length: int, dt
     return m
 
 
-def unpack_sequences(packed: torch.Tensor, cu_seqlens: torch.Tensor) -> list[torch.Tensor]:
+@reference_kwargs(packed_output="packed")
+def unpack_sequences(packed: torch.Tensor, cu_seqlens: torch.Tensor, original_lengths=None) -> list[torch.Tensor]:
+    """Cut a packed row back into its sequences.  `original_lengths` (one per sequence) crops each piece to its
+    length before packing (pieces are never longer than their segment)."""
     cu = cu_seqlens.tolist()
-    return [packed[..., a:b, :] if packed.dim() > 1 else packed[a:b] for a, b in zip(cu[:-1], cu[1:])]
+    out = [packed[..., a:b, :] if packed.dim() > 1 else packed[a:b] for a, b in zip(cu[:-1], cu[1:])]
+    if original_lengths is not None:
+        out = [(o[..., :int(n), :] if o.dim() > 1 else o[:int(n)]) for o, n in zip(out, original_lengths)]
+    return out
 
 
 class PackedDataset(Dataset):
@@ -103,6 +126,7 @@ def cu_seqlens_from_document_ids(document_ids: torch.Tensor) -> tuple[torch.Tens
     return cu, int((cu[1:] - cu[:-1]).max())
 
 
+@reference_kwargs(max_seq_len="max_length")
 def get_packing_stats(lengths: Sequence[int], max_length: int) -> dict:
     bins = first_fit_decreasing(lengths, max_length)
     used = sum(min(n, max_length) for n in lengths)

@@ -21,7 +21,7 @@ import torch
 
 from ..config.data_schema import (FIMMode, FineTuningFormat, PackingConfig, PackingStrategy, PreTrainingFormat,
                                   PromptEngineConfig, PromptTemplate, RLAlgorithm, TrainingStage)
-from ..core.errors import TemplateRenderError, TokenizationError
+from ..core.errors import PipelineError, TemplateRenderError, TokenizationError
 from .tokenization import TokenizerWrapper
 
 IGNORE = -100
@@ -113,9 +113,10 @@ class GRPOExample:
 _VAR = re.compile(r"\{([A-Za-z_][A-Za-z0-9_]*)\}")
 
 
-def render_template(template: str, variables: Mapping[str, Any]) -> str:
-    """Jinja2 when the template uses `{{` / `{%`, else `{var}` substitution; a missing variable is an error."""
-    if "{{" in template or "{%" in template:
+def render_template(template: str, variables: Mapping[str, Any], use_jinja: bool | None = None) -> str:
+    """Jinja2 when the template uses `{{` / `{%` (or `use_jinja=True`), else `{var}` substitution (`use_jinja=False`
+    forces it); a missing variable is an error."""
+    if use_jinja or (use_jinja is None and ("{{" in template or "{%" in template)):
         try:
             import jinja2
             return jinja2.Environment(undefined=jinja2.StrictUndefined).from_string(template).render(**variables)
@@ -622,10 +623,16 @@ def batch_to_dict(examples: Sequence) -> dict[str, torch.Tensor]:
     return out
 
 
-def create_dataset_map_fn(engine: PromptEngine) -> Callable[[Mapping[str, Any]], dict]:
-    """Function for `datasets.Dataset.map`: row -> plain dict of lists."""
+def create_dataset_map_fn(engine: PromptEngine, drop_errors: bool = False) -> Callable[[Mapping[str, Any]], dict]:
+    """Function for `datasets.Dataset.map`: row -> plain dict of lists.  With `drop_errors` a row that cannot be
+    processed maps to empty lists (filter on `len(input_ids) > 0` afterwards) instead of raising."""
     def fn(row):
-        return engine.process(row).to_dict()
+        try:
+            return engine.process(row).to_dict()
+        except PipelineError:
+            if not drop_errors:
+                raise
+            return {"input_ids": [], "attention_mask": [], "labels": []}
     return fn
 
 

@@ -21,6 +21,7 @@ from typing import Any, Callable
 import torch
 
 from ..core.errors import CheckpointLoadError, HubError
+from ..utils.refargs import ANY, reference_kwargs
 
 try:
     from safetensors.torch import load_file as _st_load, save_file as _st_save
@@ -77,6 +78,7 @@ class RetryPolicy:
         return int(round(self.delay(attempt) * 1e3))
 
 
+@reference_kwargs({"metrics": ANY}, circuit="breaker")
 def execute_with_retry(fn: Callable, policy: RetryPolicy | None = None, breaker: CircuitBreaker | None = None,
                        sleep: Callable[[float], None] = time.sleep):
     policy = policy or RetryPolicy()
@@ -98,6 +100,7 @@ def execute_with_retry(fn: Callable, policy: RetryPolicy | None = None, breaker:
     raise HubError(f"operation failed after {policy.max_attempts} attempts", cause=last)
 
 
+@reference_kwargs(chunk_size="chunk")
 def compute_sha256(path: str | os.PathLike, chunk: int = 1 << 22) -> str:
     h = hashlib.sha256()
     with open(path, "rb") as f:
@@ -241,11 +244,32 @@ def load_pretrained(path: str | os.PathLike, dtype=torch.bfloat16, device=None):
     return model
 
 
-def generate_model_card(model_name: str, base_model: str = "", config: dict | None = None, metrics: dict | None = None,
-                        tags: list[str] | None = None) -> str:
+def generate_model_card(model_name, base_model: str = "", config: dict | None = None, metrics: dict | None = None,
+                        tags: list[str] | None = None, *, model=None, description: str = "",
+                        training_config: dict | None = None, serialization_info=None, license: str = "",   # noqa: A002
+                        language: str | list | None = None) -> str:
+    """README.md text with the YAML front matter the hub reads.  The reference's calling form
+    `generate_model_card(model, model_name, description=..., training_config=..., serialization_info=...)` is taken as
+    well: a module as first argument supplies the parameter count, `training_config` is `config`."""
+    if not isinstance(model_name, str):              # (model, model_name, ...): shift
+        model, model_name, base_model = model_name, base_model, ""
+    config = config if config is not None else training_config
     tags = tags or ["trainscale-b200"]
-    lines = ["---", "library_name: trainscale-b200", f"base_model: {base_model}" if base_model else "base_model: none",
-             "tags:"] + [f"- {t}" for t in tags] + ["---", "", f"# {model_name}", ""]
+    front = ["---", "library_name: trainscale-b200", f"base_model: {base_model}" if base_model else "base_model: none"]
+    if license:
+        front.append(f"license: {license}")
+    if language:
+        front += ["language:"] + [f"- {l}" for l in ([language] if isinstance(language, str) else language)]
+    lines = front + ["tags:"] + [f"- {t}" for t in tags] + ["---", "", f"# {model_name}", ""]
+    if description:
+        lines += [description, ""]
+    if model is not None and hasattr(model, "parameters"):
+        n = sum(p.numel() for p in model.parameters())
+        lines += ["## Model", "", f"- **Parameters**: {n:,}", f"- **Class**: {type(model).__name__}", ""]
+    if serialization_info is not None:
+        lines += ["## Files", "", f"- **Format**: {getattr(serialization_info, 'format', '?')}",
+                  f"- **Shards**: {len(getattr(serialization_info, 'shards', ()))}",
+                  f"- **Bytes**: {getattr(serialization_info, 'total_bytes', 0):,}", ""]
     if metrics:
         lines += ["## Metrics", ""] + [f"- **{k}**: {v}" for k, v in metrics.items()] + [""]
     if config:

@@ -13,8 +13,10 @@ from typing import Any, Mapping, Sequence
 
 from ..core.errors import ColumnNotFoundError, DatasetNotFoundError, SplitNotFoundError
 from ..core.types import Err, Ok, Result
+from ..utils.refargs import ANY, reference_kwargs
 
 
+@reference_kwargs(s1="a", s2="b")
 def levenshtein_distance(a: str, b: str) -> int:
     if a == b:
         return 0

@@ -28,6 +28,7 @@ from ..ops import norm as _norm
 from ..ops import rope as _rope
 from ..losses import Fast_CrossEntropyLoss, FusedCrossEntropyFunction  # noqa: F401
 from ..utils.explicit_backward import ExplicitBackward as _ExplicitBackward
+from ..utils.refargs import ANY, reference_kwargs
 from ..parallel.dist_kernels import (DistributedBackend, DistributedConfig, DistributedKernels,  # noqa: F401
                                      get_distributed_backend, get_world_info, pinned_memory_transfer)
 from ..utils.cuda_graphs import CompilationConfig, compile_model  # noqa: F401
@@ -64,6 +65,7 @@ def is_triton_available() -> bool:
     return False
 
 
+@reference_kwargs(device_id="device")
 def get_accelerator_arch(device: int = 0) -> AcceleratorArch:
     if not torch.cuda.is_available():
         return AcceleratorArch.CPU
@@ -72,10 +74,12 @@ def get_accelerator_arch(device: int = 0) -> AcceleratorArch:
         major, AcceleratorArch.OTHER)
 
 
+@reference_kwargs(device_id="device")
 def supports_tma(device: int = 0) -> bool:
     return torch.cuda.is_available() and torch.cuda.get_device_capability(device)[0] >= 9
 
 
+@reference_kwargs(device_id="device")
 def supports_wgmma(device: int = 0) -> bool:
     """wgmma is the Hopper instruction; Blackwell's tensor-core path is tcgen05 (see `supports_tcgen05`)."""
     return torch.cuda.is_available() and torch.cuda.get_device_capability(device)[0] == 9
@@ -112,20 +116,36 @@ def fused_layer_norm(x, weight, bias=None, eps: float = 1e-5):
     return _norm.layernorm(x, weight, bias, eps)
 
 
+@reference_kwargs(X="x")
 def fast_rms_layernorm(x, weight, eps: float = 1e-6, gemma: bool = False):
     return _norm.rmsnorm(x, weight, eps, None, 1.0 if gemma else 0.0)[0]
 
 
-def fused_add_rms_layernorm(x, residual, weight, eps: float = 1e-6):
-    """(norm(x + residual), x + residual): the sum is formed inside the norm kernel."""
-    return _norm.rmsnorm(x, weight, eps, residual)
+@reference_kwargs(X="x")
+def fused_add_rms_layernorm(x, residual, weight, eps: float = 1e-6, return_residual: bool = False):
+    """norm(x + residual), the sum being formed inside the norm kernel; with `return_residual` the pair
+    (norm(x + residual), x + residual)."""
+    y, h = _norm.rmsnorm(x, weight, eps, residual)
+    return (y, h) if return_residual else y
+
+
+def layernorm(X, weight=None, bias=None, eps: float = 1e-5):
+    """LayerNorm over the last dimension with the reference's argument names
+    (data_pipeline/trainer/kernels/layernorm_kernels.py); the op itself is `ops.norm.layernorm`."""
+    if weight is None:
+        return F.layer_norm(X, (X.shape[-1],), None, None, eps)
+    return _norm.layernorm(X, weight, bias, eps)
 
 
 def fused_softmax(x, dim: int = -1):
     return _act.softmax(x, dim)
 
 
-def fused_gelu(x, approximate: str = "tanh"):
+@reference_kwargs(approx="approximate")
+def fused_gelu(x, approximate: str | bool = "tanh"):
+    """`approximate`: "tanh" / "none" (or the reference's boolean: True = tanh form)."""
+    if isinstance(approximate, bool):
+        approximate = "tanh" if approximate else "none"
     return _act.gelu(x, approximate)
 
 
@@ -133,13 +153,23 @@ def swiglu_forward(gate, up):
     return _act.swiglu(gate, up)
 
 
-def geglu_forward(gate, up, approximate: str = "tanh"):
+@reference_kwargs(approx="approximate")
+def geglu_forward(gate, up, approximate: str | bool = "tanh"):
+    if isinstance(approximate, bool):
+        approximate = "tanh" if approximate else "none"
     return _act.glu(torch.cat((gate, up), dim=-1), "gelu_tanh" if approximate == "tanh" else "gelu")
 
 
 def fast_cross_entropy_loss(logits, labels, ignore_index: int = -100, label_smoothing: float = 0.0,
-                            reduction: str = "mean"):
-    """logits [..., V], labels [...] -> scalar (mean over non-ignored tokens) or per-token losses (reduction="none")."""
+                            reduction: str = "mean", logit_softcapping: float = 0.0, logit_scaling: float = 0.0,
+                            n_items: int | None = None):
+    """logits [..., V], labels [...] -> scalar (mean over non-ignored tokens) or per-token losses (reduction="none").
+    `logit_scaling` multiplies and `logit_softcapping` (c tanh(z / c)) caps the logits first; `n_items` replaces the
+    count of non-ignored tokens as the mean's denominator (data_pipeline/trainer/kernels/triton_kernels.py:427)."""
+    if logit_scaling:
+        logits = logits * logit_scaling
+    if logit_softcapping:
+        logits = logit_softcapping * torch.tanh(logits / logit_softcapping)
     z, y = logits.reshape(-1, logits.shape[-1]), labels.reshape(-1)
     if z.is_cuda and z.dtype == torch.bfloat16:
         rows = _ce.cross_entropy_rows(z, y, ignore_index, label_smoothing)
@@ -148,7 +178,9 @@ def fast_cross_entropy_loss(logits, labels, ignore_index: int = -100, label_smoo
     if reduction == "none":
         return rows.view(labels.shape)
     s = rows.sum()
-    return s / (y != ignore_index).sum().clamp(min=1) if reduction == "mean" else s
+    if reduction != "mean":
+        return s
+    return s / (n_items if n_items is not None else (y != ignore_index).sum().clamp(min=1))
 
 
 Fast_RMS_LayerNorm = _norm._RMSNormFn
@@ -366,10 +398,26 @@ def is_flash_attn_available() -> bool:
     return supports_tcgen05()
 
 
-def flash_attention(q, k, v, causal: bool = True, softmax_scale: float | None = None, window_size: int | None = None,
-                    softcap: float = 0.0, cu_seqlens: torch.Tensor | None = None) -> torch.Tensor:
-    """q [B, S, Hq, D], k / v [B, S, Hkv, D] -> [B, S, Hq, D].  bf16 CUDA inputs run the tcgen05 flash kernels
-    (forward and backward); anything else the fp32 reference."""
+def flash_attention(q=None, k=None, v=None, causal: bool | None = None, softmax_scale: float | None = None,
+                    window_size: int | None = None, softcap: float = 0.0, cu_seqlens: torch.Tensor | None = None, *,
+                    query=None, key=None, value=None, dropout_p: float = 0.0, scale: float | None = None,
+                    sliding_window: int | None = None, return_softmax: bool = False):
+    """q [B, S, Hq, D], k / v [B, S, Hkv, D] -> [B, S, Hq, D], causal unless told otherwise.  bf16 CUDA inputs run the
+    tcgen05 flash kernels (forward and backward); anything else the fp32 reference.
+
+    The reference's keyword form `flash_attention(query=, key=, value=, causal=False, scale=, sliding_window=)` uses ITS
+    conventions: [B, H, S, D] tensors in and out, not causal unless asked, and `return_softmax=True` wraps the result
+    in `AttentionOutput` (data_pipeline/trainer/kernels/flash_attention.py:795).  Dropout is not implemented."""
+    if dropout_p:
+        raise NotImplementedError("attention dropout is not supported by this framework")
+    if query is not None:
+        o = flash_attention(query.transpose(1, 2).contiguous(), key.transpose(1, 2).contiguous(),
+                            value.transpose(1, 2).contiguous(), bool(causal), scale if scale is not None else softmax_scale,
+                            sliding_window if sliding_window is not None else window_size, softcap).transpose(1, 2)
+        return AttentionOutput(o) if return_softmax else o
+    causal = True if causal is None else causal
+    softmax_scale = softmax_scale if softmax_scale is not None else scale
+    window_size = window_size if window_size is not None else sliding_window
     B, S, Hq, D = q.shape
     Hkv = k.shape[2]
     if q.is_cuda and q.dtype == torch.bfloat16 and k.shape[1] == S:
@@ -383,10 +431,23 @@ def flash_attention(q, k, v, causal: bool = True, softmax_scale: float | None = 
     return _attn.attention_reference(q, k, v, causal, softmax_scale, window_size, softcap, doc).to(q.dtype)
 
 
-def naive_attention(q, k, v, causal: bool = True, softmax_scale: float | None = None):
-    return _attn.attention_reference(q, k, v, causal, softmax_scale).to(q.dtype)
+def naive_attention(q=None, k=None, v=None, causal: bool = True, softmax_scale: float | None = None, *, query=None,
+                    key=None, value=None, dropout_p: float = 0.0, scale: float | None = None, attn_mask=None):
+    """fp32 attention maths.  Positional / q-k-v form: [B, S, H, D], causal by default.  The reference's keyword form
+    (`query=, key=, value=`) uses ITS layout, [B, H, S, D], and takes an additive or boolean `attn_mask`
+    (data_pipeline/trainer/kernels/flash_attention.py:895).  Dropout is not implemented (dropout_p must be 0)."""
+    if dropout_p:
+        raise NotImplementedError("attention dropout is not supported by this framework")
+    if query is not None:
+        if attn_mask is not None:
+            return F.scaled_dot_product_attention(query.float(), key.float(), value.float(), attn_mask=attn_mask,
+                                                  is_causal=False, scale=scale).to(query.dtype)
+        o = _attn.attention_reference(query.transpose(1, 2), key.transpose(1, 2), value.transpose(1, 2), causal, scale)
+        return o.transpose(1, 2).to(query.dtype)
+    return _attn.attention_reference(q, k, v, causal, softmax_scale if softmax_scale is not None else scale).to(q.dtype)
 
 
+@reference_kwargs({"dropout_p": (0, 0.0, None)}, Q="q", K="k", V="v")
 def scaled_dot_product_attention(q, k, v, attn_mask=None, is_causal: bool = False, scale: float | None = None):
     """[B, H, S, D] layout of torch's function; an explicit mask takes torch's path, causal / full the flash kernels."""
     if attn_mask is not None:
@@ -394,29 +455,71 @@ def scaled_dot_product_attention(q, k, v, attn_mask=None, is_causal: bool = Fals
     return flash_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), is_causal, scale).transpose(1, 2)
 
 
-def slow_attention_softcapping(q, k, v, softcap: float, causal: bool = True, softmax_scale: float | None = None):
-    """fp32 reference of soft-capped attention: scores -> softcap * tanh(scores / softcap)."""
-    return _attn.attention_reference(q, k, v, causal, softmax_scale, None, softcap).to(q.dtype)
+def _softcap_args(q, k, v, softcap, causal, softmax_scale, Q, K, V, causal_mask, config, query_scalar):
+    """Common part of the two soft-capped entry points: the reference's form passes [B, H, S, D] tensors as Q / K / V,
+    the mask object instead of a flag, and the soft-max scale either as `query_scalar` (scale = query_scalar^-0.5) or
+    inside `config` (`query_pre_attn_scalar`, `attn_logit_softcapping`)."""
+    ref_form = Q is not None
+    if ref_form:
+        q, k, v = Q.transpose(1, 2), K.transpose(1, 2), V.transpose(1, 2)
+        causal = causal_mask is not None if causal_mask is not None or causal is None else causal
+    if config is not None:
+        softcap = softcap if softcap is not None else getattr(config, "attn_logit_softcapping", 0.0)
+        query_scalar = query_scalar if query_scalar is not None else getattr(config, "query_pre_attn_scalar", None)
+    if softmax_scale is None and query_scalar:
+        softmax_scale = float(query_scalar) ** -0.5
+    return q, k, v, float(softcap or 0.0), True if causal is None else bool(causal), softmax_scale, ref_form
 
 
-def attention_softcapping_compiled(q, k, v, softcap: float, causal: bool = True, softmax_scale: float | None = None):
-    """Soft-capped attention on the flash kernel (the cap is applied to the scores inside the kernel)."""
-    return flash_attention(q, k, v, causal, softmax_scale, None, softcap)
+def slow_attention_softcapping(q=None, k=None, v=None, softcap: float | None = None, causal: bool | None = None,
+                               softmax_scale: float | None = None, *, Q=None, K=None, V=None, causal_mask=None,
+                               config=None, bsz=None, q_len=None, query_scalar=None):
+    """fp32 reference of soft-capped attention: scores -> softcap * tanh(scores / softcap).  [B, S, H, D] in and out;
+    with the reference's `Q= K= V=` form [B, H, S, D] in and [B, S, H * D] out (`bsz` / `q_len` are implied)."""
+    q, k, v, softcap, causal, softmax_scale, ref = _softcap_args(q, k, v, softcap, causal, softmax_scale, Q, K, V,
+                                                                 causal_mask, config, query_scalar)
+    o = _attn.attention_reference(q, k, v, causal, softmax_scale, None, softcap).to(q.dtype)
+    return o.reshape(o.shape[0], o.shape[1], -1) if ref else o
 
 
+def attention_softcapping_compiled(q=None, k=None, v=None, softcap: float | None = None, causal: bool | None = None,
+                                   softmax_scale: float | None = None, *, Q=None, K=None, V=None, causal_mask=None,
+                                   query_scalar=None, num_heads=None, num_kv_heads=None, head_dim=None):
+    """Soft-capped attention on the flash kernel (the cap is applied to the scores inside the kernel).  Same two
+    calling forms as `slow_attention_softcapping`; head counts are read from the tensors."""
+    q, k, v, softcap, causal, softmax_scale, ref = _softcap_args(q, k, v, softcap, causal, softmax_scale, Q, K, V,
+                                                                 causal_mask, None, query_scalar)
+    o = flash_attention(q.contiguous(), k.contiguous(), v.contiguous(), causal, softmax_scale, None, softcap)
+    return o.reshape(o.shape[0], o.shape[1], -1) if ref else o
+
+
+@reference_kwargs(max_seq_len="seq_len")
 def create_causal_mask(seq_len: int, device=None, dtype=torch.float32) -> torch.Tensor:
     return torch.full((seq_len, seq_len), float("-inf"), device=device, dtype=dtype).triu(1)
 
 
+@reference_kwargs(max_seq_len="seq_len", window_size="window")
 def create_sliding_window_causal_mask(seq_len: int, window: int, device=None, dtype=torch.float32) -> torch.Tensor:
     i = torch.arange(seq_len, device=device)
     keep = (i[None, :] <= i[:, None]) & (i[:, None] - i[None, :] < window)
     return torch.zeros(seq_len, seq_len, device=device, dtype=dtype).masked_fill(~keep, float("-inf"))
 
 
-def inference_attention_single_token(q, k_cache, v_cache, seq_lens: torch.Tensor | None = None,
-                                     softmax_scale: float | None = None) -> torch.Tensor:
-    """Decode step: q [B, Hq, D] against caches [B, S_max, Hkv, D] (valid prefix `seq_lens[b]`) -> [B, Hq, D]."""
+def inference_attention_single_token(q=None, k_cache=None, v_cache=None, seq_lens: torch.Tensor | None = None,
+                                     softmax_scale: float | None = None, *, Q=None, K=None, V=None, config=None
+                                     ) -> torch.Tensor:
+    """Decode step: q [B, Hq, D] against caches [B, S_max, Hkv, D] (valid prefix `seq_lens[b]`) -> [B, Hq, D].
+    The reference's form: Q [B, Hq, 1, D], K / V [B, Hkv, S, D] and a config with `query_pre_attn_scalar` /
+    `attn_logit_softcapping` -> [B, 1, Hq * D] (data_pipeline/trainer/kernels/flex_attention.py:1032)."""
+    if Q is not None:
+        qs = getattr(config, "query_pre_attn_scalar", None)
+        cap = float(getattr(config, "attn_logit_softcapping", 0.0) or 0.0)
+        scale = float(qs) ** -0.5 if qs and qs != 1.0 else None
+        if cap:
+            o = _attn.attention_reference(Q.transpose(1, 2), K.transpose(1, 2), V.transpose(1, 2), False, scale, None, cap)
+            return o.reshape(Q.shape[0], 1, -1).to(Q.dtype)
+        o = inference_attention_single_token(Q[:, :, 0], K.transpose(1, 2), V.transpose(1, 2), None, scale)
+        return o.reshape(Q.shape[0], 1, -1)
     B, Hq, D = q.shape
     S, Hkv = k_cache.shape[1], k_cache.shape[2]
     scale = softmax_scale if softmax_scale is not None else 1.0 / math.sqrt(D)
@@ -505,6 +608,7 @@ class RoPEConfig:
     longrope_long_factor: Optional[List[float]] = None
 
 
+@reference_kwargs({"dtype": ANY}, max_seq_len="end")
 def precompute_freqs_cis(dim: int, end: int, theta: float = 10000.0, scaling_factor: float = 1.0, device=None):
     """(cos, sin) tables [end, dim/2] (linear position scaling when scaling_factor != 1)."""
     return _rope.rope_tables(end, dim, theta, device=device,
@@ -546,13 +650,44 @@ class RoPEFrequencyCache:
             cls._shared._cache.clear()
 
 
-def fast_rope_embedding(q, k, cos, sin, positions=None, interleaved: bool = False):
-    """q [B, S, Hq, D], k [B, S, Hkv, D], tables [max_pos, D/2] -> rotated (q, k)."""
+def _tables(cos, sin):
+    cos, sin = cos.squeeze(), sin.squeeze()
+    return cos.float().contiguous(), sin.float().contiguous()
+
+
+@reference_kwargs(Q="q")
+def fast_rope_embedding(q, k, cos, sin=None, positions=None, interleaved: bool = False):
+    """q [B, S, Hq, D], k [B, S, Hkv, D], tables [max_pos, D/2] -> rotated (q, k).  The three-argument form
+    `fast_rope_embedding(Q, cos, sin)` rotates one tensor and returns it."""
+    if sin is None:                                   # (Q, cos, sin)
+        c, s_ = _tables(k, cos)
+        return _rope.apply_rope(q, c, s_, None, 0, interleaved)
     return _rope.apply_rope(q, cos, sin, positions, 0, interleaved), _rope.apply_rope(k, cos, sin, positions, 0, interleaved)
 
 
-def inplace_rope_embedding(qkv, n_heads: int, n_kv_heads: int, head_dim: int, cos, sin, positions=None):
-    """Rotates the q and k heads of a fused [B, S, (Hq + 2 Hkv) D] buffer (each k head once)."""
+def apply_rope(q, k, cos, sin, interleaved: bool = False):
+    """(q', k') for q [B, S, Hq, D], k [B, S, Hkv, D] and tables [max_pos, D/2]
+    (data_pipeline/trainer/kernels/triton_kernels.py:984); the single-tensor op is `ops.rope.apply_rope`."""
+    c, s_ = _tables(cos, sin)
+    return _rope.apply_rope(q, c, s_, None, 0, interleaved), _rope.apply_rope(k, c, s_, None, 0, interleaved)
+
+
+def inplace_rope_embedding(qkv=None, n_heads=None, n_kv_heads=None, head_dim=None, cos=None, sin=None, positions=None, *,
+                           Q=None, K=None, position_offset: int = 0):
+    """Rotates the q and k heads of a fused [B, S, (Hq + 2 Hkv) D] buffer (each k head once).  The reference's form
+    `inplace_rope_embedding(Q, K, cos, sin, position_offset)` rotates two separate [B, S, H, D] tensors in place and
+    returns them."""
+    if Q is not None or torch.is_tensor(n_heads):
+        if Q is None:                                 # positional: (Q, K, cos, sin, position_offset)
+            Q, K = qkv, n_heads
+            if isinstance(cos, int):
+                position_offset = cos
+            cos, sin = n_kv_heads, head_dim
+        c, s_ = _tables(cos, sin)
+        with torch.no_grad():
+            Q.copy_(_rope.apply_rope(Q, c, s_, None, position_offset, False))
+            K.copy_(_rope.apply_rope(K, c, s_, None, position_offset, False))
+        return Q, K
     return _rope.apply_rope_qkv(qkv, n_heads + n_kv_heads, head_dim, cos, sin, positions)
 
 
@@ -569,8 +704,17 @@ def torch_amp_custom_fwd(fn=None, **_kw):
 torch_amp_custom_bwd = torch_amp_custom_fwd
 
 
-def matmul_lora(x, W, A=None, B=None, s: float = 1.0):
-    """x W^T + s (x A^T) B^T with the adapter product accumulated by the GEMM epilogue (A [r, in], B [out, r])."""
+def matmul_lora(x, W, *rest, A=None, B=None, s: float | None = None, W_quant=None, scaling: float | None = None):
+    """x W^T + s (x A^T) B^T with the adapter product accumulated by the GEMM epilogue (A [r, in], B [out, r]).
+    Positional tails: (A, B, s) or, in the reference's order, (W_quant, A, B, scaling) - told apart by their number;
+    a quantisation state must be None here (quantised bases go through `quantization.FP8Linear` / `QuantState`)."""
+    if len(rest) == 4:
+        W_quant, A, B, scaling = rest
+    elif rest:
+        A, B, s = (list(rest) + [None, None])[:3] if len(rest) < 3 else rest
+    if W_quant is not None:
+        raise NotImplementedError("matmul_lora takes a dense base weight; dequantise first (quantization.fast_dequantize)")
+    s = s if s is not None else (scaling if scaling is not None else 1.0)
     if A is None or B is None:
         return _gemm.linear(x, W)
     from ..lora import _LoRALinearFn
@@ -584,11 +728,32 @@ def get_lora_parameters(module):
     return W, A, B, float(getattr(module, "scaling", 1.0))
 
 
-def apply_lora_qkv(x, Wq, Wk, Wv, Aq=None, Bq=None, Ak=None, Bk=None, Av=None, Bv=None, s: float = 1.0):
+def _proj(x, module):
+    W, A, B, s = get_lora_parameters(module)
+    y = matmul_lora(x, W, A, B, s)
+    b = getattr(module, "bias", None)
+    return y if b is None else y + b
+
+
+def apply_lora_qkv(x=None, Wq=None, Wk=None, Wv=None, Aq=None, Bq=None, Ak=None, Bk=None, Av=None, Bv=None, s: float = 1.0,
+                   *, q_proj=None, k_proj=None, v_proj=None, X=None, inplace: bool = True):
+    """(q, k, v) projections with their adapters.  Tensor form: (x, Wq, Wk, Wv, adapters..., s).  Module form of the
+    reference: (q_proj, k_proj, v_proj, X) with modules that carry `weight`, `lora_A`, `lora_B`, `scaling`
+    (data_pipeline/trainer/kernels/fast_lora_mlp.py:1293); `inplace` has no meaning here."""
+    if isinstance(x, nn.Module) or q_proj is not None:
+        q_proj, k_proj, v_proj, X = (x, Wq, Wk, Wv) if q_proj is None else (q_proj, k_proj, v_proj, X)
+        return _proj(X, q_proj), _proj(X, k_proj), _proj(X, v_proj)
     return matmul_lora(x, Wq, Aq, Bq, s), matmul_lora(x, Wk, Ak, Bk, s), matmul_lora(x, Wv, Av, Bv, s)
 
 
-def apply_lora_mlp_swiglu(x, Wg, Wu, Wd, Ag=None, Bg=None, Au=None, Bu=None, Ad=None, Bd=None, s: float = 1.0):
+def apply_lora_mlp_swiglu(x=None, Wg=None, Wu=None, Wd=None, Ag=None, Bg=None, Au=None, Bu=None, Ad=None, Bd=None,
+                          s: float = 1.0, *, mlp_module=None, X=None, inplace: bool = True):
+    """down(silu(gate(x)) * up(x)) with adapters on all three.  Module form of the reference: (mlp_module, X) with
+    `gate_proj` / `up_proj` / `down_proj` children."""
+    if isinstance(x, nn.Module) or mlp_module is not None:
+        mlp_module, X = (x, Wg) if mlp_module is None else (mlp_module, X)
+        h = _act.swiglu(_proj(X, mlp_module.gate_proj), _proj(X, mlp_module.up_proj))
+        return _proj(h, mlp_module.down_proj)
     h = _act.swiglu(matmul_lora(x, Wg, Ag, Bg, s), matmul_lora(x, Wu, Au, Bu, s))
     return matmul_lora(h, Wd, Ad, Bd, s)
 
@@ -641,8 +806,19 @@ class LoRA_QKV(_LoRABlock):
 
 
 def validate_lora_gradients(T: int = 64, hidden: int = 64, out: int = 96, r: int = 8, device=None, dtype=None,
-                            atol: float | None = None) -> dict:
-    """Gradients of `matmul_lora` (custom backward with accumulating GEMMs) against autograd on the plain formula."""
+                            atol: float | None = None, *, X=None, W=None, A=None, B=None, scaling: float = 1.0,
+                            eps: float = 1e-4, rtol: float = 1e-3):
+    """Gradients of `matmul_lora` (custom backward with accumulating GEMMs) against autograd on the plain formula.
+    Without tensors: random operands of the given sizes, returns {dx, dA, dB: relative error, passed}.  With the
+    reference's tensors (X, W, A, B, scaling - by position or name) the check runs on them and returns a bool."""
+    if torch.is_tensor(T) or X is not None:
+        X, W, A, B = (T, hidden, out, r) if X is None else (X, W, A, B)
+        leaves = [t.detach().clone().requires_grad_(True) for t in (X, A, B)]
+        matmul_lora(leaves[0], W, leaves[1], leaves[2], float(scaling)).float().pow(2).sum().backward()
+        ref = [t.detach().float().clone().requires_grad_(True) for t in (X, A, B)]
+        (ref[0] @ W.float().t() + scaling * (ref[0] @ ref[1].t()) @ ref[2].t()).pow(2).sum().backward()
+        tol = atol if atol is not None else 1e-3
+        return all(torch.allclose(a.grad.float(), b.grad, atol=tol, rtol=rtol) for a, b in zip(leaves, ref))
     device = device or ("cuda" if torch.cuda.is_available() else "cpu")
     dtype = dtype or (torch.bfloat16 if device == "cuda" else torch.float32)
     g = torch.Generator().manual_seed(0)
@@ -667,9 +843,23 @@ class MoEKernelConfig:
     activation: str = "silu"
 
 
-def moe_grouped_gemm(x, expert_ids, weights, w_gate_up, w_down, activation: str = "silu"):
+def moe_grouped_gemm(x=None, expert_ids=None, weights=None, w_gate_up=None, w_down=None, activation: str = "silu", *,
+                     X=None, W=None, topk=None, expert_offsets=None, gather_indices=None, topk_weights=None,
+                     permute_x: bool = False, permute_y: bool = False, fuse_topk_weights: bool = False,
+                     fwd_config=None, bwd_config=None):
     """Top-k expert FFN over tokens x [T, H]: device-side routing plan, permute into 128-aligned expert segments,
-    grouped tcgen05 GEMMs, weighted combine (w_gate_up [E, 2I, H], w_down [E, H, I])."""
+    grouped tcgen05 GEMMs, weighted combine (w_gate_up [E, 2I, H], w_down [E, H, I]).
+
+    The reference's single grouped GEMM `moe_grouped_gemm(X, W, topk, expert_offsets, gather_indices, ...)` (one weight
+    [E, N, K], rows grouped by `expert_offsets`) is `kernels.moe.moe_grouped_gemm_forward`; it is reached from here by
+    those keywords, or positionally when the third argument is the integer `topk`."""
+    if X is not None or isinstance(weights, int):
+        from .moe import moe_grouped_gemm_forward
+        if X is None:
+            X, W, topk, expert_offsets = x, expert_ids, weights, w_gate_up
+            gather_indices = gather_indices if gather_indices is not None else w_down
+        return moe_grouped_gemm_forward(X, W, topk, expert_offsets, gather_indices, topk_weights, permute_x, permute_y,
+                                        fuse_topk_weights, fwd_config)
     if _moe.available(x):
         return _moe.moe_ffn(x, expert_ids, weights, w_gate_up, w_down, activation)
     out = torch.zeros(x.shape, dtype=torch.float32, device=x.device)       # per-expert loop (CPU / non-bf16 inputs)
@@ -708,27 +898,92 @@ class FP8Config:
         return get_fp8_spec(self.backward_format)
 
 
-def row_quantize_fp8(x2):
-    return _fp8.quant_row(x2)
+def _fp8_dtype(fp8_format):
+    if fp8_format is None or isinstance(fp8_format, torch.dtype):
+        return fp8_format or torch.float8_e4m3fn
+    return torch.float8_e5m2 if "5" in str(getattr(fp8_format, "value", fp8_format)) else torch.float8_e4m3fn
 
 
-def block_quantize_fp8(w):
-    return _fp8.quant_block(w)
+def _on_kernel(t, block=128, dtype=torch.float8_e4m3fn):
+    return t.is_cuda and t.dtype == torch.bfloat16 and block == 128 and dtype == torch.float8_e4m3fn and t.dim() == 2 \
+        and t.shape[1] % 128 == 0
 
 
-def block_dequantize_fp8(q, scale):
-    return _fp8.dequant(q, scale, "block")
+@reference_kwargs(x="x2")
+def row_quantize_fp8(x2, fp8_format=None):
+    """(q, scale [rows]) with x ~ q * scale; e4m3 unless `fp8_format` says e5m2."""
+    dt = _fp8_dtype(fp8_format)
+    if _on_kernel(x2, 128, dt):
+        return _fp8.quant_row(x2)
+    from ..quantization import row_quantize_fp8 as _rq
+    return _rq(x2, dt)
 
 
-def fp8_matmul_block_scaled(x2, w):
-    """x2 [M, K] bf16, w [N, K] bf16 -> x2 w^T through e4m3 operands (1x128 activation / 128x128 weight scales)."""
+@reference_kwargs(y="q", scales="scale", out_dtype="dtype")
+def row_dequantize_fp8(q, scale, dtype=torch.bfloat16):
+    from ..quantization import row_dequantize_fp8 as _rd
+    return _rd(q, scale, dtype)
+
+
+@reference_kwargs(x="w")
+def block_quantize_fp8(w, block_size: int = 128, fp8_format=None):
+    """(q, scale [ceil(N / b), ceil(K / b)]) with w ~ q * scale per b x b block."""
+    dt = _fp8_dtype(fp8_format)
+    if _on_kernel(w, block_size, dt):
+        return _fp8.quant_block(w)
+    from ..quantization import block_quantize_fp8 as _bq
+    return _bq(w, block_size, dt)
+
+
+@reference_kwargs(y="q", scales="scale")
+def block_dequantize_fp8(q, scale, block_size: int = 128, out_dtype=None):
+    if q.is_cuda and block_size == 128 and out_dtype in (None, torch.float32):
+        return _fp8.dequant(q, scale, "block")
+    from ..quantization import block_dequantize_fp8 as _bd
+    return _bd(q, scale, block_size, out_dtype or torch.bfloat16)
+
+
+def _expand_scale(scale, shape):
+    """Per-row [M], per-row-block [M, K/b] or per-block [M/b, K/b] scales broadcast to `shape` = (M, K)."""
+    s = scale.float()
+    if s.dim() == 1:
+        return s[:, None].expand(shape)
+    for d in (0, 1):
+        if s.shape[d] != shape[d]:
+            s = s.repeat_interleave(-(-shape[d] // s.shape[d]), dim=d).narrow(d, 0, shape[d])
+    return s
+
+
+def _fp8_matmul_prequantized(A, A_scale, B, B_scale, out_dtype):
+    """The reference's operand form: A [M, K] and B [K, N] already in fp8 with their scales (any of the layouts that
+    `_expand_scale` understands).  The product is formed on the dequantised values."""
+    a = A.float() * _expand_scale(A_scale, A.shape)
+    b = B.float() * _expand_scale(B_scale, B.shape)
+    return (a @ b).to(out_dtype or torch.bfloat16)
+
+
+def fp8_matmul_block_scaled(x2=None, w=None, *args, A=None, A_scale=None, B=None, B_scale=None, out_dtype=None,
+                            block_size: int = 128):
+    """x2 [M, K] bf16, w [N, K] bf16 -> x2 w^T through e4m3 operands (1x128 activation / 128x128 weight scales).
+    With four tensors (A, A_scale, B [K, N], B_scale - positionally or by those names) the operands are taken as
+    already quantised (data_pipeline/trainer/kernels/fp8_kernels.py:844)."""
+    if args or A is not None:
+        ops_ = [t for t in (x2, w) + args if t is not None] if A is None else [A, A_scale, B, B_scale]
+        return _fp8_matmul_prequantized(*ops_[:4], out_dtype)
     aq, sa = _fp8.quant_act(x2)
     bq, sb = _fp8.quant_block(w)
     return _fp8.gemm_fp8(aq, sa, bq, sb, w.shape[0])
 
 
-def fp8_matmul_row_scaled(x2, w):
-    """Per-row scaled operands; the product is formed on the dequantised bf16 values (tcgen05 bf16 GEMM)."""
+def fp8_matmul_row_scaled(x2=None, w=None, *args, A=None, A_scale=None, B=None, B_scale=None, out_dtype=None):
+    """Per-row scaled operands; the product is formed on the dequantised bf16 values (tcgen05 bf16 GEMM).  Four tensors
+    select the pre-quantised form as in `fp8_matmul_block_scaled` (B [K, N] with one scale per column or row)."""
+    if args or A is not None:
+        ops_ = [t for t in (x2, w) + args if t is not None] if A is None else [A, A_scale, B, B_scale]
+        a, sa, b, sb = ops_[:4]
+        # B is [K, N]: a row-wise quantised [N, K] weight, transposed, carries one scale per COLUMN here
+        bfull = b.float() * (sb.float().reshape(1, -1) if sb.numel() == b.shape[1] else _expand_scale(sb, b.shape))
+        return ((a.float() * _expand_scale(sa, a.shape)) @ bfull).to(out_dtype or torch.bfloat16)
     xq, xs = _fp8.quant_row(x2)
     wq, ws = _fp8.quant_row(w)
     return _gemm.matmul_nt(_fp8.dequant(xq, xs, "row").to(x2.dtype), _fp8.dequant(wq, ws, "row").to(w.dtype))

@@ -15,6 +15,7 @@ import torch
 import torch.nn as nn
 
 from .ops import gemm
+from .utils.refargs import ANY, reference_kwargs
 
 
 class LoRALinear(nn.Module):
@@ -157,6 +158,7 @@ def _targets_for(model_cfg) -> dict:
             "down_proj": ("mlp", "w_down", 0, H)}
 
 
+@reference_kwargs(config="r")
 def get_peft_model(model, r: int = 16, lora_alpha: float = 32.0, lora_dropout: float = 0.0,
                    target_modules: list[str] | None = None, use_rslora: bool = True, modules_to_save: list[str] | None = None,
                    init_lora_weights: bool | str = True, rank_pattern: dict | None = None):
@@ -215,6 +217,7 @@ def merge_and_unload(model):
     return model
 
 
+@reference_kwargs(config="lora_cfg")
 def apply_lora(model, lora_cfg):
     """From a SOTAConfig `lora` section."""
     return get_peft_model(model, lora_cfg.r, lora_cfg.lora_alpha, lora_cfg.lora_dropout, list(lora_cfg.target_modules),

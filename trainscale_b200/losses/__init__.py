@@ -23,11 +23,14 @@ from ..utils.explicit_backward import ExplicitBackward as _ExplicitBackward
 
 # ------------------------------------------------------------------------------------------------ helpers
 def compute_log_probs(logits: torch.Tensor, labels: torch.Tensor, ignore_index: int = -100,
-                      average: bool = False) -> torch.Tensor:
-    """Per-sequence sum (or mean) of label-token log-probs. logits [B,S,V] and labels [B,S] already aligned."""
+                      average: bool = False, per_token: bool = False) -> torch.Tensor:
+    """Per-sequence sum (or mean) of label-token log-probs; with `per_token` the [B, S] values themselves (0 at ignored
+    positions).  logits [B,S,V] and labels [B,S] already aligned."""
     lp = torch.log_softmax(logits.float(), dim=-1)
     mask = labels != ignore_index
     tok = lp.gather(-1, labels.clamp(min=0).unsqueeze(-1)).squeeze(-1) * mask
+    if per_token:
+        return tok
     s = tok.sum(-1)
     return s / mask.sum(-1).clamp(min=1) if average else s
 

@@ -14,9 +14,12 @@ from typing import Sequence
 import torch
 import torch.distributed as dist
 
+from ..utils.refargs import ANY, reference_kwargs
+
 from .throughput import PEAK_TFLOPS, ThroughputTracker, device_peak_tflops  # noqa: F401
 
 
+@reference_kwargs(operation="op", process_group="group")
 def sync_metric(value: float | torch.Tensor, op: str = "mean", group=None) -> float:
     if not (dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1):
         return float(value)
@@ -27,6 +30,7 @@ def sync_metric(value: float | torch.Tensor, op: str = "mean", group=None) -> fl
     return float(t / dist.get_world_size(group)) if op == "mean" else float(t)
 
 
+@reference_kwargs(metrics="values", operation="op", process_group="group")
 def sync_metrics(values: dict[str, float], op: str = "mean", group=None) -> dict[str, float]:
     if not (dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1):
         return dict(values)

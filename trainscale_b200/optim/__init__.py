@@ -20,7 +20,8 @@ from ..ops import optim as K
 
 
 @torch.no_grad()
-def clip_grad_norm_(parameters: Iterable[torch.Tensor], max_norm: float, norm_type: float = 2.0) -> torch.Tensor:
+def clip_grad_norm_(parameters: Iterable[torch.Tensor], max_norm: float, norm_type: float = 2.0,
+                    error_if_nonfinite: bool = False) -> torch.Tensor:
     grads = [p.grad for p in parameters if p.grad is not None]
     if not grads:
         return torch.zeros(())
@@ -28,6 +29,8 @@ def clip_grad_norm_(parameters: Iterable[torch.Tensor], max_norm: float, norm_ty
         total = torch.stack([g.abs().max() for g in grads]).max()
     else:
         total = torch.stack([torch.linalg.vector_norm(g.float(), norm_type) for g in grads]).norm(norm_type)
+    if error_if_nonfinite and not bool(torch.isfinite(total)):
+        raise RuntimeError(f"the total gradient norm is {float(total)}: gradients are not clipped")
     coef = (max_norm / (total + 1e-6)).clamp(max=1.0)
     for g in grads:
         g.mul_(coef.to(g.dtype))

@@ -483,38 +483,96 @@ def reduce_scatter_with_fp32_accumulation(output: torch.Tensor, input: torch.Ten
     return output
 
 
-def allreduce_layernorm_grads(model, group) -> None:
-    """Sequence parallelism: norm weights saw only this rank's tokens; sum their gradients over the TP group."""
+def _chunks(model) -> list:
+    """A model, or the reference's list of model chunks (virtual pipeline stages), as a list."""
+    return list(model) if isinstance(model, (list, tuple)) else [model]
+
+
+def _grad_of(p):
+    return p.grad if p.grad is not None else getattr(p, "main_grad", None)
+
+
+def allreduce_layernorm_grads(model, group=None, *, tp_group=None, sequence_parallel: bool = True,
+                              qk_layernorm: bool = False) -> None:
+    """Sequence parallelism: norm weights saw only this rank's tokens; sum their gradients over the TP group.  With
+    `qk_layernorm` the per-head q / k norm weights are summed too (they see only this rank's heads' tokens).
+    `model` may be a list of chunks; `tp_group` is the reference's name for `group`; nothing happens unless
+    `sequence_parallel` or `qk_layernorm` (data_pipeline/trainer/distributed/finalize_grads.py:148-208)."""
+    group = group if group is not None else tp_group
+    if group is None or not dist.is_initialized() or dist.get_world_size(group) <= 1:
+        return
     from .tp import TPContext, allreduce_sequence_parallel_grads
     ctx = TPContext(group, dist.get_world_size(group), dist.get_rank(group), True)
-    allreduce_sequence_parallel_grads(model, ctx)
+    for chunk in _chunks(model):
+        if sequence_parallel:
+            allreduce_sequence_parallel_grads(chunk, ctx)
+        if qk_layernorm:
+            for name, p in chunk.named_parameters():
+                if ("q_layernorm" in name or "k_layernorm" in name or "q_norm" in name or "k_norm" in name) \
+                        and _grad_of(p) is not None:
+                    dist.all_reduce(_grad_of(p), group=group)
 
 
-def allreduce_word_embedding_grads(stage_module, group, first_rank: int, last_rank: int) -> None:
-    """Tied embeddings on the first and last pipeline stage: sum their gradients."""
-    from .pp import allreduce_tied_embedding_grads
-    allreduce_tied_embedding_grads(stage_module, group, first_rank, last_rank)
+def allreduce_word_embedding_grads(stage_module, group=None, first_rank: int | None = None, last_rank: int | None = None,
+                                   *, embedding_group=None, pp_group=None,
+                                   share_embeddings_and_output_weights: bool = True) -> None:
+    """Tied embeddings on the first and last pipeline stage: sum their gradients.  Two calling forms: this framework's
+    (stage module, pipeline group, first rank, last rank), and the reference's (model or list of chunks,
+    embedding_group= the group of the two end stages), where the shared weight is looked up on the chunks
+    (`embed_tokens`, `tied_embedding`, `lm_head`)."""
+    if not share_embeddings_and_output_weights:
+        return
+    if first_rank is not None and last_rank is not None and not isinstance(stage_module, (list, tuple)):
+        from .pp import allreduce_tied_embedding_grads
+        allreduce_tied_embedding_grads(stage_module, group if group is not None else pp_group, first_rank, last_rank)
+        return
+    g = embedding_group if embedding_group is not None else group
+    if g is None or not dist.is_initialized() or dist.get_world_size(g) <= 1:
+        return
+    for chunk in _chunks(stage_module):
+        for attr in ("embed_tokens", "tied_embedding", "lm_head", "word_embeddings"):
+            mod = getattr(chunk, attr, None) or getattr(getattr(chunk, "model", None), attr, None)
+            w = getattr(mod, "weight", None)
+            if w is not None and _grad_of(w) is not None:
+                dist.all_reduce(_grad_of(w), group=g)
+                return
 
 
-def finalize_model_grads(model, *, tp_group=None, sequence_parallel: bool = False, pp_group=None, stage_module=None,
-                         first_rank: int = 0, last_rank: int = 0, num_tokens: torch.Tensor | None = None,
-                         dp_group=None) -> None:
+def finalize_model_grads(model, num_tokens: torch.Tensor | None = None, *, tp_group=None, sequence_parallel: bool = False,
+                         pp_group=None, stage_module=None, first_rank: int = 0, last_rank: int = 0, dp_group=None,
+                         embedding_group=None, pos_embedding_group=None, qk_layernorm: bool = False,
+                         share_embeddings_and_output_weights: bool = True, force_all_reduce: bool = False) -> None:
     """Everything that must happen to gradients between backward and the optimizer step besides the data-parallel
-    reduction (data_pipeline/trainer/distributed/finalize_grads.py:314): SP norm-weight all-reduce, tied-embedding
-    all-reduce across pipeline ends, optional scaling by the global number of tokens."""
-    if sequence_parallel and tp_group is not None:
-        allreduce_layernorm_grads(model, tp_group)
+    reduction (data_pipeline/trainer/distributed/finalize_grads.py:314): SP / qk norm-weight all-reduce, tied-embedding
+    all-reduce across pipeline ends, position-embedding all-reduce, optional scaling by the global number of tokens.
+    `model` may be a list of chunks.  `force_all_reduce` also sums every gradient over `dp_group` (for engines that do
+    not reduce by themselves)."""
+    chunks = _chunks(model)
+    if force_all_reduce and dp_group is not None and dist.is_initialized() and dist.get_world_size(dp_group) > 1:
+        for c in chunks:
+            for p in c.parameters():
+                if _grad_of(p) is not None:
+                    dist.all_reduce(_grad_of(p), group=dp_group)
+                    _grad_of(p).div_(dist.get_world_size(dp_group))
+    if (sequence_parallel or qk_layernorm) and tp_group is not None:
+        allreduce_layernorm_grads(chunks, tp_group, sequence_parallel=sequence_parallel, qk_layernorm=qk_layernorm)
     if pp_group is not None and stage_module is not None:
         allreduce_word_embedding_grads(stage_module, pp_group, first_rank, last_rank)
+    elif embedding_group is not None:
+        allreduce_word_embedding_grads(chunks, embedding_group=embedding_group, pp_group=pp_group,
+                                       share_embeddings_and_output_weights=share_embeddings_and_output_weights)
+    if pos_embedding_group is not None:
+        allreduce_position_embedding_grads(chunks, pos_embedding_group)
     if num_tokens is not None:
         total = num_tokens.detach().float().clone()
         if dist.is_initialized() and dp_group is not False:
             dist.all_reduce(total, group=dp_group)
         scale = 1.0 / total.clamp(min=1.0)
-        for p in model.parameters():
-            g = getattr(p, "main_grad", None) if p.grad is None else p.grad
-            if g is not None:
-                g.mul_(scale.to(g.dtype))
+        for c in chunks:
+            for p in c.parameters():
+                g = _grad_of(p)
+                if g is not None:
+                    g.mul_(scale.to(g.dtype))
 
 
 class GradientSynchronizer:
@@ -631,15 +689,19 @@ class DistributedManager:
 
 
 # ------------------------------------------------------------------------------------------------ more of the utility surface
-def allreduce_position_embedding_grads(model, group, attr: str = "position_embeddings") -> None:
-    """Learned position embeddings replicated over a group (e.g. on several pipeline stages): sum their gradients."""
+def allreduce_position_embedding_grads(model, group=None, attr: str = "position_embeddings", *,
+                                       pos_embedding_group=None) -> None:
+    """Learned position embeddings replicated over a group (e.g. on several pipeline stages): sum their gradients.
+    `model` may be a list of chunks; `pos_embedding_group` is the reference's name for `group`."""
+    group = group if group is not None else pos_embedding_group
     if group is None or not dist.is_initialized():
         return
-    for name, p in model.named_parameters():
-        if attr in name:
-            g = getattr(p, "main_grad", None) if p.grad is None else p.grad
-            if g is not None:
-                dist.all_reduce(g, group=group)
+    for chunk in _chunks(model):
+        for name, p in chunk.named_parameters():
+            if attr in name:
+                g = getattr(p, "main_grad", None) if p.grad is None else p.grad
+                if g is not None:
+                    dist.all_reduce(g, group=group)
 
 
 def scale_grads_by_token_count(model, num_tokens: torch.Tensor, group=None) -> torch.Tensor:

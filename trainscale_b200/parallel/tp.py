@@ -24,6 +24,7 @@ import torch.nn.functional as F
 
 from ..ops import gemm
 from ..utils.explicit_backward import ExplicitBackward as _ExplicitBackward
+from ..utils.refargs import ANY, reference_kwargs
 
 
 @dataclass
@@ -165,13 +166,35 @@ class _ScatterSeq(torch.autograd.Function):         # SP entry: split tokens fwd
         return _all_gather_dim(g, ctx.tp, 0), None
 
 
-def copy_to_tensor_parallel_region(x, tp): return _CopyToTP.apply(x, tp) if tp.active else x
-def reduce_from_tensor_parallel_region(x, tp): return _ReduceFromTP.apply(x, tp) if tp.active else x
-def scatter_to_tensor_parallel_region(x, tp): return _ScatterToTP.apply(x, tp) if tp.active else x
-def gather_from_tensor_parallel_region(x, tp): return _GatherFromTP.apply(x, tp) if tp.active else x
-def all_gather_from_sequence_parallel_region(x, tp): return _GatherSeq.apply(x, tp) if tp.active else x
-def reduce_scatter_to_sequence_parallel_region(x, tp): return _ReduceScatterSeq.apply(x, tp) if tp.active else x
-def scatter_to_sequence_parallel_region(x, tp): return _ScatterSeq.apply(x, tp) if tp.active else x
+def _default_tp() -> TPContext:
+    """Context of the registered tensor-parallel group (`tensor_parallel_context` / `ProcessGroupManager.initialize`);
+    an inactive one when there is none.  Lets the region functions be called the reference's way, without a context."""
+    m = ProcessGroupManager.get()
+    g = m.tp_group if m.initialized else None
+    return TPContext.from_group(g) if g is not None else TPContext(None)
+
+
+def _region(fn_cls, dim):
+    # the collective's dimension is fixed per function: last dim for the tensor-parallel pair, tokens (0) for the
+    # sequence-parallel ones; the reference's `dim` argument is accepted when it names that dimension
+    @reference_kwargs({"dim": (dim, None), "async_op": (False, None)}, input_="x")
+    def region(x, tp=None):
+        tp = tp if tp is not None else _default_tp()
+        return fn_cls.apply(x, tp) if tp.active else x
+    return region
+
+
+copy_to_tensor_parallel_region = _region(_CopyToTP, None)
+reduce_from_tensor_parallel_region = _region(_ReduceFromTP, None)
+scatter_to_tensor_parallel_region = _region(_ScatterToTP, -1)
+gather_from_tensor_parallel_region = _region(_GatherFromTP, -1)
+all_gather_from_sequence_parallel_region = _region(_GatherSeq, 0)
+reduce_scatter_to_sequence_parallel_region = _region(_ReduceScatterSeq, 0)
+scatter_to_sequence_parallel_region = _region(_ScatterSeq, 0)
+for _n in ("copy_to_tensor_parallel_region", "reduce_from_tensor_parallel_region", "scatter_to_tensor_parallel_region",
+           "gather_from_tensor_parallel_region", "all_gather_from_sequence_parallel_region",
+           "reduce_scatter_to_sequence_parallel_region", "scatter_to_sequence_parallel_region"):
+    globals()[_n].__name__ = globals()[_n].__qualname__ = _n
 
 
 # ------------------------------------------------------------------------------------------------ layers

@@ -15,6 +15,8 @@ from typing import Any, Callable, Iterable
 import torch
 import torch.nn as nn
 
+from ..utils.refargs import ANY, reference_kwargs
+
 
 class Capability(str, Enum):
     BF16 = "bf16"
@@ -376,7 +378,14 @@ class ModelInfo:
 MODEL_REGISTRY: dict[str, ModelInfo] = {}
 
 
-def register_models_from_meta(meta: Iterable[ModelInfo]) -> int:
+@reference_kwargs(model_meta="meta")
+def register_models_from_meta(meta, include_original: bool = True) -> int:
+    """Family-level records (an iterable of `ModelInfo`) go to MODEL_REGISTRY; a `catalog.FamilyMeta` (one release: sizes x
+    instruct tags x quantisation flavours, the reference's ModelMeta) registers its checkpoints in
+    `catalog.CHECKPOINT_REGISTRY`.  Returns how many entries were added."""
+    from .catalog import FamilyMeta, register_family
+    if isinstance(meta, FamilyMeta):
+        return register_family(meta, include_original)
     n = 0
     for m in meta:
         MODEL_REGISTRY[m.family] = m
@@ -403,6 +412,7 @@ register_models_from_meta([
 ])
 
 
+@reference_kwargs(model_id="name_or_path")
 def get_model_info(name_or_path: str) -> ModelInfo | None:
     n = name_or_path.lower()
     for fam, info in MODEL_REGISTRY.items():
@@ -498,6 +508,7 @@ def _is_rmsnorm(m: nn.Module) -> bool:
     return type(m).__name__.endswith("RMSNorm") and hasattr(m, "weight") and m.weight is not None and m.weight.dim() == 1
 
 
+@reference_kwargs(module="model")
 def auto_patch_layernorm(model: nn.Module) -> int:
     """`nn.LayerNorm` and `*RMSNorm` modules -> `ops.norm.layernorm` / `ops.norm.rmsnorm` (sm_100a kernels for bf16 CUDA
     rows, PyTorch maths otherwise)."""
@@ -521,6 +532,7 @@ def auto_patch_layernorm(model: nn.Module) -> int:
     return n
 
 
+@reference_kwargs(module="model")
 def auto_patch_mlp(model: nn.Module) -> int:
     """Gated MLPs (`gate_proj` / `up_proj` / `down_proj` without biases, SiLU or GELU gate) -> framework GEMMs and the
     fused gate * up kernel."""
@@ -548,6 +560,7 @@ def auto_patch_mlp(model: nn.Module) -> int:
     return n
 
 
+@reference_kwargs(module="model")
 def auto_patch_rope(model: nn.Module) -> int:
     """Replaces `apply_rotary_pos_emb` in the Python module that defines the model's attention class with a version on
     the framework rotary kernel (rotate-half layout, cos / sin of shape [B, S, D] as transformers passes them).
@@ -582,6 +595,7 @@ def auto_patch_rope(model: nn.Module) -> int:
     return n
 
 
+@reference_kwargs(module="model")
 def auto_patch_fp8_linear(model: nn.Module, min_features: int = 1024, skip: tuple[str, ...] = ("lm_head",)) -> int:
     """Bias-free `nn.Linear` layers with both dimensions >= `min_features` and divisible by 128 -> block-scaled fp8
     GEMM (bf16 CUDA inputs; other inputs take the original path)."""
@@ -613,6 +627,7 @@ def auto_patch(model: nn.Module, layernorm: bool = True, mlp: bool = True, rope:
 ModelMeta = ModelInfo          # name used by the per-family registration files of the reference
 
 
+@reference_kwargs(module="model")
 def auto_patch_attention(model: nn.Module, name: str = "trainscale_flash") -> int:
     """Registers the framework's flash attention with transformers' attention interface and switches the model's
     config to it, so that an unconverted HuggingFace model runs its attention on the tcgen05 kernels.  Calls that carry
