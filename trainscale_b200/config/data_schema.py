@@ -19,6 +19,8 @@ from typing import Any, Dict, List, Mapping, Optional, Tuple
 
 import yaml
 
+from ..utils.refargs import ANY, reference_kwargs
+
 from ..core.errors import ConfigurationError, SchemaValidationError, YAMLParseError
 from ..core.types import Err, Ok, Result
 
@@ -356,6 +358,7 @@ class PipelineConfig:
 _ENV = re.compile(r"\$\{([A-Za-z_][A-Za-z0-9_]*)(?::-([^}]*))?\}")
 
 
+@reference_kwargs(value="obj")
 def interpolate_env_vars(obj):
     """${VAR} / ${VAR:-default} interpolation inside strings (data_pipeline/trainer/core/config.py:54)."""
     if isinstance(obj, str):

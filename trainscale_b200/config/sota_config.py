@@ -490,40 +490,63 @@ class SOTAConfig:
 
 
 # ---------------------------------------------------------------- presets (data_pipeline/trainer/core/sota_config.py:625-691)
+def _preset(fn):
+    """Presets also take the reference's `model_name=` for `model` and `max_seq_length=`, which is written to
+    `data.max_seq_length` of the returned configuration."""
+    import functools
+    import inspect
+
+    @functools.wraps(fn)
+    def wrapper(model: str = "", *, model_name: str | None = None, max_seq_length: int | None = None):
+        cfg = fn(model_name if model_name is not None else model)
+        if max_seq_length is not None:
+            cfg.data.max_seq_length = int(max_seq_length)
+        return cfg
+    wrapper.__signature__ = inspect.signature(wrapper, follow_wrapped=False)
+    return wrapper
+
+
+@_preset
 def get_qlora_preset(model: str = "") -> SOTAConfig:
     return SOTAConfig(training_mode=TrainingMode.QLORA, model=ModelConfig(name_or_path=model),
                       lora=LoRAConfig(r=16, lora_alpha=32), optimizer=OptimizerConfig(learning_rate=2e-4))
 
 
+@_preset
 def get_lora_preset(model: str = "") -> SOTAConfig:
     return SOTAConfig(training_mode=TrainingMode.LORA, model=ModelConfig(name_or_path=model),
                       lora=LoRAConfig(r=64, lora_alpha=128), optimizer=OptimizerConfig(learning_rate=1e-4))
 
 
+@_preset
 def get_full_finetune_preset(model: str = "") -> SOTAConfig:
     return SOTAConfig(training_mode=TrainingMode.FULL_FINETUNE, model=ModelConfig(name_or_path=model),
                       lora=LoRAConfig(enabled=False), optimizer=OptimizerConfig(learning_rate=2e-5),
                       scheduler=SchedulerConfig(type=SchedulerType.WSD))
 
 
+@_preset
 def get_fp8_preset(model: str = "") -> SOTAConfig:
     c = get_full_finetune_preset(model)
     c.hardware.precision = Precision.FP8_E4M3
     return c
 
 
+@_preset
 def get_rl_grpo_preset(model: str = "") -> SOTAConfig:
     return SOTAConfig(training_mode=TrainingMode.RL, model=ModelConfig(name_or_path=model),
                       rl=RLConfig(enabled=True, algorithm=RLAlgorithm.GRPO),
                       optimizer=OptimizerConfig(learning_rate=1e-6))
 
 
+@_preset
 def get_pretrain_preset(model: str = "") -> SOTAConfig:
     return SOTAConfig(training_mode=TrainingMode.PRETRAIN, model=ModelConfig(name_or_path=model),
                       lora=LoRAConfig(enabled=False), optimizer=OptimizerConfig(learning_rate=3e-4, weight_decay=0.1),
                       scheduler=SchedulerConfig(type=SchedulerType.WSD, warmup_ratio=0.01))
 
 
+@_preset
 def get_dpo_preset(model: str = "") -> SOTAConfig:
     """Preference optimisation with the DPO loss (beta 0.1) against a frozen copy of the starting weights."""
     return SOTAConfig(training_mode=TrainingMode.RL, model=ModelConfig(name_or_path=model),

@@ -15,6 +15,7 @@ from typing import Any, Dict, List, Optional
 import yaml
 from pydantic import BaseModel, Field, field_validator, model_validator
 
+from ..utils.refargs import ANY, reference_kwargs
 from .data_schema import interpolate_env_vars
 
 
@@ -163,6 +164,7 @@ class TrainingArguments(BaseModel):
                              "logging_steps": self.logging.logging_steps}}
 
 
+@reference_kwargs(overrides="override")
 def merge_configs(base: Dict[str, Any], override: Dict[str, Any]) -> Dict[str, Any]:
     out = copy.deepcopy(base)
     for k, v in (override or {}).items():
@@ -173,9 +175,15 @@ def merge_configs(base: Dict[str, Any], override: Dict[str, Any]) -> Dict[str, A
     return out
 
 
-def load_training_config(path, overrides: Dict[str, Any] | None = None) -> TrainingArguments:
+@reference_kwargs(yaml_path="path")
+def load_training_config(path, overrides: Dict[str, Any] | None = None, config_key: str = "training_arguments",
+                         interpolate_env: bool = True) -> TrainingArguments:
+    """`TrainingArguments` from the `config_key` section of a YAML file (the whole file when it has no such section),
+    with ${VAR} / ${VAR:-default} interpolation unless `interpolate_env=False`."""
     raw = yaml.safe_load(Path(path).read_text()) or {}
-    raw = interpolate_env_vars(raw.get("training_arguments", raw))
+    raw = raw.get(config_key, raw) if config_key else raw
+    if interpolate_env:
+        raw = interpolate_env_vars(raw)
     return TrainingArguments(**merge_configs(raw, overrides or {}))
 
 

@@ -16,6 +16,7 @@ import torch
 
 from .core.errors import HubError
 from .hub import HubManager, ModelSerializer, generate_model_card
+from .utils.refargs import ANY, reference_kwargs
 
 
 def merge_lora_weights(model):
@@ -23,7 +24,23 @@ def merge_lora_weights(model):
     return merge_and_unload(model)
 
 
-def save_safetensors(model, out_dir, max_shard_gb: float = 5.0, tokenizer=None) -> Path:
+def _shard_gb(size) -> float:
+    """"5GB" / "500MB" / a number of bytes -> GiB."""
+    if isinstance(size, str):
+        t = size.strip().upper()
+        for unit, f in (("GB", 1.0), ("MB", 1 / 1024), ("KB", 1 / 1024 ** 2)):
+            if t.endswith(unit):
+                return float(t[:-2]) * f
+        return float(t) / 2 ** 30
+    return float(size) / 2 ** 30
+
+
+@reference_kwargs(output_dir="out_dir")
+def save_safetensors(model, out_dir, max_shard_gb: float = 5.0, tokenizer=None, *, max_shard_size=None) -> Path:
+    """Sharded safetensors (+ index, config.json, tokenizer files) under `out_dir`.  `max_shard_size` is the
+    reference's spelling of the shard limit: "5GB", "500MB" or a number of bytes."""
+    if max_shard_size is not None:
+        max_shard_gb = _shard_gb(max_shard_size)
     out = Path(out_dir)
     sd = model.to_hf_state_dict() if hasattr(model, "to_hf_state_dict") else model.state_dict()
     ModelSerializer(int(max_shard_gb * 2 ** 30)).save(sd, out)
@@ -35,8 +52,22 @@ def save_safetensors(model, out_dir, max_shard_gb: float = 5.0, tokenizer=None) 
     return out
 
 
-def export_to_gguf(model_dir, out_file, quantization: str = "f16", converter: str | None = None) -> Path:
-    """Needs llama.cpp's `convert_hf_to_gguf.py` (path in `converter` or on PATH); raises HubError when absent."""
+def export_to_gguf(model_dir=None, out_file=None, quantization: str = "f16", converter: str | None = None, *, model=None,
+                   tokenizer=None, output_dir=None) -> Path:
+    """Needs llama.cpp's `convert_hf_to_gguf.py` (path in `converter` or on PATH); raises HubError when absent.
+    The reference's form `export_to_gguf(model, tokenizer, output_dir, quantization)` (a module first) saves the model
+    as safetensors under `output_dir` and converts that folder to `output_dir/model-<quantization>.gguf`."""
+    if model is not None or isinstance(model_dir, torch.nn.Module):
+        model = model if model is not None else model_dir
+        tokenizer = tokenizer if tokenizer is not None else (out_file if not isinstance(out_file, (str, Path)) else None)
+        output_dir = output_dir if output_dir is not None else (quantization if converter in
+                                                                ("f16", "bf16", "q8_0", "f32", "q4_k_m", "q5_k_m") else None)
+        if output_dir is None:
+            raise ValueError("export_to_gguf(model, tokenizer, output_dir, quantization): output_dir is required")
+        if converter in ("f16", "bf16", "q8_0", "f32", "q4_k_m", "q5_k_m"):
+            quantization, converter = converter, None
+        model_dir = save_safetensors(model, output_dir, tokenizer=tokenizer)
+        out_file = Path(output_dir) / f"model-{quantization}.gguf"
     conv = converter or shutil.which("convert_hf_to_gguf.py") or shutil.which("convert-hf-to-gguf.py")
     if conv is None:
         raise HubError("GGUF export needs llama.cpp's convert_hf_to_gguf.py; pass converter=<path>")
@@ -47,17 +78,35 @@ def export_to_gguf(model_dir, out_file, quantization: str = "f16", converter: st
     return out
 
 
-def create_vllm_config(model_dir, tensor_parallel_size: int = 1, max_model_len: int = 8192, dtype: str = "bfloat16",
-                       gpu_memory_utilization: float = 0.9) -> Path:
+@reference_kwargs(model_path="model_dir")
+def create_vllm_config(model_dir, tensor_parallel_size: int | str = 1, max_model_len: int = 8192, dtype: str = "bfloat16",
+                       gpu_memory_utilization: float = 0.9, *, output_dir=None) -> Path:
+    """Writes serving_config.json (engine arguments for this framework's server or vLLM) into `output_dir`, by default
+    the model folder; `create_vllm_config(model_path, output_dir)` is the reference's positional form."""
+    if isinstance(tensor_parallel_size, (str, Path)):             # (model_path, output_dir)
+        output_dir, tensor_parallel_size = tensor_parallel_size, 1
     cfg = {"model": str(model_dir), "tensor_parallel_size": tensor_parallel_size, "max_model_len": max_model_len,
            "dtype": dtype, "gpu_memory_utilization": gpu_memory_utilization, "enable_prefix_caching": True}
-    p = Path(model_dir) / "serving_config.json"
+    target = Path(output_dir if output_dir is not None else model_dir)
+    target.mkdir(parents=True, exist_ok=True)
+    p = target / "serving_config.json"
     p.write_text(json.dumps(cfg, indent=2))
     return p
 
 
-def push_to_hub(folder, repo_id: str, token: str | None = None, private: bool = False) -> str | None:
-    return HubManager(repo_id, token, private).push(folder, "export")
+def push_to_hub(folder=None, repo_id: str | None = None, token: str | None = None, private: bool = False, *, model=None,
+                tokenizer=None, commit_message: str = "export") -> str | None:
+    """Upload a folder.  The reference's form `push_to_hub(model, tokenizer, repo_id, token, private, commit_message)`
+    (a module first) saves the model and tokenizer to a temporary folder and uploads that."""
+    if model is not None or isinstance(folder, torch.nn.Module):
+        import tempfile
+        if model is None:                                 # positional: (model, tokenizer, repo_id, token?)
+            model, tokenizer, repo_id, token = folder, repo_id, token, (private if isinstance(private, str) else None)
+            private = False if isinstance(private, str) else private
+        with tempfile.TemporaryDirectory(prefix="ts_export_") as tmp:
+            save_safetensors(model, tmp, tokenizer=tokenizer)
+            return HubManager(repo_id, token, private).push(tmp, commit_message)
+    return HubManager(repo_id, token, private).push(folder, commit_message)
 
 
 def export_model(model, out_dir, fmt: str = "safetensors", tokenizer=None, merge_lora: bool = True,

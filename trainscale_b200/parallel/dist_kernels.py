@@ -17,6 +17,8 @@ from typing import Any, Sequence
 import torch
 import torch.distributed as dist
 
+from ..utils.refargs import ANY, reference_kwargs
+
 ReduceOp = dist.ReduceOp
 
 
@@ -457,6 +459,7 @@ class ZeroCopyTransfer:
         return host
 
 
+@reference_kwargs(x="tensor")
 def pinned_memory_transfer(tensor: torch.Tensor, device: torch.device | str, non_blocking: bool = True) -> torch.Tensor:
     dev = torch.device(device)
     if dev.type != "cuda" or tensor.is_cuda:

@@ -22,6 +22,8 @@ import numpy as np
 import torch
 import torch.distributed as dist
 
+from ..utils.refargs import ANY, reference_kwargs
+
 logger = logging.getLogger("trainscale_b200")
 
 
@@ -303,30 +305,49 @@ class TensorPool:
 
 
 @torch.no_grad()
-def fused_clip_grad_norm_(parameters, max_norm: float, group=None) -> torch.Tensor:
-    """Global L2 norm over `.grad` (all-reduced over `group` for sharded grads), coefficient max_norm / (norm + 1e-6)
-    clamped to 1, applied in place. The coefficient stays on the device."""
+@reference_kwargs({"foreach": ANY}, model_or_params="parameters", process_group="group")
+def fused_clip_grad_norm_(parameters, max_norm: float, group=None, norm_type: float = 2.0,
+                          error_if_nonfinite: bool = False) -> torch.Tensor:
+    """Global norm over `.grad` (all-reduced over `group` for sharded grads), coefficient max_norm / (norm + 1e-6)
+    clamped to 1, applied in place. The coefficient stays on the device.  `parameters` may be a module."""
+    if isinstance(parameters, torch.nn.Module):
+        parameters = parameters.parameters()
     grads = [p.grad for p in parameters if p.grad is not None]
     if not grads:
         return torch.zeros(())
-    sq = torch.stack([g.float().pow(2).sum() for g in grads]).sum()
-    if group is not None and dist.is_initialized() and dist.get_world_size(group) > 1:
-        dist.all_reduce(sq, group=group)
-    norm = sq.sqrt()
+    sharded = group is not None and dist.is_initialized() and dist.get_world_size(group) > 1
+    if norm_type == float("inf"):
+        norm = torch.stack([g.float().abs().max() for g in grads]).max()
+        if sharded:
+            dist.all_reduce(norm, op=dist.ReduceOp.MAX, group=group)
+    else:
+        sq = torch.stack([g.float().abs().pow(norm_type).sum() for g in grads]).sum()
+        if sharded:
+            dist.all_reduce(sq, group=group)
+        norm = sq.pow(1.0 / norm_type)
+    if error_if_nonfinite and not bool(torch.isfinite(norm)):
+        raise RuntimeError(f"the total gradient norm is {float(norm)}")
     coef = (max_norm / (norm + 1e-6)).clamp(max=1.0)
     for g in grads:
         g.mul_(coef.to(g.dtype))
     return norm
 
 
-def dist_reduce(t: torch.Tensor, op: str = "mean", group=None) -> torch.Tensor:
+@reference_kwargs({"async_op": (False, None)}, tensor="t", process_group="group")
+def dist_reduce(t: torch.Tensor, op="mean", group=None) -> torch.Tensor:
+    """`op`: "mean" | "sum" | "max" | "min", or a `torch.distributed.ReduceOp`."""
     if not (dist.is_initialized() and dist.get_world_size(group) > 1):
         return t
     t = t.clone()
-    dist.all_reduce(t, op=dist.ReduceOp.MAX if op == "max" else dist.ReduceOp.SUM, group=group)
+    if not isinstance(op, str):
+        dist.all_reduce(t, op=op, group=group)
+        return t
+    red = {"max": dist.ReduceOp.MAX, "min": dist.ReduceOp.MIN}.get(op, dist.ReduceOp.SUM)
+    dist.all_reduce(t, op=red, group=group)
     return t / dist.get_world_size(group) if op == "mean" else t
 
 
+@reference_kwargs({"contiguous": ANY}, tensor="t", process_group="group")
 def dist_all_gather(t: torch.Tensor, group=None) -> list[torch.Tensor]:
     if not (dist.is_initialized() and dist.get_world_size(group) > 1):
         return [t]
@@ -335,8 +356,13 @@ def dist_all_gather(t: torch.Tensor, group=None) -> list[torch.Tensor]:
     return out
 
 
-def set_deterministic_seed(seed: int, rank: int = 0, fully_deterministic: bool = False) -> int:
-    s = seed + rank
+def set_deterministic_seed(seed: int, rank: int = 0, fully_deterministic: bool = False, *, state=None,
+                           per_rank_offset: bool = True) -> int:
+    """Seeds python / numpy / torch with seed + rank and returns that number.  `state` (a DistributedState) supplies
+    the rank; `per_rank_offset=False` gives every rank the same seed."""
+    if state is not None:
+        rank = int(getattr(state, "rank", rank))
+    s = seed + (rank if per_rank_offset else 0)
     random.seed(s)
     np.random.seed(s % 2 ** 32)
     torch.manual_seed(s)
@@ -414,14 +440,20 @@ class GradScaler:
         self.scale_value, self._good = sd["scale"], sd["good"]
 
 
-def log_rank_0(msg: str, level: int = logging.INFO):
+@reference_kwargs(message="msg")
+def log_rank_0(msg: str, level: int | str = logging.INFO, include_timestamp: bool = False):
     if not dist.is_initialized() or dist.get_rank() == 0:
+        if isinstance(level, str):
+            level = getattr(logging, level.upper(), logging.INFO)
+        if include_timestamp:
+            msg = f"[{datetime.datetime.now().isoformat(timespec='seconds')}] {msg}"
         logger.log(level, msg)
 
 
 @contextlib.contextmanager
-def main_process_first():
-    """Rank 0 runs the block first (e.g. dataset preprocessing with a cache), the others after it."""
+def main_process_first(dist_manager=None):
+    """Rank 0 runs the block first (e.g. dataset preprocessing with a cache), the others after it.  `dist_manager` is
+    accepted for the reference's call form; rank and world come from torch.distributed either way."""
     multi = dist.is_initialized() and dist.get_world_size() > 1
     if multi and dist.get_rank() != 0:
         dist.barrier()
@@ -461,6 +493,8 @@ class HeartbeatMonitor:
 
 
 # ------------------------------------------------------------------------------------------------ gradient plumbing
+@reference_kwargs({"async_op": (False, None), "op": (None, dist.ReduceOp.SUM)}, output_tensor="output",
+                  input_tensor="input")
 def reduce_scatter_with_fp32_accumulation(output: torch.Tensor, input: torch.Tensor, group=None) -> torch.Tensor:
     """Reduce-scatter of a low-precision tensor whose sum is taken in fp32: every rank receives the W slices meant
     for it (all-to-all) and adds them in fp32 (data_pipeline/trainer/distributed/reduce_scatter_fp32.py:90).
@@ -847,8 +881,16 @@ class DistributedLogger:
 _GROUPS: dict[str, object] = {}
 
 
-def setup_distributed(backend: str | None = None, timeout_s: int = 1800) -> DistributedState:
-    """Rendezvous from the launcher's environment (no-op for a single process); selects this rank's GPU."""
+def setup_distributed(backend: str | None = None, timeout_s: int = 1800, *, config=None) -> DistributedState:
+    """Rendezvous from the launcher's environment (no-op for a single process); selects this rank's GPU.  `config`
+    (a mapping or object with `backend` / `timeout_seconds`) fills what the arguments leave unset."""
+    if backend is not None and not isinstance(backend, str):        # setup_distributed(config, backend=None)
+        config, backend = backend, None
+    if config is not None:
+        get = config.get if isinstance(config, dict) else (lambda k, d=None: getattr(config, k, d))
+        backend = backend or get("backend")
+        backend = getattr(backend, "value", backend)
+        timeout_s = int(get("timeout_seconds", None) or get("timeout_s", None) or timeout_s)
     return DistributedState.initialize(backend, timeout_s)
 
 
@@ -863,6 +905,7 @@ def get_process_group(name: str = "world"):
     return _GROUPS.get(name)
 
 
+@reference_kwargs({"async_op": (False, None), "compression": (None, "none", False)}, process_group="group")
 def sync_gradients(model, group=None, average: bool = True, bucket_mb: float = 25.0) -> None:
     """One-shot bucketed all-reduce of a plain model's `.grad`s (for code that does not use an engine)."""
     if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size(group) == 1:
@@ -891,10 +934,21 @@ def prepare_model_for_distributed(model, strategy: str = "ddp", device=None, **e
     return model, eng
 
 
-def save_checkpoint_distributed(path, model, engine=None, extra: dict | None = None) -> None:
-    """Collective: rank 0 writes the full weights (+ `extra`), every rank writes its optimizer shard."""
+def save_checkpoint_distributed(path, model=None, engine=None, extra: dict | None = None, *, state_dict=None,
+                                state=None, barrier_after: bool = True) -> None:
+    """Collective: rank 0 writes the full weights (+ `extra`), every rank writes its optimizer shard.  The reference's
+    form `save_checkpoint_distributed(state_dict, path, state)` writes a ready state dict from rank 0 to the FILE `path`."""
     from ..ckpt import _to_cpu, atomic_torch_save
     from pathlib import Path
+    if isinstance(path, dict) or state_dict is not None:
+        sd, file = (path, model) if isinstance(path, dict) else (state_dict, path)
+        on = dist.is_available() and dist.is_initialized()
+        if not on or dist.get_rank() == 0:
+            Path(file).parent.mkdir(parents=True, exist_ok=True)
+            atomic_torch_save(_to_cpu(sd), Path(file))
+        if on and barrier_after:
+            dist.barrier()
+        return
     path = Path(path)
     on = dist.is_available() and dist.is_initialized()
     rank, world = (dist.get_rank(), dist.get_world_size()) if on else (0, 1)
@@ -908,11 +962,16 @@ def save_checkpoint_distributed(path, model, engine=None, extra: dict | None = N
         dist.barrier()
 
 
-def load_checkpoint_distributed(path, model, engine=None, strict: bool = True) -> dict:
-    """Inverse of `save_checkpoint_distributed`; optimizer shards saved at another world size are re-sliced."""
+def load_checkpoint_distributed(path, model=None, engine=None, strict: bool = True, *, state=None, map_location="cpu"
+                                ) -> dict:
+    """Inverse of `save_checkpoint_distributed`; optimizer shards saved at another world size are re-sliced.  A `path`
+    that is a file (the reference's form, `load_checkpoint_distributed(path, state, map_location)`) is read on every
+    rank and returned as it is."""
     from ..ckpt import engine_layout, reshard_optimizer_state
     from pathlib import Path
     path = Path(path)
+    if path.is_file():
+        return torch.load(path, map_location=map_location, weights_only=False)
     blob = torch.load(path / "model.pt", map_location="cpu", weights_only=False)
     summon = engine.summon_full_params() if engine is not None and hasattr(engine, "summon_full_params") \
         else contextlib.nullcontext()

@@ -23,6 +23,8 @@ from typing import Any, Callable, NamedTuple, Sequence
 
 import torch
 import torch.distributed as dist
+
+from ..utils.refargs import ANY, reference_kwargs
 import torch.nn as nn
 
 from ..core.types import Err, Ok, Result
@@ -481,12 +483,16 @@ class CheckpointFunction(torch.autograd.Function):
         return (None, None) + grads
 
 
-def selective_checkpoint(module: nn.Module, *args, enabled: bool = True):
-    """Run `module(*args)` under recompute-in-backward when `enabled` (parameters get their gradients in backward)."""
+@reference_kwargs({"preserve_rng_state": ANY}, function="module")
+def selective_checkpoint(module, *args, enabled: bool = True):
+    """Run `module(*args)` under recompute-in-backward when `enabled` (parameters get their gradients in backward).
+    `module` may be any callable (`function=` in the reference's spelling)."""
     if not enabled or not torch.is_grad_enabled():
         return module(*args)
     # a dummy that requires grad makes autograd call backward even when no input does (first stage: token ids)
-    anchor = torch.zeros((), requires_grad=True, device=next(module.parameters()).device)
+    dev = next(module.parameters()).device if isinstance(module, nn.Module) and any(True for _ in module.parameters()) \
+        else next((a.device for a in args if torch.is_tensor(a)), torch.device("cpu"))
+    anchor = torch.zeros((), requires_grad=True, device=dev)
     return CheckpointFunction.apply(lambda *a: module(*a[:-1]), len(args) + 1, *args, anchor)
 
 
@@ -901,10 +907,19 @@ _SCHEDULES = {ScheduleType.GPIPE: GPipeSchedule, ScheduleType.ONE_F_ONE_B: OneFO
               ScheduleType.ZERO_BUBBLE: ZeroBubbleSchedule, ScheduleType.CHIMERA: ChimeraSchedule}
 
 
-def create_schedule(stages: Sequence[PipelineStage], config: PipelineConfig, loss_fn: Callable,
-                    communicator: P2PCommunicator | None = None, memory_manager: ActivationMemoryManager | None = None,
-                    ctx: DistributedContext | None = None) -> PipelineSchedule:
-    return _SCHEDULES[config.schedule](stages, config, loss_fn, communicator, memory_manager, ctx)
+def create_schedule(stages, config=None, loss_fn=None, communicator: P2PCommunicator | None = None,
+                    memory_manager: ActivationMemoryManager | None = None, ctx: DistributedContext | None = None, *,
+                    schedule_type=None) -> PipelineSchedule:
+    """Schedule object for `config.schedule`.  The reference passes the kind first, `create_schedule(schedule_type,
+    stages, config, loss_fn, ...)` (data_pipeline/trainer/distributed/pipeline_parallel.py:2029): a `ScheduleType` or
+    its name in the first position, or `schedule_type=`, overrides `config.schedule`."""
+    if isinstance(stages, (ScheduleType, str)):
+        schedule_type, stages, config, loss_fn, communicator, memory_manager = (stages, config, loss_fn, communicator,
+                                                                                memory_manager, ctx)
+        ctx = None
+    kind = config.schedule if schedule_type is None else schedule_type
+    kind = kind if isinstance(kind, ScheduleType) else ScheduleType(str(kind).lower())
+    return _SCHEDULES[kind](stages, config, loss_fn, communicator, memory_manager, ctx)
 
 
 # ------------------------------------------------------------------------------------------------ wrapper
@@ -952,21 +967,53 @@ class PipelineParallel(nn.Module):
 # ------------------------------------------------------------------------------------------------ partitioning
 def split_model_into_stages(model: nn.Module | Sequence[nn.Module], num_stages: int,
                             costs: Sequence[float] | None = None, device: torch.device | str | None = None,
-                            checkpoint_activations: bool = False) -> list[PipelineStage]:
+                            checkpoint_activations: bool = False, *, split_points: Sequence[str] | None = None,
+                            balance: Sequence[int] | None = None) -> list[PipelineStage]:
     """Cut a sequence of layers (an `nn.Sequential`, a list of modules, or a module whose children form the chain)
-    into `num_stages` contiguous stages: equal layer counts, or minimal maximum cost when `costs` are given."""
-    layers = list(model) if isinstance(model, (nn.Sequential, list, tuple, nn.ModuleList)) else list(model.children())
+    into `num_stages` contiguous stages: equal layer counts, or minimal maximum cost when `costs` are given.
+    `balance` fixes the number of layers per stage; `split_points` names the child modules at which a new stage
+    begins (data_pipeline/trainer/distributed/pipeline_parallel.py:2318)."""
+    if isinstance(model, (nn.Sequential, list, tuple, nn.ModuleList)):
+        named = [(str(i), m) for i, m in enumerate(model)]
+    else:
+        named = list(model.named_children())
+    layers = [m for _, m in named]
     if len(layers) < num_stages:
         raise ValueError(f"{len(layers)} layers cannot fill {num_stages} stages")
-    ranges = PP.split_layers(len(layers), num_stages, costs)
+    if balance is not None:
+        if len(balance) != num_stages or sum(balance) != len(layers) or min(balance) < 1:
+            raise ValueError(f"balance {list(balance)} must give {num_stages} positive counts summing to {len(layers)}")
+        cuts = [0]
+        for n in balance:
+            cuts.append(cuts[-1] + n)
+        ranges = [range(a, b) for a, b in zip(cuts, cuts[1:])]
+    elif split_points is not None:
+        names = [n for n, _ in named]
+        cuts = [0] + sorted(names.index(p) for p in split_points) + [len(layers)]
+        if len(cuts) - 1 != num_stages or any(b <= a for a, b in zip(cuts, cuts[1:])):
+            raise ValueError(f"split_points {list(split_points)} do not give {num_stages} non-empty stages")
+        ranges = [range(a, b) for a, b in zip(cuts, cuts[1:])]
+    else:
+        ranges = PP.split_layers(len(layers), num_stages, costs)
     return [PipelineStage(nn.Sequential(*[layers[i] for i in r]), s, num_stages, device, checkpoint_activations)
             for s, r in enumerate(ranges)]
 
 
-def estimate_stage_memory(stage: nn.Module, batch_size: int = 1, seq_len: int = 1, hidden: int | None = None,
-                          dtype_bytes: int = 2, optimizer_bytes_per_param: int = 12, in_flight: int = 1) -> dict:
+def estimate_stage_memory(stage: nn.Module = None, batch_size: int = 1, seq_len: int = 1, hidden: int | None = None,
+                          dtype_bytes: int = 2, optimizer_bytes_per_param: int = 12, in_flight: int = 1, *,
+                          stages: Sequence[nn.Module] | None = None, input_shape: Sequence[int] | None = None,
+                          dtype: torch.dtype | None = None):
     """Bytes a stage needs: parameters + gradients + optimizer state + `in_flight` micro-batches of activations
-    (counted as outputs of its linear layers, or batch*seq*hidden per child when `hidden` is given)."""
+    (counted as outputs of its linear layers, or batch*seq*hidden per child when `hidden` is given).
+    The reference's form `estimate_stage_memory(stages, input_shape, dtype)` returns one total in MiB per stage."""
+    if stages is not None or isinstance(stage, (list, tuple)):
+        stages = stages if stages is not None else stage
+        shape = tuple(input_shape if input_shape is not None else (batch_size if isinstance(batch_size, (list, tuple))
+                                                                   else (1, 1)))
+        b, sq = (shape + (1, 1))[:2]
+        eb = torch.empty((), dtype=dtype).element_size() if dtype is not None else dtype_bytes
+        return [estimate_stage_memory(st, b, sq, None, eb, optimizer_bytes_per_param, in_flight)["total"] / 2 ** 20
+                for st in stages]
     n = sum(p.numel() for p in stage.parameters())
     if hidden is not None:
         act = batch_size * seq_len * hidden * dtype_bytes * max(1, len(list(stage.modules())) - 1)
@@ -978,10 +1025,17 @@ def estimate_stage_memory(stage: nn.Module, batch_size: int = 1, seq_len: int = 
             "total": n * (2 * dtype_bytes + optimizer_bytes_per_param) + act * in_flight}
 
 
+@reference_kwargs({"target_memory_mb": ANY}, model="layers")
 def balance_stages_by_memory(layers: Sequence[nn.Module], num_stages: int, batch_size: int = 1, seq_len: int = 1,
-                             schedule: str = "1f1b") -> list[range]:
+                             schedule: str = "1f1b", *, input_shape: Sequence[int] | None = None) -> list[range]:
     """Contiguous split minimising the largest stage footprint.  Under 1F1B stage s keeps P - s micro-batches of
-    activations alive, so early stages are charged more per layer; two passes refine the split with those weights."""
+    activations alive, so early stages are charged more per layer; two passes refine the split with those weights.
+    `layers` may be a module (its children are the layers); `input_shape` = (batch, seq, ...) sets both sizes."""
+    if isinstance(layers, nn.Module) and not isinstance(layers, (nn.Sequential, nn.ModuleList)):
+        layers = list(layers.children())
+    layers = list(layers)
+    if input_shape is not None:
+        batch_size, seq_len = (tuple(input_shape) + (1, 1))[:2]
     base = [estimate_stage_memory(l, batch_size, seq_len) for l in layers]
     costs = [b["total"] for b in base]
     ranges = PP.split_layers(len(layers), num_stages, costs)
@@ -997,6 +1051,7 @@ def balance_stages_by_memory(layers: Sequence[nn.Module], num_stages: int, batch
     return ranges
 
 
+@reference_kwargs(tensor="batch")
 def split_into_microbatches(batch, num_microbatches: int):
     """Tensor -> list of chunks along dim 0; dict of tensors -> list of dicts."""
     if isinstance(batch, dict):
@@ -1004,6 +1059,7 @@ def split_into_microbatches(batch, num_microbatches: int):
     return list(batch.chunk(num_microbatches, dim=0))
 
 
+@reference_kwargs(microbatches="outputs")
 def merge_microbatches(outputs: Sequence) -> Any:
     if not outputs:
         return outputs
@@ -1015,8 +1071,25 @@ def merge_microbatches(outputs: Sequence) -> Any:
 
 
 @contextlib.contextmanager
-def pipeline_profiler(pipeline: PipelineParallel, name: str = "pipeline", log: Callable[[str], None] | None = None):
-    """Times the block (CUDA-synchronised when the stages are on a GPU) and reports the schedule's counters."""
+def pipeline_profiler(pipeline=None, name: str = "pipeline", log: Callable[[str], None] | None = None, *,
+                      config: "ProfilingConfig | None" = None, output_dir: str | None = None):
+    """Times the block (CUDA-synchronised when the stages are on a GPU) and reports the schedule's counters.
+    The reference's form `pipeline_profiler(config, output_dir)` (a ProfilingConfig first) wraps the block in
+    `torch.profiler` and writes a Chrome trace under `output_dir` when `config.enabled`; it yields the profiler."""
+    if isinstance(pipeline, ProfilingConfig) or config is not None:
+        config = config if config is not None else pipeline
+        out = output_dir if output_dir is not None else (name if name != "pipeline" else "./profiles")
+        if not config.enabled:
+            yield None
+            return
+        import os
+        from torch.profiler import ProfilerActivity, profile
+        os.makedirs(out, exist_ok=True)
+        acts = [ProfilerActivity.CPU] + ([ProfilerActivity.CUDA] if torch.cuda.is_available() else [])
+        with profile(activities=acts) as prof:
+            yield prof
+        prof.export_chrome_trace(os.path.join(out, "pipeline_trace.json"))
+        return
     dev = pipeline.stages[0].device if len(pipeline.stages) else torch.device("cpu")
     if dev.type == "cuda":
         torch.cuda.synchronize(dev)

@@ -212,7 +212,22 @@ def quantize_nf4(w: torch.Tensor, block: int = 64):
     return packed, absmax.squeeze(1), w.shape
 
 
-def fast_dequantize(packed: torch.Tensor, absmax: torch.Tensor, shape, dtype=torch.bfloat16) -> torch.Tensor:
+def fast_dequantize(packed: torch.Tensor = None, absmax: torch.Tensor = None, shape=None, dtype=torch.bfloat16, *,
+                    weight: torch.Tensor | None = None, quant_state=None, out_dtype=None) -> torch.Tensor:
+    """NF4 codes + per-block absmax -> dense tensor.  The reference's form `fast_dequantize(weight, quant_state,
+    out_dtype)` is taken too: a floating-point `weight` is only cast; a packed one uses `quant_state` (or the state
+    attached to it by `quantize_nf4_param`)."""
+    if weight is not None or absmax is None or isinstance(absmax, QuantState):
+        weight = weight if weight is not None else packed
+        quant_state = quant_state if quant_state is not None else (absmax if isinstance(absmax, QuantState) else None)
+        dtype = out_dtype or (shape if isinstance(shape, torch.dtype) else dtype)
+        if weight.is_floating_point():
+            return weight.to(dtype)
+        qs = quant_state or get_quant_state(weight)
+        if qs is None:
+            raise ValueError("a packed weight needs its quant_state")
+        return fast_dequantize(weight, qs.absmax, tuple(qs.shape), dtype)
+    dtype = out_dtype or dtype
     hi, lo = (packed >> 4).long(), (packed & 0xF).long()
     idx = torch.stack((hi, lo), dim=-1).flatten(1)
     vals = NF4_LEVELS.to(packed.device)[idx] * absmax.unsqueeze(1)
@@ -222,8 +237,25 @@ def fast_dequantize(packed: torch.Tensor, absmax: torch.Tensor, shape, dtype=tor
     return vals.reshape(-1)[:n].view(shape).to(dtype)
 
 
-def estimate_memory_usage(n_params: float, weight_bits: int = 16, trainable_fraction: float = 1.0,
-                          optimizer_bytes_per_param: float = 12.0, grad_bits: int = 16) -> dict:
+def estimate_memory_usage(n_params: float = None, weight_bits: int = 16, trainable_fraction: float = 1.0,
+                          optimizer_bytes_per_param: float = 12.0, grad_bits: int = 16, *,
+                          model_size_billion: float | None = None, config: "QuantizationConfig | None" = None,
+                          batch_size: int = 1, seq_length: int = 2048) -> dict:
+    """Weights + gradients + optimizer state in GiB.  The reference's form (`model_size_billion`, a
+    `QuantizationConfig`, batch size, sequence length - by name, or positionally when the second argument is a config)
+    returns its keys: model_gb, lora_gb (2 % of the base), activation_gb, gradient_gb, total_gb
+    (data_pipeline/trainer/quantization.py:264-297)."""
+    if model_size_billion is not None or isinstance(weight_bits, QuantizationConfig):
+        if model_size_billion is None:
+            model_size_billion, config = n_params, weight_bits
+        bits = 4 if config.load_in_4bit else 8 if (config.load_in_8bit or getattr(config, "load_in_fp8", False)) else 16
+        quantized = bits < 16
+        model_gb = model_size_billion * 1e9 * bits / 8 / 2 ** 30
+        lora_gb = 0.02 * model_gb
+        act_gb = batch_size * seq_length * int(model_size_billion * 1000) * 2 * 4 / 2 ** 30
+        grad_gb = lora_gb if quantized else model_gb
+        return {"model_gb": round(model_gb, 2), "lora_gb": round(lora_gb, 2), "activation_gb": round(act_gb, 2),
+                "gradient_gb": round(grad_gb, 2), "total_gb": round(model_gb + lora_gb + act_gb + grad_gb, 2)}
     gb = 1 / 2 ** 30
     weights = n_params * weight_bits / 8
     grads = n_params * trainable_fraction * grad_bits / 8

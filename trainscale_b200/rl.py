@@ -18,22 +18,63 @@ import torch.nn.functional as F
 
 from .losses import CPOLoss, DPOLoss, KTOLoss, ORPOLoss, SimPOLoss
 from .ops import cross_entropy as ce_ops
+from .utils.refargs import ANY, reference_kwargs
 
 
-def selective_log_softmax(logits: torch.Tensor, index: torch.Tensor) -> torch.Tensor:
-    """log_softmax(logits)[..., index] without keeping the full log-softmax."""
+@reference_kwargs(input_ids="index")
+def selective_log_softmax(logits: torch.Tensor, index: torch.Tensor, temperature: float = 1.0,
+                          logit_softcapping: float = 0.0, logit_scale: float = 0.0) -> torch.Tensor:
+    """log_softmax(logits)[..., index] without keeping the full log-softmax.  Optional transforms of the logits, in
+    this order: soft-cap c tanh(z / c), scale, divide by the temperature."""
+    if logit_softcapping:
+        logits = logit_softcapping * torch.tanh(logits / logit_softcapping)
+    if logit_scale:
+        logits = logits * logit_scale
+    if temperature != 1.0:
+        logits = logits / temperature
     sel = logits.gather(-1, index.unsqueeze(-1)).squeeze(-1).float()
     return sel - torch.logsumexp(logits.float(), dim=-1)
 
 
+@reference_kwargs(hidden_states="hidden", input_ids="labels")
 def chunked_log_softmax(hidden: torch.Tensor, lm_head: torch.Tensor, labels: torch.Tensor, chunk_tokens: int = 4096,
-                        ignore_index: int = -100) -> torch.Tensor:
-    """Per-token log p(label) from hidden states, chunked over tokens: only [B, L] values are kept."""
+                        ignore_index: int = -100, *, num_chunks: int | None = None, temperature: float = 1.0,
+                        logit_softcapping: float = 0.0, logit_scale: float = 0.0) -> torch.Tensor:
+    """Per-token log p(label) from hidden states, chunked over tokens: only [B, L] values are kept.  `num_chunks`
+    (the reference's knob) sets the chunk size to tokens / num_chunks.  Temperature and logit scale act on the hidden
+    states (the head is linear); soft-capping is not linear and takes the chunked PyTorch path."""
+    tokens = labels.numel()
+    if num_chunks:
+        chunk_tokens = max(1, -(-tokens // int(num_chunks)))
+    if logit_softcapping:
+        h2, y = hidden.reshape(-1, hidden.shape[-1]), labels.reshape(-1)
+        out = []
+        for a in range(0, tokens, chunk_tokens):
+            z = h2[a:a + chunk_tokens].float() @ lm_head.float().t()
+            out.append(selective_log_softmax(z, y[a:a + chunk_tokens].clamp(min=0), temperature, logit_softcapping,
+                                             logit_scale) * (y[a:a + chunk_tokens] != ignore_index))
+        return torch.cat(out).view(labels.shape)
+    factor = (logit_scale or 1.0) / temperature
+    if factor != 1.0:
+        hidden = hidden * factor
     return ce_ops.fused_linear_token_logprobs(hidden, lm_head, labels, ignore_index, chunk_tokens)
 
 
-def compute_advantages(rewards: torch.Tensor, group_size: int, eps: float = 1e-4, scale: bool = True) -> torch.Tensor:
-    """Group-normalised advantages: rewards [N] with consecutive groups of `group_size` samples per prompt."""
+def compute_advantages(rewards: torch.Tensor, group_size: int | str | None = None, eps: float = 1e-4, scale: bool = True,
+                       *, baseline: str | None = None) -> torch.Tensor:
+    """Group-normalised advantages: rewards [N] with consecutive groups of `group_size` samples per prompt.
+
+    The reference's form `compute_advantages(rewards [B, G], baseline="mean" | "max" | "min" | "none", eps)` subtracts the
+    per-row baseline and divides by the standard deviation of ALL advantages (data_pipeline/trainer/rl_training.py:241);
+    it is selected by `baseline=` or by a string in the second position, and returns the [B, G] shape."""
+    if isinstance(group_size, str) or baseline is not None or group_size is None:
+        kind = baseline if baseline is not None else (group_size or "mean")
+        r = rewards.float()
+        base = {"mean": lambda: r.mean(-1, keepdim=True), "max": lambda: r.max(-1, keepdim=True).values,
+                "min": lambda: r.min(-1, keepdim=True).values}.get(kind, lambda: 0.0)()
+        a = r - base
+        std = a.std() if a.numel() > 1 else a.new_zeros(())
+        return a / std if float(std) > eps else a
     r = rewards.float().view(-1, group_size)
     a = r - r.mean(1, keepdim=True)
     if scale:
@@ -45,9 +86,47 @@ def _masked_mean(x, mask, dim=None):
     return (x * mask).sum(dim) / mask.sum(dim).clamp(min=1)
 
 
-def grpo_loss(logp: torch.Tensor, old_logp: torch.Tensor, ref_logp: torch.Tensor | None, advantages: torch.Tensor,
-              mask: torch.Tensor, clip: float = 0.2, beta: float = 0.01) -> torch.Tensor:
-    """Clipped surrogate per token, averaged per sequence then over the batch, plus the k3 KL estimator."""
+def _seq_mean(x, mask):
+    return (x * mask).sum(-1) / mask.sum(-1).clamp(min=1)
+
+
+def _reference_rl_loss(kind: str, policy_log_probs, ref_log_probs, third, mask, beta=0.04, epsilon=0.1, temperature=1.0):
+    """The reference's sequence-level formulations (data_pipeline/trainer/rl_training.py:297-430), returning
+    (loss, metrics).  grpo: -E[A * mean log pi] + beta * KL-per-token; drgrpo: PPO-style clipping of the sequence-level
+    ratio pi / pi_ref; dapo: policy gradient weighted by softmax(rewards / temperature) over each group."""
+    lp, lr = _seq_mean(policy_log_probs, mask), _seq_mean(ref_log_probs, mask)
+    log_ratio = policy_log_probs - ref_log_probs
+    metrics = {}
+    if kind == "grpo":
+        pg = -(third * lp).mean()
+        kl_tok = log_ratio * mask
+        kl = beta * kl_tok.sum(-1).mean() / mask.sum(-1).clamp(min=1).mean()
+        metrics["kl_div"] = float((kl_tok.mean()).detach())
+    elif kind == "drgrpo":
+        ratio = torch.exp(_seq_mean(log_ratio, mask))
+        adv = third.reshape(-1)
+        pg = -torch.minimum(ratio.reshape(-1) * adv, ratio.clamp(1 - epsilon, 1 + epsilon).reshape(-1) * adv).mean()
+        kl_seq = _seq_mean(log_ratio, mask)
+        kl = beta * kl_seq.mean()
+        metrics.update(kl_div=float((kl_seq.mean()).detach()), ratio_mean=float((ratio.mean()).detach()))
+    else:
+        soft = torch.softmax(third.float() / temperature, dim=-1)
+        pg = -(soft * lp).sum(-1).mean()
+        kl = beta * _seq_mean(log_ratio, mask).mean()
+        metrics["soft_advantages_entropy"] = float(-(soft * soft.clamp_min(1e-30).log()).sum(-1).mean().detach())
+    loss = pg + kl
+    metrics.update(pg_loss=float((pg).detach()), kl_loss=float((kl).detach()), total_loss=float((loss).detach()))
+    return loss, metrics
+
+
+def grpo_loss(logp: torch.Tensor = None, old_logp: torch.Tensor = None, ref_logp: torch.Tensor | None = None,
+              advantages: torch.Tensor = None, mask: torch.Tensor = None, clip: float = 0.2, beta: float = 0.01, *,
+              policy_log_probs=None, ref_log_probs=None):
+    """Clipped surrogate per token, averaged per sequence then over the batch, plus the k3 KL estimator.
+    Called with the reference's keywords (`policy_log_probs=, ref_log_probs=, advantages=, mask=, beta=`) it computes
+    the reference's sequence-level loss instead and returns (loss, metrics): see `_reference_rl_loss`."""
+    if policy_log_probs is not None:
+        return _reference_rl_loss("grpo", policy_log_probs, ref_log_probs, advantages, mask, beta)
     ratio = torch.exp(logp - old_logp)
     a = advantages.unsqueeze(-1)
     obj = torch.minimum(ratio * a, ratio.clamp(1 - clip, 1 + clip) * a)
@@ -58,8 +137,13 @@ def grpo_loss(logp: torch.Tensor, old_logp: torch.Tensor, ref_logp: torch.Tensor
     return _masked_mean(per_tok, mask, dim=-1).mean()
 
 
-def drgrpo_loss(logp, old_logp, advantages, mask, clip: float = 0.2, max_len: int | None = None) -> torch.Tensor:
-    """Dr. GRPO: no std scaling in the advantage and a constant length normaliser (removes the length bias)."""
+def drgrpo_loss(logp=None, old_logp=None, advantages=None, mask=None, clip: float = 0.2, max_len: int | None = None, *,
+                policy_log_probs=None, ref_log_probs=None, beta: float = 0.04, epsilon: float = 0.1):
+    """Dr. GRPO: no std scaling in the advantage and a constant length normaliser (removes the length bias).
+    With the reference's keywords (`policy_log_probs=, ref_log_probs=, ..., beta=, epsilon=`): its formulation,
+    returning (loss, metrics)."""
+    if policy_log_probs is not None:
+        return _reference_rl_loss("drgrpo", policy_log_probs, ref_log_probs, advantages, mask, beta, epsilon)
     ratio = torch.exp(logp - old_logp)
     a = advantages.unsqueeze(-1)
     obj = torch.minimum(ratio * a, ratio.clamp(1 - clip, 1 + clip) * a)
@@ -67,16 +151,32 @@ def drgrpo_loss(logp, old_logp, advantages, mask, clip: float = 0.2, max_len: in
     return -((obj * mask).sum(-1) / L).mean()
 
 
-def dapo_loss(logp, old_logp, advantages, mask, clip_low: float = 0.2, clip_high: float = 0.28) -> torch.Tensor:
-    """DAPO: decoupled clip range and token-level normalisation over the whole batch."""
+def dapo_loss(logp=None, old_logp=None, advantages=None, mask=None, clip_low: float = 0.2, clip_high: float = 0.28, *,
+              policy_log_probs=None, ref_log_probs=None, rewards=None, beta: float = 0.04, temperature: float = 1.0):
+    """DAPO: decoupled clip range and token-level normalisation over the whole batch.  With the reference's keywords
+    (`policy_log_probs=, ref_log_probs=, rewards=, mask=, beta=, temperature=`): its soft-advantage formulation,
+    returning (loss, metrics)."""
+    if policy_log_probs is not None:
+        return _reference_rl_loss("dapo", policy_log_probs, ref_log_probs, rewards, mask, beta, temperature=temperature)
     ratio = torch.exp(logp - old_logp)
     a = advantages.unsqueeze(-1)
     obj = torch.minimum(ratio * a, ratio.clamp(1 - clip_low, 1 + clip_high) * a)
     return -(obj * mask).sum() / mask.sum().clamp(min=1)
 
 
-def left_pack_padding(ids: torch.Tensor, mask: torch.Tensor, pad_id: int = 0):
-    """Move real tokens to the left of every row (stable), padding to the right."""
+@reference_kwargs(input_ids="ids")
+def left_pack_padding(ids: torch.Tensor, mask: torch.Tensor | int | None = None, pad_id: int = 0, *,
+                      pad_token_id: int | None = None):
+    """Move real tokens to the left of every row (stable), padding to the right: returns (ids, mask).
+
+    The reference's function of this name, `left_pack_padding(input_ids, pad_token_id)`, goes the other way: it moves
+    the PADDING to the left (real tokens end flush right, as its attention path wants) and returns the ids alone
+    (data_pipeline/trainer/rl_training.py:434).  That form is selected by an integer second argument or `pad_token_id=`."""
+    if pad_token_id is not None or isinstance(mask, int):
+        pad = pad_token_id if pad_token_id is not None else mask
+        real = ids != pad
+        order = torch.argsort(real.int(), dim=1, stable=True)          # padding first, tokens keep their order
+        return ids.gather(1, order)
     order = torch.argsort((mask == 0).int(), dim=1, stable=True)
     return ids.gather(1, order).masked_fill(mask.gather(1, order) == 0, pad_id), mask.gather(1, order)
 
