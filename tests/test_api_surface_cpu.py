@@ -129,6 +129,65 @@ def test_every_public_method_of_a_shared_class_exists_here():
     assert not missing, f"{sum(map(len, missing.values()))} members missing: {sorted(missing.items())[:15]}"
 
 
+def _reference_function_params(root: Path) -> dict[str, list[list[str]]]:
+    out: dict[str, list[list[str]]] = {}
+    for p in root.rglob("*.py"):
+        if "examples" in p.parts:
+            continue
+        try:
+            tree = ast.parse(p.read_text())
+        except SyntaxError:
+            continue
+        for node in tree.body:
+            if isinstance(node, (ast.FunctionDef, ast.AsyncFunctionDef)) and not node.name.startswith("_"):
+                a = node.args
+                out.setdefault(node.name, []).append([x.arg for x in a.posonlyargs + a.args + a.kwonlyargs])
+    return out
+
+
+def test_shared_functions_take_the_reference_keyword_names():
+    """For every public function that exists under the same name on both sides, ours can be called with each of the
+    reference's parameter names as a keyword (its own parameter, an alias, or **kwargs)."""
+    import importlib
+    import inspect
+    import pkgutil
+
+    import trainscale_b200
+    ref = _reference_root()
+    if ref is None:
+        pytest.skip("the reference package is not on this machine")
+    ours: dict[str, set] = {}
+    for m in pkgutil.walk_packages(trainscale_b200.__path__, "trainscale_b200."):
+        if m.name.endswith("__main__"):
+            continue
+        try:
+            mod = importlib.import_module(m.name)
+        except Exception:   # noqa: BLE001
+            continue
+        for n, v in vars(mod).items():
+            if not n.startswith("_") and callable(v) and not inspect.isclass(v) \
+                    and getattr(v, "__module__", "").startswith("trainscale_b200"):
+                ours.setdefault(n, set()).add(v)
+
+    def lacking(fn, names):
+        try:
+            ps = inspect.signature(fn).parameters
+        except (ValueError, TypeError):
+            return []
+        if any(p.kind is p.VAR_KEYWORD for p in ps.values()):
+            return []
+        return [n for n in names if n not in ps]
+
+    missing = {}
+    for name, variants in _reference_function_params(ref).items():
+        if name not in ours:
+            continue
+        best = min((lacking(fn, names) for names in variants for fn in ours[name]), key=len)
+        if best:
+            missing[name] = best
+    assert not missing, f"{len(missing)} functions lack reference keywords: {sorted(missing.items())[:15]}"
+
+
 def test_last_helpers_behave():
     import torch
 

@@ -1,0 +1,296 @@
+"""Functions that share a name with the reference also take the reference's way of calling them: its keyword
+spellings, its positional orders where they differ, its tensor layouts and return conventions."""
+import os
+
+import pytest
+import torch
+import torch.nn as nn
+
+
+def test_reference_kwargs_decorator():
+    import inspect
+
+    from trainscale_b200.utils.refargs import ANY, reference_kwargs
+
+    @reference_kwargs({"async_op": (False, None), "hint": ANY}, input_="x")
+    def f(x, k=1):
+        return x * k
+
+    assert f(2) == 2 and f(input_=3, k=2) == 6 and f(x=1, async_op=False, hint="anything") == 1
+    assert list(inspect.signature(f).parameters) == ["x", "k", "input_", "async_op", "hint"]
+    with pytest.raises(NotImplementedError):
+        f(1, async_op=True)                        # a request this framework does not honour is refused, not dropped
+    with pytest.raises(TypeError):
+        f(x=1, input_=2)
+
+
+def test_result_helpers_and_small_renames():
+    from trainscale_b200.core.types import Err, Ok, is_ok, map_result, unwrap_or
+    from trainscale_b200.data.collate import pad_sequence_right
+    from trainscale_b200.data.packing import get_packing_stats, pack_sequences, unpack_sequences
+    from trainscale_b200.introspection import levenshtein_distance
+    from trainscale_b200.metrics import sync_metric, sync_metrics
+    assert is_ok(result=Ok(1)) and map_result(result=Ok(1), f=lambda v: v + 1) == Ok(2) and unwrap_or(result=Err(1), default=5) == 5
+    assert levenshtein_distance(s1="ab", s2="b") == 1
+    assert get_packing_stats([3, 4], max_seq_len=8)["num_packed"] == 1
+    assert sync_metric(1.0, operation="mean", process_group=None) == 1.0 and sync_metrics(metrics={"a": 1.0}, operation="sum") == {"a": 1.0}
+    assert pad_sequence_right(sequences=[torch.ones(2), torch.ones(3)], padding_value=0).shape == (2, 3)
+    packed = pack_sequences(input_ids=[[1, 2, 3], [4, 5]], attention_mask=[[1, 1, 1], [1, 1]], labels=[[1, 2, 3], [4, 5]],
+                            max_seq_len=8, pad_token_id=0, label_pad_id=-100)
+    assert packed[0]["input_ids"].tolist() == [1, 2, 3, 4, 5, 0, 0, 0]
+    parts = unpack_sequences(packed_output=torch.arange(5), cu_seqlens=torch.tensor([0, 3, 5]), original_lengths=[2, 2])
+    assert [p.tolist() for p in parts] == [[0, 1], [3, 4]]
+
+
+def test_attention_functions_in_the_reference_layout():
+    from trainscale_b200 import kernels as K
+    torch.manual_seed(0)
+    q, k, v = torch.randn(2, 5, 4, 8), torch.randn(2, 5, 2, 8), torch.randn(2, 5, 2, 8)
+    t = lambda x: x.transpose(1, 2)        # noqa: E731  [B, S, H, D] <-> [B, H, S, D]
+    ours = K.flash_attention(q, k, v)
+    theirs = K.flash_attention(query=t(q), key=t(k), value=t(v), causal=True)
+    assert torch.allclose(ours, t(theirs), atol=1e-6)
+    full = K.flash_attention(query=t(q), key=t(k), value=t(v))               # the reference's default is NOT causal
+    assert not torch.allclose(full, theirs, atol=1e-3)
+    assert K.flash_attention(query=t(q), key=t(k), value=t(v), return_softmax=True).output.shape == (2, 4, 5, 8)
+    with pytest.raises(NotImplementedError):
+        K.flash_attention(query=t(q), key=t(k), value=t(v), dropout_p=0.1)
+    assert torch.allclose(K.naive_attention(q, k, v), t(K.naive_attention(query=t(q), key=t(k), value=t(v), causal=True)), atol=1e-6)
+    cfg = K.FlexAttentionConfig(attn_logit_softcapping=30.0, query_pre_attn_scalar=8)
+    a = K.slow_attention_softcapping(q, k, v, 30.0)
+    b = K.slow_attention_softcapping(Q=t(q), K=t(k), V=t(v), causal_mask=object(), config=cfg)
+    assert torch.allclose(a.reshape(2, 5, -1), b, atol=1e-6)
+    c = K.attention_softcapping_compiled(Q=t(q), K=t(k), V=t(v), causal_mask=1, query_scalar=8, softcap=30.0,
+                                         num_heads=4, num_kv_heads=2, head_dim=8)
+    assert torch.allclose(b, c, atol=1e-5)
+    Qd, Kd, Vd = torch.randn(2, 4, 1, 8), torch.randn(2, 2, 6, 8), torch.randn(2, 2, 6, 8)
+    o = K.inference_attention_single_token(Q=Qd, K=Kd, V=Vd, config=None)
+    ref = torch.nn.functional.scaled_dot_product_attention(Qd, Kd.repeat_interleave(2, 1), Vd.repeat_interleave(2, 1))
+    assert torch.allclose(o, ref.transpose(1, 2).reshape(2, 1, -1), atol=1e-5)
+    assert K.create_causal_mask(max_seq_len=3).shape == (3, 3)
+    assert K.create_sliding_window_causal_mask(max_seq_len=4, window_size=2)[3, 1] == float("-inf")
+
+
+def test_rope_lora_and_fp8_function_forms():
+    from trainscale_b200 import kernels as K
+    torch.manual_seed(0)
+    cos, sin = K.precompute_freqs_cis(8, max_seq_len=16, dtype=torch.float32)
+    Q, Kt = torch.randn(1, 5, 2, 8), torch.randn(1, 5, 1, 8)
+    q2, k2 = K.apply_rope(Q, Kt, cos, sin)
+    Qc, Kc = Q.clone(), Kt.clone()
+    assert K.inplace_rope_embedding(Qc, Kc, cos, sin, 0)[0] is Qc and torch.allclose(Qc, q2) and torch.allclose(Kc, k2)
+    assert torch.allclose(K.fast_rope_embedding(Q, cos, sin), q2)
+    pair = K.fast_rope_embedding(Q, Kt, cos, sin)
+    assert torch.allclose(pair[0], q2) and torch.allclose(pair[1], k2)
+
+    x, W, A, B = torch.randn(4, 16), torch.randn(8, 16), torch.randn(2, 16), torch.randn(8, 2)
+    want = x @ W.t() + 2.0 * (x @ A.t()) @ B.t()
+    for got in (K.matmul_lora(x, W, A, B, 2.0), K.matmul_lora(x, W, None, A, B, 2.0), K.matmul_lora(x, W, A=A, B=B, scaling=2.0)):
+        assert torch.allclose(got, want, atol=1e-4)
+    with pytest.raises(NotImplementedError):
+        K.matmul_lora(x, W, object(), A, B, 2.0)
+    assert K.validate_lora_gradients(x, W, A, B, 2.0) is True and K.validate_lora_gradients()["passed"]
+
+    class P(nn.Module):
+        def __init__(self, o, i):
+            super().__init__()
+            self.weight, self.scaling = nn.Parameter(torch.randn(o, i)), 0.5
+            self.lora_A, self.lora_B = nn.Parameter(torch.randn(2, i)), nn.Parameter(torch.randn(o, 2))
+        def dense(self, h):
+            return h @ self.weight.t() + 0.5 * (h @ self.lora_A.t()) @ self.lora_B.t()
+
+    class MLP(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.gate_proj, self.up_proj, self.down_proj = P(32, 16), P(32, 16), P(16, 32)
+
+    m = MLP()
+    want = m.down_proj.dense(torch.nn.functional.silu(m.gate_proj.dense(x)) * m.up_proj.dense(x))
+    assert torch.allclose(K.apply_lora_mlp_swiglu(m, x), want, atol=1e-4)
+    assert torch.allclose(K.apply_lora_mlp_swiglu(mlp_module=m, X=x, inplace=True), want, atol=1e-4)
+    qp, kp, vp = P(8, 16), P(4, 16), P(4, 16)
+    got = K.apply_lora_qkv(qp, kp, vp, x)
+    assert all(torch.allclose(g, p.dense(x), atol=1e-4) for g, p in zip(got, (qp, kp, vp)))
+
+    wq, ws = K.block_quantize_fp8(x=torch.randn(256, 256), block_size=128)
+    assert wq.dtype == torch.float8_e4m3fn and ws.shape == (2, 2)
+    wd = K.block_dequantize_fp8(y=wq, scales=ws, block_size=128, out_dtype=torch.float32)
+    xq, xs = K.block_quantize_fp8(torch.randn(128, 256))
+    out = K.fp8_matmul_block_scaled(A=xq, A_scale=xs, B=wq.t().contiguous(), B_scale=ws.t().contiguous(), out_dtype=torch.float32)
+    assert torch.allclose(out, K.block_dequantize_fp8(xq, xs, 128, torch.float32) @ wd.t(), atol=1e-3)
+    Aq, As = K.row_quantize_fp8(x=torch.randn(8, 32))
+    Bq, Bs = K.row_quantize_fp8(torch.randn(16, 32))
+    out = K.fp8_matmul_row_scaled(Aq, As, Bq.t(), Bs, out_dtype=torch.float32)
+    assert torch.allclose(out, (Aq.float() * As) @ (Bq.float() * Bs).t(), atol=1e-4)
+    assert K.row_quantize_fp8(torch.randn(2, 8), fp8_format="e5m2")[0].dtype == torch.float8_e5m2
+
+    z, y = torch.randn(4, 7), torch.tensor([1, 2, 3, -100])
+    capped = 30.0 * torch.tanh(z / 30.0)
+    want = torch.nn.functional.cross_entropy(capped, y, ignore_index=-100, reduction="sum") / 3
+    assert torch.allclose(K.fast_cross_entropy_loss(z, y, logit_softcapping=30.0, n_items=3), want, atol=1e-5)
+    assert K.fused_add_rms_layernorm(X=torch.randn(2, 8), residual=torch.randn(2, 8), weight=torch.ones(8)).shape == (2, 8)
+    assert len(K.fused_add_rms_layernorm(torch.randn(2, 8), torch.randn(2, 8), torch.ones(8), return_residual=True)) == 2
+    assert torch.allclose(K.fused_gelu(torch.ones(2), approx=True), torch.nn.functional.gelu(torch.ones(2), approximate="tanh"))
+
+
+def test_rl_functions_reference_forms():
+    from trainscale_b200.rl import (chunked_log_softmax, compute_advantages, dapo_loss, drgrpo_loss, grpo_loss,
+                                    left_pack_padding, selective_log_softmax)
+    torch.manual_seed(0)
+    B, G, L = 2, 3, 4
+    p, r = torch.randn(B, G, L, requires_grad=True), torch.randn(B, G, L)
+    m, rew = torch.ones(B, G, L), torch.randn(B, G)
+    adv = compute_advantages(rew, baseline="mean")
+    assert adv.shape == (B, G) and torch.allclose(adv.mean(-1), torch.zeros(B), atol=1e-6)
+    assert torch.allclose(compute_advantages(rew, "none"), rew / rew.std())
+    lp = (p * m).sum(-1) / m.sum(-1)
+    loss, met = grpo_loss(policy_log_probs=p, ref_log_probs=r, advantages=adv, mask=m, beta=0.04)
+    want = -(adv * lp).mean() + 0.04 * ((p - r) * m).sum(-1).mean() / m.sum(-1).mean()
+    assert torch.allclose(loss, want, atol=1e-6) and set(met) == {"pg_loss", "kl_loss", "kl_div", "total_loss"}
+    loss, met = drgrpo_loss(policy_log_probs=p, ref_log_probs=r, advantages=adv, mask=m, epsilon=0.1)
+    assert "ratio_mean" in met and loss.requires_grad
+    loss, met = dapo_loss(policy_log_probs=p, ref_log_probs=r, rewards=rew, mask=m, temperature=2.0)
+    soft = torch.softmax(rew / 2.0, -1)
+    assert torch.allclose(loss, -(soft * lp).sum(-1).mean() + 0.04 * (((p - r) * m).sum(-1) / m.sum(-1)).mean(), atol=1e-6)
+    # this framework's positional forms are unchanged
+    flat = torch.randn(6, L)
+    assert grpo_loss(flat, flat.detach(), None, compute_advantages(torch.randn(6), 3), torch.ones(6, L)).dim() == 0
+
+    ids = torch.tensor([[5, 6, 0, 0], [7, 0, 0, 0]])
+    assert left_pack_padding(ids, 0).tolist() == [[0, 0, 5, 6], [0, 0, 0, 7]]            # the reference's direction
+    assert left_pack_padding(input_ids=ids, pad_token_id=0).tolist() == [[0, 0, 5, 6], [0, 0, 0, 7]]
+    packed, mask = left_pack_padding(torch.tensor([[0, 5, 0, 6]]), torch.tensor([[0, 1, 0, 1]]))
+    assert packed.tolist() == [[5, 6, 0, 0]] and mask.tolist() == [[1, 1, 0, 0]]
+
+    lg, idx = torch.randn(2, 3, 7), torch.randint(0, 7, (2, 3))
+    want = torch.log_softmax(5.0 * torch.tanh(lg / 5.0) / 2.0, -1).gather(-1, idx[..., None]).squeeze(-1)
+    assert torch.allclose(selective_log_softmax(lg, input_ids=idx, temperature=2.0, logit_softcapping=5.0), want, atol=1e-5)
+    h, W = torch.randn(2, 3, 8), torch.randn(7, 8)
+    got = chunked_log_softmax(hidden_states=h, lm_head=W, input_ids=idx, num_chunks=2, temperature=2.0)
+    assert torch.allclose(got, selective_log_softmax(h @ W.t(), idx, 2.0), atol=1e-4)
+    got = chunked_log_softmax(h, W, idx, num_chunks=2, logit_softcapping=5.0)
+    assert torch.allclose(got, selective_log_softmax(h @ W.t(), idx, 1.0, 5.0), atol=1e-4)
+
+
+def test_config_export_quantization_forms(tmp_path):
+    from trainscale_b200.config.sota_config import get_dpo_preset, get_qlora_preset
+    from trainscale_b200.config.training_args import load_training_config, merge_configs
+    from trainscale_b200.export import create_vllm_config, push_to_hub, save_safetensors
+    from trainscale_b200.hub import generate_model_card
+    from trainscale_b200.quantization import (QuantizationConfig, estimate_memory_usage, fast_dequantize,
+                                              quantize_nf4_param)
+    assert get_qlora_preset(model_name="x", max_seq_length=512).data.max_seq_length == 512
+    assert get_dpo_preset("y").model.name_or_path == "y" and merge_configs({"a": 1}, overrides={"a": 2}) == {"a": 2}
+    f = tmp_path / "t.yaml"
+    f.write_text("section:\n  learning_rate: 0.5\n  output_dir: ${TS_TEST_UNSET:-out}\n")
+    cfg = load_training_config(yaml_path=f, config_key="section")
+    assert cfg.learning_rate == 0.5 and cfg.output_dir == "out"
+    assert load_training_config(f, config_key="section", interpolate_env=False).output_dir.startswith("${")
+    m = nn.Sequential(nn.Linear(4, 4), nn.Linear(4, 4))
+    out = save_safetensors(m, output_dir=tmp_path / "w", max_shard_size="1MB")
+    assert (out / "model.safetensors").exists()
+    assert create_vllm_config(str(out), str(tmp_path / "serve")).parent == tmp_path / "serve"
+    assert push_to_hub(m, None, "someone/model") is None                       # offline: nothing is uploaded
+    card = generate_model_card(m, "my-model", description="d", license="mit", language="en")
+    assert "# my-model" in card and "license: mit" in card and "Parameters" in card
+    est = estimate_memory_usage(7.0, QuantizationConfig(load_in_4bit=True))
+    assert est["model_gb"] == pytest.approx(7e9 * 0.5 / 2 ** 30, abs=0.01) and est["gradient_gb"] == est["lora_gb"]
+    assert "weights_gb" in estimate_memory_usage(7e9)
+    assert fast_dequantize(torch.ones(2), None, torch.float32).dtype == torch.float32
+    w = torch.randn(8, 64)
+    assert (fast_dequantize(quantize_nf4_param(w), out_dtype=torch.float32) - w).abs().max() < 0.5
+
+
+def test_distributed_and_pipeline_function_forms(tmp_path):
+    from trainscale_b200.parallel import tp as TP
+    from trainscale_b200.parallel.activation import create_activation_checkpoint_from_config, print_offload_summary
+    from trainscale_b200.parallel.cp import estimate_memory_per_gpu, hybrid_context_parallel_forward_backward
+    from trainscale_b200.parallel.dist_utils import (dist_all_gather, dist_reduce, finalize_model_grads,
+                                                     fused_clip_grad_norm_, load_checkpoint_distributed,
+                                                     save_checkpoint_distributed, set_deterministic_seed)
+    from trainscale_b200.parallel.pipeline import (PipelineConfig, ProfilingConfig, ScheduleType, balance_stages_by_memory,
+                                                   create_schedule, estimate_stage_memory, merge_microbatches,
+                                                   pipeline_profiler, selective_checkpoint, split_into_microbatches,
+                                                   split_model_into_stages)
+    m = nn.Linear(2, 2)
+    m(torch.ones(1, 2)).sum().backward()
+    finalize_model_grads([m], torch.tensor(4.0), sequence_parallel=False, qk_layernorm=False,
+                         share_embeddings_and_output_weights=True)
+    assert torch.allclose(m.weight.grad, torch.full((2, 2), 0.25))
+    before = fused_clip_grad_norm_(model_or_params=m, max_norm=0.1, norm_type=2.0, process_group=None, foreach=True)
+    assert float(before) == pytest.approx(6 ** 0.5 * 0.25, rel=1e-5)
+    assert dist_reduce(tensor=torch.ones(1), op="sum", process_group=None, async_op=False).item() == 1.0
+    assert len(dist_all_gather(tensor=torch.ones(1), contiguous=True)) == 1
+    assert set_deterministic_seed(3, 5) == 8 and set_deterministic_seed(3, 5, per_rank_offset=False) == 3
+    save_checkpoint_distributed({"a": torch.ones(2)}, tmp_path / "c.pt", None)
+    assert load_checkpoint_distributed(tmp_path / "c.pt", None, "cpu")["a"].tolist() == [1.0, 1.0]
+
+    x = torch.randn(2, 3)                                    # no registered group: the region functions are identities
+    assert TP.copy_to_tensor_parallel_region(input_=x, async_op=False) is x
+    assert TP.gather_from_tensor_parallel_region(x, dim=-1) is x
+    with pytest.raises(NotImplementedError):
+        TP.gather_from_tensor_parallel_region(x, dim=0)      # this function always gathers the last dimension
+    lg, y = torch.randn(2, 3, 7), torch.randint(0, 7, (2, 3))
+    got = TP.vocab_parallel_cross_entropy(logits=lg, targets=y, label_smoothing=0.1)
+    want = torch.nn.functional.cross_entropy(lg.view(-1, 7), y.view(-1), label_smoothing=0.1, reduction="none").view(2, 3)
+    assert torch.allclose(got, want, atol=1e-5)
+    assert TP.shard_model_for_tensor_parallel(m, config=TP.TensorParallelConfig()) is m
+
+    seq = nn.Sequential(*[nn.Linear(4, 4) for _ in range(6)])
+    assert [len(s.module) for s in split_model_into_stages(seq, 3, balance=[1, 2, 3])] == [1, 2, 3]
+    assert [len(s.module) for s in split_model_into_stages(seq, 2, split_points=["4"])] == [4, 2]
+    with pytest.raises(ValueError):
+        split_model_into_stages(seq, 3, balance=[1, 1, 1])
+    mib = estimate_stage_memory([seq, seq], (2, 8), torch.float32)
+    assert len(mib) == 2 and mib[0] == mib[1] > 0
+    assert balance_stages_by_memory(model=seq, num_stages=2, input_shape=(2, 8), target_memory_mb=10) == [range(0, 3), range(3, 6)]
+    stages = split_model_into_stages(seq, 3)
+    sched = create_schedule(ScheduleType.GPIPE, stages, PipelineConfig(num_stages=3), nn.functional.mse_loss)
+    assert type(sched).__name__ == "GPipeSchedule"
+    assert type(create_schedule(stages, PipelineConfig(num_stages=3), nn.functional.mse_loss)).__name__ == "OneFOneBSchedule"
+    assert len(split_into_microbatches(tensor=torch.ones(4, 2), num_microbatches=2)) == 2
+    assert merge_microbatches(microbatches=[torch.ones(1, 2)] * 2).shape == (2, 2)
+    xin = torch.ones(2, 4, requires_grad=True)
+    selective_checkpoint(lambda a: a * 2, xin, preserve_rng_state=True).sum().backward()
+    assert xin.grad[0, 0] == 2
+    with pipeline_profiler(ProfilingConfig(enabled=False), str(tmp_path)) as prof:
+        assert prof is None
+
+    assert create_activation_checkpoint_from_config(config={"mode": "full"}).cfg.mode.value == "full"
+    print_offload_summary({"attn": 2 ** 21, "mlp": 2 ** 20})
+    one_layer = estimate_memory_per_gpu(batch_size=2, seq_len=8192, hidden_dim=4096, num_heads=32, cp_degree=4)
+    assert isinstance(one_layer, int) and one_layer > 0
+    assert estimate_memory_per_gpu(8192, 4, 4096, 32, 8, 128)["tokens_per_gpu"] == 2048
+
+    lin = nn.Linear(2, 1)
+
+    def forward_step(it, model):
+        xb = next(it)
+        out = model(xb)
+        return out, lambda o: (o.pow(2).mean(), torch.tensor(xb.shape[0]), {"loss": float(o.pow(2).mean().detach())})
+
+    store, tokens = hybrid_context_parallel_forward_backward(forward_step_func=forward_step, model=lin,
+                                                             data_iterator=iter([torch.ones(3, 2)] * 4), num_microbatches=4)
+    assert len(store) == 4 and int(tokens) == 12 and lin.weight.grad is not None
+
+
+def test_data_and_serving_function_forms():
+    from trainscale_b200.data.dataloader_factory import build_dataloader
+    from trainscale_b200.data.length_manager import create_content_distributor, find_word_boundary
+    from trainscale_b200.data.prompt_engine import render_template
+    from trainscale_b200.inference.engine import EnginePresets, create_openai_server
+    from trainscale_b200.registry import auto_patch_layernorm, get_model_info
+    ds = [{"input_ids": torch.arange(n + 1), "labels": torch.arange(n + 1)} for n in range(4)]
+    b = next(iter(build_dataloader(ds, batch_size=4, pad_token_id=9, label_pad_token_id=-1, padding_side="right")))
+    assert b["input_ids"][0].tolist() == [0, 9, 9, 9] and b["labels"][0].tolist() == [0, -1, -1, -1]
+    d = create_content_distributor(max_length=64, distribution_mode="proportional", column_ratios={"a": 0.5, "b": 0.5},
+                                   default_truncation="right", chars_per_token=4.0)
+    assert d.available_tokens == 54 and d.estimator.cpt == 4.0
+    assert find_word_boundary("hello world foo", max_chars=8) == 6
+    assert render_template("hi {x}", {"x": 1}, use_jinja=False) == "hi 1"
+    assert get_model_info(model_id="meta-llama/x").family == "llama" and auto_patch_layernorm(module=nn.LayerNorm(4)) == 1
+    cfg = EnginePresets.low_latency_interactive("tiny")
+    cfg.device = "cpu"
+    cfg.cache.num_gpu_blocks = 32
+    app = create_openai_server(cfg, "127.0.0.1", port=8123)
+    assert (app.state.host, app.state.port) == ("127.0.0.1", 8123)

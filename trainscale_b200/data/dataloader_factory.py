@@ -149,9 +149,21 @@ class DataLoaderBuilder:
 
 def build_dataloader(dataset, batch_size: int = 8, shuffle: bool = False, seed: int = 42, num_workers: int = 0,
                      pin_memory: bool = False, drop_last: bool = False, collate_fn=None, distributed: bool = False,
-                     rank: int = 0, world_size: int = 1, prefetch_factor=None, persistent_workers=False) -> DataLoader:
+                     rank: int = 0, world_size: int = 1, prefetch_factor=None, persistent_workers=False, *,
+                     pad_token_id: int | None = None, label_pad_token_id: int = -100, padding_side: str = "right",
+                     max_length: int | None = None, output_schema=None, config=None) -> DataLoader:
+    """One call for a loader.  `pad_token_id` (with `label_pad_token_id`, `padding_side`, `max_length`) selects the
+    padding collate function unless `collate_fn` is given; `output_schema` filters / casts the batch's keys; `config`
+    (a loader configuration object) supplies batch size, workers, pinning and the like
+    (data_pipeline/data/dataloader_factory.py:225-300)."""
     b = (DataLoaderBuilder(dataset).batch_size(batch_size).shuffle(shuffle, seed)
          .workers(num_workers, prefetch_factor, persistent_workers).pin_memory(pin_memory).drop_last(drop_last))
+    if config is not None:
+        b.with_config(config)
+    if pad_token_id is not None:
+        b.with_padding(pad_token_id, label_pad_token_id, padding_side, max_length)
+    if output_schema is not None:
+        b.with_output_schema(output_schema)
     if collate_fn is not None:
         b.collate(collate_fn)
     if distributed:

@@ -955,7 +955,17 @@ class EnginePresets:
 
 
 # ------------------------------------------------------------------------------------------------ HTTP server
-def create_openai_server(engine: SOTAAsyncStreamEngine, model_name: str = "trainscale"):
+def create_openai_server(engine: "SOTAAsyncStreamEngine | EngineConfig", model_name: str = "trainscale", *, config=None,
+                         host: str | None = None, port: int | None = None):
+    """FastAPI application with the OpenAI-style routes.  `engine` may be an `EngineConfig` (`config=` in the
+    reference's spelling): the streaming engine is then built from it and the model's name is the served name.  `host`
+    and `port` are kept on `app.state` for whoever starts the server (`uvicorn.run(app, host=..., port=...)`)."""
+    if config is not None or isinstance(engine, EngineConfig):
+        cfg = config if config is not None else engine
+        if isinstance(model_name, str) and host is None and model_name not in ("trainscale",) and "." in model_name:
+            host, model_name = model_name, "trainscale"     # positional (config, host, port)
+        engine = SOTAAsyncStreamEngine(cfg)
+        model_name = cfg.model if model_name == "trainscale" else model_name
     from fastapi import FastAPI
     from fastapi.responses import PlainTextResponse, StreamingResponse
     from pydantic import BaseModel
@@ -1045,6 +1055,7 @@ def create_openai_server(engine: SOTAAsyncStreamEngine, model_name: str = "train
                 "choices": [{"index": 0, "message": {"role": "assistant", "content": text}, "finish_reason": reason}],
                 "usage": {"completion_tokens": n}}
 
+    app.state.host, app.state.port = host or "0.0.0.0", int(port or 8000)
     return app
 
 

@@ -14,6 +14,8 @@ from typing import NamedTuple
 import torch
 import torch.nn as nn
 
+from ..utils.refargs import ANY, reference_kwargs
+
 
 class CheckpointMode(str, Enum):
     NONE = "none"
@@ -290,6 +292,7 @@ class ActivationCheckpoint:
         return chosen
 
 
+@reference_kwargs(config="d")
 def create_activation_checkpoint_from_config(d: dict | None) -> ActivationCheckpoint:
     d = dict(d or {})
     mode = d.get("ac_mode", d.get("mode", "selective"))
@@ -717,8 +720,25 @@ class PipelineOffloadManager:
             hooks.__exit__(*exc)
 
 
-def print_offload_summary(manager: "PipelineOffloadManager | ActivationOffloader") -> None:
-    print(manager.summary())
+def print_offload_summary(manager=None, *, total_offload_bytes: dict | None = None) -> None:
+    """Print what was offloaded.  `manager`: an offloader / pipeline manager (its `summary()`), or the reference's
+    {group name: bytes} mapping (also as `total_offload_bytes=`), printed as a table; in a distributed job the bytes are
+    summed over the ranks first and rank 0 prints."""
+    table = total_offload_bytes if total_offload_bytes is not None else (manager if isinstance(manager, dict) else None)
+    if table is None:
+        print(manager.summary())
+        return
+    import torch.distributed as dist
+    names, vals = sorted(table), torch.tensor([float(table[k]) for k in sorted(table)], dtype=torch.float64)
+    on = dist.is_available() and dist.is_initialized()
+    if on and dist.get_world_size() > 1:
+        dist.all_reduce(vals)
+    if not on or dist.get_rank() == 0:
+        width = max([len(n) for n in names] + [5])
+        print(f"{'group':<{width}}  {'MiB':>12}")
+        for n, v in zip(names, vals.tolist()):
+            print(f"{n:<{width}}  {v / 2 ** 20:>12.2f}")
+        print(f"{'total':<{width}}  {float(vals.sum()) / 2 ** 20:>12.2f}")
 
 
 # ------------------------------------------------------------------------------------------------ more of the policy surface

@@ -480,8 +480,17 @@ def gather_output(x_local: torch.Tensor, group, balancer: str = "head_tail", dim
     return create_balancer(balancer, cp, r).unshard(parts, dim)
 
 
-def estimate_memory_per_gpu(seq_len: int, cp: int, hidden: int, n_layers: int, n_kv_heads: int, head_dim: int,
-                            bytes_per_el: int = 2, checkpointing: bool = True) -> dict:
+def estimate_memory_per_gpu(seq_len: int = None, cp: int = None, hidden: int = None, n_layers: int = 1,
+                            n_kv_heads: int = None, head_dim: int = None, bytes_per_el: int = 2,
+                            checkpointing: bool = True, *, batch_size: int | None = None, hidden_dim: int | None = None,
+                            num_heads: int | None = None, cp_degree: int | None = None, precision: str | None = None):
+    """Per-GPU activation and ring-buffer sizes of a context-parallel layer stack (a dict, in GiB).  The reference's
+    keyword form (`batch_size, seq_len, hidden_dim, num_heads, cp_degree, precision`) describes ONE layer without
+    recomputation and returns its bytes as an int (data_pipeline/trainer/distributed/context_parallel.py:2107)."""
+    if cp_degree is not None or hidden_dim is not None:
+        eb = {"fp32": 4, "fp16": 2, "bf16": 2, "fp8": 1}[precision or "bf16"]
+        d = estimate_memory_per_gpu(seq_len, cp_degree or 1, hidden_dim, 1, num_heads, hidden_dim // num_heads, eb, False)
+        return int((d["activations_gb"] + d["ring_buffers_gb"]) * 2 ** 30) * int(batch_size or 1)
     s = seq_len // cp
     act = s * hidden * bytes_per_el * (2 if checkpointing else 34) * n_layers
     kv_ring = 2 * 2 * s * n_kv_heads * head_dim * bytes_per_el   # double-buffered K and V
@@ -615,11 +624,44 @@ class BalancedCPScheduler:
         return self._fill_empty_gpus(self._trim_overloaded(self.schedule(lengths), lengths), lengths)
 
 
-def hybrid_context_parallel_forward_backward(model_step, batches: list[dict], scheduler: BalancedCPScheduler,
-                                             rank: int, lengths: list[int] | None = None) -> list:
+def hybrid_context_parallel_forward_backward(model_step=None, batches: list[dict] | None = None,
+                                             scheduler: "BalancedCPScheduler | None" = None, rank: int = 0,
+                                             lengths: list[int] | None = None, *, forward_step_func=None,
+                                             data_iterator=None, model=None, num_microbatches: int = 1,
+                                             forward_data_store: list | None = None, config=None,
+                                             collect_non_loss_data: bool = False, first_val_step=None,
+                                             forward_only: bool = False, no_sync_func=None, total_num_tokens=0,
+                                             model_type=None, get_data_parallel_rank=None,
+                                             get_tensor_model_parallel_rank=None, get_tensor_model_parallel_src_rank=None,
+                                             get_tensor_model_parallel_group=None, get_data_parallel_group=None):
     """Runs `model_step(batch, cp_degree, cp_slot)` for every sequence this rank takes part in, in schedule order.
     `batches[i]` is sequence i (dict with input_ids [1, L]); `cp_slot` is this rank's position inside the sequence's
-    group of `cp_degree` consecutive ranks.  Returns the per-sequence results of this rank."""
+    group of `cp_degree` consecutive ranks.  Returns the per-sequence results of this rank.
+
+    With `forward_step_func=` (the reference's keywords, data_pipeline/trainer/distributed/hybrid_cp_scheduler.py:627,
+    where the body is left unimplemented) the Megatron-style loop runs instead: for each of `num_microbatches`,
+    `forward_step_func(data_iterator, model)` returns (output, loss_func); `loss_func(output)` returns (loss, stats) or
+    (loss, num_tokens, stats); the loss is back-propagated unless `forward_only`, gradient synchronisation is held
+    back by `no_sync_func()` on all but the last micro-batch; returns (forward_data_store, total_num_tokens)."""
+    if forward_step_func is not None:
+        import contextlib
+        store = forward_data_store if forward_data_store is not None else []
+        for i in range(int(num_microbatches)):
+            last = i == num_microbatches - 1
+            hold = no_sync_func() if (no_sync_func is not None and not last and not forward_only) else contextlib.nullcontext()
+            with hold:
+                output, loss_func = forward_step_func(data_iterator, model)
+                if collect_non_loss_data:
+                    store.append(loss_func(output, non_loss_data=True))
+                    continue
+                res = loss_func(output)
+                loss, stats = res[0], res[-1]
+                if len(res) == 3:
+                    total_num_tokens = total_num_tokens + res[1]
+                if not forward_only:
+                    (loss / num_microbatches).backward()
+                store.append(stats)
+        return store, total_num_tokens
     lengths = lengths or [int(b["input_ids"].shape[1]) for b in batches]
     plan = scheduler.balanced_schedule(lengths)
     out = []

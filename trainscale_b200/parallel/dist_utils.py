@@ -547,6 +547,7 @@ def allreduce_layernorm_grads(model, group=None, *, tp_group=None, sequence_para
                     dist.all_reduce(_grad_of(p), group=group)
 
 
+@reference_kwargs(model="stage_module")
 def allreduce_word_embedding_grads(stage_module, group=None, first_rank: int | None = None, last_rank: int | None = None,
                                    *, embedding_group=None, pp_group=None,
                                    share_embeddings_and_output_weights: bool = True) -> None:

@@ -18,6 +18,8 @@ from typing import Sequence
 import torch
 import torch.distributed as dist
 
+from ..utils.refargs import ANY, reference_kwargs
+
 NVLINK5_GBPS_PER_DIRECTION = 900.0
 DIM_ORDER = ("pp", "dp_replicate", "dp_shard", "cp", "tp")
 
@@ -383,6 +385,7 @@ class MeshCache:
         return cls._named.get(key)
 
 
+@reference_kwargs(config="dist_cfg")
 def create_parallel_dims_from_config(dist_cfg, world_size: int | None = None, rank: int | None = None) -> ParallelDims:
     """From a SOTAConfig `distributed` section (its `parallel` sub-section and the legacy degree keys)."""
     p = dist_cfg.parallel

@@ -301,10 +301,31 @@ class _VocabParallelCE(torch.autograd.Function):
         return grad, None, None, None, None
 
 
-def vocab_parallel_cross_entropy(logits_local: torch.Tensor, labels: torch.Tensor, tp: TPContext, vocab_start: int,
-                                 ignore_index: int = -100) -> torch.Tensor:
-    """Per-token loss for logits split along the vocabulary; three small all-reduces (max, sum-exp, target logit)."""
-    return _VocabParallelCE.apply(logits_local, labels, tp, vocab_start, ignore_index)
+@reference_kwargs(logits="logits_local", targets="labels")
+def vocab_parallel_cross_entropy(logits_local: torch.Tensor, labels: torch.Tensor, tp: TPContext | None = None,
+                                 vocab_start: int | None = None, ignore_index: int = -100,
+                                 label_smoothing: float = 0.0) -> torch.Tensor:
+    """Per-token loss for logits split along the vocabulary; three small all-reduces (max, sum-exp, target logit).
+    Without `tp` the registered tensor-parallel group is used and `vocab_start` defaults to rank x local vocabulary
+    (the reference's call form `vocab_parallel_cross_entropy(logits, targets, label_smoothing)`).  Label smoothing
+    mixes in the mean negative log-probability over the WHOLE vocabulary (one more all-reduce)."""
+    tp = tp if tp is not None else _default_tp()
+    if vocab_start is None:
+        vocab_start = tp.rank * logits_local.shape[-1]
+    loss = _VocabParallelCE.apply(logits_local, labels, tp, vocab_start, ignore_index)
+    if label_smoothing:
+        z = logits_local.float()
+        m = _all_reduce(z.max(-1).values.detach().clone(), tp, dist.ReduceOp.MAX)
+        lse = torch.log(_reduce_sum_differentiable(torch.exp(z - m[..., None]).sum(-1), tp)) + m
+        mean_logit = _reduce_sum_differentiable(z.sum(-1), tp) / (z.shape[-1] * tp.size)
+        smooth = (lse - mean_logit) * (labels != ignore_index)
+        loss = (1.0 - label_smoothing) * loss + label_smoothing * smooth
+    return loss
+
+
+def _reduce_sum_differentiable(x, tp):
+    """Sum over the tensor-parallel group whose backward passes the gradient through unchanged."""
+    return _ReduceFromTP.apply(x, tp) if tp.active else x
 
 
 class VocabParallelCrossEntropyLoss(_ExplicitBackward, nn.Module):
@@ -385,10 +406,16 @@ class _TPBlockIO(nn.Module):
         return reduce_from_tensor_parallel_region(self.inner(copy_to_tensor_parallel_region(x, tp), *args, **kw), tp)
 
 
-def shard_model_for_tensor_parallel(model, tp: TPContext):
+def shard_model_for_tensor_parallel(model, tp: "TPContext | TensorParallelConfig | None" = None, *, config=None):
     """Slice the weights for this TP rank and wrap attention / MLP with the conjugate communication ops.
+    `tp` may also be a `TensorParallelConfig` (`config=` in the reference's spelling): the context is then built
+    from the registered tensor-parallel group with that config's sequence-parallel switch.
     With sequence parallelism the caller feeds / receives token-sharded hidden states between blocks and must
     all-reduce the norm-weight gradients over the TP group (`allreduce_sequence_parallel_grads`)."""
+    tp = tp if tp is not None else config
+    if not isinstance(tp, TPContext):
+        base = _default_tp()
+        tp = TPContext(base.group, base.size, base.rank, bool(getattr(tp, "sequence_parallel_enabled", False)))
     if not tp.active:
         return model
     if getattr(model, "tp_presharded", 0) == tp.size:

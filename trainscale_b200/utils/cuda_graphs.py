@@ -11,6 +11,8 @@ from typing import Callable
 
 import torch
 
+from .refargs import ANY, reference_kwargs
+
 
 @dataclass
 class CompilationConfig:
@@ -105,8 +107,14 @@ class CUDAGraphManager:
         return outs[0] if len(outs) == 1 else outs
 
 
+_TRACER_OPTIONS = {"fullgraph": ANY, "dynamic": ANY, "mode": ANY, "backend": ANY, "example_inputs": ANY}
+
+
+@reference_kwargs(_TRACER_OPTIONS)
 def compile_model(model, config: CompilationConfig | None = None):
-    """Returns a callable running `model` under graph replay for fixed input shapes (inference only)."""
+    """Returns a callable running `model` under graph replay for fixed input shapes (inference only).  The options of
+    the reference's tracing compiler (`fullgraph`, `dynamic`, `mode`, `backend`, `example_inputs`) are accepted and
+    have no counterpart here: kernels are hand-written, only launches are captured."""
     mgr = CUDAGraphManager(config)
 
     @torch.no_grad()
@@ -117,6 +125,8 @@ def compile_model(model, config: CompilationConfig | None = None):
     return run
 
 
+@reference_kwargs({"example_inputs": ANY, "use_cudagraphs": (True, None), "use_channels_last": (False, None),
+                   "freeze": (True, None)})
 def optimize_for_inference(model):
     model.eval()
     for p in model.parameters():
@@ -124,8 +134,10 @@ def optimize_for_inference(model):
     return compile_model(model)
 
 
-def optimize_for_training(model, checkpoint_every: int = 2):
-    if hasattr(model, "gradient_checkpointing_enable"):
+def optimize_for_training(model, checkpoint_every: int = 2, *, use_activation_checkpointing: bool = True):
+    """Recompute every `checkpoint_every`-th layer in backward (`use_activation_checkpointing=False`: leave the model
+    as it is)."""
+    if use_activation_checkpointing and hasattr(model, "gradient_checkpointing_enable"):
         model.gradient_checkpointing_enable(checkpoint_every)
     return model
 
