@@ -89,11 +89,52 @@ class DistributedMetricBuffer:
     clear = reset
 
 
+def _with_name(init):
+    """Constructor wrapper: every metric takes `name=` (the key under which a collection reports it)."""
+    import functools
+    import inspect
+
+    @functools.wraps(init)
+    def wrapper(self, *args, name: str | None = None, **kwargs):
+        init(self, *args, **kwargs)
+        if name is not None:
+            self.name = name
+    sig = inspect.signature(init)
+    params = list(sig.parameters.values())
+    tail = [p for p in params if p.kind is inspect.Parameter.VAR_KEYWORD]
+    head = [p for p in params if p.kind is not inspect.Parameter.VAR_KEYWORD]
+    if "name" not in sig.parameters:
+        head.append(inspect.Parameter("name", inspect.Parameter.KEYWORD_ONLY, default=None))
+    wrapper.__signature__ = sig.replace(parameters=head + tail)
+    return wrapper
+
+
+def _with_reference_update(update):
+    """`update(predictions=, targets=)`: the reference's names for the first two arguments of any metric's update."""
+    import inspect
+    names = [p for p in inspect.signature(update).parameters if p != "self"][:2]
+    renames = {ref: ours for ref, ours in zip(("predictions", "targets"), names) if ref != ours}
+    return reference_kwargs(**renames)(update) if renames else update
+
+
 class Metric:
     """update / compute / reset; calling a metric resets it, feeds one batch and returns the value
-    (data_pipeline/trainer/metrics/__init__.py:16-40).  `name` is the key under which a collection reports it."""
+    (data_pipeline/trainer/metrics/__init__.py:16-40).  `name` is the key under which a collection reports it; every
+    subclass's constructor takes it as a keyword, and every `update` also answers to `predictions=` / `targets=`."""
     name: str = ""
 
+    def __init__(self, name: str | None = None):
+        if name is not None:
+            self.name = name
+
+    def __init_subclass__(cls, **kw):
+        super().__init_subclass__(**kw)
+        if "__init__" in cls.__dict__:
+            cls.__init__ = _with_name(cls.__dict__["__init__"])
+        if "update" in cls.__dict__:
+            cls.update = _with_reference_update(cls.__dict__["update"])
+
+    @reference_kwargs(predictions="preds")
     def update(self, preds, targets): raise NotImplementedError
     def compute(self) -> float: raise NotImplementedError
     def reset(self): raise NotImplementedError
@@ -109,8 +150,8 @@ class Metric:
 
 
 class _Counts(Metric):
-    def __init__(self, num_classes: int | None = None, average: str = "macro", ignore_index: int = -100):
-        self.num_classes, self.average, self.ignore_index = num_classes, average, ignore_index
+    def __init__(self, num_classes: int | None = None, average: str = "macro", ignore_index: int = -100, top_k: int = 1):
+        self.num_classes, self.average, self.ignore_index, self.top_k = num_classes, average, ignore_index, int(top_k)
         self.reset()
 
     def reset(self):
@@ -119,12 +160,16 @@ class _Counts(Metric):
     def update(self, preds, targets):
         p = torch.as_tensor(preds)
         t = torch.as_tensor(targets)
+        hits = None
         if p.dim() > t.dim():
+            if self.top_k > 1:                      # a hit when the target is among the k highest scores
+                topk = p.topk(min(self.top_k, p.shape[-1]), dim=-1).indices.reshape(-1, min(self.top_k, p.shape[-1]))
+                hits = (topk == t.reshape(-1, 1)).any(-1)
             p = p.argmax(-1)
         p, t = p.reshape(-1), t.reshape(-1)
         keep = t != self.ignore_index
         p, t = p[keep], t[keep]
-        self.correct += int((p == t).sum())
+        self.correct += int(hits[keep].sum()) if hits is not None else int((p == t).sum())
         self.total += int(t.numel())
         for c in torch.unique(torch.cat((p, t))).tolist():
             self.tp[c] += int(((p == c) & (t == c)).sum())
@@ -350,6 +395,7 @@ class MetricCollection:
     def add(self, metric: Metric) -> None:
         self.metrics[metric.name or type(metric).__name__.lower()] = metric
 
+    @reference_kwargs(predictions="preds")
     def update(self, preds, targets) -> None:
         for m in self.metrics.values():
             m.update(preds, targets)

@@ -13,6 +13,8 @@ from collections import deque
 from typing import Iterable
 
 import torch
+
+from ..utils.refargs import ANY, reference_kwargs
 import torch.distributed as dist
 
 from .throughput import ThroughputTracker
@@ -106,6 +108,7 @@ class LossTracker:
         return {"ema": self.ema, "sum": self.sum, "tokens": self.tokens, "samples": self.samples, "steps": self.steps,
                 "last": self._last, "history": list(self._history[-100:])}
 
+    @reference_kwargs(state="sd")
     def load_state_dict(self, sd: dict) -> None:
         self.ema, self.sum, self.tokens = sd.get("ema"), sd.get("sum", 0.0), sd.get("tokens", 0)
         self.samples, self.steps, self._last = sd.get("samples", 0), sd.get("steps", 0), sd.get("last", 0.0)
@@ -245,6 +248,7 @@ class GradientTracker:
         return {"norms": list(self.norms), "nan_count": self.nan_count, "clipped": self.clipped, "ema": self._ema,
                 "steps": self._steps, "history": list(self._history[-100:])}
 
+    @reference_kwargs(state="sd")
     def load_state_dict(self, sd: dict) -> None:
         self.norms.extend(sd.get("norms", []))
         self.nan_count, self.clipped = sd.get("nan_count", 0), sd.get("clipped", 0)
@@ -346,6 +350,7 @@ class TrainingMetrics:
                 "throughput": self.throughput.state_dict(), "lr": self._lr, "global_step": self._global_step,
                 "epoch": self._epoch, "epoch_step": self._epoch_step}
 
+    @reference_kwargs(state="sd")
     def load_state_dict(self, sd: dict) -> None:
         self.loss.load_state_dict(sd.get("loss", {}))
         self.gradient.load_state_dict(sd.get("grad", {}))
