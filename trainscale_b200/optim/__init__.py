@@ -17,6 +17,10 @@ import torch
 from torch.optim import Optimizer
 
 from ..ops import optim as K
+from ..utils.refargs import ANY, reference_kwargs
+
+_IMPL_OPTIONS = {"use_triton": ANY, "fused_foreach": ANY, "enable_metrics": ANY}     # implementation switches of
+# the reference's optimizers (Triton / foreach paths, metric collection): accepted, no effect on the kernels used here
 
 
 @torch.no_grad()
@@ -40,12 +44,30 @@ def clip_grad_norm_(parameters: Iterable[torch.Tensor], max_norm: float, norm_ty
 class AdamW(Optimizer):
     """Decoupled AdamW. CUDA fp32 tensors with bf16/fp32 grads use the fused flat kernel (one launch per tensor)."""
 
-    def __init__(self, params, lr=2e-5, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01, amsgrad=False, fused=True):
+    @reference_kwargs(_IMPL_OPTIONS)
+    def __init__(self, params, lr=2e-5, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01, amsgrad=False, fused=True,
+                 max_grad_norm: float | None = None, grad_accumulation_steps: int = 1):
+        """`max_grad_norm`: clip the global gradient norm before every update.  `grad_accumulation_steps` = n: the
+        update happens on every n-th `step()` call, on the MEAN of the gradients seen since the last update (the caller
+        must not zero the gradients in between); data_pipeline/trainer/optimizers/adamw.py:1010-1030."""
         super().__init__(params, dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay, amsgrad=amsgrad, fused=fused))
+        self.max_grad_norm, self.grad_accumulation_steps = max_grad_norm, max(1, int(grad_accumulation_steps))
+        self._micro = 0
 
     @torch.no_grad()
     def step(self, closure=None):
         loss = closure() if closure is not None else None
+        n = getattr(self, "grad_accumulation_steps", 1)
+        if n > 1:
+            self._micro += 1
+            if self._micro % n:
+                return loss
+            for g in self.param_groups:
+                for p in g["params"]:
+                    if p.grad is not None:
+                        p.grad.div_(n)
+        if getattr(self, "max_grad_norm", None):
+            clip_grad_norm_([p for g in self.param_groups for p in g["params"]], self.max_grad_norm)
         for g in self.param_groups:
             b1, b2 = g["betas"]
             for p in g["params"]:
@@ -109,6 +131,7 @@ class Adam8bit(Optimizer):
     """AdamW whose moments are stored as block-wise int8 (+ one fp32 scale per 256 values); the second moment is
     stored as sqrt(v) to keep its dynamic range inside 8 bits."""
 
+    @reference_kwargs({"percentile_clipping": (100, 100.0, None), "stochastic_rounding": (False, None)})
     def __init__(self, params, lr=2e-5, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01, block_size=256,
                  min_8bit_size=4096):
         super().__init__(params, dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay, block_size=block_size,
@@ -189,7 +212,13 @@ class Lion(Optimizer):
 
 
 class LAMB(Optimizer):
-    def __init__(self, params, lr=1e-3, betas=(0.9, 0.999), eps=1e-6, weight_decay=0.01, clamp_trust=(0.0, 10.0)):
+    @reference_kwargs({"use_triton": ANY, "always_adapt": (False, None)})
+    def __init__(self, params, lr=1e-3, betas=(0.9, 0.999), eps=1e-6, weight_decay=0.01, clamp_trust=(0.0, 10.0),
+                 trust_ratio_clip: float | None = None):
+        """`trust_ratio_clip`: upper bound of the layer-wise trust ratio (the reference's name; `clamp_trust` gives
+        both bounds)."""
+        if trust_ratio_clip is not None:
+            clamp_trust = (clamp_trust[0], float(trust_ratio_clip))
         super().__init__(params, dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay, clamp_trust=clamp_trust))
 
     @torch.no_grad()
@@ -226,6 +255,7 @@ class LAMB(Optimizer):
 class AdaFactor(Optimizer):
     """Factored second moments for matrices (row / column EMA), update clipping by RMS, optional relative step."""
 
+    @reference_kwargs(_IMPL_OPTIONS)
     def __init__(self, params, lr=None, eps=(1e-30, 1e-3), clip_threshold=1.0, decay_rate=-0.8, beta1=None,
                  weight_decay=0.0, scale_parameter=True, relative_step=True, warmup_init=False):
         super().__init__(params, dict(lr=lr, eps=eps, clip_threshold=clip_threshold, decay_rate=decay_rate, beta1=beta1,
@@ -414,6 +444,7 @@ class DistributedAdaFactor(AdaFactor):
 class CAME(Optimizer):
     """Confidence-guided AdaFactor: a second factored EMA of the update's instability rescales the step."""
 
+    @reference_kwargs({"confidence_threshold": ANY})    # the confidence term is always on: it is what CAME is
     def __init__(self, params, lr=2e-4, eps=(1e-30, 1e-16), clip_threshold=1.0, betas=(0.9, 0.999, 0.9999), weight_decay=0.0):
         super().__init__(params, dict(lr=lr, eps=eps, clip_threshold=clip_threshold, betas=betas, weight_decay=weight_decay))
 
@@ -463,8 +494,13 @@ class SophiaG(Optimizer):
     """Clipped second-order step: p -= lr * clip(m / max(rho * h, eps), 1). Call `update_hessian()` every k steps
     after a backward on sampled labels (Gauss-Newton-Bartlett) or with `hutchinson=True` grads."""
 
-    def __init__(self, params, lr=1e-4, betas=(0.965, 0.99), rho=0.04, weight_decay=0.1, eps=1e-15):
+    @reference_kwargs({"maximize": (False, None)})
+    def __init__(self, params, lr=1e-4, betas=(0.965, 0.99), rho=0.04, weight_decay=0.1, eps=1e-15,
+                 hessian_update_interval: int = 10):
+        """`hessian_update_interval`: how often the caller is expected to refresh the curvature estimate; kept as an
+        attribute for the training loop (`step_count % optimizer.hessian_update_interval == 0` -> `update_hessian`)."""
         super().__init__(params, dict(lr=lr, betas=betas, rho=rho, weight_decay=weight_decay, eps=eps))
+        self.hessian_update_interval = int(hessian_update_interval)
 
     @torch.no_grad()
     def update_hessian(self, batch_size: int = 1):
@@ -531,6 +567,8 @@ class SophiaG(Optimizer):
 class Prodigy(Optimizer):
     """Parameter-free AdamW: the step size scale d is estimated from <g, x0 - x> / ||s||_1."""
 
+    @reference_kwargs({"decouple": (True, None), "use_bias_correction": (False, None), "safeguard_warmup": (False, None),
+                       "beta3": (None,)})
     def __init__(self, params, lr=1.0, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0, d0=1e-6, d_coef=1.0, growth_rate=float("inf")):
         super().__init__(params, dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay, d=d0, d0=d0, d_coef=d_coef,
                                       growth_rate=growth_rate, k=0, d_numerator=0.0))
@@ -722,6 +760,7 @@ class Muon(Optimizer):
 class ADOPT(Optimizer):
     """Adam with the second moment of the PREVIOUS step in the normaliser (converges for any beta2)."""
 
+    @reference_kwargs({"decouple": (True, None)})       # weight decay is always the decoupled (AdamW) form here
     def __init__(self, params, lr=1e-3, betas=(0.9, 0.9999), eps=1e-6, weight_decay=0.0, clip_lambda=lambda k: k ** 0.25):
         super().__init__(params, dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay, clip_lambda=clip_lambda))
 
@@ -896,7 +935,17 @@ class AdaFactorState:
         return d
 
     @classmethod
-    def from_dict(cls, d: dict, device=None) -> "AdaFactorState":
+    @reference_kwargs(state_dict="d")
+    def from_dict(cls, d: dict, device=None, *, shape=None, dtype=None, use_momentum: bool | None = None) -> "AdaFactorState":
+        """`shape`, `dtype` and `use_momentum` fill in what a dictionary written elsewhere does not carry."""
+        d = dict(d)
+        if shape is not None:
+            d.setdefault("shape", list(shape))
+        if dtype is not None:
+            d.setdefault("dtype", str(dtype))
+        if use_momentum is not None:
+            d.setdefault("use_momentum", use_momentum)
+        d.setdefault("factored", "exp_avg_sq_row" in d)
         dtype = getattr(torch, str(d.get("dtype", "torch.float32")).replace("torch.", ""))
         st = cls(tuple(d["shape"]), device, dtype, bool(d["factored"]), bool(d.get("use_momentum", "exp_avg" in d)),
                  bool(d.get("use_kahan", "kahan_comp" in d)))
@@ -1046,6 +1095,7 @@ class BaseOptimizer(Optimizer):
     global-norm clipping before the update (`max_grad_norm` in the defaults), step metrics.
     (data_pipeline/trainer/optimizers/base.py:248, sota_optimizers.py:539)"""
 
+    @reference_kwargs({"use_triton": ANY, "fused": ANY})
     def __init__(self, params, defaults: dict, *, foreach=None, differentiable: bool = False):
         defaults = dict(defaults)
         defaults.setdefault("max_grad_norm", None)

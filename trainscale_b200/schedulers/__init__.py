@@ -12,6 +12,8 @@ from __future__ import annotations
 import math
 from typing import Callable
 
+from ..utils.refargs import ANY, reference_kwargs
+
 
 def warmup_factor(step: int, warmup_steps: int, kind: str = "linear") -> float:
     if warmup_steps <= 0 or step >= warmup_steps:
@@ -28,16 +30,25 @@ class BaseScheduler:
     """lr(step) = base_lr * factor(step). Subclasses implement `decay(progress_step)` in [0, 1]."""
 
     def __init__(self, optimizer, num_training_steps: int, warmup_steps: int = 0, min_lr_ratio: float = 0.0,
-                 warmup_type: str = "linear", last_step: int = -1):
+                 warmup_type: str = "linear", last_step: int = -1, *, warmup_ratio: float = 0.0,
+                 warmup_start_lr: float | None = None, min_lr: float | None = None, last_epoch: int | None = None):
+        """`warmup_ratio` gives the warm-up length as a fraction of the run when `warmup_steps` is 0; `warmup_start_lr`
+        is the absolute rate the warm-up starts from (default 0, i.e. the pure ramp); `min_lr` is the floor as an absolute
+        rate (`min_lr_ratio` as a fraction of the base rate; the larger of the two holds); `last_epoch` is torch's name
+        for `last_step`.  (data_pipeline/trainer/schedulers: BaseScheduler / BaseEnhancedScheduler constructors.)"""
         self.optimizer = optimizer
         self.num_training_steps = max(1, int(num_training_steps))
-        self.warmup_steps = int(warmup_steps)
+        self.warmup_steps = int(warmup_steps) if warmup_steps else int(warmup_ratio * self.num_training_steps)
         self.min_lr_ratio = float(min_lr_ratio)
-        self.warmup_type = warmup_type
+        self.warmup_type = getattr(warmup_type, "value", warmup_type)
         self.base_lrs = [g.get("initial_lr", g["lr"]) for g in optimizer.param_groups]
         for g, b in zip(optimizer.param_groups, self.base_lrs):
             g.setdefault("initial_lr", b)
-        self.last_step = last_step
+        ref = max(self.base_lrs[0], 1e-30)
+        if min_lr is not None:
+            self.min_lr_ratio = max(self.min_lr_ratio, float(min_lr) / ref)
+        self.warmup_start_ratio = 0.0 if warmup_start_lr is None else float(warmup_start_lr) / ref
+        self.last_step = last_step if last_epoch is None else last_epoch
         self.step()
 
     def decay(self, s: int) -> float:   # s = steps after warm-up
@@ -45,7 +56,8 @@ class BaseScheduler:
 
     def factor(self, step: int) -> float:
         if step < self.warmup_steps:
-            return warmup_factor(step, self.warmup_steps, self.warmup_type)
+            w = warmup_factor(step, self.warmup_steps, self.warmup_type)
+            return self.warmup_start_ratio + (1.0 - self.warmup_start_ratio) * w
         d = self.decay(step - self.warmup_steps)
         return self.min_lr_ratio + (1.0 - self.min_lr_ratio) * d
 
@@ -57,14 +69,16 @@ class BaseScheduler:
     def get_last_lr(self) -> list[float]:
         return [g["lr"] for g in self.optimizer.param_groups]
 
-    def step(self) -> None:
-        self.last_step += 1
+    def step(self, step: int | None = None) -> None:
+        """Advance by one, or jump to `step`."""
+        self.last_step = self.last_step + 1 if step is None else int(step)
         for g, lr in zip(self.optimizer.param_groups, self.get_lr()):
             g["lr"] = lr
 
     def state_dict(self) -> dict:
         return {"last_step": self.last_step, "base_lrs": list(self.base_lrs)}
 
+    @reference_kwargs(state_dict="sd")
     def load_state_dict(self, sd: dict) -> None:
         self.last_step = sd["last_step"] - 1
         self.base_lrs = list(sd.get("base_lrs", self.base_lrs))
@@ -103,6 +117,10 @@ class PolynomialDecayScheduler(BaseScheduler):
 
 
 class InverseSquareRootScheduler(BaseScheduler):
+    @reference_kwargs(warmup_init_lr="warmup_start_lr")
+    def __init__(self, optimizer, num_training_steps: int, warmup_steps: int = 0, min_lr_ratio: float = 0.0, **kw):
+        super().__init__(optimizer, num_training_steps, warmup_steps, min_lr_ratio, **kw)
+
     def decay(self, s):
         w = max(1, self.warmup_steps)
         return math.sqrt(w / (w + s))
@@ -131,12 +149,17 @@ class WSDScheduler(BaseScheduler):
 
 
 class REXScheduler(BaseScheduler):
-    """Reflected exponential: (1 - p) / (0.5 + 0.5 (1 - p))."""
+    """Reflected exponential: (1 - p) / ((1 - gamma) + gamma (1 - p)), gamma = 0.5 in the paper."""
+
+    def __init__(self, optimizer, num_training_steps: int, warmup_steps: int = 0, min_lr_ratio: float = 0.0,
+                 gamma: float = 0.5, **kw):
+        self.gamma = float(gamma)
+        super().__init__(optimizer, num_training_steps, warmup_steps, min_lr_ratio, **kw)
 
     def decay(self, s):
         total = max(1, self.num_training_steps - self.warmup_steps)
         p = min(1.0, s / total)
-        return (1.0 - p) / (0.5 + 0.5 * (1.0 - p))
+        return (1.0 - p) / ((1.0 - self.gamma) + self.gamma * (1.0 - p))
 
 
 class CosineRestartScheduler(BaseScheduler):
