@@ -19,6 +19,8 @@ from dataclasses import dataclass, field
 from pathlib import Path
 from typing import Any
 
+from ..utils.refargs import ANY, reference_kwargs
+
 logger = logging.getLogger("trainscale_b200")
 
 HOOKS = ("on_init_end", "on_train_begin", "on_train_end", "on_epoch_begin", "on_epoch_end", "on_step_begin",
@@ -47,6 +49,10 @@ class Callback:
     order = 0
     trainer: Any = None
 
+    def __init__(self, trainer=None):
+        if trainer is not None:
+            self.trainer = trainer
+
     @property
     def priority(self) -> int:
         return self.order
@@ -74,11 +80,13 @@ class CallbackHandler:
         for c in callbacks or []:
             self.add(c)
 
+    @reference_kwargs(callback="cb")
     def add(self, cb: Callback | type) -> None:
         cb = cb() if isinstance(cb, type) else cb
         self.callbacks.append(cb)
         self.callbacks.sort(key=lambda c: c.order)
 
+    @reference_kwargs(callback_type="cb_type")
     def remove(self, cb_type: type) -> None:
         self.callbacks = [c for c in self.callbacks if not isinstance(c, cb_type)]
 
@@ -117,10 +125,25 @@ class CallbackHandler:
 
 
 class EarlyStoppingCallback(Callback):
-    def __init__(self, patience: int = 3, threshold: float = 0.0, metric: str = "eval_loss", greater_is_better=False):
+    """Stops training after `patience` evaluations without an improvement of more than `threshold`.  The reference's
+    names are taken too: `monitor` (metric), `min_delta` (threshold), `mode` = "min" | "max" (greater_is_better) and
+    `restore_best`, which keeps a host copy of the best weights and loads it back when training ends."""
+
+    @reference_kwargs(monitor="metric", min_delta="threshold")
+    def __init__(self, patience: int = 3, threshold: float = 0.0, metric: str = "eval_loss", greater_is_better=False,
+                 mode: str | None = None, restore_best: bool = False):
+        if mode is not None:
+            if mode not in ("min", "max"):
+                raise ValueError("mode must be 'min' or 'max'")
+            greater_is_better = mode == "max"
         self.patience, self.threshold, self.metric, self.greater = patience, threshold, metric, greater_is_better
+        self.restore_best, self.best_state = restore_best, None
         self.best: float | None = None
         self.counter = 0
+
+    def on_train_end(self, ctx):
+        if self.restore_best and self.best_state is not None and ctx.model is not None:
+            ctx.model.load_state_dict(self.best_state)
 
     def on_evaluate(self, ctx):
         v = ctx.metrics.get(self.metric)
@@ -130,6 +153,8 @@ class EarlyStoppingCallback(Callback):
                                          else (v < self.best - self.threshold))
         if improved:
             self.best, self.counter = v, 0
+            if self.restore_best and ctx.model is not None:
+                self.best_state = {k: t.detach().to("cpu", copy=True) for k, t in ctx.model.state_dict().items()}
         else:
             self.counter += 1
             if self.counter >= self.patience:
@@ -139,8 +164,18 @@ class EarlyStoppingCallback(Callback):
 class CheckpointCallback(Callback):
     """save_strategy steps | epoch | best, rotation by save_total_limit (checkpoint-best is never pruned)."""
 
+    @reference_kwargs(save_dir="output_dir")
     def __init__(self, output_dir: str, save_strategy: str = "steps", save_steps: int = 100, save_total_limit: int = 3,
-                 metric: str = "eval_loss", greater_is_better: bool = False):
+                 metric: str = "eval_loss", greater_is_better: bool = False, config=None):
+        """`config`: a checkpoint configuration object (`save_strategy`, `save_steps`, `save_total_limit`,
+        `metric_for_best_model`, `greater_is_better`) whose attributes replace the keyword defaults."""
+        if config is not None:
+            save_strategy = getattr(config, "save_strategy", save_strategy)
+            save_strategy = getattr(save_strategy, "value", save_strategy)
+            save_steps = getattr(config, "save_steps", save_steps)
+            save_total_limit = getattr(config, "save_total_limit", save_total_limit)
+            metric = getattr(config, "metric_for_best_model", metric) or metric
+            greater_is_better = getattr(config, "greater_is_better", greater_is_better)
         self.output_dir, self.strategy, self.save_steps = Path(output_dir), save_strategy, save_steps
         self.limit, self.metric, self.greater = save_total_limit, metric, greater_is_better
         self.best = None
@@ -186,7 +221,12 @@ class LoggingBackend(str, Enum):
 
 class LoggingCallback(Callback):
     def __init__(self, logging_steps: int = 10, backends: tuple[str, ...] = ("console",), log_dir: str | None = None,
-                 rank: int = 0):
+                 rank: int = 0, config=None):
+        """`config`: a logging configuration object (`logging_steps`, `report_to`, `logging_dir`)."""
+        if config is not None:
+            logging_steps = getattr(config, "logging_steps", logging_steps)
+            backends = tuple(getattr(config, "report_to", backends) or backends)
+            log_dir = getattr(config, "logging_dir", log_dir)
         self.logging_steps, self.backends, self.log_dir, self.rank = logging_steps, backends, log_dir, rank
         self._tb = None
         self._wandb = None
@@ -239,8 +279,9 @@ class LoggingCallback(Callback):
 
 
 class ProgressCallback(Callback):
-    def __init__(self, rank: int = 0):
-        self.rank, self.bar = rank, None
+    def __init__(self, rank: int = 0, refresh_rate: int = 1):
+        """`refresh_rate`: the bar is advanced every that many steps (by that many)."""
+        self.rank, self.bar, self.refresh_rate, self._pending = rank, None, max(1, int(refresh_rate)), 0
 
     def on_train_begin(self, ctx):
         if self.rank == 0:
@@ -252,8 +293,12 @@ class ProgressCallback(Callback):
 
     def on_step_end(self, ctx):
         if self.bar is not None:
-            self.bar.update(1)
+            self._pending += 1
+            if self._pending >= self.refresh_rate:
+                self.bar.update(self._pending)
+                self._pending = 0
 
     def on_train_end(self, ctx):
         if self.bar is not None:
+            self.bar.update(self._pending)
             self.bar.close()

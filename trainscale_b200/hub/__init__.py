@@ -115,6 +115,7 @@ def compute_sha256(path: str | os.PathLike, chunk: int = 1 << 22) -> str:
 class ModelSerializer:
     """state dict -> `model.safetensors` or `model-0000i-of-0000n.safetensors` + `model.safetensors.index.json`."""
 
+    @reference_kwargs(shard_size_bytes="max_shard_bytes")
     def __init__(self, max_shard_bytes: int = 5 * 2 ** 30, prefer_safetensors: bool = True):
         if max_shard_bytes <= 0:
             raise ValueError("max_shard_bytes must be positive")
@@ -202,10 +203,17 @@ class ModelSerializer:
 
 
 class ModelDeserializer:
+    @reference_kwargs(num_workers="num_threads")
     def __init__(self, verify_integrity: bool = True, num_threads: int = 4):
         self.verify, self.num_threads = verify_integrity, num_threads
 
-    def load(self, in_dir: str | os.PathLike) -> dict[str, torch.Tensor]:
+    @reference_kwargs(model_dir="in_dir")
+    def load(self, in_dir: str | os.PathLike, device=None) -> dict[str, torch.Tensor]:
+        """State dict of the folder; `device` moves the tensors there (they are read on the host)."""
+        sd = self._load(in_dir)
+        return sd if device is None else {k: v.to(device) for k, v in sd.items()}
+
+    def _load(self, in_dir: str | os.PathLike) -> dict[str, torch.Tensor]:
         d = Path(in_dir)
         idx = d / "model.safetensors.index.json"
         if idx.exists() and HAVE_SAFETENSORS:
@@ -280,6 +288,7 @@ def generate_model_card(model_name, base_model: str = "", config: dict | None = 
 class HubManager:
     """Thin wrapper over `huggingface_hub` with retry + circuit breaker; a no-op target directory when offline."""
 
+    @reference_kwargs(config="repo_id")
     def __init__(self, repo_id: "str | HubConfig | None" = None, token: str | None = None, private: bool = False,
                  policy: RetryPolicy | None = None):
         self._config = None
@@ -425,13 +434,53 @@ class HubManager:
 class CheckpointManager:
     """Atomic directory checkpoints with metadata, pruning and best / latest tracking."""
 
+    @reference_kwargs(save_dir="root", hub_manager="hub", max_checkpoints="save_total_limit")
     def __init__(self, root: str | os.PathLike, save_total_limit: int = 3, metric: str = "eval_loss",
                  greater_is_better: bool = False, hub: HubManager | None = None):
         self.root, self.limit, self.metric, self.greater, self.hub = Path(root), save_total_limit, metric, greater_is_better, hub
         self.root.mkdir(parents=True, exist_ok=True)
         self.best_value: float | None = None
 
-    def save(self, step: int, writer: Callable[[Path], None], metrics: dict | None = None) -> Path:
+    def save(self, *args, **kwargs):
+        """`save(step, writer, metrics=None)`: `writer(dir)` fills the checkpoint folder; returns its path.
+        The reference's form `save(model, optimizer=None, step=0, epoch=0, loss=inf, extra_state=None)` (a module first,
+        or `model=`) writes the weights (safetensors), `optimizer.pt` and `training_state.json` itself and returns
+        Ok(CheckpointMetadata) / Err(HubError)."""
+        ref = bool(args and isinstance(args[0], torch.nn.Module)) or "model" in kwargs
+        names = ("model", "optimizer", "step", "epoch", "loss", "extra_state") if ref else ("step", "writer", "metrics")
+        if len(args) > len(names):
+            raise TypeError(f"save() takes at most {len(names)} positional arguments")
+        bound = dict(zip(names, args))
+        for k, v in kwargs.items():
+            if k in bound:
+                raise TypeError(f"save() got multiple values for argument {k!r}")
+            if k not in names:
+                raise TypeError(f"save() got an unexpected keyword argument {k!r}")
+            bound[k] = v
+        if ref:
+            return self._save_model(bound["model"], bound.get("optimizer"), int(bound.get("step", 0)),
+                                    int(bound.get("epoch", 0)), float(bound.get("loss", float("inf"))),
+                                    bound.get("extra_state"))
+        return self._save_with(int(bound["step"]), bound["writer"], bound.get("metrics"))
+
+    def _save_model(self, model, optimizer, step: int, epoch: int, loss: float, extra_state: dict | None):
+        from ..core.types import Err, Ok
+        state = {"step": step, "epoch": epoch, "loss": loss, **(extra_state or {})}
+
+        def write(d: Path):
+            r = ModelSerializer().serialize(model, d, f"checkpoint-{step}")
+            if r.is_err():
+                raise r.error
+            if optimizer is not None:
+                torch.save(optimizer.state_dict(), d / "optimizer.pt")
+            (d / "training_state.json").write_text(json.dumps(state, indent=2, default=str))
+        try:
+            path = self._save_with(step, write, {"epoch": epoch, "loss": loss, self.metric: loss})
+            return Ok(CheckpointMetadata.read(path))
+        except Exception as e:   # noqa: BLE001
+            return Err(HubError(f"failed to save checkpoint: {e}", code=HubErrorCode.SERIALIZATION_ERROR))
+
+    def _save_with(self, step: int, writer: Callable[[Path], None], metrics: dict | None = None) -> Path:
         final = self.root / f"checkpoint-{step}"
         tmp = self.root / f".tmp-checkpoint-{step}"
         if tmp.exists():

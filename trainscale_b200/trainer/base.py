@@ -31,7 +31,19 @@ class Trainer:
     def __init__(self, model: nn.Module, args: TrainingArguments | None = None, train_dataloader: Iterable | None = None,
                  eval_dataloader: Iterable | None = None, optimizer=None, scheduler=None, callbacks: list | None = None,
                  compute_loss: Callable | None = None, compute_metrics: Callable | None = None,
-                 train_dataset=None, eval_dataset=None, data_collator: Callable | None = None):
+                 train_dataset=None, eval_dataset=None, data_collator: Callable | None = None, *,
+                 optimizers: tuple | None = None, loss_fn: Callable | None = None):
+        """`optimizers` = (optimizer, scheduler) and `loss_fn(outputs_or_logits, labels)` are the reference's spellings
+        (data_pipeline/trainer/base.py:150-190) of `optimizer` / `scheduler` and of a loss computed from the model's
+        output and the batch's labels."""
+        if optimizers is not None:
+            optimizer = optimizer if optimizer is not None else optimizers[0]
+            scheduler = scheduler if scheduler is not None else (optimizers[1] if len(optimizers) > 1 else None)
+        if loss_fn is not None and compute_loss is None:
+            def compute_loss(m, batch, _f=loss_fn):
+                out = m(**{k: v for k, v in batch.items() if k not in ("labels",)})
+                out = out.logits if hasattr(out, "logits") else (out[0] if isinstance(out, tuple) else out)
+                return _f(out, batch["labels"])
         self.model, self.args = model, args or TrainingArguments()
         self.train_dataset, self.eval_dataset, self.data_collator = train_dataset, eval_dataset, data_collator
         if train_dataloader is None and train_dataset is not None:
@@ -84,7 +96,10 @@ class Trainer:
     def _to_device(self, batch):
         return {k: (v.to(self.device) if torch.is_tensor(v) else v) for k, v in batch.items()}
 
-    def train(self) -> dict:
+    def train(self, resume_from_checkpoint: str | None = None) -> dict:
+        """`resume_from_checkpoint`: a folder written by `save_model`; its weights are loaded before the loop."""
+        if resume_from_checkpoint:
+            self.load_model(resume_from_checkpoint)
         a = self.args
         if self.optimizer is None:
             self.optimizer = self.create_optimizer()
@@ -158,7 +173,11 @@ class Trainer:
         return m
 
     @torch.no_grad()
-    def predict(self, dataloader: Iterable) -> list:
+    def predict(self, dataloader: Iterable = None, *, dataset=None) -> list:
+        """Model outputs per batch.  `dataset=` (a map-style dataset) is batched with the evaluation settings."""
+        if dataset is not None:
+            dataloader = self._loader(dataset, self.args.per_device_eval_batch_size or self.args.per_device_train_batch_size,
+                                      False, False)
         self.model.eval()
         outs = []
         for batch in dataloader:
@@ -240,7 +259,33 @@ class FineTuningTrainer(Trainer):
 
 
 class Seq2SeqTrainer(Trainer):
+    def __init__(self, *a, teacher_forcing_ratio: float = 1.0, scheduled_sampling: bool = False, num_beams: int = 1,
+                 length_penalty: float = 1.0, **kw):
+        """`num_beams` / `length_penalty` are handed to the model's own `generate`; `teacher_forcing_ratio` < 1 (or
+        `scheduled_sampling`, which decays the ratio linearly over training) replaces that fraction of the decoder inputs
+        by the model's own greedy predictions from a first, gradient-free pass."""
+        super().__init__(*a, **kw)
+        self.teacher_forcing_ratio, self.scheduled_sampling = float(teacher_forcing_ratio), scheduled_sampling
+        self.num_beams, self.length_penalty = num_beams, length_penalty
+
+    def _decoder_inputs(self, batch):
+        ratio = self.teacher_forcing_ratio
+        if self.scheduled_sampling and self.state.max_steps:
+            ratio = max(0.0, 1.0 - self.state.global_step / self.state.max_steps)
+        if ratio >= 1.0 or "decoder_input_ids" not in batch or not self.model.training:
+            return batch
+        with torch.no_grad():
+            out = self.model(**{k: v for k, v in batch.items() if k in ("input_ids", "attention_mask", "decoder_input_ids")})
+            logits = out.logits if hasattr(out, "logits") else (out[0] if isinstance(out, tuple) else out)
+            own = logits.argmax(-1)
+        dec = batch["decoder_input_ids"]
+        shifted = torch.cat((dec[:, :1], own[:, :-1]), 1)               # prediction for position t feeds position t+1
+        use_own = torch.rand(dec.shape, device=dec.device) >= ratio
+        use_own[:, 0] = False
+        return {**batch, "decoder_input_ids": torch.where(use_own, shifted, dec)}
+
     def compute_loss(self, batch):
+        batch = self._decoder_inputs(batch)
         out = self.model(**{k: v for k, v in batch.items() if k in ("input_ids", "attention_mask", "decoder_input_ids", "labels")})
         if hasattr(out, "loss") and out.loss is not None:
             return out.loss
@@ -274,16 +319,33 @@ class Seq2SeqTrainer(Trainer):
 
 
 class TextGenerationTrainer(Trainer):
+    def __init__(self, *a, top_k: int = 0, top_p: float = 1.0, temperature: float = 1.0, repetition_penalty: float = 1.0,
+                 **kw):
+        """Sampling defaults of `generate` (each call may override them)."""
+        super().__init__(*a, **kw)
+        self.top_k, self.top_p, self.temperature, self.repetition_penalty = top_k, top_p, temperature, repetition_penalty
+
     @torch.no_grad()
-    def generate(self, input_ids: torch.Tensor, max_new_tokens: int = 32, temperature: float = 1.0, top_k: int = 0,
-                 top_p: float = 1.0, eos_token_id: int | None = None) -> torch.Tensor:
+    def generate(self, input_ids: torch.Tensor, max_new_tokens: int = 32, temperature: float | None = None,
+                 top_k: int | None = None, top_p: float | None = None, eos_token_id: int | None = None,
+                 do_sample: bool = True) -> torch.Tensor:
+        """`do_sample=False`: greedy decoding (temperature 0)."""
         from ..inference.sampling import sample
+        temperature = self.temperature if temperature is None else temperature
+        top_k = self.top_k if top_k is None else top_k
+        top_p = self.top_p if top_p is None else top_p
+        if not do_sample:
+            temperature = 0.0
         self.model.eval()
         ids = input_ids.to(self.device)
         for _ in range(max_new_tokens):
             out = self.model(input_ids=ids)
             logits = (out.logits if hasattr(out, "logits") else out)[:, -1].float()
             B = logits.shape[0]
+            if self.repetition_penalty != 1.0:
+                seen = torch.zeros_like(logits, dtype=torch.bool).scatter_(1, ids, True)
+                logits = torch.where(seen, torch.where(logits > 0, logits / self.repetition_penalty,
+                                                       logits * self.repetition_penalty), logits)
             nxt, _ = sample(logits, [temperature] * B, [top_k] * B, [top_p] * B, [0.0] * B, [None] * B)
             ids = torch.cat((ids, nxt.unsqueeze(1)), dim=1)
             if eos_token_id is not None and bool((nxt == eos_token_id).all()):
