@@ -19,6 +19,8 @@ from typing import Any, Dict, List, Optional, Union
 import torch
 import yaml
 
+from ..utils.refargs import ANY, reference_kwargs
+
 
 class TrainingMode(str, Enum):
     FULL_FINETUNE = "full"
@@ -443,6 +445,7 @@ class SOTAConfig:
                 raise ValueError(f"distributed.parallel.{n} must be >= 1")
 
     @classmethod
+    @reference_kwargs(d="raw")
     def from_dict(cls, raw: Dict[str, Any]) -> "SOTAConfig":
         """Sections this class does not know (the data half's keys: type, version, dataset, prompt_template, ...)
         are ignored, exactly like the reference loads one YAML file twice."""

@@ -38,9 +38,16 @@ class CollateFn:
 
     def __init__(self, pad_token_id: int = 0, label_pad_token_id: int = -100, padding_side: str = "right",
                  max_length: int | None = None, pad_values: Mapping[str, int] | None = None,
-                 pad_to_multiple_of: int | None = None):
+                 pad_to_multiple_of: int | None = None, output_schema=None, label_dtype: torch.dtype | None = None):
+        """`output_schema` (a config OutputSchema) supplies per-key pad values; `label_dtype` casts every `*labels`
+        tensor of the batch (e.g. torch.float for regression targets)."""
         self.pad_token_id, self.label_pad, self.side = pad_token_id, label_pad_token_id, padding_side
         self.max_length, self.pad_values, self.multiple = max_length, dict(pad_values or {}), pad_to_multiple_of
+        self.label_dtype = label_dtype
+        if output_schema is not None:
+            for k, spec in getattr(output_schema, "tensors", {}).items():
+                if k != "input_ids":
+                    self.pad_values.setdefault(k, spec.pad_value)
 
     def _pad_value(self, key: str) -> int:
         if key in self.pad_values:
@@ -87,6 +94,10 @@ class CollateFn:
                 mk = key[:-len("labels")] + "attention_mask"
                 if mk in out and torch.is_tensor(out[mk]) and out[mk].shape == out[key].shape:
                     out[key] = out[key].masked_fill(out[mk] == 0, self.label_pad)
+        if getattr(self, "label_dtype", None) is not None:
+            for key in out:
+                if key.endswith("labels") and torch.is_tensor(out[key]):
+                    out[key] = out[key].to(self.label_dtype)
         if "document_ids" in out and torch.is_tensor(out["document_ids"]) and "cu_seqlens" not in out:
             from .packing import cu_seqlens_from_document_ids
             out["cu_seqlens"], out["max_seqlen"] = cu_seqlens_from_document_ids(out["document_ids"])

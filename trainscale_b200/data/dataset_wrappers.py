@@ -5,12 +5,13 @@ and tensor conversion; `StreamingPreprocessedDataset` sharded per DataLoader wor
 """
 from __future__ import annotations
 
-from typing import Any, Iterable, Mapping
+from typing import Any, Callable, Iterable, Mapping
 
 import torch
 from torch.utils.data import Dataset, IterableDataset, get_worker_info
 
 from ..core.errors import PipelineError
+from ..utils.refargs import ANY, reference_kwargs
 
 
 def _to_tensors(d: Mapping[str, Any]) -> dict:
@@ -33,8 +34,11 @@ def _to_tensors(d: Mapping[str, Any]) -> dict:
 
 
 class PreprocessedDataset(Dataset):
+    @reference_kwargs(hf_dataset="dataset", prompt_engine="engine", cache_enabled="cache")
     def __init__(self, dataset, engine, column_mapping: Mapping[str, str] | None = None, cache: bool = True,
-                 max_cache_items: int = 1 << 20):
+                 max_cache_items: int = 1 << 20, transform: Callable | None = None):
+        """`transform(item) -> item` runs on every processed example (after tensor conversion, before caching)."""
+        self.transform = transform
         self.dataset, self.engine, self.mapping = dataset, engine, dict(column_mapping or {})
         self.cache = {} if cache else None
         self.max_cache_items = max_cache_items
@@ -54,6 +58,8 @@ class PreprocessedDataset(Dataset):
             return self.cache[i]
         ex = self.engine.process(self._apply_mapping(self.dataset[i]))
         item = _to_tensors(ex.to_dict())
+        if getattr(self, "transform", None) is not None:
+            item = self.transform(item)
         if self.cache is not None and len(self.cache) < self.max_cache_items:
             self.cache[i] = item
         return item
@@ -71,7 +77,8 @@ class PreprocessedDataset(Dataset):
         """The same preprocessing over a subset of rows (data_pipeline/data/dataset_wrappers.py:179-196)."""
         indices = list(indices)
         sub = self.dataset.select(indices) if hasattr(self.dataset, "select") else [self.dataset[i] for i in indices]
-        return PreprocessedDataset(sub, self.engine, self.mapping, self.cache is not None, self.max_cache_items)
+        return PreprocessedDataset(sub, self.engine, self.mapping, self.cache is not None, self.max_cache_items,
+                                   getattr(self, "transform", None))
 
 
 class _BufferShuffle:
@@ -96,8 +103,16 @@ class _BufferShuffle:
 
 
 class StreamingPreprocessedDataset(IterableDataset):
+    @reference_kwargs(hf_iterable="iterable", prompt_engine="engine")
     def __init__(self, iterable: Iterable, engine, column_mapping: Mapping[str, str] | None = None, rank: int = 0,
-                 world_size: int = 1, skip_errors: bool = True, max_items: int | None = None):
+                 world_size: int = 1, skip_errors: bool = True, max_items: int | None = None,
+                 buffer_size: int | None = None, transform: Callable | None = None):
+        """`buffer_size`: shuffle the stream through a buffer of that many rows (see `shuffle`); `transform(item)` runs
+        on every processed example."""
+        self.transform = transform
+        if buffer_size:
+            iterable = iterable.shuffle(buffer_size=buffer_size) if hasattr(iterable, "shuffle") \
+                else _BufferShuffle(iterable, buffer_size)
         self.iterable, self.engine, self.mapping = iterable, engine, dict(column_mapping or {})
         self.rank, self.world, self.skip_errors, self.max_items = rank, world_size, skip_errors, max_items
         self.num_errors = 0
@@ -138,7 +153,8 @@ class StreamingPreprocessedDataset(IterableDataset):
                 if self.skip_errors:
                     continue
                 raise
-            yield _to_tensors(ex.to_dict())
+            item = _to_tensors(ex.to_dict())
+            yield self.transform(item) if getattr(self, "transform", None) is not None else item
             n += 1
             if self.max_items is not None and n >= self.max_items:
                 return

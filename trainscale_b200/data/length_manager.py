@@ -189,12 +189,26 @@ class TokenEstimator:
 class TokenAwareContentDistributor:
     """Split a total token budget over text columns and truncate each column to its share."""
 
+    @reference_kwargs(total_max_tokens="max_length", distribution_mode="mode")
     def __init__(self, mode: ContentDistributionMode = ContentDistributionMode.PROPORTIONAL, max_length: int = 2048,
                  columns: Sequence[ColumnContentConfig] = (), special_tokens_budget: int = 10, tokenizer=None,
-                 chars_per_token: float = CHARS_PER_TOKEN, exact: bool = False):
-        self.mode = ContentDistributionMode(mode)
+                 chars_per_token: float = CHARS_PER_TOKEN, exact: bool = False, *,
+                 column_ratios: Mapping[str, float] | None = None,
+                 column_configs: Mapping[str, ColumnContentConfig] | None = None,
+                 default_truncation: TruncationStrategy | str | None = None):
+        """`column_ratios` ({name: share}) and `column_configs` ({name: ColumnContentConfig}) are the reference's
+        mapping forms of `columns`; `default_truncation` applies to columns that come from ratios alone."""
+        if isinstance(mode, int) and not isinstance(mode, ContentDistributionMode):      # (total_max_tokens, mode, ...)
+            mode, max_length = (max_length if not isinstance(max_length, int) else ContentDistributionMode.PROPORTIONAL), mode
+        self.mode = ContentDistributionMode(getattr(mode, "value", mode))
         self.max_length, self.special = max_length, special_tokens_budget
-        self.columns = {c.name: c for c in columns}
+        trunc = TruncationStrategy(default_truncation) if default_truncation is not None else TruncationStrategy.SMART
+        cols = {c.name: c for c in columns}
+        for n, r in (column_ratios or {}).items():
+            cols.setdefault(n, ColumnContentConfig(n, ratio=r, truncation=trunc))
+        for n, c in (column_configs or {}).items():
+            cols[n] = c if c.name == n else ColumnContentConfig(**{**c.__dict__, "name": n})
+        self.columns = cols
         self.estimator = TokenEstimator(tokenizer, chars_per_token, exact)
 
     def _cfg(self, name: str) -> ColumnContentConfig:
@@ -289,8 +303,18 @@ class TokenAwareContentDistributor:
                 alloc[n] += min(want[n], int(left * weights[n] / wsum))
         return alloc
 
-    def distribute(self, example: Mapping[str, str], columns: Sequence[str] | None = None) -> dict[str, str]:
-        """Truncate the text columns of `example` so that together they fit the budget."""
+    @reference_kwargs(text_columns="columns")
+    def distribute(self, example: Mapping[str, str], columns: Sequence[str] | None = None,
+                   label_column: str | None = None) -> dict[str, str]:
+        """Truncate the text columns of `example` so that together they fit the budget.  `label_column` is treated as
+        a label for this call (labels are served first in the adaptive mode) and is included in the columns."""
+        if label_column is not None and label_column in example:
+            import dataclasses
+            cur = self._cfg(label_column)
+            if not cur.is_label:
+                self.columns = {**self.columns, label_column: dataclasses.replace(cur, is_label=True)}
+            if columns is not None and label_column not in columns:
+                columns = list(columns) + [label_column]
         cols = [c for c in (columns or example.keys()) if isinstance(example.get(c), str)]
         lengths = {c: self.estimator.estimate(example[c]) for c in cols}
         alloc = self.allocate(lengths)
@@ -335,8 +359,12 @@ class LengthManager:
                 cc.max_tokens if cc.max_tokens is not None else self.config.max_total_length)
         return smart_truncate(text, max_chars, cc.truncation)
 
-    def preprocess_example(self, example: Mapping[str, str]) -> dict[str, str]:
-        """Per-column limits first, then priority trimming until the total fits."""
+    def preprocess_example(self, example: Mapping[str, str], text_columns: Sequence[str] | None = None) -> dict[str, str]:
+        """Per-column limits first, then priority trimming until the total fits.  `text_columns` restricts both steps
+        to those columns (the others pass through untouched)."""
+        if text_columns is not None:
+            part = self.preprocess_example({k: example[k] for k in text_columns if k in example})
+            return {**example, **part}
         out = dict(example)
         for name, cc in self._column_configs.items():
             if isinstance(out.get(name), str) and (cc.max_length is not None or cc.max_chars is not None):
@@ -369,6 +397,7 @@ class LengthManager:
     def _next_power_of_two(n: int) -> int:
         return 1 if n <= 1 else 1 << (n - 1).bit_length()
 
+    @reference_kwargs(batch_lengths="lengths")
     def get_effective_max_length(self, lengths: Sequence[int]) -> int:
         """Padded length of a batch under the configured padding strategy."""
         longest = max(lengths) if lengths else 0

@@ -97,6 +97,7 @@ def unpack_sequences(packed: torch.Tensor, cu_seqlens: torch.Tensor, original_le
 
 
 class PackedDataset(Dataset):
+    @reference_kwargs({"batch_size": ANY}, max_seq_len="max_length")      # batching is the DataLoader's job here
     def __init__(self, dataset, max_length: int, pad_token_id: int = 0, window: int = 1024):
         seqs = [dataset[i] for i in range(len(dataset))]
         self.items = []

@@ -17,6 +17,7 @@ from ..config.data_schema import (ContentDistributionMode, PipelineConfig, Promp
                                   load_config, load_config_dict)
 from ..core.errors import DataLoadingError, DatasetNotFoundError, PipelineError, SplitNotFoundError
 from ..core.types import Err, Ok, Result
+from ..utils.refargs import ANY, reference_kwargs
 from ..introspection import ColumnMapper, DatasetIntrospector
 from .collate import create_collate_fn
 from .dataloader_factory import build_dataloader
@@ -27,16 +28,40 @@ from .tokenization import create_tokenizer
 
 
 class DataPipeline:
-    def __init__(self, config: PipelineConfig, token: str | None = None, trust_remote_code: bool = False):
+    def __init__(self, config: PipelineConfig | None = None, token: str | None = None, trust_remote_code: bool = False, *,
+                 dataset_name: str | None = None, dataset_config=None, tokenizer=None, tokenizer_config=None,
+                 prompt_template=None, output_schema=None, dataloader_config=None, pipeline_config=None):
+        """From a full `PipelineConfig` (`config` / `pipeline_config`), or assembled from parts the way the reference's
+        constructor takes them (data_pipeline/pipeline.py:107-160): a dataset name or `DatasetConfig`, a ready tokenizer
+        or a `TokenizerConfig`, a `PromptTemplate`, an `OutputSchema`, a `DataLoaderConfig`."""
+        config = config if config is not None else pipeline_config
+        if isinstance(config, str):                         # DataPipeline("org/dataset", ...): the shorthand
+            dataset_name, config = config, None
+        if config is None:
+            from ..config.data_schema import DataLoaderConfig, DatasetConfig, OutputSchema, PromptTemplate, TokenizerConfig
+            if dataset_config is None and dataset_name is None:
+                raise ValueError("DataPipeline needs a PipelineConfig, a dataset_config or a dataset_name")
+            name = getattr(tokenizer, "name_or_path", None) or "byte"
+            config = PipelineConfig(
+                "data_module", "1.0", dataset_config if dataset_config is not None else DatasetConfig(dataset_name),
+                tokenizer_config if tokenizer_config is not None else TokenizerConfig(name),
+                prompt_template if prompt_template is not None else PromptTemplate(),
+                None, output_schema if output_schema is not None else OutputSchema(),
+                dataloader_config if dataloader_config is not None else DataLoaderConfig())
         self.config = config
         self.token = token or os.environ.get("HF_TOKEN")
         self.trust_remote_code = trust_remote_code
         self._tokenizer = None
+        if tokenizer is not None:
+            from .tokenization import TokenizerWrapper
+            self._tokenizer = tokenizer if isinstance(tokenizer, TokenizerWrapper) else \
+                TokenizerWrapper(tokenizer, max_length=getattr(self.config.tokenizer, "max_length", 2048))
         self._engine = None
         self._memory: dict[str, Sequence[Mapping[str, Any]]] = {}
         self.introspector = DatasetIntrospector(self.token)
 
     @classmethod
+    @reference_kwargs(config_path="path_or_dict")
     def from_config(cls, path_or_dict, token: str | None = None, trust_remote_code: bool = False) -> Result:
         r = load_config_dict(path_or_dict) if isinstance(path_or_dict, Mapping) else load_config(path_or_dict)
         if r.is_err():
@@ -94,7 +119,17 @@ class DataPipeline:
         st = self.config.dataset.stages.get(stage) if self.config.dataset.stages else None
         return list(st.splits) if st is not None else []
 
-    def load_dataset(self, split: str = "train") -> Result:
+    def load_dataset(self, split: str = "train", streaming: bool | None = None) -> Result:
+        """`streaming`: override the dataset's configured mode for this call (hub datasets only; local files and
+        registered rows are always materialised)."""
+        if streaming is not None and streaming != self.config.dataset.streaming:
+            import dataclasses
+            saved = self.config
+            self.config = dataclasses.replace(saved, dataset=dataclasses.replace(saved.dataset, streaming=bool(streaming)))
+            try:
+                return self.load_dataset(split)
+            finally:
+                self.config = saved
         ds = self.config.dataset
         spec = ds.splits.get(split)
         real = spec.name if spec is not None else split
@@ -137,8 +172,9 @@ class DataPipeline:
         except Exception as e:   # noqa: BLE001
             raise DatasetNotFoundError(f"cannot load dataset {ds.name!r} split {real!r}", cause=e)
 
-    def get_preprocessed_dataset(self, split: str = "train", rank: int = 0, world_size: int = 1) -> Result:
-        r = self.load_dataset(split)
+    def get_preprocessed_dataset(self, split: str = "train", rank: int = 0, world_size: int = 1,
+                                 streaming: bool | None = None) -> Result:
+        r = self.load_dataset(split, streaming)
         if r.is_err():
             return r
         try:
@@ -146,11 +182,12 @@ class DataPipeline:
         except PipelineError as e:
             return Err(e)
         ds = self.config.dataset
-        return Ok(create_preprocessed_dataset(r.unwrap(), engine, streaming=ds.streaming,
+        return Ok(create_preprocessed_dataset(r.unwrap(), engine, streaming=ds.streaming if streaming is None else streaming,
                                               column_mapping=dict(ds.column_mapping), rank=rank, world_size=world_size))
 
     def get_dataloader(self, split: str = "train", batch_size: int | None = None, distributed: bool = False,
-                       rank: int = 0, world_size: int = 1, shuffle: bool | None = None) -> Result:
+                       rank: int = 0, world_size: int = 1, shuffle: bool | None = None,
+                       num_workers: int | None = None) -> Result:
         r = self.get_preprocessed_dataset(split, rank, world_size)
         if r.is_err():
             return r
@@ -162,7 +199,7 @@ class DataPipeline:
             return Ok(build_dataloader(
                 r.unwrap(), batch_size=batch_size or dl.batch_size,
                 shuffle=(dl.shuffle if shuffle is None else shuffle) and split.startswith("train"), seed=dl.seed,
-                num_workers=dl.num_workers, pin_memory=dl.pin_memory, drop_last=dl.drop_last, collate_fn=collate,
+                num_workers=dl.num_workers if num_workers is None else num_workers, pin_memory=dl.pin_memory, drop_last=dl.drop_last, collate_fn=collate,
                 distributed=distributed, rank=rank, world_size=world_size, prefetch_factor=dl.prefetch_factor,
                 persistent_workers=dl.persistent_workers))
         except PipelineError as e:

@@ -564,8 +564,21 @@ class PromptEngine:
         return cls(config, tokenizer, distributor, template)
 
     @classmethod
-    def from_legacy(cls, template: PromptTemplate, tokenizer, max_length: int = 2048, distributor=None) -> "PromptEngine":
-        """Build from a bare `prompt_template` section (no `prompt_engine` block in the YAML)."""
+    def from_legacy(cls, template: PromptTemplate, tokenizer, max_length: int = 2048, distributor=None, *,
+                    length_manager=None, per_column_limits: Mapping[str, int] | None = None) -> "PromptEngine":
+        """Build from a bare `prompt_template` section (no `prompt_engine` block in the YAML).  `length_manager` (a
+        LengthManager) or `per_column_limits` ({column: max tokens}) trim the row's text columns before templating, when
+        no distributor does."""
+        if distributor is None and (length_manager is not None or per_column_limits):
+            from .length_manager import create_length_manager
+            lm = length_manager if length_manager is not None else create_length_manager(
+                max_total_length=max_length, per_column_limits=dict(per_column_limits), tokenizer=tokenizer)
+
+            class _Trim:
+                def distribute(self, row):
+                    return lm.preprocess_example({k: v for k, v in row.items() if isinstance(v, str)}) | \
+                        {k: v for k, v in row.items() if not isinstance(v, str)}
+            distributor = _Trim()
         import dataclasses
         fmt = {"chat": FineTuningFormat.CHAT, "completion": FineTuningFormat.COMPLETION}.get(template.format_type,
                                                                                               FineTuningFormat.CUSTOM)
@@ -587,9 +600,11 @@ class PromptEngine:
             row = self.distributor.distribute(row)
         return row
 
+    @reference_kwargs(example="row")
     def process(self, row: Mapping[str, Any]):
         return self.processor.process(self._preprocess_example(row))
 
+    @reference_kwargs(examples="rows")
     def process_batch(self, rows: Iterable[Mapping[str, Any]], skip_errors: bool = False) -> list:
         out = []
         for r in rows:
@@ -600,9 +615,14 @@ class PromptEngine:
                     raise
         return out
 
-    def pack_documents(self, texts: Sequence[str], packing: PackingConfig | None = None) -> list[PackedExample]:
+    @reference_kwargs(examples="texts")
+    def pack_documents(self, texts: Sequence, packing: PackingConfig | None = None) -> list[PackedExample]:
+        """`texts`: strings, or rows (mappings) from which the configured text column is taken."""
         if not isinstance(self.processor, _PreTrainingProcessor):
             raise TokenizationError("pack_documents needs a pre_training prompt engine")
+        if texts and isinstance(texts[0], Mapping):
+            col = getattr(getattr(self.config, "pre_training", None), "text_column", "text")
+            texts = [t[col] for t in texts]
         return self.processor.pack_documents(texts, packing)
 
     def describe(self) -> dict:

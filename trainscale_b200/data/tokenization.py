@@ -12,6 +12,8 @@ from typing import Any, Iterable, Sequence
 
 import torch
 
+from ..utils.refargs import ANY, reference_kwargs
+
 from ..core.errors import TokenizationError
 
 
@@ -169,13 +171,24 @@ class Encoding:
 class TokenizerWrapper:
     def __init__(self, tokenizer, max_length: int = 2048, padding: str | bool = "max_length", truncation: bool = True,
                  padding_side: str = "right", truncation_side: str = "right", add_special_tokens: bool = True,
-                 special_tokens: dict | None = None):
+                 special_tokens: dict | None = None, *, config=None, original_vocab_size: int | None = None,
+                 vocab_was_modified: bool | None = None):
+        """`config` (a TokenizerConfig) supplies the settings above; `original_vocab_size` is the vocabulary size before
+        the caller added tokens itself (the reference passes it, with `vocab_was_modified`, when it loaded and extended
+        the tokenizer before wrapping it); both are otherwise derived."""
+        if config is not None and not isinstance(config, (int, float)):
+            max_length = getattr(config, "max_length", max_length)
+            padding, truncation = getattr(config, "padding", padding), getattr(config, "truncation", truncation)
+            padding_side = getattr(config, "padding_side", padding_side)
+            truncation_side = getattr(config, "truncation_side", truncation_side)
+            add_special_tokens = getattr(config, "add_special_tokens", add_special_tokens)
+            special_tokens = special_tokens or dict(getattr(config, "special_tokens", {}) or {})
         self.tokenizer = tokenizer
         self.max_length, self.padding, self.truncation = max_length, padding, truncation
         self.add_special_tokens = add_special_tokens
         tokenizer.padding_side, tokenizer.truncation_side = padding_side, truncation_side
         self.pad_resolution = _ensure_pad_token(tokenizer)
-        self._initial_vocab = len(tokenizer)
+        self._initial_vocab = len(tokenizer) if original_vocab_size is None else int(original_vocab_size)
         if special_tokens:
             self.add_special_tokens_dict(special_tokens)
 
@@ -235,14 +248,16 @@ class TokenizerWrapper:
                              return_attention_mask=False)
         return list(out["input_ids"])
 
-    def count_tokens(self, text: str) -> int:
-        return len(self.encode_raw(text))
+    def count_tokens(self, text: str, add_special_tokens: bool = False) -> int:
+        return len(self.encode_raw(text, add_special_tokens=add_special_tokens))
 
+    @reference_kwargs({"clean_up_tokenization_spaces": ANY}, token_ids="ids")
     def decode(self, ids, skip_special_tokens: bool = True) -> str:
         if torch.is_tensor(ids):
             ids = ids.tolist()
         return self.tokenizer.decode(ids, skip_special_tokens=skip_special_tokens)
 
+    @reference_kwargs({"already_has_special_tokens": ANY}, token_ids="ids")
     def get_special_tokens_mask(self, ids: Sequence[int]) -> list[int]:
         special = {i for i in (self.pad_token_id, self.eos_token_id, self.bos_token_id,
                                getattr(self.tokenizer, "unk_token_id", None)) if i is not None}

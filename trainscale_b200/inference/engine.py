@@ -24,6 +24,8 @@ from typing import Any, AsyncIterator, Iterable
 
 import torch
 
+from ..utils.refargs import ANY, reference_kwargs
+
 from ..core.types import Err, Ok, Result
 from ..ops import _lib, activation, attention, gemm, norm, rope
 from .kv_cache import PagedKVCache
@@ -175,10 +177,13 @@ class RequestMetrics:
         if self.first_token is None:
             self.first_token = time.perf_counter()
 
-    def mark_complete(self, completion_tokens: int | None = None) -> None:
+    @reference_kwargs(num_generated="completion_tokens")
+    def mark_complete(self, completion_tokens: int | None = None, num_prompt: int | None = None) -> None:
         self.finished = time.perf_counter()
         if completion_tokens is not None:
             self.completion_tokens = completion_tokens
+        if num_prompt is not None:
+            self.prompt_tokens = num_prompt
 
 
 class MetricsAggregator:
@@ -188,7 +193,8 @@ class MetricsAggregator:
     def add(self, m: RequestMetrics) -> None:
         self.records.append(m)
 
-    record = add
+    def record(self, metrics: RequestMetrics) -> None:
+        self.records.append(metrics)
 
     def summarize(self) -> dict:
         """`summary()`, or {"status": "no_requests_completed"} before the first finished request."""
@@ -711,15 +717,29 @@ class EngineCore:
         return text
 
 
+def _lora_request_parts(req) -> tuple[str, str | None]:
+    """(adapter name, adapter directory or None) from a name, a mapping or an object with `lora_name` / `lora_path`."""
+    if isinstance(req, str):
+        return req, None
+    get = req.get if isinstance(req, dict) else (lambda k, d=None: getattr(req, k, d))
+    return get("lora_name"), get("lora_path", None)
+
+
 class EngineBuilder:
     def __init__(self, config: EngineConfig | None = None):
         self.config = config or EngineConfig()
 
-    def build_sync(self, model=None, tokenizer=None) -> "SOTAInferenceEngine":
-        return SOTAInferenceEngine(self.config, model, tokenizer)
+    def build_sync(self, model=None, tokenizer=None, *, config: EngineConfig | None = None) -> "SOTAInferenceEngine":
+        """`config` replaces the builder's own configuration for this engine (a config in the first position works
+        too: `EngineBuilder().build_sync(config)`)."""
+        if isinstance(model, EngineConfig):
+            config, model = model, None
+        return SOTAInferenceEngine(config or self.config, model, tokenizer)
 
-    def build_async(self, model=None, tokenizer=None) -> "SOTAAsyncStreamEngine":
-        return SOTAAsyncStreamEngine(self.config, model, tokenizer)
+    def build_async(self, model=None, tokenizer=None, *, config: EngineConfig | None = None) -> "SOTAAsyncStreamEngine":
+        if isinstance(model, EngineConfig):
+            config, model = model, None
+        return SOTAAsyncStreamEngine(config or self.config, model, tokenizer)
 
 
 class SOTAInferenceEngine:
@@ -753,7 +773,12 @@ class SOTAInferenceEngine:
             out.append(resp)
         return out
 
-    def generate(self, prompts: str | Iterable[str], params: GenerationParams | None = None) -> Result:
+    def generate(self, prompts: str | Iterable[str], params: GenerationParams | None = None, lora_request=None) -> Result:
+        """`lora_request`: {"lora_name": ..., "lora_path": ...} (or an object with those attributes, or just the name
+        of a loaded adapter): the adapter is loaded on first use and applied to these prompts."""
+        if lora_request is not None:
+            name, path = _lora_request_parts(lora_request)
+            return self.generate_with_lora(prompts, name, path, params=params)
         try:
             single = isinstance(prompts, str)
             if self.config.speculative.enabled and self.draft_model is not None:
@@ -782,8 +807,8 @@ class SOTAInferenceEngine:
     def metrics(self) -> "MetricsAggregator":
         return self.core.metrics
 
-    def generate_single(self, prompt: str, params: GenerationParams | None = None) -> Result:
-        return self.generate(prompt, params)
+    def generate_single(self, prompt: str, params: GenerationParams | None = None, lora_request=None) -> Result:
+        return self.generate(prompt, params, lora_request)
 
     def generate_with_lora(self, prompts: str | Iterable[str], lora_name: str, lora_path: str | None = None,
                            lora_id: int | None = None, params: GenerationParams | None = None) -> Result:
@@ -827,7 +852,17 @@ class SOTAAsyncStreamEngine:
         self._task = None
 
     async def generate_stream(self, prompt: str, params: GenerationParams | None = None,
-                              request_id: str | None = None) -> AsyncIterator[StreamChunk]:
+                              request_id: str | None = None, lora_request=None) -> AsyncIterator[StreamChunk]:
+        if lora_request is not None:
+            import copy as _copy
+            name, path = _lora_request_parts(lora_request)
+            if name not in self.core.adapter_states:
+                if path is None:
+                    raise ValueError(f"adapter {name!r} is not loaded and the request names no lora_path")
+                from ..lora import adapter_state_from_dir
+                self.core.load_adapters({**self.core.adapter_states, name: adapter_state_from_dir(self.core.model, path)})
+            params = _copy.copy(params) if params is not None else GenerationParams()
+            params.lora_name = name
         r = self.core.add_request(prompt, params, request_id)
         q: asyncio.Queue = asyncio.Queue()
         self._queues[r.request_id] = q
@@ -857,11 +892,12 @@ class SOTAAsyncStreamEngine:
     def active_request_count(self) -> int:
         return len(self._queues)
 
-    async def generate(self, prompt: str, params: GenerationParams | None = None, request_id: str | None = None) -> Result:
+    async def generate(self, prompt: str, params: GenerationParams | None = None, request_id: str | None = None,
+                       lora_request=None) -> Result:
         """Non-streaming form: runs the streaming path and returns the whole completion."""
         try:
             text, ids, reason, rid = [], [], None, request_id
-            async for c in self.generate_stream(prompt, params, request_id):
+            async for c in self.generate_stream(prompt, params, request_id, lora_request):
                 rid = c.request_id
                 text.append(c.text)
                 if c.token_id is not None and c.token_id >= 0:

@@ -64,6 +64,7 @@ class DatasetIntrospector:
     def clear_cache(self) -> None:
         self._cache.clear()
 
+    @reference_kwargs({"trust_remote_code": ANY}, dataset_id="name_or_data")
     def discover(self, name_or_data, config_name: str | None = None) -> Result:
         """Metadata of rows in memory, of a local file / directory, or of a hub dataset.  Hub and path look-ups are
         cached per (name, config) until `clear_cache()`."""
@@ -120,7 +121,15 @@ class DatasetIntrospector:
         except Exception as e:   # noqa: BLE001
             raise DatasetNotFoundError(f"dataset {name!r} not found locally and the hub is unreachable", cause=e)
 
-    def get_default_split(self, md: DatasetMetadata) -> Result:
+    def get_default_split(self, md: "DatasetMetadata | str | None" = None, config: str | None = None, *,
+                          dataset_id=None) -> Result:
+        """Preferred split of discovered metadata, or of a dataset given by id / path / rows (discovered first)."""
+        md = md if md is not None else dataset_id
+        if not isinstance(md, DatasetMetadata):
+            r = self.discover(md, config)
+            if r.is_err():
+                return r
+            md = r.unwrap()
         for s in self.SPLIT_PREFERENCE:
             if s in md.splits:
                 return Ok(s)
@@ -136,8 +145,15 @@ class ColumnMapper:
                "completion": ("answer", "response", "output", "target"), "chosen": ("preferred", "winner", "accepted"),
                "rejected": ("dispreferred", "loser", "refused"), "messages": ("conversation", "conversations", "dialog")}
 
-    def __init__(self, max_distance: int = 2, case_sensitive: bool = False):
-        self.max_distance, self.case_sensitive = max_distance, case_sensitive
+    def __init__(self, max_distance: int = 2, case_sensitive: bool = False,
+                 custom_patterns: Mapping[str, Sequence[str]] | None = None, min_fuzzy_score: float | None = None):
+        """`custom_patterns`: extra aliases {wanted column: (accepted names...)}; `min_fuzzy_score` in [0, 1]: a fuzzy
+        match must have at least this normalised similarity (in addition to the edit-distance bound)."""
+        self.max_distance, self.case_sensitive, self.min_fuzzy_score = max_distance, case_sensitive, min_fuzzy_score
+        if custom_patterns:
+            self.ALIASES = {**self.ALIASES}
+            for k, names in custom_patterns.items():
+                self.ALIASES[k] = tuple(self.ALIASES.get(k, ())) + tuple(n.lower() for n in names)
 
     def _norm(self, s: str) -> str:
         return s if self.case_sensitive else s.lower()
@@ -156,10 +172,20 @@ class ColumnMapper:
             d = levenshtein_distance(w, self._norm(a))
             if d < best_d:
                 best, best_d = a, d
+        if best is not None and self.min_fuzzy_score is not None and \
+                normalized_similarity(wanted, best) < self.min_fuzzy_score:
+            return None
         return best if best_d <= self.max_distance else None
 
-    def map_columns(self, required: Sequence[str], available: Sequence[str], explicit: Mapping[str, str] | None = None
-                    ) -> Result:
+    def map_columns(self, required: Sequence[str] | None = None, available: Sequence[str] | None = None,
+                    explicit: Mapping[str, str] | None = None, *, source_columns: Sequence[str] | None = None,
+                    target_schema: Sequence[str] | None = None, explicit_mapping: Mapping[str, str] | None = None) -> Result:
+        """{wanted column: dataset column}.  `map_columns(required, available, explicit)`; the reference names the same
+        three things `target_schema`, `source_columns`, `explicit_mapping` and passes the SOURCE columns first."""
+        if source_columns is not None or target_schema is not None:
+            required = target_schema if target_schema is not None else available
+            available = source_columns if source_columns is not None else required
+        explicit = explicit if explicit is not None else explicit_mapping
         out, missing = {}, []
         for r in required:
             if explicit and r in explicit:

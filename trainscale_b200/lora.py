@@ -21,10 +21,22 @@ from .utils.refargs import ANY, reference_kwargs
 class LoRALinear(nn.Module):
     """Low-rank update for one row block [row0, row0+rows) of a (possibly fused) weight."""
 
-    def __init__(self, in_features: int, rows: int, r: int = 16, alpha: float = 32.0, dropout: float = 0.0,
-                 use_rslora: bool = True, row0: int = 0, total_rows: int | None = None, dtype=None, device=None,
-                 init: bool | str = True):
+    def __init__(self, in_features: int, rows: int | None = None, r: int = 16, alpha: float = 32.0, dropout: float = 0.0,
+                 use_rslora: bool | None = None, row0: int = 0, total_rows: int | None = None, dtype=None, device=None,
+                 init: bool | str = True, bias: bool = False, *, out_features: int | None = None,
+                 lora_alpha: float | None = None, lora_dropout: float | None = None):
+        """`rows` is the adapter's output width.  `bias=True` adds a trainable output bias, used by the stand-alone
+        form (`forward` with a base weight).  The reference's names `out_features`, `lora_alpha`, `lora_dropout` are
+        taken as well; a layer built with them scales by alpha / r like the reference's (data_pipeline/trainer/lora.py:95)
+        unless `use_rslora` is given, whereas this framework's default is the rank-stabilised alpha / sqrt(r)."""
+        ref_form = out_features is not None or lora_alpha is not None
+        rows = rows if rows is not None else out_features
+        alpha = alpha if lora_alpha is None else lora_alpha
+        dropout = dropout if lora_dropout is None else lora_dropout
+        if use_rslora is None:
+            use_rslora = not ref_form
         super().__init__()
+        self._want_bias = bias
         self.r, self.row0, self.rows, self.total_rows = r, row0, rows, total_rows or rows
         self.scaling = alpha / math.sqrt(r) if use_rslora else alpha / r
         self.lora_A = nn.Parameter(torch.empty(r, in_features, dtype=dtype, device=device))
@@ -32,7 +44,7 @@ class LoRALinear(nn.Module):
         self.dropout = nn.Dropout(dropout) if dropout > 0 else None
         self._init = init
         self.weight = None            # frozen base weight: only when built by `from_linear` (stand-alone layer)
-        self.bias_param = None
+        self.bias_param = nn.Parameter(torch.zeros(rows, dtype=dtype, device=device)) if bias else None
         self.reset_lora_parameters()
 
     def reset_lora_parameters(self) -> None:

@@ -183,9 +183,24 @@ def left_pack_padding(ids: torch.Tensor, mask: torch.Tensor | int | None = None,
 
 class GRPOCompute:
     def __init__(self, group_size: int = 8, clip: float = 0.2, beta: float = 0.01, variant: str = "grpo",
-                 model: nn.Module | None = None, reward_clip: float | None = None, chunk_tokens: int = 4096):
+                 model: nn.Module | None = None, reward_clip: float | None = None, chunk_tokens: int = 4096, *,
+                 ref_model: nn.Module | None = None, config=None):
+        """`GRPOCompute(model, ref_model, config)` is the reference's form: `config` (an RL configuration object)
+        supplies num_generations (group size), clip_range, kl_coef (beta), algorithm (variant) and reward_clip."""
+        if isinstance(group_size, nn.Module):                 # positional (model, ref_model, config)
+            model, group_size = group_size, 8
+            if isinstance(clip, nn.Module) or clip is None:
+                ref_model, clip = clip, 0.2
+            if not isinstance(beta, (int, float)):
+                config, beta = beta, 0.01
+        if config is not None:
+            group_size = int(getattr(config, "num_generations", group_size))
+            clip = float(getattr(config, "clip_range", clip))
+            beta = float(getattr(config, "kl_coef", beta))
+            variant = str(getattr(getattr(config, "algorithm", variant), "value", getattr(config, "algorithm", variant))).lower()
+            reward_clip = getattr(config, "reward_clip", reward_clip)
         self.group_size, self.clip, self.beta, self.variant = group_size, clip, beta, variant
-        self.model, self.reward_clip, self.chunk_tokens = model, reward_clip, chunk_tokens
+        self.model, self.ref_model, self.reward_clip, self.chunk_tokens = model, ref_model, reward_clip, chunk_tokens
 
     def compute_log_probs(self, input_ids: torch.Tensor, attention_mask: torch.Tensor | None = None,
                           model: nn.Module | None = None) -> torch.Tensor:
@@ -228,14 +243,30 @@ class GRPOCompute:
 class RewardModel(nn.Module):
     """Decoder backbone + scalar head read at the last real token."""
 
-    def __init__(self, backbone):
+    def __init__(self, backbone=None, *, model=None, reward_fn=None):
+        """`RewardModel(backbone)`: a framework decoder gets a scalar value head.  `model=` / `reward_fn=` are the
+        reference's form (data_pipeline/trainer/rl_training.py:607): any classifier whose last-position logit is the
+        score, or a function (input_ids, attention_mask, **kw) -> [B]; with neither, rewards are zero."""
         super().__init__()
+        self.reward_fn, self.scorer = reward_fn, None
+        backbone = backbone if backbone is not None else model
         self.backbone = backbone
-        h = backbone.config.hidden_size
-        p = next(backbone.parameters())
-        self.value_head = nn.Linear(h, 1, bias=False, dtype=p.dtype, device=p.device)
+        if backbone is not None and hasattr(getattr(backbone, "config", None), "hidden_size") and hasattr(backbone, "model"):
+            h = backbone.config.hidden_size
+            p = next(backbone.parameters())
+            self.value_head = nn.Linear(h, 1, bias=False, dtype=p.dtype, device=p.device)
+        else:
+            self.scorer, self.backbone = backbone, None
 
-    def forward(self, input_ids, attention_mask=None):
+    def forward(self, input_ids, attention_mask=None, **kwargs):
+        if self.backbone is None:
+            if self.scorer is not None:
+                out = self.scorer(input_ids=input_ids, attention_mask=attention_mask)
+                logits = out.logits if hasattr(out, "logits") else out
+                return logits[:, -1].reshape(logits.shape[0], -1)[:, 0].float() if logits.dim() > 1 else logits.float()
+            if self.reward_fn is not None:
+                return self.reward_fn(input_ids, attention_mask, **kwargs)
+            return torch.zeros(input_ids.shape[0], device=input_ids.device)
         h = self.backbone.model(input_ids)
         if attention_mask is None:
             last = torch.full((h.shape[0],), h.shape[1] - 1, device=h.device)
