@@ -62,6 +62,23 @@ def test_every_public_name_of_the_reference_exists_here():
     assert not missing, f"{len(missing)} names without a counterpart: {sorted(missing.items())[:20]}"
 
 
+def test_every_module_of_the_package_imports():
+    """The surface tests skip modules that fail to import, so a broken import must fail on its own."""
+    import importlib
+    import pkgutil
+
+    import trainscale_b200
+    failed = {}
+    for m in pkgutil.walk_packages(trainscale_b200.__path__, "trainscale_b200."):
+        if m.name.endswith("__main__"):
+            continue
+        try:
+            importlib.import_module(m.name)
+        except Exception as e:   # noqa: BLE001
+            failed[m.name] = repr(e)[:120]
+    assert not failed, failed
+
+
 def _reference_methods(root: Path) -> dict[str, set[str]]:
     """{class name: public method names} over every module-level class of the reference (same-named classes of
     different files are merged)."""

@@ -22,6 +22,7 @@ import torch
 from ..config.data_schema import (FIMMode, FineTuningFormat, PackingConfig, PackingStrategy, PreTrainingFormat,
                                   PromptEngineConfig, PromptTemplate, RLAlgorithm, TrainingStage)
 from ..core.errors import PipelineError, TemplateRenderError, TokenizationError
+from ..utils.refargs import ANY, reference_kwargs
 from .tokenization import TokenizerWrapper
 
 IGNORE = -100
