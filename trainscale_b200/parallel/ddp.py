@@ -19,6 +19,8 @@ import torch
 import torch.distributed as dist
 import torch.nn as nn
 
+from ..utils.refargs import ANY, reference_kwargs
+
 from ..core.types import Err, Ok, Result
 
 BUCKET_MB = {"b200_nvlink": (80, 40), "h100_nvlink": (50, 25), "a100_nvlink": (40, 25), "pcie": (25, 25), "cpu": (25, 25)}
@@ -97,10 +99,12 @@ def allreduce_hook(group, bucket: torch.Tensor) -> torch.Tensor:
 class CastCompressionHook:
     """All-reduce in fp16 / bf16 (with a pre-scale by 1/world so the sum cannot overflow), then cast back."""
 
-    def __init__(self, dtype: torch.dtype):
-        self.dtype = dtype
+    def __init__(self, dtype: torch.dtype, process_group=None):
+        """`process_group`: used when the hook is called with group None (the engines of this module always pass one)."""
+        self.dtype, self.process_group = dtype, process_group
 
     def __call__(self, group, bucket: torch.Tensor) -> torch.Tensor:
+        group = group if group is not None else self.process_group
         w = dist.get_world_size(group)
         low = (bucket / w).to(self.dtype)
         dist.all_reduce(low, group=group)
@@ -111,7 +115,11 @@ class CastCompressionHook:
 class PowerSGDHook:
     """Rank-r PowerSGD with error feedback on 2-D views of each bucket; plain all-reduce for the first iterations."""
 
-    def __init__(self, rank: int = 4, start_iter: int = 10, seed: int = 0):
+    @reference_kwargs({"use_error_feedback": (True, None)}, matrix_rank="rank", warmup_steps="start_iter")
+    def __init__(self, rank: int = 4, start_iter: int = 10, seed: int = 0, process_group=None):
+        """Error feedback is always on (without it the low-rank projection does not converge); `process_group` is used
+        when the hook is called with group None."""
+        self.process_group = process_group
         self.rank, self.start_iter, self.iter = rank, start_iter, 0
         self.state: dict[int, dict] = {}
         self.gen = torch.Generator().manual_seed(seed)
@@ -124,6 +132,7 @@ class PowerSGDHook:
 
     def __call__(self, group, bucket: torch.Tensor, key: int = 0) -> torch.Tensor:
         self.iter += 1
+        group = group if group is not None else self.process_group
         w = dist.get_world_size(group)
         if self.iter <= self.start_iter or bucket.numel() < 4 * self.rank * self.rank:
             dist.all_reduce(bucket, group=group)
@@ -154,14 +163,16 @@ class PowerSGDHook:
 class TopKSparsificationHook:
     """Keep the largest-|g| fraction per rank (error feedback for the rest), exchange (index, value) pairs."""
 
-    def __init__(self, ratio: float = 0.01):
-        self.ratio = ratio
+    @reference_kwargs({"use_triton": ANY}, k_ratio="ratio")
+    def __init__(self, ratio: float = 0.01, process_group=None):
+        self.ratio, self.process_group = ratio, process_group
         self.err: dict[int, torch.Tensor] = {}
 
     def reset_state(self) -> None:
         self.err.clear()
 
     def __call__(self, group, bucket: torch.Tensor, key: int = 0) -> torch.Tensor:
+        group = group if group is not None else self.process_group
         w = dist.get_world_size(group)
         g = bucket.float() + self.err.get(key, 0)
         k = max(1, int(g.numel() * self.ratio))
@@ -182,13 +193,15 @@ class TopKSparsificationHook:
 
 
 class FP16CompressionHook(CastCompressionHook):
-    def __init__(self):
-        super().__init__(torch.float16)
+    @reference_kwargs({"use_triton": ANY, "initial_loss_scale": ANY})   # the pre-scale by 1 / world replaces a loss scale
+    def __init__(self, process_group=None):
+        super().__init__(torch.float16, process_group)
 
 
 class BF16CompressionHook(CastCompressionHook):
-    def __init__(self):
-        super().__init__(torch.bfloat16)
+    @reference_kwargs({"use_triton": ANY, "initial_loss_scale": ANY})
+    def __init__(self, process_group=None):
+        super().__init__(torch.bfloat16, process_group)
 
 
 class FP8CompressionHook:
@@ -355,6 +368,7 @@ class MemoryPressureMonitor:
     above `critical` it releases the allocator cache itself.  Readings come from torch's allocator (or from the
     injected `probe`, for tests): nothing on the device is configured."""
 
+    @reference_kwargs(high_watermark_fraction="high", critical_watermark_fraction="critical")
     def __init__(self, device: torch.device | str | None = None, high: float = 0.85, critical: float = 0.95,
                  probe: Callable[[], tuple[int, int]] | None = None):
         self.device = torch.device(device) if device is not None else None
@@ -413,6 +427,7 @@ class MemoryPressureMonitor:
 class HierarchicalAllReduceManager:
     """intra-node reduce -> inter-node all-reduce among node leaders -> intra-node broadcast."""
 
+    @reference_kwargs({"global_group": (None,)})     # the hierarchy is always built over the default (world) group
     def __init__(self, local_world: int | None = None):
         self.world, self.rank = dist.get_world_size(), dist.get_rank()
         self.local_world = local_world or int(os.environ.get("LOCAL_WORLD_SIZE", self.world))
@@ -528,10 +543,15 @@ class SOTADDPEngine:
 
 class DDPInitializer:
     @staticmethod
-    def init_process_group(backend: str = "nccl", timeout_seconds: int = 1800) -> Result:
-        """env:// rendezvous from torchrun variables. NCCL debug output is enabled by DDP_DEBUG=1."""
+    def init_process_group(backend: str = "nccl", timeout_seconds: int = 1800, init_method: str | None = None,
+                           world_size: int | None = None, rank: int | None = None,
+                           timeout_minutes: float | None = None) -> Result:
+        """env:// rendezvous from torchrun variables (or `init_method` with explicit `world_size` / `rank`). NCCL debug
+        output is enabled by DDP_DEBUG=1.  `timeout_minutes` is the reference's unit for the same limit."""
         if dist.is_initialized():
             return Ok(dist.get_world_size())
+        if timeout_minutes is not None:
+            timeout_seconds = int(timeout_minutes * 60)
         try:
             if backend == "nccl" and not torch.cuda.is_available():
                 backend = "gloo"
@@ -544,6 +564,12 @@ class DDPInitializer:
                 lr = int(os.environ.get("LOCAL_RANK", "0"))
                 torch.cuda.set_device(lr)
                 kw["device_id"] = torch.device("cuda", lr)
+            if init_method:
+                kw["init_method"] = init_method
+            if world_size is not None:
+                kw["world_size"] = int(world_size)
+            if rank is not None:
+                kw["rank"] = int(rank)
             dist.init_process_group(backend, timeout=datetime.timedelta(seconds=timeout_seconds), **kw)
             return Ok(dist.get_world_size())
         except Exception as e:   # noqa: BLE001

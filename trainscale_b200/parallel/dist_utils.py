@@ -61,7 +61,9 @@ class DistributedState:
                    int(e.get("LOCAL_WORLD_SIZE", e.get("WORLD_SIZE", 1))), DistributedBackend.auto_detect().value)
 
     @classmethod
-    def initialize(cls, backend: str | None = None, timeout_s: int = 1800) -> "DistributedState":
+    def initialize(cls, backend: str | None = None, timeout_s: int = 1800, init_method: str | None = None
+                   ) -> "DistributedState":
+        """`init_method`: torch's rendezvous URL (default: env://, i.e. MASTER_ADDR / MASTER_PORT)."""
         st = cls.from_environment()
         if backend:
             st.backend = backend
@@ -73,6 +75,8 @@ class DistributedState:
                 configure_nccl_environment()
                 torch.cuda.set_device(st.local_rank)
                 kw["device_id"] = torch.device("cuda", st.local_rank)
+            if init_method:
+                kw["init_method"] = init_method
             dist.init_process_group(st.backend, rank=st.rank, world_size=st.world_size,
                                     timeout=datetime.timedelta(seconds=timeout_s), **kw)
             st.initialized_here = True
@@ -164,8 +168,10 @@ class NanoTimer:
     """Device timer: `with timer("fwd"):` records two CUDA events; durations are read by `flush()` for events that
     have completed (no synchronisation)."""
 
-    def __init__(self):
-        self.cuda = torch.cuda.is_available()
+    def __init__(self, name: str = "", use_cuda: bool | None = None):
+        """`name`: default label of `start()` / `stop()` spans; `use_cuda=False` forces the host clock."""
+        self.name = name
+        self.cuda = torch.cuda.is_available() if use_cuda is None else (bool(use_cuda) and torch.cuda.is_available())
         self.pending: list[tuple[str, object, object]] = []
         self.totals: dict[str, float] = {}
         self.counts: dict[str, int] = {}
@@ -614,8 +620,11 @@ class GradientSynchronizer:
     """`with sync.accumulate(step):` suppresses the engine's gradient reduction except on the last micro-batch of an
     accumulation window (data_pipeline/trainer/distributed/__init__.py GradientSynchronizer)."""
 
-    def __init__(self, engine, accumulation_steps: int = 1):
-        self.engine, self.steps = engine, max(1, accumulation_steps)
+    @reference_kwargs({"async_sync": ANY}, model="engine")
+    def __init__(self, engine, accumulation_steps: int = 1, bucket_size_mb: float = 25.0):
+        """`engine`: a sharded / DDP engine, or a plain module (`model=`), whose gradients `sync_gradients()` then
+        reduces in buckets of `bucket_size_mb`."""
+        self.engine, self.steps, self.bucket_size_mb = engine, max(1, accumulation_steps), bucket_size_mb
 
     def should_sync(self, micro_step: int) -> bool:
         return (micro_step + 1) % self.steps == 0
@@ -657,11 +666,17 @@ class DistributedManager:
 
     _instance: "DistributedManager | None" = None
 
-    def __new__(cls):
+    def __new__(cls, config=None):
         if cls._instance is None:
             cls._instance = super().__new__(cls)
             cls._instance.state = None
+            cls._instance.config = None
+        if config is not None:
+            cls._instance.config = config          # a distributed configuration (backend, timeout_seconds, ...)
         return cls._instance
+
+    def __init__(self, config=None):
+        pass
 
     @classmethod
     def get_instance(cls) -> "DistributedManager":
@@ -676,9 +691,12 @@ class DistributedManager:
             dist.destroy_process_group()
         self.state = None
 
-    def init_process_group(self, backend: str | None = None) -> "DistributedState":
-        self.state = DistributedState.from_environment()
-        self.state.initialize(backend)
+    def init_process_group(self, backend: str | None = None, init_method: str | None = None) -> "DistributedState":
+        cfg = getattr(self, "config", None)
+        get = (cfg.get if isinstance(cfg, dict) else (lambda k, d=None: getattr(cfg, k, d))) if cfg is not None else \
+            (lambda k, d=None: d)
+        backend = backend or getattr(get("backend"), "value", get("backend"))
+        self.state = DistributedState.initialize(backend, int(get("timeout_seconds", 1800) or 1800), init_method)
         return self.state
 
     @property
@@ -699,18 +717,25 @@ class DistributedManager:
         return FlatShardedEngine(model, EngineConfig(sharding_strategy=sharding, param_dtype=p.dtype, **engine_kwargs),
                                  device=p.device)
 
-    def all_reduce(self, t: torch.Tensor, op: str = "sum", group=None) -> torch.Tensor:
+    @reference_kwargs({"async_op": (False, None)}, tensor="t")
+    def all_reduce(self, t: torch.Tensor, op="sum", group=None) -> torch.Tensor:
         return dist_reduce(t, op, group)
 
+    @reference_kwargs({"async_op": (False, None)}, tensor="t")
     def all_gather(self, t: torch.Tensor, group=None) -> list[torch.Tensor]:
         return dist_all_gather(t, group)
 
+    @reference_kwargs(tensor="t")
     def broadcast(self, t: torch.Tensor, src: int = 0, group=None) -> torch.Tensor:
         if dist.is_initialized() and dist.get_world_size(group) > 1:
             dist.broadcast(t, src, group=group)
         return t
 
-    def reduce_dict(self, d: dict, average: bool = True, group=None) -> dict:
+    @reference_kwargs(values="d")
+    def reduce_dict(self, d: dict, average: bool = True, group=None, op: str | None = None) -> dict:
+        """`op`: "mean" / "sum" (the reference's argument) instead of `average`."""
+        if op is not None:
+            average = str(getattr(op, "value", op)).lower() in ("mean", "avg", "average")
         if not dist.is_initialized() or dist.get_world_size(group) == 1:
             return dict(d)
         keys = sorted(d)
@@ -758,9 +783,15 @@ _scale_grads_by_token_count = scale_grads_by_token_count
 class DeviceManager:
     """Which device this process uses and what it can do (read-only queries)."""
 
-    def __init__(self, local_rank: int | None = None):
+    @reference_kwargs(device_id="local_rank")
+    def __init__(self, local_rank: int | None = None, device_type: str | None = None):
+        """`device_type`: "cuda" | "cpu" | None (auto); asking for "cuda" without one raises DeviceNotAvailableError."""
         self.local_rank = int(os.environ.get("LOCAL_RANK", "0")) if local_rank is None else local_rank
-        self.cuda = torch.cuda.is_available()
+        dt = getattr(device_type, "value", device_type)
+        if dt in ("cuda", "gpu") and not torch.cuda.is_available():
+            from ..core.errors import DeviceNotAvailableError
+            raise DeviceNotAvailableError("no CUDA device is visible", device_type="cuda", available_devices=("cpu",))
+        self.cuda = torch.cuda.is_available() and dt not in ("cpu",)
 
     @property
     def device(self) -> torch.device:
@@ -845,6 +876,7 @@ class HardwareTopology:
 class DistributedLogger:
     """Rank-aware logging: by default only rank 0 emits; `all_ranks=True` prefixes every line with the rank."""
 
+    @reference_kwargs(verbose_all_ranks="all_ranks")
     def __init__(self, name: str = "trainscale_b200", all_ranks: bool = False, level: int = logging.INFO):
         self._log = logging.getLogger(name)
         self._log.setLevel(level)
@@ -861,8 +893,12 @@ class DistributedLogger:
         elif r == 0:
             self._log.log(level, msg, *a)
 
+    @reference_kwargs(message="msg")
+
     def info(self, msg: str, *a) -> None:
         self._emit(logging.INFO, msg, *a)
+
+    @reference_kwargs(message="msg")
 
     def warning(self, msg: str, *a) -> None:
         self._emit(logging.WARNING, msg, *a)
@@ -872,8 +908,12 @@ class DistributedLogger:
         import time
         self._emit(logging.INFO, "METRIC|%d|%s|%s|%s|rank=%d", time.time_ns(), name, value, unit, self._rank())
 
+    @reference_kwargs(message="msg")
+
     def error(self, msg: str, *a) -> None:          # errors are never silenced
         self._log.error(f"[rank {self._rank()}] {msg}", *a)
+
+    @reference_kwargs(message="msg")
 
     def debug(self, msg: str, *a) -> None:
         self._emit(logging.DEBUG, msg, *a)

@@ -22,6 +22,8 @@ import torch
 import torch.distributed as dist
 import torch.nn as nn
 
+from ..utils.refargs import ANY, reference_kwargs
+
 from ..core.types import Err, Ok, Result
 from .flat_engine import EngineConfig, FlatShardedEngine
 
@@ -154,8 +156,11 @@ class MemoryPool:
     """Recycles device buffers by power-of-two size class so that the per-layer gather / reduce buffers of a step
     never go back to the caching allocator (fsdp2.py:463-586 keeps the same interface)."""
 
-    def __init__(self, device: torch.device | str = "cpu", max_cached_bytes: int = 8 * 2 ** 30):
+    def __init__(self, device: torch.device | str = "cpu", max_cached_bytes: int = 8 * 2 ** 30,
+                 dtype: torch.dtype | None = None):
+        """`dtype`: default element type of `allocate` (bf16 when not given)."""
         self.device = torch.device(device)
+        self.default_dtype = dtype or torch.bfloat16
         self.max_cached_bytes = max_cached_bytes
         self._free: dict[tuple[int, torch.dtype], list[torch.Tensor]] = {}
         self._out: dict[int, tuple[int, torch.dtype]] = {}
@@ -166,7 +171,16 @@ class MemoryPool:
     def _bucket_size(numel: int) -> int:
         return 1 << max(9, (max(1, numel) - 1).bit_length())
 
-    def allocate(self, numel: int, dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    def allocate(self, numel: "int | tuple" = None, dtype: torch.dtype | None = None, *, shape=None) -> torch.Tensor:
+        """A flat buffer of `numel` elements; with a shape (`shape=`, or a tuple in the first position) the buffer is
+        viewed in that shape.  `free` takes either form back."""
+        shape = shape if shape is not None else (tuple(numel) if isinstance(numel, (tuple, list, torch.Size)) else None)
+        if shape is not None:
+            n = 1
+            for d in shape:
+                n *= int(d)
+            return self.allocate(n, dtype).view(tuple(shape))
+        dtype = dtype or getattr(self, "default_dtype", torch.bfloat16)
         key = (self._bucket_size(numel), dtype)
         lst = self._free.get(key)
         if lst:
@@ -205,6 +219,7 @@ class StreamManager:
     """Named side streams (all-gather, reduce-scatter, host transfer) next to the compute stream, with the event
     hand-offs between them.  On a CPU device every accessor returns None and the syncs are no-ops."""
 
+    @reference_kwargs({"is_amd": (False, None)})
     def __init__(self, device: torch.device | str):
         self.device = torch.device(device)
         self._cuda = self.device.type == "cuda"
@@ -226,6 +241,8 @@ class StreamManager:
     @property
     def transfer(self):
         return self._transfer
+
+    @reference_kwargs(dst="waiter", src="producer")
 
     def sync_stream_to(self, waiter, producer) -> None:
         if self._cuda and waiter is not None and producer is not None:
@@ -348,8 +365,11 @@ class MetricsCollector:
     """Phase timers that never block the host: on CUDA a phase records an event pair and the elapsed time is read
     at the NEXT `record_step` (after the events have certainly completed); on CPU a wall clock is used."""
 
-    def __init__(self, device: torch.device | str = "cpu", history: int = 1000, enabled: bool = True):
-        self.device = torch.device(device)
+    @reference_kwargs(max_history="history")
+    def __init__(self, device: torch.device | str = "cpu", history: int = 1000, enabled: bool = True,
+                 enable_gpu_timing: bool = True):
+        """`enable_gpu_timing=False`: phases are timed on the host clock even on a GPU."""
+        self.device = torch.device(device) if enable_gpu_timing else torch.device("cpu")
         self.enabled = enabled
         self._cur = FSDPMetrics()
         self._hist: deque[dict] = deque(maxlen=history)
@@ -432,7 +452,14 @@ class GradientAccumulator:
     """fp32 side buffers that sum micro-batch gradients of a plain model (the engine accumulates in its own flat
     buffers; this class serves models trained without it)."""
 
-    def __init__(self, accumulation_steps: int = 1, dtype: torch.dtype = torch.float32):
+    def __init__(self, accumulation_steps: "int | nn.Module" = 1, dtype: torch.dtype = torch.float32, *, model=None,
+                 use_triton: bool = False, block_size: int | None = None):
+        """`GradientAccumulator(model, accumulation_steps)` is the reference's order: the model is kept as
+        `self.model` (the methods still take it explicitly); `use_triton` / `block_size` have no counterpart here."""
+        if isinstance(accumulation_steps, nn.Module):
+            model, accumulation_steps = accumulation_steps, (dtype if isinstance(dtype, int) else 1)
+            dtype = torch.float32 if isinstance(dtype, int) else dtype
+        self.model = model
         self.accumulation_steps = max(1, accumulation_steps)
         self.dtype = dtype
         self._step = 0
@@ -645,6 +672,8 @@ class SOTAFSDP2:
             # always a copy: under FULL_SHARD the full buffers are released again when this block ends
             sd = {k: (v.cpu() if cpu_offload and v.is_cuda else v.clone()) for k, v in sd.items()}
         return {"model": sd if (full_state_dict or self._world_size == 1) else {}, "optimizer": self.engine.state_dict()}
+
+    @reference_kwargs(state_dict="state")
 
     def load_state_dict(self, state: dict[str, Any], strict: bool = True) -> None:
         m = self._wrapped_model
