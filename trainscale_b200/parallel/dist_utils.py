@@ -893,13 +893,13 @@ class DistributedLogger:
         elif r == 0:
             self._log.log(level, msg, *a)
 
-    @reference_kwargs(message="msg")
 
+    @reference_kwargs(message="msg")
     def info(self, msg: str, *a) -> None:
         self._emit(logging.INFO, msg, *a)
 
-    @reference_kwargs(message="msg")
 
+    @reference_kwargs(message="msg")
     def warning(self, msg: str, *a) -> None:
         self._emit(logging.WARNING, msg, *a)
 
@@ -908,13 +908,13 @@ class DistributedLogger:
         import time
         self._emit(logging.INFO, "METRIC|%d|%s|%s|%s|rank=%d", time.time_ns(), name, value, unit, self._rank())
 
-    @reference_kwargs(message="msg")
 
+    @reference_kwargs(message="msg")
     def error(self, msg: str, *a) -> None:          # errors are never silenced
         self._log.error(f"[rank {self._rank()}] {msg}", *a)
 
-    @reference_kwargs(message="msg")
 
+    @reference_kwargs(message="msg")
     def debug(self, msg: str, *a) -> None:
         self._emit(logging.DEBUG, msg, *a)
 

@@ -242,8 +242,8 @@ class StreamManager:
     def transfer(self):
         return self._transfer
 
-    @reference_kwargs(dst="waiter", src="producer")
 
+    @reference_kwargs(dst="waiter", src="producer")
     def sync_stream_to(self, waiter, producer) -> None:
         if self._cuda and waiter is not None and producer is not None:
             ev = torch.cuda.Event()
@@ -673,8 +673,8 @@ class SOTAFSDP2:
             sd = {k: (v.cpu() if cpu_offload and v.is_cuda else v.clone()) for k, v in sd.items()}
         return {"model": sd if (full_state_dict or self._world_size == 1) else {}, "optimizer": self.engine.state_dict()}
 
-    @reference_kwargs(state_dict="state")
 
+    @reference_kwargs(state_dict="state")
     def load_state_dict(self, state: dict[str, Any], strict: bool = True) -> None:
         m = self._wrapped_model
         if state.get("model"):

@@ -198,10 +198,74 @@ for _n in ("copy_to_tensor_parallel_region", "reduce_from_tensor_parallel_region
 
 
 # ------------------------------------------------------------------------------------------------ layers
+def _tp_ctor(third: str, **renames):
+    """Constructor adapter of the tensor-parallel layers.  This framework passes the parallel context explicitly as
+    the third argument (`Layer(in, out, tp, ...)`); the reference keeps it in process-global state and its third
+    positional parameter is something else (`third`).  With this adapter a layer can be built either way: when no
+    `TPContext` is given, the context of the registered tensor-parallel group is used (`tensor_parallel_context`), and
+    the reference's options are honoured: `sequence_parallel` (a switch of the context), `init_method(weight)` (run on
+    every weight of the layer after construction), `skip_bias_add` (refused: the bias is always added here), plus
+    per-class keyword `renames`."""
+    import dataclasses
+    import functools
+    import inspect
+
+    def deco(init):
+        sig = inspect.signature(init)
+
+        @functools.wraps(init)
+        def wrapper(self, *args, init_method=None, skip_bias_add=False, sequence_parallel=None, **kw):
+            if skip_bias_add:
+                raise NotImplementedError("skip_bias_add is not supported: the bias is added inside the layer")
+            for ref, ours in renames.items():
+                if ref in kw:
+                    kw[ours] = kw.pop(ref)
+            args = list(args)
+            given = kw.get("tp") if "tp" in kw else (args[2] if len(args) >= 3 and isinstance(args[2], TPContext) else None)
+            if given is None:
+                if len(args) > 3:
+                    raise TypeError("without a TPContext, pass the options after the third argument by keyword")
+                if len(args) == 3:
+                    kw[third] = args.pop()
+                given = _default_tp()
+                kw["tp"] = given
+            if sequence_parallel is not None and bool(sequence_parallel) != given.sequence_parallel:
+                new = dataclasses.replace(given, sequence_parallel=bool(sequence_parallel))
+                if "tp" in kw:
+                    kw["tp"] = new
+                else:
+                    args[2] = new
+            init(self, *args, **kw)
+            if init_method is not None:
+                with torch.no_grad():
+                    for n, p in self.named_parameters():
+                        if n.endswith("weight") and p.dim() > 1:
+                            init_method(p)
+
+        params = [p.replace(default=None) if p.name == "tp" else p for p in sig.parameters.values()]
+        # keep a valid ordering: parameters after `tp` need defaults too for inspection purposes only
+        fixed, seen_default = [], False
+        for p in params:
+            if p.kind in (p.POSITIONAL_ONLY, p.POSITIONAL_OR_KEYWORD):
+                if p.default is not p.empty:
+                    seen_default = True
+                elif seen_default:
+                    p = p.replace(default=None)
+            fixed.append(p)
+        tail = [p for p in fixed if p.kind is inspect.Parameter.VAR_KEYWORD]
+        head = [p for p in fixed if p.kind is not inspect.Parameter.VAR_KEYWORD]
+        extra = [inspect.Parameter(n, inspect.Parameter.KEYWORD_ONLY, default=None)
+                 for n in ("init_method", "skip_bias_add", "sequence_parallel", *renames) if n not in sig.parameters]
+        wrapper.__signature__ = sig.replace(parameters=head + extra + tail)
+        return wrapper
+    return deco
+
+
 class ColumnParallelLinear(nn.Module):
     """y_local = x W_local^T with W split along the output dim. With SP the input tokens are all-gathered first
     (fused into the GEMM on the `fused` back-end)."""
 
+    @_tp_ctor("bias")
     def __init__(self, in_features: int, out_features: int, tp: TPContext, bias: bool = False, gather_output=False,
                  dtype=None, device=None):
         super().__init__()
@@ -212,6 +276,8 @@ class ColumnParallelLinear(nn.Module):
         self.bias = nn.Parameter(torch.zeros(out_features // tp.size, dtype=dtype, device=device)) if bias else None
         nn.init.normal_(self.weight, std=0.02)
 
+
+    @reference_kwargs(input_="x")
     def forward(self, x):
         tp = self.tp
         if tp.active and tp.sequence_parallel:
@@ -231,6 +297,7 @@ class RowParallelLinear(nn.Module):
     """y = sum_r x_r W_r^T with W split along the input dim; the partial sums are all-reduced, or reduce-scattered
     over tokens with SP (fused into the GEMM epilogue on the `fused` back-end)."""
 
+    @_tp_ctor("bias")
     def __init__(self, in_features: int, out_features: int, tp: TPContext, bias: bool = False, input_is_parallel=True,
                  dtype=None, device=None):
         super().__init__()
@@ -240,6 +307,8 @@ class RowParallelLinear(nn.Module):
         self.bias = nn.Parameter(torch.zeros(out_features, dtype=dtype, device=device)) if bias else None
         nn.init.normal_(self.weight, std=0.02)
 
+
+    @reference_kwargs(input_="x")
     def forward(self, x):
         tp = self.tp
         if not self.input_is_parallel:
@@ -255,7 +324,10 @@ class RowParallelLinear(nn.Module):
 
 
 class VocabParallelEmbedding(nn.Module):
-    def __init__(self, num_embeddings: int, embedding_dim: int, tp: TPContext, dtype=None, device=None):
+    @_tp_ctor("padding_idx")
+    def __init__(self, num_embeddings: int, embedding_dim: int, tp: TPContext, dtype=None, device=None,
+                 padding_idx: int | None = None):
+        """`padding_idx`: that token's row is zero and receives no gradient (on the rank that owns it)."""
         super().__init__()
         self.tp = tp
         self.num_embeddings = num_embeddings
@@ -263,13 +335,20 @@ class VocabParallelEmbedding(nn.Module):
         self.start, self.end = tp.rank * per, min(num_embeddings, (tp.rank + 1) * per)
         self.weight = nn.Parameter(torch.empty(per, embedding_dim, dtype=dtype, device=device))
         nn.init.normal_(self.weight, std=0.02)
+        self.padding_idx = padding_idx
+        self._local_pad = padding_idx - self.start if padding_idx is not None and self.start <= padding_idx < self.end \
+            else None
+        if self._local_pad is not None:
+            with torch.no_grad():
+                self.weight[self._local_pad].zero_()
 
+    @reference_kwargs(input_="ids")
     def forward(self, ids):
         if not self.tp.active:
-            return F.embedding(ids, self.weight)
+            return F.embedding(ids, self.weight, padding_idx=self._local_pad)
         mask = (ids < self.start) | (ids >= self.end)
         local = (ids - self.start).masked_fill(mask, 0)
-        out = F.embedding(local, self.weight).masked_fill(mask.unsqueeze(-1), 0.0)
+        out = F.embedding(local, self.weight, padding_idx=self._local_pad).masked_fill(mask.unsqueeze(-1), 0.0)
         return reduce_from_tensor_parallel_region(out, self.tp)
 
 
@@ -557,17 +636,22 @@ class ParallelEmbedding(nn.Module):
     """Embedding table split along the HIDDEN dimension: every rank looks up all tokens in its slice of columns and the
     slices are all-gathered (no masking needed, unlike the vocabulary split)."""
 
+    @_tp_ctor("padding_idx")
     def __init__(self, num_embeddings: int, embedding_dim: int, tp: TPContext, gather_output: bool = True,
-                 dtype=None, device=None):
+                 dtype=None, device=None, padding_idx: int | None = None):
         super().__init__()
         assert embedding_dim % tp.size == 0, "embedding_dim must divide by the TP size"
-        self.tp, self.gather_output = tp, gather_output
+        self.tp, self.gather_output, self.padding_idx = tp, gather_output, padding_idx
         self.num_embeddings, self.embedding_dim = num_embeddings, embedding_dim
         self.weight = nn.Parameter(torch.empty(num_embeddings, embedding_dim // tp.size, dtype=dtype, device=device))
         nn.init.normal_(self.weight, std=0.02)
+        if padding_idx is not None:
+            with torch.no_grad():
+                self.weight[padding_idx].zero_()
 
+    @reference_kwargs(input_="ids")
     def forward(self, ids):
-        out = F.embedding(ids, self.weight)
+        out = F.embedding(ids, self.weight, padding_idx=self.padding_idx)
         return gather_from_tensor_parallel_region(out, self.tp) if self.gather_output else out
 
 
@@ -576,15 +660,28 @@ class SequenceParallelLayerNorm(nn.Module):
     each rank sees only 1/tp of the tokens, so their gradients must be summed over the group: the parameters carry
     `sequence_parallel = True` and `allreduce_sequence_parallel_grads` picks them up."""
 
-    def __init__(self, hidden_size: int, eps: float = 1e-5, rms: bool = True, bias: bool = False, dtype=None,
-                 device=None):
+    def __init__(self, hidden_size: int | None = None, eps: float = 1e-5, rms: bool | None = None, bias: bool | None = None,
+                 dtype=None, device=None, *, normalized_shape=None, elementwise_affine: bool = True,
+                 sequence_parallel: bool = True):
+        """`SequenceParallelLayerNorm(hidden_size)` is an RMSNorm (this framework's decoders use nothing else).  Built with
+        the reference's `normalized_shape=` it is a LayerNorm with bias, as there
+        (data_pipeline/trainer/distributed/tensor_parallel.py, SequenceParallelLayerNorm); `rms` / `bias` override either.
+        `sequence_parallel=False` leaves the parameters unmarked (their gradients are then not summed over the group)."""
+        if not elementwise_affine:
+            raise NotImplementedError("a norm without weights has nothing to synchronise: use torch's functional norm")
+        ref_form = normalized_shape is not None
+        if ref_form:
+            hidden_size = normalized_shape if isinstance(normalized_shape, int) else tuple(normalized_shape)[-1]
+        rms = (not ref_form) if rms is None else rms
+        bias = ref_form if bias is None else bias
         super().__init__()
         self.eps, self.rms = eps, rms
         self.weight = nn.Parameter(torch.ones(hidden_size, dtype=dtype, device=device))
         self.bias = nn.Parameter(torch.zeros(hidden_size, dtype=dtype, device=device)) if (bias and not rms) else None
         for p in self.parameters():
-            p.sequence_parallel = True
+            p.sequence_parallel = bool(sequence_parallel)
 
+    @reference_kwargs(input_="x")
     def forward(self, x):
         from ..ops import norm as N
         if self.rms:
@@ -596,9 +693,11 @@ class ParallelMLP(nn.Module):
     """Column-parallel up (gate|up for gated activations) -> activation -> row-parallel down: one collective per
     direction (all-reduce, or all-gather + reduce-scatter of tokens with sequence parallelism)."""
 
+    @_tp_ctor("activation", use_gated="gated")
     def __init__(self, hidden_size: int, intermediate_size: int, tp: TPContext, gated: bool = True,
-                 activation: str = "silu", bias: bool = False, dtype=None, device=None):
+                 activation: str = "silu", bias: bool = False, dtype=None, device=None, dropout_prob: float = 0.0):
         super().__init__()
+        self.dropout = nn.Dropout(dropout_prob) if dropout_prob else None
         self.tp, self.gated, self.activation = tp, gated, activation
         self.up = ColumnParallelLinear(hidden_size, intermediate_size, tp, bias, dtype=dtype, device=device)
         self.gate = ColumnParallelLinear(hidden_size, intermediate_size, tp, bias, dtype=dtype, device=device) \
@@ -608,18 +707,23 @@ class ParallelMLP(nn.Module):
     def _act(self, x):
         return {"silu": F.silu, "gelu": F.gelu, "relu": F.relu}[self.activation](x)
 
+    @reference_kwargs(hidden_states="x")
     def forward(self, x):
         h = self._act(self.gate(x)) * self.up(x) if self.gated else self._act(self.up(x))
-        return self.down(h)
+        y = self.down(h)
+        return self.dropout(y) if getattr(self, "dropout", None) is not None else y
 
 
 class ParallelSelfAttention(nn.Module):
     """Heads split over the tensor group: column-parallel q / k / v (grouped-query: kv heads split too), local causal
     attention over this rank's heads, row-parallel output projection."""
 
+    @_tp_ctor("num_kv_heads", num_attention_heads="num_heads", num_key_value_heads="num_kv_heads")
     def __init__(self, hidden_size: int, num_heads: int, tp: TPContext, num_kv_heads: int | None = None,
                  head_dim: int | None = None, causal: bool = True, rope_theta: float | None = 10000.0, bias: bool = False,
-                 dtype=None, device=None):
+                 dtype=None, device=None, attention_dropout: float = 0.0):
+        if attention_dropout:
+            raise NotImplementedError("attention dropout is not supported by the attention kernels")
         super().__init__()
         kv = num_kv_heads or num_heads
         assert num_heads % tp.size == 0 and kv % tp.size == 0, "heads must divide by the TP size"
@@ -641,8 +745,11 @@ class ParallelSelfAttention(nn.Module):
         x1, x2 = x.float()[..., : D // 2], x.float()[..., D // 2:]
         return torch.cat((x1 * cos - x2 * sin, x2 * cos + x1 * sin), -1).to(x.dtype)
 
+    @reference_kwargs({"attention_mask": (None,), "position_embeddings": (None,)}, hidden_states="x")
     def forward(self, x):
-        """x: [B, S, H] (with sequence parallelism [B, S/tp, H]; B must be 1 there, tokens are the sharded axis)."""
+        """x: [B, S, H] (with sequence parallelism [B, S/tp, H]; B must be 1 there, tokens are the sharded axis).
+        Masking is causal (or none) as configured and rotary positions are computed inside: an explicit
+        `attention_mask` / `position_embeddings` is refused."""
         tp = self.tp
         sp = tp.active and tp.sequence_parallel
         B = x.shape[0]
@@ -769,13 +876,18 @@ class FusedColumnParallelLinearWithGELU(nn.Module):
 
     def __init__(self, in_features: int, out_features: int, tp: TPContext | None = None, *, bias: bool = True,
                  gather_output: bool = False, sequence_parallel: bool = False, approximate: str = "tanh", dtype=None,
-                 device=None):
+                 device=None, init_method=None):
         super().__init__()
         tp = tp if tp is not None else _mgr().tp_context(sequence_parallel)
         self.linear = ColumnParallelLinear(in_features, out_features, tp, bias=bias, gather_output=False, dtype=dtype,
                                            device=device)
+        if init_method is not None:
+            with torch.no_grad():
+                init_method(self.linear.weight)
         self.gather_output, self.approximate = gather_output, approximate
 
+
+    @reference_kwargs(input_="x")
     def forward(self, x):
         from ..ops import activation
         y = activation.gelu(self.linear(x), self.approximate)
@@ -788,13 +900,15 @@ class FusedRowParallelLinearWithDropout(nn.Module):
 
     def __init__(self, in_features: int, out_features: int, tp: TPContext | None = None, *, bias: bool = True,
                  input_is_parallel: bool = True, sequence_parallel: bool = False, dropout_prob: float = 0.0, dtype=None,
-                 device=None):
+                 device=None, init_method=None):
         super().__init__()
         tp = tp if tp is not None else _mgr().tp_context(sequence_parallel)
         self.linear = RowParallelLinear(in_features, out_features, tp, bias=bias, input_is_parallel=input_is_parallel,
-                                        dtype=dtype, device=device)
+                                        dtype=dtype, device=device, init_method=init_method)
         self.dropout_prob = dropout_prob
 
+
+    @reference_kwargs(input_="x")
     def forward(self, x):
         y = self.linear(x)
         return torch.nn.functional.dropout(y, self.dropout_prob, self.training) if self.dropout_prob > 0 else y
