@@ -553,8 +553,24 @@ class ProcessGroupManager:
             cls._instance = cls()
         return cls._instance
 
-    def initialize(self, tensor_parallel_size: int = 1, pipeline_parallel_size: int = 1) -> "ProcessGroupManager":
-        """Collective over the whole job."""
+    def initialize(self, tensor_parallel_size: "int | TensorParallelConfig" = 1, pipeline_parallel_size: int = 1, *,
+                   config=None, rank: int | None = None, world_size: int | None = None, backend: str | None = None
+                   ) -> "ProcessGroupManager":
+        """Collective over the whole job.  `initialize(config, rank, world_size, backend)` is the reference's form: the
+        sizes come from the `TensorParallelConfig`; rank / world size / backend are those of the running process group
+        (they are checked against it when given, never used to create one)."""
+        cfg = config if config is not None else (tensor_parallel_size if not isinstance(tensor_parallel_size, int) else None)
+        if cfg is not None:
+            self.config = cfg
+            if isinstance(pipeline_parallel_size, int) and rank is None and config is None and pipeline_parallel_size != 1:
+                rank, pipeline_parallel_size = pipeline_parallel_size, 1          # positional (config, rank, ...)
+            tensor_parallel_size = int(getattr(cfg, "tensor_parallel_size", 1))
+            pipeline_parallel_size = int(getattr(cfg, "pipeline_parallel_size", pipeline_parallel_size))
+        if dist.is_available() and dist.is_initialized():
+            if world_size is not None and int(world_size) != dist.get_world_size():
+                raise ValueError(f"world_size={world_size} but the process group has {dist.get_world_size()} ranks")
+            if rank is not None and int(rank) != dist.get_rank():
+                raise ValueError(f"rank={rank} but this process is rank {dist.get_rank()}")
         from .dist_kernels import create_process_groups
         self.tp_size, self.pp_size = tensor_parallel_size, pipeline_parallel_size
         if dist.is_available() and dist.is_initialized():
@@ -618,7 +634,14 @@ class ProcessGroupManager:
             streams[key] = torch.cuda.Stream()
         return streams[key]
 
-    def acquire_buffer(self, shape, dtype=torch.float32, device=None) -> torch.Tensor:
+    def acquire_buffer(self, shape=None, dtype=torch.float32, device=None, *, numel: int | None = None) -> torch.Tensor:
+        """A pooled scratch tensor of `shape` (or flat, of `numel` elements; `acquire_buffer(dtype, numel)` is the
+        reference's order)."""
+        if isinstance(shape, torch.dtype):
+            shape, dtype = (dtype if isinstance(dtype, int) else numel), shape
+        if shape is None:
+            shape = numel
+        shape = (int(shape),) if isinstance(shape, int) else tuple(shape)
         from .dist_utils import TensorPool
         pools = self.__dict__.setdefault("_pools", {})
         dev = torch.device(device) if device is not None else (
@@ -627,6 +650,7 @@ class ProcessGroupManager:
             pools[dev] = TensorPool(dev)
         return pools[dev].acquire(shape, dtype)
 
+    @reference_kwargs(buffer="tensor")
     def release_buffer(self, tensor: torch.Tensor) -> None:
         for pool in self.__dict__.get("_pools", {}).values():
             pool.release(tensor)
