@@ -294,3 +294,52 @@ def test_data_and_serving_function_forms():
     cfg.cache.num_gpu_blocks = 32
     app = create_openai_server(cfg, "127.0.0.1", port=8123)
     assert (app.state.host, app.state.port) == ("127.0.0.1", 8123)
+
+
+def test_expert_parallel_blocks_take_the_reference_forms():
+    """Routers return the dense routing record for `hidden_states=`; experts take activation / dropout / use_gated; the
+    layers return (output, auxiliary loss, router logits); padded tokens are routed nowhere."""
+    import warnings
+    from trainscale_b200.parallel.ep import (AllToAllDispatcher, ExpertChoiceRouter, ExpertFFN, ExpertParallelConfig,
+                                             ExpertParallelMoE, GroupedExperts, HierarchicalMoE, MoELayer, SoftMoERouter,
+                                             TopKRouter)
+    warnings.simplefilter("ignore")
+    cfg = ExpertParallelConfig(num_experts=4, top_k=2, hidden_size=16, intermediate_size=32)
+    torch.manual_seed(0)
+    x = torch.randn(2, 5, 16)
+    flat = x.reshape(-1, 16)
+    pad = torch.zeros(2, 5, dtype=torch.bool)
+    pad[1, 3:] = True
+    out = TopKRouter(config=cfg)(hidden_states=x, padding_mask=pad)
+    assert out.dispatch_mask.shape[:2] == (10, 4) and out.dispatch_mask[8:].sum() == 0
+    assert abs(float(out.combine_weights.sum()) - 8.0) < 1e-4            # 8 live tokens, weights of a token sum to 1
+    assert ExpertChoiceRouter(config=cfg)(hidden_states=x, padding_mask=pad).dispatch_mask[8:].sum() == 0
+    soft = SoftMoERouter(config=cfg)(hidden_states=x, padding_mask=pad)
+    assert torch.allclose(soft.dispatch_mask.sum(0), torch.ones(4, 1), atol=1e-5) and soft.dispatch_mask[8:].abs().sum() == 0
+    plain = ExpertFFN(hidden_size=16, intermediate_size=32, activation="gelu", dropout=0.0, use_gated=False)
+    assert plain.w_gate_up.shape == (32, 16)
+    ref = torch.nn.functional.gelu(flat @ plain.w_gate_up.t()) @ plain.w_down.t()
+    assert torch.allclose(plain(flat), ref, atol=1e-5)
+    assert ExpertFFN(16, 32, "relu", 0.1, True)(x).shape == x.shape
+    with pytest.raises(ValueError):
+        ExpertFFN(16, 32, activation="nope")
+    experts = GroupedExperts(4, hidden_size=16, intermediate_size=32)
+    y = experts(tokens=flat, expert_indices=out.expert_indices, expert_weights=out.expert_weights)
+    assert y.shape == flat.shape and y[8:].abs().sum() == 0              # padded tokens carry zero weights
+    layer = MoELayer(config=cfg)
+    o, aux, logits = layer(hidden_states=x, attention_mask=(~pad).long(), output_router_logits=True)
+    assert o.shape == x.shape and logits.shape == (10, 4) and aux.dim() == 0 and o[1, 3:].abs().sum() == 0
+    assert torch.allclose(layer(x)[0], o[0], atol=1e-6)
+    ep = ExpertParallelMoE(config=cfg)                                    # no process group: every expert is local
+    layer.load_state_dict(ep.state_dict())
+    assert torch.allclose(ep(hidden_states=x)[0], layer(x), atol=1e-6) and ep.get_routing_statistics()["forward_count"] == 1
+    ho, haux = HierarchicalMoE(config=cfg, num_groups=2)(hidden_states=x, attention_mask=(~pad).long())
+    assert ho.shape == x.shape and ho[1, 3:].abs().sum() == 0 and haux.dim() == 0
+    d = AllToAllDispatcher(4, 4, 6, None)
+    mask = torch.zeros(10, 4, dtype=torch.bool).scatter_(1, out.expert_indices, True)
+    rows, counts = d.dispatch(tokens=flat, dispatch_mask=mask)
+    assert rows.shape == (4, 6, 16) and counts.tolist() == mask.sum(0).clamp(max=6).tolist()
+    w = torch.zeros(10, 4).scatter_(1, out.expert_indices, out.expert_weights.detach())
+    kept = (mask.long().cumsum(0) - 1 < 6) & mask
+    back = d.combine(expert_outputs=rows, combine_weights=w, original_positions=torch.arange(10), num_tokens=10)
+    assert torch.allclose(back, flat * (w * kept).sum(1, keepdim=True), atol=1e-5)

@@ -23,6 +23,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from ..ops import activation, gemm
+from ..utils.refargs import reference_kwargs
 
 
 @dataclass
@@ -62,15 +63,57 @@ def moe_capacity(tokens: int, num_experts: int, top_k: int, capacity_factor: flo
 
 
 # ------------------------------------------------------------------------------------------------ routers
+def _dense_routing(cfg, logits, w, idx, aux_loss, padding_mask=None, meta=None):
+    """A top-k decision (weights / experts [T, k], logits [T, E]) as the dense capacity-slotted `RoutingOutput`: slot of
+    a (token, choice) inside its expert = number of earlier slots routed to the same expert; slots past the capacity
+    are dropped; padded tokens (`padding_mask` True) are routed nowhere."""
+    T, E = logits.shape
+    k = idx.shape[1]
+    C = moe_capacity(T, E, k, cfg.capacity_factor, cfg.min_capacity)
+    live = torch.ones(T, dtype=torch.bool, device=logits.device) if padding_mask is None \
+        else ~padding_mask.reshape(-1).to(torch.bool)
+    hot = F.one_hot(idx.reshape(-1), E) * live.repeat_interleave(k)[:, None]        # [T*k, E]
+    slot = (hot.cumsum(0) - hot).gather(1, idx.reshape(-1, 1)).reshape(T, k)
+    keep = (slot < C) & live[:, None]
+    w = w * live[:, None].to(w.dtype)
+    dispatch = torch.zeros(T, E, C, dtype=torch.bool, device=logits.device)
+    combine = torch.zeros(T, E, C, dtype=w.dtype, device=logits.device)
+    t = torch.arange(T, device=logits.device)[:, None].expand_as(idx)
+    dispatch[t[keep], idx[keep], slot[keep]] = True
+    combine[t[keep], idx[keep], slot[keep]] = w[keep]
+    info = {"capacity": C, "dropped": int((~keep & live[:, None]).sum()), "tokens_per_expert": hot.sum(0)}
+    info.update(meta or {})
+    return RoutingOutput(dispatch, combine, idx, w, logits, aux_loss, info)
+
+
+def _aux_total(cfg, aux: dict):
+    total = 0.0
+    if "load_balance" in aux:
+        total = total + cfg.aux_loss_weight * aux["load_balance"]
+    if "z_loss" in aux:
+        total = total + cfg.z_loss_weight * aux["z_loss"]
+    return total if torch.is_tensor(total) else torch.zeros(())
+
+
 class TopKRouter(nn.Module):
+    """`router(x [T, H])` -> (weights, experts, aux dict); `router(hidden_states=[B, S, H], padding_mask=[B, S])` ->
+    the dense `RoutingOutput` (data_pipeline/trainer/distributed/expert_parallel.py:653)."""
+
+    @reference_kwargs(config="cfg")
     def __init__(self, cfg: ExpertParallelConfig, dtype=None, device=None):
         super().__init__()
         self.cfg = cfg
         self.weight = nn.Parameter(torch.empty(cfg.num_experts, cfg.hidden_size, dtype=dtype, device=device))
         nn.init.normal_(self.weight, std=0.02)
 
-    def forward(self, x: torch.Tensor):
+    def forward(self, x: torch.Tensor | None = None, *, hidden_states=None, padding_mask=None):
         """x [T, H] -> (weights [T, k], experts [T, k], aux dict)."""
+        if hidden_states is not None:
+            flat = hidden_states.reshape(-1, hidden_states.shape[-1])
+            w, idx, aux = self.forward(flat)
+            logits = F.linear(flat.float(), self.weight.float())
+            return _dense_routing(self.cfg, logits, w, idx, _aux_total(self.cfg, aux), padding_mask,
+                                  {"importance_cv2": aux["importance_cv2"]})
         cfg = self.cfg
         logits = F.linear(x.float(), self.weight.float())
         if self.training and cfg.jitter > 0:
@@ -88,13 +131,37 @@ class TopKRouter(nn.Module):
 class ExpertChoiceRouter(nn.Module):
     """Each expert picks its top-`capacity` tokens (perfect balance, tokens may get 0..E experts)."""
 
+    @reference_kwargs(config="cfg")
     def __init__(self, cfg: ExpertParallelConfig, dtype=None, device=None):
         super().__init__()
         self.cfg = cfg
         self.weight = nn.Parameter(torch.empty(cfg.num_experts, cfg.hidden_size, dtype=dtype, device=device))
         nn.init.normal_(self.weight, std=0.02)
 
-    def forward(self, x):
+    def forward(self, x=None, *, hidden_states=None, padding_mask=None):
+        """x [T, H] -> (weights [E, cap], tokens [E, cap], aux).  `forward(hidden_states=, padding_mask=)` gives the
+        dense `RoutingOutput` instead: slot c of expert e holds its c-th chosen token
+        (data_pipeline/trainer/distributed/expert_parallel.py:903)."""
+        if hidden_states is not None:
+            flat = hidden_states.reshape(-1, hidden_states.shape[-1])
+            logits = F.linear(flat.float(), self.weight.float())
+            if padding_mask is not None:
+                logits = logits.masked_fill(padding_mask.reshape(-1, 1).to(torch.bool), float("-inf"))
+            probs = torch.softmax(logits, dim=-1).nan_to_num(0.0)
+            T, E = probs.shape
+            cap = min(T, moe_capacity(T, E, self.cfg.top_k, self.cfg.capacity_factor, self.cfg.min_capacity))
+            w, tok = probs.t().topk(cap, dim=-1)                                      # [E, cap]
+            dispatch = torch.zeros(T, E, cap, dtype=torch.bool, device=flat.device)
+            combine = torch.zeros(T, E, cap, dtype=w.dtype, device=flat.device)
+            e = torch.arange(E, device=flat.device)[:, None].expand_as(tok)
+            c = torch.arange(cap, device=flat.device)[None, :].expand_as(tok)
+            live = w > 0
+            dispatch[tok[live], e[live], c[live]] = True
+            combine[tok[live], e[live], c[live]] = w[live]
+            k = min(self.cfg.top_k, E)
+            tw, ti = combine.sum(-1).topk(k, dim=-1)
+            return RoutingOutput(dispatch, combine, ti, tw.to(hidden_states.dtype), logits, logits.new_zeros(()),
+                                 {"capacity": cap, "tokens_per_expert": dispatch.sum((0, 2))})
         cfg = self.cfg
         T = x.shape[0]
         probs = torch.softmax(F.linear(x.float(), self.weight.float()), dim=-1)     # [T, E]
@@ -106,13 +173,31 @@ class ExpertChoiceRouter(nn.Module):
 class SoftMoERouter(nn.Module):
     """Soft MoE: every slot is a convex combination of all tokens (fully differentiable, no dropping)."""
 
+    @reference_kwargs(config="cfg")
     def __init__(self, cfg: ExpertParallelConfig, slots_per_expert: int = 1, dtype=None, device=None):
         super().__init__()
         self.cfg, self.slots = cfg, slots_per_expert
         self.phi = nn.Parameter(torch.empty(cfg.hidden_size, cfg.num_experts * slots_per_expert, dtype=dtype, device=device))
         nn.init.normal_(self.phi, std=0.02)
 
-    def forward(self, x):
+    def forward(self, x=None, *, hidden_states=None, padding_mask=None):
+        """x [T, H] -> (dispatch [T, E*slots], combine [T, E*slots], {}).  `forward(hidden_states=, padding_mask=)`
+        returns them as a `RoutingOutput` whose masks are the soft weights [T, E, slots]: padded tokens get no share of
+        a slot (data_pipeline/trainer/distributed/expert_parallel.py:1046)."""
+        if hidden_states is not None:
+            flat = hidden_states.reshape(-1, hidden_states.shape[-1])
+            logits = flat.float() @ self.phi.float()
+            T, E = flat.shape[0], self.cfg.num_experts
+            dl = logits if padding_mask is None else logits.masked_fill(padding_mask.reshape(-1, 1).to(torch.bool), float("-inf"))
+            dispatch = torch.softmax(dl, dim=0).nan_to_num(0.0).view(T, E, self.slots)
+            combine = torch.softmax(logits, dim=1).view(T, E, self.slots)
+            if padding_mask is not None:
+                combine = combine * (~padding_mask.reshape(-1).to(torch.bool))[:, None, None]
+            per_expert = combine.sum(-1)
+            k = min(self.cfg.top_k, E)
+            tw, ti = per_expert.topk(k, dim=-1)
+            return RoutingOutput(dispatch, combine, ti, tw, logits.view(T, E, self.slots).mean(-1), logits.new_zeros(()),
+                                 {"slots_per_expert": self.slots})
         logits = x.float() @ self.phi.float()                  # [T, E*slots]
         dispatch = torch.softmax(logits, dim=0)                # over tokens
         combine = torch.softmax(logits, dim=1)                 # over slots
@@ -120,36 +205,99 @@ class SoftMoERouter(nn.Module):
 
 
 # ------------------------------------------------------------------------------------------------ experts
+_PLAIN_ACT = {"silu": F.silu, "swish": F.silu, "gelu": F.gelu, "relu": F.relu,
+              "gelu_tanh": lambda v: F.gelu(v, approximate="tanh"), "gelu_new": lambda v: F.gelu(v, approximate="tanh")}
+_GLU_ACT = {"silu": "silu", "swish": "silu", "gelu": "gelu", "gelu_tanh": "gelu_tanh", "gelu_new": "gelu_tanh"}
+
+
+def _ffn(x, w_up, w_down, act: str, gated: bool):
+    """One feed-forward block: act(gate) * up (gated; gate | up stacked in `w_up`) or act(up), then the down projection.
+    The gated silu / gelu forms run the fused GLU kernel; relu and the ungated forms are plain PyTorch."""
+    h = gemm.linear(x, w_up)
+    if gated and act in _GLU_ACT:
+        h = activation.glu(h, _GLU_ACT[act])
+    elif gated:
+        g, u = h.chunk(2, dim=-1)
+        h = _PLAIN_ACT[act](g) * u
+    else:
+        h = _PLAIN_ACT[act](h)
+    return gemm.linear(h, w_down)
+
+
+def _expert_options(rest, activation, dropout, use_gated, dtype, device):
+    """The positional tail of an expert's constructor: `(dtype, device)`, or the reference's `(activation, dropout,
+    use_gated)` when it starts with the activation's name."""
+    if rest and isinstance(rest[0], str):
+        if len(rest) > 3:
+            raise TypeError("at most (activation, dropout, use_gated) after the sizes")
+        activation = rest[0]
+        dropout = float(rest[1]) if len(rest) > 1 else dropout
+        use_gated = bool(rest[2]) if len(rest) > 2 else use_gated
+    elif rest:
+        if len(rest) > 2:
+            raise TypeError("at most (dtype, device) after the sizes")
+        dtype = rest[0]
+        device = rest[1] if len(rest) > 1 else device
+    return activation, dropout, use_gated, dtype, device
+
+
 class ExpertFFN(nn.Module):
-    def __init__(self, hidden: int, inter: int, dtype=None, device=None):
+    """One expert: `down(act(gate(x)) * up(x))`, or `down(act(up(x)))` with `use_gated=False`
+    (data_pipeline/trainer/distributed/expert_parallel.py:1126)."""
+
+    @reference_kwargs(hidden_size="hidden", intermediate_size="inter")
+    def __init__(self, hidden: int, inter: int, *rest, dtype=None, device=None, activation: str = "silu",
+                 dropout: float = 0.0, use_gated: bool = True):
         super().__init__()
-        self.w_gate_up = nn.Parameter(torch.empty(2 * inter, hidden, dtype=dtype, device=device))
+        activation, dropout, use_gated, dtype, device = _expert_options(rest, activation, dropout, use_gated, dtype, device)
+        if activation not in _PLAIN_ACT:
+            raise ValueError(f"unknown activation {activation!r}; one of {sorted(_PLAIN_ACT)}")
+        self.act, self.use_gated = activation, bool(use_gated)
+        self.w_gate_up = nn.Parameter(torch.empty((2 if use_gated else 1) * inter, hidden, dtype=dtype, device=device))
         self.w_down = nn.Parameter(torch.empty(hidden, inter, dtype=dtype, device=device))
+        self.dropout = nn.Dropout(dropout) if dropout > 0 else nn.Identity()
         nn.init.normal_(self.w_gate_up, std=0.02)
         nn.init.normal_(self.w_down, std=0.02)
 
     def forward(self, x):
-        return gemm.linear(activation.glu(gemm.linear(x, self.w_gate_up)), self.w_down)
+        return self.dropout(_ffn(x, self.w_gate_up, self.w_down, self.act, self.use_gated))
 
 
 class GroupedExperts(nn.Module):
     """E experts stored as stacked weights; `forward(x_sorted, counts)` runs each expert on its contiguous slice."""
 
-    def __init__(self, num_experts: int, hidden: int, inter: int, dtype=None, device=None):
+    @reference_kwargs(hidden_size="hidden", intermediate_size="inter")
+    def __init__(self, num_experts: int, hidden: int, inter: int, *rest, dtype=None, device=None,
+                 activation: str = "silu", dropout: float = 0.0, use_gated: bool = True):
         super().__init__()
-        self.num_experts = num_experts
-        self.w_gate_up = nn.Parameter(torch.empty(num_experts, 2 * inter, hidden, dtype=dtype, device=device))
+        activation, dropout, use_gated, dtype, device = _expert_options(rest, activation, dropout, use_gated, dtype, device)
+        if activation not in _PLAIN_ACT:
+            raise ValueError(f"unknown activation {activation!r}; one of {sorted(_PLAIN_ACT)}")
+        self.num_experts, self.act, self.use_gated = num_experts, activation, bool(use_gated)
+        self.w_gate_up = nn.Parameter(torch.empty(num_experts, (2 if use_gated else 1) * inter, hidden, dtype=dtype, device=device))
         self.w_down = nn.Parameter(torch.empty(num_experts, hidden, inter, dtype=dtype, device=device))
+        self.dropout = nn.Dropout(dropout) if dropout > 0 else nn.Identity()
         nn.init.normal_(self.w_gate_up, std=0.02)
         nn.init.normal_(self.w_down, std=0.02)
 
-    def forward(self, x_sorted: torch.Tensor, counts: list[int]) -> torch.Tensor:
+    def forward(self, x_sorted: torch.Tensor | None = None, counts: "list[int] | None" = None, expert_weights=None, *,
+                tokens=None, expert_indices=None) -> torch.Tensor:
+        """`forward(x_sorted, counts)`: rows already grouped by expert.  `forward(tokens, expert_indices, expert_weights)`
+        (tokens [T, H], choices and weights [T, k]) groups them, runs the experts and returns the weighted sum per token
+        (data_pipeline/trainer/distributed/expert_parallel.py:1267)."""
+        if tokens is not None or torch.is_tensor(counts) or expert_indices is not None:
+            x = tokens if tokens is not None else x_sorted
+            idx = expert_indices if expert_indices is not None else counts
+            if expert_weights is None:
+                raise TypeError("forward(tokens, expert_indices, expert_weights) needs the routing weights")
+            xs, order, cnt = permute_tokens(x, idx, self.num_experts)
+            return unpermute_tokens(self.forward(xs, cnt.tolist()), order, expert_weights.to(x.dtype), x.shape[0])
         outs, off = [], 0
         for e, n in enumerate(counts):
             if n == 0:
                 continue
             xe = x_sorted[off:off + n]
-            outs.append(gemm.linear(activation.glu(gemm.linear(xe, self.w_gate_up[e])), self.w_down[e]))
+            outs.append(self.dropout(_ffn(xe, self.w_gate_up[e], self.w_down[e], self.act, self.use_gated)))
             off += n
         if not outs:
             return x_sorted.new_zeros(0, x_sorted.shape[-1])
@@ -157,7 +305,11 @@ class GroupedExperts(nn.Module):
 
 
 class SharedExpert(ExpertFFN):
-    pass
+    """Expert every token passes through, next to the routed ones."""
+
+    @property
+    def ffn(self) -> "SharedExpert":
+        return self
 
 
 def permute_tokens(x: torch.Tensor, experts: torch.Tensor, num_experts: int):
@@ -180,6 +332,7 @@ def unpermute_tokens(y_sorted: torch.Tensor, order: torch.Tensor, weights: torch
 class MoELayer(nn.Module):
     """Single-process MoE block (all experts local)."""
 
+    @reference_kwargs(config="cfg")
     def __init__(self, cfg: ExpertParallelConfig, dtype=None, device=None):
         super().__init__()
         self.cfg = cfg
@@ -233,6 +386,7 @@ class MoELayer(nn.Module):
     def _local(self, x2, idx, w):
         from ..ops import moe as moe_ops
         if moe_ops.available(x2) and isinstance(self.experts, GroupedExperts) \
+                and self.experts.use_gated and self.experts.act == "silu" and isinstance(self.experts.dropout, nn.Identity) \
                 and self.experts.w_gate_up.dtype == torch.bfloat16 and self.experts.w_down.shape[-1] % 64 == 0 \
                 and x2.shape[-1] % 64 == 0:
             # device-side plan + one grouped tcgen05 GEMM per projection: no host sync on the expert counts
@@ -241,7 +395,37 @@ class MoELayer(nn.Module):
         ys = self.experts(xs, counts.tolist())
         return unpermute_tokens(ys, order, w, x2.shape[0])
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
+    def _masked(self, run, x2, attention_mask):
+        """`run` on the valid rows only (`attention_mask` 1 = valid); padded rows come out as zeros and take no part in
+        the routing statistics."""
+        if attention_mask is None:
+            return self.route_and_run(x2, run)
+        valid = attention_mask.reshape(-1).to(torch.bool)
+        out = torch.zeros_like(x2)
+        if valid.any():
+            out[valid] = self.route_and_run(x2[valid], run)
+        return out
+
+    def _reference_forward(self, run, hidden_states, attention_mask, output_router_logits):
+        shp = hidden_states.shape
+        x2 = hidden_states.reshape(-1, shp[-1])
+        y = self._masked(run, x2, attention_mask)
+        for s in self.shared:
+            y = y + s(x2)
+        logits = None
+        if output_router_logits:
+            w = getattr(self.router, "weight", None)
+            logits = F.linear(x2.float(), w.float()) if w is not None else x2.float() @ self.router.phi.float()
+        aux = self.aux_loss if torch.is_tensor(self.aux_loss) else x2.new_zeros(())
+        return y.view(shp), aux, logits
+
+    def forward(self, x: torch.Tensor | None = None, *, hidden_states=None, attention_mask=None,
+                output_router_logits: bool = False):
+        """`layer(x)` -> output (the auxiliary loss is left in `aux_loss`).  `layer(hidden_states=, attention_mask=,
+        output_router_logits=)` -> (output, auxiliary loss, router logits or None)
+        (data_pipeline/trainer/distributed/expert_parallel.py:1480)."""
+        if hidden_states is not None:
+            return self._reference_forward(self._local, hidden_states, attention_mask, output_router_logits)
         shp = x.shape
         x2 = x.reshape(-1, shp[-1])
         y = self.route_and_run(x2, self._local)
@@ -269,18 +453,100 @@ class _AllToAll(torch.autograd.Function):
 class AllToAllDispatcher:
     """Moves expert-sorted token rows to the ranks that own the experts, and back."""
 
-    def __init__(self, group, num_experts: int):
+    def __init__(self, *args, group=None, num_experts: int | None = None, num_local_experts: int | None = None,
+                 capacity: int | None = None):
+        """`AllToAllDispatcher(group, num_experts)`, or the reference's `(num_experts, num_local_experts, capacity,
+        group)` (data_pipeline/trainer/distributed/expert_parallel.py:232); the capacity is only used by the
+        mask form of `dispatch`."""
+        if args and isinstance(args[0], int):                       # (num_experts, num_local_experts, capacity, group)
+            names = ("num_experts", "num_local_experts", "capacity", "group")
+        else:
+            names = ("group", "num_experts")
+        if len(args) > len(names):
+            raise TypeError(f"at most {names} positionally")
+        given = dict(zip(names, args))
+        group = given.get("group", group)
+        num_experts = given.get("num_experts", num_experts)
+        num_local_experts = given.get("num_local_experts", num_local_experts)
+        capacity = given.get("capacity", capacity)
+        if num_experts is None:
+            raise TypeError("num_experts is required")
         self.group = group
-        self.world = dist.get_world_size(group)
-        self.rank = dist.get_rank(group)
+        self.world = get_expert_parallel_world_size(group)
+        self.rank = get_expert_parallel_rank(group)
         assert num_experts % self.world == 0, "num_experts must divide by the expert-parallel size"
         self.num_experts, self.local_experts = num_experts, num_experts // self.world
+        if num_local_experts is not None and int(num_local_experts) != self.local_experts:
+            raise ValueError(f"num_local_experts={num_local_experts} but {num_experts} experts over {self.world} ranks "
+                             f"give {self.local_experts}")
+        self.capacity = capacity
+        self._slots = None
 
-    def dispatch(self, x_sorted: torch.Tensor, counts: torch.Tensor):
+    num_local_experts = property(lambda self: self.local_experts)
+    world_size = property(lambda self: self.world)
+
+    # ---- capacity-slotted form: dispatch(tokens, dispatch_mask [T, E]) / combine(expert_outputs, combine_weights, ...)
+    def _dispatch_mask(self, tokens: torch.Tensor, mask: torch.Tensor):
+        T, H = tokens.shape
+        E, W, El = self.num_experts, self.world, self.local_experts
+        mask = mask.to(torch.bool)
+        C = int(self.capacity) if self.capacity is not None else max(int(mask.sum(0).max()), 1)
+        slot = mask.long().cumsum(0) - 1                                   # [T, E] position of a token inside its expert
+        keep = mask & (slot < C)
+        t, e = keep.nonzero(as_tuple=True)
+        send = tokens.new_zeros(E, C, H).index_put((e, slot[t, e]), tokens[t])
+        counts = keep.sum(0)
+        self._slots = (t, e, slot[t, e], C)
+        if W == 1:
+            self._order = None
+            return send, counts
+        recv_counts = torch.empty_like(counts)
+        dist.all_to_all_single(recv_counts, counts.contiguous(), group=self.group)       # [W, El] by source rank
+        n = El * C
+        recv = _AllToAll.apply(send.view(E * C, H), [n] * W, [n] * W, self.group).view(W, El, C, H)
+        # per local expert: the valid rows of every source rank, in rank order, then the empty slots
+        valid = torch.arange(C, device=tokens.device)[None, None, :] < recv_counts.view(W, El, 1)
+        valid = valid.permute(1, 0, 2).reshape(El, W * C)
+        order = torch.argsort((~valid).to(torch.uint8), dim=1, stable=True)
+        rows = recv.permute(1, 0, 2, 3).reshape(El, W * C, H)
+        self._order = order
+        return rows.gather(1, order[..., None].expand(-1, -1, H)), recv_counts.view(W, El).sum(0)
+
+    def _combine_mask(self, expert_outputs, combine_weights, original_positions=None, num_tokens=None):
+        if self._slots is None:
+            raise RuntimeError("combine(expert_outputs, combine_weights, ...) follows dispatch(tokens, dispatch_mask)")
+        t, e, s, C = self._slots
+        W, El, H = self.world, self.local_experts, expert_outputs.shape[-1]
+        if W > 1:
+            rows = torch.zeros_like(expert_outputs).scatter(1, self._order[..., None].expand(-1, -1, H), expert_outputs)
+            rows = rows.view(El, W, C, H).permute(1, 0, 2, 3).reshape(W * El * C, H)
+            n = El * C
+            expert_outputs = _AllToAll.apply(rows, [n] * W, [n] * W, self.group).view(self.num_experts, C, H)
+        if combine_weights.dim() == 3:                                      # [T, E, C] -> weight of the slot used
+            wt = combine_weights[t, e, s]
+        else:
+            wt = combine_weights[t, e]
+        T = int(num_tokens) if num_tokens is not None else combine_weights.shape[0]
+        pos = t if original_positions is None else original_positions.to(t.device)[t]
+        out = expert_outputs.new_zeros(T, H, dtype=torch.float32)
+        out = out.index_add(0, pos, (expert_outputs[e, s] * wt[:, None].to(expert_outputs.dtype)).float())
+        return out.to(expert_outputs.dtype)
+
+    def dispatch(self, x_sorted: torch.Tensor | None = None, counts: torch.Tensor | None = None, *, tokens=None,
+                 dispatch_mask=None):
         """counts [E] (tokens this rank routes to each global expert). Returns (rows for my experts ordered by
-        (source rank, local expert), recv_counts [W, E_local], bookkeeping)."""
+        (source rank, local expert), recv_counts [W, E_local], bookkeeping).
+
+        `dispatch(tokens [T, H], dispatch_mask [T, E])` is the capacity-slotted form: returns (rows
+        [E_local, W * capacity, H], valid rows per local expert); the rows of one expert are those of rank 0, rank 1, ...
+        followed by zero rows."""
+        if tokens is not None or dispatch_mask is not None or (counts is not None and counts.dim() == 2):
+            return self._dispatch_mask(tokens if tokens is not None else x_sorted,
+                                       dispatch_mask if dispatch_mask is not None else counts)
         W, El = self.world, self.local_experts
         send_counts = counts.view(W, El)
+        if W == 1:                                       # every expert is local: nothing moves
+            return x_sorted, send_counts, None
         recv_counts = torch.empty_like(send_counts)
         dist.all_to_all_single(recv_counts, send_counts.contiguous(), group=self.group)
         in_splits = send_counts.sum(1).tolist()
@@ -288,7 +554,16 @@ class AllToAllDispatcher:
         recv = _AllToAll.apply(x_sorted, in_splits, out_splits, self.group)
         return recv, recv_counts, (in_splits, out_splits)
 
-    def combine(self, y: torch.Tensor, book) -> torch.Tensor:
+    def combine(self, y: torch.Tensor | None = None, book=None, original_positions=None, num_tokens=None, *,
+                expert_outputs=None, combine_weights=None) -> torch.Tensor:
+        """`combine(y, book)` undoes `dispatch(x_sorted, counts)`.  `combine(expert_outputs, combine_weights [T, E] or
+        [T, E, C], original_positions, num_tokens)` undoes the mask form and returns the weighted sum per token."""
+        if expert_outputs is not None or combine_weights is not None or torch.is_tensor(book):
+            return self._combine_mask(expert_outputs if expert_outputs is not None else y,
+                                      combine_weights if combine_weights is not None else book,
+                                      original_positions, num_tokens)
+        if book is None:
+            return y
         in_splits, out_splits = book
         return _AllToAll.apply(y, out_splits, in_splits, self.group)
 
@@ -296,9 +571,11 @@ class AllToAllDispatcher:
 class ExpertParallelMoE(MoELayer):
     """MoE block whose experts are sharded over an expert-parallel group (E / W local experts per rank)."""
 
-    def __init__(self, cfg: ExpertParallelConfig, group, dtype=None, device=None):
+    @reference_kwargs(config="cfg")
+    def __init__(self, cfg: ExpertParallelConfig, group=None, dtype=None, device=None):
         nn.Module.__init__(self)
         self.cfg = cfg
+        group = group if group is not None else getattr(cfg, "expert_parallel_group", None)
         self.router = TopKRouter(cfg, dtype, device)
         self.dispatcher = AllToAllDispatcher(group, cfg.num_experts)
         self.experts = GroupedExperts(self.dispatcher.local_experts, cfg.hidden_size, cfg.intermediate_size, dtype, device)
@@ -327,13 +604,21 @@ class ExpertParallelMoE(MoELayer):
         ys = d.combine(back, book)
         return unpermute_tokens(ys, order, w, x2.shape[0])
 
-    def forward(self, x):
+    moe_layer = property(lambda self: self)
+
+    def forward(self, x=None, *, hidden_states=None, attention_mask=None, output_router_logits: bool = False):
+        self.__dict__["_forward_count"] = self.__dict__.get("_forward_count", 0) + 1
+        if hidden_states is not None:
+            if attention_mask is not None and self.dispatcher.world > 1:
+                # every rank must enter the all-to-all: route all rows, zero the padded ones afterwards
+                out, aux, logits = self._reference_forward(self._distributed, hidden_states, None, output_router_logits)
+                return out * attention_mask.reshape(*out.shape[:-1], 1).to(out.dtype), aux, logits
+            return self._reference_forward(self._distributed, hidden_states, attention_mask, output_router_logits)
         shp = x.shape
         x2 = x.reshape(-1, shp[-1])
         y = self.route_and_run(x2, self._distributed)
         for s in self.shared:
             y = y + s(x2)
-        self.__dict__["_forward_count"] = self.__dict__.get("_forward_count", 0) + 1
         return y.view(shp)
 
     def get_routing_statistics(self) -> dict:
@@ -345,6 +630,7 @@ class ExpertParallelMoE(MoELayer):
 class HierarchicalMoE(nn.Module):
     """Two-level routing: a coarse router picks a group, the group's MoE picks experts."""
 
+    @reference_kwargs(config="cfg")
     def __init__(self, cfg: ExpertParallelConfig, num_groups: int = 2, dtype=None, device=None):
         super().__init__()
         assert cfg.num_experts % num_groups == 0
@@ -353,16 +639,25 @@ class HierarchicalMoE(nn.Module):
         self.groups = nn.ModuleList(MoELayer(sub, dtype, device) for _ in range(num_groups))
         self.coarse = nn.Linear(cfg.hidden_size, num_groups, bias=False, dtype=dtype, device=device)
 
-    def forward(self, x):
+    def forward(self, x=None, *, hidden_states=None, attention_mask=None):
+        """`layer(x)` -> output; `layer(hidden_states=, attention_mask=)` -> (output, auxiliary loss): padded rows
+        (mask 0) are routed nowhere and come out as zeros."""
+        reference_form = hidden_states is not None
+        x = hidden_states if reference_form else x
         shp = x.shape
         x2 = x.reshape(-1, shp[-1])
         g = torch.softmax(self.coarse(x2).float(), -1)
         top = g.argmax(-1)
+        if attention_mask is not None:
+            top = top.masked_fill(~attention_mask.reshape(-1).to(torch.bool), -1)
         out = torch.zeros_like(x2)
         for gi, layer in enumerate(self.groups):
             m = top == gi
             if m.any():
                 out[m] = layer(x2[m]) * g[m, gi].unsqueeze(-1).to(x2.dtype)
+        if reference_form:
+            aux = self.aux_loss
+            return out.view(shp), aux if torch.is_tensor(aux) else x2.new_zeros(())
         return out.view(shp)
 
     @property
@@ -700,22 +995,12 @@ class RouterBase(nn.Module):
             total = total + cfg.aux_loss_weight * terms["importance_loss"]
         return total, terms
 
-    def forward(self, x: torch.Tensor) -> RoutingOutput:
+    def forward(self, x: torch.Tensor | None = None, padding_mask=None, *, hidden_states=None) -> RoutingOutput:
+        """[..., H] (and the padding mask [...], True = padded token) -> the dense `RoutingOutput`."""
         cfg = self.config
+        x = hidden_states if hidden_states is not None else x
         flat = x.reshape(-1, x.shape[-1])
         logits = self.router(flat).float()
         w, idx, probs = self.route(logits)
-        T, E = probs.shape
-        C = moe_capacity(T, E, cfg.top_k, cfg.capacity_factor, cfg.min_capacity)
-        # slot of every (token, choice) inside its expert: rank among the earlier slots routed to the same expert
-        hot = F.one_hot(idx.reshape(-1), E)                                        # [T*k, E]
-        slot = (hot.cumsum(0) - hot).gather(1, idx.reshape(-1, 1)).reshape(T, cfg.top_k)
-        keep = slot < C
-        dispatch = torch.zeros(T, E, C, dtype=torch.bool, device=x.device)
-        combine = torch.zeros(T, E, C, dtype=w.dtype, device=x.device)
-        t = torch.arange(T, device=x.device)[:, None].expand_as(idx)
-        dispatch[t[keep], idx[keep], slot[keep]] = True
-        combine[t[keep], idx[keep], slot[keep]] = w[keep]
         aux = cfg.aux_loss_weight * load_balance_loss(self.loss_type, probs, idx, logits, cfg.z_loss_weight)
-        meta = {"capacity": C, "dropped": int((~keep).sum()), "tokens_per_expert": hot.sum(0)}
-        return RoutingOutput(dispatch, combine, idx, w, logits, aux, meta)
+        return _dense_routing(cfg, logits, w, idx, aux, padding_mask)
