@@ -343,3 +343,58 @@ def test_expert_parallel_blocks_take_the_reference_forms():
     kept = (mask.long().cumsum(0) - 1 < 6) & mask
     back = d.combine(expert_outputs=rows, combine_weights=w, original_positions=torch.arange(10), num_tokens=10)
     assert torch.allclose(back, flat * (w * kept).sum(1, keepdim=True), atol=1e-5)
+
+
+def test_context_parallel_classes_take_the_reference_forms():
+    from trainscale_b200.parallel.cp import (BalancedCPScheduler, ContextParallel, ContextParallelAttention,
+                                             ContextParallelConfig, ContextParallelEngine, RingBufferPool,
+                                             RingCommunicator, TensorArena)
+
+    class Group:
+        def size(self):
+            return 8
+
+    s = BalancedCPScheduler(max_seq_len_per_rank=1024, dp_cp_group=Group())
+    assert s.total_hdp_gpus == 8 and s.gpus_needed(seq_len=3000) == 4 and s.get_total_workload(seq_length=100, cp_size=2) == 5000.0
+    samples = list(enumerate([4000, 3000, 900, 800, 700, 600, 500, 400, 300, 200, 100, 2048]))
+    est = lambda l, cp=None: l * l / (cp or 1)                                   # noqa: E731
+    buckets = s.make_buckets_equal(samples, est)
+    assert len(buckets) == 3 and [x for b in buckets for x in b] == samples      # order kept, one bucket per CP degree
+    micro, left, times, ids = s.next_hdp_group(samples, est, 8, delta=0.05, strategy="dp")
+    assert len(micro) == len(times) == len(ids) == 8 and all(micro)             # no GPU idles
+    assert micro[0] == [4000] and ids[0] == [0] and times[0] == 4000 * 4000 / 4
+    placed = {i for gpu in ids for i in gpu}
+    assert placed | {i for i, _ in left} == set(range(12)) and not placed & {i for i, _ in left}
+    assert s.next_hdp_group([4000, 900, 800], 0) == ([(0, 4), (1, 1), (2, 1)], 3)            # the native form still works
+    with pytest.raises(ValueError):
+        s.next_hdp_group(samples, est, 8, strategy="zz")
+
+    arena = TensorArena(capacity_bytes=1024, device="cpu", dtype=torch.float16)
+    assert arena.size == 1024 and arena.default_dtype is torch.float16
+    assert len(RingBufferPool((2, 3), torch.float32, "cpu", num_buffers=3, pin_memory=False).buffers) == 3
+    assert len(RingBufferPool(2, (2, 3), torch.float32).buffers) == 2
+    cfg = ContextParallelConfig(cp_degree=1)
+    n = cfg.compute_memory_requirement(batch_size=2, seq_len=128, hidden_dim=64, num_heads=4)
+    per = 2 * 128 * 64 * 2
+    assert n == cfg.compute_memory_requirement(2, 128, 64, 4) == 3 * per + cfg.ring_buffer_count * 2 * per + per + 2 * 4 * 128 * 4
+    assert isinstance(cfg.compute_memory_requirement(128, 64, 2, 4, 16), dict)
+    ring = RingCommunicator(cp_rank=0, cp_world_size=1, process_group=None, device="cpu", k_shape=(1, 4, 2, 8),
+                            v_shape=(1, 4, 2, 8), dtype=torch.float32)
+    k, v = torch.randn(1, 4, 2, 8), torch.randn(1, 4, 2, 8)
+    kr, vr, event = ring.start_send_recv(k_local=k, v_local=v)
+    ring.wait_recv(event=event)
+    assert torch.equal(kr, k) and torch.equal(vr, v)
+    engine = ContextParallelEngine(cfg)
+    assert engine.initialize(cp_mesh=None).is_ok()
+    attn = ContextParallelAttention(cfg, engine, 16, 2)
+    q = torch.randn(1, 6, 16)
+    out = attn(q, q, q)
+    heads_first = q.view(1, 6, 2, 8).transpose(1, 2)
+    assert out.shape == q.shape
+    assert torch.allclose(attn(heads_first, heads_first, heads_first).transpose(1, 2).reshape(1, 6, 16), out, atol=1e-6)
+    wrapper = ContextParallel({"cp_degree": 1})
+    ids_ = torch.arange(8).view(1, 8)
+    shards = wrapper.shard_inputs(ids_, ids_.clone())
+    assert len(shards) == 4 and shards[2] is None and torch.equal(shards[0], ids_)
+    assert torch.equal(wrapper.restore_sequence(sharded_output=q, seq_dim=1), q)
+    assert torch.equal(engine.gather_output(sharded_output=q), q)

@@ -28,6 +28,8 @@ import torch
 import torch.distributed as dist
 import torch.nn as nn
 
+from ..utils.refargs import ANY, reference_kwargs
+
 from ..ops.attention import attention_reference
 
 
@@ -508,9 +510,22 @@ class BalancedCPScheduler:
     """Per-sequence CP degree = next power of two of len / max_tokens_per_rank; greedy balance of the quadratic
     workload L^2 / cp over GPUs (data_pipeline/trainer/distributed/hybrid_cp_scheduler.py:149-621)."""
 
-    def __init__(self, cfg: HybridCPConfig):
-        self.cfg = cfg
+    def __init__(self, cfg: "HybridCPConfig | int | None" = None, dp_cp_group=None, *, max_seq_len_per_rank: int | None = None):
+        """`BalancedCPScheduler(HybridCPConfig(...))`, or the reference's `(max_seq_len_per_rank, dp_cp_group)`: the world
+        is then the size of that group (of the default group, or 1, when it is None)."""
+        if max_seq_len_per_rank is not None or isinstance(cfg, int):
+            per_rank = int(max_seq_len_per_rank if max_seq_len_per_rank is not None else cfg)
+            if dp_cp_group is not None and hasattr(dp_cp_group, "size"):
+                world = int(dp_cp_group.size())
+            else:
+                world = dist.get_world_size() if dist.is_available() and dist.is_initialized() else 1
+            cfg = HybridCPConfig(max_tokens_per_rank=per_rank, world_size=world)
+        self.cfg = cfg if cfg is not None else HybridCPConfig()
 
+    max_seq_len_per_rank = property(lambda self: self.cfg.max_tokens_per_rank)
+    total_hdp_gpus = property(lambda self: self.cfg.world_size)
+
+    @reference_kwargs(seq_len="length")
     def gpus_needed(self, length: int) -> int:
         n = max(1, math.ceil(length / self.cfg.max_tokens_per_rank))
         return min(self.cfg.world_size, 1 << (n - 1).bit_length())
@@ -538,12 +553,38 @@ class BalancedCPScheduler:
         return plan
 
     # -- the reference scheduler's finer-grained steps (hybrid_cp_scheduler.py:149-621), on the same cost model
+    @reference_kwargs(seq_length="length", cp_size="cp")
     def get_total_workload(self, length: int, cp: int | None = None) -> float:
         """Attention work one GPU does for a sequence of `length` split over `cp` GPUs: L^2 / cp."""
         return self.workload(length, cp or self.gpus_needed(length))
 
-    def make_buckets_equal(self, lengths: list[int], num_buckets: int) -> list[list[int]]:
-        """Longest-processing-time split of sequence indices into `num_buckets` buckets of near-equal total work."""
+    def _buckets_in_order(self, samples: list, estimator) -> list:
+        """(sample id, length) pairs cut, in the given order, into k consecutive runs of near-equal work, k = number of
+        distinct CP degrees among them (data_pipeline/trainer/distributed/hybrid_cp_scheduler.py:197)."""
+        from collections import deque
+        if not samples:
+            return []
+        k = len({self.gpus_needed(l) for _, l in samples})
+        work = [float(estimator(l, self.gpus_needed(l))) for _, l in samples]
+        target, out, cur, acc = sum(work) / k, [], [], 0.0
+        for i, s in enumerate(samples):
+            must_close = len(samples) - i <= k - len(out) - 1          # keep one sample for each bucket still to open
+            if cur and len(out) < k - 1 and (acc + work[i] > 1.1 * target or must_close):
+                out.append(deque(cur))
+                cur, acc = [], 0.0
+            cur.append(s)
+            acc += work[i]
+        out.append(deque(cur))
+        return out
+
+    def make_buckets_equal(self, lengths: list | None = None, num_buckets=None, *, sample_seqlens=None,
+                           compute_estimator=None):
+        """Longest-processing-time split of sequence indices into `num_buckets` buckets of near-equal total work.
+        `make_buckets_equal(sample_seqlens, compute_estimator)` is the reference's form: (id, length) pairs kept in
+        order, one deque per distinct CP degree."""
+        if sample_seqlens is not None or compute_estimator is not None or callable(num_buckets):
+            return self._buckets_in_order(list(sample_seqlens if sample_seqlens is not None else lengths),
+                                          compute_estimator or num_buckets)
         buckets: list[list[int]] = [[] for _ in range(num_buckets)]
         load = [0.0] * num_buckets
         for i in sorted(range(len(lengths)), key=lambda k: -self.get_total_workload(lengths[k])):
@@ -552,8 +593,41 @@ class BalancedCPScheduler:
             load[b] += self.get_total_workload(lengths[i])
         return buckets
 
-    def next_hdp_group(self, lengths: list[int], start: int = 0) -> tuple[list[tuple[int, int]], int]:
-        """Takes sequences from `start` on until their GPU demand fills the world: returns [(index, cp)], next start."""
+    def _next_group_reference(self, samples: list, estimator, total_gpus: int, delta: float, strategy: str):
+        """(micro_batches, leftovers, exec_times, sample_ids_per_gpu) for the samples that fit `total_gpus` once: every
+        GPU of a sample's group lists the sample's full length and is charged estimator(length, cp)
+        (data_pipeline/trainer/distributed/hybrid_cp_scheduler.py:264)."""
+        if strategy not in ("dp", "pp"):
+            raise ValueError(f"strategy must be 'dp' or 'pp', got {strategy!r}")
+        W = int(total_gpus)
+        sched = self if W == self.cfg.world_size else BalancedCPScheduler(HybridCPConfig(self.cfg.max_tokens_per_rank, W))
+        samples = list(samples)
+        lengths = [l for _, l in samples]
+        chosen, nxt = sched.next_hdp_group(lengths, 0) if samples else ([], 0)
+        # more single-GPU samples may ride along while the spread of the per-GPU times stays within delta
+        idx = [i for i, _ in chosen]
+        plan = sched.balanced_schedule([lengths[i] for i in idx]) if idx else [[] for _ in range(W)]
+        times = [sum(float(estimator(lengths[idx[j]], cp)) for j, cp in gpu) for gpu in plan]
+        while nxt < len(samples) and sched.gpus_needed(lengths[nxt]) == 1 and times:
+            lo = min(range(W), key=times.__getitem__)
+            cost = float(estimator(lengths[nxt], 1))
+            if times[lo] + cost > (1.0 + delta) * max(times):
+                break
+            idx.append(nxt)
+            plan[lo].append((len(idx) - 1, 1))
+            times[lo] += cost
+            nxt += 1
+        micro = [[lengths[idx[j]] for j, _ in gpu] for gpu in plan]
+        ids = [[samples[idx[j]][0] for j, _ in gpu] for gpu in plan]
+        return micro, samples[nxt:], times, ids
+
+    def next_hdp_group(self, lengths: list | None = None, start=0, total_gpus: int | None = None, delta: float = 0.05,
+                       strategy: str = "dp", *, sample_seqlens=None, compute_estimator=None):
+        """Takes sequences from `start` on until their GPU demand fills the world: returns [(index, cp)], next start.
+        `next_hdp_group(sample_seqlens, compute_estimator, total_gpus, delta, strategy)` is the reference's form."""
+        if sample_seqlens is not None or compute_estimator is not None or callable(start):
+            return self._next_group_reference(sample_seqlens if sample_seqlens is not None else lengths,
+                                              compute_estimator or start, total_gpus or self.cfg.world_size, delta, strategy)
         used, out, i = 0, [], start
         while i < len(lengths):
             cp = self.gpus_needed(lengths[i])
@@ -702,7 +776,10 @@ class TensorArena:
 
     ALIGN = 256
 
-    def __init__(self, size_bytes: int, device: torch.device | str = "cpu"):
+    @reference_kwargs(capacity_bytes="size_bytes")
+    def __init__(self, size_bytes: int, device: torch.device | str = "cpu", dtype: torch.dtype | None = None):
+        """`dtype`: the element type most allocations will have (recorded as `default_dtype`; the arena itself is bytes)."""
+        self.default_dtype = dtype
         self.size = int(size_bytes)
         self.buf = torch.empty(self.size, dtype=torch.uint8, device=device)
         self.offset = 0
@@ -738,10 +815,27 @@ class RingBufferPool:
 
     FREE, COMPUTE, SENDING, RECEIVING = range(4)
 
-    def __init__(self, count: int, shape: tuple, dtype: torch.dtype, device: torch.device | str = "cpu"):
+    def __init__(self, *args, count: int | None = None, shape=None, dtype: torch.dtype | None = None,
+                 device: torch.device | str | None = None, num_buffers: int | None = None, pin_memory: bool = False):
+        """`RingBufferPool(count, shape, dtype, device)`, or the reference's `(shape, dtype, device, num_buffers=3,
+        pin_memory=False)` (data_pipeline/trainer/distributed/context_parallel.py RingBufferPool); `pin_memory` pins
+        host-side buffers when a CUDA device is present."""
+        names = ("shape", "dtype", "device", "num_buffers", "pin_memory") if args and not isinstance(args[0], int) \
+            else ("count", "shape", "dtype", "device")
+        if len(args) > len(names):
+            raise TypeError(f"at most {names} positionally")
+        given = dict(zip(names, args))
+        shape, dtype = given.get("shape", shape), given.get("dtype", dtype)
+        device = given.get("device", device) or "cpu"
+        pin_memory = given.get("pin_memory", pin_memory)
+        count = given.get("count", count)
+        count = int(count if count is not None else given.get("num_buffers", num_buffers if num_buffers is not None else 3))
+        if shape is None or dtype is None:
+            raise TypeError("shape and dtype are required")
         if count < 2:
             raise ValueError("a ring needs at least two buffers")
-        self.buffers = [torch.empty(shape, dtype=dtype, device=device) for _ in range(count)]
+        pin = bool(pin_memory) and torch.device(device).type == "cpu" and torch.cuda.is_available()
+        self.buffers = [torch.empty(tuple(shape), dtype=dtype, device=device, pin_memory=pin) for _ in range(count)]
         self.state = [self.FREE] * count
 
     def _take(self, new_state: int) -> int:
@@ -824,8 +918,21 @@ class ContextParallelConfig:
         except (ValueError, KeyError, TypeError) as e:
             return Err(ValueError(str(e)))
 
-    def compute_memory_requirement(self, seq_len: int, hidden: int, n_layers: int, n_kv_heads: int, head_dim: int,
-                                   bytes_per_el: int = 2) -> dict:
+    def compute_memory_requirement(self, *args, **kwargs):
+        """`(seq_len, hidden, n_layers, n_kv_heads, head_dim, bytes_per_el=2)` -> dict in GiB for a layer stack; the
+        reference's `(batch_size, seq_len, hidden_dim, num_heads)` -> bytes of ONE layer's q / k / v, ring buffers,
+        output and log-sum-exp at 2 bytes per element (data_pipeline/trainer/distributed/context_parallel.py:615)."""
+        if {"batch_size", "hidden_dim", "num_heads"} & set(kwargs) or (len(args) == 4 and not kwargs):
+            names = ("batch_size", "seq_len", "hidden_dim", "num_heads")
+            a = dict(zip(names, args), **kwargs)
+            b, s, h, nh = (int(a[n]) for n in names)
+            local = s // self.cp_degree
+            per_tensor = b * local * h * 2
+            return 3 * per_tensor + self.ring_buffer_count * 2 * per_tensor + per_tensor + b * nh * local * 4
+        return self._memory_of_stack(*args, **kwargs)
+
+    def _memory_of_stack(self, seq_len: int, hidden: int, n_layers: int, n_kv_heads: int, head_dim: int,
+                         bytes_per_el: int = 2) -> dict:
         return estimate_memory_per_gpu(seq_len, self.cp_degree, hidden, n_layers, n_kv_heads, head_dim, bytes_per_el,
                                        self.use_activation_checkpointing)
 
@@ -833,17 +940,42 @@ class ContextParallelConfig:
 class RingCommunicator:
     """Neighbour exchange of the ring: send to rank+1, receive from rank-1, as one batched call."""
 
-    def __init__(self, group=None):
+    def __init__(self, group=None, *, cp_rank: int | None = None, cp_world_size: int | None = None, process_group=None,
+                 device=None, k_shape=None, v_shape=None, dtype: torch.dtype | None = None):
+        """`RingCommunicator(group)`; the reference's keyword form names the rank and size itself and the shapes of
+        the k / v blocks (receive buffers are then allocated once and reused by `start_send_recv(k_local=, v_local=)`)
+        (data_pipeline/trainer/distributed/context_parallel.py RingCommunicator)."""
+        group = process_group if process_group is not None else group
         self.group = group
         on = dist.is_available() and dist.is_initialized()
-        self.world = dist.get_world_size(group) if on else 1
-        self.rank = dist.get_rank(group) if on else 0
+        self.world = int(cp_world_size) if cp_world_size is not None else (dist.get_world_size(group) if on else 1)
+        self.rank = int(cp_rank) if cp_rank is not None else (dist.get_rank(group) if on else 0)
+        if self.world > 1 and not on:
+            raise RuntimeError("a ring of more than one rank needs an initialised process group")
         self.bytes_sent = 0
+        self._recv_kv = None
+        if k_shape is not None and v_shape is not None:
+            if tuple(k_shape) != tuple(v_shape):
+                raise ValueError("k and v travel as one message: their shapes must match")
+            self._recv_kv = [torch.empty((2, *k_shape), dtype=dtype or torch.float32, device=device or "cpu") for _ in range(2)]
+            self._turn = 0
 
     def _global(self, r: int) -> int:
         return dist.get_global_rank(self.group, r) if self.group is not None else r
 
-    def start_send_recv(self, send: torch.Tensor, recv: torch.Tensor):
+    def start_send_recv(self, send: torch.Tensor | None = None, recv: torch.Tensor | None = None, *, k_local=None,
+                        v_local=None):
+        """`start_send_recv(send, recv)` -> handles.  `start_send_recv(k_local=, v_local=)` -> (k_recv, v_recv, handles):
+        the blocks of the previous rank, valid once `wait_recv(handles)` returned; two receive buffers alternate, so
+        the blocks of one step stay readable while the next step's transfer runs."""
+        if k_local is not None or v_local is not None:
+            send = torch.stack((k_local, v_local))
+            if self._recv_kv is not None and self._recv_kv[0].shape == send.shape and self._recv_kv[0].dtype == send.dtype:
+                recv = self._recv_kv[self._turn]
+                self._turn ^= 1
+            else:
+                recv = torch.empty_like(send)
+            return recv[0], recv[1], self.start_send_recv(send, recv)
         if self.world == 1:
             recv.copy_(send)
             return []
@@ -853,6 +985,7 @@ class RingCommunicator:
         return dist.batch_isend_irecv(ops)
 
     @staticmethod
+    @reference_kwargs(event="handles")
     def wait_recv(handles) -> None:
         for h in handles:
             h.wait()
@@ -882,8 +1015,12 @@ class ContextParallelEngine:
         self._rank, self._world = 0, 1
         self.arena: TensorArena | None = None
 
-    def initialize(self, group=None, device: torch.device | str = "cpu"):
+    def initialize(self, group=None, device: torch.device | str = "cpu", *, cp_mesh=None):
+        """`cp_mesh`: a one-dimensional DeviceMesh whose group is the context-parallel group."""
         from ..core.types import Err, Ok
+        group = cp_mesh if cp_mesh is not None else group
+        if group is not None and hasattr(group, "get_group"):
+            group = group.get_group()
         self.group = group if group is not None else self.group
         on = dist.is_available() and dist.is_initialized()
         self._world = dist.get_world_size(self.group) if on else 1
@@ -937,6 +1074,7 @@ class ContextParallelEngine:
         self._metrics.bytes_sent += 2 * k.numel() * k.element_size() * (self._world - 1)
         return ring_attention(q, k, v, self.group)
 
+    @reference_kwargs(sharded_output="x_local")
     def gather_output(self, x_local: torch.Tensor, seq_dim: int = 1) -> torch.Tensor:
         if self._world == 1:
             return x_local
@@ -953,13 +1091,39 @@ class ContextParallelAttention(nn.Module):
     """Attention core for modules that produce q / k / v themselves: ring attention when the engine spans more than one
     rank, plain causal attention otherwise."""
 
-    def __init__(self, engine: ContextParallelEngine):
+    def __init__(self, engine: "ContextParallelEngine | ContextParallelConfig | None" = None, *rest, config=None,
+                 hidden_dim: int | None = None, num_heads: int | None = None, head_dim: int | None = None):
+        """`ContextParallelAttention(engine)`: q / k / v arrive as [B, S_local, heads, D].  The reference's
+        `(config, engine, hidden_dim, num_heads, head_dim=None)` names the head split, and q / k / v then arrive as
+        [B, S_local, hidden] or [B, heads, S_local, D] and the output has the input's shape
+        (data_pipeline/trainer/distributed/context_parallel.py:1965)."""
         super().__init__()
+        if isinstance(engine, ContextParallelConfig) or (engine is None and rest):
+            config, engine, rest = engine, (rest[0] if rest else None), rest[1:]
+        if rest:
+            given = dict(zip(("hidden_dim", "num_heads", "head_dim"), rest))
+            hidden_dim, num_heads = given.get("hidden_dim", hidden_dim), given.get("num_heads", num_heads)
+            head_dim = given.get("head_dim", head_dim)
+        if engine is None:
+            raise TypeError("an initialised ContextParallelEngine is required")
         self.engine = engine
+        self.config = config if config is not None else engine.config
+        self.hidden_dim, self.num_heads = hidden_dim, num_heads
+        self.head_dim = head_dim or (hidden_dim // num_heads if hidden_dim and num_heads else None)
+        self.scale = 1.0 / math.sqrt(self.head_dim) if self.head_dim else None
 
     def forward(self, query: torch.Tensor, key: torch.Tensor, value: torch.Tensor,
                 attention_mask: torch.Tensor | None = None, position_ids: torch.Tensor | None = None) -> torch.Tensor:
-        return self.engine.ring_attention_forward(query, key, value, attention_mask)
+        if self.num_heads is None:
+            return self.engine.ring_attention_forward(query, key, value, attention_mask)
+        if query.dim() == 3:                                # [B, S, hidden] -> [B, S, heads, D] and back
+            B, S, _ = query.shape
+            split = lambda t: t.view(B, S, -1, self.head_dim)            # noqa: E731
+            out = self.engine.ring_attention_forward(split(query), split(key), split(value), attention_mask)
+            return out.reshape(B, S, -1)
+        out = self.engine.ring_attention_forward(query.transpose(1, 2), key.transpose(1, 2), value.transpose(1, 2),
+                                                 attention_mask)
+        return out.transpose(1, 2)
 
 
 def create_context_parallel_engine(cp_degree: int = 1, load_balancer: str = "head_tail", use_ring_attention: bool = True,
@@ -976,15 +1140,42 @@ def create_context_parallel_engine(cp_degree: int = 1, load_balancer: str = "hea
 class ContextParallel:
     """Two-call convenience wrapper: `shard_inputs(batch)` before the model, `restore_sequence(x)` after it."""
 
-    def __init__(self, group=None, load_balancer: str = "head_tail"):
+    def __init__(self, group=None, load_balancer: str = "head_tail", *, config=None):
+        """`ContextParallel(group, load_balancer)`, or the reference's `ContextParallel(config)` with a
+        `ContextParallelConfig` or a dict of its fields: the wrapper then drives a `ContextParallelEngine`, initialised
+        by the first `shard_inputs` (data_pipeline/trainer/distributed/context_parallel.py:2147)."""
+        if isinstance(group, (ContextParallelConfig, dict)):
+            config, group = group, None
+        self._engine = None
+        if config is not None:
+            config = ContextParallelConfig(**config) if isinstance(config, dict) else config
+            self._config, self._engine, self._initialized = config, ContextParallelEngine(config), False
+            load_balancer = config.load_balancer.name.lower()
         self.group, self.load_balancer = group, load_balancer
         on = dist.is_available() and dist.is_initialized()
         self.world = dist.get_world_size(group) if on else 1
         self.rank = dist.get_rank(group) if on else 0
 
-    def shard_inputs(self, batch: dict) -> dict:
-        return shard_inputs(batch, self.world, self.rank, self.load_balancer) if self.world > 1 else batch
+    def shard_inputs(self, batch: "dict | torch.Tensor | None" = None, labels=None, attention_mask=None, position_ids=None,
+                     cp_mesh=None, seq_dim: int = 1, *, input_ids=None):
+        """`shard_inputs(batch dict)` -> dict; `shard_inputs(input_ids, labels, attention_mask, position_ids, cp_mesh,
+        seq_dim)` -> the tuple of this rank's shards."""
+        if isinstance(batch, dict):
+            return shard_inputs(batch, self.world, self.rank, self.load_balancer) if self.world > 1 else batch
+        input_ids = input_ids if input_ids is not None else batch
+        eng = self._engine
+        if eng is None:
+            eng = self._engine = ContextParallelEngine(ContextParallelConfig(cp_degree=self.world,
+                                                                             load_balancer=self.load_balancer), self.group)
+            self._initialized = False
+        if not self._initialized:
+            r = eng.initialize(cp_mesh if cp_mesh is not None else self.group, input_ids.device)
+            r.unwrap()                                       # raises the engine's error (group of the wrong size, ...)
+            self._initialized = True
+            self.group, self.world, self.rank = eng.group, eng.cp_world_size, eng.cp_rank
+        return eng.shard_inputs(input_ids, labels, attention_mask, position_ids, seq_dim)
 
+    @reference_kwargs(sharded_output="x_local", seq_dim="dim")
     def restore_sequence(self, x_local: torch.Tensor, dim: int = 1) -> torch.Tensor:
         return gather_output(x_local, self.group, self.load_balancer, dim) if self.world > 1 else x_local
 

@@ -168,9 +168,12 @@ class NanoTimer:
     """Device timer: `with timer("fwd"):` records two CUDA events; durations are read by `flush()` for events that
     have completed (no synchronisation)."""
 
-    def __init__(self, name: str = "", use_cuda: bool | None = None):
-        """`name`: default label of `start()` / `stop()` spans; `use_cuda=False` forces the host clock."""
-        self.name = name
+    def __init__(self, name: str = "", use_cuda: bool | None = None, stream=None):
+        """`name`: default label of `start()` / `stop()` spans; `use_cuda=False` forces the host clock; `stream`: the
+        CUDA stream whose work is timed (the current stream when None)."""
+        if use_cuda is not None and not isinstance(use_cuda, bool):      # CUDATimer(name, stream)
+            use_cuda, stream = None, use_cuda
+        self.name, self.stream = name, stream
         self.cuda = torch.cuda.is_available() if use_cuda is None else (bool(use_cuda) and torch.cuda.is_available())
         self.pending: list[tuple[str, object, object]] = []
         self.totals: dict[str, float] = {}
@@ -180,9 +183,9 @@ class NanoTimer:
     def __call__(self, name: str):
         if self.cuda:
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            a.record()
+            a.record(self.stream)
             yield
-            b.record()
+            b.record(self.stream)
             self.pending.append((name, a, b))
         else:
             t0 = time.perf_counter()
@@ -212,14 +215,14 @@ class NanoTimer:
     def start(self) -> "NanoTimer":
         if self.cuda:
             self._a, self._b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            self._a.record()
+            self._a.record(self.stream)
         else:
             self._a, self._b = time.perf_counter_ns(), None
         return self
 
     def stop(self) -> "NanoTimer":
         if self.cuda:
-            self._b.record()
+            self._b.record(self.stream)
         else:
             self._b = time.perf_counter_ns()
         return self
