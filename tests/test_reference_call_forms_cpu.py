@@ -398,3 +398,52 @@ def test_context_parallel_classes_take_the_reference_forms():
     assert len(shards) == 4 and shards[2] is None and torch.equal(shards[0], ids_)
     assert torch.equal(wrapper.restore_sequence(sharded_output=q, seq_dim=1), q)
     assert torch.equal(engine.gather_output(sharded_output=q), q)
+
+
+def test_pipeline_and_checkpoint_classes_take_the_reference_forms():
+    import torch.nn as nn
+    from trainscale_b200.parallel.activation import (ActivationCheckpoint, ActivationCheckpointConfig, ActivationOffloader,
+                                                     ActivationPool, SelectiveCheckpointPolicy)
+    from trainscale_b200.parallel.dist_utils import TensorPool
+    from trainscale_b200.parallel.pipeline import (ActivationMemoryManager, CheckpointFunction, CommunicationConfig,
+                                                   GradientBucket, InterleavedOneFOneBSchedule, MemoryConfig,
+                                                   P2PCommunicator, PipelineConfig, PipelineStage, VirtualPipelineStage)
+    mem = ActivationMemoryManager(MemoryConfig(), "cpu")
+    mem.stash_activation(0, 1, torch.ones(2))
+    assert torch.equal(mem.pop_activation(0, 1), torch.ones(2))
+    mem.stash_activation(stage_id=1, microbatch_id=2, activation=torch.zeros(1))
+    assert mem.pop_activation(stage_id=1, microbatch_id=2).numel() == 1
+    comm = P2PCommunicator(CommunicationConfig(), "cpu", None)
+    assert comm.send_async(torch.ones(1), dst_rank=1, tag=0).is_err()           # no process group: an Err, not a raise
+    assert comm.recv_sync(src_rank=0).is_err()
+    bucket = GradientBucket(max_size_bytes=100, device="cpu", dtype=torch.float16)
+    assert (bucket.capacity, bucket.dtype, bucket.device) == (100, torch.float16, "cpu")
+    lin = nn.Linear(4, 4)
+    x = torch.randn(2, 4, requires_grad=True)
+    CheckpointFunction.apply(lambda a: lin(a).relu(), True, x).sum().backward()
+    recomputed = lin.weight.grad.clone()
+    lin.zero_grad()
+    lin(x).relu().sum().backward()
+    assert torch.allclose(recomputed, lin.weight.grad)
+    config = PipelineConfig(num_stages=2, num_microbatches=2, memory=MemoryConfig(enable_activation_checkpointing=True))
+    stage = PipelineStage(lin, 0, 2, None, config)
+    assert stage.checkpoint_activations and stage(input_=x, checkpoint=True).shape == (2, 4)
+    virtual = VirtualPipelineStage([stage, stage], virtual_stage_id=0, physical_stage_id=0)
+    assert virtual.virtual_stage_id == 0 and virtual.forward(x, 1, True).shape == (2, 4) and virtual.forward(0, x).shape == (2, 4)
+    native = VirtualPipelineStage([stage, stage], 1, 2)
+    assert native.virtual_stage_id(1) == 3
+    sched = InterleavedOneFOneBSchedule([PipelineStage(nn.Linear(4, 4), i, 4) for i in range(4)],
+                                        PipelineConfig(num_stages=2, num_microbatches=2, schedule="interleaved"),
+                                        lambda a, b: (a - b).pow(2).mean(), num_chunks=2)
+    assert sched.num_chunks == 2 and sched.config.num_virtual_stages == 2
+    model = nn.Sequential(lin)
+    assert ActivationCheckpoint(config=ActivationCheckpointConfig()).apply(model, batch_size=2, seq_len=16) is model
+    assert SelectiveCheckpointPolicy(config=ActivationCheckpointConfig()).config is not None
+    assert ActivationOffloader(ActivationCheckpointConfig(), torch.device("cpu")).min_bytes == 1 << 20
+    pool = ActivationPool(initial_capacity=2, max_capacity=1, device="cpu")
+    pool.release(tensor=pool.acquire((2, 2), torch.float32))
+    pool.release(tensor=torch.ones(3))                                         # over the buffer bound: not kept
+    assert pool.get_stats()["buffers_cached"] == 1
+    tensors = TensorPool("cpu", pin_memory=True)
+    tensors.free(tensor=tensors.acquire((4,)))
+    assert tensors.get_stats()["releases"] == 1

@@ -156,6 +156,7 @@ class SelectiveCheckpointPolicy:
     _KINDS = {"attention": ("attention", "attn"), "ffn": ("mlp", "ffn", "feed_forward", "feedforward"),
               "layernorm": ("layernorm", "layer_norm", "rmsnorm", "rms_norm"), "residual": ("residual", "skip")}
 
+    @reference_kwargs(config="cfg")
     def __init__(self, cfg: ActivationCheckpointConfig | None = None, num_layers: int = 0):
         self.cfg, self.L = cfg or ActivationCheckpointConfig(), num_layers
         self.config = self.cfg
@@ -209,6 +210,7 @@ class SelectiveCheckpointPolicy:
 
 
 class ActivationCheckpoint:
+    @reference_kwargs(config="cfg")
     def __init__(self, cfg: ActivationCheckpointConfig | None = None):
         self.cfg = cfg or ActivationCheckpointConfig()
         self.config = self.cfg
@@ -264,9 +266,21 @@ class ActivationCheckpoint:
         self.profiler.clear()
         self._stats = {"layers_wrapped": 0, "applications": 0}
 
-    def apply(self, model) -> list[int]:
+    def apply(self, model, batch_size: int | None = None, seq_len: int | None = None):
         """Configure the framework decoder (it recomputes layer i when i % checkpoint_every == 0) or wrap generic
-        `nn.ModuleList` layers with torch's checkpoint wrapper. Returns the checkpointed layer indices."""
+        `nn.ModuleList` layers with torch's checkpoint wrapper. Returns the checkpointed layer indices.
+
+        `apply(model, batch_size, seq_len)` is the reference's form: the expected activation size of a layer is
+        recorded in the statistics and the (modified) MODEL is returned, its chosen layers in
+        `model._ts_checkpointed_layers` (data_pipeline/trainer/distributed/activation_checkpoint.py:1875)."""
+        if batch_size is not None or seq_len is not None:
+            chosen = self.apply(model)
+            hidden = getattr(getattr(model, "config", None), "hidden_size", None)
+            if hidden:
+                self._stats["layer_activation_bytes"] = self.profiler.estimate_activation_memory(
+                    int(batch_size or 1), int(seq_len or 4096), int(hidden))
+            model._ts_checkpointed_layers, model._ts_activation_checkpoint = chosen, self
+            return model
         inner = getattr(model, "model", model)
         layers = getattr(inner, "layers", None)
         if layers is None:
@@ -323,7 +337,14 @@ class ActivationOffloader:
     """`with offloader.scope():` moves saved activations >= min_bytes to pinned host memory on a copy stream and
     brings them back on demand in backward (saved-tensor hooks)."""
 
-    def __init__(self, min_bytes: int = 1 << 20):
+    def __init__(self, min_bytes: "int | ActivationCheckpointConfig" = 1 << 20, device=None, *, config=None):
+        """`ActivationOffloader(min_bytes)`, or the reference's `(config, device)`: tensors below the configuration's
+        `offload_min_bytes` (1 MiB when it has none) stay on the device."""
+        if isinstance(min_bytes, ActivationCheckpointConfig):
+            config, min_bytes = min_bytes, None
+        if config is not None and min_bytes is None or config is not None and min_bytes == 1 << 20:
+            min_bytes = int(getattr(config, "offload_min_bytes", 1 << 20))
+        self.config, self.device = config, device
         self.min_bytes = min_bytes
         self.pool = PinnedTensorPool()
         self.cuda = torch.cuda.is_available()
@@ -479,6 +500,7 @@ class ChunkOffloadHandler(ActivationOffloader):
         self.offload_groups, self._reloaded, self._pending = [], set(), {}
         self.torch_tensor_count = 0
 
+    @reference_kwargs(src_tensor="src")
     def offload_tensor(self, src: torch.Tensor, use_cpu_pool: bool = True):
         """Copy `src` to the host; returns the state that `reload_tensor` takes: (device, host tensor, pooled, group)."""
         host = self.pool.get(src.shape, src.dtype) if use_cpu_pool else torch.empty(src.shape, dtype=src.dtype)
@@ -746,8 +768,12 @@ class ActivationPool:
     """Device buffers for recomputed activations, recycled by (shape, dtype): a layer's recomputation in step n reuses
     the storage its recomputation used in step n-1 instead of going through the allocator."""
 
-    def __init__(self, max_bytes: int = 8 * 2 ** 30):
+    def __init__(self, max_bytes: int = 8 * 2 ** 30, *, initial_capacity: int | None = None,
+                 max_capacity: int | None = None, device=None):
+        """`max_bytes` bounds the bytes kept; `max_capacity` (the reference's bound) the NUMBER of buffers kept;
+        `device`: where `acquire` allocates by default; `initial_capacity` is a hint only (buffers appear on release)."""
         self.max_bytes = max_bytes
+        self.max_capacity, self.initial_capacity, self.device = max_capacity, initial_capacity, device
         self._free: dict[tuple, list[torch.Tensor]] = {}
         self.bytes_cached = 0
         self.hits = self.misses = 0
@@ -767,6 +793,8 @@ class ActivationPool:
         nb = t.numel() * t.element_size()
         if self.bytes_cached + nb > self.max_bytes:
             return
+        if self.max_capacity is not None and sum(len(v) for v in self._free.values()) >= self.max_capacity:
+            return
         self._free.setdefault((tuple(t.shape), t.dtype, str(t.device)), []).append(t.detach())
         self.bytes_cached += nb
 
@@ -774,10 +802,12 @@ class ActivationPool:
         self._free.clear()
         self.bytes_cached = 0
 
-    def acquire(self, shape, dtype: torch.dtype = torch.bfloat16, device="cpu") -> torch.Tensor:
-        return self.get(shape, dtype, device)
+    def acquire(self, shape, dtype: torch.dtype = torch.bfloat16, device=None) -> torch.Tensor:
+        return self.get(shape, dtype, device if device is not None else (self.device if self.device is not None else "cpu"))
 
-    release = put
+    @reference_kwargs(tensor="t")
+    def release(self, t: torch.Tensor) -> None:
+        self.put(t)
 
     @property
     def hit_rate(self) -> float:

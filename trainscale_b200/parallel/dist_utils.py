@@ -260,8 +260,13 @@ class TensorPool:
     staging copies do not hit the allocator every step (data_pipeline/trainer/distributed/sota_utils.py:511-640).
     `acquire(shape, dtype)` returns a view of a pooled buffer, `release(t)` gives it back."""
 
-    def __init__(self, device=None, max_bytes: int = 4 * 2 ** 30):
+    def __init__(self, device=None, max_bytes: int = 4 * 2 ** 30, *, pin_memory: bool = False):
+        """`pin_memory`: host-side pools allocate page-locked buffers (when a CUDA device is present), for staging
+        copies that overlap with compute (data_pipeline/trainer/distributed/activation_offload.py TensorPool)."""
+        if isinstance(max_bytes, bool):                          # TensorPool(device, pin_memory)
+            pin_memory, max_bytes = max_bytes, 4 * 2 ** 30
         self.device = torch.device(device) if device is not None else torch.device("cpu")
+        self.pin_memory = bool(pin_memory) and self.device.type == "cpu" and torch.cuda.is_available()
         self.max_bytes = max_bytes
         self._free: dict[tuple, list[torch.Tensor]] = {}
         self._owner: dict[int, torch.Tensor] = {}
@@ -284,7 +289,7 @@ class TensorPool:
             self._held -= cls_bytes
             self._stats["hits"] += 1
         else:
-            buf = torch.empty(cls_bytes // esz, dtype=dtype, device=self.device)
+            buf = torch.empty(cls_bytes // esz, dtype=dtype, device=self.device, pin_memory=self.pin_memory)
         out = buf[:n].view(shape)
         self._owner[out.data_ptr()] = buf
         return out.zero_() if zero else out
@@ -301,12 +306,16 @@ class TensorPool:
         self._free.setdefault((nbytes, buf.dtype), []).append(buf)
         self._held += nbytes
 
-    def free(self) -> None:
-        """Drop every pooled buffer (outstanding tensors stay valid)."""
+    def free(self, tensor: torch.Tensor | None = None) -> None:
+        """`free()` drops every pooled buffer (outstanding tensors stay valid); `free(tensor)` gives one tensor back to
+        the pool, like `release`."""
+        if tensor is not None:
+            return self.release(tensor)
         self._free.clear()
         self._held = 0
 
-    reset = free
+    def reset(self) -> None:
+        self.free()
 
     def get_stats(self) -> dict:
         a = self._stats["acquires"]

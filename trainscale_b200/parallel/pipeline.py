@@ -160,10 +160,11 @@ class DistributedContext:
             return 0
         return self._ranks.index(self.rank) if self._ranks is not None else dist.get_rank(self.group)
 
-    def initialize_pipeline_group(self, ranks: Sequence[int]) -> "DistributedContext":
-        """Collective over the whole job: creates the group of `ranks` (every rank must call it with the same list)."""
+    def initialize_pipeline_group(self, ranks: Sequence[int], backend: str | None = None) -> "DistributedContext":
+        """Collective over the whole job: creates the group of `ranks` (every rank must call it with the same list);
+        `backend`: of the new group (that of the default group when None)."""
         self._ranks = list(ranks)
-        self.group = dist.new_group(self._ranks) if dist.is_initialized() else None
+        self.group = dist.new_group(self._ranks, backend=backend) if dist.is_initialized() else None
         return self
 
     def global_rank_of(self, pipeline_rank: int) -> int:
@@ -247,12 +248,30 @@ class ActivationMemoryManager:
             return sum(ActivationMemoryManager._nbytes(o) for o in obj)
         return 0
 
-    def stash_activation(self, key: tuple, value: Any) -> None:
+    @staticmethod
+    def _key(key, microbatch_id, stage_id):
+        if stage_id is not None or microbatch_id is not None:
+            return (key if stage_id is None else stage_id, microbatch_id)
+        return key
+
+    def stash_activation(self, key: "tuple | int | None" = None, value: Any = None, activation: Any = None, *,
+                         stage_id: int | None = None, microbatch_id: int | None = None) -> None:
+        """`stash_activation(key, value)`, or `(stage_id, microbatch_id, activation)`: the key is then the pair."""
+        if activation is not None or stage_id is not None or microbatch_id is not None:
+            if activation is None:                       # (stage_id, microbatch_id, activation) positionally
+                raise TypeError("stash_activation(stage_id, microbatch_id, activation) needs the activation")
+            if stage_id is None and microbatch_id is None:
+                key, value = (key, value), activation
+            else:
+                key, value = self._key(key, microbatch_id if microbatch_id is not None else value, stage_id), activation
         self._stash[key] = value
         self._cur += self._nbytes(value)
         self._peak = max(self._peak, self._cur)
 
-    def pop_activation(self, key: tuple) -> Any:
+    def pop_activation(self, key: "tuple | int | None" = None, microbatch_id: int | None = None, *,
+                       stage_id: int | None = None) -> Any:
+        """`pop_activation(key)` or `pop_activation(stage_id, microbatch_id)`."""
+        key = self._key(key, microbatch_id, stage_id)
         v = self._stash.pop(key)
         self._cur -= self._nbytes(v)
         return v
@@ -317,9 +336,22 @@ class P2PCommunicator:
     """Sends / receives of activations and their gradients between pipeline ranks.  With `static_shapes` the shape and
     dtype of a link's tensor travel once (a small int64 header) and are assumed afterwards."""
 
-    def __init__(self, ctx: DistributedContext | None = None, device: torch.device | str = "cpu",
-                 config: CommunicationConfig | None = None, pool: TensorPool | None = None):
+    def __init__(self, ctx: "DistributedContext | CommunicationConfig | PipelineConfig | None" = None,
+                 device: torch.device | str = "cpu", config: CommunicationConfig | None = None,
+                 pool: TensorPool | None = None, *, group=None):
+        """`P2PCommunicator(ctx, device, config, pool)`, or the reference's `(config, device, group)` with the
+        communication (or whole pipeline) configuration first and the process group of the pipeline
+        (data_pipeline/trainer/distributed/pipeline_parallel.py:629)."""
+        if isinstance(ctx, (CommunicationConfig, PipelineConfig)):
+            if config is not None and not isinstance(config, CommunicationConfig):
+                group, config = config, None                             # positional (config, device, group)
+            config, ctx = ctx, None
+        if isinstance(config, PipelineConfig):
+            config = config.communication
+        if group is not None:
+            ctx = DistributedContext(group)
         self.ctx = ctx or _DEFAULT_CTX
+        self.group = self.ctx.group
         self.device = torch.device(device)
         self.config = config or CommunicationConfig()
         self.pool = pool
@@ -349,7 +381,24 @@ class P2PCommunicator:
         self._meta[tag_key] = md
         return md
 
-    def send_async(self, tensor: torch.Tensor, dst: int, kind: str = "act"):
+    def _as_result(self, fn, *args):
+        """The reference's spelling (`dst_rank=` / `src_rank=`, integer `tag=`) returns Ok(...) / Err(...) instead of raising."""
+        from ..core.types import Err, Ok
+        if not (dist.is_available() and dist.is_initialized()):
+            return Err(RuntimeError(f"{PipelineError.COMMUNICATION.value}: torch.distributed is not initialised"))
+        try:
+            return Ok(fn(*args))
+        except (RuntimeError, ValueError) as e:
+            return Err(RuntimeError(f"{PipelineError.COMMUNICATION.value}: {e}"))
+
+    @staticmethod
+    def _kind(kind, tag):
+        return kind if tag is None else f"tag{int(tag)}"
+
+    def send_async(self, tensor: torch.Tensor, dst: int | None = None, kind: str = "act", *, dst_rank: int | None = None,
+                   tag: int | None = None):
+        if dst_rank is not None or tag is not None:
+            return self._as_result(self.send_async, tensor, dst_rank if dst_rank is not None else dst, self._kind(kind, tag))
         t = tensor.detach().contiguous()
         self._send_meta(t, dst, ("s", dst, kind))
         w = dist.isend(t, dst, group=self.ctx.group)
@@ -357,7 +406,10 @@ class P2PCommunicator:
         self.bytes_sent += t.numel() * t.element_size()
         return w
 
-    def recv_async(self, src: int, kind: str = "act", meta: TensorMetadata | None = None):
+    def recv_async(self, src: int | None = None, kind: str = "act", meta: TensorMetadata | None = None, *,
+                   src_rank: int | None = None, tag: int | None = None):
+        if src_rank is not None or tag is not None:
+            return self._as_result(self.recv_async, src_rank if src_rank is not None else src, self._kind(kind, tag), meta)
         md = meta or self._recv_meta(src, ("r", src, kind))
         buf = self.pool.allocate(md.shape, md.dtype) if self.pool is not None else \
             torch.empty(md.shape, dtype=md.dtype, device=self.device)
@@ -365,10 +417,15 @@ class P2PCommunicator:
         self.bytes_received += buf.numel() * buf.element_size()
         return buf, w
 
-    def send_sync(self, tensor: torch.Tensor, dst: int, kind: str = "act") -> None:
+    def send_sync(self, tensor: torch.Tensor, dst: int | None = None, kind: str = "act", *, dst_rank: int | None = None):
+        if dst_rank is not None:
+            return self._as_result(self.send_sync, tensor, dst_rank, kind)
         self.send_async(tensor, dst, kind).wait()
 
-    def recv_sync(self, src: int, kind: str = "act", meta: TensorMetadata | None = None) -> torch.Tensor:
+    def recv_sync(self, src: int | None = None, kind: str = "act", meta: TensorMetadata | None = None, *,
+                  src_rank: int | None = None):
+        if src_rank is not None:
+            return self._as_result(self.recv_sync, src_rank, kind, meta)
         buf, w = self.recv_async(src, kind, meta)
         w.wait()
         return buf
@@ -420,8 +477,11 @@ class P2PCommunicator:
 class GradientBucket:
     """Flat gradient bucket of a stage, all-reduced over its data-parallel group in one call."""
 
-    def __init__(self, capacity_bytes: int = 25 * 2 ** 20, dtype: torch.dtype = torch.float32):
-        self.capacity, self.dtype = capacity_bytes, dtype
+    @reference_kwargs(max_size_bytes="capacity_bytes")
+    def __init__(self, capacity_bytes: int = 25 * 2 ** 20, dtype: torch.dtype = torch.float32, device=None):
+        if not isinstance(dtype, torch.dtype):                  # (max_size_bytes, device, dtype)
+            dtype, device = (device if isinstance(device, torch.dtype) else torch.float32), dtype
+        self.capacity, self.dtype, self.device = capacity_bytes, dtype, device
         self._items: list[tuple[torch.Tensor, torch.Tensor]] = []
         self._bytes = 0
 
@@ -451,10 +511,15 @@ class CheckpointFunction(torch.autograd.Function):
     """Recompute-in-backward for one stage call: keeps the inputs and the RNG state, drops everything else."""
 
     @staticmethod
-    def forward(ctx, run_fn, n_inputs, *args):
+    def forward(ctx, run_function, preserve_rng_state, *args):
+        """`apply(run_function, preserve_rng_state, *inputs)`; an int in the second place is the number of leading
+        `args` that are inputs (the rest are ignored), with the RNG state kept."""
+        run_fn = run_function
+        n_inputs = len(args) if isinstance(preserve_rng_state, bool) else int(preserve_rng_state)
         ctx.run_fn = run_fn
-        ctx.cpu_rng = torch.get_rng_state()
-        ctx.cuda_rng = torch.cuda.get_rng_state() if torch.cuda.is_available() and any(
+        ctx.preserve_rng = preserve_rng_state is not False
+        ctx.cpu_rng = torch.get_rng_state() if ctx.preserve_rng else None
+        ctx.cuda_rng = torch.cuda.get_rng_state() if ctx.preserve_rng and torch.cuda.is_available() and any(
             torch.is_tensor(a) and a.is_cuda for a in args) else None
         ctx.save_for_backward(*[a for a in args[:n_inputs] if torch.is_tensor(a)])
         ctx.layout = [torch.is_tensor(a) for a in args[:n_inputs]]
@@ -470,8 +535,9 @@ class CheckpointFunction(torch.autograd.Function):
             if torch.is_tensor(x) and not x.is_floating_point():
                 x.requires_grad_(False)
         devs = [torch.cuda.current_device()] if ctx.cuda_rng is not None else []
-        with torch.random.fork_rng(devices=devs):
-            torch.set_rng_state(ctx.cpu_rng)
+        with torch.random.fork_rng(devices=devs, enabled=ctx.preserve_rng):
+            if ctx.preserve_rng:
+                torch.set_rng_state(ctx.cpu_rng)
             if ctx.cuda_rng is not None:
                 torch.cuda.set_rng_state(ctx.cuda_rng)
             with torch.enable_grad():
@@ -501,8 +567,14 @@ class PipelineStage(nn.Module):
     """One stage: a module plus its place in the pipeline, optional recompute, and forward timing."""
 
     def __init__(self, module: nn.Module, stage_id: int, num_stages: int, device: torch.device | str | None = None,
-                 checkpoint_activations: bool = False):
+                 checkpoint_activations: "bool | PipelineConfig" = False, *, config: "PipelineConfig | None" = None):
+        """`config`: the pipeline configuration; activations are recomputed when its memory section asks for it."""
         super().__init__()
+        if isinstance(checkpoint_activations, PipelineConfig):           # (module, stage_id, num_stages, device, config)
+            config, checkpoint_activations = checkpoint_activations, False
+        if config is not None:
+            checkpoint_activations = checkpoint_activations or bool(config.memory.enable_activation_checkpointing)
+        self.config = config
         self.module = module
         self.stage_id, self.num_stages = stage_id, num_stages
         self.checkpoint_activations = checkpoint_activations
@@ -523,9 +595,13 @@ class PipelineStage(nn.Module):
     def is_last(self) -> bool:
         return self.stage_id == self.num_stages - 1
 
-    def forward(self, *inputs):
+    def forward(self, *inputs, input_=None, checkpoint: bool | None = None):
+        """`stage(*inputs)`; `stage(input_=x, checkpoint=True)` recomputes this call whatever the stage's setting."""
+        if input_ is not None:
+            inputs = (input_,) + inputs
+        on = self.checkpoint_activations and self.training if checkpoint is None else bool(checkpoint)
         t0 = time.perf_counter()
-        out = selective_checkpoint(self.module, *inputs, enabled=self.checkpoint_activations and self.training)
+        out = selective_checkpoint(self.module, *inputs, enabled=on)
         self._times.append((time.perf_counter() - t0) * 1e3)
         return out
 
@@ -538,20 +614,48 @@ class PipelineStage(nn.Module):
 class VirtualPipelineStage:
     """The V model chunks one rank holds under the interleaved schedule (virtual stage = chunk * P + rank)."""
 
-    def __init__(self, stages: Sequence[PipelineStage], physical_rank: int, num_physical: int):
-        self.stages, self.physical_rank, self.num_physical = list(stages), physical_rank, num_physical
+    class _StageId(int):
+        """This rank's first virtual stage as an int; called with a chunk id it gives that chunk's virtual stage."""
+
+        def __new__(cls, value, step):
+            self = int.__new__(cls, value)
+            self.step = step
+            return self
+
+        def __call__(self, chunk_id: int) -> int:
+            return int(chunk_id) * self.step + int(self) % self.step if self.step else int(self)
+
+    def __init__(self, stages: Sequence[PipelineStage], physical_rank: int | None = None, num_physical: int | None = None, *,
+                 virtual_stage_id: int | None = None, physical_stage_id: int | None = None):
+        """`VirtualPipelineStage(stages, physical_rank, num_physical)`; with the reference's keywords
+        (`virtual_stage_id`, `physical_stage_id`) the number of physical stages is taken from the stages themselves
+        (data_pipeline/trainer/distributed/pipeline_parallel.py:1101)."""
+        self.stages = list(stages)
+        if virtual_stage_id is not None or physical_stage_id is not None:
+            physical_rank = physical_stage_id if physical_stage_id is not None else 0
+            total = getattr(self.stages[0], "num_stages", len(self.stages)) if self.stages else 1
+            num_physical = max(1, total // max(1, len(self.stages)))
+        self.physical_rank, self.num_physical = int(physical_rank or 0), int(num_physical or 1)
+        self.physical_stage_id = self.physical_rank
+        first = virtual_stage_id if virtual_stage_id is not None else self.physical_rank
+        self.virtual_stage_id = self._StageId(first, self.num_physical)
+        self.num_stages = len(self.stages)
 
     @property
     def num_chunks(self) -> int:
         return len(self.stages)
 
     def get_stage(self, chunk_id: int) -> PipelineStage:
-        return self.stages[chunk_id]
+        return self.stages[chunk_id % len(self.stages)]
 
-    def virtual_stage_id(self, chunk_id: int) -> int:
-        return chunk_id * self.num_physical + self.physical_rank
-
-    def forward(self, chunk_id: int, *inputs):
+    def forward(self, chunk_id=None, *inputs, input_=None, checkpoint: bool | None = None):
+        """`forward(chunk_id, *inputs)`, or the reference's `forward(input_, chunk_id, checkpoint=False)`."""
+        if torch.is_tensor(chunk_id):                                   # (input_, chunk_id, checkpoint)
+            input_, chunk_id, inputs = chunk_id, inputs[0], inputs[1:]
+            if inputs and isinstance(inputs[0], bool):
+                checkpoint, inputs = inputs[0], inputs[1:]
+        if input_ is not None:
+            return self.get_stage(chunk_id)(input_, *inputs, checkpoint=checkpoint)
         return self.stages[chunk_id](*inputs)
 
     __call__ = forward
@@ -840,6 +944,20 @@ class OneFOneBSchedule(PipelineSchedule):
 class InterleavedOneFOneBSchedule(PipelineSchedule):
     """1F1B over V model chunks per rank (virtual stage = chunk * P + rank): the bubble shrinks by 1/V."""
     schedule_name = "interleaved"
+
+    def __init__(self, stages, config, loss_fn, communicator=None, memory_manager=None, ctx=None, *,
+                 num_chunks: int | None = None):
+        """`num_chunks`: model chunks per rank; must agree with `config.num_virtual_stages` (which it sets when that is
+        still 1)."""
+        if isinstance(ctx, int) and num_chunks is None:                 # (..., memory_manager, num_chunks) positionally
+            num_chunks, ctx = ctx, None
+        if num_chunks is not None and int(num_chunks) != config.num_virtual_stages:
+            if config.num_virtual_stages != 1:
+                raise ValueError(f"num_chunks={num_chunks} but config.num_virtual_stages={config.num_virtual_stages}")
+            import dataclasses
+            config = dataclasses.replace(config, num_virtual_stages=int(num_chunks))
+        super().__init__(stages, config, loss_fn, communicator, memory_manager, ctx)
+        self.num_chunks = config.num_virtual_stages
 
 
 class ZeroBubbleSchedule(PipelineSchedule):
