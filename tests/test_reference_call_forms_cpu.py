@@ -447,3 +447,52 @@ def test_pipeline_and_checkpoint_classes_take_the_reference_forms():
     tensors = TensorPool("cpu", pin_memory=True)
     tensors.free(tensor=tensors.acquire((4,)))
     assert tensors.get_stats()["releases"] == 1
+
+
+def test_zero_bubble_classes_take_the_reference_forms():
+    import torch.nn as nn
+    from trainscale_b200.parallel.pipeline import ActivationMemoryManager, MemoryConfig
+    from trainscale_b200.parallel.zbpp import (GradientDecomposer, ModelPartitioner, PipelineStageModule, ScheduleConfig,
+                                               SplitBackwardFunction, StageProfile, ZBPPBenchmark, ZBPPOptimizer,
+                                               ZBPPRuntimeEngine, ZeroBubblePipeline)
+    torch.manual_seed(0)
+    decomposer = GradientDecomposer(False, torch.float32, True)
+    memory = ActivationMemoryManager(MemoryConfig(), "cpu")
+    x = torch.randn(6, 8, requires_grad=True)
+    lin = nn.Linear(8, 4)
+    y = SplitBackwardFunction.apply(x, lin.weight, lin.bias, 1, 3, decomposer, memory)
+    go = torch.randn_like(y)
+    y.backward(go)
+    want = torch.autograd.grad(lin(x), [x, lin.weight, lin.bias], go)
+    assert torch.allclose(x.grad, want[0], atol=1e-6) and torch.allclose(lin.bias.grad, want[2], atol=1e-6)
+    assert lin.weight.grad is None                                             # the weight gradient is deferred ...
+    deferred = decomposer.compute_b_params(memory.retrieve_activation(3, "stage_1_input"),
+                                           memory.retrieve_activation(3, "stage_1_grad_output"), lin.weight)
+    assert torch.allclose(deferred, want[1], atol=1e-5)                        # ... and comes out of what was stored
+    bench = ZBPPBenchmark(torch.device("cpu"), torch.float32)
+    assert bench.validate_gradient_decomposition(8, 16, 12) is True
+    assert bench.validate_schedule_optimality(4, 8) is True and bench.validate_memory_compliance(4, 8, 256) is True
+    stages = [PipelineStageModule(nn.Sequential(nn.Linear(8, 8), nn.Tanh()), i, decomposer, memory, torch.float32)
+              for i in range(2)]
+    config = ScheduleConfig(2, 4, 1 << 30, [StageProfile(100., 100., 100., 1, 0, 0., 0.) for _ in range(2)])
+    optimizer = ZBPPOptimizer([p for s in stages for p in s.parameters()], lr=1e-2, use_triton=True)
+    engine = ZBPPRuntimeEngine(stages, config, optimizer, rank=0, world_size=1, device=torch.device("cpu"),
+                               dtype=torch.float32)
+    batches = [torch.randn(3, 8) for _ in range(4)]
+    labels = [torch.randn(3, 8) for _ in range(4)]
+    first = engine.train_step(batches, labels, nn.functional.mse_loss)
+    second = engine.train_step(micro_batches=batches, labels=labels)
+    assert set(first) >= {"loss", "bubble_fraction", "throughput_samples_per_s"} and second["loss"] < first["loss"]
+    with pytest.raises(ValueError):
+        engine.train_step(micro_batches=batches[:2], labels=labels[:2])
+    assert engine.profile_stage(batches[0], 1, 2).forward_us > 0
+    pipe = ZeroBubblePipeline(nn.Sequential(*[nn.Linear(8, 8) for _ in range(4)]), 2, 4)
+    assert torch.is_tensor(pipe.train_step(torch.randn(8, 8), torch.randn(8, 8)))
+    assert "loss" in pipe.train_step(micro_batches=batches, labels=labels, loss_fn=nn.functional.l1_loss)
+    assert pipe.engine.loss_fn is nn.functional.l1_loss
+    pipe.train_step(torch.randn(8, 8), torch.randn(8, 8))
+    assert pipe.engine.loss_fn is not nn.functional.l1_loss                    # the per-step loss did not stick
+    assert len(pipe.profile_stages(batches[0], num_warmup=1, num_iterations=1)) == 2
+    assert ModelPartitioner(nn.Sequential(*[nn.Linear(8, 8) for _ in range(4)]), 2, balance_metric="layers").costs == [1.0] * 4
+    assert stages[0](input_tensor=batches[0], microbatch_id=7).shape == (3, 8)
+    assert memory.retrieve_activation(7, "stage_0_input").shape == (3, 8)

@@ -25,6 +25,7 @@ import torch.nn as nn
 
 from . import pipeline as PL
 from . import pp as PP
+from ..utils.refargs import ANY, reference_kwargs
 
 
 class OpType(enum.IntEnum):
@@ -309,16 +310,39 @@ class ZBPPScheduleOptimizer:
 class GradientDecomposer:
     """B_input / B_params as two walks over one retained autograd graph."""
 
-    def __init__(self, use_triton: bool = False):
+    def __init__(self, use_triton: bool = False, dtype: torch.dtype | None = None, accumulate_grads: bool = True):
+        """`dtype`: of the gradients the linear forms return (that of their operands when None); `accumulate_grads`:
+        default of `compute_b_params(..., accumulate=)` for instances."""
         self._triton = False        # there is no Triton path: autograd + the framework's own kernels do the work
+        self.dtype, self.accumulate_grads = dtype, accumulate_grads
 
     @property
     def using_triton(self) -> bool:
         return self._triton
 
     @staticmethod
-    def compute_b_input(output: torch.Tensor, inputs: Sequence[torch.Tensor], grad_output: torch.Tensor | None,
-                        retain_graph: bool = True) -> tuple[torch.Tensor | None, ...]:
+    def _linear_b_input(grad_output: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+        """dL/dx of y = x W^T: grad_output [.., Out] @ weight [Out, In] (tensor-core GEMM on CUDA bf16)."""
+        from ..ops import gemm
+        return gemm.matmul_nn(grad_output, weight).view(*grad_output.shape[:-1], weight.shape[1])
+
+    @staticmethod
+    def _linear_b_params(input_tensor: torch.Tensor, grad_output: torch.Tensor, weight: torch.Tensor | None = None):
+        """dL/dW of y = x W^T: grad_output^T [Out, N] @ input [N, In]."""
+        from ..ops import gemm
+        go = grad_output.reshape(-1, grad_output.shape[-1])
+        return gemm.matmul_tn(go, input_tensor.reshape(-1, input_tensor.shape[-1]))
+
+    @staticmethod
+    def compute_b_input(output: torch.Tensor = None, inputs: "Sequence[torch.Tensor] | torch.Tensor" = None,
+                        grad_output: torch.Tensor | None = None, retain_graph: bool = True, *,
+                        weight: torch.Tensor | None = None) -> "tuple[torch.Tensor | None, ...] | torch.Tensor":
+        """`compute_b_input(output, inputs, grad_output)`: input gradients by a walk over the retained graph.
+        `compute_b_input(grad_output, weight)` is the closed form for a linear layer
+        (data_pipeline/trainer/distributed/zbpp.py GradientDecomposer.compute_b_input)."""
+        if weight is not None or torch.is_tensor(inputs):
+            return GradientDecomposer._linear_b_input(grad_output if output is None else output,
+                                                      weight if weight is not None else inputs)
         ins = [x for x in inputs if torch.is_tensor(x) and x.requires_grad]
         if not ins:
             return tuple(None for _ in inputs)
@@ -326,8 +350,17 @@ class GradientDecomposer:
         return tuple(next(gs) if torch.is_tensor(x) and x.requires_grad else None for x in inputs)
 
     @staticmethod
-    def compute_b_params(output: torch.Tensor, params: Sequence[nn.Parameter], grad_output: torch.Tensor | None,
-                         accumulate: bool = True) -> list[torch.Tensor | None]:
+    def compute_b_params(output: torch.Tensor = None, params: "Sequence[nn.Parameter] | torch.Tensor" = None,
+                         grad_output: torch.Tensor | None = None, accumulate: bool = True, *,
+                         input_tensor: torch.Tensor | None = None, weight: torch.Tensor | None = None):
+        """`compute_b_params(output, params, grad_output)`: parameter gradients by a second walk over the graph.
+        `compute_b_params(input_tensor, grad_output, weight)` is the closed form for a linear layer and returns dL/dW."""
+        if input_tensor is not None or (torch.is_tensor(params) and not isinstance(params, nn.Parameter)) \
+                or (torch.is_tensor(params) and torch.is_tensor(output) and params.dim() >= 2 and output.dim() >= 2
+                    and params.shape[:-1] == output.shape[:-1] and output.grad_fn is None):
+            x = input_tensor if input_tensor is not None else output
+            go = params if torch.is_tensor(params) else grad_output
+            return GradientDecomposer._linear_b_params(x, go, weight)
         ps = [p for p in params if p.requires_grad]
         gs = torch.autograd.grad(output, ps, grad_output, allow_unused=True) if ps else ()
         if accumulate:
@@ -338,7 +371,7 @@ class GradientDecomposer:
         return list(gs)
 
 
-class SplitBackwardFunction(torch.autograd.Function):
+class _StageSplitFunction(torch.autograd.Function):
     """Wraps one stage call inside an outer graph: backward returns only the input gradients and parks the weight
     gradient work (a closure over the retained inner graph) on the stage's queue."""
 
@@ -359,21 +392,67 @@ class SplitBackwardFunction(torch.autograd.Function):
         return (None, None) + tuple(gx)
 
 
+class SplitBackwardFunction(torch.autograd.Function):
+    """One linear layer y = x W^T + b with a split backward: `apply(input_tensor, weight, bias, stage_id, microbatch_id,
+    decomposer, memory_manager)`.  Backward returns dL/dx (and the cheap dL/db) at once and returns no dL/dW: input and
+    output gradient are left in the memory manager under `stage_<id>_input` / `stage_<id>_grad_output` of the
+    micro-batch, for `decomposer.compute_b_params(input, grad_output, weight)` to run in an idle slot
+    (data_pipeline/trainer/distributed/zbpp.py:505).  Whole stage modules are split by `PipelineStageModule`."""
+
+    @staticmethod
+    def forward(ctx, input_tensor, weight, bias=None, stage_id=0, microbatch_id=0, decomposer=None, memory_manager=None):
+        ctx.save_for_backward(input_tensor, weight)
+        ctx.has_bias = bias is not None
+        ctx.ids, ctx.decomposer, ctx.manager = (stage_id, microbatch_id), decomposer or GradientDecomposer(), memory_manager
+        if memory_manager is not None:
+            memory_manager.store_activation(microbatch_id=microbatch_id, name=f"stage_{stage_id}_input",
+                                            tensor=input_tensor.detach())
+        from ..ops import gemm
+        return gemm.linear(input_tensor, weight, bias)
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        x, w = ctx.saved_tensors
+        gx = ctx.decomposer.compute_b_input(grad_output, w) if ctx.needs_input_grad[0] else None
+        if ctx.manager is not None:
+            ctx.manager.store_activation(microbatch_id=ctx.ids[1], name=f"stage_{ctx.ids[0]}_grad_output",
+                                         tensor=grad_output.detach())
+        gb = grad_output.reshape(-1, grad_output.shape[-1]).sum(0) if ctx.has_bias else None
+        return gx, None, gb, None, None, None, None
+
+
 class PipelineStageModule(nn.Module):
     """A stage whose backward is split: `loss.backward()` through it produces input gradients at once and leaves the
     weight gradients to `execute_deferred_b_params()`."""
 
-    def __init__(self, module: nn.Module, stage_id: int = 0, split_backward: bool = True):
+    def __init__(self, module: nn.Module, stage_id: int = 0, split_backward: "bool | GradientDecomposer" = True,
+                 memory_manager=None, dtype: torch.dtype | None = None, *, decomposer: "GradientDecomposer | None" = None):
+        """`PipelineStageModule(module, stage_id, split_backward)`, or the reference's `(module, stage_id, decomposer,
+        memory_manager, dtype)`: the memory manager then records each micro-batch's stage input (for
+        `forward(input_tensor, microbatch_id)`), `dtype` casts the module
+        (data_pipeline/trainer/distributed/zbpp.py:568)."""
         super().__init__()
-        self.module, self.stage_id, self.split_backward = module, stage_id, split_backward
+        if isinstance(split_backward, GradientDecomposer):
+            decomposer, split_backward = split_backward, True
+        self.module, self.stage_id, self.split_backward = module, stage_id, bool(split_backward)
+        self._decomposer, self._memory_manager, self._dtype = decomposer or GradientDecomposer(), memory_manager, dtype
+        if dtype is not None:
+            self.module.to(dtype)
         self._deferred: list[Callable[[], Any]] = []
 
-    def forward(self, *inputs):
+    def forward(self, *inputs, input_tensor=None, microbatch_id: int | None = None):
+        if input_tensor is not None:
+            inputs = (input_tensor,) + inputs
+        if len(inputs) == 2 and isinstance(inputs[1], int) and not isinstance(inputs[1], bool) and microbatch_id is None:
+            inputs, microbatch_id = inputs[:1], inputs[1]                # (input_tensor, microbatch_id)
+        if microbatch_id is not None and self._memory_manager is not None and torch.is_tensor(inputs[0]):
+            self._memory_manager.store_activation(microbatch_id=microbatch_id, name=f"stage_{self.stage_id}_input",
+                                                  tensor=inputs[0].detach())
         if not (self.split_backward and torch.is_grad_enabled()):
             return self.module(*inputs)
         # the anchor makes autograd visit this node even when no input requires grad (first stage)
         dev = next(self.module.parameters()).device
-        return SplitBackwardFunction.apply(self, torch.zeros((), requires_grad=True, device=dev), *inputs)
+        return _StageSplitFunction.apply(self, torch.zeros((), requires_grad=True, device=dev), *inputs)
 
     @property
     def num_deferred(self) -> int:
@@ -397,7 +476,9 @@ class ZBPPOptimizer:
     factor in the rare step where the global norm exceeds the threshold or another stage saw a non-finite value."""
 
     def __init__(self, params, lr: float = 1e-4, betas=(0.9, 0.999), eps: float = 1e-8, weight_decay: float = 0.01,
-                 max_grad_norm: float | None = 1.0, num_stages: int = 1, enable_sync_bypass: bool = True, group=None):
+                 max_grad_norm: float | None = 1.0, num_stages: int = 1, enable_sync_bypass: bool = True, group=None, *,
+                 use_triton: bool = False):
+        """`use_triton` is accepted and has no effect: the update runs the framework's own fused AdamW kernel."""
         from ..optim import AdamW
         self.params = [p for p in params if p.requires_grad]
         self.inner = AdamW(self.params, lr=lr, betas=betas, eps=eps, weight_decay=weight_decay)
@@ -502,14 +583,29 @@ class ModelPartitioner:
     """Cuts a chain of layers into P contiguous stages with the smallest possible heaviest stage (exact dynamic
     programme over prefix sums, O(n^2 P)); cost = parameter count unless measured costs are given."""
 
-    def __init__(self, model: nn.Module | Sequence[nn.Module], num_stages: int, costs: Sequence[float] | None = None):
+    def __init__(self, model: nn.Module | Sequence[nn.Module], num_stages: int,
+                 costs: "Sequence[float] | str | None" = None, *, balance_metric: str | None = None):
+        """`balance_metric` (when no measured `costs` are given): "params" = parameter count, "flops" = multiply-adds
+        per token (2 x the weights of matrix-shaped parameters; vectors cost nothing), "layers" = every layer equal."""
         self.layers = list(model) if isinstance(model, (nn.Sequential, nn.ModuleList, list, tuple)) \
             else list(model.children())
         if len(self.layers) < num_stages:
             raise ValueError(f"{len(self.layers)} layers cannot fill {num_stages} stages")
         self.num_stages = num_stages
-        self.costs = list(costs) if costs is not None else \
-            [float(sum(p.numel() for p in l.parameters())) + 1.0 for l in self.layers]
+        if isinstance(costs, str):                                       # ModelPartitioner(model, num_stages, "flops")
+            balance_metric, costs = costs, None
+        metric = balance_metric or "params"
+        if metric not in ("params", "flops", "layers"):
+            raise ValueError(f"balance_metric must be 'params', 'flops' or 'layers', got {metric!r}")
+        self.balance_metric = metric
+        if costs is not None:
+            self.costs = list(costs)
+        elif metric == "layers":
+            self.costs = [1.0] * len(self.layers)
+        elif metric == "flops":
+            self.costs = [2.0 * sum(p.numel() for p in l.parameters() if p.dim() >= 2) + 1.0 for l in self.layers]
+        else:
+            self.costs = [float(sum(p.numel() for p in l.parameters())) + 1.0 for l in self.layers]
 
     @staticmethod
     def _dp_partition(costs: Sequence[float], k: int) -> list[int]:
@@ -559,10 +655,41 @@ class ZBPPRuntimeEngine:
     """Profiles the stages, builds the schedule, runs training steps.  `stages`: every stage (one process) or this
     rank's stage (with a `ctx` spanning the pipeline ranks)."""
 
-    def __init__(self, stages: Sequence[nn.Module], num_microbatches: int, loss_fn: Callable, num_stages: int | None = None,
+    def __init__(self, stages: Sequence[nn.Module] | None = None, num_microbatches: "int | ScheduleConfig | None" = None,
+                 loss_fn: "Callable | ZBPPOptimizer | None" = None, num_stages: int | None = None,
                  memory_limit_bytes: int = 4 * 2 ** 30, optimizer_factory: Callable | None = None,
                  enable_sync_bypass: bool = True, ctx: PL.DistributedContext | None = None,
-                 stage_profiles: Sequence[StageProfile] | None = None, enable_interleaving: bool = True):
+                 stage_profiles: Sequence[StageProfile] | None = None, enable_interleaving: bool = True, *,
+                 stage_modules: Sequence[nn.Module] | None = None, schedule_config: ScheduleConfig | None = None,
+                 optimizer: "ZBPPOptimizer | None" = None, rank: int | None = None, world_size: int | None = None,
+                 device=None, dtype: torch.dtype | None = None, grad_scaler=None):
+        """`ZBPPRuntimeEngine(stages, num_microbatches, loss_fn, ...)`, or the reference's `(stage_modules,
+        schedule_config, optimizer, rank, world_size, device, dtype, grad_scaler)`: sizes, memory limit and stage
+        profiles then come from the `ScheduleConfig`, the one optimizer steps after every `train_step`, the loss function
+        arrives with `train_step(micro_batches, labels, loss_fn)`, and with `world_size > 1` the pipeline spans the
+        default process group (data_pipeline/trainer/distributed/zbpp.py:1356)."""
+        stages = stage_modules if stage_modules is not None else stages
+        if isinstance(num_microbatches, ScheduleConfig):                 # positional reference form
+            ref = (num_microbatches, loss_fn, num_stages, memory_limit_bytes, optimizer_factory)
+            schedule_config, optimizer = ref[0], ref[1]
+            rank = ref[2] if rank is None and isinstance(ref[2], int) else rank
+            world_size = ref[3] if world_size is None and ref[3] != 4 * 2 ** 30 else world_size
+            device = ref[4] if device is None else device
+            loss_fn, num_stages, memory_limit_bytes, optimizer_factory = None, None, 4 * 2 ** 30, None
+        self.grad_scaler, self.dtype, self.device = grad_scaler, dtype, device
+        self._single_optimizer = optimizer
+        self._reference_form = schedule_config is not None
+        if schedule_config is not None:
+            num_stages, num_microbatches = schedule_config.num_stages, schedule_config.num_microbatches
+            memory_limit_bytes = schedule_config.memory_limit_bytes
+            stage_profiles = schedule_config.stage_profiles
+            enable_sync_bypass, enable_interleaving = schedule_config.enable_sync_bypass, schedule_config.enable_interleaving
+            # the engine splits the backward itself: a stage that splits its own would leave its weight gradients parked
+            stages = [m.module if isinstance(m, PipelineStageModule) else m for m in stages]
+            if device is not None or dtype is not None:
+                stages = [m.to(device=device, dtype=dtype) for m in stages]
+            if (world_size or 1) > 1 and ctx is None:
+                ctx = PL.DistributedContext(ranks=list(range(world_size)))
         self.ctx = ctx or PL.DistributedContext()
         self.num_stages = num_stages or len(stages)
         self.num_microbatches = num_microbatches
@@ -570,9 +697,12 @@ class ZBPPRuntimeEngine:
         self.enable_sync_bypass, self.enable_interleaving = enable_sync_bypass, enable_interleaving
         self.stages = [m if isinstance(m, PL.PipelineStage) else PL.PipelineStage(m, i, self.num_stages)
                        for i, m in enumerate(stages)]
-        self.loss_fn = loss_fn
+        self.loss_fn = self._ctor_loss_fn = loss_fn
         self.stage_profiles = list(stage_profiles) if stage_profiles is not None else None
         self.optimizers = [optimizer_factory(st.parameters()) for st in self.stages] if optimizer_factory else []
+        if self._single_optimizer is not None:
+            self.optimizers = [self._single_optimizer]
+        self.step_times: list[float] = []
         self._result: ScheduleResult | None = None
         self._schedule: _OptimizedSchedule | None = None
         self.steps = 0
@@ -589,8 +719,18 @@ class ZBPPRuntimeEngine:
                    for k, st in zip(n, self.stages)]
         return out
 
-    def profile_stage(self, stage_index: int, sample_input: torch.Tensor, repeats: int = 3) -> StageProfile:
-        """Wall-clock forward / B_input / B_params of one local stage on `sample_input` (CUDA-synchronised)."""
+    def profile_stage(self, stage_index: "int | torch.Tensor" = 0, sample_input: torch.Tensor | None = None,
+                      repeats: int = 3, *, num_warmup: int | None = None, num_iterations: int | None = None) -> StageProfile:
+        """Wall-clock forward / B_input / B_params of one local stage on `sample_input` (CUDA-synchronised).
+        `profile_stage(sample_input, num_warmup, num_iterations)` measures the first local stage."""
+        if torch.is_tensor(stage_index):                                 # (sample_input, num_warmup, num_iterations)
+            if sample_input is not None and num_warmup is None:
+                num_warmup = int(sample_input)
+                if repeats != 3 and num_iterations is None:
+                    num_iterations = repeats
+            stage_index, sample_input = 0, stage_index
+        repeats = int(num_iterations) if num_iterations is not None else repeats
+        warm = max(1, int(num_warmup)) if num_warmup is not None else 1
         st = self.stages[stage_index]
         dev = st.device
         x = sample_input.to(dev)
@@ -604,7 +744,7 @@ class ZBPPRuntimeEngine:
         tf = tb = tw = 0.0
         act_bytes = 0
         params = [p for p in st.parameters() if p.requires_grad]
-        for i in range(repeats + 1):
+        for i in range(repeats + warm):
             sync()
             t0 = time.perf_counter()
             y = st(x)
@@ -618,7 +758,7 @@ class ZBPPRuntimeEngine:
             torch.autograd.grad(y, params, g, allow_unused=True)
             sync()
             t3 = time.perf_counter()
-            if i:                                      # first pass is warm-up
+            if i >= warm:                              # the first passes are warm-up
                 tf, tb, tw = tf + (t1 - t0), tb + (t2 - t1), tw + (t3 - t2)
             act_bytes = y.numel() * y.element_size() + x.numel() * x.element_size()
         k = 1e6 / repeats
@@ -636,7 +776,34 @@ class ZBPPRuntimeEngine:
         self._schedule = _OptimizedSchedule(self._result, self.stages, pc, self.loss_fn, comm, None, self.ctx)
         return self._result
 
-    def train_step(self, input_batches: Sequence[torch.Tensor], target_batches: Sequence[torch.Tensor]) -> torch.Tensor:
+    def train_step(self, input_batches: Sequence[torch.Tensor] | None = None,
+                   target_batches: Sequence[torch.Tensor] | None = None, loss_fn: Callable | None = None, *,
+                   micro_batches: Sequence[torch.Tensor] | None = None, labels: Sequence[torch.Tensor] | None = None):
+        """`train_step(input_batches, target_batches)` -> loss.  The reference's `train_step(micro_batches, labels,
+        loss_fn)` -> {"loss", "step_time_s", "throughput_samples_per_s", "bubble_fraction"}; without labels the loss
+        function is called with the output alone."""
+        reference_form = micro_batches is not None or labels is not None or loss_fn is not None or self._reference_form
+        if micro_batches is not None:
+            input_batches = micro_batches
+        if labels is not None:
+            target_batches = labels
+        if reference_form:
+            if len(input_batches) != self.num_microbatches:
+                raise ValueError(f"expected {self.num_microbatches} micro-batches, got {len(input_batches)}")
+            fn = loss_fn or self.loss_fn
+            if fn is None:
+                raise TypeError("a loss function is required: train_step(micro_batches, labels, loss_fn)")
+            if target_batches is None:
+                target_batches = [torch.zeros((), device=b.device) for b in input_batches]
+                fn = (lambda f: lambda out, _unused: f(out))(fn)
+            self.loss_fn = fn
+            if self._schedule is not None:
+                self._schedule.loss_fn = fn
+        elif self.loss_fn is not self._ctor_loss_fn:     # a loss function passed to one step does not outlive it
+            self.loss_fn = self._ctor_loss_fn
+            if self._schedule is not None:
+                self._schedule.loss_fn = self.loss_fn
+        t0 = time.perf_counter()
         if self._schedule is None:
             self.generate_schedule()
         self.validate_pending()                          # settle last step's optimistic updates first
@@ -645,7 +812,14 @@ class ZBPPRuntimeEngine:
             opt.step()
             opt.zero_grad()
         self.steps += 1
-        return loss
+        if not reference_form:
+            return loss
+        value = float(loss.detach()) if torch.is_tensor(loss) else float(loss)    # reading the loss waits for the device
+        dt = time.perf_counter() - t0
+        self.step_times.append(dt)
+        n = sum(int(b.shape[0]) for b in input_batches)
+        return {"loss": value, "step_time_s": dt, "throughput_samples_per_s": n / dt if dt > 0 else 0.0,
+                "bubble_fraction": self._result.bubble_fraction if self._result is not None else 0.0}
 
     def validate_pending(self) -> int:
         """Global-norm check of the optimistic updates of the previous step: the local stages' squared norms are summed
@@ -697,20 +871,27 @@ class ZeroBubblePipeline:
             enable_sync_bypass, ctx)
         self.stages = mine
 
-    def train_step(self, inputs: torch.Tensor | Sequence[torch.Tensor],
-                   targets: torch.Tensor | Sequence[torch.Tensor]) -> torch.Tensor:
+    def train_step(self, inputs: "torch.Tensor | Sequence[torch.Tensor] | None" = None,
+                   targets: "torch.Tensor | Sequence[torch.Tensor] | None" = None, loss_fn: Callable | None = None, *,
+                   micro_batches=None, labels=None):
+        """`train_step(inputs, targets)` -> loss (whole batches are cut into the micro-batches).  The reference's
+        `train_step(micro_batches, labels, loss_fn)` -> metrics dict, like the engine's."""
+        if micro_batches is not None or labels is not None or loss_fn is not None:
+            return self.engine.train_step(micro_batches=micro_batches if micro_batches is not None else inputs,
+                                          labels=labels if labels is not None else targets, loss_fn=loss_fn or self.loss_fn)
         if torch.is_tensor(inputs):
             inputs = list(inputs.chunk(self.num_microbatches, dim=0))
         if torch.is_tensor(targets):
             targets = list(targets.chunk(self.num_microbatches, dim=0))
         return self.engine.train_step(inputs, targets)
 
-    def profile_stages(self, sample_input: torch.Tensor, repeats: int = 3) -> list[StageProfile]:
+    @reference_kwargs(num_iterations="repeats")
+    def profile_stages(self, sample_input: torch.Tensor, repeats: int = 3, *, num_warmup: int | None = None) -> list[StageProfile]:
         """Measures every local stage on a sample micro-batch (chained through the stages) and rebuilds the schedule
         with the measured costs (single-process layout)."""
         profs, x = [], sample_input
         for i, st in enumerate(self.engine.stages):
-            profs.append(self.engine.profile_stage(i, x, repeats))
+            profs.append(self.engine.profile_stage(i, x, repeats, num_warmup=num_warmup))
             with torch.no_grad():
                 x = st(x.to(st.device))
         if len(profs) == self.num_stages:
@@ -753,10 +934,48 @@ class ZBPPBenchmark:
     """Self-checks: the gradient split equals a plain backward, the schedule beats 1F1B and respects the memory limit,
     and a throughput measurement."""
 
-    def __init__(self, pipeline: ZeroBubblePipeline, sample_input: torch.Tensor, sample_target: torch.Tensor):
+    def __init__(self, pipeline: "ZeroBubblePipeline | torch.device | str | None" = None,
+                 sample_input: "torch.Tensor | torch.dtype | None" = None, sample_target: torch.Tensor | None = None, *,
+                 device=None, dtype: torch.dtype | None = None):
+        """`ZBPPBenchmark(pipeline, sample_input, sample_target)` checks that pipeline.  The reference's
+        `ZBPPBenchmark(device, dtype)` is free-standing: each check builds what it needs from the sizes it is given and
+        returns a bool (data_pipeline/trainer/distributed/zbpp.py:1943)."""
+        if not isinstance(pipeline, ZeroBubblePipeline) and pipeline is not None:
+            device, pipeline = pipeline, None
+            if isinstance(sample_input, torch.dtype):
+                dtype, sample_input = sample_input, None
         self.pipeline, self.x, self.y = pipeline, sample_input, sample_target
+        self.device = torch.device(device) if device is not None else torch.device("cpu")
+        self.dtype = dtype or torch.float32
 
-    def validate_gradient_decomposition(self, atol: float = 1e-5) -> dict[str, Any]:
+    # ---- free-standing checks
+    def _linear_decomposition(self, batch_size: int, in_features: int, out_features: int, atol: float, rtol: float) -> bool:
+        g = torch.Generator().manual_seed(0)
+        x = torch.randn(batch_size, in_features, generator=g).to(self.device, self.dtype).requires_grad_(True)
+        w = (torch.randn(out_features, in_features, generator=g) / in_features ** 0.5).to(self.device, self.dtype).requires_grad_(True)
+        go = torch.randn(batch_size, out_features, generator=g).to(self.device, self.dtype)
+        want_x, want_w = torch.autograd.grad(nn.functional.linear(x.float(), w.float()), [x, w], go.float())
+        d = GradientDecomposer(dtype=self.dtype)
+        got_x = d.compute_b_input(go, w.detach())
+        got_w = d.compute_b_params(x.detach(), go, w.detach())
+        return bool(torch.allclose(got_x.float(), want_x.float(), atol=atol, rtol=rtol)
+                    and torch.allclose(got_w.float(), want_w.float(), atol=atol, rtol=rtol))
+
+    @staticmethod
+    def _uniform_schedule(num_stages: int, num_microbatches: int, memory_limit_bytes: int, activation_bytes: int = 1 << 20):
+        prof = [StageProfile(100.0, 100.0, 100.0, activation_bytes, 0, 0.0, 0.0) for _ in range(num_stages)]
+        return ZBPPScheduleOptimizer(ScheduleConfig(num_stages, num_microbatches, memory_limit_bytes, prof)).optimize()
+
+    def validate_gradient_decomposition(self, batch_size: "int | float | None" = None, in_features: int = 512,
+                                        out_features: int = 256, atol: float | None = None, rtol: float = 1e-2):
+        """With a pipeline: its first stage's split backward against a plain backward -> dict.  Free-standing
+        (`batch_size, in_features, out_features, atol, rtol`): the closed forms of a linear layer against autograd -> bool."""
+        if self.pipeline is None:
+            return self._linear_decomposition(int(batch_size or 32), in_features, out_features,
+                                              1e-2 if atol is None else atol, rtol)
+        if isinstance(batch_size, float) and atol is None:               # validate_gradient_decomposition(1e-5)
+            atol = batch_size
+        atol = 1e-5 if atol is None else atol
         st = self.pipeline.stages[0]
         x = self.x[: max(1, self.x.shape[0] // self.pipeline.num_microbatches)].to(st.device)
         if x.is_floating_point():
@@ -771,20 +990,59 @@ class ZBPPBenchmark:
         err = max((float((a - b).abs().max()) for a, b in zip(got, want) if a is not None and b is not None), default=0.0)
         return {"max_abs_error": err, "passed": err <= atol}
 
-    def validate_schedule_optimality(self) -> dict[str, Any]:
+    def validate_schedule_optimality(self, num_stages: int | None = None, num_microbatches: int | None = None):
+        if self.pipeline is None:
+            P, M = int(num_stages or 4), int(num_microbatches or 8)
+            r = self._uniform_schedule(P, M, 1 << 40)
+            base = PP.simulate([PP.one_f_one_b_schedule(s, P, M) for s in range(P)])["bubble_fraction"]
+            return bool(r.bubble_fraction <= base + 1e-9)
         r = self.pipeline.schedule_result or self.pipeline.engine.generate_schedule()
         P, M = self.pipeline.num_stages, self.pipeline.num_microbatches
         base = PP.simulate([PP.one_f_one_b_schedule(s, P, M) for s in range(P)])["bubble_fraction"]
         return {"bubble_fraction": r.bubble_fraction, "one_f_one_b_bubble": base,
                 "passed": r.bubble_fraction <= base + 1e-9}
 
-    def validate_memory_compliance(self) -> dict[str, Any]:
+    def validate_memory_compliance(self, num_stages: int | None = None, num_microbatches: int | None = None,
+                                   memory_limit_mb: int = 256):
+        if self.pipeline is None:
+            lim = int(memory_limit_mb) * 2 ** 20
+            r = self._uniform_schedule(int(num_stages or 4), int(num_microbatches or 8), lim, activation_bytes=lim // 16)
+            return bool(all(v <= lim for v in r.peak_memory_bytes.values()))
         r = self.pipeline.schedule_result or self.pipeline.engine.generate_schedule()
         lim = self.pipeline.engine.memory_limit_bytes
         return {"peak_memory_bytes": r.peak_memory_bytes, "limit": lim,
                 "passed": all(v <= lim for v in r.peak_memory_bytes.values())}
 
-    def benchmark_throughput(self, steps: int = 3, warmup: int = 1) -> dict[str, Any]:
+    def _free_standing_throughput(self, model, num_stages, num_microbatches, batch_size, seq_len, hidden_dim, num_steps):
+        if model is None:
+            model = nn.Sequential(*[nn.Sequential(nn.Linear(hidden_dim, hidden_dim), nn.GELU()) for _ in range(2 * num_stages)])
+        model = model.to(self.device, self.dtype)
+        pipe = ZeroBubblePipeline(model, num_stages, num_microbatches)
+        x = torch.randn(batch_size * num_microbatches, seq_len, hidden_dim, device=self.device, dtype=self.dtype)
+        y = torch.randn_like(x)
+        pipe.train_step(x, y)                                            # warm-up
+        if self.device.type == "cuda":
+            torch.cuda.synchronize(self.device)
+        t0 = time.perf_counter()
+        for _ in range(num_steps):
+            loss = pipe.train_step(x, y)
+        if self.device.type == "cuda":
+            torch.cuda.synchronize(self.device)
+        dt = (time.perf_counter() - t0) / max(1, num_steps)
+        return {"step_ms": dt * 1e3, "samples_per_s": x.shape[0] / dt, "tokens_per_s": x.shape[0] * seq_len / dt,
+                "bubble_fraction": pipe.bubble_fraction, "final_loss": float(loss)}
+
+    def benchmark_throughput(self, steps: "int | nn.Module | None" = 3, warmup: int = 1, *, model: nn.Module | None = None,
+                             num_stages: int = 4, num_microbatches: int = 8, batch_size: int = 4, seq_len: int = 128,
+                             hidden_dim: int = 512, num_steps: int | None = None) -> dict[str, Any]:
+        """With a pipeline: `steps` timed steps of it.  Free-standing: builds (or takes) a model of `hidden_dim`, cuts it
+        into `num_stages` and times `num_steps` steps on [batch_size * num_microbatches, seq_len, hidden_dim]."""
+        if self.pipeline is None:
+            if isinstance(steps, nn.Module):
+                model = steps
+            return self._free_standing_throughput(model, num_stages, num_microbatches, batch_size, seq_len, hidden_dim,
+                                                  int(num_steps if num_steps is not None else 5))
+        steps = int(num_steps) if num_steps is not None else steps
         dev = self.pipeline.stages[0].device
         for _ in range(warmup):
             self.pipeline.train_step(self.x, self.y)
@@ -799,6 +1057,13 @@ class ZBPPBenchmark:
         return {"step_ms": dt * 1e3, "samples_per_s": self.x.shape[0] / dt}
 
     def run_all(self) -> dict[str, Any]:
+        if self.pipeline is None:
+            out = {"gradient_decomposition": {"passed": self.validate_gradient_decomposition()},
+                   "schedule": {"passed": self.validate_schedule_optimality()},
+                   "memory": {"passed": self.validate_memory_compliance()},
+                   "throughput": self.benchmark_throughput(hidden_dim=64, seq_len=16, num_steps=2)}
+            out["passed"] = all(v.get("passed", True) for v in out.values())
+            return out
         out = {"gradient_decomposition": self.validate_gradient_decomposition(),
                "schedule": self.validate_schedule_optimality(), "memory": self.validate_memory_compliance(),
                "throughput": self.benchmark_throughput()}
