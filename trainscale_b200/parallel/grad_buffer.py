@@ -66,12 +66,38 @@ class ParamAndGradBucket:
         return self.grad_data.numel()
 
 
+def _is_ddp_config(x) -> bool:
+    """A data-parallel configuration object (any class carrying the switches), as opposed to a process group."""
+    return x is not None and any(hasattr(x, n) for n in ("use_distributed_optimizer", "overlap_grad_reduce",
+                                                          "average_in_collective", "overlap_param_gather"))
+
+
 class ParamAndGradBucketGroup:
     """Buckets whose collectives are issued together.  Gradient side: all-reduce, or reduce-scatter into this rank's
     shard when the distributed optimizer is on.  Parameter side: all-gather of the updated shards."""
 
     def __init__(self, buckets: Sequence[ParamAndGradBucket], group=None, use_distributed_optimizer: bool = False,
-                 overlap_grad_reduce: bool = True, overlap_param_gather: bool = False, average: bool = True):
+                 overlap_grad_reduce: bool = True, overlap_param_gather: bool = False, average: bool = True, *,
+                 ddp_config=None, collective_group=None, collective_group_size: int | None = None):
+        """`ParamAndGradBucketGroup(buckets, group, use_distributed_optimizer, ...)`, or the reference's `(buckets,
+        ddp_config, collective_group, collective_group_size)`: the switches are then read from the configuration object
+        (`use_distributed_optimizer`, `overlap_grad_reduce`, `overlap_param_gather`, `average_in_collective`)
+        (data_pipeline/trainer/distributed/grad_buffer.py:262)."""
+        if _is_ddp_config(group):                                        # positional (buckets, ddp_config, group, size)
+            ddp_config, group = group, None
+            if not isinstance(use_distributed_optimizer, bool):
+                collective_group, use_distributed_optimizer = use_distributed_optimizer, False
+            if not isinstance(overlap_grad_reduce, bool):
+                collective_group_size, overlap_grad_reduce = int(overlap_grad_reduce), True
+        if ddp_config is not None:
+            use_distributed_optimizer = bool(getattr(ddp_config, "use_distributed_optimizer", False))
+            overlap_grad_reduce = bool(getattr(ddp_config, "overlap_grad_reduce", False))
+            overlap_param_gather = bool(getattr(ddp_config, "overlap_param_gather", False))
+            average = bool(getattr(ddp_config, "average_in_collective", True))
+        group = collective_group if collective_group is not None else group
+        if collective_group_size is not None and int(collective_group_size) != _world(group):
+            raise ValueError(f"collective_group_size={collective_group_size} but the group has {_world(group)} ranks")
+        self.ddp_config = ddp_config
         self.buckets = list(buckets)
         self.group = group
         self.world, self.rank = _world(group), _rank(group)
@@ -178,7 +204,26 @@ class ParamAndGradBuffer:
     def __init__(self, params: Iterable[nn.Parameter], param_dtype: torch.dtype = torch.bfloat16,
                  grad_dtype: torch.dtype = torch.float32, group=None, bucket_size: int | None = 40_000_000,
                  use_distributed_optimizer: bool = False, gradient_scaling_factor: float = 1.0,
-                 device: torch.device | str | None = None, install_hooks: bool = True):
+                 device: torch.device | str | None = None, install_hooks: bool = True, *, ddp_config=None,
+                 data_parallel_group=None, param_to_name: dict | None = None):
+        """`ParamAndGradBuffer(params, param_dtype, grad_dtype, group, bucket_size, ...)`, or the reference's
+        `(ddp_config, param_dtype, grad_dtype, params, data_parallel_group, bucket_size, param_to_name,
+        gradient_scaling_factor)`: `use_distributed_optimizer` then comes from the configuration object, and
+        `param_to_name` labels parameters in error messages (data_pipeline/trainer/distributed/grad_buffer.py:703)."""
+        if _is_ddp_config(params):                                       # the reference's positional order
+            ref = (params, group, bucket_size, use_distributed_optimizer, gradient_scaling_factor, device)
+            ddp_config, params = ref[0], ref[1]
+            data_parallel_group = ref[2] if not isinstance(ref[2], int) else data_parallel_group
+            bucket_size = ref[3] if isinstance(ref[3], int) and not isinstance(ref[3], bool) else \
+                (ref[2] if isinstance(ref[2], int) else 40_000_000)
+            if isinstance(ref[4], dict):
+                param_to_name, gradient_scaling_factor = ref[4], (ref[5] if isinstance(ref[5], (int, float)) else 1.0)
+            use_distributed_optimizer, group = False, None
+            device = None if not isinstance(device, (str, torch.device)) or isinstance(ref[5], (int, float)) else device
+        if ddp_config is not None:
+            use_distributed_optimizer = bool(getattr(ddp_config, "use_distributed_optimizer", use_distributed_optimizer))
+        group = data_parallel_group if data_parallel_group is not None else group
+        self.ddp_config, self.param_to_name = ddp_config, dict(param_to_name or {})
         self.params = [p for p in params if p.requires_grad]
         if not self.params:
             raise ValueError("no trainable parameters")

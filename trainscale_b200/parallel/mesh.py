@@ -53,8 +53,9 @@ class ParallelDimsConfig:
 class ParallelDims:
     """Coordinates of this rank and the process groups along every (possibly flattened) dimension."""
 
+    @reference_kwargs(config="cfg")
     def __init__(self, cfg: ParallelDimsConfig, rank: int | None = None, create_groups: bool = True):
-        self.cfg = cfg.resolve()
+        self.cfg = self.config = cfg.resolve()
         self.rank = rank if rank is not None else (dist.get_rank() if dist.is_initialized() else 0)
         self.sizes = {d: getattr(self.cfg, d) for d in DIM_ORDER}
         self.coords = self._coords_of(self.rank)
@@ -328,7 +329,11 @@ class MeshCache:
         return (c.pp, c.dp_replicate, c.dp_shard, c.cp, c.tp, c.ep, c.etp, c.world_size)
 
     @classmethod
-    def get(cls, cfg: ParallelDimsConfig, rank: int | None = None) -> "ParallelDims":
+    def get(cls, cfg: "ParallelDimsConfig | str | None" = None, rank: int | None = None, *, name: str | None = None):
+        """`get(cfg, rank)` -> the cached `ParallelDims` of that layout; `get(name)` -> the mesh stored under a
+        dimension name by `set` (None when absent)."""
+        if name is not None or isinstance(cfg, str):
+            return cls.get_named(name if name is not None else cfg)
         k = cls._key(cfg) + (rank,)
         if k not in cls._cache:
             cls._cache[k] = ParallelDims(cfg, rank)
