@@ -35,6 +35,23 @@ def main():
     nxt, prv = (rank + 1) % world, (rank - 1) % world
     got = k.pipeline_send_recv(torch.full((3,), float(rank)), torch.empty(3), nxt, prv)
     ok &= float(got[0]) == prv
+    # the reference's call forms: asynchronous fused all-reduce (copy back in wait_pending), list reduce-scatter,
+    # (x, dim, group) order of the sequence-parallel helpers, tagged point-to-point
+    a2, b2 = torch.full((300,), float(rank)), torch.full((7,), float(rank), dtype=torch.float64)
+    k.all_reduce_fused([a2, b2], average=True, async_op=True)
+    k.wait_pending()
+    ok &= abs(float(a2[0]) - (world - 1) / 2) < 1e-6 and abs(float(b2[0]) - (world - 1) / 2) < 1e-9
+    mine_out = torch.empty(3)
+    k.reduce_scatter(output=mine_out, input_tensors=[torch.full((3,), float(rank * 10 + r)) for r in range(world)])
+    ok &= float(mine_out[0]) == sum(r * 10 + rank for r in range(world))
+    sp0 = k.sequence_parallel_all_gather(x=torch.full((2, 4), float(rank)), dim=0, group=None, async_op=True)
+    k.wait_pending()
+    ok &= sp0.shape == (2 * world, 4) and float(sp0[2 * (world - 1), 0]) == world - 1
+    got2 = k.pipeline_send_recv(torch.full((3,), float(rank)), torch.empty(3), nxt, prv, send_tag=5, recv_tag=5)
+    ok &= float(got2[0]) == prv
+    bc = k.broadcast(torch.full((2,), float(rank)), 1, None, async_op=True)
+    k.wait_pending()
+    ok &= float(bc[0]) == 1.0
     # groups: tp=2, pp=1 -> dp = world/2
     groups = DK.create_process_groups(tensor_parallel_size=2)
     ok &= dist.get_world_size(groups["tensor"]) == 2 and groups["pipeline"] is None

@@ -203,6 +203,7 @@ class GradientCompressor:
         e = self._error_buffers.get(key)
         return t if e is None else t + e
 
+    @reference_kwargs(tensor_id="key")
     def compress(self, tensor: torch.Tensor, key: Any = None) -> tuple[list[torch.Tensor], dict]:
         key = id(tensor) if key is None else key
         ctx = {"shape": tensor.shape, "dtype": tensor.dtype, "key": key}
@@ -235,7 +236,10 @@ class GradientCompressor:
         ctx["mode"] = "none"
         return [tensor], ctx
 
-    def decompress(self, payload: Sequence[torch.Tensor], ctx: dict) -> torch.Tensor:
+    @reference_kwargs(tensor="payload", metadata="ctx")
+    def decompress(self, payload: "Sequence[torch.Tensor] | torch.Tensor", ctx: dict) -> torch.Tensor:
+        if torch.is_tensor(payload):
+            payload = [payload]
         mode = ctx["mode"]
         if mode == "powersgd":
             p, q = payload
@@ -249,6 +253,17 @@ class GradientCompressor:
             out.index_add_(0, idx, vals)
             return out.view(ctx["shape"]).to(ctx["dtype"])
         return payload[0].to(ctx["dtype"]).view(ctx["shape"])
+
+
+class _Deferred:
+    """A pending collective plus the host-side step that completes it (copy back, scaling) once it has finished."""
+
+    def __init__(self, work, then):
+        self.work, self.then = work, then
+
+    def wait(self):
+        self.work.wait()
+        self.then()
 
 
 class DistributedKernels:
@@ -280,13 +295,18 @@ class DistributedKernels:
         return tensor
 
     def all_reduce_fused(self, tensors: Sequence[torch.Tensor], op=ReduceOp.SUM, group=None,
-                         average: bool = False) -> None:
-        """Bucket by dtype / size, one all-reduce per flat bucket, results copied back in place."""
+                         average: bool = False, async_op: bool = False) -> None:
+        """Bucket by dtype / size, one all-reduce per flat bucket, results copied back in place.  With `async_op` the
+        reductions are only issued; the copy back (and the averaging) happens in `wait_pending()`."""
         if self._n(group) == 1 or not tensors:
             return
         for b in self._buckets.create_buckets(list(tensors)):
             flat = b.flatten()
-            dist.all_reduce(flat, op=op, group=group)
+            w = dist.all_reduce(flat, op=op, group=group, async_op=async_op)
+            if async_op:
+                self._pending.append(_Deferred(w, (lambda f=flat, bb=b: (f.div_(self._n(group)) if average else f,
+                                                                        bb.unflatten()))))
+                continue
             if average:
                 flat.div_(self._n(group))
             b.unflatten()
@@ -295,14 +315,19 @@ class DistributedKernels:
         self.all_reduce_fused(tensors, op, group)
 
     # ---------------------------------------------------------------- gathers / scatters
-    def all_gather(self, tensor: torch.Tensor, group=None, dim: int = 0) -> torch.Tensor:
+    def all_gather(self, tensor: torch.Tensor, group=None, dim: int = 0, async_op: bool = False) -> torch.Tensor:
+        """Concatenation of every rank's tensor along `dim`.  `async_op` (dimension 0 only; other dimensions need the
+        data for the concatenation and run synchronously): the result is complete after `wait_pending()`."""
         n = self._n(group)
         if n == 1:
             return tensor
+        if async_op and dim == 0:
+            return self.all_gather_into_tensor(None, tensor, group, async_op=True)
         parts = [torch.empty_like(tensor) for _ in range(n)]
         dist.all_gather(parts, tensor.contiguous(), group=group)
         return torch.cat(parts, dim=dim)
 
+    @reference_kwargs(input_tensor="tensor")
     def all_gather_into_tensor(self, output: torch.Tensor | None, tensor: torch.Tensor, group=None,
                                async_op: bool = False) -> torch.Tensor:
         n = self._n(group)
@@ -317,8 +342,22 @@ class DistributedKernels:
         self._track(dist.all_gather_into_tensor(output, tensor.contiguous(), group=group, async_op=async_op), async_op)
         return output
 
-    def reduce_scatter(self, tensor: torch.Tensor, op=ReduceOp.SUM, group=None, dim: int = 0) -> torch.Tensor:
-        """Sum over the group, keep this rank's slice along `dim`."""
+    def reduce_scatter(self, tensor: torch.Tensor | None = None, op=ReduceOp.SUM, group=None, dim: int = 0, *,
+                       output: torch.Tensor | None = None, input_tensors: Sequence[torch.Tensor] | None = None,
+                       async_op: bool = False) -> torch.Tensor:
+        """Sum over the group, keep this rank's slice along `dim`.  `reduce_scatter(output, input_tensors, op, group,
+        async_op)` is the list form: rank r receives the reduction of every rank's `input_tensors[r]` in `output`."""
+        if input_tensors is not None or isinstance(op, (list, tuple)):
+            if isinstance(op, (list, tuple)):                            # positional (output, input_tensors, op, group)
+                output, input_tensors, op, group = tensor, op, (group if group is not None else ReduceOp.SUM), \
+                    (dim if not isinstance(dim, int) else None)
+            output = output if output is not None else tensor
+            if self._n(group) == 1:
+                output.copy_(input_tensors[0])
+                return output
+            self._track(dist.reduce_scatter(output, [t.contiguous() for t in input_tensors], op=op, group=group,
+                                            async_op=async_op), async_op)
+            return output
         n = self._n(group)
         if n == 1:
             return tensor
@@ -327,6 +366,7 @@ class DistributedKernels:
         dist.reduce_scatter(out, parts, op=op, group=group)
         return out
 
+    @reference_kwargs(input_tensor="tensor")
     def reduce_scatter_tensor(self, output: torch.Tensor | None, tensor: torch.Tensor, op=ReduceOp.SUM, group=None,
                               async_op: bool = False) -> torch.Tensor:
         n = self._n(group)
@@ -343,23 +383,37 @@ class DistributedKernels:
         return output
 
     # ---------------------------------------------------------------- sequence / tensor parallel helpers
-    def sequence_parallel_all_gather(self, tensor: torch.Tensor, group=None, seq_dim: int = 1) -> torch.Tensor:
+    @staticmethod
+    def _dim_group(group, seq_dim):
+        """`(x, dim, group)` is the reference's order, `(tensor, group, seq_dim)` ours: an int in the group's place is
+        the dimension."""
+        if isinstance(group, int) and not isinstance(group, bool):
+            return (seq_dim if not isinstance(seq_dim, int) else None), group
+        return group, seq_dim
+
+    @reference_kwargs(x="tensor", dim="seq_dim")
+    def sequence_parallel_all_gather(self, tensor: torch.Tensor, group=None, seq_dim: int = 1,
+                                     async_op: bool = False) -> torch.Tensor:
         """[.., S/n, ..] -> [.., S, ..]: rank r holds the r-th slice of the sequence."""
+        group, seq_dim = self._dim_group(group, seq_dim)
         if self._n(group) == 1:
             return tensor
         if seq_dim == 0:
-            return self.all_gather_into_tensor(None, tensor, group)
+            return self.all_gather_into_tensor(None, tensor, group, async_op=async_op)
         return self.all_gather(tensor, group, dim=seq_dim)
 
-    def sequence_parallel_reduce_scatter(self, tensor: torch.Tensor, group=None, seq_dim: int = 1) -> torch.Tensor:
+    @reference_kwargs(x="tensor", dim="seq_dim")
+    def sequence_parallel_reduce_scatter(self, tensor: torch.Tensor, group=None, seq_dim: int = 1,
+                                         async_op: bool = False) -> torch.Tensor:
+        group, seq_dim = self._dim_group(group, seq_dim)
         if self._n(group) == 1:
             return tensor
         if seq_dim == 0:
-            return self.reduce_scatter_tensor(None, tensor, group=group)
+            return self.reduce_scatter_tensor(None, tensor, group=group, async_op=async_op)
         return self.reduce_scatter(tensor, group=group, dim=seq_dim)
 
-    def tensor_parallel_all_reduce(self, tensor: torch.Tensor, group=None) -> torch.Tensor:
-        return self.all_reduce(tensor, group=group)
+    def tensor_parallel_all_reduce(self, tensor: torch.Tensor, group=None, async_op: bool = False) -> torch.Tensor:
+        return self.all_reduce(tensor, group=group, async_op=async_op)
 
     def tensor_parallel_all_gather(self, tensor: torch.Tensor, group=None, dim: int = -1) -> torch.Tensor:
         return self.all_gather(tensor, group, dim=dim)
@@ -368,16 +422,18 @@ class DistributedKernels:
         return self.reduce_scatter(tensor, group=group, dim=dim)
 
     # ---------------------------------------------------------------- pipeline point-to-point
-    def pipeline_send(self, tensor: torch.Tensor, dst: int, group=None, async_op: bool = True):
-        w = dist.isend(tensor.contiguous(), dst, group=group)
+    @reference_kwargs(dst_rank="dst")
+    def pipeline_send(self, tensor: torch.Tensor, dst: int, group=None, async_op: bool = True, tag: int = 0):
+        w = dist.isend(tensor.contiguous(), dst, group=group, tag=tag)
         if async_op:
             self._pending.append(w)
         else:
             w.wait()
         return w
 
-    def pipeline_recv(self, tensor: torch.Tensor, src: int, group=None, async_op: bool = False):
-        w = dist.irecv(tensor, src, group=group)
+    @reference_kwargs(src_rank="src")
+    def pipeline_recv(self, tensor: torch.Tensor, src: int, group=None, async_op: bool = False, tag: int = 0):
+        w = dist.irecv(tensor, src, group=group, tag=tag)
         if async_op:
             self._pending.append(w)
         else:
@@ -385,13 +441,14 @@ class DistributedKernels:
         return tensor
 
     def pipeline_send_recv(self, send_tensor: torch.Tensor | None, recv_tensor: torch.Tensor | None,
-                           send_dst: int | None, recv_src: int | None, group=None) -> torch.Tensor | None:
+                           send_dst: int | None, recv_src: int | None, group=None, send_tag: int = 0,
+                           recv_tag: int = 0) -> torch.Tensor | None:
         """Both directions in one batched call, so two neighbours exchanging at the same time cannot deadlock."""
         ops = []
         if send_tensor is not None and send_dst is not None:
-            ops.append(dist.P2POp(dist.isend, send_tensor.contiguous(), send_dst, group))
+            ops.append(dist.P2POp(dist.isend, send_tensor.contiguous(), send_dst, group, tag=send_tag))
         if recv_tensor is not None and recv_src is not None:
-            ops.append(dist.P2POp(dist.irecv, recv_tensor, recv_src, group))
+            ops.append(dist.P2POp(dist.irecv, recv_tensor, recv_src, group, tag=recv_tag))
         for w in (dist.batch_isend_irecv(ops) if ops else []):
             w.wait()
         return recv_tensor
@@ -399,11 +456,12 @@ class DistributedKernels:
     send_recv = pipeline_send_recv
 
     # ---------------------------------------------------------------- misc
-    def broadcast(self, tensor: torch.Tensor, src: int = 0, group=None) -> torch.Tensor:
+    def broadcast(self, tensor: torch.Tensor, src: int = 0, group=None, async_op: bool = False) -> torch.Tensor:
         if self._n(group) > 1:
-            dist.broadcast(tensor, src, group=group)
+            self._track(dist.broadcast(tensor, src, group=group, async_op=async_op), async_op)
         return tensor
 
+    @reference_kwargs(object_list="objects")
     def broadcast_object_list(self, objects: list, src: int = 0, group=None) -> list:
         if self._n(group) > 1:
             dist.broadcast_object_list(objects, src, group=group)

@@ -55,7 +55,7 @@ class ParallelDims:
 
     @reference_kwargs(config="cfg")
     def __init__(self, cfg: ParallelDimsConfig, rank: int | None = None, create_groups: bool = True):
-        self.cfg = self.config = cfg.resolve()
+        self.cfg = cfg.resolve()
         self.rank = rank if rank is not None else (dist.get_rank() if dist.is_initialized() else 0)
         self.sizes = {d: getattr(self.cfg, d) for d in DIM_ORDER}
         self.coords = self._coords_of(self.rank)
