@@ -496,3 +496,45 @@ def test_zero_bubble_classes_take_the_reference_forms():
     assert ModelPartitioner(nn.Sequential(*[nn.Linear(8, 8) for _ in range(4)]), 2, balance_metric="layers").costs == [1.0] * 4
     assert stages[0](input_tensor=batches[0], microbatch_id=7).shape == (3, 8)
     assert memory.retrieve_activation(7, "stage_0_input").shape == (3, 8)
+
+
+def test_kernel_modules_take_the_reference_forms():
+    from trainscale_b200.kernels import (FP8Config, FP8Linear, FP8ScaleManager, FlashAttention, FlashAttentionConfig,
+                                         FlexAttention, FlexAttentionConfig, MultiHeadFlashAttention, RMSNorm,
+                                         TritonGeGLU, TritonSwiGLU)
+    torch.manual_seed(0)
+    x = torch.randn(2, 3, 16)
+    plain = RMSNorm(16, 1e-6, False)
+    assert plain.weight is None and not list(plain.parameters())
+    assert torch.allclose(plain(X=x), RMSNorm(16, elementwise_affine=True)(x), atol=1e-6)
+    geglu = TritonGeGLU(16, 32, True, False)
+    assert geglu.activation == "gelu" and geglu.b_down.shape == (16,) and geglu(x).shape == x.shape
+    assert TritonSwiGLU(16, 32, bias=True)(x).shape == x.shape
+    attn = FlashAttention(head_dim=8, num_heads=4, num_kv_heads=2, causal=True, dropout=0.0, sliding_window=None)
+    q, k, v = torch.randn(2, 4, 6, 8), torch.randn(2, 2, 6, 8), torch.randn(2, 2, 6, 8)
+    want = torch.nn.functional.scaled_dot_product_attention(q, k.repeat_interleave(2, 1), v.repeat_interleave(2, 1),
+                                                            is_causal=True)
+    assert torch.allclose(attn(q, k, v), want, atol=1e-5)                       # heads-first layout in and out
+    assert torch.allclose(attn(query=q, key=k, value=v), want, atol=1e-5)
+    native = FlashAttention(FlashAttentionConfig())
+    assert torch.allclose(native(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)).transpose(1, 2), want, atol=1e-5)
+    flex = FlexAttention(FlexAttentionConfig(num_attention_heads=4, num_key_value_heads=2, head_dim=8,
+                                             query_pre_attn_scalar=8))
+    merged = flex(Q=q, K=k, V=v, attention_mask=None, is_causal=True, use_inference_mode=False)
+    assert torch.allclose(merged, want.transpose(1, 2).reshape(2, 6, 32), atol=1e-5)
+    layer = MultiHeadFlashAttention(embed_dim=32, num_heads=4, num_kv_heads=2, dropout=0.0, bias=True, causal=True,
+                                    sliding_window=None)
+    tokens = torch.randn(2, 6, 32)
+    full = layer(tokens)
+    wq, wk, wv = layer.wqkv.split((32, 16, 16))
+    bq, bk, bv = layer.bqkv.split((32, 16, 16))
+    key_cache = (tokens[:, :5] @ wk.t() + bk).view(2, 5, 2, 8).transpose(1, 2)
+    value_cache = (tokens[:, :5] @ wv.t() + bv).view(2, 5, 2, 8).transpose(1, 2)
+    last = layer(query=tokens[:, 5:], key=tokens[:, 5:], value=tokens[:, 5:], key_cache=key_cache, value_cache=value_cache)
+    assert torch.allclose(last, full[:, 5:], atol=1e-5)                         # decoding behind a cache == full pass
+    assert torch.allclose(layer(tokens, tokens, tokens), full, atol=1e-5)
+    assert MultiHeadFlashAttention(32, 4).bqkv is None
+    assert FP8Linear(128, 16, False, 128)(X=torch.randn(2, 128, dtype=torch.bfloat16)).shape == (2, 16)
+    with pytest.raises(ValueError):
+        FP8Linear(128, 16, block_size=64)
+    assert FP8ScaleManager(FP8Config(), "cpu").device == "cpu"

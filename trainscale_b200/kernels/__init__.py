@@ -191,13 +191,25 @@ Fast_GeGLU = _act._GluFn
 class TritonRMSNorm(nn.Module):
     """RMSNorm module on the fused row kernel (name kept from the reference; nothing here is Triton)."""
 
-    def __init__(self, hidden_size: int, eps: float = 1e-6, dtype=None, device=None):
+    def __init__(self, hidden_size: int, eps: float = 1e-6, dtype=None, device=None, *, elementwise_affine: bool = True):
+        """`elementwise_affine=False`: no learnable scale (the kernel runs with a constant vector of ones)."""
         super().__init__()
-        self.weight = nn.Parameter(torch.ones(hidden_size, dtype=dtype, device=device))
-        self.eps = eps
+        if isinstance(dtype, bool):                          # RMSNorm(hidden_size, eps, elementwise_affine, device, dtype)
+            elementwise_affine, dtype = dtype, None
+        if device is not None and isinstance(device, torch.dtype):
+            dtype, device = device, None
+        self.hidden_size, self.eps, self.elementwise_affine = hidden_size, eps, bool(elementwise_affine)
+        ones = torch.ones(hidden_size, dtype=dtype, device=device)
+        if self.elementwise_affine:
+            self.weight = nn.Parameter(ones)
+        else:
+            self.register_parameter("weight", None)
+            self.register_buffer("_ones", ones, persistent=False)
 
+    @reference_kwargs(X="x")
     def forward(self, x, residual=None):
-        y, res = _norm.rmsnorm(x, self.weight, self.eps, residual)
+        w = self.weight if self.weight is not None else self._ones.to(x.dtype)
+        y, res = _norm.rmsnorm(x, w, self.eps, residual)
         return y if residual is None else (y, res)
 
 
@@ -206,19 +218,35 @@ class TritonSwiGLU(nn.Module):
 
     activation = "silu"
 
-    def __init__(self, hidden_size: int, intermediate_size: int, dtype=None, device=None):
+    def __init__(self, hidden_size: int, intermediate_size: int, dtype=None, device=None, *, bias: bool = False):
+        """`bias=True` adds biases to the gate|up and the down projections (`TritonSwiGLU(hidden, inter, bias)` is
+        the reference's positional form)."""
         super().__init__()
+        if isinstance(dtype, bool):
+            bias, dtype = dtype, None
         self.w_gate_up = nn.Parameter(torch.empty(2 * intermediate_size, hidden_size, dtype=dtype, device=device))
         self.w_down = nn.Parameter(torch.empty(hidden_size, intermediate_size, dtype=dtype, device=device))
+        self.b_gate_up = nn.Parameter(torch.zeros(2 * intermediate_size, dtype=dtype, device=device)) if bias else None
+        self.b_down = nn.Parameter(torch.zeros(hidden_size, dtype=dtype, device=device)) if bias else None
         nn.init.normal_(self.w_gate_up, std=0.02)
         nn.init.normal_(self.w_down, std=0.02)
 
     def forward(self, x):
-        return _gemm.linear(_act.glu(_gemm.linear(x, self.w_gate_up), self.activation), self.w_down)
+        return _gemm.linear(_act.glu(_gemm.linear(x, self.w_gate_up, self.b_gate_up), self.activation), self.w_down,
+                            self.b_down)
 
 
 class TritonGeGLU(TritonSwiGLU):
+    """`approx=True` (default): the tanh approximation of GELU; `approx=False`: the exact erf form."""
     activation = "gelu_tanh"
+
+    def __init__(self, hidden_size: int, intermediate_size: int, dtype=None, device=None, *, bias: bool = False,
+                 approx: bool = True):
+        if isinstance(dtype, bool) and isinstance(device, bool):          # (hidden, inter, bias, approx)
+            bias, approx, dtype, device = dtype, device, None, None
+        super().__init__(hidden_size, intermediate_size, dtype, device, bias=bias)
+        self.approx = bool(approx)
+        self.activation = "gelu_tanh" if approx else "gelu"
 
 
 RMSNorm, SwiGLU, GeGLU = TritonRMSNorm, TritonSwiGLU, TritonGeGLU
@@ -534,14 +562,39 @@ def inference_attention_single_token(q=None, k_cache=None, v_cache=None, seq_len
 
 
 class FlashAttention(nn.Module):
-    def __init__(self, config: FlashAttentionConfig | None = None):
+    """`FlashAttention(config)(q, k, v)`: [B, S, H, D] tensors.  The reference's `FlashAttention(head_dim, num_heads,
+    num_kv_heads, causal=False, dropout, sliding_window)(query, key, value, attn_mask)` takes and returns [B, H, S, D]
+    (data_pipeline/trainer/kernels/flash_attention.py:953); an explicit `attn_mask` goes through the fp32 path."""
+
+    def __init__(self, config: "FlashAttentionConfig | int | None" = None, num_heads: int | None = None,
+                 num_kv_heads: int | None = None, causal: bool | None = None, dropout: float = 0.0,
+                 sliding_window: int | None = None, *, head_dim: int | None = None):
         super().__init__()
+        self.heads_first = head_dim is not None or isinstance(config, int)
+        if self.heads_first:
+            head_dim = head_dim if head_dim is not None else config
+            config = FlashAttentionConfig(causal=bool(causal), dropout=dropout, head_dim=head_dim, num_heads=num_heads,
+                                          num_kv_heads=num_kv_heads or num_heads, sliding_window=sliding_window)
         self.config = config or FlashAttentionConfig()
         if self.config.dropout:
             raise ValueError("attention dropout is not supported")
 
-    def forward(self, q, k, v, cu_seqlens=None):
+    head_dim = property(lambda self: self.config.head_dim)
+    num_heads = property(lambda self: self.config.num_heads)
+    num_kv_heads = property(lambda self: self.config.num_kv_heads)
+    causal = property(lambda self: self.config.causal)
+    sliding_window = property(lambda self: self.config.window_size)
+
+    def forward(self, q=None, k=None, v=None, cu_seqlens=None, *, query=None, key=None, value=None, attn_mask=None):
         c = self.config
+        if query is not None or self.heads_first:
+            query, key, value = (query if query is not None else q), (key if key is not None else k), \
+                (value if value is not None else v)
+            attn_mask = attn_mask if attn_mask is not None else cu_seqlens
+            if attn_mask is not None:
+                return naive_attention(query=query, key=key, value=value, attn_mask=attn_mask, scale=c.softmax_scale)
+            return flash_attention(query=query, key=key, value=value, causal=c.causal, scale=c.softmax_scale,
+                                   sliding_window=c.window_size, softcap=c.softcap)
         return flash_attention(q, k, v, c.causal, c.softmax_scale, c.window_size, c.softcap, cu_seqlens)
 
 
@@ -556,32 +609,111 @@ class FlexAttention(FlashAttention):
             raise ValueError("sliding-window attention needs window_size")
         super().__init__(config)
 
+    def forward(self, q=None, k=None, v=None, cu_seqlens=None, *, Q=None, K=None, V=None, attention_mask=None,
+                is_causal: bool | None = None, use_inference_mode: bool = False):
+        """`attn(q, k, v)`: [B, S, H, D] in and out.  The reference's `attn(Q=, K=, V=, attention_mask=, is_causal=,
+        use_inference_mode=)` takes [B, heads, S, D] and returns [B, q_len, heads * D]; scale, soft-cap and window come
+        from the configuration (data_pipeline/trainer/kernels/flex_attention.py:1319)."""
+        if Q is None:
+            return super().forward(q, k, v, cu_seqlens)
+        from . import flex as _flex
+        c = self.config
+        causal = c.causal if is_causal is None else bool(is_causal)
+        if use_inference_mode and Q.shape[2] == 1 and attention_mask is None:
+            return inference_attention_single_token(Q, K, V, c)
+        if attention_mask is not None:
+            return _flex.sdpa_attention_forward(Q, K, V, c, attn_mask=attention_mask, is_causal=causal)
+        return _flex.flash_attention_forward(Q, K, V, c, causal=causal)
+
 
 class MultiHeadFlashAttention(nn.Module):
     """Self-attention block: fused qkv projection, rotary embedding, flash attention, output projection."""
 
-    def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int | None = None, head_dim: int | None = None,
-                 causal: bool = True, rope_theta: float | None = 10000.0, max_position: int = 8192, dtype=None,
-                 device=None):
+    def __init__(self, hidden_size: int | None = None, num_heads: int | None = None, num_kv_heads: int | None = None,
+                 head_dim: int | None = None, causal: bool | None = None, rope_theta: float | None = 10000.0,
+                 max_position: int = 8192, dtype=None, device=None, *, embed_dim: int | None = None,
+                 dropout: float = 0.0, bias: bool | None = None, sliding_window: int | None = None):
+        """`MultiHeadFlashAttention(hidden_size, num_heads, ...)`: causal, rotary positions, no biases.  The reference's
+        keyword form (`embed_dim=, num_heads, num_kv_heads, dropout, bias=True, causal=False, sliding_window`) is a
+        plain attention layer: no rotary embedding, biases on by default, `forward(query, key, value, key_cache,
+        value_cache)` (data_pipeline/trainer/kernels/flash_attention.py MultiHeadFlashAttention)."""
         super().__init__()
+        reference_form = embed_dim is not None
+        if reference_form:
+            hidden_size, rope_theta = embed_dim, None
+            causal = False if causal is None else causal
+            bias = True if bias is None else bias
+        if dropout:
+            raise ValueError("attention dropout is not supported")
+        causal = True if causal is None else causal
+        self.embed_dim = hidden_size
         self.h, self.kv = num_heads, num_kv_heads or num_heads
         self.d = head_dim or hidden_size // num_heads
         self.causal, self.rope_theta, self.max_position = causal, rope_theta, max_position
+        self.sliding_window = sliding_window
         self.wqkv = nn.Parameter(torch.empty((self.h + 2 * self.kv) * self.d, hidden_size, dtype=dtype, device=device))
         self.wo = nn.Parameter(torch.empty(hidden_size, self.h * self.d, dtype=dtype, device=device))
+        self.bqkv = nn.Parameter(torch.zeros((self.h + 2 * self.kv) * self.d, dtype=dtype, device=device)) if bias else None
+        self.bo = nn.Parameter(torch.zeros(hidden_size, dtype=dtype, device=device)) if bias else None
         nn.init.normal_(self.wqkv, std=0.02)
         nn.init.normal_(self.wo, std=0.02)
         self._tables = None
 
-    def forward(self, x, cu_seqlens=None):
+    num_heads = property(lambda self: self.h)
+    num_kv_heads = property(lambda self: self.kv)
+    head_dim = property(lambda self: self.d)
+
+    def _cross(self, query, key, value, key_cache, value_cache):
+        """Separate query / key / value inputs and an optional [B, Hkv, N, D] cache in front of the new keys: q, k and v
+        are projected with their slices of the fused weight."""
+        nq, nk = self.h * self.d, self.kv * self.d
+        bq, bk, bv = (None, None, None) if self.bqkv is None else self.bqkv.split((nq, nk, nk))
+        wq, wk, wv = self.wqkv.split((nq, nk, nk))
+        B, M, _ = query.shape
+        q = _gemm.linear(query, wq, bq).view(B, M, self.h, self.d)
+        k = _gemm.linear(key, wk, bk).view(B, key.shape[1], self.kv, self.d)
+        v = _gemm.linear(value, wv, bv).view(B, value.shape[1], self.kv, self.d)
+        if key_cache is not None and value_cache is not None:
+            k = torch.cat((key_cache.transpose(1, 2), k), dim=1)
+            v = torch.cat((value_cache.transpose(1, 2), v), dim=1)
+        if k.shape[1] == M:
+            o = flash_attention(q, k, v, self.causal, None, self.sliding_window)
+        else:                                               # the queries are the LAST M positions of the keys
+            N = k.shape[1]
+            rep = self.h // self.kv
+            kk, vv = k.repeat_interleave(rep, 2).transpose(1, 2), v.repeat_interleave(rep, 2).transpose(1, 2)
+            mask = None
+            if self.causal or self.sliding_window:
+                qi = torch.arange(N - M, N, device=q.device)[:, None]
+                ki = torch.arange(N, device=q.device)[None, :]
+                mask = torch.ones(M, N, dtype=torch.bool, device=q.device)
+                if self.causal:
+                    mask &= ki <= qi
+                if self.sliding_window:
+                    mask &= ki > qi - self.sliding_window
+            o = F.scaled_dot_product_attention(q.transpose(1, 2).float(), kk.float(), vv.float(), attn_mask=mask) \
+                .transpose(1, 2).to(q.dtype)
+        return _gemm.linear(o.reshape(B, M, nq), self.wo, self.bo)
+
+    def forward(self, x=None, cu_seqlens=None, value=None, key_cache=None, value_cache=None, *, query=None, key=None):
+        """`attn(x, cu_seqlens)`: self-attention.  `attn(query, key, value, key_cache, value_cache)` (key and value
+        default to the query): attention of `query` over `key` / `value`, optionally behind a cache."""
+        query = query if query is not None else x
+        if key is None and torch.is_tensor(cu_seqlens) and cu_seqlens.is_floating_point():
+            key, cu_seqlens = cu_seqlens, None               # positional (query, key, value)
+        if key is not None or value is not None or key_cache is not None:
+            key = key if key is not None else query
+            return self._cross(query, key, value if value is not None else key, key_cache, value_cache)
+        x = query
         B, S, _ = x.shape
-        qkv = _gemm.linear(x, self.wqkv)
+        qkv = _gemm.linear(x, self.wqkv, self.bqkv)
         if self.rope_theta:
             if self._tables is None or self._tables[0].device != x.device or self._tables[0].shape[0] < S:
                 self._tables = _rope.rope_tables(max(S, self.max_position), self.d, self.rope_theta, device=x.device)
             qkv = _rope.apply_rope_qkv(qkv, self.h + self.kv, self.d, *self._tables)
-        o = _attn.attention_qkv(qkv, self.h, self.kv, self.d, self.causal, cu_seqlens=cu_seqlens)
-        return _gemm.linear(o, self.wo)
+        o = _attn.attention_qkv(qkv, self.h, self.kv, self.d, self.causal, window=self.sliding_window,
+                                cu_seqlens=cu_seqlens)
+        return _gemm.linear(o, self.wo, self.bo)
 
 
 # ------------------------------------------------------------------------------------------------ rotary embeddings
@@ -994,8 +1126,10 @@ class FP8ScaleManager:
 
     FMAX = {FP8Format.E4M3: 448.0, FP8Format.E5M2: 57344.0}
 
-    def __init__(self, config: FP8Config | None = None):
+    def __init__(self, config: FP8Config | None = None, device=None):
+        """`device`: where the per-tensor scale tensors of `get_meta` live (the tensor's own device when None)."""
         self.config = config or FP8Config()
+        self.device = device
         self.history: dict[str, list[float]] = {}
 
     def update(self, name: str, tensor: torch.Tensor) -> float:
@@ -1035,12 +1169,19 @@ class FP8Linear(nn.Module):
     """Linear layer whose forward and input-gradient products run on the block-scaled fp8 kernel (bf16 CUDA inputs
     with in_features a multiple of 128); weight gradient and parameters stay bf16."""
 
-    def __init__(self, in_features: int, out_features: int, bias: bool = False, dtype=torch.bfloat16, device=None):
+    def __init__(self, in_features: int, out_features: int, bias: bool = False, dtype=torch.bfloat16, device=None, *,
+                 block_size: int = 128):
         super().__init__()
+        if isinstance(dtype, int) and not isinstance(dtype, torch.dtype):     # (in, out, bias, block_size, device, dtype)
+            block_size, dtype = dtype, torch.bfloat16
+        if block_size != 128:
+            raise ValueError("the block-scaled fp8 GEMM uses 128 x 128 weight blocks")
+        self.block_size = block_size
         self.weight = nn.Parameter(torch.empty(out_features, in_features, dtype=dtype, device=device))
         self.bias = nn.Parameter(torch.zeros(out_features, dtype=dtype, device=device)) if bias else None
         nn.init.normal_(self.weight, std=0.02)
 
+    @reference_kwargs(X="x")
     def forward(self, x):
         y = _fp8.fp8_linear(x, self.weight) if _fp8.available(x) and self.weight.shape[0] % 8 == 0 \
             else _gemm.linear(x, self.weight)
