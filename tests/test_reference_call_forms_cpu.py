@@ -538,3 +538,66 @@ def test_kernel_modules_take_the_reference_forms():
     with pytest.raises(ValueError):
         FP8Linear(128, 16, block_size=64)
     assert FP8ScaleManager(FP8Config(), "cpu").device == "cpu"
+
+
+def test_remaining_reference_forms_of_shared_classes():
+    import torch.nn as nn
+    import torch._inductor.config as inductor
+    from trainscale_b200.benchmark_suite import BenchmarkSuite
+    from trainscale_b200.kernels.compat import InductorConfig
+    from trainscale_b200.losses import ChunkedCrossEntropyLoss, HuberLoss
+    from trainscale_b200.metrics.throughput import ThroughputTracker
+    from trainscale_b200.parallel.activation import ActivationCheckpointConfig, HierarchicalCheckpointManager
+    from trainscale_b200.parallel.dist_kernels import DistributedKernels, GradientCompressor, ZeroCopyTransfer
+    from trainscale_b200.parallel.grad_buffer import ParamAndGradBucketGroup, ParamAndGradBuffer
+    from trainscale_b200.parallel.mesh import MeshCache, ParallelDims, ParallelDimsConfig
+    from trainscale_b200.registry import DependencyGraph, KernelPatcher
+    from trainscale_b200.utils.cuda_graphs import InductorConfigManager, ModelCompiler
+    from types import SimpleNamespace
+
+    graph = DependencyGraph()
+    graph.add_module(name="a", dependencies=["b"])
+    assert graph.edges == {"a": {"b"}, "b": set()}
+    lin = nn.Linear(2, 2)
+    assert KernelPatcher().patch(lin, model_info=None) is lin
+    tracker = ThroughputTracker()
+    assert tracker.compute_mfu(flops_per_token=1e9, seq_len=128) == 0.0           # nothing measured yet
+    tracker.load_state_dict(state=tracker.state_dict())
+    z, y = torch.randn(10, 7), torch.randint(0, 7, (10,))
+    assert torch.allclose(ChunkedCrossEntropyLoss(chunk_size=4)(logits=z, labels=y), nn.functional.cross_entropy(z, y))
+    assert float(HuberLoss()(pred=z, target=z + 1)) == 0.5
+    before = inductor.max_autotune
+    InductorConfigManager.apply(InductorConfig(max_autotune=not before))          # the class-level form of the reference
+    assert inductor.max_autotune != before
+    InductorConfigManager.restore()
+    assert inductor.max_autotune == before
+    assert InductorConfigManager(max_autotune=True).apply() == {}                 # recorded only unless asked to apply
+    assert ModelCompiler().compile(lin, example_inputs=torch.randn(1, 2))(torch.ones(1, 2)).shape == (1, 2)
+    copies = ZeroCopyTransfer(16)
+    assert copies.staging_bytes == 16 * 2 ** 20 and copies.host_to_device(x=z, device=None, use_pool=False) is z
+    assert BenchmarkSuite().run_rms_norm([4], [2048], [4096]) == [] or torch.cuda.is_available()
+    planner = HierarchicalCheckpointManager(config=ActivationCheckpointConfig(), num_layers=12)
+    assert planner.num_layers == 12 and not planner.layers
+
+    dims = ParallelDims(config=ParallelDimsConfig(world_size=1))
+    assert dims.config.world_size == 1
+    MeshCache.set("tp", "mesh-of-tp")
+    assert MeshCache.get("tp") == "mesh-of-tp" and MeshCache.get(name="absent") is None
+    ddp = SimpleNamespace(use_distributed_optimizer=False, overlap_grad_reduce=False, average_in_collective=True)
+    names = {p: n for n, p in lin.named_parameters()}
+    buffer = ParamAndGradBuffer(ddp, torch.float32, torch.float32, list(lin.parameters()), None, 1000, names, 0.5)
+    assert buffer.numel_unpadded == 6 and buffer.gradient_scaling_factor == 0.5 and len(buffer.param_to_name) == 2
+    group = ParamAndGradBucketGroup(buffer.buckets, ddp, None, 1)
+    assert group.overlap_grad_reduce is False and group.average is True
+    with pytest.raises(ValueError):
+        ParamAndGradBucketGroup(buffer.buckets, ddp_config=ddp, collective_group=None, collective_group_size=2)
+
+    kernels = DistributedKernels()                                                # no process group: identities
+    t = torch.ones(4, 2)
+    assert kernels.sequence_parallel_all_gather(x=t, dim=1, group=None, async_op=False) is t
+    out = torch.empty(4, 2)
+    assert float(kernels.reduce_scatter(output=out, input_tensors=[t * 2]).sum()) == 16.0
+    assert kernels.all_gather_into_tensor(None, input_tensor=t) is t and kernels.broadcast_object_list(object_list=[1]) == [1]
+    compressor = GradientCompressor(use_fp16=True)
+    payload, meta = compressor.compress(t, tensor_id=3)
+    assert compressor.decompress(tensor=payload[0], metadata=meta).dtype is torch.float32

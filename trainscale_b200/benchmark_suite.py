@@ -56,10 +56,10 @@ class Timer:
         return total / iters
 
 
-def bench_rmsnorm(t, small):
+def bench_rmsnorm(t, small, shapes=None):
     from .ops import norm
     out = []
-    shapes = [(4, 2048, 4096)] if small else [(4, 2048, 4096), (4, 4096, 8192), (32, 2048, 4096), (32, 4096, 8192)]
+    shapes = shapes or ([(4, 2048, 4096)] if small else [(4, 2048, 4096), (4, 4096, 8192), (32, 2048, 4096), (32, 4096, 8192)])
     for B, S, D in shapes:
         x = torch.randn(B * S, D, device="cuda", dtype=torch.bfloat16)
         w = torch.ones(D, device="cuda", dtype=torch.bfloat16)
@@ -69,10 +69,10 @@ def bench_rmsnorm(t, small):
     return out
 
 
-def bench_swiglu(t, small):
+def bench_swiglu(t, small, sizes=None):
     from .ops import activation
     out = []
-    for rows, I in ([(2048, 11008)] if small else [(2048, 11008), (8192, 14336)]):
+    for rows, I in (sizes or ([(2048, 11008)] if small else [(2048, 11008), (8192, 14336)])):
         gu = torch.randn(rows, 2 * I, device="cuda", dtype=torch.bfloat16)
         ms = t(lambda: activation.glu(gu), graph=True)
         base = t(lambda: F.silu(gu[:, :I]) * gu[:, I:], graph=True)
@@ -80,11 +80,11 @@ def bench_swiglu(t, small):
     return out
 
 
-def bench_rope(t, small):
+def bench_rope(t, small, seq_lens=None, dim: int = 128):
     from .ops import rope
     out = []
-    for S in ([4096] if small else [4096, 8192, 16384]):
-        Hq, Hkv, D = 32, 8, 128
+    for S in (seq_lens or ([4096] if small else [4096, 8192, 16384])):
+        Hq, Hkv, D = 32, 8, dim
         cos, sin = rope.rope_tables(S, D, 500000.0, "cuda")
         qkv = torch.randn(1, S, (Hq + 2 * Hkv) * D, device="cuda", dtype=torch.bfloat16)
         # the decoder's form: q|k rotated where the projection wrote them (no copy)
@@ -96,11 +96,11 @@ def bench_rope(t, small):
     return out
 
 
-def bench_cross_entropy(t, small):
+def bench_cross_entropy(t, small, vocab_size: int = 128256, token_counts=None):
     from .ops import cross_entropy as ce
     out = []
-    V = 128256
-    for T in ([4096] if small else [4096, 16384]):
+    V = vocab_size
+    for T in (token_counts or ([4096] if small else [4096, 16384])):
         logits = torch.randn(T, V, device="cuda", dtype=torch.bfloat16)
         labels = torch.randint(0, V, (T,), device="cuda")
         ms = t(lambda: ce.cross_entropy_logits(logits, labels), iters=5)
@@ -124,11 +124,11 @@ def bench_gemm(t, small):
     return out
 
 
-def bench_attention(t, small):
+def bench_attention(t, small, seq_lens=None, head_dim: int = 128):
     from .ops import flash
     out = []
-    for S in ([2048] if small else [4096, 8192, 16384]):
-        Hq, Hkv, D = 32, 8, 128
+    for S in (seq_lens or ([2048] if small else [4096, 8192, 16384])):
+        Hq, Hkv, D = 32, 8, head_dim
         qkv = torch.randn(1, S, (Hq + 2 * Hkv) * D, device="cuda", dtype=torch.bfloat16, requires_grad=True)
         ms = t(lambda: flash.flash_forward_only(qkv.detach(), Hq, Hkv, D, True))
         q, k, v = [x.transpose(1, 2) for x in qkv.detach().view(1, S, Hq + 2 * Hkv, D).split((Hq, Hkv, Hkv), 2)]
@@ -153,10 +153,10 @@ def bench_adamw(t, small):
     return [dict(name=f"adamw_flat n={n}", ms=ms, baseline_ms=None, gbs=n * 28 / ms / 1e6)]
 
 
-def bench_fp8(t, small):
+def bench_fp8(t, small, shapes=None):
     from .ops import fp8
     out = []
-    for M, N, K in ([(4096, 4096, 4096)] if small else [(8192, 4096, 4096), (8192, 28672, 4096), (8192, 4096, 14336)]):
+    for M, N, K in (shapes or ([(4096, 4096, 4096)] if small else [(8192, 4096, 4096), (8192, 28672, 4096), (8192, 4096, 14336)])):
         x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
         w = (torch.randn(N, K, device="cuda") / K ** 0.5).to(torch.bfloat16)
         xq, xs = fp8.quant_act(x)
@@ -386,38 +386,49 @@ class BenchmarkSuite:
         self.results: list[dict] = []
         self._timer: Timer | None = None
 
-    def _run(self, fn) -> list[dict]:
+    def _run(self, fn, **sizes) -> list[dict]:
         if not torch.cuda.is_available():
             return []
         if self._timer is None:
             self._timer = Timer(64 if self.small else 256)
-        rows = fn(self._timer, self.small)
+        rows = fn(self._timer, self.small, **{k: v for k, v in sizes.items() if v is not None})
         self.results += rows
         return rows
 
-    def run_rms_norm(self):
-        return self._run(bench_rmsnorm)
+    # the size arguments are the reference's (data_pipeline/trainer/kernels/benchmark_suite.py:111-300); None keeps this
+    # suite's own shapes
+    def run_rms_norm(self, batch_sizes=None, seq_lens=None, hidden_dims=None):
+        shapes = None
+        if batch_sizes or seq_lens or hidden_dims:
+            shapes = [(b, s, d) for b in (batch_sizes or [4]) for s in (seq_lens or [2048]) for d in (hidden_dims or [4096])]
+        return self._run(bench_rmsnorm, shapes=shapes)
 
     def run_layer_norm(self):
         return self._run(bench_layernorm)
 
-    def run_fused_gelu(self):
-        return self._run(bench_gelu)
+    def run_fused_gelu(self, sizes=None):
+        """`sizes`: (rows, cols) pairs."""
+        return self._run(bench_gelu, counts=[r * c for r, c in sizes] if sizes else None)
 
-    def run_swiglu(self):
-        return self._run(bench_swiglu)
+    def run_swiglu(self, sizes=None):
+        """`sizes`: (rows, intermediate size) pairs."""
+        return self._run(bench_swiglu, sizes=list(sizes) if sizes else None)
 
-    def run_fp8_quantization(self):
-        return self._run(bench_fp8)
+    def run_fp8_quantization(self, sizes=None):
+        """`sizes`: (rows, cols) of the activation that is quantised (and multiplied by a cols x cols weight)."""
+        return self._run(bench_fp8, shapes=[(r, c, c) for r, c in sizes] if sizes else None)
 
-    def run_rope(self):
-        return self._run(bench_rope)
+    def run_rope(self, seq_lens=None, dim: int | None = None):
+        return self._run(bench_rope, seq_lens=list(seq_lens) if seq_lens else None, dim=dim)
 
-    def run_flash_attention(self):
-        return self._run(bench_attention)
+    def run_flash_attention(self, seq_lens=None, head_dim: int | None = None):
+        if head_dim not in (None, 64, 128):
+            raise ValueError("the flash kernels cover head dimensions 64 and 128")
+        return self._run(bench_attention, seq_lens=list(seq_lens) if seq_lens else None, head_dim=head_dim)
 
-    def run_cross_entropy(self):
-        return self._run(bench_cross_entropy)
+    def run_cross_entropy(self, vocab_size: int | None = None, batch_tokens: int | None = None):
+        return self._run(bench_cross_entropy, vocab_size=vocab_size,
+                         token_counts=[int(batch_tokens)] if batch_tokens else None)
 
     def run_gemm(self):
         return self._run(bench_gemm)
@@ -451,10 +462,10 @@ class BenchmarkSuite:
         return "\n".join(lines)
 
 
-def bench_gelu(t, small):
+def bench_gelu(t, small, counts=None):
     from .ops import activation
     out = []
-    for n in ([1 << 24] if small else [1 << 24, 1 << 27]):
+    for n in (counts or ([1 << 24] if small else [1 << 24, 1 << 27])):
         x = torch.randn(n, device="cuda", dtype=torch.bfloat16)
         ms = t(lambda: activation.gelu(x, "tanh"), graph=True)
         base = t(lambda: F.gelu(x, approximate="tanh"), graph=True)

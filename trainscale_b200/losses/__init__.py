@@ -114,7 +114,19 @@ class ChunkedCrossEntropyLoss(nn.Module):
         self.chunk_size, self.ignore_index, self.label_smoothing = chunk_size, ignore_index, label_smoothing
         self.reduction, self.softcap = reduction, softcap
 
-    def forward(self, hidden, weight, labels):
+    def forward(self, hidden=None, weight=None, labels=None, *, logits=None):
+        """`forward(hidden, lm_head_weight, labels)` never builds the logits.  The reference's `forward(logits, labels)`
+        (data_pipeline/trainer/loss/sota_losses.py ChunkedCrossEntropyLoss) takes logits that already exist and walks
+        them in row chunks of `chunk_size`, so that only one chunk is upcast at a time."""
+        if logits is not None or labels is None:
+            logits, labels = (logits if logits is not None else hidden), (labels if labels is not None else weight)
+            z, y = logits.reshape(-1, logits.shape[-1]), labels.reshape(-1)
+            rows = torch.cat([F.cross_entropy(z[i:i + self.chunk_size].float(), y[i:i + self.chunk_size],
+                                              ignore_index=self.ignore_index, label_smoothing=self.label_smoothing,
+                                              reduction="none") for i in range(0, z.shape[0], self.chunk_size)])
+            if self.reduction == "none":
+                return rows.view(labels.shape)
+            return rows.sum() / (y != self.ignore_index).sum().clamp(min=1) if self.reduction == "mean" else rows.sum()
         loss, _ = ce_ops.fused_linear_cross_entropy(hidden, weight, labels.reshape(-1), self.ignore_index,
                                                     self.label_smoothing, 1.0, self.softcap,
                                                     min(self.chunk_size, 8192), self.reduction)
@@ -528,7 +540,10 @@ class ExpertEntropyLoss(nn.Module):
 # ------------------------------------------------------------------------------------------------ regression / ranking / segmentation
 class MSELoss(nn.MSELoss): ...
 class MAELoss(nn.L1Loss): ...
-class HuberLoss(nn.HuberLoss): ...
+class HuberLoss(nn.HuberLoss):
+    @reference_kwargs(pred="input")
+    def forward(self, input: torch.Tensor, target: torch.Tensor) -> torch.Tensor:
+        return super().forward(input, target)
 class SmoothL1Loss(nn.SmoothL1Loss): ...
 
 

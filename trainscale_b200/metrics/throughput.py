@@ -13,6 +13,7 @@ from collections import deque
 from pathlib import Path
 
 import torch
+from ..utils.refargs import ANY, reference_kwargs  # noqa: F401
 
 PEAK_TFLOPS = {"B200": 2250.0, "H200": 989.0, "H100": 989.0, "A100": 312.0, "L40S": 362.0, "A10": 125.0, "T4": 65.0,
                "V100": 125.0, "RTX 4090": 330.0, "RTX 3090": 142.0}
@@ -89,10 +90,15 @@ class ThroughputTracker:
     def tflops(self) -> float:
         return self.tokens_per_second() * self.flops_per_token / 1e12
 
-    def compute_mfu(self, model_params: int | None = None, peak_tflops: float | None = None) -> float:
-        """Achieved FLOP/s over the peak of all GPUs.  FLOPs per token: the tracker's own figure, or 6 x `model_params`
-        (forward + backward of a dense decoder, attention not counted) when that is given."""
+    def compute_mfu(self, model_params: int | None = None, peak_tflops: float | None = None, *,
+                    flops_per_token: float | None = None, seq_len: int | None = None) -> float:
+        """Achieved FLOP/s over the peak of all GPUs.  FLOPs per token: `flops_per_token` when given, else the tracker's
+        own figure, or 6 x `model_params` (forward + backward of a dense decoder, attention not counted) when that is
+        given.  `seq_len` is accepted for the reference's signature; the 6 N estimate does not depend on it."""
         denom = (peak_tflops if peak_tflops is not None else self.peak) * self.world_size
+        if flops_per_token is not None:
+            rate = self.tokens_per_second() or self.tokens_per_sec()
+            return rate * float(flops_per_token) / 1e12 / denom if denom > 0 else 0.0
         if model_params:
             rate = self.tokens_per_second() or self.tokens_per_sec()
             return rate * 6.0 * model_params / 1e12 / denom if denom > 0 else 0.0
@@ -102,6 +108,7 @@ class ThroughputTracker:
         return {"total_tokens": self.total_tokens, "total_seconds": self.total_seconds,
                 "total_samples": self.total_samples, "step_count": self.step_count}
 
+    @reference_kwargs(state="sd")
     def load_state_dict(self, sd):
         self.total_tokens, self.total_seconds = sd["total_tokens"], sd["total_seconds"]
         self.total_samples, self.step_count = sd.get("total_samples", 0), sd.get("step_count", 0)

@@ -836,12 +836,15 @@ class HierarchicalCheckpointManager:
     keeps only ITS input (g tensors), re-running itself when its turn comes.  Peak kept activations are about
     L / g + g layer inputs (minimal at g = sqrt(L)) for two extra forwards."""
 
-    def __init__(self, layers, group_size: int | None = None, use_reentrant: bool = False, levels: int | None = None):
+    def __init__(self, layers=None, group_size: int | None = None, use_reentrant: bool = False, levels: int | None = None,
+                 *, config: "ActivationCheckpointConfig | None" = None, num_layers: int | None = None):
         """`layers`: the modules of the chain.  The planning-only form `HierarchicalCheckpointManager(config,
         num_layers)` (data_pipeline/trainer/distributed/activation_checkpoint.py:1466) builds the segment hierarchy
         without modules: `segment_size` x 2^level layers per segment at each of `hierarchy_levels` levels."""
+        if config is not None:
+            layers, group_size = config, (num_layers if num_layers is not None else group_size)
         if isinstance(layers, ActivationCheckpointConfig):
-            cfg, L = layers, int(group_size or 0)
+            cfg, L = layers, int((num_layers if num_layers is not None else group_size) or 0)
             self.layers, group_size, levels = [], cfg.segment_size, cfg.hierarchy_levels
             use_reentrant = cfg.use_reentrant
         else:

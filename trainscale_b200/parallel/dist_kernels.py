@@ -480,7 +480,14 @@ class DistributedKernels:
 class ZeroCopyTransfer:
     """Host <-> device copies through a reusable pinned staging buffer, on their own stream."""
 
-    def __init__(self, device: torch.device | str | None = None, staging_bytes: int = 64 * 2 ** 20):
+    def __init__(self, device: "torch.device | str | int | None" = None, staging_bytes: int = 64 * 2 ** 20, *,
+                 pool_size_mb: int | None = None):
+        """`pool_size_mb` (the reference's only argument, also taken positionally as an int): size of the pinned staging
+        buffer."""
+        if isinstance(device, int) and not isinstance(device, bool):
+            pool_size_mb, device = device, None
+        if pool_size_mb is not None:
+            staging_bytes = int(pool_size_mb) * 2 ** 20
         self.device = torch.device(device) if device is not None else \
             (torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu"))
         self._cuda = self.device.type == "cuda"
@@ -496,19 +503,33 @@ class ZeroCopyTransfer:
             self._staging[dtype] = buf
         return buf[:numel]
 
-    def host_to_device(self, tensor: torch.Tensor, non_blocking: bool = True) -> torch.Tensor:
+    @reference_kwargs(x="tensor")
+    def host_to_device(self, tensor: torch.Tensor, non_blocking: bool = True, *, device=None,
+                       use_pool: bool = True) -> torch.Tensor:
+        """`device`: target (this object's device when None); `use_pool=False` pins a fresh buffer instead of the shared
+        staging buffer (safe when several transfers are in flight)."""
+        if device is not None and torch.device(device) != self.device:
+            return ZeroCopyTransfer(device, self.staging_bytes).host_to_device(tensor, non_blocking, use_pool=use_pool)
         if not self._cuda:
             return tensor
-        src = tensor if tensor.is_pinned() else self._pinned(tensor.numel(), tensor.dtype).copy_(tensor.reshape(-1))
+        if tensor.is_pinned():
+            src = tensor
+        elif use_pool:
+            src = self._pinned(tensor.numel(), tensor.dtype).copy_(tensor.reshape(-1))
+        else:
+            src = torch.empty(tensor.numel(), dtype=tensor.dtype, pin_memory=True).copy_(tensor.reshape(-1))
         with torch.cuda.stream(self._stream):
             out = src.to(self.device, non_blocking=non_blocking).view(tensor.shape)
         torch.cuda.current_stream(self.device).wait_stream(self._stream)
         return out
 
-    def device_to_host(self, tensor: torch.Tensor, non_blocking: bool = False) -> torch.Tensor:
+    @reference_kwargs(x="tensor")
+    def device_to_host(self, tensor: torch.Tensor, non_blocking: bool = False, *, use_pool: bool = False) -> torch.Tensor:
+        """`use_pool=True` lands in the shared staging buffer: the result is only valid until the next transfer."""
         if not tensor.is_cuda:
             return tensor
-        host = torch.empty(tensor.shape, dtype=tensor.dtype, pin_memory=True)
+        host = self._pinned(tensor.numel(), tensor.dtype).view(tensor.shape) if use_pool else \
+            torch.empty(tensor.shape, dtype=tensor.dtype, pin_memory=True)
         self._stream.wait_stream(torch.cuda.current_stream(self.device))
         with torch.cuda.stream(self._stream):
             host.copy_(tensor, non_blocking=True)

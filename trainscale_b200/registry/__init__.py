@@ -107,6 +107,7 @@ class DependencyGraph:
         self.edges: dict[str, set[str]] = {}
         self.declared: set[str] = set()       # nodes added themselves, as opposed to only named as a dependency
 
+    @reference_kwargs(name="node", dependencies="deps")
     def add(self, node: str, deps: Iterable[str] = ()):
         deps = list(deps)
         self.declared.add(node)
@@ -462,12 +463,21 @@ class KernelPatcher:
         return {n: self.matrix.resolve(n, self.hw) for n in ("gemm_tcgen05", "flash_attention_tcgen05", "rmsnorm_cuda",
                                                               "fused_linear_ce", "fused_collectives")}
 
-    def patch(self, model, dtype=torch.bfloat16, device=None):
-        """Framework decoders pass through; HF Llama-family models are converted; anything else is returned as is."""
+    def patch(self, model, dtype=torch.bfloat16, device=None, *, model_info=None):
+        """Framework decoders pass through; HF Llama-family models are converted; anything else is returned as is.
+        `model_info` (a `ModelInfo`, also accepted in `dtype`'s place as in the reference's `patch(model, model_info)`)
+        names the architecture when the class name does not."""
         from ..models.llama import LlamaForCausalLM
+        if dtype is not None and not isinstance(dtype, torch.dtype):
+            model_info, dtype = dtype, torch.bfloat16
         if isinstance(model, LlamaForCausalLM):
             return model
         arch = type(model).__name__
+        if model_info is not None and arch not in ("LlamaForCausalLM", "MistralForCausalLM", "Qwen2ForCausalLM",
+                                                   "MixtralForCausalLM", "GemmaForCausalLM"):
+            family = str(getattr(model_info, "architecture", None) or getattr(model_info, "model_type", "") or "").lower()
+            arch = {"llama": "LlamaForCausalLM", "mistral": "MistralForCausalLM", "qwen2": "Qwen2ForCausalLM",
+                    "mixtral": "MixtralForCausalLM", "gemma": "GemmaForCausalLM"}.get(family, arch)
         if arch in ("LlamaForCausalLM", "MistralForCausalLM", "Qwen2ForCausalLM", "MixtralForCausalLM",
                     "GemmaForCausalLM") and \
                 not any(k.endswith("o_proj.bias") for k in model.state_dict()):

@@ -117,9 +117,14 @@ def compile_model(model, config: CompilationConfig | None = None):
     have no counterpart here: kernels are hand-written, only launches are captured."""
     mgr = CUDAGraphManager(config)
 
+    def call(*tensors):
+        out = model(*tensors)
+        return out.logits if hasattr(out, "logits") else out
+
     @torch.no_grad()
-    def run(input_ids):
-        return mgr.run(lambda x: model(input_ids=x).logits, input_ids)
+    def run(*args, input_ids=None):
+        """`run(input_ids)` for a language model (its logits come back), or the positional tensors of any module."""
+        return mgr.run(call, *(((input_ids,) if input_ids is not None else ()) + args))
 
     run.manager = mgr
     return run
@@ -151,8 +156,15 @@ class ModelCompiler:
         self.config = config or CompilationConfig()
         self.graphs = CUDAGraphManager()
 
-    def compile(self, model):
-        return compile_model(model, self.config)
+    def compile(self, model, example_inputs=None):
+        """`example_inputs` (a tensor or a tuple of them): one call is made right away, so that the graph of that shape
+        is captured here and not on the first training step."""
+        compiled = compile_model(model, self.config)
+        if example_inputs is not None:
+            args = example_inputs if isinstance(example_inputs, (tuple, list)) else (example_inputs,)
+            with torch.no_grad():
+                compiled(*args)
+        return compiled
 
     def for_inference(self, model):
         return optimize_for_inference(model)
@@ -211,8 +223,31 @@ class InductorConfigManager:
         except Exception:
             return None
 
-    def apply(self) -> dict[str, object]:
-        """Returns the options that were actually set on torch's inductor config (empty unless apply_to_torch)."""
+    _last: "InductorConfigManager | None" = None
+
+    @classmethod
+    def from_config(cls, config, apply_to_torch: bool = True) -> "InductorConfigManager":
+        """Manager for an `InductorConfig` dataclass: `triton_x` fields become the `triton.x` options, `extra` is merged."""
+        import dataclasses
+        fields = dataclasses.asdict(config) if dataclasses.is_dataclass(config) else dict(config)
+        extra = fields.pop("extra", None) or {}
+        opts = {("triton." + k[len("triton_"):] if k.startswith("triton_") else k): v for k, v in fields.items()}
+        opts.update(extra)
+        m = cls(apply_to_torch=apply_to_torch)
+        m.options.update(opts)
+        return m
+
+    def apply(self=None, config=None) -> dict[str, object]:
+        """Returns the options that were actually set on torch's inductor config (empty unless apply_to_torch).
+        `InductorConfigManager.apply(config)` on the CLASS is the reference's form: the `InductorConfig` is applied to
+        torch's inductor settings (for user code that calls `torch.compile`), `InductorConfigManager.restore()` on the
+        class undoes it."""
+        if not isinstance(self, InductorConfigManager):
+            config = config if config is not None else self
+            InductorConfigManager._last = InductorConfigManager.from_config(config)
+            return InductorConfigManager._last.apply()
+        if config is not None:
+            self.options.update(InductorConfigManager.from_config(config).options)
         done: dict[str, object] = {}
         cfg = self._target() if self.apply_to_torch else None
         if cfg is None:
@@ -228,7 +263,11 @@ class InductorConfigManager:
                 done[k] = v
         return done
 
-    def restore(self) -> None:
+    def restore(self=None) -> None:
+        if not isinstance(self, InductorConfigManager):           # InductorConfigManager.restore() on the class
+            if InductorConfigManager._last is not None:
+                InductorConfigManager._last.restore()
+            return
         cfg = self._target()
         if cfg is None:
             return
