@@ -250,3 +250,70 @@ def test_last_helpers_behave():
                                      "hardware": {"device": "cpu", "precision": "fp32"},
                                      "distributed": {"enabled": False}})
     assert isinstance(tr, SOTATrainer)
+
+
+def _reference_method_params(root: Path) -> dict[tuple[str, str], list[list[str]]]:
+    """{(class, method): [parameter names of each definition]} for constructors and public methods of the reference's
+    module-level classes.  `forward` / `backward` of autograd functions are left out: `Function.apply` passes their
+    arguments by position, so their parameter names are not part of any call."""
+    out: dict[tuple[str, str], list[list[str]]] = {}
+    for p in root.rglob("*.py"):
+        if "examples" in p.parts:
+            continue
+        try:
+            tree = ast.parse(p.read_text())
+        except SyntaxError:
+            continue
+        for node in tree.body:
+            if not isinstance(node, ast.ClassDef) or node.name.startswith("_"):
+                continue
+            bases = {getattr(b, "attr", getattr(b, "id", "")) for b in node.bases}
+            for n in node.body:
+                if not isinstance(n, (ast.FunctionDef, ast.AsyncFunctionDef)):
+                    continue
+                if n.name.startswith("_") and n.name != "__init__":
+                    continue
+                decorators = {getattr(d, "id", getattr(d, "attr", "")) for d in n.decorator_list}
+                if "property" in decorators or "setter" in decorators:
+                    continue
+                if "Function" in bases and n.name in ("forward", "backward"):
+                    continue
+                a = n.args
+                names = [x.arg for x in a.posonlyargs + a.args + a.kwonlyargs if x.arg not in ("self", "cls")]
+                out.setdefault((node.name, n.name), []).append(names)
+    return out
+
+
+def test_shared_methods_take_the_reference_keyword_names():
+    """For every class that exists under the same name on both sides, the constructor and each public method of ours
+    can be called with every parameter name of the reference's as a keyword."""
+    import inspect
+
+    ref = _reference_root()
+    if ref is None:
+        pytest.skip("the reference package is not on this machine")
+    ours = _our_classes()
+
+    def lacking(fn, names):
+        if fn is None or isinstance(fn, property):
+            return []
+        try:
+            ps = inspect.signature(fn).parameters
+        except (ValueError, TypeError):
+            return []
+        if any(p.kind is p.VAR_KEYWORD for p in ps.values()):
+            return []
+        return [n for n in names if n not in ps]
+
+    missing = {}
+    for (cname, mname), variants in _reference_method_params(ref).items():
+        if cname not in ours:
+            continue
+        targets = [c if mname == "__init__" else inspect.getattr_static(c, mname, None) for c in ours[cname]]
+        targets = [getattr(t, "__func__", t) for t in targets if t is not None]
+        if not targets:
+            continue
+        best = min((lacking(fn, names) for names in variants for fn in targets), key=len)
+        if best:
+            missing[f"{cname}.{mname}"] = best
+    assert not missing, f"{len(missing)} methods lack reference keywords: {sorted(missing.items())[:15]}"

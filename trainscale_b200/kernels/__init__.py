@@ -26,7 +26,7 @@ from ..ops import gemm as _gemm
 from ..ops import moe as _moe
 from ..ops import norm as _norm
 from ..ops import rope as _rope
-from ..losses import Fast_CrossEntropyLoss, FusedCrossEntropyFunction  # noqa: F401
+from ..losses import FusedCrossEntropyFunction  # noqa: F401
 from ..utils.explicit_backward import ExplicitBackward as _ExplicitBackward
 from ..utils.refargs import ANY, reference_kwargs
 from ..parallel.dist_kernels import (DistributedBackend, DistributedConfig, DistributedKernels,  # noqa: F401
@@ -183,9 +183,68 @@ def fast_cross_entropy_loss(logits, labels, ignore_index: int = -100, label_smoo
     return s / (n_items if n_items is not None else (y != ignore_index).sum().clamp(min=1))
 
 
-Fast_RMS_LayerNorm = _norm._RMSNormFn
-Fast_SwiGLU = _act._GluFn
-Fast_GeGLU = _act._GluFn
+# ---- `apply`-style entry points with the reference's argument order (data_pipeline/trainer/kernels/triton_kernels.py);
+# the backward passes are those of the ops underneath.  `forward(ctx, ...)` / `backward(ctx, ...)` exist for code that
+# embeds the op in its own autograd function.
+from .compat import _FunctionPair  # noqa: E402
+
+
+class Fast_RMS_LayerNorm(_FunctionPair):
+    """`apply(X, weight, eps)` -> RMS-normalised X."""
+
+    @staticmethod
+    def apply(X, weight, eps: float = 1e-6):
+        return _norm.rmsnorm(X, weight, eps)[0]
+
+    @classmethod
+    def forward(cls, ctx, X, weight, eps: float = 1e-6):
+        return super().forward(ctx, X, weight, eps)
+
+    @classmethod
+    def backward(cls, ctx, dY):
+        return super().backward(ctx, dY)
+
+
+class Fast_SwiGLU(_FunctionPair):
+    """`apply(gate, up)` -> silu(gate) * up."""
+
+    @staticmethod
+    def apply(gate, up):
+        return _act.swiglu(gate, up)
+
+    @classmethod
+    def forward(cls, ctx, gate, up):
+        return super().forward(ctx, gate, up)
+
+
+class Fast_GeGLU(_FunctionPair):
+    """`apply(gate, up, approx=False)` -> gelu(gate) * up (tanh approximation when `approx`)."""
+
+    @staticmethod
+    def apply(gate, up, approx: bool = False):
+        return geglu_forward(gate, up, bool(approx))
+
+    @classmethod
+    def forward(cls, ctx, gate, up, approx: bool = False):
+        return super().forward(ctx, gate, up, approx)
+
+
+class Fast_CrossEntropyLoss(_FunctionPair):
+    """`apply(logits [N, V], labels [N], logit_softcapping=0, logit_scaling=0)` -> per-row losses [N] (0 for ignored
+    rows); the mean over the non-ignored rows is `fast_cross_entropy_loss`."""
+
+    @staticmethod
+    def apply(logits, labels, logit_softcapping: float = 0.0, logit_scaling: float = 0.0):
+        return fast_cross_entropy_loss(logits, labels, reduction="none", logit_softcapping=logit_softcapping,
+                                       logit_scaling=logit_scaling)
+
+    @classmethod
+    def forward(cls, ctx, logits, labels, logit_softcapping: float = 0.0, logit_scaling: float = 0.0):
+        return super().forward(ctx, logits, labels, logit_softcapping, logit_scaling)
+
+    @classmethod
+    def backward(cls, ctx, dlosses):
+        return super().backward(ctx, dlosses)
 
 
 class TritonRMSNorm(nn.Module):
@@ -823,7 +882,20 @@ def inplace_rope_embedding(qkv=None, n_heads=None, n_kv_heads=None, head_dim=Non
     return _rope.apply_rope_qkv(qkv, n_heads + n_kv_heads, head_dim, cos, sin, positions)
 
 
-Fast_RoPE_Embedding = _rope._RopeFn
+class Fast_RoPE_Embedding(_FunctionPair):
+    """`apply(Q [B, S, H, D], cos, sin)` -> rotated Q (data_pipeline/trainer/kernels/rope_kernels.py:1210)."""
+
+    @staticmethod
+    def apply(Q, cos, sin):
+        return fast_rope_embedding(Q, cos, sin)
+
+    @classmethod
+    def forward(cls, ctx, Q, cos, sin):
+        return super().forward(ctx, Q, cos, sin)
+
+    @classmethod
+    def backward(cls, ctx, dQ):
+        return super().backward(ctx, dQ)
 
 
 # ------------------------------------------------------------------------------------------------ fused LoRA

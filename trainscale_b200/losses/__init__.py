@@ -102,7 +102,6 @@ class FusedCrossEntropyLoss(_ExplicitBackward, CrossEntropyLoss):
 
 
 FusedCrossEntropyFunction = ce_ops.FusedCrossEntropyFunction
-Fast_CrossEntropyLoss = FusedCrossEntropyLoss      # name used by data_pipeline/trainer/kernels/triton_kernels.py:330
 
 
 class ChunkedCrossEntropyLoss(nn.Module):
