@@ -601,3 +601,100 @@ def test_remaining_reference_forms_of_shared_classes():
     compressor = GradientCompressor(use_fp16=True)
     payload, meta = compressor.compress(t, tensor_id=3)
     assert compressor.decompress(tensor=payload[0], metadata=meta).dtype is torch.float32
+
+
+def test_optimizer_scheduler_and_callback_options_of_the_reference():
+    from trainscale_b200 import callbacks as C
+    from trainscale_b200 import optim as O
+    from trainscale_b200 import schedulers as S
+    lin = nn.Linear(4, 4)
+    opt = O.AdamW(lin.parameters(), lr=1e-2, use_triton=False, max_grad_norm=1.0, grad_accumulation_steps=1)
+    lin(torch.randn(2, 4)).sum().backward()
+    opt.step()
+    O.AdamW(lin.parameters(), use_triton=True)                                  # implementation switch: same maths, no effect
+    O.LAMB(lin.parameters(), trust_ratio_clip=5.0)
+    O.SophiaG(lin.parameters(), hessian_update_interval=5)
+    sched = S.BaseScheduler(opt, 100, warmup_ratio=0.1, warmup_start_lr=0.0, min_lr=1e-4, last_epoch=-1)
+    assert sched.warmup_steps == 10
+    rex = S.REXScheduler(opt, 100, gamma=0.9)
+    rex.step(step=50)
+    S.InverseSquareRootScheduler(opt, 100, warmup_steps=10, warmup_init_lr=1e-7)
+    stop = C.EarlyStoppingCallback(patience=1, monitor="eval_loss", min_delta=0.1, mode="min", restore_best=False)
+    assert stop.metric == "eval_loss" and stop.threshold == 0.1
+    handler = C.CallbackHandler()
+    seen = []
+
+    class Probe(C.Callback):
+        def on_step_end(self, ctx):
+            seen.append("step")
+
+    probe = Probe()
+    handler.add_callback(probe)
+    handler.trigger("on_step_end", C.CallbackContext())
+    handler.remove_callback(probe)
+    handler.trigger("on_step_end", C.CallbackContext())
+    assert seen == ["step"]
+    assert C.ProgressCallback(refresh_rate=5).refresh_rate == 5
+
+
+def test_checkpoint_manager_and_trainer_take_the_reference_forms(tmp_path):
+    from trainscale_b200.hub import CheckpointManager
+    from trainscale_b200.trainer.base import Trainer
+    from trainscale_b200.config.training_args import TrainingArguments
+    lin = nn.Linear(4, 2)
+    manager = CheckpointManager(save_dir=str(tmp_path / "ckpts"), hub_manager=None, max_checkpoints=2)
+    results = [manager.save(lin, step=s, loss=1.0 / (s + 1)) for s in (1, 2, 3)]
+    assert all(r.is_ok() for r in results)
+    latest = manager.get_latest_checkpoint()
+    assert latest is not None and "3" in str(latest)
+    assert len([p for p in (tmp_path / "ckpts").iterdir() if p.is_dir()]) <= 2    # the bound is kept
+
+    class Net(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.lin = nn.Linear(4, 2)
+
+        def forward(self, x):
+            return self.lin(x)
+
+    net = Net()
+    data = [{"x": torch.randn(4), "labels": torch.randn(2)} for _ in range(8)]
+
+    def collate(rows):
+        return {k: torch.stack([r[k] for r in rows]) for k in ("x", "labels")}
+
+    opt = torch.optim.SGD(net.parameters(), lr=0.1)
+    args = TrainingArguments(output_dir=str(tmp_path / "run"), per_device_train_batch_size=4, num_train_epochs=1,
+                             max_steps=2, logging_steps=1, save_strategy="no")
+    trainer = Trainer(net, args, train_dataset=data, eval_dataset=data, data_collator=collate, optimizers=(opt, None),
+                      loss_fn=nn.functional.mse_loss)
+    assert next(iter(trainer.get_train_dataloader()))["x"].shape == (4, 4)
+    before = net.lin.weight.detach().clone()
+    trainer.train()
+    assert not torch.equal(before, net.lin.weight.detach())
+
+
+def test_tensor_parallel_layers_build_without_a_context_and_managers_take_configs():
+    from trainscale_b200.parallel.dist_utils import DistributedManager, GradientSynchronizer
+    from trainscale_b200.parallel.tp import (ColumnParallelLinear, ParallelMLP, ProcessGroupManager, RowParallelLinear,
+                                             TensorParallelConfig, VocabParallelEmbedding)
+    col = ColumnParallelLinear(16, 8, bias=True, init_method=lambda w: nn.init.constant_(w, 0.5))
+    assert float(col.weight.detach().mean()) == 0.5                             # one rank: the whole layer, initialised as asked
+    x = torch.randn(2, 16)
+    row = RowParallelLinear(8, 16, init_method=nn.init.zeros_)
+    assert row(col(x)).abs().sum() == 0
+    with pytest.raises(NotImplementedError):
+        ColumnParallelLinear(16, 8, skip_bias_add=True)
+    emb = VocabParallelEmbedding(32, 8, padding_idx=0)
+    assert emb(torch.tensor([[0, 3]]))[0, 0].abs().sum() == 0                   # the padding row is zero
+    mlp = ParallelMLP(16, 32, use_gated=True, dropout_prob=0.0)
+    assert mlp(hidden_states=x).shape == x.shape
+    groups = ProcessGroupManager.get()
+    groups.initialize(TensorParallelConfig())
+    buf = groups.acquire_buffer(torch.float32, 16)
+    assert buf.shape == (16,)
+    groups.release_buffer(buffer=buf)
+    manager = DistributedManager(config=None)
+    assert manager.world_size == 1
+    sync = GradientSynchronizer(model=nn.Linear(2, 2), bucket_size_mb=1.0, async_sync=False)
+    sync.sync_gradients()

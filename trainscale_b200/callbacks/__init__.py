@@ -88,6 +88,9 @@ class CallbackHandler:
 
     @reference_kwargs(callback_type="cb_type")
     def remove(self, cb_type: type) -> None:
+        if not isinstance(cb_type, type):                 # an instance: remove exactly that callback
+            self.callbacks = [c for c in self.callbacks if c is not cb_type]
+            return
         self.callbacks = [c for c in self.callbacks if not isinstance(c, cb_type)]
 
     def fire(self, hook: str, ctx: CallbackContext) -> CallbackContext:
