@@ -223,3 +223,35 @@ def test_reference_example_yamls_load_through_both_loaders(path):
     r = load_config(path)
     assert r.is_ok(), r
     assert r.unwrap().tokenizer.name_or_path
+
+
+def test_the_reference_example_configurations_load():
+    """Every example YAML shipped with the reference loads with the loader of its own type: trainer configurations
+    (`config_type` / `training_mode` at the top) as `SOTAConfig`, data-pipeline configurations (`type`, `version`,
+    `dataset`) through `load_config`, and the flat training-arguments file through `load_training_config`."""
+    import glob
+    from pathlib import Path
+
+    import yaml as _yaml
+    from trainscale_b200.config.data_schema import load_config
+    from trainscale_b200.config.sota_config import SOTAConfig
+    from trainscale_b200.config.training_args import load_training_config
+
+    root = Path("/root/reference/data_pipeline/examples")
+    files = sorted(glob.glob(str(root / "**" / "*.yaml"), recursive=True))
+    if not files:
+        pytest.skip("the reference's examples are not on this machine")
+    seen = {"sota": 0, "data": 0, "args": 0}
+    for f in files:
+        top = _yaml.safe_load(open(f))
+        if "training_mode" in top or "config_type" in top:
+            cfg = SOTAConfig.from_yaml(f)
+            assert cfg.model.name_or_path or cfg.model.architecture is not None, f
+            seen["sota"] += 1
+        if "dataset" in top and "type" in top:
+            assert load_config(f).is_ok(), f
+            seen["data"] += 1
+        if "dataset" not in top and "training" in top and "training_mode" not in top:
+            assert load_training_config(f).output_dir, f
+            seen["args"] += 1
+    assert seen["sota"] >= 5 and seen["data"] >= 8 and seen["args"] >= 1, seen
