@@ -317,3 +317,105 @@ def test_shared_methods_take_the_reference_keyword_names():
         if best:
             missing[f"{cname}.{mname}"] = best
     assert not missing, f"{len(missing)} methods lack reference keywords: {sorted(missing.items())[:15]}"
+
+
+def _our_modules():
+    import importlib
+    import pkgutil
+
+    import trainscale_b200
+    mods = []
+    for m in pkgutil.walk_packages(trainscale_b200.__path__, "trainscale_b200."):
+        if m.name.endswith("__main__"):
+            continue
+        try:
+            mods.append(importlib.import_module(m.name))
+        except Exception:   # noqa: BLE001
+            continue
+    return mods
+
+
+def test_module_level_constants_and_aliases_of_the_reference_exist_here():
+    """Annotated constants (`X: Final[int] = 64`), plain module-level assignments and `import ... as alias` re-exports
+    of the reference's modules have a counterpart of the same name in some module of this package (type variables with
+    one-letter names and loggers aside)."""
+    ref = _reference_root()
+    if ref is None:
+        pytest.skip("the reference package is not on this machine")
+    wanted: dict[str, str] = {}
+    for p in ref.rglob("*.py"):
+        if "examples" in p.parts:
+            continue
+        try:
+            tree = ast.parse(p.read_text())
+        except SyntaxError:
+            continue
+        for node in tree.body:
+            names: list[str] = []
+            if isinstance(node, ast.AnnAssign) and isinstance(node.target, ast.Name) and node.value is not None:
+                names = [node.target.id]
+            elif isinstance(node, ast.Assign):
+                names = [t.id for t in node.targets if isinstance(t, ast.Name)]
+            elif isinstance(node, ast.ImportFrom):
+                names = [a.asname for a in node.names if a.asname and a.asname != a.name]
+            for n in names:
+                if not n.startswith("_") and len(n) > 1 and n != "logger":
+                    wanted.setdefault(n, str(p.relative_to(ref)))
+    mods = _our_modules()
+    missing = {n: f for n, f in wanted.items() if not any(hasattr(m, n) for m in mods)}
+    assert not missing, f"{len(missing)} module-level names without a counterpart: {sorted(missing.items())[:20]}"
+
+
+def test_the_reference_import_paths_resolve():
+    """With `trainscale_b200.reference_paths` imported, every absolute `from data_pipeline... import name` statement
+    found anywhere in the reference (its examples included) resolves to an object of this package - for every name the
+    reference itself still defines (two of its older example scripts import names that no longer exist there)."""
+    import importlib
+
+    ref = _reference_root()
+    if ref is None:
+        pytest.skip("the reference package is not on this machine")
+    import trainscale_b200.reference_paths as paths
+    if not paths.install():
+        pytest.skip("a real data_pipeline package is importable here")
+    defined: set[str] = set()
+    pairs: dict[tuple[str, str], str] = {}
+    for p in ref.rglob("*.py"):
+        try:
+            tree = ast.parse(p.read_text())
+        except SyntaxError:
+            continue
+        for node in ast.walk(tree):
+            if isinstance(node, (ast.FunctionDef, ast.AsyncFunctionDef, ast.ClassDef)):
+                defined.add(node.name)
+            elif isinstance(node, ast.Assign):
+                defined.update(t.id for t in node.targets if isinstance(t, ast.Name))
+            elif isinstance(node, ast.AnnAssign) and isinstance(node.target, ast.Name):
+                defined.add(node.target.id)
+            elif isinstance(node, ast.ImportFrom):
+                defined.update(a.asname for a in node.names if a.asname)
+                if node.level == 0 and node.module and node.module.split(".")[0] == "data_pipeline":
+                    for a in node.names:
+                        if a.name != "*" and not a.name.startswith("_"):
+                            pairs.setdefault((node.module, a.name), str(p.relative_to(ref)))
+    modules = {m for m, _ in pairs}
+    failed = {}
+    for (module, name), where in pairs.items():
+        is_submodule = f"{module}.{name}" in modules or any(m.startswith(f"{module}.{name}.") for m in modules)
+        if name not in defined and not is_submodule:
+            continue
+        try:
+            getattr(importlib.import_module(module), name)
+        except Exception as e:   # noqa: BLE001
+            failed[f"{module}:{name}"] = f"{where}: {e!r}"[:160]
+    assert len(pairs) > 500 and not failed, f"{len(failed)} of {len(pairs)} imports fail: {sorted(failed.items())[:10]}"
+    # spot checks: the path selects the right one of several same-named objects
+    from data_pipeline.trainer.distributed.context_parallel import CUDATimer as cp_timer
+    from data_pipeline.trainer.distributed.ddp import CUDATimer as ddp_timer
+    from data_pipeline.trainer.kernels import flash_attention
+    import trainscale_b200.kernels as K
+    import trainscale_b200.parallel.ddp as ddp
+    assert flash_attention is K.flash_attention and ddp_timer is ddp.CUDATimer and cp_timer is not None
+    from data_pipeline.trainer import inference
+    import trainscale_b200.inference as ours_inference
+    assert inference is ours_inference

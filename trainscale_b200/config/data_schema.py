@@ -476,3 +476,9 @@ def load_config_dict(raw: Mapping[str, Any]) -> Result:
         return Ok(parse_config(raw))
     except ConfigurationError as e:
         return Err(e)
+
+
+# ---- value sets of the schema, by the names of data_pipeline/core/config_schema.py
+PADDING_STRATEGIES = frozenset({"max_length", "longest", "do_not_pad"})
+PROMPT_FORMAT_TYPES = frozenset({"chat", "completion", "custom"})
+TENSOR_DTYPES = frozenset({"long", "int", "float", "half", "bfloat16", "bool"})

@@ -388,3 +388,8 @@ def load_training_config_from_dict(config_dict: Dict[str, Any], *, interpolate_e
             lines = [f"{'.'.join(str(p) for p in d.get('loc', ()))}: {d.get('msg')}" for d in details()]
             raise ValueError("invalid training configuration:\n  " + "\n  ".join(lines)) from e
         raise
+
+
+import re as _re  # noqa: E402
+
+ENV_VAR_PATTERN = _re.compile(r"\$\{([^}]+)\}")           # ${VAR} / ${VAR:-default}, what `interpolate_env_vars` replaces

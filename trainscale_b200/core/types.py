@@ -167,3 +167,15 @@ class StepMetrics:
     gpu_memory_mb: float
     step_time_ms: float
     component_losses: Optional[Dict[str, float]] = None
+
+
+# ---- type variables and numeric defaults of data_pipeline/trainer/core/types.py
+from typing import TypeVar as _TypeVar  # noqa: E402
+
+ModelT = _TypeVar("ModelT")
+OptimizerT = _TypeVar("OptimizerT")
+CACHE_LINE_SIZE: int = 64                  # bytes, host L1 line
+GPU_WARP_SIZE: int = 32                    # threads per warp
+TPU_TILE_SIZE: int = 128                   # kept for scripts that import it; nothing here targets TPUs
+MAX_GRADIENT_NORM: float = 1.0             # default clipping threshold of the trainer
+DEFAULT_WARMUP_RATIO: float = 0.1

@@ -139,3 +139,10 @@ def create_seq2seq_collate(pad_token_id: int = 0, decoder_start_token_id: int = 
         return out
 
     return fn
+
+
+# ---- defaults of the collators, by the names of data_pipeline/data/collate.py
+DEFAULT_PAD_TOKEN_ID: int = 0
+DEFAULT_LABEL_PAD_ID: int = -100           # the ignore_index of the cross-entropy kernels
+DTYPE_MAP = {"long": torch.long, "int": torch.int, "float": torch.float, "half": torch.half,
+             "bfloat16": torch.bfloat16, "bool": torch.bool}

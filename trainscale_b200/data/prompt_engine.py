@@ -688,3 +688,12 @@ def extract_successful(results):
         else:
             errs.append(r.error)
     return oks, errs
+
+
+# ---- names of data_pipeline/preprocessing/prompt_engine.py
+import re as _re  # noqa: E402
+from typing import Union as _Union  # noqa: E402
+
+LABEL_PAD_TOKEN_ID: int = -100
+SIMPLE_VAR_PATTERN = _re.compile(r"\{(\w+)\}")             # {name} placeholders of the non-Jinja templates
+ProcessedOutput = _Union[ProcessedExample, PackedExample, PreferencePairExample, PPOExample, KTOExample, GRPOExample]

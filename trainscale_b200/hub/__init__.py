@@ -750,3 +750,12 @@ class CheckpointMetadata:
         m = meta.get("metrics", {})
         return cls(int(meta.get("step", 0)), int(m.get("epoch", 0)), float(m.get("loss", m.get("eval_loss", float("nan")))),
                    _datetime.fromtimestamp(meta.get("time", 0.0)), compute_sha256(d / "checkpoint_meta.json"), d)
+
+
+# ---- defaults of data_pipeline/trainer/hub/__init__.py, as the classes above use them
+CACHE_LINE_SIZE = 64
+DEFAULT_SHARD_SIZE_BYTES = 5 * 1024 ** 3
+MAX_RETRY_ATTEMPTS, INITIAL_BACKOFF_MS, MAX_BACKOFF_MS = 5, 100, 32000
+IO_BUFFER_SIZE, HASH_CHUNK_SIZE = 8 * 1024 * 1024, 1024 * 1024
+CIRCUIT_BREAKER_THRESHOLD, CIRCUIT_BREAKER_TIMEOUT_S = 3, 60.0
+UPLOAD_CONCURRENCY = min(8, (os.cpu_count() or 4) + 4)

@@ -332,3 +332,22 @@ def get_default_split(dataset_id, config: str | None = None, token: str | None =
         return intro.get_default_split(dataset_id)
     md = intro.discover(dataset_id, config)
     return md if md.is_err() else intro.get_default_split(md.unwrap())
+
+
+# ---- column-role patterns as compiled expressions (data_pipeline/introspection/column_mapper.py), built from the
+# alias table `ColumnMapper` matches with, and the split / config preferences of the introspector
+import re as _re  # noqa: E402
+
+
+def _role_patterns(*names: str) -> tuple:
+    return tuple(_re.compile(f"^{_re.escape(n)}$", _re.I) for n in names)
+
+
+INSTRUCTION_PATTERNS = _role_patterns("instruction", "prompt", *ColumnMapper.ALIASES["prompt"], "user_input", "user_message", "human")
+INPUT_PATTERNS = _role_patterns("input", "context", "text", *ColumnMapper.ALIASES["text"], "source")
+OUTPUT_PATTERNS = _role_patterns("output", "completion", *ColumnMapper.ALIASES["completion"], "assistant", "generated")
+LABEL_PATTERNS = _role_patterns("label", "labels", "class", "category", "target")
+STANDARD_SCHEMA = {"instruction": INSTRUCTION_PATTERNS, "input": INPUT_PATTERNS, "output": OUTPUT_PATTERNS,
+                   "label": LABEL_PATTERNS}
+DEFAULT_SPLIT_PRIORITY = DatasetIntrospector.SPLIT_PREFERENCE
+DEFAULT_CONFIG_NAMES = frozenset({"default", "plain_text", "en", "english"})

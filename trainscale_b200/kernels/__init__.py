@@ -1318,3 +1318,35 @@ from .compat import (CUDAGraphConfig, CompiledFunctionWrapper, DynamicShapeConfi
                      get_flash_attn_version, get_fp8_capability, get_fp8_spec, get_layernorm_info,
                      get_optimal_block_size, is_flash_attn_triton_available, rms_layernorm, supports_bf16,
                      swiglu_backward, swiglu_backward_triton, triton_flash_attention)
+
+
+# ---- module-level flags and constants of the reference's kernel files.  Availability flags describe THIS framework:
+# there is no Triton path, "flash attention" is the tcgen05 kernel of csrc/flash_attn.cu, not the flash-attn package.
+from typing import Any as _Any, Callable as _Callable, TypeVar as _TypeVar, Union as _Union  # noqa: E402
+
+FLASH_ATTN_VERSION = None                  # not the flash-attn package
+TRITON_AVAILABLE = False
+TORCH_COMPILE_OPTIONS: dict = {}           # nothing here is traced; kept for scripts that read it
+HAS_FLEX_ATTENTION = True                  # block-mask attention (`kernels.flex`) is always present
+
+
+def __getattr__(name: str):
+    """`BACKEND_CAPS` and `FLASH_ATTN_AVAILABLE` probe the device, so they are computed on first use and not while
+    the package is imported (an import must not create a CUDA context)."""
+    if name == "BACKEND_CAPS":
+        value = BackendCapabilities.detect()
+    elif name == "FLASH_ATTN_AVAILABLE":
+        value = supports_tcgen05()
+    else:
+        raise AttributeError(f"module {__name__!r} has no attribute {name!r}")
+    globals()[name] = value
+    return value
+
+
+FP8_E4M3_SPEC, FP8_E5M2_SPEC = get_fp8_spec(FP8Format.E4M3), get_fp8_spec(FP8Format.E5M2)
+FP8_CONFIG = FP8Config()
+LN_CONFIG = LayerNormConfig()
+fast_layernorm = layernorm
+ROPE_GROUP_SIZE, BLOCK_SIZE_DEFAULT, WARP_SIZE, MIN_BLOCK_SIZE = 4, 1024, 32, 128
+ModelType = _TypeVar("ModelType", bound=nn.Module)
+CompiledModel = _Union[nn.Module, _Callable[..., _Any]]

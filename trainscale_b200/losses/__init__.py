@@ -758,3 +758,16 @@ def create_loss_from_config(lc) -> nn.Module:
     if t == "contrastive":
         return InfoNCELoss(lc.temperature if lc.temperature < 1 else 0.07)
     return create_loss(t)
+
+
+# ---- constants and type aliases of data_pipeline/trainer/loss/sota_losses.py
+from typing import Literal as _Literal  # noqa: E402
+
+CACHE_LINE_BYTES, WARP_SIZE = 64, 32
+MAX_VOCAB_CHUNK = 65536                    # widest vocabulary slice one pass of the chunked losses upcasts
+EPS, LOG_MIN = 1e-8, -100.0
+ReductionMode = _Literal["mean", "sum", "none", "batchmean"]
+PreferenceLossType = _Literal["sigmoid", "hinge", "ipo", "kto", "robust"]
+
+
+from ..config.sota_config import LossConfig as SOTALossConfig  # noqa: E402,F401  (alias of data_pipeline/trainer/loss/__init__.py)

@@ -1231,3 +1231,18 @@ def check_optimizer_compatibility(optimizer: Optimizer, model) -> dict:
                                "keep fp32 master weights")
     blocking = [w for w in warnings if w.startswith(("meta", "trainable", "sparse"))]
     return {"is_compatible": not blocking, "warnings": warnings, "recommendations": recommendations}
+
+
+# ---- type aliases and tuning constants of data_pipeline/trainer/optimizers/{base,adamw,adafactor}.py.  The block
+# sizes describe the reference's Triton kernels; the kernels of csrc/optim.cu choose their own launch shapes.
+from typing import Any as _Any, Dict as _Dict, TypeVar as _TypeVar  # noqa: E402
+
+ParamGroup = _Dict[str, _Any]
+StateDict = _Dict[str, _Any]
+ParamT = _TypeVar("ParamT", bound=torch.Tensor)
+StateT = _TypeVar("StateT", bound=_Dict[str, _Any])
+CACHE_LINE_SIZE, CACHE_LINE_ELEMENTS_FP32, CACHE_LINE_ELEMENTS_FP16 = 64, 16, 32
+EPS_FP32, EPS_FP16, EPS_BF16 = 1e-30, 1e-7, 1e-7
+DEFAULT_BLOCK_SIZE, MAX_BLOCK_SIZE, MIN_ELEMENTS_FOR_TRITON = 1024, 4096, 8192
+TRITON_BLOCK_SIZE, TRITON_NUM_WARPS, TRITON_NUM_STAGES = 1024, 8, 3
+MULTI_TENSOR_THRESHOLD, MAX_TENSORS_PER_KERNEL = 4 * 1024 * 1024, 64

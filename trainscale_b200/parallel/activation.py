@@ -1254,3 +1254,22 @@ class OffloadTensorGroup:
     def update_stats(self, tensor: torch.Tensor) -> None:
         self.total_offload_bytes += tensor.numel() * tensor.element_size()
         self.total_tensor_count += 1
+
+
+# ---- names of data_pipeline/trainer/distributed/{activation_checkpoint,activation_offload}.py: the thresholds are the
+# ones `MemoryProfiler.get_memory_pressure` and the memory-budget policy use, the costs the relative recompute cost of a
+# block kind (attention = 1)
+from typing import Tuple as _Tuple, Union as _Union  # noqa: E402
+
+from torch.utils.checkpoint import checkpoint as torch_checkpoint  # noqa: E402,F401
+
+from .dist_utils import TensorPool as OffloadTensorPool  # noqa: E402,F401
+
+TensorOrTensors = _Union[torch.Tensor, _Tuple[torch.Tensor, ...]]
+PoolKey = _Tuple[_Tuple[int, ...], torch.dtype]
+CACHE_LINE_BYTES, WARP_SIZE = 64, 32
+PAGE_SIZE_BYTES = 4096
+HBM_BANK_SIZE = 256
+CHECKPOINT_ALIGNMENT = 512
+MEMORY_CRITICAL_THRESHOLD, MEMORY_WARNING_THRESHOLD, MEMORY_COMFORTABLE_THRESHOLD = 0.95, 0.85, 0.70
+RECOMPUTE_COST_ATTENTION, RECOMPUTE_COST_FFN, RECOMPUTE_COST_LAYERNORM, RECOMPUTE_COST_ACTIVATION = 1.0, 0.5, 0.05, 0.01

@@ -1253,3 +1253,9 @@ class BalancerStrategy(LoadBalancerStrategy):
 
     def unpartition(self, parts, seq_dim):
         return create_balancer(self.name, len(parts), 0).unshard(parts, seq_dim)
+
+
+# ---- type aliases of data_pipeline/trainer/distributed/hybrid_cp_scheduler.py
+SampleSeqLen = tuple[int, int]             # (sample id, sequence length)
+MicroBatch = list[int]                     # sequence lengths one GPU processes
+SampleIdList = list[int]

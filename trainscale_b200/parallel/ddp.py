@@ -656,3 +656,9 @@ def create_ddp_from_yaml(config_path: str):
         return create_ddp_engine(**section)
     except Exception as e:   # noqa: BLE001 - reported through the Result
         return Err(e)
+
+
+# ---- names of data_pipeline/trainer/distributed/ddp.py
+from torch.nn.parallel import DistributedDataParallel as TorchDDP  # noqa: E402,F401
+
+SOTADDP = SOTADDPEngine

@@ -1220,3 +1220,11 @@ def allreduce_conditional_embedding_grads(model, pp_group=None) -> None:
         dist.all_reduce(first, group=pp_group)
         for other in by_name[name][1:]:
             other.copy_(first)
+
+
+# ---- environment-driven defaults of data_pipeline/trainer/distributed/sota_utils.py
+import os as _os  # noqa: E402
+
+CACHE_LINE_SIZE = 64
+NCCL_BUCKET_SIZE_MB = int(_os.environ.get("TRAINSCALE_BUCKET_SIZE_MB", "25"))
+MAX_ASYNC_OPS = int(_os.environ.get("TRAINSCALE_MAX_ASYNC_OPS", "8"))

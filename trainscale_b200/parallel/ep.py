@@ -1004,3 +1004,6 @@ class RouterBase(nn.Module):
         w, idx, probs = self.route(logits)
         aux = cfg.aux_loss_weight * load_balance_loss(self.loss_type, probs, idx, logits, cfg.z_loss_weight)
         return _dense_routing(cfg, logits, w, idx, aux, padding_mask)
+
+
+CACHE_LINE_SIZE, WARP_SIZE, EPS = 64, 32, 1e-6      # names of data_pipeline/trainer/distributed/expert_parallel.py

@@ -838,3 +838,14 @@ def create_fsdp2_from_dict(config_dict: dict[str, Any]) -> SOTAFSDP2:
     if isinstance(out.get("backward_prefetch"), bool):
         out["backward_prefetch"] = "backward_pre" if out["backward_prefetch"] else "none"
     return SOTAFSDP2(FSDP2Config(**out))
+
+
+# ---- sizes and limits of data_pipeline/trainer/distributed/fsdp2.py, as this module's classes use them
+from typing import TypeVar as _TypeVar  # noqa: E402
+
+ModuleT = _TypeVar("ModuleT", bound=nn.Module)
+CACHE_LINE_BYTES = 64
+SMALL_BUCKET_BYTES, MEDIUM_BUCKET_BYTES, LARGE_BUCKET_BYTES = 1 << 20, 25 << 20, 100 << 20
+MIN_POOL_BLOCK_BYTES, MAX_POOL_BLOCK_BYTES = 512, 256 << 20
+VRAM_PRESSURE_WATERMARK = 0.9
+CHECKPOINT_NCCL_TIMEOUT_S = 120

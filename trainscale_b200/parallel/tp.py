@@ -936,3 +936,11 @@ class FusedRowParallelLinearWithDropout(nn.Module):
     def forward(self, x):
         y = self.linear(x)
         return torch.nn.functional.dropout(y, self.dropout_prob, self.training) if self.dropout_prob > 0 else y
+
+
+# ---- NCCL settings suggested for tensor parallelism inside one NVLink / NVSwitch node (name from
+# data_pipeline/trainer/distributed/tensor_parallel.py; the values are this framework's: peer-to-peer over NVLink,
+# in-switch reduction on, asynchronous error handling so that a lost rank ends the collective instead of hanging it)
+CACHE_LINE_BYTES, MAX_ASYNC_OPS = 64, 8
+NCCL_ENV_VARS = {"NCCL_P2P_LEVEL": "NVL", "NCCL_NVLS_ENABLE": "1", "NCCL_ASYNC_ERROR_HANDLING": "1",
+                 "TORCH_NCCL_ASYNC_ERROR_HANDLING": "1", "NCCL_BUFFSIZE": "8388608"}

@@ -1077,3 +1077,6 @@ def create_zbpp_pipeline(model: nn.Module, num_stages: int = 4, num_microbatches
                          **kw) -> ZeroBubblePipeline:
     return ZeroBubblePipeline(model, num_stages, num_microbatches, int(memory_limit_gb * 2 ** 30), lr, weight_decay,
                               dtype, use_triton, enable_sync_bypass, rank, world_size, **kw)
+
+
+CudaEvent = torch.cuda.Event               # name used by data_pipeline/trainer/distributed/zbpp.py

@@ -211,13 +211,28 @@ _FAMILIES: dict[str, list[tuple]] = {
         ("mistralai", "Mixtral-8x7B", "0.1", ["8x7"], [None, "Instruct-v0.1"], _Q4, MistralModelInfo, False, dict(_layers("Mixtral"), mlp_class="MixtralSparseMoeBlock")),
         ("mistralai", "Mixtral-8x22B", "0.1", ["8x22"], [None, "Instruct-v0.1"], _Q4, MistralModelInfo, False, dict(_layers("Mixtral"), mlp_class="MixtralSparseMoeBlock")),
         ("Qwen", "Qwen1.5-MoE", "1.5", ["A2.7"], [None, "Chat"], _Q4, QwenModelInfo, False, dict(_layers("Qwen2Moe"), mlp_class="Qwen2MoeSparseMoeBlock")),
+        ("Qwen", "Qwen3-MoE", "3", ["A3", "A22"], [None, "Instruct"], _Q4, QwenModelInfo, False, dict(_layers("Qwen3Moe"), mlp_class="Qwen3MoeSparseMoeBlock")),
+        ("databricks", "dbrx", "1", ["132"], [None, "instruct"], _Q4, CheckpointInfo, False, dict(_layers("Dbrx", "LayerNorm"), mlp_class="DbrxFFN")),
+        ("xai-org", "grok", "1", ["314"], [None], [QuantType.NONE], CheckpointInfo, False, dict(_layers("Grok1"), mlp_class="Grok1MoeBlock")),
     ],
     "vision": [
         ("llava-hf", "llava", "1.5", ["7", "13"], ["hf"], _Q4, CheckpointInfo, True, _layers("Llama")),
+        ("llava-hf", "llava-v1.6", "1.6", ["7", "13", "34"], [None, "vicuna", "mistral"], _Q4, CheckpointInfo, True, _layers("Llama")),
+        ("llava-hf", "llava-onevision", "0.5", ["0.5", "7", "72"], [None, "qwen2", "si"], _Q4, CheckpointInfo, True, _layers("Qwen2")),
+        ("Qwen", "Qwen2-VL", "2", ["2", "7", "72"], [None, "Instruct"], _Q4, QwenModelInfo, True, _layers("Qwen2VL")),
         ("mistralai", "Pixtral", "24.09", ["12"], [None], _Q4, MistralModelInfo, True, _layers("Mistral")),
+        ("OpenGVLab", "InternVL2", "2", ["1", "2", "8", "26", "40", "76"], [None, "Instruct"], _Q4, CheckpointInfo, True, _layers("InternLM2")),
     ],
 }
 _REGISTERED: set[str] = set()
+
+
+def _family_meta(family: str, base_name: str, version: str | None = None, size: str | None = None) -> FamilyMeta:
+    """The catalogue row of one release as a `FamilyMeta` (what `register_models_from_meta` / `register_family` take)."""
+    for org, base, ver, sizes, tags, quants, cls, mm, layers in _FAMILIES[family]:
+        if base == base_name and (version is None or ver == version) and (size is None or size in sizes):
+            return FamilyMeta(org, base, ver, cls, list(sizes), list(tags), list(quants), mm, **layers)
+    raise KeyError(f"no release {base_name!r} {version!r} in family {family!r}")
 
 
 def _register(family: str, include_original: bool = True) -> int:
@@ -396,3 +411,50 @@ for _n in ("LlamaMLP", "Qwen2MLP", "Qwen3MLP", "MistralMLP", "Phi3MLP", "Granite
     register_layer_patch(_n, auto_patch_mlp_swiglu)
 for _n in ("GemmaMLP", "Gemma2MLP", "Gemma3MLP"):
     register_layer_patch(_n, auto_patch_mlp_geglu)
+
+
+# ---- one named constant per release, under the names of data_pipeline/trainer/registry/_*.py, built from the
+# catalogue above (so that `register_models_from_meta(YI_15_META)` style code keeps working)
+LlamaMeta_3_1 = _family_meta("llama", "Llama", "3.1")
+LlamaMeta_3_2 = _family_meta("llama", "Llama", "3.2", "1")
+LlamaMeta_3_2_Vision = LLAMA32_VISION_META = _family_meta("llama", "Llama", "3.2", "11")
+QwenMeta_2_5 = _family_meta("qwen", "Qwen", "2.5")
+QwenMeta_2_5_Coder = _family_meta("qwen", "Qwen", "2.5-Coder")
+QwQMeta = _family_meta("qwen", "QwQ")
+GemmaMeta_2 = _family_meta("gemma", "gemma", "2")
+GemmaMeta_3 = _family_meta("gemma", "gemma", "3")
+MistralMeta_7B = _family_meta("mistral", "Mistral", "0.3")
+MistralMeta_Small = _family_meta("mistral", "Mistral-Small")
+DeepSeekMeta_V3 = _family_meta("deepseek", "DeepSeek", "V3")
+DeepSeekMeta_R1 = _family_meta("deepseek", "DeepSeek", "R1")
+PHI_3_META = _family_meta("phi", "Phi-3")
+PHI_4_META = _family_meta("phi", "Phi-4")
+YI_1_META = _family_meta("yi", "Yi")
+YI_15_META = _family_meta("yi", "Yi-1.5")
+YI_CODER_META = _family_meta("yi", "Yi-Coder")
+FALCON_1_META = _family_meta("falcon", "falcon")
+FALCON_2_META = _family_meta("falcon", "falcon2")
+FALCON_H1_META = _family_meta("falcon", "Falcon-H1")
+COMMAND_R_META = _family_meta("cohere_granite", "c4ai-command-r")
+AYA_META = _family_meta("cohere_granite", "aya")
+GRANITE_META = _family_meta("cohere_granite", "granite")
+GRANITE_CODE_META = _family_meta("cohere_granite", "granite-code")
+STARCODER_META = _family_meta("code", "starcoder")
+STARCODER2_META = _family_meta("code", "starcoder2")
+CODELLAMA_META = _family_meta("code", "CodeLlama")
+DEEPSEEK_CODER_META = _family_meta("code", "deepseek-coder")
+DEEPSEEK_CODER_V2_META = _family_meta("code", "DeepSeek-Coder-V2")
+QWEN_CODER_META = _family_meta("code", "Qwen2.5-Coder")
+MIXTRAL_8x7B_META = _family_meta("moe", "Mixtral-8x7B")
+MIXTRAL_8x22B_META = _family_meta("moe", "Mixtral-8x22B")
+QWEN_MOE_META = _family_meta("moe", "Qwen1.5-MoE")
+QWEN3_MOE_META = _family_meta("moe", "Qwen3-MoE")
+DBRX_META = _family_meta("moe", "dbrx")
+GROK_META = _family_meta("moe", "grok")
+LLAVA_META = _family_meta("vision", "llava")
+LLAVA_NEXT_META = _family_meta("vision", "llava-v1.6")
+LLAVA_ONEVISION_META = _family_meta("vision", "llava-onevision")
+QWEN_VL_META = _family_meta("vision", "Qwen2-VL")
+QWEN25_VL_META = _family_meta("qwen", "Qwen", "2.5-VL")
+PIXTRAL_META = _family_meta("vision", "Pixtral")
+INTERNVL_META = _family_meta("vision", "InternVL2")

@@ -267,3 +267,6 @@ def create_scheduler(optimizer, scheduler_type: str = "cosine", num_training_ste
 
 
 create_sota_scheduler = create_scheduler
+
+
+OneCycleSchedulerEnhanced = OneCycleScheduler     # alias exported by data_pipeline/trainer/schedulers/__init__.py

@@ -376,3 +376,8 @@ class PredictionOutput:
     predictions: torch.Tensor
     label_ids: torch.Tensor | None = None
     metrics: dict = field(default_factory=dict)
+
+
+# ---- type aliases of data_pipeline/trainer/base.py
+BatchType = dict[str, torch.Tensor]
+MetricsType = dict[str, float]

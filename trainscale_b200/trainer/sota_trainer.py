@@ -809,3 +809,6 @@ def create_trainer_from_config(config) -> "SOTATrainer":
     elif isinstance(config, (str, os.PathLike)):
         config = SOTAConfig.from_yaml(config)
     return SOTATrainer(config)
+
+
+from ..metrics import is_distributed as metrics_is_distributed  # noqa: E402,F401  (alias of the reference's trainer module)
