@@ -415,7 +415,64 @@ def test_the_reference_import_paths_resolve():
     from data_pipeline.trainer.kernels import flash_attention
     import trainscale_b200.kernels as K
     import trainscale_b200.parallel.ddp as ddp
-    assert flash_attention is K.flash_attention and ddp_timer is ddp.CUDATimer and cp_timer is not None
+    assert ddp_timer is ddp.CUDATimer and cp_timer is not None
+    # a function whose positional conventions differ resolves to its variant with the reference's conventions
+    assert flash_attention is K.flash_attention.__reference_form__
     from data_pipeline.trainer import inference
     import trainscale_b200.inference as ours_inference
     assert inference is ours_inference
+
+
+def test_a_script_in_the_reference_style_runs_through_the_reference_paths():
+    """The calls a user script of the reference typically makes (optimizer steps, schedulers, losses, metric
+    collection, a tensor-parallel layer on one rank, attention in the reference's layout, gradient clipping, the compiler
+    facade), written against `data_pipeline...` imports and run on this package."""
+    import torch
+    import torch.nn as nn
+
+    import trainscale_b200.reference_paths as paths
+    if not paths.install():
+        pytest.skip("a real data_pipeline package is importable here")
+    from data_pipeline.trainer import (AdaFactor, AdamW, CosineScheduler, CrossEntropyLoss, DeviceManager, FocalLoss, LAMB,
+                                       TrainingArguments, clip_grad_norm_, is_main_process)
+    from data_pipeline.trainer.distributed import ColumnParallelLinear
+    from data_pipeline.trainer.distributed.expert_parallel import ExpertParallelConfig, MoELayer
+    from data_pipeline.trainer.kernels import compile_model, flash_attention
+    from data_pipeline.trainer.metrics import Accuracy, F1Score, MetricCollection
+
+    torch.manual_seed(0)
+    for make in (lambda p: AdamW(p, lr=1e-3), lambda p: LAMB(p, lr=1e-3), lambda p: AdaFactor(p, lr=1e-3)):
+        model = nn.Linear(64, 10)
+        before = model.weight.detach().clone()
+        opt = make(model.parameters())
+        model(torch.randn(4, 64)).sum().backward()
+        opt.step()
+        assert not torch.equal(before, model.weight.detach())
+    opt = torch.optim.Adam(nn.Linear(4, 4).parameters(), lr=1e-3)
+    sched = CosineScheduler(opt, num_training_steps=100, warmup_steps=10)
+    lrs = []
+    for _ in range(100):
+        sched.step()
+        lrs.append(sched.get_last_lr()[0])
+    assert max(lrs) == pytest.approx(1e-3, rel=1e-3) and lrs[-1] < lrs[50] < lrs[11]
+    logits, targets = torch.randn(32, 10), torch.randint(0, 10, (32,))
+    assert CrossEntropyLoss(label_smoothing=0.1)(logits, targets).item() > 0 and FocalLoss(gamma=2.0)(logits, targets).item() > 0
+    collection = MetricCollection([Accuracy(), F1Score(average="macro")])
+    collection.update(torch.randn(100, 5), torch.randint(0, 5, (100,)))
+    results = collection.compute()
+    assert 0.0 <= results["accuracy"] <= 1.0 and "f1" in results
+    assert ColumnParallelLinear(64, 128)(torch.randn(4, 64)).shape == (4, 128)
+    out, aux, _ = MoELayer(ExpertParallelConfig(num_experts=4, top_k=2, hidden_size=64, intermediate_size=128))(
+        hidden_states=torch.randn(2, 8, 64))
+    assert out.shape == (2, 8, 64) and aux.dim() == 0
+    q = torch.randn(2, 4, 16, 32)
+    k, v = torch.randn_like(q), torch.randn_like(q)
+    want = nn.functional.scaled_dot_product_attention(q, k, v, is_causal=True)
+    assert torch.allclose(flash_attention(q, k, v, causal=True), want, atol=1e-5)     # [batch, heads, seq, dim], as there
+    assert DeviceManager.auto_detect().device is not None and is_main_process()
+    model = nn.Linear(64, 10)
+    model(torch.randn(4, 64)).sum().backward()
+    clip_grad_norm_(model.parameters(), max_norm=1.0)
+    assert float(torch.nn.utils.clip_grad_norm_(model.parameters(), float("inf"))) <= 1.0 + 1e-4
+    assert compile_model(model, mode="default")(torch.randn(4, 64)).shape == (4, 10)
+    assert TrainingArguments(output_dir="out").output_dir == "out"

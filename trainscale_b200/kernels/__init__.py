@@ -534,6 +534,24 @@ def naive_attention(q=None, k=None, v=None, causal: bool = True, softmax_scale: 
     return _attn.attention_reference(q, k, v, causal, softmax_scale if softmax_scale is not None else scale).to(q.dtype)
 
 
+def _reference_flash_attention(query, key, value, causal: bool = False, dropout_p: float = 0.0, scale: float | None = None,
+                               sliding_window: int | None = None, return_softmax: bool = False, **options):
+    """`flash_attention` in the reference's positional order and conventions ([B, H, S, D], not causal by default);
+    what `from data_pipeline.trainer.kernels import flash_attention` gives under `reference_paths`."""
+    return flash_attention(query=query, key=key, value=value, causal=causal, dropout_p=dropout_p, scale=scale,
+                           sliding_window=sliding_window, return_softmax=return_softmax, **options)
+
+
+def _reference_naive_attention(query, key, value, causal: bool = False, dropout_p: float = 0.0, scale: float | None = None,
+                               attn_mask=None):
+    return naive_attention(query=query, key=key, value=value, causal=causal, dropout_p=dropout_p, scale=scale,
+                           attn_mask=attn_mask)
+
+
+flash_attention.__reference_form__ = _reference_flash_attention
+naive_attention.__reference_form__ = _reference_naive_attention
+
+
 @reference_kwargs({"dropout_p": (0, 0.0, None)}, Q="q", K="k", V="v")
 def scaled_dot_product_attention(q, k, v, attn_mask=None, is_causal: bool = False, scale: float | None = None):
     """[B, H, S, D] layout of torch's function; an explicit mask takes torch's path, causal / full the flash kernels."""

@@ -12,7 +12,10 @@ on `sys.path` is never shadowed (`install()` then refuses, unless `force=True`).
 
 How a name is found: the reference path selects which of our modules are searched first (`_ROUTES`: e.g. anything under
 `data_pipeline.trainer.distributed.context_parallel` looks in `parallel.cp` first), then every module of the package
-is searched.  `from data_pipeline.trainer import inference` style imports of whole sub-packages resolve to our
+is searched.  Where the POSITIONAL conventions of a function differ between the two sides (`flash_attention`: the
+reference passes [batch, heads, seq, dim] and is not causal by default), the name resolves to the variant with the
+reference's conventions (the function's `__reference_form__`), so positional calls mean what they meant there.
+`from data_pipeline.trainer import inference` style imports of whole sub-packages resolve to our
 sub-package of that name.  Any dotted path below `data_pipeline` is importable; a name this package does not have
 raises ImportError as usual.
 """
@@ -152,6 +155,7 @@ class _ReferenceModule(types.ModuleType):
                     value = importlib.import_module(f"{_OURS}.{name}")
                 except ImportError:
                     raise AttributeError(f"{self.__name__}: {_OURS} has no counterpart of {name!r}") from None
+        value = getattr(value, "__reference_form__", value)   # same op, the reference's positional order and layout
         setattr(self, name, value)
         return value
 
