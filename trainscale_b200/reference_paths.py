@@ -90,6 +90,7 @@ _ROUTES: dict[str, tuple[str, ...]] = {
     "trainer.quantization": ("quantization",),
     "trainer.export": ("export",),
     "trainer.rl": ("rl",),
+    "trainer.rl_training": ("rl",),
     "trainer.inference": ("inference", "inference.engine"),
     "trainer": ("trainer.sota_trainer", "trainer.base", "config.sota_config", "config.training_args"),
 }

@@ -386,3 +386,26 @@ def autotune_batch_and_chunks(total_rows: int, seq_len: int, hidden_dim: int, vo
     while total_rows % rows:
         rows -= 1
     return rows, chunks
+
+
+# ---- the three group-relative losses in the reference's POSITIONAL order (data_pipeline/trainer/rl_training.py:297-440):
+# what `from data_pipeline.trainer.rl_training import grpo_loss` resolves to under `reference_paths`, so that
+# `grpo_loss(policy_log_probs, ref_log_probs, advantages, mask, beta)` called by position means what it means there
+def _reference_grpo_loss(policy_log_probs, ref_log_probs, advantages, mask, beta: float = 0.04):
+    return grpo_loss(policy_log_probs=policy_log_probs, ref_log_probs=ref_log_probs, advantages=advantages, mask=mask,
+                     beta=beta)
+
+
+def _reference_drgrpo_loss(policy_log_probs, ref_log_probs, advantages, mask, beta: float = 0.04, epsilon: float = 0.1):
+    return drgrpo_loss(policy_log_probs=policy_log_probs, ref_log_probs=ref_log_probs, advantages=advantages, mask=mask,
+                       beta=beta, epsilon=epsilon)
+
+
+def _reference_dapo_loss(policy_log_probs, ref_log_probs, rewards, mask, beta: float = 0.04, temperature: float = 1.0):
+    return dapo_loss(policy_log_probs=policy_log_probs, ref_log_probs=ref_log_probs, rewards=rewards, mask=mask, beta=beta,
+                     temperature=temperature)
+
+
+grpo_loss.__reference_form__ = _reference_grpo_loss
+drgrpo_loss.__reference_form__ = _reference_drgrpo_loss
+dapo_loss.__reference_form__ = _reference_dapo_loss
