@@ -698,3 +698,44 @@ def test_tensor_parallel_layers_build_without_a_context_and_managers_take_config
     assert manager.world_size == 1
     sync = GradientSynchronizer(model=nn.Linear(2, 2), bucket_size_mb=1.0, async_sync=False)
     sync.sync_gradients()
+
+
+def test_factory_functions_take_the_reference_positional_order():
+    """Factories whose leading arguments come in another order in the reference recognise that order by type."""
+    import torch.nn as nn
+    from trainscale_b200.config.sota_config import LossConfig, OptimizerConfig
+    from trainscale_b200.data.collate import create_causal_lm_collate
+    from trainscale_b200.data.length_manager import create_content_distributor
+    from trainscale_b200.kernels import create_causal_mask, create_sliding_window_causal_mask
+    from trainscale_b200.losses import create_loss
+    from trainscale_b200.optim import create_optimizer
+    from trainscale_b200.parallel.dist_utils import DistributedState, prepare_model_for_distributed
+    from trainscale_b200.schedulers import create_scheduler
+    lin = nn.Linear(4, 4)
+    opt = create_optimizer("adamw", lin.parameters(), 1e-3, 0.1)                 # (name, params, lr, weight_decay)
+    assert type(opt).__name__ == "AdamW" and opt.param_groups[0]["lr"] == 1e-3 and opt.param_groups[0]["weight_decay"] == 0.1
+    assert type(create_optimizer(lin.parameters(), OptimizerConfig())).__name__ == "AdamW"
+    sgd = torch.optim.SGD(lin.parameters(), lr=0.1)
+    assert type(create_scheduler("cosine", sgd, 100, 10)).__name__ == "CosineScheduler"      # (name, optimizer, ...)
+    assert type(create_scheduler(sgd, "linear", 100)).__name__ == "LinearScheduler"
+    assert isinstance(create_loss(LossConfig()), nn.Module) and type(create_loss("focal")).__name__ == "FocalLoss"
+    assert create_content_distributor(128, "proportional").available_tokens <= 128          # (max_length, mode)
+    assert type(create_causal_lm_collate(0, 128, "right")).__name__ == "CollateFn"          # (pad, max_length, side)
+    assert type(create_causal_lm_collate(0, True)).__name__ == "_ShiftedCollate"
+    model, engine = prepare_model_for_distributed(lin, DistributedState(), "single")         # (model, state, strategy)
+    assert model is lin and engine is None
+    assert create_causal_mask(4, torch.float32, "cpu").shape == (4, 4)                       # (n, dtype, device)
+    assert create_sliding_window_causal_mask(4, 2, torch.float32, "cpu")[3, 0] == float("-inf")
+
+
+def test_region_functions_and_seed_take_the_reference_positional_order():
+    from trainscale_b200.parallel.dist_utils import DistributedState, set_deterministic_seed
+    from trainscale_b200.parallel.tp import (all_gather_from_sequence_parallel_region, copy_to_tensor_parallel_region,
+                                             gather_from_tensor_parallel_region)
+    x = torch.randn(4, 8)
+    assert set_deterministic_seed(1, DistributedState(), True, False) == 1 and set_deterministic_seed(1, 3) == 4
+    assert copy_to_tensor_parallel_region(x, False) is x                     # (input_, async_op) on one rank: identity
+    assert gather_from_tensor_parallel_region(x, -1) is x and gather_from_tensor_parallel_region(x, 1) is x
+    assert all_gather_from_sequence_parallel_region(x, 0) is x
+    with pytest.raises(NotImplementedError):
+        gather_from_tensor_parallel_region(x, 0)                             # another dimension is not silently ignored

@@ -123,8 +123,17 @@ class _ShiftedCollate(CollateFn):
         return out
 
 
-def create_causal_lm_collate(pad_token_id: int = 0, shift_labels: bool = False, **kw) -> CollateFn:
-    """Labels default to input_ids; with `shift_labels` they are pre-shifted (for models that do not shift)."""
+def create_causal_lm_collate(pad_token_id: int = 0, shift_labels: "bool | int | None" = False, padding_side: str | None = None,
+                             **kw) -> CollateFn:
+    """Labels default to input_ids; with `shift_labels` they are pre-shifted (for models that do not shift).
+    `create_causal_lm_collate(pad_token_id, max_length, padding_side)` is the positional form of
+    data_pipeline/data/collate.py: an int (or None) in the second place is the maximum length."""
+    if shift_labels is None or (isinstance(shift_labels, int) and not isinstance(shift_labels, bool)):
+        if shift_labels is not None:
+            kw.setdefault("max_length", shift_labels)
+        shift_labels = False
+    if padding_side is not None:
+        kw.setdefault("padding_side", padding_side)
     return _ShiftedCollate(pad_token_id, **kw) if shift_labels else CollateFn(pad_token_id, **kw)
 
 

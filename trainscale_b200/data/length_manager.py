@@ -475,7 +475,11 @@ def create_content_distributor(mode="proportional", max_length: int = 2048, colu
                                default_truncation: TruncationStrategy | str | None = None,
                                chars_per_token: float = CHARS_PER_TOKEN) -> TokenAwareContentDistributor:
     """`column_configs` ({name: ColumnContentConfig}) gives full per-column settings and wins over the short forms
-    (ratios, label columns, priorities); `default_truncation` applies to columns built from the short forms."""
+    (ratios, label columns, priorities); `default_truncation` applies to columns built from the short forms.
+    `create_content_distributor(max_length, distribution_mode, ...)` (the length first, as in
+    data_pipeline/preprocessing/length_manager.py) is taken as well."""
+    if isinstance(mode, int) and not isinstance(mode, bool):
+        mode, max_length = (max_length if not isinstance(max_length, int) else "proportional"), mode
     names = set(column_ratios or {}) | set(label_columns) | set(priorities or {})
     trunc = TruncationStrategy(default_truncation) if default_truncation is not None else TruncationStrategy.SMART
     cols = {n: ColumnContentConfig(n, priority=(priorities or {}).get(n, 0), ratio=(column_ratios or {}).get(n),

@@ -600,11 +600,15 @@ def attention_softcapping_compiled(q=None, k=None, v=None, softcap: float | None
 
 @reference_kwargs(max_seq_len="seq_len")
 def create_causal_mask(seq_len: int, device=None, dtype=torch.float32) -> torch.Tensor:
+    if isinstance(device, torch.dtype):                      # (max_seq_len, dtype, device), the reference's order
+        device, dtype = (dtype if not isinstance(dtype, torch.dtype) else None), device
     return torch.full((seq_len, seq_len), float("-inf"), device=device, dtype=dtype).triu(1)
 
 
 @reference_kwargs(max_seq_len="seq_len", window_size="window")
 def create_sliding_window_causal_mask(seq_len: int, window: int, device=None, dtype=torch.float32) -> torch.Tensor:
+    if isinstance(device, torch.dtype):                      # (max_seq_len, window_size, dtype, device)
+        device, dtype = (dtype if not isinstance(dtype, torch.dtype) else None), device
     i = torch.arange(seq_len, device=device)
     keep = (i[None, :] <= i[:, None]) & (i[:, None] - i[None, :] < window)
     return torch.zeros(seq_len, seq_len, device=device, dtype=dtype).masked_fill(~keep, float("-inf"))

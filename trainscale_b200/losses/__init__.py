@@ -729,7 +729,11 @@ class MultiTaskLoss(nn.Module):
         return sum(torch.exp(-self.log_vars[i]) * l + self.log_vars[i] for i, l in enumerate(losses))
 
 
-def create_loss(name: str = "cross_entropy", **kw) -> nn.Module:
+def create_loss(name="cross_entropy", **kw) -> nn.Module:
+    """`create_loss("focal", gamma=2.0)`, or `create_loss(config)` with a loss configuration object (anything with a
+    `type` field, e.g. the `loss` section of a SOTAConfig), as in data_pipeline/trainer/loss/__init__.py."""
+    if hasattr(name, "type") and not isinstance(name, str):
+        return create_loss_from_config(name)
     return LossRegistry.create(getattr(name, "value", name), **kw)
 
 

@@ -801,8 +801,19 @@ _OPTIMIZERS = {"adamw": AdamW, "fused_adamw": AdamW, "adam8bit": Adam8bit, "adam
                "adopt": ADOPT}
 
 
-def create_optimizer(params, config=None, name: str | None = None, **kw) -> Optimizer:
-    """From a SOTAConfig `optimizer` section (or a name + keyword arguments)."""
+def create_optimizer(params, config=None, name: str | None = None, *extra, **kw) -> Optimizer:
+    """From a SOTAConfig `optimizer` section (or a name + keyword arguments).  The reference's
+    `create_optimizer(name, params, lr, weight_decay, **kwargs)` (a string first) is taken as well
+    (data_pipeline/trainer/optimizers/sota_optimizers.py create_optimizer)."""
+    if isinstance(params, str):                               # (name, params, lr, weight_decay)
+        ref_name, params, lr = params, config, name
+        if lr is not None:
+            kw.setdefault("lr", lr)
+        if extra:
+            kw.setdefault("weight_decay", extra[0])
+        config, name, extra = None, ref_name, extra[1:]
+    if extra:
+        raise TypeError("create_optimizer() got too many positional arguments")
     params = [p for p in params if p.requires_grad] if not isinstance(params, list) or (params and torch.is_tensor(params[0])) else params
     if config is not None:
         name = name or getattr(config.type, "value", config.type)

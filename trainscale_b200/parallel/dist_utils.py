@@ -374,10 +374,16 @@ def dist_all_gather(t: torch.Tensor, group=None) -> list[torch.Tensor]:
     return out
 
 
-def set_deterministic_seed(seed: int, rank: int = 0, fully_deterministic: bool = False, *, state=None,
-                           per_rank_offset: bool = True) -> int:
+def set_deterministic_seed(seed: int, rank: "int | DistributedState" = 0, fully_deterministic: bool = False, *more,
+                           state=None, per_rank_offset: bool = True) -> int:
     """Seeds python / numpy / torch with seed + rank and returns that number.  `state` (a DistributedState) supplies
-    the rank; `per_rank_offset=False` gives every rank the same seed."""
+    the rank; `per_rank_offset=False` gives every rank the same seed.  The positional form `(seed, state,
+    per_rank_offset, fully_deterministic)` of data_pipeline/trainer/distributed/sota_utils.py is taken as well."""
+    if isinstance(rank, DistributedState):                    # (seed, state, per_rank_offset, fully_deterministic)
+        state, per_rank_offset, rank = rank, bool(fully_deterministic), 0
+        fully_deterministic = bool(more[0]) if more else False
+    elif more:
+        raise TypeError("set_deterministic_seed() got too many positional arguments")
     if state is not None:
         rank = int(getattr(state, "rank", rank))
     s = seed + (rank if per_rank_offset else 0)
@@ -970,7 +976,12 @@ def sync_gradients(model, group=None, average: bool = True, bucket_mb: float = 2
 
 def prepare_model_for_distributed(model, strategy: str = "ddp", device=None, **engine_kwargs):
     """Moves the model to this rank's device and builds the engine for `strategy` (ddp | fsdp | zero2 | zero3 |
-    single).  Returns (model, engine); the engine is None for `single`."""
+    single).  Returns (model, engine); the engine is None for `single`.  `prepare_model_for_distributed(model, state,
+    strategy)` with a `DistributedState` second (data_pipeline/trainer/distributed/sota_utils.py) is taken as well: the
+    state supplies the device."""
+    if isinstance(strategy, DistributedState):
+        state, strategy = strategy, (device if isinstance(device, str) else "ddp")
+        device = getattr(state, "device", None)
     dev = torch.device(device) if device is not None else DeviceManager().set_device()
     model.to(dev)
     s = strategy.lower()

@@ -179,6 +179,14 @@ def _region(fn_cls, dim):
     # sequence-parallel ones; the reference's `dim` argument is accepted when it names that dimension
     @reference_kwargs({"dim": (dim, None), "async_op": (False, None)}, input_="x")
     def region(x, tp=None):
+        if isinstance(tp, (bool, int)):
+            # the reference's second positional argument: `dim` (must name this function's dimension) or `async_op`
+            if isinstance(tp, bool):
+                if tp:
+                    raise NotImplementedError("async_op=True is not supported by the region functions")
+            elif dim is None or tp not in (dim, dim % max(x.dim(), 1), dim - x.dim() if dim >= 0 else dim + x.dim()):
+                raise NotImplementedError(f"this region function works on dimension {dim}, not {tp}")
+            tp = None
         tp = tp if tp is not None else _default_tp()
         return fn_cls.apply(x, tp) if tp.active else x
     return region

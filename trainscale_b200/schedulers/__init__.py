@@ -252,7 +252,11 @@ _REGISTRY: dict[str, Callable] = {
 
 def create_scheduler(optimizer, scheduler_type: str = "cosine", num_training_steps: int = 1000, warmup_steps: int = 0,
                      warmup_ratio: float = 0.0, min_lr_ratio: float = 0.0, **kw) -> BaseScheduler:
-    """warm-up = warmup_steps, else int(warmup_ratio * N) (data_pipeline/trainer/trainers/sota_trainer.py:1814-1818)."""
+    """warm-up = warmup_steps, else int(warmup_ratio * N) (data_pipeline/trainer/trainers/sota_trainer.py:1814-1818).
+    `create_scheduler(name, optimizer, ...)`, the order of data_pipeline/trainer/schedulers/sota_schedulers.py, is taken
+    as well (a string or scheduler-type enum first)."""
+    if isinstance(optimizer, str) or hasattr(optimizer, "value"):
+        optimizer, scheduler_type = scheduler_type, optimizer
     name = getattr(scheduler_type, "value", scheduler_type).lower()
     if name not in _REGISTRY:
         raise ValueError(f"unknown scheduler {name!r}; choose from {sorted(_REGISTRY)}")

@@ -46,6 +46,7 @@ def reference_kwargs(_accept: dict | tuple | None = None, **renames: str):
         extra = [inspect.Parameter(n, inspect.Parameter.KEYWORD_ONLY, default=None)
                  for n in list(renames) + list(accept) if n not in sig.parameters]
         wrapper.__signature__ = sig.replace(parameters=head + extra + tail)
+        wrapper.__reference_renames__ = {**getattr(fn, "__reference_renames__", {}), **renames}
         return wrapper
 
     return deco
