@@ -739,3 +739,17 @@ def test_region_functions_and_seed_take_the_reference_positional_order():
     assert all_gather_from_sequence_parallel_region(x, 0) is x
     with pytest.raises(NotImplementedError):
         gather_from_tensor_parallel_region(x, 0)                             # another dimension is not silently ignored
+
+
+def test_estimators_take_the_reference_positional_order():
+    import torch.nn as nn
+    from trainscale_b200.parallel.cp import estimate_memory_per_gpu
+    from trainscale_b200.parallel.pipeline import balance_stages_by_memory
+    from trainscale_b200.quantization import estimate_memory_usage
+    assert estimate_memory_usage(7.0, None)["model_gb"] == pytest.approx(7e9 * 2 / 2 ** 30, abs=0.01)   # no config: 16 bit
+    chain = nn.Sequential(nn.Linear(8, 8), nn.Linear(8, 8))
+    assert balance_stages_by_memory(chain, 2, (2, 8)) == [range(0, 1), range(1, 2)]                  # (model, n, input_shape)
+    by_position = estimate_memory_per_gpu(1, 8192, 4096, 32, 2)                                       # (b, s, h, heads, cp)
+    assert isinstance(by_position, int)
+    assert by_position == estimate_memory_per_gpu(batch_size=1, seq_len=8192, hidden_dim=4096, num_heads=32, cp_degree=2)
+    assert estimate_memory_per_gpu(8192, 2, 4096, 1, 8, 128)["tokens_per_gpu"] == 4096                # the native form

@@ -489,6 +489,9 @@ def estimate_memory_per_gpu(seq_len: int = None, cp: int = None, hidden: int = N
     """Per-GPU activation and ring-buffer sizes of a context-parallel layer stack (a dict, in GiB).  The reference's
     keyword form (`batch_size, seq_len, hidden_dim, num_heads, cp_degree, precision`) describes ONE layer without
     recomputation and returns its bytes as an int (data_pipeline/trainer/distributed/context_parallel.py:2107)."""
+    if head_dim is None and n_kv_heads is not None and cp_degree is None and hidden_dim is None:
+        # five positional sizes and no head dimension: (batch_size, seq_len, hidden_dim, num_heads, cp_degree)
+        batch_size, seq_len, hidden_dim, num_heads, cp_degree = seq_len, cp, hidden, n_layers, n_kv_heads
     if cp_degree is not None or hidden_dim is not None:
         eb = {"fp32": 4, "fp16": 2, "bf16": 2, "fp8": 1}[precision or "bf16"]
         d = estimate_memory_per_gpu(seq_len, cp_degree or 1, hidden_dim, 1, num_heads, hidden_dim // num_heads, eb, False)

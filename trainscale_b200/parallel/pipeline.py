@@ -1152,6 +1152,8 @@ def balance_stages_by_memory(layers: Sequence[nn.Module], num_stages: int, batch
     if isinstance(layers, nn.Module) and not isinstance(layers, (nn.Sequential, nn.ModuleList)):
         layers = list(layers.children())
     layers = list(layers)
+    if isinstance(batch_size, (tuple, list, torch.Size)):        # (model, num_stages, input_shape), the reference's order
+        input_shape, batch_size = batch_size, 1
     if input_shape is not None:
         batch_size, seq_len = (tuple(input_shape) + (1, 1))[:2]
     base = [estimate_stage_memory(l, batch_size, seq_len) for l in layers]

@@ -245,9 +245,10 @@ def estimate_memory_usage(n_params: float = None, weight_bits: int = 16, trainab
     `QuantizationConfig`, batch size, sequence length - by name, or positionally when the second argument is a config)
     returns its keys: model_gb, lora_gb (2 % of the base), activation_gb, gradient_gb, total_gb
     (data_pipeline/trainer/quantization.py:264-297)."""
-    if model_size_billion is not None or isinstance(weight_bits, QuantizationConfig):
+    if model_size_billion is not None or isinstance(weight_bits, QuantizationConfig) or weight_bits is None:
         if model_size_billion is None:
             model_size_billion, config = n_params, weight_bits
+        config = config if config is not None else QuantizationConfig()       # no configuration: 16-bit weights
         bits = 4 if config.load_in_4bit else 8 if (config.load_in_8bit or getattr(config, "load_in_fp8", False)) else 16
         quantized = bits < 16
         model_gb = model_size_billion * 1e9 * bits / 8 / 2 ** 30
