@@ -476,3 +476,27 @@ def test_a_script_in_the_reference_style_runs_through_the_reference_paths():
     assert float(torch.nn.utils.clip_grad_norm_(model.parameters(), float("inf"))) <= 1.0 + 1e-4
     assert compile_model(model, mode="default")(torch.randn(4, 64)).shape == (4, 10)
     assert TrainingArguments(output_dir="out").output_dir == "out"
+
+
+def test_soft_capped_attention_by_position_through_the_reference_paths():
+    """`slow_attention_softcapping(Q, K, V, causal_mask, config, bsz, q_len)` and its two siblings, called by position
+    with [batch, heads, seq, dim] tensors as the reference's callers do, against the formula written out."""
+    import torch
+
+    import trainscale_b200.reference_paths as paths
+    if not paths.install():
+        pytest.skip("a real data_pipeline package is importable here")
+    from data_pipeline.trainer.kernels.flex_attention import (FlexAttentionConfig, attention_softcapping_compiled,
+                                                              inference_attention_single_token,
+                                                              slow_attention_softcapping)
+    torch.manual_seed(0)
+    cfg = FlexAttentionConfig(num_attention_heads=4, num_key_value_heads=2, head_dim=8, query_pre_attn_scalar=8,
+                              attn_logit_softcapping=30.0)
+    Q, K, V = torch.randn(1, 4, 6, 8), torch.randn(1, 2, 6, 8), torch.randn(1, 2, 6, 8)
+    mask = torch.zeros(6, 6).masked_fill(torch.ones(6, 6, dtype=torch.bool).triu(1), float("-inf"))
+    scores = (Q @ K.repeat_interleave(2, 1).transpose(-1, -2)) * 8 ** -0.5
+    want = (torch.softmax(30 * torch.tanh(scores / 30) + mask, -1) @ V.repeat_interleave(2, 1)).transpose(1, 2).reshape(1, 6, 32)
+    assert torch.allclose(slow_attention_softcapping(Q, K, V, mask, cfg, 1, 6), want, atol=1e-5)
+    assert torch.allclose(attention_softcapping_compiled(Q, K, V, mask, 8.0, 30.0, 4, 2, 8), want, atol=1e-5)
+    last = inference_attention_single_token(Q[:, :, -1:], K, V, cfg)                 # the last query sees every key
+    assert torch.allclose(last, want[:, -1:], atol=1e-5)

@@ -642,6 +642,27 @@ def inference_attention_single_token(q=None, k_cache=None, v_cache=None, seq_len
     return o.reshape(B, Hq, D).to(q.dtype)
 
 
+# ---- the same three functions in the reference's POSITIONAL order ([B, H, S, D] tensors, mask object, config); served
+# under the reference's import path (data_pipeline/trainer/kernels/flex_attention.py:731, 1032, 1397)
+def _reference_slow_attention_softcapping(Q, K, V, causal_mask, config, bsz=None, q_len=None):
+    return slow_attention_softcapping(Q=Q, K=K, V=V, causal_mask=causal_mask, config=config, bsz=bsz, q_len=q_len)
+
+
+def _reference_attention_softcapping_compiled(Q, K, V, causal_mask, query_scalar, softcap, num_heads=None,
+                                              num_kv_heads=None, head_dim=None):
+    return attention_softcapping_compiled(Q=Q, K=K, V=V, causal_mask=causal_mask, query_scalar=query_scalar,
+                                          softcap=softcap, num_heads=num_heads, num_kv_heads=num_kv_heads, head_dim=head_dim)
+
+
+def _reference_inference_attention_single_token(Q, K, V, config):
+    return inference_attention_single_token(Q=Q, K=K, V=V, config=config)
+
+
+slow_attention_softcapping.__reference_form__ = _reference_slow_attention_softcapping
+attention_softcapping_compiled.__reference_form__ = _reference_attention_softcapping_compiled
+inference_attention_single_token.__reference_form__ = _reference_inference_attention_single_token
+
+
 class FlashAttention(nn.Module):
     """`FlashAttention(config)(q, k, v)`: [B, S, H, D] tensors.  The reference's `FlashAttention(head_dim, num_heads,
     num_kv_heads, causal=False, dropout, sliding_window)(query, key, value, attn_mask)` takes and returns [B, H, S, D]
