@@ -753,3 +753,15 @@ def test_estimators_take_the_reference_positional_order():
     assert isinstance(by_position, int)
     assert by_position == estimate_memory_per_gpu(batch_size=1, seq_len=8192, hidden_dim=4096, num_heads=32, cp_degree=2)
     assert estimate_memory_per_gpu(8192, 2, 4096, 1, 8, 128)["tokens_per_gpu"] == 4096                # the native form
+
+
+def test_pack_sequences_takes_the_reference_positional_columns():
+    from trainscale_b200.data.packing import pack_sequences
+    ids = torch.tensor([[5, 6, 0, 0], [7, 0, 0, 0]])
+    mask = (ids != 0).long()
+    by_position = pack_sequences(ids, mask, ids.clone(), 8, 0)               # (input_ids, attention_mask, labels, max, pad)
+    by_name = pack_sequences(input_ids=ids, attention_mask=mask, labels=ids.clone(), max_length=8, pad_token_id=0)
+    assert by_position[0]["input_ids"].tolist() == [5, 6, 7, 0, 0, 0, 0, 0]
+    assert all(torch.equal(by_position[0][k], by_name[0][k]) for k in by_name[0] if torch.is_tensor(by_name[0][k]))
+    assert pack_sequences([{"input_ids": torch.tensor([1, 2])}], 4)[0]["input_ids"].tolist() == [1, 2, 0, 0]   # native form
+    assert pack_sequences([torch.tensor([1, 2]), torch.tensor([3])], None, None, 4)[0]["input_ids"].tolist() == [1, 2, 3, 0]

@@ -33,10 +33,19 @@ def first_fit_decreasing(lengths: Sequence[int], max_length: int) -> list[list[i
 
 @reference_kwargs(max_seq_len="max_length", label_pad_id="label_pad")
 def pack_sequences(sequences: Sequence[dict] | None = None, max_length: int = 2048, pad_token_id: int = 0,
-                   label_pad: int = -100, *, input_ids=None, attention_mask=None, labels=None) -> list[dict]:
+                   label_pad: int = -100, *more, input_ids=None, attention_mask=None, labels=None) -> list[dict]:
     """Each input dict holds 1-D `input_ids` (and optionally `labels`); returns packed dicts of tensors.  The
     reference's column form is taken too: `input_ids` / `attention_mask` / `labels` as lists (or padded [N, L] tensors)
     of the N sequences, the mask giving each row's real length."""
+    if not isinstance(max_length, int) or more:
+        # the reference's positional order: (input_ids, attention_mask, labels, max_seq_len, pad_token_id, label_pad_id)
+        given = (max_length, pad_token_id, label_pad) + tuple(more)
+        input_ids, attention_mask, labels = sequences, given[0], (given[1] if not isinstance(given[1], int) else None)
+        tail = [g for g in given[2:] if isinstance(g, int)]
+        max_length = tail[0] if tail else 2048
+        pad_token_id = tail[1] if len(tail) > 1 else 0
+        label_pad = tail[2] if len(tail) > 2 else -100
+        sequences = None
     if sequences is None or input_ids is not None or (torch.is_tensor(sequences) and sequences.dim() == 2):
         ids = input_ids if input_ids is not None else sequences
         rows = []
