@@ -230,6 +230,7 @@ def test_the_reference_example_configurations_load():
     (`config_type` / `training_mode` at the top) as `SOTAConfig`, data-pipeline configurations (`type`, `version`,
     `dataset`) through `load_config`, and the flat training-arguments file through `load_training_config`."""
     import glob
+    import os
     from pathlib import Path
 
     import yaml as _yaml
@@ -237,7 +238,10 @@ def test_the_reference_example_configurations_load():
     from trainscale_b200.config.sota_config import SOTAConfig
     from trainscale_b200.config.training_args import load_training_config
 
-    root = Path("/root/reference/data_pipeline/examples")
+    here = Path(__file__).resolve().parents[1]
+    roots = [here / "baseline" / "_ref" / "data_pipeline" / "examples",
+             Path(os.environ.get("TRAINSCALE_REFERENCE", "/nonexistent")) / "data_pipeline" / "examples"]
+    root = next((r for r in roots if r.is_dir()), roots[0])
     files = sorted(glob.glob(str(root / "**" / "*.yaml"), recursive=True))
     if not files:
         pytest.skip("the reference's examples are not on this machine")
